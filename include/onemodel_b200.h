@@ -1,0 +1,403 @@
+/*
+ * onemodel_b200.h - C ABI of libonemodel_b200.so: the B200 (sm_100a) training backend for the autograd
+ * hot path of RecursiveAI.OneModel.Training (forward ops that fill the tape's saved slots, every per-op
+ * backward function, the fused optimizer step, gradient clipping, data-parallel gradient exchange).
+ *
+ * Conventions
+ *  - Every function returns an om_status (0 = OM_OK). The message of the last failure on a context is read
+ *    with om_last_error. No C++ exception crosses this boundary.
+ *  - All tensor pointers are DEVICE pointers unless a parameter name ends in _host. Tensors are float32,
+ *    row-major and contiguous unless strides are passed explicitly. The caller owns all memory it passes;
+ *    the library keeps no pointer past a call except registered data-parallel buckets.
+ *  - One om_ctx per device; calls on one context are serialised by the caller (the reference engine is
+ *    single-threaded: src/OneModel/Tensors/Autograd/Engine.cs:112-120). Work is asynchronous on the
+ *    context's stream until om_sync or a device-to-host copy.
+ *  - Results never depend on launch geometry chosen at run time: every reduction has a fixed partition and
+ *    a fixed combine order and no kernel uses floating-point atomics (the reference's rule that a result
+ *    must not depend on the thread count, src/OneModel/Tensors/TensorKernels.cs:57-61).
+ *  - The reference has no FFI for this path (tests/OneModel.Tests/PackageGuardTests.cs:54-66 bans P/Invoke
+ *    under src/). Each entry point names the managed function whose body it replaces.
+ */
+#ifndef ONEMODEL_B200_H
+#define ONEMODEL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+typedef struct om_ctx om_ctx;
+
+typedef enum om_status {
+  OM_OK = 0,
+  OM_ERR_SHAPE = 1,       /* TensorShapeException in the reference */
+  OM_ERR_INDEX = 2,       /* ArgumentOutOfRangeException: embedding id / NLL target / CTC label out of range
+                             (src/OneModel/Tensors/Ops.Layers.cs:590-600,667-676) */
+  OM_ERR_OOM = 3,
+  OM_ERR_CUDA = 4,
+  OM_ERR_NCCL = 5,
+  OM_ERR_TIMEOUT = 6,     /* a bounded device-side or host-side wait ran out */
+  OM_ERR_UNSUPPORTED = 7,
+  OM_ERR_ARG = 8
+} om_status;
+
+/* Context flags. OM_TF32: matrix products run on the tcgen05 tensor pipe with TF32 operands and fp32
+ * accumulation (TensorCompute.Mode = Fast); without it they run on an fp32 FMA kernel that keeps the
+ * reference's one-accumulator, increasing-k order (TensorCompute.Mode = Exact tier of tolerance,
+ * src/OneModel/Tensors/Autograd/TensorCompute.cs:22-78). OM_BF16_OPERANDS: operands of matrix products are
+ * rounded to bfloat16 (round to nearest even) and multiplied on the tensor pipe with fp32 accumulation.
+ * OM_CHECKED: index operands are range-checked on the device and buffers carry canary words
+ * (the reference's Checked build, docs/tensors.md:108-110). */
+#define OM_TF32 1u
+#define OM_BF16_OPERANDS 2u
+#define OM_CHECKED 4u
+
+typedef enum om_dtype { OM_F32 = 0, OM_I32 = 1, OM_I64 = 2 } om_dtype;
+
+/* ---- context, memory, streams ---------------------------------------------------------------------- */
+
+int32_t om_version(void);
+int32_t om_ctx_create(int32_t device, uint32_t flags, om_ctx** out);
+int32_t om_ctx_destroy(om_ctx* ctx);
+int32_t om_ctx_set_flags(om_ctx* ctx, uint32_t flags);
+int32_t om_ctx_get_flags(om_ctx* ctx, uint32_t* flags);
+/* Copies the last error message (NUL terminated, truncated to n) of this context; ctx may be NULL for
+ * errors of om_ctx_create. */
+int32_t om_last_error(om_ctx* ctx, char* buf, size_t n);
+/* The CUDA stream (cudaStream_t) all work of this context is ordered on. */
+int32_t om_ctx_stream(om_ctx* ctx, void** stream);
+
+/* Pooled device memory with the reference pool's size classes b*{1.25,1.5,1.75,2}
+ * (replaces BufferPool.Rent / release, src/OneModel/Tensors/Memory/BufferPool.cs:67; docs/tensors.md:93-118).
+ * Freed blocks are reused in stream order; om_pool_trim returns cached blocks to the driver. */
+int32_t om_alloc(om_ctx* ctx, size_t bytes, int32_t zero, void** dptr);
+int32_t om_free(om_ctx* ctx, void* dptr);
+int32_t om_pool_trim(om_ctx* ctx);
+int32_t om_pool_stats(om_ctx* ctx, uint64_t* bytes_in_use, uint64_t* bytes_cached, uint64_t* driver_allocs);
+int32_t om_memcpy_h2d(om_ctx* ctx, void* dst, const void* src_host, size_t bytes);
+int32_t om_memcpy_d2h(om_ctx* ctx, void* dst_host, const void* src, size_t bytes); /* synchronises */
+int32_t om_memcpy_d2d(om_ctx* ctx, void* dst, const void* src, size_t bytes);
+int32_t om_memset(om_ctx* ctx, void* dst, int32_t byte, size_t bytes);
+int32_t om_host_alloc_pinned(om_ctx* ctx, size_t bytes, void** hptr);
+int32_t om_host_free_pinned(om_ctx* ctx, void* hptr);
+/* Waits for the stream and returns the device status word: OM_ERR_INDEX if a checked kernel saw an index
+ * out of range, OM_ERR_TIMEOUT if a bounded device wait expired. The word is cleared. */
+int32_t om_sync(om_ctx* ctx);
+
+/* Whole-step CUDA graph capture of the calls made between begin and end on this context. */
+int32_t om_graph_begin(om_ctx* ctx);
+int32_t om_graph_end(om_ctx* ctx, void** graph_exec);
+int32_t om_graph_launch(om_ctx* ctx, void* graph_exec);
+int32_t om_graph_destroy(om_ctx* ctx, void* graph_exec);
+
+/* Per-entry-point device timers (CUDA events on the context's stream around every call).
+ * om_profile_read writes up to cap rows; names are the entry point names. */
+typedef struct om_profile_row {
+  char name[48];
+  uint64_t calls;
+  double ms;
+  double flops; /* algorithmic flops reported by the entry point (0 for bandwidth-bound kernels) */
+  double bytes; /* algorithmic bytes reported by the entry point */
+} om_profile_row;
+int32_t om_profile_enable(om_ctx* ctx, int32_t on);
+int32_t om_profile_reset(om_ctx* ctx);
+int32_t om_profile_read(om_ctx* ctx, om_profile_row* rows, int32_t cap, int32_t* n);
+
+/* ---- dense products --------------------------------------------------------------------------------- */
+
+/* C[m,n] = op(A)[m,k] * op(B)[k,n] (+ C when accumulate != 0), row-major, leading dimensions in elements.
+ * op(X) = X^T when transX != 0 (X is then stored [k,m] resp. [n,k]).
+ * Replaces Dense.Gemm (src/OneModel/Tensors/Autograd/Dense.cs:12-48) under Ops.MatMul (Ops.cs:117-144) and
+ * both products of the MatMul backward (BackwardOps.cs:69-82): dA = g*B^T, dB = A^T*g with no transposed copy.
+ * Each output element has one accumulator summed in increasing k (fp32 path), or a fixed split of k into
+ * equal parts combined in increasing order (tensor-pipe path). */
+int32_t om_matmul(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m, int32_t n, int32_t k,
+                  const float* A, int32_t lda, const float* B, int32_t ldb, float* C, int32_t ldc,
+                  int32_t accumulate);
+/* Same, over `batch` matrices at the given element strides (0 broadcasts an operand).
+ * Replaces Ops.MatMulBatched and BatchMatMul backward (Ops.GraphOps.cs:24; BackwardGraphOps.cs:10-66). */
+int32_t om_matmul_batched(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m, int32_t n, int32_t k,
+                          const float* A, int32_t lda, int64_t strideA, const float* B, int32_t ldb,
+                          int64_t strideB, float* C, int32_t ldc, int64_t strideC, int32_t batch,
+                          int32_t accumulate);
+/* y[rows,out] = x[rows,in] * W[out,in]^T + bias[out] (bias may be NULL), optionally followed by an
+ * activation (om_unary_op, OM_UNARY_NONE for none) whose pre-activation is written to pre (may be NULL).
+ * Fuses the Reshape/MatMul/Add chain of Ops.Linear (Ops.Layers.cs:715-733). */
+int32_t om_linear_fwd(om_ctx* ctx, const float* x, const float* W, const float* bias, int32_t rows,
+                      int32_t in_features, int32_t out_features, float* y);
+/* Backward of om_linear_fwd: dx = g*W (NULL to skip), dW = g^T*x (NULL to skip), dbias = column sums of g
+ * (NULL to skip). accumulate_w != 0 adds into dW/dbias (Engine.AddInto, Engine.cs:330-344).
+ * Replaces the Reshape/Add/MatMul/Permute records of one Linear (call stack: BackwardOps.cs:69-82,107-122,156-194). */
+int32_t om_linear_bwd(om_ctx* ctx, const float* g, const float* x, const float* W, int32_t rows,
+                      int32_t in_features, int32_t out_features, float* dx, float* dW, float* dbias,
+                      int32_t accumulate_w);
+
+/* ---- elementwise ------------------------------------------------------------------------------------ */
+
+typedef enum om_binary_op { OM_ADD = 0, OM_SUB = 1, OM_MUL = 2, OM_DIV = 3 } om_binary_op;
+typedef enum om_unary_op {
+  OM_UNARY_NONE = 0, OM_RELU = 1, OM_GELU_ERF = 2, OM_GELU_TANH = 3, OM_SIGMOID = 4, OM_TANH = 5,
+  OM_NEG = 6, OM_EXP = 7, OM_SQRT = 8, OM_ERF = 9
+} om_unary_op;
+
+/* out = a (op) b over a broadcast shape of rank <= 8; strides in elements, 0 on broadcast axes; out is
+ * contiguous. Replaces ITensorKernels.Binary (src/OneModel/Tensors/TensorKernels.cs:62-98) under
+ * Ops.Add/Sub/Mul/Div (Ops.cs:15-96). */
+int32_t om_binary(om_ctx* ctx, int32_t op, int32_t rank, const int32_t* shape, const float* a,
+                  const int64_t* a_strides, const float* b, const int64_t* b_strides, float* out);
+/* y = f(x) over n contiguous elements. Replaces ITensorKernels.Unary under Ops.Relu/Neg (Ops.cs:98-115),
+ * Ops.Gelu/Sigmoid/Tanh (Ops.Nn.cs:86-160), Ops.Erf/Exp/Sqrt (Ops.GraphOps.cs:100-200). */
+int32_t om_unary(om_ctx* ctx, int32_t op, const float* x, float* y, int64_t n);
+/* dx = g * f'(saved). saved is the OUTPUT for RELU, SIGMOID, TANH, EXP, SQRT and the INPUT for GELU_*, ERF,
+ * exactly as the reference's records save them. Replaces ReluGradBin, SigmoidGradBin, TanhGradBin,
+ * GeluGradBin (src/OneModel/Kernels/TrainElementwise.cs:42-85; BackwardOps.cs:66-68; BackwardNn.cs:12-21)
+ * and the Erf/Exp/Sqrt cases of BackwardGraphOps.cs:10-139. */
+int32_t om_unary_bwd(om_ctx* ctx, int32_t op, const float* g, const float* saved, float* dx, int64_t n);
+/* dst[i] += src[i] in element order. Replaces Engine.AddInto (Engine.cs:330-344). */
+int32_t om_add_into(om_ctx* ctx, float* dst, const float* src, int64_t n);
+/* y[i] = x[i] * s (Mean backward division is x * (1/n) only when exact; this entry divides: y = x / d). */
+int32_t om_div_scalar(om_ctx* ctx, const float* x, float d, float* y, int64_t n);
+int32_t om_fill(om_ctx* ctx, float* dst, float value, int64_t n);
+/* Zero-fills count buffers in one launch. Replaces Optimizer.ZeroGrad -> Backprop.ZeroGrad
+ * (src/OneModel.Training/Optimizers.cs:222-228; Engine.cs:77-91). ptrs_host/len_host are host arrays. */
+int32_t om_zero(om_ctx* ctx, int32_t count, float* const* ptrs_host, const int64_t* len_host);
+
+/* ---- data movement and broadcast sums ---------------------------------------------------------------- */
+
+/* dst (strided) = src (strided) over `shape`, rank <= 8, strides in elements (negative allowed for Flip).
+ * Covers Permute/Slice/Select/Expand/Flip/Concat clones and the slice-write of Slice/Select backward
+ * (BackwardOps.cs:86-140; BackwardNn.cs:112-128; Tensor.Views.cs:11-21). */
+int32_t om_strided_copy(om_ctx* ctx, int32_t rank, const int32_t* shape, const float* src,
+                        const int64_t* src_strides, float* dst, const int64_t* dst_strides);
+/* out[target] = sum of g over broadcast axes; g contiguous of `shape`; t_strides are the target's element
+ * strides per axis of g, 0 where the target was broadcast. Sums in increasing element order with a double
+ * accumulator per output (fixed two-level order). Replaces BackwardOps.SumTo (BackwardOps.cs:201-269). */
+int32_t om_sum_to(om_ctx* ctx, int32_t rank, const int32_t* shape, const float* g,
+                  const int64_t* t_strides, float* out, int64_t out_len);
+/* out[cols] = column sums of g[rows,cols] (bias gradient; the common case of SumTo), double accumulation. */
+int32_t om_colsum(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, float* out, int32_t accumulate);
+/* Sum/Mean forward over one axis or all (axis < 0) of a contiguous tensor viewed as [outer, n, inner]
+ * (Ops.Nn.cs:162-231), double accumulation in increasing order. */
+int32_t om_reduce_fwd(om_ctx* ctx, const float* x, int64_t outer, int64_t n, int64_t inner, int32_t mean,
+                      float* y);
+/* Sum/Mean backward: dx[outer,n,inner] = g[outer,inner] (/ n when mean). Replaces ReduceBackward
+ * (BackwardNn.cs:145-168). */
+int32_t om_reduce_bwd(om_ctx* ctx, const float* g, int64_t outer, int64_t n, int64_t inner, int32_t mean,
+                      float* dx);
+
+/* ---- softmax family and losses ------------------------------------------------------------------------ */
+
+/* Rows of `cols` elements. Forward: Ops.Softmax / Ops.LogSoftmax (Ops.Layers.cs:17-96): row max subtracted,
+ * exp summed in double, lse = max + log(sum). Backward: BackwardNn.cs:26-80 (row sums in double). */
+int32_t om_softmax_fwd(om_ctx* ctx, const float* x, int32_t rows, int32_t cols, float* y);
+int32_t om_softmax_bwd(om_ctx* ctx, const float* g, const float* y, int32_t rows, int32_t cols, float* dx);
+int32_t om_logsoftmax_fwd(om_ctx* ctx, const float* x, int32_t rows, int32_t cols, float* y);
+int32_t om_logsoftmax_bwd(om_ctx* ctx, const float* g, const float* y, int32_t rows, int32_t cols, float* dx);
+/* loss = -(sum or mean over counted rows) logp[n, target[n]]; rows whose target == ignore_index are skipped.
+ * count (device int32, may be NULL) receives the number of counted rows. Out-of-range targets set the
+ * device status word to OM_ERR_INDEX. Replaces Ops.NllLoss (Ops.Layers.cs:644-699). */
+int32_t om_nll_fwd(om_ctx* ctx, const float* logp, const void* targets, int32_t target_dtype, int32_t rows,
+                   int32_t cols, int32_t mean, int64_t ignore_index, float* loss, int32_t* count);
+/* dx[rows,cols] = 0 except -g/count (mean) or -g at [n, target[n]]; g is the device scalar gradient of the
+ * loss. Replaces NllBackward (BackwardNn.cs:602-634). */
+int32_t om_nll_bwd(om_ctx* ctx, const float* g, const void* targets, int32_t target_dtype, int32_t rows,
+                   int32_t cols, int32_t mean, int64_t ignore_index, float* dx);
+/* Fused LogSoftmax + NllLoss of Losses.CrossEntropy (src/OneModel.Training/Losses.cs:21-32): forward writes
+ * logp (may be NULL when only the loss is wanted... it is needed by the backward) and the loss; backward
+ * writes dlogits = g*(exp(logp) * s - onehot)/count directly, the composition of NllBackward and the
+ * LogSoftmax backward above. `denominator` > 0 overrides the counted-row divisor (data-parallel shards
+ * divide by the global count). */
+int32_t om_cross_entropy_fwd(om_ctx* ctx, const float* logits, const void* targets, int32_t target_dtype,
+                             int32_t rows, int32_t cols, int32_t mean, int64_t ignore_index,
+                             float denominator, float* logp, float* loss, int32_t* count);
+int32_t om_cross_entropy_bwd(om_ctx* ctx, const float* g, const float* logp, const void* targets,
+                             int32_t target_dtype, int32_t rows, int32_t cols, int32_t mean,
+                             int64_t ignore_index, float denominator, float* dlogits);
+
+/* ---- normalisation ------------------------------------------------------------------------------------ */
+
+/* y = (x-mean)*inv*gamma + beta per row; mean[rows], inv[rows] (may be NULL) receive the saved statistics.
+ * Replaces Ops.LayerNorm -> NormKernels.Rows (Ops.Layers.cs:109-145; Kernels/Exact/NormKernels.cs:39-128). */
+int32_t om_layernorm_fwd(om_ctx* ctx, const float* x, const float* gamma, const float* beta, int32_t rows,
+                         int32_t cols, float eps, float* y, float* mean, float* inv);
+/* dx, dgamma, dbeta (each may be NULL). Row sums and the column accumulators of dgamma/dbeta are double,
+ * combined in a fixed order. Replaces LayerNormBackward (BackwardNn.cs:170-242). */
+int32_t om_layernorm_bwd(om_ctx* ctx, const float* g, const float* x, const float* gamma, const float* mean,
+                         const float* inv, int32_t rows, int32_t cols, float* dx, float* dgamma,
+                         float* dbeta, int32_t accumulate_params);
+/* NCHW batch normalisation. Training: batch statistics in double, running stats updated in place with the
+ * unbiased variance (Ops.Layers.cs:158-277). mean[C], inv[C] receive the saved statistics. */
+int32_t om_batchnorm_fwd(om_ctx* ctx, const float* x, const float* gamma, const float* beta,
+                         float* running_mean, float* running_var, int32_t n, int32_t c, int32_t plane,
+                         int32_t training, float momentum, float eps, float* y, float* mean, float* inv);
+/* Replaces BatchNormBackward (BackwardNn.cs:244-307). */
+int32_t om_batchnorm_bwd(om_ctx* ctx, const float* g, const float* x, const float* gamma, const float* mean,
+                         const float* inv, int32_t n, int32_t c, int32_t plane, int32_t training, float* dx,
+                         float* dgamma, float* dbeta, int32_t accumulate_params);
+
+/* ---- embedding ------------------------------------------------------------------------------------------ */
+
+/* out[i,:] = table[ids[i],:]. Ids outside [0,V) set OM_ERR_INDEX. Replaces Ops.Embedding (Ops.Layers.cs:549-628). */
+int32_t om_embedding_fwd(om_ctx* ctx, const float* table, int32_t v, int32_t dim, const void* ids,
+                         int32_t id_dtype, int64_t n, float* out);
+/* dtable[V,dim]: rows of g added per id in increasing position order starting from zero (or from the
+ * existing contents when accumulate != 0), padding id skipped. No atomics: positions are sorted by id on the
+ * device and each table row is summed by one thread in position order. Replaces EmbeddingBackward
+ * (BackwardNn.cs:508-546). */
+int32_t om_embedding_bwd(om_ctx* ctx, const float* g, const void* ids, int32_t id_dtype, int64_t n,
+                         int32_t v, int32_t dim, int64_t padding_index, float* dtable, int32_t accumulate);
+
+/* ---- attention ------------------------------------------------------------------------------------------ */
+
+/* out = softmax(scale*Q*K^T + mask)*V per (batch, head); q [B,H,Lq,D], k,v [B,H,Lk,D] contiguous; mask
+ * additive [Lq,Lk] (mask_batch_stride 0) or [B,Lq,Lk] (stride Lq*Lk) or NULL. lse [B,H,Lq] (may be NULL)
+ * receives the row log-sum-exp for the backward. Replaces Ops.Attention -> AttentionDriver.Run
+ * (Ops.Layers.cs:746-807; Kernels/AttentionDriver.cs:29). */
+int32_t om_attention_fwd(om_ctx* ctx, const float* q, const float* k, const float* v, const float* mask,
+                         int64_t mask_batch_stride, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d,
+                         float scale, float* out, float* lse);
+/* dq, dk, dv (each may be NULL) from g = dOut, recomputing P from q,k (and lse when given).
+ * Replaces AttentionBackward (BackwardNn.cs:636-701). */
+int32_t om_attention_bwd(om_ctx* ctx, const float* g, const float* q, const float* k, const float* v,
+                         const float* mask, int64_t mask_batch_stride, const float* lse, int32_t b,
+                         int32_t h, int32_t lq, int32_t lk, int32_t d, float scale, float* dq, float* dk,
+                         float* dv);
+
+/* ---- pooling and convolution ---------------------------------------------------------------------------- */
+
+/* The 16 integers of ConvShape (src/OneModel/Kernels/Conv.cs:11-13) in the reference's order. */
+typedef struct om_conv_shape {
+  int32_t n, cin, h, w, cout, kh, kw;
+  int32_t stride_h, stride_w, pad_top, pad_left, pad_bottom, pad_right, dil_h, dil_w, groups;
+} om_conv_shape;
+/* y [N,Cout,OH,OW] = conv(x [N,Cin,H,W], w [Cout,Cin/g,KH,KW]) + bias (may be NULL).
+ * Replaces Ops.Conv2d -> Conv.Run (Ops.Layers.cs:279-348). */
+int32_t om_conv2d_fwd(om_ctx* ctx, const om_conv_shape* s, const float* x, const float* w, const float* bias,
+                      float* y);
+/* Replaces the three branches of ConvBackward (BackwardNn.cs:317-402). */
+int32_t om_conv2d_dgrad(om_ctx* ctx, const om_conv_shape* s, const float* g, const float* w, float* dx);
+int32_t om_conv2d_wgrad(om_ctx* ctx, const om_conv_shape* s, const float* g, const float* x, float* dw,
+                        int32_t accumulate);
+int32_t om_conv2d_dbias(om_ctx* ctx, const om_conv_shape* s, const float* g, float* dbias, int32_t accumulate);
+
+/* Max pooling over NCHW planes; idx receives the Int32 flat NCHW index of each maximum (first wins ties,
+ * NaN wins), bit-exact with ReferenceKernels.MaxPool2d (src/OneModel/Tensors/TensorKernels.cs:242-295). */
+int32_t om_maxpool_fwd(om_ctx* ctx, const float* x, int32_t planes, int32_t h, int32_t w, int32_t kh,
+                       int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, float* y, int32_t* idx);
+/* dx[idx[i]] += g[i] in output order from zero, without atomics (each input element gathers the outputs
+ * that selected it in increasing output index). Replaces MaxPoolBackward (BackwardOps.cs:285-298). */
+int32_t om_maxpool_bwd(om_ctx* ctx, const float* g, const int32_t* idx, int32_t planes, int32_t h, int32_t w,
+                       int32_t oh, int32_t ow, int32_t kh, int32_t kw, int32_t sh, int32_t sw, int32_t ph,
+                       int32_t pw, float* dx);
+/* Average pooling (Ops.Layers.cs:414-461) and AvgPoolBackward / PoolWindow (BackwardNn.cs:464-506). */
+int32_t om_avgpool_fwd(om_ctx* ctx, const float* x, int32_t planes, int32_t h, int32_t w, int32_t kh,
+                       int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t count_include_pad,
+                       float* y);
+int32_t om_avgpool_bwd(om_ctx* ctx, const float* g, int32_t planes, int32_t h, int32_t w, int32_t kh,
+                       int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t count_include_pad,
+                       float* dx);
+
+/* ---- recurrent and CTC ---------------------------------------------------------------------------------- */
+
+/* One LSTM layer direction over x [T,B,I]: gates = x*W_ih^T + b_ih + h*W_hh^T + b_hh in i,f,g,o order.
+ * Outputs y [T,B,H] and the saved slots gates [T,B,4H] (post-activation), c [T,B,H], tanh_c [T,B,H].
+ * h0/c0 may be NULL (zeros). Replaces Ops.LstmLayer (src/OneModel/Tensors/Ops.Recurrent.cs:40-146). */
+int32_t om_lstm_layer_fwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h,
+                          const float* x, const float* w_ih, const float* w_hh, const float* b_ih,
+                          const float* b_hh, const float* h0, const float* c0, float* y, float* gates,
+                          float* c, float* tanh_c);
+/* Backward through time. gy [T,B,H]; ghn, gcn (may be NULL) are gradients of the final states. Outputs (each
+ * may be NULL): dx [T,B,I], dw_ih [4H,I], dw_hh [4H,H], db_ih [4H], db_hh [4H], dh0, dc0 [B,H].
+ * Replaces LstmBackward + ColumnSums (BackwardRecurrent.cs:10-113,224-246). */
+int32_t om_lstm_layer_bwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h,
+                          const float* gy, const float* ghn, const float* gcn, const float* x,
+                          const float* y, const float* w_ih, const float* w_hh, const float* h0,
+                          const float* c0, const float* gates, const float* c, const float* tanh_c,
+                          float* dx, float* dw_ih, float* dw_hh, float* db_ih, float* db_hh, float* dh0,
+                          float* dc0);
+
+/* CTC negative log-likelihood per sequence from log-probabilities lp [T,B,C] (double-precision alpha
+ * recursion in log space), targets concatenated (int32) with target_lengths[B], input_lengths[B].
+ * nll[B] receives the per-sequence losses (zero_infinity replaces +inf by 0); loss receives the reduction
+ * (0 = none: loss unused, 1 = mean over batch of nll/max(1,len), 2 = sum).
+ * Replaces Ops.CtcLoss -> CtcLossMath.Alpha (src/OneModel/Tensors/CtcLoss.cs:40-217). */
+int32_t om_ctc_loss(om_ctx* ctx, const float* lp, int32_t t, int32_t b, int32_t c, const int32_t* targets,
+                    const int32_t* target_lengths, const int32_t* input_lengths, int32_t blank,
+                    int32_t reduction, int32_t zero_infinity, float* nll, float* loss);
+/* grad [T,B,C] of the reduced loss with respect to lp given g (device: scalar for mean/sum, [B] for none).
+ * Replaces CtcBackward -> CtcLossMath.Gradient (BackwardRecurrent.cs:253-296; CtcLoss.cs:219-281). */
+int32_t om_ctc_grad(om_ctx* ctx, const float* g, const float* lp, int32_t t, int32_t b, int32_t c,
+                    const int32_t* targets, const int32_t* target_lengths, const int32_t* input_lengths,
+                    const float* nll, int32_t blank, int32_t reduction, int32_t zero_infinity, float* grad);
+/* Greedy CTC decode of lp [T,B,C]: per step argmax (lowest index on ties, NaN never wins), merged runs,
+ * blanks dropped. labels [B,T] padded with -1, lengths [B]. Integers are bit-exact with Ctc.Greedy
+ * (src/OneModel/Tensors/Ctc.cs:89-190). */
+int32_t om_ctc_greedy(om_ctx* ctx, const float* lp, int32_t t, int32_t b, int32_t c,
+                      const int32_t* input_lengths, int32_t blank, int32_t* labels, int32_t* lengths);
+
+/* ---- optimizers ------------------------------------------------------------------------------------------ */
+
+/* Per-step scalars of Adam/AdamW computed on the host in double exactly as Adam.BeginStep does
+ * (src/OneModel.Training/Optimizers.cs:501-508): step_size = (float)(lr / (1 - beta1^t)),
+ * sqrt_bc2 = (float)sqrt(1 - beta2^t). grad_scale multiplies every gradient first (1 = the reference;
+ * data-parallel runs pass 1 because the loss is already divided by the global row count). */
+typedef struct om_adam_hyper {
+  float lr, beta1, beta2, eps, weight_decay, step_size, sqrt_bc2, grad_scale;
+  int32_t decoupled; /* AdamW */
+  int32_t amsgrad;
+} om_adam_hyper;
+/* One fused multi-tensor launch over n_tensors parameters: per element exactly the rounding sequence of
+ * Adam.UpdateRange (Optimizers.cs:554-589), no fused multiply-add. Host arrays of device pointers; vmax may be
+ * NULL unless amsgrad. If hyper_dev is not NULL the kernel reads the scalars from that device struct instead
+ * (so a captured graph can be replayed with new per-step scalars). */
+int32_t om_optim_adam_step(om_ctx* ctx, int32_t n_tensors, float* const* p_host, const float* const* g_host,
+                           float* const* m_host, float* const* v_host, float* const* vmax_host,
+                           const int64_t* len_host, const om_adam_hyper* hyper_host,
+                           const om_adam_hyper* hyper_dev);
+typedef struct om_sgd_hyper {
+  float lr, weight_decay, momentum, dampening, grad_scale;
+  int32_t nesterov;
+  int32_t has_momentum;
+} om_sgd_hyper;
+/* Sgd.Update (Optimizers.cs:335-373). first_host[i] != 0 marks a momentum buffer not yet initialised. */
+int32_t om_optim_sgd_step(om_ctx* ctx, int32_t n_tensors, float* const* p_host, const float* const* g_host,
+                          float* const* buf_host, const int32_t* first_host, const int64_t* len_host,
+                          const om_sgd_hyper* hyper_host, const om_sgd_hyper* hyper_dev);
+/* Global gradient-norm clipping: norm = sqrt(sum g^2) accumulated in double in parameter and element order
+ * (fixed two-level partition), coef = (float)(max_norm/(norm+1e-6)); gradients are scaled when coef < 1 and
+ * the norm is finite. total_norm (device float, may be NULL) receives the norm.
+ * Replaces GradClip.ClipNorm (src/OneModel.Training/Schedules.cs:22-100). */
+int32_t om_grad_norm_clip(om_ctx* ctx, int32_t n_tensors, float* const* g_host, const int64_t* len_host,
+                          float max_norm, int32_t infinity_norm, float* total_norm);
+/* Replaces GradClip.ClipValue (Schedules.cs:120-143). */
+int32_t om_grad_clip_value(om_ctx* ctx, int32_t n_tensors, float* const* g_host, const int64_t* len_host,
+                           float clip);
+
+/* ---- data parallel ---------------------------------------------------------------------------------------- */
+
+/* The reference is single-process; these have no counterpart there. One rank per process and GPU.
+ * om_dp_unique_id fills a 128-byte NCCL id on rank 0 which the caller distributes to all ranks;
+ * om_dp_init joins the communicator. Buckets are contiguous ranges of gradient memory registered once;
+ * om_dp_allreduce_bucket launches ncclAllReduce(sum, fp32) on a communication stream after the work
+ * already queued on the context stream; om_dp_wait makes the context stream wait for all launched buckets
+ * and polls the communicator for asynchronous errors with a host deadline (OM_ERR_TIMEOUT / OM_ERR_NCCL). */
+int32_t om_dp_unique_id(om_ctx* ctx, uint8_t id128[128]);
+int32_t om_dp_init(om_ctx* ctx, const uint8_t id128[128], int32_t rank, int32_t world);
+int32_t om_dp_register_bucket(om_ctx* ctx, int32_t bucket_id, float* base, int64_t count);
+int32_t om_dp_allreduce_bucket(om_ctx* ctx, int32_t bucket_id);
+int32_t om_dp_allreduce(om_ctx* ctx, void* buf, int64_t count, int32_t dtype); /* small in-stream sums */
+int32_t om_dp_wait(om_ctx* ctx, int32_t timeout_ms);
+int32_t om_dp_finalize(om_ctx* ctx);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* ONEMODEL_B200_H */

@@ -1,0 +1,107 @@
+// Shared internals of libonemodel_b200: the context object, error plumbing, the device memory pool and
+// the per-entry-point profiler. Nothing here is visible through the C ABI except the opaque om_ctx.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/onemodel_b200.h"
+
+namespace om {
+
+// Device pool with the reference pool's size classes: for the power of two b below the request, the next of
+// b*{1.25,1.5,1.75,2} (docs/tensors.md:93-118 of the reference). Blocks are cached per class and reused in
+// stream order (single stream per context).
+struct Pool {
+  std::unordered_map<void*, size_t> live;              // ptr -> class bytes
+  std::map<size_t, std::vector<void*>> cache;          // class bytes -> free blocks
+  uint64_t bytes_in_use = 0, bytes_cached = 0, driver_allocs = 0;
+  static size_t size_class(size_t bytes);
+};
+
+struct ProfileEntry {
+  uint64_t calls = 0;
+  double flops = 0, bytes = 0;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;
+  double ms = 0;
+};
+
+struct DpState;  // om_dp.cu
+
+}  // namespace om
+
+struct om_ctx {
+  int device = 0;
+  uint32_t flags = 0;
+  cudaStream_t stream = nullptr;
+  std::string last_error;
+  int32_t* status_host = nullptr;  // pinned, device-visible status word
+  int32_t* status_dev = nullptr;
+  int sm_count = 148;
+  om::Pool pool;
+  bool profiling = false;
+  bool capturing = false;
+  std::map<std::string, om::ProfileEntry> profile;
+  std::vector<cudaEvent_t> event_pool;
+  om::DpState* dp = nullptr;
+};
+
+namespace om {
+
+extern thread_local std::string g_create_error;
+
+int32_t fail(om_ctx* ctx, int32_t code, const char* fmt, ...);
+int32_t check_cuda(om_ctx* ctx, cudaError_t e, const char* what);
+int32_t pool_alloc(om_ctx* ctx, size_t bytes, bool zero, void** out);
+int32_t pool_free(om_ctx* ctx, void* p);
+
+struct ProfileScope {
+  om_ctx* ctx;
+  ProfileEntry* e = nullptr;
+  cudaEvent_t start = nullptr;
+  ProfileScope(om_ctx* c, const char* name, double flops, double bytes);
+  ~ProfileScope();
+};
+
+#define OM_CHECK_CTX(ctx)                              \
+  do {                                                 \
+    if ((ctx) == nullptr) return OM_ERR_ARG;           \
+    cudaError_t _e = cudaSetDevice((ctx)->device);     \
+    if (_e != cudaSuccess) return om::check_cuda((ctx), _e, "cudaSetDevice"); \
+  } while (0)
+
+#define OM_CUDA(ctx, call)                                       \
+  do {                                                           \
+    cudaError_t _e = (call);                                     \
+    if (_e != cudaSuccess) return om::check_cuda((ctx), _e, #call); \
+  } while (0)
+
+#define OM_LAUNCH_CHECK(ctx, what)                                \
+  do {                                                            \
+    cudaError_t _e = cudaGetLastError();                          \
+    if (_e != cudaSuccess) return om::check_cuda((ctx), _e, what); \
+  } while (0)
+
+#define OM_TRY(expr)                 \
+  do {                               \
+    int32_t _s = (expr);             \
+    if (_s != OM_OK) return _s;      \
+  } while (0)
+
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Grid size for a grid-stride kernel: enough CTAs to fill the machine a few times over, never more than the work.
+static inline int grid_for(om_ctx* ctx, int64_t work_items, int per_block, int waves = 8) {
+  int64_t need = ceil_div(work_items, per_block);
+  int64_t cap = (int64_t)ctx->sm_count * waves;
+  if (need < 1) need = 1;
+  return (int)(need < cap ? need : cap);
+}
+
+}  // namespace om

@@ -1,0 +1,386 @@
+// Context, pooled device memory, copies, graph capture and the per-entry-point profiler.
+#include <stdarg.h>
+
+#include <algorithm>
+
+#include "om_common.cuh"
+
+namespace om {
+
+thread_local std::string g_create_error;
+
+int32_t fail(om_ctx* ctx, int32_t code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->last_error = buf; else g_create_error = buf;
+  return code;
+}
+
+int32_t check_cuda(om_ctx* ctx, cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return OM_OK;
+  int32_t code = (e == cudaErrorMemoryAllocation) ? OM_ERR_OOM : OM_ERR_CUDA;
+  return fail(ctx, code, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+size_t Pool::size_class(size_t bytes) {
+  if (bytes <= 256) return 256;
+  size_t b = 256;
+  while ((b << 1) < bytes) b <<= 1;  // b < bytes <= 2b
+  size_t q = b >> 2;
+  for (int i = 1; i <= 4; i++) {
+    size_t c = b + q * i;
+    if (c >= bytes) return c;
+  }
+  return b << 1;
+}
+
+int32_t pool_alloc(om_ctx* ctx, size_t bytes, bool zero, void** out) {
+  *out = nullptr;
+  size_t cls = Pool::size_class(bytes == 0 ? 1 : bytes);
+  Pool& p = ctx->pool;
+  void* ptr = nullptr;
+  auto it = p.cache.find(cls);
+  if (it != p.cache.end() && !it->second.empty()) {
+    ptr = it->second.back();
+    it->second.pop_back();
+    p.bytes_cached -= cls;
+  } else {
+    if (ctx->capturing) {
+      return fail(ctx, OM_ERR_UNSUPPORTED,
+                  "device allocation of %zu bytes during graph capture: run one uncaptured step first so the pool holds every block",
+                  cls);
+    }
+    cudaError_t e = cudaMalloc(&ptr, cls);
+    if (e == cudaErrorMemoryAllocation) {
+      cudaGetLastError();
+      // Give cached blocks back to the driver and retry once.
+      cudaStreamSynchronize(ctx->stream);
+      for (auto& kv : p.cache) {
+        for (void* q : kv.second) cudaFree(q);
+        kv.second.clear();
+      }
+      p.bytes_cached = 0;
+      e = cudaMalloc(&ptr, cls);
+    }
+    if (e != cudaSuccess) return check_cuda(ctx, e, "cudaMalloc");
+    p.driver_allocs++;
+  }
+  p.live[ptr] = cls;
+  p.bytes_in_use += cls;
+  if (zero) {
+    cudaError_t e = cudaMemsetAsync(ptr, 0, bytes, ctx->stream);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "cudaMemsetAsync");
+  }
+  *out = ptr;
+  return OM_OK;
+}
+
+int32_t pool_free(om_ctx* ctx, void* ptr) {
+  if (!ptr) return OM_OK;
+  Pool& p = ctx->pool;
+  auto it = p.live.find(ptr);
+  if (it == p.live.end()) return fail(ctx, OM_ERR_ARG, "om_free: %p was not allocated by this context", ptr);
+  size_t cls = it->second;
+  p.live.erase(it);
+  p.bytes_in_use -= cls;
+  p.cache[cls].push_back(ptr);
+  p.bytes_cached += cls;
+  return OM_OK;
+}
+
+static cudaEvent_t get_event(om_ctx* ctx) {
+  if (!ctx->event_pool.empty()) {
+    cudaEvent_t e = ctx->event_pool.back();
+    ctx->event_pool.pop_back();
+    return e;
+  }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+
+ProfileScope::ProfileScope(om_ctx* c, const char* name, double flops, double bytes) : ctx(c) {
+  if (!c->profiling || c->capturing) return;
+  e = &c->profile[name];
+  e->calls++;
+  e->flops += flops;
+  e->bytes += bytes;
+  start = get_event(c);
+  cudaEventRecord(start, c->stream);
+}
+
+ProfileScope::~ProfileScope() {
+  if (!e) return;
+  cudaEvent_t stop = get_event(ctx);
+  cudaEventRecord(stop, ctx->stream);
+  e->pending.emplace_back(start, stop);
+}
+
+static void profile_drain(om_ctx* ctx) {
+  cudaStreamSynchronize(ctx->stream);
+  for (auto& kv : ctx->profile) {
+    for (auto& pr : kv.second.pending) {
+      float ms = 0;
+      if (cudaEventElapsedTime(&ms, pr.first, pr.second) == cudaSuccess) kv.second.ms += ms;
+      ctx->event_pool.push_back(pr.first);
+      ctx->event_pool.push_back(pr.second);
+    }
+    kv.second.pending.clear();
+  }
+}
+
+}  // namespace om
+
+using namespace om;
+
+extern "C" {
+
+int32_t om_version(void) { return 100; }
+
+int32_t om_ctx_create(int32_t device, uint32_t flags, om_ctx** out) {
+  if (!out) return OM_ERR_ARG;
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return fail(nullptr, OM_ERR_CUDA, "no CUDA device is visible (%s): this library has no CPU path",
+                e == cudaSuccess ? "device count 0" : cudaGetErrorString(e));
+  }
+  if (device < 0 || device >= count) return fail(nullptr, OM_ERR_ARG, "device %d of %d", device, count);
+  if ((e = cudaSetDevice(device)) != cudaSuccess) return check_cuda(nullptr, e, "cudaSetDevice");
+  cudaDeviceProp prop;
+  if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) return check_cuda(nullptr, e, "cudaGetDeviceProperties");
+  if (prop.major != 10) {
+    return fail(nullptr, OM_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                prop.major, prop.minor);
+  }
+  om_ctx* ctx = new om_ctx();
+  ctx->device = device;
+  ctx->flags = flags;
+  ctx->sm_count = prop.multiProcessorCount;
+  if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) {
+    delete ctx;
+    return check_cuda(nullptr, e, "cudaStreamCreate");
+  }
+  if ((e = cudaHostAlloc((void**)&ctx->status_host, 64, cudaHostAllocMapped)) != cudaSuccess) {
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return check_cuda(nullptr, e, "cudaHostAlloc");
+  }
+  memset(ctx->status_host, 0, 64);
+  cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0);
+  *out = ctx;
+  return OM_OK;
+}
+
+int32_t om_dp_finalize(om_ctx* ctx);
+
+int32_t om_ctx_destroy(om_ctx* ctx) {
+  if (!ctx) return OM_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->dp) om_dp_finalize(ctx);
+  for (auto& kv : ctx->pool.cache)
+    for (void* p : kv.second) cudaFree(p);
+  for (auto& kv : ctx->pool.live) cudaFree(kv.first);
+  for (auto& kv : ctx->profile)
+    for (auto& pr : kv.second.pending) {
+      cudaEventDestroy(pr.first);
+      cudaEventDestroy(pr.second);
+    }
+  for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
+  cudaFreeHost(ctx->status_host);
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return OM_OK;
+}
+
+int32_t om_ctx_set_flags(om_ctx* ctx, uint32_t flags) {
+  if (!ctx) return OM_ERR_ARG;
+  ctx->flags = flags;
+  return OM_OK;
+}
+
+int32_t om_ctx_get_flags(om_ctx* ctx, uint32_t* flags) {
+  if (!ctx || !flags) return OM_ERR_ARG;
+  *flags = ctx->flags;
+  return OM_OK;
+}
+
+int32_t om_last_error(om_ctx* ctx, char* buf, size_t n) {
+  if (!buf || n == 0) return OM_ERR_ARG;
+  const std::string& s = ctx ? ctx->last_error : g_create_error;
+  size_t len = std::min(n - 1, s.size());
+  memcpy(buf, s.data(), len);
+  buf[len] = 0;
+  return OM_OK;
+}
+
+int32_t om_ctx_stream(om_ctx* ctx, void** stream) {
+  if (!ctx || !stream) return OM_ERR_ARG;
+  *stream = (void*)ctx->stream;
+  return OM_OK;
+}
+
+int32_t om_alloc(om_ctx* ctx, size_t bytes, int32_t zero, void** dptr) {
+  OM_CHECK_CTX(ctx);
+  if (!dptr) return OM_ERR_ARG;
+  return pool_alloc(ctx, bytes, zero != 0, dptr);
+}
+
+int32_t om_free(om_ctx* ctx, void* dptr) {
+  if (!ctx) return OM_ERR_ARG;
+  return pool_free(ctx, dptr);
+}
+
+int32_t om_pool_trim(om_ctx* ctx) {
+  OM_CHECK_CTX(ctx);
+  OM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (auto& kv : ctx->pool.cache) {
+    for (void* p : kv.second) cudaFree(p);
+    kv.second.clear();
+  }
+  ctx->pool.bytes_cached = 0;
+  return OM_OK;
+}
+
+int32_t om_pool_stats(om_ctx* ctx, uint64_t* in_use, uint64_t* cached, uint64_t* driver_allocs) {
+  if (!ctx) return OM_ERR_ARG;
+  if (in_use) *in_use = ctx->pool.bytes_in_use;
+  if (cached) *cached = ctx->pool.bytes_cached;
+  if (driver_allocs) *driver_allocs = ctx->pool.driver_allocs;
+  return OM_OK;
+}
+
+int32_t om_memcpy_h2d(om_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  OM_CHECK_CTX(ctx);
+  if (bytes == 0) return OM_OK;
+  OM_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return OM_OK;
+}
+
+int32_t om_memcpy_d2h(om_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  OM_CHECK_CTX(ctx);
+  if (bytes != 0) OM_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  OM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return OM_OK;
+}
+
+int32_t om_memcpy_d2d(om_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  OM_CHECK_CTX(ctx);
+  if (bytes == 0) return OM_OK;
+  OM_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return OM_OK;
+}
+
+int32_t om_memset(om_ctx* ctx, void* dst, int32_t byte, size_t bytes) {
+  OM_CHECK_CTX(ctx);
+  if (bytes == 0) return OM_OK;
+  OM_CUDA(ctx, cudaMemsetAsync(dst, byte, bytes, ctx->stream));
+  return OM_OK;
+}
+
+int32_t om_host_alloc_pinned(om_ctx* ctx, size_t bytes, void** hptr) {
+  OM_CHECK_CTX(ctx);
+  if (!hptr) return OM_ERR_ARG;
+  OM_CUDA(ctx, cudaHostAlloc(hptr, bytes == 0 ? 1 : bytes, cudaHostAllocDefault));
+  return OM_OK;
+}
+
+int32_t om_host_free_pinned(om_ctx* ctx, void* hptr) {
+  OM_CHECK_CTX(ctx);
+  OM_CUDA(ctx, cudaFreeHost(hptr));
+  return OM_OK;
+}
+
+int32_t om_sync(om_ctx* ctx) {
+  OM_CHECK_CTX(ctx);
+  OM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  int32_t s = *(volatile int32_t*)ctx->status_host;
+  if (s != 0) {
+    int32_t detail = ((volatile int32_t*)ctx->status_host)[1];
+    *(volatile int32_t*)ctx->status_host = 0;
+    ((volatile int32_t*)ctx->status_host)[1] = 0;
+    const char* what = s == OM_ERR_INDEX ? "an index operand was out of range"
+                       : s == OM_ERR_TIMEOUT ? "a bounded device-side wait expired"
+                                             : "a kernel reported an error";
+    return fail(ctx, s, "device status %d: %s (detail %d)", s, what, detail);
+  }
+  return OM_OK;
+}
+
+int32_t om_graph_begin(om_ctx* ctx) {
+  OM_CHECK_CTX(ctx);
+  if (ctx->capturing) return fail(ctx, OM_ERR_ARG, "om_graph_begin: already capturing");
+  OM_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+  ctx->capturing = true;
+  return OM_OK;
+}
+
+int32_t om_graph_end(om_ctx* ctx, void** graph_exec) {
+  OM_CHECK_CTX(ctx);
+  if (!ctx->capturing) return fail(ctx, OM_ERR_ARG, "om_graph_end: not capturing");
+  ctx->capturing = false;
+  cudaGraph_t graph = nullptr;
+  OM_CUDA(ctx, cudaStreamEndCapture(ctx->stream, &graph));
+  cudaGraphExec_t exec = nullptr;
+  cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "cudaGraphInstantiate");
+  *graph_exec = (void*)exec;
+  return OM_OK;
+}
+
+int32_t om_graph_launch(om_ctx* ctx, void* graph_exec) {
+  OM_CHECK_CTX(ctx);
+  OM_CUDA(ctx, cudaGraphLaunch((cudaGraphExec_t)graph_exec, ctx->stream));
+  return OM_OK;
+}
+
+int32_t om_graph_destroy(om_ctx* ctx, void* graph_exec) {
+  OM_CHECK_CTX(ctx);
+  if (graph_exec) OM_CUDA(ctx, cudaGraphExecDestroy((cudaGraphExec_t)graph_exec));
+  return OM_OK;
+}
+
+int32_t om_profile_enable(om_ctx* ctx, int32_t on) {
+  if (!ctx) return OM_ERR_ARG;
+  if (!on && ctx->profiling) {
+    cudaSetDevice(ctx->device);
+    profile_drain(ctx);
+  }
+  ctx->profiling = on != 0;
+  return OM_OK;
+}
+
+int32_t om_profile_reset(om_ctx* ctx) {
+  OM_CHECK_CTX(ctx);
+  profile_drain(ctx);
+  ctx->profile.clear();
+  return OM_OK;
+}
+
+int32_t om_profile_read(om_ctx* ctx, om_profile_row* rows, int32_t cap, int32_t* n) {
+  OM_CHECK_CTX(ctx);
+  profile_drain(ctx);
+  int32_t i = 0;
+  for (auto& kv : ctx->profile) {
+    if (i < cap && rows) {
+      memset(&rows[i], 0, sizeof rows[i]);
+      strncpy(rows[i].name, kv.first.c_str(), sizeof rows[i].name - 1);
+      rows[i].calls = kv.second.calls;
+      rows[i].ms = kv.second.ms;
+      rows[i].flops = kv.second.flops;
+      rows[i].bytes = kv.second.bytes;
+    }
+    i++;
+  }
+  if (n) *n = i;
+  return OM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,114 @@
+// Entry points of the dense products: pick the tensor-pipe kernel (tcgen05, om_gemm_tc.cu) when the context asks
+// for TF32 or BF16 operands and the shape qualifies, else the fp32 FMA kernel (om_gemm_simt.cu). Both run on the
+// GPU; there is no host path.
+#include "om_common.cuh"
+
+namespace om {
+
+int32_t gemm_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
+                  const float* B, int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch, int acc);
+bool gemm_tc_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B,
+                       int ldb, const float* C, int ldc);
+int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb,
+                float* C, int ldc, int acc, const float* bias);
+
+__global__ void add_bias_rows_kernel(float* __restrict__ y, const float* __restrict__ bias, int64_t rows, int32_t cols) {
+  int64_t total = rows * cols;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  if ((cols & 3) == 0) {
+    int64_t n4 = total >> 2;
+    int32_t c4 = cols >> 2;
+    float4* y4 = reinterpret_cast<float4*>(y);
+    const float4* b4 = reinterpret_cast<const float4*>(bias);
+    for (int64_t j = i; j < n4; j += stride) {
+      float4 v = y4[j], b = b4[j % c4];
+      v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+      y4[j] = v;
+    }
+  } else {
+    for (int64_t j = i; j < total; j += stride) y[j] += bias[j % cols];
+  }
+}
+
+static int32_t check_gemm_args(om_ctx* ctx, const char* who, int ta, int tb, int m, int n, int k, int lda, int ldb, int ldc) {
+  if (m < 0 || n < 0 || k < 0) return fail(ctx, OM_ERR_SHAPE, "%s: m %d n %d k %d", who, m, n, k);
+  int min_lda = ta ? m : k, min_ldb = tb ? k : n;
+  if (lda < (min_lda > 1 ? min_lda : 1) || ldb < (min_ldb > 1 ? min_ldb : 1) || ldc < (n > 1 ? n : 1))
+    return fail(ctx, OM_ERR_SHAPE, "%s: leading dimensions lda %d ldb %d ldc %d too small for m %d n %d k %d", who, lda, ldb, ldc, m, n, k);
+  return OM_OK;
+}
+
+int32_t gemm_dispatch(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B,
+                      int ldb, float* C, int ldc, int acc, const float* bias) {
+  if (m == 0 || n == 0) return OM_OK;
+  if ((ctx->flags & (OM_TF32 | OM_BF16_OPERANDS)) && gemm_tc_supported(ctx, ta, tb, m, n, k, A, lda, B, ldb, C, ldc))
+    return gemm_tc(ctx, ta, tb, m, n, k, A, lda, B, ldb, C, ldc, acc, bias);
+  OM_TRY(gemm_simt(ctx, ta, tb, m, n, k, A, lda, 0, B, ldb, 0, C, ldc, 0, 1, acc));
+  if (bias) {
+    if (ldc != n) return fail(ctx, OM_ERR_UNSUPPORTED, "bias epilogue needs a dense output");
+    add_bias_rows_kernel<<<grid_for(ctx, ((int64_t)m * n + 3) / 4, 256), 256, 0, ctx->stream>>>(C, bias, m, n);
+    OM_LAUNCH_CHECK(ctx, "add_bias_rows");
+  }
+  return OM_OK;
+}
+
+}  // namespace om
+
+using namespace om;
+
+extern "C" {
+
+int32_t om_colsum(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, float* out, int32_t accumulate);
+
+int32_t om_matmul(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m, int32_t n, int32_t k, const float* A,
+                  int32_t lda, const float* B, int32_t ldb, float* C, int32_t ldc, int32_t accumulate) {
+  OM_CHECK_CTX(ctx);
+  OM_TRY(check_gemm_args(ctx, "om_matmul", transA, transB, m, n, k, lda, ldb, ldc));
+  ProfileScope prof(ctx, "om_matmul", 2.0 * m * n * k, 4.0 * ((double)m * k + (double)k * n + (double)m * n));
+  return gemm_dispatch(ctx, transA, transB, m, n, k, A, lda, B, ldb, C, ldc, accumulate, nullptr);
+}
+
+int32_t om_matmul_batched(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m, int32_t n, int32_t k,
+                          const float* A, int32_t lda, int64_t strideA, const float* B, int32_t ldb, int64_t strideB,
+                          float* C, int32_t ldc, int64_t strideC, int32_t batch, int32_t accumulate) {
+  OM_CHECK_CTX(ctx);
+  OM_TRY(check_gemm_args(ctx, "om_matmul_batched", transA, transB, m, n, k, lda, ldb, ldc));
+  if (batch < 0 || batch > 65535) return fail(ctx, OM_ERR_SHAPE, "om_matmul_batched: batch %d", batch);
+  ProfileScope prof(ctx, "om_matmul_batched", 2.0 * m * n * k * batch,
+                    4.0 * batch * ((double)m * k + (double)k * n + (double)m * n));
+  return gemm_simt(ctx, transA, transB, m, n, k, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, batch, accumulate);
+}
+
+int32_t om_linear_fwd(om_ctx* ctx, const float* x, const float* W, const float* bias, int32_t rows,
+                      int32_t in_features, int32_t out_features, float* y) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 0 || in_features < 1 || out_features < 1)
+    return fail(ctx, OM_ERR_SHAPE, "om_linear_fwd: rows %d in %d out %d", rows, in_features, out_features);
+  ProfileScope prof(ctx, "om_linear_fwd", 2.0 * rows * in_features * out_features,
+                    4.0 * ((double)rows * in_features + (double)in_features * out_features + (double)rows * out_features));
+  return gemm_dispatch(ctx, 0, 1, rows, out_features, in_features, x, in_features, W, in_features, y, out_features, 0, bias);
+}
+
+int32_t om_linear_bwd(om_ctx* ctx, const float* g, const float* x, const float* W, int32_t rows, int32_t in_features,
+                      int32_t out_features, float* dx, float* dW, float* dbias, int32_t accumulate_w) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 0 || in_features < 1 || out_features < 1)
+    return fail(ctx, OM_ERR_SHAPE, "om_linear_bwd: rows %d in %d out %d", rows, in_features, out_features);
+  if (dx) {
+    ProfileScope prof(ctx, "om_linear_bwd.dgrad", 2.0 * rows * in_features * out_features,
+                      4.0 * ((double)rows * in_features + (double)in_features * out_features + (double)rows * out_features));
+    // dx[rows, in] = g[rows, out] * W[out, in]
+    OM_TRY(gemm_dispatch(ctx, 0, 0, rows, in_features, out_features, g, out_features, W, in_features, dx, in_features, 0, nullptr));
+  }
+  if (dW) {
+    ProfileScope prof(ctx, "om_linear_bwd.wgrad", 2.0 * rows * in_features * out_features,
+                      4.0 * ((double)rows * in_features + (double)in_features * out_features + (double)rows * out_features));
+    // dW[out, in] = g[rows, out]^T * x[rows, in]
+    OM_TRY(gemm_dispatch(ctx, 1, 0, out_features, in_features, rows, g, out_features, x, in_features, dW, in_features, accumulate_w, nullptr));
+  }
+  if (dbias) OM_TRY(om_colsum(ctx, g, rows, out_features, dbias, accumulate_w));
+  return OM_OK;
+}
+
+}  // extern "C"

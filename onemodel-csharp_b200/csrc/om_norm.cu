@@ -1,0 +1,386 @@
+// Layer normalisation (rows) and batch normalisation (NCHW channels), forward and backward. Bandwidth-bound:
+// every kernel streams its operands once with coalesced 128-byte warp accesses. Statistics that the reference
+// accumulates in double (BackwardNn.cs:170-307, Ops.Layers.cs:185-219) are accumulated in double here too, over a
+// partition that depends only on the shape and is combined in a fixed order.
+#include "om_common.cuh"
+
+namespace om {
+
+__device__ __forceinline__ double wsum_d(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float wsum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ---- layer norm forward: one warp per row -------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+layernorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                     int32_t rows, int32_t cols, float eps, float* __restrict__ y, float* __restrict__ mean_out,
+                     float* __restrict__ inv_out) {
+  int lane = threadIdx.x & 31;
+  int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  int64_t warps = (int64_t)gridDim.x * 8;
+  float n = (float)cols;
+  for (int64_t r = warp; r < rows; r += warps) {
+    const float* xr = x + r * cols;
+    float s = 0.f;
+    for (int j = lane; j < cols; j += 32) s += xr[j];
+    float mean = wsum_f(s) / n;
+    float q = 0.f;
+    for (int j = lane; j < cols; j += 32) {
+      float d = xr[j] - mean;
+      q += d * d;
+    }
+    float inv = 1.0f / sqrtf((wsum_f(q) / n) + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[r] = mean;
+      if (inv_out) inv_out[r] = inv;
+    }
+    float* yr = y + r * cols;
+    for (int j = lane; j < cols; j += 32) yr[j] = (((xr[j] - mean) * inv) * gamma[j]) + beta[j];
+  }
+}
+
+// ---- layer norm backward -------------------------------------------------------------------------------------------
+// CTA = 8 warps owns kLnRowsPerCta consecutive rows; warp w takes rows w, w+8, ... of the chunk. Each lane keeps the
+// dgamma/dbeta contributions of its columns (lane, lane+32, ...) in double registers, the 8 warps are combined in warp
+// order through shared memory, and the chunk's column partials go to global memory for the fixed-order second stage.
+constexpr int kLnRowsPerCta = 64;
+
+template <int NC>
+__global__ void __launch_bounds__(256)
+layernorm_bwd_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
+                     const float* __restrict__ mean, const float* __restrict__ inv, int32_t rows, int32_t cols,
+                     float* __restrict__ dx, double* __restrict__ part_gamma, double* __restrict__ part_beta) {
+  extern __shared__ double sm[];  // [8][cols] for gamma then [8][cols] for beta
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int r0 = blockIdx.x * kLnRowsPerCta;
+  const int r1 = min(rows, r0 + kLnRowsPerCta);
+  double ag[NC], ab[NC];
+  float gam[NC];
+#pragma unroll
+  for (int i = 0; i < NC; i++) {
+    ag[i] = 0.0;
+    ab[i] = 0.0;
+    int j = lane + 32 * i;
+    gam[i] = j < cols ? gamma[j] : 0.f;
+  }
+  const bool params = part_gamma != nullptr || part_beta != nullptr;
+  for (int r = r0 + w; r < r1; r += 8) {
+    const float* xr = x + (int64_t)r * cols;
+    const float* gr = g + (int64_t)r * cols;
+    float m = mean[r], s = inv[r];
+    float xh[NC], gv[NC];
+    double sum1 = 0.0, sum2 = 0.0;
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+      int j = lane + 32 * i;
+      if (j < cols) {
+        gv[i] = gr[j];
+        xh[i] = (xr[j] - m) * s;
+        float dxhat = gv[i] * gam[i];
+        sum1 += (double)dxhat;
+        sum2 += (double)(dxhat * xh[i]);
+        if (params) {
+          ag[i] += (double)(gv[i] * xh[i]);
+          ab[i] += (double)gv[i];
+        }
+      } else {
+        gv[i] = 0.f;
+        xh[i] = 0.f;
+      }
+    }
+    if (dx) {
+      sum1 = wsum_d(sum1);
+      sum2 = wsum_d(sum2);
+      float m1 = (float)(sum1 / cols), m2 = (float)(sum2 / cols);
+      float* dr = dx + (int64_t)r * cols;
+#pragma unroll
+      for (int i = 0; i < NC; i++) {
+        int j = lane + 32 * i;
+        if (j < cols) dr[j] = s * (((gv[i] * gam[i]) - m1) - (xh[i] * m2));
+      }
+    }
+  }
+  if (!params) return;
+  double* smg = sm;
+  double* smb = sm + 8 * cols;
+#pragma unroll
+  for (int i = 0; i < NC; i++) {
+    int j = lane + 32 * i;
+    if (j < cols) {
+      smg[w * cols + j] = ag[i];
+      smb[w * cols + j] = ab[i];
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < cols; j += 256) {
+    double tg = 0.0, tb = 0.0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      tg += smg[k * cols + j];
+      tb += smb[k * cols + j];
+    }
+    if (part_gamma) part_gamma[(int64_t)blockIdx.x * cols + j] = tg;
+    if (part_beta) part_beta[(int64_t)blockIdx.x * cols + j] = tb;
+  }
+}
+
+__global__ void column_partials_finish_kernel(const double* __restrict__ pa, const double* __restrict__ pb, int chunks,
+                                              int32_t cols, float* __restrict__ oa, float* __restrict__ ob,
+                                              int accumulate) {
+  int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= cols) return;
+  if (pa && oa) {
+    double t = 0.0;
+    for (int c = 0; c < chunks; c++) t += pa[(int64_t)c * cols + j];
+    oa[j] = accumulate ? oa[j] + (float)t : (float)t;
+  }
+  if (pb && ob) {
+    double t = 0.0;
+    for (int c = 0; c < chunks; c++) t += pb[(int64_t)c * cols + j];
+    ob[j] = accumulate ? ob[j] + (float)t : (float)t;
+  }
+}
+
+// ---- batch norm ------------------------------------------------------------------------------------------------------
+// Channel statistics: CTA (ch, slice) sums the planes of images [slice*ipc, (slice+1)*ipc) of channel ch. MODE 0: sum x.
+// MODE 1: sum (x - mu64)^2. MODE 2 (backward): sum g*xhat and sum g.
+constexpr int kBnThreads = 256;
+
+template <int MODE>
+__global__ void __launch_bounds__(kBnThreads)
+bn_partial_kernel(const float* __restrict__ x, const float* __restrict__ g, const double* __restrict__ mu64,
+                  const float* __restrict__ mean, const float* __restrict__ inv, int32_t n, int32_t c, int32_t plane,
+                  int32_t ipc, double* __restrict__ pa, double* __restrict__ pb) {
+  __shared__ double sa[kBnThreads / 32], sb[kBnThreads / 32];
+  const int ch = blockIdx.x, slice = blockIdx.y;
+  const int i0 = slice * ipc, i1 = min(n, i0 + ipc);
+  double a = 0.0, b = 0.0;
+  double mu = MODE == 1 ? mu64[ch] : 0.0;
+  float mm = MODE == 2 ? mean[ch] : 0.f, s = MODE == 2 ? inv[ch] : 0.f;
+  for (int i = i0; i < i1; i++) {
+    const int64_t o = ((int64_t)i * c + ch) * plane;
+    for (int p = threadIdx.x; p < plane; p += kBnThreads) {
+      if (MODE == 0) {
+        a += (double)x[o + p];
+      } else if (MODE == 1) {
+        double d = (double)x[o + p] - mu;
+        a += d * d;
+      } else {
+        float gg = g[o + p];
+        a += (double)(gg * ((x[o + p] - mm) * s));
+        b += (double)gg;
+      }
+    }
+  }
+  a = wsum_d(a);
+  if (MODE == 2) b = wsum_d(b);
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) {
+    sa[w] = a;
+    sb[w] = b;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double ta = 0.0, tb = 0.0;
+#pragma unroll
+    for (int k = 0; k < kBnThreads / 32; k++) {
+      ta += sa[k];
+      tb += sb[k];
+    }
+    pa[(int64_t)slice * c + ch] = ta;
+    if (MODE == 2) pb[(int64_t)slice * c + ch] = tb;
+  }
+}
+
+__global__ void bn_mean_kernel(const double* __restrict__ pa, int slices, int32_t c, double m, double* __restrict__ mu64) {
+  int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= c) return;
+  double t = 0.0;
+  for (int s = 0; s < slices; s++) t += pa[(int64_t)s * c + ch];
+  mu64[ch] = t / m;
+}
+
+__global__ void bn_finish_stats_kernel(const double* __restrict__ pa, const double* __restrict__ mu64, int slices,
+                                       int32_t c, double m, float momentum, float eps, float* __restrict__ mean,
+                                       float* __restrict__ inv, float* __restrict__ rm, float* __restrict__ rv) {
+  int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= c) return;
+  double ss = 0.0;
+  for (int s = 0; s < slices; s++) ss += pa[(int64_t)s * c + ch];
+  double var = ss / m;
+  double mu = mu64[ch];
+  mean[ch] = (float)mu;
+  inv[ch] = 1.0f / sqrtf((float)var + eps);
+  double unbiased = m > 1 ? var * m / (m - 1) : var;
+  // (1 - momentum) is float arithmetic promoted to double in the reference: ((1 - momentum) * rm) + (momentum * mu64).
+  float keep = 1 - momentum;
+  rm[ch] = (float)(((double)(keep * rm[ch])) + ((double)momentum * mu));
+  rv[ch] = (float)(((double)(keep * rv[ch])) + ((double)momentum * unbiased));
+}
+
+__global__ void bn_eval_stats_kernel(const float* __restrict__ rm, const float* __restrict__ rv, int32_t c, float eps,
+                                     float* __restrict__ mean, float* __restrict__ inv) {
+  int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= c) return;
+  mean[ch] = rm[ch];
+  inv[ch] = 1.0f / sqrtf(rv[ch] + eps);
+}
+
+// grid.x = n*c planes (grid-stride), threads stride the plane.
+__global__ void bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                const float* __restrict__ mean, const float* __restrict__ inv, int64_t planes, int32_t c,
+                                int32_t plane, float* __restrict__ y) {
+  for (int64_t pl = blockIdx.x; pl < planes; pl += gridDim.x) {
+    int ch = (int)(pl % c);
+    float mm = mean[ch], s = inv[ch], gg = gamma[ch], bb = beta[ch];
+    const float* xp = x + pl * plane;
+    float* yp = y + pl * plane;
+    for (int p = threadIdx.x; p < plane; p += blockDim.x) yp[p] = (((xp[p] - mm) * s) * gg) + bb;
+  }
+}
+
+__global__ void bn_bwd_apply_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
+                                    const float* __restrict__ mean, const float* __restrict__ inv,
+                                    const double* __restrict__ pa, const double* __restrict__ pb, int slices, double m,
+                                    int64_t planes, int32_t c, int32_t plane, int training, float* __restrict__ dx) {
+  for (int64_t pl = blockIdx.x; pl < planes; pl += gridDim.x) {
+    int ch = (int)(pl % c);
+    double sg = 0.0, sb = 0.0;
+    for (int s = 0; s < slices; s++) {
+      sg += pa[(int64_t)s * c + ch];
+      sb += pb[(int64_t)s * c + ch];
+    }
+    float mm = mean[ch], s = inv[ch], k = gamma[ch] * s;
+    float cb = (float)(sb / m), cg = (float)(sg / m);
+    const float* xp = x + pl * plane;
+    const float* gp = g + pl * plane;
+    float* dp = dx + pl * plane;
+    for (int p = threadIdx.x; p < plane; p += blockDim.x)
+      dp[p] = training ? k * ((gp[p] - cb) - (((xp[p] - mm) * s) * cg)) : k * gp[p];
+  }
+}
+
+}  // namespace om
+
+using namespace om;
+
+extern "C" {
+
+int32_t om_layernorm_fwd(om_ctx* ctx, const float* x, const float* gamma, const float* beta, int32_t rows, int32_t cols,
+                         float eps, float* y, float* mean, float* inv) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "om_layernorm_fwd: [%d,%d]", rows, cols);
+  if (rows == 0 || cols == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_layernorm_fwd", 0, 8.0 * rows * (double)cols);
+  int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 8);
+  layernorm_fwd_kernel<<<grid, 256, 0, ctx->stream>>>(x, gamma, beta, rows, cols, eps, y, mean, inv);
+  OM_LAUNCH_CHECK(ctx, "om_layernorm_fwd");
+  return OM_OK;
+}
+
+int32_t om_layernorm_bwd(om_ctx* ctx, const float* g, const float* x, const float* gamma, const float* mean,
+                         const float* inv, int32_t rows, int32_t cols, float* dx, float* dgamma, float* dbeta,
+                         int32_t accumulate_params) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "om_layernorm_bwd: [%d,%d]", rows, cols);
+  if (cols == 0) return OM_OK;
+  if (cols > 1024) return fail(ctx, OM_ERR_UNSUPPORTED, "om_layernorm_bwd: rows wider than 1024 (%d) are not implemented", cols);
+  ProfileScope prof(ctx, "om_layernorm_bwd", 0, 12.0 * rows * (double)cols);
+  int chunks = (int)ceil_div(rows > 0 ? rows : 1, kLnRowsPerCta);
+  double *pg = nullptr, *pb = nullptr;
+  if (dgamma) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&pg));
+  if (dbeta) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&pb));
+  size_t smem = (dgamma || dbeta) ? sizeof(double) * 16 * (size_t)cols : 0;
+  int nc = (int)ceil_div(cols, 32);
+#define OM_LN_BWD(NC)                                                                                                  \
+  do {                                                                                                                 \
+    if (smem > 48 * 1024)                                                                                              \
+      OM_CUDA(ctx, cudaFuncSetAttribute(layernorm_bwd_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    layernorm_bwd_kernel<NC><<<chunks, 256, smem, ctx->stream>>>(g, x, gamma, mean, inv, rows, cols, dx, pg, pb);       \
+  } while (0)
+  if (nc <= 4) OM_LN_BWD(4);
+  else if (nc <= 8) OM_LN_BWD(8);
+  else if (nc <= 12) OM_LN_BWD(12);
+  else if (nc <= 16) OM_LN_BWD(16);
+  else if (nc <= 24) OM_LN_BWD(24);
+  else OM_LN_BWD(32);
+#undef OM_LN_BWD
+  if (dgamma || dbeta)
+    column_partials_finish_kernel<<<(unsigned)ceil_div(cols, 128), 128, 0, ctx->stream>>>(pg, pb, chunks, cols, dgamma, dbeta, accumulate_params);
+  if (pg) pool_free(ctx, pg);
+  if (pb) pool_free(ctx, pb);
+  OM_LAUNCH_CHECK(ctx, "om_layernorm_bwd");
+  return OM_OK;
+}
+
+static int bn_slices(int n) { return n < 16 ? (n > 0 ? n : 1) : 16; }
+
+int32_t om_batchnorm_fwd(om_ctx* ctx, const float* x, const float* gamma, const float* beta, float* running_mean,
+                         float* running_var, int32_t n, int32_t c, int32_t plane, int32_t training, float momentum,
+                         float eps, float* y, float* mean, float* inv) {
+  OM_CHECK_CTX(ctx);
+  if (n < 0 || c < 0 || plane < 0) return fail(ctx, OM_ERR_SHAPE, "om_batchnorm_fwd: n %d c %d plane %d", n, c, plane);
+  if (training && (int64_t)n * plane < 1) return fail(ctx, OM_ERR_SHAPE, "BatchNorm2d in training needs at least one value per channel.");
+  if (c == 0) return OM_OK;
+  double total = (double)n * c * plane;
+  ProfileScope prof(ctx, "om_batchnorm_fwd", 0, (training ? 16.0 : 8.0) * total);
+  if (training) {
+    int slices = bn_slices(n), ipc = (int)ceil_div(n, slices);
+    double *pa = nullptr, *mu64 = nullptr;
+    OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)slices * c, false, (void**)&pa));
+    OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)c, false, (void**)&mu64));
+    double m = (double)n * plane;
+    dim3 grid(c, slices);
+    bn_partial_kernel<0><<<grid, kBnThreads, 0, ctx->stream>>>(x, nullptr, nullptr, nullptr, nullptr, n, c, plane, ipc, pa, nullptr);
+    bn_mean_kernel<<<(unsigned)ceil_div(c, 128), 128, 0, ctx->stream>>>(pa, slices, c, m, mu64);
+    bn_partial_kernel<1><<<grid, kBnThreads, 0, ctx->stream>>>(x, nullptr, mu64, nullptr, nullptr, n, c, plane, ipc, pa, nullptr);
+    bn_finish_stats_kernel<<<(unsigned)ceil_div(c, 128), 128, 0, ctx->stream>>>(pa, mu64, slices, c, m, momentum, eps, mean, inv, running_mean, running_var);
+    pool_free(ctx, pa);
+    pool_free(ctx, mu64);
+  } else {
+    bn_eval_stats_kernel<<<(unsigned)ceil_div(c, 128), 128, 0, ctx->stream>>>(running_mean, running_var, c, eps, mean, inv);
+  }
+  int64_t planes = (int64_t)n * c;
+  if (planes > 0 && plane > 0) {
+    int threads = plane >= 256 ? 256 : (plane >= 64 ? 64 : 32);
+    bn_apply_kernel<<<(unsigned)std::min<int64_t>(planes, (int64_t)ctx->sm_count * 16), threads, 0, ctx->stream>>>(x, gamma, beta, mean, inv, planes, c, plane, y);
+  }
+  OM_LAUNCH_CHECK(ctx, "om_batchnorm_fwd");
+  return OM_OK;
+}
+
+int32_t om_batchnorm_bwd(om_ctx* ctx, const float* g, const float* x, const float* gamma, const float* mean,
+                         const float* inv, int32_t n, int32_t c, int32_t plane, int32_t training, float* dx,
+                         float* dgamma, float* dbeta, int32_t accumulate_params) {
+  OM_CHECK_CTX(ctx);
+  if (n < 0 || c < 0 || plane < 0) return fail(ctx, OM_ERR_SHAPE, "om_batchnorm_bwd: n %d c %d plane %d", n, c, plane);
+  if (c == 0) return OM_OK;
+  double total = (double)n * c * plane;
+  ProfileScope prof(ctx, "om_batchnorm_bwd", 0, 20.0 * total);
+  int slices = bn_slices(n), ipc = (int)ceil_div(n > 0 ? n : 1, slices);
+  double *pa = nullptr, *pb = nullptr;
+  OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)slices * c, false, (void**)&pa));
+  OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)slices * c, false, (void**)&pb));
+  bn_partial_kernel<2><<<dim3(c, slices), kBnThreads, 0, ctx->stream>>>(x, g, nullptr, mean, inv, n, c, plane, ipc, pa, pb);
+  int64_t planes = (int64_t)n * c;
+  if (dx && planes > 0 && plane > 0) {
+    int threads = plane >= 256 ? 256 : (plane >= 64 ? 64 : 32);
+    bn_bwd_apply_kernel<<<(unsigned)std::min<int64_t>(planes, (int64_t)ctx->sm_count * 16), threads, 0, ctx->stream>>>(
+        g, x, gamma, mean, inv, pa, pb, slices, (double)n * plane, planes, c, plane, training, dx);
+  }
+  if (dgamma || dbeta)
+    column_partials_finish_kernel<<<(unsigned)ceil_div(c, 128), 128, 0, ctx->stream>>>(pa, pb, slices, c, dgamma, dbeta, accumulate_params);
+  pool_free(ctx, pa);
+  pool_free(ctx, pb);
+  OM_LAUNCH_CHECK(ctx, "om_batchnorm_bwd");
+  return OM_OK;
+}
+
+}  // extern "C"
