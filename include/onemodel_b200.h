@@ -93,6 +93,8 @@ int32_t om_sync(om_ctx* ctx);
 int32_t om_graph_begin(om_ctx* ctx);
 int32_t om_graph_end(om_ctx* ctx, void** graph_exec);
 int32_t om_graph_launch(om_ctx* ctx, void* graph_exec);
+/* Number of kernel nodes in the graph produced by the last om_graph_end on this context. */
+int32_t om_graph_last_kernel_nodes(om_ctx* ctx, int32_t* n);
 int32_t om_graph_destroy(om_ctx* ctx, void* graph_exec);
 
 /* Per-entry-point device timers (CUDA events on the context's stream around every call).

@@ -47,6 +47,7 @@ struct om_ctx {
   om::Pool pool;
   bool profiling = false;
   bool capturing = false;
+  int32_t last_graph_kernel_nodes = 0;
   std::map<std::string, om::ProfileEntry> profile;
   std::vector<cudaEvent_t> event_pool;
   om::DpState* dp = nullptr;

@@ -327,11 +327,31 @@ int32_t om_graph_end(om_ctx* ctx, void** graph_exec) {
   ctx->capturing = false;
   cudaGraph_t graph = nullptr;
   OM_CUDA(ctx, cudaStreamEndCapture(ctx->stream, &graph));
+  {
+    size_t n = 0;
+    ctx->last_graph_kernel_nodes = 0;
+    if (cudaGraphGetNodes(graph, nullptr, &n) == cudaSuccess && n > 0) {
+      std::vector<cudaGraphNode_t> nodes(n);
+      if (cudaGraphGetNodes(graph, nodes.data(), &n) == cudaSuccess) {
+        for (size_t i = 0; i < n; i++) {
+          cudaGraphNodeType type;
+          if (cudaGraphNodeGetType(nodes[i], &type) == cudaSuccess && type == cudaGraphNodeTypeKernel)
+            ctx->last_graph_kernel_nodes++;
+        }
+      }
+    }
+  }
   cudaGraphExec_t exec = nullptr;
   cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
   cudaGraphDestroy(graph);
   if (e != cudaSuccess) return check_cuda(ctx, e, "cudaGraphInstantiate");
   *graph_exec = (void*)exec;
+  return OM_OK;
+}
+
+int32_t om_graph_last_kernel_nodes(om_ctx* ctx, int32_t* n) {
+  if (!ctx || !n) return OM_ERR_ARG;
+  *n = ctx->last_graph_kernel_nodes;
   return OM_OK;
 }
 

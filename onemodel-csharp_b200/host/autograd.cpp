@@ -1,0 +1,227 @@
+// The tape and the reverse-mode engine: the same traversal and accumulation order as the reference's
+// Backprop.Run / Engine.Execute / Emit / AccumulateLeaf (src/OneModel/Tensors/Autograd/Engine.cs:28-344).
+#include <atomic>
+
+#include "omh.hpp"
+
+namespace omh {
+
+static thread_local bool t_grad_enabled = true;
+static thread_local ActivationScope* t_scope = nullptr;
+static std::atomic<int> s_pass{0};
+std::function<void(AutogradMeta*)> Backprop::GradReadyHook;
+
+bool GradMode::Enabled() { return t_grad_enabled; }
+GradMode::NoGrad::NoGrad() : prev(t_grad_enabled) { t_grad_enabled = false; }
+GradMode::NoGrad::~NoGrad() { t_grad_enabled = prev; }
+
+ActivationScope::ActivationScope() : outer(t_scope) { t_scope = this; }
+ActivationScope::~ActivationScope() {
+  tracked.clear();
+  t_scope = outer;
+}
+void ActivationScope::Track(const Tensor& t) {
+  if (t_scope) t_scope->tracked.push_back(t);
+}
+
+std::shared_ptr<BackwardRecord> BackwardRecord::Create(OpKind op, int savedSlots, const std::vector<Tensor>& inputs) {
+  auto rec = std::make_shared<BackwardRecord>();
+  rec->Op = op;
+  rec->SavedSlots.resize(savedSlots);
+  for (const Tensor& t : inputs) {
+    rec->Inputs.push_back(t.RequiresGrad() ? t.Autograd() : nullptr);
+    rec->InputShapes.push_back(t.GetShape());
+    rec->InputTypes.push_back(t.GetDType());
+  }
+  return rec;
+}
+
+std::shared_ptr<BackwardRecord> BackwardRecord::Create(OpKind op, int savedSlots, std::initializer_list<const Tensor*> inputs) {
+  std::vector<Tensor> v;
+  for (const Tensor* t : inputs) v.push_back(*t);
+  return Create(op, savedSlots, v);
+}
+
+Tensor BackwardRecord::Attach(const Tensor& output, int outputIndex) {
+  auto meta = std::make_shared<AutogradMeta>();
+  meta->RequiresGrad = true;
+  meta->GradFn = shared_from_this();
+  meta->OutputIndex = outputIndex;
+  return output.WithAutograd(meta);
+}
+
+void BackwardRecord::Release() {
+  IsReleased = true;
+  for (Tensor& t : SavedSlots) t = Tensor();
+}
+
+void Backprop::Run(const Tensor& root, const Tensor* gradient, bool retainGraph) {
+  if (root.IsEmpty() || !root.RequiresGrad()) throw InvalidOperationException("Backward needs a tensor that requires gradients.");
+  Tensor g;
+  if (gradient) {
+    if (gradient->GetShape() != root.GetShape())
+      throw TensorShapeException("The gradient has shape " + gradient->GetShape().ToString() + ", the tensor " + root.GetShape().ToString() + ".");
+    g = gradient->Clone();
+  } else {
+    if (root.Length() != 1) throw TensorShapeException("Backward without a gradient needs a one-element tensor.");
+    g = Tensor::Create(DType::F32, root.GetShape());
+    g.Fill(1.f);
+  }
+  auto meta = root.Autograd();
+  GradMode::NoGrad noGrad;
+  Engine engine;
+  if (!meta->GradFn) {
+    Engine::AccumulateLeaf(*meta, g, true);
+    return;
+  }
+  engine.Execute(meta->GradFn, g, retainGraph);
+}
+
+void Backprop::ZeroGrad(const Tensor& leaf) {
+  auto& m = leaf.Autograd();
+  if (m && !m->Grad.IsEmpty()) m->GradIsZero = true;
+}
+
+void Backprop::ClearGrad(const Tensor& leaf) {
+  auto& m = leaf.Autograd();
+  if (m) {
+    m->Grad = Tensor();
+    m->GradIsZero = false;
+  }
+}
+
+// Leaves reached by the traversal, with the number of tape edges that will deliver a gradient to each: when the
+// count reaches zero the leaf's gradient is final for this pass.
+static thread_local std::vector<std::pair<AutogradMeta*, int>>* t_leaf_edges = nullptr;
+
+static void leaf_arrived(AutogradMeta* leaf) {
+  if (!t_leaf_edges) return;
+  for (auto& kv : *t_leaf_edges) {
+    if (kv.first == leaf) {
+      if (--kv.second == 0 && Backprop::GradReadyHook) Backprop::GradReadyHook(leaf);
+      return;
+    }
+  }
+}
+
+void Engine::Execute(const std::shared_ptr<BackwardRecord>& root, Tensor rootGrad, bool retain) {
+  int mark = ++s_pass;
+  std::vector<BackwardRecord*> order;
+  std::vector<std::pair<BackwardRecord*, int>> stack;
+  std::vector<std::pair<AutogradMeta*, int>> leaf_edges;
+  root->VisitMark = mark;
+  stack.emplace_back(root.get(), 0);
+  while (!stack.empty()) {
+    BackwardRecord* rec = stack.back().first;
+    int next = stack.back().second;
+    if (rec->IsReleased)
+      throw InvalidOperationException(
+          "Backward ran through a graph whose saved tensors were already freed by an earlier backward. Pass retainGraph: true to the first call.");
+    if (next < rec->InputCount()) {
+      stack.back().second = next + 1;
+      AutogradMeta* in = rec->Inputs[next].get();
+      if (in && in->GradFn) {
+        BackwardRecord* producer = in->GradFn.get();
+        if (producer->VisitMark != mark) {
+          producer->VisitMark = mark;
+          stack.emplace_back(producer, 0);
+        }
+      } else if (in && in->RequiresGrad) {
+        bool found = false;
+        for (auto& kv : leaf_edges)
+          if (kv.first == in) {
+            kv.second++;
+            found = true;
+            break;
+          }
+        if (!found) leaf_edges.emplace_back(in, 1);
+      }
+    } else {
+      order.push_back(rec);
+      stack.pop_back();
+    }
+  }
+
+  root->PendingGrad = rootGrad;
+  t_leaf_edges = &leaf_edges;
+  struct Cleanup {
+    std::vector<BackwardRecord*>& order;
+    ~Cleanup() {
+      for (BackwardRecord* r : order) r->PendingGrad = Tensor();
+      t_leaf_edges = nullptr;
+    }
+  } cleanup{order};
+  for (int i = (int)order.size() - 1; i >= 0; i--) {
+    BackwardRecord* rec = order[i];
+    Tensor g = rec->PendingGrad;
+    rec->PendingGrad = Tensor();
+    if (g.IsEmpty()) {
+      // No gradient reached this record: its leaf inputs still count as served.
+      for (auto& in : rec->Inputs)
+        if (in && !in->GradFn) leaf_arrived(in.get());
+      continue;
+    }
+    RunBackwardOp(*this, *rec, g);
+    if (!retain) rec->Release();
+  }
+}
+
+void Engine::Emit(BackwardRecord& rec, int i, const Tensor& grad, bool owned) {
+  AutogradMeta* meta = rec.Inputs[i].get();
+  if (!meta) return;
+  if (!meta->GradFn) {
+    AccumulateLeaf(*meta, grad, owned);
+    leaf_arrived(meta);
+    return;
+  }
+  BackwardRecord& p = *meta->GradFn;
+  if (p.PendingGrad.IsEmpty()) {
+    p.PendingGrad = owned ? grad : grad.Clone();
+  } else {
+    AddInto(p.PendingGrad, grad);
+  }
+}
+
+void Engine::AccumulateLeaf(AutogradMeta& leaf, const Tensor& grad, bool owned) {
+  if (!leaf.RequiresGrad) return;
+  if (leaf.Grad.IsEmpty()) {
+    // A view (aliased gradient) must not be adopted: the leaf's gradient outlives the step.
+    leaf.Grad = (owned && grad.IsContiguous() && grad.Offset() == 0) ? grad.Detach() : grad.Clone();
+    leaf.GradIsZero = false;
+  } else if (leaf.GradIsZero) {
+    // Logically 0 + grad: overwrite instead of zero-fill then add.
+    Tensor src = grad.Contiguous();
+    Check(om_memcpy_d2d(Device::Current(), leaf.Grad.RawData(), src.RawData(), (size_t)src.Length() * 4));
+    leaf.GradIsZero = false;
+  } else {
+    AddInto(leaf.Grad, grad);
+  }
+}
+
+bool Engine::LeafTarget(BackwardRecord& rec, int i, float** ptr, bool* accumulate) {
+  AutogradMeta* meta = rec.Inputs[i].get();
+  if (!meta || meta->GradFn || !meta->RequiresGrad) return false;
+  if (meta->Grad.IsEmpty()) {
+    meta->Grad = Tensor::Create(DType::F32, rec.InputShapes[i]);
+    meta->GradIsZero = true;
+  }
+  if (meta->Grad.GetShape() != rec.InputShapes[i]) return false;
+  *ptr = meta->Grad.Data();
+  *accumulate = !meta->GradIsZero;
+  return true;
+}
+
+void Engine::LeafWritten(BackwardRecord& rec, int i) {
+  AutogradMeta* meta = rec.Inputs[i].get();
+  meta->GradIsZero = false;
+  leaf_arrived(meta);
+}
+
+void Engine::AddInto(const Tensor& dst, const Tensor& src) {
+  if (dst.GetShape() != src.GetShape())
+    throw TensorShapeException("Gradient shape " + src.GetShape().ToString() + " does not match " + dst.GetShape().ToString() + ".");
+  Tensor s = src.Contiguous();
+  Check(om_add_into(Device::Current(), dst.Data(), s.Data(), dst.Length()));
+}
+
+}  // namespace omh

@@ -1,0 +1,389 @@
+// The backward function of every OpKind: reads the record and the incoming gradient (contiguous, the output's shape)
+// and emits one gradient per input that needs one, as BackwardOps.Run / RunNn do in the reference
+// (src/OneModel/Tensors/Autograd/BackwardOps.cs:13-145, BackwardNn.cs:7-143). All arithmetic runs on the device.
+#include "omh.hpp"
+
+namespace omh {
+
+static om_ctx* C() { return Device::Current(); }
+
+void RunSpatialBackward(Engine& e, BackwardRecord& r, const Tensor& g);  // backward_spatial.cpp
+
+// Sums g down to `target` (undoing a broadcast). Returns g itself with same = true when the shapes already match
+// (BackwardOps.SumTo, BackwardOps.cs:201-269).
+static Tensor SumTo(const Tensor& g, const Shape& target, bool* same) {
+  *same = g.GetShape() == target;
+  if (*same) return g;
+  int rank = g.Rank(), lead = rank - target.rank;
+  if (lead < 0) throw TensorShapeException("Cannot sum " + g.GetShape().ToString() + " down to " + target.ToString() + ".");
+  std::array<int64_t, kMaxRank> ts{};
+  int64_t acc = 1;
+  for (int ax = rank - 1; ax >= 0; ax--) {
+    int t = ax - lead;
+    if (t < 0 || target[t] == 1) {
+      ts[ax] = 0;
+    } else {
+      ts[ax] = acc;
+      acc *= target[t];
+    }
+  }
+  Tensor gc = g.Contiguous();
+  Tensor out = Tensor::Create(DType::F32, target);
+  Check(om_sum_to(C(), rank, gc.GetShape().d.data(), gc.Data(), ts.data(), out.Data(), out.Length()));
+  return out;
+}
+
+static Tensor UnaryGrad(om_unary_op op, const Tensor& g, const Tensor& saved) {
+  Tensor gc = g.Contiguous();
+  Tensor dx = Tensor::Create(DType::F32, saved.GetShape());
+  Check(om_unary_bwd(C(), op, gc.Data(), saved.Data(), dx.Data(), dx.Length()));
+  return dx;
+}
+
+static Tensor NegOf(const Tensor& g) {
+  Tensor gc = g.Contiguous();
+  Tensor r = Tensor::Create(DType::F32, g.GetShape());
+  Check(om_unary(C(), OM_NEG, gc.Data(), r.Data(), r.Length()));
+  return r;
+}
+
+// Add and Sub: the output gradient summed down to each input's shape; Sub negates the second (BackwardOps.cs:156-194).
+static void EmitSummed(Engine& e, BackwardRecord& r, const Tensor& g, bool negateSecond) {
+  bool need0 = r.NeedsInputGrad(0), need1 = r.NeedsInputGrad(1);
+  if (need0) {
+    bool same;
+    Tensor s = SumTo(g, r.InputShapes[0], &same);
+    if (!same) Engine::Emit(r, 0, s, true);
+    else if (!need1) e.EmitAliased(r, 0, g);
+    else Engine::Emit(r, 0, g, false);
+  }
+  if (need1) {
+    bool same;
+    Tensor s = SumTo(g, r.InputShapes[1], &same);
+    if (negateSecond) Engine::Emit(r, 1, NegOf(s), true);
+    else if (!same) Engine::Emit(r, 1, s, true);
+    else e.EmitAliased(r, 1, g);
+  }
+}
+
+static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
+  const Tensor& x = r.Saved(0);
+  const Tensor& w = r.Saved(1);
+  int rows = (int)r.Ints[0], inF = (int)r.Ints[1], outF = (int)r.Ints[2];
+  Tensor gc = g.Contiguous();
+  bool hasBias = r.InputCount() == 3;
+  Tensor dx;
+  if (r.NeedsInputGrad(0)) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+  // Weight and bias gradients go straight into the leaf's gradient buffer when there is one.
+  float *dwp = nullptr, *dbp = nullptr;
+  bool accw = false, accb = false, wleaf = false, bleaf = false;
+  Tensor dw, db;
+  if (r.NeedsInputGrad(1)) {
+    wleaf = Engine::LeafTarget(r, 1, &dwp, &accw);
+    if (!wleaf) {
+      dw = Tensor::Create(DType::F32, r.InputShapes[1]);
+      dwp = dw.Data();
+    }
+  }
+  if (hasBias && r.NeedsInputGrad(2)) {
+    bleaf = Engine::LeafTarget(r, 2, &dbp, &accb);
+    if (!bleaf) {
+      db = Tensor::Create(DType::F32, r.InputShapes[2]);
+      dbp = db.Data();
+    }
+  }
+  if (accw == accb || !dwp || !dbp) {
+    Check(om_linear_bwd(C(), gc.Data(), x.Data(), w.Data(), rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, dbp,
+                        (dwp ? accw : accb) ? 1 : 0));
+  } else {
+    Check(om_linear_bwd(C(), gc.Data(), x.Data(), w.Data(), rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, nullptr, accw));
+    Check(om_linear_bwd(C(), gc.Data(), x.Data(), w.Data(), rows, inF, outF, nullptr, nullptr, dbp, accb));
+  }
+  // Emission order of the reference's record chain: bias (Add record), then input and weight (MatMul record).
+  if (hasBias && r.NeedsInputGrad(2)) {
+    if (bleaf) Engine::LeafWritten(r, 2); else Engine::Emit(r, 2, db, true);
+  }
+  if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
+  if (r.NeedsInputGrad(1)) {
+    if (wleaf) Engine::LeafWritten(r, 1); else Engine::Emit(r, 1, dw, true);
+  }
+}
+
+static bool GemmLayout(const Tensor& t, int* trans, int* ld) {
+  int64_t s0 = t.Strides()[0], s1 = t.Strides()[1];
+  int rr = t.GetShape()[0], c = t.GetShape()[1];
+  if ((s1 == 1 || c == 1) && (s0 >= c || rr == 1)) {
+    *trans = 0;
+    *ld = (int)(rr == 1 ? std::max<int64_t>(c, 1) : s0);
+    return true;
+  }
+  if ((s0 == 1 || rr == 1) && (s1 >= rr || c == 1)) {
+    *trans = 1;
+    *ld = (int)(c == 1 ? std::max<int64_t>(rr, 1) : s1);
+    return true;
+  }
+  return false;
+}
+
+// dA = g B^T, dB = A^T g (BackwardOps.cs:69-82); the saved operands may be transposed views, read in place.
+static void MatMulBackward(BackwardRecord& r, const Tensor& g) {
+  const Tensor& a = r.Saved(0);
+  const Tensor& b = r.Saved(1);
+  Tensor gc = g.Contiguous();
+  int m = a.GetShape()[0], k = a.GetShape()[1], n = b.GetShape()[1];
+  int ta, tb, lda, ldb;
+  GemmLayout(a, &ta, &lda);
+  GemmLayout(b, &tb, &ldb);
+  if (r.NeedsInputGrad(0)) {
+    Tensor da = Tensor::Create(DType::F32, Shape{m, k});
+    // da[m,k] = g[m,n] * op(b)^T : B operand of the product is op(b)^T, i.e. transposed flag flipped.
+    Check(om_matmul(C(), 0, !tb, m, k, n, gc.Data(), n, b.Data(), ldb, da.Data(), k, 0));
+    Engine::Emit(r, 0, da, true);
+  }
+  if (r.NeedsInputGrad(1)) {
+    Tensor db = Tensor::Create(DType::F32, Shape{k, n});
+    Check(om_matmul(C(), !ta, 0, k, n, m, a.Data(), lda, gc.Data(), n, db.Data(), n, 0));
+    Engine::Emit(r, 1, db, true);
+  }
+}
+
+static void ReduceBackward(BackwardRecord& r, const Tensor& g) {
+  const Shape& in = r.InputShapes[0];
+  int axis = (int)r.Ints[0];
+  int64_t outer = 1, n = 1, inner = 1;
+  if (axis < 0) {
+    n = in.Length();
+  } else {
+    n = in[axis];
+    for (int i = 0; i < axis; i++) outer *= in[i];
+    for (int i = axis + 1; i < in.rank; i++) inner *= in[i];
+  }
+  Tensor gc = g.Contiguous();
+  Tensor dx = Tensor::Create(DType::F32, in);
+  Check(om_reduce_bwd(C(), gc.Data(), outer, n, inner, r.Op == OpKind::Mean, dx.Data()));
+  Engine::Emit(r, 0, dx, true);
+}
+
+static void NormParamGrads(BackwardRecord& r, float** dg, float** db, bool* acc, Tensor* tg, Tensor* tb, bool* gleaf, bool* bleaf) {
+  bool ag = false, ab = false;
+  *dg = *db = nullptr;
+  *gleaf = *bleaf = false;
+  if (r.NeedsInputGrad(1)) {
+    *gleaf = Engine::LeafTarget(r, 1, dg, &ag);
+    if (!*gleaf) {
+      *tg = Tensor::Create(DType::F32, r.InputShapes[1]);
+      *dg = tg->Data();
+    }
+  }
+  if (r.NeedsInputGrad(2)) {
+    *bleaf = Engine::LeafTarget(r, 2, db, &ab);
+    if (!*bleaf) {
+      *tb = Tensor::Create(DType::F32, r.InputShapes[2]);
+      *db = tb->Data();
+    }
+  }
+  if (*dg && *db && ag != ab) {
+    // Mixed accumulate states cannot share one launch: fall back to temporaries and Emit.
+    if (*gleaf) { *tg = Tensor::Create(DType::F32, r.InputShapes[1]); *dg = tg->Data(); *gleaf = false; }
+    if (*bleaf) { *tb = Tensor::Create(DType::F32, r.InputShapes[2]); *db = tb->Data(); *bleaf = false; }
+    ag = ab = false;
+  }
+  *acc = *dg ? ag : ab;
+}
+
+static void EmitNormParams(BackwardRecord& r, const Tensor& tg, const Tensor& tb, bool gleaf, bool bleaf) {
+  if (r.NeedsInputGrad(1)) {
+    if (gleaf) Engine::LeafWritten(r, 1); else Engine::Emit(r, 1, tg, true);
+  }
+  if (r.NeedsInputGrad(2)) {
+    if (bleaf) Engine::LeafWritten(r, 2); else Engine::Emit(r, 2, tb, true);
+  }
+}
+
+static void LayerNormBackward(BackwardRecord& r, const Tensor& g) {
+  const Tensor &x = r.Saved(0), &gamma = r.Saved(1), &mean = r.Saved(2), &inv = r.Saved(3);
+  int cols = x.GetShape()[x.Rank() - 1];
+  int rows = cols == 0 ? 0 : (int)(x.Length() / cols);
+  Tensor gc = g.Contiguous();
+  Tensor dx;
+  if (r.NeedsInputGrad(0)) dx = Tensor::Create(DType::F32, x.GetShape());
+  float *dg, *db;
+  bool acc, gleaf, bleaf;
+  Tensor tg, tb;
+  NormParamGrads(r, &dg, &db, &acc, &tg, &tb, &gleaf, &bleaf);
+  Check(om_layernorm_bwd(C(), gc.Data(), x.Data(), gamma.Data(), mean.Data(), inv.Data(), rows, cols,
+                         dx.IsEmpty() ? nullptr : dx.Data(), dg, db, acc));
+  if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
+  EmitNormParams(r, tg, tb, gleaf, bleaf);
+}
+
+static void BatchNormBackward(BackwardRecord& r, const Tensor& g) {
+  const Tensor &x = r.Saved(0), &gamma = r.Saved(1), &mean = r.Saved(2), &inv = r.Saved(3);
+  int n = x.GetShape()[0], c = x.GetShape()[1], plane = (int)(x.Length() / std::max(1, n * c));
+  Tensor gc = g.Contiguous();
+  Tensor dx;
+  if (r.NeedsInputGrad(0)) dx = Tensor::Create(DType::F32, x.GetShape());
+  float *dg, *db;
+  bool acc, gleaf, bleaf;
+  Tensor tg, tb;
+  NormParamGrads(r, &dg, &db, &acc, &tg, &tb, &gleaf, &bleaf);
+  Check(om_batchnorm_bwd(C(), gc.Data(), x.Data(), gamma.Data(), mean.Data(), inv.Data(), n, c, plane, r.Ints[0] != 0,
+                         dx.IsEmpty() ? nullptr : dx.Data(), dg, db, acc));
+  if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
+  EmitNormParams(r, tg, tb, gleaf, bleaf);
+}
+
+static void EmbeddingBackward(BackwardRecord& r, const Tensor& g) {
+  const Tensor& ids = r.Saved(0);
+  const Shape& ts = r.InputShapes[0];
+  Tensor gc = g.Contiguous();
+  float* dt = nullptr;
+  bool acc = false;
+  Tensor tmp;
+  bool leaf = Engine::LeafTarget(r, 0, &dt, &acc);
+  if (!leaf) {
+    tmp = Tensor::Create(DType::F32, ts);
+    dt = tmp.Data();
+  }
+  Check(om_embedding_bwd(C(), gc.Data(), ids.RawData(), (int32_t)ids.GetDType(), ids.Length(), ts[0], ts[1], r.Ints[0], dt, acc));
+  if (leaf) Engine::LeafWritten(r, 0); else Engine::Emit(r, 0, tmp, true);
+}
+
+static void AttentionBackward(BackwardRecord& r, const Tensor& g) {
+  const Tensor &q = r.Saved(0), &k = r.Saved(1), &v = r.Saved(2), &mask = r.Saved(3);
+  int b = q.GetShape()[0], h = q.GetShape()[1], lq = q.GetShape()[2], d = q.GetShape()[3], lk = k.GetShape()[2];
+  Tensor gc = g.Contiguous();
+  Tensor dq, dk, dv;
+  if (r.NeedsInputGrad(0)) dq = Tensor::Create(DType::F32, q.GetShape());
+  if (r.NeedsInputGrad(1)) dk = Tensor::Create(DType::F32, k.GetShape());
+  if (r.NeedsInputGrad(2)) dv = Tensor::Create(DType::F32, v.GetShape());
+  Check(om_attention_bwd(C(), gc.Data(), q.Data(), k.Data(), v.Data(), mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0],
+                         nullptr, b, h, lq, lk, d, (float)r.Floats[0], dq.IsEmpty() ? nullptr : dq.Data(),
+                         dk.IsEmpty() ? nullptr : dk.Data(), dv.IsEmpty() ? nullptr : dv.Data()));
+  if (!dq.IsEmpty()) Engine::Emit(r, 0, dq, true);
+  if (!dk.IsEmpty()) Engine::Emit(r, 1, dk, true);
+  if (!dv.IsEmpty()) Engine::Emit(r, 2, dv, true);
+}
+
+void RunBackwardOp(Engine& e, BackwardRecord& r, const Tensor& g) {
+  switch (r.Op) {
+    case OpKind::Add: EmitSummed(e, r, g, false); break;
+    case OpKind::Sub: EmitSummed(e, r, g, true); break;
+    case OpKind::Mul:
+      for (int i = 0; i < 2; i++)
+        if (r.NeedsInputGrad(i)) {
+          GradMode::NoGrad ng;
+          Tensor t = Ops::Mul(g, r.Saved(1 - i));
+          bool same;
+          Engine::Emit(r, i, SumTo(t, r.InputShapes[i], &same), true);
+        }
+      break;
+    case OpKind::Div:
+      if (r.NeedsInputGrad(0)) {
+        Tensor t = Ops::Div(g, r.Saved(1));
+        bool same;
+        Engine::Emit(r, 0, SumTo(t, r.InputShapes[0], &same), true);
+      }
+      if (r.NeedsInputGrad(1)) {
+        // d(a/b)/db = -a/b^2
+        const Tensor& b = r.Saved(1);
+        Tensor t = Ops::Neg(Ops::Div(Ops::Mul(g, r.Saved(0)), Ops::Mul(b, b)));
+        bool same;
+        Engine::Emit(r, 1, SumTo(t, r.InputShapes[1], &same), true);
+      }
+      break;
+    case OpKind::Neg: Engine::Emit(r, 0, NegOf(g), true); break;
+    case OpKind::Relu: Engine::Emit(r, 0, UnaryGrad(OM_RELU, g, r.Saved(0)), true); break;
+    case OpKind::Gelu: Engine::Emit(r, 0, UnaryGrad(r.Ints[0] == 1 ? OM_GELU_TANH : OM_GELU_ERF, g, r.Saved(0)), true); break;
+    case OpKind::Sigmoid: Engine::Emit(r, 0, UnaryGrad(OM_SIGMOID, g, r.Saved(0)), true); break;
+    case OpKind::Tanh: Engine::Emit(r, 0, UnaryGrad(OM_TANH, g, r.Saved(0)), true); break;
+    case OpKind::MatMul: MatMulBackward(r, g); break;
+    case OpKind::Linear: LinearBackward(e, r, g); break;
+    case OpKind::Slice: {
+      Tensor dx = Tensor::Zeros(DType::F32, r.InputShapes[0]);
+      Tensor dst = dx.Slice((int)r.Ints[0], (int)r.Ints[1], (int)r.Ints[2], (int)r.Ints[3]);
+      Check(om_strided_copy(C(), g.Rank(), g.GetShape().d.data(), g.Data(), g.Strides().data(), dst.Data(), dst.Strides().data()));
+      Engine::Emit(r, 0, dx, true);
+      break;
+    }
+    case OpKind::Select: {
+      Tensor dx = Tensor::Zeros(DType::F32, r.InputShapes[0]);
+      Tensor dst = dx.Select((int)r.Ints[0], (int)r.Ints[1]);
+      Check(om_strided_copy(C(), g.Rank(), g.GetShape().d.data(), g.Data(), g.Strides().data(), dst.Data(), dst.Strides().data()));
+      Engine::Emit(r, 0, dx, true);
+      break;
+    }
+    case OpKind::Permute: {
+      std::vector<int> inv(r.Ints.size());
+      for (size_t i = 0; i < r.Ints.size(); i++) inv[(size_t)r.Ints[i]] = (int)i;
+      Engine::Emit(r, 0, g.Permute(inv).Clone(), true);
+      break;
+    }
+    case OpKind::Reshape: e.EmitAliased(r, 0, g.Contiguous().Reshape(r.InputShapes[0])); break;
+    case OpKind::Expand: {
+      bool same;
+      Tensor s = SumTo(g, r.InputShapes[0], &same);
+      if (same) e.EmitAliased(r, 0, g); else Engine::Emit(r, 0, s, true);
+      break;
+    }
+    case OpKind::Flip: Engine::Emit(r, 0, g.Flip((int)r.Ints[0]).Clone(), true); break;
+    case OpKind::Sum:
+    case OpKind::Mean: ReduceBackward(r, g); break;
+    case OpKind::Softmax: {
+      const Tensor& y = r.Saved(0);
+      int cols = y.GetShape()[y.Rank() - 1];
+      int rows = cols == 0 ? 0 : (int)(y.Length() / cols);
+      Tensor gc = g.Contiguous();
+      Tensor dx = Tensor::Create(DType::F32, y.GetShape());
+      Check(om_softmax_bwd(C(), gc.Data(), y.Data(), rows, cols, dx.Data()));
+      Engine::Emit(r, 0, dx, true);
+      break;
+    }
+    case OpKind::LogSoftmax: {
+      const Tensor& y = r.Saved(0);
+      int cols = y.GetShape()[y.Rank() - 1];
+      int rows = cols == 0 ? 0 : (int)(y.Length() / cols);
+      Tensor gc = g.Contiguous();
+      Tensor dx = Tensor::Create(DType::F32, y.GetShape());
+      Check(om_logsoftmax_bwd(C(), gc.Data(), y.Data(), rows, cols, dx.Data()));
+      Engine::Emit(r, 0, dx, true);
+      break;
+    }
+    case OpKind::NllLoss: {
+      const Tensor& t = r.Saved(0);
+      const Shape& ls = r.InputShapes[0];
+      Tensor gc = g.Contiguous();
+      Tensor dx = Tensor::Create(DType::F32, ls);
+      Check(om_nll_bwd(C(), gc.Data(), t.RawData(), (int32_t)t.GetDType(), ls[0], ls[1], r.Ints[0] != 0, r.Ints[1], dx.Data()));
+      Engine::Emit(r, 0, dx, true);
+      break;
+    }
+    case OpKind::CrossEntropy: {
+      const Tensor &logp = r.Saved(0), &t = r.Saved(1);
+      const Shape& ls = r.InputShapes[0];
+      Tensor gc = g.Contiguous();
+      Tensor dx = Tensor::Create(DType::F32, ls);
+      Check(om_cross_entropy_bwd(C(), gc.Data(), logp.Data(), t.RawData(), (int32_t)t.GetDType(), ls[0], ls[1],
+                                 r.Ints[0] != 0, r.Ints[1], (float)r.Floats[0], dx.Data()));
+      Engine::Emit(r, 0, dx, true);
+      break;
+    }
+    case OpKind::LayerNorm: LayerNormBackward(r, g); break;
+    case OpKind::BatchNorm: BatchNormBackward(r, g); break;
+    case OpKind::Embedding: EmbeddingBackward(r, g); break;
+    case OpKind::Attention: AttentionBackward(r, g); break;
+    case OpKind::Concat: {
+      int axis = (int)r.Ints[0];
+      int start = 0;
+      for (int i = 0; i < r.InputCount(); i++) {
+        int len = r.InputShapes[i][axis];
+        if (r.NeedsInputGrad(i)) Engine::Emit(r, i, g.Slice(axis, start, start + len).Clone(), true);
+        start += len;
+      }
+      break;
+    }
+    default: RunSpatialBackward(e, r, g); break;
+  }
+}
+
+}  // namespace omh

@@ -1,0 +1,258 @@
+// Plain-C surface of the host mirror (libonemodel_b200_host.so), used by the Python tests and the bench through
+// ctypes: tensors are opaque handles, operations are dispatched by name, and every C++ exception becomes a status
+// code (1 shape, 2 index, 9 invalid operation, 10 other) with the message kept for omh_last_error.
+#include <string.h>
+
+#include <map>
+
+#include "omh.hpp"
+
+using namespace omh;
+
+#define OMH_API extern "C" __attribute__((visibility("default")))
+
+static thread_local std::string t_error;
+
+template <class F>
+static int32_t Guard(F&& f) {
+  try {
+    f();
+    return 0;
+  } catch (const TensorShapeException& e) {
+    t_error = e.what();
+    return 1;
+  } catch (const ArgumentOutOfRangeException& e) {
+    t_error = e.what();
+    return 2;
+  } catch (const InvalidOperationException& e) {
+    t_error = e.what();
+    return 9;
+  } catch (const BackendException& e) {
+    t_error = e.what();
+    return 100 + e.status;
+  } catch (const std::exception& e) {
+    t_error = e.what();
+    return 10;
+  }
+}
+
+struct omh_tensor { Tensor t; };
+static omh_tensor* Box(const Tensor& t) { return t.IsEmpty() ? nullptr : new omh_tensor{t}; }
+static Tensor Unbox(const omh_tensor* h) { return h ? h->t : Tensor(); }
+
+OMH_API int32_t omh_last_error(char* buf, size_t n) {
+  if (!buf || !n) return 1;
+  size_t len = std::min(n - 1, t_error.size());
+  memcpy(buf, t_error.data(), len);
+  buf[len] = 0;
+  return 0;
+}
+
+OMH_API int32_t omh_init(int32_t device, uint32_t flags, om_ctx** out) {
+  om_ctx* ctx = nullptr;
+  int32_t s = om_ctx_create(device, flags, &ctx);
+  if (s != OM_OK) {
+    char buf[512];
+    om_last_error(nullptr, buf, sizeof buf);
+    t_error = buf;
+    return 100 + s;
+  }
+  Device::SetCurrent(ctx);
+  if (out) *out = ctx;
+  return 0;
+}
+
+OMH_API int32_t omh_set_current(om_ctx* ctx) {
+  Device::SetCurrent(ctx);
+  return 0;
+}
+
+OMH_API int32_t omh_tensor_from_host(int32_t dtype, int32_t rank, const int32_t* shape, const void* data, omh_tensor** out) {
+  return Guard([&] {
+    Shape s;
+    if (rank > kMaxRank) throw TensorShapeException("Too many dimensions.");
+    s.rank = rank;
+    for (int i = 0; i < rank; i++) s.d[i] = shape[i];
+    Tensor t = Tensor::Create((DType)dtype, s);
+    if (data && t.Length() > 0) t.CopyFromHost(data);
+    *out = new omh_tensor{t};
+  });
+}
+
+OMH_API int32_t omh_tensor_free(omh_tensor* h) {
+  delete h;
+  return 0;
+}
+
+OMH_API int32_t omh_tensor_info(const omh_tensor* h, int32_t* dtype, int32_t* rank, int32_t* shape, int64_t* strides) {
+  if (!h) return 1;
+  *dtype = (int32_t)h->t.GetDType();
+  *rank = h->t.Rank();
+  for (int i = 0; i < h->t.Rank(); i++) {
+    shape[i] = h->t.GetShape()[i];
+    if (strides) strides[i] = h->t.Strides()[i];
+  }
+  return 0;
+}
+
+OMH_API int32_t omh_tensor_to_host(const omh_tensor* h, void* dst) {
+  return Guard([&] { h->t.CopyToHost(dst); });
+}
+
+OMH_API int32_t omh_tensor_copy_from_host(omh_tensor* h, const void* src) {
+  return Guard([&] { h->t.CopyFromHost(src); });
+}
+
+OMH_API void* omh_tensor_data(const omh_tensor* h) { return h ? h->t.RawData() : nullptr; }
+
+OMH_API int32_t omh_tensor_set_requires_grad(omh_tensor* h, int32_t on) {
+  return Guard([&] { h->t.SetRequiresGrad(on != 0); });
+}
+
+OMH_API int32_t omh_tensor_requires_grad(const omh_tensor* h) { return h && h->t.RequiresGrad(); }
+
+OMH_API int32_t omh_tensor_grad(const omh_tensor* h, omh_tensor** out) {
+  return Guard([&] { *out = Box(h->t.Grad()); });
+}
+
+OMH_API int32_t omh_tensor_zero_grad(const omh_tensor* h) {
+  return Guard([&] { Backprop::ZeroGrad(h->t); });
+}
+
+OMH_API int32_t omh_tensor_clear_grad(const omh_tensor* h) {
+  return Guard([&] { Backprop::ClearGrad(h->t); });
+}
+
+OMH_API int32_t omh_backward(const omh_tensor* h, const omh_tensor* gradient, int32_t retain) {
+  return Guard([&] {
+    Tensor g = Unbox(gradient);
+    h->t.Backward(gradient ? &g : nullptr, retain != 0);
+  });
+}
+
+OMH_API int32_t omh_no_grad(int32_t on) {
+  static thread_local std::vector<GradMode::NoGrad*> stack;
+  if (on) stack.push_back(new GradMode::NoGrad());
+  else if (!stack.empty()) {
+    delete stack.back();
+    stack.pop_back();
+  }
+  return 0;
+}
+
+// One entry for every operation and view: inputs are handles (null = empty tensor), plus integer and float arguments.
+OMH_API int32_t omh_call(const char* op, int32_t n_in, omh_tensor* const* in, int32_t n_ints, const int64_t* ints,
+                         int32_t n_floats, const double* fl, omh_tensor** out) {
+  return Guard([&] {
+    std::string name = op;
+    auto T = [&](int i) { return i < n_in ? Unbox(in[i]) : Tensor(); };
+    auto I = [&](int i, int64_t dflt = 0) { return i < n_ints ? ints[i] : dflt; };
+    auto F = [&](int i, double dflt = 0) { return i < n_floats ? fl[i] : dflt; };
+    auto ShapeFromInts = [&](int from) {
+      Shape s;
+      for (int i = from; i < n_ints; i++) s.d[s.rank++] = (int)ints[i];
+      return s;
+    };
+    Tensor r;
+    if (name == "add") r = Ops::Add(T(0), T(1));
+    else if (name == "sub") r = Ops::Sub(T(0), T(1));
+    else if (name == "mul") r = Ops::Mul(T(0), T(1));
+    else if (name == "div") r = Ops::Div(T(0), T(1));
+    else if (name == "neg") r = Ops::Neg(T(0));
+    else if (name == "relu") r = Ops::Relu(T(0));
+    else if (name == "gelu") r = Ops::Gelu(T(0), I(0) != 0);
+    else if (name == "sigmoid") r = Ops::Sigmoid(T(0));
+    else if (name == "tanh") r = Ops::Tanh(T(0));
+    else if (name == "matmul") r = Ops::MatMul(T(0), T(1));
+    else if (name == "sum") r = n_ints ? Ops::Sum(T(0), (int)I(0), I(1) != 0) : Ops::Sum(T(0));
+    else if (name == "mean") r = n_ints ? Ops::Mean(T(0), (int)I(0), I(1) != 0) : Ops::Mean(T(0));
+    else if (name == "softmax") r = Ops::Softmax(T(0), (int)I(0, -1));
+    else if (name == "log_softmax") r = Ops::LogSoftmax(T(0), (int)I(0, -1));
+    else if (name == "layer_norm") r = Ops::LayerNorm(T(0), T(1), T(2), (float)F(0, 1e-5));
+    else if (name == "batch_norm2d") r = Ops::BatchNorm2d(T(0), T(1), T(2), T(3), T(4), I(0) != 0, (float)F(0, 0.1), (float)F(1, 1e-5));
+    else if (name == "embedding") r = Ops::Embedding(T(0), T(1), (int)I(0, -1));
+    else if (name == "nll_loss") r = Ops::NllLoss(T(0), T(1), I(0, 1) != 0, (int)I(1, -100));
+    else if (name == "cross_entropy") r = Ops::CrossEntropy(T(0), T(1), I(0, 1) != 0, (int)I(1, -100), (float)F(0, 0));
+    else if (name == "linear") r = Ops::Linear(T(0), T(1), T(2));
+    else if (name == "attention") r = Ops::Attention(T(0), T(1), T(2), T(3), (float)F(0, 0));
+    else if (name == "concat") {
+      std::vector<Tensor> xs;
+      for (int i = 0; i < n_in; i++) xs.push_back(T(i));
+      r = Ops::Concat(xs, (int)I(0));
+    } else if (name == "global_avg_pool2d") r = Ops::GlobalAvgPool2d(T(0));
+    else if (name == "conv2d") {
+      Conv2dParams p;
+      p.strideH = (int)I(0, 1); p.strideW = (int)I(1, 1);
+      p.padTop = (int)I(2); p.padLeft = (int)I(3); p.padBottom = (int)I(4); p.padRight = (int)I(5);
+      p.dilH = (int)I(6, 1); p.dilW = (int)I(7, 1); p.groups = (int)I(8, 1);
+      r = Ops::Conv2d(T(0), T(1), T(2), p);
+    } else if (name == "max_pool2d") r = Ops::MaxPool2d(T(0), (int)I(0), (int)I(1), (int)I(2), (int)I(3), (int)I(4), (int)I(5));
+    else if (name == "avg_pool2d") r = Ops::AvgPool2d(T(0), (int)I(0), (int)I(1), (int)I(2), (int)I(3), (int)I(4), (int)I(5), I(6) != 0);
+    else if (name == "lstm_layer") r = Ops::LstmLayer(T(0), T(1), T(2), T(3), T(4), I(0) != 0);
+    else if (name == "ctc_loss") r = Ops::CtcLoss(T(0), T(1), T(2), T(3), (int)I(0), (int)I(1, 1), I(2) != 0);
+    else if (name == "reshape") r = T(0).Reshape(ShapeFromInts(0));
+    else if (name == "permute") {
+      std::vector<int> axes;
+      for (int i = 0; i < n_ints; i++) axes.push_back((int)ints[i]);
+      r = T(0).Permute(axes);
+    } else if (name == "t") r = T(0).T();
+    else if (name == "slice") r = T(0).Slice((int)I(0), (int)I(1), (int)I(2), (int)I(3, 1));
+    else if (name == "select") r = T(0).Select((int)I(0), (int)I(1));
+    else if (name == "expand") r = T(0).Expand(ShapeFromInts(0));
+    else if (name == "flip") r = T(0).Flip((int)I(0));
+    else if (name == "clone") r = T(0).Clone();
+    else if (name == "contiguous") r = T(0).Contiguous();
+    else if (name == "detach") r = T(0).Detach();
+    else throw InvalidOperationException("Unknown operation '" + name + "'.");
+    *out = Box(r);
+  });
+}
+
+// ---- optimizers -----------------------------------------------------------------------------------------------------
+struct omh_optim { std::unique_ptr<Optimizer> o; };
+
+// kind: 0 SGD (f: lr, momentum, dampening, weight_decay; i: nesterov), 1 Adam, 2 AdamW (f: lr, beta1, beta2, eps,
+// weight_decay; i: amsgrad).
+OMH_API int32_t omh_optim_create(int32_t kind, int32_t n, omh_tensor* const* params, const double* f, const int64_t* i,
+                                 omh_optim** out) {
+  return Guard([&] {
+    std::vector<Tensor> ps;
+    for (int k = 0; k < n; k++) ps.push_back(params[k]->t);
+    std::unique_ptr<Optimizer> o;
+    if (kind == 0) o.reset(new Sgd(ps, (float)f[0], (float)f[1], (float)f[2], (float)f[3], i[0] != 0));
+    else if (kind == 1) o.reset(new Adam(ps, (float)f[0], (float)f[1], (float)f[2], (float)f[3], (float)f[4], false, i[0] != 0));
+    else if (kind == 2) o.reset(new AdamW(ps, (float)f[0], (float)f[1], (float)f[2], (float)f[3], (float)f[4], i[0] != 0));
+    else throw InvalidOperationException("Unknown optimizer kind.");
+    *out = new omh_optim{std::move(o)};
+  });
+}
+OMH_API int32_t omh_optim_free(omh_optim* o) {
+  delete o;
+  return 0;
+}
+OMH_API int32_t omh_optim_step(omh_optim* o) {
+  return Guard([&] { o->o->Step(); });
+}
+OMH_API int32_t omh_optim_zero_grad(omh_optim* o) {
+  return Guard([&] { o->o->ZeroGrad(); });
+}
+OMH_API int32_t omh_optim_set_lr(omh_optim* o, float lr) {
+  o->o->LearningRate = lr;
+  return 0;
+}
+OMH_API int32_t omh_clip_norm(int32_t n, omh_tensor* const* params, float max_norm, int32_t infinity, float* total) {
+  return Guard([&] {
+    std::vector<Tensor> ps;
+    for (int k = 0; k < n; k++) ps.push_back(params[k]->t);
+    *total = GradClip::ClipNorm(ps, max_norm, infinity != 0);
+  });
+}
+OMH_API int32_t omh_clip_value(int32_t n, omh_tensor* const* params, float clip) {
+  return Guard([&] {
+    std::vector<Tensor> ps;
+    for (int k = 0; k < n; k++) ps.push_back(params[k]->t);
+    GradClip::ClipValue(ps, clip);
+  });
+}
+OMH_API float omh_lr_cosine(float base, int64_t step, int64_t total, float eta_min) { return LrSchedule::Cosine(base, step, total, eta_min); }
+OMH_API float omh_lr_linear_warmup(float base, int64_t step, int64_t warmup, float start) { return LrSchedule::LinearWarmup(base, step, warmup, start); }

@@ -1,0 +1,129 @@
+// Modules and initialisation, after src/OneModel.Training/{NnModule,Layers,Recurrent,Generator,Losses}.cs.
+#include <math.h>
+
+#include "omh.hpp"
+
+namespace omh {
+
+uint64_t Generator::NextUInt64() {
+  state_ += 0x9E3779B97F4A7C15ULL;
+  uint64_t z = state_;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+  return z ^ (z >> 31);
+}
+
+// Init.Uniform (Layers.cs:11-21): uniform in [-bound, bound), drawn in row-major order.
+static Tensor InitUniform(Generator& g, float bound, const Shape& s) {
+  std::vector<float> h((size_t)s.Length());
+  for (float& v : h) v = g.Uniform(-bound, bound);
+  return Tensor::FromHost(h.data(), s);
+}
+
+static Tensor InitConstant(float value, const Shape& s) {
+  Tensor t = Tensor::Create(DType::F32, s);
+  t.Fill(value);
+  return t;
+}
+
+Tensor NnModule::RegisterParameter(const std::string& name, Tensor t) {
+  t.SetRequiresGrad(true);
+  params_.emplace_back(name, t);
+  return t;
+}
+
+std::vector<std::pair<std::string, Tensor>> NnModule::NamedParameters(const std::string& prefix) const {
+  std::vector<std::pair<std::string, Tensor>> out;
+  for (auto& p : params_) out.emplace_back(prefix + p.first, p.second);
+  for (auto& c : children_) {
+    auto sub = c.second->NamedParameters(prefix + c.first + ".");
+    out.insert(out.end(), sub.begin(), sub.end());
+  }
+  return out;
+}
+
+std::vector<Tensor> NnModule::Parameters() const {
+  std::vector<Tensor> out;
+  for (auto& p : NamedParameters()) out.push_back(p.second);
+  return out;
+}
+
+void NnModule::Train(bool on) {
+  Training = on;
+  for (auto& c : children_) c.second->Train(on);
+}
+
+Linear::Linear(int inFeatures, int outFeatures, Generator& g, bool bias) {
+  if (inFeatures < 1 || outFeatures < 1) throw ArgumentOutOfRangeException("Linear needs positive feature counts.");
+  float bound = 1.0f / sqrtf((float)inFeatures);
+  Weight = RegisterParameter("weight", InitUniform(g, bound, Shape{outFeatures, inFeatures}));
+  if (bias) Bias = RegisterParameter("bias", InitUniform(g, bound, Shape{outFeatures}));
+}
+
+LayerNorm::LayerNorm(int width, float eps) : Epsilon(eps) {
+  Gamma = RegisterParameter("weight", InitConstant(1.f, Shape{width}));
+  Beta = RegisterParameter("bias", InitConstant(0.f, Shape{width}));
+}
+
+// Embedding rows are uniform in [-1, 1) (Layers.cs:268-313).
+Embedding::Embedding(int count, int width, Generator& g, int paddingIndex) : PaddingIndex(paddingIndex) {
+  Weight = RegisterParameter("weight", InitUniform(g, 1.0f, Shape{count, width}));
+}
+
+Conv2d::Conv2d(int inCh, int outCh, int kernel, Generator& g, int stride, int padding, bool bias) {
+  float bound = 1.0f / sqrtf((float)(inCh * kernel * kernel));
+  Weight = RegisterParameter("weight", InitUniform(g, bound, Shape{outCh, inCh, kernel, kernel}));
+  if (bias) Bias = RegisterParameter("bias", InitUniform(g, bound, Shape{outCh}));
+  P.strideH = P.strideW = stride;
+  P.padTop = P.padLeft = P.padBottom = P.padRight = padding;
+}
+
+BatchNorm2d::BatchNorm2d(int channels, float momentum, float eps) : Momentum(momentum), Epsilon(eps) {
+  Gamma = RegisterParameter("weight", InitConstant(1.f, Shape{channels}));
+  Beta = RegisterParameter("bias", InitConstant(0.f, Shape{channels}));
+  RunningMean = InitConstant(0.f, Shape{channels});
+  RunningVar = InitConstant(1.f, Shape{channels});
+}
+
+MultiHeadAttention::MultiHeadAttention(int width, int heads, Generator& g) : Heads(heads) {
+  if (heads < 1) throw ArgumentOutOfRangeException("heads must be at least 1.");
+  if (width < 1 || width % heads != 0)
+    throw std::invalid_argument("Width " + std::to_string(width) + " must be positive and divisible by the head count " + std::to_string(heads) + ".");
+  Q = RegisterModule("q", new Linear(width, width, g));
+  K = RegisterModule("k", new Linear(width, width, g));
+  V = RegisterModule("v", new Linear(width, width, g));
+  O = RegisterModule("o", new Linear(width, width, g));
+}
+
+Tensor MultiHeadAttention::Forward(const Tensor& input, const Tensor& mask) {
+  if (input.Rank() != 3) throw TensorShapeException("MultiHeadAttention needs [batch, length, width], not " + input.GetShape().ToString() + ".");
+  int b = input.GetShape()[0], n = input.GetShape()[1], d = input.GetShape()[2], dh = d / Heads;
+  auto split = [&](const Tensor& z) { return z.Reshape(Shape{b, n, Heads, dh}).Permute({0, 2, 1, 3}); };
+  Tensor q = split(Q->Forward(input));
+  Tensor k = split(K->Forward(input));
+  Tensor v = split(V->Forward(input));
+  Tensor a = Ops::Attention(q, k, v, mask).Permute({0, 2, 1, 3}).Reshape(Shape{b, n, d});
+  return O->Forward(a);
+}
+
+TransformerEncoderLayer::TransformerEncoderLayer(int width, int heads, int ff, Generator& g) {
+  Attn = RegisterModule("attn", new MultiHeadAttention(width, heads, g));
+  Norm1 = RegisterModule("norm1", new LayerNorm(width));
+  Ff1 = RegisterModule("ff1", new Linear(width, ff, g));
+  Ff2 = RegisterModule("ff2", new Linear(ff, width, g));
+  Norm2 = RegisterModule("norm2", new LayerNorm(width));
+}
+
+Tensor TransformerEncoderLayer::Forward(const Tensor& input, const Tensor& mask) {
+  Tensor a = Attn->Forward(input, mask);
+  Tensor x1 = Norm1->Forward(Ops::Add(input, a));
+  Tensor f = Ff2->Forward(Ops::Gelu(Ff1->Forward(x1)));
+  return Norm2->Forward(Ops::Add(x1, f));
+}
+
+Tensor Losses::Mse(const Tensor& x, const Tensor& target) {
+  Tensor d = Ops::Sub(x, target);
+  return Ops::Mean(Ops::Mul(d, d));
+}
+
+}  // namespace omh

@@ -1,0 +1,444 @@
+// C++ mirror of the reference's managed training API for the autograd hot path, written above the C ABI of
+// libonemodel_b200.so. Names and semantics follow RecursiveAI.OneModel.Tensors / RecursiveAI.OneModel.Training:
+//   Tensor (strided view + autograd meta)       src/OneModel/Tensors/Tensor.cs:29-50,396-473
+//   BackwardRecord / AutogradMeta / OpKind       src/OneModel/Tensors/Autograd/{BackwardRecord,Autograd}.cs
+//   Backprop / Engine                            src/OneModel/Tensors/Autograd/Engine.cs:21-344
+//   Ops.*                                        src/OneModel/Tensors/Ops*.cs
+//   NnModule, layers, Losses, optimizers         src/OneModel.Training/*.cs
+// Every tensor lives in device memory; every op calls the C ABI and nothing here computes on the host except
+// scalar bookkeeping (shapes, schedules, Adam's per-step bias corrections in double).
+#pragma once
+#include <stdint.h>
+
+#include <array>
+#include <functional>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "onemodel_b200.h"
+
+namespace omh {
+
+// ---- errors (the reference's exception types) -----------------------------------------------------------------------
+struct TensorShapeException : std::runtime_error { using std::runtime_error::runtime_error; };
+struct ArgumentOutOfRangeException : std::runtime_error { using std::runtime_error::runtime_error; };
+struct InvalidOperationException : std::runtime_error { using std::runtime_error::runtime_error; };
+struct BackendException : std::runtime_error {
+  int32_t status;
+  BackendException(int32_t s, const std::string& m) : std::runtime_error(m), status(s) {}
+};
+
+// ---- device ----------------------------------------------------------------------------------------------------------
+// The process-wide compute selection of the reference (TensorCompute, Autograd/TensorCompute.cs:22-78) becomes the
+// current device context.
+struct Device {
+  static om_ctx* Current();
+  static void SetCurrent(om_ctx* ctx);
+};
+void Check(int32_t status);  // throws the mapped exception with om_last_error's text
+
+// ---- shape -------------------------------------------------------------------------------------------------------------
+constexpr int kMaxRank = 8;
+struct Shape {
+  int rank = 0;
+  std::array<int32_t, kMaxRank> d{};
+  Shape() = default;
+  Shape(std::initializer_list<int> dims);
+  explicit Shape(const std::vector<int>& dims);
+  int operator[](int i) const { return d[i]; }
+  int64_t Length() const;
+  bool operator==(const Shape& o) const;
+  bool operator!=(const Shape& o) const { return !(*this == o); }
+  std::string ToString() const;
+};
+
+enum class DType : int32_t { F32 = OM_F32, I32 = OM_I32, I64 = OM_I64 };
+inline size_t SizeOf(DType t) { return t == DType::I64 ? 8 : 4; }
+
+struct Buffer {
+  om_ctx* ctx = nullptr;
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  bool owned = true;
+  Buffer(om_ctx* c, size_t n, bool zero);
+  Buffer(om_ctx* c, void* external, size_t n) : ctx(c), ptr(external), bytes(n), owned(false) {}
+  ~Buffer();
+  Buffer(const Buffer&) = delete;
+  Buffer& operator=(const Buffer&) = delete;
+};
+
+struct BackwardRecord;
+struct AutogradMeta;
+class Tensor;
+
+// ---- tensor ------------------------------------------------------------------------------------------------------------
+class Tensor {
+ public:
+  Tensor() = default;
+  static Tensor Create(DType t, const Shape& s, bool zero = false);
+  static Tensor Zeros(DType t, const Shape& s) { return Create(t, s, true); }
+  static Tensor FromHost(const float* data, const Shape& s);
+  static Tensor FromHostInt32(const int32_t* data, const Shape& s);
+  static Tensor FromHostInt64(const int64_t* data, const Shape& s);
+  // A tensor over caller-owned device memory (not freed by the tensor).
+  static Tensor Wrap(void* device_ptr, DType t, const Shape& s);
+
+  bool IsEmpty() const { return !buf_; }
+  const Shape& GetShape() const { return shape_; }
+  int Rank() const { return shape_.rank; }
+  int64_t Length() const { return IsEmpty() ? 0 : shape_.Length(); }
+  DType GetDType() const { return dtype_; }
+  const std::array<int64_t, kMaxRank>& Strides() const { return strides_; }
+  bool IsContiguous() const;
+  float* Data() const;  // device pointer to the first element
+  void* RawData() const;
+
+  // views (each records a view record when the source requires grad; Tensor.Views.cs:11-21)
+  Tensor Reshape(const Shape& s) const;
+  Tensor Permute(const std::vector<int>& axes) const;
+  Tensor T() const;
+  Tensor Transpose(int a, int b) const;
+  Tensor Slice(int axis, int start, int end, int step = 1) const;
+  Tensor Select(int axis, int index) const;
+  Tensor Expand(const Shape& s) const;
+  Tensor Flip(int axis) const;
+  Tensor Clone() const;        // contiguous copy, no autograd link
+  Tensor Contiguous() const;   // this if contiguous, else Clone
+  Tensor Detach() const;
+  void Fill(float v) const;
+  void CopyFromHost(const void* src) const;  // contiguous only
+  void CopyToHost(void* dst) const;          // any layout (clones when strided); synchronises
+  std::vector<float> ToVector() const;
+  float Item() const;
+
+  // autograd surface (Tensor.cs:396-473)
+  bool RequiresGrad() const;
+  Tensor& SetRequiresGrad(bool on = true);
+  Tensor Grad() const;
+  void Backward(const Tensor* gradient = nullptr, bool retainGraph = false) const;
+  const std::shared_ptr<AutogradMeta>& Autograd() const { return meta_; }
+  Tensor WithAutograd(std::shared_ptr<AutogradMeta> m) const;
+
+  // internal: same storage with a different view
+  Tensor View(const Shape& s, const std::array<int64_t, kMaxRank>& strides, int64_t offset) const;
+  int64_t Offset() const { return offset_; }
+  const std::shared_ptr<Buffer>& Storage() const { return buf_; }
+
+ private:
+  std::shared_ptr<Buffer> buf_;
+  int64_t offset_ = 0;  // elements
+  Shape shape_;
+  std::array<int64_t, kMaxRank> strides_{};
+  DType dtype_ = DType::F32;
+  std::shared_ptr<AutogradMeta> meta_;
+};
+
+std::array<int64_t, kMaxRank> ContiguousStrides(const Shape& s);
+
+// ---- autograd types ---------------------------------------------------------------------------------------------------
+// The reference's 43 kinds (Autograd.cs:7-97) plus the fused kinds this backend records in their place: Linear for
+// the Reshape/MatMul/Add chain of Ops.Linear, CrossEntropy for LogSoftmax+NllLoss, GlobalAvgPool for Mean over planes.
+enum class OpKind {
+  None = 0, Add, Sub, Mul, Div, Neg, Relu, MatMul, MaxPool2d, Cast, Slice, Permute, Reshape, Expand, Flip, Select, Gelu,
+  Sigmoid, Tanh, Sum, Mean, Softmax, LogSoftmax, LayerNorm, BatchNorm, Conv2d, AvgPool2d, Concat, Embedding, NllLoss,
+  Attention, Lstm, Gru, CtcLoss, ConvTranspose2d, Resize2d, Conv1d, BatchMatMul, Erf, Exp, Sqrt, Pow, Where, Gather,
+  Linear, CrossEntropy
+};
+
+struct AutogradMeta {
+  bool RequiresGrad = false;
+  std::shared_ptr<BackwardRecord> GradFn;  // null for a leaf
+  int OutputIndex = 0;
+  Tensor Grad;
+  // The gradient buffer is kept across steps; after ZeroGrad its contents are logically zero and are overwritten by
+  // the first gradient that arrives instead of being zero-filled and then added to.
+  bool GradIsZero = false;
+  bool IsLeaf() const { return !GradFn; }
+};
+
+struct BackwardRecord : std::enable_shared_from_this<BackwardRecord> {
+  OpKind Op = OpKind::None;
+  std::vector<std::shared_ptr<AutogradMeta>> Inputs;  // null where the input needs no gradient
+  std::vector<Shape> InputShapes;
+  std::vector<DType> InputTypes;
+  std::vector<Tensor> SavedSlots;
+  std::vector<int64_t> Ints;
+  std::vector<double> Floats;
+  Tensor PendingGrad;
+  int VisitMark = 0;
+  bool IsReleased = false;
+
+  static std::shared_ptr<BackwardRecord> Create(OpKind op, int savedSlots, std::initializer_list<const Tensor*> inputs);
+  static std::shared_ptr<BackwardRecord> Create(OpKind op, int savedSlots, const std::vector<Tensor>& inputs);
+  int InputCount() const { return (int)Inputs.size(); }
+  bool NeedsInputGrad(int i) const { return Inputs[i] != nullptr; }
+  const Tensor& Saved(int slot) const { return SavedSlots[slot]; }
+  void Save(int slot, const Tensor& t) { SavedSlots[slot] = t; }
+  Tensor Attach(const Tensor& output, int outputIndex = 0);
+  void Release();
+};
+
+// RAII no-grad scope (GradMode.NoGrad, Autograd.cs:149).
+struct GradMode {
+  static bool Enabled();
+  struct NoGrad {
+    bool prev;
+    NoGrad();
+    ~NoGrad();
+  };
+};
+
+// The reference frees every step temporary when the scope is disposed (ActivationScope.cs:18-106). Device buffers here
+// are reference counted, so disposing the scope only drops the scope's own references; it is kept so that training
+// loops read the same.
+struct ActivationScope {
+  ActivationScope();
+  ~ActivationScope();
+  static void Track(const Tensor& t);
+  std::vector<Tensor> tracked;
+  ActivationScope* outer;
+};
+
+struct Backprop {
+  static void Run(const Tensor& root, const Tensor* gradient = nullptr, bool retainGraph = false);
+  static void ZeroGrad(const Tensor& leaf);
+  static void ClearGrad(const Tensor& leaf);
+  // Called when the last gradient of a leaf has arrived in the running backward pass (data-parallel bucket trigger).
+  static std::function<void(AutogradMeta*)> GradReadyHook;
+};
+
+class Engine {
+ public:
+  void Execute(const std::shared_ptr<BackwardRecord>& root, Tensor rootGrad, bool retain);
+  static void Emit(BackwardRecord& rec, int i, const Tensor& grad, bool owned);
+  void EmitAliased(BackwardRecord& rec, int i, const Tensor& view) { Emit(rec, i, view, true); }
+  static void AccumulateLeaf(AutogradMeta& leaf, const Tensor& grad, bool owned);
+  // If input i is a leaf that keeps a gradient buffer, returns that buffer and whether the kernel must add to it
+  // (accumulate) or overwrite it; the caller then calls LeafWritten instead of Emit.
+  static bool LeafTarget(BackwardRecord& rec, int i, float** ptr, bool* accumulate);
+  static void LeafWritten(BackwardRecord& rec, int i);
+  static void AddInto(const Tensor& dst, const Tensor& src);
+};
+
+void RunBackwardOp(Engine& e, BackwardRecord& r, const Tensor& g);
+
+// ---- ops ---------------------------------------------------------------------------------------------------------------
+struct Conv2dParams {
+  int strideH = 1, strideW = 1, padTop = 0, padLeft = 0, padBottom = 0, padRight = 0, dilH = 1, dilW = 1, groups = 1;
+};
+
+struct Ops {
+  static Tensor Add(const Tensor& a, const Tensor& b);
+  static Tensor Sub(const Tensor& a, const Tensor& b);
+  static Tensor Mul(const Tensor& a, const Tensor& b);
+  static Tensor Div(const Tensor& a, const Tensor& b);
+  static Tensor Neg(const Tensor& x);
+  static Tensor Relu(const Tensor& x);
+  static Tensor MatMul(const Tensor& a, const Tensor& b);
+  static Tensor Gelu(const Tensor& x, bool approximateTanh = false);
+  static Tensor Sigmoid(const Tensor& x);
+  static Tensor Tanh(const Tensor& x);
+  static Tensor Sum(const Tensor& x);
+  static Tensor Sum(const Tensor& x, int axis, bool keepDim = false);
+  static Tensor Mean(const Tensor& x);
+  static Tensor Mean(const Tensor& x, int axis, bool keepDim = false);
+  static Tensor Softmax(const Tensor& x, int axis = -1);
+  static Tensor LogSoftmax(const Tensor& x, int axis = -1);
+  static Tensor LayerNorm(const Tensor& x, const Tensor& gamma, const Tensor& beta, float epsilon = 1e-5f);
+  static Tensor BatchNorm2d(const Tensor& x, const Tensor& gamma, const Tensor& beta, const Tensor& runningMean,
+                            const Tensor& runningVar, bool training, float momentum = 0.1f, float epsilon = 1e-5f);
+  static Tensor Conv2d(const Tensor& x, const Tensor& weight, const Tensor& bias, const Conv2dParams& p);
+  static Tensor MaxPool2d(const Tensor& x, int kh, int kw, int sh, int sw, int ph = 0, int pw = 0);
+  static Tensor AvgPool2d(const Tensor& x, int kh, int kw, int sh, int sw, int ph = 0, int pw = 0, bool countIncludePad = false);
+  static Tensor GlobalAvgPool2d(const Tensor& x);
+  static Tensor Concat(const std::vector<Tensor>& xs, int axis);
+  static Tensor Embedding(const Tensor& table, const Tensor& ids, int paddingIndex = -1);
+  static Tensor NllLoss(const Tensor& logProbs, const Tensor& targets, bool mean = true, int ignoreIndex = -100);
+  static Tensor CrossEntropy(const Tensor& logits, const Tensor& targets, bool mean = true, int ignoreIndex = -100,
+                             float denominator = 0.f);
+  static Tensor Linear(const Tensor& x, const Tensor& weight, const Tensor& bias);
+  static Tensor Attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& mask, float scale = 0.f);
+  // One LSTM layer direction: returns y [T,B,H]; hn/cn receive the final states when not null.
+  static Tensor LstmLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, const Tensor& bIh, const Tensor& bHh,
+                          bool reverse, Tensor* hn = nullptr, Tensor* cn = nullptr);
+  static Tensor CtcLoss(const Tensor& logProbs, const Tensor& targets, const Tensor& inputLengths,
+                        const Tensor& targetLengths, int blank, int reduction, bool zeroInfinity);
+  static bool Recording(std::initializer_list<const Tensor*> inputs);
+};
+
+// ---- modules, losses, optimizers -------------------------------------------------------------------------------------
+class Generator {  // SplitMix64, src/OneModel.Training/Generator.cs:10-48
+ public:
+  explicit Generator(uint64_t seed) : state_(seed) {}
+  uint64_t NextUInt64();
+  float NextSingle() { return (float)(NextUInt64() >> 40) * (1.0f / 16777216.0f); }
+  float Uniform(float low, float high) { return low + (high - low) * NextSingle(); }
+ private:
+  uint64_t state_;
+};
+
+class NnModule {
+ public:
+  virtual ~NnModule() = default;
+  virtual Tensor Forward(const Tensor& input) = 0;
+  // Parameters in registration order, children after own parameters (NnModule.cs:139-311).
+  std::vector<std::pair<std::string, Tensor>> NamedParameters(const std::string& prefix = "") const;
+  std::vector<Tensor> Parameters() const;
+  void Train(bool on = true);
+  bool Training = true;
+ protected:
+  Tensor RegisterParameter(const std::string& name, Tensor t);
+  template <class M> M* RegisterModule(const std::string& name, M* m) {
+    children_.emplace_back(name, std::unique_ptr<NnModule>(m));
+    return m;
+  }
+  std::vector<std::pair<std::string, Tensor>> params_;
+  std::vector<std::pair<std::string, std::unique_ptr<NnModule>>> children_;
+};
+
+struct Linear : NnModule {
+  Tensor Weight, Bias;
+  Linear(int inFeatures, int outFeatures, Generator& g, bool bias = true);
+  Tensor Forward(const Tensor& x) override { return Ops::Linear(x, Weight, Bias); }
+};
+struct LayerNorm : NnModule {
+  Tensor Gamma, Beta;
+  float Epsilon;
+  explicit LayerNorm(int width, float eps = 1e-5f);
+  Tensor Forward(const Tensor& x) override { return Ops::LayerNorm(x, Gamma, Beta, Epsilon); }
+};
+struct Embedding : NnModule {
+  Tensor Weight;
+  int PaddingIndex;
+  Embedding(int count, int width, Generator& g, int paddingIndex = -1);
+  Tensor Forward(const Tensor& ids) override { return Ops::Embedding(Weight, ids, PaddingIndex); }
+};
+struct Conv2d : NnModule {
+  Tensor Weight, Bias;
+  Conv2dParams P;
+  Conv2d(int inCh, int outCh, int kernel, Generator& g, int stride = 1, int padding = 0, bool bias = true);
+  Tensor Forward(const Tensor& x) override { return Ops::Conv2d(x, Weight, Bias, P); }
+};
+struct BatchNorm2d : NnModule {
+  Tensor Gamma, Beta, RunningMean, RunningVar;
+  float Momentum, Epsilon;
+  explicit BatchNorm2d(int channels, float momentum = 0.1f, float eps = 1e-5f);
+  Tensor Forward(const Tensor& x) override {
+    return Ops::BatchNorm2d(x, Gamma, Beta, RunningMean, RunningVar, Training, Momentum, Epsilon);
+  }
+};
+struct MultiHeadAttention : NnModule {
+  Linear *Q, *K, *V, *O;
+  int Heads;
+  MultiHeadAttention(int width, int heads, Generator& g);
+  Tensor Forward(const Tensor& x) override { return Forward(x, Tensor()); }
+  Tensor Forward(const Tensor& x, const Tensor& mask);
+};
+struct TransformerEncoderLayer : NnModule {
+  MultiHeadAttention* Attn;
+  LayerNorm *Norm1, *Norm2;
+  Linear *Ff1, *Ff2;
+  TransformerEncoderLayer(int width, int heads, int ff, Generator& g);
+  Tensor Forward(const Tensor& x) override { return Forward(x, Tensor()); }
+  Tensor Forward(const Tensor& x, const Tensor& mask);
+};
+// Stacked (bi)directional LSTM over [T,B,I] (src/OneModel.Training/Recurrent.cs:13-67).
+struct Recurrent : NnModule {
+  int Hidden, Layers;
+  bool Bidirectional;
+  std::vector<Tensor> WIh, WHh, BIh, BHh;  // per layer and direction
+  Recurrent(int input, int hidden, int layers, bool bidirectional, Generator& g);
+  Tensor Forward(const Tensor& x) override;
+};
+
+struct Losses {
+  static Tensor CrossEntropy(const Tensor& logits, const Tensor& targets, bool mean = true, int ignoreIndex = -100) {
+    return Ops::CrossEntropy(logits, targets, mean, ignoreIndex);
+  }
+  static Tensor NllLoss(const Tensor& logp, const Tensor& targets, bool mean = true, int ignoreIndex = -100) {
+    return Ops::NllLoss(logp, targets, mean, ignoreIndex);
+  }
+  static Tensor Mse(const Tensor& x, const Tensor& target);
+};
+
+class Optimizer {
+ public:
+  explicit Optimizer(std::vector<Tensor> parameters);
+  virtual ~Optimizer() = default;
+  void Step();      // Optimizers.cs:184-219
+  void ZeroGrad();  // Optimizers.cs:222-228
+  float LearningRate = 1e-3f;
+  float WeightDecay = 0.f;
+  int64_t StepCount = 0;
+  const std::vector<Tensor>& Parameters() const { return params_; }
+  // When set, the fused kernels read their per-step scalars from this device struct (graph replay).
+  void* HyperDevice = nullptr;
+  virtual size_t HyperBytes() const = 0;
+  virtual void FillHyper(void* host, int64_t step) const = 0;  // scalars for the given 1-based step
+  virtual std::vector<Tensor> StateTensors() const = 0;
+ protected:
+  virtual void BeginStep() {}
+  virtual void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) = 0;
+  std::vector<Tensor> params_;
+  std::vector<int> index_;  // positions in params_ of the tensors of the running Step
+};
+
+class Sgd : public Optimizer {
+ public:
+  Sgd(std::vector<Tensor> parameters, float lr, float momentum = 0.f, float dampening = 0.f, float weightDecay = 0.f,
+      bool nesterov = false);
+  size_t HyperBytes() const override { return sizeof(om_sgd_hyper); }
+  void FillHyper(void* host, int64_t step) const override;
+  std::vector<Tensor> StateTensors() const override { return buffers_; }
+  float GradScale = 1.f;
+ protected:
+  void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) override;
+ private:
+  float momentum_, dampening_;
+  bool nesterov_;
+  std::vector<Tensor> buffers_;
+  std::vector<int32_t> initialized_;
+};
+
+class Adam : public Optimizer {
+ public:
+  Adam(std::vector<Tensor> parameters, float lr = 1e-3f, float beta1 = 0.9f, float beta2 = 0.999f, float eps = 1e-8f,
+       float weightDecay = 0.f, bool decoupled = false, bool amsgrad = false);
+  size_t HyperBytes() const override { return sizeof(om_adam_hyper); }
+  void FillHyper(void* host, int64_t step) const override;
+  std::vector<Tensor> StateTensors() const override;
+  float GradScale = 1.f;
+ protected:
+  void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) override;
+ private:
+  float beta1_, beta2_, eps_;
+  bool decoupled_, amsgrad_;
+  std::vector<Tensor> m_, v_, vmax_;
+};
+
+class AdamW : public Adam {
+ public:
+  AdamW(std::vector<Tensor> parameters, float lr = 1e-3f, float beta1 = 0.9f, float beta2 = 0.999f, float eps = 1e-8f,
+        float weightDecay = 0.01f, bool amsgrad = false)
+      : Adam(std::move(parameters), lr, beta1, beta2, eps, weightDecay, true, amsgrad) {}
+};
+
+struct GradClip {
+  // Returns the total norm (synchronises to read it).
+  static float ClipNorm(const std::vector<Tensor>& parameters, float maxNorm, bool infinityNorm = false);
+  // Same without the read-back; norm_out (device float, may be null) receives the norm.
+  static void ClipNormAsync(const std::vector<Tensor>& parameters, float maxNorm, bool infinityNorm, float* norm_out);
+  static void ClipValue(const std::vector<Tensor>& parameters, float clipValue);
+};
+
+// Learning-rate schedules are pure host functions of the step (Schedules.cs:151-422).
+struct LrSchedule {
+  static float Cosine(float base, int64_t step, int64_t total, float etaMin = 0.f);
+  static float LinearWarmup(float base, int64_t step, int64_t warmup, float startFactor);
+  static float StepDecay(float base, int64_t step, int64_t stepSize, float gamma);
+};
+
+}  // namespace omh

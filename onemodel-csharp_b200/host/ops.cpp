@@ -1,0 +1,384 @@
+// Eager forward operations. Each computes on the device through the C ABI and, when an input requires a gradient
+// and recording is on, attaches a BackwardRecord with the same saved slots, Ints and Floats as the reference's
+// Ops.* (src/OneModel/Tensors/Ops.cs, Ops.Nn.cs, Ops.Layers.cs, Ops.Recurrent.cs, CtcLoss.cs).
+#include <math.h>
+
+#include "omh.hpp"
+
+namespace omh {
+
+static om_ctx* C() { return Device::Current(); }
+
+bool Ops::Recording(std::initializer_list<const Tensor*> inputs) {
+  if (!GradMode::Enabled()) return false;
+  for (const Tensor* t : inputs)
+    if (t && !t->IsEmpty() && t->RequiresGrad()) return true;
+  return false;
+}
+
+static void RequireFloat32(const Tensor& t) {
+  if (t.GetDType() != DType::F32) throw TensorShapeException("A float32 tensor is required.");
+}
+
+static Tensor NewOut(const Shape& s) {
+  Tensor r = Tensor::Create(DType::F32, s);
+  ActivationScope::Track(r);
+  return r;
+}
+
+// Broadcast shape of a and b, and each operand's strides over it (0 on broadcast axes).
+static Shape Broadcast(const Tensor& a, const Tensor& b, std::array<int64_t, kMaxRank>& sa, std::array<int64_t, kMaxRank>& sb) {
+  Shape s;
+  s.rank = std::max(a.Rank(), b.Rank());
+  for (int i = 0; i < s.rank; i++) {
+    int ia = i - (s.rank - a.Rank()), ib = i - (s.rank - b.Rank());
+    int da = ia >= 0 ? a.GetShape()[ia] : 1, db = ib >= 0 ? b.GetShape()[ib] : 1;
+    if (da != db && da != 1 && db != 1)
+      throw TensorShapeException("Shapes " + a.GetShape().ToString() + " and " + b.GetShape().ToString() + " do not broadcast.");
+    s.d[i] = da == 1 ? db : da;
+    sa[i] = (ia >= 0 && da != 1) ? a.Strides()[ia] : 0;
+    sb[i] = (ib >= 0 && db != 1) ? b.Strides()[ib] : 0;
+  }
+  return s;
+}
+
+static Tensor Binary(OpKind kind, om_binary_op op, const Tensor& a, const Tensor& b) {
+  RequireFloat32(a);
+  RequireFloat32(b);
+  std::array<int64_t, kMaxRank> sa{}, sb{};
+  Shape s = Broadcast(a, b, sa, sb);
+  Tensor r = NewOut(s);
+  Check(om_binary(C(), op, s.rank, s.d.data(), a.Data(), sa.data(), b.Data(), sb.data(), r.Data()));
+  if (!Ops::Recording({&a, &b})) return r;
+  bool saves = kind == OpKind::Mul || kind == OpKind::Div;
+  auto rec = BackwardRecord::Create(kind, saves ? 2 : 0, {&a, &b});
+  if (saves) {
+    rec->Save(0, a.Detach());
+    rec->Save(1, b.Detach());
+  }
+  return rec->Attach(r);
+}
+
+Tensor Ops::Add(const Tensor& a, const Tensor& b) { return Binary(OpKind::Add, OM_ADD, a, b); }
+Tensor Ops::Sub(const Tensor& a, const Tensor& b) { return Binary(OpKind::Sub, OM_SUB, a, b); }
+Tensor Ops::Mul(const Tensor& a, const Tensor& b) { return Binary(OpKind::Mul, OM_MUL, a, b); }
+Tensor Ops::Div(const Tensor& a, const Tensor& b) { return Binary(OpKind::Div, OM_DIV, a, b); }
+
+// saved: 0 = nothing, 1 = output, 2 = input
+static Tensor Unary(OpKind kind, om_unary_op op, const Tensor& x, int saved, std::vector<int64_t> ints = {}) {
+  RequireFloat32(x);
+  Tensor xc = x.Contiguous();
+  Tensor r = NewOut(x.GetShape());
+  Check(om_unary(C(), op, xc.Data(), r.Data(), r.Length()));
+  if (!Ops::Recording({&x})) return r;
+  auto rec = BackwardRecord::Create(kind, saved ? 1 : 0, {&x});
+  if (saved == 1) rec->Save(0, r.Detach());
+  if (saved == 2) rec->Save(0, xc.Detach());
+  rec->Ints = std::move(ints);
+  return rec->Attach(r);
+}
+
+Tensor Ops::Neg(const Tensor& x) { return Unary(OpKind::Neg, OM_NEG, x, 0); }
+Tensor Ops::Relu(const Tensor& x) { return Unary(OpKind::Relu, OM_RELU, x, 1); }
+Tensor Ops::Gelu(const Tensor& x, bool tanhForm) {
+  return Unary(OpKind::Gelu, tanhForm ? OM_GELU_TANH : OM_GELU_ERF, x, 2, {tanhForm ? 1 : 0});
+}
+Tensor Ops::Sigmoid(const Tensor& x) { return Unary(OpKind::Sigmoid, OM_SIGMOID, x, 1); }
+Tensor Ops::Tanh(const Tensor& x) { return Unary(OpKind::Tanh, OM_TANH, x, 1); }
+
+// Leading dimension and transposition of a 2-D view that the GEMM can read in place; false if it needs a copy.
+static bool GemmLayout(const Tensor& t, int* trans, int* ld) {
+  int64_t s0 = t.Strides()[0], s1 = t.Strides()[1];
+  int r = t.GetShape()[0], c = t.GetShape()[1];
+  if ((s1 == 1 || c == 1) && (s0 >= c || r == 1)) {
+    *trans = 0;
+    *ld = (int)(r == 1 ? std::max<int64_t>(c, 1) : s0);
+    return true;
+  }
+  if ((s0 == 1 || r == 1) && (s1 >= r || c == 1)) {
+    *trans = 1;
+    *ld = (int)(c == 1 ? std::max<int64_t>(r, 1) : s1);
+    return true;
+  }
+  return false;
+}
+
+Tensor Ops::MatMul(const Tensor& a, const Tensor& b) {
+  RequireFloat32(a);
+  RequireFloat32(b);
+  if (a.Rank() != 2 || b.Rank() != 2 || a.GetShape()[1] != b.GetShape()[0])
+    throw TensorShapeException("MatMul needs [M,K] and [K,N], not " + a.GetShape().ToString() + " and " + b.GetShape().ToString());
+  int m = a.GetShape()[0], k = a.GetShape()[1], n = b.GetShape()[1];
+  Tensor av = a, bv = b;
+  int ta, tb, lda, ldb;
+  if (!GemmLayout(av, &ta, &lda)) {
+    av = a.Contiguous();
+    GemmLayout(av, &ta, &lda);
+  }
+  if (!GemmLayout(bv, &tb, &ldb)) {
+    bv = b.Contiguous();
+    GemmLayout(bv, &tb, &ldb);
+  }
+  Tensor r = NewOut(Shape{m, n});
+  Check(om_matmul(C(), ta, tb, m, n, k, av.Data(), lda, bv.Data(), ldb, r.Data(), n, 0));
+  if (!Recording({&a, &b})) return r;
+  auto rec = BackwardRecord::Create(OpKind::MatMul, 2, {&a, &b});
+  rec->Save(0, av.Detach());
+  rec->Save(1, bv.Detach());
+  return rec->Attach(r);
+}
+
+static Tensor Reduce(OpKind kind, const Tensor& x, int axis, bool keepDim, bool all) {
+  RequireFloat32(x);
+  Tensor xc = x.Contiguous();
+  int64_t outer = 1, n = xc.Length(), inner = 1;
+  int ax = -1;
+  Shape os;
+  if (!all) {
+    ax = axis < 0 ? axis + x.Rank() : axis;
+    if (ax < 0 || ax >= x.Rank()) throw TensorShapeException("Axis out of range.");
+    n = x.GetShape()[ax];
+    for (int i = 0; i < ax; i++) outer *= x.GetShape()[i];
+    for (int i = ax + 1; i < x.Rank(); i++) inner *= x.GetShape()[i];
+    for (int i = 0; i < x.Rank(); i++) {
+      if (i != ax) os.d[os.rank++] = x.GetShape()[i];
+      else if (keepDim) os.d[os.rank++] = 1;
+    }
+  }
+  Tensor r = NewOut(os);
+  Check(om_reduce_fwd(C(), xc.Data(), outer, n, inner, kind == OpKind::Mean, r.Data()));
+  if (!Ops::Recording({&x})) return r;
+  auto rec = BackwardRecord::Create(kind, 0, {&x});
+  rec->Ints = {all ? -1 : ax, keepDim ? 1 : 0};
+  return rec->Attach(r);
+}
+
+Tensor Ops::Sum(const Tensor& x) { return Reduce(OpKind::Sum, x, 0, false, true); }
+Tensor Ops::Sum(const Tensor& x, int axis, bool keepDim) { return Reduce(OpKind::Sum, x, axis, keepDim, false); }
+Tensor Ops::Mean(const Tensor& x) { return Reduce(OpKind::Mean, x, 0, false, true); }
+Tensor Ops::Mean(const Tensor& x, int axis, bool keepDim) { return Reduce(OpKind::Mean, x, axis, keepDim, false); }
+
+static Tensor SoftmaxLike(OpKind kind, const Tensor& x, int axis) {
+  RequireFloat32(x);
+  int ax = axis < 0 ? axis + x.Rank() : axis;
+  if (ax != x.Rank() - 1) {
+    Tensor t = x.Transpose(ax, x.Rank() - 1);
+    Tensor y = kind == OpKind::Softmax ? Ops::Softmax(t, -1) : Ops::LogSoftmax(t, -1);
+    return y.Transpose(ax, x.Rank() - 1);
+  }
+  Tensor xc = x.Contiguous();
+  Tensor r = NewOut(x.GetShape());
+  int cols = x.GetShape()[ax];
+  int rows = cols == 0 ? 0 : (int)(x.Length() / cols);
+  if (kind == OpKind::Softmax) Check(om_softmax_fwd(C(), xc.Data(), rows, cols, r.Data()));
+  else Check(om_logsoftmax_fwd(C(), xc.Data(), rows, cols, r.Data()));
+  if (!Ops::Recording({&x})) return r;
+  auto rec = BackwardRecord::Create(kind, 1, {&x});
+  rec->Save(0, r.Detach());
+  return rec->Attach(r);
+}
+Tensor Ops::Softmax(const Tensor& x, int axis) { return SoftmaxLike(OpKind::Softmax, x, axis); }
+Tensor Ops::LogSoftmax(const Tensor& x, int axis) { return SoftmaxLike(OpKind::LogSoftmax, x, axis); }
+
+Tensor Ops::LayerNorm(const Tensor& x, const Tensor& gamma, const Tensor& beta, float eps) {
+  int cols = x.GetShape()[x.Rank() - 1];
+  if (gamma.Rank() != 1 || beta.Rank() != 1 || gamma.GetShape()[0] != cols || beta.GetShape()[0] != cols)
+    throw TensorShapeException("LayerNorm over " + std::to_string(cols) + " features needs gamma and beta of shape [" +
+                               std::to_string(cols) + "], not " + gamma.GetShape().ToString() + " and " + beta.GetShape().ToString() + ".");
+  int rows = cols == 0 ? 0 : (int)(x.Length() / cols);
+  Tensor xc = x.Contiguous(), gc = gamma.Contiguous(), bc = beta.Contiguous();
+  Tensor r = NewOut(x.GetShape());
+  bool rec = Recording({&x, &gamma, &beta});
+  Tensor mean, inv;
+  if (rec) {
+    mean = Tensor::Create(DType::F32, Shape{rows});
+    inv = Tensor::Create(DType::F32, Shape{rows});
+  }
+  Check(om_layernorm_fwd(C(), xc.Data(), gc.Data(), bc.Data(), rows, cols, eps, r.Data(), rec ? mean.Data() : nullptr,
+                         rec ? inv.Data() : nullptr));
+  if (!rec) return r;
+  auto br = BackwardRecord::Create(OpKind::LayerNorm, 4, {&x, &gamma, &beta});
+  br->Save(0, xc.Detach());
+  br->Save(1, gc.Detach());
+  br->Save(2, mean);
+  br->Save(3, inv);
+  br->Floats = {eps};
+  return br->Attach(r);
+}
+
+Tensor Ops::BatchNorm2d(const Tensor& x, const Tensor& gamma, const Tensor& beta, const Tensor& runningMean,
+                        const Tensor& runningVar, bool training, float momentum, float eps) {
+  RequireFloat32(x);
+  if (x.Rank() != 4) throw TensorShapeException("BatchNorm2d needs an (N,C,H,W) input, not " + x.GetShape().ToString() + ".");
+  int n = x.GetShape()[0], c = x.GetShape()[1], plane = x.GetShape()[2] * x.GetShape()[3];
+  for (const Tensor* t : {&gamma, &beta, &runningMean, &runningVar})
+    if (t->Rank() != 1 || t->GetShape()[0] != c)
+      throw TensorShapeException("BatchNorm2d over " + std::to_string(c) + " channels needs per-channel tensors of shape [" + std::to_string(c) + "].");
+  Tensor xc = x.Contiguous(), gc = gamma.Contiguous(), bc = beta.Contiguous();
+  Tensor mean = Tensor::Create(DType::F32, Shape{c}), inv = Tensor::Create(DType::F32, Shape{c});
+  Tensor r = NewOut(x.GetShape());
+  Check(om_batchnorm_fwd(C(), xc.Data(), gc.Data(), bc.Data(), runningMean.Data(), runningVar.Data(), n, c, plane,
+                         training, momentum, eps, r.Data(), mean.Data(), inv.Data()));
+  if (!Recording({&x, &gamma, &beta})) return r;
+  auto br = BackwardRecord::Create(OpKind::BatchNorm, 4, {&x, &gamma, &beta});
+  br->Save(0, xc.Detach());
+  br->Save(1, gc.Detach());
+  br->Save(2, mean);
+  br->Save(3, inv);
+  br->Ints = {training ? 1 : 0};
+  br->Floats = {eps};
+  return br->Attach(r);
+}
+
+Tensor Ops::Embedding(const Tensor& table, const Tensor& ids, int paddingIndex) {
+  RequireFloat32(table);
+  if (table.Rank() != 2 || (ids.GetDType() != DType::I32 && ids.GetDType() != DType::I64))
+    throw TensorShapeException("Embedding needs a [V, D] float32 table and Int32 or Int64 ids.");
+  if (ids.Rank() + 1 > kMaxRank) throw TensorShapeException("Too many dimensions.");
+  Tensor tc = table.Contiguous();
+  Tensor ic = ids.IsContiguous() ? ids : ids.Clone();
+  int v = table.GetShape()[0], dim = table.GetShape()[1];
+  Shape os = ids.GetShape();
+  os.d[os.rank++] = dim;
+  Tensor r = NewOut(os);
+  Check(om_embedding_fwd(C(), tc.Data(), v, dim, ic.RawData(), (int32_t)ic.GetDType(), ids.Length(), r.Data()));
+  if (!Recording({&table})) return r;
+  auto rec = BackwardRecord::Create(OpKind::Embedding, 1, {&table});
+  rec->Save(0, ic.Detach());
+  rec->Ints = {paddingIndex};
+  return rec->Attach(r);
+}
+
+Tensor Ops::NllLoss(const Tensor& logProbs, const Tensor& targets, bool mean, int ignoreIndex) {
+  RequireFloat32(logProbs);
+  if (logProbs.Rank() != 2 || targets.Rank() != 1 || targets.GetShape()[0] != logProbs.GetShape()[0] ||
+      (targets.GetDType() != DType::I32 && targets.GetDType() != DType::I64))
+    throw TensorShapeException("NllLoss needs [N, C] log-probabilities and [N] Int32 or Int64 targets, not " +
+                               logProbs.GetShape().ToString() + " and " + targets.GetShape().ToString() + ".");
+  int rows = logProbs.GetShape()[0], cols = logProbs.GetShape()[1];
+  Tensor lc = logProbs.Contiguous();
+  Tensor tc = targets.IsContiguous() ? targets : targets.Clone();
+  Tensor r = NewOut(Shape{});
+  Check(om_nll_fwd(C(), lc.Data(), tc.RawData(), (int32_t)tc.GetDType(), rows, cols, mean, ignoreIndex, r.Data(), nullptr));
+  if (!Recording({&logProbs})) return r;
+  auto rec = BackwardRecord::Create(OpKind::NllLoss, 1, {&logProbs});
+  rec->Save(0, tc.Detach());
+  rec->Ints = {mean ? 1 : 0, ignoreIndex};
+  return rec->Attach(r);
+}
+
+Tensor Ops::CrossEntropy(const Tensor& logits, const Tensor& targets, bool mean, int ignoreIndex, float denominator) {
+  RequireFloat32(logits);
+  if (logits.Rank() != 2 || targets.Rank() != 1 || targets.GetShape()[0] != logits.GetShape()[0] ||
+      (targets.GetDType() != DType::I32 && targets.GetDType() != DType::I64))
+    throw TensorShapeException("CrossEntropy needs [N, C] logits and [N] Int32 or Int64 targets, not " +
+                               logits.GetShape().ToString() + " and " + targets.GetShape().ToString() + ".");
+  int rows = logits.GetShape()[0], cols = logits.GetShape()[1];
+  Tensor lc = logits.Contiguous();
+  Tensor tc = targets.IsContiguous() ? targets : targets.Clone();
+  Tensor logp = Tensor::Create(DType::F32, logits.GetShape());
+  Tensor r = NewOut(Shape{});
+  Check(om_cross_entropy_fwd(C(), lc.Data(), tc.RawData(), (int32_t)tc.GetDType(), rows, cols, mean, ignoreIndex,
+                             denominator, logp.Data(), r.Data(), nullptr));
+  if (!Recording({&logits})) return r;
+  auto rec = BackwardRecord::Create(OpKind::CrossEntropy, 2, {&logits});
+  rec->Save(0, logp);
+  rec->Save(1, tc.Detach());
+  rec->Ints = {mean ? 1 : 0, ignoreIndex};
+  rec->Floats = {denominator};
+  return rec->Attach(r);
+}
+
+Tensor Ops::Linear(const Tensor& x, const Tensor& weight, const Tensor& bias) {
+  if (weight.Rank() != 2 || x.Rank() < 1 || x.GetShape()[x.Rank() - 1] != weight.GetShape()[1])
+    throw TensorShapeException("Linear: input " + x.GetShape().ToString() + " does not fit weights " + weight.GetShape().ToString() + " ([out, in]).");
+  int inF = weight.GetShape()[1], outF = weight.GetShape()[0];
+  int rows = (int)(x.Length() / std::max(1, inF));
+  Tensor xc = x.Contiguous(), wc = weight.Contiguous();
+  Tensor bc = bias.IsEmpty() ? Tensor() : bias.Contiguous();
+  Shape os = x.GetShape();
+  os.d[os.rank - 1] = outF;
+  Tensor r = NewOut(os);
+  Check(om_linear_fwd(C(), xc.Data(), wc.Data(), bc.IsEmpty() ? nullptr : bc.Data(), rows, inF, outF, r.Data()));
+  if (!Recording({&x, &weight, &bias})) return r;
+  Tensor none;
+  auto rec = bias.IsEmpty() ? BackwardRecord::Create(OpKind::Linear, 2, {&x, &weight})
+                            : BackwardRecord::Create(OpKind::Linear, 2, {&x, &weight, &bias});
+  rec->Save(0, xc.Detach());
+  rec->Save(1, wc.Detach());
+  rec->Ints = {rows, inF, outF};
+  return rec->Attach(r);
+}
+
+Tensor Ops::Attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& mask, float scale) {
+  if (q.Rank() != 4 || k.Rank() != 4 || v.Rank() != 4 || k.GetShape() != v.GetShape() || q.GetShape()[0] != k.GetShape()[0] ||
+      q.GetShape()[1] != k.GetShape()[1] || q.GetShape()[3] != k.GetShape()[3] || q.GetShape()[3] % 2 != 0)
+    throw TensorShapeException("Attention needs [B,H,L,D] tensors with matching batch, heads and even D, not " +
+                               q.GetShape().ToString() + ", " + k.GetShape().ToString() + ", " + v.GetShape().ToString() + ".");
+  int b = q.GetShape()[0], h = q.GetShape()[1], lq = q.GetShape()[2], lk = k.GetShape()[2], d = q.GetShape()[3];
+  int64_t maskStride = 0;
+  Tensor mc;
+  if (!mask.IsEmpty()) {
+    RequireFloat32(mask);
+    bool ok = (mask.Rank() == 2 && mask.GetShape()[0] == lq && mask.GetShape()[1] == lk) ||
+              (mask.Rank() == 3 && mask.GetShape()[0] == b && mask.GetShape()[1] == lq && mask.GetShape()[2] == lk);
+    if (!ok) throw TensorShapeException("The mask must be [" + std::to_string(lq) + "," + std::to_string(lk) + "] or [" +
+                                        std::to_string(b) + "," + std::to_string(lq) + "," + std::to_string(lk) + "], not " + mask.GetShape().ToString() + ".");
+    mc = mask.Contiguous().Detach();
+    maskStride = mask.Rank() == 2 ? 0 : (int64_t)lq * lk;
+  }
+  if (scale == 0.f || isnan(scale)) scale = 1.0f / sqrtf((float)d);
+  Tensor qc = q.Contiguous(), kc = k.Contiguous(), vc = v.Contiguous();
+  Tensor r = NewOut(q.GetShape());
+  Check(om_attention_fwd(C(), qc.Data(), kc.Data(), vc.Data(), mc.IsEmpty() ? nullptr : mc.Data(), maskStride, b, h, lq, lk,
+                         d, scale, r.Data(), nullptr));
+  if (!Recording({&q, &k, &v})) return r;
+  auto rec = BackwardRecord::Create(OpKind::Attention, 4, {&q, &k, &v});
+  rec->Save(0, qc.Detach());
+  rec->Save(1, kc.Detach());
+  rec->Save(2, vc.Detach());
+  if (!mc.IsEmpty()) rec->Save(3, mc);
+  rec->Floats = {scale};
+  rec->Ints = {maskStride};
+  return rec->Attach(r);
+}
+
+Tensor Ops::Concat(const std::vector<Tensor>& xs, int axis) {
+  if (xs.empty()) throw TensorShapeException("Concat needs at least one tensor.");
+  int rank = xs[0].Rank();
+  int ax = axis < 0 ? axis + rank : axis;
+  Shape os = xs[0].GetShape();
+  int total = 0;
+  for (const Tensor& t : xs) {
+    RequireFloat32(t);
+    if (t.Rank() != rank) throw TensorShapeException("Concat needs tensors of one rank.");
+    for (int i = 0; i < rank; i++)
+      if (i != ax && t.GetShape()[i] != os[i]) throw TensorShapeException("Concat: shapes differ off the axis.");
+    total += t.GetShape()[ax];
+  }
+  os.d[ax] = total;
+  Tensor r = NewOut(os);
+  int start = 0;
+  bool any = false;
+  for (const Tensor& t : xs) {
+    int len = t.GetShape()[ax];
+    Tensor dst = r.Slice(ax, start, start + len);
+    Check(om_strided_copy(C(), rank, t.GetShape().d.data(), t.Data(), t.Strides().data(), dst.Data(), dst.Strides().data()));
+    start += len;
+    any = any || t.RequiresGrad();
+  }
+  if (!GradMode::Enabled() || !any) return r;
+  auto rec = BackwardRecord::Create(OpKind::Concat, 0, xs);
+  rec->Ints = {ax};
+  return rec->Attach(r);
+}
+
+Tensor Ops::GlobalAvgPool2d(const Tensor& x) {
+  if (x.Rank() != 4) throw TensorShapeException("GlobalAvgPool2d needs an (N,C,H,W) input.");
+  int n = x.GetShape()[0], c = x.GetShape()[1], plane = x.GetShape()[2] * x.GetShape()[3];
+  // Mean over the flattened plane, kept as [N, C, 1, 1] like the reference (Ops.Layers.cs:463-478).
+  Tensor flat = x.Reshape(Shape{n, c, plane});
+  return Mean(flat, 2, false).Reshape(Shape{n, c, 1, 1});
+}
+
+}  // namespace omh

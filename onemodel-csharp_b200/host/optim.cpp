@@ -1,0 +1,193 @@
+// Optimizers, gradient clipping and learning-rate schedules, after src/OneModel.Training/{Optimizers,Schedules}.cs.
+// The per-step scalars are computed here on the host in double exactly as the reference does; the per-element
+// update runs in one fused multi-tensor launch on the device.
+#include <math.h>
+
+#include "omh.hpp"
+
+namespace omh {
+
+static om_ctx* C() { return Device::Current(); }
+
+Optimizer::Optimizer(std::vector<Tensor> parameters) : params_(std::move(parameters)) {
+  for (const Tensor& p : params_) {
+    if (p.GetDType() != DType::F32 || !p.IsContiguous())
+      throw TensorShapeException("Optimizers need contiguous float32 parameters.");
+  }
+}
+
+void Optimizer::ZeroGrad() {
+  for (const Tensor& p : params_) Backprop::ZeroGrad(p);
+}
+
+// Optimizer.Step (Optimizers.cs:184-219): parameters without a gradient are skipped.
+void Optimizer::Step() {
+  BeginStep();
+  std::vector<float*> p;
+  std::vector<const float*> g;
+  std::vector<int64_t> len;
+  index_.clear();
+  for (size_t i = 0; i < params_.size(); i++) {
+    const Tensor& t = params_[i];
+    if (!t.RequiresGrad()) continue;
+    Tensor grad = t.Grad();  // materialises zeros if the step produced no gradient for this parameter
+    if (grad.IsEmpty()) continue;
+    p.push_back(t.Data());
+    g.push_back(grad.Data());
+    len.push_back(t.Length());
+    index_.push_back((int)i);
+  }
+  Launch(p, g, len);
+  StepCount++;
+}
+
+// ---- SGD ------------------------------------------------------------------------------------------------------------
+Sgd::Sgd(std::vector<Tensor> parameters, float lr, float momentum, float dampening, float weightDecay, bool nesterov)
+    : Optimizer(std::move(parameters)), momentum_(momentum), dampening_(dampening), nesterov_(nesterov) {
+  LearningRate = lr;
+  WeightDecay = weightDecay;
+  if (nesterov && (momentum <= 0.f || dampening != 0.f))
+    throw std::invalid_argument("Nesterov momentum needs a positive momentum and zero dampening.");
+  if (momentum != 0.f) {
+    for (const Tensor& p : params_) buffers_.push_back(Tensor::Zeros(DType::F32, p.GetShape()));
+    initialized_.assign(params_.size(), 0);
+  }
+}
+
+void Sgd::FillHyper(void* host, int64_t) const {
+  om_sgd_hyper* h = (om_sgd_hyper*)host;
+  h->lr = LearningRate;
+  h->weight_decay = WeightDecay;
+  h->momentum = momentum_;
+  h->dampening = dampening_;
+  h->grad_scale = GradScale;
+  h->nesterov = nesterov_;
+  h->has_momentum = momentum_ != 0.f;
+}
+
+void Sgd::Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) {
+  om_sgd_hyper h;
+  FillHyper(&h, StepCount + 1);
+  std::vector<float*> buf;
+  std::vector<int32_t> first;
+  if (h.has_momentum) {
+    for (int i : index_) {
+      buf.push_back(buffers_[i].Data());
+      first.push_back(initialized_[i] == 0);
+      initialized_[i] = 1;
+    }
+  }
+  Check(om_optim_sgd_step(C(), (int32_t)p.size(), p.data(), g.data(), h.has_momentum ? buf.data() : nullptr,
+                          h.has_momentum ? first.data() : nullptr, len.data(), &h, (const om_sgd_hyper*)HyperDevice));
+}
+
+// ---- Adam -----------------------------------------------------------------------------------------------------------
+Adam::Adam(std::vector<Tensor> parameters, float lr, float beta1, float beta2, float eps, float weightDecay, bool decoupled,
+           bool amsgrad)
+    : Optimizer(std::move(parameters)), beta1_(beta1), beta2_(beta2), eps_(eps), decoupled_(decoupled), amsgrad_(amsgrad) {
+  LearningRate = lr;
+  WeightDecay = weightDecay;
+  for (const Tensor& p : params_) {
+    m_.push_back(Tensor::Zeros(DType::F32, p.GetShape()));
+    v_.push_back(Tensor::Zeros(DType::F32, p.GetShape()));
+    if (amsgrad) vmax_.push_back(Tensor::Zeros(DType::F32, p.GetShape()));
+  }
+}
+
+std::vector<Tensor> Adam::StateTensors() const {
+  std::vector<Tensor> s = m_;
+  s.insert(s.end(), v_.begin(), v_.end());
+  s.insert(s.end(), vmax_.begin(), vmax_.end());
+  return s;
+}
+
+// Adam.IntPow: binary powering in double (Optimizers.cs:483-499).
+static double IntPow(double b, int64_t n) {
+  double result = 1.0;
+  while (n > 0) {
+    if (n & 1) result *= b;
+    b *= b;
+    n >>= 1;
+  }
+  return result;
+}
+
+// Adam.BeginStep (Optimizers.cs:501-508).
+void Adam::FillHyper(void* host, int64_t t) const {
+  om_adam_hyper* h = (om_adam_hyper*)host;
+  double bc1 = 1.0 - IntPow((double)beta1_, t);
+  double bc2 = 1.0 - IntPow((double)beta2_, t);
+  h->lr = LearningRate;
+  h->beta1 = beta1_;
+  h->beta2 = beta2_;
+  h->eps = eps_;
+  h->weight_decay = WeightDecay;
+  h->step_size = (float)((double)LearningRate / bc1);
+  h->sqrt_bc2 = (float)sqrt(bc2);
+  h->grad_scale = GradScale;
+  h->decoupled = decoupled_;
+  h->amsgrad = amsgrad_;
+}
+
+void Adam::Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) {
+  om_adam_hyper h;
+  FillHyper(&h, StepCount + 1);
+  std::vector<float*> m, v, vm;
+  for (int i : index_) {
+    m.push_back(m_[i].Data());
+    v.push_back(v_[i].Data());
+    if (amsgrad_) vm.push_back(vmax_[i].Data());
+  }
+  Check(om_optim_adam_step(C(), (int32_t)p.size(), p.data(), g.data(), m.data(), v.data(), amsgrad_ ? vm.data() : nullptr,
+                           len.data(), &h, (const om_adam_hyper*)HyperDevice));
+}
+
+// ---- clipping -------------------------------------------------------------------------------------------------------
+static void CollectGrads(const std::vector<Tensor>& parameters, std::vector<float*>& g, std::vector<int64_t>& len) {
+  for (const Tensor& p : parameters) {
+    Tensor grad = p.Grad();
+    if (grad.IsEmpty()) continue;
+    g.push_back(grad.Data());
+    len.push_back(grad.Length());
+  }
+}
+
+void GradClip::ClipNormAsync(const std::vector<Tensor>& parameters, float maxNorm, bool infinityNorm, float* norm_out) {
+  if (!(maxNorm > 0.f)) throw ArgumentOutOfRangeException("The maximum norm must be positive.");
+  std::vector<float*> g;
+  std::vector<int64_t> len;
+  CollectGrads(parameters, g, len);
+  Check(om_grad_norm_clip(C(), (int32_t)g.size(), g.data(), len.data(), maxNorm, infinityNorm, norm_out));
+}
+
+float GradClip::ClipNorm(const std::vector<Tensor>& parameters, float maxNorm, bool infinityNorm) {
+  Tensor norm = Tensor::Create(DType::F32, Shape{});
+  ClipNormAsync(parameters, maxNorm, infinityNorm, norm.Data());
+  return norm.Item();
+}
+
+void GradClip::ClipValue(const std::vector<Tensor>& parameters, float clipValue) {
+  if (!(clipValue >= 0.f)) throw ArgumentOutOfRangeException("The bound must not be negative.");
+  std::vector<float*> g;
+  std::vector<int64_t> len;
+  CollectGrads(parameters, g, len);
+  Check(om_grad_clip_value(C(), (int32_t)g.size(), g.data(), len.data(), clipValue));
+}
+
+// ---- schedules (closed forms of the PyTorch schedulers the reference matches, Schedules.cs:171-422) -------------------
+float LrSchedule::Cosine(float base, int64_t step, int64_t total, float etaMin) {
+  double t = (double)(step < total ? step : total) / (double)total;
+  return (float)((double)etaMin + ((double)base - (double)etaMin) * (1.0 + cos(M_PI * t)) / 2.0);
+}
+
+float LrSchedule::LinearWarmup(float base, int64_t step, int64_t warmup, float startFactor) {
+  if (step >= warmup) return base;
+  double f = (double)startFactor + (1.0 - (double)startFactor) * (double)step / (double)warmup;
+  return (float)((double)base * f);
+}
+
+float LrSchedule::StepDecay(float base, int64_t step, int64_t stepSize, float gamma) {
+  return (float)((double)base * pow((double)gamma, (double)(step / stepSize)));
+}
+
+}  // namespace omh

@@ -1,0 +1,350 @@
+// Training-step drivers for the benchmark configurations, written against the host mirror exactly as a user of the
+// reference writes a loop (tests/GuideSamples/TrainingGuide.cs:48-67 of the reference):
+//   scope; loss = model.Forward(x); opt.ZeroGrad(); loss.Backward(); opt.Step();
+// plus what the reference does not have: whole-step CUDA graph replay and data-parallel gradient buckets.
+#include <string.h>
+
+#include <map>
+
+#include "omh.hpp"
+
+using namespace omh;
+
+#define OMH_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+thread_local std::string t_error;
+
+template <class F>
+int32_t Guard(F&& f) {
+  try {
+    f();
+    return 0;
+  } catch (const TensorShapeException& e) {
+    t_error = e.what();
+    return 1;
+  } catch (const ArgumentOutOfRangeException& e) {
+    t_error = e.what();
+    return 2;
+  } catch (const BackendException& e) {
+    t_error = e.what();
+    return 100 + e.status;
+  } catch (const std::exception& e) {
+    t_error = e.what();
+    return 10;
+  }
+}
+
+// ---- models ----------------------------------------------------------------------------------------------------------
+
+// Config 1: 784 -> 512 -> ReLU -> 512 -> ReLU -> 10, softmax cross-entropy.
+struct Mlp : NnModule {
+  std::vector<Linear*> layers;
+  Mlp(const std::vector<int>& widths, Generator& g) {
+    for (size_t i = 0; i + 1 < widths.size(); i++)
+      layers.push_back(RegisterModule(std::to_string(2 * i), new Linear(widths[i], widths[i + 1], g)));
+  }
+  Tensor Forward(const Tensor& x) override {
+    Tensor h = x;
+    for (size_t i = 0; i < layers.size(); i++) {
+      h = layers[i]->Forward(h);
+      if (i + 1 < layers.size()) h = Ops::Relu(h);
+    }
+    return h;
+  }
+};
+
+// Configs 3 and 5: token + learned position embeddings, N post-norm encoder layers, masked-LM head on gathered rows.
+struct MlmEncoder : NnModule {
+  Embedding *Tok, *Pos;
+  std::vector<TransformerEncoderLayer*> layers;
+  Linear* Head;
+  int Width;
+  MlmEncoder(int nLayers, int width, int heads, int ff, int vocab, int seq, Generator& g) : Width(width) {
+    Tok = RegisterModule("tok", new Embedding(vocab, width, g));
+    Pos = RegisterModule("pos", new Embedding(seq, width, g));
+    for (int i = 0; i < nLayers; i++)
+      layers.push_back(RegisterModule("layers." + std::to_string(i), new TransformerEncoderLayer(width, heads, ff, g)));
+    Head = RegisterModule("head", new Linear(width, vocab, g));
+  }
+  Tensor Forward(const Tensor&) override { throw InvalidOperationException("use Logits(ids, positions, rows)"); }
+  // ids [B,S]; positions [S] = 0..S-1; rows [R] = flat indices of the masked positions. Returns logits [R, vocab].
+  Tensor Logits(const Tensor& ids, const Tensor& positions, const Tensor& rows) {
+    Tensor x = Ops::Add(Tok->Forward(ids), Pos->Forward(positions));
+    for (auto* l : layers) x = l->Forward(x);
+    int b = ids.GetShape()[0], s = ids.GetShape()[1];
+    Tensor hidden = x.Reshape(Shape{b * s, Width});
+    // Row gather on an activation, the idiom of Ops.Recurrent.cs:362 in the reference.
+    Tensor picked = Ops::Embedding(hidden, rows);
+    return Head->Forward(picked);
+  }
+};
+
+}  // namespace
+
+struct omh_trainer {
+  int kind = 0;
+  std::vector<int64_t> cfg;
+  std::unique_ptr<NnModule> model;
+  std::unique_ptr<Optimizer> opt;
+  std::vector<std::pair<std::string, Tensor>> params;
+  // persistent device inputs
+  std::vector<Tensor> inputs;
+  Tensor positions;
+  Tensor loss_out;     // device scalar that survives the step
+  Tensor flat_grads;   // all gradients, contiguous, in reverse registration order
+  float ce_denominator = 0.f;
+  float clip_norm = 0.f;
+  // graph replay
+  void* graph = nullptr;
+  Tensor hyper_dev;
+  std::vector<uint8_t> hyper_host;
+  int64_t steps_done = 0;
+  // data parallel
+  int world = 1, rank = 0;
+  struct BucketInfo { int64_t begin, end; int pending; int total; };
+  std::vector<BucketInfo> buckets;
+  std::map<AutogradMeta*, int> bucket_of;
+};
+
+static void BuildFlatGrads(omh_trainer* t) {
+  int64_t total = 0;
+  for (auto& p : t->params) total += p.second.Length();
+  t->flat_grads = Tensor::Zeros(DType::F32, Shape{(int)std::min<int64_t>(total, INT32_MAX)});
+  if (total > INT32_MAX) throw TensorShapeException("more than 2^31-1 parameters");
+  // Reverse registration order: the gradients that become final first (last layers) sit at the front, so the first
+  // buckets complete early in the backward sweep.
+  int64_t off = 0;
+  const int64_t bucket_elems = 6 * 1024 * 1024;  // ~25 MB of fp32
+  int64_t bucket_begin = 0;
+  for (int i = (int)t->params.size() - 1; i >= 0; i--) {
+    Tensor& p = t->params[i].second;
+    auto meta = p.Autograd();
+    Tensor view = t->flat_grads.View(p.GetShape(), ContiguousStrides(p.GetShape()), off);
+    meta->Grad = view;
+    meta->GradIsZero = true;
+    int64_t len = p.Length();
+    if (off + len - bucket_begin > bucket_elems && off > bucket_begin) {
+      t->buckets.push_back({bucket_begin, off, 0, 0});
+      bucket_begin = off;
+    }
+    t->bucket_of[meta.get()] = (int)t->buckets.size();
+    off += len;
+  }
+  t->buckets.push_back({bucket_begin, off, 0, 0});
+  for (auto& kv : t->bucket_of) t->buckets[kv.second].total++;
+}
+
+static Tensor Forward(omh_trainer* t) {
+  if (t->kind == 1) {
+    Tensor logits = t->model->Forward(t->inputs[0]);
+    return Ops::CrossEntropy(logits, t->inputs[1], true, -100, t->ce_denominator);
+  }
+  auto* m = static_cast<MlmEncoder*>(t->model.get());
+  Tensor logits = m->Logits(t->inputs[0], t->positions, t->inputs[1]);
+  return Ops::CrossEntropy(logits, t->inputs[2], true, -100, t->ce_denominator);
+}
+
+// One training step on the device inputs; leaves the loss in t->loss_out.
+static void StepBody(omh_trainer* t) {
+  om_ctx* ctx = Device::Current();
+  ActivationScope scope;
+  Tensor loss = Forward(t);
+  Check(om_memcpy_d2d(ctx, t->loss_out.RawData(), loss.RawData(), 4));
+  t->opt->ZeroGrad();
+  if (t->world > 1) {
+    for (auto& b : t->buckets) b.pending = b.total;
+    Backprop::GradReadyHook = [t, ctx](AutogradMeta* leaf) {
+      auto it = t->bucket_of.find(leaf);
+      if (it == t->bucket_of.end()) return;
+      auto& b = t->buckets[it->second];
+      if (--b.pending == 0) Check(om_dp_allreduce_bucket(ctx, it->second));
+    };
+  }
+  loss.Backward();
+  if (t->world > 1) {
+    Backprop::GradReadyHook = nullptr;
+    // Buckets whose parameters got no gradient this step are still exchanged so that all ranks agree.
+    for (size_t i = 0; i < t->buckets.size(); i++)
+      if (t->buckets[i].pending > 0) Check(om_dp_allreduce_bucket(ctx, (int32_t)i));
+    Check(om_dp_allreduce(ctx, t->loss_out.RawData(), 1, OM_F32));
+    Check(om_dp_wait(ctx, 0));
+  }
+  if (t->clip_norm > 0.f) GradClip::ClipNormAsync(t->opt->Parameters(), t->clip_norm, false, nullptr);
+  t->opt->Step();
+}
+
+OMH_API int32_t omh_trainer_last_error(char* buf, size_t n) {
+  size_t len = std::min(n - 1, t_error.size());
+  memcpy(buf, t_error.data(), len);
+  buf[len] = 0;
+  return 0;
+}
+
+// kind 1 (MLP): cfg = [batch, in, h1, h2, out]. kind 3 (masked-LM encoder): cfg = [batch, seq, layers, width, heads,
+// ff, vocab, masked_rows]. hyper = [lr, weight_decay, clip_norm (0 = off)].
+OMH_API int32_t omh_trainer_create(int32_t kind, const int64_t* cfg, int32_t ncfg, uint64_t seed, const double* hyper,
+                                   omh_trainer** out) {
+  return Guard([&] {
+    auto t = std::make_unique<omh_trainer>();
+    t->kind = kind;
+    t->cfg.assign(cfg, cfg + ncfg);
+    Generator g(seed);
+    if (kind == 1) {
+      if (ncfg < 3) throw TensorShapeException("MLP config needs [batch, widths...]");
+      std::vector<int> widths;
+      for (int i = 1; i < ncfg; i++) widths.push_back((int)cfg[i]);
+      t->model.reset(new Mlp(widths, g));
+      t->inputs.push_back(Tensor::Zeros(DType::F32, Shape{(int)cfg[0], widths[0]}));
+      t->inputs.push_back(Tensor::Zeros(DType::I64, Shape{(int)cfg[0]}));
+    } else if (kind == 3) {
+      if (ncfg != 8) throw TensorShapeException("encoder config needs 8 integers");
+      int batch = (int)cfg[0], seq = (int)cfg[1], rows = (int)cfg[7];
+      t->model.reset(new MlmEncoder((int)cfg[2], (int)cfg[3], (int)cfg[4], (int)cfg[5], (int)cfg[6], seq, g));
+      t->inputs.push_back(Tensor::Zeros(DType::I32, Shape{batch, seq}));
+      t->inputs.push_back(Tensor::Zeros(DType::I32, Shape{rows}));
+      t->inputs.push_back(Tensor::Zeros(DType::I64, Shape{rows}));
+      std::vector<int32_t> pos(seq);
+      for (int i = 0; i < seq; i++) pos[i] = i;
+      t->positions = Tensor::FromHostInt32(pos.data(), Shape{seq});
+    } else {
+      throw InvalidOperationException("unknown trainer kind");
+    }
+    t->params = t->model->NamedParameters();
+    std::vector<Tensor> ps;
+    for (auto& p : t->params) ps.push_back(p.second);
+    t->opt.reset(new AdamW(ps, (float)hyper[0], 0.9f, 0.999f, 1e-8f, (float)hyper[1]));
+    t->clip_norm = (float)hyper[2];
+    t->loss_out = Tensor::Zeros(DType::F32, Shape{});
+    BuildFlatGrads(t.get());
+    *out = t.release();
+  });
+}
+
+OMH_API int32_t omh_trainer_free(omh_trainer* t) {
+  if (t && t->graph) om_graph_destroy(Device::Current(), t->graph);
+  delete t;
+  return 0;
+}
+
+OMH_API int32_t omh_trainer_param_count(omh_trainer* t) { return (int32_t)t->params.size(); }
+
+OMH_API int32_t omh_trainer_param_info(omh_trainer* t, int32_t i, char* name, size_t n, int32_t* rank, int32_t* shape) {
+  if (i < 0 || i >= (int)t->params.size()) return 1;
+  strncpy(name, t->params[i].first.c_str(), n - 1);
+  name[n - 1] = 0;
+  *rank = t->params[i].second.Rank();
+  for (int k = 0; k < *rank; k++) shape[k] = t->params[i].second.GetShape()[k];
+  return 0;
+}
+
+OMH_API int32_t omh_trainer_get_param(omh_trainer* t, int32_t i, float* dst) {
+  return Guard([&] { t->params[i].second.CopyToHost(dst); });
+}
+OMH_API int32_t omh_trainer_set_param(omh_trainer* t, int32_t i, const float* src) {
+  return Guard([&] { t->params[i].second.CopyFromHost(src); });
+}
+OMH_API int32_t omh_trainer_get_grad(omh_trainer* t, int32_t i, float* dst) {
+  return Guard([&] {
+    Tensor g = t->params[i].second.Grad();
+    if (g.IsEmpty()) throw InvalidOperationException("no gradient yet");
+    g.CopyToHost(dst);
+  });
+}
+
+OMH_API int32_t omh_trainer_input_count(omh_trainer* t) { return (int32_t)t->inputs.size(); }
+OMH_API int64_t omh_trainer_input_bytes(omh_trainer* t, int32_t i) {
+  return t->inputs[i].Length() * (int64_t)SizeOf(t->inputs[i].GetDType());
+}
+
+// Joins a data-parallel group; the cross-entropy then divides by `global_rows` (the counted rows of all ranks) so that
+// the summed gradients are the gradient of the global mean.
+OMH_API int32_t omh_trainer_dp_init(omh_trainer* t, const uint8_t* id128, int32_t rank, int32_t world, int64_t global_rows) {
+  return Guard([&] {
+    om_ctx* ctx = Device::Current();
+    Check(om_dp_init(ctx, id128, rank, world));
+    t->world = world;
+    t->rank = rank;
+    t->ce_denominator = (float)global_rows;
+    for (size_t i = 0; i < t->buckets.size(); i++)
+      Check(om_dp_register_bucket(ctx, (int32_t)i, t->flat_grads.Data() + t->buckets[i].begin, t->buckets[i].end - t->buckets[i].begin));
+  });
+}
+
+static void CopyInputs(omh_trainer* t, const void* const* inputs_host) {
+  om_ctx* ctx = Device::Current();
+  for (size_t i = 0; i < t->inputs.size(); i++)
+    Check(om_memcpy_h2d(ctx, t->inputs[i].RawData(), inputs_host[i], (size_t)omh_trainer_input_bytes(t, (int32_t)i)));
+}
+
+static void RunStep(omh_trainer* t) {
+  om_ctx* ctx = Device::Current();
+  if (t->graph) {
+    // Per-step scalars of the optimizer for this step, written where the captured kernels read them.
+    t->opt->FillHyper(t->hyper_host.data(), t->steps_done + 1);
+    Check(om_memcpy_h2d(ctx, t->hyper_dev.RawData(), t->hyper_host.data(), t->hyper_host.size()));
+    Check(om_graph_launch(ctx, t->graph));
+    t->opt->StepCount = t->steps_done + 1;
+  } else {
+    StepBody(t);
+  }
+  t->steps_done++;
+}
+
+// The call a user makes: host batch in, loss out. inputs_host[i] should be pinned for an asynchronous copy.
+OMH_API int32_t omh_trainer_step(omh_trainer* t, const void* const* inputs_host, float* loss) {
+  return Guard([&] {
+    CopyInputs(t, inputs_host);
+    RunStep(t);
+    if (loss) Check(om_memcpy_d2h(Device::Current(), loss, t->loss_out.RawData(), 4));
+  });
+}
+
+// Copies a batch to the device without stepping, and steps on the resident batch without copies or read-back.
+OMH_API int32_t omh_trainer_load_inputs(omh_trainer* t, const void* const* inputs_host) {
+  return Guard([&] {
+    CopyInputs(t, inputs_host);
+    Check(om_sync(Device::Current()));
+  });
+}
+OMH_API int32_t omh_trainer_step_resident(omh_trainer* t) {
+  return Guard([&] { RunStep(t); });
+}
+OMH_API int32_t omh_trainer_read_loss(omh_trainer* t, float* loss) {
+  return Guard([&] { Check(om_memcpy_d2h(Device::Current(), loss, t->loss_out.RawData(), 4)); });
+}
+OMH_API int32_t omh_trainer_sync(omh_trainer*) {
+  return Guard([&] { Check(om_sync(Device::Current())); });
+}
+
+// Captures one step into a CUDA graph; later steps replay it. At least one eager step must have run so that the memory
+// pool already holds every block the step needs.
+OMH_API int32_t omh_trainer_enable_graph(omh_trainer* t) {
+  return Guard([&] {
+    if (t->graph) return;
+    if (t->steps_done < 1) throw InvalidOperationException("run at least one eager step before capturing");
+    om_ctx* ctx = Device::Current();
+    t->hyper_host.assign(t->opt->HyperBytes(), 0);
+    t->hyper_dev = Tensor::Zeros(DType::F32, Shape{(int)(t->opt->HyperBytes() + 3) / 4});
+    t->opt->HyperDevice = t->hyper_dev.RawData();
+    Check(om_sync(ctx));
+    int64_t saved_count = t->opt->StepCount;
+    Check(om_graph_begin(ctx));
+    int32_t st = 0;
+    try {
+      StepBody(t);
+    } catch (...) {
+      void* g = nullptr;
+      om_graph_end(ctx, &g);
+      if (g) om_graph_destroy(ctx, g);
+      t->opt->HyperDevice = nullptr;
+      throw;
+    }
+    (void)st;
+    Check(om_graph_end(ctx, &t->graph));
+    t->opt->StepCount = saved_count;  // capturing executed nothing
+  });
+}
+
+OMH_API int64_t omh_trainer_steps_done(omh_trainer* t) { return t->steps_done; }

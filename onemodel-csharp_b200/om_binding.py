@@ -1,0 +1,481 @@
+"""ctypes binding of libonemodel_b200.so (the C ABI) and libonemodel_b200_host.so (the C++ mirror of the
+reference's Tensor/autograd/optimizer API). Used by the tests, the smoke entry and the bench.
+
+There is no CPU path: loading fails loudly when a library is missing, and creating a context fails when no
+sm_100 device is visible.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+KERNEL_LIB = os.path.join(_HERE, "libonemodel_b200.so")
+HOST_LIB = os.path.join(_HERE, "libonemodel_b200_host.so")
+
+OM_F32, OM_I32, OM_I64 = 0, 1, 2
+OM_TF32, OM_BF16_OPERANDS, OM_CHECKED = 1, 2, 4
+_NP2OM = {np.dtype("float32"): OM_F32, np.dtype("int32"): OM_I32, np.dtype("int64"): OM_I64}
+_OM2NP = {OM_F32: np.float32, OM_I32: np.int32, OM_I64: np.int64}
+
+UNARY = dict(none=0, relu=1, gelu_erf=2, gelu_tanh=3, sigmoid=4, tanh=5, neg=6, exp=7, sqrt=8, erf=9)
+BINARY = dict(add=0, sub=1, mul=2, div=3)
+
+
+class OmError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"[status {status}] {message}")
+        self.status = status
+
+
+class ShapeError(OmError):
+    pass
+
+
+class IndexOutOfRange(OmError):
+    pass
+
+
+_kernel = None
+_host = None
+
+
+def kernel_lib():
+    """The C-ABI library. Raises if it has not been built."""
+    global _kernel
+    if _kernel is None:
+        if not os.path.exists(KERNEL_LIB):
+            raise RuntimeError(f"{KERNEL_LIB} is missing: run __graft_entry__.build() (there is no fallback path)")
+        _kernel = C.CDLL(KERNEL_LIB, mode=C.RTLD_GLOBAL)
+    return _kernel
+
+
+def host_lib():
+    global _host
+    if _host is None:
+        kernel_lib()
+        if not os.path.exists(HOST_LIB):
+            raise RuntimeError(f"{HOST_LIB} is missing: run __graft_entry__.build()")
+        _host = C.CDLL(HOST_LIB, mode=C.RTLD_GLOBAL)
+        _host.omh_tensor_data.restype = C.c_void_p
+        _host.omh_lr_cosine.restype = C.c_float
+        _host.omh_lr_cosine.argtypes = [C.c_float, C.c_int64, C.c_int64, C.c_float]
+        _host.omh_lr_linear_warmup.restype = C.c_float
+        _host.omh_lr_linear_warmup.argtypes = [C.c_float, C.c_int64, C.c_int64, C.c_float]
+    return _host
+
+
+def _raise(status, message):
+    code = status - 100 if status >= 100 else status
+    if code == 1:
+        raise ShapeError(code, message)
+    if code == 2:
+        raise IndexOutOfRange(code, message)
+    raise OmError(code, message)
+
+
+class Context:
+    """One om_ctx: a device, a stream and a memory pool. `ctx.call("om_xxx", ...)` checks the status."""
+
+    def __init__(self, device=0, flags=0):
+        self.lib = kernel_lib()
+        self.host = host_lib()
+        self.handle = C.c_void_p()
+        st = self.host.omh_init(C.c_int32(device), C.c_uint32(flags), C.byref(self.handle))
+        if st != 0:
+            buf = C.create_string_buffer(512)
+            self.host.omh_last_error(buf, 512)
+            _raise(st, buf.value.decode())
+        self.flags = flags
+
+    def make_current(self):
+        self.host.omh_set_current(self.handle)
+
+    def set_flags(self, flags):
+        self.call("om_ctx_set_flags", self.handle, C.c_uint32(flags))
+        self.flags = flags
+
+    def last_error(self):
+        buf = C.create_string_buffer(512)
+        self.lib.om_last_error(self.handle, buf, C.c_size_t(512))
+        return buf.value.decode()
+
+    def call(self, name, *args):
+        st = getattr(self.lib, name)(*args)
+        if st != 0:
+            _raise(st, self.last_error())
+
+    def sync(self):
+        self.call("om_sync", self.handle)
+
+    def close(self):
+        if self.handle:
+            self.lib.om_ctx_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    # ---- raw device arrays for per-entry-point tests ----
+    def to_device(self, array):
+        a = np.ascontiguousarray(array)
+        return DeviceArray(self, a.shape, a.dtype, a)
+
+    def empty(self, shape, dtype=np.float32):
+        return DeviceArray(self, tuple(np.atleast_1d(shape)) if not isinstance(shape, tuple) else shape, np.dtype(dtype))
+
+    def zeros(self, shape, dtype=np.float32):
+        d = self.empty(shape, dtype)
+        self.call("om_memset", self.handle, d.ptr, C.c_int32(0), C.c_size_t(d.nbytes))
+        return d
+
+
+class DeviceArray:
+    def __init__(self, ctx, shape, dtype, host=None):
+        self.ctx, self.shape, self.dtype = ctx, tuple(int(s) for s in shape), np.dtype(dtype)
+        self.size = int(np.prod(self.shape)) if len(self.shape) else 1
+        self.nbytes = self.size * self.dtype.itemsize
+        self.ptr = C.c_void_p()
+        ctx.call("om_alloc", ctx.handle, C.c_size_t(max(self.nbytes, 4)), C.c_int32(0), C.byref(self.ptr))
+        if host is not None and self.nbytes:
+            h = np.ascontiguousarray(host, dtype=self.dtype)
+            ctx.call("om_memcpy_h2d", ctx.handle, self.ptr, h.ctypes.data_as(C.c_void_p), C.c_size_t(self.nbytes))
+            ctx.sync()
+
+    def numpy(self):
+        out = np.empty(self.shape, dtype=self.dtype)
+        if self.nbytes:
+            self.ctx.call("om_memcpy_d2h", self.ctx.handle, out.ctypes.data_as(C.c_void_p), self.ptr, C.c_size_t(self.nbytes))
+        return out
+
+    def __del__(self):
+        try:
+            if self.ptr and self.ctx.handle:
+                self.ctx.lib.om_free(self.ctx.handle, self.ptr)
+        except Exception:
+            pass
+
+
+def i32(v):
+    return C.c_int32(int(v))
+
+
+def i64(v):
+    return C.c_int64(int(v))
+
+
+def f32(v):
+    return C.c_float(float(v))
+
+
+def int_array(values, ctype=C.c_int32):
+    return (ctype * max(len(values), 1))(*[int(v) for v in values])
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Host mirror: Tensor with autograd
+
+
+def _hcheck(st):
+    if st != 0:
+        buf = C.create_string_buffer(512)
+        host_lib().omh_last_error(buf, C.c_size_t(512))
+        _raise(st, buf.value.decode())
+
+
+class Tensor:
+    """Handle to an omh::Tensor (device memory, autograd meta). Mirrors RecursiveAI.OneModel.Tensors.Tensor."""
+
+    def __init__(self, handle):
+        self.h = handle
+
+    @staticmethod
+    def from_numpy(a, requires_grad=False):
+        a = np.ascontiguousarray(a)
+        if a.dtype not in _NP2OM:
+            a = a.astype(np.float32)
+        h = C.c_void_p()
+        shape = int_array(a.shape)
+        _hcheck(host_lib().omh_tensor_from_host(i32(_NP2OM[a.dtype]), i32(a.ndim), shape, a.ctypes.data_as(C.c_void_p), C.byref(h)))
+        t = Tensor(h)
+        if requires_grad:
+            t.requires_grad = True
+        return t
+
+    def __del__(self):
+        try:
+            if self.h:
+                host_lib().omh_tensor_free(self.h)
+        except Exception:
+            pass
+
+    def _info(self):
+        dt, rank = C.c_int32(), C.c_int32()
+        shape = (C.c_int32 * 8)()
+        strides = (C.c_int64 * 8)()
+        _hcheck(host_lib().omh_tensor_info(self.h, C.byref(dt), C.byref(rank), shape, strides))
+        return dt.value, tuple(shape[: rank.value]), tuple(strides[: rank.value])
+
+    @property
+    def shape(self):
+        return self._info()[1]
+
+    @property
+    def dtype(self):
+        return _OM2NP[self._info()[0]]
+
+    def numpy(self):
+        dt, shape, _ = self._info()
+        out = np.empty(shape, dtype=_OM2NP[dt])
+        if out.size:
+            _hcheck(host_lib().omh_tensor_to_host(self.h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def item(self):
+        return float(self.numpy().reshape(-1)[0])
+
+    def copy_from(self, a):
+        a = np.ascontiguousarray(a, dtype=self.dtype)
+        _hcheck(host_lib().omh_tensor_copy_from_host(self.h, a.ctypes.data_as(C.c_void_p)))
+
+    @property
+    def data_ptr(self):
+        return host_lib().omh_tensor_data(self.h)
+
+    @property
+    def requires_grad(self):
+        return bool(host_lib().omh_tensor_requires_grad(self.h))
+
+    @requires_grad.setter
+    def requires_grad(self, on):
+        _hcheck(host_lib().omh_tensor_set_requires_grad(self.h, i32(1 if on else 0)))
+
+    @property
+    def grad(self):
+        h = C.c_void_p()
+        _hcheck(host_lib().omh_tensor_grad(self.h, C.byref(h)))
+        return Tensor(h) if h else None
+
+    def zero_grad(self):
+        _hcheck(host_lib().omh_tensor_zero_grad(self.h))
+
+    def clear_grad(self):
+        _hcheck(host_lib().omh_tensor_clear_grad(self.h))
+
+    def backward(self, gradient=None, retain_graph=False):
+        _hcheck(host_lib().omh_backward(self.h, gradient.h if gradient is not None else None, i32(1 if retain_graph else 0)))
+
+    # views
+    def reshape(self, *shape):
+        return call("reshape", [self], ints=_flat(shape))
+
+    def permute(self, *axes):
+        return call("permute", [self], ints=_flat(axes))
+
+    def t(self):
+        return call("t", [self])
+
+    def slice(self, axis, start, end, step=1):
+        return call("slice", [self], ints=[axis, start, end, step])
+
+    def select(self, axis, index):
+        return call("select", [self], ints=[axis, index])
+
+    def expand(self, *shape):
+        return call("expand", [self], ints=_flat(shape))
+
+    def flip(self, axis):
+        return call("flip", [self], ints=[axis])
+
+    def clone(self):
+        return call("clone", [self])
+
+    def detach(self):
+        return call("detach", [self])
+
+    def __add__(self, o):
+        return call("add", [self, o])
+
+    def __sub__(self, o):
+        return call("sub", [self, o])
+
+    def __mul__(self, o):
+        return call("mul", [self, o])
+
+    def __truediv__(self, o):
+        return call("div", [self, o])
+
+    def __neg__(self):
+        return call("neg", [self])
+
+
+def _flat(xs):
+    if len(xs) == 1 and isinstance(xs[0], (tuple, list)):
+        return list(xs[0])
+    return list(xs)
+
+
+def call(op, inputs, ints=(), floats=()):
+    """Ops.* by name (see omh_call in host/capi.cpp): returns a Tensor."""
+    n = len(inputs)
+    arr = (C.c_void_p * max(n, 1))(*[(t.h if t is not None else None) for t in inputs])
+    ia = (C.c_int64 * max(len(ints), 1))(*[int(v) for v in ints])
+    fa = (C.c_double * max(len(floats), 1))(*[float(v) for v in floats])
+    out = C.c_void_p()
+    _hcheck(host_lib().omh_call(op.encode(), i32(n), arr, i32(len(ints)), ia, i32(len(floats)), fa, C.byref(out)))
+    return Tensor(out)
+
+
+class no_grad:
+    def __enter__(self):
+        host_lib().omh_no_grad(i32(1))
+
+    def __exit__(self, *a):
+        host_lib().omh_no_grad(i32(0))
+
+
+class Optimizer:
+    """Sgd / Adam / AdamW of RecursiveAI.OneModel.Training (Optimizers.cs)."""
+
+    def __init__(self, kind, params, floats, ints):
+        self.params = list(params)
+        arr = (C.c_void_p * len(self.params))(*[p.h for p in self.params])
+        fa = (C.c_double * len(floats))(*floats)
+        ia = (C.c_int64 * max(len(ints), 1))(*ints)
+        self.h = C.c_void_p()
+        _hcheck(host_lib().omh_optim_create(i32(kind), i32(len(self.params)), arr, fa, ia, C.byref(self.h)))
+
+    @staticmethod
+    def sgd(params, lr, momentum=0.0, dampening=0.0, weight_decay=0.0, nesterov=False):
+        return Optimizer(0, params, [lr, momentum, dampening, weight_decay], [1 if nesterov else 0])
+
+    @staticmethod
+    def adam(params, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, amsgrad=False):
+        return Optimizer(1, params, [lr, beta1, beta2, eps, weight_decay], [1 if amsgrad else 0])
+
+    @staticmethod
+    def adamw(params, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, amsgrad=False):
+        return Optimizer(2, params, [lr, beta1, beta2, eps, weight_decay], [1 if amsgrad else 0])
+
+    def step(self):
+        _hcheck(host_lib().omh_optim_step(self.h))
+
+    def zero_grad(self):
+        _hcheck(host_lib().omh_optim_zero_grad(self.h))
+
+    def set_lr(self, lr):
+        host_lib().omh_optim_set_lr(self.h, C.c_float(lr))
+
+    def __del__(self):
+        try:
+            if self.h:
+                host_lib().omh_optim_free(self.h)
+        except Exception:
+            pass
+
+
+def clip_norm(params, max_norm, infinity=False):
+    arr = (C.c_void_p * len(params))(*[p.h for p in params])
+    total = C.c_float()
+    _hcheck(host_lib().omh_clip_norm(i32(len(params)), arr, C.c_float(max_norm), i32(1 if infinity else 0), C.byref(total)))
+    return total.value
+
+
+def clip_value(params, clip):
+    arr = (C.c_void_p * len(params))(*[p.h for p in params])
+    _hcheck(host_lib().omh_clip_value(i32(len(params)), arr, C.c_float(clip)))
+
+
+class Trainer:
+    """A benchmark-configuration training loop held on the device (host/trainer.cpp).
+
+    kind 'mlp': cfg = [batch, in, hidden..., out]; kind 'mlm': cfg = [batch, seq, layers, width, heads, ff, vocab, rows].
+    step(inputs) takes the host batch (numpy arrays) and returns the loss: the call a user makes."""
+
+    KINDS = {"mlp": 1, "mlm": 3}
+
+    def __init__(self, kind, cfg, lr, weight_decay=0.01, clip_norm=0.0, seed=0):
+        self.h = C.c_void_p()
+        cfg_a = (C.c_int64 * len(cfg))(*[int(v) for v in cfg])
+        hyper = (C.c_double * 3)(lr, weight_decay, clip_norm)
+        self._check(host_lib().omh_trainer_create(i32(self.KINDS[kind]), cfg_a, i32(len(cfg)), C.c_uint64(seed), hyper, C.byref(self.h)))
+        self.kind, self.cfg = kind, list(cfg)
+        host_lib().omh_trainer_input_bytes.restype = C.c_int64
+        host_lib().omh_trainer_steps_done.restype = C.c_int64
+
+    @staticmethod
+    def _check(st):
+        if st != 0:
+            buf = C.create_string_buffer(512)
+            host_lib().omh_trainer_last_error(buf, C.c_size_t(512))
+            _raise(st, buf.value.decode())
+
+    def named_parameters(self):
+        out = []
+        n = host_lib().omh_trainer_param_count(self.h)
+        for i in range(n):
+            name = C.create_string_buffer(128)
+            rank = C.c_int32()
+            shape = (C.c_int32 * 8)()
+            host_lib().omh_trainer_param_info(self.h, i32(i), name, C.c_size_t(128), C.byref(rank), shape)
+            out.append((name.value.decode(), tuple(shape[: rank.value])))
+        return out
+
+    def get_param(self, i, shape):
+        a = np.empty(shape, np.float32)
+        self._check(host_lib().omh_trainer_get_param(self.h, i32(i), a.ctypes.data_as(C.c_void_p)))
+        return a
+
+    def set_param(self, i, a):
+        a = np.ascontiguousarray(a, np.float32)
+        self._check(host_lib().omh_trainer_set_param(self.h, i32(i), a.ctypes.data_as(C.c_void_p)))
+
+    def get_grad(self, i, shape):
+        a = np.empty(shape, np.float32)
+        self._check(host_lib().omh_trainer_get_grad(self.h, i32(i), a.ctypes.data_as(C.c_void_p)))
+        return a
+
+    def state_dict(self):
+        return {name: self.get_param(i, shape) for i, (name, shape) in enumerate(self.named_parameters())}
+
+    def input_bytes(self):
+        n = host_lib().omh_trainer_input_count(self.h)
+        return [int(host_lib().omh_trainer_input_bytes(self.h, i32(i))) for i in range(n)]
+
+    def _ptrs(self, inputs):
+        self._keep = [np.ascontiguousarray(a) for a in inputs]
+        for a, nbytes in zip(self._keep, self.input_bytes()):
+            assert a.nbytes == nbytes, (a.shape, a.dtype, nbytes)
+        return (C.c_void_p * len(self._keep))(*[a.ctypes.data for a in self._keep])
+
+    def step(self, inputs):
+        loss = C.c_float()
+        self._check(host_lib().omh_trainer_step(self.h, self._ptrs(inputs), C.byref(loss)))
+        return loss.value
+
+    def step_ptrs(self, ptr_table, loss_ref):
+        """step() with a prebuilt table of (pinned) host pointers: no Python-side allocation in the timed region."""
+        self._check(host_lib().omh_trainer_step(self.h, ptr_table, loss_ref))
+
+    def load_inputs(self, inputs):
+        self._check(host_lib().omh_trainer_load_inputs(self.h, self._ptrs(inputs)))
+
+    def step_resident(self):
+        self._check(host_lib().omh_trainer_step_resident(self.h))
+
+    def read_loss(self):
+        loss = C.c_float()
+        self._check(host_lib().omh_trainer_read_loss(self.h, C.byref(loss)))
+        return loss.value
+
+    def sync(self):
+        self._check(host_lib().omh_trainer_sync(self.h))
+
+    def enable_graph(self):
+        self._check(host_lib().omh_trainer_enable_graph(self.h))
+
+    def dp_init(self, id128, rank, world, global_rows):
+        buf = (C.c_uint8 * 128).from_buffer_copy(bytes(id128))
+        self._check(host_lib().omh_trainer_dp_init(self.h, buf, i32(rank), i32(world), C.c_int64(global_rows)))
+
+    def close(self):
+        if self.h:
+            host_lib().omh_trainer_free(self.h)
+            self.h = C.c_void_p()

@@ -1,0 +1,300 @@
+"""TEST INFRASTRUCTURE - NOT PART OF THE PRODUCT.
+
+numpy front end of the CPU restatement of the reference's training hot path (oracle/om_oracle_*.c), plus a small
+reverse-mode tape that replays the reference engine's traversal and accumulation order
+(src/OneModel/Tensors/Autograd/Engine.cs:124-344 of the reference: iterative DFS post-order over record inputs,
+reverse sweep, first gradient adopted, later ones added in arrival order).
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may import this module.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+i64p = np.ctypeslib.ndpointer(dtype=np.int64, flags="C_CONTIGUOUS")
+i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+
+
+def build():
+    subprocess.check_call(["make", "-s", "-C", _HERE])
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "libom_oracle.so")
+        if not os.path.exists(path):
+            build()
+        _LIB = C.CDLL(path)
+        _LIB.orc_sumsq.restype = C.c_double
+    return _LIB
+
+
+def _f(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i64(a):
+    return np.ascontiguousarray(a, dtype=np.int64)
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+# ---- plain functions ---------------------------------------------------------------------------------------------------
+
+def gemm(a, b, ta=False, tb=False, mode="fp32"):
+    """op(a) @ op(b) with the reference's one-accumulator FMA order. mode 'tf32'/'bf16' rounds the operands first."""
+    a, b = _f(a), _f(b)
+    if mode == "tf32":
+        a, b = trunc_tf32(a), trunc_tf32(b)
+    elif mode == "bf16":
+        a, b = round_bf16(a), round_bf16(b)
+    m, k = (a.shape[1], a.shape[0]) if ta else a.shape
+    n = b.shape[0] if tb else b.shape[1]
+    c = np.empty((m, n), np.float32)
+    lib().orc_gemm(int(ta), int(tb), m, n, k, _p(a), a.shape[1], _p(b), b.shape[1], _p(c), n, 0)
+    return c
+
+
+def round_bf16(x):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().orc_round_bf16(_p(x), _p(y), C.c_int64(x.size))
+    return y
+
+
+def trunc_tf32(x):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().orc_trunc_tf32(_p(x), _p(y), C.c_int64(x.size))
+    return y
+
+
+UNARY = dict(none=0, relu=1, gelu_erf=2, gelu_tanh=3, sigmoid=4, tanh=5, neg=6, exp=7, sqrt=8, erf=9)
+
+
+def unary(op, x):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().orc_unary(UNARY[op], _p(x), _p(y), C.c_int64(x.size))
+    return y
+
+
+def unary_bwd(op, g, saved):
+    g, saved = _f(g), _f(saved)
+    dx = np.empty_like(saved)
+    lib().orc_unary_bwd(UNARY[op], _p(g), _p(saved), _p(dx), C.c_int64(g.size))
+    return dx
+
+
+def sum_to(g, target_shape):
+    """BackwardOps.SumTo: g summed down to target_shape (double accumulators)."""
+    g = _f(g)
+    target_shape = tuple(target_shape)
+    if g.shape == target_shape:
+        return g
+    rank, lead = g.ndim, g.ndim - len(target_shape)
+    ts = [0] * rank
+    acc = 1
+    for ax in range(rank - 1, -1, -1):
+        t = ax - lead
+        if t < 0 or target_shape[t] == 1:
+            ts[ax] = 0
+        else:
+            ts[ax] = acc
+            acc *= target_shape[t]
+    out = np.empty(target_shape, np.float32)
+    shape = (C.c_int32 * max(rank, 1))(*g.shape)
+    tsa = (C.c_int64 * max(rank, 1))(*ts)
+    lib().orc_sum_to(rank, shape, _p(g), tsa, _p(out), C.c_int64(out.size))
+    return out
+
+
+def reduce_fwd(x, axis, mean):
+    x = _f(x)
+    if axis is None:
+        outer, n, inner, oshape = 1, x.size, 1, ()
+    else:
+        axis %= x.ndim
+        outer = int(np.prod(x.shape[:axis], dtype=np.int64))
+        n, inner = x.shape[axis], int(np.prod(x.shape[axis + 1:], dtype=np.int64))
+        oshape = x.shape[:axis] + x.shape[axis + 1:]
+    y = np.empty(oshape, np.float32)
+    lib().orc_reduce_fwd(_p(x), C.c_int64(outer), C.c_int64(n), C.c_int64(inner), int(mean), _p(y))
+    return y
+
+
+def reduce_bwd(g, in_shape, axis, mean):
+    g = _f(g)
+    if axis is None:
+        outer, n, inner = 1, int(np.prod(in_shape, dtype=np.int64)), 1
+    else:
+        outer = int(np.prod(in_shape[:axis], dtype=np.int64))
+        n, inner = in_shape[axis], int(np.prod(in_shape[axis + 1:], dtype=np.int64))
+    dx = np.empty(in_shape, np.float32)
+    lib().orc_reduce_bwd(_p(g), C.c_int64(outer), C.c_int64(n), C.c_int64(inner), int(mean), _p(dx))
+    return dx
+
+
+def _rows(x):
+    cols = x.shape[-1]
+    return (x.size // cols if cols else 0), cols
+
+
+def softmax_fwd(x):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().orc_softmax_fwd(_p(x), *_rows(x), _p(y))
+    return y
+
+
+def logsoftmax_fwd(x):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().orc_logsoftmax_fwd(_p(x), *_rows(x), _p(y))
+    return y
+
+
+def softmax_bwd(g, y):
+    g, y = _f(g), _f(y)
+    dx = np.empty_like(y)
+    lib().orc_softmax_bwd(_p(g), _p(y), *_rows(y), _p(dx))
+    return dx
+
+
+def logsoftmax_bwd(g, y):
+    g, y = _f(g), _f(y)
+    dx = np.empty_like(y)
+    lib().orc_logsoftmax_bwd(_p(g), _p(y), *_rows(y), _p(dx))
+    return dx
+
+
+def nll_fwd(logp, targets, mean=True, ignore=-100):
+    logp, targets = _f(logp), _i64(targets)
+    loss = np.zeros((), np.float32)
+    count = lib().orc_nll_fwd(_p(logp), _p(targets), logp.shape[0], logp.shape[1], int(mean), C.c_int64(ignore), _p(loss))
+    if count < 0:
+        raise IndexError("target outside the classes")
+    return loss, count
+
+
+def nll_bwd(g, targets, shape, mean=True, ignore=-100):
+    targets = _i64(targets)
+    dx = np.empty(shape, np.float32)
+    lib().orc_nll_bwd(C.c_float(float(g)), _p(targets), shape[0], shape[1], int(mean), C.c_int64(ignore), _p(dx))
+    return dx
+
+
+def layernorm_fwd(x, gamma, beta, eps=1e-5):
+    x, gamma, beta = _f(x), _f(gamma), _f(beta)
+    rows, cols = _rows(x)
+    y, mean, inv = np.empty_like(x), np.empty(rows, np.float32), np.empty(rows, np.float32)
+    lib().orc_layernorm_fwd(_p(x), _p(gamma), _p(beta), rows, cols, C.c_float(eps), _p(y), _p(mean), _p(inv))
+    return y, mean, inv
+
+
+def layernorm_bwd(g, x, gamma, mean, inv):
+    g, x, gamma = _f(g), _f(x), _f(gamma)
+    rows, cols = _rows(x)
+    dx, dg, db = np.empty_like(x), np.empty(cols, np.float32), np.empty(cols, np.float32)
+    lib().orc_layernorm_bwd(_p(g), _p(x), _p(gamma), _p(_f(mean)), _p(_f(inv)), rows, cols, _p(dx), _p(dg), _p(db))
+    return dx, dg, db
+
+
+def batchnorm_fwd(x, gamma, beta, rm, rv, training=True, momentum=0.1, eps=1e-5):
+    """rm, rv are updated in place (float32 arrays)."""
+    x = _f(x)
+    n, c = x.shape[0], x.shape[1]
+    plane = x.size // max(1, n * c)
+    y, mu, iv = np.empty_like(x), np.empty(c, np.float32), np.empty(c, np.float32)
+    lib().orc_batchnorm_fwd(_p(x), _p(_f(gamma)), _p(_f(beta)), _p(rm), _p(rv), n, c, plane, int(training),
+                            C.c_float(momentum), C.c_float(eps), _p(y), _p(mu), _p(iv))
+    return y, mu, iv
+
+
+def batchnorm_bwd(g, x, gamma, mu, iv, training=True):
+    g, x = _f(g), _f(x)
+    n, c = x.shape[0], x.shape[1]
+    plane = x.size // max(1, n * c)
+    dx, dg, db = np.empty_like(x), np.empty(c, np.float32), np.empty(c, np.float32)
+    lib().orc_batchnorm_bwd(_p(g), _p(x), _p(_f(gamma)), _p(_f(mu)), _p(_f(iv)), n, c, plane, int(training), _p(dx), _p(dg), _p(db))
+    return dx, dg, db
+
+
+def embedding_fwd(table, ids):
+    table, ids = _f(table), _i64(ids)
+    out = np.empty(ids.shape + (table.shape[1],), np.float32)
+    if lib().orc_embedding_fwd(_p(table), table.shape[0], table.shape[1], _p(ids), C.c_int64(ids.size), _p(out)) != 0:
+        raise IndexError("id outside the table")
+    return out
+
+
+def embedding_bwd(g, ids, v, dim, pad=-1):
+    g, ids = _f(g), _i64(ids)
+    dt = np.empty((v, dim), np.float32)
+    lib().orc_embedding_bwd(_p(g), _p(ids), C.c_int64(ids.size), v, dim, C.c_int64(pad), _p(dt))
+    return dt
+
+
+def _mask_args(mask, lq, lk):
+    if mask is None:
+        return None, 0
+    m = _f(mask)
+    return m, (0 if m.ndim == 2 else lq * lk)
+
+
+def attention_fwd(q, k, v, mask=None, scale=None):
+    q, k, v = _f(q), _f(k), _f(v)
+    b, h, lq, d = q.shape
+    lk = k.shape[2]
+    scale = np.float32(1.0) / np.sqrt(np.float32(d)) if scale is None else np.float32(scale)
+    m, mbs = _mask_args(mask, lq, lk)
+    out = np.empty_like(q)
+    lib().orc_attention_fwd(_p(q), _p(k), _p(v), _p(m), C.c_int64(mbs), b, h, lq, lk, d, C.c_float(scale), _p(out))
+    return out
+
+
+def attention_bwd(g, q, k, v, mask=None, scale=None):
+    g, q, k, v = _f(g), _f(q), _f(k), _f(v)
+    b, h, lq, d = q.shape
+    lk = k.shape[2]
+    scale = np.float32(1.0) / np.sqrt(np.float32(d)) if scale is None else np.float32(scale)
+    m, mbs = _mask_args(mask, lq, lk)
+    dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    lib().orc_attention_bwd(_p(g), _p(q), _p(k), _p(v), _p(m), C.c_int64(mbs), b, h, lq, lk, d, C.c_float(scale), _p(dq), _p(dk), _p(dv))
+    return dq, dk, dv
+
+
+def adam_step(p, g, m, v, vmax, t, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, decoupled=False, amsgrad=False):
+    """In place on p, m, v (and vmax). t is the 1-based step."""
+    lib().orc_adam_step(_p(p), _p(_f(g)), _p(m), _p(v), _p(vmax), C.c_int64(p.size), C.c_float(lr), C.c_float(beta1),
+                        C.c_float(beta2), C.c_float(eps), C.c_float(wd), int(decoupled), int(amsgrad), C.c_int64(t))
+
+
+def sgd_step(p, g, buf, first, lr, wd=0.0, momentum=0.0, dampening=0.0, nesterov=False):
+    lib().orc_sgd_step(_p(p), _p(_f(g)), _p(buf), C.c_int64(p.size), C.c_float(lr), C.c_float(wd), C.c_float(momentum),
+                       C.c_float(dampening), int(nesterov), int(momentum != 0.0), int(first))
+
+
+def clip_norm(grads, max_norm, infinity=False):
+    """GradClip.ClipNorm on a list of arrays, in place. Returns the total norm (float32)."""
+    acc = 0.0
+    for g in grads:
+        acc = lib().orc_sumsq(_p(g), C.c_int64(g.size), C.c_double(acc), int(infinity))
+    norm = acc if infinity else float(np.sqrt(np.float64(acc)))
+    total = np.float32(norm)
+    if not np.isfinite(norm):
+        return total
+    coef = np.float32(np.float64(np.float32(max_norm)) / (norm + 1e-6))
+    if coef < 1:
+        for g in grads:
+            lib().orc_scale(_p(g), C.c_int64(g.size), C.c_float(coef))
+    return total

@@ -1,0 +1,344 @@
+"""TEST INFRASTRUCTURE - NOT PART OF THE PRODUCT.
+
+A reverse-mode tape over numpy arrays whose kernels are the C restatement in oracle.py. It replays the reference
+engine: records hold their inputs' metas, Backward does an iterative DFS post-order from the root, sweeps it in
+reverse, adopts the first gradient that reaches a node and adds later ones in arrival order
+(src/OneModel/Tensors/Autograd/Engine.cs:124-344). Ops record exactly what the reference's Ops.* record, including the
+Reshape / MatMul / Add / Permute chain of Ops.Linear (src/OneModel/Tensors/Ops.Layers.cs:715-733).
+"""
+import numpy as np
+
+from . import oracle as K
+
+
+class Meta:
+    __slots__ = ("requires_grad", "grad_fn", "grad")
+
+    def __init__(self, requires_grad, grad_fn):
+        self.requires_grad, self.grad_fn, self.grad = requires_grad, grad_fn, None
+
+
+class Record:
+    __slots__ = ("op", "inputs", "shapes", "saved", "args", "pending", "mark", "backward")
+
+    def __init__(self, op, inputs, saved=(), args=None, backward=None):
+        self.op = op
+        self.inputs = [t.meta if (t is not None and t.requires_grad) else None for t in inputs]
+        self.shapes = [t.shape if t is not None else None for t in inputs]
+        self.saved, self.args, self.pending, self.mark, self.backward = saved, args, None, 0, backward
+
+
+class T:
+    """A float32 (or integer) array with optional autograd meta."""
+
+    def __init__(self, value, requires_grad=False, _meta=None):
+        self.v = value if isinstance(value, np.ndarray) else np.asarray(value)
+        if self.v.dtype == np.float64:
+            self.v = self.v.astype(np.float32)
+        self.meta = _meta if _meta is not None else (Meta(True, None) if requires_grad else None)
+
+    @property
+    def requires_grad(self):
+        return self.meta is not None and self.meta.requires_grad
+
+    @property
+    def shape(self):
+        return self.v.shape
+
+    @property
+    def grad(self):
+        return None if self.meta is None else self.meta.grad
+
+    def zero_grad(self):
+        if self.meta is not None and self.meta.grad is not None:
+            self.meta.grad = np.zeros_like(self.meta.grad)
+
+    def backward(self):
+        backward(self)
+
+    # views
+    def reshape(self, *shape):
+        shape = shape[0] if len(shape) == 1 and isinstance(shape[0], (tuple, list)) else shape
+        out = np.ascontiguousarray(self.v).reshape(shape)
+        return _attach(out, Record("reshape", [self], backward=lambda r, g: [(0, g.reshape(r.shapes[0]), "alias")]), [self])
+
+    def permute(self, *axes):
+        axes = axes[0] if len(axes) == 1 and isinstance(axes[0], (tuple, list)) else axes
+        inv = np.argsort(axes)
+        out = self.v.transpose(axes)
+        return _attach(out, Record("permute", [self], backward=lambda r, g: [(0, np.ascontiguousarray(g.transpose(inv)), "own")]), [self])
+
+    def t(self):
+        return self.permute(1, 0)
+
+    def slice(self, axis, start, end):
+        idx = [slice(None)] * self.v.ndim
+        idx[axis] = slice(start, end)
+        idx = tuple(idx)
+
+        def bw(r, g):
+            dx = np.zeros(r.shapes[0], np.float32)
+            dx[idx] = g
+            return [(0, dx, "own")]
+
+        return _attach(self.v[idx], Record("slice", [self], backward=bw), [self])
+
+
+_grad_enabled = True
+_pass = 0
+
+
+def _attach(value, rec, inputs):
+    if not _grad_enabled or not any(t is not None and t.requires_grad for t in inputs):
+        return T(value)
+    return T(value, _meta=Meta(True, rec))
+
+
+def backward(root, gradient=None):
+    """Backprop.Run + Engine.Execute."""
+    global _pass, _grad_enabled
+    if root.meta is None or not root.requires_grad:
+        raise RuntimeError("Backward needs a tensor that requires gradients.")
+    g = np.ones(root.shape, np.float32) if gradient is None else np.array(gradient, np.float32)
+    if root.meta.grad_fn is None:
+        _accumulate_leaf(root.meta, g, True)
+        return
+    _pass += 1
+    mark = _pass
+    order, stack = [], [[root.meta.grad_fn, 0]]
+    root.meta.grad_fn.mark = mark
+    while stack:
+        rec, nxt = stack[-1]
+        if nxt < len(rec.inputs):
+            stack[-1][1] = nxt + 1
+            m = rec.inputs[nxt]
+            prod = m.grad_fn if m is not None else None
+            if prod is not None and prod.mark != mark:
+                prod.mark = mark
+                stack.append([prod, 0])
+        else:
+            order.append(rec)
+            stack.pop()
+    root.meta.grad_fn.pending = g
+    prev, _grad_enabled = _grad_enabled, False
+    try:
+        for rec in reversed(order):
+            g, rec.pending = rec.pending, None
+            if g is None:
+                continue
+            for i, grad, how in rec.backward(rec, np.ascontiguousarray(g)):
+                if grad is not None:
+                    _emit(rec, i, grad, how != "shared")
+            rec.saved = ()
+    finally:
+        _grad_enabled = prev
+        for rec in order:
+            rec.pending = None
+
+
+def _emit(rec, i, grad, owned):
+    meta = rec.inputs[i]
+    if meta is None:
+        return
+    if meta.grad_fn is None:
+        _accumulate_leaf(meta, grad, owned)
+        return
+    p = meta.grad_fn
+    if p.pending is None:
+        p.pending = grad if owned else grad.copy()
+    else:
+        p.pending = _add_into(p.pending, grad)
+
+
+def _accumulate_leaf(meta, grad, owned):
+    if not meta.requires_grad:
+        return
+    if meta.grad is None:
+        meta.grad = np.array(grad, np.float32, copy=True)
+    else:
+        meta.grad = _add_into(meta.grad, grad)
+
+
+def _add_into(dst, src):
+    # Engine.AddInto: dst[i] += src[i] in element order (float32 adds).
+    if not dst.flags.writeable or not dst.flags.c_contiguous:
+        dst = np.array(dst, np.float32, copy=True)
+    np.add(dst, src, out=dst)
+    return dst
+
+
+class no_grad:
+    def __enter__(self):
+        global _grad_enabled
+        self.prev, _grad_enabled = _grad_enabled, False
+
+    def __exit__(self, *a):
+        global _grad_enabled
+        _grad_enabled = self.prev
+
+
+# ---- ops ---------------------------------------------------------------------------------------------------------------
+
+def _emit_summed(r, g, negate_second):
+    """BackwardOps.EmitSummed (BackwardOps.cs:156-194)."""
+    out = []
+    need0, need1 = r.inputs[0] is not None, r.inputs[1] is not None
+    if need0:
+        s = K.sum_to(g, r.shapes[0])
+        same = g.shape == tuple(r.shapes[0])
+        out.append((0, s if not same else g, "own" if (not same or not need1) else "shared"))
+    if need1:
+        s = K.sum_to(g, r.shapes[1])
+        if negate_second:
+            out.append((1, s * np.float32(-1.0), "own"))
+        else:
+            out.append((1, s, "own"))
+    return out
+
+
+def add(a, b):
+    return _attach(a.v + b.v, Record("add", [a, b], backward=lambda r, g: _emit_summed(r, g, False)), [a, b])
+
+
+def sub(a, b):
+    return _attach(a.v - b.v, Record("sub", [a, b], backward=lambda r, g: _emit_summed(r, g, True)), [a, b])
+
+
+def mul(a, b):
+    def bw(r, g):
+        av, bv = r.saved
+        return [(0, K.sum_to(g * bv, r.shapes[0]), "own"), (1, K.sum_to(g * av, r.shapes[1]), "own")]
+
+    return _attach(a.v * b.v, Record("mul", [a, b], saved=(a.v, b.v), backward=bw), [a, b])
+
+
+def relu(x):
+    y = K.unary("relu", x.v)
+    return _attach(y, Record("relu", [x], saved=(y,), backward=lambda r, g: [(0, K.unary_bwd("relu", g, r.saved[0]), "own")]), [x])
+
+
+def gelu(x):
+    xc = np.ascontiguousarray(x.v)
+    return _attach(K.unary("gelu_erf", xc), Record("gelu", [x], saved=(xc,), backward=lambda r, g: [(0, K.unary_bwd("gelu_erf", g, r.saved[0]), "own")]), [x])
+
+
+GEMM_MODE = "fp32"  # 'tf32' / 'bf16' round the operands of every product first (the tensor-pipe configurations)
+
+
+def matmul(a, b):
+    """Ops.MatMul + MatMul backward (Ops.cs:117-144; BackwardOps.cs:69-82): dA = g b^T, dB = a^T g."""
+    av, bv = np.ascontiguousarray(a.v), np.ascontiguousarray(b.v)
+
+    def bw(r, g):
+        sa, sb = r.saved
+        out = []
+        if r.inputs[0] is not None:
+            out.append((0, K.gemm(g, sb, tb=True, mode=GEMM_MODE), "own"))
+        if r.inputs[1] is not None:
+            out.append((1, K.gemm(sa, g, ta=True, mode=GEMM_MODE), "own"))
+        return out
+
+    return _attach(K.gemm(av, bv, mode=GEMM_MODE), Record("matmul", [a, b], saved=(av, bv), backward=bw), [a, b])
+
+
+def linear(x, w, b=None):
+    """Ops.Linear: Reshape -> MatMul(x2d, W.T()) -> Add(bias) -> Reshape."""
+    in_f, out_f = w.shape[1], w.shape[0]
+    y = matmul(x.reshape(x.v.size // max(1, in_f), in_f), w.t())
+    if b is not None:
+        y = add(y, b)
+    return y.reshape(x.shape[:-1] + (out_f,))
+
+
+def mean(x, axis=None):
+    def bw(r, g):
+        return [(0, K.reduce_bwd(g, r.shapes[0], r.args, True), "own")]
+
+    ax = None if axis is None else axis % x.v.ndim
+    return _attach(K.reduce_fwd(x.v, ax, True), Record("mean", [x], args=ax, backward=bw), [x])
+
+
+def sum_(x, axis=None):
+    def bw(r, g):
+        return [(0, K.reduce_bwd(g, r.shapes[0], r.args, False), "own")]
+
+    ax = None if axis is None else axis % x.v.ndim
+    return _attach(K.reduce_fwd(x.v, ax, False), Record("sum", [x], args=ax, backward=bw), [x])
+
+
+def log_softmax(x):
+    y = K.logsoftmax_fwd(x.v)
+    return _attach(y, Record("log_softmax", [x], saved=(y,), backward=lambda r, g: [(0, K.logsoftmax_bwd(g, r.saved[0]), "own")]), [x])
+
+
+def nll_loss(logp, targets, mean=True, ignore=-100):
+    loss, _ = K.nll_fwd(logp.v, targets, mean, ignore)
+    tg = np.asarray(targets, np.int64)
+
+    def bw(r, g):
+        return [(0, K.nll_bwd(float(g.reshape(-1)[0]), tg, r.shapes[0], mean, ignore), "own")]
+
+    return _attach(np.asarray(loss, np.float32), Record("nll", [logp], backward=bw), [logp])
+
+
+def cross_entropy(logits, targets, mean=True, ignore=-100):
+    """Losses.CrossEntropy (src/OneModel.Training/Losses.cs:21-32)."""
+    return nll_loss(log_softmax(logits), targets, mean, ignore)
+
+
+def layer_norm(x, gamma, beta, eps=1e-5):
+    xc = np.ascontiguousarray(x.v)
+    y, mu, inv = K.layernorm_fwd(xc, gamma.v, beta.v, eps)
+
+    def bw(r, g):
+        sx, sg, smu, sinv = r.saved
+        dx, dg, db = K.layernorm_bwd(g, sx, sg, smu, sinv)
+        return [(0, dx, "own"), (1, dg, "own"), (2, db, "own")]
+
+    return _attach(y, Record("layer_norm", [x, gamma, beta], saved=(xc, gamma.v, mu, inv), backward=bw), [x, gamma, beta])
+
+
+def batch_norm2d(x, gamma, beta, rm, rv, training=True, momentum=0.1, eps=1e-5):
+    xc = np.ascontiguousarray(x.v)
+    y, mu, iv = K.batchnorm_fwd(xc, gamma.v, beta.v, rm, rv, training, momentum, eps)
+
+    def bw(r, g):
+        sx, sg, smu, siv = r.saved
+        dx, dg, db = K.batchnorm_bwd(g, sx, sg, smu, siv, training)
+        return [(0, dx, "own"), (1, dg, "own"), (2, db, "own")]
+
+    return _attach(y, Record("batch_norm", [x, gamma, beta], saved=(xc, gamma.v, mu, iv), backward=bw), [x, gamma, beta])
+
+
+def embedding(table, ids, pad=-1):
+    idv = np.asarray(ids, np.int64)
+    v, dim = table.shape
+
+    def bw(r, g):
+        return [(0, K.embedding_bwd(g, idv, v, dim, pad), "own")]
+
+    return _attach(K.embedding_fwd(table.v, idv), Record("embedding", [table], backward=bw), [table])
+
+
+def attention(q, k, v, mask=None, scale=None):
+    qc, kc, vc = (np.ascontiguousarray(t.v) for t in (q, k, v))
+
+    def bw(r, g):
+        dq, dk, dv = K.attention_bwd(g, *r.saved, mask=mask, scale=scale)
+        return [(0, dq, "own"), (1, dk, "own"), (2, dv, "own")]
+
+    return _attach(K.attention_fwd(qc, kc, vc, mask, scale), Record("attention", [q, k, v], saved=(qc, kc, vc), backward=bw), [q, k, v])
+
+
+def concat(xs, axis):
+    def bw(r, g):
+        out, start = [], 0
+        for i, s in enumerate(r.shapes):
+            ln = s[axis]
+            idx = [slice(None)] * g.ndim
+            idx[axis] = slice(start, start + ln)
+            out.append((i, np.ascontiguousarray(g[tuple(idx)]), "own"))
+            start += ln
+        return out
+
+    return _attach(np.concatenate([t.v for t in xs], axis=axis), Record("concat", list(xs), backward=bw), list(xs))

@@ -1,0 +1,102 @@
+"""Model-level parity on the GPU through the host mirror (Tensor / Ops / Backprop / optimizers above the C ABI):
+the reference's own fixtures at the reference's tolerances, and step-by-step agreement with the CPU oracle."""
+import numpy as np
+import pytest
+
+import models
+from backends import GpuBackend, OracleBackend, load_fixture, scaled_diff
+from test_oracle_golden import OPTIM, run_optim_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def B(ctx):
+    ctx.set_flags(0)
+    return GpuBackend(ctx)
+
+
+def test_autograd_encoder_gradients(B):
+    fx = load_fixture("autograd", "encoder")
+    loss, y, w = models.autograd_encoder(B, fx)
+    assert scaled_diff(B.numpy(y), fx["out.y"]) <= 1e-4
+    B.backward(loss)
+    largest = max(np.max(np.abs(fx["grad." + k])) for k in w)
+    for k, t in w.items():
+        ref = fx["grad." + k]
+        if np.max(np.abs(ref)) < 1e-5 * largest:
+            assert np.max(np.abs(B.grad(t))) < 1e-5 * largest, k
+        else:
+            assert scaled_diff(B.grad(t), ref) <= 1e-4, k
+
+
+def test_training_mlp_curve(B):
+    fx = load_fixture("training", "mlp")
+    losses, params = models.train_mlp(B, fx)
+    assert np.max(np.abs(losses - fx["out.loss"]) / np.abs(fx["out.loss"])) <= 1e-3
+    for k, v in params.items():
+        assert scaled_diff(v, fx["out." + k]) <= 1e-3, k
+
+
+def test_training_encoder_curve(B):
+    fx = load_fixture("training", "encoder")
+    losses, params = models.train_encoder(B, fx)
+    assert np.max(np.abs(losses - fx["out.loss"]) / np.abs(fx["out.loss"])) <= 1e-3
+    for k, v in params.items():
+        if not k.endswith("bk"):
+            assert scaled_diff(v, fx["out." + k]) <= 1e-3, k
+
+
+def test_training_mlp_matches_oracle_closely(B, oracle_built):
+    """Same program on both sides: 100 SGD steps stay within 1e-5 scaled (fp32 FMA products are bit-identical;
+    only double-accumulated sums may round differently)."""
+    fx = load_fixture("training", "mlp")
+    lg, pg = models.train_mlp(B, fx)
+    lo, po = models.train_mlp(OracleBackend(), fx)
+    assert np.max(np.abs(lg - lo) / np.abs(lo)) <= 1e-5
+    for k in pg:
+        assert scaled_diff(pg[k], po[k]) <= 1e-5, k
+
+
+@pytest.mark.parametrize("name", sorted(OPTIM))
+def test_optimizer_steps(B, name):
+    fx = load_fixture("training", "optim")
+    kind, kw = OPTIM[name]
+    out = run_optim_case(B, fx, kind, kw)
+    for step, (p, q) in out.items():
+        assert scaled_diff(p, fx[f"out.{name}.p.{step}"]) <= 1e-6
+        assert scaled_diff(q, fx[f"out.{name}.q.{step}"]) <= 1e-6
+
+
+def test_clip_norm(B):
+    fx = load_fixture("training", "optim")
+    for label, max_norm, inf in (("norm_small", 0.5, False), ("norm_large", 100.0, False), ("norm_inf", 0.7, True)):
+        p, q = B.tensor(fx["in.p"], True), B.tensor(fx["in.q"], True)
+        B.set_grad(p, fx["in.grad.p.0"])
+        B.set_grad(q, fx["in.grad.q.0"])
+        total = B.clip_norm([p, q], max_norm, inf)
+        ref = float(fx[f"out.clip.{label}.total"][0])
+        assert abs(total - ref) <= 1e-6 * abs(ref)
+        assert scaled_diff(B.grad(p), fx[f"out.clip.{label}.p"]) <= 1e-6
+        assert scaled_diff(B.grad(q), fx[f"out.clip.{label}.q"]) <= 1e-6
+
+
+def test_engine_semantics(B):
+    """Diamond sums, retain-graph rule, no-grad, shape errors (tests/OneModel.Tests/Tensors/BackwardEngineTests.cs:12-106)."""
+    import om_binding as omb
+    x = B.tensor(np.array([1.0, 2.0, 3.0]), True)
+    y = B.add(B.mul(x, x), x)            # x is used three times
+    loss = B.sum(y)
+    B.backward(loss)
+    assert np.array_equal(B.grad(x), np.array([3.0, 5.0, 7.0], np.float32))
+    with pytest.raises(omb.OmError):     # saved tensors were released by the first backward
+        B.backward(loss)
+    with omb.no_grad():
+        z = B.mul(x, x)
+    assert not z.requires_grad
+    with pytest.raises(omb.ShapeError):
+        B.add(B.tensor(np.zeros((2, 3))), B.tensor(np.zeros((4,))))
+    with pytest.raises(omb.ShapeError):
+        B.backward(B.mul(x, x))          # not a one-element tensor
+    x.zero_grad()
+    assert not B.grad(x).any()

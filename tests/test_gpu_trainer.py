@@ -1,0 +1,70 @@
+"""The benchmark configurations' training steps (host/trainer.cpp, the path bench.py times) against the CPU oracle
+running the same model on the same weights and batches, at sizes the oracle finishes in seconds."""
+import numpy as np
+import pytest
+
+import om_binding as omb
+import synth
+from backends import scaled_diff
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def configs(oracle_built):
+    from oracle import configs
+    return configs
+
+
+def test_mlp_config_100_steps_loss_within_1_percent(ctx, configs):
+    """Config 1 at full size (784-512-512-10, batch 128, AdamW): loss after 100 steps within 1% of the CPU path;
+    measured agreement is far tighter on the fp32 path, so it is also checked at 1e-4."""
+    ctx.set_flags(0)
+    ctx.make_current()
+    tr = omb.Trainer("mlp", [128, 784, 512, 512, 10], lr=1e-3, weight_decay=0.01, seed=0)
+    named = tr.named_parameters()
+    params = [tr.get_param(i, s) for i, (_, s) in enumerate(named)]
+    state = {}
+    for step in range(100):
+        x, y = synth.mlp_batch(128, 784, 10, step)
+        lg = tr.step([x, y])
+        lo, _ = configs.mlp_step(params, x, y, step + 1, state=state)
+        assert abs(lg - lo) <= 1e-4 * abs(lo), step
+    assert abs(lg - lo) <= 0.01 * abs(lo)
+    for i, (name, s) in enumerate(named):
+        assert scaled_diff(tr.get_param(i, s), params[i]) <= 1e-4, name
+    tr.close()
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_mlm_config_small(ctx, configs, graph):
+    """Configs 3/5 at reduced size: per-parameter gradients after step 1 (scaled 1e-4) and losses over 6 AdamW steps,
+    eager and replayed from a captured CUDA graph."""
+    ctx.set_flags(0)
+    ctx.make_current()
+    batch, seq, layers, width, heads, ff, vocab, rows = 4, 16, 2, 32, 4, 64, 101, 10
+    tr = omb.Trainer("mlm", [batch, seq, layers, width, heads, ff, vocab, rows], lr=1e-3, weight_decay=0.01, seed=0)
+    named = tr.named_parameters()
+    weights = {n: tr.get_param(i, s) for i, (n, s) in enumerate(named)}
+    state = {}
+    for step in range(6):
+        ids, pos, labels = synth.mlm_batch(batch, seq, vocab, rows, step)
+        if graph and step == 1:
+            tr.enable_graph()
+        before = {k: v.copy() for k, v in weights.items()}
+        lg = tr.step([ids, pos, labels])
+        lo, grads = configs.mlm_step(weights, ids.astype(np.int64), pos.astype(np.int64), labels, layers, heads, step + 1, state, lr=1e-3)
+        assert abs(lg - lo) <= 1e-4 * abs(lo), step
+        if step == 0:
+            largest = max(np.max(np.abs(g)) for g in grads.values())
+            for i, (n, s) in enumerate(named):
+                gg = tr.get_grad(i, s)
+                if np.max(np.abs(grads[n])) < 1e-5 * largest:
+                    assert np.max(np.abs(gg)) < 1e-5 * largest, n
+                else:
+                    assert scaled_diff(gg, grads[n]) <= 1e-4, n
+        del before
+    for i, (n, s) in enumerate(named):
+        if not n.endswith("attn.k.bias"):
+            assert scaled_diff(tr.get_param(i, s), weights[n]) <= 1e-3, n
+    tr.close()
