@@ -48,15 +48,13 @@ int32_t pool_alloc(om_ctx* ctx, size_t bytes, bool zero, void** out) {
     it->second.pop_back();
     p.bytes_cached -= cls;
   } else {
-    if (ctx->capturing) {
-      return fail(ctx, OM_ERR_UNSUPPORTED,
-                  "device allocation of %zu bytes during graph capture: run one uncaptured step first so the pool holds every block",
-                  cls);
-    }
+    // During graph capture (relaxed mode) a driver allocation is still legal; the block stays owned by the pool, so the
+    // captured address remains valid for every replay.
     cudaError_t e = cudaMalloc(&ptr, cls);
     if (e == cudaErrorMemoryAllocation) {
       cudaGetLastError();
       // Give cached blocks back to the driver and retry once.
+      if (ctx->capturing) return check_cuda(ctx, e, "cudaMalloc during graph capture");
       cudaStreamSynchronize(ctx->stream);
       for (auto& kv : p.cache) {
         for (void* q : kv.second) cudaFree(q);
@@ -316,7 +314,7 @@ int32_t om_sync(om_ctx* ctx) {
 int32_t om_graph_begin(om_ctx* ctx) {
   OM_CHECK_CTX(ctx);
   if (ctx->capturing) return fail(ctx, OM_ERR_ARG, "om_graph_begin: already capturing");
-  OM_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+  OM_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
   ctx->capturing = true;
   return OM_OK;
 }

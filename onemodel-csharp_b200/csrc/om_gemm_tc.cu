@@ -1,9 +1,411 @@
-// Tensor-pipe matrix product (tcgen05 + TMEM + TMA). Placeholder until the kernel lands: reports "not supported"
-// so that every product runs on the fp32 FMA kernel.
+// Matrix product on the Blackwell tensor pipe: tcgen05.mma with TF32 operands read from shared memory, fp32
+// accumulators in tensor memory (TMEM), operand tiles brought in by TMA (cp.async.bulk.tensor, 128-byte swizzle, no
+// multicast) through a ring of mbarrier-guarded stages.
+//
+// One CTA computes one 128 x 128 tile of C (optionally one k-slice of it: fixed split-k with an ordered second pass,
+// no floating-point atomics). Warp roles: warp 0 issues TMA loads, warp 1 owns the TMEM allocation and issues the
+// MMAs (one elected thread), warps 2-5 read the accumulator back (tcgen05.ld) and write C.
+//
+// All four operand orientations run without a transposed copy: an operand whose contraction index k is contiguous in
+// memory is a "K-major" tile, one whose m (or n) index is contiguous is an "MN-major" tile; the shared-memory matrix
+// descriptor and the instruction descriptor's major bits tell the tensor core which one it is reading.
+//   forward  y = x W^T      : A K-major,  B K-major
+//   dgrad    dx = g W       : A K-major,  B MN-major
+//   wgrad    dW = g^T x     : A MN-major, B MN-major
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the kernel raises OM_ERR_TIMEOUT in the context's status
+// word, every role leaves its loop, TMEM is released and the kernel returns.
+#include <cuda.h>
+
 #include "om_common.cuh"
+
 namespace om {
-bool gemm_tc_supported(om_ctx*, int, int, int, int, int, const float*, int, const float*, int, const float*, int) { return false; }
-int32_t gemm_tc(om_ctx* ctx, int, int, int, int, int, const float*, int, const float*, int, float*, int, int, const float*) {
-  return fail(ctx, OM_ERR_UNSUPPORTED, "tensor-pipe GEMM not built");
+
+constexpr int BM = 128, BN = 128, BK = 32;       // BK fp32 elements = one 128-byte swizzle row
+constexpr int STAGES = 6;
+constexpr int UMMA_K = 8;                        // tf32: 32 bytes of k per instruction
+constexpr int A_TILE_BYTES = BM * BK * 4;        // 16 KiB
+constexpr int B_TILE_BYTES = BN * BK * 4;
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int TC_THREADS = 192;
+constexpr int TMEM_COLS = 128;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;        // polls of a (hardware-suspended) try_wait before giving up
+constexpr size_t TC_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+
+struct TcParams {
+  int m, n, k;
+  int k_per_split;      // multiple of BK
+  int splits;
+  float* c;             // C (splits == 1) or the partial workspace [splits][m][n]
+  int ldc;
+  int accumulate;       // only when splits == 1
+  const float* bias;    // only when splits == 1
+  int32_t* status;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false (and raises the abort flag) when the bound is hit or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int where) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  if (atomicCAS(status, 0, (int32_t)OM_ERR_TIMEOUT) == 0) status[1] = where;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+// Arrives on the mbarrier when all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading and stride byte offsets in 16-byte units,
+// descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= 1ull << 46;   // version
+  d |= 2ull << 61;   // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::tf32: fp32 accumulator, TF32 A and B, major bits, N >> 3, M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc_tf32(bool a_mn, bool b_mn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+
+// ---- the kernel -------------------------------------------------------------------------------------------------------
+// A_MN / B_MN: the operand tile is MN-major (its m / n index is contiguous in global memory).
+// K-major tile in shared memory : 128 rows (m or n) x 128 bytes of k, 8-row swizzle atoms 1024 bytes apart.
+// MN-major tile in shared memory: 4 chunks of [BK k-rows x 128 bytes of m/n]; chunks BK*128 bytes apart (leading
+//                                 offset), 8-row k groups 1024 bytes apart (stride offset).
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int split = blockIdx.z;
+  const int k_begin = split * p.k_per_split;
+  const int k_end = min(p.k, k_begin + p.k_per_split);
+  const int k_blocks = (k_end - k_begin + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer ----
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; kb++) {
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
+        if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, abort_flag, p.status, 1)) break;
+        uint8_t* a_dst = smem + (size_t)s * STAGE_BYTES;
+        uint8_t* b_dst = a_dst + A_TILE_BYTES;
+        const int k0 = k_begin + kb * BK;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        if (A_MN) {
+#pragma unroll
+          for (int j = 0; j < BM / 32; j++) tma_load_2d(a_dst + j * (BK * 128), &map_a, m0 + 32 * j, k0, &full[s]);
+        } else {
+          tma_load_2d(a_dst, &map_a, k0, m0, &full[s]);
+        }
+        if (B_MN) {
+#pragma unroll
+          for (int j = 0; j < BN / 32; j++) tma_load_2d(b_dst + j * (BK * 128), &map_b, n0 + 32 * j, k0, &full[s]);
+        } else {
+          tma_load_2d(b_dst, &map_b, k0, n0, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(A_MN, B_MN);
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; kb++) {
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
+        ok = mbar_wait(&full[s], round & 1, abort_flag, p.status, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+        const uint32_t b_addr = a_addr + A_TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < BK / UMMA_K; ks++) {
+          // K-major: step 32 bytes along the swizzled row. MN-major: step one 8-row k group (1024 bytes).
+          const uint64_t adesc = A_MN ? make_desc(a_addr + ks * 1024, BK * 128, 1024) : make_desc(a_addr + ks * (UMMA_K * 4), 16, 1024);
+          const uint64_t bdesc = B_MN ? make_desc(b_addr + ks * 1024, BK * 128, 1024) : make_desc(b_addr + ks * (UMMA_K * 4), 16, 1024);
+          umma_tf32(tmem_base, adesc, bdesc, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);   // frees the stage when these MMAs have read it
+      }
+      umma_commit(acc_full);      // accumulator complete (or nothing outstanding after an abort)
+    }
+  } else {
+    // ---- epilogue: warps 2..5 own TMEM lane quadrants (warp % 4) ----
+    const int quad = warp & 3;
+    const int row = m0 + quad * 32 + lane;
+    bool ok = true;
+    if (k_blocks > 0) ok = mbar_wait(acc_full, 0, abort_flag, p.status, 3);
+    tc_fence_after();
+    float* c = p.c + (size_t)split * p.m * p.ldc;
+    if (ok) {
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 32; cb++) {
+        uint32_t r[32];
+        if (k_blocks > 0) {
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j++) r[j] = 0u;
+        }
+        const int col0 = n0 + cb * 32;
+        if (row < p.m && col0 < p.n) {
+          float* crow = c + (size_t)row * p.ldc + col0;
+          const bool vec = col0 + 32 <= p.n && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
+          if (vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              if (p.bias) {
+                v.x += p.bias[col0 + j]; v.y += p.bias[col0 + j + 1]; v.z += p.bias[col0 + j + 2]; v.w += p.bias[col0 + j + 3];
+              }
+              if (p.accumulate) {
+                float4 o = *reinterpret_cast<float4*>(crow + j);
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              *reinterpret_cast<float4*>(crow + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              if (col0 + j < p.n) {
+                float v = __uint_as_float(r[j]);
+                if (p.bias) v += p.bias[col0 + j];
+                if (p.accumulate) v += crow[j];
+                crow[j] = v;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// out = (accumulate ? out : 0) + part[0] + part[1] + ... in increasing split order.
+// The split sums are formed first, then bias and the previous contents are added, as the unsplit epilogue does.
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits, int64_t mn, int n, const float* __restrict__ bias,
+                                     float* __restrict__ out, int accumulate) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t j = i; j < mn; j += stride) {
+    float acc = part[j];
+    for (int s = 1; s < splits; s++) acc += part[(int64_t)s * mn + j];
+    if (bias) acc += bias[j % n];
+    if (accumulate) acc += out[j];
+    out[j] = acc;
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// A rank-2 fp32 tensor map over a row-major matrix [outer, inner] with leading dimension ld, box [box_outer, 32].
+static bool make_map(CUtensorMap* map, const float* base, int inner, int outer, int ld, int box_outer) {
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {32, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+bool gemm_tc_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb,
+                       const float* C, int ldc) {
+  (void)ctx; (void)ta; (void)tb; (void)C; (void)ldc;
+  if (!(ctx->flags & OM_TF32)) return false;
+  if (!encode_fn()) return false;
+  if (m < 1 || n < 1 || k < 1) return false;
+  if ((lda & 3) || (ldb & 3)) return false;                                    // TMA: row pitch multiple of 16 bytes
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return false;
+  if ((double)m * n * k < 32.0 * 32 * 32) return false;                        // tiny products stay on the FMA kernel
+  return true;
+}
+
+int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb, float* C,
+                int ldc, int acc, const float* bias) {
+  // op(A) is [m, k]. ta == 0: stored [m, k] (K-major tile, map inner = k). ta != 0: stored [k, m] (MN-major, inner = m).
+  // op(B) is [k, n]. tb != 0: stored [n, k] (K-major, inner = k). tb == 0: stored [k, n] (MN-major, inner = n).
+  const bool a_mn = ta != 0, b_mn = tb == 0;
+  CUtensorMap map_a, map_b;
+  bool ok = a_mn ? make_map(&map_a, A, m, k, lda, BK) : make_map(&map_a, A, k, m, lda, BM);
+  ok = ok && (b_mn ? make_map(&map_b, B, n, k, ldb, BK) : make_map(&map_b, B, k, n, ldb, BN));
+  if (!ok) return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed (m %d n %d k %d lda %d ldb %d)", m, n, k, lda, ldb);
+
+  const int tiles = (int)(ceil_div(m, BM) * ceil_div(n, BN));
+  const int k_blocks = (int)ceil_div(k, BK);
+  // Fixed split of k: enough slices to give every SM a tile, each slice at least 8 k-blocks deep. The split count is
+  // a function of the shape only, so results do not depend on the device or on timing.
+  int splits = 1;
+  if (tiles < 148 && k_blocks >= 16) {
+    splits = (int)std::min<int64_t>(ceil_div(148, tiles), k_blocks / 8);
+    if (splits < 1) splits = 1;
+    if (splits > 32) splits = 32;
+  }
+  const int kb_per_split = (int)ceil_div(k_blocks, splits);
+  splits = (int)ceil_div(k_blocks, kb_per_split);
+
+  TcParams p;
+  p.m = m; p.n = n; p.k = k;
+  p.k_per_split = kb_per_split * BK;
+  p.splits = splits;
+  p.status = ctx->status_dev;
+  float* workspace = nullptr;
+  if (splits > 1) {
+    OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)splits * m * n, false, (void**)&workspace));
+    p.c = workspace; p.ldc = n; p.accumulate = 0; p.bias = nullptr;
+  } else {
+    p.c = C; p.ldc = ldc; p.accumulate = acc; p.bias = bias;
+  }
+  dim3 grid((unsigned)ceil_div(n, BN), (unsigned)ceil_div(m, BM), (unsigned)splits);
+#define OM_TC_LAUNCH(AMN, BMN)                                                                                         \
+  do {                                                                                                                 \
+    static bool attr_set = false;                                                                                      \
+    if (!attr_set) {                                                                                                   \
+      OM_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<AMN, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM)); \
+      attr_set = true;                                                                                                 \
+    }                                                                                                                  \
+    gemm_tc_kernel<AMN, BMN><<<grid, TC_THREADS, TC_SMEM, ctx->stream>>>(map_a, map_b, p);                               \
+  } while (0)
+  if (!a_mn && !b_mn) OM_TC_LAUNCH(false, false);
+  else if (!a_mn && b_mn) OM_TC_LAUNCH(false, true);
+  else if (a_mn && !b_mn) OM_TC_LAUNCH(true, false);
+  else OM_TC_LAUNCH(true, true);
+#undef OM_TC_LAUNCH
+  OM_LAUNCH_CHECK(ctx, "gemm_tc");
+  if (splits > 1) {
+    int64_t mn = (int64_t)m * n;
+    if (ldc != n) {
+      pool_free(ctx, workspace);
+      return fail(ctx, OM_ERR_UNSUPPORTED, "split-k product needs a dense output");
+    }
+    splitk_reduce_kernel<<<grid_for(ctx, mn, 256), 256, 0, ctx->stream>>>(workspace, splits, mn, n, bias, C, acc);
+    pool_free(ctx, workspace);
+    OM_LAUNCH_CHECK(ctx, "splitk_reduce");
+  }
+  return OM_OK;
+}
+
 }  // namespace om

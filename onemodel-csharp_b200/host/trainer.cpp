@@ -217,6 +217,8 @@ OMH_API int32_t omh_trainer_create(int32_t kind, const int64_t* cfg, int32_t ncf
     t->opt.reset(new AdamW(ps, (float)hyper[0], 0.9f, 0.999f, 1e-8f, (float)hyper[1]));
     t->clip_norm = (float)hyper[2];
     t->loss_out = Tensor::Zeros(DType::F32, Shape{});
+    t->hyper_host.assign(t->opt->HyperBytes(), 0);
+    t->hyper_dev = Tensor::Zeros(DType::F32, Shape{(int)(t->opt->HyperBytes() + 3) / 4});
     BuildFlatGrads(t.get());
     *out = t.release();
   });
@@ -325,8 +327,6 @@ OMH_API int32_t omh_trainer_enable_graph(omh_trainer* t) {
     if (t->graph) return;
     if (t->steps_done < 1) throw InvalidOperationException("run at least one eager step before capturing");
     om_ctx* ctx = Device::Current();
-    t->hyper_host.assign(t->opt->HyperBytes(), 0);
-    t->hyper_dev = Tensor::Zeros(DType::F32, Shape{(int)(t->opt->HyperBytes() + 3) / 4});
     t->opt->HyperDevice = t->hyper_dev.RawData();
     Check(om_sync(ctx));
     int64_t saved_count = t->opt->StepCount;

@@ -1,0 +1,86 @@
+"""The tensor-pipe matrix product (tcgen05 / TMEM / TMA, TF32 operands, fp32 accumulation) against the CPU oracle.
+
+Two comparisons per case: against the oracle fed the same TF32-truncated operands (isolates the kernel: only the
+accumulation order differs, scaled error <= 2e-5), and against the plain fp32 oracle at the contract's TF32 tier,
+rtol 1e-3 with an absolute term scaled to the products' magnitude (|d| <= 1e-3 |ref| + 1e-5 * sqrt(k) * |a||b| bound)."""
+import numpy as np
+import pytest
+
+import om_binding as omb
+from backends import scaled_diff
+from om_binding import i32
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    (128, 128, 32), (128, 128, 256), (256, 384, 384), (8192, 384, 384), (384, 384, 8192), (1536, 384, 8192),
+    (1229, 1000, 384), (130, 260, 100), (128, 12, 784), (64, 512, 512), (100, 36, 4096),
+]
+
+
+def run(ctx, ta, tb, m, n, k, a, b, acc=0, c0=None):
+    da, db = ctx.to_device(a), ctx.to_device(b)
+    dc = ctx.to_device(c0) if c0 is not None else ctx.empty((m, n))
+    ctx.call("om_matmul", ctx.handle, i32(ta), i32(tb), i32(m), i32(n), i32(k), da.ptr, i32(a.shape[1]), db.ptr,
+             i32(b.shape[1]), dc.ptr, i32(n), i32(acc))
+    ctx.sync()
+    return dc.numpy()
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_tf32_matmul(ctx, oracle_built, ta, tb, m, n, k):
+    K = oracle_built
+    ctx.set_flags(omb.OM_TF32)
+    try:
+        r = np.random.default_rng(m + 3 * n + 7 * k + ta * 2 + tb)
+        a = r.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
+        b = r.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+        got = run(ctx, ta, tb, m, n, k, a, b)
+        ref_tf32 = K.gemm(a, b, bool(ta), bool(tb), mode="tf32")
+        ref = K.gemm(a, b, bool(ta), bool(tb))
+        assert scaled_diff(got, ref_tf32) <= 2e-5
+        bound = 1e-3 * np.abs(ref) + 1e-5 * np.sqrt(k) * 4.0
+        assert np.all(np.abs(got - ref) <= bound)
+        # accumulate: C += A B
+        c0 = r.standard_normal((m, n)).astype(np.float32)
+        got2 = run(ctx, ta, tb, m, n, k, a, b, acc=1, c0=c0)
+        assert scaled_diff(got2, ref_tf32 + c0) <= 2e-5
+        # run-to-run determinism (fixed split of k, ordered combine, no atomics)
+        assert np.array_equal(got, run(ctx, ta, tb, m, n, k, a, b))
+    finally:
+        ctx.set_flags(0)
+
+
+def test_tf32_linear_with_bias_and_backward(ctx, oracle_built):
+    K = oracle_built
+    ctx.set_flags(omb.OM_TF32)
+    try:
+        r = np.random.default_rng(1)
+        rows, inf, outf = 1024, 384, 1536
+        x, w = r.standard_normal((rows, inf)).astype(np.float32), (r.standard_normal((outf, inf)) * 0.05).astype(np.float32)
+        b, g = r.standard_normal(outf).astype(np.float32), r.standard_normal((rows, outf)).astype(np.float32)
+        X, W, Bv, G = ctx.to_device(x), ctx.to_device(w), ctx.to_device(b), ctx.to_device(g)
+        Y, DX, DW, DB = ctx.empty((rows, outf)), ctx.empty((rows, inf)), ctx.empty((outf, inf)), ctx.empty((outf,))
+        ctx.call("om_linear_fwd", ctx.handle, X.ptr, W.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), Y.ptr)
+        ctx.call("om_linear_bwd", ctx.handle, G.ptr, X.ptr, W.ptr, i32(rows), i32(inf), i32(outf), DX.ptr, DW.ptr, DB.ptr, i32(0))
+        ctx.sync()
+        assert scaled_diff(Y.numpy(), K.gemm(x, w, tb=True, mode="tf32") + b) <= 2e-5
+        assert scaled_diff(DX.numpy(), K.gemm(g, w, mode="tf32")) <= 2e-5
+        assert scaled_diff(DW.numpy(), K.gemm(g, x, ta=True, mode="tf32")) <= 2e-5
+        assert scaled_diff(Y.numpy(), K.gemm(x, w, tb=True) + b) <= 1e-3
+    finally:
+        ctx.set_flags(0)
+
+
+def test_unaligned_operands_use_the_fp32_kernel(ctx, oracle_built):
+    """Leading dimensions that are not a multiple of four elements cannot be described to TMA: such products run on
+    the fp32 FMA kernel and are bit-exact."""
+    K = oracle_built
+    ctx.set_flags(omb.OM_TF32)
+    try:
+        r = np.random.default_rng(2)
+        a, b = r.standard_normal((64, 91)).astype(np.float32), r.standard_normal((91, 53)).astype(np.float32)
+        assert np.array_equal(run(ctx, 0, 0, 64, 53, 91, a, b), K.gemm(a, b))
+    finally:
+        ctx.set_flags(0)
