@@ -121,14 +121,15 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading and stride byte offsets in 16-byte units,
-// descriptor version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// descriptor version 1, and the swizzle: 2 = 128-byte swizzle on 16-byte units (K-major tiles), 1 = 128-byte swizzle
+// on 32-byte units, the only layout the tensor core accepts for MN-major operands of 32-bit elements.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint64_t layout_type) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= 1ull << 46;   // version
-  d |= 2ull << 61;   // SWIZZLE_128B
+  d |= layout_type << 61;
   return d;
 }
 
@@ -142,7 +143,8 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(bool a_mn, bool b_mn) {
 // A_MN / B_MN: the operand tile is MN-major (its m / n index is contiguous in global memory).
 // K-major tile in shared memory : 128 rows (m or n) x 128 bytes of k, 8-row swizzle atoms 1024 bytes apart.
 // MN-major tile in shared memory: 4 chunks of [BK k-rows x 128 bytes of m/n]; chunks BK*128 bytes apart (leading
-//                                 offset), 8-row k groups 1024 bytes apart (stride offset).
+//                                 offset), 4-row k groups (the 32-byte-unit swizzle atom) 512 bytes apart (stride
+//                                 offset); one MMA consumes 8 k-rows = 1024 bytes.
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
@@ -220,8 +222,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
         for (int ks = 0; ks < BK / UMMA_K; ks++) {
           // K-major: step 32 bytes along the swizzled row. MN-major: step one 8-row k group (1024 bytes).
-          const uint64_t adesc = A_MN ? make_desc(a_addr + ks * 1024, BK * 128, 1024) : make_desc(a_addr + ks * (UMMA_K * 4), 16, 1024);
-          const uint64_t bdesc = B_MN ? make_desc(b_addr + ks * 1024, BK * 128, 1024) : make_desc(b_addr + ks * (UMMA_K * 4), 16, 1024);
+          const uint64_t adesc = A_MN ? make_desc(a_addr + ks * 1024, BK * 128, 512, 1) : make_desc(a_addr + ks * (UMMA_K * 4), 16, 1024, 2);
+          const uint64_t bdesc = B_MN ? make_desc(b_addr + ks * 1024, BK * 128, 512, 1) : make_desc(b_addr + ks * (UMMA_K * 4), 16, 1024, 2);
           umma_tf32(tmem_base, adesc, bdesc, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&empty[s]);   // frees the stage when these MMAs have read it
@@ -321,13 +323,16 @@ static EncodeTiledFn encode_fn() {
 }
 
 // A rank-2 fp32 tensor map over a row-major matrix [outer, inner] with leading dimension ld, box [box_outer, 32].
-static bool make_map(CUtensorMap* map, const float* base, int inner, int outer, int ld, int box_outer) {
+// K-major tiles use the 16-byte-unit 128B swizzle, MN-major tiles the 32-byte-unit one. The TFLOAT32 element type makes
+// TMA round each value to TF32 (nearest) on the way in; the tensor core would otherwise truncate the low 13 bits.
+static bool make_map(CUtensorMap* map, const float* base, int inner, int outer, int ld, int box_outer, bool mn_major) {
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
   cuuint32_t box[2] = {32, (cuuint32_t)box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -350,8 +355,8 @@ int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A
   // op(B) is [k, n]. tb != 0: stored [n, k] (K-major, inner = k). tb == 0: stored [k, n] (MN-major, inner = n).
   const bool a_mn = ta != 0, b_mn = tb == 0;
   CUtensorMap map_a, map_b;
-  bool ok = a_mn ? make_map(&map_a, A, m, k, lda, BK) : make_map(&map_a, A, k, m, lda, BM);
-  ok = ok && (b_mn ? make_map(&map_b, B, n, k, ldb, BK) : make_map(&map_b, B, k, n, ldb, BN));
+  bool ok = a_mn ? make_map(&map_a, A, m, k, lda, BK, true) : make_map(&map_a, A, k, m, lda, BM, false);
+  ok = ok && (b_mn ? make_map(&map_b, B, n, k, ldb, BK, true) : make_map(&map_b, B, k, n, ldb, BN, false));
   if (!ok) return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed (m %d n %d k %d lda %d ldb %d)", m, n, k, lda, ldb);
 
   const int tiles = (int)(ceil_div(m, BM) * ceil_div(n, BN));

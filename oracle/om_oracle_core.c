@@ -72,11 +72,13 @@ static float bf16_round(float x) {
 API void orc_round_bf16(const float* x, float* y, int64_t n) {
   for (int64_t i = 0; i < n; i++) y[i] = bf16_round(x[i]);
 }
-/* TF32 operand rounding as the tensor pipe applies it (low 13 mantissa bits dropped). */
-API void orc_trunc_tf32(const float* x, float* y, int64_t n) {
+/* TF32 operand rounding (10 explicit mantissa bits): mode 0 drops the low 13 bits (what the tensor pipe does to raw
+ * fp32 operands), mode 1 rounds to nearest, ties to even (what the product's TMA loads do; measured on B200). */
+API void orc_round_tf32(const float* x, float* y, int64_t n, int nearest) {
   for (int64_t i = 0; i < n; i++) {
     uint32_t u;
     memcpy(&u, &x[i], 4);
+    if ((u & 0x7f800000u) != 0x7f800000u && nearest) u += 0xfffu + ((u >> 13) & 1u);
     u &= 0xffffe000u;
     memcpy(&y[i], &u, 4);
   }

@@ -54,7 +54,7 @@ def gemm(a, b, ta=False, tb=False, mode="fp32"):
     """op(a) @ op(b) with the reference's one-accumulator FMA order. mode 'tf32'/'bf16' rounds the operands first."""
     a, b = _f(a), _f(b)
     if mode == "tf32":
-        a, b = trunc_tf32(a), trunc_tf32(b)
+        a, b = round_tf32(a), round_tf32(b)
     elif mode == "bf16":
         a, b = round_bf16(a), round_bf16(b)
     m, k = (a.shape[1], a.shape[0]) if ta else a.shape
@@ -71,10 +71,10 @@ def round_bf16(x):
     return y
 
 
-def trunc_tf32(x):
+def round_tf32(x, nearest=True):
     x = _f(x)
     y = np.empty_like(x)
-    lib().orc_trunc_tf32(_p(x), _p(y), C.c_int64(x.size))
+    lib().orc_round_tf32(_p(x), _p(y), C.c_int64(x.size), int(nearest))
     return y
 
 

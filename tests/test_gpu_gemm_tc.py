@@ -1,8 +1,9 @@
 """The tensor-pipe matrix product (tcgen05 / TMEM / TMA, TF32 operands, fp32 accumulation) against the CPU oracle.
 
-Two comparisons per case: against the oracle fed the same TF32-truncated operands (isolates the kernel: only the
-accumulation order differs, scaled error <= 2e-5), and against the plain fp32 oracle at the contract's TF32 tier,
-rtol 1e-3 with an absolute term scaled to the products' magnitude (|d| <= 1e-3 |ref| + 1e-5 * sqrt(k) * |a||b| bound)."""
+Two comparisons per case: against the oracle fed the same TF32-rounded operands (round to nearest even, as the TMA
+loads round them; isolates the kernel: only the fp32 accumulation order differs, scaled error <= 2e-5), and against
+the plain fp32 oracle at the contract's TF32 tier: every element within the rigorous 2^-9 * (|A||B|) bound and the
+scaled error inside 1e-3."""
 import numpy as np
 import pytest
 
@@ -37,11 +38,20 @@ def test_tf32_matmul(ctx, oracle_built, ta, tb, m, n, k):
         a = r.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
         b = r.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
         got = run(ctx, ta, tb, m, n, k, a, b)
+        if a.shape[1] % 4 or b.shape[1] % 4:
+            # a row pitch that is not a multiple of 16 bytes cannot be described to TMA: fp32 FMA kernel, bit-exact
+            assert np.array_equal(got, K.gemm(a, b, bool(ta), bool(tb)))
+            return
         ref_tf32 = K.gemm(a, b, bool(ta), bool(tb), mode="tf32")
         ref = K.gemm(a, b, bool(ta), bool(tb))
         assert scaled_diff(got, ref_tf32) <= 2e-5
-        bound = 1e-3 * np.abs(ref) + 1e-5 * np.sqrt(k) * 4.0
-        assert np.all(np.abs(got - ref) <= bound)
+        # TF32 keeps 10 mantissa bits of each operand: every product is within 2^-9 relative, so every element is within
+        # 2^-9 * (|A| |B|) of the fp32 result (the k*u*sum|ab| form of bound the reference's GEMM tests use,
+        # docs/kernels-gemm.md:82-84), and the scaled error stays inside the 1e-3 tier.
+        aa = np.abs(a.T if ta else a).astype(np.float64)
+        bb = np.abs(b.T if tb else b).astype(np.float64)
+        assert np.all(np.abs(got.astype(np.float64) - ref) <= 2.0 ** -9 * (aa @ bb) + 1e-5)
+        assert scaled_diff(got, ref) <= 1e-3
         # accumulate: C += A B
         c0 = r.standard_normal((m, n)).astype(np.float32)
         got2 = run(ctx, ta, tb, m, n, k, a, b, acc=1, c0=c0)
@@ -69,6 +79,7 @@ def test_tf32_linear_with_bias_and_backward(ctx, oracle_built):
         assert scaled_diff(DX.numpy(), K.gemm(g, w, mode="tf32")) <= 2e-5
         assert scaled_diff(DW.numpy(), K.gemm(g, x, ta=True, mode="tf32")) <= 2e-5
         assert scaled_diff(Y.numpy(), K.gemm(x, w, tb=True) + b) <= 1e-3
+        assert scaled_diff(DW.numpy(), K.gemm(g, x, ta=True)) <= 1e-3
     finally:
         ctx.set_flags(0)
 
