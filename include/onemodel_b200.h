@@ -132,6 +132,14 @@ int32_t om_matmul_batched(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m
  * Fuses the Reshape/MatMul/Add chain of Ops.Linear (Ops.Layers.cs:715-733). */
 int32_t om_linear_fwd(om_ctx* ctx, const float* x, const float* W, const float* bias, int32_t rows,
                       int32_t in_features, int32_t out_features, float* y);
+/* The same with an explicit row pitch of y / g in elements (>= out_features). A pitch that is a multiple of four
+ * keeps wide outputs whose width is not (the 30522-column vocabulary logits) on the tensor pipe, whose TMA loads need
+ * 16-byte aligned rows. */
+int32_t om_linear_fwd_ld(om_ctx* ctx, const float* x, const float* W, const float* bias, int32_t rows,
+                         int32_t in_features, int32_t out_features, float* y, int32_t ldy);
+int32_t om_linear_bwd_ld(om_ctx* ctx, const float* g, int32_t ldg, const float* x, const float* W, int32_t rows,
+                         int32_t in_features, int32_t out_features, float* dx, float* dW, float* dbias,
+                         int32_t accumulate_w);
 /* Backward of om_linear_fwd: dx = g*W (NULL to skip), dW = g^T*x (NULL to skip), dbias = column sums of g
  * (NULL to skip). accumulate_w != 0 adds into dW/dbias (Engine.AddInto, Engine.cs:330-344).
  * Replaces the Reshape/Add/MatMul/Permute records of one Linear (call stack: BackwardOps.cs:69-82,107-122,156-194). */
@@ -220,6 +228,13 @@ int32_t om_cross_entropy_fwd(om_ctx* ctx, const float* logits, const void* targe
 int32_t om_cross_entropy_bwd(om_ctx* ctx, const float* g, const float* logp, const void* targets,
                              int32_t target_dtype, int32_t rows, int32_t cols, int32_t mean,
                              int64_t ignore_index, float denominator, float* dlogits);
+/* The same with one row pitch `ld` (elements, >= cols) shared by logits, logp and dlogits. */
+int32_t om_cross_entropy_fwd_ld(om_ctx* ctx, const float* logits, const void* targets, int32_t target_dtype,
+                                int32_t rows, int32_t cols, int32_t ld, int32_t mean, int64_t ignore_index,
+                                float denominator, float* logp, float* loss, int32_t* count);
+int32_t om_cross_entropy_bwd_ld(om_ctx* ctx, const float* g, const float* logp, const void* targets,
+                                int32_t target_dtype, int32_t rows, int32_t cols, int32_t ld, int32_t mean,
+                                int64_t ignore_index, float denominator, float* dlogits);
 
 /* ---- normalisation ------------------------------------------------------------------------------------ */
 
@@ -336,11 +351,13 @@ int32_t om_ctc_loss(om_ctx* ctx, const float* lp, int32_t t, int32_t b, int32_t 
 int32_t om_ctc_grad(om_ctx* ctx, const float* g, const float* lp, int32_t t, int32_t b, int32_t c,
                     const int32_t* targets, const int32_t* target_lengths, const int32_t* input_lengths,
                     const float* nll, int32_t blank, int32_t reduction, int32_t zero_infinity, float* grad);
-/* Greedy CTC decode of lp [T,B,C]: per step argmax (lowest index on ties, NaN never wins), merged runs,
- * blanks dropped. labels [B,T] padded with -1, lengths [B]. Integers are bit-exact with Ctc.Greedy
- * (src/OneModel/Tensors/Ctc.cs:89-190). */
+/* Greedy CTC decode of lp [T,B,C]: per step argmax (lowest index on ties, NaN never wins over a number),
+ * merged runs, blanks dropped. labels, first_step, last_step are [B,T] padded with -1 (first/last may be
+ * NULL): the label of each kept run and the first and last frame it covers; lengths [B]. Integers are
+ * bit-exact with Ctc.Greedy (src/OneModel/Tensors/Ctc.cs:89-190). */
 int32_t om_ctc_greedy(om_ctx* ctx, const float* lp, int32_t t, int32_t b, int32_t c,
-                      const int32_t* input_lengths, int32_t blank, int32_t* labels, int32_t* lengths);
+                      const int32_t* input_lengths, int32_t blank, int32_t* labels, int32_t* first_step,
+                      int32_t* last_step, int32_t* lengths);
 
 /* ---- optimizers ------------------------------------------------------------------------------------------ */
 

@@ -278,7 +278,7 @@ constexpr int kColsumRowsPerChunk = 512;
 // Stage 1 of a column sum over g[rows, cols]: CTA (bx, by) owns 32 columns and one chunk of kColsumRowsPerChunk rows.
 // 8 row-lanes per column accumulate in double over rows lane, lane+8, ...; the 8 lane sums are combined in lane
 // order. partial[chunk, col] is written in double.
-__global__ void colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols,
+__global__ void colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld,
                                      double* __restrict__ partial) {
   __shared__ double sm[8][33];
   int col = blockIdx.x * 32 + threadIdx.x;
@@ -286,7 +286,7 @@ __global__ void colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, 
   int r1 = min(rows, r0 + kColsumRowsPerChunk);
   double acc = 0.0;
   if (col < cols) {
-    for (int r = r0 + threadIdx.y; r < r1; r += 8) acc += (double)g[(int64_t)r * cols + col];
+    for (int r = r0 + threadIdx.y; r < r1; r += 8) acc += (double)g[(int64_t)r * ld + col];
   }
   sm[threadIdx.y][threadIdx.x] = acc;
   __syncthreads();
@@ -409,6 +409,22 @@ __global__ void reduce_bwd_kernel(const float* __restrict__ g, int64_t outer, in
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Column sums of g[rows, cols] whose rows are ld elements apart.
+int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64_t ld, float* out, int32_t accumulate) {
+  if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "om_colsum: [%d,%d]", rows, cols);
+  if (cols == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_colsum", 0, 4.0 * rows * cols + 4.0 * cols);
+  int chunks = (int)ceil_div(rows > 0 ? rows : 1, kColsumRowsPerChunk);
+  double* partial = nullptr;
+  OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&partial));
+  dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)chunks);
+  colsum_stage1_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(g, rows, cols, ld, partial);
+  colsum_stage2_kernel<<<(unsigned)ceil_div(cols, 128), 128, 0, ctx->stream>>>(partial, chunks, cols, out, accumulate);
+  pool_free(ctx, partial);
+  OM_LAUNCH_CHECK(ctx, "om_colsum");
+  return OM_OK;
+}
 
 }  // namespace om
 
@@ -634,18 +650,7 @@ int32_t om_strided_copy(om_ctx* ctx, int32_t rank, const int32_t* shape, const f
 
 int32_t om_colsum(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, float* out, int32_t accumulate) {
   OM_CHECK_CTX(ctx);
-  if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "om_colsum: [%d,%d]", rows, cols);
-  if (cols == 0) return OM_OK;
-  ProfileScope prof(ctx, "om_colsum", 0, 4.0 * rows * cols + 4.0 * cols);
-  int chunks = (int)ceil_div(rows > 0 ? rows : 1, kColsumRowsPerChunk);
-  double* partial = nullptr;
-  OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&partial));
-  dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)chunks);
-  colsum_stage1_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(g, rows, cols, partial);
-  colsum_stage2_kernel<<<(unsigned)ceil_div(cols, 128), 128, 0, ctx->stream>>>(partial, chunks, cols, out, accumulate);
-  pool_free(ctx, partial);
-  OM_LAUNCH_CHECK(ctx, "om_colsum");
-  return OM_OK;
+  return colsum_ld(ctx, g, rows, cols, cols, out, accumulate);
 }
 
 int32_t om_sum_to(om_ctx* ctx, int32_t rank, const int32_t* shape, const float* g, const int64_t* t_strides,

@@ -12,11 +12,13 @@ bool gemm_tc_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const f
 int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb,
                 float* C, int ldc, int acc, const float* bias);
 
-__global__ void add_bias_rows_kernel(float* __restrict__ y, const float* __restrict__ bias, int64_t rows, int32_t cols) {
+__global__ void add_bias_rows_kernel(float* __restrict__ y, const float* __restrict__ bias, int64_t rows, int32_t cols, int64_t ld) {
   int64_t total = rows * cols;
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  if ((cols & 3) == 0) {
+  if (ld != cols) {
+    for (int64_t j = i; j < total; j += stride) y[(j / cols) * ld + (j % cols)] += bias[j % cols];
+  } else if ((cols & 3) == 0) {
     int64_t n4 = total >> 2;
     int32_t c4 = cols >> 2;
     float4* y4 = reinterpret_cast<float4*>(y);
@@ -46,8 +48,7 @@ int32_t gemm_dispatch(om_ctx* ctx, int ta, int tb, int m, int n, int k, const fl
     return gemm_tc(ctx, ta, tb, m, n, k, A, lda, B, ldb, C, ldc, acc, bias);
   OM_TRY(gemm_simt(ctx, ta, tb, m, n, k, A, lda, 0, B, ldb, 0, C, ldc, 0, 1, acc));
   if (bias) {
-    if (ldc != n) return fail(ctx, OM_ERR_UNSUPPORTED, "bias epilogue needs a dense output");
-    add_bias_rows_kernel<<<grid_for(ctx, ((int64_t)m * n + 3) / 4, 256), 256, 0, ctx->stream>>>(C, bias, m, n);
+    add_bias_rows_kernel<<<grid_for(ctx, ((int64_t)m * n + 3) / 4, 256), 256, 0, ctx->stream>>>(C, bias, m, n, ldc);
     OM_LAUNCH_CHECK(ctx, "add_bias_rows");
   }
   return OM_OK;
@@ -60,6 +61,11 @@ using namespace om;
 extern "C" {
 
 int32_t om_colsum(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, float* out, int32_t accumulate);
+}
+namespace om {
+int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64_t ld, float* out, int32_t accumulate);
+}
+extern "C" {
 
 int32_t om_matmul(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m, int32_t n, int32_t k, const float* A,
                   int32_t lda, const float* B, int32_t ldb, float* C, int32_t ldc, int32_t accumulate) {
@@ -80,35 +86,45 @@ int32_t om_matmul_batched(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m
   return gemm_simt(ctx, transA, transB, m, n, k, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, batch, accumulate);
 }
 
-int32_t om_linear_fwd(om_ctx* ctx, const float* x, const float* W, const float* bias, int32_t rows,
-                      int32_t in_features, int32_t out_features, float* y) {
+int32_t om_linear_fwd_ld(om_ctx* ctx, const float* x, const float* W, const float* bias, int32_t rows, int32_t in_features,
+                         int32_t out_features, float* y, int32_t ldy) {
   OM_CHECK_CTX(ctx);
-  if (rows < 0 || in_features < 1 || out_features < 1)
-    return fail(ctx, OM_ERR_SHAPE, "om_linear_fwd: rows %d in %d out %d", rows, in_features, out_features);
+  if (rows < 0 || in_features < 1 || out_features < 1 || ldy < out_features)
+    return fail(ctx, OM_ERR_SHAPE, "om_linear_fwd: rows %d in %d out %d ldy %d", rows, in_features, out_features, ldy);
   ProfileScope prof(ctx, "om_linear_fwd", 2.0 * rows * in_features * out_features,
                     4.0 * ((double)rows * in_features + (double)in_features * out_features + (double)rows * out_features));
-  return gemm_dispatch(ctx, 0, 1, rows, out_features, in_features, x, in_features, W, in_features, y, out_features, 0, bias);
+  return gemm_dispatch(ctx, 0, 1, rows, out_features, in_features, x, in_features, W, in_features, y, ldy, 0, bias);
+}
+
+int32_t om_linear_fwd(om_ctx* ctx, const float* x, const float* W, const float* bias, int32_t rows, int32_t in_features,
+                      int32_t out_features, float* y) {
+  return om_linear_fwd_ld(ctx, x, W, bias, rows, in_features, out_features, y, out_features);
+}
+
+int32_t om_linear_bwd_ld(om_ctx* ctx, const float* g, int32_t ldg, const float* x, const float* W, int32_t rows,
+                         int32_t in_features, int32_t out_features, float* dx, float* dW, float* dbias, int32_t accumulate_w) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 0 || in_features < 1 || out_features < 1 || ldg < out_features)
+    return fail(ctx, OM_ERR_SHAPE, "om_linear_bwd: rows %d in %d out %d ldg %d", rows, in_features, out_features, ldg);
+  const double flops = 2.0 * rows * in_features * out_features;
+  const double bytes = 4.0 * ((double)rows * in_features + (double)in_features * out_features + (double)rows * out_features);
+  if (dx) {
+    ProfileScope prof(ctx, "om_linear_bwd.dgrad", flops, bytes);
+    // dx[rows, in] = g[rows, out] * W[out, in]
+    OM_TRY(gemm_dispatch(ctx, 0, 0, rows, in_features, out_features, g, ldg, W, in_features, dx, in_features, 0, nullptr));
+  }
+  if (dW) {
+    ProfileScope prof(ctx, "om_linear_bwd.wgrad", flops, bytes);
+    // dW[out, in] = g[rows, out]^T * x[rows, in]
+    OM_TRY(gemm_dispatch(ctx, 1, 0, out_features, in_features, rows, g, ldg, x, in_features, dW, in_features, accumulate_w, nullptr));
+  }
+  if (dbias) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w));
+  return OM_OK;
 }
 
 int32_t om_linear_bwd(om_ctx* ctx, const float* g, const float* x, const float* W, int32_t rows, int32_t in_features,
                       int32_t out_features, float* dx, float* dW, float* dbias, int32_t accumulate_w) {
-  OM_CHECK_CTX(ctx);
-  if (rows < 0 || in_features < 1 || out_features < 1)
-    return fail(ctx, OM_ERR_SHAPE, "om_linear_bwd: rows %d in %d out %d", rows, in_features, out_features);
-  if (dx) {
-    ProfileScope prof(ctx, "om_linear_bwd.dgrad", 2.0 * rows * in_features * out_features,
-                      4.0 * ((double)rows * in_features + (double)in_features * out_features + (double)rows * out_features));
-    // dx[rows, in] = g[rows, out] * W[out, in]
-    OM_TRY(gemm_dispatch(ctx, 0, 0, rows, in_features, out_features, g, out_features, W, in_features, dx, in_features, 0, nullptr));
-  }
-  if (dW) {
-    ProfileScope prof(ctx, "om_linear_bwd.wgrad", 2.0 * rows * in_features * out_features,
-                      4.0 * ((double)rows * in_features + (double)in_features * out_features + (double)rows * out_features));
-    // dW[out, in] = g[rows, out]^T * x[rows, in]
-    OM_TRY(gemm_dispatch(ctx, 1, 0, out_features, in_features, rows, g, out_features, x, in_features, dW, in_features, accumulate_w, nullptr));
-  }
-  if (dbias) OM_TRY(om_colsum(ctx, g, rows, out_features, dbias, accumulate_w));
-  return OM_OK;
+  return om_linear_bwd_ld(ctx, g, out_features, x, W, rows, in_features, out_features, dx, dW, dbias, accumulate_w);
 }
 
 }  // extern "C"

@@ -11,12 +11,16 @@ template <int BM, int BN, int BK, int TM, int TN, bool TA, bool TB>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(int m, int n, int k, const float* __restrict__ A, int lda, int64_t strideA,
                  const float* __restrict__ B, int ldb, int64_t strideB, float* __restrict__ C, int ldc,
-                 int64_t strideC, int accumulate) {
+                 int64_t strideC, int accumulate, int batch, int batch_per_z) {
   constexpr int THREADS = (BM / TM) * (BN / TN);
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
-  A += blockIdx.z * strideA;
-  B += blockIdx.z * strideB;
+  // batch_per_z == 0: blockIdx.z is the matrix of a batch. Otherwise this CTA sums the products of matrices
+  // [z0, z1) into one accumulator (in increasing matrix order) and writes output chunk blockIdx.z.
+  const int z0 = batch_per_z ? blockIdx.z * batch_per_z : blockIdx.z;
+  const int z1 = batch_per_z ? min(batch, z0 + batch_per_z) : z0 + 1;
+  const float* A0 = A;
+  const float* B0 = B;
   C += blockIdx.z * strideC;
   const int tid = threadIdx.x;
   const int tx = tid % (BN / TN), ty = tid / (BN / TN);
@@ -27,6 +31,9 @@ gemm_simt_kernel(int m, int n, int k, const float* __restrict__ A, int lda, int6
 #pragma unroll
     for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
 
+  for (int z = z0; z < z1; z++) {
+  A = A0 + z * strideA;
+  B = B0 + z * strideB;
   for (int k0 = 0; k0 < k; k0 += BK) {
     // A tile -> As[kk][mm]
     if (TA) {
@@ -91,6 +98,7 @@ gemm_simt_kernel(int m, int n, int k, const float* __restrict__ A, int lda, int6
     }
     __syncthreads();
   }
+  }
 #pragma unroll
   for (int i = 0; i < TM; i++) {
     int gm = m0 + ty * TM + i;
@@ -107,13 +115,13 @@ gemm_simt_kernel(int m, int n, int k, const float* __restrict__ A, int lda, int6
 
 template <int BM, int BN, int BK, int TM, int TN>
 static void launch_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
-                        const float* B, int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch, int acc) {
-  dim3 grid((unsigned)ceil_div(n, BN), (unsigned)ceil_div(m, BM), (unsigned)batch);
+                        const float* B, int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch, int acc, int bpz = 0) {
+  dim3 grid((unsigned)ceil_div(n, BN), (unsigned)ceil_div(m, BM), (unsigned)(bpz ? ceil_div(batch, bpz) : batch));
   constexpr int T = (BM / TM) * (BN / TN);
-  if (!ta && !tb) gemm_simt_kernel<BM, BN, BK, TM, TN, false, false><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc);
-  else if (!ta && tb) gemm_simt_kernel<BM, BN, BK, TM, TN, false, true><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc);
-  else if (ta && !tb) gemm_simt_kernel<BM, BN, BK, TM, TN, true, false><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc);
-  else gemm_simt_kernel<BM, BN, BK, TM, TN, true, true><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc);
+  if (!ta && !tb) gemm_simt_kernel<BM, BN, BK, TM, TN, false, false><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz);
+  else if (!ta && tb) gemm_simt_kernel<BM, BN, BK, TM, TN, false, true><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz);
+  else if (ta && !tb) gemm_simt_kernel<BM, BN, BK, TM, TN, true, false><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz);
+  else gemm_simt_kernel<BM, BN, BK, TM, TN, true, true><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz);
 }
 
 int32_t gemm_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
@@ -126,6 +134,17 @@ int32_t gemm_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float*
     launch_simt<64, 64, 16, 4, 4>(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, batch, acc);
   }
   OM_LAUNCH_CHECK(ctx, "gemm_simt");
+  return OM_OK;
+}
+
+// Sums the products of `batch` matrix pairs in chunks of batch_per_chunk: partial[c] = sum over the chunk's matrices
+// of op(A_z) op(B_z), each partial dense [m, n], chunk c at partial + c * chunk_stride.
+int32_t gemm_simt_batch_reduce(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
+                               const float* B, int ldb, int64_t sB, float* partial, int64_t chunk_stride, int batch,
+                               int batch_per_chunk) {
+  if (m == 0 || n == 0 || batch == 0) return OM_OK;
+  launch_simt<64, 64, 16, 4, 4>(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, partial, n, chunk_stride, batch, 0, batch_per_chunk);
+  OM_LAUNCH_CHECK(ctx, "gemm_simt_batch_reduce");
   return OM_OK;
 }
 

@@ -29,7 +29,7 @@ constexpr int B_TILE_BYTES = BN * BK * 4;
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int TC_THREADS = 192;
 constexpr int TMEM_COLS = 128;
-constexpr uint32_t SPIN_LIMIT = 1u << 24;        // polls of a (hardware-suspended) try_wait before giving up
+constexpr long long WAIT_CYCLES = 2000000000LL;   // about one second of SM clock: the bound of every mbarrier wait
 constexpr size_t TC_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
 struct TcParams {
@@ -65,9 +65,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait. Returns false (and raises the abort flag) when the bound is hit or another role aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int where) {
-  for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; i++) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_CYCLES) break;
+    }
   }
   *abort_flag = 1;
   if (atomicCAS(status, 0, (int32_t)OM_ERR_TIMEOUT) == 0) status[1] = where;
@@ -291,16 +295,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 // out = (accumulate ? out : 0) + part[0] + part[1] + ... in increasing split order.
 // The split sums are formed first, then bias and the previous contents are added, as the unsplit epilogue does.
-__global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits, int64_t mn, int n, const float* __restrict__ bias,
-                                     float* __restrict__ out, int accumulate) {
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits, int64_t mn, int n, int64_t ldc,
+                                     const float* __restrict__ bias, float* __restrict__ out, int accumulate) {
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t j = i; j < mn; j += stride) {
     float acc = part[j];
     for (int s = 1; s < splits; s++) acc += part[(int64_t)s * mn + j];
+    int64_t o = (j / n) * ldc + (j % n);
     if (bias) acc += bias[j % n];
-    if (accumulate) acc += out[j];
-    out[j] = acc;
+    if (accumulate) acc += out[o];
+    out[o] = acc;
   }
 }
 
@@ -402,11 +407,7 @@ int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A
   OM_LAUNCH_CHECK(ctx, "gemm_tc");
   if (splits > 1) {
     int64_t mn = (int64_t)m * n;
-    if (ldc != n) {
-      pool_free(ctx, workspace);
-      return fail(ctx, OM_ERR_UNSUPPORTED, "split-k product needs a dense output");
-    }
-    splitk_reduce_kernel<<<grid_for(ctx, mn, 256), 256, 0, ctx->stream>>>(workspace, splits, mn, n, bias, C, acc);
+    splitk_reduce_kernel<<<grid_for(ctx, mn, 256), 256, 0, ctx->stream>>>(workspace, splits, mn, n, ldc, bias, C, acc);
     pool_free(ctx, workspace);
     OM_LAUNCH_CHECK(ctx, "splitk_reduce");
   }

@@ -55,16 +55,16 @@ enum RowOp { SOFTMAX_FWD, LOGSOFTMAX_FWD, SOFTMAX_BWD, LOGSOFTMAX_BWD };
 // a = x (fwd) or g (bwd); b = y (bwd only).
 template <int G, int OP>
 __global__ void __launch_bounds__(kRowThreads)
-row_kernel(const float* __restrict__ a, const float* __restrict__ b, int32_t rows, int32_t cols, float* __restrict__ out) {
+row_kernel(const float* __restrict__ a, const float* __restrict__ b, int32_t rows, int32_t cols, int64_t ld, float* __restrict__ out) {
   __shared__ double sm[kRowThreads / 32];
   const int lane = G == 32 ? (threadIdx.x & 31) : threadIdx.x;
   const int64_t group = G == 32 ? ((int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5)) : blockIdx.x;
   const int64_t groups = G == 32 ? (int64_t)gridDim.x * (kRowThreads / 32) : gridDim.x;
   // Uniform trip count per CTA keeps __syncthreads legal for G == kRowThreads (the whole CTA shares `row`).
   for (int64_t row = group; row < rows; row += groups) {
-    const float* ar = a + row * cols;
-    const float* br = b ? b + row * cols : nullptr;
-    float* orow = out + row * cols;
+    const float* ar = a + row * ld;
+    const float* br = b ? b + row * ld : nullptr;
+    float* orow = out + row * ld;
     if (OP == SOFTMAX_FWD || OP == LOGSOFTMAX_FWD) {
       float mx = -INFINITY;
       for (int j = lane; j < cols; j += G) mx = fmaxf(mx, ar[j]);
@@ -94,17 +94,18 @@ row_kernel(const float* __restrict__ a, const float* __restrict__ b, int32_t row
 }
 
 template <int OP>
-static int32_t launch_rows(om_ctx* ctx, const char* name, const float* a, const float* b, int32_t rows, int32_t cols, float* out) {
+static int32_t launch_rows(om_ctx* ctx, const char* name, const float* a, const float* b, int32_t rows, int32_t cols, float* out, int64_t ld = 0) {
+  if (ld == 0) ld = cols;
   if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "%s: [%d,%d]", name, rows, cols);
   if (rows == 0 || cols == 0) return OM_OK;
   double bytes = (b ? 12.0 : 8.0) * rows * (double)cols;
   ProfileScope prof(ctx, name, 0, bytes);
   if (cols >= kWideRow) {
     int grid = (int)std::min<int64_t>(rows, (int64_t)ctx->sm_count * 8);
-    row_kernel<kRowThreads, OP><<<grid, kRowThreads, 0, ctx->stream>>>(a, b, rows, cols, out);
+    row_kernel<kRowThreads, OP><<<grid, kRowThreads, 0, ctx->stream>>>(a, b, rows, cols, ld, out);
   } else {
     int grid = (int)std::min<int64_t>(ceil_div(rows, kRowThreads / 32), (int64_t)ctx->sm_count * 8);
-    row_kernel<32, OP><<<grid, kRowThreads, 0, ctx->stream>>>(a, b, rows, cols, out);
+    row_kernel<32, OP><<<grid, kRowThreads, 0, ctx->stream>>>(a, b, rows, cols, ld, out);
   }
   OM_LAUNCH_CHECK(ctx, name);
   return OM_OK;
@@ -120,7 +121,7 @@ __device__ __forceinline__ void report(int32_t* status, int32_t code, int32_t de
 
 // One CTA of 1024 threads: loss = -(sum of logp[i, t_i]) over counted rows (double, fixed tree), count of counted rows.
 __global__ void nll_fwd_kernel(const float* __restrict__ logp, const void* __restrict__ targets, int dtype, int32_t rows,
-                               int32_t cols, int mean, int64_t ignore, float denominator, float* __restrict__ loss,
+                               int32_t cols, int64_t ld, int mean, int64_t ignore, float denominator, float* __restrict__ loss,
                                int32_t* __restrict__ count_out, int32_t* status) {
   __shared__ double ssum[1024];
   __shared__ int scount[1024];
@@ -133,7 +134,7 @@ __global__ void nll_fwd_kernel(const float* __restrict__ logp, const void* __res
       report(status, OM_ERR_INDEX, i);
       continue;
     }
-    s -= (double)logp[(int64_t)i * cols + t];
+    s -= (double)logp[(int64_t)i * ld + t];
     c++;
   }
   ssum[threadIdx.x] = s;
@@ -194,15 +195,15 @@ __global__ void nll_bwd_kernel(const float* __restrict__ g, const void* __restri
 // applied to the NLL gradient, which has a single non-zero per row).
 __global__ void __launch_bounds__(kRowThreads)
 cross_entropy_bwd_kernel(const float* __restrict__ g, const float* __restrict__ logp, const void* __restrict__ targets,
-                         int dtype, int32_t rows, int32_t cols, int mean, int64_t ignore, float denominator,
+                         int dtype, int32_t rows, int32_t cols, int64_t ld, int mean, int64_t ignore, float denominator,
                          const int32_t* __restrict__ count, float* __restrict__ dx) {
   float scale = nll_scale(g, mean, count, denominator);
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     int64_t t = target_at(targets, dtype, row);
     bool counted = t != ignore;
     float s = counted ? -scale : 0.f;
-    const float* y = logp + row * cols;
-    float* d = dx + row * cols;
+    const float* y = logp + row * ld;
+    float* d = dx + row * ld;
     for (int j = threadIdx.x; j < cols; j += kRowThreads) {
       float gv = (counted && j == t) ? -scale : 0.f;
       d[j] = gv - (expf(y[j]) * s);
@@ -244,7 +245,7 @@ int32_t om_nll_fwd(om_ctx* ctx, const float* logp, const void* targets, int32_t 
   OM_CHECK_CTX(ctx);
   OM_TRY(check_targets(ctx, "om_nll_fwd", target_dtype, rows, cols));
   ProfileScope prof(ctx, "om_nll_fwd", 0, 12.0 * rows);
-  nll_fwd_kernel<<<1, 1024, 0, ctx->stream>>>(logp, targets, target_dtype, rows, cols, mean, ignore_index, 0.f, loss, count, ctx->status_dev);
+  nll_fwd_kernel<<<1, 1024, 0, ctx->stream>>>(logp, targets, target_dtype, rows, cols, cols, mean, ignore_index, 0.f, loss, count, ctx->status_dev);
   OM_LAUNCH_CHECK(ctx, "om_nll_fwd");
   return OM_OK;
 }
@@ -264,34 +265,48 @@ int32_t om_nll_bwd(om_ctx* ctx, const float* g, const void* targets, int32_t tar
   return OM_OK;
 }
 
-int32_t om_cross_entropy_fwd(om_ctx* ctx, const float* logits, const void* targets, int32_t target_dtype, int32_t rows,
-                             int32_t cols, int32_t mean, int64_t ignore_index, float denominator, float* logp,
-                             float* loss, int32_t* count) {
+int32_t om_cross_entropy_fwd_ld(om_ctx* ctx, const float* logits, const void* targets, int32_t target_dtype, int32_t rows,
+                                int32_t cols, int32_t ld, int32_t mean, int64_t ignore_index, float denominator, float* logp,
+                                float* loss, int32_t* count) {
   OM_CHECK_CTX(ctx);
   OM_TRY(check_targets(ctx, "om_cross_entropy_fwd", target_dtype, rows, cols));
+  if (ld < cols) return fail(ctx, OM_ERR_SHAPE, "om_cross_entropy_fwd: row pitch %d < %d", ld, cols);
   if (!logp) return fail(ctx, OM_ERR_ARG, "om_cross_entropy_fwd: logp is required (the backward reads it)");
-  OM_TRY(launch_rows<LOGSOFTMAX_FWD>(ctx, "om_cross_entropy_fwd.logsoftmax", logits, nullptr, rows, cols, logp));
+  OM_TRY(launch_rows<LOGSOFTMAX_FWD>(ctx, "om_cross_entropy_fwd.logsoftmax", logits, nullptr, rows, cols, logp, ld));
   ProfileScope prof(ctx, "om_cross_entropy_fwd.nll", 0, 12.0 * rows);
-  nll_fwd_kernel<<<1, 1024, 0, ctx->stream>>>(logp, targets, target_dtype, rows, cols, mean, ignore_index, denominator, loss, count, ctx->status_dev);
+  nll_fwd_kernel<<<1, 1024, 0, ctx->stream>>>(logp, targets, target_dtype, rows, cols, ld, mean, ignore_index, denominator, loss, count, ctx->status_dev);
   OM_LAUNCH_CHECK(ctx, "om_cross_entropy_fwd");
   return OM_OK;
 }
 
-int32_t om_cross_entropy_bwd(om_ctx* ctx, const float* g, const float* logp, const void* targets, int32_t target_dtype,
-                             int32_t rows, int32_t cols, int32_t mean, int64_t ignore_index, float denominator,
-                             float* dlogits) {
+int32_t om_cross_entropy_fwd(om_ctx* ctx, const float* logits, const void* targets, int32_t target_dtype, int32_t rows,
+                             int32_t cols, int32_t mean, int64_t ignore_index, float denominator, float* logp,
+                             float* loss, int32_t* count) {
+  return om_cross_entropy_fwd_ld(ctx, logits, targets, target_dtype, rows, cols, cols, mean, ignore_index, denominator, logp, loss, count);
+}
+
+int32_t om_cross_entropy_bwd_ld(om_ctx* ctx, const float* g, const float* logp, const void* targets, int32_t target_dtype,
+                                int32_t rows, int32_t cols, int32_t ld, int32_t mean, int64_t ignore_index, float denominator,
+                                float* dlogits) {
   OM_CHECK_CTX(ctx);
   OM_TRY(check_targets(ctx, "om_cross_entropy_bwd", target_dtype, rows, cols));
+  if (ld < cols) return fail(ctx, OM_ERR_SHAPE, "om_cross_entropy_bwd: row pitch %d < %d", ld, cols);
   if ((int64_t)rows * cols == 0) return OM_OK;
   ProfileScope prof(ctx, "om_cross_entropy_bwd", 0, 8.0 * rows * (double)cols);
   int32_t* count = nullptr;
   OM_TRY(pool_alloc(ctx, 256, false, (void**)&count));
   count_targets_kernel<<<1, 1024, 0, ctx->stream>>>(targets, target_dtype, rows, ignore_index, count);
   int grid = (int)std::min<int64_t>(rows, (int64_t)ctx->sm_count * 8);
-  cross_entropy_bwd_kernel<<<grid, kRowThreads, 0, ctx->stream>>>(g, logp, targets, target_dtype, rows, cols, mean, ignore_index, denominator, count, dlogits);
+  cross_entropy_bwd_kernel<<<grid, kRowThreads, 0, ctx->stream>>>(g, logp, targets, target_dtype, rows, cols, ld, mean, ignore_index, denominator, count, dlogits);
   pool_free(ctx, count);
   OM_LAUNCH_CHECK(ctx, "om_cross_entropy_bwd");
   return OM_OK;
+}
+
+int32_t om_cross_entropy_bwd(om_ctx* ctx, const float* g, const float* logp, const void* targets, int32_t target_dtype,
+                             int32_t rows, int32_t cols, int32_t mean, int64_t ignore_index, float denominator,
+                             float* dlogits) {
+  return om_cross_entropy_bwd_ld(ctx, g, logp, targets, target_dtype, rows, cols, cols, mean, ignore_index, denominator, dlogits);
 }
 
 }  // extern "C"

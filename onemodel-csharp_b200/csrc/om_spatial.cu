@@ -1,0 +1,400 @@
+// Convolution and pooling, forward and backward, on NCHW tensors.
+//
+// Convolution follows the data flow of the reference's ConvBackward (BackwardNn.cs:317-462): the input is unfolded
+// (im2col) once per call for all images, the products run as strided-batched GEMMs over the images (one launch per
+// group, the weight matrix shared by all images), and the input gradient is folded back (col2im) as a GATHER: every
+// input element adds the taps that touch it in increasing (ky, kx) order, which is the order of the reference's
+// scatter loop, so no atomics are needed. The weight gradient sums over images inside the kernel (fixed chunks of
+// images per CTA, partials combined in chunk order).
+#include "om_common.cuh"
+
+namespace om {
+
+int32_t gemm_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
+                  const float* B, int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch, int acc);
+int32_t gemm_simt_batch_reduce(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
+                               const float* B, int ldb, int64_t sB, float* partial, int64_t chunk_stride, int batch,
+                               int batch_per_chunk);
+
+struct ConvGeom {
+  int n, cin, h, w, cout, kh, kw, sh, sw, pt, pl, dh, dw, groups, oh, ow;
+};
+
+static bool conv_geom(const om_conv_shape* s, ConvGeom* g) {
+  g->n = s->n; g->cin = s->cin; g->h = s->h; g->w = s->w; g->cout = s->cout; g->kh = s->kh; g->kw = s->kw;
+  g->sh = s->stride_h; g->sw = s->stride_w; g->pt = s->pad_top; g->pl = s->pad_left; g->dh = s->dil_h; g->dw = s->dil_w;
+  g->groups = s->groups;
+  if (g->n < 0 || g->cin < 1 || g->cout < 1 || g->kh < 1 || g->kw < 1 || g->sh < 1 || g->sw < 1 || g->dh < 1 || g->dw < 1 ||
+      g->groups < 1 || g->cin % g->groups || g->cout % g->groups || g->pt < 0 || g->pl < 0 || s->pad_bottom < 0 || s->pad_right < 0)
+    return false;
+  g->oh = (g->h + g->pt + s->pad_bottom - g->dh * (g->kh - 1) - 1) / g->sh + 1;
+  g->ow = (g->w + g->pl + s->pad_right - g->dw * (g->kw - 1) - 1) / g->sw + 1;
+  return g->oh >= 1 && g->ow >= 1;
+}
+
+// cols[n][(c*KH+ky)*KW+kx][oy*OW+ox] = x[n][c][oy*sh-pt+ky*dh][ox*sw-pl+kx*dw], zero outside the image.
+__global__ void im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __restrict__ cols, int64_t total) {
+  const int plane = g.oh * g.ow;
+  const int kk_all = g.cin * g.kh * g.kw;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = i; e < total; e += stride) {
+    int p = (int)(e % plane);
+    int64_t r = e / plane;
+    int kidx = (int)(r % kk_all);
+    int n = (int)(r / kk_all);
+    int kx = kidx % g.kw, ky = (kidx / g.kw) % g.kh, c = kidx / (g.kw * g.kh);
+    int oy = p / g.ow, ox = p % g.ow;
+    int iy = oy * g.sh - g.pt + ky * g.dh, ix = ox * g.sw - g.pl + kx * g.dw;
+    float v = 0.f;
+    if ((unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w) v = x[(((int64_t)n * g.cin + c) * g.h + iy) * g.w + ix];
+    cols[e] = v;
+  }
+}
+
+// dx[n][c][iy][ix] = sum over (ky, kx) in increasing order of dcols[n][(c,ky,kx)][oy*OW+ox] where the tap lands on (iy, ix).
+__global__ void col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restrict__ dx, int64_t total) {
+  const int plane = g.oh * g.ow;
+  const int64_t kk_all = (int64_t)g.cin * g.kh * g.kw;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = i; e < total; e += stride) {
+    int ix = (int)(e % g.w);
+    int iy = (int)((e / g.w) % g.h);
+    int c = (int)((e / ((int64_t)g.w * g.h)) % g.cin);
+    int n = (int)(e / ((int64_t)g.w * g.h * g.cin));
+    const float* base = dcols + ((int64_t)n * kk_all + (int64_t)c * g.kh * g.kw) * plane;
+    float acc = 0.f;
+    for (int ky = 0; ky < g.kh; ky++) {
+      int ty = iy + g.pt - ky * g.dh;
+      if (ty < 0 || ty % g.sh) continue;
+      int oy = ty / g.sh;
+      if (oy >= g.oh) continue;
+      for (int kx = 0; kx < g.kw; kx++) {
+        int tx = ix + g.pl - kx * g.dw;
+        if (tx < 0 || tx % g.sw) continue;
+        int ox = tx / g.sw;
+        if (ox >= g.ow) continue;
+        acc += base[(int64_t)(ky * g.kw + kx) * plane + oy * g.ow + ox];
+      }
+    }
+    dx[e] = acc;
+  }
+}
+
+__global__ void add_plane_bias_kernel(float* __restrict__ y, const float* __restrict__ bias, int cout, int plane, int64_t total) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = i; e < total; e += stride) y[e] += bias[(e / plane) % cout];
+}
+
+// dbias[co] = sum over n (in order) of the double plane sums of g[n][co][:]. One CTA per channel.
+__global__ void __launch_bounds__(256)
+conv_dbias_kernel(const float* __restrict__ g, int n, int cout, int plane, float* __restrict__ dbias, int accumulate) {
+  __shared__ double sm[256];
+  const int co = blockIdx.x;
+  double acc = 0.0;
+  for (int i = 0; i < n; i++) {
+    const float* p = g + ((int64_t)i * cout + co) * plane;
+    for (int e = threadIdx.x; e < plane; e += 256) acc += (double)p[e];
+  }
+  sm[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) dbias[co] = accumulate ? dbias[co] + (float)sm[0] : (float)sm[0];
+}
+
+__global__ void chunk_reduce_kernel(const float* __restrict__ part, int chunks, int64_t len, float* __restrict__ out, int accumulate) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t j = i; j < len; j += stride) {
+    float acc = part[j];
+    for (int c = 1; c < chunks; c++) acc += part[(int64_t)c * len + j];
+    out[j] = accumulate ? out[j] + acc : acc;
+  }
+}
+
+// ---- pooling --------------------------------------------------------------------------------------------------------------
+struct PoolGeom {
+  int h, w, oh, ow, kh, kw, sh, sw, ph, pw;
+};
+
+static bool pool_out(int size, int kernel, int stride, int pad, int* out) {
+  if (kernel < 1 || stride < 1 || pad < 0 || pad >= kernel) return false;
+  int64_t span = (int64_t)size + 2 * pad - kernel;
+  if (span < 0) return false;
+  *out = (int)(span / stride) + 1;
+  return true;
+}
+
+// First maximum wins ties, NaN wins over numbers (ReferenceKernels.MaxPool2d, TensorKernels.cs:242-295).
+__global__ void maxpool_fwd_kernel(PoolGeom g, const float* __restrict__ x, int64_t total, float* __restrict__ y, int32_t* __restrict__ idx) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = i; e < total; e += stride) {
+    int ox = (int)(e % g.ow), oy = (int)((e / g.ow) % g.oh);
+    int64_t pl = e / ((int64_t)g.ow * g.oh);
+    const float* xp = x + pl * g.h * g.w;
+    float best = -INFINITY;
+    int bestIdx = -1;
+    for (int ky = 0; ky < g.kh; ky++) {
+      int yy = oy * g.sh - g.ph + ky;
+      if ((unsigned)yy >= (unsigned)g.h) continue;
+      for (int kx = 0; kx < g.kw; kx++) {
+        int xx = ox * g.sw - g.pw + kx;
+        if ((unsigned)xx >= (unsigned)g.w) continue;
+        float v = xp[yy * g.w + xx];
+        bool wins = bestIdx < 0 || (v > best && !(best != best)) || ((v != v) && !(best != best));
+        if (wins) {
+          best = v;
+          bestIdx = (int)(pl * g.h * g.w) + yy * g.w + xx;
+        }
+      }
+    }
+    y[e] = best;
+    if (idx) idx[e] = bestIdx;
+  }
+}
+
+// dx[j] = sum of g[i] over the outputs i (in increasing i) whose saved index is j.
+__global__ void maxpool_bwd_kernel(PoolGeom g, const float* __restrict__ gr, const int32_t* __restrict__ idx, int64_t total,
+                                   float* __restrict__ dx) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = i; e < total; e += stride) {
+    int ix = (int)(e % g.w), iy = (int)((e / g.w) % g.h);
+    int64_t pl = e / ((int64_t)g.w * g.h);
+    int oy0 = max(0, (iy + g.ph - g.kh + g.sh) / g.sh), oy1 = min(g.oh - 1, (iy + g.ph) / g.sh);
+    int ox0 = max(0, (ix + g.pw - g.kw + g.sw) / g.sw), ox1 = min(g.ow - 1, (ix + g.pw) / g.sw);
+    float acc = 0.f;
+    for (int oy = oy0; oy <= oy1; oy++)
+      for (int ox = ox0; ox <= ox1; ox++) {
+        int64_t o = (pl * g.oh + oy) * g.ow + ox;
+        if (idx[o] == (int32_t)e) acc += gr[o];
+      }
+    dx[e] = acc;
+  }
+}
+
+// The in-bounds window of output (oy, ox) and its divisor (PoolWindow, BackwardNn.cs:490-506).
+__device__ __forceinline__ void pool_window(const PoolGeom& g, int include_pad, int oy, int ox, int* y0, int* y1, int* x0, int* x1, int* count) {
+  int ys = oy * g.sh - g.ph, xs = ox * g.sw - g.pw;
+  int ye = min(ys + g.kh, g.h + g.ph), xe = min(xs + g.kw, g.w + g.pw);
+  int padded = (ye - ys) * (xe - xs);
+  *y0 = max(ys, 0);
+  *x0 = max(xs, 0);
+  *y1 = min(ye, g.h);
+  *x1 = min(xe, g.w);
+  *count = include_pad ? padded : max(1, (*y1 - *y0) * (*x1 - *x0));
+}
+
+__global__ void avgpool_fwd_kernel(PoolGeom g, int include_pad, const float* __restrict__ x, int64_t total, float* __restrict__ y) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = i; e < total; e += stride) {
+    int ox = (int)(e % g.ow), oy = (int)((e / g.ow) % g.oh);
+    int64_t pl = e / ((int64_t)g.ow * g.oh);
+    int y0, y1, x0, x1, count;
+    pool_window(g, include_pad, oy, ox, &y0, &y1, &x0, &x1, &count);
+    const float* xp = x + pl * g.h * g.w;
+    float sum = 0.f;
+    for (int yy = y0; yy < y1; yy++)
+      for (int xx = x0; xx < x1; xx++) sum += xp[yy * g.w + xx];
+    y[e] = sum / (float)count;
+  }
+}
+
+__global__ void avgpool_bwd_kernel(PoolGeom g, int include_pad, const float* __restrict__ gr, int64_t total, float* __restrict__ dx) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = i; e < total; e += stride) {
+    int ix = (int)(e % g.w), iy = (int)((e / g.w) % g.h);
+    int64_t pl = e / ((int64_t)g.w * g.h);
+    int oy0 = max(0, (iy + g.ph - g.kh + g.sh) / g.sh), oy1 = min(g.oh - 1, (iy + g.ph) / g.sh);
+    int ox0 = max(0, (ix + g.pw - g.kw + g.sw) / g.sw), ox1 = min(g.ow - 1, (ix + g.pw) / g.sw);
+    float acc = 0.f;
+    for (int oy = oy0; oy <= oy1; oy++)
+      for (int ox = ox0; ox <= ox1; ox++) {
+        int y0, y1, x0, x1, count;
+        pool_window(g, include_pad, oy, ox, &y0, &y1, &x0, &x1, &count);
+        if (iy >= y0 && iy < y1 && ix >= x0 && ix < x1) acc += gr[(pl * g.oh + oy) * g.ow + ox] / (float)count;
+      }
+    dx[e] = acc;
+  }
+}
+
+static int32_t unfold(om_ctx* ctx, const ConvGeom& g, const float* x, float** cols) {
+  int64_t total = (int64_t)g.n * g.cin * g.kh * g.kw * g.oh * g.ow;
+  OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)(total > 0 ? total : 1), false, (void**)cols));
+  if (total > 0) im2col_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, x, *cols, total);
+  return OM_OK;
+}
+
+}  // namespace om
+
+using namespace om;
+
+extern "C" {
+
+int32_t om_conv2d_fwd(om_ctx* ctx, const om_conv_shape* s, const float* x, const float* w, const float* bias, float* y) {
+  OM_CHECK_CTX(ctx);
+  ConvGeom g;
+  if (!s || !conv_geom(s, &g)) return fail(ctx, OM_ERR_SHAPE, "Invalid convolution geometry.");
+  if (g.n == 0) return OM_OK;
+  const int cg = g.cin / g.groups, og = g.cout / g.groups, kk = cg * g.kh * g.kw, plane = g.oh * g.ow;
+  if (g.n > 65535) return fail(ctx, OM_ERR_UNSUPPORTED, "om_conv2d_fwd: more than 65535 images in one call");
+  ProfileScope prof(ctx, "om_conv2d_fwd", 2.0 * g.n * g.cout * (double)kk * plane, 4.0 * ((double)g.n * g.cin * g.h * g.w + (double)g.n * g.cout * plane));
+  float* cols = nullptr;
+  OM_TRY(unfold(ctx, g, x, &cols));
+  int32_t st = OM_OK;
+  for (int grp = 0; grp < g.groups && st == OM_OK; grp++) {
+    // y_n[og, P] = W_g[og, kk] * cols_n[kk, P]
+    st = gemm_simt(ctx, 0, 0, og, plane, kk, w + (size_t)grp * og * kk, kk, 0, cols + (size_t)grp * kk * plane, plane,
+                   (int64_t)g.groups * kk * plane, y + (size_t)grp * og * plane, plane, (int64_t)g.cout * plane, g.n, 0);
+  }
+  pool_free(ctx, cols);
+  OM_TRY(st);
+  if (bias) {
+    int64_t total = (int64_t)g.n * g.cout * plane;
+    add_plane_bias_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(y, bias, g.cout, plane, total);
+  }
+  OM_LAUNCH_CHECK(ctx, "om_conv2d_fwd");
+  return OM_OK;
+}
+
+int32_t om_conv2d_dgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, const float* w, float* dx) {
+  OM_CHECK_CTX(ctx);
+  ConvGeom g;
+  if (!s || !conv_geom(s, &g)) return fail(ctx, OM_ERR_SHAPE, "Invalid convolution geometry.");
+  if (g.n == 0) return OM_OK;
+  if (g.n > 65535) return fail(ctx, OM_ERR_UNSUPPORTED, "om_conv2d_dgrad: more than 65535 images in one call");
+  const int cg = g.cin / g.groups, og = g.cout / g.groups, kk = cg * g.kh * g.kw, plane = g.oh * g.ow;
+  ProfileScope prof(ctx, "om_conv2d_dgrad", 2.0 * g.n * g.cout * (double)kk * plane, 4.0 * ((double)g.n * g.cin * g.h * g.w + (double)g.n * g.cout * plane));
+  float* dcols = nullptr;
+  int64_t total_cols = (int64_t)g.n * g.groups * kk * plane;
+  OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)total_cols, false, (void**)&dcols));
+  int32_t st = OM_OK;
+  for (int grp = 0; grp < g.groups && st == OM_OK; grp++) {
+    // dcols_n[kk, P] = W_g^T[kk, og] * g_n[og, P]
+    st = gemm_simt(ctx, 1, 0, kk, plane, og, w + (size_t)grp * og * kk, kk, 0, gr + (size_t)grp * og * plane, plane,
+                   (int64_t)g.cout * plane, dcols + (size_t)grp * kk * plane, plane, (int64_t)g.groups * kk * plane, g.n, 0);
+  }
+  if (st == OM_OK) {
+    int64_t total = (int64_t)g.n * g.cin * g.h * g.w;
+    col2im_gather_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, dcols, dx, total);
+  }
+  pool_free(ctx, dcols);
+  OM_TRY(st);
+  OM_LAUNCH_CHECK(ctx, "om_conv2d_dgrad");
+  return OM_OK;
+}
+
+int32_t om_conv2d_wgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, const float* x, float* dw, int32_t accumulate) {
+  OM_CHECK_CTX(ctx);
+  ConvGeom g;
+  if (!s || !conv_geom(s, &g)) return fail(ctx, OM_ERR_SHAPE, "Invalid convolution geometry.");
+  const int cg = g.cin / g.groups, og = g.cout / g.groups, kk = cg * g.kh * g.kw, plane = g.oh * g.ow;
+  const int64_t wlen = (int64_t)g.cout * kk;
+  if (g.n == 0) {
+    if (!accumulate) OM_CUDA(ctx, cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)wlen, ctx->stream));
+    return OM_OK;
+  }
+  ProfileScope prof(ctx, "om_conv2d_wgrad", 2.0 * g.n * g.cout * (double)kk * plane, 4.0 * ((double)g.n * g.cin * g.h * g.w + (double)g.n * g.cout * plane));
+  float* cols = nullptr;
+  OM_TRY(unfold(ctx, g, x, &cols));
+  // Images are summed inside the kernel in fixed chunks; the chunk size depends on the shape only.
+  const int tiles = (int)(ceil_div(og, 64) * ceil_div(kk, 64)) * g.groups;
+  int chunks = (int)std::min<int64_t>(g.n, std::max<int64_t>(1, ceil_div(2 * 148, tiles)));
+  const int per_chunk = (int)ceil_div(g.n, chunks);
+  chunks = (int)ceil_div(g.n, per_chunk);
+  float* partial = nullptr;
+  int32_t st = pool_alloc(ctx, sizeof(float) * (size_t)chunks * wlen, false, (void**)&partial);
+  for (int grp = 0; grp < g.groups && st == OM_OK; grp++) {
+    // dW_g[og, kk] = sum_n g_n[og, P] * cols_n[kk, P]^T ; partial chunk c lives at partial + c*wlen
+    st = gemm_simt_batch_reduce(ctx, 0, 1, og, kk, plane, gr + (size_t)grp * og * plane, plane, (int64_t)g.cout * plane,
+                                cols + (size_t)grp * kk * plane, plane, (int64_t)g.groups * kk * plane,
+                                partial + (size_t)grp * og * kk, wlen, g.n, per_chunk);
+  }
+  if (st == OM_OK) chunk_reduce_kernel<<<grid_for(ctx, wlen, 256), 256, 0, ctx->stream>>>(partial, chunks, wlen, dw, accumulate);
+  pool_free(ctx, cols);
+  if (partial) pool_free(ctx, partial);
+  OM_TRY(st);
+  OM_LAUNCH_CHECK(ctx, "om_conv2d_wgrad");
+  return OM_OK;
+}
+
+int32_t om_conv2d_dbias(om_ctx* ctx, const om_conv_shape* s, const float* gr, float* dbias, int32_t accumulate) {
+  OM_CHECK_CTX(ctx);
+  ConvGeom g;
+  if (!s || !conv_geom(s, &g)) return fail(ctx, OM_ERR_SHAPE, "Invalid convolution geometry.");
+  ProfileScope prof(ctx, "om_conv2d_dbias", 0, 4.0 * g.n * g.cout * (double)g.oh * g.ow);
+  conv_dbias_kernel<<<g.cout, 256, 0, ctx->stream>>>(gr, g.n, g.cout, g.oh * g.ow, dbias, accumulate);
+  OM_LAUNCH_CHECK(ctx, "om_conv2d_dbias");
+  return OM_OK;
+}
+
+static int32_t pool_geom(om_ctx* ctx, const char* who, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, PoolGeom* g) {
+  g->h = h; g->w = w; g->kh = kh; g->kw = kw; g->sh = sh; g->sw = sw; g->ph = ph; g->pw = pw;
+  if (h < 0 || w < 0 || !pool_out(h, kh, sh, ph, &g->oh) || !pool_out(w, kw, sw, pw, &g->ow))
+    return fail(ctx, OM_ERR_SHAPE, "%s: Invalid pooling window (kernel %dx%d, stride %dx%d, pad %dx%d) for %dx%d.", who, kh, kw, sh, sw, ph, pw, h, w);
+  return OM_OK;
+}
+
+int32_t om_maxpool_fwd(om_ctx* ctx, const float* x, int32_t planes, int32_t h, int32_t w, int32_t kh, int32_t kw, int32_t sh,
+                       int32_t sw, int32_t ph, int32_t pw, float* y, int32_t* idx) {
+  OM_CHECK_CTX(ctx);
+  PoolGeom g;
+  OM_TRY(pool_geom(ctx, "om_maxpool_fwd", h, w, kh, kw, sh, sw, ph, pw, &g));
+  if ((int64_t)planes * h * w > INT32_MAX) return fail(ctx, OM_ERR_SHAPE, "om_maxpool_fwd: more than 2^31-1 input elements");
+  int64_t total = (int64_t)planes * g.oh * g.ow;
+  if (total <= 0) return OM_OK;
+  ProfileScope prof(ctx, "om_maxpool_fwd", 0, 4.0 * planes * ((double)h * w + 2.0 * g.oh * g.ow));
+  maxpool_fwd_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, x, total, y, idx);
+  OM_LAUNCH_CHECK(ctx, "om_maxpool_fwd");
+  return OM_OK;
+}
+
+int32_t om_maxpool_bwd(om_ctx* ctx, const float* gr, const int32_t* idx, int32_t planes, int32_t h, int32_t w, int32_t oh,
+                       int32_t ow, int32_t kh, int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, float* dx) {
+  OM_CHECK_CTX(ctx);
+  PoolGeom g;
+  OM_TRY(pool_geom(ctx, "om_maxpool_bwd", h, w, kh, kw, sh, sw, ph, pw, &g));
+  if (g.oh != oh || g.ow != ow) return fail(ctx, OM_ERR_SHAPE, "om_maxpool_bwd: output %dx%d does not match the window", oh, ow);
+  int64_t total = (int64_t)planes * h * w;
+  if (total <= 0) return OM_OK;
+  ProfileScope prof(ctx, "om_maxpool_bwd", 0, 4.0 * planes * ((double)h * w + 2.0 * oh * ow));
+  maxpool_bwd_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, gr, idx, total, dx);
+  OM_LAUNCH_CHECK(ctx, "om_maxpool_bwd");
+  return OM_OK;
+}
+
+int32_t om_avgpool_fwd(om_ctx* ctx, const float* x, int32_t planes, int32_t h, int32_t w, int32_t kh, int32_t kw, int32_t sh,
+                       int32_t sw, int32_t ph, int32_t pw, int32_t count_include_pad, float* y) {
+  OM_CHECK_CTX(ctx);
+  PoolGeom g;
+  OM_TRY(pool_geom(ctx, "om_avgpool_fwd", h, w, kh, kw, sh, sw, ph, pw, &g));
+  int64_t total = (int64_t)planes * g.oh * g.ow;
+  if (total <= 0) return OM_OK;
+  ProfileScope prof(ctx, "om_avgpool_fwd", 0, 4.0 * planes * ((double)h * w + g.oh * g.ow));
+  avgpool_fwd_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, count_include_pad, x, total, y);
+  OM_LAUNCH_CHECK(ctx, "om_avgpool_fwd");
+  return OM_OK;
+}
+
+int32_t om_avgpool_bwd(om_ctx* ctx, const float* gr, int32_t planes, int32_t h, int32_t w, int32_t kh, int32_t kw, int32_t sh,
+                       int32_t sw, int32_t ph, int32_t pw, int32_t count_include_pad, float* dx) {
+  OM_CHECK_CTX(ctx);
+  PoolGeom g;
+  OM_TRY(pool_geom(ctx, "om_avgpool_bwd", h, w, kh, kw, sh, sw, ph, pw, &g));
+  int64_t total = (int64_t)planes * h * w;
+  if (total <= 0) return OM_OK;
+  ProfileScope prof(ctx, "om_avgpool_bwd", 0, 4.0 * planes * ((double)h * w + g.oh * g.ow));
+  avgpool_bwd_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, count_include_pad, gr, total, dx);
+  OM_LAUNCH_CHECK(ctx, "om_avgpool_bwd");
+  return OM_OK;
+}
+
+}  // extern "C"

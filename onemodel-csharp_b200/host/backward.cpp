@@ -70,7 +70,15 @@ static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
   const Tensor& x = r.Saved(0);
   const Tensor& w = r.Saved(1);
   int rows = (int)r.Ints[0], inF = (int)r.Ints[1], outF = (int)r.Ints[2];
-  Tensor gc = g.Contiguous();
+  // A row-pitched rank-2 gradient (unit inner stride) is read in place.
+  int ldg = outF;
+  Tensor gc;
+  if (g.Rank() == 2 && rows > 1 && g.Strides()[1] == 1 && g.Strides()[0] > outF) {
+    gc = g;
+    ldg = (int)g.Strides()[0];
+  } else {
+    gc = g.Contiguous();
+  }
   bool hasBias = r.InputCount() == 3;
   Tensor dx;
   if (r.NeedsInputGrad(0)) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
@@ -93,11 +101,11 @@ static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
     }
   }
   if (accw == accb || !dwp || !dbp) {
-    Check(om_linear_bwd(C(), gc.Data(), x.Data(), w.Data(), rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, dbp,
-                        (dwp ? accw : accb) ? 1 : 0));
+    Check(om_linear_bwd_ld(C(), gc.Data(), ldg, x.Data(), w.Data(), rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, dbp,
+                           (dwp ? accw : accb) ? 1 : 0));
   } else {
-    Check(om_linear_bwd(C(), gc.Data(), x.Data(), w.Data(), rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, nullptr, accw));
-    Check(om_linear_bwd(C(), gc.Data(), x.Data(), w.Data(), rows, inF, outF, nullptr, nullptr, dbp, accb));
+    Check(om_linear_bwd_ld(C(), gc.Data(), ldg, x.Data(), w.Data(), rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, nullptr, accw));
+    Check(om_linear_bwd_ld(C(), gc.Data(), ldg, x.Data(), w.Data(), rows, inF, outF, nullptr, nullptr, dbp, accb));
   }
   // Emission order of the reference's record chain: bias (Add record), then input and weight (MatMul record).
   if (hasBias && r.NeedsInputGrad(2)) {
@@ -362,9 +370,11 @@ void RunBackwardOp(Engine& e, BackwardRecord& r, const Tensor& g) {
       const Tensor &logp = r.Saved(0), &t = r.Saved(1);
       const Shape& ls = r.InputShapes[0];
       Tensor gc = g.Contiguous();
-      Tensor dx = Tensor::Create(DType::F32, ls);
-      Check(om_cross_entropy_bwd(C(), gc.Data(), logp.Data(), t.RawData(), (int32_t)t.GetDType(), ls[0], ls[1],
-                                 r.Ints[0] != 0, r.Ints[1], (float)r.Floats[0], dx.Data()));
+      int ld = (int)r.Ints[2];
+      Tensor dx = ld == ls[1] ? Tensor::Create(DType::F32, ls)
+                              : Tensor::Create(DType::F32, Shape{ls[0], ld}).View(ls, {(int64_t)ld, 1}, 0);
+      Check(om_cross_entropy_bwd_ld(C(), gc.Data(), logp.Data(), t.RawData(), (int32_t)t.GetDType(), ls[0], ls[1], ld,
+                                    r.Ints[0] != 0, r.Ints[1], (float)r.Floats[0], dx.Data()));
       Engine::Emit(r, 0, dx, true);
       break;
     }

@@ -276,15 +276,22 @@ Tensor Ops::CrossEntropy(const Tensor& logits, const Tensor& targets, bool mean,
   int rows = logits.GetShape()[0], cols = logits.GetShape()[1];
   Tensor lc = logits.Contiguous();
   Tensor tc = targets.IsContiguous() ? targets : targets.Clone();
-  Tensor logp = Tensor::Create(DType::F32, logits.GetShape());
+  // Row-pitched logits (see Ops::Linear) are read in place; logp and the gradient keep the same pitch.
+  int ld = cols;
+  if (rows > 1 && logits.Strides()[1] == 1 && logits.Strides()[0] > cols) {
+    lc = logits;
+    ld = (int)logits.Strides()[0];
+  }
+  Tensor logp = ld == cols ? Tensor::Create(DType::F32, logits.GetShape())
+                           : Tensor::Create(DType::F32, Shape{rows, ld}).View(logits.GetShape(), {(int64_t)ld, 1}, 0);
   Tensor r = NewOut(Shape{});
-  Check(om_cross_entropy_fwd(C(), lc.Data(), tc.RawData(), (int32_t)tc.GetDType(), rows, cols, mean, ignoreIndex,
-                             denominator, logp.Data(), r.Data(), nullptr));
+  Check(om_cross_entropy_fwd_ld(C(), lc.Data(), tc.RawData(), (int32_t)tc.GetDType(), rows, cols, ld, mean, ignoreIndex,
+                                denominator, logp.Data(), r.Data(), nullptr));
   if (!Recording({&logits})) return r;
   auto rec = BackwardRecord::Create(OpKind::CrossEntropy, 2, {&logits});
   rec->Save(0, logp);
   rec->Save(1, tc.Detach());
-  rec->Ints = {mean ? 1 : 0, ignoreIndex};
+  rec->Ints = {mean ? 1 : 0, ignoreIndex, ld};
   rec->Floats = {denominator};
   return rec->Attach(r);
 }
@@ -298,8 +305,12 @@ Tensor Ops::Linear(const Tensor& x, const Tensor& weight, const Tensor& bias) {
   Tensor bc = bias.IsEmpty() ? Tensor() : bias.Contiguous();
   Shape os = x.GetShape();
   os.d[os.rank - 1] = outF;
-  Tensor r = NewOut(os);
-  Check(om_linear_fwd(C(), xc.Data(), wc.Data(), bc.IsEmpty() ? nullptr : bc.Data(), rows, inF, outF, r.Data()));
+  // A wide rank-2 output whose width is not a multiple of four (the vocabulary logits) gets a row pitch that is, so
+  // that the backward products can read it with TMA; consumers see an ordinary strided view.
+  const bool pitched = os.rank == 2 && (outF & 3) != 0 && (int64_t)rows * outF >= (1 << 20);
+  const int ld = pitched ? ((outF + 3) & ~3) : outF;
+  Tensor r = pitched ? Tensor::Create(DType::F32, Shape{rows, ld}).View(os, {(int64_t)ld, 1}, 0) : NewOut(os);
+  Check(om_linear_fwd_ld(C(), xc.Data(), wc.Data(), bc.IsEmpty() ? nullptr : bc.Data(), rows, inF, outF, r.Data(), ld));
   if (!Recording({&x, &weight, &bias})) return r;
   Tensor none;
   auto rec = bias.IsEmpty() ? BackwardRecord::Create(OpKind::Linear, 2, {&x, &weight})

@@ -298,3 +298,124 @@ def clip_norm(grads, max_norm, infinity=False):
         for g in grads:
             lib().orc_scale(_p(g), C.c_int64(g.size), C.c_float(coef))
     return total
+
+
+# ---- convolution, pooling, LSTM, CTC (om_oracle_spatial.c) ---------------------------------------------------------------
+
+class _ConvShape(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("n", "cin", "h", "w", "cout", "kh", "kw", "sh", "sw", "pt", "pl", "pb", "pr", "dh", "dw", "groups")]
+
+
+def _conv_shape(x, w, stride, padding, dilation=1, groups=1):
+    s = _ConvShape(x.shape[0], x.shape[1], x.shape[2], x.shape[3], w.shape[0], w.shape[2], w.shape[3], stride, stride,
+                   padding, padding, padding, padding, dilation, dilation, groups)
+    oh = (s.h + 2 * padding - dilation * (s.kh - 1) - 1) // stride + 1
+    ow = (s.w + 2 * padding - dilation * (s.kw - 1) - 1) // stride + 1
+    return s, oh, ow
+
+
+def conv2d_fwd(x, w, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    x, w = _f(x), _f(w)
+    s, oh, ow = _conv_shape(x, w, stride, padding, dilation, groups)
+    y = np.empty((s.n, s.cout, oh, ow), np.float32)
+    b = _f(bias) if bias is not None else None
+    lib().orc_conv2d_fwd(C.byref(s), _p(x), _p(w), _p(b), _p(y))
+    return y
+
+
+def conv2d_bwd(g, x, w, stride=1, padding=0, dilation=1, groups=1, need_dx=True):
+    g, x, w = _f(g), _f(x), _f(w)
+    s, _, _ = _conv_shape(x, w, stride, padding, dilation, groups)
+    dx = np.empty_like(x) if need_dx else None
+    dw, db = np.empty_like(w), np.empty(w.shape[0], np.float32)
+    lib().orc_conv2d_bwd(C.byref(s), _p(g), _p(x), _p(w), _p(dx), _p(dw), _p(db))
+    return dx, dw, db
+
+
+def _pool_out(size, k, s, p):
+    return (size + 2 * p - k) // s + 1
+
+
+def maxpool_fwd(x, kh, kw, sh, sw, ph=0, pw=0):
+    x = _f(x)
+    n, c, h, w = x.shape
+    oh, ow = _pool_out(h, kh, sh, ph), _pool_out(w, kw, sw, pw)
+    y, idx = np.empty((n, c, oh, ow), np.float32), np.empty((n, c, oh, ow), np.int32)
+    lib().orc_maxpool_fwd(_p(x), n * c, h, w, kh, kw, sh, sw, ph, pw, oh, ow, _p(y), _p(idx))
+    return y, idx
+
+
+def maxpool_bwd(g, idx, in_shape):
+    g, idx = _f(g), np.ascontiguousarray(idx, np.int32)
+    dx = np.empty(in_shape, np.float32)
+    lib().orc_maxpool_bwd(_p(g), _p(idx), C.c_int64(g.size), C.c_int64(dx.size), _p(dx))
+    return dx
+
+
+def avgpool_fwd(x, kh, kw, sh, sw, ph=0, pw=0, include_pad=False):
+    x = _f(x)
+    n, c, h, w = x.shape
+    oh, ow = _pool_out(h, kh, sh, ph), _pool_out(w, kw, sw, pw)
+    y = np.empty((n, c, oh, ow), np.float32)
+    lib().orc_avgpool_fwd(_p(x), n * c, h, w, kh, kw, sh, sw, ph, pw, int(include_pad), oh, ow, _p(y))
+    return y
+
+
+def avgpool_bwd(g, in_shape, kh, kw, sh, sw, ph=0, pw=0, include_pad=False):
+    g = _f(g)
+    n, c, h, w = in_shape
+    dx = np.empty(in_shape, np.float32)
+    lib().orc_avgpool_bwd(_p(g), n * c, h, w, kh, kw, sh, sw, ph, pw, int(include_pad), g.shape[2], g.shape[3], _p(dx))
+    return dx
+
+
+def lstm_fwd(x, wih, whh, bih, bhh, reverse=False):
+    x, wih, whh = _f(x), _f(wih), _f(whh)
+    t, b, i = x.shape
+    h = whh.shape[1]
+    y, gates = np.empty((t, b, h), np.float32), np.empty((t, b, 4 * h), np.float32)
+    c, tc = np.empty((t, b, h), np.float32), np.empty((t, b, h), np.float32)
+    lib().orc_lstm_fwd(int(reverse), t, b, i, h, _p(x), _p(wih), _p(whh), _p(_f(bih) if bih is not None else None),
+                       _p(_f(bhh) if bhh is not None else None), _p(y), _p(gates), _p(c), _p(tc))
+    return y, gates, c, tc
+
+
+def lstm_bwd(gy, x, y, wih, whh, gates, c, tc, reverse=False):
+    gy, x, y, wih, whh = _f(gy), _f(x), _f(y), _f(wih), _f(whh)
+    t, b, i = x.shape
+    h = whh.shape[1]
+    dx, dwih, dwhh = np.empty_like(x), np.empty_like(wih), np.empty_like(whh)
+    dbih, dbhh = np.empty(4 * h, np.float32), np.empty(4 * h, np.float32)
+    lib().orc_lstm_bwd(int(reverse), t, b, i, h, _p(gy), _p(x), _p(y), _p(wih), _p(whh), _p(_f(gates)), _p(_f(c)), _p(_f(tc)),
+                       _p(dx), _p(dwih), _p(dwhh), _p(dbih), _p(dbhh))
+    return dx, dwih, dwhh, dbih, dbhh
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, np.int32)
+
+
+def ctc_loss(lp, targets, tlen, ilen, blank=0, reduction=1, zero_inf=False):
+    lp, targets, tlen, ilen = _f(lp), _i32(targets), _i32(tlen), _i32(ilen)
+    t, b, c = lp.shape
+    nll, loss = np.empty(b, np.float32), np.zeros((), np.float32)
+    lib().orc_ctc_loss(_p(lp), t, b, c, _p(targets), _p(tlen), _p(ilen), blank, reduction, int(zero_inf), _p(nll), _p(loss))
+    return (nll if reduction == 0 else loss), nll
+
+
+def ctc_grad(g, lp, targets, tlen, ilen, blank=0, reduction=1):
+    lp, targets, tlen, ilen = _f(lp), _i32(targets), _i32(tlen), _i32(ilen)
+    t, b, c = lp.shape
+    grad = np.empty_like(lp)
+    lib().orc_ctc_grad(_p(_f(np.atleast_1d(g))), _p(lp), t, b, c, _p(targets), _p(tlen), _p(ilen), blank, reduction, _p(grad))
+    return grad
+
+
+def ctc_greedy(lp, ilen=None, blank=0):
+    lp = _f(lp)
+    t, b, c = lp.shape
+    labels, first, last = (np.empty((b, t), np.int32) for _ in range(3))
+    lengths = np.empty(b, np.int32)
+    il = _i32(ilen) if ilen is not None else None
+    lib().orc_ctc_greedy(_p(lp), t, b, c, _p(il), blank, _p(labels), _p(first), _p(last), _p(lengths))
+    return labels, first, last, lengths

@@ -342,3 +342,50 @@ def concat(xs, axis):
         return out
 
     return _attach(np.concatenate([t.v for t in xs], axis=axis), Record("concat", list(xs), backward=bw), list(xs))
+
+
+def conv2d(x, w, b=None, stride=1, padding=0):
+    xc, wc = np.ascontiguousarray(x.v), np.ascontiguousarray(w.v)
+
+    def bw(r, g):
+        dx, dw, db = K.conv2d_bwd(g, r.saved[0], r.saved[1], stride, padding, need_dx=r.inputs[0] is not None)
+        out = [(2, db, "own"), (1, dw, "own")] if b is not None else [(1, dw, "own")]
+        if dx is not None:
+            out.append((0, dx, "own"))
+        return out
+
+    ins = [x, w] + ([b] if b is not None else [])
+    return _attach(K.conv2d_fwd(xc, wc, b.v if b is not None else None, stride, padding), Record("conv2d", ins, saved=(xc, wc), backward=bw), ins)
+
+
+def max_pool2d(x, k, stride=None):
+    kh, kw = (k, k) if isinstance(k, int) else k
+    sh, sw = (kh, kw) if stride is None else ((stride, stride) if isinstance(stride, int) else stride)
+    y, idx = K.maxpool_fwd(x.v, kh, kw, sh, sw)
+    return _attach(y, Record("max_pool", [x], saved=(idx,), backward=lambda r, g: [(0, K.maxpool_bwd(g, r.saved[0], r.shapes[0]), "own")]), [x])
+
+
+def avg_pool2d(x, k):
+    return _attach(K.avgpool_fwd(x.v, k, k, k, k), Record("avg_pool", [x], backward=lambda r, g: [(0, K.avgpool_bwd(g, r.shapes[0], k, k, k, k), "own")]), [x])
+
+
+def lstm_layer(x, wih, whh, bih, bhh, reverse=False):
+    xc = np.ascontiguousarray(x.v)
+    y, gates, c, tc = K.lstm_fwd(xc, wih.v, whh.v, bih.v, bhh.v, reverse)
+
+    def bw(r, g):
+        dx, dwih, dwhh, dbih, dbhh = K.lstm_bwd(g, r.saved[0], r.saved[1], r.saved[2], r.saved[3], r.saved[4], r.saved[5], r.saved[6], reverse)
+        return [(0, dx, "own"), (1, dwih, "own"), (2, dwhh, "own"), (3, dbih, "own"), (4, dbhh, "own")]
+
+    ins = [x, wih, whh, bih, bhh]
+    return _attach(y, Record("lstm", ins, saved=(xc, y, wih.v, whh.v, gates, c, tc), backward=bw), ins)
+
+
+def ctc_loss(lp, targets, ilen, tlen, blank=0, reduction=1, zero_inf=False):
+    lpc = np.ascontiguousarray(lp.v)
+    loss, _ = K.ctc_loss(lpc, targets, tlen, ilen, blank, reduction, zero_inf)
+
+    def bw(r, g):
+        return [(0, K.ctc_grad(g.reshape(-1), r.saved[0], targets, tlen, ilen, blank, reduction), "own")]
+
+    return _attach(np.asarray(loss, np.float32), Record("ctc", [lp], saved=(lpc,), backward=bw), [lp])

@@ -58,6 +58,10 @@ class OracleBackend:
     def conv2d(self, x, w, b, stride=1, padding=0): return self.tape.conv2d(x, w, b, stride, padding)
     def max_pool2d(self, x, k): return self.tape.max_pool2d(x, k)
     def avg_pool2d(self, x, k): return self.tape.avg_pool2d(x, k)
+    def lstm_layer(self, x, wih, whh, bih, bhh, reverse=False): return self.tape.lstm_layer(x, wih, whh, bih, bhh, reverse)
+    def concat(self, xs, axis): return self.tape.concat(xs, axis)
+    def ctc_loss(self, lp, targets, ilen, tlen, blank=0, reduction=1, zero_inf=False):
+        return self.tape.ctc_loss(lp, targets, ilen, tlen, blank, reduction, zero_inf)
     def running(self, a): return np.array(a, np.float32)
     def running_numpy(self, r): return np.asarray(r)
     def backward(self, loss): loss.backward()
@@ -112,7 +116,16 @@ class GpuBackend:
         return self.omb.call("batch_norm2d", [x, g, b, rm, rv], ints=[1 if training else 0], floats=[0.1, 1e-5])
     def conv2d(self, x, w, b, stride=1, padding=0):
         return self.omb.call("conv2d", [x, w, b], ints=[stride, stride, padding, padding, padding, padding, 1, 1, 1])
-    def max_pool2d(self, x, k): return self.omb.call("max_pool2d", [x], ints=[k, k, k, k, 0, 0])
+    def max_pool2d(self, x, k):
+        kh, kw = (k, k) if isinstance(k, int) else k
+        return self.omb.call("max_pool2d", [x], ints=[kh, kw, kh, kw, 0, 0])
+    def lstm_layer(self, x, wih, whh, bih, bhh, reverse=False):
+        return self.omb.call("lstm_layer", [x, wih, whh, bih, bhh], ints=[1 if reverse else 0])
+    def concat(self, xs, axis): return self.omb.call("concat", list(xs), ints=[axis])
+    def ctc_loss(self, lp, targets, ilen, tlen, blank=0, reduction=1, zero_inf=False):
+        T = self.omb.Tensor.from_numpy
+        return self.omb.call("ctc_loss", [lp, T(np.asarray(targets, np.int32)), T(np.asarray(ilen, np.int32)), T(np.asarray(tlen, np.int32))],
+                             ints=[blank, reduction, 1 if zero_inf else 0])
     def avg_pool2d(self, x, k): return self.omb.call("avg_pool2d", [x], ints=[k, k, k, k, 0, 0, 0])
     def running(self, a): return self.omb.Tensor.from_numpy(np.asarray(a, np.float32))
     def running_numpy(self, r): return r.numpy()

@@ -76,3 +76,68 @@ def train_encoder(B, fx, steps=None):
         opt.step()
         losses.append(float(B.numpy(loss).reshape(-1)[0]))
     return np.array(losses, np.float32), {k: B.numpy(w[k]) for k in names}
+
+
+def cnn_forward(B, w, x, rm1, rv1, rm2, rv2, batch):
+    """The conv net of testdata/autograd/cnn and testdata/training/cnn: conv-bn-relu-maxpool, conv-bn-relu-avgpool, linear."""
+    h = B.conv2d(x, w["c1w"], w["c1b"], 1, 1)
+    h = B.batch_norm2d(h, w["bn1g"], w["bn1b"], rm1, rv1, True)
+    h = B.max_pool2d(B.relu(h), 2)
+    h = B.conv2d(h, w["c2w"], w["c2b"], 1, 1)
+    h = B.batch_norm2d(h, w["bn2g"], w["bn2b"], rm2, rv2, True)
+    h = B.avg_pool2d(B.relu(h), 2)
+    return B.linear(h.reshape(batch, 72), w["fcw"], w["fcb"])
+
+
+CNN_PARAMS = ["c1w", "c1b", "bn1g", "bn1b", "c2w", "c2b", "bn2g", "bn2b", "fcw", "fcb"]
+
+
+def autograd_cnn(B, fx):
+    """testdata/autograd/cnn: loss = NLL(log_softmax(logits)); returns (loss, logits, params incl. x, running stats)."""
+    w = {k: B.tensor(fx["in." + k], True) for k in CNN_PARAMS + ["x"]}
+    rs = [B.running(np.zeros(4)), B.running(np.ones(4)), B.running(np.zeros(8)), B.running(np.ones(8))]
+    logits = cnn_forward(B, w, w["x"], *rs, batch=4)
+    loss = B.nll_loss(B.log_softmax(logits), B.ids(fx["in.targets"].astype(np.int64)))
+    return loss, logits, w, rs
+
+
+def train_cnn(B, fx, steps=None):
+    """testdata/training/cnn: AdamW lr 3e-3 wd 0.01, cosine schedule to 0 over 60 steps, gradient-norm clipping at 0.5."""
+    w = {k: B.tensor(fx["in." + k], True) for k in CNN_PARAMS}
+    params = [w[k] for k in CNN_PARAMS]
+    opt = B.optimizer("adamw", params, 3e-3, weight_decay=0.01)
+    rs = [B.running(np.zeros(4)), B.running(np.ones(4)), B.running(np.zeros(8)), B.running(np.ones(8))]
+    x, y, order = fx["in.x"], fx["in.y"].astype(np.int64), fx["in.order"].astype(np.int64)
+    total = len(order)
+    losses, norms = [], []
+    for s in range(total if steps is None else steps):
+        # LrSchedule.Cos closed form (Schedules.cs:171-260): eta_min + (base - eta_min) (1 + cos(pi s / T)) / 2
+        opt.set_lr(float(np.float32(3e-3 * (1.0 + np.cos(np.pi * s / total)) / 2.0)))
+        idx = order[s]
+        logits = cnn_forward(B, w, B.tensor(x[idx]), *rs, batch=len(idx))
+        loss = B.cross_entropy(logits, B.ids(y[idx]))
+        opt.zero_grad()
+        B.backward(loss)
+        norms.append(B.clip_norm(params, 0.5))
+        opt.step()
+        losses.append(float(B.numpy(loss).reshape(-1)[0]))
+    return np.array(losses, np.float32), np.array(norms, np.float32), {k: B.numpy(w[k]) for k in CNN_PARAMS}, [B.running_numpy(r) for r in rs]
+
+
+def autograd_crnn(B, fx):
+    """testdata/autograd/crnn: conv-relu-maxpool x2, 2-layer BiLSTM(5), linear to 7 classes, log-softmax, CTC mean."""
+    names = [k[3:] for k in fx if k.startswith("in.") and k[3:] not in ("targets", "input_lengths", "target_lengths")]
+    w = {k: B.tensor(fx["in." + k], True) for k in names}
+    h = B.max_pool2d(B.relu(B.conv2d(w["x"], w["c1w"], w["c1b"], 1, 1)), 2)
+    h = B.max_pool2d(B.relu(B.conv2d(h, w["c2w"], w["c2b"], 1, 1)), (4, 1))      # [2, 6, 1, 12]
+    seq = h.reshape(2, 6, 12).permute(2, 0, 1)                                   # [T = 12, B, 6]
+    for layer in range(2):
+        outs = []
+        for d, sfx in enumerate(("", "_reverse")):
+            p = f"lstm.%s_l{layer}{sfx}"
+            outs.append(B.lstm_layer(seq, w[p % "weight_ih"], w[p % "weight_hh"], w[p % "bias_ih"], w[p % "bias_hh"], d == 1))
+        seq = B.concat(outs, 2)
+    lp = B.log_softmax(B.linear(seq, w["fcw"], w["fcb"]))
+    loss = B.ctc_loss(lp, fx["in.targets"].astype(np.int32), fx["in.input_lengths"].astype(np.int32),
+                      fx["in.target_lengths"].astype(np.int32), 0, 1, False)
+    return loss, lp, w

@@ -1,0 +1,196 @@
+"""Convolution, pooling, LSTM and CTC entry points against the CPU oracle, and the reference's CNN / CRNN fixtures on
+the GPU. Integer results (max-pool indices, greedy CTC labels and frame spans) are compared bit-exactly."""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import pytest
+
+import models
+import om_binding as omb
+from backends import ROOT, GpuBackend, load_fixture, scaled_diff
+from om_binding import f32, i32
+from test_oracle_golden import check_grads
+
+pytestmark = pytest.mark.gpu
+
+
+class ConvShape(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n", "cin", "h", "w", "cout", "kh", "kw", "stride_h", "stride_w", "pad_top", "pad_left",
+                                         "pad_bottom", "pad_right", "dil_h", "dil_w", "groups")]
+
+
+@pytest.fixture(scope="module")
+def K(oracle_built):
+    return oracle_built
+
+
+@pytest.mark.parametrize("n,cin,h,w,cout,k,stride,pad,groups", [
+    (4, 3, 32, 32, 64, 3, 1, 1, 1), (8, 64, 16, 16, 128, 3, 2, 1, 1), (2, 1, 32, 40, 8, 3, 1, 1, 1),
+    (3, 4, 9, 8, 6, 3, 1, 0, 2), (2, 6, 7, 7, 6, 1, 1, 0, 1), (5, 8, 12, 12, 8, 3, 2, 1, 4)])
+def test_conv2d_fwd_bwd(ctx, K, n, cin, h, w, cout, k, stride, pad, groups):
+    ctx.set_flags(0)
+    r = np.random.default_rng(n + cin + h)
+    x = r.standard_normal((n, cin, h, w)).astype(np.float32)
+    wt = (r.standard_normal((cout, cin // groups, k, k)) * 0.2).astype(np.float32)
+    b = r.standard_normal(cout).astype(np.float32)
+    y_ref = K.conv2d_fwd(x, wt, b, stride, pad, 1, groups)
+    g = r.standard_normal(y_ref.shape).astype(np.float32)
+    dx_ref, dw_ref, db_ref = K.conv2d_bwd(g, x, wt, stride, pad, 1, groups)
+    s = ConvShape(n, cin, h, w, cout, k, k, stride, stride, pad, pad, pad, pad, 1, 1, groups)
+    X, W, Bv, G = ctx.to_device(x), ctx.to_device(wt), ctx.to_device(b), ctx.to_device(g)
+    Y, DX, DW, DB = ctx.empty(y_ref.shape), ctx.empty(x.shape), ctx.empty(wt.shape), ctx.empty((cout,))
+    ctx.call("om_conv2d_fwd", ctx.handle, C.byref(s), X.ptr, W.ptr, Bv.ptr, Y.ptr)
+    assert scaled_diff(Y.numpy(), y_ref) <= 1e-6
+    ctx.call("om_conv2d_dgrad", ctx.handle, C.byref(s), G.ptr, W.ptr, DX.ptr)
+    assert np.array_equal(DX.numpy(), dx_ref)          # same products, same tap order: identical bits
+    ctx.call("om_conv2d_wgrad", ctx.handle, C.byref(s), G.ptr, X.ptr, DW.ptr, i32(0))
+    assert scaled_diff(DW.numpy(), dw_ref) <= 1e-5     # images are summed in chunks, not one by one
+    ctx.call("om_conv2d_dbias", ctx.handle, C.byref(s), G.ptr, DB.ptr, i32(0))
+    assert scaled_diff(DB.numpy(), db_ref) <= 1e-6
+    ctx.call("om_conv2d_wgrad", ctx.handle, C.byref(s), G.ptr, X.ptr, DW.ptr, i32(1))
+    assert scaled_diff(DW.numpy(), 2 * dw_ref) <= 1e-5
+    ctx.sync()
+
+
+@pytest.mark.parametrize("kh,kw,sh,sw,ph,pw", [(2, 2, 2, 2, 0, 0), (4, 1, 4, 1, 0, 0), (3, 3, 2, 2, 1, 1), (2, 1, 2, 1, 0, 0), (3, 2, 1, 1, 1, 0)])
+def test_pooling(ctx, K, kh, kw, sh, sw, ph, pw):
+    r = np.random.default_rng(kh * 10 + kw)
+    x = r.standard_normal((3, 5, 16, 12)).astype(np.float32)
+    x[0, 0, :4, :4] = 1.0           # ties: the first maximum must win
+    x[1, 2, 5, 5] = np.nan          # NaN wins over numbers
+    X = ctx.to_device(x)
+    oh, ow = (16 + 2 * ph - kh) // sh + 1, (12 + 2 * pw - kw) // sw + 1
+    if ph == 0 and pw == 0:
+        y_ref, idx_ref = K.maxpool_fwd(x, kh, kw, sh, sw)
+        Y, I = ctx.empty(y_ref.shape), ctx.empty(y_ref.shape, np.int32)
+        ctx.call("om_maxpool_fwd", ctx.handle, X.ptr, i32(15), i32(16), i32(12), i32(kh), i32(kw), i32(sh), i32(sw), i32(0), i32(0), Y.ptr, I.ptr)
+        assert np.array_equal(I.numpy(), idx_ref)                         # integers: exact
+        assert np.array_equal(Y.numpy(), y_ref, equal_nan=True)
+        g = r.standard_normal(y_ref.shape).astype(np.float32)
+        G, DX = ctx.to_device(g), ctx.empty(x.shape)
+        ctx.call("om_maxpool_bwd", ctx.handle, G.ptr, I.ptr, i32(15), i32(16), i32(12), i32(oh), i32(ow), i32(kh), i32(kw), i32(sh), i32(sw), i32(0), i32(0), DX.ptr)
+        assert np.array_equal(DX.numpy(), K.maxpool_bwd(g, idx_ref, x.shape))
+    xa = np.nan_to_num(x)
+    Xa = ctx.to_device(xa)
+    for inc in (0, 1):
+        y_ref = K.avgpool_fwd(xa, kh, kw, sh, sw, ph, pw, bool(inc))
+        Y = ctx.empty(y_ref.shape)
+        ctx.call("om_avgpool_fwd", ctx.handle, Xa.ptr, i32(15), i32(16), i32(12), i32(kh), i32(kw), i32(sh), i32(sw), i32(ph), i32(pw), i32(inc), Y.ptr)
+        assert np.array_equal(Y.numpy(), y_ref)
+        g = r.standard_normal(y_ref.shape).astype(np.float32)
+        G, DX = ctx.to_device(g), ctx.empty(x.shape)
+        ctx.call("om_avgpool_bwd", ctx.handle, G.ptr, i32(15), i32(16), i32(12), i32(kh), i32(kw), i32(sh), i32(sw), i32(ph), i32(pw), i32(inc), DX.ptr)
+        assert np.array_equal(DX.numpy(), K.avgpool_bwd(g, x.shape, kh, kw, sh, sw, ph, pw, bool(inc)))
+
+
+@pytest.mark.parametrize("reverse", [0, 1])
+@pytest.mark.parametrize("t,b,i,h", [(12, 2, 6, 5), (64, 64, 256, 256), (7, 3, 10, 8)])
+def test_lstm_layer(ctx, K, reverse, t, b, i, h):
+    ctx.set_flags(0)
+    r = np.random.default_rng(t + b + i)
+    scale = 0.4 if h < 64 else 0.05
+    x = r.standard_normal((t, b, i)).astype(np.float32)
+    wih, whh = (r.standard_normal((4 * h, i)) * scale).astype(np.float32), (r.standard_normal((4 * h, h)) * scale).astype(np.float32)
+    bih, bhh = (r.standard_normal(4 * h) * 0.2).astype(np.float32), (r.standard_normal(4 * h) * 0.2).astype(np.float32)
+    y_ref, gates_ref, c_ref, tc_ref = K.lstm_fwd(x, wih, whh, bih, bhh, bool(reverse))
+    gy = r.standard_normal(y_ref.shape).astype(np.float32)
+    refs = K.lstm_bwd(gy, x, y_ref, wih, whh, gates_ref, c_ref, tc_ref, bool(reverse))
+    X, WI, WH, BI, BH, GY = (ctx.to_device(a) for a in (x, wih, whh, bih, bhh, gy))
+    Y, GA, Cc, TC = ctx.empty(y_ref.shape), ctx.empty(gates_ref.shape), ctx.empty(c_ref.shape), ctx.empty(tc_ref.shape)
+    ctx.call("om_lstm_layer_fwd", ctx.handle, i32(reverse), i32(t), i32(b), i32(i), i32(h), X.ptr, WI.ptr, WH.ptr, BI.ptr, BH.ptr, None, None,
+             Y.ptr, GA.ptr, Cc.ptr, TC.ptr)
+    assert scaled_diff(Y.numpy(), y_ref) <= 1e-5 and scaled_diff(Cc.numpy(), c_ref) <= 1e-5
+    outs = [ctx.empty(a.shape) for a in refs]
+    ctx.call("om_lstm_layer_bwd", ctx.handle, i32(reverse), i32(t), i32(b), i32(i), i32(h), GY.ptr, None, None, X.ptr, Y.ptr, WI.ptr, WH.ptr,
+             None, None, GA.ptr, Cc.ptr, TC.ptr, *[o.ptr for o in outs], None, None)
+    for o, ref, name in zip(outs, refs, ("dx", "dw_ih", "dw_hh", "db_ih", "db_hh")):
+        assert scaled_diff(o.numpy(), ref) <= 1e-4, name
+    ctx.sync()
+
+
+def test_ctc_loss_grad_greedy(ctx, K):
+    r = np.random.default_rng(4)
+    t, b, c = 64, 64, 97
+    logits = r.standard_normal((t, b, c)).astype(np.float32)
+    lp = K.logsoftmax_fwd(logits)
+    tl = r.integers(5, 21, b).astype(np.int32)
+    tg = r.integers(1, c, int(tl.sum())).astype(np.int32)
+    il = np.full(b, t, np.int32)
+    il[3], tl[5] = 7, 0            # one infeasible sequence (more labels than frames), one empty target
+    tg = r.integers(1, c, int(tl.sum())).astype(np.int32)
+    LP, TG, TL, IL = ctx.to_device(lp), ctx.to_device(tg), ctx.to_device(tl), ctx.to_device(il)
+    for red in (1, 2, 0):
+        loss_ref, nll_ref = K.ctc_loss(lp, tg, tl, il, 0, red, True)
+        NLL, L = ctx.empty((b,)), ctx.empty(())
+        ctx.call("om_ctc_loss", ctx.handle, LP.ptr, i32(t), i32(b), i32(c), TG.ptr, TL.ptr, IL.ptr, i32(0), i32(red), i32(1), NLL.ptr, L.ptr)
+        assert np.array_equal(NLL.numpy(), nll_ref)               # same double-precision recursion: identical bits
+        if red:
+            assert float(L.numpy()) == float(loss_ref)
+        g = np.float32(0.5) if red else r.standard_normal(b).astype(np.float32)
+        Gd, GR = ctx.to_device(np.atleast_1d(g)), ctx.empty(lp.shape)
+        ctx.call("om_ctc_grad", ctx.handle, Gd.ptr, LP.ptr, i32(t), i32(b), i32(c), TG.ptr, TL.ptr, IL.ptr, None, i32(0), i32(red), i32(1), GR.ptr)
+        assert np.array_equal(GR.numpy(), K.ctc_grad(g, lp, tg, tl, il, 0, red))
+    lab_ref, first_ref, last_ref, len_ref = K.ctc_greedy(lp, il, 0)
+    LAB, FI, LA, LE = ctx.empty((b, t), np.int32), ctx.empty((b, t), np.int32), ctx.empty((b, t), np.int32), ctx.empty((b,), np.int32)
+    ctx.call("om_ctc_greedy", ctx.handle, LP.ptr, i32(t), i32(b), i32(c), IL.ptr, i32(0), LAB.ptr, FI.ptr, LA.ptr, LE.ptr)
+    assert np.array_equal(LE.numpy(), len_ref) and np.array_equal(LAB.numpy(), lab_ref)
+    assert np.array_equal(FI.numpy(), first_ref) and np.array_equal(LA.numpy(), last_ref)
+    ctx.sync()
+
+
+def test_ctc_bad_label_reports_index_error(ctx):
+    lp = np.zeros((4, 1, 3), np.float32)
+    LP, TG, TL, IL = ctx.to_device(lp), ctx.to_device(np.array([5], np.int32)), ctx.to_device(np.array([1], np.int32)), ctx.to_device(np.array([4], np.int32))
+    ctx.call("om_ctc_loss", ctx.handle, LP.ptr, i32(4), i32(1), i32(3), TG.ptr, TL.ptr, IL.ptr, i32(0), i32(1), i32(0), ctx.empty((1,)).ptr, ctx.empty(()).ptr)
+    with pytest.raises(omb.IndexOutOfRange):
+        ctx.sync()
+
+
+def test_ctc_greedy_known_answers(ctx):
+    cases = json.load(open(os.path.join(ROOT, "tests", "golden", "reference_testdata", "ctc", "cases.json")))["cases"]
+    for c in cases:
+        t, n, blank = c["steps"], c["classes"], c["blank"]
+        LP = ctx.to_device(np.array(c["scores"], np.float32).reshape(t, 1, n))
+        LAB, FI, LA, LE = ctx.empty((1, t), np.int32), ctx.empty((1, t), np.int32), ctx.empty((1, t), np.int32), ctx.empty((1,), np.int32)
+        ctx.call("om_ctc_greedy", ctx.handle, LP.ptr, i32(t), i32(1), i32(n), None, i32(blank), LAB.ptr, FI.ptr, LA.ptr, LE.ptr)
+        k = int(LE.numpy()[0])
+        assert LAB.numpy()[0, :k].tolist() == c["greedy"]["labels"]
+        assert FI.numpy()[0, :k].tolist() == c["greedy"]["first"] and LA.numpy()[0, :k].tolist() == c["greedy"]["last"]
+
+
+@pytest.fixture()
+def B(ctx):
+    ctx.set_flags(0)
+    return GpuBackend(ctx)
+
+
+def test_autograd_cnn_fixture(B):
+    fx = load_fixture("autograd", "cnn")
+    loss, logits, w, rs = models.autograd_cnn(B, fx)
+    assert scaled_diff(B.numpy(logits), fx["out.logits"]) <= 1e-4
+    B.backward(loss)
+    check_grads(B, fx, w)
+    for r, k in zip(rs, ("rm1", "rv1", "rm2", "rv2")):
+        assert scaled_diff(B.running_numpy(r), fx["out." + k]) <= 1e-5, k
+
+
+def test_autograd_crnn_fixture(B):
+    fx = load_fixture("autograd", "crnn")
+    loss, lp, w = models.autograd_crnn(B, fx)
+    assert scaled_diff(B.numpy(lp), fx["out.lp"]) <= 1e-4
+    ref = float(fx["out.loss"].reshape(-1)[0])
+    assert abs(float(B.numpy(loss).reshape(-1)[0]) - ref) <= 1e-5 * abs(ref)
+    B.backward(loss)
+    check_grads(B, fx, w)
+
+
+def test_training_cnn_fixture(B):
+    fx = load_fixture("training", "cnn")
+    losses, norms, params, rs = models.train_cnn(B, fx)
+    assert np.max(np.abs(losses - fx["out.loss"]) / np.abs(fx["out.loss"])) <= 1e-3
+    assert np.max(np.abs(norms - fx["out.gradnorm"]) / np.abs(fx["out.gradnorm"])) <= 1e-3
+    for k, v in params.items():
+        if k not in ("c1b", "c2b"):
+            assert scaled_diff(v, fx["out." + k]) <= 1e-3, k

@@ -96,3 +96,76 @@ def test_clip_norm(B):
         assert abs(total - float(fx[f"out.clip.{label}.total"][0])) <= 1e-6 * abs(float(fx[f"out.clip.{label}.total"][0]))
         assert scaled_diff(B.grad(p), fx[f"out.clip.{label}.p"]) <= 1e-6
         assert scaled_diff(B.grad(q), fx[f"out.clip.{label}.q"]) <= 1e-6
+
+
+def check_grads(B, fx, w, tol=1e-4):
+    largest = max(np.max(np.abs(fx["grad." + k])) for k in w)
+    for k, t in w.items():
+        ref = fx["grad." + k]
+        if np.max(np.abs(ref)) < 1e-5 * largest:      # zero-in-theory gradients (a bias in front of batch norm)
+            assert np.max(np.abs(B.grad(t))) < 1e-5 * largest, k
+        else:
+            assert scaled_diff(B.grad(t), ref) <= tol, k
+
+
+def test_autograd_cnn_gradients(B):
+    fx = load_fixture("autograd", "cnn")
+    loss, logits, w, rs = models.autograd_cnn(B, fx)
+    assert scaled_diff(B.numpy(logits), fx["out.logits"]) <= 1e-4
+    B.backward(loss)
+    check_grads(B, fx, w)
+    for r, k in zip(rs, ("rm1", "rv1", "rm2", "rv2")):
+        assert scaled_diff(B.running_numpy(r), fx["out." + k]) <= 1e-5, k
+
+
+def test_autograd_crnn_gradients_and_ctc_losses(B):
+    fx = load_fixture("autograd", "crnn")
+    loss, lp, w = models.autograd_crnn(B, fx)
+    assert scaled_diff(B.numpy(lp), fx["out.lp"]) <= 1e-4
+    assert abs(float(B.numpy(loss).reshape(-1)[0]) - float(fx["out.loss"].reshape(-1)[0])) <= 1e-5 * abs(float(fx["out.loss"].reshape(-1)[0]))
+    B.backward(loss)
+    check_grads(B, fx, w)
+
+
+def test_training_cnn_curve(B):
+    fx = load_fixture("training", "cnn")
+    losses, norms, params, rs = models.train_cnn(B, fx)
+    assert np.max(np.abs(losses - fx["out.loss"]) / np.abs(fx["out.loss"])) <= 1e-3
+    assert np.max(np.abs(norms - fx["out.gradnorm"]) / np.abs(fx["out.gradnorm"])) <= 1e-3
+    for k, v in params.items():
+        if k in ("c1b", "c2b"):
+            continue  # a bias in front of batch norm has zero true gradient (TrainingCurveTests.cs:49-60)
+        assert scaled_diff(v, fx["out." + k]) <= 1e-3, k
+
+
+def test_ctc_reductions_and_infeasible_targets(oracle_built):
+    K = oracle_built
+    fx = load_fixture("autograd", "crnn")
+    lp = fx["out.lp"]
+    tg, il, tl = fx["in.targets"].astype(np.int32), fx["in.input_lengths"].astype(np.int32), fx["in.target_lengths"].astype(np.int32)
+    for red, name in ((0, "none"), (2, "sum"), (1, "mean")):
+        got, _ = K.ctc_loss(lp, tg, tl, il, 0, red)
+        assert np.max(np.abs(np.atleast_1d(got) - fx["out.ctc_" + name]) / np.abs(fx["out.ctc_" + name])) <= 1e-5
+    short = np.array([12, 2], np.int32)
+    got, _ = K.ctc_loss(lp, tg, tl, short, 0, 0, False)
+    assert np.isinf(got[1]) and np.isinf(fx["out.ctc_inf_none"][1]) and abs(got[0] - fx["out.ctc_inf_none"][0]) <= 1e-5 * abs(got[0])
+    got, _ = K.ctc_loss(lp, tg, tl, short, 0, 0, True)
+    assert got[1] == 0.0 and fx["out.ctc_zeroinf_none"][1] == 0.0
+
+
+def test_ctc_greedy_known_answers(oracle_built):
+    """testdata/ctc/cases.json: greedy labels and the first / last frame of every run are exact integers (CtcTests.cs:26-60)."""
+    import json, os
+    from backends import ROOT
+    K = oracle_built
+    cases = json.load(open(os.path.join(ROOT, "tests", "golden", "reference_testdata", "ctc", "cases.json")))["cases"]
+    checked = 0
+    for c in cases:
+        t, n, blank = c["steps"], c["classes"], c["blank"]
+        scores = np.array(c["scores"], np.float32).reshape(t, 1, n)
+        labels, first, last, lengths = K.ctc_greedy(scores, None, blank)
+        k = int(lengths[0])
+        assert labels[0, :k].tolist() == c["greedy"]["labels"]
+        assert first[0, :k].tolist() == c["greedy"]["first"] and last[0, :k].tolist() == c["greedy"]["last"]
+        checked += 1
+    assert checked >= 10
