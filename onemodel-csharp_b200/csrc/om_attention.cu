@@ -11,6 +11,19 @@ namespace om {
 
 int32_t gemm_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
                   const float* B, int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch, int acc);
+bool gemm_tc_batched_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA,
+                               const float* B, int ldb, long long sB, int batch);
+int32_t gemm_tc_batched(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, const float* B,
+                        int ldb, long long sB, float* C, int ldc, long long sC, int batch, int acc, const float* bias);
+
+// One product per (batch, head): on the tensor pipe (TF32) when the context asks for it and the strides allow TMA,
+// else on the fp32 FMA kernel.
+static int32_t head_gemm(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA, const float* B,
+                         int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch) {
+  if (batch > 1 && (ldc & 3) == 0 && (sC & 3) == 0 && gemm_tc_batched_supported(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, batch))
+    return gemm_tc_batched(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, batch, 0, nullptr);
+  return gemm_simt(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, batch, 0);
+}
 
 __device__ __forceinline__ double att_wsum_d(double v) {
 #pragma unroll
@@ -99,11 +112,11 @@ int32_t om_attention_fwd(om_ctx* ctx, const float* q, const float* k, const floa
   float* s = nullptr;
   int64_t rows = (int64_t)bh * lq;
   OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)rows * lk, false, (void**)&s));
-  int32_t st = gemm_simt(ctx, 0, 1, lq, lk, d, q, d, (int64_t)lq * d, k, d, (int64_t)lk * d, s, lk, (int64_t)lq * lk, bh, 0);
+  int32_t st = head_gemm(ctx, 0, 1, lq, lk, d, q, d, (int64_t)lq * d, k, d, (int64_t)lk * d, s, lk, (int64_t)lq * lk, bh);
   if (st == OM_OK) {
     int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 16);
     att_softmax_kernel<<<grid, 256, 0, ctx->stream>>>(s, mask, mask_batch_stride, h, lq, lk, rows, scale, lse);
-    st = gemm_simt(ctx, 0, 0, lq, d, lk, s, lk, (int64_t)lq * lk, v, d, (int64_t)lk * d, out, d, (int64_t)lq * d, bh, 0);
+    st = head_gemm(ctx, 0, 0, lq, d, lk, s, lk, (int64_t)lq * lk, v, d, (int64_t)lk * d, out, d, (int64_t)lq * d, bh);
   }
   pool_free(ctx, s);
   OM_TRY(st);
@@ -130,19 +143,19 @@ int32_t om_attention_bwd(om_ctx* ctx, const float* g, const float* q, const floa
   }
   const int64_t sq = (int64_t)lq * d, sk = (int64_t)lk * d, ss = (int64_t)lq * lk;
   int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 16);
-  st = gemm_simt(ctx, 0, 1, lq, lk, d, q, d, sq, k, d, sk, p, lk, ss, bh, 0);
+  st = head_gemm(ctx, 0, 1, lq, lk, d, q, d, sq, k, d, sk, p, lk, ss, bh);
   if (st == OM_OK) {
     att_softmax_kernel<<<grid, 256, 0, ctx->stream>>>(p, mask, mask_batch_stride, h, lq, lk, rows, scale, nullptr);
     // dV = P^T dO
-    if (dv) st = gemm_simt(ctx, 1, 0, lk, d, lq, p, lk, ss, g, d, sq, dv, d, sk, bh, 0);
+    if (dv) st = head_gemm(ctx, 1, 0, lk, d, lq, p, lk, ss, g, d, sq, dv, d, sk, bh);
   }
   if (st == OM_OK && (dq || dk)) {
     // dP = dO V^T, then dS in place
-    st = gemm_simt(ctx, 0, 1, lq, lk, d, g, d, sq, v, d, sk, dp, lk, ss, bh, 0);
+    st = head_gemm(ctx, 0, 1, lq, lk, d, g, d, sq, v, d, sk, dp, lk, ss, bh);
     if (st == OM_OK) {
       att_ds_kernel<<<grid, 256, 0, ctx->stream>>>(dp, p, lk, rows, scale);
-      if (dq) st = gemm_simt(ctx, 0, 0, lq, d, lk, dp, lk, ss, k, d, sk, dq, d, sq, bh, 0);
-      if (st == OM_OK && dk) st = gemm_simt(ctx, 1, 0, lk, d, lq, dp, lk, ss, q, d, sq, dk, d, sk, bh, 0);
+      if (dq) st = head_gemm(ctx, 0, 0, lq, d, lk, dp, lk, ss, k, d, sk, dq, d, sq, bh);
+      if (st == OM_OK && dk) st = head_gemm(ctx, 1, 0, lk, d, lq, dp, lk, ss, q, d, sq, dk, d, sk, bh);
     }
   }
   pool_free(ctx, p);

@@ -11,6 +11,10 @@ bool gemm_tc_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const f
                        int ldb, const float* C, int ldc);
 int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb,
                 float* C, int ldc, int acc, const float* bias);
+bool gemm_tc_batched_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA,
+                               const float* B, int ldb, long long sB, int batch);
+int32_t gemm_tc_batched(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, const float* B,
+                        int ldb, long long sB, float* C, int ldc, long long sC, int batch, int acc, const float* bias);
 
 __global__ void add_bias_rows_kernel(float* __restrict__ y, const float* __restrict__ bias, int64_t rows, int32_t cols, int64_t ld) {
   int64_t total = rows * cols;
@@ -83,6 +87,9 @@ int32_t om_matmul_batched(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m
   if (batch < 0 || batch > 65535) return fail(ctx, OM_ERR_SHAPE, "om_matmul_batched: batch %d", batch);
   ProfileScope prof(ctx, "om_matmul_batched", 2.0 * m * n * k * batch,
                     4.0 * batch * ((double)m * k + (double)k * n + (double)m * n));
+  if (batch > 1 && (ldc & 3) == 0 && (strideC & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+      gemm_tc_batched_supported(ctx, transA, transB, m, n, k, A, lda, strideA, B, ldb, strideB, batch))
+    return gemm_tc_batched(ctx, transA, transB, m, n, k, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, batch, accumulate, nullptr);
   return gemm_simt(ctx, transA, transB, m, n, k, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, batch, accumulate);
 }
 

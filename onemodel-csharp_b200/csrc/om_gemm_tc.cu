@@ -22,7 +22,7 @@
 namespace om {
 
 constexpr int BM = 128, BN = 128, BK = 32;       // BK fp32 elements = one 128-byte swizzle row
-constexpr int STAGES = 6;
+constexpr int STAGES = 3;                        // 96 KiB of operand tiles: two CTAs per SM, one's epilogue under the other's MMAs
 constexpr int UMMA_K = 8;                        // tf32: 32 bytes of k per instruction
 constexpr int A_TILE_BYTES = BM * BK * 4;        // 16 KiB
 constexpr int B_TILE_BYTES = BN * BK * 4;
@@ -41,6 +41,8 @@ struct TcParams {
   int accumulate;       // only when splits == 1
   const float* bias;    // only when splits == 1
   int32_t* status;
+  int batched;          // blockIdx.z is a matrix of a strided batch (then splits == 1)
+  long long stride_c;   // elements between the C matrices of a batch
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------------------
@@ -78,10 +80,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+// Tile load through a rank-3 tensor map (inner, outer, matrix of the batch).
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
       : "memory");
 }
 
@@ -150,7 +153,7 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(bool a_mn, bool b_mn) {
 //                                 offset), 4-row k groups (the 32-byte-unit swizzle atom) 512 bytes apart (stride
 //                                 offset); one MMA consumes 8 k-rows = 1024 bytes.
 template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -162,7 +165,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const int split = blockIdx.z;
+  const int split = p.batched ? 0 : blockIdx.z;
+  const int zb = p.batched ? blockIdx.z : 0;
   const int k_begin = split * p.k_per_split;
   const int k_end = min(p.k, k_begin + p.k_per_split);
   const int k_blocks = (k_end - k_begin + BK - 1) / BK;
@@ -198,15 +202,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_expect_tx(&full[s], STAGE_BYTES);
         if (A_MN) {
 #pragma unroll
-          for (int j = 0; j < BM / 32; j++) tma_load_2d(a_dst + j * (BK * 128), &map_a, m0 + 32 * j, k0, &full[s]);
+          for (int j = 0; j < BM / 32; j++) tma_load_3d(a_dst + j * (BK * 128), &map_a, m0 + 32 * j, k0, zb, &full[s]);
         } else {
-          tma_load_2d(a_dst, &map_a, k0, m0, &full[s]);
+          tma_load_3d(a_dst, &map_a, k0, m0, zb, &full[s]);
         }
         if (B_MN) {
 #pragma unroll
-          for (int j = 0; j < BN / 32; j++) tma_load_2d(b_dst + j * (BK * 128), &map_b, n0 + 32 * j, k0, &full[s]);
+          for (int j = 0; j < BN / 32; j++) tma_load_3d(b_dst + j * (BK * 128), &map_b, n0 + 32 * j, k0, zb, &full[s]);
         } else {
-          tma_load_2d(b_dst, &map_b, k0, n0, &full[s]);
+          tma_load_3d(b_dst, &map_b, k0, n0, zb, &full[s]);
         }
       }
     }
@@ -241,7 +245,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     bool ok = true;
     if (k_blocks > 0) ok = mbar_wait(acc_full, 0, abort_flag, p.status, 3);
     tc_fence_after();
-    float* c = p.c + (size_t)split * p.m * p.ldc;
+    float* c = p.c + (size_t)split * p.m * p.ldc + (size_t)zb * p.stride_c;
     if (ok) {
 #pragma unroll 1
       for (int cb = 0; cb < BN / 32; cb++) {
@@ -330,15 +334,17 @@ static EncodeTiledFn encode_fn() {
 // A rank-2 fp32 tensor map over a row-major matrix [outer, inner] with leading dimension ld, box [box_outer, 32].
 // K-major tiles use the 16-byte-unit 128B swizzle, MN-major tiles the 32-byte-unit one. The TFLOAT32 element type makes
 // TMA round each value to TF32 (nearest) on the way in; the tensor core would otherwise truncate the low 13 bits.
-static bool make_map(CUtensorMap* map, const float* base, int inner, int outer, int ld, int box_outer, bool mn_major) {
-  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
-  cuuint32_t box[2] = {32, (cuuint32_t)box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+static bool make_map(CUtensorMap* map, const float* base, int inner, int outer, int ld, int box_outer, bool mn_major,
+                     int batch = 1, long long batch_stride = 0) {
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)(batch > 1 ? batch_stride : (long long)ld * outer) * 4};
+  if (strides[1] < 16) strides[1] = 16;
+  strides[1] = (strides[1] + 15) & ~(cuuint64_t)15;   // only read when batch > 1, where the caller guarantees alignment
+  cuuint32_t box[3] = {32, (cuuint32_t)box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
@@ -354,14 +360,32 @@ bool gemm_tc_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const f
   return true;
 }
 
+int32_t gemm_tc_batched(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, const float* B,
+                        int ldb, long long sB, float* C, int ldc, long long sC, int batch, int acc, const float* bias);
+
 int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb, float* C,
                 int ldc, int acc, const float* bias) {
+  return gemm_tc_batched(ctx, ta, tb, m, n, k, A, lda, 0, B, ldb, 0, C, ldc, 0, 1, acc, bias);
+}
+
+// Strided batch: matrix z of A, B, C starts sA, sB, sC elements after matrix z - 1 (0 shares an operand). The batch
+// rides on blockIdx.z, so a batched product never splits k.
+bool gemm_tc_batched_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA,
+                               const float* B, int ldb, long long sB, int batch) {
+  if (!gemm_tc_supported(ctx, ta, tb, m, n, k, A, lda, B, ldb, nullptr, 0)) return false;
+  if (batch < 1 || batch > 65535) return false;
+  if (batch > 1 && ((sA & 3) || (sB & 3) || sA <= 0 || sB <= 0)) return false;
+  return true;
+}
+
+int32_t gemm_tc_batched(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, const float* B,
+                        int ldb, long long sB, float* C, int ldc, long long sC, int batch, int acc, const float* bias) {
   // op(A) is [m, k]. ta == 0: stored [m, k] (K-major tile, map inner = k). ta != 0: stored [k, m] (MN-major, inner = m).
   // op(B) is [k, n]. tb != 0: stored [n, k] (K-major, inner = k). tb == 0: stored [k, n] (MN-major, inner = n).
   const bool a_mn = ta != 0, b_mn = tb == 0;
   CUtensorMap map_a, map_b;
-  bool ok = a_mn ? make_map(&map_a, A, m, k, lda, BK, true) : make_map(&map_a, A, k, m, lda, BM, false);
-  ok = ok && (b_mn ? make_map(&map_b, B, n, k, ldb, BK, true) : make_map(&map_b, B, k, n, ldb, BN, false));
+  bool ok = a_mn ? make_map(&map_a, A, m, k, lda, BK, true, batch, sA) : make_map(&map_a, A, k, m, lda, BM, false, batch, sA);
+  ok = ok && (b_mn ? make_map(&map_b, B, n, k, ldb, BK, true, batch, sB) : make_map(&map_b, B, k, n, ldb, BN, false, batch, sB));
   if (!ok) return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed (m %d n %d k %d lda %d ldb %d)", m, n, k, lda, ldb);
 
   const int tiles = (int)(ceil_div(m, BM) * ceil_div(n, BN));
@@ -369,7 +393,7 @@ int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A
   // Fixed split of k: enough slices to give every SM a tile, each slice at least 8 k-blocks deep. The split count is
   // a function of the shape only, so results do not depend on the device or on timing.
   int splits = 1;
-  if (tiles < 148 && k_blocks >= 16) {
+  if (batch == 1 && tiles < 148 && k_blocks >= 16) {
     splits = (int)std::min<int64_t>(ceil_div(148, tiles), k_blocks / 8);
     if (splits < 1) splits = 1;
     if (splits > 32) splits = 32;
@@ -382,6 +406,8 @@ int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A
   p.k_per_split = kb_per_split * BK;
   p.splits = splits;
   p.status = ctx->status_dev;
+  p.batched = batch > 1;
+  p.stride_c = sC;
   float* workspace = nullptr;
   if (splits > 1) {
     OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)splits * m * n, false, (void**)&workspace));
@@ -389,7 +415,7 @@ int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A
   } else {
     p.c = C; p.ldc = ldc; p.accumulate = acc; p.bias = bias;
   }
-  dim3 grid((unsigned)ceil_div(n, BN), (unsigned)ceil_div(m, BM), (unsigned)splits);
+  dim3 grid((unsigned)ceil_div(n, BN), (unsigned)ceil_div(m, BM), (unsigned)(batch > 1 ? batch : splits));
 #define OM_TC_LAUNCH(AMN, BMN)                                                                                         \
   do {                                                                                                                 \
     static bool attr_set = false;                                                                                      \

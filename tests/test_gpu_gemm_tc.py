@@ -9,7 +9,7 @@ import pytest
 
 import om_binding as omb
 from backends import scaled_diff
-from om_binding import i32
+from om_binding import f32, i32, i64
 
 pytestmark = pytest.mark.gpu
 
@@ -93,5 +93,56 @@ def test_unaligned_operands_use_the_fp32_kernel(ctx, oracle_built):
         r = np.random.default_rng(2)
         a, b = r.standard_normal((64, 91)).astype(np.float32), r.standard_normal((91, 53)).astype(np.float32)
         assert np.array_equal(run(ctx, 0, 0, 64, 53, 91, a, b), K.gemm(a, b))
+    finally:
+        ctx.set_flags(0)
+
+
+@pytest.mark.parametrize("ta,tb,m,n,k,batch", [(0, 1, 128, 128, 32, 24), (0, 0, 128, 32, 128, 24), (1, 0, 128, 32, 128, 24),
+                                               (0, 1, 200, 72, 40, 5), (1, 1, 96, 160, 64, 3), (0, 0, 64, 64, 512, 7)])
+def test_tf32_strided_batch(ctx, oracle_built, ta, tb, m, n, k, batch):
+    """One launch over a strided batch (rank-3 tensor maps): every slice equals the single product of that slice."""
+    K = oracle_built
+    ctx.set_flags(omb.OM_TF32)
+    try:
+        r = np.random.default_rng(m + n + k + batch)
+        a = r.standard_normal((batch,) + ((k, m) if ta else (m, k))).astype(np.float32)
+        b = r.standard_normal((batch,) + ((n, k) if tb else (k, n))).astype(np.float32)
+        da, db, dc = ctx.to_device(a), ctx.to_device(b), ctx.empty((batch, m, n))
+        ctx.call("om_matmul_batched", ctx.handle, i32(ta), i32(tb), i32(m), i32(n), i32(k), da.ptr, i32(a.shape[2]),
+                 i64(a.shape[1] * a.shape[2]), db.ptr, i32(b.shape[2]), i64(b.shape[1] * b.shape[2]), dc.ptr, i32(n),
+                 i64(m * n), i32(batch), i32(0))
+        ctx.sync()
+        got = dc.numpy()
+        for z in range(batch):
+            assert scaled_diff(got[z], K.gemm(a[z], b[z], bool(ta), bool(tb), mode="tf32")) <= 2e-5, z
+            single = run(ctx, ta, tb, m, n, k, a[z], b[z])
+            # A single product of a small shape splits k over several CTAs, the batched launch never does: the same
+            # rounded operands summed in another order.
+            assert np.array_equal(got[z], single) if k < 512 else scaled_diff(got[z], single) <= 2e-5, z
+    finally:
+        ctx.set_flags(0)
+
+
+@pytest.mark.parametrize("b,h,lq,lk,d,masked", [(3, 4, 128, 128, 32, 0), (2, 2, 64, 192, 64, 1), (2, 3, 100, 100, 32, 0)])
+def test_tf32_attention(ctx, oracle_built, b, h, lq, lk, d, masked):
+    """Attention forward and backward with the head products on the tensor pipe, at the TF32 tier of the contract."""
+    K = oracle_built
+    ctx.set_flags(omb.OM_TF32)
+    try:
+        r = np.random.default_rng(b * 7 + lq)
+        q, k, v, g = (r.standard_normal(s).astype(np.float32) for s in [(b, h, lq, d), (b, h, lk, d), (b, h, lk, d), (b, h, lq, d)])
+        mask = np.where(r.random((lq, lk)) < 0.25, -4.0, 0.0).astype(np.float32) if masked else None
+        scale = np.float32(1.0 / np.sqrt(np.float32(d)))
+        Q, Kk, V, G = ctx.to_device(q), ctx.to_device(k), ctx.to_device(v), ctx.to_device(g)
+        M = ctx.to_device(mask) if mask is not None else None
+        O, DQ, DK, DV = ctx.empty(q.shape), ctx.empty(q.shape), ctx.empty(k.shape), ctx.empty(v.shape)
+        ctx.call("om_attention_fwd", ctx.handle, Q.ptr, Kk.ptr, V.ptr, M.ptr if M else None, i64(0), i32(b), i32(h), i32(lq),
+                 i32(lk), i32(d), f32(scale), O.ptr, None)
+        ctx.call("om_attention_bwd", ctx.handle, G.ptr, Q.ptr, Kk.ptr, V.ptr, M.ptr if M else None, i64(0), None, i32(b),
+                 i32(h), i32(lq), i32(lk), i32(d), f32(scale), DQ.ptr, DK.ptr, DV.ptr)
+        ctx.sync()
+        assert scaled_diff(O.numpy(), K.attention_fwd(q, k, v, mask)) <= 1e-3
+        dq, dk, dv = K.attention_bwd(g, q, k, v, mask)
+        assert scaled_diff(DQ.numpy(), dq) <= 1e-3 and scaled_diff(DK.numpy(), dk) <= 1e-3 and scaled_diff(DV.numpy(), dv) <= 1e-3
     finally:
         ctx.set_flags(0)
