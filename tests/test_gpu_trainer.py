@@ -69,3 +69,39 @@ def test_mlm_config_small(ctx, configs, graph):
         if not n.endswith("attn.k.bias"):
             assert scaled_diff(tr.get_param(i, s), weights[n]) <= 1e-3, n
     tr.close()
+
+
+def _run_c3(steps, graph_at, tf32):
+    cfg = [64, 128, 6, 384, 12, 1536, 30522, 1229]
+    tr = omb.Trainer("mlm", cfg, lr=1e-4, weight_decay=0.01, seed=0)
+    losses = []
+    for step in range(steps):
+        if graph_at is not None and step == graph_at:
+            tr.enable_graph()
+        ids, pos, labels = synth.mlm_batch(64, 128, 30522, 1229, step)
+        losses.append(np.float32(tr.step([ids, pos, labels])))
+    named = tr.named_parameters()
+    params = [tr.get_param(i, s) for i, (_, s) in enumerate(named)]
+    tr.close()
+    return np.array(losses), params
+
+
+@pytest.mark.parametrize("tf32", [False, True])
+def test_full_size_encoder_step_is_deterministic_and_graph_equals_eager(ctx, tf32):
+    """Config 3 at its full size (6 x d384 h12 ff1536, seq 128, batch 64, vocab 30522, 1229 masked rows), where the
+    oracle would take minutes per step: the size-independent properties. Two runs from the same seed give the same
+    bits (fixed reduction orders, no float atomics), a run replayed from a captured graph gives the bits of the eager
+    run, and the first loss is ln(vocab) to within the spread of the initial logits."""
+    ctx.set_flags(omb.OM_TF32 if tf32 else 0)
+    ctx.make_current()
+    try:
+        la, pa = _run_c3(4, None, tf32)
+        lb, pb = _run_c3(4, None, tf32)
+        lc, pc = _run_c3(4, 2, tf32)
+        assert np.array_equal(la, lb) and np.array_equal(la, lc)
+        for a, b, c in zip(pa, pb, pc):
+            assert np.array_equal(a, b) and np.array_equal(a, c)
+        assert abs(float(la[0]) - np.log(30522.0)) < 0.5
+        assert np.all(np.isfinite(la))
+    finally:
+        ctx.set_flags(0)
