@@ -191,6 +191,16 @@ int32_t om_sum_to(om_ctx* ctx, int32_t rank, const int32_t* shape, const float* 
                   const int64_t* t_strides, float* out, int64_t out_len);
 /* out[cols] = column sums of g[rows,cols] (bias gradient; the common case of SumTo), double accumulation. */
 int32_t om_colsum(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, float* out, int32_t accumulate);
+/* om_colsum without any device allocation. No counterpart in the reference: an addition for hosts that must not
+ * allocate device memory once they are running (their whole device budget is handed out at start-up, or a driver
+ * allocation's device-wide synchronisation and late out-of-memory failure are not acceptable in the middle of a run).
+ * The per-chunk partial sums go to a fixed 1 MiB array inside the loaded module instead of the context's pool, so the
+ * call takes nothing from the pool or the driver. Same arithmetic and same bits as om_colsum.
+ * Limit: ceil(rows / 512) * cols <= 131072; beyond it the call returns OM_ERR_UNSUPPORTED and om_colsum is the one to use.
+ * The first call on a device looks the array's address up (set-up work: make it before any stream capture). The array
+ * is shared by every call on the device and keeps its last contents; calls that overlap on one device race on it, so
+ * the caller serialises them. */
+int32_t om_colsum_static(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, float* out, int32_t accumulate);
 /* Sum/Mean forward over one axis or all (axis < 0) of a contiguous tensor viewed as [outer, n, inner]
  * (Ops.Nn.cs:162-231), double accumulation in increasing order. */
 int32_t om_reduce_fwd(om_ctx* ctx, const float* x, int64_t outer, int64_t n, int64_t inner, int32_t mean,
