@@ -295,6 +295,28 @@ int32_t om_attention_bwd(om_ctx* ctx, const float* g, const float* q, const floa
                          int32_t h, int32_t lq, int32_t lk, int32_t d, float scale, float* dq, float* dk,
                          float* dv);
 
+/* Element strides of an activation seen as [B, H, L, D] with D contiguous: where the [L, D] matrix of (batch, head)
+ * starts (batch, head) and how far apart its rows are (row >= D). [B,H,L,D] contiguous is {H*L*D, L*D, D}; the output
+ * of a Linear, [B, L, H*D], read per head without a copy is {L*H*D, D, H*D}. */
+typedef struct om_head_strides {
+  int64_t batch, head, row;
+} om_head_strides;
+/* om_attention_fwd / om_attention_bwd on activations addressed through om_head_strides, so that the head split
+ * ([B,L,H*D] -> [B,H,L,D]) and merge permutes around Ops.Attention (the Reshape + Permute pairs of
+ * MultiHeadAttention.Forward, Layers.cs:503-520, and their inverse-permute copies in the backward, BackwardOps.cs:86-99)
+ * need no copy: the tensor-map (or the fp32 kernel's index arithmetic) walks the strided layout directly. */
+int32_t om_attention_fwd_strided(om_ctx* ctx, const float* q, const om_head_strides* qs, const float* k,
+                                 const om_head_strides* ks, const float* v, const om_head_strides* vs,
+                                 const float* mask, int64_t mask_batch_stride, int32_t b, int32_t h, int32_t lq,
+                                 int32_t lk, int32_t d, float scale, float* out, const om_head_strides* os,
+                                 float* lse);
+int32_t om_attention_bwd_strided(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q,
+                                 const om_head_strides* qs, const float* k, const om_head_strides* ks,
+                                 const float* v, const om_head_strides* vs, const float* mask,
+                                 int64_t mask_batch_stride, const float* lse, int32_t b, int32_t h, int32_t lq,
+                                 int32_t lk, int32_t d, float scale, float* dq, const om_head_strides* dqs,
+                                 float* dk, const om_head_strides* dks, float* dv, const om_head_strides* dvs);
+
 /* ---- pooling and convolution ---------------------------------------------------------------------------- */
 
 /* The 16 integers of ConvShape (src/OneModel/Kernels/Conv.cs:11-13) in the reference's order. */

@@ -9,20 +9,37 @@
 
 namespace om {
 
-int32_t gemm_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
-                  const float* B, int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch, int acc);
-bool gemm_tc_batched_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA,
-                               const float* B, int ldb, long long sB, int batch);
-int32_t gemm_tc_batched(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, const float* B,
-                        int ldb, long long sB, float* C, int ldc, long long sC, int batch, int acc, const float* bias);
+int32_t gemm_simt_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA, int64_t iA,
+                        const float* B, int ldb, int64_t sB, int64_t iB, float* C, int ldc, int64_t sC, int64_t iC, int batch,
+                        int inner, int acc);
+bool gemm_tc_heads_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, long long iA,
+                             const float* B, int ldb, long long sB, long long iB, int batch, int inner);
+int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, long long iA,
+                      const float* B, int ldb, long long sB, long long iB, float* C, int ldc, long long sC, long long iC, int batch,
+                      int inner, int acc, const float* bias);
+
+// Where the [l, d] matrix of (batch b, head h) of an activation starts and how its rows are spaced: element strides.
+struct HeadView {
+  const float* p;
+  int64_t batch, head, row;
+};
 
 // One product per (batch, head): on the tensor pipe (TF32) when the context asks for it and the strides allow TMA,
 // else on the fp32 FMA kernel.
-static int32_t head_gemm(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA, const float* B,
-                         int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch) {
-  if (batch > 1 && (ldc & 3) == 0 && (sC & 3) == 0 && gemm_tc_batched_supported(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, batch))
-    return gemm_tc_batched(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, batch, 0, nullptr);
-  return gemm_simt(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, batch, 0);
+static int32_t head_gemm(om_ctx* ctx, int ta, int tb, int m, int n, int k, HeadView A, HeadView B, float* C, HeadView Cv, int bh,
+                         int heads) {
+  if (bh > 1 && (Cv.row & 3) == 0 && (Cv.batch & 3) == 0 && (Cv.head & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+      A.row <= INT32_MAX && B.row <= INT32_MAX &&
+      gemm_tc_heads_supported(ctx, ta, tb, m, n, k, A.p, (int)A.row, A.batch, A.head, B.p, (int)B.row, B.batch, B.head, bh, heads))
+    return gemm_tc_heads(ctx, ta, tb, m, n, k, A.p, (int)A.row, A.batch, A.head, B.p, (int)B.row, B.batch, B.head, C, (int)Cv.row,
+                         Cv.batch, Cv.head, bh, heads, 0, nullptr);
+  return gemm_simt_heads(ctx, ta, tb, m, n, k, A.p, (int)A.row, A.batch, A.head, B.p, (int)B.row, B.batch, B.head, C, (int)Cv.row,
+                         Cv.batch, Cv.head, bh, heads, 0);
+}
+
+static HeadView view_of(const float* p, const om_head_strides* s) { return HeadView{p, s->batch, s->head, s->row}; }
+static HeadView scores_view(const float* p, int heads, int lq, int lk) {
+  return HeadView{p, (int64_t)heads * lq * lk, (int64_t)lq * lk, (int64_t)lk};
 }
 
 __device__ __forceinline__ double att_wsum_d(double v) {
@@ -37,6 +54,9 @@ __device__ __forceinline__ float att_wmax_f(float v) {
 }
 
 // In place over s [BH*Lq, Lk]: p = softmax(s*scale + mask). One warp per row. lse (may be NULL) gets max + log(sum).
+// NP > 0: the row (lk <= 32 * NP) stays in registers between the three sweeps - one read and one write of the scores.
+// NP == 0: any length, the sweeps go through memory. Same arithmetic and summation order in both.
+template <int NP>
 __global__ void __launch_bounds__(256)
 att_softmax_kernel(float* __restrict__ s, const float* __restrict__ mask, int64_t mask_batch_stride, int32_t heads,
                    int32_t lq, int32_t lk, int64_t rows, float scale, float* __restrict__ lse) {
@@ -51,27 +71,53 @@ att_softmax_kernel(float* __restrict__ s, const float* __restrict__ mask, int64_
       int64_t b = r / ((int64_t)lq * heads);
       mr = mask + b * mask_batch_stride + i * lk;
     }
-    float mx = -INFINITY;
-    for (int j = lane; j < lk; j += 32) {
-      float v = (sr[j] * scale) + (mr ? mr[j] : 0.f);
-      sr[j] = v;
-      mx = fmaxf(mx, v);
+    if (NP > 0) {
+      float v[NP > 0 ? NP : 1];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < NP; u++) {
+        int j = lane + 32 * u;
+        v[u] = j < lk ? (sr[j] * scale) + (mr ? mr[j] : 0.f) : -INFINITY;
+        mx = fmaxf(mx, v[u]);
+      }
+      mx = att_wmax_f(mx);
+      // A fully masked row (all -inf) gives exp(nan); keep the reference's behaviour of propagating it.
+      double sum = 0.0;
+#pragma unroll
+      for (int u = 0; u < NP; u++) {
+        if (lane + 32 * u < lk) {
+          v[u] = expf(v[u] - mx);
+          sum += (double)v[u];
+        }
+      }
+      float fs = (float)att_wsum_d(sum);
+#pragma unroll
+      for (int u = 0; u < NP; u++)
+        if (lane + 32 * u < lk) sr[lane + 32 * u] = v[u] / fs;
+      if (lse && lane == 0) lse[r] = mx + logf(fs);
+    } else {
+      float mx = -INFINITY;
+      for (int j = lane; j < lk; j += 32) {
+        float v = (sr[j] * scale) + (mr ? mr[j] : 0.f);
+        sr[j] = v;
+        mx = fmaxf(mx, v);
+      }
+      mx = att_wmax_f(mx);
+      double sum = 0.0;
+      for (int j = lane; j < lk; j += 32) {
+        float e = expf(sr[j] - mx);
+        sr[j] = e;
+        sum += (double)e;
+      }
+      float fs = (float)att_wsum_d(sum);
+      for (int j = lane; j < lk; j += 32) sr[j] = sr[j] / fs;
+      if (lse && lane == 0) lse[r] = mx + logf(fs);
     }
-    mx = att_wmax_f(mx);
-    // A fully masked row (all -inf) gives exp(nan); keep the reference's behaviour of propagating it.
-    double sum = 0.0;
-    for (int j = lane; j < lk; j += 32) {
-      float e = expf(sr[j] - mx);
-      sr[j] = e;
-      sum += (double)e;
-    }
-    float fs = (float)att_wsum_d(sum);
-    for (int j = lane; j < lk; j += 32) sr[j] = sr[j] / fs;
-    if (lse && lane == 0) lse[r] = mx + logf(fs);
   }
 }
 
-// In place over dp: ds = p * (dp - dot) * scale with dot = sum_j dp*p in double.
+// In place over dp: ds = p * (dp - dot) * scale with dot = sum_j dp*p in double. NP as above.
+template <int NP>
 __global__ void __launch_bounds__(256)
 att_ds_kernel(float* __restrict__ dp, const float* __restrict__ p, int32_t lk, int64_t rows, float scale) {
   int lane = threadIdx.x & 31;
@@ -80,11 +126,41 @@ att_ds_kernel(float* __restrict__ dp, const float* __restrict__ p, int32_t lk, i
   for (int64_t r = warp; r < rows; r += warps) {
     float* d = dp + r * lk;
     const float* pr = p + r * lk;
-    double dot = 0.0;
-    for (int j = lane; j < lk; j += 32) dot += (double)(d[j] * pr[j]);
-    float df = (float)att_wsum_d(dot);
-    for (int j = lane; j < lk; j += 32) d[j] = (pr[j] * (d[j] - df)) * scale;
+    if (NP > 0) {
+      float dv[NP > 0 ? NP : 1], pv[NP > 0 ? NP : 1];
+      double dot = 0.0;
+#pragma unroll
+      for (int u = 0; u < NP; u++) {
+        int j = lane + 32 * u;
+        if (j < lk) {
+          dv[u] = d[j];
+          pv[u] = pr[j];
+          dot += (double)(dv[u] * pv[u]);
+        }
+      }
+      float df = (float)att_wsum_d(dot);
+#pragma unroll
+      for (int u = 0; u < NP; u++)
+        if (lane + 32 * u < lk) d[lane + 32 * u] = (pv[u] * (dv[u] - df)) * scale;
+    } else {
+      double dot = 0.0;
+      for (int j = lane; j < lk; j += 32) dot += (double)(d[j] * pr[j]);
+      float df = (float)att_wsum_d(dot);
+      for (int j = lane; j < lk; j += 32) d[j] = (pr[j] * (d[j] - df)) * scale;
+    }
   }
+}
+
+static void launch_att_softmax(om_ctx* ctx, int grid, float* s, const float* mask, int64_t mbs, int h, int lq, int lk, int64_t rows,
+                               float scale, float* lse) {
+  if (lk <= 128) att_softmax_kernel<4><<<grid, 256, 0, ctx->stream>>>(s, mask, mbs, h, lq, lk, rows, scale, lse);
+  else if (lk <= 512) att_softmax_kernel<16><<<grid, 256, 0, ctx->stream>>>(s, mask, mbs, h, lq, lk, rows, scale, lse);
+  else att_softmax_kernel<0><<<grid, 256, 0, ctx->stream>>>(s, mask, mbs, h, lq, lk, rows, scale, lse);
+}
+static void launch_att_ds(om_ctx* ctx, int grid, float* dp, const float* p, int lk, int64_t rows, float scale) {
+  if (lk <= 128) att_ds_kernel<4><<<grid, 256, 0, ctx->stream>>>(dp, p, lk, rows, scale);
+  else if (lk <= 512) att_ds_kernel<16><<<grid, 256, 0, ctx->stream>>>(dp, p, lk, rows, scale);
+  else att_ds_kernel<0><<<grid, 256, 0, ctx->stream>>>(dp, p, lk, rows, scale);
 }
 
 static int32_t check_att(om_ctx* ctx, const char* who, int b, int h, int lq, int lk, int d) {
@@ -94,17 +170,28 @@ static int32_t check_att(om_ctx* ctx, const char* who, int b, int h, int lq, int
   return OM_OK;
 }
 
+static int32_t check_strides(om_ctx* ctx, const char* who, const om_head_strides* s, int d) {
+  if (s == nullptr || s->row < d || s->batch < 0 || s->head < 0 || s->row > INT32_MAX)
+    return fail(ctx, OM_ERR_SHAPE, "%s: rows of an activation must be at least D = %d elements apart and strides non-negative", who, d);
+  return OM_OK;
+}
+
 }  // namespace om
 
 using namespace om;
 
 extern "C" {
 
-int32_t om_attention_fwd(om_ctx* ctx, const float* q, const float* k, const float* v, const float* mask,
-                         int64_t mask_batch_stride, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d, float scale,
-                         float* out, float* lse) {
+int32_t om_attention_fwd_strided(om_ctx* ctx, const float* q, const om_head_strides* qs, const float* k, const om_head_strides* ks,
+                                 const float* v, const om_head_strides* vs, const float* mask, int64_t mask_batch_stride, int32_t b,
+                                 int32_t h, int32_t lq, int32_t lk, int32_t d, float scale, float* out, const om_head_strides* os,
+                                 float* lse) {
   OM_CHECK_CTX(ctx);
   OM_TRY(check_att(ctx, "Attention", b, h, lq, lk, d));
+  OM_TRY(check_strides(ctx, "Attention", qs, d));
+  OM_TRY(check_strides(ctx, "Attention", ks, d));
+  OM_TRY(check_strides(ctx, "Attention", vs, d));
+  OM_TRY(check_strides(ctx, "Attention", os, d));
   int bh = b * h;
   if (bh == 0 || lq == 0) return OM_OK;
   if (lk == 0) return fail(ctx, OM_ERR_SHAPE, "Attention: no keys");
@@ -112,11 +199,12 @@ int32_t om_attention_fwd(om_ctx* ctx, const float* q, const float* k, const floa
   float* s = nullptr;
   int64_t rows = (int64_t)bh * lq;
   OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)rows * lk, false, (void**)&s));
-  int32_t st = head_gemm(ctx, 0, 1, lq, lk, d, q, d, (int64_t)lq * d, k, d, (int64_t)lk * d, s, lk, (int64_t)lq * lk, bh);
+  const HeadView Q = view_of(q, qs), K = view_of(k, ks), V = view_of(v, vs), O = view_of(out, os), S = scores_view(s, h, lq, lk);
+  int32_t st = head_gemm(ctx, 0, 1, lq, lk, d, Q, K, s, S, bh, h);
   if (st == OM_OK) {
     int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 16);
-    att_softmax_kernel<<<grid, 256, 0, ctx->stream>>>(s, mask, mask_batch_stride, h, lq, lk, rows, scale, lse);
-    st = head_gemm(ctx, 0, 0, lq, d, lk, s, lk, (int64_t)lq * lk, v, d, (int64_t)lk * d, out, d, (int64_t)lq * d, bh);
+    launch_att_softmax(ctx, grid, s, mask, mask_batch_stride, h, lq, lk, rows, scale, lse);
+    st = head_gemm(ctx, 0, 0, lq, d, lk, S, V, out, O, bh, h);
   }
   pool_free(ctx, s);
   OM_TRY(st);
@@ -124,12 +212,28 @@ int32_t om_attention_fwd(om_ctx* ctx, const float* q, const float* k, const floa
   return OM_OK;
 }
 
-int32_t om_attention_bwd(om_ctx* ctx, const float* g, const float* q, const float* k, const float* v, const float* mask,
-                         int64_t mask_batch_stride, const float* lse, int32_t b, int32_t h, int32_t lq, int32_t lk,
-                         int32_t d, float scale, float* dq, float* dk, float* dv) {
+int32_t om_attention_fwd(om_ctx* ctx, const float* q, const float* k, const float* v, const float* mask,
+                         int64_t mask_batch_stride, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d, float scale,
+                         float* out, float* lse) {
+  const om_head_strides sq = {(int64_t)h * lq * d, (int64_t)lq * d, d}, sk = {(int64_t)h * lk * d, (int64_t)lk * d, d};
+  return om_attention_fwd_strided(ctx, q, &sq, k, &sk, v, &sk, mask, mask_batch_stride, b, h, lq, lk, d, scale, out, &sq, lse);
+}
+
+int32_t om_attention_bwd_strided(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs,
+                                 const float* k, const om_head_strides* ks, const float* v, const om_head_strides* vs,
+                                 const float* mask, int64_t mask_batch_stride, const float* lse, int32_t b, int32_t h, int32_t lq,
+                                 int32_t lk, int32_t d, float scale, float* dq, const om_head_strides* dqs, float* dk,
+                                 const om_head_strides* dks, float* dv, const om_head_strides* dvs) {
   OM_CHECK_CTX(ctx);
   (void)lse;
   OM_TRY(check_att(ctx, "Attention backward", b, h, lq, lk, d));
+  OM_TRY(check_strides(ctx, "Attention backward", gs, d));
+  OM_TRY(check_strides(ctx, "Attention backward", qs, d));
+  OM_TRY(check_strides(ctx, "Attention backward", ks, d));
+  OM_TRY(check_strides(ctx, "Attention backward", vs, d));
+  if (dq) OM_TRY(check_strides(ctx, "Attention backward", dqs, d));
+  if (dk) OM_TRY(check_strides(ctx, "Attention backward", dks, d));
+  if (dv) OM_TRY(check_strides(ctx, "Attention backward", dvs, d));
   int bh = b * h;
   if (bh == 0 || lq == 0 || lk == 0) return OM_OK;
   ProfileScope prof(ctx, "om_attention_bwd", 8.0 * bh * (double)lq * lk * d, 4.0 * bh * ((double)lq * d * 4 + (double)lk * d * 4));
@@ -141,21 +245,22 @@ int32_t om_attention_bwd(om_ctx* ctx, const float* g, const float* q, const floa
     pool_free(ctx, p);
     return st;
   }
-  const int64_t sq = (int64_t)lq * d, sk = (int64_t)lk * d, ss = (int64_t)lq * lk;
+  const HeadView G = view_of(g, gs), Q = view_of(q, qs), K = view_of(k, ks), V = view_of(v, vs);
+  const HeadView P = scores_view(p, h, lq, lk), DP = scores_view(dp, h, lq, lk);
   int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 16);
-  st = head_gemm(ctx, 0, 1, lq, lk, d, q, d, sq, k, d, sk, p, lk, ss, bh);
+  st = head_gemm(ctx, 0, 1, lq, lk, d, Q, K, p, P, bh, h);
   if (st == OM_OK) {
-    att_softmax_kernel<<<grid, 256, 0, ctx->stream>>>(p, mask, mask_batch_stride, h, lq, lk, rows, scale, nullptr);
+    launch_att_softmax(ctx, grid, p, mask, mask_batch_stride, h, lq, lk, rows, scale, nullptr);
     // dV = P^T dO
-    if (dv) st = head_gemm(ctx, 1, 0, lk, d, lq, p, lk, ss, g, d, sq, dv, d, sk, bh);
+    if (dv) st = head_gemm(ctx, 1, 0, lk, d, lq, P, G, dv, view_of(dv, dvs), bh, h);
   }
   if (st == OM_OK && (dq || dk)) {
     // dP = dO V^T, then dS in place
-    st = head_gemm(ctx, 0, 1, lq, lk, d, g, d, sq, v, d, sk, dp, lk, ss, bh);
+    st = head_gemm(ctx, 0, 1, lq, lk, d, G, V, dp, DP, bh, h);
     if (st == OM_OK) {
-      att_ds_kernel<<<grid, 256, 0, ctx->stream>>>(dp, p, lk, rows, scale);
-      if (dq) st = head_gemm(ctx, 0, 0, lq, d, lk, dp, lk, ss, k, d, sk, dq, d, sq, bh);
-      if (st == OM_OK && dk) st = head_gemm(ctx, 1, 0, lk, d, lq, dp, lk, ss, q, d, sq, dk, d, sk, bh);
+      launch_att_ds(ctx, grid, dp, p, lk, rows, scale);
+      if (dq) st = head_gemm(ctx, 0, 0, lq, d, lk, DP, K, dq, view_of(dq, dqs), bh, h);
+      if (st == OM_OK && dk) st = head_gemm(ctx, 1, 0, lk, d, lq, DP, Q, dk, view_of(dk, dks), bh, h);
     }
   }
   pool_free(ctx, p);
@@ -163,6 +268,14 @@ int32_t om_attention_bwd(om_ctx* ctx, const float* g, const float* q, const floa
   OM_TRY(st);
   OM_LAUNCH_CHECK(ctx, "om_attention_bwd");
   return OM_OK;
+}
+
+int32_t om_attention_bwd(om_ctx* ctx, const float* g, const float* q, const float* k, const float* v, const float* mask,
+                         int64_t mask_batch_stride, const float* lse, int32_t b, int32_t h, int32_t lq, int32_t lk,
+                         int32_t d, float scale, float* dq, float* dk, float* dv) {
+  const om_head_strides sq = {(int64_t)h * lq * d, (int64_t)lq * d, d}, sk = {(int64_t)h * lk * d, (int64_t)lk * d, d};
+  return om_attention_bwd_strided(ctx, g, &sq, q, &sq, k, &sk, v, &sk, mask, mask_batch_stride, lse, b, h, lq, lk, d, scale, dq, &sq,
+                                  dk, &sk, dv, &sk);
 }
 
 }  // extern "C"

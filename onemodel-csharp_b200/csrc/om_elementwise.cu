@@ -298,6 +298,54 @@ __global__ void colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, 
   }
 }
 
+// Stage 1 for rows that are 16-byte aligned (ld a multiple of four, aligned base): the same sums in the same order as
+// colsum_stage1_kernel - per column eight row lanes over rows lane, lane + 8, ... of the chunk in double, lanes then
+// combined in lane order - but each thread owns four adjacent columns (one 16-byte load per row) and keeps eight rows
+// in flight. A CTA is 8 column groups x 8 row lanes and covers 32 columns of one chunk.
+__global__ void __launch_bounds__(64)
+colsum_stage1_vec4_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial) {
+  __shared__ double sm[8][33];
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const int col = blockIdx.x * 32 + tx * 4;
+  const int r0 = blockIdx.y * kColsumRowsPerChunk;
+  const int r1 = min(rows, r0 + kColsumRowsPerChunk);
+  double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+  if (col + 3 < cols) {
+    int r = r0 + ty;
+    for (; r + 56 < r1; r += 64) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) v[u] = __ldg(reinterpret_cast<const float4*>(g + (int64_t)(r + 8 * u) * ld + col));
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        a0 += (double)v[u].x; a1 += (double)v[u].y; a2 += (double)v[u].z; a3 += (double)v[u].w;
+      }
+    }
+    for (; r < r1; r += 8) {
+      float4 v = __ldg(reinterpret_cast<const float4*>(g + (int64_t)r * ld + col));
+      a0 += (double)v.x; a1 += (double)v.y; a2 += (double)v.z; a3 += (double)v.w;
+    }
+  } else if (col < cols) {
+    for (int r = r0 + ty; r < r1; r += 8) {
+      const float* row = g + (int64_t)r * ld + col;
+      a0 += (double)row[0];
+      if (col + 1 < cols) a1 += (double)row[1];
+      if (col + 2 < cols) a2 += (double)row[2];
+    }
+  }
+  sm[ty][tx * 4 + 0] = a0; sm[ty][tx * 4 + 1] = a1; sm[ty][tx * 4 + 2] = a2; sm[ty][tx * 4 + 3] = a3;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    if (c < cols) {
+      double t = 0.0;
+#pragma unroll
+      for (int l = 0; l < 8; l++) t += sm[l][threadIdx.x];
+      partial[(int64_t)blockIdx.y * cols + c] = t;
+    }
+  }
+}
+
 __global__ void colsum_stage2_kernel(const double* __restrict__ partial, int32_t chunks, int32_t cols,
                                      float* __restrict__ out, int accumulate) {
   int col = blockIdx.x * blockDim.x + threadIdx.x;
@@ -419,7 +467,10 @@ int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64
   double* partial = nullptr;
   OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&partial));
   dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)chunks);
-  colsum_stage1_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(g, rows, cols, ld, partial);
+  if ((ld & 3) == 0 && aligned16(g))
+    colsum_stage1_vec4_kernel<<<grid, 64, 0, ctx->stream>>>(g, rows, cols, ld, partial);
+  else
+    colsum_stage1_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(g, rows, cols, ld, partial);
   colsum_stage2_kernel<<<(unsigned)ceil_div(cols, 128), 128, 0, ctx->stream>>>(partial, chunks, cols, out, accumulate);
   pool_free(ctx, partial);
   OM_LAUNCH_CHECK(ctx, "om_colsum");

@@ -11,7 +11,8 @@ template <int BM, int BN, int BK, int TM, int TN, bool TA, bool TB>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(int m, int n, int k, const float* __restrict__ A, int lda, int64_t strideA,
                  const float* __restrict__ B, int ldb, int64_t strideB, float* __restrict__ C, int ldc,
-                 int64_t strideC, int accumulate, int batch, int batch_per_z) {
+                 int64_t strideC, int accumulate, int batch, int batch_per_z, int inner, int64_t innerA, int64_t innerB,
+                 int64_t innerC) {
   constexpr int THREADS = (BM / TM) * (BN / TN);
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
@@ -21,7 +22,9 @@ gemm_simt_kernel(int m, int n, int k, const float* __restrict__ A, int lda, int6
   const int z1 = batch_per_z ? min(batch, z0 + batch_per_z) : z0 + 1;
   const float* A0 = A;
   const float* B0 = B;
-  C += blockIdx.z * strideC;
+  // Matrix z of an operand starts (z / inner) * stride + (z % inner) * innerStride elements in: inner == 1 is the plain
+  // strided batch, inner == heads addresses [batch, length, heads, d] activations per (batch, head) without a copy.
+  C += (blockIdx.z / inner) * strideC + (blockIdx.z % inner) * innerC;
   const int tid = threadIdx.x;
   const int tx = tid % (BN / TN), ty = tid / (BN / TN);
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -32,8 +35,8 @@ gemm_simt_kernel(int m, int n, int k, const float* __restrict__ A, int lda, int6
     for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
 
   for (int z = z0; z < z1; z++) {
-  A = A0 + z * strideA;
-  B = B0 + z * strideB;
+  A = A0 + (z / inner) * strideA + (z % inner) * innerA;
+  B = B0 + (z / inner) * strideB + (z % inner) * innerB;
   for (int k0 = 0; k0 < k; k0 += BK) {
     // A tile -> As[kk][mm]
     if (TA) {
@@ -115,26 +118,34 @@ gemm_simt_kernel(int m, int n, int k, const float* __restrict__ A, int lda, int6
 
 template <int BM, int BN, int BK, int TM, int TN>
 static void launch_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
-                        const float* B, int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch, int acc, int bpz = 0) {
+                        const float* B, int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch, int acc, int bpz = 0,
+                        int inner = 1, int64_t iA = 0, int64_t iB = 0, int64_t iC = 0) {
   dim3 grid((unsigned)ceil_div(n, BN), (unsigned)ceil_div(m, BM), (unsigned)(bpz ? ceil_div(batch, bpz) : batch));
   constexpr int T = (BM / TM) * (BN / TN);
-  if (!ta && !tb) gemm_simt_kernel<BM, BN, BK, TM, TN, false, false><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz);
-  else if (!ta && tb) gemm_simt_kernel<BM, BN, BK, TM, TN, false, true><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz);
-  else if (ta && !tb) gemm_simt_kernel<BM, BN, BK, TM, TN, true, false><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz);
-  else gemm_simt_kernel<BM, BN, BK, TM, TN, true, true><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz);
+  if (!ta && !tb) gemm_simt_kernel<BM, BN, BK, TM, TN, false, false><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz, inner, iA, iB, iC);
+  else if (!ta && tb) gemm_simt_kernel<BM, BN, BK, TM, TN, false, true><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz, inner, iA, iB, iC);
+  else if (ta && !tb) gemm_simt_kernel<BM, BN, BK, TM, TN, true, false><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz, inner, iA, iB, iC);
+  else gemm_simt_kernel<BM, BN, BK, TM, TN, true, true><<<grid, T, 0, ctx->stream>>>(m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, acc, batch, bpz, inner, iA, iB, iC);
+}
+
+int32_t gemm_simt_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA, int64_t iA,
+                        const float* B, int ldb, int64_t sB, int64_t iB, float* C, int ldc, int64_t sC, int64_t iC, int batch,
+                        int inner, int acc) {
+  if (m == 0 || n == 0 || batch == 0) return OM_OK;
+  if (inner < 1) inner = 1;
+  int64_t tiles128 = ceil_div(m, 128) * ceil_div(n, 128) * batch;
+  if (tiles128 >= ctx->sm_count) {
+    launch_simt<128, 128, 16, 8, 8>(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, batch, acc, 0, inner, iA, iB, iC);
+  } else {
+    launch_simt<64, 64, 16, 4, 4>(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, batch, acc, 0, inner, iA, iB, iC);
+  }
+  OM_LAUNCH_CHECK(ctx, "gemm_simt");
+  return OM_OK;
 }
 
 int32_t gemm_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
                   const float* B, int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch, int acc) {
-  if (m == 0 || n == 0 || batch == 0) return OM_OK;
-  int64_t tiles128 = ceil_div(m, 128) * ceil_div(n, 128) * batch;
-  if (tiles128 >= ctx->sm_count) {
-    launch_simt<128, 128, 16, 8, 8>(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, batch, acc);
-  } else {
-    launch_simt<64, 64, 16, 4, 4>(ctx, ta, tb, m, n, k, A, lda, sA, B, ldb, sB, C, ldc, sC, batch, acc);
-  }
-  OM_LAUNCH_CHECK(ctx, "gemm_simt");
-  return OM_OK;
+  return gemm_simt_heads(ctx, ta, tb, m, n, k, A, lda, sA, 0, B, ldb, sB, 0, C, ldc, sC, 0, batch, 1, acc);
 }
 
 // Sums the products of `batch` matrix pairs in chunks of batch_per_chunk: partial[c] = sum over the chunk's matrices

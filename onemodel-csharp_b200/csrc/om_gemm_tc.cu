@@ -42,7 +42,9 @@ struct TcParams {
   const float* bias;    // only when splits == 1
   int32_t* status;
   int batched;          // blockIdx.z is a matrix of a strided batch (then splits == 1)
-  long long stride_c;   // elements between the C matrices of a batch
+  int inner;            // matrix z sits at outer index z / inner, inner index z % inner (1 = plain strided batch)
+  long long stride_c;   // elements between the C matrices of consecutive outer indices
+  long long inner_c;    // ... and of consecutive inner indices
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------------------
@@ -80,11 +82,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
-// Tile load through a rank-3 tensor map (inner, outer, matrix of the batch).
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+// Tile load through a rank-4 tensor map (contiguous index, row index, inner batch index, outer batch index).
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
       : "memory");
 }
 
@@ -167,6 +169,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int split = p.batched ? 0 : blockIdx.z;
   const int zb = p.batched ? blockIdx.z : 0;
+  const int zo = zb / p.inner, zi = zb % p.inner;
   const int k_begin = split * p.k_per_split;
   const int k_end = min(p.k, k_begin + p.k_per_split);
   const int k_blocks = (k_end - k_begin + BK - 1) / BK;
@@ -202,15 +205,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_expect_tx(&full[s], STAGE_BYTES);
         if (A_MN) {
 #pragma unroll
-          for (int j = 0; j < BM / 32; j++) tma_load_3d(a_dst + j * (BK * 128), &map_a, m0 + 32 * j, k0, zb, &full[s]);
+          for (int j = 0; j < BM / 32; j++) tma_load_4d(a_dst + j * (BK * 128), &map_a, m0 + 32 * j, k0, zi, zo, &full[s]);
         } else {
-          tma_load_3d(a_dst, &map_a, k0, m0, zb, &full[s]);
+          tma_load_4d(a_dst, &map_a, k0, m0, zi, zo, &full[s]);
         }
         if (B_MN) {
 #pragma unroll
-          for (int j = 0; j < BN / 32; j++) tma_load_3d(b_dst + j * (BK * 128), &map_b, n0 + 32 * j, k0, zb, &full[s]);
+          for (int j = 0; j < BN / 32; j++) tma_load_4d(b_dst + j * (BK * 128), &map_b, n0 + 32 * j, k0, zi, zo, &full[s]);
         } else {
-          tma_load_3d(b_dst, &map_b, k0, n0, zb, &full[s]);
+          tma_load_4d(b_dst, &map_b, k0, n0, zi, zo, &full[s]);
         }
       }
     }
@@ -240,15 +243,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else {
     // ---- epilogue: warps 2..5 own TMEM lane quadrants (warp % 4) ----
+    // tcgen05.ld hands lane l the 32 columns of accumulator row l. Storing from there would make every warp store touch
+    // 32 different rows (16 bytes each); instead each 32 x 32 block is turned through shared memory (the operand stages are
+    // dead once acc_full has fired) so that eight lanes cover one 128-byte row segment and a warp store writes four full
+    // row segments.
     const int quad = warp & 3;
-    const int row = m0 + quad * 32 + lane;
     bool ok = true;
     if (k_blocks > 0) ok = mbar_wait(acc_full, 0, abort_flag, p.status, 3);
     tc_fence_after();
-    float* c = p.c + (size_t)split * p.m * p.ldc + (size_t)zb * p.stride_c;
-    if (ok) {
+    float* c = p.c + (size_t)split * p.m * p.ldc + (size_t)zo * p.stride_c + (size_t)zi * p.inner_c;
+    constexpr int STG_LD = 36;                                   // floats per staged row: 144 bytes keeps float4 alignment and
+    float* stg = reinterpret_cast<float*>(smem) + quad * 32 * STG_LD;   // spreads the eight rows of a phase over all banks
+    const int row_base = m0 + quad * 32;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && ((p.ldc & 3) == 0);
+    if (ok && row_base < p.m) {
 #pragma unroll 1
       for (int cb = 0; cb < BN / 32; cb++) {
+        const int col0 = n0 + cb * 32;
+        if (col0 >= p.n) break;
         uint32_t r[32];
         if (k_blocks > 0) {
           tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
@@ -257,32 +269,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; j++) r[j] = 0u;
         }
-        const int col0 = n0 + cb * 32;
-        if (row < p.m && col0 < p.n) {
-          float* crow = c + (size_t)row * p.ldc + col0;
-          const bool vec = col0 + 32 <= p.n && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
-          if (vec) {
+        __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              if (p.bias) {
-                v.x += p.bias[col0 + j]; v.y += p.bias[col0 + j + 1]; v.z += p.bias[col0 + j + 2]; v.w += p.bias[col0 + j + 3];
-              }
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(stg + lane * STG_LD + j) =
+              make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        __syncwarp();
+        if (aligned && col0 + 32 <= p.n) {
+          const int cc = (lane & 7) * 4;                         // this lane's four columns of the block
+          float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (p.bias) bv = *reinterpret_cast<const float4*>(p.bias + col0 + cc);
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const int rr = i * 4 + (lane >> 3);
+            const int row = row_base + rr;
+            if (row < p.m) {
+              float4 v = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cc);
+              if (p.bias) { v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w; }
+              float4* dst = reinterpret_cast<float4*>(c + (size_t)row * p.ldc + col0 + cc);
               if (p.accumulate) {
-                float4 o = *reinterpret_cast<float4*>(crow + j);
+                float4 o = *dst;
                 v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
               }
-              *reinterpret_cast<float4*>(crow + j) = v;
+              *dst = v;
             }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-              if (col0 + j < p.n) {
-                float v = __uint_as_float(r[j]);
-                if (p.bias) v += p.bias[col0 + j];
-                if (p.accumulate) v += crow[j];
-                crow[j] = v;
-              }
+          }
+        } else {
+          // Ragged right edge or an unaligned C: lane l owns column l of the block, one row per step.
+          const int col = col0 + lane;
+          if (col < p.n) {
+            const float bvs = p.bias ? p.bias[col] : 0.f;
+            for (int rr = 0; rr < 32; rr++) {
+              const int row = row_base + rr;
+              if (row >= p.m) break;
+              float v = stg[rr * STG_LD + lane];
+              if (p.bias) v += bvs;
+              float* dst = c + (size_t)row * p.ldc + col;
+              if (p.accumulate) v += *dst;
+              *dst = v;
             }
           }
         }
@@ -331,18 +355,23 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// A rank-2 fp32 tensor map over a row-major matrix [outer, inner] with leading dimension ld, box [box_outer, 32].
+// A rank-4 fp32 tensor map over row-major matrices [outer, inner] with leading dimension ld, box [box_outer, 32]:
+// dimension 2 walks the `inner_count` matrices that lie inner_stride elements apart, dimension 3 the `outer_count`
+// groups outer_stride apart (a plain matrix has both counts 1; a strided batch has inner_count 1; activations laid out
+// [batch, length, heads, d] are addressed per (batch, head) with inner = heads). Strides need not be ordered.
 // K-major tiles use the 16-byte-unit 128B swizzle, MN-major tiles the 32-byte-unit one. The TFLOAT32 element type makes
-// TMA round each value to TF32 (nearest) on the way in; the tensor core would otherwise truncate the low 13 bits.
+// TMA round each value to TF32 (nearest even) on the way in; the tensor core would otherwise truncate the low 13 bits.
 static bool make_map(CUtensorMap* map, const float* base, int inner, int outer, int ld, int box_outer, bool mn_major,
-                     int batch = 1, long long batch_stride = 0) {
-  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)batch};
-  cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)(batch > 1 ? batch_stride : (long long)ld * outer) * 4};
-  if (strides[1] < 16) strides[1] = 16;
-  strides[1] = (strides[1] + 15) & ~(cuuint64_t)15;   // only read when batch > 1, where the caller guarantees alignment
-  cuuint32_t box[3] = {32, (cuuint32_t)box_outer, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                     int outer_count = 1, long long outer_stride = 0, int inner_count = 1, long long inner_stride = 0) {
+  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)inner_count, (cuuint64_t)outer_count};
+  // Strides of dimensions of extent 1 are never used for addressing but must still be multiples of 16 bytes.
+  cuuint64_t fallback = (((cuuint64_t)ld * outer * 4) + 15) & ~(cuuint64_t)15;
+  if (fallback < 16) fallback = 16;
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 4, inner_count > 1 ? (cuuint64_t)inner_stride * 4 : fallback,
+                           outer_count > 1 ? (cuuint64_t)outer_stride * 4 : fallback};
+  cuuint32_t box[4] = {32, (cuuint32_t)box_outer, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -368,24 +397,42 @@ int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A
   return gemm_tc_batched(ctx, ta, tb, m, n, k, A, lda, 0, B, ldb, 0, C, ldc, 0, 1, acc, bias);
 }
 
-// Strided batch: matrix z of A, B, C starts sA, sB, sC elements after matrix z - 1 (0 shares an operand). The batch
-// rides on blockIdx.z, so a batched product never splits k.
-bool gemm_tc_batched_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA,
-                               const float* B, int ldb, long long sB, int batch) {
+// Batched products. Matrix z of an operand starts (z / inner) * s + (z % inner) * i elements in: inner == 1 is the
+// plain strided batch (stride s), inner == heads addresses [batch, length, heads, d] activations per (batch, head)
+// in place. The batch rides on blockIdx.z, so a batched product never splits k.
+bool gemm_tc_heads_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, long long iA,
+                             const float* B, int ldb, long long sB, long long iB, int batch, int inner) {
   if (!gemm_tc_supported(ctx, ta, tb, m, n, k, A, lda, B, ldb, nullptr, 0)) return false;
-  if (batch < 1 || batch > 65535) return false;
-  if (batch > 1 && ((sA & 3) || (sB & 3) || sA <= 0 || sB <= 0)) return false;
+  if (batch < 1 || batch > 65535 || inner < 1 || batch % inner != 0) return false;
+  if (batch / inner > 1 && ((sA & 3) || (sB & 3) || sA <= 0 || sB <= 0)) return false;
+  if (inner > 1 && ((iA & 3) || (iB & 3) || iA <= 0 || iB <= 0)) return false;
   return true;
 }
 
+bool gemm_tc_batched_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA,
+                               const float* B, int ldb, long long sB, int batch) {
+  return gemm_tc_heads_supported(ctx, ta, tb, m, n, k, A, lda, sA, 0, B, ldb, sB, 0, batch, 1);
+}
+
+int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, long long iA,
+                      const float* B, int ldb, long long sB, long long iB, float* C, int ldc, long long sC, long long iC, int batch,
+                      int inner, int acc, const float* bias);
+
 int32_t gemm_tc_batched(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, const float* B,
                         int ldb, long long sB, float* C, int ldc, long long sC, int batch, int acc, const float* bias) {
+  return gemm_tc_heads(ctx, ta, tb, m, n, k, A, lda, sA, 0, B, ldb, sB, 0, C, ldc, sC, 0, batch, 1, acc, bias);
+}
+
+int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, long long iA,
+                      const float* B, int ldb, long long sB, long long iB, float* C, int ldc, long long sC, long long iC, int batch,
+                      int inner, int acc, const float* bias) {
   // op(A) is [m, k]. ta == 0: stored [m, k] (K-major tile, map inner = k). ta != 0: stored [k, m] (MN-major, inner = m).
   // op(B) is [k, n]. tb != 0: stored [n, k] (K-major, inner = k). tb == 0: stored [k, n] (MN-major, inner = n).
   const bool a_mn = ta != 0, b_mn = tb == 0;
+  const int outer = batch / inner;
   CUtensorMap map_a, map_b;
-  bool ok = a_mn ? make_map(&map_a, A, m, k, lda, BK, true, batch, sA) : make_map(&map_a, A, k, m, lda, BM, false, batch, sA);
-  ok = ok && (b_mn ? make_map(&map_b, B, n, k, ldb, BK, true, batch, sB) : make_map(&map_b, B, k, n, ldb, BN, false, batch, sB));
+  bool ok = a_mn ? make_map(&map_a, A, m, k, lda, BK, true, outer, sA, inner, iA) : make_map(&map_a, A, k, m, lda, BM, false, outer, sA, inner, iA);
+  ok = ok && (b_mn ? make_map(&map_b, B, n, k, ldb, BK, true, outer, sB, inner, iB) : make_map(&map_b, B, k, n, ldb, BN, false, outer, sB, inner, iB));
   if (!ok) return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed (m %d n %d k %d lda %d ldb %d)", m, n, k, lda, ldb);
 
   const int tiles = (int)(ceil_div(m, BM) * ceil_div(n, BN));
@@ -407,7 +454,9 @@ int32_t gemm_tc_batched(om_ctx* ctx, int ta, int tb, int m, int n, int k, const 
   p.splits = splits;
   p.status = ctx->status_dev;
   p.batched = batch > 1;
+  p.inner = inner;
   p.stride_c = sC;
+  p.inner_c = iC;
   float* workspace = nullptr;
   if (splits > 1) {
     OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)splits * m * n, false, (void**)&workspace));

@@ -131,20 +131,38 @@ layernorm_bwd_kernel(const float* __restrict__ g, const float* __restrict__ x, c
   }
 }
 
-__global__ void column_partials_finish_kernel(const double* __restrict__ pa, const double* __restrict__ pb, int chunks,
-                                              int32_t cols, float* __restrict__ oa, float* __restrict__ ob,
-                                              int accumulate) {
-  int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= cols) return;
-  if (pa && oa) {
-    double t = 0.0;
-    for (int c = 0; c < chunks; c++) t += pa[(int64_t)c * cols + j];
-    oa[j] = accumulate ? oa[j] + (float)t : (float)t;
+// out[j] = sum over chunks of partial[chunk, j] for one or two tables of double partials. A CTA owns 32 columns; 16
+// chunk lanes each add chunks lane, lane + 16, ... in increasing order, then the lane sums are added in lane order: a
+// fixed order, so the result does not depend on the launch.
+__global__ void __launch_bounds__(512)
+column_partials_finish_kernel(const double* __restrict__ pa, const double* __restrict__ pb, int chunks, int32_t cols,
+                              float* __restrict__ oa, float* __restrict__ ob, int accumulate) {
+  __shared__ double sa[16][33], sb[16][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + tx;
+  double ta = 0.0, tb = 0.0;
+  if (j < cols) {
+    if (pa && oa)
+      for (int c = ty; c < chunks; c += 16) ta += pa[(int64_t)c * cols + j];
+    if (pb && ob)
+      for (int c = ty; c < chunks; c += 16) tb += pb[(int64_t)c * cols + j];
   }
-  if (pb && ob) {
-    double t = 0.0;
-    for (int c = 0; c < chunks; c++) t += pb[(int64_t)c * cols + j];
-    ob[j] = accumulate ? ob[j] + (float)t : (float)t;
+  sa[ty][tx] = ta;
+  sb[ty][tx] = tb;
+  __syncthreads();
+  if (ty == 0 && j < cols) {
+    if (pa && oa) {
+      double t = 0.0;
+#pragma unroll
+      for (int l = 0; l < 16; l++) t += sa[l][tx];
+      oa[j] = accumulate ? oa[j] + (float)t : (float)t;
+    }
+    if (pb && ob) {
+      double t = 0.0;
+#pragma unroll
+      for (int l = 0; l < 16; l++) t += sb[l][tx];
+      ob[j] = accumulate ? ob[j] + (float)t : (float)t;
+    }
   }
 }
 
@@ -313,7 +331,7 @@ int32_t om_layernorm_bwd(om_ctx* ctx, const float* g, const float* x, const floa
   else OM_LN_BWD(32);
 #undef OM_LN_BWD
   if (dgamma || dbeta)
-    column_partials_finish_kernel<<<(unsigned)ceil_div(cols, 128), 128, 0, ctx->stream>>>(pg, pb, chunks, cols, dgamma, dbeta, accumulate_params);
+    column_partials_finish_kernel<<<(unsigned)ceil_div(cols, 32), 512, 0, ctx->stream>>>(pg, pb, chunks, cols, dgamma, dbeta, accumulate_params);
   if (pg) pool_free(ctx, pg);
   if (pb) pool_free(ctx, pb);
   OM_LAUNCH_CHECK(ctx, "om_layernorm_bwd");
@@ -376,7 +394,7 @@ int32_t om_batchnorm_bwd(om_ctx* ctx, const float* g, const float* x, const floa
         g, x, gamma, mean, inv, pa, pb, slices, (double)n * plane, planes, c, plane, training, dx);
   }
   if (dgamma || dbeta)
-    column_partials_finish_kernel<<<(unsigned)ceil_div(c, 128), 128, 0, ctx->stream>>>(pa, pb, slices, c, dgamma, dbeta, accumulate_params);
+    column_partials_finish_kernel<<<(unsigned)ceil_div(c, 32), 512, 0, ctx->stream>>>(pa, pb, slices, c, dgamma, dbeta, accumulate_params);
   pool_free(ctx, pa);
   pool_free(ctx, pb);
   OM_LAUNCH_CHECK(ctx, "om_batchnorm_bwd");

@@ -257,7 +257,31 @@ static void EmbeddingBackward(BackwardRecord& r, const Tensor& g) {
   if (leaf) Engine::LeafWritten(r, 0); else Engine::Emit(r, 0, tmp, true);
 }
 
+// The record of Ops::AttentionHeads (Ints = {maskStride, heads}): activations [B, L, H*D], possibly row-pitched.
+static void AttentionHeadsBackward(BackwardRecord& r, const Tensor& g) {
+  const Tensor &q = r.Saved(0), &k = r.Saved(1), &v = r.Saved(2), &mask = r.Saved(3);
+  int heads = (int)r.Ints[1];
+  int b = q.GetShape()[0], lq = q.GetShape()[1], lk = k.GetShape()[1], d = q.GetShape()[2] / heads;
+  Tensor gc = g.Contiguous();
+  Tensor dq, dk, dv;
+  if (r.NeedsInputGrad(0)) dq = Tensor::Create(DType::F32, q.GetShape());
+  if (r.NeedsInputGrad(1)) dk = Tensor::Create(DType::F32, k.GetShape());
+  if (r.NeedsInputGrad(2)) dv = Tensor::Create(DType::F32, v.GetShape());
+  auto strides = [&](const Tensor& t) { return om_head_strides{t.Strides()[0], (int64_t)d, t.Strides()[1]}; };
+  om_head_strides gs = strides(gc), qs = strides(q), ks = strides(k), vs = strides(v), dqs{}, dks{}, dvs{};
+  if (!dq.IsEmpty()) dqs = strides(dq);
+  if (!dk.IsEmpty()) dks = strides(dk);
+  if (!dv.IsEmpty()) dvs = strides(dv);
+  Check(om_attention_bwd_strided(C(), gc.Data(), &gs, q.Data(), &qs, k.Data(), &ks, v.Data(), &vs, mask.IsEmpty() ? nullptr : mask.Data(),
+                                 r.Ints[0], nullptr, b, heads, lq, lk, d, (float)r.Floats[0], dq.IsEmpty() ? nullptr : dq.Data(), &dqs,
+                                 dk.IsEmpty() ? nullptr : dk.Data(), &dks, dv.IsEmpty() ? nullptr : dv.Data(), &dvs));
+  if (!dq.IsEmpty()) Engine::Emit(r, 0, dq, true);
+  if (!dk.IsEmpty()) Engine::Emit(r, 1, dk, true);
+  if (!dv.IsEmpty()) Engine::Emit(r, 2, dv, true);
+}
+
 static void AttentionBackward(BackwardRecord& r, const Tensor& g) {
+  if (r.Ints.size() > 1) return AttentionHeadsBackward(r, g);
   const Tensor &q = r.Saved(0), &k = r.Saved(1), &v = r.Saved(2), &mask = r.Saved(3);
   int b = q.GetShape()[0], h = q.GetShape()[1], lq = q.GetShape()[2], d = q.GetShape()[3], lk = k.GetShape()[2];
   Tensor gc = g.Contiguous();

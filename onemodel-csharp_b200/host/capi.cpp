@@ -175,6 +175,7 @@ OMH_API int32_t omh_call(const char* op, int32_t n_in, omh_tensor* const* in, in
     else if (name == "cross_entropy") r = Ops::CrossEntropy(T(0), T(1), I(0, 1) != 0, (int)I(1, -100), (float)F(0, 0));
     else if (name == "linear") r = Ops::Linear(T(0), T(1), T(2));
     else if (name == "attention") r = Ops::Attention(T(0), T(1), T(2), T(3), (float)F(0, 0));
+    else if (name == "attention_heads") r = Ops::AttentionHeads(T(0), T(1), T(2), (int)I(0, 1), T(3), (float)F(0, 0));
     else if (name == "concat") {
       std::vector<Tensor> xs;
       for (int i = 0; i < n_in; i++) xs.push_back(T(i));

@@ -97,12 +97,9 @@ MultiHeadAttention::MultiHeadAttention(int width, int heads, Generator& g) : Hea
 
 Tensor MultiHeadAttention::Forward(const Tensor& input, const Tensor& mask) {
   if (input.Rank() != 3) throw TensorShapeException("MultiHeadAttention needs [batch, length, width], not " + input.GetShape().ToString() + ".");
-  int b = input.GetShape()[0], n = input.GetShape()[1], d = input.GetShape()[2], dh = d / Heads;
-  auto split = [&](const Tensor& z) { return z.Reshape(Shape{b, n, Heads, dh}).Permute({0, 2, 1, 3}); };
-  Tensor q = split(Q->Forward(input));
-  Tensor k = split(K->Forward(input));
-  Tensor v = split(V->Forward(input));
-  Tensor a = Ops::Attention(q, k, v, mask).Permute({0, 2, 1, 3}).Reshape(Shape{b, n, d});
+  // The head split and merge (Reshape + Permute(0, 2, 1, 3) around Ops.Attention in the reference) are folded into the
+  // attention kernels' addressing: q, k, v stay [batch, length, width] and so does the result.
+  Tensor a = Ops::AttentionHeads(Q->Forward(input), K->Forward(input), V->Forward(input), Heads, mask);
   return O->Forward(a);
 }
 

@@ -261,6 +261,7 @@ struct Ops {
                              float denominator = 0.f);
   static Tensor Linear(const Tensor& x, const Tensor& weight, const Tensor& bias);
   static Tensor Attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& mask, float scale = 0.f);
+  static Tensor AttentionHeads(const Tensor& q, const Tensor& k, const Tensor& v, int heads, const Tensor& mask, float scale = 0.f);
   // One LSTM layer direction: returns y [T,B,H]; hn/cn receive the final states when not null.
   static Tensor LstmLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, const Tensor& bIh, const Tensor& bHh,
                           bool reverse, Tensor* hn = nullptr, Tensor* cn = nullptr);

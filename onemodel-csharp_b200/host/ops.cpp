@@ -274,13 +274,15 @@ Tensor Ops::CrossEntropy(const Tensor& logits, const Tensor& targets, bool mean,
     throw TensorShapeException("CrossEntropy needs [N, C] logits and [N] Int32 or Int64 targets, not " +
                                logits.GetShape().ToString() + " and " + targets.GetShape().ToString() + ".");
   int rows = logits.GetShape()[0], cols = logits.GetShape()[1];
-  Tensor lc = logits.Contiguous();
   Tensor tc = targets.IsContiguous() ? targets : targets.Clone();
   // Row-pitched logits (see Ops::Linear) are read in place; logp and the gradient keep the same pitch.
   int ld = cols;
+  Tensor lc;
   if (rows > 1 && logits.Strides()[1] == 1 && logits.Strides()[0] > cols) {
     lc = logits;
     ld = (int)logits.Strides()[0];
+  } else {
+    lc = logits.Contiguous();
   }
   Tensor logp = ld == cols ? Tensor::Create(DType::F32, logits.GetShape())
                            : Tensor::Create(DType::F32, Shape{rows, ld}).View(logits.GetShape(), {(int64_t)ld, 1}, 0);
@@ -351,6 +353,55 @@ Tensor Ops::Attention(const Tensor& q, const Tensor& k, const Tensor& v, const T
   if (!mc.IsEmpty()) rec->Save(3, mc);
   rec->Floats = {scale};
   rec->Ints = {maskStride};
+  return rec->Attach(r);
+}
+
+// Row-pitched [B, L, D] activation (innermost stride 1, row stride >= D) usable in place, else a contiguous clone.
+static Tensor HeadsOperand(const Tensor& t) {
+  const auto& st = t.Strides();
+  if (t.GetShape()[2] > 0 && st[2] == 1 && st[1] >= t.GetShape()[2] && st[0] >= 0) return t;
+  return t.Contiguous();
+}
+static om_head_strides HeadStridesOf(const Tensor& t, int dh) { return om_head_strides{t.Strides()[0], (int64_t)dh, t.Strides()[1]}; }
+
+// Attention over activations that are still [batch, length, heads * d]: the Reshape + Permute(0, 2, 1, 3) pairs that
+// MultiHeadAttention.Forward (Layers.cs:503-520 of the reference) wraps around Ops.Attention are folded into the
+// kernels' addressing, forward and backward, so the four head-split copies and their four inverse copies per layer
+// disappear. Same arithmetic per (batch, head) as Ops::Attention.
+Tensor Ops::AttentionHeads(const Tensor& q, const Tensor& k, const Tensor& v, int heads, const Tensor& mask, float scale) {
+  if (q.Rank() != 3 || k.Rank() != 3 || v.Rank() != 3 || k.GetShape() != v.GetShape() || q.GetShape()[0] != k.GetShape()[0] ||
+      q.GetShape()[2] != k.GetShape()[2] || heads < 1 || q.GetShape()[2] % heads != 0 || (q.GetShape()[2] / heads) % 2 != 0)
+    throw TensorShapeException("Attention over heads needs [B,L,H*D] tensors with matching batch and width and even D, not " +
+                               q.GetShape().ToString() + ", " + k.GetShape().ToString() + ", " + v.GetShape().ToString() + ".");
+  RequireFloat32(q);
+  RequireFloat32(k);
+  RequireFloat32(v);
+  int b = q.GetShape()[0], lq = q.GetShape()[1], lk = k.GetShape()[1], width = q.GetShape()[2], d = width / heads;
+  int64_t maskStride = 0;
+  Tensor mc;
+  if (!mask.IsEmpty()) {
+    RequireFloat32(mask);
+    bool ok = (mask.Rank() == 2 && mask.GetShape()[0] == lq && mask.GetShape()[1] == lk) ||
+              (mask.Rank() == 3 && mask.GetShape()[0] == b && mask.GetShape()[1] == lq && mask.GetShape()[2] == lk);
+    if (!ok) throw TensorShapeException("The mask must be [" + std::to_string(lq) + "," + std::to_string(lk) + "] or [" +
+                                        std::to_string(b) + "," + std::to_string(lq) + "," + std::to_string(lk) + "], not " + mask.GetShape().ToString() + ".");
+    mc = mask.Contiguous().Detach();
+    maskStride = mask.Rank() == 2 ? 0 : (int64_t)lq * lk;
+  }
+  if (scale == 0.f || isnan(scale)) scale = 1.0f / sqrtf((float)d);
+  Tensor qc = HeadsOperand(q), kc = HeadsOperand(k), vc = HeadsOperand(v);
+  Tensor r = NewOut(q.GetShape());
+  om_head_strides qs = HeadStridesOf(qc, d), ks = HeadStridesOf(kc, d), vs = HeadStridesOf(vc, d), os = HeadStridesOf(r, d);
+  Check(om_attention_fwd_strided(C(), qc.Data(), &qs, kc.Data(), &ks, vc.Data(), &vs, mc.IsEmpty() ? nullptr : mc.Data(), maskStride,
+                                 b, heads, lq, lk, d, scale, r.Data(), &os, nullptr));
+  if (!Recording({&q, &k, &v})) return r;
+  auto rec = BackwardRecord::Create(OpKind::Attention, 4, {&q, &k, &v});
+  rec->Save(0, qc.Detach());
+  rec->Save(1, kc.Detach());
+  rec->Save(2, vc.Detach());
+  if (!mc.IsEmpty()) rec->Save(3, mc);
+  rec->Floats = {scale};
+  rec->Ints = {maskStride, heads};
   return rec->Attach(r);
 }
 

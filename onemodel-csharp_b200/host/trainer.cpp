@@ -2,6 +2,7 @@
 // reference writes a loop (tests/GuideSamples/TrainingGuide.cs:48-67 of the reference):
 //   scope; loss = model.Forward(x); opt.ZeroGrad(); loss.Backward(); opt.Step();
 // plus what the reference does not have: whole-step CUDA graph replay and data-parallel gradient buckets.
+#include <math.h>
 #include <string.h>
 
 #include <map>
@@ -81,6 +82,77 @@ struct MlmEncoder : NnModule {
   }
 };
 
+// 12-uniform Irwin-Hall normal on the generator's stream (the reference's SampleRng.NextNormal, Data/SampleRng.cs:83-88).
+static float NextNormal(Generator& g) {
+  float acc = 0.f;
+  for (int i = 0; i < 12; i++) acc += g.NextSingle();
+  return acc - 6.0f;
+}
+// He-normal weights, N(0, 2 / fanIn); the reference has no normal initialiser, the CNN configuration asks for one.
+static void HeNormal(Tensor& w, int fanIn, Generator& g) {
+  std::vector<float> h((size_t)w.Length());
+  float scale = sqrtf(2.0f / (float)fanIn);
+  for (float& v : h) v = NextNormal(g) * scale;
+  w.CopyFromHost(h.data());
+}
+static void ZeroFill(Tensor& t) {
+  std::vector<float> h((size_t)t.Length(), 0.f);
+  t.CopyFromHost(h.data());
+}
+
+// Config 2: [Conv 3x3 pad 1 (bias) + BatchNorm + ReLU] x n with per-conv stride, global average pool, Linear.
+struct SmallCnn : NnModule {
+  std::vector<Conv2d*> convs;
+  std::vector<BatchNorm2d*> norms;
+  Linear* Fc;
+  SmallCnn(int inCh, const std::vector<int>& channels, const std::vector<int>& strides, int classes, Generator& g) {
+    int c = inCh;
+    for (size_t i = 0; i < channels.size(); i++) {
+      convs.push_back(RegisterModule("conv" + std::to_string(i), new Conv2d(c, channels[i], 3, g, strides[i], 1, true)));
+      norms.push_back(RegisterModule("bn" + std::to_string(i), new BatchNorm2d(channels[i])));
+      HeNormal(convs.back()->Weight, c * 9, g);
+      ZeroFill(convs.back()->Bias);
+      c = channels[i];
+    }
+    Fc = RegisterModule("fc", new Linear(c, classes, g));
+    HeNormal(Fc->Weight, c, g);
+    ZeroFill(Fc->Bias);
+  }
+  Tensor Forward(const Tensor& x) override {
+    Tensor h = x;
+    for (size_t i = 0; i < convs.size(); i++) h = Ops::Relu(norms[i]->Forward(convs[i]->Forward(h)));
+    Tensor pooled = Ops::GlobalAvgPool2d(h);
+    return Fc->Forward(pooled.Reshape(Shape{pooled.GetShape()[0], pooled.GetShape()[1]}));
+  }
+};
+
+// Config 4: four Conv 3x3 + ReLU + MaxPool stages that reduce the height to 1, a 2-layer bidirectional LSTM over the
+// width axis, Linear to the classes, log-softmax. Returns log-probabilities [T, B, classes].
+struct Crnn : NnModule {
+  Conv2d* Convs[4];
+  Recurrent* Rnn;
+  Linear* Fc;
+  Crnn(const int channels[4], int hidden, int classes, Generator& g) {
+    int c = 1;
+    for (int i = 0; i < 4; i++) {
+      Convs[i] = RegisterModule("conv" + std::to_string(i), new Conv2d(c, channels[i], 3, g, 1, 1, true));
+      c = channels[i];
+    }
+    Rnn = RegisterModule("lstm", new Recurrent(c, hidden, 2, true, g));
+    Fc = RegisterModule("fc", new Linear(2 * hidden, classes, g));
+  }
+  Tensor Forward(const Tensor& x) override {
+    static const int pool[4][2] = {{2, 2}, {2, 2}, {2, 1}, {4, 1}};
+    Tensor h = x;
+    for (int i = 0; i < 4; i++) h = Ops::MaxPool2d(Ops::Relu(Convs[i]->Forward(h)), pool[i][0], pool[i][1], pool[i][0], pool[i][1]);
+    if (h.GetShape()[2] != 1) throw TensorShapeException("The CRNN needs an input height of 32, got a feature map " + h.GetShape().ToString() + ".");
+    int b = h.GetShape()[0], c = h.GetShape()[1], t = h.GetShape()[3];
+    Tensor seq = h.Reshape(Shape{b, c, t}).Permute({2, 0, 1});   // [T, B, C]
+    Tensor y = Rnn->Forward(seq);
+    return Ops::LogSoftmax(Fc->Forward(y), -1);
+  }
+};
+
 }  // namespace
 
 struct omh_trainer {
@@ -92,6 +164,7 @@ struct omh_trainer {
   // persistent device inputs
   std::vector<Tensor> inputs;
   Tensor positions;
+  Tensor input_lengths;   // CRNN: every sequence spans all frames
   Tensor loss_out;     // device scalar that survives the step
   Tensor flat_grads;   // all gradients, contiguous, in reverse registration order
   float ce_denominator = 0.f;
@@ -141,6 +214,14 @@ static Tensor Forward(omh_trainer* t) {
     Tensor logits = t->model->Forward(t->inputs[0]);
     return Ops::CrossEntropy(logits, t->inputs[1], true, -100, t->ce_denominator);
   }
+  if (t->kind == 2) {
+    Tensor logits = t->model->Forward(t->inputs[0]);
+    return Ops::CrossEntropy(logits, t->inputs[1], true, -100, t->ce_denominator);
+  }
+  if (t->kind == 4) {
+    Tensor lp = t->model->Forward(t->inputs[0]);
+    return Ops::CtcLoss(lp, t->inputs[1], t->input_lengths, t->inputs[2], 0, 1, true);
+  }
   auto* m = static_cast<MlmEncoder*>(t->model.get());
   Tensor logits = m->Logits(t->inputs[0], t->positions, t->inputs[1]);
   return Ops::CrossEntropy(logits, t->inputs[2], true, -100, t->ce_denominator);
@@ -182,7 +263,8 @@ OMH_API int32_t omh_trainer_last_error(char* buf, size_t n) {
   return 0;
 }
 
-// kind 1 (MLP): cfg = [batch, in, h1, h2, out]. kind 3 (masked-LM encoder): cfg = [batch, seq, layers, width, heads,
+// kind 1 (MLP, AdamW): cfg = [batch, in, h1, h2, out]. kind 2 (CNN, SGD momentum 0.9) and kind 4 (CRNN + CTC, Adam): see
+// below. kind 3 (masked-LM encoder, AdamW): cfg = [batch, seq, layers, width, heads,
 // ff, vocab, masked_rows]. hyper = [lr, weight_decay, clip_norm (0 = off)].
 OMH_API int32_t omh_trainer_create(int32_t kind, const int64_t* cfg, int32_t ncfg, uint64_t seed, const double* hyper,
                                    omh_trainer** out) {
@@ -208,13 +290,36 @@ OMH_API int32_t omh_trainer_create(int32_t kind, const int64_t* cfg, int32_t ncf
       std::vector<int32_t> pos(seq);
       for (int i = 0; i < seq; i++) pos[i] = i;
       t->positions = Tensor::FromHostInt32(pos.data(), Shape{seq});
+    } else if (kind == 2) {
+      // [batch, in_channels, height, width, classes, n, channels x n, strides x n]
+      if (ncfg < 6 || ncfg != 6 + 2 * cfg[5]) throw TensorShapeException("CNN config needs [batch, in_ch, h, w, classes, n, channels..., strides...]");
+      int n = (int)cfg[5];
+      std::vector<int> ch, st;
+      for (int i = 0; i < n; i++) ch.push_back((int)cfg[6 + i]);
+      for (int i = 0; i < n; i++) st.push_back((int)cfg[6 + n + i]);
+      t->model.reset(new SmallCnn((int)cfg[1], ch, st, (int)cfg[4], g));
+      t->inputs.push_back(Tensor::Zeros(DType::F32, Shape{(int)cfg[0], (int)cfg[1], (int)cfg[2], (int)cfg[3]}));
+      t->inputs.push_back(Tensor::Zeros(DType::I64, Shape{(int)cfg[0]}));
+    } else if (kind == 4) {
+      // [batch, height, width, classes, hidden, max_label, c1, c2, c3, c4]
+      if (ncfg != 10) throw TensorShapeException("CRNN config needs 10 integers");
+      int batch = (int)cfg[0], frames = (int)cfg[2] / 4;
+      const int ch[4] = {(int)cfg[6], (int)cfg[7], (int)cfg[8], (int)cfg[9]};
+      t->model.reset(new Crnn(ch, (int)cfg[4], (int)cfg[3], g));
+      t->inputs.push_back(Tensor::Zeros(DType::F32, Shape{batch, 1, (int)cfg[1], (int)cfg[2]}));
+      t->inputs.push_back(Tensor::Zeros(DType::I32, Shape{batch * (int)cfg[5]}));   // labels, concatenated
+      t->inputs.push_back(Tensor::Zeros(DType::I32, Shape{batch}));                 // label lengths
+      std::vector<int32_t> il(batch, frames);
+      t->input_lengths = Tensor::FromHostInt32(il.data(), Shape{batch});
     } else {
       throw InvalidOperationException("unknown trainer kind");
     }
     t->params = t->model->NamedParameters();
     std::vector<Tensor> ps;
     for (auto& p : t->params) ps.push_back(p.second);
-    t->opt.reset(new AdamW(ps, (float)hyper[0], 0.9f, 0.999f, 1e-8f, (float)hyper[1]));
+    if (kind == 2) t->opt.reset(new Sgd(ps, (float)hyper[0], 0.9f, 0.f, (float)hyper[1], false));
+    else if (kind == 4) t->opt.reset(new Adam(ps, (float)hyper[0], 0.9f, 0.999f, 1e-8f, (float)hyper[1]));
+    else t->opt.reset(new AdamW(ps, (float)hyper[0], 0.9f, 0.999f, 1e-8f, (float)hyper[1]));
     t->clip_norm = (float)hyper[2];
     t->loss_out = Tensor::Zeros(DType::F32, Shape{});
     t->hyper_host.assign(t->opt->HyperBytes(), 0);

@@ -389,7 +389,7 @@ class Trainer:
     kind 'mlp': cfg = [batch, in, hidden..., out]; kind 'mlm': cfg = [batch, seq, layers, width, heads, ff, vocab, rows].
     step(inputs) takes the host batch (numpy arrays) and returns the loss: the call a user makes."""
 
-    KINDS = {"mlp": 1, "mlm": 3}
+    KINDS = {"mlp": 1, "cnn": 2, "mlm": 3, "crnn": 4}
 
     def __init__(self, kind, cfg, lr, weight_decay=0.01, clip_norm=0.0, seed=0):
         self.h = C.c_void_p()

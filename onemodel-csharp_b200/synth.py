@@ -100,3 +100,22 @@ def mlp_batch(batch, width, classes, step=0, rank=0):
     x = normal(derive(1, 0, step, rank), (batch, width))
     y = integers(derive(2, 0, step, rank), (batch,), classes)
     return x, y
+
+
+def cnn_batch(batch, channels, height, width, classes, step=0, rank=0):
+    """Config 2: images N(0,1), labels uniform in [0, classes)."""
+    x = normal(derive(1, 0, step, rank), (batch, channels, height, width))
+    y = integers(derive(2, 0, step, rank), (batch,), classes)
+    return x, y
+
+
+def crnn_batch(batch, height, width, classes, max_label, min_label=5, step=0, rank=0):
+    """Config 4: grayscale images U(0,1); per image a label of length uniform in [min_label, max_label] of symbols uniform
+    in [1, classes). Returns x, the concatenated labels padded with zeros to batch * max_label (int32), the lengths."""
+    x = uniform(derive(1, 0, step, rank), (batch, 1, height, width))
+    lengths = (integers(derive(2, 0, step, rank), (batch,), max_label - min_label + 1) + min_label).astype(np.int32)
+    symbols = (integers(derive(2, 1, step, rank), (batch * max_label,), classes - 1) + 1).astype(np.int32)
+    targets = np.zeros(batch * max_label, np.int32)
+    total = int(lengths.sum())
+    targets[:total] = symbols[:total]
+    return x, targets, lengths

@@ -67,8 +67,89 @@ def _adamw(params, grads, state, t, lr, wd):
         K.adam_step(p, g, s["m"], s["v"], None, t, lr, 0.9, 0.999, 1e-8, wd, True, False)
 
 
+def mlm_init(seq, layers, width, ff, vocab, seed=0):
+    """Parameter set of the masked-LM encoder under the product's parameter names, uniform(+-1/sqrt(fan_in)) as the
+    reference's Linear default (Layers.cs:59-64). Values come from numpy's generator: callers that compare with the GPU
+    load these same arrays into it."""
+    rng = np.random.default_rng(seed)
+    named = {"tok.weight": rng.uniform(-1, 1, (vocab, width)).astype(np.float32),
+             "pos.weight": rng.uniform(-1, 1, (seq, width)).astype(np.float32)}
+
+    def lin(o, i):
+        b = 1.0 / np.sqrt(i)
+        return rng.uniform(-b, b, (o, i)).astype(np.float32), rng.uniform(-b, b, o).astype(np.float32)
+
+    for l in range(layers):
+        p = f"layers.{l}."
+        for n in "qkvo":
+            named[p + f"attn.{n}.weight"], named[p + f"attn.{n}.bias"] = lin(width, width)
+        named[p + "norm1.weight"], named[p + "norm1.bias"] = np.ones(width, np.float32), np.zeros(width, np.float32)
+        named[p + "ff1.weight"], named[p + "ff1.bias"] = lin(ff, width)
+        named[p + "ff2.weight"], named[p + "ff2.bias"] = lin(width, ff)
+        named[p + "norm2.weight"], named[p + "norm2.bias"] = np.ones(width, np.float32), np.zeros(width, np.float32)
+    named["head.weight"], named["head.bias"] = lin(vocab, width)
+    return named
+
+
 def mlm_step(named, ids, rows, labels, layers, heads, t, state, lr=1e-4, wd=0.01):
     loss, grads = mlm_forward_backward(named, ids, rows, labels, layers, heads)
     names = list(named)
     _adamw([named[k] for k in names], [grads[k] for k in names], state, t, lr, wd)
+    return loss, grads
+
+
+def cnn_forward_backward(named, running, x, y, strides):
+    """Config 2: [conv 3x3 pad 1 + batch norm + ReLU] per entry of strides, global average pool, linear, cross-entropy.
+    named: conv{i}.weight/bias, bn{i}.weight/bias, fc.weight/bias. running: {bn{i}: (mean, var)}, updated in place."""
+    w = {k: A.T(v, True) for k, v in named.items()}
+    h = A.T(x)
+    for i, s in enumerate(strides):
+        h = A.conv2d(h, w[f"conv{i}.weight"], w[f"conv{i}.bias"], s, 1)
+        rm, rv = running[f"bn{i}"]
+        h = A.relu(A.batch_norm2d(h, w[f"bn{i}.weight"], w[f"bn{i}.bias"], rm, rv, True))
+    n, c = h.shape[0], h.shape[1]
+    pooled = A.mean(h.reshape(n, c, h.shape[2] * h.shape[3]), 2)
+    loss = A.cross_entropy(A.linear(pooled, w["fc.weight"], w["fc.bias"]), y)
+    loss.backward()
+    return float(loss.v), {k: t.grad for k, t in w.items()}
+
+
+def cnn_step(named, running, x, y, strides, state, lr=0.1, momentum=0.9, wd=0.0):
+    """One SGD-momentum step (Sgd.Update, Optimizers.cs:335-373). state: {name: buffer}, empty before the first step."""
+    loss, grads = cnn_forward_backward(named, running, x, y, strides)
+    for k, p in named.items():
+        first = k not in state
+        buf = state.setdefault(k, np.zeros_like(p))
+        K.sgd_step(p, grads[k], buf, first, lr, wd, momentum, 0.0, False)
+    return loss, grads
+
+
+def crnn_forward_backward(named, x, targets, target_lengths):
+    """Config 4: four conv 3x3 + ReLU + max-pool stages ((2,2),(2,2),(2,1),(4,1)), a 2-layer bidirectional LSTM over the
+    width axis, linear, log-softmax, CTC (blank 0, mean, zero-infinity). named: conv{i}.*, lstm.*, fc.*."""
+    w = {k: A.T(v, True) for k, v in named.items()}
+    h = A.T(x)
+    for i, pool in enumerate(((2, 2), (2, 2), (2, 1), (4, 1))):
+        h = A.max_pool2d(A.relu(A.conv2d(h, w[f"conv{i}.weight"], w[f"conv{i}.bias"], 1, 1)), pool)
+    b, c, _, t = h.shape
+    seq = h.reshape(b, c, t).permute(2, 0, 1)
+    for layer in range(2):
+        outs = []
+        for d, sfx in enumerate(("", "_reverse")):
+            p = f"lstm.%s_l{layer}{sfx}"
+            outs.append(A.lstm_layer(seq, w[p % "weight_ih"], w[p % "weight_hh"], w[p % "bias_ih"], w[p % "bias_hh"], d == 1))
+        seq = A.concat(outs, 2)
+    lp = A.log_softmax(A.linear(seq, w["fc.weight"], w["fc.bias"]))
+    ilen = np.full(b, t, np.int32)
+    loss = A.ctc_loss(lp, np.asarray(targets, np.int32), ilen, np.asarray(target_lengths, np.int32), 0, 1, True)
+    loss.backward()
+    return float(loss.v), {k: v.grad for k, v in w.items()}
+
+
+def crnn_step(named, x, targets, target_lengths, t, state, lr=1e-3):
+    """One Adam step (coupled weight decay 0; Adam.UpdateRange, Optimizers.cs:554-589)."""
+    loss, grads = crnn_forward_backward(named, x, targets, target_lengths)
+    for i, (k, p) in enumerate(named.items()):
+        s = state.setdefault(k, dict(m=np.zeros_like(p), v=np.zeros_like(p)))
+        K.adam_step(p, grads[k], s["m"], s["v"], None, t, lr, 0.9, 0.999, 1e-8, 0.0, False, False)
     return loss, grads

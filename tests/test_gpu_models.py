@@ -100,3 +100,50 @@ def test_engine_semantics(B):
         B.backward(B.mul(x, x))          # not a one-element tensor
     x.zero_grad()
     assert not B.grad(x).any()
+
+
+@pytest.mark.parametrize("tf32", [False, True])
+@pytest.mark.parametrize("b,l,heads,dh,packed", [(3, 128, 4, 32, False), (2, 50, 3, 16, False), (2, 128, 12, 32, True)])
+def test_attention_over_heads_equals_the_permuted_form(ctx, B, tf32, b, l, heads, dh, packed):
+    """Ops.AttentionHeads on [batch, length, heads*d] activations against the reference's form (Reshape + Permute around
+    Ops.Attention, Layers.cs:503-520): values and all three input gradients. With the fp32 products the two run the same
+    arithmetic per (batch, head) and agree to the bit; on the tensor pipe both round operands the same way. `packed`
+    feeds q, k, v as column slices of one [batch, length, 3*width] tensor (row-pitched views, no copy)."""
+    import om_binding as omb
+    ctx.set_flags(omb.OM_TF32 if tf32 else 0)
+    try:
+        d = heads * dh
+        r = np.random.default_rng(b * l + heads)
+        w = r.standard_normal((b, l, d)).astype(np.float32)
+        if packed:
+            qkv = r.standard_normal((b, l, 3 * d)).astype(np.float32)
+            srcs = [qkv[:, :, i * d:(i + 1) * d].copy() for i in range(3)]
+        else:
+            srcs = [r.standard_normal((b, l, d)).astype(np.float32) for _ in range(3)]
+
+        def run(fused):
+            if packed:
+                root = B.tensor(qkv, True)
+                q, k, v = (root.slice(2, i * d, (i + 1) * d) for i in range(3))
+                leaves = [root]
+            else:
+                leaves = [B.tensor(s, True) for s in srcs]
+                q, k, v = leaves
+            if fused:
+                a = omb.call("attention_heads", [q, k, v, None], ints=[heads], floats=[0.0])
+            else:
+                split = lambda z: omb.call("contiguous", [z]).reshape(b, l, heads, dh).permute(0, 2, 1, 3)
+                a = omb.call("attention", [split(q), split(k), split(v), None], floats=[0.0]).permute(0, 2, 1, 3).reshape(b, l, d)
+            B.backward(B.sum(B.mul(a, B.tensor(w))))
+            return a.numpy(), [B.grad(t) for t in leaves]
+
+        ya, ga = run(True)
+        yb, gb = run(False)
+        if tf32:
+            assert scaled_diff(ya, yb) <= 2e-5
+            assert all(scaled_diff(x, y) <= 2e-5 for x, y in zip(ga, gb))
+        else:
+            assert np.array_equal(ya, yb)
+            assert all(np.array_equal(x, y) for x, y in zip(ga, gb))
+    finally:
+        ctx.set_flags(0)

@@ -105,3 +105,58 @@ def test_full_size_encoder_step_is_deterministic_and_graph_equals_eager(ctx, tf3
         assert np.all(np.isfinite(la))
     finally:
         ctx.set_flags(0)
+
+
+def test_cnn_config_small(ctx, configs):
+    """Config 2 at reduced size (conv + batch norm + ReLU x 4 with the strided stages, global average pool, linear; SGD
+    momentum 0.9): per-parameter gradients after step 1 and the loss curve over 8 steps against the CPU path."""
+    ctx.set_flags(0)
+    ctx.make_current()
+    batch, ch, strides = 8, [8, 8, 16, 16], [1, 1, 2, 1]
+    cfg = [batch, 3, 16, 16, 10, len(ch)] + ch + strides
+    tr = omb.Trainer("cnn", cfg, lr=0.05, weight_decay=0.0, seed=0)
+    named = tr.named_parameters()
+    weights = {n: tr.get_param(i, s) for i, (n, s) in enumerate(named)}
+    running = {f"bn{i}": (np.zeros(c, np.float32), np.ones(c, np.float32)) for i, c in enumerate(ch)}
+    state = {}
+    for step in range(8):
+        x, y = synth.cnn_batch(batch, 3, 16, 16, 10, step)
+        lg = tr.step([x, y])
+        lo, grads = configs.cnn_step(weights, running, x, y, strides, state, lr=0.05)
+        assert abs(lg - lo) <= 1e-3 * abs(lo), step
+        if step == 0:
+            largest = max(np.max(np.abs(g)) for g in grads.values())
+            for i, (n, s) in enumerate(named):
+                gg = tr.get_grad(i, s)
+                # A convolution bias in front of a batch norm has an exactly zero gradient; both sides hold rounding noise.
+                if np.max(np.abs(grads[n])) < 1e-5 * largest:
+                    assert np.max(np.abs(gg)) < 1e-5 * largest, n
+                else:
+                    assert scaled_diff(gg, grads[n]) <= 1e-4, n
+    assert abs(lg - lo) <= 0.01 * abs(lo)
+    tr.close()
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_crnn_config_small(ctx, configs, graph):
+    """Config 4 at reduced size (4 conv/pool stages to height 1, 2-layer BiLSTM, linear, log-softmax, CTC; Adam): gradients
+    after step 1 and losses over 5 steps, eager and replayed from a captured graph."""
+    ctx.set_flags(0)
+    ctx.make_current()
+    batch, height, width, classes, hidden, max_label = 4, 32, 48, 11, 8, 5
+    cfg = [batch, height, width, classes, hidden, max_label, 4, 6, 8, 8]
+    tr = omb.Trainer("crnn", cfg, lr=1e-3, weight_decay=0.0, seed=0)
+    named = tr.named_parameters()
+    weights = {n: tr.get_param(i, s) for i, (n, s) in enumerate(named)}
+    state = {}
+    for step in range(5):
+        x, targets, lengths = synth.crnn_batch(batch, height, width, classes, max_label, 2, step)
+        if graph and step == 1:
+            tr.enable_graph()
+        lg = tr.step([x, targets, lengths])
+        lo, grads = configs.crnn_step(weights, x, targets[: int(lengths.sum())], lengths, step + 1, state)
+        assert abs(lg - lo) <= 1e-4 * abs(lo), step
+        if step == 0:
+            for i, (n, s) in enumerate(named):
+                assert scaled_diff(tr.get_grad(i, s), grads[n]) <= 1e-4, n
+    tr.close()
