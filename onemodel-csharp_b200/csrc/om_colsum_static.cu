@@ -4,7 +4,7 @@
 // driver for a new block. This variant keeps the table in a fixed array that is part of the loaded module, so the call
 // never asks the pool or the driver for memory: a host that has handed its whole device budget out at start-up, or
 // that must not risk the device-wide synchronisation and the late out-of-memory failure of a driver allocation in the
-// middle of a run, can still take a bias gradient. The arithmetic (row chunks of 512, eight row lanes per column
+// middle of a run, can still take a bias gradient. The arithmetic (row chunks of 512, 32 row lanes per column
 // summed in double, lanes then chunks combined in increasing order) is that of om_colsum, so the two entry points
 // give the same bits.
 //
@@ -21,6 +21,7 @@
 namespace om {
 
 constexpr int kStaticRowsPerChunk = 512;
+constexpr int kStaticLanes = 32;   // row lanes per column, as in om_colsum
 // 131072 doubles = 1 MiB. A call needs ceil(rows / 512) * cols slots.
 constexpr long long kStaticSlots = 131072;
 constexpr int kStaticMaxDevices = 64;
@@ -30,22 +31,23 @@ static __device__ __align__(256) double g_colsum_scratch[kStaticSlots];
 static std::mutex g_scratch_mutex;
 static double* g_scratch_addr[kStaticMaxDevices] = {nullptr};
 
-__global__ void colsum_static_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld,
+__global__ void __launch_bounds__(1024)
+colsum_static_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld,
                                             double* __restrict__ partial) {
-  __shared__ double sm[8][33];
+  __shared__ double sm[kStaticLanes][33];
   int col = blockIdx.x * 32 + threadIdx.x;
   int r0 = blockIdx.y * kStaticRowsPerChunk;
   int r1 = min(rows, r0 + kStaticRowsPerChunk);
   double acc = 0.0;
   if (col < cols) {
-    for (int r = r0 + threadIdx.y; r < r1; r += 8) acc += (double)g[(int64_t)r * ld + col];
+    for (int r = r0 + threadIdx.y; r < r1; r += kStaticLanes) acc += (double)g[(int64_t)r * ld + col];
   }
   sm[threadIdx.y][threadIdx.x] = acc;
   __syncthreads();
   if (threadIdx.y == 0 && col < cols) {
     double t = 0.0;
 #pragma unroll
-    for (int l = 0; l < 8; l++) t += sm[l][threadIdx.x];
+    for (int l = 0; l < kStaticLanes; l++) t += sm[l][threadIdx.x];
     partial[(int64_t)blockIdx.y * cols + col] = t;
   }
 }
@@ -95,7 +97,7 @@ extern "C" int32_t om_colsum_static(om_ctx* ctx, const float* g, int32_t rows, i
   double* partial = nullptr;
   OM_TRY(scratch_for(ctx, &partial));
   dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)chunks);
-  colsum_static_stage1_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(g, rows, cols, cols, partial);
+  colsum_static_stage1_kernel<<<grid, dim3(32, kStaticLanes), 0, ctx->stream>>>(g, rows, cols, cols, partial);
   colsum_static_stage2_kernel<<<(unsigned)ceil_div(cols, 128), 128, 0, ctx->stream>>>(partial, (int)chunks, cols, out, accumulate);
   OM_LAUNCH_CHECK(ctx, "om_colsum_static");
   return OM_OK;

@@ -275,58 +275,58 @@ __global__ void transpose2d_kernel(const float* __restrict__ src, float* __restr
 
 constexpr int kColsumRowsPerChunk = 512;
 
+constexpr int kColsumLanes = 32;
+
 // Stage 1 of a column sum over g[rows, cols]: CTA (bx, by) owns 32 columns and one chunk of kColsumRowsPerChunk rows.
-// 8 row-lanes per column accumulate in double over rows lane, lane+8, ...; the 8 lane sums are combined in lane
+// 32 row-lanes per column accumulate in double over rows lane, lane+32, ...; the 32 lane sums are combined in lane
 // order. partial[chunk, col] is written in double.
-__global__ void colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld,
-                                     double* __restrict__ partial) {
-  __shared__ double sm[8][33];
+__global__ void __launch_bounds__(1024)
+colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial) {
+  __shared__ double sm[kColsumLanes][33];
   int col = blockIdx.x * 32 + threadIdx.x;
   int r0 = blockIdx.y * kColsumRowsPerChunk;
   int r1 = min(rows, r0 + kColsumRowsPerChunk);
   double acc = 0.0;
   if (col < cols) {
-    for (int r = r0 + threadIdx.y; r < r1; r += 8) acc += (double)g[(int64_t)r * ld + col];
+    for (int r = r0 + threadIdx.y; r < r1; r += kColsumLanes) acc += (double)g[(int64_t)r * ld + col];
   }
   sm[threadIdx.y][threadIdx.x] = acc;
   __syncthreads();
   if (threadIdx.y == 0 && col < cols) {
     double t = 0.0;
 #pragma unroll
-    for (int l = 0; l < 8; l++) t += sm[l][threadIdx.x];
+    for (int l = 0; l < kColsumLanes; l++) t += sm[l][threadIdx.x];
     partial[(int64_t)blockIdx.y * cols + col] = t;
   }
 }
 
 // Stage 1 for rows that are 16-byte aligned (ld a multiple of four, aligned base): the same sums in the same order as
-// colsum_stage1_kernel - per column eight row lanes over rows lane, lane + 8, ... of the chunk in double, lanes then
-// combined in lane order - but each thread owns four adjacent columns (one 16-byte load per row) and keeps eight rows
-// in flight. A CTA is 8 column groups x 8 row lanes and covers 32 columns of one chunk.
-__global__ void __launch_bounds__(64)
+// colsum_stage1_kernel, but each thread owns four adjacent columns (one 16-byte load per row) and has all of its 16
+// rows in flight at once. A CTA is 8 column groups x 32 row lanes and covers 32 columns of one chunk.
+__global__ void __launch_bounds__(256)
 colsum_stage1_vec4_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial) {
-  __shared__ double sm[8][33];
+  __shared__ double sm[kColsumLanes][33];
+  constexpr int PER_LANE = kColsumRowsPerChunk / kColsumLanes;
   const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
   const int col = blockIdx.x * 32 + tx * 4;
   const int r0 = blockIdx.y * kColsumRowsPerChunk;
   const int r1 = min(rows, r0 + kColsumRowsPerChunk);
   double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
   if (col + 3 < cols) {
-    int r = r0 + ty;
-    for (; r + 56 < r1; r += 64) {
-      float4 v[8];
+    float4 v[PER_LANE];
 #pragma unroll
-      for (int u = 0; u < 8; u++) v[u] = __ldg(reinterpret_cast<const float4*>(g + (int64_t)(r + 8 * u) * ld + col));
+    for (int u = 0; u < PER_LANE; u++) {
+      const int r = r0 + ty + kColsumLanes * u;
+      v[u] = r < r1 ? __ldg(reinterpret_cast<const float4*>(g + (int64_t)r * ld + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 #pragma unroll
-      for (int u = 0; u < 8; u++) {
+    for (int u = 0; u < PER_LANE; u++) {
+      if (r0 + ty + kColsumLanes * u < r1) {
         a0 += (double)v[u].x; a1 += (double)v[u].y; a2 += (double)v[u].z; a3 += (double)v[u].w;
       }
     }
-    for (; r < r1; r += 8) {
-      float4 v = __ldg(reinterpret_cast<const float4*>(g + (int64_t)r * ld + col));
-      a0 += (double)v.x; a1 += (double)v.y; a2 += (double)v.z; a3 += (double)v.w;
-    }
   } else if (col < cols) {
-    for (int r = r0 + ty; r < r1; r += 8) {
+    for (int r = r0 + ty; r < r1; r += kColsumLanes) {
       const float* row = g + (int64_t)r * ld + col;
       a0 += (double)row[0];
       if (col + 1 < cols) a1 += (double)row[1];
@@ -340,7 +340,7 @@ colsum_stage1_vec4_kernel(const float* __restrict__ g, int32_t rows, int32_t col
     if (c < cols) {
       double t = 0.0;
 #pragma unroll
-      for (int l = 0; l < 8; l++) t += sm[l][threadIdx.x];
+      for (int l = 0; l < kColsumLanes; l++) t += sm[l][threadIdx.x];
       partial[(int64_t)blockIdx.y * cols + c] = t;
     }
   }
@@ -468,9 +468,9 @@ int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64
   OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&partial));
   dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)chunks);
   if ((ld & 3) == 0 && aligned16(g))
-    colsum_stage1_vec4_kernel<<<grid, 64, 0, ctx->stream>>>(g, rows, cols, ld, partial);
+    colsum_stage1_vec4_kernel<<<grid, 256, 0, ctx->stream>>>(g, rows, cols, ld, partial);
   else
-    colsum_stage1_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(g, rows, cols, ld, partial);
+    colsum_stage1_kernel<<<grid, dim3(32, kColsumLanes), 0, ctx->stream>>>(g, rows, cols, ld, partial);
   colsum_stage2_kernel<<<(unsigned)ceil_div(cols, 128), 128, 0, ctx->stream>>>(partial, chunks, cols, out, accumulate);
   pool_free(ctx, partial);
   OM_LAUNCH_CHECK(ctx, "om_colsum");
