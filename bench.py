@@ -32,7 +32,11 @@ for p in (ROOT, PKG):
 
 WORKLOADS = {
     # name: (kind, cfg, lr, description, algorithmic GFLOP per step and GPU)
-    "c1": ("mlp", [128, 784, 512, 512, 10], 1e-3, "MLP 784-512-512-10 b128 AdamW fp32", 0.411),
+    "c1": ("mlp", [128, 784, 512, 512, 10], 1e-3, "MLP 784-512-512-10 b128 AdamW", 0.411),
+    "c2": ("cnn", [256, 3, 32, 32, 10, 8, 64, 64, 128, 128, 256, 256, 512, 512, 1, 1, 2, 1, 2, 1, 2, 1], 0.1,
+           "CNN 8x(conv3x3+BN+ReLU) 64-64-128-128-256-256-512-512 on 256x3x32x32, avg pool, linear 10, SGD momentum 0.9", 320.7),
+    "c4": ("crnn", [64, 32, 256, 97, 256, 20, 64, 128, 256, 256], 1e-3,
+           "CRNN conv 64-128-256-256 + 2-layer BiLSTM-256 + linear 97 on 64x1x32x256 (T=64), CTC, Adam", 240.8),
     "c3": ("mlm", [64, 128, 6, 384, 12, 1536, 30522, 1229], 1e-4,
            "MiniLM-shape encoder 6x(d384,h12,ff1536) seq128 b64/GPU vocab30522, 1229 masked rows, AdamW, TF32 products", 637.3),
     "c5": ("mlm", [32, 512, 12, 768, 12, 3072, 30522, 2458], 1e-4,
@@ -46,6 +50,10 @@ def make_batches(kind, cfg, count, rank):
     for s in range(count):
         if kind == "mlp":
             out.append(list(synth.mlp_batch(cfg[0], cfg[1], cfg[-1], s, rank)))
+        elif kind == "cnn":
+            out.append(list(synth.cnn_batch(cfg[0], cfg[1], cfg[2], cfg[3], cfg[4], s, rank)))
+        elif kind == "crnn":
+            out.append(list(synth.crnn_batch(cfg[0], cfg[1], cfg[2], cfg[3], cfg[5], 5, s, rank)))
         else:
             out.append(list(synth.mlm_batch(cfg[0], cfg[1], cfg[6], cfg[7], s, rank)))
     return out
@@ -80,46 +88,60 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": float(np.median([s for s, _ in self.samples])), "sm_max_mhz": self.max_mhz, "reasons": reasons}
 
 
-def cpu_baseline(workload, steps=1, warmup=0):
+WEIGHT_DECAY = {"mlp": 0.01, "mlm": 0.01, "cnn": 0.0, "crnn": 0.0}
+# Batch of the CPU sample: the full step where that takes seconds, a slice of the batch where it would take minutes
+# (samples/s does not depend on the batch for these models; the sample string says what was run).
+CPU_SAMPLE_BATCH = {"c1": 128, "c2": 256, "c3": 64, "c4": 64, "c5": 2}
+
+
+def cpu_baseline(workload, steps=1, warmup=0, batch_override=0):
     """Times the CPU restatement of the reference's training step on this box's cores. Returns (samples/s, dict)."""
     from oracle import configs, oracle as K
     import synth
     K.build()
     kind, cfg, lr, desc, _ = WORKLOADS[workload]
     cores = os.cpu_count() or 1
-    rng = np.random.default_rng(0)
+    batch = batch_override or CPU_SAMPLE_BATCH[workload]
+    times = []
     if kind == "mlp":
+        rng = np.random.default_rng(0)
         widths = cfg[1:]
         params = []
         for i in range(len(widths) - 1):
             bound = 1.0 / np.sqrt(widths[i])
             params += [rng.uniform(-bound, bound, (widths[i + 1], widths[i])).astype(np.float32), rng.uniform(-bound, bound, widths[i + 1]).astype(np.float32)]
-        state, times = {}, []
+        state = {}
         for s in range(warmup + steps):
-            x, y = synth.mlp_batch(cfg[0], cfg[1], cfg[-1], s)
+            x, y = synth.mlp_batch(batch, cfg[1], cfg[-1], s)
             t0 = time.perf_counter()
             configs.mlp_step(params, x, y, s + 1, lr=lr, state=state)
             if s >= warmup:
                 times.append(time.perf_counter() - t0)
-        batch = cfg[0]
+    elif kind == "cnn":
+        n = cfg[5]
+        channels, strides = cfg[6:6 + n], cfg[6 + n:6 + 2 * n]
+        named, running = configs.cnn_init(cfg[1], channels, cfg[4])
+        state = {}
+        for s in range(warmup + steps):
+            x, y = synth.cnn_batch(batch, cfg[1], cfg[2], cfg[3], cfg[4], s)
+            t0 = time.perf_counter()
+            configs.cnn_step(named, running, x, y, strides, state, lr=lr)
+            if s >= warmup:
+                times.append(time.perf_counter() - t0)
+    elif kind == "crnn":
+        named = configs.crnn_init(cfg[6:10], cfg[4], cfg[3])
+        state = {}
+        for s in range(warmup + steps):
+            x, targets, lengths = synth.crnn_batch(batch, cfg[1], cfg[2], cfg[3], cfg[5], 5, s)
+            t0 = time.perf_counter()
+            configs.crnn_step(named, x, targets[: int(lengths.sum())], lengths, s + 1, state, lr=lr)
+            if s >= warmup:
+                times.append(time.perf_counter() - t0)
     else:
-        batch, seq, layers, width, heads, ff, vocab, rows = cfg
-        named = {"tok.weight": rng.uniform(-1, 1, (vocab, width)).astype(np.float32), "pos.weight": rng.uniform(-1, 1, (seq, width)).astype(np.float32)}
-
-        def lin(o, i):
-            b = 1.0 / np.sqrt(i)
-            return rng.uniform(-b, b, (o, i)).astype(np.float32), rng.uniform(-b, b, o).astype(np.float32)
-
-        for l in range(layers):
-            p = f"layers.{l}."
-            for n in "qkvo":
-                named[p + f"attn.{n}.weight"], named[p + f"attn.{n}.bias"] = lin(width, width)
-            named[p + "norm1.weight"], named[p + "norm1.bias"] = np.ones(width, np.float32), np.zeros(width, np.float32)
-            named[p + "ff1.weight"], named[p + "ff1.bias"] = lin(ff, width)
-            named[p + "ff2.weight"], named[p + "ff2.bias"] = lin(width, ff)
-            named[p + "norm2.weight"], named[p + "norm2.bias"] = np.ones(width, np.float32), np.zeros(width, np.float32)
-        named["head.weight"], named["head.bias"] = lin(vocab, width)
-        state, times = {}, []
+        _, seq, layers, width, heads, ff, vocab, rows = cfg
+        rows = max(1, int(round(rows * batch / cfg[0])))
+        named = configs.mlm_init(seq, layers, width, ff, vocab)
+        state = {}
         for s in range(warmup + steps):
             ids, pos, labels = synth.mlm_batch(batch, seq, vocab, rows, s)
             t0 = time.perf_counter()
@@ -127,15 +149,18 @@ def cpu_baseline(workload, steps=1, warmup=0):
             if s >= warmup:
                 times.append(time.perf_counter() - t0)
     sec = float(np.median(times))
+    what = "full" if batch == cfg[0] else f"batch-{batch} slice of the batch-{cfg[0]}"
     return batch / sec, {"value": batch / sec, "unit": "samples/s", "cores": cores, "kind": "port",
-                         "sample": f"{steps} full step(s) of {workload} (batch {batch}), median; OpenMP over {cores} host threads in the products, attention heads and softmax rows",
+                         "sample": f"{steps} {what} step(s) of {workload}, median; OpenMP over {cores} host threads in the products, "
+                                   "convolutions, attention heads and softmax rows, the rest single-threaded as the reference is",
                          "ms_per_step": sec * 1e3}
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    value, cb = cpu_baseline(args.workload, steps=max(1, min(args.steps, 3)), warmup=1 if args.workload == "c1" else 0)
+    value, cb = cpu_baseline(args.workload, steps=max(1, min(args.steps, 3)), warmup=1 if args.workload == "c1" else 0,
+                             batch_override=args.cpu_batch)
     kind, cfg, lr, desc, _ = WORKLOADS[args.workload]
     line = {"impl": "reference", "metric": "train samples/s (fwd+bwd+AdamW)", "value": value, "unit": "samples/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"],
@@ -175,6 +200,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-batch", type=int, default=0, help="batch of the CPU baseline sample (0 = the workload default)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--fp32", action="store_true", help="products on the fp32 FMA kernel instead of the tensor pipe")
     ap.add_argument("--skip-cpu", action="store_true")
@@ -198,7 +224,7 @@ def main():
     W, K = max(3, args.warmup), max(1, args.steps)
     flags = 0 if args.fp32 else omb.OM_TF32
     ctx = omb.Context(local_rank, flags)
-    tr = omb.Trainer(kind, cfg, lr=lr, weight_decay=0.01, seed=0)
+    tr = omb.Trainer(kind, cfg, lr=lr, weight_decay=WEIGHT_DECAY[kind], seed=0)
     batch = cfg[0]
     rows = cfg[7] if kind == "mlm" else batch
     if world > 1:
@@ -244,13 +270,31 @@ def main():
     # ---- value: resident inputs, device-timed ----
     tr.load_inputs([t.numpy() for t in pinned[0]])
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(ext)
-    for i in range(K):
-        tr.step_resident()
-    e1.record(ext)
-    barrier()
-    dev_ms = e0.elapsed_time(e1)
+    # A workload whose parameters, optimizer state and activations fit the 126 MB L2 is timed step by step with a 256 MB
+    # write in between (outside the timed pairs), so that no step finds its operands in cache.
+    flush_l2 = kind == "mlp"
+    if flush_l2:
+        scrub = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device=torch.device("cuda", local_rank))
+        pairs = []
+        for i in range(K):
+            with torch.cuda.stream(ext):
+                scrub.fill_(float(i))
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(ext)
+            tr.step_resident()
+            b.record(ext)
+            pairs.append((a, b))
+        barrier()
+        dev_ms = sum(a.elapsed_time(b) for a, b in pairs)
+        del scrub
+    else:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ext)
+        for i in range(K):
+            tr.step_resident()
+        e1.record(ext)
+        barrier()
+        dev_ms = e0.elapsed_time(e1)
     # ---- e2e: host batch in, loss out, every step ----
     barrier()
     t0 = time.perf_counter()
@@ -274,7 +318,7 @@ def main():
         prof_tr = tr
         if world == 1:
             # A fresh trainer without a graph so that every entry point is timed individually.
-            prof_tr = omb.Trainer(kind, cfg, lr=lr, weight_decay=0.01, seed=0)
+            prof_tr = omb.Trainer(kind, cfg, lr=lr, weight_decay=WEIGHT_DECAY[kind], seed=0)
             prof_tr.step(batches[0])
             prof_tr.step(batches[1])
             ctx.call("om_profile_reset", ctx.handle)
@@ -291,7 +335,7 @@ def main():
             n = C.c_int32()
             ctx.call("om_profile_read", ctx.handle, rows_buf, C.c_int32(128), C.byref(n))
             table = [(r.name.decode(), int(r.calls), r.ms, r.flops, r.bytes) for r in rows_buf[: n.value]]
-            gemm = [r for r in table if r[0].startswith(("om_linear", "om_matmul"))]
+            gemm = [r for r in table if r[3] > 0 and r[0].startswith(("om_linear", "om_matmul", "om_conv2d", "om_lstm"))]
             g_ms, g_fl, g_calls = sum(r[2] for r in gemm), sum(r[3] for r in gemm), sum(r[1] for r in gemm)
             total_ms = sum(r[2] for r in table)
             peaks = {}
@@ -311,13 +355,14 @@ def main():
                     peak, peak_src = 1590.0 / 2, "fallback bf16 1.59 PFLOP/s / 2"
             achieved = g_fl / (g_ms * 1e-3) / 1e12 if g_ms > 0 else 0.0
             roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
-                        "traffic": None, "kernel": "matrix products (om_linear_fwd / om_linear_bwd dgrad+wgrad)",
+                        "traffic": None, "kernel": "dense contractions: " + ", ".join(sorted({r[0] for r in gemm})),
                         "launches_per_step": g_calls / psteps, "avg_launch_ms": g_ms / max(g_calls, 1),
                         "share_of_step_device_time": g_ms / total_ms if total_ms else None, "peak_source": peak_src,
                         "by_entry_point_ms_per_step": {r[0]: round(r[2] / psteps, 4) for r in sorted(table, key=lambda r: -r[2])[:12]}}
             prof_tr.close()
             if not args.skip_cpu:
-                _, cpu = cpu_baseline(args.workload, steps=1 if args.workload != "c1" else 20, warmup=0 if args.workload != "c1" else 3)
+                _, cpu = cpu_baseline(args.workload, steps=1 if args.workload != "c1" else 20, warmup=0 if args.workload != "c1" else 3,
+                                      batch_override=args.cpu_batch)
 
     if rank == 0:
         samples = batch * world * K
@@ -326,7 +371,8 @@ def main():
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32" if args.fp32 else "tf32", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {desc}", "global_batch": batch * world, "parallelism": f"dp{world}",
-                       "l2": "per-step working set (weights, optimizer state, activations) exceeds the 126 MB L2; no flush needed",
+                       "l2": ("256 MB written between timed steps (the working set fits L2); e2e steps are not flushed" if flush_l2 else
+                              "per-step working set (weights, optimizer state, activations) exceeds the 126 MB L2; no flush needed"),
                        "graph": not args.no_graph, "final_loss": final_loss},
             "e2e": {"value": samples / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": int(kernels_per_step.value) * K if kernels_per_step.value else None,

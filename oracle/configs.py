@@ -153,3 +153,41 @@ def crnn_step(named, x, targets, target_lengths, t, state, lr=1e-3):
         s = state.setdefault(k, dict(m=np.zeros_like(p), v=np.zeros_like(p)))
         K.adam_step(p, grads[k], s["m"], s["v"], None, t, lr, 0.9, 0.999, 1e-8, 0.0, False, False)
     return loss, grads
+
+
+def cnn_init(in_ch, channels, classes, seed=0):
+    """Parameters and running statistics of the config-2 network: He-normal weights, zero biases, unit batch norms."""
+    rng = np.random.default_rng(seed)
+    named, running, c = {}, {}, in_ch
+    for i, o in enumerate(channels):
+        named[f"conv{i}.weight"] = (rng.standard_normal((o, c, 3, 3)) * np.sqrt(2.0 / (c * 9))).astype(np.float32)
+        named[f"conv{i}.bias"] = np.zeros(o, np.float32)
+        named[f"bn{i}.weight"], named[f"bn{i}.bias"] = np.ones(o, np.float32), np.zeros(o, np.float32)
+        running[f"bn{i}"] = (np.zeros(o, np.float32), np.ones(o, np.float32))
+        c = o
+    named["fc.weight"] = (rng.standard_normal((classes, c)) * np.sqrt(2.0 / c)).astype(np.float32)
+    named["fc.bias"] = np.zeros(classes, np.float32)
+    return named, running
+
+
+def crnn_init(channels, hidden, classes, seed=0):
+    """Parameters of the config-4 network, uniform(+-1/sqrt(fan_in)) as the reference's defaults."""
+    rng = np.random.default_rng(seed)
+    named, c = {}, 1
+
+    def uni(shape, fan):
+        b = 1.0 / np.sqrt(fan)
+        return rng.uniform(-b, b, shape).astype(np.float32)
+
+    for i, o in enumerate(channels):
+        named[f"conv{i}.weight"], named[f"conv{i}.bias"] = uni((o, c, 3, 3), c * 9), uni((o,), c * 9)
+        c = o
+    for layer in range(2):
+        inp = c if layer == 0 else 2 * hidden
+        for sfx in ("", "_reverse"):
+            named[f"lstm.weight_ih_l{layer}{sfx}"] = uni((4 * hidden, inp), hidden)
+            named[f"lstm.weight_hh_l{layer}{sfx}"] = uni((4 * hidden, hidden), hidden)
+            named[f"lstm.bias_ih_l{layer}{sfx}"] = uni((4 * hidden,), hidden)
+            named[f"lstm.bias_hh_l{layer}{sfx}"] = uni((4 * hidden,), hidden)
+    named["fc.weight"], named["fc.bias"] = uni((classes, 2 * hidden), 2 * hidden), uni((classes,), 2 * hidden)
+    return named
