@@ -6,6 +6,13 @@
 // input element adds the taps that touch it in increasing (ky, kx) order, which is the order of the reference's
 // scatter loop, so no atomics are needed. The weight gradient sums over images inside the kernel (fixed chunks of
 // images per CTA, partials combined in chunk order).
+//
+// With OM_TF32 set (and one group, TMA-describable pitches) the three products instead run on the tensor pipe as ONE
+// product each over all images: the unfolded input is laid out [K, N*P] (K = Cin*KH*KW taps, P = OH*OW pixels), the
+// output gradient is brought from [N, Cout, P] to [Cout, N*P], and
+//   forward  y_t [Cout, N*P] = W [Cout, K] * cols [K, N*P]          (then back to NCHW with the bias in the same pass)
+//   dgrad    dcols [K, N*P]  = W^T * g_t [Cout, N*P]                 (then the same col2im gather)
+//   wgrad    dW [Cout, K]    = g_t [Cout, N*P] * cols^T              (one product with k = N*P, fixed split of k)
 #include "om_common.cuh"
 
 namespace om {
@@ -15,6 +22,11 @@ int32_t gemm_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float*
 int32_t gemm_simt_batch_reduce(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
                                const float* B, int ldb, int64_t sB, float* partial, int64_t chunk_stride, int batch,
                                int batch_per_chunk);
+
+bool gemm_tc_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B,
+                       int ldb, const float* C, int ldc);
+int32_t gemm_tc(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb,
+                float* C, int ldc, int acc, const float* bias);
 
 struct ConvGeom {
   int n, cin, h, w, cout, kh, kw, sh, sw, pt, pl, dh, dw, groups, oh, ow;
@@ -33,7 +45,10 @@ static bool conv_geom(const om_conv_shape* s, ConvGeom* g) {
 }
 
 // cols[n][(c*KH+ky)*KW+kx][oy*OW+ox] = x[n][c][oy*sh-pt+ky*dh][ox*sw-pl+kx*dw], zero outside the image.
-__global__ void im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __restrict__ cols, int64_t total) {
+// The element of tap row k, image n, pixel p sits at k * k_stride + n * n_stride + p: (P, K*P) is the per-image layout
+// [N][K][P], (N*P, P) the all-images layout [K][N*P].
+__global__ void im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __restrict__ cols, int64_t total,
+                              int64_t k_stride, int64_t n_stride) {
   const int plane = g.oh * g.ow;
   const int kk_all = g.cin * g.kh * g.kw;
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -48,14 +63,13 @@ __global__ void im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __
     int iy = oy * g.sh - g.pt + ky * g.dh, ix = ox * g.sw - g.pl + kx * g.dw;
     float v = 0.f;
     if ((unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w) v = x[(((int64_t)n * g.cin + c) * g.h + iy) * g.w + ix];
-    cols[e] = v;
+    cols[(int64_t)kidx * k_stride + (int64_t)n * n_stride + p] = v;
   }
 }
 
 // dx[n][c][iy][ix] = sum over (ky, kx) in increasing order of dcols[n][(c,ky,kx)][oy*OW+ox] where the tap lands on (iy, ix).
-__global__ void col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restrict__ dx, int64_t total) {
-  const int plane = g.oh * g.ow;
-  const int64_t kk_all = (int64_t)g.cin * g.kh * g.kw;
+__global__ void col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restrict__ dx, int64_t total,
+                                     int64_t k_stride, int64_t n_stride) {
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t e = i; e < total; e += stride) {
@@ -63,7 +77,7 @@ __global__ void col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols
     int iy = (int)((e / g.w) % g.h);
     int c = (int)((e / ((int64_t)g.w * g.h)) % g.cin);
     int n = (int)(e / ((int64_t)g.w * g.h * g.cin));
-    const float* base = dcols + ((int64_t)n * kk_all + (int64_t)c * g.kh * g.kw) * plane;
+    const float* base = dcols + (int64_t)n * n_stride + (int64_t)c * g.kh * g.kw * k_stride;
     float acc = 0.f;
     for (int ky = 0; ky < g.kh; ky++) {
       int ty = iy + g.pt - ky * g.dh;
@@ -75,7 +89,7 @@ __global__ void col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols
         if (tx < 0 || tx % g.sw) continue;
         int ox = tx / g.sw;
         if (ox >= g.ow) continue;
-        acc += base[(int64_t)(ky * g.kw + kx) * plane + oy * g.ow + ox];
+        acc += base[(int64_t)(ky * g.kw + kx) * k_stride + oy * g.ow + ox];
       }
     }
     dx[e] = acc;
@@ -86,6 +100,35 @@ __global__ void add_plane_bias_kernel(float* __restrict__ y, const float* __rest
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t e = i; e < total; e += stride) y[e] += bias[(e / plane) % cout];
+}
+
+// t[c][n*plane + p] = g[n][c][p]: one float4 per thread when the plane allows it.
+__global__ void nchw_to_cnhw_kernel(const float* __restrict__ g, float* __restrict__ t, int n, int c, int plane, int64_t total) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t np = (int64_t)n * plane;
+  for (int64_t e = i; e < total; e += stride) {
+    int p = (int)(e % plane);
+    int64_t r = e / plane;
+    int ch = (int)(r % c);
+    int img = (int)(r / c);
+    t[(int64_t)ch * np + (int64_t)img * plane + p] = g[e];
+  }
+}
+// y[n][c][p] = t[c][n*plane + p] + bias[c]
+__global__ void cnhw_to_nchw_bias_kernel(const float* __restrict__ t, const float* __restrict__ bias, float* __restrict__ y, int n, int c,
+                                         int plane, int64_t total) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t np = (int64_t)n * plane;
+  for (int64_t e = i; e < total; e += stride) {
+    int p = (int)(e % plane);
+    int64_t r = e / plane;
+    int ch = (int)(r % c);
+    int img = (int)(r / c);
+    float v = t[(int64_t)ch * np + (int64_t)img * plane + p];
+    y[e] = bias ? v + bias[ch] : v;
+  }
 }
 
 // dbias[co] = sum over n (in order) of the double plane sums of g[n][co][:]. One CTA per channel.
@@ -226,10 +269,31 @@ __global__ void avgpool_bwd_kernel(PoolGeom g, int include_pad, const float* __r
   }
 }
 
-static int32_t unfold(om_ctx* ctx, const ConvGeom& g, const float* x, float** cols) {
+static int32_t unfold(om_ctx* ctx, const ConvGeom& g, const float* x, float** cols, bool all_images = false) {
   int64_t total = (int64_t)g.n * g.cin * g.kh * g.kw * g.oh * g.ow;
   OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)(total > 0 ? total : 1), false, (void**)cols));
-  if (total > 0) im2col_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, x, *cols, total);
+  const int64_t plane = (int64_t)g.oh * g.ow, kk_all = (int64_t)g.cin * g.kh * g.kw;
+  if (total > 0)
+    im2col_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, x, *cols, total, all_images ? g.n * plane : plane,
+                                                                     all_images ? plane : kk_all * plane);
+  return OM_OK;
+}
+
+// The all-images tensor-pipe formulation applies: TF32 asked for, one group, every pitch a multiple of four floats.
+static bool conv_on_tensor_pipe(om_ctx* ctx, const ConvGeom& g, bool need_w_kmajor) {
+  if (!(ctx->flags & OM_TF32) || g.groups != 1) return false;
+  const int64_t np = (int64_t)g.n * g.oh * g.ow;
+  const int kk = g.cin * g.kh * g.kw;
+  if (np > INT32_MAX || (np & 3)) return false;
+  if (need_w_kmajor && (kk & 3)) return false;          // W [Cout, K] is read with row pitch K
+  return (double)g.cout * kk * (double)np >= 32.0 * 32 * 32;
+}
+
+static int32_t to_cnhw(om_ctx* ctx, const ConvGeom& g, const float* gr, float** out) {
+  const int plane = g.oh * g.ow;
+  int64_t total = (int64_t)g.n * g.cout * plane;
+  OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)total, false, (void**)out));
+  nchw_to_cnhw_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(gr, *out, g.n, g.cout, plane, total);
   return OM_OK;
 }
 
@@ -247,6 +311,22 @@ int32_t om_conv2d_fwd(om_ctx* ctx, const om_conv_shape* s, const float* x, const
   const int cg = g.cin / g.groups, og = g.cout / g.groups, kk = cg * g.kh * g.kw, plane = g.oh * g.ow;
   if (g.n > 65535) return fail(ctx, OM_ERR_UNSUPPORTED, "om_conv2d_fwd: more than 65535 images in one call");
   ProfileScope prof(ctx, "om_conv2d_fwd", 2.0 * g.n * g.cout * (double)kk * plane, 4.0 * ((double)g.n * g.cin * g.h * g.w + (double)g.n * g.cout * plane));
+  if (conv_on_tensor_pipe(ctx, g, true)) {
+    const int np = g.n * plane;
+    float *cols = nullptr, *yt = nullptr;
+    OM_TRY(unfold(ctx, g, x, &cols, true));
+    int32_t st = pool_alloc(ctx, sizeof(float) * (size_t)g.cout * np, false, (void**)&yt);
+    if (st == OM_OK) st = gemm_tc(ctx, 0, 0, g.cout, np, kk, w, kk, cols, np, yt, np, 0, nullptr);
+    if (st == OM_OK) {
+      int64_t total = (int64_t)g.cout * np;
+      cnhw_to_nchw_bias_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(yt, bias, y, g.n, g.cout, plane, total);
+    }
+    pool_free(ctx, cols);
+    if (yt) pool_free(ctx, yt);
+    OM_TRY(st);
+    OM_LAUNCH_CHECK(ctx, "om_conv2d_fwd");
+    return OM_OK;
+  }
   float* cols = nullptr;
   OM_TRY(unfold(ctx, g, x, &cols));
   int32_t st = OM_OK;
@@ -276,6 +356,22 @@ int32_t om_conv2d_dgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, co
   float* dcols = nullptr;
   int64_t total_cols = (int64_t)g.n * g.groups * kk * plane;
   OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)total_cols, false, (void**)&dcols));
+  if (conv_on_tensor_pipe(ctx, g, true)) {
+    const int np = g.n * plane;
+    float* gt = nullptr;
+    int32_t st = to_cnhw(ctx, g, gr, &gt);
+    // dcols [K, N*P] = W^T [K, Cout] * g_t [Cout, N*P]
+    if (st == OM_OK) st = gemm_tc(ctx, 1, 0, kk, np, g.cout, w, kk, gt, np, dcols, np, 0, nullptr);
+    if (st == OM_OK) {
+      int64_t total = (int64_t)g.n * g.cin * g.h * g.w;
+      col2im_gather_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, dcols, dx, total, np, plane);
+    }
+    if (gt) pool_free(ctx, gt);
+    pool_free(ctx, dcols);
+    OM_TRY(st);
+    OM_LAUNCH_CHECK(ctx, "om_conv2d_dgrad");
+    return OM_OK;
+  }
   int32_t st = OM_OK;
   for (int grp = 0; grp < g.groups && st == OM_OK; grp++) {
     // dcols_n[kk, P] = W_g^T[kk, og] * g_n[og, P]
@@ -284,7 +380,8 @@ int32_t om_conv2d_dgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, co
   }
   if (st == OM_OK) {
     int64_t total = (int64_t)g.n * g.cin * g.h * g.w;
-    col2im_gather_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, dcols, dx, total);
+    col2im_gather_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, dcols, dx, total, plane,
+                                                                            (int64_t)g.cin * g.kh * g.kw * plane);
   }
   pool_free(ctx, dcols);
   OM_TRY(st);
@@ -303,6 +400,19 @@ int32_t om_conv2d_wgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, co
     return OM_OK;
   }
   ProfileScope prof(ctx, "om_conv2d_wgrad", 2.0 * g.n * g.cout * (double)kk * plane, 4.0 * ((double)g.n * g.cin * g.h * g.w + (double)g.n * g.cout * plane));
+  if (conv_on_tensor_pipe(ctx, g, false)) {
+    const int np = g.n * plane;
+    float *cols = nullptr, *gt = nullptr;
+    OM_TRY(unfold(ctx, g, x, &cols, true));
+    int32_t st = to_cnhw(ctx, g, gr, &gt);
+    // dW [Cout, K] = g_t [Cout, N*P] * cols^T [N*P, K]: both operands k-contiguous, k = N*P split in fixed slices.
+    if (st == OM_OK) st = gemm_tc(ctx, 0, 1, g.cout, kk, np, gt, np, cols, np, dw, kk, accumulate, nullptr);
+    pool_free(ctx, cols);
+    if (gt) pool_free(ctx, gt);
+    OM_TRY(st);
+    OM_LAUNCH_CHECK(ctx, "om_conv2d_wgrad");
+    return OM_OK;
+  }
   float* cols = nullptr;
   OM_TRY(unfold(ctx, g, x, &cols));
   // Images are summed inside the kernel in fixed chunks; the chunk size depends on the shape only.

@@ -54,6 +54,39 @@ def test_conv2d_fwd_bwd(ctx, K, n, cin, h, w, cout, k, stride, pad, groups):
     ctx.sync()
 
 
+@pytest.mark.parametrize("n,cin,h,w,cout,k,stride,pad", [
+    (8, 64, 16, 16, 128, 3, 2, 1), (16, 32, 16, 16, 64, 3, 1, 1), (4, 3, 32, 32, 64, 3, 1, 1), (6, 16, 10, 10, 24, 3, 1, 1),
+    (4, 128, 4, 4, 256, 3, 1, 1)])
+def test_conv2d_on_the_tensor_pipe(ctx, K, n, cin, h, w, cout, k, stride, pad):
+    """With OM_TF32 the three convolution products run as one tensor-pipe product over all images (TF32 operands, fp32
+    accumulation): forward, input gradient and weight gradient within the TF32 tier of the contract (1e-3 scaled).
+    Shapes whose pitches TMA cannot describe (K = 27 for the forward of a 3-channel input) stay on the fp32 kernel."""
+    ctx.set_flags(omb.OM_TF32)
+    try:
+        r = np.random.default_rng(n * 7 + cin)
+        x = r.standard_normal((n, cin, h, w)).astype(np.float32)
+        wt = (r.standard_normal((cout, cin, k, k)) * 0.2).astype(np.float32)
+        b = r.standard_normal(cout).astype(np.float32)
+        y_ref = K.conv2d_fwd(x, wt, b, stride, pad, 1, 1)
+        g = r.standard_normal(y_ref.shape).astype(np.float32)
+        dx_ref, dw_ref, _ = K.conv2d_bwd(g, x, wt, stride, pad, 1, 1)
+        s = ConvShape(n, cin, h, w, cout, k, k, stride, stride, pad, pad, pad, pad, 1, 1, 1)
+        X, W, Bv, G = ctx.to_device(x), ctx.to_device(wt), ctx.to_device(b), ctx.to_device(g)
+        Y, DX, DW = ctx.empty(y_ref.shape), ctx.empty(x.shape), ctx.empty(wt.shape)
+        ctx.call("om_conv2d_fwd", ctx.handle, C.byref(s), X.ptr, W.ptr, Bv.ptr, Y.ptr)
+        ctx.call("om_conv2d_dgrad", ctx.handle, C.byref(s), G.ptr, W.ptr, DX.ptr)
+        ctx.call("om_conv2d_wgrad", ctx.handle, C.byref(s), G.ptr, X.ptr, DW.ptr, i32(0))
+        ctx.sync()
+        assert scaled_diff(Y.numpy(), y_ref) <= 1e-3
+        assert scaled_diff(DX.numpy(), dx_ref) <= 1e-3
+        assert scaled_diff(DW.numpy(), dw_ref) <= 1e-3
+        ctx.call("om_conv2d_wgrad", ctx.handle, C.byref(s), G.ptr, X.ptr, DW.ptr, i32(1))
+        ctx.sync()
+        assert scaled_diff(DW.numpy(), 2 * dw_ref) <= 1e-3
+    finally:
+        ctx.set_flags(0)
+
+
 @pytest.mark.parametrize("kh,kw,sh,sw,ph,pw", [(2, 2, 2, 2, 0, 0), (4, 1, 4, 1, 0, 0), (3, 3, 2, 2, 1, 1), (2, 1, 2, 1, 0, 0), (3, 2, 1, 1, 1, 0)])
 def test_pooling(ctx, K, kh, kw, sh, sw, ph, pw):
     r = np.random.default_rng(kh * 10 + kw)
