@@ -182,19 +182,33 @@ bn_partial_kernel(const float* __restrict__ x, const float* __restrict__ g, cons
   double a = 0.0, b = 0.0;
   double mu = MODE == 1 ? mu64[ch] : 0.0;
   float mm = MODE == 2 ? mean[ch] : 0.f, s = MODE == 2 ? inv[ch] : 0.f;
-  for (int i = i0; i < i1; i++) {
-    const int64_t o = ((int64_t)i * c + ch) * plane;
-    for (int p = threadIdx.x; p < plane; p += kBnThreads) {
-      if (MODE == 0) {
-        a += (double)x[o + p];
-      } else if (MODE == 1) {
-        double d = (double)x[o + p] - mu;
-        a += d * d;
-      } else {
-        float gg = g[o + p];
-        a += (double)(gg * ((x[o + p] - mm) * s));
-        b += (double)gg;
-      }
+  // The slice's planes as one index space; with a plane that is a multiple of four a thread reads 16 bytes at a time.
+  const int64_t span = (int64_t)(i1 - i0) * plane;
+  auto term = [&](float xv, float gv) {
+    if (MODE == 0) {
+      a += (double)xv;
+    } else if (MODE == 1) {
+      double d = (double)xv - mu;
+      a += d * d;
+    } else {
+      a += (double)(gv * ((xv - mm) * s));
+      b += (double)gv;
+    }
+  };
+  if ((plane & 3) == 0) {
+    for (int64_t e = (int64_t)threadIdx.x * 4; e < span; e += kBnThreads * 4) {
+      const int i = i0 + (int)(e / plane);
+      const int64_t o = ((int64_t)i * c + ch) * plane + (e % plane);
+      const float4 xv = __ldg(reinterpret_cast<const float4*>(x + o));
+      float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (MODE == 2) gv = __ldg(reinterpret_cast<const float4*>(g + o));
+      term(xv.x, gv.x); term(xv.y, gv.y); term(xv.z, gv.z); term(xv.w, gv.w);
+    }
+  } else {
+    for (int64_t e = threadIdx.x; e < span; e += kBnThreads) {
+      const int i = i0 + (int)(e / plane);
+      const int64_t o = ((int64_t)i * c + ch) * plane + (e % plane);
+      term(x[o], MODE == 2 ? g[o] : 0.f);
     }
   }
   a = wsum_d(a);
@@ -251,37 +265,67 @@ __global__ void bn_eval_stats_kernel(const float* __restrict__ rm, const float* 
   inv[ch] = 1.0f / sqrtf(rv[ch] + eps);
 }
 
-// grid.x = n*c planes (grid-stride), threads stride the plane.
-__global__ void bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
-                                const float* __restrict__ mean, const float* __restrict__ inv, int64_t planes, int32_t c,
-                                int32_t plane, float* __restrict__ y) {
-  for (int64_t pl = blockIdx.x; pl < planes; pl += gridDim.x) {
-    int ch = (int)(pl % c);
-    float mm = mean[ch], s = inv[ch], gg = gamma[ch], bb = beta[ch];
-    const float* xp = x + pl * plane;
-    float* yp = y + pl * plane;
-    for (int p = threadIdx.x; p < plane; p += blockDim.x) yp[p] = (((xp[p] - mm) * s) * gg) + bb;
+// Element-wise over the whole tensor, VEC consecutive elements of one plane per thread (VEC == 4: plane % 4 == 0).
+template <int VEC>
+__global__ void __launch_bounds__(256)
+bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                const float* __restrict__ mean, const float* __restrict__ inv, int64_t total, int32_t c, int32_t plane,
+                float* __restrict__ y) {
+  int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * VEC;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x * VEC;
+  for (int64_t e = i; e < total; e += stride) {
+    const int ch = (int)((e / plane) % c);
+    const float mm = mean[ch], s = inv[ch], gg = gamma[ch], bb = beta[ch];
+    if (VEC == 4) {
+      float4 v = __ldg(reinterpret_cast<const float4*>(x + e));
+      v.x = (((v.x - mm) * s) * gg) + bb; v.y = (((v.y - mm) * s) * gg) + bb;
+      v.z = (((v.z - mm) * s) * gg) + bb; v.w = (((v.w - mm) * s) * gg) + bb;
+      *reinterpret_cast<float4*>(y + e) = v;
+    } else {
+      y[e] = (((x[e] - mm) * s) * gg) + bb;
+    }
   }
 }
 
-__global__ void bn_bwd_apply_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
-                                    const float* __restrict__ mean, const float* __restrict__ inv,
-                                    const double* __restrict__ pa, const double* __restrict__ pb, int slices, double m,
-                                    int64_t planes, int32_t c, int32_t plane, int training, float* __restrict__ dx) {
-  for (int64_t pl = blockIdx.x; pl < planes; pl += gridDim.x) {
-    int ch = (int)(pl % c);
-    double sg = 0.0, sb = 0.0;
-    for (int s = 0; s < slices; s++) {
-      sg += pa[(int64_t)s * c + ch];
-      sb += pb[(int64_t)s * c + ch];
+// Per-channel scalars of the backward: k = gamma * inv, cb = mean(g), cg = mean(g * xhat), from the slice partials.
+__global__ void bn_bwd_coef_kernel(const float* __restrict__ gamma, const float* __restrict__ inv, const double* __restrict__ pa,
+                                   const double* __restrict__ pb, int slices, double m, int32_t c, float* __restrict__ coef) {
+  int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= c) return;
+  double sg = 0.0, sb = 0.0;
+  for (int s = 0; s < slices; s++) {
+    sg += pa[(int64_t)s * c + ch];
+    sb += pb[(int64_t)s * c + ch];
+  }
+  coef[ch] = gamma[ch] * inv[ch];
+  coef[c + ch] = (float)(sb / m);
+  coef[2 * c + ch] = (float)(sg / m);
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(256)
+bn_bwd_apply_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ mean,
+                    const float* __restrict__ inv, const float* __restrict__ coef, int64_t total, int32_t c, int32_t plane,
+                    int training, float* __restrict__ dx) {
+  int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * VEC;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x * VEC;
+  for (int64_t e = i; e < total; e += stride) {
+    const int ch = (int)((e / plane) % c);
+    const float mm = mean[ch], s = inv[ch], k = coef[ch], cb = coef[c + ch], cg = coef[2 * c + ch];
+    if (VEC == 4) {
+      const float4 gv = __ldg(reinterpret_cast<const float4*>(g + e));
+      const float4 xv = __ldg(reinterpret_cast<const float4*>(x + e));
+      float4 o;
+      if (training) {
+        o.x = k * ((gv.x - cb) - (((xv.x - mm) * s) * cg)); o.y = k * ((gv.y - cb) - (((xv.y - mm) * s) * cg));
+        o.z = k * ((gv.z - cb) - (((xv.z - mm) * s) * cg)); o.w = k * ((gv.w - cb) - (((xv.w - mm) * s) * cg));
+      } else {
+        o.x = k * gv.x; o.y = k * gv.y; o.z = k * gv.z; o.w = k * gv.w;
+      }
+      *reinterpret_cast<float4*>(dx + e) = o;
+    } else {
+      dx[e] = training ? k * ((g[e] - cb) - (((x[e] - mm) * s) * cg)) : k * g[e];
     }
-    float mm = mean[ch], s = inv[ch], k = gamma[ch] * s;
-    float cb = (float)(sb / m), cg = (float)(sg / m);
-    const float* xp = x + pl * plane;
-    const float* gp = g + pl * plane;
-    float* dp = dx + pl * plane;
-    for (int p = threadIdx.x; p < plane; p += blockDim.x)
-      dp[p] = training ? k * ((gp[p] - cb) - (((xp[p] - mm) * s) * cg)) : k * gp[p];
   }
 }
 
@@ -367,8 +411,9 @@ int32_t om_batchnorm_fwd(om_ctx* ctx, const float* x, const float* gamma, const 
   }
   int64_t planes = (int64_t)n * c;
   if (planes > 0 && plane > 0) {
-    int threads = plane >= 256 ? 256 : (plane >= 64 ? 64 : 32);
-    bn_apply_kernel<<<(unsigned)std::min<int64_t>(planes, (int64_t)ctx->sm_count * 16), threads, 0, ctx->stream>>>(x, gamma, beta, mean, inv, planes, c, plane, y);
+    const int64_t total = planes * plane;
+    if ((plane & 3) == 0) bn_apply_kernel<4><<<grid_for(ctx, total / 4, 256), 256, 0, ctx->stream>>>(x, gamma, beta, mean, inv, total, c, plane, y);
+    else bn_apply_kernel<1><<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(x, gamma, beta, mean, inv, total, c, plane, y);
   }
   OM_LAUNCH_CHECK(ctx, "om_batchnorm_fwd");
   return OM_OK;
@@ -389,9 +434,13 @@ int32_t om_batchnorm_bwd(om_ctx* ctx, const float* g, const float* x, const floa
   bn_partial_kernel<2><<<dim3(c, slices), kBnThreads, 0, ctx->stream>>>(x, g, nullptr, mean, inv, n, c, plane, ipc, pa, pb);
   int64_t planes = (int64_t)n * c;
   if (dx && planes > 0 && plane > 0) {
-    int threads = plane >= 256 ? 256 : (plane >= 64 ? 64 : 32);
-    bn_bwd_apply_kernel<<<(unsigned)std::min<int64_t>(planes, (int64_t)ctx->sm_count * 16), threads, 0, ctx->stream>>>(
-        g, x, gamma, mean, inv, pa, pb, slices, (double)n * plane, planes, c, plane, training, dx);
+    float* coef = nullptr;
+    OM_TRY(pool_alloc(ctx, sizeof(float) * 3 * (size_t)c, false, (void**)&coef));
+    bn_bwd_coef_kernel<<<(unsigned)ceil_div(c, 128), 128, 0, ctx->stream>>>(gamma, inv, pa, pb, slices, (double)n * plane, c, coef);
+    const int64_t total = planes * plane;
+    if ((plane & 3) == 0) bn_bwd_apply_kernel<4><<<grid_for(ctx, total / 4, 256), 256, 0, ctx->stream>>>(g, x, mean, inv, coef, total, c, plane, training, dx);
+    else bn_bwd_apply_kernel<1><<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, x, mean, inv, coef, total, c, plane, training, dx);
+    pool_free(ctx, coef);
   }
   if (dgamma || dbeta)
     column_partials_finish_kernel<<<(unsigned)ceil_div(c, 32), 512, 0, ctx->stream>>>(pa, pb, slices, c, dgamma, dbeta, accumulate_params);

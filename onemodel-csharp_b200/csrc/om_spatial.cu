@@ -44,40 +44,46 @@ static bool conv_geom(const om_conv_shape* s, ConvGeom* g) {
   return g->oh >= 1 && g->ow >= 1;
 }
 
-// cols[n][(c*KH+ky)*KW+kx][oy*OW+ox] = x[n][c][oy*sh-pt+ky*dh][ox*sw-pl+kx*dw], zero outside the image.
+// cols[(c*KH+ky)*KW+kx][n][oy*OW+ox] = x[n][c][oy*sh-pt+ky*dh][ox*sw-pl+kx*dw], zero outside the image.
 // The element of tap row k, image n, pixel p sits at k * k_stride + n * n_stride + p: (P, K*P) is the per-image layout
-// [N][K][P], (N*P, P) the all-images layout [K][N*P].
-__global__ void im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __restrict__ cols, int64_t total,
-                              int64_t k_stride, int64_t n_stride) {
+// [N][K][P], (N*P, P) the all-images layout [K][N*P]. blockIdx.y is the tap row; a thread owns VEC consecutive pixels
+// of one image (VEC == 4 needs P, the strides and the base to be multiples of four: one 16-byte store).
+template <int VEC>
+__global__ void __launch_bounds__(256)
+im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __restrict__ cols, int64_t pixels_all, int64_t k_stride, int64_t n_stride) {
   const int plane = g.oh * g.ow;
-  const int kk_all = g.cin * g.kh * g.kw;
-  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t e = i; e < total; e += stride) {
-    int p = (int)(e % plane);
-    int64_t r = e / plane;
-    int kidx = (int)(r % kk_all);
-    int n = (int)(r / kk_all);
-    int kx = kidx % g.kw, ky = (kidx / g.kw) % g.kh, c = kidx / (g.kw * g.kh);
-    int oy = p / g.ow, ox = p % g.ow;
-    int iy = oy * g.sh - g.pt + ky * g.dh, ix = ox * g.sw - g.pl + kx * g.dw;
-    float v = 0.f;
-    if ((unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w) v = x[(((int64_t)n * g.cin + c) * g.h + iy) * g.w + ix];
-    cols[(int64_t)kidx * k_stride + (int64_t)n * n_stride + p] = v;
+  const int kidx = blockIdx.y;
+  const int kx = kidx % g.kw, ky = (kidx / g.kw) % g.kh, c = kidx / (g.kw * g.kh);
+  int64_t q0 = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * VEC;
+  int64_t qstride = (int64_t)gridDim.x * blockDim.x * VEC;
+  for (int64_t q = q0; q < pixels_all; q += qstride) {
+    const int n = (int)(q / plane);
+    const int p = (int)(q - (int64_t)n * plane);
+    const float* xc = x + ((int64_t)n * g.cin + c) * g.h * g.w;
+    float v[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; j++) {
+      const int pj = p + j;
+      const int oy = pj / g.ow, ox = pj - oy * g.ow;
+      const int iy = oy * g.sh - g.pt + ky * g.dh, ix = ox * g.sw - g.pl + kx * g.dw;
+      v[j] = ((unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w) ? __ldg(xc + iy * g.w + ix) : 0.f;
+    }
+    float* dst = cols + (int64_t)kidx * k_stride + (int64_t)n * n_stride + p;
+    if (VEC == 4) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+    else dst[0] = v[0];
   }
 }
 
-// dx[n][c][iy][ix] = sum over (ky, kx) in increasing order of dcols[n][(c,ky,kx)][oy*OW+ox] where the tap lands on (iy, ix).
-__global__ void col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restrict__ dx, int64_t total,
-                                     int64_t k_stride, int64_t n_stride) {
-  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t e = i; e < total; e += stride) {
-    int ix = (int)(e % g.w);
-    int iy = (int)((e / g.w) % g.h);
-    int c = (int)((e / ((int64_t)g.w * g.h)) % g.cin);
-    int n = (int)(e / ((int64_t)g.w * g.h * g.cin));
-    const float* base = dcols + (int64_t)n * n_stride + (int64_t)c * g.kh * g.kw * k_stride;
+// dx[n][c][iy][ix] = sum over (ky, kx) in increasing order of dcols[(c,ky,kx)][n][oy*OW+ox] where the tap lands on (iy, ix).
+// blockIdx.y = channel, blockIdx.z = image, threads over the input plane.
+__global__ void __launch_bounds__(256)
+col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restrict__ dx, int64_t k_stride, int64_t n_stride) {
+  const int c = blockIdx.y, n = blockIdx.z;
+  const int hw = g.h * g.w;
+  const float* base = dcols + (int64_t)n * n_stride + (int64_t)c * g.kh * g.kw * k_stride;
+  float* out = dx + ((int64_t)n * g.cin + c) * hw;
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < hw; e += gridDim.x * blockDim.x) {
+    const int iy = e / g.w, ix = e - iy * g.w;
     float acc = 0.f;
     for (int ky = 0; ky < g.kh; ky++) {
       int ty = iy + g.pt - ky * g.dh;
@@ -92,7 +98,7 @@ __global__ void col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols
         acc += base[(int64_t)(ky * g.kw + kx) * k_stride + oy * g.ow + ox];
       }
     }
-    dx[e] = acc;
+    out[e] = acc;
   }
 }
 
@@ -102,44 +108,60 @@ __global__ void add_plane_bias_kernel(float* __restrict__ y, const float* __rest
   for (int64_t e = i; e < total; e += stride) y[e] += bias[(e / plane) % cout];
 }
 
-// t[c][n*plane + p] = g[n][c][p]: one float4 per thread when the plane allows it.
-__global__ void nchw_to_cnhw_kernel(const float* __restrict__ g, float* __restrict__ t, int n, int c, int plane, int64_t total) {
-  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+// t[c][n*plane + p] = g[n][c][p]. A thread moves VEC consecutive pixels of one plane (VEC == 4: plane a multiple of four).
+template <int VEC>
+__global__ void __launch_bounds__(256)
+nchw_to_cnhw_kernel(const float* __restrict__ g, float* __restrict__ t, int n, int c, int plane, int64_t total) {
+  int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * VEC;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x * VEC;
   const int64_t np = (int64_t)n * plane;
   for (int64_t e = i; e < total; e += stride) {
-    int p = (int)(e % plane);
-    int64_t r = e / plane;
-    int ch = (int)(r % c);
-    int img = (int)(r / c);
-    t[(int64_t)ch * np + (int64_t)img * plane + p] = g[e];
+    const int64_t r = e / plane;
+    const int p = (int)(e - r * plane);
+    const int img = (int)(r / c), ch = (int)(r - (int64_t)img * c);
+    float* dst = t + (int64_t)ch * np + (int64_t)img * plane + p;
+    if (VEC == 4) *reinterpret_cast<float4*>(dst) = __ldg(reinterpret_cast<const float4*>(g + e));
+    else *dst = g[e];
   }
 }
 // y[n][c][p] = t[c][n*plane + p] + bias[c]
-__global__ void cnhw_to_nchw_bias_kernel(const float* __restrict__ t, const float* __restrict__ bias, float* __restrict__ y, int n, int c,
-                                         int plane, int64_t total) {
-  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+template <int VEC>
+__global__ void __launch_bounds__(256)
+cnhw_to_nchw_bias_kernel(const float* __restrict__ t, const float* __restrict__ bias, float* __restrict__ y, int n, int c, int plane,
+                         int64_t total) {
+  int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * VEC;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x * VEC;
   const int64_t np = (int64_t)n * plane;
   for (int64_t e = i; e < total; e += stride) {
-    int p = (int)(e % plane);
-    int64_t r = e / plane;
-    int ch = (int)(r % c);
-    int img = (int)(r / c);
-    float v = t[(int64_t)ch * np + (int64_t)img * plane + p];
-    y[e] = bias ? v + bias[ch] : v;
+    const int64_t r = e / plane;
+    const int p = (int)(e - r * plane);
+    const int img = (int)(r / c), ch = (int)(r - (int64_t)img * c);
+    const float* src = t + (int64_t)ch * np + (int64_t)img * plane + p;
+    const float bv = bias ? bias[ch] : 0.f;
+    if (VEC == 4) {
+      float4 v = __ldg(reinterpret_cast<const float4*>(src));
+      if (bias) { v.x += bv; v.y += bv; v.z += bv; v.w += bv; }
+      *reinterpret_cast<float4*>(y + e) = v;
+    } else {
+      y[e] = bias ? *src + bv : *src;
+    }
   }
 }
 
-// dbias[co] = sum over n (in order) of the double plane sums of g[n][co][:]. One CTA per channel.
+// dbias[co] = sum over images of the plane sums of g[n][co][:], in double. Stage 1: CTA (co, slice) sums the planes of a
+// fixed slice of images (thread partials in a fixed tree); stage 2 adds the slices in order.
+constexpr int kDbiasSlices = 16;
 __global__ void __launch_bounds__(256)
-conv_dbias_kernel(const float* __restrict__ g, int n, int cout, int plane, float* __restrict__ dbias, int accumulate) {
+conv_dbias_partial_kernel(const float* __restrict__ g, int n, int cout, int plane, int per_slice, double* __restrict__ partial) {
   __shared__ double sm[256];
-  const int co = blockIdx.x;
+  const int co = blockIdx.x, slice = blockIdx.y;
+  const int i0 = slice * per_slice, i1 = min(n, i0 + per_slice);
   double acc = 0.0;
-  for (int i = 0; i < n; i++) {
-    const float* p = g + ((int64_t)i * cout + co) * plane;
-    for (int e = threadIdx.x; e < plane; e += 256) acc += (double)p[e];
+  const int64_t span = (int64_t)(i1 - i0) * plane;
+  for (int64_t e = threadIdx.x; e < span; e += 256) {
+    const int i = i0 + (int)(e / plane);
+    const int p = (int)(e % plane);
+    acc += (double)g[((int64_t)i * cout + co) * plane + p];
   }
   sm[threadIdx.x] = acc;
   __syncthreads();
@@ -147,7 +169,14 @@ conv_dbias_kernel(const float* __restrict__ g, int n, int cout, int plane, float
     if ((int)threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
     __syncthreads();
   }
-  if (threadIdx.x == 0) dbias[co] = accumulate ? dbias[co] + (float)sm[0] : (float)sm[0];
+  if (threadIdx.x == 0) partial[(int64_t)slice * cout + co] = sm[0];
+}
+__global__ void conv_dbias_finish_kernel(const double* __restrict__ partial, int slices, int cout, float* __restrict__ dbias, int accumulate) {
+  int co = blockIdx.x * blockDim.x + threadIdx.x;
+  if (co >= cout) return;
+  double t = 0.0;
+  for (int s = 0; s < slices; s++) t += partial[(int64_t)s * cout + co];
+  dbias[co] = accumulate ? dbias[co] + (float)t : (float)t;
 }
 
 __global__ void chunk_reduce_kernel(const float* __restrict__ part, int chunks, int64_t len, float* __restrict__ out, int accumulate) {
@@ -271,11 +300,18 @@ __global__ void avgpool_bwd_kernel(PoolGeom g, int include_pad, const float* __r
 
 static int32_t unfold(om_ctx* ctx, const ConvGeom& g, const float* x, float** cols, bool all_images = false) {
   int64_t total = (int64_t)g.n * g.cin * g.kh * g.kw * g.oh * g.ow;
-  OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)(total > 0 ? total : 1), false, (void**)cols));
   const int64_t plane = (int64_t)g.oh * g.ow, kk_all = (int64_t)g.cin * g.kh * g.kw;
-  if (total > 0)
-    im2col_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, x, *cols, total, all_images ? g.n * plane : plane,
-                                                                     all_images ? plane : kk_all * plane);
+  if (kk_all > 65535 || g.cin > 65535 || g.n > 65535)
+    return fail(ctx, OM_ERR_UNSUPPORTED, "convolution: more than 65535 images, input channels or taps per output in one call");
+  OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)(total > 0 ? total : 1), false, (void**)cols));
+  if (total > 0) {
+    const int64_t pixels_all = (int64_t)g.n * plane;
+    const bool vec = (plane & 3) == 0;
+    dim3 grid((unsigned)std::min<int64_t>(ceil_div(pixels_all, vec ? 1024 : 256), 65535), (unsigned)kk_all);
+    const int64_t ks = all_images ? pixels_all : plane, ns = all_images ? plane : kk_all * plane;
+    if (vec) im2col_kernel<4><<<grid, 256, 0, ctx->stream>>>(g, x, *cols, pixels_all, ks, ns);
+    else im2col_kernel<1><<<grid, 256, 0, ctx->stream>>>(g, x, *cols, pixels_all, ks, ns);
+  }
   return OM_OK;
 }
 
@@ -293,7 +329,8 @@ static int32_t to_cnhw(om_ctx* ctx, const ConvGeom& g, const float* gr, float** 
   const int plane = g.oh * g.ow;
   int64_t total = (int64_t)g.n * g.cout * plane;
   OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)total, false, (void**)out));
-  nchw_to_cnhw_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(gr, *out, g.n, g.cout, plane, total);
+  if ((plane & 3) == 0) nchw_to_cnhw_kernel<4><<<grid_for(ctx, total / 4, 256), 256, 0, ctx->stream>>>(gr, *out, g.n, g.cout, plane, total);
+  else nchw_to_cnhw_kernel<1><<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(gr, *out, g.n, g.cout, plane, total);
   return OM_OK;
 }
 
@@ -319,7 +356,8 @@ int32_t om_conv2d_fwd(om_ctx* ctx, const om_conv_shape* s, const float* x, const
     if (st == OM_OK) st = gemm_tc(ctx, 0, 0, g.cout, np, kk, w, kk, cols, np, yt, np, 0, nullptr);
     if (st == OM_OK) {
       int64_t total = (int64_t)g.cout * np;
-      cnhw_to_nchw_bias_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(yt, bias, y, g.n, g.cout, plane, total);
+      if ((plane & 3) == 0) cnhw_to_nchw_bias_kernel<4><<<grid_for(ctx, total / 4, 256), 256, 0, ctx->stream>>>(yt, bias, y, g.n, g.cout, plane, total);
+      else cnhw_to_nchw_bias_kernel<1><<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(yt, bias, y, g.n, g.cout, plane, total);
     }
     pool_free(ctx, cols);
     if (yt) pool_free(ctx, yt);
@@ -363,8 +401,8 @@ int32_t om_conv2d_dgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, co
     // dcols [K, N*P] = W^T [K, Cout] * g_t [Cout, N*P]
     if (st == OM_OK) st = gemm_tc(ctx, 1, 0, kk, np, g.cout, w, kk, gt, np, dcols, np, 0, nullptr);
     if (st == OM_OK) {
-      int64_t total = (int64_t)g.n * g.cin * g.h * g.w;
-      col2im_gather_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, dcols, dx, total, np, plane);
+      dim3 cgrid((unsigned)std::min<int64_t>(ceil_div((int64_t)g.h * g.w, 256), 64), (unsigned)g.cin, (unsigned)g.n);
+      col2im_gather_kernel<<<cgrid, 256, 0, ctx->stream>>>(g, dcols, dx, np, plane);
     }
     if (gt) pool_free(ctx, gt);
     pool_free(ctx, dcols);
@@ -379,9 +417,8 @@ int32_t om_conv2d_dgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, co
                    (int64_t)g.cout * plane, dcols + (size_t)grp * kk * plane, plane, (int64_t)g.groups * kk * plane, g.n, 0);
   }
   if (st == OM_OK) {
-    int64_t total = (int64_t)g.n * g.cin * g.h * g.w;
-    col2im_gather_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, dcols, dx, total, plane,
-                                                                            (int64_t)g.cin * g.kh * g.kw * plane);
+    dim3 cgrid((unsigned)std::min<int64_t>(ceil_div((int64_t)g.h * g.w, 256), 64), (unsigned)g.cin, (unsigned)g.n);
+    col2im_gather_kernel<<<cgrid, 256, 0, ctx->stream>>>(g, dcols, dx, plane, (int64_t)g.cin * g.kh * g.kw * plane);
   }
   pool_free(ctx, dcols);
   OM_TRY(st);
@@ -441,7 +478,16 @@ int32_t om_conv2d_dbias(om_ctx* ctx, const om_conv_shape* s, const float* gr, fl
   ConvGeom g;
   if (!s || !conv_geom(s, &g)) return fail(ctx, OM_ERR_SHAPE, "Invalid convolution geometry.");
   ProfileScope prof(ctx, "om_conv2d_dbias", 0, 4.0 * g.n * g.cout * (double)g.oh * g.ow);
-  conv_dbias_kernel<<<g.cout, 256, 0, ctx->stream>>>(gr, g.n, g.cout, g.oh * g.ow, dbias, accumulate);
+  if (g.n == 0) {
+    if (!accumulate) OM_CUDA(ctx, cudaMemsetAsync(dbias, 0, sizeof(float) * (size_t)g.cout, ctx->stream));
+    return OM_OK;
+  }
+  const int slices = g.n < kDbiasSlices ? g.n : kDbiasSlices, per_slice = (int)ceil_div(g.n, slices);
+  double* partial = nullptr;
+  OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)slices * g.cout, false, (void**)&partial));
+  conv_dbias_partial_kernel<<<dim3(g.cout, slices), 256, 0, ctx->stream>>>(gr, g.n, g.cout, g.oh * g.ow, per_slice, partial);
+  conv_dbias_finish_kernel<<<(unsigned)ceil_div(g.cout, 128), 128, 0, ctx->stream>>>(partial, slices, g.cout, dbias, accumulate);
+  pool_free(ctx, partial);
   OM_LAUNCH_CHECK(ctx, "om_conv2d_dbias");
   return OM_OK;
 }

@@ -66,7 +66,82 @@ static void EmitSummed(Engine& e, BackwardRecord& r, const Tensor& g, bool negat
   }
 }
 
+// The record of Ops::LinearPacked (Ints = {rows, inF, outF, parts, hasBias}; inputs x, weights..., biases...): the input
+// gradient is one product over the packed weights; the weight and bias gradients are one product and one column sum
+// when the leaves' gradient buffers are adjacent like the parameters, else one per part on column slices of g.
+static void LinearPackedBackward(BackwardRecord& r, const Tensor& g) {
+  const Tensor& x = r.Saved(0);
+  const int rows = (int)r.Ints[0], inF = (int)r.Ints[1], outF = (int)r.Ints[2], parts = (int)r.Ints[3];
+  const bool hasBias = r.Ints[4] != 0;
+  Tensor gc = g.Contiguous();
+  const float* wpacked = r.Saved(1).Data();
+  Tensor dx;
+  if (r.NeedsInputGrad(0)) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+  std::vector<float*> wp(parts, nullptr), bp(parts, nullptr);
+  std::vector<bool> wacc(parts, false), bacc(parts, false), wleaf(parts, false), bleaf(parts, false);
+  std::vector<Tensor> wtmp(parts), btmp(parts);
+  std::vector<int> outs(parts);
+  for (int i = 0; i < parts; i++) {
+    outs[i] = r.InputShapes[1 + i][0];
+    if (r.NeedsInputGrad(1 + i)) {
+      bool acc = false;
+      wleaf[i] = Engine::LeafTarget(r, 1 + i, &wp[i], &acc);
+      wacc[i] = acc;
+      if (!wleaf[i]) {
+        wtmp[i] = Tensor::Create(DType::F32, r.InputShapes[1 + i]);
+        wp[i] = wtmp[i].Data();
+      }
+    }
+    if (hasBias && r.NeedsInputGrad(1 + parts + i)) {
+      bool acc = false;
+      bleaf[i] = Engine::LeafTarget(r, 1 + parts + i, &bp[i], &acc);
+      bacc[i] = acc;
+      if (!bleaf[i]) {
+        btmp[i] = Tensor::Create(DType::F32, r.InputShapes[1 + parts + i]);
+        bp[i] = btmp[i].Data();
+      }
+    }
+  }
+  auto packed = [&](const std::vector<float*>& ptr, const std::vector<bool>& acc, bool weights) {
+    for (int i = 0; i < parts; i++) {
+      if (!ptr[i] || acc[i] != acc[0]) return false;
+      if (i > 0 && ptr[i] != ptr[i - 1] + (size_t)outs[i - 1] * (weights ? inF : 1)) return false;
+    }
+    return true;
+  };
+  const bool wp_one = packed(wp, wacc, true), bp_one = hasBias && packed(bp, bacc, false);
+  // Input gradient (+ the packed weight / bias gradients when they can ride along).
+  if (!dx.IsEmpty() || wp_one || bp_one) {
+    if (wp_one && bp_one && wacc[0] != bacc[0]) {
+      Check(om_linear_bwd_ld(C(), gc.Data(), outF, x.Data(), wpacked, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), wp[0], nullptr, wacc[0]));
+      Check(om_linear_bwd_ld(C(), gc.Data(), outF, x.Data(), wpacked, rows, inF, outF, nullptr, nullptr, bp[0], bacc[0]));
+    } else {
+      Check(om_linear_bwd_ld(C(), gc.Data(), outF, x.Data(), wpacked, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(),
+                             wp_one ? wp[0] : nullptr, bp_one ? bp[0] : nullptr, (wp_one ? wacc[0] : (bp_one && bacc[0])) ? 1 : 0));
+    }
+  }
+  int col = 0;
+  for (int i = 0; i < parts; i++) {
+    const float* gi = gc.Data() + col;
+    const float* wi = wpacked + (size_t)col * inF;
+    if (!wp_one && wp[i]) Check(om_linear_bwd_ld(C(), gi, outF, x.Data(), wi, rows, inF, outs[i], nullptr, wp[i], nullptr, wacc[i]));
+    if (hasBias && !bp_one && bp[i]) Check(om_linear_bwd_ld(C(), gi, outF, x.Data(), wi, rows, inF, outs[i], nullptr, nullptr, bp[i], bacc[i]));
+    col += outs[i];
+  }
+  // Emission order as for the single layer, part by part: bias, (input once), weight.
+  for (int i = 0; i < parts; i++)
+    if (hasBias && r.NeedsInputGrad(1 + parts + i)) {
+      if (bleaf[i]) Engine::LeafWritten(r, 1 + parts + i); else Engine::Emit(r, 1 + parts + i, btmp[i], true);
+    }
+  if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
+  for (int i = 0; i < parts; i++)
+    if (r.NeedsInputGrad(1 + i)) {
+      if (wleaf[i]) Engine::LeafWritten(r, 1 + i); else Engine::Emit(r, 1 + i, wtmp[i], true);
+    }
+}
+
 static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
+  if (r.Ints.size() == 5) return LinearPackedBackward(r, g);
   const Tensor& x = r.Saved(0);
   const Tensor& w = r.Saved(1);
   int rows = (int)r.Ints[0], inF = (int)r.Ints[1], outF = (int)r.Ints[2];
@@ -280,7 +355,23 @@ static void AttentionHeadsBackward(BackwardRecord& r, const Tensor& g) {
   if (!dv.IsEmpty()) Engine::Emit(r, 2, dv, true);
 }
 
+// The record of Ops::AttentionPacked (Ints = {maskStride, heads, 1}): q | k | v packed along the last axis of one tensor.
+static void AttentionPackedBackward(BackwardRecord& r, const Tensor& g) {
+  const Tensor &qkv = r.Saved(0), &mask = r.Saved(3);
+  const int heads = (int)r.Ints[1];
+  const int b = qkv.GetShape()[0], l = qkv.GetShape()[1], width = qkv.GetShape()[2] / 3, d = width / heads;
+  if (!r.NeedsInputGrad(0)) return;
+  Tensor gc = g.Contiguous();
+  Tensor dqkv = Tensor::Create(DType::F32, qkv.GetShape());
+  om_head_strides ps{(int64_t)l * 3 * width, (int64_t)d, (int64_t)3 * width}, gs{(int64_t)l * width, (int64_t)d, (int64_t)width};
+  Check(om_attention_bwd_strided(C(), gc.Data(), &gs, qkv.Data(), &ps, qkv.Data() + width, &ps, qkv.Data() + 2 * width, &ps,
+                                 mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0], nullptr, b, heads, l, l, d, (float)r.Floats[0],
+                                 dqkv.Data(), &ps, dqkv.Data() + width, &ps, dqkv.Data() + 2 * width, &ps));
+  Engine::Emit(r, 0, dqkv, true);
+}
+
 static void AttentionBackward(BackwardRecord& r, const Tensor& g) {
+  if (r.Ints.size() > 2) return AttentionPackedBackward(r, g);
   if (r.Ints.size() > 1) return AttentionHeadsBackward(r, g);
   const Tensor &q = r.Saved(0), &k = r.Saved(1), &v = r.Saved(2), &mask = r.Saved(3);
   int b = q.GetShape()[0], h = q.GetShape()[1], lq = q.GetShape()[2], d = q.GetShape()[3], lk = k.GetShape()[2];

@@ -60,6 +60,12 @@ Linear::Linear(int inFeatures, int outFeatures, Generator& g, bool bias) {
   if (bias) Bias = RegisterParameter("bias", InitUniform(g, bound, Shape{outFeatures}));
 }
 
+Linear::Linear(Tensor weight, Tensor bias) {
+  if (weight.Rank() != 2) throw TensorShapeException("Linear weights are [out, in].");
+  Weight = RegisterParameter("weight", weight);
+  if (!bias.IsEmpty()) Bias = RegisterParameter("bias", bias);
+}
+
 LayerNorm::LayerNorm(int width, float eps) : Epsilon(eps) {
   Gamma = RegisterParameter("weight", InitConstant(1.f, Shape{width}));
   Beta = RegisterParameter("bias", InitConstant(0.f, Shape{width}));
@@ -89,9 +95,20 @@ MultiHeadAttention::MultiHeadAttention(int width, int heads, Generator& g) : Hea
   if (heads < 1) throw ArgumentOutOfRangeException("heads must be at least 1.");
   if (width < 1 || width % heads != 0)
     throw std::invalid_argument("Width " + std::to_string(width) + " must be positive and divisible by the head count " + std::to_string(heads) + ".");
-  Q = RegisterModule("q", new Linear(width, width, g));
-  K = RegisterModule("k", new Linear(width, width, g));
-  V = RegisterModule("v", new Linear(width, width, g));
+  // The three input projections live in one [3 * width, width] allocation (and one [3 * width] bias) so that they run
+  // as a single product; q, k, v stay separate parameters (views), drawn in the reference's order: q.weight, q.bias,
+  // k.weight, k.bias, v.weight, v.bias (Layers.cs:479-492).
+  const float bound = 1.0f / sqrtf((float)width);
+  std::vector<float> hw((size_t)3 * width * width), hb((size_t)3 * width);
+  for (int i = 0; i < 3; i++) {
+    for (size_t j = 0; j < (size_t)width * width; j++) hw[(size_t)i * width * width + j] = g.Uniform(-bound, bound);
+    for (int j = 0; j < width; j++) hb[(size_t)i * width + j] = g.Uniform(-bound, bound);
+  }
+  Tensor pw = Tensor::FromHost(hw.data(), Shape{3 * width, width}), pb = Tensor::FromHost(hb.data(), Shape{3 * width});
+  Linear** slots[3] = {&Q, &K, &V};
+  const char* names[3] = {"q", "k", "v"};
+  for (int i = 0; i < 3; i++)
+    *slots[i] = RegisterModule(names[i], new Linear(pw.Slice(0, i * width, (i + 1) * width), pb.Slice(0, i * width, (i + 1) * width)));
   O = RegisterModule("o", new Linear(width, width, g));
 }
 
@@ -99,7 +116,11 @@ Tensor MultiHeadAttention::Forward(const Tensor& input, const Tensor& mask) {
   if (input.Rank() != 3) throw TensorShapeException("MultiHeadAttention needs [batch, length, width], not " + input.GetShape().ToString() + ".");
   // The head split and merge (Reshape + Permute(0, 2, 1, 3) around Ops.Attention in the reference) are folded into the
   // attention kernels' addressing: q, k, v stay [batch, length, width] and so does the result.
-  Tensor a = Ops::AttentionHeads(Q->Forward(input), K->Forward(input), V->Forward(input), Heads, mask);
+  Tensor a;
+  if (Ops::Adjacent({Q->Weight, K->Weight, V->Weight}) && Ops::Adjacent({Q->Bias, K->Bias, V->Bias}))
+    a = Ops::AttentionPacked(Ops::LinearPacked(input, {Q->Weight, K->Weight, V->Weight}, {Q->Bias, K->Bias, V->Bias}), Heads, mask);
+  else
+    a = Ops::AttentionHeads(Q->Forward(input), K->Forward(input), V->Forward(input), Heads, mask);
   return O->Forward(a);
 }
 

@@ -262,6 +262,12 @@ struct Ops {
   static Tensor Linear(const Tensor& x, const Tensor& weight, const Tensor& bias);
   static Tensor Attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& mask, float scale = 0.f);
   static Tensor AttentionHeads(const Tensor& q, const Tensor& k, const Tensor& v, int heads, const Tensor& mask, float scale = 0.f);
+  // Several Linear layers over the same input whose weights (and biases) are adjacent in memory, as one product:
+  // returns [..., sum of out features]. Throws when the parameters are not adjacent.
+  static Tensor LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, const std::vector<Tensor>& biases);
+  static bool Adjacent(const std::vector<Tensor>& parts);
+  // Self-attention over the packed projections [B, L, 3 * H * D] (q | k | v along the last axis).
+  static Tensor AttentionPacked(const Tensor& qkv, int heads, const Tensor& mask, float scale = 0.f);
   // One LSTM layer direction: returns y [T,B,H]; hn/cn receive the final states when not null.
   static Tensor LstmLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, const Tensor& bIh, const Tensor& bHh,
                           bool reverse, Tensor* hn = nullptr, Tensor* cn = nullptr);
@@ -303,6 +309,8 @@ class NnModule {
 struct Linear : NnModule {
   Tensor Weight, Bias;
   Linear(int inFeatures, int outFeatures, Generator& g, bool bias = true);
+  // Adopts existing storage (views into a packed allocation) as the parameters.
+  Linear(Tensor weight, Tensor bias);
   Tensor Forward(const Tensor& x) override { return Ops::Linear(x, Weight, Bias); }
 };
 struct LayerNorm : NnModule {

@@ -405,6 +405,77 @@ Tensor Ops::AttentionHeads(const Tensor& q, const Tensor& k, const Tensor& v, in
   return rec->Attach(r);
 }
 
+bool Ops::Adjacent(const std::vector<Tensor>& parts) {
+  for (size_t i = 0; i < parts.size(); i++) {
+    if (parts[i].IsEmpty() || !parts[i].IsContiguous() || parts[i].GetDType() != DType::F32) return false;
+    if (i > 0 && parts[i].Data() != parts[i - 1].Data() + parts[i - 1].Length()) return false;
+  }
+  return !parts.empty();
+}
+
+Tensor Ops::LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, const std::vector<Tensor>& biases) {
+  if (weights.empty() || weights.size() > 3 || (!biases.empty() && biases.size() != weights.size()))
+    throw TensorShapeException("LinearPacked needs one to three weight matrices and as many biases (or none).");
+  if (!Adjacent(weights) || (!biases.empty() && !Adjacent(biases)))
+    throw InvalidOperationException("LinearPacked: the parameters are not adjacent in memory.");
+  int inF = weights[0].GetShape()[1], outF = 0;
+  for (size_t i = 0; i < weights.size(); i++) {
+    if (weights[i].Rank() != 2 || weights[i].GetShape()[1] != inF || (!biases.empty() && biases[i].Length() != weights[i].GetShape()[0]))
+      throw TensorShapeException("LinearPacked: the weight matrices must share the input width and match their biases.");
+    outF += weights[i].GetShape()[0];
+  }
+  if (x.Rank() < 1 || x.GetShape()[x.Rank() - 1] != inF)
+    throw TensorShapeException("Linear: input " + x.GetShape().ToString() + " does not fit weights [" + std::to_string(outF) + "," + std::to_string(inF) + "] ([out, in]).");
+  int rows = (int)(x.Length() / std::max(1, inF));
+  Tensor xc = x.Contiguous();
+  Shape os = x.GetShape();
+  os.d[os.rank - 1] = outF;
+  Tensor r = NewOut(os);
+  Check(om_linear_fwd_ld(C(), xc.Data(), weights[0].Data(), biases.empty() ? nullptr : biases[0].Data(), rows, inF, outF, r.Data(), outF));
+  std::vector<Tensor> ins = {x};
+  for (auto& w : weights) ins.push_back(w);
+  for (auto& b : biases) ins.push_back(b);
+  bool rec_needed = false;
+  for (auto& t : ins) rec_needed = rec_needed || t.RequiresGrad();
+  if (!GradMode::Enabled() || !rec_needed) return r;
+  auto rec = BackwardRecord::Create(OpKind::Linear, 1 + (int)weights.size(), ins);
+  rec->Save(0, xc.Detach());
+  for (size_t i = 0; i < weights.size(); i++) rec->Save(1 + (int)i, weights[i].Detach());
+  rec->Ints = {rows, inF, outF, (int64_t)weights.size(), biases.empty() ? 0 : 1};
+  return rec->Attach(r);
+}
+
+Tensor Ops::AttentionPacked(const Tensor& qkv, int heads, const Tensor& mask, float scale) {
+  if (qkv.Rank() != 3 || heads < 1 || qkv.GetShape()[2] % (3 * heads) != 0 || (qkv.GetShape()[2] / (3 * heads)) % 2 != 0)
+    throw TensorShapeException("Packed attention needs [B, L, 3*H*D] with even D, not " + qkv.GetShape().ToString() + ".");
+  RequireFloat32(qkv);
+  int b = qkv.GetShape()[0], l = qkv.GetShape()[1], width = qkv.GetShape()[2] / 3, d = width / heads;
+  int64_t maskStride = 0;
+  Tensor mc;
+  if (!mask.IsEmpty()) {
+    RequireFloat32(mask);
+    bool ok = (mask.Rank() == 2 && mask.GetShape()[0] == l && mask.GetShape()[1] == l) ||
+              (mask.Rank() == 3 && mask.GetShape()[0] == b && mask.GetShape()[1] == l && mask.GetShape()[2] == l);
+    if (!ok) throw TensorShapeException("The mask must be [" + std::to_string(l) + "," + std::to_string(l) + "] or [" +
+                                        std::to_string(b) + "," + std::to_string(l) + "," + std::to_string(l) + "], not " + mask.GetShape().ToString() + ".");
+    mc = mask.Contiguous().Detach();
+    maskStride = mask.Rank() == 2 ? 0 : (int64_t)l * l;
+  }
+  if (scale == 0.f || isnan(scale)) scale = 1.0f / sqrtf((float)d);
+  Tensor pc = qkv.Contiguous();
+  Tensor r = NewOut(Shape{b, l, width});
+  om_head_strides ps{(int64_t)l * 3 * width, (int64_t)d, (int64_t)3 * width}, os{(int64_t)l * width, (int64_t)d, (int64_t)width};
+  Check(om_attention_fwd_strided(C(), pc.Data(), &ps, pc.Data() + width, &ps, pc.Data() + 2 * width, &ps, mc.IsEmpty() ? nullptr : mc.Data(),
+                                 maskStride, b, heads, l, l, d, scale, r.Data(), &os, nullptr));
+  if (!Recording({&qkv})) return r;
+  auto rec = BackwardRecord::Create(OpKind::Attention, 4, {&qkv});
+  rec->Save(0, pc.Detach());
+  if (!mc.IsEmpty()) rec->Save(3, mc);
+  rec->Floats = {scale};
+  rec->Ints = {maskStride, heads, 1};
+  return rec->Attach(r);
+}
+
 Tensor Ops::Concat(const std::vector<Tensor>& xs, int axis) {
   if (xs.empty()) throw TensorShapeException("Concat needs at least one tensor.");
   int rank = xs[0].Rank();

@@ -191,7 +191,11 @@ static void BuildFlatGrads(omh_trainer* t) {
   int64_t off = 0;
   const int64_t bucket_elems = 6 * 1024 * 1024;  // ~25 MB of fp32
   int64_t bucket_begin = 0;
-  for (int i = (int)t->params.size() - 1; i >= 0; i--) {
+  // Parameters that are adjacent views of one allocation (the packed q, k, v projections) get gradients that are adjacent in the same
+  // order, so that their weight gradient can be written by one product.
+  const int np = (int)t->params.size();
+  std::vector<bool> placed(np, false);
+  auto place = [&](int i) {
     Tensor& p = t->params[i].second;
     auto meta = p.Autograd();
     Tensor view = t->flat_grads.View(p.GetShape(), ContiguousStrides(p.GetShape()), off);
@@ -204,6 +208,29 @@ static void BuildFlatGrads(omh_trainer* t) {
     }
     t->bucket_of[meta.get()] = (int)t->buckets.size();
     off += len;
+    placed[i] = true;
+  };
+  auto before = [&](int i) {   // the parameter whose storage ends where parameter i starts, or -1
+    for (int j = 0; j < np; j++)
+      if (j != i && !placed[j] && t->params[j].second.Storage() == t->params[i].second.Storage() &&
+          t->params[j].second.Data() + t->params[j].second.Length() == t->params[i].second.Data()) return j;
+    return -1;
+  };
+  auto after = [&](int i) {
+    for (int j = 0; j < np; j++)
+      if (j != i && !placed[j] && t->params[j].second.Storage() == t->params[i].second.Storage() &&
+          t->params[i].second.Data() + t->params[i].second.Length() == t->params[j].second.Data()) return j;
+    return -1;
+  };
+  for (int i = np - 1; i >= 0; i--) {
+    if (placed[i]) continue;
+    int first = i;
+    for (int guard = 0, j; guard < np && (j = before(first)) >= 0; guard++) first = j;
+    for (int cur = first; cur >= 0;) {
+      int nxt = after(cur);
+      place(cur);
+      cur = nxt;
+    }
   }
   t->buckets.push_back({bucket_begin, off, 0, 0});
   for (auto& kv : t->bucket_of) t->buckets[kv.second].total++;
