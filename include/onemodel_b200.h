@@ -177,6 +177,26 @@ int32_t om_fill(om_ctx* ctx, float* dst, float value, int64_t n);
  * (src/OneModel.Training/Optimizers.cs:222-228; Engine.cs:77-91). ptrs_host/len_host are host arrays. */
 int32_t om_zero(om_ctx* ctx, int32_t count, float* const* ptrs_host, const int64_t* len_host);
 
+/* y = x^p with the reference's exact cases for p in {1, 2, 0.5, -1} (Ops.Pow / PowScalar, Ops.GraphOps.cs:175-206), and
+ * dx = g * d/dx x^p (PowDerivative, BackwardGraphOps.cs:44-76); x is the saved input. */
+int32_t om_pow(om_ctx* ctx, const float* x, float exponent, float* y, int64_t n);
+int32_t om_pow_bwd(om_ctx* ctx, const float* g, const float* x, float exponent, float* dx, int64_t n);
+/* out = condition ? a : b over n contiguous elements (all three already broadcast to one shape, as Ops.Where does
+ * before its loop, Ops.GraphOps.cs:244-300). The condition is Int32, non-zero = true: this ABI has no one-byte tensor
+ * type, the binding widens the reference's Bool tensor when it uploads it. om_where_bwd: out = (condition == wanted) ? g : 0
+ * (WhereBackward, BackwardGraphOps.cs:78-103). */
+int32_t om_where(om_ctx* ctx, const int32_t* condition, const float* a, const float* b, float* out, int64_t n);
+int32_t om_where_bwd(om_ctx* ctx, const int32_t* condition, const float* g, int32_t wanted, float* out, int64_t n);
+/* Gather along one axis of data viewed as [outer, n, inner] with `count` indices (Int32 / Int64, negative counts from
+ * the end): out [outer, count, inner] (Ops.Gather, Ops.GraphOps.cs:306-394). An index outside the axis sets the device
+ * status word to OM_ERR_INDEX. om_gather_bwd: dx [outer, n, inner] = slices of g added per destination in increasing
+ * index position (GatherBackward, BackwardGraphOps.cs:105-139); every destination element is written (zero when no
+ * index points at it). */
+int32_t om_gather_fwd(om_ctx* ctx, const float* data, const void* ids, int32_t id_dtype, int64_t outer, int64_t count,
+                      int64_t n, int64_t inner, float* out);
+int32_t om_gather_bwd(om_ctx* ctx, const float* g, const void* ids, int32_t id_dtype, int64_t outer, int64_t count,
+                      int64_t n, int64_t inner, float* dx);
+
 /* ---- data movement and broadcast sums ---------------------------------------------------------------- */
 
 /* dst (strided) = src (strided) over `shape`, rank <= 8, strides in elements (negative allowed for Flip).
@@ -351,6 +371,15 @@ int32_t om_avgpool_bwd(om_ctx* ctx, const float* g, int32_t planes, int32_t h, i
                        int32_t kw, int32_t sh, int32_t sw, int32_t ph, int32_t pw, int32_t count_include_pad,
                        float* dx);
 
+/* Resize of NCHW planes [planes, H, W] to [planes, out_h, out_w]: mode 0 nearest (source index min(floor(dst*in/out), in-1)),
+ * mode 1 bilinear with or without aligned corners; the source coordinate rule of Ops.SourceCoord (Ops.Spatial.cs:200-235).
+ * Replaces Ops.Resize2d (Ops.Spatial.cs:148-197). The backward gathers, per input pixel, the weighted terms the
+ * reference scatters in output order (ResizeBackward, BackwardRecurrent.cs:371-412). */
+int32_t om_resize2d_fwd(om_ctx* ctx, const float* x, int64_t planes, int32_t h, int32_t w, int32_t out_h, int32_t out_w,
+                        int32_t mode, int32_t align_corners, float* y);
+int32_t om_resize2d_bwd(om_ctx* ctx, const float* g, int64_t planes, int32_t h, int32_t w, int32_t out_h, int32_t out_w,
+                        int32_t mode, int32_t align_corners, float* dx);
+
 /* ---- recurrent and CTC ---------------------------------------------------------------------------------- */
 
 /* One LSTM layer direction over x [T,B,I]: gates = x*W_ih^T + b_ih + h*W_hh^T + b_hh in i,f,g,o order.
@@ -369,6 +398,21 @@ int32_t om_lstm_layer_bwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, in
                           const float* c0, const float* gates, const float* c, const float* tanh_c,
                           float* dx, float* dw_ih, float* dw_hh, float* db_ih, float* db_hh, float* dh0,
                           float* dc0);
+
+/* One direction of one GRU layer over a whole sequence, PyTorch's gate formulation. x [T,B,I], w_ih [3H,I],
+ * w_hh [3H,H], b_ih / b_hh [3H] or NULL, h0 [B,H] or NULL (zeros). Outputs: y [T,B,H] and the saved slots of the
+ * backward: gates [T,B,3H] (activated r, z, n) and hn [T,B,H] (the hidden side of n, W_hn h' + b_hn).
+ * Replaces Ops.GruLayer (Ops.Recurrent.cs:148-260). */
+int32_t om_gru_layer_fwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* x,
+                         const float* w_ih, const float* w_hh, const float* b_ih, const float* b_hh,
+                         const float* h0, float* y, float* gates, float* hn);
+/* Backward through time of om_gru_layer_fwd from gy [T,B,H]. Each output may be NULL: dx [T,B,I], dw_ih [3H,I],
+ * dw_hh [3H,H], db_ih [3H] (column sums of the input-side gate gradients), db_hh [3H] (of the hidden-side ones,
+ * whose n column carries the factor r), dh0 [B,H]. Replaces GruBackward + ColumnSums (BackwardRecurrent.cs:115-246). */
+int32_t om_gru_layer_bwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* gy,
+                         const float* x, const float* y, const float* w_ih, const float* w_hh, const float* h0,
+                         const float* gates, const float* hn, float* dx, float* dw_ih, float* dw_hh,
+                         float* db_ih, float* db_hh, float* dh0);
 
 /* CTC negative log-likelihood per sequence from log-probabilities lp [T,B,C] (double-precision alpha
  * recursion in log space), targets concatenated (int32) with target_lengths[B], input_lengths[B].

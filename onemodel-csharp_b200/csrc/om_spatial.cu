@@ -298,6 +298,94 @@ __global__ void avgpool_bwd_kernel(PoolGeom g, int include_pad, const float* __r
   }
 }
 
+// ---- resize ---------------------------------------------------------------------------------------------------------------
+// Source coordinate of one output index (Ops.SourceCoord, Ops.Spatial.cs:200-235 of the reference). mode 0 nearest, 1 bilinear.
+__device__ __forceinline__ void source_coord(int mode, int align, int dst, int in_size, int out_size, int* i0, int* i1, float* lambda) {
+  if (mode == 0) {
+    float scale = (float)in_size / (float)out_size;
+    int v = (int)floorf((float)dst * scale);
+    *i0 = v < in_size - 1 ? v : in_size - 1;
+    *i1 = *i0;
+    *lambda = 0.f;
+    return;
+  }
+  float src;
+  if (align) {
+    float scale = out_size > 1 ? (float)(in_size - 1) / (float)(out_size - 1) : 0.f;
+    src = scale * (float)dst;
+  } else {
+    float scale = (float)in_size / (float)out_size;
+    src = (scale * ((float)dst + 0.5f)) - 0.5f;
+    if (src < 0.f) src = 0.f;
+  }
+  int a = (int)src;
+  if (a > in_size - 1) a = in_size - 1;
+  *i0 = a;
+  *i1 = a + (a < in_size - 1 ? 1 : 0);
+  *lambda = src - (float)a;
+}
+
+__global__ void resize_fwd_kernel(const float* __restrict__ x, int64_t planes, int h, int w, int oh, int ow, int mode, int align,
+                                  float* __restrict__ y) {
+  int64_t total = planes * oh * ow;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    int ox = (int)(i % ow), oy = (int)((i / ow) % oh);
+    int64_t pl = i / ((int64_t)ow * oh);
+    const float* sp = x + pl * h * w;
+    int y0, y1, x0, x1;
+    float ly, lx;
+    source_coord(mode, align, oy, h, oh, &y0, &y1, &ly);
+    source_coord(mode, align, ox, w, ow, &x0, &x1, &lx);
+    float v;
+    if (mode == 0) {
+      v = sp[y0 * w + x0];
+    } else {
+      float top = ((1.f - lx) * sp[y0 * w + x0]) + (lx * sp[y0 * w + x1]);
+      float bottom = ((1.f - lx) * sp[y1 * w + x0]) + (lx * sp[y1 * w + x1]);
+      v = ((1.f - ly) * top) + (ly * bottom);
+    }
+    y[i] = v;
+  }
+}
+
+// dx[pl][iy][ix]: the reference scatters every output pixel's four weighted terms in output order (ResizeBackward,
+// BackwardRecurrent.cs:371-412); here every input pixel gathers the same terms in the same order, so no atomics are needed.
+__global__ void resize_bwd_kernel(const float* __restrict__ g, int64_t planes, int h, int w, int oh, int ow, int mode, int align,
+                                  float* __restrict__ dx) {
+  int64_t total = planes * h * w;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    int ix = (int)(i % w), iy = (int)((i / w) % h);
+    int64_t pl = i / ((int64_t)w * h);
+    const float* gp = g + pl * oh * ow;
+    float acc = 0.f;
+    for (int oy = 0; oy < oh; oy++) {
+      int y0, y1;
+      float ly;
+      source_coord(mode, align, oy, h, oh, &y0, &y1, &ly);
+      if (y0 != iy && y1 != iy) continue;
+      for (int ox = 0; ox < ow; ox++) {
+        int x0, x1;
+        float lx;
+        source_coord(mode, align, ox, w, ow, &x0, &x1, &lx);
+        if (x0 != ix && x1 != ix) continue;
+        float gg = gp[oy * ow + ox];
+        if (mode == 0) {
+          acc += gg;
+        } else {
+          float t = (1.f - ly) * gg, b = ly * gg;
+          if (y0 == iy && x0 == ix) acc += (1.f - lx) * t;
+          if (y0 == iy && x1 == ix) acc += lx * t;
+          if (y1 == iy && x0 == ix) acc += (1.f - lx) * b;
+          if (y1 == iy && x1 == ix) acc += lx * b;
+        }
+      }
+    }
+    dx[i] = acc;
+  }
+}
+
 static int32_t unfold(om_ctx* ctx, const ConvGeom& g, const float* x, float** cols, bool all_images = false) {
   int64_t total = (int64_t)g.n * g.cin * g.kh * g.kw * g.oh * g.ow;
   const int64_t plane = (int64_t)g.oh * g.ow, kk_all = (int64_t)g.cin * g.kh * g.kw;
@@ -489,6 +577,33 @@ int32_t om_conv2d_dbias(om_ctx* ctx, const om_conv_shape* s, const float* gr, fl
   conv_dbias_finish_kernel<<<(unsigned)ceil_div(g.cout, 128), 128, 0, ctx->stream>>>(partial, slices, g.cout, dbias, accumulate);
   pool_free(ctx, partial);
   OM_LAUNCH_CHECK(ctx, "om_conv2d_dbias");
+  return OM_OK;
+}
+
+int32_t om_resize2d_fwd(om_ctx* ctx, const float* x, int64_t planes, int32_t h, int32_t w, int32_t out_h, int32_t out_w, int32_t mode,
+                        int32_t align_corners, float* y) {
+  OM_CHECK_CTX(ctx);
+  if (planes < 0 || h < 1 || w < 1 || out_h < 1 || out_w < 1 || mode < 0 || mode > 1)
+    return fail(ctx, OM_ERR_SHAPE, "Resize2d needs an (N,C,H,W) input and a positive output size (planes %lld, %dx%d -> %dx%d, mode %d)",
+                (long long)planes, h, w, out_h, out_w, mode);
+  int64_t total = planes * out_h * out_w;
+  if (total == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_resize2d_fwd", 0, 4.0 * (planes * (double)h * w + total));
+  resize_fwd_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(x, planes, h, w, out_h, out_w, mode, align_corners && mode == 1, y);
+  OM_LAUNCH_CHECK(ctx, "om_resize2d_fwd");
+  return OM_OK;
+}
+
+int32_t om_resize2d_bwd(om_ctx* ctx, const float* g, int64_t planes, int32_t h, int32_t w, int32_t out_h, int32_t out_w, int32_t mode,
+                        int32_t align_corners, float* dx) {
+  OM_CHECK_CTX(ctx);
+  if (planes < 0 || h < 1 || w < 1 || out_h < 1 || out_w < 1 || mode < 0 || mode > 1)
+    return fail(ctx, OM_ERR_SHAPE, "Resize2d backward: planes %lld, %dx%d -> %dx%d, mode %d", (long long)planes, h, w, out_h, out_w, mode);
+  int64_t total = planes * h * w;
+  if (total == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_resize2d_bwd", 0, 4.0 * (planes * (double)out_h * out_w + total));
+  resize_bwd_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, planes, h, w, out_h, out_w, mode, align_corners && mode == 1, dx);
+  OM_LAUNCH_CHECK(ctx, "om_resize2d_bwd");
   return OM_OK;
 }
 

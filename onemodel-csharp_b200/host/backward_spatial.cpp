@@ -72,6 +72,31 @@ static void LstmBackward(BackwardRecord& r, const Tensor& gy) {
   dwi.Done(r, 1); dwh.Done(r, 2); dbi.Done(r, 3); dbh.Done(r, 4);
 }
 
+static void GruBackward(BackwardRecord& r, const Tensor& gy) {
+  const Tensor &x = r.Saved(0), &wIh = r.Saved(1), &wHh = r.Saved(2), &gates = r.Saved(3), &hn = r.Saved(4), &y = r.Saved(5), &h0 = r.Saved(6);
+  bool reverse = r.Ints[0] != 0;
+  int steps = (int)r.Ints[1], batch = (int)r.Ints[2], inSize = (int)r.Ints[3], h = (int)r.Ints[4];
+  Tensor gc = gy.Contiguous();
+  Tensor dx, dh0;
+  if (r.NeedsInputGrad(0)) dx = Tensor::Create(DType::F32, x.GetShape());
+  if (r.NeedsInputGrad(5)) dh0 = Tensor::Create(DType::F32, Shape{batch, h});
+  GradSlot dwi(r, 1), dwh(r, 2), dbi(r, 3), dbh(r, 4);
+  auto Plain = [&](GradSlot& s, int i) {
+    if (s.needed && s.leaf && s.accumulate) {
+      s.leaf = false;
+      s.tmp = Tensor::Create(DType::F32, r.InputShapes[i]);
+      s.ptr = s.tmp.Data();
+    }
+  };
+  Plain(dwi, 1); Plain(dwh, 2); Plain(dbi, 3); Plain(dbh, 4);
+  Check(om_gru_layer_bwd(C(), reverse, steps, batch, inSize, h, gc.Data(), x.Data(), y.Data(), wIh.Data(), wHh.Data(),
+                         h0.IsEmpty() ? nullptr : h0.Data(), gates.Data(), hn.Data(), dx.IsEmpty() ? nullptr : dx.Data(), dwi.ptr, dwh.ptr,
+                         dbi.ptr, dbh.ptr, dh0.IsEmpty() ? nullptr : dh0.Data()));
+  if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
+  dwi.Done(r, 1); dwh.Done(r, 2); dbi.Done(r, 3); dbh.Done(r, 4);
+  if (!dh0.IsEmpty()) Engine::Emit(r, 5, dh0, true);
+}
+
 void RunSpatialBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
   (void)e;
   switch (r.Op) {
@@ -96,6 +121,7 @@ void RunSpatialBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
       break;
     }
     case OpKind::Lstm: LstmBackward(r, g); break;
+    case OpKind::Gru: GruBackward(r, g); break;
     case OpKind::CtcLoss: {
       const Tensor &lp = r.Saved(0), &targets = r.Saved(1), &ilen = r.Saved(2), &tlen = r.Saved(3);
       Tensor gc = g.Contiguous();
@@ -106,8 +132,7 @@ void RunSpatialBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
       Engine::Emit(r, 0, dx, true);
       break;
     }
-    default:
-      throw InvalidOperationException("No backward function for op kind " + std::to_string((int)r.Op) + ".");
+    default: RunGraphBackward(r, g); break;
   }
 }
 

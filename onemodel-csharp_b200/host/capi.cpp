@@ -190,6 +190,20 @@ OMH_API int32_t omh_call(const char* op, int32_t n_in, omh_tensor* const* in, in
     } else if (name == "max_pool2d") r = Ops::MaxPool2d(T(0), (int)I(0), (int)I(1), (int)I(2), (int)I(3), (int)I(4), (int)I(5));
     else if (name == "avg_pool2d") r = Ops::AvgPool2d(T(0), (int)I(0), (int)I(1), (int)I(2), (int)I(3), (int)I(4), (int)I(5), I(6) != 0);
     else if (name == "lstm_layer") r = Ops::LstmLayer(T(0), T(1), T(2), T(3), T(4), I(0) != 0);
+    else if (name == "conv_transpose2d") {
+      ConvTranspose2dParams p;
+      p.strideH = (int)I(0, 1); p.strideW = (int)I(1, 1); p.padH = (int)I(2); p.padW = (int)I(3); p.outPadH = (int)I(4); p.outPadW = (int)I(5);
+      p.dilH = (int)I(6, 1); p.dilW = (int)I(7, 1); p.groups = (int)I(8, 1);
+      r = Ops::ConvTranspose2d(T(0), T(1), T(2), p);
+    } else if (name == "resize2d") r = Ops::Resize2d(T(0), (int)I(0), (int)I(1), (int)I(2), I(3) != 0);
+    else if (name == "matmul_batched") r = Ops::MatMulBatched(T(0), T(1));
+    else if (name == "erf") r = Ops::Erf(T(0));
+    else if (name == "exp") r = Ops::Exp(T(0));
+    else if (name == "sqrt") r = Ops::Sqrt(T(0));
+    else if (name == "pow") r = Ops::Pow(T(0), (float)F(0, 1));
+    else if (name == "where") r = Ops::Where(T(0), T(1), T(2));
+    else if (name == "gather") r = Ops::Gather(T(0), T(1), (int)I(0));
+    else if (name == "gru_layer") r = Ops::GruLayer(T(0), T(1), T(2), T(3), T(4), T(5), I(0) != 0);
     else if (name == "ctc_loss") r = Ops::CtcLoss(T(0), T(1), T(2), T(3), (int)I(0), (int)I(1, 1), I(2) != 0);
     else if (name == "reshape") r = T(0).Reshape(ShapeFromInts(0));
     else if (name == "permute") {

@@ -224,10 +224,15 @@ class Engine {
 };
 
 void RunBackwardOp(Engine& e, BackwardRecord& r, const Tensor& g);
+void RunGraphBackward(BackwardRecord& r, const Tensor& g);
 
 // ---- ops ---------------------------------------------------------------------------------------------------------------
 struct Conv2dParams {
   int strideH = 1, strideW = 1, padTop = 0, padLeft = 0, padBottom = 0, padRight = 0, dilH = 1, dilW = 1, groups = 1;
+};
+
+struct ConvTranspose2dParams {
+  int strideH = 1, strideW = 1, padH = 0, padW = 0, outPadH = 0, outPadW = 0, dilH = 1, dilW = 1, groups = 1;
 };
 
 struct Ops {
@@ -271,6 +276,21 @@ struct Ops {
   // One LSTM layer direction: returns y [T,B,H]; hn/cn receive the final states when not null.
   static Tensor LstmLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, const Tensor& bIh, const Tensor& bHh,
                           bool reverse, Tensor* hn = nullptr, Tensor* cn = nullptr);
+  // One GRU layer direction (Ops.Recurrent.cs:148-260): returns y [T,B,H]; h0 [B,H] may be empty (zeros).
+  static Tensor GruLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, const Tensor& bIh, const Tensor& bHh,
+                         const Tensor& h0, bool reverse);
+  // Graph-op family (Ops.GraphOps.cs of the reference).
+  static Tensor MatMulBatched(const Tensor& a, const Tensor& b);
+  static Tensor Erf(const Tensor& x);
+  static Tensor Exp(const Tensor& x);
+  static Tensor Sqrt(const Tensor& x);
+  static Tensor Pow(const Tensor& x, float exponent);
+  static Tensor Where(const Tensor& condition, const Tensor& x, const Tensor& y);
+  static Tensor Gather(const Tensor& data, const Tensor& indices, int axis);
+  // Transposed convolution, the adjoint of Conv2d (Ops.Spatial.cs:43-130): x [N,Cin,H,W], weight [Cin,Cout/G,KH,KW].
+  static Tensor ConvTranspose2d(const Tensor& x, const Tensor& weight, const Tensor& bias, const ConvTranspose2dParams& p);
+  // mode 0 nearest, 1 bilinear (Ops.Spatial.cs:148-197).
+  static Tensor Resize2d(const Tensor& x, int outH, int outW, int mode, bool alignCorners);
   static Tensor CtcLoss(const Tensor& logProbs, const Tensor& targets, const Tensor& inputLengths,
                         const Tensor& targetLengths, int blank, int reduction, bool zeroInfinity);
   static bool Recording(std::initializer_list<const Tensor*> inputs);

@@ -134,6 +134,43 @@ Tensor Ops::LstmLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, con
   return br->Attach(y);
 }
 
+Tensor Ops::GruLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, const Tensor& bIh, const Tensor& bHh, const Tensor& h0,
+                     bool reverse) {
+  if (x.Rank() != 3 || wIh.Rank() != 2 || wHh.Rank() != 2 || wIh.GetShape()[0] % 3 != 0 || wIh.GetShape()[1] != x.GetShape()[2] ||
+      wHh.GetShape()[0] != wIh.GetShape()[0] || wHh.GetShape()[1] * 3 != wHh.GetShape()[0])
+    throw TensorShapeException("GruLayer needs x [T,B,I], wIh [3H,I], wHh [3H,H], not " + x.GetShape().ToString() + ", " +
+                               wIh.GetShape().ToString() + ", " + wHh.GetShape().ToString() + ".");
+  int steps = x.GetShape()[0], batch = x.GetShape()[1], inSize = x.GetShape()[2], h = wHh.GetShape()[1];
+  for (const Tensor* b : {&bIh, &bHh})
+    if (!b->IsEmpty() && (b->Rank() != 1 || b->GetShape()[0] != 3 * h)) throw TensorShapeException("GruLayer biases must have shape [3H].");
+  if (!h0.IsEmpty() && (h0.Rank() != 2 || h0.GetShape()[0] != batch || h0.GetShape()[1] != h))
+    throw TensorShapeException("GruLayer: the initial state must be [B,H], not " + h0.GetShape().ToString() + ".");
+  Tensor xc = x.Contiguous(), wi = wIh.Contiguous(), wh = wHh.Contiguous();
+  Tensor bi = bIh.IsEmpty() ? Tensor() : bIh.Contiguous(), bh = bHh.IsEmpty() ? Tensor() : bHh.Contiguous();
+  Tensor h0c = h0.IsEmpty() ? Tensor() : h0.Contiguous();
+  Tensor y = NewOut(Shape{steps, batch, h});
+  Tensor gates = Tensor::Create(DType::F32, Shape{steps, batch, 3 * h});
+  Tensor hn = Tensor::Create(DType::F32, Shape{steps, batch, h});
+  Check(om_gru_layer_fwd(C(), reverse, steps, batch, inSize, h, xc.Data(), wi.Data(), wh.Data(), bi.IsEmpty() ? nullptr : bi.Data(),
+                         bh.IsEmpty() ? nullptr : bh.Data(), h0c.IsEmpty() ? nullptr : h0c.Data(), y.Data(), gates.Data(), hn.Data()));
+  // Record inputs: x, wIh, wHh, bIh, bHh, h0 (the reference's order); absent ones are empty tensors.
+  std::vector<Tensor> ins = {x, wIh, wHh, bIh, bHh, h0};
+  bool rec = false;
+  if (GradMode::Enabled())
+    for (const Tensor& t : ins) rec = rec || (!t.IsEmpty() && t.RequiresGrad());
+  if (!rec) return y;
+  auto br = BackwardRecord::Create(OpKind::Gru, 7, ins);
+  br->Save(0, xc.Detach());
+  br->Save(1, wi.Detach());
+  br->Save(2, wh.Detach());
+  br->Save(3, gates);
+  br->Save(4, hn);
+  br->Save(5, y.Detach());
+  if (!h0c.IsEmpty()) br->Save(6, h0c.Detach());
+  br->Ints = {reverse ? 1 : 0, steps, batch, inSize, h};
+  return br->Attach(y);
+}
+
 // logProbs [T,B,C]; targets (Int32, concatenated), inputLengths and targetLengths (Int32 [B]) live on the device.
 // reduction: 0 none, 1 mean, 2 sum (CtcReduction of the reference).
 Tensor Ops::CtcLoss(const Tensor& logProbs, const Tensor& targets, const Tensor& inputLengths, const Tensor& targetLengths,

@@ -284,6 +284,97 @@ API void orc_lstm_bwd(int reverse, int steps, int batch, int in_size, int h, con
   free(dG); free(dh); free(dc); free(zeros); free(hprev);
 }
 
+/* ---- GRU (Ops.Recurrent.cs:148-260; BackwardRecurrent.cs:115-221), PyTorch's formulation, optional initial state --- */
+API void orc_gru_fwd(int reverse, int steps, int batch, int in_size, int h, const float* x, const float* wih, const float* whh,
+                     const float* bih, const float* bhh, const float* h0, float* y, float* gates, float* hn) {
+  int h3 = 3 * h, bh = batch * h;
+  float* rec = (float*)malloc(sizeof(float) * (size_t)batch * h3);
+  float* zeros = (float*)calloc((size_t)bh, sizeof(float));
+  orc_gemm(0, 1, steps * batch, h3, in_size, x, in_size, wih, in_size, gates, h3, 0);
+  for (int f = 0; f < steps; f++) {
+    int t = reverse ? steps - 1 - f : f, pt = reverse ? t + 1 : t - 1;
+    const float* hp = f == 0 ? (h0 ? h0 : zeros) : y + (size_t)pt * bh;
+    orc_gemm(0, 1, batch, h3, h, hp, h, whh, h, rec, h3, 0);
+    for (int b = 0; b < batch; b++) {
+      float* g = gates + ((size_t)t * batch + b) * h3;
+      float* rr = rec + (size_t)b * h3;
+      if (bih) for (int i = 0; i < h3; i++) g[i] = g[i] + bih[i];
+      if (bhh) for (int i = 0; i < h3; i++) rr[i] = rr[i] + bhh[i];
+      for (int i = 0; i < 2 * h; i++) g[i] = sigm(g[i] + rr[i]);
+      float* hside = hn + ((size_t)t * batch + b) * h;
+      for (int j = 0; j < h; j++) hside[j] = rr[2 * h + j];
+      for (int j = 0; j < h; j++) {
+        float prod = g[j] * hside[j];
+        g[2 * h + j] = tanhf(g[2 * h + j] + prod);
+      }
+      float* ho = y + ((size_t)t * batch + b) * h;
+      for (int j = 0; j < h; j++) {
+        float z = g[h + j];
+        float keep = (1.0f - z) * g[2 * h + j];
+        float carry = z * hp[b * h + j];
+        ho[j] = keep + carry;
+      }
+    }
+  }
+  free(rec);
+  free(zeros);
+}
+
+API void orc_gru_bwd(int reverse, int steps, int batch, int in_size, int h, const float* gy, const float* x, const float* y,
+                     const float* wih, const float* whh, const float* h0, const float* gates, const float* hn, float* dx,
+                     float* dwih, float* dwhh, float* dbih, float* dbhh, float* dh0) {
+  int h3 = 3 * h, bh = batch * h, rows = steps * batch;
+  float* dX = (float*)malloc(sizeof(float) * (size_t)rows * h3);
+  float* dH = (float*)malloc(sizeof(float) * (size_t)rows * h3);
+  float* dn = (float*)calloc((size_t)bh, sizeof(float));
+  float* direct = (float*)malloc(sizeof(float) * (size_t)bh);
+  float* zeros = (float*)calloc((size_t)bh, sizeof(float));
+  float* hprev = (float*)malloc(sizeof(float) * (size_t)rows * h);
+  for (int s = 0; s < steps; s++) {
+    int t = reverse ? s : steps - 1 - s, pt = reverse ? t + 1 : t - 1;
+    int first = reverse ? t == steps - 1 : t == 0;
+    const float* hpv = first ? (h0 ? h0 : zeros) : y + (size_t)pt * bh;
+    memcpy(hprev + (size_t)t * bh, hpv, sizeof(float) * bh);
+    for (int b = 0; b < batch; b++) {
+      size_t row = (size_t)t * batch + b;
+      const float* g = gates + row * h3;
+      float* dxr = dX + row * h3;
+      float* dhr = dH + row * h3;
+      for (int j = 0; j < h; j++) {
+        int k = b * h + j;
+        float rg = g[j], zg = g[h + j], ng = g[2 * h + j];
+        float dHt = gy[row * h + j] + dn[k];
+        float dz = dHt * (hpv[k] - ng);
+        float dNew = dHt * (1.0f - zg);
+        direct[k] = dHt * zg;
+        float dan = dNew * (1.0f - (ng * ng));
+        float drg = dan * hn[row * h + j];
+        float dar = (drg * rg) * (1.0f - rg);
+        float daz = (dz * zg) * (1.0f - zg);
+        dxr[j] = dar; dxr[h + j] = daz; dxr[2 * h + j] = dan;
+        dhr[j] = dar; dhr[h + j] = daz; dhr[2 * h + j] = dan * rg;
+      }
+    }
+    orc_gemm(0, 0, batch, h, h3, dH + (size_t)t * batch * h3, h3, whh, h, dn, h, 0);
+    for (int i = 0; i < bh; i++) dn[i] += direct[i];
+  }
+  if (dx) orc_gemm(0, 0, rows, in_size, h3, dX, h3, wih, in_size, dx, in_size, 0);
+  if (dwih) orc_gemm(1, 0, h3, in_size, rows, dX, h3, x, in_size, dwih, in_size, 0);
+  if (dwhh) orc_gemm(1, 0, h3, h, rows, dH, h3, hprev, h, dwhh, h, 0);
+  for (int which = 0; which < 2; which++) {
+    float* out = which ? dbhh : dbih;
+    const float* src = which ? dH : dX;
+    if (!out) continue;
+    double* a = (double*)calloc((size_t)h3, sizeof(double));
+    for (int i = 0; i < rows; i++)
+      for (int c = 0; c < h3; c++) a[c] += src[(size_t)i * h3 + c];
+    for (int c = 0; c < h3; c++) out[c] = (float)a[c];
+    free(a);
+  }
+  if (dh0) memcpy(dh0, dn, sizeof(float) * bh);
+  free(dX); free(dH); free(dn); free(direct); free(zeros); free(hprev);
+}
+
 /* ---- CTC (src/OneModel/Tensors/CtcLoss.cs:170-281; Ctc.cs:515-616) ----------------------------------------------------- */
 static double ctc_exp(double x) {
   if (!(x > -700.0)) return 0.0;

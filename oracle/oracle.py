@@ -391,6 +391,27 @@ def lstm_bwd(gy, x, y, wih, whh, gates, c, tc, reverse=False):
     return dx, dwih, dwhh, dbih, dbhh
 
 
+def gru_fwd(x, wih, whh, bih, bhh, h0=None, reverse=False):
+    x, wih, whh = _f(x), _f(wih), _f(whh)
+    t, b, i = x.shape
+    h = whh.shape[1]
+    y, gates, hn = np.empty((t, b, h), np.float32), np.empty((t, b, 3 * h), np.float32), np.empty((t, b, h), np.float32)
+    lib().orc_gru_fwd(int(reverse), t, b, i, h, _p(x), _p(wih), _p(whh), _p(_f(bih) if bih is not None else None),
+                      _p(_f(bhh) if bhh is not None else None), _p(_f(h0) if h0 is not None else None), _p(y), _p(gates), _p(hn))
+    return y, gates, hn
+
+
+def gru_bwd(gy, x, y, wih, whh, h0, gates, hn, reverse=False):
+    gy, x, y, wih, whh = _f(gy), _f(x), _f(y), _f(wih), _f(whh)
+    t, b, i = x.shape
+    h = whh.shape[1]
+    dx, dwih, dwhh = np.empty_like(x), np.empty_like(wih), np.empty_like(whh)
+    dbih, dbhh, dh0 = np.empty(3 * h, np.float32), np.empty(3 * h, np.float32), np.empty((b, h), np.float32)
+    lib().orc_gru_bwd(int(reverse), t, b, i, h, _p(gy), _p(x), _p(y), _p(wih), _p(whh), _p(_f(h0) if h0 is not None else None),
+                      _p(_f(gates)), _p(_f(hn)), _p(dx), _p(dwih), _p(dwhh), _p(dbih), _p(dbhh), _p(dh0))
+    return dx, dwih, dwhh, dbih, dbhh, dh0
+
+
 def _i32(a):
     return np.ascontiguousarray(a, np.int32)
 

@@ -381,6 +381,23 @@ def lstm_layer(x, wih, whh, bih, bhh, reverse=False):
     return _attach(y, Record("lstm", ins, saved=(xc, y, wih.v, whh.v, gates, c, tc), backward=bw), ins)
 
 
+def gru_layer(x, wih, whh, bih, bhh, h0=None, reverse=False):
+    """Ops.GruLayer (Ops.Recurrent.cs:148-260): inputs x, wIh, wHh, bIh, bHh and the optional initial state."""
+    xc = np.ascontiguousarray(x.v)
+    h0v = None if h0 is None else np.ascontiguousarray(h0.v)
+    y, gates, hn = K.gru_fwd(xc, wih.v, whh.v, bih.v, bhh.v, h0v, reverse)
+
+    def bw(r, g):
+        dx, dwih, dwhh, dbih, dbhh, dh0 = K.gru_bwd(g, r.saved[0], r.saved[1], r.saved[2], r.saved[3], r.saved[4], r.saved[5], r.saved[6], reverse)
+        out = [(0, dx, "own"), (1, dwih, "own"), (2, dwhh, "own"), (3, dbih, "own"), (4, dbhh, "own")]
+        if h0 is not None:
+            out.append((5, dh0, "own"))
+        return out
+
+    ins = [x, wih, whh, bih, bhh] + ([h0] if h0 is not None else [])
+    return _attach(y, Record("gru", ins, saved=(xc, y, wih.v, whh.v, h0v, gates, hn), backward=bw), ins)
+
+
 def ctc_loss(lp, targets, ilen, tlen, blank=0, reduction=1, zero_inf=False):
     lpc = np.ascontiguousarray(lp.v)
     loss, _ = K.ctc_loss(lpc, targets, tlen, ilen, blank, reduction, zero_inf)
@@ -389,3 +406,185 @@ def ctc_loss(lp, targets, ilen, tlen, blank=0, reduction=1, zero_inf=False):
         return [(0, K.ctc_grad(g.reshape(-1), r.saved[0], targets, tlen, ilen, blank, reduction), "own")]
 
     return _attach(np.asarray(loss, np.float32), Record("ctc", [lp], saved=(lpc,), backward=bw), [lp])
+
+
+# ---- graph-op family (Ops.GraphOps.cs; BackwardGraphOps.cs of the reference), restated with numpy --------------------
+def _sum_to(g, shape):
+    """BackwardOps.SumTo: sums over the axes the operand broadcast, double accumulation, rounded once."""
+    g64 = np.asarray(g, np.float64)
+    while g64.ndim > len(shape):
+        g64 = g64.sum(axis=0)
+    for i, d in enumerate(shape):
+        if d == 1 and g64.shape[i] != 1:
+            g64 = g64.sum(axis=i, keepdims=True)
+    return g64.astype(np.float32)
+
+
+def matmul_batched(a, b):
+    """Ops.MatMulBatched (Ops.GraphOps.cs:24-100): broadcast batch axes; dA = g b^T, dB = a^T g summed back."""
+    def bw(r, g):
+        av, bv = r.saved
+        ga = np.matmul(g, np.swapaxes(bv, -1, -2)).astype(np.float32)
+        gb = np.matmul(np.swapaxes(av, -1, -2), g).astype(np.float32)
+        return [(0, _sum_to(ga, av.shape).reshape(av.shape), "own"), (1, _sum_to(gb, bv.shape).reshape(bv.shape), "own")]
+
+    return _attach(np.matmul(a.v, b.v).astype(np.float32), Record("batch_matmul", [a, b], saved=(a.v, b.v), backward=bw), [a, b])
+
+
+def _erf(x):
+    from scipy.special import erf
+    return erf(x.astype(np.float64)).astype(np.float32)
+
+
+def erf(x):
+    bw = lambda r, g: [(0, (g * (np.float32(1.1283791671) * np.exp(-(r.saved[0] * r.saved[0])))).astype(np.float32), "own")]
+    return _attach(_erf(x.v), Record("erf", [x], saved=(x.v,), backward=bw), [x])
+
+
+def exp(x):
+    y = np.exp(x.v).astype(np.float32)
+    return _attach(y, Record("exp", [x], saved=(y,), backward=lambda r, g: [(0, g * r.saved[0], "own")]), [x])
+
+
+def sqrt(x):
+    y = np.sqrt(x.v).astype(np.float32)
+    return _attach(y, Record("sqrt", [x], saved=(y,), backward=lambda r, g: [(0, g / (np.float32(2) * r.saved[0]), "own")]), [x])
+
+
+def pow_(x, p):
+    """Ops.Pow / PowDerivative with the exact cases 1, 2, 0.5, -1 (Ops.GraphOps.cs:175-206; BackwardGraphOps.cs:69-76)."""
+    p = np.float32(p)
+    xv = x.v
+    y = xv if p == 1 else xv * xv if p == 2 else np.sqrt(xv) if p == 0.5 else np.float32(1) / xv if p == -1 else np.power(xv, p)
+
+    def bw(r, g):
+        v = r.saved[0]
+        if p == 1:
+            d = np.ones_like(v)
+        elif p == 2:
+            d = v + v
+        elif p == 0.5:
+            d = np.float32(1) / (np.sqrt(v) + np.sqrt(v))
+        elif p == -1:
+            d = np.float32(-1) / (v * v)
+        else:
+            d = p * np.power(v, p - np.float32(1))
+        return [(0, (g * d).astype(np.float32), "own")]
+
+    return _attach(y.astype(np.float32), Record("pow", [x], saved=(xv,), backward=bw), [x])
+
+
+def where(cond, a, b):
+    """Ops.Where (Ops.GraphOps.cs:244-300): cond broadcast with both sides; each side gets g where it was chosen, summed back."""
+    c = np.asarray(cond) != 0
+    shape = np.broadcast_shapes(c.shape, a.v.shape, b.v.shape)
+    cb = np.broadcast_to(c, shape)
+
+    def bw(r, g):
+        return [(0, _sum_to(np.where(cb, g, np.float32(0)), a.v.shape).reshape(a.v.shape), "own"),
+                (1, _sum_to(np.where(cb, np.float32(0), g), b.v.shape).reshape(b.v.shape), "own")]
+
+    y = np.where(cb, np.broadcast_to(a.v, shape), np.broadcast_to(b.v, shape)).astype(np.float32)
+    return _attach(y, Record("where", [a, b], backward=bw), [a, b])
+
+
+def gather(data, indices, axis):
+    """Ops.Gather / GatherBackward (Ops.GraphOps.cs:306-394; BackwardGraphOps.cs:105-139): negative indices count from the end;
+    the backward adds slices that share a destination in increasing index position."""
+    idx = np.asarray(indices).astype(np.int64)
+    ax = axis % data.v.ndim
+    n = data.v.shape[ax]
+    norm = np.where(idx < 0, idx + n, idx)
+    if norm.min(initial=0) < 0 or norm.max(initial=0) >= n:
+        raise IndexError("Gather index outside the axis")
+    y = np.take(data.v, norm, axis=ax)
+
+    def bw(r, g):
+        dx = np.zeros(data.v.shape, np.float32)
+        dxm, gm = np.moveaxis(dx, ax, 0), np.moveaxis(g.reshape(data.v.shape[:ax] + (norm.size,) + data.v.shape[ax + 1:]), ax, 0)
+        for j, i in enumerate(norm.reshape(-1)):
+            dxm[i] += gm[j]
+        return [(0, dx, "own")]
+
+    return _attach(y.astype(np.float32), Record("gather", [data], backward=bw), [data])
+
+
+def conv_transpose2d(x, w, b=None, stride=1, padding=0, output_padding=0, groups=1):
+    """Ops.ConvTranspose2d (Ops.Spatial.cs:43-130): the adjoint of Conv2d, computed as the input gradient of the convolution
+    whose input is this op's output; backward dx = Conv2d(g, W), dW = the adjoint convolution's weight gradient, dbias = sum g
+    in double (ConvTransposeBackward, BackwardRecurrent.cs:304-369)."""
+    xv, wv = np.ascontiguousarray(x.v), np.ascontiguousarray(w.v)
+    n, cin, h, wd = xv.shape
+    cout, kh, kw = wv.shape[1] * groups, wv.shape[2], wv.shape[3]
+    oh = (h - 1) * stride - 2 * padding + (kh - 1) + output_padding + 1
+    ow = (wd - 1) * stride - 2 * padding + (kw - 1) + output_padding + 1
+    shape_only = np.zeros((n, cout, oh, ow), np.float32)
+    y = K.conv2d_bwd(xv, shape_only, wv, stride, padding, 1, groups)[0]
+    if b is not None:
+        y = (y + b.v.reshape(1, cout, 1, 1)).astype(np.float32)
+
+    def bw(r, g):
+        out = [(0, K.conv2d_fwd(g, wv, None, stride, padding, 1, groups), "own"),
+               (1, K.conv2d_bwd(xv, g, wv, stride, padding, 1, groups, need_dx=False)[1], "own")]
+        if b is not None:
+            out.append((2, np.asarray(g, np.float64).sum(axis=(2, 3)).sum(axis=0).astype(np.float32), "own"))
+        return out
+
+    ins = [x, w] + ([b] if b is not None else [])
+    return _attach(y, Record("conv_transpose2d", ins, backward=bw), ins)
+
+
+def _source_coord(mode, align, dst, in_size, out_size):
+    """Ops.SourceCoord (Ops.Spatial.cs:200-235) in float32."""
+    f = np.float32
+    if mode == 0:
+        scale = f(in_size) / f(out_size)
+        i0 = min(int(np.floor(f(dst) * scale)), in_size - 1)
+        return i0, i0, f(0)
+    if align:
+        scale = f(in_size - 1) / f(out_size - 1) if out_size > 1 else f(0)
+        src = scale * f(dst)
+    else:
+        scale = f(in_size) / f(out_size)
+        src = (scale * (f(dst) + f(0.5))) - f(0.5)
+        if src < 0:
+            src = f(0)
+    i0 = min(int(src), in_size - 1)
+    i1 = i0 + (1 if i0 < in_size - 1 else 0)
+    return i0, i1, f(src - f(i0))
+
+
+def resize2d(x, out_h, out_w, mode=0, align_corners=False):
+    """Ops.Resize2d / ResizeBackward (Ops.Spatial.cs:148-197; BackwardRecurrent.cs:371-412): mode 0 nearest, 1 bilinear."""
+    xv = np.ascontiguousarray(x.v)
+    n, c, h, w = xv.shape
+    align = bool(align_corners) and mode == 1
+    ys = [_source_coord(mode, align, oy, h, out_h) for oy in range(out_h)]
+    xs = [_source_coord(mode, align, ox, w, out_w) for ox in range(out_w)]
+    f = np.float32
+    y = np.empty((n, c, out_h, out_w), np.float32)
+    for oy, (y0, y1, ly) in enumerate(ys):
+        for ox, (x0, x1, lx) in enumerate(xs):
+            if mode == 0:
+                y[:, :, oy, ox] = xv[:, :, y0, x0]
+            else:
+                top = ((f(1) - lx) * xv[:, :, y0, x0]) + (lx * xv[:, :, y0, x1])
+                bottom = ((f(1) - lx) * xv[:, :, y1, x0]) + (lx * xv[:, :, y1, x1])
+                y[:, :, oy, ox] = ((f(1) - ly) * top) + (ly * bottom)
+
+    def bw(r, g):
+        dx = np.zeros_like(xv)
+        for oy, (y0, y1, ly) in enumerate(ys):
+            for ox, (x0, x1, lx) in enumerate(xs):
+                gg = g[:, :, oy, ox]
+                if mode == 0:
+                    dx[:, :, y0, x0] += gg
+                else:
+                    t, bt = (f(1) - ly) * gg, ly * gg
+                    dx[:, :, y0, x0] += (f(1) - lx) * t
+                    dx[:, :, y0, x1] += lx * t
+                    dx[:, :, y1, x0] += (f(1) - lx) * bt
+                    dx[:, :, y1, x1] += lx * bt
+        return [(0, dx, "own")]
+
+    return _attach(y, Record("resize2d", [x], backward=bw), [x])

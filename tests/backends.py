@@ -60,6 +60,21 @@ class OracleBackend:
     def avg_pool2d(self, x, k): return self.tape.avg_pool2d(x, k)
     def lstm_layer(self, x, wih, whh, bih, bhh, reverse=False): return self.tape.lstm_layer(x, wih, whh, bih, bhh, reverse)
     def concat(self, xs, axis): return self.tape.concat(xs, axis)
+    def gru_layer(self, x, wih, whh, bih, bhh, h0=None, reverse=False): return self.tape.gru_layer(x, wih, whh, bih, bhh, h0, reverse)
+    def matmul_batched(self, a, b): return self.tape.matmul_batched(a, b)
+    def conv_transpose2d(self, x, w, b, stride=1, padding=0, output_padding=0, groups=1):
+        return self.tape.conv_transpose2d(x, w, b, stride, padding, output_padding, groups)
+    def resize2d(self, x, oh, ow, mode=0, align=False): return self.tape.resize2d(x, oh, ow, mode, align)
+    def erf(self, x): return self.tape.erf(x)
+    def exp(self, x): return self.tape.exp(x)
+    def sqrt(self, x): return self.tape.sqrt(x)
+    def pow(self, x, p): return self.tape.pow_(x, p)
+    def where(self, c, a, b): return self.tape.where(c, a, b)
+    def gather(self, data, idx, axis): return self.tape.gather(data, idx, axis)
+    def select(self, t, axis, index):
+        shape = list(t.shape)
+        del shape[axis]
+        return t.slice(axis, index, index + 1).reshape(*shape)
     def ctc_loss(self, lp, targets, ilen, tlen, blank=0, reduction=1, zero_inf=False):
         return self.tape.ctc_loss(lp, targets, ilen, tlen, blank, reduction, zero_inf)
     def running(self, a): return np.array(a, np.float32)
@@ -122,6 +137,19 @@ class GpuBackend:
     def lstm_layer(self, x, wih, whh, bih, bhh, reverse=False):
         return self.omb.call("lstm_layer", [x, wih, whh, bih, bhh], ints=[1 if reverse else 0])
     def concat(self, xs, axis): return self.omb.call("concat", list(xs), ints=[axis])
+    def gru_layer(self, x, wih, whh, bih, bhh, h0=None, reverse=False):
+        return self.omb.call("gru_layer", [x, wih, whh, bih, bhh, h0], ints=[1 if reverse else 0])
+    def select(self, t, axis, index): return t.select(axis, index)
+    def matmul_batched(self, a, b): return self.omb.call("matmul_batched", [a, b])
+    def conv_transpose2d(self, x, w, b, stride=1, padding=0, output_padding=0, groups=1):
+        return self.omb.call("conv_transpose2d", [x, w, b], ints=[stride, stride, padding, padding, output_padding, output_padding, 1, 1, groups])
+    def resize2d(self, x, oh, ow, mode=0, align=False): return self.omb.call("resize2d", [x], ints=[oh, ow, mode, 1 if align else 0])
+    def erf(self, x): return self.omb.call("erf", [x])
+    def exp(self, x): return self.omb.call("exp", [x])
+    def sqrt(self, x): return self.omb.call("sqrt", [x])
+    def pow(self, x, p): return self.omb.call("pow", [x], floats=[p])
+    def where(self, c, a, b): return self.omb.call("where", [self.omb.Tensor.from_numpy(np.asarray(c, np.int32)), a, b])
+    def gather(self, data, idx, axis): return self.omb.call("gather", [data, self.omb.Tensor.from_numpy(np.asarray(idx, np.int64))], ints=[axis])
     def ctc_loss(self, lp, targets, ilen, tlen, blank=0, reduction=1, zero_inf=False):
         T = self.omb.Tensor.from_numpy
         return self.omb.call("ctc_loss", [lp, T(np.asarray(targets, np.int32)), T(np.asarray(ilen, np.int32)), T(np.asarray(tlen, np.int32))],

@@ -141,3 +141,56 @@ def autograd_crnn(B, fx):
     loss = B.ctc_loss(lp, fx["in.targets"].astype(np.int32), fx["in.input_lengths"].astype(np.int32),
                       fx["in.target_lengths"].astype(np.int32), 0, 1, False)
     return loss, lp, w
+
+
+def autograd_gru(B, fx):
+    """testdata/autograd/gru: 1-layer bidirectional GRU (batch first, with initial state) -> weighted sum
+    (tests/OneModel.Tests/Tensors/RnnOracleTests.cs:158-175 of the reference)."""
+    names = [k[3:] for k in fx if k.startswith("in.") and k != "in.proj"]
+    w = {k: B.tensor(fx["in." + k], True) for k in names}
+    seq = w["x"].permute(1, 0, 2)                       # [T, B, I]
+    outs = []
+    for d, sfx in enumerate(("", "_reverse")):
+        p = f"gru.%s_l0{sfx}"
+        outs.append(B.gru_layer(seq, w[p % "weight_ih"], w[p % "weight_hh"], w[p % "bias_ih"], w[p % "bias_hh"],
+                                B.select(w["h0"], 0, d), d == 1))
+    y = B.concat(outs, 2).permute(1, 0, 2)              # [B, T, 2H]
+    loss = B.sum(B.mul(y, B.tensor(fx["in.proj"])))
+    return loss, y, w
+
+
+def graph_ops_case(B, seed=0):
+    """One graph through every op of the graph-op family (Ops.GraphOps.cs): returns the loss and the leaves."""
+    r = np.random.default_rng(seed)
+    a = B.tensor(r.standard_normal((2, 3, 4, 5)).astype(np.float32), True)
+    b = B.tensor(r.standard_normal((3, 5, 6)).astype(np.float32), True)        # batch axes broadcast against a's
+    c = B.tensor((r.random((4, 6)) + 0.5).astype(np.float32), True)
+    d = B.tensor(r.standard_normal((1, 6)).astype(np.float32), True)
+    m = B.matmul_batched(a, b)                                                   # [2, 3, 4, 6]
+    t = B.add(B.erf(m), B.exp(B.mul(m, B.tensor(np.full((1,), 0.1, np.float32)))))
+    t = B.add(t, B.sqrt(c))                                                      # c broadcasts over the batch axes
+    t = B.add(t, B.pow(c, 2.0))
+    t = B.add(t, B.pow(c, -1.0))
+    t = B.add(t, B.pow(c, 0.5))
+    t = B.add(t, B.pow(c, 1.7))
+    cond = (r.random((3, 4, 6)) < 0.5).astype(np.int32)
+    t = B.where(cond, t, d)                                                      # d [1, 6] broadcasts
+    g = B.gather(t, np.array([[2, -1], [0, 2]]), 2)                              # axis of 4 -> [2, 3, 2, 2, 6], repeated rows
+    w = B.tensor(r.standard_normal((2, 3, 2, 2, 6)).astype(np.float32))
+    loss = B.sum(B.mul(g, w))
+    return loss, g, {"a": a, "b": b, "c": c, "d": d}
+
+
+def autograd_decoder(B, fx):
+    """testdata/autograd/decoder: conv, two transposed convolutions (stride 2; stride 2 with padding, output padding and two
+    groups), nearest and bilinear resizes (tests/OneModel.Tests/Tensors/RnnOracleTests.cs:177-201 of the reference)."""
+    w = {k: B.tensor(fx["in." + k], True) for k in ("x", "c1w", "c1b", "t1w", "t1b", "t2w", "t2b", "c2w", "c2b")}
+    h = B.relu(B.conv2d(w["x"], w["c1w"], w["c1b"], 1, 1))
+    h = B.relu(B.conv_transpose2d(h, w["t1w"], w["t1b"], 2, 0, 0, 1))
+    h = B.relu(B.conv_transpose2d(h, w["t2w"], w["t2b"], 2, 1, 1, 2))
+    h = B.resize2d(h, 13, 30, 0, False)
+    h = B.conv2d(h, w["c2w"], w["c2b"], 1, 1)
+    a = B.resize2d(h, 9, 17, 1, False)
+    c = B.resize2d(h, 16, 11, 1, True)
+    loss = B.add(B.sum(B.mul(a, B.tensor(fx["in.pa"]))), B.sum(B.mul(c, B.tensor(fx["in.pc"]))))
+    return loss, a, c, w

@@ -5,7 +5,7 @@ import pytest
 
 import models
 from backends import GpuBackend, OracleBackend, load_fixture, scaled_diff
-from test_oracle_golden import OPTIM, run_optim_case
+from test_oracle_golden import OPTIM, check_graph_ops, run_optim_case
 
 pytestmark = pytest.mark.gpu
 
@@ -147,3 +147,9 @@ def test_attention_over_heads_equals_the_permuted_form(ctx, B, tf32, b, l, heads
             assert all(np.array_equal(x, y) for x, y in zip(ga, gb))
     finally:
         ctx.set_flags(0)
+
+
+def test_graph_op_family(B):
+    """MatMulBatched (broadcast batch axes), Erf, Exp, Sqrt, Pow, Where, Gather and their backward functions on the GPU
+    against the PyTorch golden file the CPU oracle is pinned on (fp32 products: the 1e-4 tier, here far inside it)."""
+    check_graph_ops(B, 1e-5)

@@ -219,6 +219,56 @@ def test_autograd_crnn_fixture(B):
     check_grads(B, fx, w)
 
 
+def test_autograd_gru_fixture(B):
+    """Bidirectional GRU with an initial state against the reference's PyTorch fixture (RnnOracleTests.cs:158-175)."""
+    fx = load_fixture("autograd", "gru")
+    loss, y, w = models.autograd_gru(B, fx)
+    assert scaled_diff(B.numpy(y), fx["out.y"]) <= 1e-5
+    ref = float(fx["out.loss"].reshape(-1)[0])
+    assert abs(float(B.numpy(loss).reshape(-1)[0]) - ref) <= 1e-5 * abs(ref)
+    B.backward(loss)
+    check_grads(B, fx, w)
+
+
+@pytest.mark.parametrize("reverse,with_h0,with_bias", [(False, True, True), (True, False, True), (False, False, False)])
+def test_gru_layer_entry_points(ctx, K, reverse, with_h0, with_bias):
+    """om_gru_layer_fwd / om_gru_layer_bwd through the C ABI against the CPU oracle at a larger size (fp32 products)."""
+    ctx.set_flags(0)
+    t, b, i, h = 9, 5, 24, 16
+    r = np.random.default_rng(t + i + reverse)
+    x = r.standard_normal((t, b, i)).astype(np.float32)
+    wih, whh = (r.standard_normal((3 * h, i)) * 0.3).astype(np.float32), (r.standard_normal((3 * h, h)) * 0.3).astype(np.float32)
+    bih = (r.standard_normal(3 * h) * 0.1).astype(np.float32) if with_bias else None
+    bhh = (r.standard_normal(3 * h) * 0.1).astype(np.float32) if with_bias else None
+    h0 = r.standard_normal((b, h)).astype(np.float32) if with_h0 else None
+    gy = r.standard_normal((t, b, h)).astype(np.float32)
+    y_ref, gates_ref, hn_ref = K.gru_fwd(x, wih, whh, bih, bhh, h0, reverse)
+    refs = K.gru_bwd(gy, x, y_ref, wih, whh, h0, gates_ref, hn_ref, reverse)
+    dev = lambda a: ctx.to_device(a) if a is not None else None
+    ptr = lambda d: d.ptr if d is not None else None
+    X, WI, WH, BI, BH, H0, GY = dev(x), dev(wih), dev(whh), dev(bih), dev(bhh), dev(h0), dev(gy)
+    Y, G, HN = ctx.empty((t, b, h)), ctx.empty((t, b, 3 * h)), ctx.empty((t, b, h))
+    ctx.call("om_gru_layer_fwd", ctx.handle, i32(reverse), i32(t), i32(b), i32(i), i32(h), X.ptr, WI.ptr, WH.ptr, ptr(BI), ptr(BH), ptr(H0),
+             Y.ptr, G.ptr, HN.ptr)
+    assert scaled_diff(Y.numpy(), y_ref) <= 1e-5
+    DX, DWI, DWH, DBI, DBH, DH0 = ctx.empty(x.shape), ctx.empty(wih.shape), ctx.empty(whh.shape), ctx.empty((3 * h,)), ctx.empty((3 * h,)), ctx.empty((b, h))
+    ctx.call("om_gru_layer_bwd", ctx.handle, i32(reverse), i32(t), i32(b), i32(i), i32(h), GY.ptr, X.ptr, Y.ptr, WI.ptr, WH.ptr, ptr(H0),
+             G.ptr, HN.ptr, DX.ptr, DWI.ptr, DWH.ptr, DBI.ptr, DBH.ptr, DH0.ptr)
+    ctx.sync()
+    for got, ref, name in zip((DX, DWI, DWH, DBI, DBH, DH0), refs, ("dx", "dw_ih", "dw_hh", "db_ih", "db_hh", "dh0")):
+        assert scaled_diff(got.numpy(), ref) <= 1e-4, name
+
+
+def test_autograd_decoder_fixture(B):
+    """Transposed convolutions and resizes against the reference's PyTorch fixture (RnnOracleTests.cs:177-201)."""
+    fx = load_fixture("autograd", "decoder")
+    loss, a, c, w = models.autograd_decoder(B, fx)
+    assert scaled_diff(B.numpy(a), fx["out.a"]) <= 1e-5
+    assert scaled_diff(B.numpy(c), fx["out.c"]) <= 1e-5
+    B.backward(loss)
+    check_grads(B, fx, w)
+
+
 def test_training_cnn_fixture(B):
     fx = load_fixture("training", "cnn")
     losses, norms, params, rs = models.train_cnn(B, fx)

@@ -127,6 +127,41 @@ def test_autograd_crnn_gradients_and_ctc_losses(B):
     check_grads(B, fx, w)
 
 
+def test_autograd_gru_gradients(B):
+    fx = load_fixture("autograd", "gru")
+    loss, y, w = models.autograd_gru(B, fx)
+    assert scaled_diff(B.numpy(y), fx["out.y"]) <= 1e-5
+    ref = float(fx["out.loss"].reshape(-1)[0])
+    assert abs(float(B.numpy(loss).reshape(-1)[0]) - ref) <= 1e-5 * abs(ref)
+    B.backward(loss)
+    check_grads(B, fx, w)
+
+
+def test_autograd_decoder_gradients(B):
+    fx = load_fixture("autograd", "decoder")
+    loss, a, c, w = models.autograd_decoder(B, fx)
+    assert scaled_diff(B.numpy(a), fx["out.a"]) <= 1e-5
+    assert scaled_diff(B.numpy(c), fx["out.c"]) <= 1e-5
+    B.backward(loss)
+    check_grads(B, fx, w)
+
+
+def check_graph_ops(B, tol):
+    """The graph-op family against tests/golden/graph_ops.npz (PyTorch CPU, generated by tests/golden/make_graphops_golden.py)."""
+    import os
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "graph_ops.npz"))
+    loss, out, w = models.graph_ops_case(B)
+    assert scaled_diff(B.numpy(out), gold["out"]) <= tol
+    assert abs(float(B.numpy(loss).reshape(-1)[0]) - float(gold["loss"])) <= tol * 10 * abs(float(gold["loss"]))
+    B.backward(loss)
+    for k, t in w.items():
+        assert scaled_diff(B.grad(t), gold["grad_" + k]) <= tol, k
+
+
+def test_graph_ops_against_pytorch_golden(B):
+    check_graph_ops(B, 1e-6)
+
+
 def test_training_cnn_curve(B):
     fx = load_fixture("training", "cnn")
     losses, norms, params, rs = models.train_cnn(B, fx)
