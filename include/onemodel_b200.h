@@ -473,6 +473,19 @@ int32_t om_grad_norm_clip(om_ctx* ctx, int32_t n_tensors, float* const* g_host, 
 int32_t om_grad_clip_value(om_ctx* ctx, int32_t n_tensors, float* const* g_host, const int64_t* len_host,
                            float clip);
 
+/* Row-sparse updates for embedding tables (SparseAdam and the sparse path of Sgd, Optimizers.cs:377-397,625-722). The
+ * reference carries a RowSparseGradient (sorted unique rows + coalesced values); here the same information is the
+ * dense-format table gradient of om_embedding_bwd plus touched[rows] from om_rows_touched (how many positions of the
+ * step's id list name each row; ids equal to padding_index are skipped, an id outside [0, rows) sets OM_ERR_INDEX).
+ * Only rows with touched != 0 are updated; the moments of the other rows do not decay. step_size is the host-computed
+ * lr * sqrt(1 - beta2^t) / (1 - beta1^t) of SparseAdam.BeginStep (double arithmetic, rounded once). */
+int32_t om_rows_touched(om_ctx* ctx, const void* ids, int32_t id_dtype, int64_t n, int32_t rows, int64_t padding_index,
+                        int32_t* touched);
+int32_t om_optim_sparse_adam_step(om_ctx* ctx, float* p, const float* g, float* m, float* v, const int32_t* touched,
+                                  int32_t rows, int32_t width, float beta1, float beta2, float eps, float step_size);
+int32_t om_optim_sparse_sgd_step(om_ctx* ctx, float* p, const float* g, const int32_t* touched, int32_t rows,
+                                 int32_t width, float lr);
+
 /* ---- data parallel ---------------------------------------------------------------------------------------- */
 
 /* The reference is single-process; these have no counterpart there. One rank per process and GPU.

@@ -241,6 +241,58 @@ static int grid_chunks(om_ctx* ctx, int chunks) {
   return chunks < cap ? (chunks > 0 ? chunks : 1) : cap;
 }
 
+// ---- row-sparse updates (SparseAdam, sparse Sgd): only the table rows that a step touched are updated ------------------
+// touched[row] = how many positions of this step's id list name the row (0 = untouched, its parameters AND moments stay
+// as they are: SparseAdam does not decay the moments of absent rows). grad is the dense-format table gradient of
+// om_embedding_bwd, whose touched rows hold the coalesced sums the reference's RowSparseGradient holds.
+__global__ void rows_touched_kernel(const void* __restrict__ ids, int dtype, int64_t n, int32_t rows, int64_t pad,
+                                    int32_t* __restrict__ touched, int32_t* status) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    long long id = dtype == OM_I64 ? ((const long long*)ids)[i] : (long long)((const int32_t*)ids)[i];
+    if (id == pad) continue;
+    if (id < 0 || id >= rows) {
+      atomicCAS(status, 0, (int32_t)OM_ERR_INDEX);
+      continue;
+    }
+    atomicAdd(&touched[id], 1);
+  }
+}
+
+// One warp per row. SparseAdam.UpdateSparse (Optimizers.cs:696-722), this rounding sequence, no fused multiply-add:
+//   m = b1*m + (1-b1)*g;  v = b2*v + ((1-b2)*g)*g;  p -= (stepSize*m) / (sqrt(v) + eps)
+__global__ void sparse_adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                                   const int32_t* __restrict__ touched, int32_t rows, int32_t width, float b1, float b2, float eps,
+                                   float step_size) {
+  const int lane = threadIdx.x & 31;
+  const float omb1 = __fsub_rn(1.f, b1), omb2 = __fsub_rn(1.f, b2);
+  int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t r = warp; r < rows; r += warps) {
+    if (touched[r] == 0) continue;
+    const int64_t o = r * width;
+    for (int j = lane; j < width; j += 32) {
+      float gi = g[o + j];
+      float mi = __fadd_rn(__fmul_rn(b1, m[o + j]), __fmul_rn(omb1, gi));
+      float vi = __fadd_rn(__fmul_rn(b2, v[o + j]), __fmul_rn(__fmul_rn(omb2, gi), gi));
+      m[o + j] = mi;
+      v[o + j] = vi;
+      p[o + j] = __fsub_rn(p[o + j], __fdiv_rn(__fmul_rn(step_size, mi), __fadd_rn(__fsqrt_rn(vi), eps)));
+    }
+  }
+}
+
+// Sgd.UpdateSparse (Optimizers.cs:377-397): p -= lr * g on the touched rows; no momentum, no weight decay.
+__global__ void sparse_sgd_kernel(float* __restrict__ p, const float* __restrict__ g, const int32_t* __restrict__ touched, int32_t rows,
+                                  int32_t width, float lr) {
+  const int lane = threadIdx.x & 31;
+  int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t r = warp; r < rows; r += warps) {
+    if (touched[r] == 0) continue;
+    const int64_t o = r * width;
+    for (int j = lane; j < width; j += 32) p[o + j] = __fsub_rn(p[o + j], __fmul_rn(lr, g[o + j]));
+  }
+}
+
 }  // namespace om
 
 using namespace om;
@@ -338,6 +390,37 @@ int32_t om_grad_clip_value(om_ctx* ctx, int32_t n_tensors, float* const* g, cons
     clip_value_kernel<<<grid_chunks(ctx, chunks), 256, 0, ctx->stream>>>(t, clip);
     OM_LAUNCH_CHECK(ctx, "om_grad_clip_value");
   }
+  return OM_OK;
+}
+
+int32_t om_rows_touched(om_ctx* ctx, const void* ids, int32_t id_dtype, int64_t n, int32_t rows, int64_t padding_index, int32_t* touched) {
+  OM_CHECK_CTX(ctx);
+  if (n < 0 || rows < 0 || (id_dtype != OM_I32 && id_dtype != OM_I64)) return fail(ctx, OM_ERR_SHAPE, "om_rows_touched: n %lld rows %d", (long long)n, rows);
+  if (rows == 0) return OM_OK;
+  OM_CUDA(ctx, cudaMemsetAsync(touched, 0, sizeof(int32_t) * (size_t)rows, ctx->stream));
+  if (n > 0) rows_touched_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(ids, id_dtype, n, rows, padding_index, touched, ctx->status_dev);
+  OM_LAUNCH_CHECK(ctx, "om_rows_touched");
+  return OM_OK;
+}
+
+int32_t om_optim_sparse_adam_step(om_ctx* ctx, float* p, const float* g, float* m, float* v, const int32_t* touched, int32_t rows,
+                                  int32_t width, float beta1, float beta2, float eps, float step_size) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 0 || width < 0) return fail(ctx, OM_ERR_SHAPE, "SparseAdam parameters must be rank 2 ([rows, width]) tables.");
+  if (rows == 0 || width == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_optim_sparse_adam_step", 0, 4.0 * rows);
+  sparse_adam_kernel<<<grid_for(ctx, (int64_t)rows * 32, 256), 256, 0, ctx->stream>>>(p, g, m, v, touched, rows, width, beta1, beta2, eps, step_size);
+  OM_LAUNCH_CHECK(ctx, "om_optim_sparse_adam_step");
+  return OM_OK;
+}
+
+int32_t om_optim_sparse_sgd_step(om_ctx* ctx, float* p, const float* g, const int32_t* touched, int32_t rows, int32_t width, float lr) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 0 || width < 0) return fail(ctx, OM_ERR_SHAPE, "Sparse Sgd parameters must be rank 2 ([rows, width]) tables.");
+  if (rows == 0 || width == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_optim_sparse_sgd_step", 0, 4.0 * rows);
+  sparse_sgd_kernel<<<grid_for(ctx, (int64_t)rows * 32, 256), 256, 0, ctx->stream>>>(p, g, touched, rows, width, lr);
+  OM_LAUNCH_CHECK(ctx, "om_optim_sparse_sgd_step");
   return OM_OK;
 }
 

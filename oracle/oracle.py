@@ -440,3 +440,42 @@ def ctc_greedy(lp, ilen=None, blank=0):
     il = _i32(ilen) if ilen is not None else None
     lib().orc_ctc_greedy(_p(lp), t, b, c, _p(il), blank, _p(labels), _p(first), _p(last), _p(lengths))
     return labels, first, last, lengths
+
+
+def rows_touched(ids, rows, padding_index=-1):
+    """How many positions name each table row (ids equal to padding_index skipped): the support of the reference's
+    RowSparseGradient (RowSparseGradient.cs:14-120)."""
+    ids = np.asarray(ids).reshape(-1)
+    ids = ids[ids != padding_index]
+    return np.bincount(ids, minlength=rows).astype(np.int32)
+
+
+def int_pow(b, n):
+    """Adam.IntPow: binary powering in double (Optimizers.cs:483-499)."""
+    r, b = 1.0, float(b)
+    while n > 0:
+        if n & 1:
+            r *= b
+        b *= b
+        n >>= 1
+    return r
+
+
+def sparse_adam_step(p, g, m, v, touched, t, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8):
+    """SparseAdam.BeginStep + UpdateSparse (Optimizers.cs:680-722) in place on the touched rows of p, m, v; float32 operations
+    in the reference's order, step size from double arithmetic."""
+    f = np.float32
+    b1, b2 = f(beta1), f(beta2)
+    step = f(float(f(lr)) * np.sqrt(1.0 - int_pow(b2, t)) / (1.0 - int_pow(b1, t)))
+    rows = np.nonzero(np.asarray(touched))[0]
+    gi = g[rows].astype(f)
+    mi = b1 * m[rows] + (f(1) - b1) * gi
+    vi = b2 * v[rows] + ((f(1) - b2) * gi) * gi
+    m[rows], v[rows] = mi, vi
+    p[rows] = p[rows] - (step * mi) / (np.sqrt(vi) + f(eps))
+
+
+def sparse_sgd_step(p, g, touched, lr):
+    """Sgd.UpdateSparse (Optimizers.cs:377-397): p -= lr * g on the touched rows."""
+    rows = np.nonzero(np.asarray(touched))[0]
+    p[rows] = p[rows] - np.float32(lr) * g[rows]

@@ -153,3 +153,57 @@ def test_graph_op_family(B):
     """MatMulBatched (broadcast batch axes), Erf, Exp, Sqrt, Pow, Where, Gather and their backward functions on the GPU
     against the PyTorch golden file the CPU oracle is pinned on (fp32 products: the 1e-4 tier, here far inside it)."""
     check_graph_ops(B, 1e-5)
+
+
+@pytest.mark.parametrize("name,lr,b1,b2,eps", [("sparseadam", 0.05, 0.9, 0.999, 1e-3), ("sparseadam2", 0.02, 0.8, 0.95, 1e-8), ("sgd", 0.5, 0, 0, 0)])
+def test_row_sparse_optimizers_against_the_reference_fixture(ctx, B, name, lr, b1, b2, eps):
+    """om_rows_touched + om_optim_sparse_adam_step / om_optim_sparse_sgd_step on the embedding table, the dense optimizers on
+    the head: losses and final parameters of testdata/training/sparse within the reference's 1e-6
+    (SparseAndFrozenTests.cs:255-420); untouched rows keep their parameters and moments bit for bit."""
+    import ctypes as C
+    import om_binding as omb
+    from om_binding import f32, i32, i64
+    from oracle import oracle as K
+    fx = load_fixture("training", "sparse")
+    ids_all, y_all = fx["in.ids"].astype(np.int64), fx["in.y"].astype(np.int64)
+    emb, hw, hb = B.tensor(fx["in.emb"], True), B.tensor(fx["in.hw"], True), B.tensor(fx["in.hb"], True)
+    if name == "sgd":
+        head = omb.Optimizer.sgd([hw, hb], 0.5)
+    elif name == "sparseadam":
+        head = omb.Optimizer.adamw([hw, hb], 0.01, weight_decay=0.01)
+    else:
+        head = omb.Optimizer.adam([hw, hb], 0.01)
+    m, v, touched = ctx.zeros((40, 8)), ctx.zeros((40, 8)), ctx.empty((40,), np.int32)
+    losses, ever = [], np.zeros(40, bool)
+    for s in range(ids_all.shape[0]):
+        ids = B.ids(ids_all[s])
+        pooled = B.mean(omb.call("embedding", [emb, ids], ints=[0]), 1)
+        loss = B.cross_entropy(B.linear(pooled, hw, hb), B.ids(y_all[s]))
+        emb.zero_grad()
+        head.zero_grad()
+        B.backward(loss)
+        losses.append(float(B.numpy(loss).reshape(-1)[0]))
+        before = emb.numpy()
+        flat = omb.Tensor.from_numpy(ids_all[s].reshape(-1))
+        ctx.call("om_rows_touched", ctx.handle, C.c_void_p(flat.data_ptr), i32(omb.OM_I64), i64(30), i32(40), i64(0), touched.ptr)
+        g = emb.grad
+        if name == "sgd":
+            ctx.call("om_optim_sparse_sgd_step", ctx.handle, C.c_void_p(emb.data_ptr), C.c_void_p(g.data_ptr), touched.ptr, i32(40), i32(8), f32(lr))
+        else:
+            t = s + 1
+            step = np.float32(float(np.float32(lr)) * np.sqrt(1.0 - K.int_pow(np.float32(b2), t)) / (1.0 - K.int_pow(np.float32(b1), t)))
+            ctx.call("om_optim_sparse_adam_step", ctx.handle, C.c_void_p(emb.data_ptr), C.c_void_p(g.data_ptr), m.ptr, v.ptr, touched.ptr,
+                     i32(40), i32(8), f32(b1), f32(b2), f32(eps), f32(step))
+        head.step()
+        ctx.sync()
+        tc = touched.numpy()
+        assert np.array_equal(tc, K.rows_touched(ids_all[s], 40, 0))
+        after = emb.numpy()
+        assert np.array_equal(after[tc == 0], before[tc == 0])
+        if name != "sgd":
+            ever |= tc > 0
+            assert not np.any(m.numpy()[~ever])                  # rows never touched so far have no moment
+    want = fx[f"out.{name}.loss"]
+    assert np.max(np.abs(np.array(losses) - want) / np.abs(want)) <= 1e-6
+    for t, key in ((emb, "emb"), (hw, "hw"), (hb, "hb")):
+        assert scaled_diff(t.numpy(), fx[f"out.{name}.{key}"]) <= 1e-6, key

@@ -146,6 +146,58 @@ def test_autograd_decoder_gradients(B):
     check_grads(B, fx, w)
 
 
+def sparse_case(fx):
+    ids = fx["in.ids"].astype(np.int64)            # [steps, 6, 5], id 0 is the padding row
+    return fx["in.emb"].copy(), fx["in.hw"].copy(), fx["in.hb"].copy(), ids, fx["in.y"].astype(np.int64)
+
+
+def test_sparse_adam_and_sparse_sgd_against_the_reference_fixture(oracle_built):
+    """testdata/training/sparse (SparseAndFrozenTests.cs:255-420 of the reference): Embedding(40, 8, padding 0) -> mean over
+    the sequence -> Linear(8, 3) -> cross-entropy; the table is updated by the row-sparse optimizers, the head by AdamW / Adam /
+    Sgd. Losses and final parameters within the reference's 1e-6."""
+    from oracle import oracle as K, tape as A
+    fx = load_fixture("training", "sparse")
+
+    def run(name, table_step, head_step):
+        emb, hw, hb, ids, y = sparse_case(fx)
+        losses, state = [], {}
+        for s in range(ids.shape[0]):
+            E, W, Bv = A.T(emb, True), A.T(hw, True), A.T(hb, True)
+            loss = A.cross_entropy(A.linear(A.mean(A.embedding(E, ids[s], 0), 1), W, Bv), y[s])
+            loss.backward()
+            losses.append(float(loss.v))
+            touched = K.rows_touched(ids[s], 40, 0)
+            assert not np.any(E.grad[touched == 0])          # the dense-format gradient is zero off the touched rows
+            if s == 0 and name == "sgd":
+                assert scaled_diff(E.grad, fx["out.sgd.grad0"]) <= 1e-6
+            table_step(emb, E.grad, touched, s + 1, state)
+            head_step([hw, hb], [W.grad, Bv.grad], s + 1, state)
+        assert np.max(np.abs(np.array(losses) - fx[f"out.{name}.loss"]) / np.abs(fx[f"out.{name}.loss"])) <= 1e-6
+        for got, key in ((emb, "emb"), (hw, "hw"), (hb, "hb")):
+            assert scaled_diff(got, fx[f"out.{name}.{key}"]) <= 1e-6, (name, key)
+
+    def adam_heads(lr, wd, decoupled):
+        def step(ps, gs, t, state):
+            for i, (p, g) in enumerate(zip(ps, gs)):
+                st = state.setdefault(("h", i), dict(m=np.zeros_like(p), v=np.zeros_like(p)))
+                K.adam_step(p, g, st["m"], st["v"], None, t, lr, 0.9, 0.999, 1e-8, wd, decoupled, False)
+        return step
+
+    def sparse_adam(lr, b1, b2, eps):
+        def step(p, g, touched, t, state):
+            st = state.setdefault("t", dict(m=np.zeros_like(p), v=np.zeros_like(p)))
+            K.sparse_adam_step(p, g, st["m"], st["v"], touched, t, lr, b1, b2, eps)
+        return step
+
+    def sgd_heads(ps, gs, t, state):
+        for p, g in zip(ps, gs):
+            K.sgd_step(p, g, np.zeros_like(p), True, 0.5)
+
+    run("sgd", lambda p, g, touched, t, state: K.sparse_sgd_step(p, g, touched, 0.5), sgd_heads)
+    run("sparseadam", sparse_adam(0.05, 0.9, 0.999, 1e-3), adam_heads(0.01, 0.01, True))
+    run("sparseadam2", sparse_adam(0.02, 0.8, 0.95, 1e-8), adam_heads(0.01, 0.0, False))
+
+
 def check_graph_ops(B, tol):
     """The graph-op family against tests/golden/graph_ops.npz (PyTorch CPU, generated by tests/golden/make_graphops_golden.py)."""
     import os
