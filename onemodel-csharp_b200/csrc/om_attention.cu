@@ -18,6 +18,13 @@ int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const fl
                       const float* B, int ldb, long long sB, long long iB, float* C, int ldc, long long sC, long long iC, int batch,
                       int inner, int acc, const float* bias);
 
+bool attention_tc_fwd_supported(om_ctx* ctx, const float* q, const om_head_strides* qs, const float* k, const om_head_strides* ks,
+                                const float* v, const om_head_strides* vs, const float* out, const om_head_strides* os, int b, int h,
+                                int lq, int lk, int d);
+int32_t attention_tc_fwd(om_ctx* ctx, const float* q, const om_head_strides* qs, const float* k, const om_head_strides* ks, const float* v,
+                         const om_head_strides* vs, const float* mask, long long mask_batch_stride, int b, int h, int lq, int lk, int d,
+                         float scale, float* out, const om_head_strides* os, float* lse);
+
 // Where the [l, d] matrix of (batch b, head h) of an activation starts and how its rows are spaced: element strides.
 struct HeadView {
   const float* p;
@@ -196,6 +203,9 @@ int32_t om_attention_fwd_strided(om_ctx* ctx, const float* q, const om_head_stri
   if (bh == 0 || lq == 0) return OM_OK;
   if (lk == 0) return fail(ctx, OM_ERR_SHAPE, "Attention: no keys");
   ProfileScope prof(ctx, "om_attention_fwd", 4.0 * bh * (double)lq * lk * d, 4.0 * bh * ((double)lq * d * 2 + (double)lk * d * 2));
+  // Sequences that fit one tile run as one fused tensor-pipe kernel per (batch, head); the scores stay in tensor memory.
+  if (attention_tc_fwd_supported(ctx, q, qs, k, ks, v, vs, out, os, b, h, lq, lk, d))
+    return attention_tc_fwd(ctx, q, qs, k, ks, v, vs, mask, mask_batch_stride, b, h, lq, lk, d, scale, out, os, lse);
   float* s = nullptr;
   int64_t rows = (int64_t)bh * lq;
   OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)rows * lk, false, (void**)&s));

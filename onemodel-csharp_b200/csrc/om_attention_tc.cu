@@ -1,0 +1,294 @@
+// Fused attention on the tensor pipe for sequences that fit one tile (Lq, Lk <= 128): one CTA per (batch, head) keeps the
+// score matrix in tensor memory from the first product to the last, so the [B*H, Lq, Lk] scores and probabilities never
+// travel through HBM.
+//
+// Forward (AttentionDriver.Run in the reference, Kernels/AttentionDriver.cs:29; Ops.Attention, Ops.Layers.cs:746-807):
+//   S = Q K^T            tcgen05.mma, Q and K tiles K-major, accumulator 128 x 128 in TMEM
+//   P = softmax(scale S + mask)   each of 128 threads owns one row (tcgen05.ld gives a thread its whole row), max and
+//                                 sum are thread-local (fp32: this kernel only serves the TF32 tier)
+//   O = P V              P goes to shared memory in the K-major swizzled operand layout, V is an MN-major tile
+// and the row log-sum-exp is kept for the backward.
+//
+// Every mbarrier wait is bounded (om_tc.cuh): on expiry the kernel raises OM_ERR_TIMEOUT in the status word, all roles
+// leave, TMEM is released.
+#include "om_tc.cuh"
+
+namespace om {
+
+constexpr int ATT_TILE = 128;                 // queries and keys per CTA
+constexpr int ATT_THREADS = 160;              // warps 0-3: one accumulator row per thread; warp 4: TMA + MMA issue
+constexpr int ATT_BLOCK_BYTES = ATT_TILE * 128;   // one [128 rows x 128 bytes] operand block: 16 KiB
+
+struct AttFwdParams {
+  int lq, lk, d, heads;
+  float scale;
+  const float* mask;
+  long long mask_batch_stride;
+  float* out;
+  long long o_batch, o_head, o_row;
+  float* lse;            // [B*H, lq] or null
+  int32_t* status;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// Instruction descriptor for kind::tf32 with an fp32 accumulator: M = 128, N = n, operand major bits.
+__device__ __forceinline__ uint32_t att_idesc(int n, bool a_mn, bool b_mn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(ATT_TILE >> 4) << 24);
+}
+
+// Writes one accumulator row (values v[0..127], already TF32) into a K-major operand tile of 4 blocks [128 rows x 128 B]
+// with the 128-byte swizzle on 16-byte units: chunk c of row r sits at chunk c ^ (r & 7).
+__device__ __forceinline__ void store_row_kmajor(uint8_t* tile, int row, const float* v) {
+#pragma unroll
+  for (int kb = 0; kb < 4; kb++) {
+    uint8_t* base = tile + kb * ATT_BLOCK_BYTES + row * 128;
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+      const int j = kb * 32 + c * 4;
+      *reinterpret_cast<float4*>(base + ((c ^ (row & 7)) << 4)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+attention_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, AttFwdParams p) {
+  constexpr int DB = D / 32;                            // 128-byte blocks along the head dimension
+  constexpr uint32_t TMEM_COLS = 256;                   // S: 128 columns, O: D columns
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // P (4 blocks, a K-major operand of 128 keys) is written over the Q and K tiles, which are dead once S is complete;
+  // the same region stages the output rows at the end. V follows it.
+  uint8_t* p_s = smem;
+  uint8_t* q_s = smem;
+  uint8_t* k_s = q_s + DB * ATT_BLOCK_BYTES;
+  uint8_t* v_s = smem + 4 * ATT_BLOCK_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + DB * ATT_BLOCK_BYTES);
+  uint64_t *bar_load = bars, *bar_s = bars + 1, *bar_p = bars + 2, *bar_o = bars + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x, bi = bh / p.heads, hi = bh % p.heads;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_load, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_p, ATT_TILE);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---- loads ----
+      mbar_expect_tx(bar_load, 3 * DB * ATT_BLOCK_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < DB; kb++) {
+        tma_load_4d(q_s + kb * ATT_BLOCK_BYTES, &map_q, 32 * kb, 0, hi, bi, bar_load);
+        tma_load_4d(k_s + kb * ATT_BLOCK_BYTES, &map_k, 32 * kb, 0, hi, bi, bar_load);
+        tma_load_4d(v_s + kb * ATT_BLOCK_BYTES, &map_v, 32 * kb, 0, hi, bi, bar_load);
+      }
+      bool ok = mbar_wait(bar_load, 0, abort_flag, p.status, 11);
+      if (ok) {
+        tc_fence_after();
+        // ---- S = Q K^T: both operands K-major, k = D ----
+        const uint32_t idesc = att_idesc(ATT_TILE, false, false);
+        const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s);
+#pragma unroll
+        for (int ks = 0; ks < D / 8; ks++) {
+          const uint32_t off = (ks / 4) * ATT_BLOCK_BYTES + (ks % 4) * 32;
+          umma_tf32(tmem_base, make_desc(qa + off, 16, 1024, 2), make_desc(ka + off, 16, 1024, 2), idesc, ks > 0 ? 1u : 0u);
+        }
+      }
+      umma_commit(bar_s);
+      // ---- O = P V: P K-major from shared memory (k = 128 keys), V MN-major (n = D) ----
+      if (ok) ok = mbar_wait(bar_p, 0, abort_flag, p.status, 12);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t idesc = att_idesc(D, false, true);
+        const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s);
+#pragma unroll
+        for (int ks = 0; ks < ATT_TILE / 8; ks++) {
+          const uint64_t adesc = make_desc(pa + (ks / 4) * ATT_BLOCK_BYTES + (ks % 4) * 32, 16, 1024, 2);
+          const uint64_t bdesc = make_desc(va + ks * 1024, ATT_BLOCK_BYTES, 512, 1);
+          umma_tf32(tmem_base + ATT_TILE, adesc, bdesc, idesc, ks > 0 ? 1u : 0u);
+        }
+      }
+      umma_commit(bar_o);
+    }
+  } else {
+    // ---- one row per thread ----
+    const int row = warp * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+    bool ok = mbar_wait(bar_s, 0, abort_flag, p.status, 13);
+    tc_fence_after();
+    float v[ATT_TILE];
+    if (ok) {
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_base + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[c * 32 + j] = __uint_as_float(r[j]);
+      }
+      // scale * s + mask, row maximum, exponentials and their sum; four independent chains keep the pipes busy. The
+      // exponential is 2^(x * log2 e) on the special-function unit; the sum runs in fp32 (128 terms).
+      const float* mrow = nullptr;
+      if (p.mask && row < p.lq) mrow = p.mask + (long long)bi * p.mask_batch_stride + (long long)row * p.lk;
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (mrow == nullptr && p.lk == ATT_TILE) {
+#pragma unroll
+        for (int j = 0; j < ATT_TILE; j++) {
+          v[j] = v[j] * p.scale;
+          m4[j & 3] = fmaxf(m4[j & 3], v[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < ATT_TILE; j++) {
+          float s = -INFINITY;
+          if (j < p.lk) s = (v[j] * p.scale) + (mrow ? mrow[j] : 0.f);
+          v[j] = s;
+          m4[j & 3] = fmaxf(m4[j & 3], s);
+        }
+      }
+      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      const float mxl = mx * 1.4426950408889634f;
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < ATT_TILE; j++) {
+        float e = exp2f(fmaf(v[j], 1.4426950408889634f, -mxl));     // exp(-inf) = 0 for the columns past lk
+        v[j] = e;
+        s4[j & 3] += e;
+      }
+      const float fs = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+      const float inv = 1.0f / fs;
+#pragma unroll
+      for (int j = 0; j < ATT_TILE; j++) v[j] = to_tf32(v[j] * inv);
+      if (p.lse && row < p.lq) p.lse[(long long)bh * p.lq + row] = mx + logf(fs);
+      store_row_kmajor(p_s, row, v);
+      fence_async_smem();
+    }
+    mbar_arrive(bar_p);
+    // ---- output ----
+    if (ok) ok = mbar_wait(bar_o, 0, abort_flag, p.status, 14);
+    tc_fence_after();
+    if (ok) {
+      constexpr int STG_LD = D + 4;
+      float* stg = reinterpret_cast<float*>(p_s) + warp * 32 * STG_LD;   // the PV products have consumed P
+      float* outp = p.out + (long long)bi * p.o_batch + (long long)hi * p.o_head;
+#pragma unroll
+      for (int c = 0; c < DB; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_base + ATT_TILE + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(stg + lane * STG_LD + c * 32 + j) =
+              make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      }
+      __syncwarp();
+      // D / 4 lanes cover one output row (D floats, contiguous in memory); a warp store writes 32 / (D / 4) rows.
+      constexpr int LPR = D / 4, RPI = 32 / LPR;
+#pragma unroll
+      for (int i = 0; i < 32 / RPI; i++) {
+        const int rr = i * RPI + lane / LPR;
+        const int orow = warp * 32 + rr;
+        if (orow < p.lq) {
+          const float4 val = *reinterpret_cast<const float4*>(stg + rr * STG_LD + (lane % LPR) * 4);
+          *reinterpret_cast<float4*>(outp + (long long)orow * p.o_row + (lane % LPR) * 4) = val;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Rank-4 map over an activation seen as [B, H, L, D] through element strides; box = [32 floats, 128 rows, 1, 1].
+static bool att_map(CUtensorMap* map, const float* base, int d, int l, int heads, int batch, long long s_row, long long s_head,
+                    long long s_batch, bool mn_major) {
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)l, (cuuint64_t)heads, (cuuint64_t)batch};
+  const cuuint64_t filler = ((cuuint64_t)s_row * 4 * (cuuint64_t)l + 15) & ~(cuuint64_t)15;
+  cuuint64_t strides[3] = {(cuuint64_t)s_row * 4, heads > 1 ? (cuuint64_t)s_head * 4 : filler, batch > 1 ? (cuuint64_t)s_batch * 4 : filler};
+  cuuint32_t box[4] = {32, (cuuint32_t)ATT_TILE, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool att_operand_ok(const float* p, const om_head_strides* s, int heads, int batch) {
+  if ((reinterpret_cast<uintptr_t>(p) & 15) || (s->row & 3) || s->row <= 0) return false;
+  if (heads > 1 && ((s->head & 3) || s->head <= 0)) return false;
+  if (batch > 1 && ((s->batch & 3) || s->batch <= 0)) return false;
+  return true;
+}
+
+bool attention_tc_fwd_supported(om_ctx* ctx, const float* q, const om_head_strides* qs, const float* k, const om_head_strides* ks,
+                                const float* v, const om_head_strides* vs, const float* out, const om_head_strides* os, int b, int h,
+                                int lq, int lk, int d) {
+  if (!(ctx->flags & OM_TF32) || !encode_fn()) return false;
+  if (lq < 1 || lk < 1 || lq > ATT_TILE || lk > ATT_TILE || (d != 32 && d != 64) || b < 1 || h < 1) return false;
+  if (!att_operand_ok(q, qs, h, b) || !att_operand_ok(k, ks, h, b) || !att_operand_ok(v, vs, h, b)) return false;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (os->row & 3) || (os->head & 3) || (os->batch & 3)) return false;
+  return true;
+}
+
+int32_t attention_tc_fwd(om_ctx* ctx, const float* q, const om_head_strides* qs, const float* k, const om_head_strides* ks, const float* v,
+                         const om_head_strides* vs, const float* mask, long long mask_batch_stride, int b, int h, int lq, int lk, int d,
+                         float scale, float* out, const om_head_strides* os, float* lse) {
+  CUtensorMap mq, mk, mv;
+  if (!att_map(&mq, q, d, lq, h, b, qs->row, qs->head, qs->batch, false) || !att_map(&mk, k, d, lk, h, b, ks->row, ks->head, ks->batch, false) ||
+      !att_map(&mv, v, d, lk, h, b, vs->row, vs->head, vs->batch, true))
+    return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed for the attention operands");
+  AttFwdParams p;
+  p.lq = lq; p.lk = lk; p.d = d; p.heads = h; p.scale = scale; p.mask = mask; p.mask_batch_stride = mask_batch_stride;
+  p.out = out; p.o_batch = os->batch; p.o_head = os->head; p.o_row = os->row; p.lse = lse; p.status = ctx->status_dev;
+  const size_t smem = (size_t)((d / 32) + 4) * ATT_BLOCK_BYTES + 1024 + 256;
+  const unsigned grid = (unsigned)(b * h);
+  if (d == 32) {
+    static bool set32 = false;
+    if (!set32) {
+      OM_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      set32 = true;
+    }
+    attention_fwd_tc_kernel<32><<<grid, ATT_THREADS, smem, ctx->stream>>>(mq, mk, mv, p);
+  } else {
+    static bool set64 = false;
+    if (!set64) {
+      OM_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      set64 = true;
+    }
+    attention_fwd_tc_kernel<64><<<grid, ATT_THREADS, smem, ctx->stream>>>(mq, mk, mv, p);
+  }
+  OM_LAUNCH_CHECK(ctx, "attention_fwd_tc");
+  return OM_OK;
+}
+
+}  // namespace om
