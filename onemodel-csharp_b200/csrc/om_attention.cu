@@ -25,6 +25,15 @@ int32_t attention_tc_fwd(om_ctx* ctx, const float* q, const om_head_strides* qs,
                          const om_head_strides* vs, const float* mask, long long mask_batch_stride, int b, int h, int lq, int lk, int d,
                          float scale, float* out, const om_head_strides* os, float* lse);
 
+bool attention_tc_bwd_supported(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs,
+                                const float* k, const om_head_strides* ks, const float* v, const om_head_strides* vs, const float* lse,
+                                int b, int h, int lq, int lk, int d, const float* dq, const om_head_strides* dqs, const float* dk,
+                                const om_head_strides* dks, const float* dv, const om_head_strides* dvs);
+int32_t attention_tc_bwd(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs, const float* k,
+                         const om_head_strides* ks, const float* v, const om_head_strides* vs, const float* mask, long long mask_batch_stride,
+                         const float* lse, int b, int h, int lq, int lk, float scale, float* dq, const om_head_strides* dqs, float* dk,
+                         const om_head_strides* dks, float* dv, const om_head_strides* dvs);
+
 // Where the [l, d] matrix of (batch b, head h) of an activation starts and how its rows are spaced: element strides.
 struct HeadView {
   const float* p;
@@ -235,7 +244,6 @@ int32_t om_attention_bwd_strided(om_ctx* ctx, const float* g, const om_head_stri
                                  int32_t lk, int32_t d, float scale, float* dq, const om_head_strides* dqs, float* dk,
                                  const om_head_strides* dks, float* dv, const om_head_strides* dvs) {
   OM_CHECK_CTX(ctx);
-  (void)lse;
   OM_TRY(check_att(ctx, "Attention backward", b, h, lq, lk, d));
   OM_TRY(check_strides(ctx, "Attention backward", gs, d));
   OM_TRY(check_strides(ctx, "Attention backward", qs, d));
@@ -247,6 +255,9 @@ int32_t om_attention_bwd_strided(om_ctx* ctx, const float* g, const om_head_stri
   int bh = b * h;
   if (bh == 0 || lq == 0 || lk == 0) return OM_OK;
   ProfileScope prof(ctx, "om_attention_bwd", 8.0 * bh * (double)lq * lk * d, 4.0 * bh * ((double)lq * d * 4 + (double)lk * d * 4));
+  // One-tile sequences with the forward's log-sum-exp at hand: one fused tensor-pipe kernel per (batch, head).
+  if (attention_tc_bwd_supported(ctx, g, gs, q, qs, k, ks, v, vs, lse, b, h, lq, lk, d, dq, dqs, dk, dks, dv, dvs))
+    return attention_tc_bwd(ctx, g, gs, q, qs, k, ks, v, vs, mask, mask_batch_stride, lse, b, h, lq, lk, scale, dq, dqs, dk, dks, dv, dvs);
   int64_t rows = (int64_t)bh * lq;
   float *p = nullptr, *dp = nullptr;
   OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)rows * lk, false, (void**)&p));

@@ -230,6 +230,260 @@ attention_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   }
 }
 
+// ---- backward -------------------------------------------------------------------------------------------------------------
+// AttentionBackward of the reference (BackwardNn.cs:636-701) for one (batch, head) per CTA, head dimension 32:
+//   S = Q K^T, dP = dO V^T                      (K-major tiles, accumulators in TMEM columns 0-127 and 128-255)
+//   P = exp(scale S + mask - lse)               (lse saved by the forward), dot = rowsum(P dP), dS = P (dP - dot) scale
+//   dV = P^T dO, dQ = dS K, dK = dS^T Q         (P and dS go to shared memory as MN-major / K-major operands; the second
+//                                                operands are MN-major tiles fetched again by TMA over the dead K-major ones)
+// Rows are split over two threads (columns 0-63 and 64-127) so that eight warps share the exponentials.
+constexpr int ATT_BWD_THREADS = 288;          // warps 0-7: half an accumulator row per thread; warp 8: TMA + MMA issue
+
+struct AttBwdParams {
+  int lq, lk, heads;
+  float scale;
+  const float* mask;
+  long long mask_batch_stride;
+  const float* lse;
+  float *dq, *dk, *dv;
+  long long dq_batch, dq_head, dq_row, dk_batch, dk_head, dk_row, dv_batch, dv_head, dv_row;
+  int32_t* status;
+};
+
+// 32 consecutive floats (one 128-byte row segment) of a K-major operand block: chunk c of row r sits at c ^ (r & 7).
+__device__ __forceinline__ void store_seg_kmajor(uint8_t* block, int row, const float* v) {
+  uint8_t* base = block + row * 128;
+#pragma unroll
+  for (int c = 0; c < 8; c++)
+    *reinterpret_cast<float4*>(base + ((c ^ (row & 7)) << 4)) = make_float4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+}
+// The same 32 floats as row `krow` of an MN-major chunk [128 k-rows x 128 bytes]: 128-byte swizzle on 32-byte units,
+// address bits 5-6 ^= bits 7-8 (the k-row's low two bits).
+__device__ __forceinline__ void store_seg_mnmajor(uint8_t* chunk, int krow, const float* v) {
+  uint8_t* base = chunk + krow * 128;
+  const int x = (krow & 3) << 5;
+#pragma unroll
+  for (int c = 0; c < 8; c++)
+    *reinterpret_cast<float4*>(base + ((c << 4) ^ x)) = make_float4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+}
+
+__device__ __forceinline__ void store_rows_32(float* stg, int lane, const uint32_t (&r)[32], float* dst, long long row_stride, int row0,
+                                              int rows_valid) {
+  // stg: 32 x 36 floats of this warp. Turn the 32 x 32 block so that eight lanes write one 128-byte row.
+#pragma unroll
+  for (int j = 0; j < 32; j += 4)
+    *reinterpret_cast<float4*>(stg + lane * 36 + j) =
+        make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int rr = i * 4 + (lane >> 3);
+    if (row0 + rr < rows_valid)
+      *reinterpret_cast<float4*>(dst + (long long)(row0 + rr) * row_stride + (lane & 7) * 4) =
+          *reinterpret_cast<const float4*>(stg + rr * 36 + (lane & 7) * 4);
+  }
+  __syncwarp();
+}
+
+__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
+attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_kk,
+                        const __grid_constant__ CUtensorMap map_vk, const __grid_constant__ CUtensorMap map_gk,
+                        const __grid_constant__ CUtensorMap map_qm, const __grid_constant__ CUtensorMap map_km,
+                        const __grid_constant__ CUtensorMap map_gm, AttBwdParams p) {
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DQ = 288, COL_DK = 320;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* slot_q = smem;                               // Q K-major, later Q MN-major
+  uint8_t* slot_k = smem + 1 * ATT_BLOCK_BYTES;         // K K-major, later K MN-major
+  uint8_t* slot_v = smem + 2 * ATT_BLOCK_BYTES;         // V K-major
+  uint8_t* slot_g = smem + 3 * ATT_BLOCK_BYTES;         // dO K-major, later dO MN-major
+  uint8_t* stage_a = smem + 4 * ATT_BLOCK_BYTES;        // P^T, later dS^T: MN-major operand, 4 chunks of [128 q-rows x 128 B of keys]
+  uint8_t* stage_b = smem + 8 * ATT_BLOCK_BYTES;        // dS: K-major operand, 4 blocks of [128 q-rows x 128 B of keys]; later output staging
+  float* dots = reinterpret_cast<float*>(smem + 12 * ATT_BLOCK_BYTES);   // [2][128] partial row dots
+  uint64_t* bars = reinterpret_cast<uint64_t*>(dots + 2 * ATT_TILE);
+  uint64_t *bar_load = bars, *bar_sdp = bars + 1, *bar_mn = bars + 2, *bar_pt = bars + 3, *bar_dv = bars + 4, *bar_ds = bars + 5,
+           *bar_dqk = bars + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x, bi = bh / p.heads, hi = bh % p.heads;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_load, 1);
+    mbar_init(bar_sdp, 1);
+    mbar_init(bar_mn, 1);
+    mbar_init(bar_pt, 256);
+    mbar_init(bar_dv, 1);
+    mbar_init(bar_ds, 256);
+    mbar_init(bar_dqk, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      mbar_expect_tx(bar_load, 4 * ATT_BLOCK_BYTES);
+      tma_load_4d(slot_q, &map_qk, 0, 0, hi, bi, bar_load);
+      tma_load_4d(slot_k, &map_kk, 0, 0, hi, bi, bar_load);
+      tma_load_4d(slot_v, &map_vk, 0, 0, hi, bi, bar_load);
+      tma_load_4d(slot_g, &map_gk, 0, 0, hi, bi, bar_load);
+      bool ok = mbar_wait(bar_load, 0, abort_flag, p.status, 21);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t idesc = att_idesc(ATT_TILE, false, false);
+        const uint32_t qa = smem_u32(slot_q), ka = smem_u32(slot_k), va = smem_u32(slot_v), ga = smem_u32(slot_g);
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++)      // S = Q K^T
+          umma_tf32(tmem_base + COL_S, make_desc(qa + ks * 32, 16, 1024, 2), make_desc(ka + ks * 32, 16, 1024, 2), idesc, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++)      // dP = dO V^T
+          umma_tf32(tmem_base + COL_DP, make_desc(ga + ks * 32, 16, 1024, 2), make_desc(va + ks * 32, 16, 1024, 2), idesc, ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_sdp);
+      // The K-major tiles are dead once both products are complete: fetch the MN-major forms over them.
+      if (ok) ok = mbar_wait(bar_sdp, 0, abort_flag, p.status, 22);
+      if (ok) {
+        mbar_expect_tx(bar_mn, 3 * ATT_BLOCK_BYTES);
+        tma_load_4d(slot_q, &map_qm, 0, 0, hi, bi, bar_mn);
+        tma_load_4d(slot_k, &map_km, 0, 0, hi, bi, bar_mn);
+        tma_load_4d(slot_g, &map_gm, 0, 0, hi, bi, bar_mn);
+        ok = mbar_wait(bar_mn, 0, abort_flag, p.status, 23);
+      }
+      if (ok) ok = mbar_wait(bar_pt, 0, abort_flag, p.status, 24);
+      if (ok) {
+        tc_fence_after();
+        // dV = P^T dO: A = P^T MN-major (m = keys, k = queries), B = dO MN-major (n = 32)
+        const uint32_t idesc = att_idesc(32, true, true);
+        const uint32_t aa = smem_u32(stage_a), ga = smem_u32(slot_g);
+#pragma unroll
+        for (int ks = 0; ks < ATT_TILE / 8; ks++)
+          umma_tf32(tmem_base + COL_DV, make_desc(aa + ks * 1024, ATT_BLOCK_BYTES, 512, 1), make_desc(ga + ks * 1024, ATT_BLOCK_BYTES, 512, 1),
+                    idesc, ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_dv);
+      if (ok) ok = mbar_wait(bar_ds, 0, abort_flag, p.status, 25);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t aa = smem_u32(stage_a), ba = smem_u32(stage_b), qa = smem_u32(slot_q), ka = smem_u32(slot_k);
+        // dQ = dS K: A = dS K-major (k = keys), B = K MN-major
+        const uint32_t idesc_q = att_idesc(32, false, true);
+#pragma unroll
+        for (int ks = 0; ks < ATT_TILE / 8; ks++)
+          umma_tf32(tmem_base + COL_DQ, make_desc(ba + (ks / 4) * ATT_BLOCK_BYTES + (ks % 4) * 32, 16, 1024, 2),
+                    make_desc(ka + ks * 1024, ATT_BLOCK_BYTES, 512, 1), idesc_q, ks > 0 ? 1u : 0u);
+        // dK = dS^T Q: A = dS^T MN-major (m = keys, k = queries), B = Q MN-major
+        const uint32_t idesc_k = att_idesc(32, true, true);
+#pragma unroll
+        for (int ks = 0; ks < ATT_TILE / 8; ks++)
+          umma_tf32(tmem_base + COL_DK, make_desc(aa + ks * 1024, ATT_BLOCK_BYTES, 512, 1), make_desc(qa + ks * 1024, ATT_BLOCK_BYTES, 512, 1),
+                    idesc_k, ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_dqk);
+    }
+  } else {
+    // ---- half a row per thread: row = 32 * (warp % 4) + lane, columns 64 * (warp / 4) .. + 63 ----
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const float LOG2E = 1.4426950408889634f;
+    bool ok = mbar_wait(bar_sdp, 0, abort_flag, p.status, 26);
+    tc_fence_after();
+    float pv[64], dp[64];
+    float dot = 0.f;
+    if (ok) {
+      const float lse_l = (row < p.lq ? p.lse[(long long)bh * p.lq + row] : 0.f) * LOG2E;
+      const float* mrow = nullptr;
+      if (p.mask && row < p.lq) mrow = p.mask + (long long)bi * p.mask_batch_stride + (long long)row * p.lk;
+      float d4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        const int col0 = half * 64 + c * 32;
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32b_x32(lane_base + COL_S + col0, rs);
+        tmem_ld_32x32b_x32(lane_base + COL_DP + col0, rd);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+          float s = __uint_as_float(rs[j]) * p.scale;
+          if (mrow && col0 + j < p.lk) s = s + mrow[col0 + j];
+          float e = exp2f(fmaf(s, LOG2E, -lse_l));
+          if (col0 + j >= p.lk) e = 0.f;
+          const float d = __uint_as_float(rd[j]);
+          pv[c * 32 + j] = e;
+          dp[c * 32 + j] = d;
+          d4[j & 3] = fmaf(e, d, d4[j & 3]);
+        }
+      }
+      dots[half * ATT_TILE + row] = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      // P^T for dV: this thread's 64 keys of query `row` are two 128-byte segments of k-row `row` in chunks 2*half, 2*half+1.
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        float t[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) t[j] = to_tf32(pv[c * 32 + j]);
+        store_seg_mnmajor(stage_a + (half * 2 + c) * ATT_BLOCK_BYTES, row, t);
+      }
+      fence_async_smem();
+    }
+    mbar_arrive(bar_pt);
+    asm volatile("bar.sync 1, 256;" ::: "memory");      // both halves of every row have published their partial dots
+    if (ok) {
+      dot = dots[row] + dots[ATT_TILE + row];
+#pragma unroll
+      for (int j = 0; j < 64; j++) pv[j] = to_tf32((pv[j] * (dp[j] - dot)) * p.scale);   // dS in place
+#pragma unroll
+      for (int c = 0; c < 2; c++) store_seg_kmajor(stage_b + (half * 2 + c) * ATT_BLOCK_BYTES, row, pv + c * 32);
+      // dS^T goes where P^T was: wait until the dV product has read it.
+      ok = mbar_wait(bar_dv, 0, abort_flag, p.status, 27);
+    }
+    if (ok) {
+#pragma unroll
+      for (int c = 0; c < 2; c++) store_seg_mnmajor(stage_a + (half * 2 + c) * ATT_BLOCK_BYTES, row, pv + c * 32);
+      fence_async_smem();
+    }
+    mbar_arrive(bar_ds);
+    if (ok) ok = mbar_wait(bar_dqk, 0, abort_flag, p.status, 28);
+    tc_fence_after();
+    if (ok) {
+      // Warps 0-3 write dQ and dV, warps 4-7 write dK; each warp owns the 32 rows of its TMEM lane quadrant.
+      float* stg = reinterpret_cast<float*>(stage_b) + warp * 32 * 36;   // the dQ product has consumed dS
+      uint32_t r[32];
+      if (half == 0) {
+        if (p.dq) {
+          tmem_ld_32x32b_x32(lane_base + COL_DQ, r);
+          tmem_ld_wait();
+          store_rows_32(stg, lane, r, p.dq + (long long)bi * p.dq_batch + (long long)hi * p.dq_head, p.dq_row, quad * 32, p.lq);
+        }
+        if (p.dv) {
+          tmem_ld_32x32b_x32(lane_base + COL_DV, r);
+          tmem_ld_wait();
+          store_rows_32(stg, lane, r, p.dv + (long long)bi * p.dv_batch + (long long)hi * p.dv_head, p.dv_row, quad * 32, p.lk);
+        }
+      } else if (p.dk) {
+        tmem_ld_32x32b_x32(lane_base + COL_DK, r);
+        tmem_ld_wait();
+        store_rows_32(stg, lane, r, p.dk + (long long)bi * p.dk_batch + (long long)hi * p.dk_head, p.dk_row, quad * 32, p.lk);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // Rank-4 map over an activation seen as [B, H, L, D] through element strides; box = [32 floats, 128 rows, 1, 1].
 static bool att_map(CUtensorMap* map, const float* base, int d, int l, int heads, int batch, long long s_row, long long s_head,
                     long long s_batch, bool mn_major) {
@@ -288,6 +542,48 @@ int32_t attention_tc_fwd(om_ctx* ctx, const float* q, const om_head_strides* qs,
     attention_fwd_tc_kernel<64><<<grid, ATT_THREADS, smem, ctx->stream>>>(mq, mk, mv, p);
   }
   OM_LAUNCH_CHECK(ctx, "attention_fwd_tc");
+  return OM_OK;
+}
+
+bool attention_tc_bwd_supported(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs,
+                                const float* k, const om_head_strides* ks, const float* v, const om_head_strides* vs, const float* lse,
+                                int b, int h, int lq, int lk, int d, const float* dq, const om_head_strides* dqs, const float* dk,
+                                const om_head_strides* dks, const float* dv, const om_head_strides* dvs) {
+  if (!(ctx->flags & OM_TF32) || !encode_fn() || lse == nullptr) return false;
+  if (lq < 1 || lk < 1 || lq > ATT_TILE || lk > ATT_TILE || d != 32 || b < 1 || h < 1) return false;
+  if (!att_operand_ok(g, gs, h, b) || !att_operand_ok(q, qs, h, b) || !att_operand_ok(k, ks, h, b) || !att_operand_ok(v, vs, h, b)) return false;
+  const float* outs[3] = {dq, dk, dv};
+  const om_head_strides* os[3] = {dqs, dks, dvs};
+  for (int i = 0; i < 3; i++)
+    if (outs[i] && ((reinterpret_cast<uintptr_t>(outs[i]) & 15) || (os[i]->row & 3) || (os[i]->head & 3) || (os[i]->batch & 3))) return false;
+  return true;
+}
+
+int32_t attention_tc_bwd(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs, const float* k,
+                         const om_head_strides* ks, const float* v, const om_head_strides* vs, const float* mask, long long mask_batch_stride,
+                         const float* lse, int b, int h, int lq, int lk, float scale, float* dq, const om_head_strides* dqs, float* dk,
+                         const om_head_strides* dks, float* dv, const om_head_strides* dvs) {
+  CUtensorMap qk, kk, vk, gk, qm, km, gm;
+  bool okm = att_map(&qk, q, 32, lq, h, b, qs->row, qs->head, qs->batch, false) && att_map(&kk, k, 32, lk, h, b, ks->row, ks->head, ks->batch, false) &&
+             att_map(&vk, v, 32, lk, h, b, vs->row, vs->head, vs->batch, false) && att_map(&gk, g, 32, lq, h, b, gs->row, gs->head, gs->batch, false) &&
+             att_map(&qm, q, 32, lq, h, b, qs->row, qs->head, qs->batch, true) && att_map(&km, k, 32, lk, h, b, ks->row, ks->head, ks->batch, true) &&
+             att_map(&gm, g, 32, lq, h, b, gs->row, gs->head, gs->batch, true);
+  if (!okm) return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed for the attention backward operands");
+  AttBwdParams p;
+  p.lq = lq; p.lk = lk; p.heads = h; p.scale = scale; p.mask = mask; p.mask_batch_stride = mask_batch_stride; p.lse = lse;
+  p.dq = dq; p.dk = dk; p.dv = dv;
+  p.dq_batch = dq ? dqs->batch : 0; p.dq_head = dq ? dqs->head : 0; p.dq_row = dq ? dqs->row : 0;
+  p.dk_batch = dk ? dks->batch : 0; p.dk_head = dk ? dks->head : 0; p.dk_row = dk ? dks->row : 0;
+  p.dv_batch = dv ? dvs->batch : 0; p.dv_head = dv ? dvs->head : 0; p.dv_row = dv ? dvs->row : 0;
+  p.status = ctx->status_dev;
+  const size_t smem = (size_t)12 * ATT_BLOCK_BYTES + 2 * ATT_TILE * sizeof(float) + 1024 + 256;
+  static bool set = false;
+  if (!set) {
+    OM_CUDA(ctx, cudaFuncSetAttribute(attention_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    set = true;
+  }
+  attention_bwd_tc_kernel<<<(unsigned)(b * h), ATT_BWD_THREADS, smem, ctx->stream>>>(qk, kk, vk, gk, qm, km, gm, p);
+  OM_LAUNCH_CHECK(ctx, "attention_bwd_tc");
   return OM_OK;
 }
 

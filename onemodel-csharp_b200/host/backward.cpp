@@ -348,7 +348,7 @@ static void AttentionHeadsBackward(BackwardRecord& r, const Tensor& g) {
   if (!dk.IsEmpty()) dks = strides(dk);
   if (!dv.IsEmpty()) dvs = strides(dv);
   Check(om_attention_bwd_strided(C(), gc.Data(), &gs, q.Data(), &qs, k.Data(), &ks, v.Data(), &vs, mask.IsEmpty() ? nullptr : mask.Data(),
-                                 r.Ints[0], nullptr, b, heads, lq, lk, d, (float)r.Floats[0], dq.IsEmpty() ? nullptr : dq.Data(), &dqs,
+                                 r.Ints[0], r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, heads, lq, lk, d, (float)r.Floats[0], dq.IsEmpty() ? nullptr : dq.Data(), &dqs,
                                  dk.IsEmpty() ? nullptr : dk.Data(), &dks, dv.IsEmpty() ? nullptr : dv.Data(), &dvs));
   if (!dq.IsEmpty()) Engine::Emit(r, 0, dq, true);
   if (!dk.IsEmpty()) Engine::Emit(r, 1, dk, true);
@@ -365,7 +365,8 @@ static void AttentionPackedBackward(BackwardRecord& r, const Tensor& g) {
   Tensor dqkv = Tensor::Create(DType::F32, qkv.GetShape());
   om_head_strides ps{(int64_t)l * 3 * width, (int64_t)d, (int64_t)3 * width}, gs{(int64_t)l * width, (int64_t)d, (int64_t)width};
   Check(om_attention_bwd_strided(C(), gc.Data(), &gs, qkv.Data(), &ps, qkv.Data() + width, &ps, qkv.Data() + 2 * width, &ps,
-                                 mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0], nullptr, b, heads, l, l, d, (float)r.Floats[0],
+                                 mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0], r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, heads, l, l, d,
+                                 (float)r.Floats[0],
                                  dqkv.Data(), &ps, dqkv.Data() + width, &ps, dqkv.Data() + 2 * width, &ps));
   Engine::Emit(r, 0, dqkv, true);
 }
@@ -381,7 +382,7 @@ static void AttentionBackward(BackwardRecord& r, const Tensor& g) {
   if (r.NeedsInputGrad(1)) dk = Tensor::Create(DType::F32, k.GetShape());
   if (r.NeedsInputGrad(2)) dv = Tensor::Create(DType::F32, v.GetShape());
   Check(om_attention_bwd(C(), gc.Data(), q.Data(), k.Data(), v.Data(), mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0],
-                         nullptr, b, h, lq, lk, d, (float)r.Floats[0], dq.IsEmpty() ? nullptr : dq.Data(),
+                         r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, h, lq, lk, d, (float)r.Floats[0], dq.IsEmpty() ? nullptr : dq.Data(),
                          dk.IsEmpty() ? nullptr : dk.Data(), dv.IsEmpty() ? nullptr : dv.Data()));
   if (!dq.IsEmpty()) Engine::Emit(r, 0, dq, true);
   if (!dk.IsEmpty()) Engine::Emit(r, 1, dk, true);

@@ -343,10 +343,13 @@ Tensor Ops::Attention(const Tensor& q, const Tensor& k, const Tensor& v, const T
   if (scale == 0.f || isnan(scale)) scale = 1.0f / sqrtf((float)d);
   Tensor qc = q.Contiguous(), kc = k.Contiguous(), vc = v.Contiguous();
   Tensor r = NewOut(q.GetShape());
+  const bool recording = Recording({&q, &k, &v});
+  Tensor lse = recording ? Tensor::Create(DType::F32, Shape{b, h, lq}) : Tensor();   // row log-sum-exp, kept for the backward
   Check(om_attention_fwd(C(), qc.Data(), kc.Data(), vc.Data(), mc.IsEmpty() ? nullptr : mc.Data(), maskStride, b, h, lq, lk,
-                         d, scale, r.Data(), nullptr));
-  if (!Recording({&q, &k, &v})) return r;
-  auto rec = BackwardRecord::Create(OpKind::Attention, 4, {&q, &k, &v});
+                         d, scale, r.Data(), lse.IsEmpty() ? nullptr : lse.Data()));
+  if (!recording) return r;
+  auto rec = BackwardRecord::Create(OpKind::Attention, 5, {&q, &k, &v});
+  rec->Save(4, lse);
   rec->Save(0, qc.Detach());
   rec->Save(1, kc.Detach());
   rec->Save(2, vc.Detach());
@@ -392,10 +395,13 @@ Tensor Ops::AttentionHeads(const Tensor& q, const Tensor& k, const Tensor& v, in
   Tensor qc = HeadsOperand(q), kc = HeadsOperand(k), vc = HeadsOperand(v);
   Tensor r = NewOut(q.GetShape());
   om_head_strides qs = HeadStridesOf(qc, d), ks = HeadStridesOf(kc, d), vs = HeadStridesOf(vc, d), os = HeadStridesOf(r, d);
+  const bool recording = Recording({&q, &k, &v});
+  Tensor lse = recording ? Tensor::Create(DType::F32, Shape{b, heads, lq}) : Tensor();
   Check(om_attention_fwd_strided(C(), qc.Data(), &qs, kc.Data(), &ks, vc.Data(), &vs, mc.IsEmpty() ? nullptr : mc.Data(), maskStride,
-                                 b, heads, lq, lk, d, scale, r.Data(), &os, nullptr));
-  if (!Recording({&q, &k, &v})) return r;
-  auto rec = BackwardRecord::Create(OpKind::Attention, 4, {&q, &k, &v});
+                                 b, heads, lq, lk, d, scale, r.Data(), &os, lse.IsEmpty() ? nullptr : lse.Data()));
+  if (!recording) return r;
+  auto rec = BackwardRecord::Create(OpKind::Attention, 5, {&q, &k, &v});
+  rec->Save(4, lse);
   rec->Save(0, qc.Detach());
   rec->Save(1, kc.Detach());
   rec->Save(2, vc.Detach());
@@ -465,10 +471,13 @@ Tensor Ops::AttentionPacked(const Tensor& qkv, int heads, const Tensor& mask, fl
   Tensor pc = qkv.Contiguous();
   Tensor r = NewOut(Shape{b, l, width});
   om_head_strides ps{(int64_t)l * 3 * width, (int64_t)d, (int64_t)3 * width}, os{(int64_t)l * width, (int64_t)d, (int64_t)width};
+  const bool recording = Recording({&qkv});
+  Tensor lse = recording ? Tensor::Create(DType::F32, Shape{b, heads, l}) : Tensor();
   Check(om_attention_fwd_strided(C(), pc.Data(), &ps, pc.Data() + width, &ps, pc.Data() + 2 * width, &ps, mc.IsEmpty() ? nullptr : mc.Data(),
-                                 maskStride, b, heads, l, l, d, scale, r.Data(), &os, nullptr));
-  if (!Recording({&qkv})) return r;
-  auto rec = BackwardRecord::Create(OpKind::Attention, 4, {&qkv});
+                                 maskStride, b, heads, l, l, d, scale, r.Data(), &os, lse.IsEmpty() ? nullptr : lse.Data()));
+  if (!recording) return r;
+  auto rec = BackwardRecord::Create(OpKind::Attention, 5, {&qkv});
+  rec->Save(4, lse);
   rec->Save(0, pc.Detach());
   if (!mc.IsEmpty()) rec->Save(3, mc);
   rec->Floats = {scale};

@@ -136,10 +136,11 @@ def test_tf32_attention(ctx, oracle_built, b, h, lq, lk, d, masked):
         scale = np.float32(1.0 / np.sqrt(np.float32(d)))
         Q, Kk, V, G = ctx.to_device(q), ctx.to_device(k), ctx.to_device(v), ctx.to_device(g)
         M = ctx.to_device(mask) if mask is not None else None
-        O, DQ, DK, DV = ctx.empty(q.shape), ctx.empty(q.shape), ctx.empty(k.shape), ctx.empty(v.shape)
+        O, DQ, DK, DV, LSE = ctx.empty(q.shape), ctx.empty(q.shape), ctx.empty(k.shape), ctx.empty(v.shape), ctx.empty((b, h, lq))
         ctx.call("om_attention_fwd", ctx.handle, Q.ptr, Kk.ptr, V.ptr, M.ptr if M else None, i64(0), i32(b), i32(h), i32(lq),
-                 i32(lk), i32(d), f32(scale), O.ptr, None)
-        ctx.call("om_attention_bwd", ctx.handle, G.ptr, Q.ptr, Kk.ptr, V.ptr, M.ptr if M else None, i64(0), None, i32(b),
+                 i32(lk), i32(d), f32(scale), O.ptr, LSE.ptr)
+        # With the forward's row log-sum-exp the one-tile shapes (L <= 128, D = 32) take the fused backward kernel.
+        ctx.call("om_attention_bwd", ctx.handle, G.ptr, Q.ptr, Kk.ptr, V.ptr, M.ptr if M else None, i64(0), LSE.ptr, i32(b),
                  i32(h), i32(lq), i32(lk), i32(d), f32(scale), DQ.ptr, DK.ptr, DV.ptr)
         ctx.sync()
         # Two (forward) to three (backward) TF32 products in a chain, each rounding its operands to 11 bits: the scaled error
