@@ -88,6 +88,9 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": float(np.median([s for s, _ in self.samples])), "sm_max_mhz": self.max_mhz, "reasons": reasons}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per gemm_tc_kernel launch, averaged over the matrix-product launches of one
+# ncu capture of this workload (profiles/tensor_pipe_kernels_c3.md gives the command and the per-shape table).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c3": 50.3e6}
 WEIGHT_DECAY = {"mlp": 0.01, "mlm": 0.01, "cnn": 0.0, "crnn": 0.0}
 # Batch of the CPU sample: the full step where that takes seconds, a slice of the batch where it would take minutes
 # (samples/s does not depend on the batch for these models; the sample string says what was run).
@@ -355,7 +358,7 @@ def main():
                     peak, peak_src = 1590.0 / 2, "fallback bf16 1.59 PFLOP/s / 2"
             achieved = g_fl / (g_ms * 1e-3) / 1e12 if g_ms > 0 else 0.0
             roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
-                        "traffic": None, "kernel": "dense contractions: " + ", ".join(sorted({r[0] for r in gemm})),
+                        "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload), "kernel": "dense contractions: " + ", ".join(sorted({r[0] for r in gemm})),
                         "launches_per_step": g_calls / psteps, "avg_launch_ms": g_ms / max(g_calls, 1),
                         "share_of_step_device_time": g_ms / total_ms if total_ms else None, "peak_source": peak_src,
                         "by_entry_point_ms_per_step": {r[0]: round(r[2] / psteps, 4) for r in sorted(table, key=lambda r: -r[2])[:12]}}

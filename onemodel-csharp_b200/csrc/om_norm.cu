@@ -50,7 +50,7 @@ layernorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamm
 // CTA = 8 warps owns kLnRowsPerCta consecutive rows; warp w takes rows w, w+8, ... of the chunk. Each lane keeps the
 // dgamma/dbeta contributions of its columns (lane, lane+32, ...) in double registers, the 8 warps are combined in warp
 // order through shared memory, and the chunk's column partials go to global memory for the fixed-order second stage.
-constexpr int kLnRowsPerCta = 64;
+constexpr int kLnRowsPerCta = 16;   // two rows per warp: 512 CTAs for 8192 rows keep enough loads in flight
 
 template <int NC>
 __global__ void __launch_bounds__(256)
@@ -142,10 +142,15 @@ column_partials_finish_kernel(const double* __restrict__ pa, const double* __res
   const int j = blockIdx.x * 32 + tx;
   double ta = 0.0, tb = 0.0;
   if (j < cols) {
-    if (pa && oa)
+    // Eight loads are issued before the first add: the adds stay in increasing chunk order.
+    if (pa && oa) {
+#pragma unroll 8
       for (int c = ty; c < chunks; c += 16) ta += pa[(int64_t)c * cols + j];
-    if (pb && ob)
+    }
+    if (pb && ob) {
+#pragma unroll 8
       for (int c = ty; c < chunks; c += 16) tb += pb[(int64_t)c * cols + j];
+    }
   }
   sa[ty][tx] = ta;
   sb[ty][tx] = tb;
