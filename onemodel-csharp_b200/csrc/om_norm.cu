@@ -47,87 +47,128 @@ layernorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamm
 }
 
 // ---- layer norm backward -------------------------------------------------------------------------------------------
-// CTA = 8 warps owns kLnRowsPerCta consecutive rows; warp w takes rows w, w+8, ... of the chunk. Each lane keeps the
-// dgamma/dbeta contributions of its columns (lane, lane+32, ...) in double registers, the 8 warps are combined in warp
-// order through shared memory, and the chunk's column partials go to global memory for the fixed-order second stage.
+// dx: a warp per row, the row in registers (NC columns per lane), the two row sums in double
+// (LayerNormBackward, BackwardNn.cs:170-242 of the reference). CTA = 8 warps owns kLnRowsPerCta consecutive rows.
 constexpr int kLnRowsPerCta = 16;   // two rows per warp: 512 CTAs for 8192 rows keep enough loads in flight
 
 template <int NC>
 __global__ void __launch_bounds__(256)
 layernorm_bwd_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
                      const float* __restrict__ mean, const float* __restrict__ inv, int32_t rows, int32_t cols,
-                     float* __restrict__ dx, double* __restrict__ part_gamma, double* __restrict__ part_beta) {
-  extern __shared__ double sm[];  // [8][cols] for gamma then [8][cols] for beta
+                     float* __restrict__ dx) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int r0 = blockIdx.x * kLnRowsPerCta;
   const int r1 = min(rows, r0 + kLnRowsPerCta);
-  double ag[NC], ab[NC];
   float gam[NC];
 #pragma unroll
   for (int i = 0; i < NC; i++) {
-    ag[i] = 0.0;
-    ab[i] = 0.0;
     int j = lane + 32 * i;
     gam[i] = j < cols ? gamma[j] : 0.f;
   }
-  const bool params = part_gamma != nullptr || part_beta != nullptr;
   for (int r = r0 + w; r < r1; r += 8) {
     const float* xr = x + (int64_t)r * cols;
     const float* gr = g + (int64_t)r * cols;
-    float m = mean[r], s = inv[r];
-    float xh[NC], gv[NC];
-    double sum1 = 0.0, sum2 = 0.0;
+    const float m = mean[r], s = inv[r];
+    float xh[NC], dh[NC];
 #pragma unroll
     for (int i = 0; i < NC; i++) {
       int j = lane + 32 * i;
-      if (j < cols) {
-        gv[i] = gr[j];
-        xh[i] = (xr[j] - m) * s;
-        float dxhat = gv[i] * gam[i];
-        sum1 += (double)dxhat;
-        sum2 += (double)(dxhat * xh[i]);
-        if (params) {
-          ag[i] += (double)(gv[i] * xh[i]);
-          ab[i] += (double)gv[i];
-        }
-      } else {
-        gv[i] = 0.f;
-        xh[i] = 0.f;
+      const bool in = j < cols;
+      const float gv = in ? gr[j] : 0.f;
+      const float xv = in ? xr[j] : m;
+      xh[i] = (xv - m) * s;
+      dh[i] = gv * gam[i];
+    }
+    double sum1 = 0.0, sum2 = 0.0;
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+      if (lane + 32 * i < cols) {
+        sum1 += (double)dh[i];
+        sum2 += (double)(dh[i] * xh[i]);
       }
     }
-    if (dx) {
-      sum1 = wsum_d(sum1);
-      sum2 = wsum_d(sum2);
-      float m1 = (float)(sum1 / cols), m2 = (float)(sum2 / cols);
-      float* dr = dx + (int64_t)r * cols;
+    sum1 = wsum_d(sum1);
+    sum2 = wsum_d(sum2);
+    const float m1 = (float)(sum1 / cols), m2 = (float)(sum2 / cols);
+    float* dr = dx + (int64_t)r * cols;
 #pragma unroll
-      for (int i = 0; i < NC; i++) {
-        int j = lane + 32 * i;
-        if (j < cols) dr[j] = s * (((gv[i] * gam[i]) - m1) - (xh[i] * m2));
-      }
+    for (int i = 0; i < NC; i++) {
+      int j = lane + 32 * i;
+      if (j < cols) dr[j] = s * ((dh[i] - m1) - (xh[i] * m2));
     }
   }
-  if (!params) return;
-  double* smg = sm;
-  double* smb = sm + 8 * cols;
-#pragma unroll
-  for (int i = 0; i < NC; i++) {
-    int j = lane + 32 * i;
-    if (j < cols) {
-      smg[w * cols + j] = ag[i];
-      smb[w * cols + j] = ab[i];
+}
+
+// Column partials of the layer-norm parameter gradients: dgamma[j] = sum_r g[r,j] * xhat[r,j], dbeta[j] = sum_r g[r,j].
+// CTA (bx, by) owns 32 columns and one chunk of 512 rows: 8 column groups x 32 row lanes, a thread holds four adjacent
+// columns (16-byte loads) and 16 rows, all loads of a row pair in flight together; lanes are combined in lane order.
+constexpr int kLnParamRows = 512;
+__global__ void __launch_bounds__(256)
+layernorm_param_partials_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ mean,
+                                const float* __restrict__ inv, int32_t rows, int32_t cols, double* __restrict__ part_gamma,
+                                double* __restrict__ part_beta) {
+  __shared__ double sg[32][33], sb[32][33];
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const int col = blockIdx.x * 32 + tx * 4;
+  const int r0 = blockIdx.y * kLnParamRows, r1 = min(rows, r0 + kLnParamRows);
+  double ag[4] = {0.0, 0.0, 0.0, 0.0}, ab[4] = {0.0, 0.0, 0.0, 0.0};
+  const bool vec = (cols & 3) == 0 && col + 3 < cols;
+  for (int r = r0 + ty; r < r1; r += 64) {
+    const int r2 = r + 32;
+    float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), xa = ga, gb = ga, xb = ga;
+    float ma = 0.f, sa = 0.f, mb = 0.f, sbv = 0.f;
+    if (vec) {
+      ga = __ldg(reinterpret_cast<const float4*>(g + (int64_t)r * cols + col));
+      xa = __ldg(reinterpret_cast<const float4*>(x + (int64_t)r * cols + col));
+      ma = mean[r]; sa = inv[r];
+      if (r2 < r1) {
+        gb = __ldg(reinterpret_cast<const float4*>(g + (int64_t)r2 * cols + col));
+        xb = __ldg(reinterpret_cast<const float4*>(x + (int64_t)r2 * cols + col));
+        mb = mean[r2]; sbv = inv[r2];
+      }
+    } else {
+      float* gp[2] = {&ga.x, &gb.x};
+      float* xp[2] = {&xa.x, &xb.x};
+      for (int q = 0; q < 2; q++) {
+        const int rr = q ? r2 : r;
+        if (rr >= r1) continue;
+        for (int c = 0; c < 4; c++)
+          if (col + c < cols) {
+            gp[q][c] = g[(int64_t)rr * cols + col + c];
+            xp[q][c] = x[(int64_t)rr * cols + col + c];
+          }
+        if (q) { mb = mean[rr]; sbv = inv[rr]; } else { ma = mean[rr]; sa = inv[rr]; }
+      }
     }
+    ag[0] += (double)(ga.x * ((xa.x - ma) * sa)); ab[0] += (double)ga.x;
+    ag[1] += (double)(ga.y * ((xa.y - ma) * sa)); ab[1] += (double)ga.y;
+    ag[2] += (double)(ga.z * ((xa.z - ma) * sa)); ab[2] += (double)ga.z;
+    ag[3] += (double)(ga.w * ((xa.w - ma) * sa)); ab[3] += (double)ga.w;
+    if (r2 < r1) {
+      ag[0] += (double)(gb.x * ((xb.x - mb) * sbv)); ab[0] += (double)gb.x;
+      ag[1] += (double)(gb.y * ((xb.y - mb) * sbv)); ab[1] += (double)gb.y;
+      ag[2] += (double)(gb.z * ((xb.z - mb) * sbv)); ab[2] += (double)gb.z;
+      ag[3] += (double)(gb.w * ((xb.w - mb) * sbv)); ab[3] += (double)gb.w;
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    sg[ty][tx * 4 + c] = ag[c];
+    sb[ty][tx * 4 + c] = ab[c];
   }
   __syncthreads();
-  for (int j = threadIdx.x; j < cols; j += 256) {
-    double tg = 0.0, tb = 0.0;
+  if (threadIdx.x < 32) {
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    if (c < cols) {
+      double tg = 0.0, tb = 0.0;
 #pragma unroll
-    for (int k = 0; k < 8; k++) {
-      tg += smg[k * cols + j];
-      tb += smb[k * cols + j];
+      for (int l = 0; l < 32; l++) {
+        tg += sg[l][threadIdx.x];
+        tb += sb[l][threadIdx.x];
+      }
+      if (part_gamma) part_gamma[(int64_t)blockIdx.y * cols + c] = tg;
+      if (part_beta) part_beta[(int64_t)blockIdx.y * cols + c] = tb;
     }
-    if (part_gamma) part_gamma[(int64_t)blockIdx.x * cols + j] = tg;
-    if (part_beta) part_beta[(int64_t)blockIdx.x * cols + j] = tb;
   }
 }
 
@@ -360,27 +401,28 @@ int32_t om_layernorm_bwd(om_ctx* ctx, const float* g, const float* x, const floa
   if (cols == 0) return OM_OK;
   if (cols > 1024) return fail(ctx, OM_ERR_UNSUPPORTED, "om_layernorm_bwd: rows wider than 1024 (%d) are not implemented", cols);
   ProfileScope prof(ctx, "om_layernorm_bwd", 0, 12.0 * rows * (double)cols);
-  int chunks = (int)ceil_div(rows > 0 ? rows : 1, kLnRowsPerCta);
-  double *pg = nullptr, *pb = nullptr;
-  if (dgamma) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&pg));
-  if (dbeta) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&pb));
-  size_t smem = (dgamma || dbeta) ? sizeof(double) * 16 * (size_t)cols : 0;
+  // dx: a warp per row, the row in registers. The parameter gradients are column sums and run as their own pass over
+  // (g, x) with the column-sum blocking: for wide rows that beats carrying per-lane column partials through the row loop.
+  const int row_ctas = (int)ceil_div(rows > 0 ? rows : 1, kLnRowsPerCta);
   int nc = (int)ceil_div(cols, 32);
-#define OM_LN_BWD(NC)                                                                                                  \
-  do {                                                                                                                 \
-    if (smem > 48 * 1024)                                                                                              \
-      OM_CUDA(ctx, cudaFuncSetAttribute(layernorm_bwd_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    layernorm_bwd_kernel<NC><<<chunks, 256, smem, ctx->stream>>>(g, x, gamma, mean, inv, rows, cols, dx, pg, pb);       \
-  } while (0)
-  if (nc <= 4) OM_LN_BWD(4);
-  else if (nc <= 8) OM_LN_BWD(8);
-  else if (nc <= 12) OM_LN_BWD(12);
-  else if (nc <= 16) OM_LN_BWD(16);
-  else if (nc <= 24) OM_LN_BWD(24);
-  else OM_LN_BWD(32);
+  if (dx && rows > 0) {
+#define OM_LN_BWD(NC) layernorm_bwd_kernel<NC><<<row_ctas, 256, 0, ctx->stream>>>(g, x, gamma, mean, inv, rows, cols, dx)
+    if (nc <= 4) OM_LN_BWD(4);
+    else if (nc <= 8) OM_LN_BWD(8);
+    else if (nc <= 12) OM_LN_BWD(12);
+    else if (nc <= 16) OM_LN_BWD(16);
+    else if (nc <= 24) OM_LN_BWD(24);
+    else OM_LN_BWD(32);
 #undef OM_LN_BWD
-  if (dgamma || dbeta)
+  }
+  double *pg = nullptr, *pb = nullptr;
+  if (dgamma || dbeta) {
+    const int chunks = (int)ceil_div(rows > 0 ? rows : 1, kLnParamRows);
+    if (dgamma) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&pg));
+    if (dbeta) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&pb));
+    layernorm_param_partials_kernel<<<dim3((unsigned)ceil_div(cols, 32), (unsigned)chunks), 256, 0, ctx->stream>>>(g, x, mean, inv, rows, cols, pg, pb);
     column_partials_finish_kernel<<<(unsigned)ceil_div(cols, 32), 512, 0, ctx->stream>>>(pg, pb, chunks, cols, dgamma, dbeta, accumulate_params);
+  }
   if (pg) pool_free(ctx, pg);
   if (pb) pool_free(ctx, pb);
   OM_LAUNCH_CHECK(ctx, "om_layernorm_bwd");
