@@ -52,10 +52,12 @@ typedef enum om_status {
  * src/OneModel/Tensors/Autograd/TensorCompute.cs:22-78). OM_BF16_OPERANDS: operands of matrix products are
  * rounded to bfloat16 (round to nearest even) and multiplied on the tensor pipe with fp32 accumulation.
  * OM_CHECKED: index operands are range-checked on the device and buffers carry canary words
- * (the reference's Checked build, docs/tensors.md:108-110). */
+ * (the reference's Checked build, docs/tensors.md:108-110). OM_PAIR_TILES (with OM_TF32): wide plain products use the
+ * CTA-pair kernel (tcgen05 cta_group::2, 256-row tiles), which halves the operand bytes each SM pulls from L2. */
 #define OM_TF32 1u
 #define OM_BF16_OPERANDS 2u
 #define OM_CHECKED 4u
+#define OM_PAIR_TILES 8u
 
 typedef enum om_dtype { OM_F32 = 0, OM_I32 = 1, OM_I64 = 2 } om_dtype;
 
@@ -398,6 +400,22 @@ int32_t om_lstm_layer_bwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, in
                           const float* c0, const float* gates, const float* c, const float* tanh_c,
                           float* dx, float* dw_ih, float* dw_hh, float* db_ih, float* db_hh, float* dh0,
                           float* dc0);
+
+/* Both directions of one bidirectional LSTM layer over the same input, zero initial states: the forward direction runs on
+ * the context's stream and the reverse direction concurrently on an auxiliary stream (fork / join by events; inside
+ * om_graph_begin/end both become branches of the graph), since one direction's per-step kernels fill only a few SMs.
+ * Index 0 of every array = forward direction, 1 = reverse. b_ih / b_hh may be NULL arrays. Per direction the arithmetic
+ * is that of om_lstm_layer_fwd / om_lstm_layer_bwd (Recurrent.Forward, src/OneModel.Training/Recurrent.cs:28-67). */
+int32_t om_lstm_bilayer_fwd(om_ctx* ctx, int32_t t, int32_t b, int32_t i, int32_t h, const float* x,
+                            const float* const* w_ih, const float* const* w_hh, const float* const* b_ih,
+                            const float* const* b_hh, float* const* y, float* const* gates, float* const* c,
+                            float* const* tanh_c);
+/* dx[0] and dx[1] are the two directions' input gradients (the caller adds them); any output array may be NULL. */
+int32_t om_lstm_bilayer_bwd(om_ctx* ctx, int32_t t, int32_t b, int32_t i, int32_t h, const float* const* gy,
+                            const float* x, const float* const* y, const float* const* w_ih,
+                            const float* const* w_hh, const float* const* gates, const float* const* c,
+                            const float* const* tanh_c, float* const* dx, float* const* dw_ih,
+                            float* const* dw_hh, float* const* db_ih, float* const* db_hh);
 
 /* One direction of one GRU layer over a whole sequence, PyTorch's gate formulation. x [T,B,I], w_ih [3H,I],
  * w_hh [3H,H], b_ih / b_hh [3H] or NULL, h0 [B,H] or NULL (zeros). Outputs: y [T,B,H] and the saved slots of the

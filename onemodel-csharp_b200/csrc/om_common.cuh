@@ -6,6 +6,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <functional>
 #include <map>
 #include <string>
 #include <unordered_map>
@@ -45,6 +46,12 @@ struct om_ctx {
   int32_t* status_dev = nullptr;
   int sm_count = 148;
   om::Pool pool;
+  // A second stream for work that forks off the main one inside an entry point (the two directions of a bidirectional
+  // recurrent layer). While it is current, scratch comes from its own pool so that blocks never change streams.
+  cudaStream_t aux_stream = nullptr;
+  cudaEvent_t fork_event = nullptr, join_event = nullptr;
+  om::Pool pool_aux;
+  bool aux_active = false;
   bool profiling = false;
   bool capturing = false;
   int32_t last_graph_kernel_nodes = 0;
@@ -61,6 +68,10 @@ int32_t fail(om_ctx* ctx, int32_t code, const char* fmt, ...);
 int32_t check_cuda(om_ctx* ctx, cudaError_t e, const char* what);
 int32_t pool_alloc(om_ctx* ctx, size_t bytes, bool zero, void** out);
 int32_t pool_free(om_ctx* ctx, void* p);
+// Runs `second` on the context's auxiliary stream concurrently with `first` on the main stream (fork / join by events;
+// inside a stream capture both become branches of the captured graph). Both are synchronous host functions that enqueue
+// work on ctx->stream. Returns the first non-zero status.
+int32_t run_forked(om_ctx* ctx, const std::function<int32_t()>& first, const std::function<int32_t()>& second);
 
 struct ProfileScope {
   om_ctx* ctx;

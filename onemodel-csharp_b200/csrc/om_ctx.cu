@@ -40,7 +40,7 @@ size_t Pool::size_class(size_t bytes) {
 int32_t pool_alloc(om_ctx* ctx, size_t bytes, bool zero, void** out) {
   *out = nullptr;
   size_t cls = Pool::size_class(bytes == 0 ? 1 : bytes);
-  Pool& p = ctx->pool;
+  Pool& p = ctx->aux_active ? ctx->pool_aux : ctx->pool;
   void* ptr = nullptr;
   auto it = p.cache.find(cls);
   if (it != p.cache.end() && !it->second.empty()) {
@@ -78,15 +78,44 @@ int32_t pool_alloc(om_ctx* ctx, size_t bytes, bool zero, void** out) {
 
 int32_t pool_free(om_ctx* ctx, void* ptr) {
   if (!ptr) return OM_OK;
-  Pool& p = ctx->pool;
-  auto it = p.live.find(ptr);
-  if (it == p.live.end()) return fail(ctx, OM_ERR_ARG, "om_free: %p was not allocated by this context", ptr);
+  // A block goes back to the pool it came from (main or auxiliary stream), whichever stream is current now.
+  Pool* pp = &ctx->pool;
+  auto it = pp->live.find(ptr);
+  if (it == pp->live.end()) {
+    pp = &ctx->pool_aux;
+    it = pp->live.find(ptr);
+    if (it == pp->live.end()) return fail(ctx, OM_ERR_ARG, "om_free: %p was not allocated by this context", ptr);
+  }
+  Pool& p = *pp;
   size_t cls = it->second;
   p.live.erase(it);
   p.bytes_in_use -= cls;
   p.cache[cls].push_back(ptr);
   p.bytes_cached += cls;
   return OM_OK;
+}
+
+int32_t run_forked(om_ctx* ctx, const std::function<int32_t()>& first, const std::function<int32_t()>& second) {
+  if (!ctx->aux_stream) {
+    cudaError_t e = cudaStreamCreateWithFlags(&ctx->aux_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->fork_event, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->join_event, cudaEventDisableTiming);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "auxiliary stream");
+  }
+  cudaError_t e = cudaEventRecord(ctx->fork_event, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->aux_stream, ctx->fork_event, 0);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "fork to the auxiliary stream");
+  const int32_t s0 = first();
+  cudaStream_t main_stream = ctx->stream;
+  ctx->stream = ctx->aux_stream;
+  ctx->aux_active = true;
+  const int32_t s1 = second();
+  ctx->stream = main_stream;
+  ctx->aux_active = false;
+  e = cudaEventRecord(ctx->join_event, ctx->aux_stream);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->stream, ctx->join_event, 0);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "join from the auxiliary stream");
+  return s0 != OM_OK ? s0 : s1;
 }
 
 static cudaEvent_t get_event(om_ctx* ctx) {
@@ -185,6 +214,15 @@ int32_t om_ctx_destroy(om_ctx* ctx) {
   for (auto& kv : ctx->pool.cache)
     for (void* p : kv.second) cudaFree(p);
   for (auto& kv : ctx->pool.live) cudaFree(kv.first);
+  for (auto& kv : ctx->pool_aux.cache)
+    for (void* p : kv.second) cudaFree(p);
+  for (auto& kv : ctx->pool_aux.live) cudaFree(kv.first);
+  if (ctx->aux_stream) {
+    cudaStreamSynchronize(ctx->aux_stream);
+    cudaStreamDestroy(ctx->aux_stream);
+    cudaEventDestroy(ctx->fork_event);
+    cudaEventDestroy(ctx->join_event);
+  }
   for (auto& kv : ctx->profile)
     for (auto& pr : kv.second.pending) {
       cudaEventDestroy(pr.first);

@@ -308,9 +308,18 @@ int32_t gemm_tc_batched(om_ctx* ctx, int ta, int tb, int m, int n, int k, const 
   return gemm_tc_heads(ctx, ta, tb, m, n, k, A, lda, sA, 0, B, ldb, sB, 0, C, ldc, sC, 0, batch, 1, acc, bias);
 }
 
+bool gemm_pair_supported(om_ctx* ctx, int m, int n, int k);
+int32_t gemm_pair(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb, float* C, int ldc,
+                  int acc, const float* bias);
+
+void splitk_reduce_launch(om_ctx* ctx, const float* part, int splits, int64_t mn, int n, int64_t ldc, const float* bias, float* out, int accumulate) {
+  splitk_reduce_kernel<<<grid_for(ctx, mn, 256), 256, 0, ctx->stream>>>(part, splits, mn, n, ldc, bias, out, accumulate);
+}
+
 int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, long long iA,
                       const float* B, int ldb, long long sB, long long iB, float* C, int ldc, long long sC, long long iC, int batch,
                       int inner, int acc, const float* bias) {
+  if (batch == 1 && gemm_pair_supported(ctx, m, n, k)) return gemm_pair(ctx, ta, tb, m, n, k, A, lda, B, ldb, C, ldc, acc, bias);
   // op(A) is [m, k]. ta == 0: stored [m, k] (K-major tile, map inner = k). ta != 0: stored [k, m] (MN-major, inner = m).
   // op(B) is [k, n]. tb != 0: stored [n, k] (K-major, inner = k). tb == 0: stored [k, n] (MN-major, inner = n).
   const bool a_mn = ta != 0, b_mn = tb == 0;

@@ -328,14 +328,10 @@ using namespace om;
 
 extern "C" {
 
-int32_t om_lstm_layer_fwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* x,
-                          const float* w_ih, const float* w_hh, const float* b_ih, const float* b_hh, const float* h0,
-                          const float* c0, float* y, float* gates, float* c, float* tanh_c) {
-  OM_CHECK_CTX(ctx);
-  if (t < 0 || b < 0 || i < 1 || h < 1) return fail(ctx, OM_ERR_SHAPE, "LstmLayer: T %d B %d I %d H %d", t, b, i, h);
-  if (t == 0 || b == 0) return OM_OK;
+static int32_t lstm_fwd_body(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* x, const float* w_ih,
+                             const float* w_hh, const float* b_ih, const float* b_hh, const float* h0, const float* c0, float* y,
+                             float* gates, float* c, float* tanh_c) {
   const int h4 = 4 * h, bh = b * h;
-  ProfileScope prof(ctx, "om_lstm_layer_fwd", 2.0 * t * b * (double)h4 * (i + h), 4.0 * t * b * (double)(i + 7 * h));
   OM_TRY(gemm_dispatch(ctx, 0, 1, t * b, h4, i, x, i, w_ih, i, gates, h4, 0, nullptr));
   float *bias = nullptr, *rec = nullptr;
   const bool has_bias = b_ih || b_hh;
@@ -366,16 +362,33 @@ int32_t om_lstm_layer_fwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, in
   return OM_OK;
 }
 
-int32_t om_lstm_layer_bwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* gy,
-                          const float* ghn, const float* gcn, const float* x, const float* y, const float* w_ih,
-                          const float* w_hh, const float* h0, const float* c0, const float* gates, const float* c,
-                          const float* tanh_c, float* dx, float* dw_ih, float* dw_hh, float* db_ih, float* db_hh, float* dh0,
-                          float* dc0) {
+int32_t om_lstm_layer_fwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* x,
+                          const float* w_ih, const float* w_hh, const float* b_ih, const float* b_hh, const float* h0,
+                          const float* c0, float* y, float* gates, float* c, float* tanh_c) {
   OM_CHECK_CTX(ctx);
-  if (t < 0 || b < 0 || i < 1 || h < 1) return fail(ctx, OM_ERR_SHAPE, "LstmBackward: T %d B %d I %d H %d", t, b, i, h);
+  if (t < 0 || b < 0 || i < 1 || h < 1) return fail(ctx, OM_ERR_SHAPE, "LstmLayer: T %d B %d I %d H %d", t, b, i, h);
   if (t == 0 || b == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_lstm_layer_fwd", 2.0 * t * b * 4.0 * h * (i + h), 4.0 * t * b * (double)(i + 7 * h));
+  return lstm_fwd_body(ctx, reverse, t, b, i, h, x, w_ih, w_hh, b_ih, b_hh, h0, c0, y, gates, c, tanh_c);
+}
+
+int32_t om_lstm_bilayer_fwd(om_ctx* ctx, int32_t t, int32_t b, int32_t i, int32_t h, const float* x, const float* const* w_ih,
+                            const float* const* w_hh, const float* const* b_ih, const float* const* b_hh, float* const* y,
+                            float* const* gates, float* const* c, float* const* tanh_c) {
+  OM_CHECK_CTX(ctx);
+  if (t < 0 || b < 0 || i < 1 || h < 1) return fail(ctx, OM_ERR_SHAPE, "LstmLayer: T %d B %d I %d H %d", t, b, i, h);
+  if (t == 0 || b == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_lstm_layer_fwd", 2.0 * 2 * t * b * 4.0 * h * (i + h), 2.0 * 4.0 * t * b * (double)(i + 7 * h));
+  return run_forked(
+      ctx, [&] { return lstm_fwd_body(ctx, 0, t, b, i, h, x, w_ih[0], w_hh[0], b_ih ? b_ih[0] : nullptr, b_hh ? b_hh[0] : nullptr, nullptr, nullptr, y[0], gates[0], c[0], tanh_c[0]); },
+      [&] { return lstm_fwd_body(ctx, 1, t, b, i, h, x, w_ih[1], w_hh[1], b_ih ? b_ih[1] : nullptr, b_hh ? b_hh[1] : nullptr, nullptr, nullptr, y[1], gates[1], c[1], tanh_c[1]); });
+}
+
+static int32_t lstm_bwd_body(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* gy, const float* ghn,
+                             const float* gcn, const float* x, const float* y, const float* w_ih, const float* w_hh, const float* h0,
+                             const float* c0, const float* gates, const float* c, const float* tanh_c, float* dx, float* dw_ih,
+                             float* dw_hh, float* db_ih, float* db_hh, float* dh0, float* dc0) {
   const int h4 = 4 * h, bh = b * h, rows = t * b;
-  ProfileScope prof(ctx, "om_lstm_layer_bwd", 4.0 * t * b * (double)h4 * (i + h), 4.0 * t * b * (double)(2 * i + 12 * h));
   float *dG = nullptr, *dh = nullptr, *dc = nullptr, *hprev = nullptr;
   int32_t st = pool_alloc(ctx, sizeof(float) * (size_t)rows * h4, false, (void**)&dG);
   if (st == OM_OK) st = pool_alloc(ctx, sizeof(float) * bh, true, (void**)&dh);
@@ -416,6 +429,35 @@ int32_t om_lstm_layer_bwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, in
   OM_TRY(st);
   OM_LAUNCH_CHECK(ctx, "om_lstm_layer_bwd");
   return OM_OK;
+}
+
+int32_t om_lstm_layer_bwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* gy,
+                          const float* ghn, const float* gcn, const float* x, const float* y, const float* w_ih,
+                          const float* w_hh, const float* h0, const float* c0, const float* gates, const float* c,
+                          const float* tanh_c, float* dx, float* dw_ih, float* dw_hh, float* db_ih, float* db_hh, float* dh0,
+                          float* dc0) {
+  OM_CHECK_CTX(ctx);
+  if (t < 0 || b < 0 || i < 1 || h < 1) return fail(ctx, OM_ERR_SHAPE, "LstmBackward: T %d B %d I %d H %d", t, b, i, h);
+  if (t == 0 || b == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_lstm_layer_bwd", 4.0 * t * b * 4.0 * h * (i + h), 4.0 * t * b * (double)(2 * i + 12 * h));
+  return lstm_bwd_body(ctx, reverse, t, b, i, h, gy, ghn, gcn, x, y, w_ih, w_hh, h0, c0, gates, c, tanh_c, dx, dw_ih, dw_hh, db_ih, db_hh,
+                       dh0, dc0);
+}
+
+int32_t om_lstm_bilayer_bwd(om_ctx* ctx, int32_t t, int32_t b, int32_t i, int32_t h, const float* const* gy, const float* x,
+                            const float* const* y, const float* const* w_ih, const float* const* w_hh, const float* const* gates,
+                            const float* const* c, const float* const* tanh_c, float* const* dx, float* const* dw_ih,
+                            float* const* dw_hh, float* const* db_ih, float* const* db_hh) {
+  OM_CHECK_CTX(ctx);
+  if (t < 0 || b < 0 || i < 1 || h < 1) return fail(ctx, OM_ERR_SHAPE, "LstmBackward: T %d B %d I %d H %d", t, b, i, h);
+  if (t == 0 || b == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_lstm_layer_bwd", 2.0 * 4.0 * t * b * 4.0 * h * (i + h), 2.0 * 4.0 * t * b * (double)(2 * i + 12 * h));
+  auto dir = [&](int d) {
+    return lstm_bwd_body(ctx, d, t, b, i, h, gy[d], nullptr, nullptr, x, y[d], w_ih[d], w_hh[d], nullptr, nullptr, gates[d], c[d], tanh_c[d],
+                         dx ? dx[d] : nullptr, dw_ih ? dw_ih[d] : nullptr, dw_hh ? dw_hh[d] : nullptr, db_ih ? db_ih[d] : nullptr,
+                         db_hh ? db_hh[d] : nullptr, nullptr, nullptr);
+  };
+  return run_forked(ctx, [&] { return dir(0); }, [&] { return dir(1); });
 }
 
 static int32_t ctc_check(om_ctx* ctx, const char* who, int t, int b, int c, int blank, int reduction) {

@@ -48,7 +48,44 @@ static void ConvBackward(BackwardRecord& r, const Tensor& g) {
   }
 }
 
+// The record of Ops::LstmBidirectional: inputs x, then (wIh, wHh, bIh, bHh) per direction; slots 0 x, then per direction
+// wIh, wHh, gates, c, tanh c, y.
+static void LstmBidirectionalBackward(BackwardRecord& r, const Tensor& gy) {
+  const Tensor& x = r.Saved(0);
+  int steps = (int)r.Ints[1], batch = (int)r.Ints[2], inSize = (int)r.Ints[3], h = (int)r.Ints[4];
+  Tensor g[2], dx[2];
+  for (int d = 0; d < 2; d++) {
+    g[d] = gy.Slice(2, d * h, (d + 1) * h).Contiguous();
+    if (r.NeedsInputGrad(0)) dx[d] = Tensor::Create(DType::F32, x.GetShape());
+  }
+  std::vector<GradSlot> slots;
+  slots.reserve(8);
+  for (int k = 0; k < 8; k++) slots.emplace_back(r, 1 + k);
+  for (int k = 0; k < 8; k++) {
+    GradSlot& s = slots[k];
+    if (s.needed && s.leaf && s.accumulate) {      // the kernels overwrite: go through a temporary and add
+      s.leaf = false;
+      s.tmp = Tensor::Create(DType::F32, r.InputShapes[1 + k]);
+      s.ptr = s.tmp.Data();
+    }
+  }
+  const float *gp[2] = {g[0].Data(), g[1].Data()}, *yp[2] = {r.Saved(6).Data(), r.Saved(12).Data()};
+  const float *wih[2] = {r.Saved(1).Data(), r.Saved(7).Data()}, *whh[2] = {r.Saved(2).Data(), r.Saved(8).Data()};
+  const float *gt[2] = {r.Saved(3).Data(), r.Saved(9).Data()}, *cs[2] = {r.Saved(4).Data(), r.Saved(10).Data()};
+  const float* tc[2] = {r.Saved(5).Data(), r.Saved(11).Data()};
+  float* dxp[2] = {dx[0].IsEmpty() ? nullptr : dx[0].Data(), dx[1].IsEmpty() ? nullptr : dx[1].Data()};
+  float *dwi[2] = {slots[0].ptr, slots[4].ptr}, *dwh[2] = {slots[1].ptr, slots[5].ptr}, *dbi[2] = {slots[2].ptr, slots[6].ptr},
+        *dbh[2] = {slots[3].ptr, slots[7].ptr};
+  Check(om_lstm_bilayer_bwd(C(), steps, batch, inSize, h, gp, x.Data(), yp, wih, whh, gt, cs, tc, dxp, dwi, dwh, dbi, dbh));
+  if (!dx[0].IsEmpty()) {
+    Check(om_add_into(C(), dx[0].Data(), dx[1].Data(), dx[0].Length()));   // forward direction's share first, then the reverse one
+    Engine::Emit(r, 0, dx[0], true);
+  }
+  for (int k = 0; k < 8; k++) slots[k].Done(r, 1 + k);
+}
+
 static void LstmBackward(BackwardRecord& r, const Tensor& gy) {
+  if (r.Ints[0] == 2) return LstmBidirectionalBackward(r, gy);
   const Tensor &x = r.Saved(0), &wIh = r.Saved(1), &wHh = r.Saved(2), &gates = r.Saved(3), &cseq = r.Saved(4), &tanhC = r.Saved(5), &y = r.Saved(6);
   bool reverse = r.Ints[0] != 0;
   int steps = (int)r.Ints[1], batch = (int)r.Ints[2], inSize = (int)r.Ints[3], h = (int)r.Ints[4];

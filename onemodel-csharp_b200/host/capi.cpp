@@ -203,7 +203,11 @@ OMH_API int32_t omh_call(const char* op, int32_t n_in, omh_tensor* const* in, in
     else if (name == "pow") r = Ops::Pow(T(0), (float)F(0, 1));
     else if (name == "where") r = Ops::Where(T(0), T(1), T(2));
     else if (name == "gather") r = Ops::Gather(T(0), T(1), (int)I(0));
-    else if (name == "gru_layer") r = Ops::GruLayer(T(0), T(1), T(2), T(3), T(4), T(5), I(0) != 0);
+    else if (name == "lstm_bidirectional") {
+      std::vector<Tensor> ws;
+      for (int k = 1; k < 9; k++) ws.push_back(T(k));
+      r = Ops::LstmBidirectional(T(0), ws);
+    } else if (name == "gru_layer") r = Ops::GruLayer(T(0), T(1), T(2), T(3), T(4), T(5), I(0) != 0);
     else if (name == "ctc_loss") r = Ops::CtcLoss(T(0), T(1), T(2), T(3), (int)I(0), (int)I(1, 1), I(2) != 0);
     else if (name == "reshape") r = T(0).Reshape(ShapeFromInts(0));
     else if (name == "permute") {

@@ -276,6 +276,9 @@ struct Ops {
   // One LSTM layer direction: returns y [T,B,H]; hn/cn receive the final states when not null.
   static Tensor LstmLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, const Tensor& bIh, const Tensor& bHh,
                           bool reverse, Tensor* hn = nullptr, Tensor* cn = nullptr);
+  // Both directions of a bidirectional LSTM layer, concatenated on the feature axis: [T,B,2H]. w[0..3] = forward
+  // direction (wIh, wHh, bIh, bHh), w[4..7] = reverse direction; biases may be empty (both or none per direction).
+  static Tensor LstmBidirectional(const Tensor& x, const std::vector<Tensor>& w);
   // One GRU layer direction (Ops.Recurrent.cs:148-260): returns y [T,B,H]; h0 [B,H] may be empty (zeros).
   static Tensor GruLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, const Tensor& bIh, const Tensor& bHh,
                          const Tensor& h0, bool reverse);
@@ -408,6 +411,17 @@ class Optimizer {
   virtual size_t HyperBytes() const = 0;
   virtual void FillHyper(void* host, int64_t step) const = 0;  // scalars for the given 1-based step
   virtual std::vector<Tensor> StateTensors() const = 0;
+  // What a checkpoint stores (Checkpoint.cs, docs/training.md section 6 of the reference): the kind string, the
+  // hyper-parameters in the reference's order, and the state tensors named slot.index in the reference's order. An entry
+  // with a null tensor is the Int32 flag vector `flags` (Sgd's "initialized").
+  struct StateEntry {
+    std::string name;
+    Tensor tensor;
+    std::vector<int32_t>* flags = nullptr;
+  };
+  virtual std::string Kind() const = 0;
+  virtual std::vector<std::pair<std::string, float>> HyperParameters() const = 0;
+  virtual std::vector<StateEntry> NamedState() = 0;
  protected:
   virtual void BeginStep() {}
   virtual void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) = 0;
@@ -422,6 +436,9 @@ class Sgd : public Optimizer {
   size_t HyperBytes() const override { return sizeof(om_sgd_hyper); }
   void FillHyper(void* host, int64_t step) const override;
   std::vector<Tensor> StateTensors() const override { return buffers_; }
+  std::string Kind() const override { return "sgd"; }
+  std::vector<std::pair<std::string, float>> HyperParameters() const override;
+  std::vector<StateEntry> NamedState() override;
   float GradScale = 1.f;
  protected:
   void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) override;
@@ -439,6 +456,9 @@ class Adam : public Optimizer {
   size_t HyperBytes() const override { return sizeof(om_adam_hyper); }
   void FillHyper(void* host, int64_t step) const override;
   std::vector<Tensor> StateTensors() const override;
+  std::string Kind() const override { return decoupled_ ? "adamw" : "adam"; }
+  std::vector<std::pair<std::string, float>> HyperParameters() const override;
+  std::vector<StateEntry> NamedState() override;
   float GradScale = 1.f;
  protected:
   void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) override;

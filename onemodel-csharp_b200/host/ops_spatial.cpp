@@ -134,6 +134,64 @@ Tensor Ops::LstmLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, con
   return br->Attach(y);
 }
 
+Tensor Ops::LstmBidirectional(const Tensor& x, const std::vector<Tensor>& w) {
+  if (w.size() != 8) throw std::invalid_argument("LstmBidirectional needs wIh, wHh, bIh, bHh for both directions.");
+  if (x.Rank() != 3) throw TensorShapeException("LstmLayer needs x [T,B,I], not " + x.GetShape().ToString() + ".");
+  int steps = x.GetShape()[0], batch = x.GetShape()[1], inSize = x.GetShape()[2], h = w[1].GetShape()[1];
+  for (int d = 0; d < 2; d++) {
+    const Tensor &wi = w[4 * d], &wh = w[4 * d + 1], &bi = w[4 * d + 2], &bh = w[4 * d + 3];
+    if (wi.Rank() != 2 || wh.Rank() != 2 || wi.GetShape()[0] != 4 * h || wi.GetShape()[1] != inSize || wh.GetShape()[0] != 4 * h ||
+        wh.GetShape()[1] != h)
+      throw TensorShapeException("LstmLayer needs x [T,B,I], wIh [4H,I], wHh [4H,H], not " + x.GetShape().ToString() + ", " +
+                                 wi.GetShape().ToString() + ", " + wh.GetShape().ToString() + ".");
+    if (bi.IsEmpty() != bh.IsEmpty() || (!bi.IsEmpty() && (bi.Length() != 4 * h || bh.Length() != 4 * h)))
+      throw TensorShapeException("LstmLayer biases must have shape [4H] (both or none).");
+  }
+  Tensor xc = x.Contiguous();
+  Tensor wc[8];
+  for (int k = 0; k < 8; k++) wc[k] = w[k].IsEmpty() ? Tensor() : w[k].Contiguous();
+  Tensor y[2], gates[2], cseq[2], tanhC[2];
+  for (int d = 0; d < 2; d++) {
+    y[d] = Tensor::Create(DType::F32, Shape{steps, batch, h});
+    gates[d] = Tensor::Create(DType::F32, Shape{steps, batch, 4 * h});
+    cseq[d] = Tensor::Create(DType::F32, Shape{steps, batch, h});
+    tanhC[d] = Tensor::Create(DType::F32, Shape{steps, batch, h});
+  }
+  const bool hasBias = !wc[2].IsEmpty() && !wc[6].IsEmpty();
+  const float *wih[2] = {wc[0].Data(), wc[4].Data()}, *whh[2] = {wc[1].Data(), wc[5].Data()};
+  const float *bih[2] = {hasBias ? wc[2].Data() : nullptr, hasBias ? wc[6].Data() : nullptr};
+  const float *bhh[2] = {hasBias ? wc[3].Data() : nullptr, hasBias ? wc[7].Data() : nullptr};
+  float *yp[2] = {y[0].Data(), y[1].Data()}, *gp[2] = {gates[0].Data(), gates[1].Data()}, *cp[2] = {cseq[0].Data(), cseq[1].Data()},
+        *tp[2] = {tanhC[0].Data(), tanhC[1].Data()};
+  if (!hasBias && (!wc[2].IsEmpty() || !wc[6].IsEmpty()))
+    throw TensorShapeException("LstmBidirectional: either both directions have biases or neither.");
+  Check(om_lstm_bilayer_fwd(C(), steps, batch, inSize, h, xc.Data(), wih, whh, hasBias ? bih : nullptr, hasBias ? bhh : nullptr, yp, gp, cp, tp));
+  // [T,B,2H]: the two outputs side by side on the feature axis.
+  Tensor r = NewOut(Shape{steps, batch, 2 * h});
+  for (int d = 0; d < 2; d++) {
+    Tensor dst = r.Slice(2, d * h, (d + 1) * h).Detach();
+    Check(om_strided_copy(C(), 3, y[d].GetShape().d.data(), y[d].Data(), y[d].Strides().data(), dst.Data(), dst.Strides().data()));
+  }
+  std::vector<Tensor> ins = {x};
+  for (int k = 0; k < 8; k++) ins.push_back(w[k]);
+  bool rec = false;
+  if (GradMode::Enabled())
+    for (const Tensor& t : ins) rec = rec || (!t.IsEmpty() && t.RequiresGrad());
+  if (!rec) return r;
+  auto br = BackwardRecord::Create(OpKind::Lstm, 13, ins);
+  br->Save(0, xc.Detach());
+  for (int d = 0; d < 2; d++) {
+    br->Save(1 + 6 * d, wc[4 * d].Detach());
+    br->Save(2 + 6 * d, wc[4 * d + 1].Detach());
+    br->Save(3 + 6 * d, gates[d]);
+    br->Save(4 + 6 * d, cseq[d]);
+    br->Save(5 + 6 * d, tanhC[d]);
+    br->Save(6 + 6 * d, y[d]);
+  }
+  br->Ints = {2, steps, batch, inSize, h};     // Ints[0] == 2 marks the bidirectional record
+  return br->Attach(r);
+}
+
 Tensor Ops::GruLayer(const Tensor& x, const Tensor& wIh, const Tensor& wHh, const Tensor& bIh, const Tensor& bHh, const Tensor& h0,
                      bool reverse) {
   if (x.Rank() != 3 || wIh.Rank() != 2 || wHh.Rank() != 2 || wIh.GetShape()[0] % 3 != 0 || wIh.GetShape()[1] != x.GetShape()[2] ||
@@ -224,12 +282,13 @@ Tensor Recurrent::Forward(const Tensor& x) {
   Tensor h = x;
   int dirs = Bidirectional ? 2 : 1;
   for (int l = 0; l < Layers; l++) {
-    std::vector<Tensor> outs;
-    for (int d = 0; d < dirs; d++) {
-      int k = l * dirs + d;
-      outs.push_back(Ops::LstmLayer(h, WIh[k], WHh[k], BIh[k], BHh[k], d == 1));
+    if (dirs == 2) {
+      // Both directions in one record: they run concurrently on two streams, forward and backward.
+      int k = l * 2;
+      h = Ops::LstmBidirectional(h, {WIh[k], WHh[k], BIh[k], BHh[k], WIh[k + 1], WHh[k + 1], BIh[k + 1], BHh[k + 1]});
+      continue;
     }
-    h = dirs == 1 ? outs[0] : Ops::Concat(outs, 2);
+    h = Ops::LstmLayer(h, WIh[l], WHh[l], BIh[l], BHh[l], false);
   }
   return h;
 }

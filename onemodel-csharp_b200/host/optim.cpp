@@ -54,6 +54,21 @@ Sgd::Sgd(std::vector<Tensor> parameters, float lr, float momentum, float dampeni
   }
 }
 
+// Optimizers.cs:317-318 and 300-311: flags first, then the momentum buffers.
+std::vector<std::pair<std::string, float>> Sgd::HyperParameters() const {
+  return {{"lr", LearningRate}, {"momentum", momentum_}, {"dampening", dampening_}, {"weight_decay", WeightDecay}, {"nesterov", nesterov_ ? 1.f : 0.f}};
+}
+std::vector<Optimizer::StateEntry> Sgd::NamedState() {
+  if (initialized_.size() != params_.size()) initialized_.resize(params_.size(), 0);
+  std::vector<StateEntry> out;
+  StateEntry flags;
+  flags.name = "initialized";
+  flags.flags = &initialized_;
+  out.push_back(flags);
+  for (size_t i = 0; i < buffers_.size(); i++) out.push_back({"momentum_buffer." + std::to_string(i), buffers_[i], nullptr});
+  return out;
+}
+
 void Sgd::FillHyper(void* host, int64_t) const {
   om_sgd_hyper* h = (om_sgd_hyper*)host;
   h->lr = LearningRate;
@@ -99,6 +114,18 @@ std::vector<Tensor> Adam::StateTensors() const {
   s.insert(s.end(), v_.begin(), v_.end());
   s.insert(s.end(), vmax_.begin(), vmax_.end());
   return s;
+}
+
+// Optimizers.cs:466-467; state slots exp_avg, exp_avg_sq (and max_exp_avg_sq with amsgrad), each named slot.index.
+std::vector<std::pair<std::string, float>> Adam::HyperParameters() const {
+  return {{"lr", LearningRate}, {"beta1", beta1_}, {"beta2", beta2_}, {"epsilon", eps_}, {"weight_decay", WeightDecay}, {"amsgrad", amsgrad_ ? 1.f : 0.f}};
+}
+std::vector<Optimizer::StateEntry> Adam::NamedState() {
+  std::vector<StateEntry> out;
+  for (size_t i = 0; i < m_.size(); i++) out.push_back({"exp_avg." + std::to_string(i), m_[i], nullptr});
+  for (size_t i = 0; i < v_.size(); i++) out.push_back({"exp_avg_sq." + std::to_string(i), v_[i], nullptr});
+  for (size_t i = 0; i < vmax_.size(); i++) out.push_back({"max_exp_avg_sq." + std::to_string(i), vmax_[i], nullptr});
+  return out;
 }
 
 // Adam.IntPow: binary powering in double (Optimizers.cs:483-499).

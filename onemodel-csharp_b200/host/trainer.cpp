@@ -480,3 +480,62 @@ OMH_API int32_t omh_trainer_enable_graph(omh_trainer* t) {
 }
 
 OMH_API int64_t omh_trainer_steps_done(omh_trainer* t) { return t->steps_done; }
+
+// ---- what a checkpoint reads and writes (Checkpoint.cs of the reference; the file format lives in checkpoint.py) -------
+OMH_API int32_t omh_trainer_opt_kind(omh_trainer* t, char* buf, size_t n) {
+  std::string k = t->opt->Kind();
+  strncpy(buf, k.c_str(), n - 1);
+  buf[n - 1] = 0;
+  return 0;
+}
+OMH_API int32_t omh_trainer_hyper_count(omh_trainer* t) { return (int32_t)t->opt->HyperParameters().size(); }
+OMH_API int32_t omh_trainer_hyper_info(omh_trainer* t, int32_t i, char* name, size_t n, float* value) {
+  auto h = t->opt->HyperParameters();
+  if (i < 0 || i >= (int)h.size()) return 1;
+  strncpy(name, h[i].first.c_str(), n - 1);
+  name[n - 1] = 0;
+  *value = h[i].second;
+  return 0;
+}
+OMH_API int32_t omh_trainer_state_count(omh_trainer* t) { return (int32_t)t->opt->NamedState().size(); }
+OMH_API int32_t omh_trainer_state_info(omh_trainer* t, int32_t i, char* name, size_t n, int32_t* dtype, int32_t* rank, int32_t* shape) {
+  auto st = t->opt->NamedState();
+  if (i < 0 || i >= (int)st.size()) return 1;
+  strncpy(name, st[i].name.c_str(), n - 1);
+  name[n - 1] = 0;
+  if (st[i].flags) {
+    *dtype = OM_I32;
+    *rank = 1;
+    shape[0] = (int32_t)st[i].flags->size();
+  } else {
+    *dtype = OM_F32;
+    *rank = st[i].tensor.Rank();
+    for (int k = 0; k < *rank; k++) shape[k] = st[i].tensor.GetShape()[k];
+  }
+  return 0;
+}
+OMH_API int32_t omh_trainer_state_get(omh_trainer* t, int32_t i, void* dst) {
+  return Guard([&] {
+    auto st = t->opt->NamedState();
+    if (st.at(i).flags) memcpy(dst, st[i].flags->data(), st[i].flags->size() * 4);
+    else st[i].tensor.CopyToHost(dst);
+  });
+}
+OMH_API int32_t omh_trainer_state_set(omh_trainer* t, int32_t i, const void* src) {
+  return Guard([&] {
+    auto st = t->opt->NamedState();
+    if (st.at(i).flags) memcpy(st[i].flags->data(), src, st[i].flags->size() * 4);
+    else st[i].tensor.CopyFromHost(src);
+  });
+}
+// Restores the step count and the learning rate (Optimizer.RestoreStepCount / SetHyperParameters); the fixed settings
+// (betas, epsilon, momentum ...) are compared by the loader, not changed.
+OMH_API int32_t omh_trainer_restore(omh_trainer* t, int64_t steps, float lr) {
+  return Guard([&] {
+    if (steps < 0) throw ArgumentOutOfRangeException("The step count must not be negative.");
+    if (t->graph) throw InvalidOperationException("Restore a checkpoint before capturing the step.");
+    t->opt->StepCount = steps;
+    t->steps_done = steps;
+    t->opt->LearningRate = lr;
+  });
+}

@@ -150,3 +150,33 @@ def test_tf32_attention(ctx, oracle_built, b, h, lq, lk, d, masked):
         assert scaled_diff(DQ.numpy(), dq) <= 2e-3 and scaled_diff(DK.numpy(), dk) <= 2e-3 and scaled_diff(DV.numpy(), dv) <= 2e-3
     finally:
         ctx.set_flags(0)
+
+
+PAIR_SHAPES = [(256, 256, 64), (8192, 384, 384), (8192, 1152, 384), (1229, 30524, 384), (512, 192, 96), (384, 1536, 8192), (1000, 400, 200),
+               (300, 260, 132)]
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+@pytest.mark.parametrize("m,n,k", PAIR_SHAPES)
+def test_tf32_matmul_on_cta_pairs(ctx, oracle_built, ta, tb, m, n, k):
+    """The CTA-pair kernel (tcgen05 cta_group::2: each CTA loads half of the B tile) against the oracle on TF32-rounded
+    operands and against the one-CTA kernel: the same rounded operands and the same k order, so (without a split of k) the
+    same bits."""
+    K = oracle_built
+    r = np.random.default_rng(m * 3 + n + k)
+    a = r.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
+    b = r.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+    if a.shape[1] % 4 or b.shape[1] % 4:
+        pytest.skip("operand pitch not a multiple of 16 bytes: this shape runs on the fp32 kernel")
+    try:
+        ctx.set_flags(omb.OM_TF32 | omb.OM_PAIR_TILES)
+        got = run(ctx, ta, tb, m, n, k, a, b)
+        assert scaled_diff(got, K.gemm(a, b, bool(ta), bool(tb), mode="tf32")) <= 2e-5
+        c0 = r.standard_normal((m, n)).astype(np.float32)
+        got2 = run(ctx, ta, tb, m, n, k, a, b, acc=1, c0=c0)
+        assert scaled_diff(got2, K.gemm(a, b, bool(ta), bool(tb), mode="tf32") + c0) <= 2e-5
+        ctx.set_flags(omb.OM_TF32)
+        single = run(ctx, ta, tb, m, n, k, a, b)
+        assert scaled_diff(got, single) <= 2e-5
+    finally:
+        ctx.set_flags(0)

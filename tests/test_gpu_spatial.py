@@ -269,6 +269,41 @@ def test_autograd_decoder_fixture(B):
     check_grads(B, fx, w)
 
 
+@pytest.mark.parametrize("tf32", [False, True])
+def test_bidirectional_lstm_on_two_streams_equals_two_layers(ctx, B, tf32):
+    """Ops.LstmBidirectional (both directions concurrently, forward and backward) against two LstmLayer records joined by
+    Concat, the reference's wiring (Recurrent.cs:28-67): same kernels per direction, so the same bits."""
+    import om_binding as omb
+    ctx.set_flags(omb.OM_TF32 if tf32 else 0)
+    try:
+        t, b, i, h = 12, 6, 20, 16
+        r = np.random.default_rng(5)
+        xs = r.standard_normal((t, b, i)).astype(np.float32)
+        ws = []
+        for d in range(2):
+            ws += [(r.standard_normal((4 * h, i)) * 0.3).astype(np.float32), (r.standard_normal((4 * h, h)) * 0.3).astype(np.float32),
+                   (r.standard_normal(4 * h) * 0.1).astype(np.float32), (r.standard_normal(4 * h) * 0.1).astype(np.float32)]
+        proj = r.standard_normal((t, b, 2 * h)).astype(np.float32)
+
+        def run(fused):
+            x = B.tensor(xs, True)
+            w = [B.tensor(a, True) for a in ws]
+            if fused:
+                y = omb.call("lstm_bidirectional", [x] + w)
+            else:
+                y = B.concat([B.lstm_layer(x, w[0], w[1], w[2], w[3], False), B.lstm_layer(x, w[4], w[5], w[6], w[7], True)], 2)
+            B.backward(B.sum(B.mul(y, B.tensor(proj))))
+            return y.numpy(), [B.grad(x)] + [B.grad(p) for p in w]
+
+        ya, ga = run(True)
+        yb, gb = run(False)
+        assert np.array_equal(ya, yb)
+        for k, (p, q) in enumerate(zip(ga, gb)):
+            assert np.array_equal(p, q), k
+    finally:
+        ctx.set_flags(0)
+
+
 def test_training_cnn_fixture(B):
     fx = load_fixture("training", "cnn")
     losses, norms, params, rs = models.train_cnn(B, fx)
