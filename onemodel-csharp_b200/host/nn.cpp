@@ -42,6 +42,22 @@ std::vector<std::pair<std::string, Tensor>> NnModule::NamedParameters(const std:
   return out;
 }
 
+Tensor NnModule::RegisterBuffer(const std::string& name, Tensor t) {
+  buffers_.emplace_back(name, t);
+  return t;
+}
+
+std::vector<std::pair<std::string, Tensor>> NnModule::StateDict(const std::string& prefix) const {
+  std::vector<std::pair<std::string, Tensor>> out;
+  for (auto& p : params_) out.emplace_back(prefix + p.first, p.second);
+  for (auto& b : buffers_) out.emplace_back(prefix + b.first, b.second);
+  for (auto& c : children_) {
+    auto sub = c.second->StateDict(prefix + c.first + ".");
+    out.insert(out.end(), sub.begin(), sub.end());
+  }
+  return out;
+}
+
 std::vector<Tensor> NnModule::Parameters() const {
   std::vector<Tensor> out;
   for (auto& p : NamedParameters()) out.push_back(p.second);
@@ -87,8 +103,8 @@ Conv2d::Conv2d(int inCh, int outCh, int kernel, Generator& g, int stride, int pa
 BatchNorm2d::BatchNorm2d(int channels, float momentum, float eps) : Momentum(momentum), Epsilon(eps) {
   Gamma = RegisterParameter("weight", InitConstant(1.f, Shape{channels}));
   Beta = RegisterParameter("bias", InitConstant(0.f, Shape{channels}));
-  RunningMean = InitConstant(0.f, Shape{channels});
-  RunningVar = InitConstant(1.f, Shape{channels});
+  RunningMean = RegisterBuffer("running_mean", InitConstant(0.f, Shape{channels}));
+  RunningVar = RegisterBuffer("running_var", InitConstant(1.f, Shape{channels}));
 }
 
 MultiHeadAttention::MultiHeadAttention(int width, int heads, Generator& g) : Heads(heads) {

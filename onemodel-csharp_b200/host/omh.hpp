@@ -317,15 +317,20 @@ class NnModule {
   // Parameters in registration order, children after own parameters (NnModule.cs:139-311).
   std::vector<std::pair<std::string, Tensor>> NamedParameters(const std::string& prefix = "") const;
   std::vector<Tensor> Parameters() const;
+  // The state order of the reference (docs/training.md section 1): a module's parameters, then its buffers, then each
+  // child with a dotted path. Checkpoints store the model in this order.
+  std::vector<std::pair<std::string, Tensor>> StateDict(const std::string& prefix = "") const;
   void Train(bool on = true);
   bool Training = true;
  protected:
   Tensor RegisterParameter(const std::string& name, Tensor t);
+  Tensor RegisterBuffer(const std::string& name, Tensor t);
   template <class M> M* RegisterModule(const std::string& name, M* m) {
     children_.emplace_back(name, std::unique_ptr<NnModule>(m));
     return m;
   }
   std::vector<std::pair<std::string, Tensor>> params_;
+  std::vector<std::pair<std::string, Tensor>> buffers_;
   std::vector<std::pair<std::string, std::unique_ptr<NnModule>>> children_;
 };
 

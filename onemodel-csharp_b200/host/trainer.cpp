@@ -482,6 +482,23 @@ OMH_API int32_t omh_trainer_enable_graph(omh_trainer* t) {
 OMH_API int64_t omh_trainer_steps_done(omh_trainer* t) { return t->steps_done; }
 
 // ---- what a checkpoint reads and writes (Checkpoint.cs of the reference; the file format lives in checkpoint.py) -------
+OMH_API int32_t omh_trainer_model_state_count(omh_trainer* t) { return (int32_t)t->model->StateDict().size(); }
+OMH_API int32_t omh_trainer_model_state_info(omh_trainer* t, int32_t i, char* name, size_t n, int32_t* dtype, int32_t* rank, int32_t* shape) {
+  auto st = t->model->StateDict();
+  if (i < 0 || i >= (int)st.size()) return 1;
+  strncpy(name, st[i].first.c_str(), n - 1);
+  name[n - 1] = 0;
+  *dtype = (int32_t)st[i].second.GetDType();
+  *rank = st[i].second.Rank();
+  for (int k = 0; k < *rank; k++) shape[k] = st[i].second.GetShape()[k];
+  return 0;
+}
+OMH_API int32_t omh_trainer_model_state_get(omh_trainer* t, int32_t i, void* dst) {
+  return Guard([&] { t->model->StateDict().at(i).second.CopyToHost(dst); });
+}
+OMH_API int32_t omh_trainer_model_state_set(omh_trainer* t, int32_t i, const void* src) {
+  return Guard([&] { t->model->StateDict().at(i).second.CopyFromHost(src); });
+}
 OMH_API int32_t omh_trainer_opt_kind(omh_trainer* t, char* buf, size_t n) {
   std::string k = t->opt->Kind();
   strncpy(buf, k.c_str(), n - 1);
@@ -528,14 +545,15 @@ OMH_API int32_t omh_trainer_state_set(omh_trainer* t, int32_t i, const void* src
     else st[i].tensor.CopyFromHost(src);
   });
 }
-// Restores the step count and the learning rate (Optimizer.RestoreStepCount / SetHyperParameters); the fixed settings
+// Restores the step count, the learning rate and the weight decay (Optimizer.RestoreStepCount / SetHyperParameters); the fixed settings
 // (betas, epsilon, momentum ...) are compared by the loader, not changed.
-OMH_API int32_t omh_trainer_restore(omh_trainer* t, int64_t steps, float lr) {
+OMH_API int32_t omh_trainer_restore(omh_trainer* t, int64_t steps, float lr, float weight_decay) {
   return Guard([&] {
     if (steps < 0) throw ArgumentOutOfRangeException("The step count must not be negative.");
     if (t->graph) throw InvalidOperationException("Restore a checkpoint before capturing the step.");
     t->opt->StepCount = steps;
     t->steps_done = steps;
     t->opt->LearningRate = lr;
+    t->opt->WeightDecay = weight_decay;
   });
 }

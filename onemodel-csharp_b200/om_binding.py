@@ -435,6 +435,68 @@ class Trainer:
     def state_dict(self):
         return {name: self.get_param(i, shape) for i, (name, shape) in enumerate(self.named_parameters())}
 
+    # ---- what a checkpoint reads and writes (checkpoint.py) --------------------------------------------------------
+    _NP = {0: np.float32, 1: np.int32, 2: np.int64}
+    _DT = {0: "f32", 1: "i32", 2: "i64"}
+
+    def _entries(self, count_fn, info_fn):
+        out = []
+        for i in range(count_fn(self.h)):
+            name = C.create_string_buffer(128)
+            dtype, rank = C.c_int32(), C.c_int32()
+            shape = (C.c_int32 * 8)()
+            info_fn(self.h, i32(i), name, C.c_size_t(128), C.byref(dtype), C.byref(rank), shape)
+            out.append((name.value.decode(), self._DT[dtype.value], tuple(shape[: rank.value])))
+        return out
+
+    def model_state_entries(self):
+        """(name, dtype, shape) of the model's parameters and buffers in the reference's state order."""
+        return self._entries(host_lib().omh_trainer_model_state_count, host_lib().omh_trainer_model_state_info)
+
+    def optimizer_state_entries(self):
+        return self._entries(host_lib().omh_trainer_state_count, host_lib().omh_trainer_state_info)
+
+    def _get(self, fn, entry, i):
+        a = np.empty(entry[2], {"f32": np.float32, "i32": np.int32, "i64": np.int64}[entry[1]])
+        self._check(fn(self.h, i32(i), a.ctypes.data_as(C.c_void_p)))
+        return a
+
+    def _set(self, fn, entry, i, a):
+        a = np.ascontiguousarray(a, {"f32": np.float32, "i32": np.int32, "i64": np.int64}[entry[1]])
+        assert tuple(a.shape) == tuple(entry[2]), (a.shape, entry)
+        self._check(fn(self.h, i32(i), a.ctypes.data_as(C.c_void_p)))
+
+    def model_state_get(self, i):
+        return self._get(host_lib().omh_trainer_model_state_get, self.model_state_entries()[i], i)
+
+    def model_state_set(self, i, a):
+        self._set(host_lib().omh_trainer_model_state_set, self.model_state_entries()[i], i, a)
+
+    def optimizer_state_get(self, i):
+        return self._get(host_lib().omh_trainer_state_get, self.optimizer_state_entries()[i], i)
+
+    def optimizer_state_set(self, i, a):
+        self._set(host_lib().omh_trainer_state_set, self.optimizer_state_entries()[i], i, a)
+
+    def optimizer_kind(self):
+        buf = C.create_string_buffer(32)
+        host_lib().omh_trainer_opt_kind(self.h, buf, C.c_size_t(32))
+        return buf.value.decode()
+
+    def hyper_parameters(self):
+        out = []
+        for i in range(host_lib().omh_trainer_hyper_count(self.h)):
+            name, v = C.create_string_buffer(64), C.c_float()
+            host_lib().omh_trainer_hyper_info(self.h, i32(i), name, C.c_size_t(64), C.byref(v))
+            out.append((name.value.decode(), np.float32(v.value)))
+        return out
+
+    def steps_done(self):
+        return int(host_lib().omh_trainer_steps_done(self.h))
+
+    def restore(self, step, lr, weight_decay):
+        self._check(host_lib().omh_trainer_restore(self.h, C.c_int64(step), C.c_float(lr), C.c_float(weight_decay)))
+
     def input_bytes(self):
         n = host_lib().omh_trainer_input_count(self.h)
         return [int(host_lib().omh_trainer_input_bytes(self.h, i32(i))) for i in range(n)]
