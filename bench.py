@@ -207,6 +207,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--fp32", action="store_true", help="products on the fp32 FMA kernel instead of the tensor pipe")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--ctx-flags", type=int, default=0, help="extra context flags (8 = CTA-pair tiles, 16 = two-stream backward)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -226,6 +227,7 @@ def main():
     kind, cfg, lr, desc, gflop = WORKLOADS[args.workload]
     W, K = max(3, args.warmup), max(1, args.steps)
     flags = 0 if args.fp32 else omb.OM_TF32
+    flags |= args.ctx_flags
     ctx = omb.Context(local_rank, flags)
     tr = omb.Trainer(kind, cfg, lr=lr, weight_decay=WEIGHT_DECAY[kind], seed=0)
     batch = cfg[0]

@@ -52,12 +52,23 @@ typedef enum om_status {
  * src/OneModel/Tensors/Autograd/TensorCompute.cs:22-78). OM_BF16_OPERANDS: operands of matrix products are
  * rounded to bfloat16 (round to nearest even) and multiplied on the tensor pipe with fp32 accumulation.
  * OM_CHECKED: index operands are range-checked on the device and buffers carry canary words
- * (the reference's Checked build, docs/tensors.md:108-110). OM_PAIR_TILES (with OM_TF32): wide plain products use the
- * CTA-pair kernel (tcgen05 cta_group::2, 256-row tiles), which halves the operand bytes each SM pulls from L2. */
+ * (the reference's Checked build, docs/tensors.md:108-110). OM_PAIR_TILES (with OM_TF32): every plain product the
+ * CTA-pair kernel can take runs on it (tcgen05 cta_group::2, 256-row tiles: fewer operand bytes per SM); without the
+ * flag only products with several rounds of tiles over the device do.
+ * OM_TWO_STREAMS: a backward entry point whose gradients are independent of one another (om_linear_bwd: the input
+ * gradient on one side, the weight and bias gradients on the other) runs them on two streams of the context, forked
+ * and joined inside the call, so that products too small to fill the device overlap. Results are the same bits.
+ * OM_SEQ_KERNELS (with OM_TF32): an LSTM layer whose shape fits (hidden a multiple of 16, batch <= 256 for the backward)
+ * runs all its time steps in one cooperative launch with fp32 recurrent products, instead of a product and a gate
+ * kernel per step. OM_OVERLAP_LAUNCHES: the frequent kernels are launched as programmatic dependents of their
+ * predecessor in the stream, so that launch latency and prologue overlap the predecessor's tail (same results). */
 #define OM_TF32 1u
 #define OM_BF16_OPERANDS 2u
 #define OM_CHECKED 4u
 #define OM_PAIR_TILES 8u
+#define OM_TWO_STREAMS 16u
+#define OM_SEQ_KERNELS 32u
+#define OM_OVERLAP_LAUNCHES 64u
 
 typedef enum om_dtype { OM_F32 = 0, OM_I32 = 1, OM_I64 = 2 } om_dtype;
 

@@ -98,6 +98,8 @@ attention_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();   // tensor memory is held: later kernels may become resident
+  pdl_wait();      // everything below may depend on the previous kernel
 
   if (warp == 4) {
     if (lane == 0) {
@@ -329,6 +331,8 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();   // tensor memory is held: later kernels may become resident
+  pdl_wait();      // everything below may depend on the previous kernel
 
   if (warp == 8) {
     if (lane == 0) {
@@ -532,14 +536,14 @@ int32_t attention_tc_fwd(om_ctx* ctx, const float* q, const om_head_strides* qs,
       OM_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       set32 = true;
     }
-    attention_fwd_tc_kernel<32><<<grid, ATT_THREADS, smem, ctx->stream>>>(mq, mk, mv, p);
+    launch_chained(ctx, attention_fwd_tc_kernel<32>, grid, ATT_THREADS, smem, mq, mk, mv, p);
   } else {
     static bool set64 = false;
     if (!set64) {
       OM_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       set64 = true;
     }
-    attention_fwd_tc_kernel<64><<<grid, ATT_THREADS, smem, ctx->stream>>>(mq, mk, mv, p);
+    launch_chained(ctx, attention_fwd_tc_kernel<64>, grid, ATT_THREADS, smem, mq, mk, mv, p);
   }
   OM_LAUNCH_CHECK(ctx, "attention_fwd_tc");
   return OM_OK;
@@ -582,7 +586,7 @@ int32_t attention_tc_bwd(om_ctx* ctx, const float* g, const om_head_strides* gs,
     OM_CUDA(ctx, cudaFuncSetAttribute(attention_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     set = true;
   }
-  attention_bwd_tc_kernel<<<(unsigned)(b * h), ATT_BWD_THREADS, smem, ctx->stream>>>(qk, kk, vk, gk, qm, km, gm, p);
+  launch_chained(ctx, attention_bwd_tc_kernel, (unsigned)(b * h), ATT_BWD_THREADS, smem, qk, kk, vk, gk, qm, km, gm, p);
   OM_LAUNCH_CHECK(ctx, "attention_bwd_tc");
   return OM_OK;
 }

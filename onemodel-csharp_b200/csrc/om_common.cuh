@@ -108,6 +108,37 @@ struct ProfileScope {
 
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// ---- overlapped launches (programmatic dependent launch) ------------------------------------------------------------
+// A kernel that begins with pdl_enter() may be launched through launch_chained(): with OM_OVERLAP_LAUNCHES its CTAs
+// become resident while the previous kernel of the stream is still draining, and hold at the wait until that kernel
+// has completed and its writes are visible; launch latency and the prologue then overlap the predecessor's tail.
+// The trigger comes first so that the chain is not held up by this kernel's own wait; a kernel that allocates a scarce
+// resource its predecessor's CTAs might still need (tensor memory) triggers only after it holds the resource.
+// Without the launch attribute both instructions do nothing.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() {
+  pdl_trigger();
+  pdl_wait();
+}
+
+template <typename... KArgs, typename... Args>
+static inline void launch_chained(om_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (ctx->flags & OM_OVERLAP_LAUNCHES) ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // Grid size for a grid-stride kernel: enough CTAs to fill the machine a few times over, never more than the work.
 static inline int grid_for(om_ctx* ctx, int64_t work_items, int per_block, int waves = 8) {
   int64_t need = ceil_div(work_items, per_block);

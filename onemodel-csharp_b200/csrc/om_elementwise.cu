@@ -26,6 +26,7 @@ __device__ __forceinline__ float binary_apply(int op, float a, float b) {
 template <int OP>
 __global__ void binary_same_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
                                    int64_t n4, int64_t n) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const float4* a4 = reinterpret_cast<const float4*>(a);
@@ -46,6 +47,7 @@ __global__ void binary_same_kernel(const float* __restrict__ a, const float* __r
 template <int OP>
 __global__ void binary_rowb_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
                                    int64_t rows, int32_t cols) {
+  pdl_enter();
   int64_t total = rows * cols;
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -134,6 +136,7 @@ __device__ __forceinline__ float unary_grad(float g, float s) {
 
 template <int OP>
 __global__ void unary_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n4, int64_t n) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const float4* x4 = reinterpret_cast<const float4*>(x);
@@ -152,6 +155,7 @@ __global__ void unary_kernel(const float* __restrict__ x, float* __restrict__ y,
 template <int OP>
 __global__ void unary_bwd_kernel(const float* __restrict__ g, const float* __restrict__ s, float* __restrict__ dx,
                                  int64_t n4, int64_t n) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const float4* g4 = reinterpret_cast<const float4*>(g);
@@ -169,6 +173,7 @@ __global__ void unary_bwd_kernel(const float* __restrict__ g, const float* __res
 }
 
 __global__ void add_into_kernel(float* dst, const float* __restrict__ src, int64_t n4, int64_t n) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   float4* d4 = reinterpret_cast<float4*>(dst);
@@ -182,12 +187,14 @@ __global__ void add_into_kernel(float* dst, const float* __restrict__ src, int64
 }
 
 __global__ void div_scalar_kernel(const float* __restrict__ x, float d, float* __restrict__ y, int64_t n) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t j = i; j < n; j += stride) y[j] = x[j] / d;
 }
 
 __global__ void fill_kernel(float* __restrict__ dst, float v, int64_t n) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t j = i; j < n; j += stride) dst[j] = v;
@@ -202,6 +209,7 @@ struct ZeroTable {
 
 // blockIdx.y selects the tensor; each tensor is zeroed by gridDim.x CTAs.
 __global__ void multi_zero_kernel(ZeroTable t) {
+  pdl_enter();
   float* p = t.p[blockIdx.y];
   int64_t n = t.len[blockIdx.y];
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -220,6 +228,7 @@ __global__ void multi_zero_kernel(ZeroTable t) {
 // ---- strided copy -------------------------------------------------------------------------------------------------
 
 __global__ void strided_copy_kernel(Strided2 s, const float* __restrict__ src, float* __restrict__ dst, int64_t n) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t j = i; j < n; j += stride) {
@@ -238,6 +247,7 @@ __global__ void strided_copy_kernel(Strided2 s, const float* __restrict__ src, f
 // per thread-iteration.
 __global__ void strided_copy_vec4_kernel(Strided2 s, const float* __restrict__ src, float* __restrict__ dst,
                                          int64_t n4) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int32_t inner4 = s.shape[s.rank - 1] >> 2;
@@ -258,6 +268,7 @@ __global__ void strided_copy_vec4_kernel(Strided2 s, const float* __restrict__ s
 // 2-D transpose through a padded shared tile: dst[c, r] = src[r, c].
 __global__ void transpose2d_kernel(const float* __restrict__ src, float* __restrict__ dst, int32_t rows, int32_t cols,
                                    int64_t src_ld, int64_t dst_ld) {
+  pdl_enter();
   __shared__ float tile[32][33];
   int bx = blockIdx.x * 32, by = blockIdx.y * 32;
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
@@ -282,6 +293,7 @@ constexpr int kColsumLanes = 32;
 // order. partial[chunk, col] is written in double.
 __global__ void __launch_bounds__(1024)
 colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial) {
+  pdl_enter();
   __shared__ double sm[kColsumLanes][33];
   int col = blockIdx.x * 32 + threadIdx.x;
   int r0 = blockIdx.y * kColsumRowsPerChunk;
@@ -305,6 +317,7 @@ colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, in
 // rows in flight at once. A CTA is 8 column groups x 32 row lanes and covers 32 columns of one chunk.
 __global__ void __launch_bounds__(256)
 colsum_stage1_vec4_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial) {
+  pdl_enter();
   __shared__ double sm[kColsumLanes][33];
   constexpr int PER_LANE = kColsumRowsPerChunk / kColsumLanes;
   const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
@@ -348,6 +361,7 @@ colsum_stage1_vec4_kernel(const float* __restrict__ g, int32_t rows, int32_t col
 
 __global__ void colsum_stage2_kernel(const double* __restrict__ partial, int32_t chunks, int32_t cols,
                                      float* __restrict__ out, int accumulate) {
+  pdl_enter();
   int col = blockIdx.x * blockDim.x + threadIdx.x;
   if (col >= cols) return;
   double t = 0.0;
@@ -468,10 +482,10 @@ int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64
   OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&partial));
   dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)chunks);
   if ((ld & 3) == 0 && aligned16(g))
-    colsum_stage1_vec4_kernel<<<grid, 256, 0, ctx->stream>>>(g, rows, cols, ld, partial);
+    launch_chained(ctx, colsum_stage1_vec4_kernel, grid, 256, 0, g, rows, cols, ld, partial);
   else
-    colsum_stage1_kernel<<<grid, dim3(32, kColsumLanes), 0, ctx->stream>>>(g, rows, cols, ld, partial);
-  colsum_stage2_kernel<<<(unsigned)ceil_div(cols, 128), 128, 0, ctx->stream>>>(partial, chunks, cols, out, accumulate);
+    launch_chained(ctx, colsum_stage1_kernel, grid, dim3(32, kColsumLanes), 0, g, rows, cols, ld, partial);
+  launch_chained(ctx, colsum_stage2_kernel, (unsigned)ceil_div(cols, 128), 128, 0, partial, chunks, cols, out, accumulate);
   pool_free(ctx, partial);
   OM_LAUNCH_CHECK(ctx, "om_colsum");
   return OM_OK;
@@ -512,20 +526,20 @@ int32_t om_binary(om_ctx* ctx, int32_t op, int32_t rank, const int32_t* shape, c
     int64_t n4 = vec ? n / 4 : 0;
     int grid = grid_for(ctx, vec ? (n + 3) / 4 : n, threads);
     switch (op) {
-      case OM_ADD: binary_same_kernel<OM_ADD><<<grid, threads, 0, ctx->stream>>>(a, b, out, n4, n); break;
-      case OM_SUB: binary_same_kernel<OM_SUB><<<grid, threads, 0, ctx->stream>>>(a, b, out, n4, n); break;
-      case OM_MUL: binary_same_kernel<OM_MUL><<<grid, threads, 0, ctx->stream>>>(a, b, out, n4, n); break;
-      default: binary_same_kernel<OM_DIV><<<grid, threads, 0, ctx->stream>>>(a, b, out, n4, n); break;
+      case OM_ADD: launch_chained(ctx, binary_same_kernel<OM_ADD>, grid, threads, 0, a, b, out, n4, n); break;
+      case OM_SUB: launch_chained(ctx, binary_same_kernel<OM_SUB>, grid, threads, 0, a, b, out, n4, n); break;
+      case OM_MUL: launch_chained(ctx, binary_same_kernel<OM_MUL>, grid, threads, 0, a, b, out, n4, n); break;
+      default: launch_chained(ctx, binary_same_kernel<OM_DIV>, grid, threads, 0, a, b, out, n4, n); break;
     }
   } else if (a_contig && b_row && aligned16(a) && aligned16(b) && aligned16(out)) {
     int32_t cols = shape[rank - 1];
     int64_t rows = n / cols;
     int grid = grid_for(ctx, (n + 3) / 4, threads);
     switch (op) {
-      case OM_ADD: binary_rowb_kernel<OM_ADD><<<grid, threads, 0, ctx->stream>>>(a, b, out, rows, cols); break;
-      case OM_SUB: binary_rowb_kernel<OM_SUB><<<grid, threads, 0, ctx->stream>>>(a, b, out, rows, cols); break;
-      case OM_MUL: binary_rowb_kernel<OM_MUL><<<grid, threads, 0, ctx->stream>>>(a, b, out, rows, cols); break;
-      default: binary_rowb_kernel<OM_DIV><<<grid, threads, 0, ctx->stream>>>(a, b, out, rows, cols); break;
+      case OM_ADD: launch_chained(ctx, binary_rowb_kernel<OM_ADD>, grid, threads, 0, a, b, out, rows, cols); break;
+      case OM_SUB: launch_chained(ctx, binary_rowb_kernel<OM_SUB>, grid, threads, 0, a, b, out, rows, cols); break;
+      case OM_MUL: launch_chained(ctx, binary_rowb_kernel<OM_MUL>, grid, threads, 0, a, b, out, rows, cols); break;
+      default: launch_chained(ctx, binary_rowb_kernel<OM_DIV>, grid, threads, 0, a, b, out, rows, cols); break;
     }
   } else {
     Strided2 s;
@@ -543,16 +557,16 @@ int32_t om_binary(om_ctx* ctx, int32_t op, int32_t rank, const int32_t* shape, c
 
 #define OM_UNARY_DISPATCH(KERNEL, ...)                                                             \
   switch (op) {                                                                                    \
-    case OM_UNARY_NONE: KERNEL<OM_UNARY_NONE><<<grid, threads, 0, ctx->stream>>>(__VA_ARGS__); break; \
-    case OM_RELU: KERNEL<OM_RELU><<<grid, threads, 0, ctx->stream>>>(__VA_ARGS__); break;          \
-    case OM_GELU_ERF: KERNEL<OM_GELU_ERF><<<grid, threads, 0, ctx->stream>>>(__VA_ARGS__); break;  \
-    case OM_GELU_TANH: KERNEL<OM_GELU_TANH><<<grid, threads, 0, ctx->stream>>>(__VA_ARGS__); break; \
-    case OM_SIGMOID: KERNEL<OM_SIGMOID><<<grid, threads, 0, ctx->stream>>>(__VA_ARGS__); break;    \
-    case OM_TANH: KERNEL<OM_TANH><<<grid, threads, 0, ctx->stream>>>(__VA_ARGS__); break;          \
-    case OM_NEG: KERNEL<OM_NEG><<<grid, threads, 0, ctx->stream>>>(__VA_ARGS__); break;            \
-    case OM_EXP: KERNEL<OM_EXP><<<grid, threads, 0, ctx->stream>>>(__VA_ARGS__); break;            \
-    case OM_SQRT: KERNEL<OM_SQRT><<<grid, threads, 0, ctx->stream>>>(__VA_ARGS__); break;          \
-    case OM_ERF: KERNEL<OM_ERF><<<grid, threads, 0, ctx->stream>>>(__VA_ARGS__); break;            \
+    case OM_UNARY_NONE: launch_chained(ctx, KERNEL<OM_UNARY_NONE>, grid, threads, 0, __VA_ARGS__); break; \
+    case OM_RELU: launch_chained(ctx, KERNEL<OM_RELU>, grid, threads, 0, __VA_ARGS__); break;          \
+    case OM_GELU_ERF: launch_chained(ctx, KERNEL<OM_GELU_ERF>, grid, threads, 0, __VA_ARGS__); break;  \
+    case OM_GELU_TANH: launch_chained(ctx, KERNEL<OM_GELU_TANH>, grid, threads, 0, __VA_ARGS__); break; \
+    case OM_SIGMOID: launch_chained(ctx, KERNEL<OM_SIGMOID>, grid, threads, 0, __VA_ARGS__); break;    \
+    case OM_TANH: launch_chained(ctx, KERNEL<OM_TANH>, grid, threads, 0, __VA_ARGS__); break;          \
+    case OM_NEG: launch_chained(ctx, KERNEL<OM_NEG>, grid, threads, 0, __VA_ARGS__); break;            \
+    case OM_EXP: launch_chained(ctx, KERNEL<OM_EXP>, grid, threads, 0, __VA_ARGS__); break;            \
+    case OM_SQRT: launch_chained(ctx, KERNEL<OM_SQRT>, grid, threads, 0, __VA_ARGS__); break;          \
+    case OM_ERF: launch_chained(ctx, KERNEL<OM_ERF>, grid, threads, 0, __VA_ARGS__); break;            \
     default: return fail(ctx, OM_ERR_ARG, "unknown unary op %d", op);                              \
   }
 
@@ -591,7 +605,7 @@ int32_t om_add_into(om_ctx* ctx, float* dst, const float* src, int64_t n) {
   bool vec = aligned16(dst) && aligned16(src);
   int64_t n4 = vec ? n / 4 : 0;
   const int threads = 256;
-  add_into_kernel<<<grid_for(ctx, vec ? (n + 3) / 4 : n, threads), threads, 0, ctx->stream>>>(dst, src, n4, n);
+  launch_chained(ctx, add_into_kernel, grid_for(ctx, vec ? (n + 3) / 4 : n, threads), threads, 0, dst, src, n4, n);
   OM_LAUNCH_CHECK(ctx, "om_add_into");
   return OM_OK;
 }
@@ -600,7 +614,7 @@ int32_t om_div_scalar(om_ctx* ctx, const float* x, float d, float* y, int64_t n)
   OM_CHECK_CTX(ctx);
   if (n <= 0) return OM_OK;
   ProfileScope prof(ctx, "om_div_scalar", 0, 8.0 * n);
-  div_scalar_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(x, d, y, n);
+  launch_chained(ctx, div_scalar_kernel, grid_for(ctx, n, 256), 256, 0, x, d, y, n);
   OM_LAUNCH_CHECK(ctx, "om_div_scalar");
   return OM_OK;
 }
@@ -609,7 +623,7 @@ int32_t om_fill(om_ctx* ctx, float* dst, float value, int64_t n) {
   OM_CHECK_CTX(ctx);
   if (n <= 0) return OM_OK;
   ProfileScope prof(ctx, "om_fill", 0, 4.0 * n);
-  fill_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(dst, value, n);
+  launch_chained(ctx, fill_kernel, grid_for(ctx, n, 256), 256, 0, dst, value, n);
   OM_LAUNCH_CHECK(ctx, "om_fill");
   return OM_OK;
 }
@@ -635,7 +649,7 @@ int32_t om_zero(om_ctx* ctx, int32_t count, float* const* ptrs, const int64_t* l
     t.count = c;
     int gx = (int)std::min<int64_t>(ceil_div(longest, 256 * 4 * 4), 4 * ctx->sm_count);
     if (gx < 1) gx = 1;
-    multi_zero_kernel<<<dim3(gx, c), 256, 0, ctx->stream>>>(t);
+    launch_chained(ctx, multi_zero_kernel, dim3(gx, c), 256, 0, t);
     OM_LAUNCH_CHECK(ctx, "om_zero");
   }
   return OM_OK;
@@ -680,7 +694,7 @@ int32_t om_strided_copy(om_ctx* ctx, int32_t rank, const int32_t* shape, const f
     // dst[r, c] = src[c * ld + r]: a plain 2-D transpose.
     dim3 grid((unsigned)ceil_div(s.shape[0], 32), (unsigned)ceil_div(s.shape[1], 32));
     if (grid.y <= 65535) {
-      transpose2d_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(src, dst, s.shape[1], s.shape[0], s.sa[1], s.sb[0]);
+      launch_chained(ctx, transpose2d_kernel, grid, dim3(32, 8), 0, src, dst, s.shape[1], s.shape[0], s.sa[1], s.sb[0]);
       OM_LAUNCH_CHECK(ctx, "om_strided_copy(transpose)");
       return OM_OK;
     }
@@ -691,9 +705,9 @@ int32_t om_strided_copy(om_ctx* ctx, int32_t rank, const int32_t* shape, const f
     for (int i = 0; i < s.rank - 1; i++)
       if ((s.sa[i] & 3) || (s.sb[i] & 3)) vec = false;
   if (vec) {
-    strided_copy_vec4_kernel<<<grid_for(ctx, n / 4, threads), threads, 0, ctx->stream>>>(s, src, dst, n / 4);
+    launch_chained(ctx, strided_copy_vec4_kernel, grid_for(ctx, n / 4, threads), threads, 0, s, src, dst, n / 4);
   } else {
-    strided_copy_kernel<<<grid_for(ctx, n, threads), threads, 0, ctx->stream>>>(s, src, dst, n);
+    launch_chained(ctx, strided_copy_kernel, grid_for(ctx, n, threads), threads, 0, s, src, dst, n);
   }
   OM_LAUNCH_CHECK(ctx, "om_strided_copy");
   return OM_OK;

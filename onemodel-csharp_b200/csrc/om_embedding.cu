@@ -17,6 +17,7 @@ __device__ __forceinline__ void report_index(int32_t* status, int32_t detail) {
 
 __global__ void embedding_fwd_kernel(const float* __restrict__ table, int32_t v, int32_t dim, const void* __restrict__ ids,
                                      int dtype, int64_t n, float* __restrict__ out, int32_t* status) {
+  pdl_enter();
   int lane = threadIdx.x & 31;
   int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -42,6 +43,7 @@ __global__ void embedding_fwd_kernel(const float* __restrict__ table, int32_t v,
 
 __global__ void embedding_count_kernel(const void* __restrict__ ids, int dtype, int64_t n, int32_t v, int64_t pad,
                                        int32_t* __restrict__ count, int32_t* status) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t j = i; j < n; j += stride) {
@@ -57,6 +59,7 @@ __global__ void embedding_count_kernel(const void* __restrict__ ids, int dtype, 
 
 // Exclusive prefix sum of count[0..v) by one CTA of 1024 threads (each thread scans a contiguous span).
 __global__ void embedding_scan_kernel(const int32_t* __restrict__ count, int32_t v, int32_t* __restrict__ offset) {
+  pdl_enter();
   __shared__ int32_t totals[1024];
   int span = (v + 1023) / 1024;
   int lo = threadIdx.x * span, hi = min(v, lo + span);
@@ -81,6 +84,7 @@ __global__ void embedding_scan_kernel(const int32_t* __restrict__ count, int32_t
 __global__ void embedding_fill_kernel(const void* __restrict__ ids, int dtype, int64_t n, int32_t v, int64_t pad,
                                       const int32_t* __restrict__ offset, int32_t* __restrict__ cursor,
                                       int32_t* __restrict__ bucket) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t j = i; j < n; j += stride) {
@@ -97,6 +101,7 @@ __global__ void embedding_bwd_rows_kernel(const float* __restrict__ g, int32_t v
                                           const int32_t* __restrict__ count, const int32_t* __restrict__ offset,
                                           const int32_t* __restrict__ bucket, int32_t* __restrict__ sorted,
                                           float* __restrict__ dtable, int accumulate) {
+  pdl_enter();
   int lane = threadIdx.x & 31;
   int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -139,7 +144,7 @@ int32_t om_embedding_fwd(om_ctx* ctx, const float* table, int32_t v, int32_t dim
     return fail(ctx, OM_ERR_SHAPE, "Embedding needs a [V, D] float32 table and Int32 or Int64 ids.");
   if (n == 0 || dim == 0) return OM_OK;
   ProfileScope prof(ctx, "om_embedding_fwd", 0, 8.0 * n * dim);
-  embedding_fwd_kernel<<<grid_for(ctx, n * 32, 256), 256, 0, ctx->stream>>>(table, v, dim, ids, id_dtype, n, out, ctx->status_dev);
+  launch_chained(ctx, embedding_fwd_kernel, grid_for(ctx, n * 32, 256), 256, 0, table, v, dim, ids, id_dtype, n, out, ctx->status_dev);
   OM_LAUNCH_CHECK(ctx, "om_embedding_fwd");
   return OM_OK;
 }
@@ -159,11 +164,11 @@ int32_t om_embedding_bwd(om_ctx* ctx, const float* g, const void* ids, int32_t i
   int32_t *bucket = scratch + 3 * (size_t)v, *sorted = bucket + (n > 0 ? n : 1);
   OM_CUDA(ctx, cudaMemsetAsync(count, 0, 2 * (size_t)v * sizeof(int32_t), ctx->stream));
   if (n > 0) {
-    embedding_count_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(ids, id_dtype, n, v, padding_index, count, ctx->status_dev);
-    embedding_scan_kernel<<<1, 1024, 0, ctx->stream>>>(count, v, offset);
-    embedding_fill_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(ids, id_dtype, n, v, padding_index, offset, cursor, bucket);
+    launch_chained(ctx, embedding_count_kernel, grid_for(ctx, n, 256), 256, 0, ids, id_dtype, n, v, padding_index, count, ctx->status_dev);
+    launch_chained(ctx, embedding_scan_kernel, 1, 1024, 0, count, v, offset);
+    launch_chained(ctx, embedding_fill_kernel, grid_for(ctx, n, 256), 256, 0, ids, id_dtype, n, v, padding_index, offset, cursor, bucket);
   }
-  embedding_bwd_rows_kernel<<<grid_for(ctx, (int64_t)v * 32, 256), 256, 0, ctx->stream>>>(g, v, dim, count, offset, bucket, sorted, dtable, accumulate);
+  launch_chained(ctx, embedding_bwd_rows_kernel, grid_for(ctx, (int64_t)v * 32, 256), 256, 0, g, v, dim, count, offset, bucket, sorted, dtable, accumulate);
   pool_free(ctx, scratch);
   OM_LAUNCH_CHECK(ctx, "om_embedding_bwd");
   return OM_OK;

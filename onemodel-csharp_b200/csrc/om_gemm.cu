@@ -115,18 +115,27 @@ int32_t om_linear_bwd_ld(om_ctx* ctx, const float* g, int32_t ldg, const float* 
     return fail(ctx, OM_ERR_SHAPE, "om_linear_bwd: rows %d in %d out %d ldg %d", rows, in_features, out_features, ldg);
   const double flops = 2.0 * rows * in_features * out_features;
   const double bytes = 4.0 * ((double)rows * in_features + (double)in_features * out_features + (double)rows * out_features);
-  if (dx) {
+  auto input_side = [&]() -> int32_t {
+    if (!dx) return OM_OK;
     ProfileScope prof(ctx, "om_linear_bwd.dgrad", flops, bytes);
     // dx[rows, in] = g[rows, out] * W[out, in]
-    OM_TRY(gemm_dispatch(ctx, 0, 0, rows, in_features, out_features, g, ldg, W, in_features, dx, in_features, 0, nullptr));
-  }
-  if (dW) {
-    ProfileScope prof(ctx, "om_linear_bwd.wgrad", flops, bytes);
-    // dW[out, in] = g[rows, out]^T * x[rows, in]
-    OM_TRY(gemm_dispatch(ctx, 1, 0, out_features, in_features, rows, g, ldg, x, in_features, dW, in_features, accumulate_w, nullptr));
-  }
-  if (dbias) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w));
-  return OM_OK;
+    return gemm_dispatch(ctx, 0, 0, rows, in_features, out_features, g, ldg, W, in_features, dx, in_features, 0, nullptr);
+  };
+  auto parameter_side = [&]() -> int32_t {
+    if (dW) {
+      ProfileScope prof(ctx, "om_linear_bwd.wgrad", flops, bytes);
+      // dW[out, in] = g[rows, out]^T * x[rows, in]
+      OM_TRY(gemm_dispatch(ctx, 1, 0, out_features, in_features, rows, g, ldg, x, in_features, dW, in_features, accumulate_w, nullptr));
+    }
+    if (dbias) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w));
+    return OM_OK;
+  };
+  // The two sides share only inputs. With OM_TWO_STREAMS they overlap (not while per-entry times are being taken,
+  // which need one stream, and not for products so small that the fork and join cost more than they hide).
+  const bool fork = (ctx->flags & OM_TWO_STREAMS) && !ctx->profiling && !ctx->aux_active && dx && (dW || dbias) && rows >= 512;
+  if (fork) return run_forked(ctx, input_side, parameter_side);
+  OM_TRY(input_side());
+  return parameter_side();
 }
 
 int32_t om_linear_bwd(om_ctx* ctx, const float* g, const float* x, const float* W, int32_t rows, int32_t in_features,

@@ -30,6 +30,7 @@ constexpr int TMEM_COLS = 128;
 constexpr size_t TC_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
 struct TcParams {
+  int tma_store;        // the epilogue writes C through map_c (C and its pitches are 16-byte aligned)
   int m, n, k;
   int k_per_split;      // multiple of BK
   int splits;
@@ -58,7 +59,8 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(bool a_mn, bool b_mn) {
 //                                 offset); one MMA consumes 8 k-rows = 1024 bytes.
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(TC_THREADS, 2)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_c, TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE_BYTES);
@@ -93,6 +95,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // The CTA holds its tensor memory: later kernels of the stream may become resident now, and everything from here on
+  // (operand loads, bias, C) may depend on the previous kernel.
+  pdl_trigger();
+  pdl_wait();
 
   if (warp == 0) {
     // ---- TMA producer ----
@@ -158,7 +164,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     float* stg = reinterpret_cast<float*>(smem) + quad * 32 * STG_LD;   // spreads the eight rows of a phase over all banks
     const int row_base = m0 + quad * 32;
     const bool aligned = ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && ((p.ldc & 3) == 0);
-    if (ok && row_base < p.m) {
+    if (ok && row_base < p.m && p.tma_store) {
+      // Bulk stores: each 32 x 32 block goes to its own 4 KB of the (dead) operand stages in the 128-byte-swizzled layout
+      // of the C tensor map (16-byte chunk c of row r at chunk c ^ (r & 7): a quarter warp writes 128 distinct bytes),
+      // and one lane hands it to the TMA unit, which writes full rows, clips the ragged edges of C and, when the product
+      // accumulates, adds in place of storing. The warp does not wait for a block before it reads the next one from TMEM.
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 32; cb++) {
+        const int col0 = n0 + cb * 32;
+        if (col0 >= p.n) break;
+        uint32_t r[32];
+        if (k_blocks > 0) {
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j++) r[j] = 0u;
+        }
+        if (p.bias) add_bias32(r, p.bias, col0, p.n);
+        uint8_t* blk = smem + (size_t)(quad * (BN / 32) + cb) * 4096;
+        const uint32_t row_addr = smem_u32(blk) + (uint32_t)lane * 128u;
+#pragma unroll
+        for (int c4 = 0; c4 < 8; c4++)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)((c4 ^ (lane & 7)) << 4)), "r"(r[4 * c4]),
+                       "r"(r[4 * c4 + 1]), "r"(r[4 * c4 + 2]), "r"(r[4 * c4 + 3])
+                       : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          const int z2 = p.batched ? zi : split, z3 = p.batched ? zo : 0;
+          if (p.accumulate)
+            asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(&map_c),
+                         "r"(col0), "r"(row_base), "r"(z2), "r"(z3), "r"(smem_u32(blk))
+                         : "memory");
+          else
+            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(&map_c), "r"(col0),
+                         "r"(row_base), "r"(z2), "r"(z3), "r"(smem_u32(blk))
+                         : "memory");
+        }
+      }
+      if (lane == 0) {
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory may go once the copies have read it
+      }
+      __syncwarp();
+    } else if (ok && row_base < p.m) {
 #pragma unroll 1
       for (int cb = 0; cb < BN / 32; cb++) {
         const int col0 = n0 + cb * 32;
@@ -227,6 +277,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // The split sums are formed first, then bias and the previous contents are added, as the unsplit epilogue does.
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits, int64_t mn, int n, int64_t ldc,
                                      const float* __restrict__ bias, float* __restrict__ out, int accumulate) {
+  pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t j = i; j < mn; j += stride) {
@@ -260,6 +311,25 @@ static bool make_map(CUtensorMap* map, const float* base, int inner, int outer, 
                            CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+// The map the epilogue stores through: C as [outer_count, inner_count, m, n] fp32 with box [32 rows, 32 columns] in the
+// 16-byte-unit 128B swizzle. Fails (and the kernel then stores with ordinary instructions) when C or a pitch is not a
+// multiple of 16 bytes.
+bool make_store_map(CUtensorMap* map, float* base, int n, int m, long long ld, int inner_count, long long inner_stride,
+                           int outer_count, long long outer_stride) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld & 3) || ld < n) return false;
+  if (inner_count > 1 && ((inner_stride & 3) || inner_stride <= 0)) return false;
+  if (outer_count > 1 && ((outer_stride & 3) || outer_stride <= 0)) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)inner_count, (cuuint64_t)outer_count};
+  cuuint64_t fallback = (((cuuint64_t)ld * m * 4) + 15) & ~(cuuint64_t)15;
+  if (fallback < 16) fallback = 16;
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 4, inner_count > 1 ? (cuuint64_t)inner_stride * 4 : fallback,
+                           outer_count > 1 ? (cuuint64_t)outer_stride * 4 : fallback};
+  cuuint32_t box[4] = {32, 32, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 bool gemm_tc_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb,
@@ -313,7 +383,7 @@ int32_t gemm_pair(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float*
                   int acc, const float* bias);
 
 void splitk_reduce_launch(om_ctx* ctx, const float* part, int splits, int64_t mn, int n, int64_t ldc, const float* bias, float* out, int accumulate) {
-  splitk_reduce_kernel<<<grid_for(ctx, mn, 256), 256, 0, ctx->stream>>>(part, splits, mn, n, ldc, bias, out, accumulate);
+  launch_chained(ctx, splitk_reduce_kernel, grid_for(ctx, mn, 256), 256, 0, part, splits, mn, n, ldc, bias, out, accumulate);
 }
 
 int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, long long sA, long long iA,
@@ -358,6 +428,10 @@ int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const fl
   } else {
     p.c = C; p.ldc = ldc; p.accumulate = acc; p.bias = bias;
   }
+  CUtensorMap map_c;
+  p.tma_store = splits > 1 ? make_store_map(&map_c, workspace, n, m, n, splits, (long long)m * n, 1, 0)
+                           : make_store_map(&map_c, C, n, m, ldc, inner, iC, outer, sC);
+  if (!p.tma_store) map_c = map_a;   // never used, but the parameter must hold a valid map
   dim3 grid((unsigned)ceil_div(n, BN), (unsigned)ceil_div(m, BM), (unsigned)(batch > 1 ? batch : splits));
 #define OM_TC_LAUNCH(AMN, BMN)                                                                                         \
   do {                                                                                                                 \
@@ -366,7 +440,7 @@ int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const fl
       OM_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<AMN, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM)); \
       attr_set = true;                                                                                                 \
     }                                                                                                                  \
-    gemm_tc_kernel<AMN, BMN><<<grid, TC_THREADS, TC_SMEM, ctx->stream>>>(map_a, map_b, p);                               \
+    launch_chained(ctx, gemm_tc_kernel<AMN, BMN>, grid, TC_THREADS, TC_SMEM, map_a, map_b, map_c, p);                    \
   } while (0)
   if (!a_mn && !b_mn) OM_TC_LAUNCH(false, false);
   else if (!a_mn && b_mn) OM_TC_LAUNCH(false, true);
@@ -376,7 +450,7 @@ int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const fl
   OM_LAUNCH_CHECK(ctx, "gemm_tc");
   if (splits > 1) {
     int64_t mn = (int64_t)m * n;
-    splitk_reduce_kernel<<<grid_for(ctx, mn, 256), 256, 0, ctx->stream>>>(workspace, splits, mn, n, ldc, bias, C, acc);
+    launch_chained(ctx, splitk_reduce_kernel, grid_for(ctx, mn, 256), 256, 0, workspace, splits, mn, n, ldc, bias, C, acc);
     pool_free(ctx, workspace);
     OM_LAUNCH_CHECK(ctx, "splitk_reduce");
   }

@@ -23,6 +23,7 @@ struct PairParams {
   int accumulate;
   const float* bias;
   int32_t* status;
+  int tma_store;        // the epilogue writes C through map_c
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -73,7 +74,8 @@ __host__ __device__ constexpr uint32_t pair_idesc(int bn, bool a_mn, bool b_mn) 
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, PairParams p) {
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_c, PairParams p) {
   constexpr int HB = BN / 2;                              // rows of the B tile this CTA loads
   constexpr int A_BYTES = P_BM * P_BK * 4, B_BYTES = HB * P_BK * 4, STAGE = A_BYTES + B_BYTES;
   constexpr uint32_t TMEM_COLS = BN <= 128 ? 128 : 256;
@@ -112,6 +114,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   cluster_sync_all();                                     // both CTAs' barriers exist before anyone signals across
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -171,7 +175,52 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     float* stg = reinterpret_cast<float*>(smem) + quad * 32 * STG_LD;
     const int row_base = m0 + quad * 32;
     const bool aligned = ((reinterpret_cast<uintptr_t>(c) & 15) == 0) && ((p.ldc & 3) == 0);
-    if (ok && row_base < p.m) {
+    if (ok && row_base < p.m && p.tma_store) {
+      // Bulk stores as in the one-CTA kernel: 32 x 32 blocks staged in the swizzled layout of the C map and handed to the
+      // TMA unit. A warp cycles through four 4 KB staging blocks; before it overwrites one it waits until the bulk copy
+      // that read it (three copies back) has finished reading.
+      constexpr int RING = 4;
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 32; cb++) {
+        const int col0 = n0 + cb * 32;
+        if (col0 >= p.n) break;
+        uint32_t r[32];
+        if (k_blocks > 0) {
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j++) r[j] = 0u;
+        }
+        if (p.bias) add_bias32(r, p.bias, col0, p.n);
+        if (cb >= RING) {
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+          __syncwarp();
+        }
+        uint8_t* blk = smem + (size_t)(quad * RING + (cb % RING)) * 4096;
+        const uint32_t row_addr = smem_u32(blk) + (uint32_t)lane * 128u;
+#pragma unroll
+        for (int c4 = 0; c4 < 8; c4++)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)((c4 ^ (lane & 7)) << 4)), "r"(r[4 * c4]),
+                       "r"(r[4 * c4 + 1]), "r"(r[4 * c4 + 2]), "r"(r[4 * c4 + 3])
+                       : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          if (p.accumulate)
+            asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(&map_c),
+                         "r"(col0), "r"(row_base), "r"(split), "r"(0), "r"(smem_u32(blk))
+                         : "memory");
+          else
+            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(&map_c), "r"(col0),
+                         "r"(row_base), "r"(split), "r"(0), "r"(smem_u32(blk))
+                         : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      __syncwarp();
+    } else if (ok && row_base < p.m) {
 #pragma unroll 1
       for (int cb = 0; cb < BN / 32; cb++) {
         const int col0 = n0 + cb * 32;
@@ -236,6 +285,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
+bool make_store_map(CUtensorMap* map, float* base, int n, int m, long long ld, int inner_count, long long inner_stride, int outer_count,
+                    long long outer_stride);
 void splitk_reduce_launch(om_ctx* ctx, const float* part, int splits, int64_t mn, int n, int64_t ldc, const float* bias, float* out, int accumulate);
 
 // Rank-4 map with unit batch dimensions (the pair kernel serves plain products only).
@@ -251,13 +302,20 @@ static bool pair_map(CUtensorMap* map, const float* base, int inner, int outer, 
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// The pair kernel pays off when there is enough width for a 192- or 256-column tile and enough rows for pairs.
+// The pair kernel needs rows for pairs and a width of at least one 128-column tile. By default it takes the products
+// with several rounds of tiles over the device and no split of k (measured: 3 to 10 % faster on the widest products of a
+// 768-wide encoder, 1.44x at 4096^3, slower on products of one or two rounds, where the larger tile leaves SMs idle);
+// OM_PAIR_TILES sends every product it can take to it.
 bool gemm_pair_supported(om_ctx* ctx, int m, int n, int k) {
-  return (ctx->flags & OM_PAIR_TILES) != 0 && m >= 256 && n >= 192 && k >= 64;
+  if (m < 256 || n < 128 || k < 64) return false;
+  if (ctx->flags & OM_PAIR_TILES) return true;
+  const int64_t tiles = ceil_div(m, P_BM) * ceil_div(n, 128);
+  return tiles >= 4 * (int64_t)ctx->sm_count && m >= 1024 && n >= 256;
 }
 
 template <int BN>
-static int32_t launch_pair(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const PairParams& p, dim3 grid) {
+static int32_t launch_pair(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                           const PairParams& p, dim3 grid) {
   constexpr size_t smem = (size_t)P_STAGES * (P_BM * P_BK * 4 + (BN / 2) * P_BK * 4) + 1024 + 256;
 #define OM_PAIR(AMN, BMN)                                                                                                   \
   do {                                                                                                                      \
@@ -266,7 +324,7 @@ static int32_t launch_pair(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap&
       OM_CUDA(ctx, cudaFuncSetAttribute(gemm_pair_kernel<BN, AMN, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
       attr_set = true;                                                                                                      \
     }                                                                                                                       \
-    gemm_pair_kernel<BN, AMN, BMN><<<grid, P_THREADS, smem, ctx->stream>>>(ma, mb, p);                                      \
+    launch_chained(ctx, gemm_pair_kernel<BN, AMN, BMN>, grid, P_THREADS, smem, ma, mb, mc, p);                              \
   } while (0)
   if (!a_mn && !b_mn) OM_PAIR(false, false);
   else if (!a_mn && b_mn) OM_PAIR(false, true);
@@ -280,9 +338,22 @@ static int32_t launch_pair(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap&
 int32_t gemm_pair(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb, float* C, int ldc,
                   int acc, const float* bias) {
   const bool a_mn = ta != 0, b_mn = tb == 0;
-  // Tile width: 256 when it divides the width well, else 192 (384 = 2 x 192, 1152 = 6 x 192, 1536 = 8 x 192).
-  const int waste256 = (int)(ceil_div(n, 256) * 256 - n), waste192 = (int)(ceil_div(n, 192) * 192 - n);
-  const int bn = (waste256 * 192 <= waste192 * 256) ? 256 : 192;
+  // Tile width 128, 192 or 256: the one with the shortest estimated time, counted as rounds of CTAs over the device (two
+  // CTAs per SM) times the work of a CTA (its tile width plus a fixed part for prologue and epilogue). Wide tiles bring in
+  // fewer operand bytes per output but leave small products with too few CTAs.
+  int bn = 128;
+  {
+    const int64_t slots = 2 * (int64_t)ctx->sm_count;
+    int64_t best = 0;
+    for (int cand : {128, 192, 256}) {
+      const int64_t ctas_c = 2 * ceil_div(m, 2 * P_BM) * ceil_div(n, cand);
+      const int64_t cost = ceil_div(ctas_c, slots) * (cand + 64);
+      if (best == 0 || cost < best || (cost == best && cand > bn)) {
+        best = cost;
+        bn = cand;
+      }
+    }
+  }
   CUtensorMap map_a, map_b;
   bool ok = a_mn ? pair_map(&map_a, A, m, k, lda, P_BK, true) : pair_map(&map_a, A, k, m, lda, P_BM, false);
   ok = ok && (b_mn ? pair_map(&map_b, B, n, k, ldb, P_BK, true) : pair_map(&map_b, B, k, n, ldb, bn / 2, false));
@@ -306,8 +377,14 @@ int32_t gemm_pair(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float*
   } else {
     p.c = C; p.ldc = ldc; p.accumulate = acc; p.bias = bias;
   }
+  CUtensorMap map_c;
+  p.tma_store = splits > 1 ? make_store_map(&map_c, workspace, n, m, n, splits, (long long)m * n, 1, 0)
+                           : make_store_map(&map_c, C, n, m, ldc, 1, 0, 1, 0);
+  if (!p.tma_store) map_c = map_a;
   dim3 grid((unsigned)(2 * pairs), (unsigned)n_tiles, (unsigned)splits);
-  int32_t st = bn == 256 ? launch_pair<256>(ctx, a_mn, b_mn, map_a, map_b, p, grid) : launch_pair<192>(ctx, a_mn, b_mn, map_a, map_b, p, grid);
+  int32_t st = bn == 256   ? launch_pair<256>(ctx, a_mn, b_mn, map_a, map_b, map_c, p, grid)
+               : bn == 192 ? launch_pair<192>(ctx, a_mn, b_mn, map_a, map_b, map_c, p, grid)
+                           : launch_pair<128>(ctx, a_mn, b_mn, map_a, map_b, map_c, p, grid);
   if (st == OM_OK && splits > 1) splitk_reduce_launch(ctx, workspace, splits, (int64_t)m * n, n, ldc, bias, C, acc);
   if (workspace) pool_free(ctx, workspace);
   return st;

@@ -56,6 +56,7 @@ enum RowOp { SOFTMAX_FWD, LOGSOFTMAX_FWD, SOFTMAX_BWD, LOGSOFTMAX_BWD };
 template <int G, int OP>
 __global__ void __launch_bounds__(kRowThreads)
 row_kernel(const float* __restrict__ a, const float* __restrict__ b, int32_t rows, int32_t cols, int64_t ld, float* __restrict__ out) {
+  pdl_enter();
   __shared__ double sm[kRowThreads / 32];
   const int lane = G == 32 ? (threadIdx.x & 31) : threadIdx.x;
   const int64_t group = G == 32 ? ((int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5)) : blockIdx.x;
@@ -102,10 +103,10 @@ static int32_t launch_rows(om_ctx* ctx, const char* name, const float* a, const 
   ProfileScope prof(ctx, name, 0, bytes);
   if (cols >= kWideRow) {
     int grid = (int)std::min<int64_t>(rows, (int64_t)ctx->sm_count * 8);
-    row_kernel<kRowThreads, OP><<<grid, kRowThreads, 0, ctx->stream>>>(a, b, rows, cols, ld, out);
+    launch_chained(ctx, row_kernel<kRowThreads, OP>, grid, kRowThreads, 0, a, b, rows, cols, ld, out);
   } else {
     int grid = (int)std::min<int64_t>(ceil_div(rows, kRowThreads / 32), (int64_t)ctx->sm_count * 8);
-    row_kernel<32, OP><<<grid, kRowThreads, 0, ctx->stream>>>(a, b, rows, cols, ld, out);
+    launch_chained(ctx, row_kernel<32, OP>, grid, kRowThreads, 0, a, b, rows, cols, ld, out);
   }
   OM_LAUNCH_CHECK(ctx, name);
   return OM_OK;
@@ -123,6 +124,7 @@ __device__ __forceinline__ void report(int32_t* status, int32_t code, int32_t de
 __global__ void nll_fwd_kernel(const float* __restrict__ logp, const void* __restrict__ targets, int dtype, int32_t rows,
                                int32_t cols, int64_t ld, int mean, int64_t ignore, float denominator, float* __restrict__ loss,
                                int32_t* __restrict__ count_out, int32_t* status) {
+  pdl_enter();
   __shared__ double ssum[1024];
   __shared__ int scount[1024];
   double s = 0.0;
@@ -157,6 +159,7 @@ __global__ void nll_fwd_kernel(const float* __restrict__ logp, const void* __res
 
 __global__ void count_targets_kernel(const void* __restrict__ targets, int dtype, int32_t rows, int64_t ignore,
                                      int32_t* __restrict__ count_out) {
+  pdl_enter();
   __shared__ int scount[1024];
   int c = 0;
   for (int i = threadIdx.x; i < rows; i += 1024) c += target_at(targets, dtype, i) != ignore;
@@ -197,6 +200,7 @@ __global__ void __launch_bounds__(kRowThreads)
 cross_entropy_bwd_kernel(const float* __restrict__ g, const float* __restrict__ logp, const void* __restrict__ targets,
                          int dtype, int32_t rows, int32_t cols, int64_t ld, int mean, int64_t ignore, float denominator,
                          const int32_t* __restrict__ count, float* __restrict__ dx) {
+  pdl_enter();
   float scale = nll_scale(g, mean, count, denominator);
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     int64_t t = target_at(targets, dtype, row);
@@ -245,7 +249,7 @@ int32_t om_nll_fwd(om_ctx* ctx, const float* logp, const void* targets, int32_t 
   OM_CHECK_CTX(ctx);
   OM_TRY(check_targets(ctx, "om_nll_fwd", target_dtype, rows, cols));
   ProfileScope prof(ctx, "om_nll_fwd", 0, 12.0 * rows);
-  nll_fwd_kernel<<<1, 1024, 0, ctx->stream>>>(logp, targets, target_dtype, rows, cols, cols, mean, ignore_index, 0.f, loss, count, ctx->status_dev);
+  launch_chained(ctx, nll_fwd_kernel, 1, 1024, 0, logp, targets, target_dtype, rows, cols, cols, mean, ignore_index, 0.f, loss, count, ctx->status_dev);
   OM_LAUNCH_CHECK(ctx, "om_nll_fwd");
   return OM_OK;
 }
@@ -258,7 +262,7 @@ int32_t om_nll_bwd(om_ctx* ctx, const float* g, const void* targets, int32_t tar
   ProfileScope prof(ctx, "om_nll_bwd", 0, 4.0 * rows * (double)cols);
   int32_t* count = nullptr;
   OM_TRY(pool_alloc(ctx, 256, false, (void**)&count));
-  count_targets_kernel<<<1, 1024, 0, ctx->stream>>>(targets, target_dtype, rows, ignore_index, count);
+  launch_chained(ctx, count_targets_kernel, 1, 1024, 0, targets, target_dtype, rows, ignore_index, count);
   nll_bwd_kernel<<<grid_for(ctx, (int64_t)rows * cols, 256), 256, 0, ctx->stream>>>(g, targets, target_dtype, rows, cols, mean, ignore_index, count, dx);
   pool_free(ctx, count);
   OM_LAUNCH_CHECK(ctx, "om_nll_bwd");
@@ -274,7 +278,7 @@ int32_t om_cross_entropy_fwd_ld(om_ctx* ctx, const float* logits, const void* ta
   if (!logp) return fail(ctx, OM_ERR_ARG, "om_cross_entropy_fwd: logp is required (the backward reads it)");
   OM_TRY(launch_rows<LOGSOFTMAX_FWD>(ctx, "om_cross_entropy_fwd.logsoftmax", logits, nullptr, rows, cols, logp, ld));
   ProfileScope prof(ctx, "om_cross_entropy_fwd.nll", 0, 12.0 * rows);
-  nll_fwd_kernel<<<1, 1024, 0, ctx->stream>>>(logp, targets, target_dtype, rows, cols, ld, mean, ignore_index, denominator, loss, count, ctx->status_dev);
+  launch_chained(ctx, nll_fwd_kernel, 1, 1024, 0, logp, targets, target_dtype, rows, cols, ld, mean, ignore_index, denominator, loss, count, ctx->status_dev);
   OM_LAUNCH_CHECK(ctx, "om_cross_entropy_fwd");
   return OM_OK;
 }
@@ -295,9 +299,9 @@ int32_t om_cross_entropy_bwd_ld(om_ctx* ctx, const float* g, const float* logp, 
   ProfileScope prof(ctx, "om_cross_entropy_bwd", 0, 8.0 * rows * (double)cols);
   int32_t* count = nullptr;
   OM_TRY(pool_alloc(ctx, 256, false, (void**)&count));
-  count_targets_kernel<<<1, 1024, 0, ctx->stream>>>(targets, target_dtype, rows, ignore_index, count);
+  launch_chained(ctx, count_targets_kernel, 1, 1024, 0, targets, target_dtype, rows, ignore_index, count);
   int grid = (int)std::min<int64_t>(rows, (int64_t)ctx->sm_count * 8);
-  cross_entropy_bwd_kernel<<<grid, kRowThreads, 0, ctx->stream>>>(g, logp, targets, target_dtype, rows, cols, ld, mean, ignore_index, denominator, count, dlogits);
+  launch_chained(ctx, cross_entropy_bwd_kernel, grid, kRowThreads, 0, g, logp, targets, target_dtype, rows, cols, ld, mean, ignore_index, denominator, count, dlogits);
   pool_free(ctx, count);
   OM_LAUNCH_CHECK(ctx, "om_cross_entropy_bwd");
   return OM_OK;

@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(256)
 layernorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
                      int32_t rows, int32_t cols, float eps, float* __restrict__ y, float* __restrict__ mean_out,
                      float* __restrict__ inv_out) {
+  pdl_enter();
   int lane = threadIdx.x & 31;
   int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   int64_t warps = (int64_t)gridDim.x * 8;
@@ -56,6 +57,7 @@ __global__ void __launch_bounds__(256)
 layernorm_bwd_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
                      const float* __restrict__ mean, const float* __restrict__ inv, int32_t rows, int32_t cols,
                      float* __restrict__ dx) {
+  pdl_enter();
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int r0 = blockIdx.x * kLnRowsPerCta;
   const int r1 = min(rows, r0 + kLnRowsPerCta);
@@ -107,6 +109,7 @@ __global__ void __launch_bounds__(256)
 layernorm_param_partials_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ mean,
                                 const float* __restrict__ inv, int32_t rows, int32_t cols, double* __restrict__ part_gamma,
                                 double* __restrict__ part_beta) {
+  pdl_enter();
   __shared__ double sg[32][33], sb[32][33];
   const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
   const int col = blockIdx.x * 32 + tx * 4;
@@ -178,6 +181,7 @@ layernorm_param_partials_kernel(const float* __restrict__ g, const float* __rest
 __global__ void __launch_bounds__(512)
 column_partials_finish_kernel(const double* __restrict__ pa, const double* __restrict__ pb, int chunks, int32_t cols,
                               float* __restrict__ oa, float* __restrict__ ob, int accumulate) {
+  pdl_enter();
   __shared__ double sa[16][33], sb[16][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int j = blockIdx.x * 32 + tx;
@@ -388,7 +392,7 @@ int32_t om_layernorm_fwd(om_ctx* ctx, const float* x, const float* gamma, const 
   if (rows == 0 || cols == 0) return OM_OK;
   ProfileScope prof(ctx, "om_layernorm_fwd", 0, 8.0 * rows * (double)cols);
   int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 8);
-  layernorm_fwd_kernel<<<grid, 256, 0, ctx->stream>>>(x, gamma, beta, rows, cols, eps, y, mean, inv);
+  launch_chained(ctx, layernorm_fwd_kernel, grid, 256, 0, x, gamma, beta, rows, cols, eps, y, mean, inv);
   OM_LAUNCH_CHECK(ctx, "om_layernorm_fwd");
   return OM_OK;
 }
@@ -406,7 +410,7 @@ int32_t om_layernorm_bwd(om_ctx* ctx, const float* g, const float* x, const floa
   const int row_ctas = (int)ceil_div(rows > 0 ? rows : 1, kLnRowsPerCta);
   int nc = (int)ceil_div(cols, 32);
   if (dx && rows > 0) {
-#define OM_LN_BWD(NC) layernorm_bwd_kernel<NC><<<row_ctas, 256, 0, ctx->stream>>>(g, x, gamma, mean, inv, rows, cols, dx)
+#define OM_LN_BWD(NC) launch_chained(ctx, layernorm_bwd_kernel<NC>, row_ctas, 256, 0, g, x, gamma, mean, inv, rows, cols, dx)
     if (nc <= 4) OM_LN_BWD(4);
     else if (nc <= 8) OM_LN_BWD(8);
     else if (nc <= 12) OM_LN_BWD(12);
@@ -420,8 +424,8 @@ int32_t om_layernorm_bwd(om_ctx* ctx, const float* g, const float* x, const floa
     const int chunks = (int)ceil_div(rows > 0 ? rows : 1, kLnParamRows);
     if (dgamma) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&pg));
     if (dbeta) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&pb));
-    layernorm_param_partials_kernel<<<dim3((unsigned)ceil_div(cols, 32), (unsigned)chunks), 256, 0, ctx->stream>>>(g, x, mean, inv, rows, cols, pg, pb);
-    column_partials_finish_kernel<<<(unsigned)ceil_div(cols, 32), 512, 0, ctx->stream>>>(pg, pb, chunks, cols, dgamma, dbeta, accumulate_params);
+    launch_chained(ctx, layernorm_param_partials_kernel, dim3((unsigned)ceil_div(cols, 32), (unsigned)chunks), 256, 0, g, x, mean, inv, rows, cols, pg, pb);
+    launch_chained(ctx, column_partials_finish_kernel, (unsigned)ceil_div(cols, 32), 512, 0, pg, pb, chunks, cols, dgamma, dbeta, accumulate_params);
   }
   if (pg) pool_free(ctx, pg);
   if (pb) pool_free(ctx, pb);
@@ -490,7 +494,7 @@ int32_t om_batchnorm_bwd(om_ctx* ctx, const float* g, const float* x, const floa
     pool_free(ctx, coef);
   }
   if (dgamma || dbeta)
-    column_partials_finish_kernel<<<(unsigned)ceil_div(c, 32), 512, 0, ctx->stream>>>(pa, pb, slices, c, dgamma, dbeta, accumulate_params);
+    launch_chained(ctx, column_partials_finish_kernel, (unsigned)ceil_div(c, 32), 512, 0, pa, pb, slices, c, dgamma, dbeta, accumulate_params);
   pool_free(ctx, pa);
   pool_free(ctx, pb);
   OM_LAUNCH_CHECK(ctx, "om_batchnorm_bwd");

@@ -60,6 +60,7 @@ __device__ __forceinline__ float adam_element(float& p, float g, float& m, float
 
 __global__ void __launch_bounds__(256)
 adam_kernel(TensorTable t, om_adam_hyper hv, const om_adam_hyper* __restrict__ hd) {
+  pdl_enter();
   const om_adam_hyper h = hd ? *hd : hv;
   const float omb1 = __fsub_rn(1.0f, h.beta1), omb2 = __fsub_rn(1.0f, h.beta2);
   const float decay = __fsub_rn(1.0f, __fmul_rn(h.lr, h.weight_decay));
@@ -127,6 +128,7 @@ sgd_kernel(TensorTable t, om_sgd_hyper hv, const om_sgd_hyper* __restrict__ hd) 
 // Stage 1: one double partial per chunk (256 threads, each summing its strided elements in order, fixed tree).
 __global__ void __launch_bounds__(256)
 sumsq_kernel(TensorTable t, int infinity, double* __restrict__ partial, int chunk_base) {
+  pdl_enter();
   __shared__ double sm[256];
   const int total = t.chunk_prefix[t.n];
   for (int chunk = blockIdx.x; chunk < total; chunk += gridDim.x) {
@@ -161,6 +163,7 @@ sumsq_kernel(TensorTable t, int infinity, double* __restrict__ partial, int chun
 // Stage 2: one CTA combines the chunk partials in chunk order and writes {norm, coef}.
 __global__ void norm_finish_kernel(const double* __restrict__ partial, int chunks, int infinity, float max_norm,
                                    float* __restrict__ total_norm, float* __restrict__ coef_out) {
+  pdl_enter();
   __shared__ double sm[1024];
   double acc = 0.0;
   // Thread i owns the contiguous span [i*span, (i+1)*span) so that the combine order is the chunk order.
@@ -188,6 +191,7 @@ __global__ void norm_finish_kernel(const double* __restrict__ partial, int chunk
 
 __global__ void __launch_bounds__(256)
 scale_by_coef_kernel(TensorTable t, const float* __restrict__ coef_ptr) {
+  pdl_enter();
   const float coef = coef_ptr[0];
   if (!(coef < 1.0f)) return;
   const int total = t.chunk_prefix[t.n];
@@ -313,7 +317,7 @@ int32_t om_optim_adam_step(om_ctx* ctx, int32_t n_tensors, float* const* p, cons
     int count = std::min(kMaxTensors, n_tensors - base);
     int chunks = fill_table(t, base, count, p, g, m, v, vmax, nullptr, len);
     if (chunks == 0) continue;
-    adam_kernel<<<grid_chunks(ctx, chunks), 256, 0, ctx->stream>>>(t, *hyper_host, hyper_dev);
+    launch_chained(ctx, adam_kernel, grid_chunks(ctx, chunks), 256, 0, t, *hyper_host, hyper_dev);
     OM_LAUNCH_CHECK(ctx, "om_optim_adam_step");
   }
   return OM_OK;
@@ -361,16 +365,16 @@ int32_t om_grad_norm_clip(om_ctx* ctx, int32_t n_tensors, float* const* g, const
     int count = std::min(kMaxTensors, n_tensors - base);
     int chunks = fill_table(t, base, count, nullptr, (const float* const*)g, nullptr, nullptr, nullptr, nullptr, len);
     if (chunks == 0) continue;
-    sumsq_kernel<<<grid_chunks(ctx, chunks), 256, 0, ctx->stream>>>(t, infinity_norm, partial, chunk_base);
+    launch_chained(ctx, sumsq_kernel, grid_chunks(ctx, chunks), 256, 0, t, infinity_norm, partial, chunk_base);
     chunk_base += chunks;
   }
-  norm_finish_kernel<<<1, 1024, 0, ctx->stream>>>(partial, total_chunks, infinity_norm, max_norm, total_norm, coef);
+  launch_chained(ctx, norm_finish_kernel, 1, 1024, 0, partial, total_chunks, infinity_norm, max_norm, total_norm, coef);
   for (int base = 0; base < n_tensors; base += kMaxTensors) {
     TensorTable t;
     int count = std::min(kMaxTensors, n_tensors - base);
     int chunks = fill_table(t, base, count, g, nullptr, nullptr, nullptr, nullptr, nullptr, len);
     if (chunks == 0) continue;
-    scale_by_coef_kernel<<<grid_chunks(ctx, chunks), 256, 0, ctx->stream>>>(t, coef);
+    launch_chained(ctx, scale_by_coef_kernel, grid_chunks(ctx, chunks), 256, 0, t, coef);
   }
   pool_free(ctx, partial);
   pool_free(ctx, coef);

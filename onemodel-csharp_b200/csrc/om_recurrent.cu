@@ -9,6 +9,7 @@
 // own exp/log polynomials (Ctc.cs:515-616), one CTA per sequence; per-class sums run in increasing extended-label
 // order so the result has the reference's bits.
 #include "om_common.cuh"
+#include "om_lstm_seq.cuh"
 
 namespace om {
 
@@ -362,6 +363,43 @@ static int32_t lstm_fwd_body(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b,
   return OM_OK;
 }
 
+// All time steps of `dirs` directions in one cooperative launch (om_lstm_seq.cu): the input products and the bias sums
+// first, then the sequence kernel. Index k of the pointer tables is the direction; reverse[k] its time order.
+static int32_t lstm_fwd_seq(om_ctx* ctx, int dirs, const int32_t* reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* x,
+                            const float* const* w_ih, const float* const* w_hh, const float* const* b_ih, const float* const* b_hh,
+                            const float* const* h0, const float* const* c0, float* const* y, float* const* gates, float* const* c,
+                            float* const* tanh_c) {
+  const int h4 = 4 * h;
+  LstmSeqFwdDir d[2];
+  float* bias[2] = {nullptr, nullptr};
+  int32_t st = OM_OK;
+  for (int k = 0; k < dirs && st == OM_OK; k++) {
+    st = gemm_dispatch(ctx, 0, 1, t * b, h4, i, x, i, w_ih[k], i, gates[k], h4, 0, nullptr);
+    const float* bi = b_ih ? b_ih[k] : nullptr;
+    const float* bhh = b_hh ? b_hh[k] : nullptr;
+    if (st == OM_OK && (bi || bhh)) {
+      st = pool_alloc(ctx, sizeof(float) * h4, false, (void**)&bias[k]);
+      if (st == OM_OK) lstm_bias_kernel<<<(unsigned)ceil_div(h4, 256), 256, 0, ctx->stream>>>(bi, bhh, h4, bias[k]);
+    }
+    d[k].gates = gates[k];
+    d[k].w_hh = w_hh[k];
+    d[k].bias = bias[k];
+    d[k].h0 = h0 ? h0[k] : nullptr;
+    d[k].c0 = c0 ? c0[k] : nullptr;
+    d[k].y = y[k];
+    d[k].c = c[k];
+    d[k].tanh_c = tanh_c[k];
+    d[k].counter = nullptr;
+    d[k].reverse = reverse[k];
+  }
+  if (st == OM_OK) st = lstm_seq_fwd(ctx, dirs, t, b, h, d);
+  for (int k = 0; k < 2; k++)
+    if (bias[k]) pool_free(ctx, bias[k]);
+  OM_TRY(st);
+  OM_LAUNCH_CHECK(ctx, "om_lstm_layer_fwd");
+  return OM_OK;
+}
+
 int32_t om_lstm_layer_fwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* x,
                           const float* w_ih, const float* w_hh, const float* b_ih, const float* b_hh, const float* h0,
                           const float* c0, float* y, float* gates, float* c, float* tanh_c) {
@@ -369,6 +407,8 @@ int32_t om_lstm_layer_fwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, in
   if (t < 0 || b < 0 || i < 1 || h < 1) return fail(ctx, OM_ERR_SHAPE, "LstmLayer: T %d B %d I %d H %d", t, b, i, h);
   if (t == 0 || b == 0) return OM_OK;
   ProfileScope prof(ctx, "om_lstm_layer_fwd", 2.0 * t * b * 4.0 * h * (i + h), 4.0 * t * b * (double)(i + 7 * h));
+  if (lstm_seq_supported(ctx, 1, t, b, h, false))
+    return lstm_fwd_seq(ctx, 1, &reverse, t, b, i, h, x, &w_ih, &w_hh, &b_ih, &b_hh, &h0, &c0, &y, &gates, &c, &tanh_c);
   return lstm_fwd_body(ctx, reverse, t, b, i, h, x, w_ih, w_hh, b_ih, b_hh, h0, c0, y, gates, c, tanh_c);
 }
 
@@ -379,9 +419,36 @@ int32_t om_lstm_bilayer_fwd(om_ctx* ctx, int32_t t, int32_t b, int32_t i, int32_
   if (t < 0 || b < 0 || i < 1 || h < 1) return fail(ctx, OM_ERR_SHAPE, "LstmLayer: T %d B %d I %d H %d", t, b, i, h);
   if (t == 0 || b == 0) return OM_OK;
   ProfileScope prof(ctx, "om_lstm_layer_fwd", 2.0 * 2 * t * b * 4.0 * h * (i + h), 2.0 * 4.0 * t * b * (double)(i + 7 * h));
+  if (lstm_seq_supported(ctx, 2, t, b, h, false)) {
+    const int32_t order[2] = {0, 1};
+    return lstm_fwd_seq(ctx, 2, order, t, b, i, h, x, w_ih, w_hh, b_ih, b_hh, nullptr, nullptr, y, gates, c, tanh_c);
+  }
   return run_forked(
       ctx, [&] { return lstm_fwd_body(ctx, 0, t, b, i, h, x, w_ih[0], w_hh[0], b_ih ? b_ih[0] : nullptr, b_hh ? b_hh[0] : nullptr, nullptr, nullptr, y[0], gates[0], c[0], tanh_c[0]); },
       [&] { return lstm_fwd_body(ctx, 1, t, b, i, h, x, w_ih[1], w_hh[1], b_ih ? b_ih[1] : nullptr, b_hh ? b_hh[1] : nullptr, nullptr, nullptr, y[1], gates[1], c[1], tanh_c[1]); });
+}
+
+// hprev[t] = y[t -/+ 1], and the initial state (or zeros) at the first processed step of the forward pass.
+static void lstm_hprev(om_ctx* ctx, int32_t reverse, int32_t t, size_t bh, const float* y, const float* h0, float* hprev) {
+  const int first_t = reverse ? t - 1 : 0;
+  if (t > 1) {
+    if (reverse) cudaMemcpyAsync(hprev, y + bh, sizeof(float) * (size_t)(t - 1) * bh, cudaMemcpyDeviceToDevice, ctx->stream);
+    else cudaMemcpyAsync(hprev + bh, y, sizeof(float) * (size_t)(t - 1) * bh, cudaMemcpyDeviceToDevice, ctx->stream);
+  }
+  if (h0) cudaMemcpyAsync(hprev + (size_t)first_t * bh, h0, sizeof(float) * bh, cudaMemcpyDeviceToDevice, ctx->stream);
+  else cudaMemsetAsync(hprev + (size_t)first_t * bh, 0, sizeof(float) * bh, ctx->stream);
+}
+
+// The products over all time steps once the gate gradients dG [T*B, 4H] are complete.
+static int32_t lstm_bwd_products(om_ctx* ctx, int32_t rows, int32_t i, int32_t h, const float* dG, const float* x, const float* hprev,
+                                 const float* w_ih, float* dx, float* dw_ih, float* dw_hh, float* db_ih, float* db_hh) {
+  const int h4 = 4 * h;
+  if (dx) OM_TRY(gemm_dispatch(ctx, 0, 0, rows, i, h4, dG, h4, w_ih, i, dx, i, 0, nullptr));
+  if (dw_ih) OM_TRY(gemm_dispatch(ctx, 1, 0, h4, i, rows, dG, h4, x, i, dw_ih, i, 0, nullptr));
+  if (dw_hh) OM_TRY(gemm_dispatch(ctx, 1, 0, h4, h, rows, dG, h4, hprev, h, dw_hh, h, 0, nullptr));
+  if (db_ih) OM_TRY(colsum_ld(ctx, dG, rows, h4, h4, db_ih, 0));
+  if (db_hh) OM_TRY(colsum_ld(ctx, dG, rows, h4, h4, db_hh, 0));
+  return OM_OK;
 }
 
 static int32_t lstm_bwd_body(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, int32_t i, int32_t h, const float* gy, const float* ghn,
@@ -397,14 +464,7 @@ static int32_t lstm_bwd_body(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b,
   if (st == OM_OK) {
     if (ghn) cudaMemcpyAsync(dh, ghn, sizeof(float) * bh, cudaMemcpyDeviceToDevice, ctx->stream);
     if (gcn) cudaMemcpyAsync(dc, gcn, sizeof(float) * bh, cudaMemcpyDeviceToDevice, ctx->stream);
-    // hprev[t] = y[t -/+ 1], and the initial state (or zeros) at the first processed step of the forward pass.
-    int first_t = reverse ? t - 1 : 0;
-    if (t > 1) {
-      if (reverse) cudaMemcpyAsync(hprev, y + bh, sizeof(float) * (size_t)(t - 1) * bh, cudaMemcpyDeviceToDevice, ctx->stream);
-      else cudaMemcpyAsync(hprev + bh, y, sizeof(float) * (size_t)(t - 1) * bh, cudaMemcpyDeviceToDevice, ctx->stream);
-    }
-    if (h0) cudaMemcpyAsync(hprev + (size_t)first_t * bh, h0, sizeof(float) * bh, cudaMemcpyDeviceToDevice, ctx->stream);
-    else cudaMemsetAsync(hprev + (size_t)first_t * bh, 0, sizeof(float) * bh, ctx->stream);
+    lstm_hprev(ctx, reverse, t, (size_t)bh, y, h0, hprev);
   }
   for (int s = 0; s < t && st == OM_OK; s++) {
     int tt = reverse ? s : t - 1 - s;
@@ -415,17 +475,61 @@ static int32_t lstm_bwd_body(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b,
                                                                              gy + (size_t)tt * bh, dh, dc, cp, b, h, dG + (size_t)tt * b * h4);
     if (s < t - 1 || dh0) st = gemm_dispatch(ctx, 0, 0, b, h, h4, dG + (size_t)tt * b * h4, h4, w_hh, h, dh, h, 0, nullptr);
   }
-  if (st == OM_OK && dx) st = gemm_dispatch(ctx, 0, 0, rows, i, h4, dG, h4, w_ih, i, dx, i, 0, nullptr);
-  if (st == OM_OK && dw_ih) st = gemm_dispatch(ctx, 1, 0, h4, i, rows, dG, h4, x, i, dw_ih, i, 0, nullptr);
-  if (st == OM_OK && dw_hh) st = gemm_dispatch(ctx, 1, 0, h4, h, rows, dG, h4, hprev, h, dw_hh, h, 0, nullptr);
-  if (st == OM_OK && db_ih) st = colsum_ld(ctx, dG, rows, h4, h4, db_ih, 0);
-  if (st == OM_OK && db_hh) st = colsum_ld(ctx, dG, rows, h4, h4, db_hh, 0);
+  if (st == OM_OK) st = lstm_bwd_products(ctx, rows, i, h, dG, x, hprev, w_ih, dx, dw_ih, dw_hh, db_ih, db_hh);
   if (st == OM_OK && dh0) cudaMemcpyAsync(dh0, dh, sizeof(float) * bh, cudaMemcpyDeviceToDevice, ctx->stream);
   if (st == OM_OK && dc0) cudaMemcpyAsync(dc0, dc, sizeof(float) * bh, cudaMemcpyDeviceToDevice, ctx->stream);
   if (dG) pool_free(ctx, dG);
   if (dh) pool_free(ctx, dh);
   if (dc) pool_free(ctx, dc);
   if (hprev) pool_free(ctx, hprev);
+  OM_TRY(st);
+  OM_LAUNCH_CHECK(ctx, "om_lstm_layer_bwd");
+  return OM_OK;
+}
+
+// The backward sweep of `dirs` directions in one cooperative launch, then each direction's products (on two streams when
+// there are two directions).
+static int32_t lstm_bwd_seq(om_ctx* ctx, int dirs, const int32_t* reverse, int32_t t, int32_t b, int32_t i, int32_t h,
+                            const float* const* gy, const float* const* ghn, const float* const* gcn, const float* x,
+                            const float* const* y, const float* const* w_ih, const float* const* w_hh, const float* const* h0,
+                            const float* const* c0, const float* const* gates, const float* const* c, const float* const* tanh_c,
+                            float* const* dx, float* const* dw_ih, float* const* dw_hh, float* const* db_ih, float* const* db_hh,
+                            float* const* dh0, float* const* dc0) {
+  const int h4 = 4 * h, rows = t * b;
+  const size_t bh = (size_t)b * h;
+  float* dG[2] = {nullptr, nullptr};
+  float* hprev[2] = {nullptr, nullptr};
+  LstmSeqBwdDir d[2];
+  int32_t st = OM_OK;
+  for (int k = 0; k < dirs && st == OM_OK; k++) {
+    st = pool_alloc(ctx, sizeof(float) * (size_t)rows * h4, false, (void**)&dG[k]);
+    if (st == OM_OK) st = pool_alloc(ctx, sizeof(float) * (size_t)rows * h, false, (void**)&hprev[k]);
+    if (st != OM_OK) break;
+    lstm_hprev(ctx, reverse[k], t, bh, y[k], h0 ? h0[k] : nullptr, hprev[k]);
+    d[k].gates = gates[k];
+    d[k].tanh_c = tanh_c[k];
+    d[k].c = c[k];
+    d[k].c0 = c0 ? c0[k] : nullptr;
+    d[k].gy = gy[k];
+    d[k].ghn = ghn ? ghn[k] : nullptr;
+    d[k].gcn = gcn ? gcn[k] : nullptr;
+    d[k].w_hh = w_hh[k];
+    d[k].dG = dG[k];
+    d[k].dh0 = dh0 ? dh0[k] : nullptr;
+    d[k].dc0 = dc0 ? dc0[k] : nullptr;
+    d[k].counter = nullptr;
+    d[k].reverse = reverse[k];
+  }
+  if (st == OM_OK) st = lstm_seq_bwd(ctx, dirs, t, b, h, d);
+  auto products = [&](int k) {
+    return lstm_bwd_products(ctx, rows, i, h, dG[k], x, hprev[k], w_ih[k], dx ? dx[k] : nullptr, dw_ih ? dw_ih[k] : nullptr,
+                             dw_hh ? dw_hh[k] : nullptr, db_ih ? db_ih[k] : nullptr, db_hh ? db_hh[k] : nullptr);
+  };
+  if (st == OM_OK) st = dirs == 2 ? run_forked(ctx, [&] { return products(0); }, [&] { return products(1); }) : products(0);
+  for (int k = 0; k < 2; k++) {
+    if (dG[k]) pool_free(ctx, dG[k]);
+    if (hprev[k]) pool_free(ctx, hprev[k]);
+  }
   OM_TRY(st);
   OM_LAUNCH_CHECK(ctx, "om_lstm_layer_bwd");
   return OM_OK;
@@ -440,6 +544,9 @@ int32_t om_lstm_layer_bwd(om_ctx* ctx, int32_t reverse, int32_t t, int32_t b, in
   if (t < 0 || b < 0 || i < 1 || h < 1) return fail(ctx, OM_ERR_SHAPE, "LstmBackward: T %d B %d I %d H %d", t, b, i, h);
   if (t == 0 || b == 0) return OM_OK;
   ProfileScope prof(ctx, "om_lstm_layer_bwd", 4.0 * t * b * 4.0 * h * (i + h), 4.0 * t * b * (double)(2 * i + 12 * h));
+  if (lstm_seq_supported(ctx, 1, t, b, h, true))
+    return lstm_bwd_seq(ctx, 1, &reverse, t, b, i, h, &gy, &ghn, &gcn, x, &y, &w_ih, &w_hh, &h0, &c0, &gates, &c, &tanh_c, &dx, &dw_ih, &dw_hh,
+                        &db_ih, &db_hh, &dh0, &dc0);
   return lstm_bwd_body(ctx, reverse, t, b, i, h, gy, ghn, gcn, x, y, w_ih, w_hh, h0, c0, gates, c, tanh_c, dx, dw_ih, dw_hh, db_ih, db_hh,
                        dh0, dc0);
 }
@@ -452,6 +559,11 @@ int32_t om_lstm_bilayer_bwd(om_ctx* ctx, int32_t t, int32_t b, int32_t i, int32_
   if (t < 0 || b < 0 || i < 1 || h < 1) return fail(ctx, OM_ERR_SHAPE, "LstmBackward: T %d B %d I %d H %d", t, b, i, h);
   if (t == 0 || b == 0) return OM_OK;
   ProfileScope prof(ctx, "om_lstm_layer_bwd", 2.0 * 4.0 * t * b * 4.0 * h * (i + h), 2.0 * 4.0 * t * b * (double)(2 * i + 12 * h));
+  if (lstm_seq_supported(ctx, 2, t, b, h, true)) {
+    const int32_t order[2] = {0, 1};
+    return lstm_bwd_seq(ctx, 2, order, t, b, i, h, gy, nullptr, nullptr, x, y, w_ih, w_hh, nullptr, nullptr, gates, c, tanh_c, dx, dw_ih, dw_hh,
+                        db_ih, db_hh, nullptr, nullptr);
+  }
   auto dir = [&](int d) {
     return lstm_bwd_body(ctx, d, t, b, i, h, gy[d], nullptr, nullptr, x, y[d], w_ih[d], w_hh[d], nullptr, nullptr, gates[d], c[d], tanh_c[d],
                          dx ? dx[d] : nullptr, dw_ih ? dw_ih[d] : nullptr, dw_hh ? dw_hh[d] : nullptr, db_ih ? db_ih[d] : nullptr,

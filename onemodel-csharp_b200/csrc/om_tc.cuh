@@ -123,4 +123,22 @@ static inline EncodeTiledFn encode_fn() {
 }
 
 
+// Adds bias[col0 .. col0 + 31] to the 32 accumulator columns a lane holds (every lane of the warp the same 32 values).
+__device__ __forceinline__ void add_bias32(uint32_t (&r)[32], const float* __restrict__ bias, int col0, int n) {
+  if (col0 + 32 <= n && (reinterpret_cast<uintptr_t>(bias + col0) & 15) == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      const float4 b = __ldg(reinterpret_cast<const float4*>(bias + col0 + j));
+      r[j] = __float_as_uint(__uint_as_float(r[j]) + b.x);
+      r[j + 1] = __float_as_uint(__uint_as_float(r[j + 1]) + b.y);
+      r[j + 2] = __float_as_uint(__uint_as_float(r[j + 2]) + b.z);
+      r[j + 3] = __float_as_uint(__uint_as_float(r[j + 3]) + b.w);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; j++)
+      if (col0 + j < n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(bias + col0 + j));
+  }
+}
+
 }  // namespace om

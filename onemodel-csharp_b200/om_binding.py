@@ -14,7 +14,7 @@ KERNEL_LIB = os.path.join(_HERE, "libonemodel_b200.so")
 HOST_LIB = os.path.join(_HERE, "libonemodel_b200_host.so")
 
 OM_F32, OM_I32, OM_I64 = 0, 1, 2
-OM_TF32, OM_BF16_OPERANDS, OM_CHECKED, OM_PAIR_TILES = 1, 2, 4, 8
+OM_TF32, OM_BF16_OPERANDS, OM_CHECKED, OM_PAIR_TILES, OM_TWO_STREAMS, OM_SEQ_KERNELS, OM_OVERLAP_LAUNCHES = 1, 2, 4, 8, 16, 32, 64
 _NP2OM = {np.dtype("float32"): OM_F32, np.dtype("int32"): OM_I32, np.dtype("int64"): OM_I64}
 _OM2NP = {OM_F32: np.float32, OM_I32: np.int32, OM_I64: np.int64}
 

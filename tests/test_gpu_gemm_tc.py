@@ -180,3 +180,29 @@ def test_tf32_matmul_on_cta_pairs(ctx, oracle_built, ta, tb, m, n, k):
         assert scaled_diff(got, single) <= 2e-5
     finally:
         ctx.set_flags(0)
+
+
+@pytest.mark.parametrize("rows,inf,outf", [(8192, 384, 1536), (2048, 1536, 384), (1229, 384, 30524), (700, 100, 60)])
+def test_linear_backward_on_two_streams_gives_the_same_bits(ctx, rows, inf, outf):
+    """OM_TWO_STREAMS: the input gradient and the weight/bias gradients of om_linear_bwd run on two streams of the
+    context; every kernel is the same and writes its own outputs, so the results equal the one-stream call bit for bit,
+    call after call (the auxiliary stream takes its scratch from its own pool)."""
+    r = np.random.default_rng(rows + outf)
+    g, x, w = (r.standard_normal(s).astype(np.float32) for s in [(rows, outf), (rows, inf), (outf, inf)])
+    G, X, W = ctx.to_device(g), ctx.to_device(x), ctx.to_device(w)
+
+    def run_once(flags):
+        ctx.set_flags(flags)
+        DX, DW, DB = ctx.empty((rows, inf)), ctx.empty((outf, inf)), ctx.empty((outf,))
+        for _ in range(3):
+            ctx.call("om_linear_bwd", ctx.handle, G.ptr, X.ptr, W.ptr, i32(rows), i32(inf), i32(outf), DX.ptr, DW.ptr, DB.ptr, i32(0))
+        ctx.sync()
+        return DX.numpy(), DW.numpy(), DB.numpy()
+
+    try:
+        one = run_once(omb.OM_TF32)
+        two = run_once(omb.OM_TF32 | omb.OM_TWO_STREAMS)
+        for a, b in zip(one, two):
+            assert a.tobytes() == b.tobytes()
+    finally:
+        ctx.set_flags(0)

@@ -304,6 +304,47 @@ def test_bidirectional_lstm_on_two_streams_equals_two_layers(ctx, B, tf32):
         ctx.set_flags(0)
 
 
+@pytest.mark.parametrize("t,b,i,h", [(12, 6, 20, 16), (64, 64, 256, 256), (5, 70, 24, 32), (3, 300, 16, 16), (2, 1, 4, 48)])
+@pytest.mark.parametrize("fused", [False, True])
+def test_whole_sequence_lstm_kernels(ctx, B, t, b, i, h, fused):
+    """OM_SEQ_KERNELS: all time steps of a layer (or of both directions) in one cooperative launch, forward and backward,
+    against the step-by-step paths (fp32 and TF32). A batch above 256 rows runs the sequence kernel forward and the
+    step-by-step path backward."""
+    import om_binding as omb
+    r = np.random.default_rng(t * 100 + b)
+    xs = r.standard_normal((t, b, i)).astype(np.float32)
+    ws = []
+    for d in range(2):
+        ws += [(r.standard_normal((4 * h, i)) * 0.3).astype(np.float32), (r.standard_normal((4 * h, h)) * 0.2).astype(np.float32),
+               (r.standard_normal(4 * h) * 0.1).astype(np.float32), (r.standard_normal(4 * h) * 0.1).astype(np.float32)]
+    proj = r.standard_normal((t, b, 2 * h)).astype(np.float32)
+
+    def run(flags):
+        ctx.set_flags(flags)
+        x = B.tensor(xs, True)
+        w = [B.tensor(a, True) for a in ws]
+        if fused:
+            y = omb.call("lstm_bidirectional", [x] + w)
+        else:
+            y = B.concat([B.lstm_layer(x, w[0], w[1], w[2], w[3], False), B.lstm_layer(x, w[4], w[5], w[6], w[7], True)], 2)
+        B.backward(B.sum(B.mul(y, B.tensor(proj))))
+        return [y.numpy(), B.grad(x)] + [B.grad(p) for p in w]
+
+    try:
+        want = run(0)
+        step = run(omb.OM_TF32)
+        got = run(omb.OM_TF32 | omb.OM_SEQ_KERNELS)
+        again = run(omb.OM_TF32 | omb.OM_SEQ_KERNELS)
+        for k, (p, q0, q, q2) in enumerate(zip(want, step, got, again)):
+            # Under OM_TF32 the input products (and the x / W_ih gradients) run on the tensor pipe on both fast paths, and the
+            # rounding compounds over the time steps; the sequence kernels keep the recurrent products in fp32, so they must
+            # be at least as close to the fp32 path as the step-by-step fast path is (with a floor for the short cases).
+            assert scaled_diff(q, p) <= max(2e-3, 1.25 * scaled_diff(q0, p)), k
+            assert np.array_equal(q, q2), k   # run to run the same bits
+    finally:
+        ctx.set_flags(0)
+
+
 def test_training_cnn_fixture(B):
     fx = load_fixture("training", "cnn")
     losses, norms, params, rs = models.train_cnn(B, fx)

@@ -107,6 +107,25 @@ def test_full_size_encoder_step_is_deterministic_and_graph_equals_eager(ctx, tf3
         ctx.set_flags(0)
 
 
+def test_scheduling_flags_do_not_change_the_bits(ctx):
+    """Config 3 at full size with overlapped launches (programmatic dependent launch), the two-stream linear backward and
+    both together, eager and replayed from a captured graph: scheduling only, so the losses and every parameter after
+    four steps equal the plain run bit for bit."""
+    ctx.make_current()
+    try:
+        ctx.set_flags(omb.OM_TF32)
+        la, pa = _run_c3(4, 2, True)
+        for extra in (omb.OM_OVERLAP_LAUNCHES, omb.OM_TWO_STREAMS, omb.OM_OVERLAP_LAUNCHES | omb.OM_TWO_STREAMS):
+            ctx.set_flags(omb.OM_TF32 | extra)
+            for graph_at in (None, 2):
+                lb, pb = _run_c3(4, graph_at, True)
+                assert np.array_equal(la, lb), (extra, graph_at)
+                for a, b in zip(pa, pb):
+                    assert np.array_equal(a, b), (extra, graph_at)
+    finally:
+        ctx.set_flags(0)
+
+
 def test_cnn_config_small(ctx, configs):
     """Config 2 at reduced size (conv + batch norm + ReLU x 4 with the strided stages, global average pool, linear; SGD
     momentum 0.9): per-parameter gradients after step 1 and the loss curve over 8 steps against the CPU path."""
