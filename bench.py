@@ -228,6 +228,8 @@ def main():
     W, K = max(3, args.warmup), max(1, args.steps)
     flags = 0 if args.fp32 else omb.OM_TF32
     flags |= args.ctx_flags
+    if kind == "crnn" and not args.fp32:
+        flags |= omb.OM_SEQ_KERNELS   # the LSTM layers' time steps in one cooperative launch each
     ctx = omb.Context(local_rank, flags)
     tr = omb.Trainer(kind, cfg, lr=lr, weight_decay=WEIGHT_DECAY[kind], seed=0)
     batch = cfg[0]

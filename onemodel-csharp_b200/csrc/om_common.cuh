@@ -51,6 +51,9 @@ struct om_ctx {
   cudaStream_t aux_stream = nullptr;
   cudaEvent_t fork_event = nullptr, join_event = nullptr;
   om::Pool pool_aux;
+  // Arrival counters of kernels whose last CTA finishes a reduction (column sums): one array per stream of the context,
+  // zero between launches (the finishing CTA resets its counter).
+  unsigned* arrival[2] = {nullptr, nullptr};
   bool aux_active = false;
   bool profiling = false;
   bool capturing = false;
@@ -105,6 +108,8 @@ struct ProfileScope {
     int32_t _s = (expr);             \
     if (_s != OM_OK) return _s;      \
   } while (0)
+
+constexpr int kArrivalSlots = 4096;
 
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

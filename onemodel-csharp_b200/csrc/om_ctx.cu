@@ -200,6 +200,14 @@ int32_t om_ctx_create(int32_t device, uint32_t flags, om_ctx** out) {
   }
   memset(ctx->status_host, 0, 64);
   cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0);
+  for (int k = 0; k < 2; k++) {
+    if ((e = cudaMalloc((void**)&ctx->arrival[k], kArrivalSlots * sizeof(unsigned))) == cudaSuccess)
+      e = cudaMemset(ctx->arrival[k], 0, kArrivalSlots * sizeof(unsigned));
+    if (e != cudaSuccess) {
+      om_ctx_destroy(ctx);
+      return check_cuda(nullptr, e, "arrival counters");
+    }
+  }
   *out = ctx;
   return OM_OK;
 }
@@ -229,7 +237,9 @@ int32_t om_ctx_destroy(om_ctx* ctx) {
       cudaEventDestroy(pr.second);
     }
   for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
-  cudaFreeHost(ctx->status_host);
+  for (int k = 0; k < 2; k++)
+    if (ctx->arrival[k]) cudaFree(ctx->arrival[k]);
+  if (ctx->status_host) cudaFreeHost(ctx->status_host);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return OM_OK;

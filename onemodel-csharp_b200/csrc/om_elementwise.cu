@@ -288,13 +288,37 @@ constexpr int kColsumRowsPerChunk = 512;
 
 constexpr int kColsumLanes = 32;
 
+// Stage 2 inside stage 1: the CTA that arrives last for its 32 columns (all chunks' partial sums are then in memory)
+// adds them in increasing chunk order, exactly as colsum_stage2_kernel does, and resets the arrival counter for the next
+// launch. Which CTA arrives last does not matter for the result. `tid` is the thread's linear index in the CTA.
+__device__ __forceinline__ void colsum_finish(const double* __restrict__ partial, unsigned* __restrict__ arrival, float* __restrict__ out,
+                                              int accumulate, int32_t cols, int tid, int* is_last) {
+  __syncthreads();
+  if (tid == 0) *is_last = atomicAdd(&arrival[blockIdx.x], 1u) == gridDim.y - 1;
+  __syncthreads();
+  if (!*is_last) return;
+  __threadfence();
+  if (tid < 32) {
+    const int c = blockIdx.x * 32 + tid;
+    if (c < cols) {
+      double t = 0.0;
+      for (unsigned ch = 0; ch < gridDim.y; ch++) t += __ldcg(partial + (int64_t)ch * cols + c);
+      const float r = (float)t;
+      out[c] = accumulate ? out[c] + r : r;
+    }
+  }
+  if (tid == 0) arrival[blockIdx.x] = 0u;
+}
+
 // Stage 1 of a column sum over g[rows, cols]: CTA (bx, by) owns 32 columns and one chunk of kColsumRowsPerChunk rows.
 // 32 row-lanes per column accumulate in double over rows lane, lane+32, ...; the 32 lane sums are combined in lane
 // order. partial[chunk, col] is written in double.
 __global__ void __launch_bounds__(1024)
-colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial) {
+colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial,
+                     unsigned* __restrict__ arrival, float* __restrict__ out, int accumulate) {
   pdl_enter();
   __shared__ double sm[kColsumLanes][33];
+  __shared__ int is_last;
   int col = blockIdx.x * 32 + threadIdx.x;
   int r0 = blockIdx.y * kColsumRowsPerChunk;
   int r1 = min(rows, r0 + kColsumRowsPerChunk);
@@ -309,16 +333,20 @@ colsum_stage1_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, in
 #pragma unroll
     for (int l = 0; l < kColsumLanes; l++) t += sm[l][threadIdx.x];
     partial[(int64_t)blockIdx.y * cols + col] = t;
+    __threadfence();
   }
+  if (arrival != nullptr) colsum_finish(partial, arrival, out, accumulate, cols, threadIdx.y * 32 + threadIdx.x, &is_last);
 }
 
 // Stage 1 for rows that are 16-byte aligned (ld a multiple of four, aligned base): the same sums in the same order as
 // colsum_stage1_kernel, but each thread owns four adjacent columns (one 16-byte load per row) and has all of its 16
 // rows in flight at once. A CTA is 8 column groups x 32 row lanes and covers 32 columns of one chunk.
 __global__ void __launch_bounds__(256)
-colsum_stage1_vec4_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial) {
+colsum_stage1_vec4_kernel(const float* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial,
+                          unsigned* __restrict__ arrival, float* __restrict__ out, int accumulate) {
   pdl_enter();
   __shared__ double sm[kColsumLanes][33];
+  __shared__ int is_last;
   constexpr int PER_LANE = kColsumRowsPerChunk / kColsumLanes;
   const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
   const int col = blockIdx.x * 32 + tx * 4;
@@ -355,8 +383,10 @@ colsum_stage1_vec4_kernel(const float* __restrict__ g, int32_t rows, int32_t col
 #pragma unroll
       for (int l = 0; l < kColsumLanes; l++) t += sm[l][threadIdx.x];
       partial[(int64_t)blockIdx.y * cols + c] = t;
+      __threadfence();
     }
   }
+  if (arrival != nullptr) colsum_finish(partial, arrival, out, accumulate, cols, threadIdx.x, &is_last);
 }
 
 __global__ void colsum_stage2_kernel(const double* __restrict__ partial, int32_t chunks, int32_t cols,
@@ -481,11 +511,15 @@ int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64
   double* partial = nullptr;
   OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&partial));
   dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)chunks);
+  // One launch when the context's arrival counters cover the column blocks: the last CTA of each block of 32 columns
+  // does stage 2. Wider matrices take the two launches.
+  unsigned* arrival = grid.x <= (unsigned)kArrivalSlots ? ctx->arrival[ctx->aux_active ? 1 : 0] : nullptr;
   if ((ld & 3) == 0 && aligned16(g))
-    launch_chained(ctx, colsum_stage1_vec4_kernel, grid, 256, 0, g, rows, cols, ld, partial);
+    launch_chained(ctx, colsum_stage1_vec4_kernel, grid, 256, 0, g, rows, cols, ld, partial, arrival, out, accumulate);
   else
-    launch_chained(ctx, colsum_stage1_kernel, grid, dim3(32, kColsumLanes), 0, g, rows, cols, ld, partial);
-  launch_chained(ctx, colsum_stage2_kernel, (unsigned)ceil_div(cols, 128), 128, 0, partial, chunks, cols, out, accumulate);
+    launch_chained(ctx, colsum_stage1_kernel, grid, dim3(32, kColsumLanes), 0, g, rows, cols, ld, partial, arrival, out, accumulate);
+  if (arrival == nullptr)
+    launch_chained(ctx, colsum_stage2_kernel, (unsigned)ceil_div(cols, 128), 128, 0, partial, chunks, cols, out, accumulate);
   pool_free(ctx, partial);
   OM_LAUNCH_CHECK(ctx, "om_colsum");
   return OM_OK;

@@ -401,11 +401,12 @@ int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const fl
 
   const int tiles = (int)(ceil_div(m, BM) * ceil_div(n, BN));
   const int k_blocks = (int)ceil_div(k, BK);
-  // Fixed split of k: enough slices to give every SM a tile, each slice at least 8 k-blocks deep. The split count is
+  // Fixed split of k: slices for one full round of CTAs, each slice at least 8 k-blocks deep. The split count is
   // a function of the shape only, so results do not depend on the device or on timing.
   int splits = 1;
   if (batch == 1 && tiles < 148 && k_blocks >= 16) {
-    splits = (int)std::min<int64_t>(ceil_div(148, tiles), k_blocks / 8);
+    // As many slices as still run in one round of two CTAs per SM on a 148-SM device (a constant, not the device's count).
+    splits = (int)std::min<int64_t>(kSplitSlots / tiles, k_blocks / 8);
     if (splits < 1) splits = 1;
     if (splits > 32) splits = 32;
   }

@@ -310,7 +310,10 @@ bool gemm_pair_supported(om_ctx* ctx, int m, int n, int k) {
   if (m < 256 || n < 128 || k < 64) return false;
   if (ctx->flags & OM_PAIR_TILES) return true;
   const int64_t tiles = ceil_div(m, P_BM) * ceil_div(n, 128);
-  return tiles >= 4 * (int64_t)ctx->sm_count && m >= 1024 && n >= 256;
+  if (tiles >= 4 * (int64_t)148 && m >= 1024 && n >= 256) return true;
+  // Deep-k products with few tiles (the weight gradients of a wide layer): measured 1.3-1.4x at 768-wide layers, about
+  // even at 384.
+  return tiles < 148 && k >= 128 * P_BK && m >= 512 && m % 256 == 0 && n >= 512 && n % 256 == 0;
 }
 
 template <int BN>
@@ -343,7 +346,7 @@ int32_t gemm_pair(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float*
   // fewer operand bytes per output but leave small products with too few CTAs.
   int bn = 128;
   {
-    const int64_t slots = 2 * (int64_t)ctx->sm_count;
+    const int64_t slots = kSplitSlots;
     int64_t best = 0;
     for (int cand : {128, 192, 256}) {
       const int64_t ctas_c = 2 * ceil_div(m, 2 * P_BM) * ceil_div(n, cand);
@@ -353,6 +356,9 @@ int32_t gemm_pair(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float*
         bn = cand;
       }
     }
+    // Few tiles and a deep k (weight gradients): k is split to fill the round anyway, so take the widest tile that
+    // divides the width (fewest operand bytes per output).
+    if (2 * ceil_div(m, 2 * P_BM) * ceil_div(n, 128) < 148 && k >= 64 * P_BK) bn = n % 256 == 0 ? 256 : n % 192 == 0 ? 192 : 128;
   }
   CUtensorMap map_a, map_b;
   bool ok = a_mn ? pair_map(&map_a, A, m, k, lda, P_BK, true) : pair_map(&map_a, A, k, m, lda, P_BM, false);
@@ -362,7 +368,7 @@ int32_t gemm_pair(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float*
   const int ctas = 2 * pairs * n_tiles, k_blocks = (int)ceil_div(k, P_BK);
   int splits = 1;
   if (ctas < 148 && k_blocks >= 16) {
-    splits = (int)std::min<int64_t>(ceil_div(148, ctas), k_blocks / 8);
+    splits = (int)std::min<int64_t>(kSplitSlots / ctas, k_blocks / 8);
     if (splits < 1) splits = 1;
     if (splits > 32) splits = 32;
   }

@@ -7,6 +7,7 @@
 
 namespace om {
 
+constexpr int kSplitSlots = 296;   // CTAs of one round at two per SM on 148 SMs: the k-split target of the product kernels
 constexpr long long WAIT_CYCLES = 2000000000LL;   // about one second of SM clock: the bound of every mbarrier wait
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------------------
