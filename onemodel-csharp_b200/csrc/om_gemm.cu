@@ -5,6 +5,7 @@
 
 namespace om {
 
+void splitk_reduce_launch(om_ctx* ctx, const float* part, int splits, int64_t mn, int n, int64_t ldc, const float* bias, float* out, int accumulate);
 int32_t gemm_simt(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, int64_t sA,
                   const float* B, int ldb, int64_t sB, float* C, int ldc, int64_t sC, int batch, int acc);
 bool gemm_tc_supported(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B,
@@ -50,6 +51,28 @@ int32_t gemm_dispatch(om_ctx* ctx, int ta, int tb, int m, int n, int k, const fl
   if (m == 0 || n == 0) return OM_OK;
   if ((ctx->flags & (OM_TF32 | OM_BF16_OPERANDS)) && gemm_tc_supported(ctx, ta, tb, m, n, k, A, lda, B, ldb, C, ldc))
     return gemm_tc(ctx, ta, tb, m, n, k, A, lda, B, ldb, C, ldc, acc, bias);
+  // A deep product with a small result that the tensor-pipe kernel cannot take (a pitch that is not a multiple of 16
+  // bytes, e.g. the weight gradient of a 97-class output layer) would run as a handful of CTAs each walking all of k.
+  // In the fast tier (where the one-accumulator order of the exact tier is not promised) k is cut into a fixed number
+  // of equal slices computed as a batch and added in slice order.
+  if ((ctx->flags & OM_TF32) && k >= 1024 && (int64_t)m * n <= 262144) {
+    int slices = 0;
+    for (int cand : {32, 16, 8, 4, 2})
+      if (k % cand == 0 && k / cand >= 128) {
+        slices = cand;
+        break;
+      }
+    if (slices > 0) {
+      const int ks = k / slices;
+      float* part = nullptr;
+      OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)slices * m * n, false, (void**)&part));
+      int32_t st = gemm_simt(ctx, ta, tb, m, n, ks, A, lda, ta ? (long long)ks * lda : ks, B, ldb, tb ? ks : (long long)ks * ldb, part, n,
+                             (long long)m * n, slices, 0);
+      if (st == OM_OK) splitk_reduce_launch(ctx, part, slices, (int64_t)m * n, n, ldc, bias, C, acc);
+      pool_free(ctx, part);
+      return st;
+    }
+  }
   OM_TRY(gemm_simt(ctx, ta, tb, m, n, k, A, lda, 0, B, ldb, 0, C, ldc, 0, 1, acc));
   if (bias) {
     add_bias_rows_kernel<<<grid_for(ctx, ((int64_t)m * n + 3) / 4, 256), 256, 0, ctx->stream>>>(C, bias, m, n, ldc);

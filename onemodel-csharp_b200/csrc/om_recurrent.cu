@@ -150,8 +150,10 @@ __device__ __forceinline__ bool ctc_can_skip(const int32_t* tgt, int s) { return
 constexpr int kCtcThreads = 128;
 
 // alpha for sequence b into alpha[len, ext]; returns the negative log-likelihood (every thread gets it).
+// `rows` (2 * ext doubles of shared memory, or null) keeps the last two rows on chip, so that the step-to-step chain does
+// not wait on a round trip through L2.
 __device__ double ctc_alpha(const float* __restrict__ lp, int batch, int classes, int b, int len, const int32_t* tgt, int tl,
-                            int blank, double* __restrict__ alpha, double* sh_nll) {
+                            int blank, double* __restrict__ alpha, double* sh_nll, double* rows) {
   const int ext = 2 * tl + 1;
   if (len == 0) return tl == 0 ? 0.0 : INFINITY;
   if (tl > len) return INFINITY;  // more labels than frames: no alignment exists (and the scratch is sized for ext <= 2T+1)
@@ -161,13 +163,15 @@ __device__ double ctc_alpha(const float* __restrict__ lp, int batch, int classes
       if (t == 0) {
         a = s <= 1 ? 0.0 : -INFINITY;
       } else {
-        const double* prev = alpha + (size_t)(t - 1) * ext;
+        const double* prev = rows ? rows + ((t - 1) & 1) * ext : alpha + (size_t)(t - 1) * ext;
         a = prev[s];
         if (s >= 1) a = ctc_logadd(a, prev[s - 1]);
         if (ctc_can_skip(tgt, s)) a = ctc_logadd(a, prev[s - 2]);
       }
       double e = (double)lp[((size_t)t * batch + b) * classes + ctc_label(tgt, blank, s)];
-      alpha[(size_t)t * ext + s] = (isinf(a) && a < 0) ? -INFINITY : a + e;
+      const double v = (isinf(a) && a < 0) ? -INFINITY : a + e;
+      alpha[(size_t)t * ext + s] = v;
+      if (rows) rows[(t & 1) * ext + s] = v;
     }
     __syncthreads();
   }
@@ -183,7 +187,7 @@ __device__ double ctc_alpha(const float* __restrict__ lp, int batch, int classes
 __global__ void __launch_bounds__(kCtcThreads)
 ctc_loss_kernel(const float* __restrict__ lp, int steps, int batch, int classes, const int32_t* __restrict__ targets,
                 const int32_t* __restrict__ tlen, const int32_t* __restrict__ ilen, int blank, int zero_inf, int max_ext,
-                double* __restrict__ alpha_all, float* __restrict__ nll_out, double* __restrict__ per, int32_t* status) {
+                double* __restrict__ alpha_all, float* __restrict__ nll_out, double* __restrict__ per, int32_t* status, int use_rows) {
   __shared__ double sh_nll;
   __shared__ int sh_off;
   const int b = blockIdx.x;
@@ -206,7 +210,9 @@ ctc_loss_kernel(const float* __restrict__ lp, int steps, int batch, int classes,
     }
     return;
   }
-  double nll = ctc_alpha(lp, batch, classes, b, len, tgt, tl, blank, alpha_all + (size_t)b * steps * max_ext, &sh_nll);
+  extern __shared__ double ctc_rows[];
+  double nll = ctc_alpha(lp, batch, classes, b, len, tgt, tl, blank, alpha_all + (size_t)b * steps * max_ext, &sh_nll,
+                         use_rows ? ctc_rows : nullptr);
   if (threadIdx.x == 0) {
     double v = (isinf(nll) && zero_inf) ? 0.0 : nll;
     per[b] = v;
@@ -225,7 +231,10 @@ __global__ void ctc_reduce_kernel(const double* __restrict__ per, const int32_t*
 __global__ void __launch_bounds__(kCtcThreads)
 ctc_grad_kernel(const float* __restrict__ g, const float* __restrict__ lp, int steps, int batch, int classes,
                 const int32_t* __restrict__ targets, const int32_t* __restrict__ tlen, const int32_t* __restrict__ ilen, int blank,
-                int reduction, int max_ext, double* __restrict__ alpha_all, double* __restrict__ beta_all, float* __restrict__ grad) {
+                int reduction, int max_ext, double* __restrict__ alpha_all, double* __restrict__ beta_all, float* __restrict__ grad,
+                int use_rows) {
+  extern __shared__ double ctc_rows[];
+  double* rows = use_rows ? ctc_rows : nullptr;
   __shared__ double sh_nll;
   __shared__ int sh_off;
   const int b = blockIdx.x;
@@ -243,38 +252,42 @@ ctc_grad_kernel(const float* __restrict__ g, const float* __restrict__ lp, int s
     for (int c = threadIdx.x; c < classes; c += kCtcThreads) grad[((size_t)t * batch + b) * classes + c] = 0.f;
   double* alpha = alpha_all + (size_t)b * steps * max_ext;
   double* beta = beta_all + (size_t)b * steps * max_ext;
-  double nll = ctc_alpha(lp, batch, classes, b, len, tgt, tl, blank, alpha, &sh_nll);
+  double nll = ctc_alpha(lp, batch, classes, b, len, tgt, tl, blank, alpha, &sh_nll, rows);
   if (len == 0 || isinf(nll)) return;
   double scale = reduction == 0 ? (double)g[b] : (double)g[0];
   if (reduction == 1) scale = scale / (double)max(1, tl) / (double)batch;
+  // beta for all steps first (a chain over t) ...
   for (int t = len - 1; t >= 0; t--) {
     for (int s = threadIdx.x; s < ext; s += kCtcThreads) {
       double v;
       if (t == len - 1) {
         v = s >= ext - 2 ? 0.0 : -INFINITY;
       } else {
-        const double* nxt = beta + (size_t)(t + 1) * ext;
+        const double* nxt = rows ? rows + ((t + 1) & 1) * ext : beta + (size_t)(t + 1) * ext;
         v = nxt[s];
         if (s + 1 < ext) v = ctc_logadd(v, nxt[s + 1]);
         if (s + 2 < ext && ctc_can_skip(tgt, s + 2)) v = ctc_logadd(v, nxt[s + 2]);
       }
       double e = (double)lp[((size_t)t * batch + b) * classes + ctc_label(tgt, blank, s)];
-      beta[(size_t)t * ext + s] = (isinf(v) && v < 0) ? -INFINITY : v + e;
+      const double w = (isinf(v) && v < 0) ? -INFINITY : v + e;
+      beta[(size_t)t * ext + s] = w;
+      if (rows) rows[(t & 1) * ext + s] = w;
     }
     __syncthreads();
-    // One thread per class walks the extended labels in increasing s (LogAdd is not associative).
-    for (int c = threadIdx.x; c < classes; c += kCtcThreads) {
-      double acc = -INFINITY;
-      for (int s = 0; s < ext; s++) {
-        if (ctc_label(tgt, blank, s) != c) continue;
-        double ab = alpha[(size_t)t * ext + s] + beta[(size_t)t * ext + s];
-        if (!(isinf(ab) && ab < 0) && !(ab != ab)) acc = ctc_logadd(acc, ab);
-      }
-      if (isinf(acc) && acc < 0) continue;
-      double l = (double)lp[((size_t)t * batch + b) * classes + c];
-      grad[((size_t)t * batch + b) * classes + c] = (float)(-scale * ctc_exp(acc - l + nll));
+  }
+  // ... then the gradient of every (step, class) independently: the walk over the extended labels of one class goes in
+  // increasing s (LogAdd is not associative), but nothing orders one (step, class) against another.
+  for (int item = threadIdx.x; item < len * classes; item += kCtcThreads) {
+    const int t = item / classes, c = item % classes;
+    double acc = -INFINITY;
+    for (int s = 0; s < ext; s++) {
+      if (ctc_label(tgt, blank, s) != c) continue;
+      double ab = alpha[(size_t)t * ext + s] + beta[(size_t)t * ext + s];
+      if (!(isinf(ab) && ab < 0) && !(ab != ab)) acc = ctc_logadd(acc, ab);
     }
-    __syncthreads();
+    if (isinf(acc) && acc < 0) continue;
+    double l = (double)lp[((size_t)t * batch + b) * classes + c];
+    grad[((size_t)t * batch + b) * classes + c] = (float)(-scale * ctc_exp(acc - l + nll));
   }
 }
 
@@ -593,8 +606,10 @@ int32_t om_ctc_loss(om_ctx* ctx, const float* lp, int32_t t, int32_t b, int32_t 
   OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)b * (t > 0 ? t : 1) * max_ext, false, (void**)&alpha));
   int32_t st = pool_alloc(ctx, sizeof(double) * b, false, (void**)&per);
   if (st == OM_OK) {
-    ctc_loss_kernel<<<b, kCtcThreads, 0, ctx->stream>>>(lp, t, b, c, targets, target_lengths, input_lengths, blank, zero_infinity,
-                                                        max_ext, alpha, nll, per, ctx->status_dev);
+    const size_t rows_bytes = 2 * sizeof(double) * (size_t)max_ext;   // the last two alpha rows on chip when they fit
+    const int use_rows = rows_bytes <= 40 * 1024;
+    ctc_loss_kernel<<<b, kCtcThreads, use_rows ? rows_bytes : 0, ctx->stream>>>(lp, t, b, c, targets, target_lengths, input_lengths, blank,
+                                                                                zero_infinity, max_ext, alpha, nll, per, ctx->status_dev, use_rows);
     if (reduction != 0 && loss) ctc_reduce_kernel<<<1, 32, 0, ctx->stream>>>(per, target_lengths, b, reduction, loss);
   }
   pool_free(ctx, alpha);
@@ -617,8 +632,12 @@ int32_t om_ctc_grad(om_ctx* ctx, const float* g, const float* lp, int32_t t, int
   double *alpha = nullptr, *beta = nullptr;
   OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)b * t * max_ext, false, (void**)&alpha));
   int32_t st = pool_alloc(ctx, sizeof(double) * (size_t)b * t * max_ext, false, (void**)&beta);
-  if (st == OM_OK)
-    ctc_grad_kernel<<<b, kCtcThreads, 0, ctx->stream>>>(g, lp, t, b, c, targets, target_lengths, input_lengths, blank, reduction, max_ext, alpha, beta, grad);
+  if (st == OM_OK) {
+    const size_t rows_bytes = 2 * sizeof(double) * (size_t)max_ext;
+    const int use_rows = rows_bytes <= 40 * 1024;
+    ctc_grad_kernel<<<b, kCtcThreads, use_rows ? rows_bytes : 0, ctx->stream>>>(g, lp, t, b, c, targets, target_lengths, input_lengths, blank,
+                                                                                reduction, max_ext, alpha, beta, grad, use_rows);
+  }
   pool_free(ctx, alpha);
   if (beta) pool_free(ctx, beta);
   OM_TRY(st);

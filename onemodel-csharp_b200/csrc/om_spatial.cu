@@ -251,6 +251,48 @@ __global__ void maxpool_bwd_kernel(PoolGeom g, const float* __restrict__ gr, con
   }
 }
 
+// Windows that tile the plane (stride equal to the kernel, no padding): every input belongs to at most one window, so
+// dx[e] is g of that window when its saved index is e, else zero. 32-bit index arithmetic; a thread owns VEC adjacent
+// inputs of a row (one 16-byte store when VEC is 4: w a multiple of 4 and dx 16-byte aligned).
+template <int VEC>
+__global__ void maxpool_bwd_tiled_kernel(int h, int w, int oh, int ow, int kh, int kw, const float* __restrict__ gr,
+                                         const int32_t* __restrict__ idx, int groups, float* __restrict__ dx) {
+  const int stride = gridDim.x * blockDim.x;
+  const int wg = w / VEC;
+  for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < groups; q += stride) {
+    const int xg = q % wg, t = q / wg;
+    const int iy = t % h, pl = t / h;
+    const int oy = iy / kh;
+    const int e0 = (pl * h + iy) * w + xg * VEC;
+    float v[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; j++) v[j] = 0.f;
+    if (oy < oh) {
+      const int obase = (pl * oh + oy) * ow;
+      int last_ox = -1, last_idx = 0;
+      float last_g = 0.f;
+#pragma unroll
+      for (int j = 0; j < VEC; j++) {
+        const int ox = (xg * VEC + j) / kw;
+        if (ox < ow) {
+          if (ox != last_ox) {
+            last_ox = ox;
+            last_idx = __ldg(idx + obase + ox);
+            last_g = __ldg(gr + obase + ox);
+          }
+          if (last_idx == e0 + j) v[j] = last_g;
+        }
+      }
+    }
+    if (VEC == 4) {
+      *reinterpret_cast<float4*>(dx + e0) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; j++) dx[e0 + j] = v[j];
+    }
+  }
+}
+
 // The in-bounds window of output (oy, ox) and its divisor (PoolWindow, BackwardNn.cs:490-506).
 __device__ __forceinline__ void pool_window(const PoolGeom& g, int include_pad, int oy, int ox, int* y0, int* y1, int* x0, int* x1, int* count) {
   int ys = oy * g.sh - g.ph, xs = ox * g.sw - g.pw;
@@ -637,7 +679,13 @@ int32_t om_maxpool_bwd(om_ctx* ctx, const float* gr, const int32_t* idx, int32_t
   int64_t total = (int64_t)planes * h * w;
   if (total <= 0) return OM_OK;
   ProfileScope prof(ctx, "om_maxpool_bwd", 0, 4.0 * planes * ((double)h * w + 2.0 * oh * ow));
-  maxpool_bwd_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, gr, idx, total, dx);
+  if (kh == sh && kw == sw && ph == 0 && pw == 0 && total < (int64_t)1 << 30) {
+    if ((w & 3) == 0 && (reinterpret_cast<uintptr_t>(dx) & 15) == 0)
+      maxpool_bwd_tiled_kernel<4><<<grid_for(ctx, total / 4, 256), 256, 0, ctx->stream>>>(h, w, oh, ow, kh, kw, gr, idx, (int)(total / 4), dx);
+    else
+      maxpool_bwd_tiled_kernel<1><<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(h, w, oh, ow, kh, kw, gr, idx, (int)total, dx);
+  } else
+    maxpool_bwd_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, gr, idx, total, dx);
   OM_LAUNCH_CHECK(ctx, "om_maxpool_bwd");
   return OM_OK;
 }

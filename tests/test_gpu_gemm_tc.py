@@ -206,3 +206,27 @@ def test_linear_backward_on_two_streams_gives_the_same_bits(ctx, rows, inf, outf
             assert a.tobytes() == b.tobytes()
     finally:
         ctx.set_flags(0)
+
+
+def test_deep_product_with_an_unaligned_pitch_is_sliced_in_the_fast_tier(ctx, oracle_built):
+    """The weight gradient of a 97-class output layer: g^T [97, 4096] x [4096, 512] with g stored [4096, 97]. A pitch of 97
+    floats cannot be described to TMA, so the product runs on the fp32 FMA kernel: in the exact tier with the reference's
+    one-accumulator order (bit-exact), in the fast tier cut into equal k slices added in slice order (fp32 throughout,
+    another order: 1e-5, and the same bits from run to run)."""
+    K = oracle_built
+    r = np.random.default_rng(97)
+    m, n, k = 97, 512, 4096
+    a = r.standard_normal((k, m)).astype(np.float32)
+    b = r.standard_normal((k, n)).astype(np.float32)
+    ref = K.gemm(a, b, True, False)
+    try:
+        ctx.set_flags(0)
+        assert np.array_equal(run(ctx, 1, 0, m, n, k, a, b), ref)
+        ctx.set_flags(omb.OM_TF32)
+        got = run(ctx, 1, 0, m, n, k, a, b)
+        assert scaled_diff(got, ref) <= 1e-5
+        assert np.array_equal(got, run(ctx, 1, 0, m, n, k, a, b))
+        c0 = r.standard_normal((m, n)).astype(np.float32)
+        assert scaled_diff(run(ctx, 1, 0, m, n, k, a, b, acc=1, c0=c0), ref + c0) <= 1e-5
+    finally:
+        ctx.set_flags(0)

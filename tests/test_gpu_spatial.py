@@ -87,7 +87,8 @@ def test_conv2d_on_the_tensor_pipe(ctx, K, n, cin, h, w, cout, k, stride, pad):
         ctx.set_flags(0)
 
 
-@pytest.mark.parametrize("kh,kw,sh,sw,ph,pw", [(2, 2, 2, 2, 0, 0), (4, 1, 4, 1, 0, 0), (3, 3, 2, 2, 1, 1), (2, 1, 2, 1, 0, 0), (3, 2, 1, 1, 1, 0)])
+@pytest.mark.parametrize("kh,kw,sh,sw,ph,pw", [(2, 2, 2, 2, 0, 0), (4, 1, 4, 1, 0, 0), (3, 3, 2, 2, 1, 1), (2, 1, 2, 1, 0, 0), (3, 2, 1, 1, 1, 0),
+                                                 (3, 5, 3, 5, 0, 0)])
 def test_pooling(ctx, K, kh, kw, sh, sw, ph, pw):
     r = np.random.default_rng(kh * 10 + kw)
     x = r.standard_normal((3, 5, 16, 12)).astype(np.float32)
