@@ -89,8 +89,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();                // 0 = leader
-  const int m0 = blockIdx.x * P_BM;                       // blockIdx.x = 2 * pair + rank
-  const int n0 = blockIdx.y * BN;
+  // blockIdx.x = 2 * column tile + rank, blockIdx.y = pair of row blocks: the column tiles of one pair of row blocks are
+  // launched next to one another, so their common A rows are read from HBM once and then found in L2.
+  const int m0 = (2 * (int)blockIdx.y + (int)rank) * P_BM;
+  const int n0 = (int)(blockIdx.x >> 1) * BN;
   const int split = blockIdx.z;
   const int k_begin = split * p.k_per_split;
   const int k_end = min(p.k, k_begin + p.k_per_split);
@@ -307,7 +309,7 @@ static bool pair_map(CUtensorMap* map, const float* base, int inner, int outer, 
 // 768-wide encoder, 1.44x at 4096^3, slower on products of one or two rounds, where the larger tile leaves SMs idle);
 // OM_PAIR_TILES sends every product it can take to it.
 bool gemm_pair_supported(om_ctx* ctx, int m, int n, int k) {
-  if (m < 256 || n < 128 || k < 64) return false;
+  if (m < 256 || n < 128 || k < 64 || m > 65535 * 256) return false;
   if (ctx->flags & OM_PAIR_TILES) return true;
   const int64_t tiles = ceil_div(m, P_BM) * ceil_div(n, 128);
   if (tiles >= 4 * (int64_t)148 && m >= 1024 && n >= 256) return true;
@@ -387,7 +389,7 @@ int32_t gemm_pair(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float*
   p.tma_store = splits > 1 ? make_store_map(&map_c, workspace, n, m, n, splits, (long long)m * n, 1, 0)
                            : make_store_map(&map_c, C, n, m, ldc, 1, 0, 1, 0);
   if (!p.tma_store) map_c = map_a;
-  dim3 grid((unsigned)(2 * pairs), (unsigned)n_tiles, (unsigned)splits);
+  dim3 grid((unsigned)(2 * n_tiles), (unsigned)pairs, (unsigned)splits);
   int32_t st = bn == 256   ? launch_pair<256>(ctx, a_mn, b_mn, map_a, map_b, map_c, p, grid)
                : bn == 192 ? launch_pair<192>(ctx, a_mn, b_mn, map_a, map_b, map_c, p, grid)
                            : launch_pair<128>(ctx, a_mn, b_mn, map_a, map_b, map_c, p, grid);

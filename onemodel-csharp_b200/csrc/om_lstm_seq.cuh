@@ -13,12 +13,13 @@ struct LstmSeqFwdDir {
   float* y;              // [T, B, H]
   float* c;
   float* tanh_c;
-  unsigned* counter;     // barrier count of this direction, zero at launch
+  unsigned* counter;     // barrier counts of this direction's row groups, zero at launch
   int reverse;
 };
 struct LstmSeqFwdParams {
   LstmSeqFwdDir d[2];
   int t, b, h;
+  int passes, groups;    // a CTA covers passes x 16 batch rows; groups = row groups per direction
   int32_t* status;
 };
 
@@ -40,6 +41,7 @@ struct LstmSeqBwdDir {
 struct LstmSeqBwdParams {
   LstmSeqBwdDir d[2];
   int t, b, h;
+  int passes, groups;
   int32_t* status;
 };
 
