@@ -90,7 +90,7 @@ class ClockSampler(threading.Thread):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per gemm_tc_kernel launch, averaged over the matrix-product launches of one
 # ncu capture of this workload (profiles/tensor_pipe_kernels_c3.md gives the command and the per-shape table).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c3": 50.3e6}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c3": 50.1e6}
 WEIGHT_DECAY = {"mlp": 0.01, "mlm": 0.01, "cnn": 0.0, "crnn": 0.0}
 # Batch of the CPU sample: the full step where that takes seconds, a slice of the batch where it would take minutes
 # (samples/s does not depend on the batch for these models; the sample string says what was run).
