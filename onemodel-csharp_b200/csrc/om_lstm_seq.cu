@@ -33,8 +33,9 @@ __device__ __forceinline__ float seq_sigm(float x) { return 1.0f / (1.0f + expf(
 __device__ __forceinline__ bool seq_barrier(unsigned* counter, unsigned target, int32_t* status, int* failed, int where) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(counter, 1u);
+    // Release at device scope: the CTA's writes (ordered before this thread by the barrier above) are visible to whoever
+    // observes the count.
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
     const long long t0 = clock64();
     for (;;) {
       unsigned v;

@@ -190,7 +190,11 @@ OMH_API int32_t omh_call(const char* op, int32_t n_in, omh_tensor* const* in, in
     } else if (name == "max_pool2d") r = Ops::MaxPool2d(T(0), (int)I(0), (int)I(1), (int)I(2), (int)I(3), (int)I(4), (int)I(5));
     else if (name == "avg_pool2d") r = Ops::AvgPool2d(T(0), (int)I(0), (int)I(1), (int)I(2), (int)I(3), (int)I(4), (int)I(5), I(6) != 0);
     else if (name == "lstm_layer") r = Ops::LstmLayer(T(0), T(1), T(2), T(3), T(4), I(0) != 0);
-    else if (name == "conv_transpose2d") {
+    else if (name == "conv1d") {
+      Conv1dParams p;
+      p.stride = (int)I(0, 1); p.padLeft = (int)I(1); p.padRight = (int)I(2); p.dilation = (int)I(3, 1); p.groups = (int)I(4, 1);
+      r = Ops::Conv1d(T(0), T(1), T(2), p);
+    } else if (name == "conv_transpose2d") {
       ConvTranspose2dParams p;
       p.strideH = (int)I(0, 1); p.strideW = (int)I(1, 1); p.padH = (int)I(2); p.padW = (int)I(3); p.outPadH = (int)I(4); p.outPadW = (int)I(5);
       p.dilH = (int)I(6, 1); p.dilW = (int)I(7, 1); p.groups = (int)I(8, 1);

@@ -231,6 +231,11 @@ struct Conv2dParams {
   int strideH = 1, strideW = 1, padTop = 0, padLeft = 0, padBottom = 0, padRight = 0, dilH = 1, dilW = 1, groups = 1;
 };
 
+// Conv1dParams of the reference (Ops.Nn.cs:12-25): zero stride, dilation or groups mean 1.
+struct Conv1dParams {
+  int stride = 1, padLeft = 0, padRight = 0, dilation = 1, groups = 1;
+};
+
 struct ConvTranspose2dParams {
   int strideH = 1, strideW = 1, padH = 0, padW = 0, outPadH = 0, outPadW = 0, dilH = 1, dilW = 1, groups = 1;
 };
@@ -290,6 +295,9 @@ struct Ops {
   static Tensor Pow(const Tensor& x, float exponent);
   static Tensor Where(const Tensor& condition, const Tensor& x, const Tensor& y);
   static Tensor Gather(const Tensor& data, const Tensor& indices, int axis);
+  // 1-D cross-correlation of an NCL input with OIK weights on the 2-D kernels with a height of 1 (Ops.Layers.cs:338-402;
+  // backward BackwardNn.cs:313-321: the 2-D backward on the height-1 view).
+  static Tensor Conv1d(const Tensor& x, const Tensor& weight, const Tensor& bias, const Conv1dParams& p);
   // Transposed convolution, the adjoint of Conv2d (Ops.Spatial.cs:43-130): x [N,Cin,H,W], weight [Cin,Cout/G,KH,KW].
   static Tensor ConvTranspose2d(const Tensor& x, const Tensor& weight, const Tensor& bias, const ConvTranspose2dParams& p);
   // mode 0 nearest, 1 bilinear (Ops.Spatial.cs:148-197).

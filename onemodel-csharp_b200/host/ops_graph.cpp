@@ -169,6 +169,38 @@ static om_conv_shape AdjointShape(const Shape& xs, const Shape& ws, int oh, int 
   return s;
 }
 
+// The reference runs Conv1d on its 2-D kernels with a height of 1 and differentiates it with the 2-D backward on the
+// height-1 view; here the views are explicit (reshapes are free and differentiable) and Conv2d does the rest, so forward,
+// dx, dW and dbias are exactly those of the 2-D path.
+Tensor Ops::Conv1d(const Tensor& x, const Tensor& weight, const Tensor& bias, const Conv1dParams& p0) {
+  RequireF32(x);
+  RequireF32(weight);
+  Conv1dParams p = p0;
+  if (p.stride == 0) p.stride = 1;
+  if (p.dilation == 0) p.dilation = 1;
+  if (p.groups == 0) p.groups = 1;
+  if (x.Rank() != 3 || weight.Rank() != 3)
+    throw TensorShapeException("Conv1d needs an (N,C,L) input and (O,I,K) weights, not " + x.GetShape().ToString() + " and " +
+                               weight.GetShape().ToString() + ".");
+  if (p.groups < 1 || x.GetShape()[1] % p.groups != 0 || weight.GetShape()[0] % p.groups != 0 ||
+      weight.GetShape()[1] != x.GetShape()[1] / p.groups)
+    throw TensorShapeException("Weights " + weight.GetShape().ToString() + " do not fit input " + x.GetShape().ToString() + " with " +
+                               std::to_string(p.groups) + " groups.");
+  if (!bias.IsEmpty() && (bias.Rank() != 1 || bias.GetShape()[0] != weight.GetShape()[0]))
+    throw TensorShapeException("The bias must have shape [" + std::to_string(weight.GetShape()[0]) + "], not " + bias.GetShape().ToString() + ".");
+  const int n = x.GetShape()[0], c = x.GetShape()[1], l = x.GetShape()[2], o = weight.GetShape()[0], k = weight.GetShape()[2];
+  const long long span = (long long)p.dilation * (k - 1) + 1;
+  const long long outw = p.stride >= 1 ? ((long long)l + p.padLeft + p.padRight - span) / p.stride + 1 : 0;
+  if (p.stride < 1 || p.dilation < 1 || p.padLeft < 0 || p.padRight < 0 || (long long)l + p.padLeft + p.padRight < span || outw < 1)
+    throw TensorShapeException("Invalid convolution geometry for input " + x.GetShape().ToString() + " and kernel " + weight.GetShape().ToString() + ".");
+  Conv2dParams q;
+  q.strideH = 1; q.strideW = p.stride;
+  q.padTop = 0; q.padBottom = 0; q.padLeft = p.padLeft; q.padRight = p.padRight;
+  q.dilH = 1; q.dilW = p.dilation; q.groups = p.groups;
+  Tensor y = Conv2d(x.Reshape(Shape{n, c, 1, l}), weight.Reshape(Shape{o, weight.GetShape()[1], 1, k}), bias, q);
+  return y.Reshape(Shape{n, o, y.GetShape()[3]});
+}
+
 Tensor Ops::ConvTranspose2d(const Tensor& x, const Tensor& weight, const Tensor& bias, const ConvTranspose2dParams& p) {
   RequireF32(x);
   RequireF32(weight);

@@ -509,6 +509,49 @@ def gather(data, indices, axis):
     return _attach(y.astype(np.float32), Record("gather", [data], backward=bw), [data])
 
 
+def conv1d(x, w, b=None, stride=1, pad_left=0, pad_right=0, dilation=1, groups=1):
+    """Ops.Conv1d (Ops.Layers.cs:338-402): NCL input, OIK weights, torch.nn.Conv1d semantics with separate left and right
+    padding; backward BackwardNn.cs:313-402 on the height-1 view (dW = g im2col(x)^T, dx = col2im(W^T g), dbias = sum g).
+    Plain numpy over the kernel taps: for the small cases of the tests."""
+    xv, wv = np.ascontiguousarray(x.v), np.ascontiguousarray(w.v)
+    n, c, l = xv.shape
+    o, cg, k = wv.shape
+    og = o // groups
+    out_l = (l + pad_left + pad_right - dilation * (k - 1) - 1) // stride + 1
+    xp = np.zeros((n, c, l + pad_left + pad_right), np.float32)
+    xp[:, :, pad_left:pad_left + l] = xv
+
+    def taps(j):
+        return slice(j * dilation, j * dilation + (out_l - 1) * stride + 1, stride)
+
+    y = np.zeros((n, o, out_l), np.float32)
+    for g in range(groups):
+        for j in range(k):
+            y[:, g * og:(g + 1) * og] += np.einsum("ncl,oc->nol", xp[:, g * cg:(g + 1) * cg, taps(j)], wv[g * og:(g + 1) * og, :, j]).astype(np.float32)
+    if b is not None:
+        y += b.v[None, :, None]
+
+    def bw(r, gr):
+        gr = np.asarray(gr, np.float32)
+        dxp = np.zeros_like(xp)
+        dw = np.zeros_like(wv)
+        for g in range(groups):
+            gg = gr[:, g * og:(g + 1) * og]
+            for j in range(k):
+                dw[g * og:(g + 1) * og, :, j] = np.einsum("nol,ncl->oc", gg, xp[:, g * cg:(g + 1) * cg, taps(j)])
+                dxp[:, g * cg:(g + 1) * cg, taps(j)] += np.einsum("nol,oc->ncl", gg, wv[g * og:(g + 1) * og, :, j]).astype(np.float32)
+        out = []
+        if b is not None:
+            out.append((2, gr.astype(np.float64).sum(axis=(0, 2)).astype(np.float32), "own"))
+        out.append((1, dw, "own"))
+        if r.inputs[0] is not None:
+            out.append((0, np.ascontiguousarray(dxp[:, :, pad_left:pad_left + l]), "own"))
+        return out
+
+    ins = [x, w] + ([b] if b is not None else [])
+    return _attach(y, Record("conv1d", ins, backward=bw), ins)
+
+
 def conv_transpose2d(x, w, b=None, stride=1, padding=0, output_padding=0, groups=1):
     """Ops.ConvTranspose2d (Ops.Spatial.cs:43-130): the adjoint of Conv2d, computed as the input gradient of the convolution
     whose input is this op's output; backward dx = Conv2d(g, W), dW = the adjoint convolution's weight gradient, dbias = sum g

@@ -64,6 +64,8 @@ class OracleBackend:
     def matmul_batched(self, a, b): return self.tape.matmul_batched(a, b)
     def conv_transpose2d(self, x, w, b, stride=1, padding=0, output_padding=0, groups=1):
         return self.tape.conv_transpose2d(x, w, b, stride, padding, output_padding, groups)
+    def conv1d(self, x, w, b, stride=1, pad_left=0, pad_right=0, dilation=1, groups=1):
+        return self.tape.conv1d(x, w, b, stride, pad_left, pad_right, dilation, groups)
     def resize2d(self, x, oh, ow, mode=0, align=False): return self.tape.resize2d(x, oh, ow, mode, align)
     def erf(self, x): return self.tape.erf(x)
     def exp(self, x): return self.tape.exp(x)
@@ -143,6 +145,8 @@ class GpuBackend:
     def matmul_batched(self, a, b): return self.omb.call("matmul_batched", [a, b])
     def conv_transpose2d(self, x, w, b, stride=1, padding=0, output_padding=0, groups=1):
         return self.omb.call("conv_transpose2d", [x, w, b], ints=[stride, stride, padding, padding, output_padding, output_padding, 1, 1, groups])
+    def conv1d(self, x, w, b, stride=1, pad_left=0, pad_right=0, dilation=1, groups=1):
+        return self.omb.call("conv1d", [x, w, b] if b is not None else [x, w], ints=[stride, pad_left, pad_right, dilation, groups])
     def resize2d(self, x, oh, ow, mode=0, align=False): return self.omb.call("resize2d", [x], ints=[oh, ow, mode, 1 if align else 0])
     def erf(self, x): return self.omb.call("erf", [x])
     def exp(self, x): return self.omb.call("exp", [x])

@@ -181,6 +181,32 @@ def graph_ops_case(B, seed=0):
     return loss, g, {"a": a, "b": b, "c": c, "d": d}
 
 
+CONV1D_CASES = [
+    # n, c, l, o, k, stride, pad_left, pad_right, dilation, groups, bias
+    (2, 4, 19, 6, 3, 1, 1, 1, 1, 1, True),
+    (3, 6, 23, 4, 5, 2, 0, 3, 2, 2, True),        # stride, asymmetric padding, dilation, two groups
+    (1, 3, 8, 5, 1, 1, 0, 0, 1, 1, False),        # pointwise, no bias
+    (2, 8, 16, 8, 4, 3, 2, 1, 1, 4, True),        # "same"-style uneven padding, four groups
+]
+
+
+def conv1d_case(B, case, seed=0):
+    """One Conv1d (Ops.Conv1d of the reference) under a weighted sum: returns the loss, the output and the leaves."""
+    n, c, l, o, k, stride, pl, pr, dil, groups, has_bias = case
+    r = np.random.default_rng(seed + l)
+    x = B.tensor(r.standard_normal((n, c, l)).astype(np.float32), True)
+    w = B.tensor((r.standard_normal((o, c // groups, k)) * 0.5).astype(np.float32), True)
+    b = B.tensor(r.standard_normal(o).astype(np.float32), True) if has_bias else None
+    y = B.conv1d(x, w, b, stride, pl, pr, dil, groups)
+    out_l = (l + pl + pr - dil * (k - 1) - 1) // stride + 1
+    proj = B.tensor(r.standard_normal((n, o, out_l)).astype(np.float32))
+    loss = B.sum(B.mul(y, proj))
+    leaves = {"x": x, "w": w}
+    if has_bias:
+        leaves["b"] = b
+    return loss, y, leaves
+
+
 def autograd_decoder(B, fx):
     """testdata/autograd/decoder: conv, two transposed convolutions (stride 2; stride 2 with padding, output padding and two
     groups), nearest and bilinear resizes (tests/OneModel.Tests/Tensors/RnnOracleTests.cs:177-201 of the reference)."""

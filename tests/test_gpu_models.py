@@ -5,7 +5,7 @@ import pytest
 
 import models
 from backends import GpuBackend, OracleBackend, load_fixture, scaled_diff
-from test_oracle_golden import OPTIM, check_graph_ops, run_optim_case
+from test_oracle_golden import OPTIM, check_conv1d, check_graph_ops, run_optim_case
 
 pytestmark = pytest.mark.gpu
 
@@ -153,6 +153,13 @@ def test_graph_op_family(B):
     """MatMulBatched (broadcast batch axes), Erf, Exp, Sqrt, Pow, Where, Gather and their backward functions on the GPU
     against the PyTorch golden file the CPU oracle is pinned on (fp32 products: the 1e-4 tier, here far inside it)."""
     check_graph_ops(B, 1e-5)
+
+
+def test_conv1d_on_the_height_one_view(B):
+    """Ops.Conv1d (stride, separate left/right padding, dilation, groups, with and without bias): forward, dx, dW and dbias on
+    the GPU through the 2-D convolution entry points on a height-1 view, against the PyTorch golden file the CPU oracle is
+    pinned on."""
+    check_conv1d(B, 1e-5)
 
 
 @pytest.mark.parametrize("name,lr,b1,b2,eps", [("sparseadam", 0.05, 0.9, 0.999, 1e-3), ("sparseadam2", 0.02, 0.8, 0.95, 1e-8), ("sgd", 0.5, 0, 0, 0)])

@@ -210,6 +210,24 @@ def check_graph_ops(B, tol):
         assert scaled_diff(B.grad(t), gold["grad_" + k]) <= tol, k
 
 
+def check_conv1d(B, tol):
+    """Conv1d against tests/golden/conv1d.npz (PyTorch CPU, generated by tests/golden/make_graphops_golden.py)."""
+    import os
+    import models
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "conv1d.npz"))
+    for i, case in enumerate(models.CONV1D_CASES):
+        loss, y, leaves = models.conv1d_case(B, case)
+        B.backward(loss)
+        assert scaled_diff(B.numpy(y), gold[f"{i}.out"]) <= tol, (i, "out")
+        assert abs(float(B.numpy(loss).reshape(-1)[0]) - float(gold[f"{i}.loss"])) <= 10 * tol * max(1.0, abs(float(gold[f"{i}.loss"]))), i
+        for k, t in leaves.items():
+            assert scaled_diff(B.grad(t), gold[f"{i}.grad_{k}"]) <= tol, (i, k)
+
+
+def test_conv1d_against_pytorch_golden(B):
+    check_conv1d(B, 2e-6)
+
+
 def test_graph_ops_against_pytorch_golden(B):
     check_graph_ops(B, 1e-6)
 
