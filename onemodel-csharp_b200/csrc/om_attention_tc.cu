@@ -488,6 +488,248 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid
   }
 }
 
+// ---- forward, sequences of several tiles ---------------------------------------------------------------------------------
+// One CTA per (128 queries, batch, head) walks the key tiles twice. Pass 1 forms S_j = Q K_j^T for every key tile and keeps,
+// per row, the running maximum and the sum of exponentials (online softmax statistics: no output yet). Pass 2 forms S_j
+// again, turns it into the final probabilities P_j = exp(s - max) / sum with the statistics of pass 1, stages P_j as the
+// K-major operand and accumulates O += P_j V_j in tensor memory: nothing is ever rescaled. The second Q K^T costs tensor
+// pipe time that the kernel does not lack (its pace is set by the exponentials). S is double-buffered in tensor memory
+// and K in shared memory, so the product of the next tile and its load run under the current tile's row pass.
+// Steps g = 0 .. 2 nk - 1 number the (pass, tile) pairs; S buffer and K buffer of step g are g & 1. A score row is
+// shared by two threads (columns 0-63 and 64-127 of the tile): each keeps its own running maximum and sum through pass
+// 1 and the two are combined once, before pass 2.
+constexpr int ATT_MT_THREADS = 288;          // warps 0-7: half a score row per thread; warp 8: TMA + MMA issue
+
+template <int D>
+__global__ void __launch_bounds__(ATT_MT_THREADS, 1)
+attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, AttFwdParams p) {
+  constexpr int DB = D / 32;
+  constexpr uint32_t TMEM_COLS = 512;                   // S0: 0-127, S1: 128-255, O: 256 .. 256 + D
+  constexpr uint32_t COL_O = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;                                   // DB blocks
+  uint8_t* k_s[2] = {q_s + DB * ATT_BLOCK_BYTES, q_s + 2 * DB * ATT_BLOCK_BYTES};
+  uint8_t* v_s = q_s + 3 * DB * ATT_BLOCK_BYTES;         // DB blocks (MN-major)
+  uint8_t* p_s = q_s + 4 * DB * ATT_BLOCK_BYTES;         // 4 blocks; the output staging at the end
+  float* stats = reinterpret_cast<float*>(p_s + 4 * ATT_BLOCK_BYTES);      // [2 halves][128 rows][max, sum]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 4 * ATT_TILE);
+  uint64_t* bar_q = bars;
+  uint64_t* bar_k = bars + 1;       // [2] K tile landed
+  uint64_t* bar_v = bars + 3;       // V tile landed
+  uint64_t* bar_s = bars + 4;       // [2] S product complete (and its K buffer free)
+  uint64_t* bar_sr = bars + 6;      // [2] S buffer read by all rows
+  uint64_t* bar_p = bars + 8;       // P staged by all rows
+  uint64_t* bar_pv = bars + 9;      // P V product complete (P and V buffers free)
+  uint64_t* bar_x = bars + 10;      // both halves of every row have published their pass-1 statistics
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * ATT_TILE;
+  const int bh = blockIdx.y, bi = bh / p.heads, hi = bh % p.heads;
+  const int nk = (p.lk + ATT_TILE - 1) / ATT_TILE, steps = 2 * nk;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_q, 1);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&bar_k[i], 1);
+      mbar_init(&bar_s[i], 1);
+      mbar_init(&bar_sr[i], 2 * ATT_TILE);
+    }
+    mbar_init(bar_v, 1);
+    mbar_init(bar_p, 2 * ATT_TILE);
+    mbar_init(bar_pv, 1);
+    mbar_init(bar_x, 2 * ATT_TILE);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
+  pdl_wait();
+
+  if (warp == 8) {
+    if (lane == 0) {
+      const uint32_t idesc_s = att_idesc(ATT_TILE, false, false), idesc_o = att_idesc(D, false, true);
+      const uint32_t qa = smem_u32(q_s), va = smem_u32(v_s), pa = smem_u32(p_s);
+      auto load_k = [&](int g) {          // key tile of step g into its buffer
+        const int i = g & 1, j = g % nk;
+        mbar_expect_tx(&bar_k[i], DB * ATT_BLOCK_BYTES);
+        for (int kb = 0; kb < DB; kb++) tma_load_4d(k_s[i] + kb * ATT_BLOCK_BYTES, &map_k, 32 * kb, j * ATT_TILE, hi, bi, &bar_k[i]);
+      };
+      auto issue_s = [&](int g) {         // S[g & 1] = Q K^T for the key tile in buffer g & 1
+        const int i = g & 1;
+        const uint32_t ka = smem_u32(k_s[i]);
+#pragma unroll
+        for (int ks = 0; ks < D / 8; ks++) {
+          const uint32_t off = (ks / 4) * ATT_BLOCK_BYTES + (ks % 4) * 32;
+          umma_tf32(tmem_base + (uint32_t)(i * ATT_TILE), make_desc(qa + off, 16, 1024, 2), make_desc(ka + off, 16, 1024, 2), idesc_s, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&bar_s[i]);
+      };
+      mbar_expect_tx(bar_q, DB * ATT_BLOCK_BYTES);
+      for (int kb = 0; kb < DB; kb++) tma_load_4d(q_s + kb * ATT_BLOCK_BYTES, &map_q, 32 * kb, q0, hi, bi, bar_q);
+      load_k(0);
+      if (steps > 1) load_k(1);
+      bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, 41);
+      if (ok) ok = mbar_wait(&bar_k[0], 0, abort_flag, p.status, 42);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int g = 0; g < steps && ok; g++) {
+        const int i = g & 1;
+        // 1. the product of the next step, as soon as its key tile has landed and its S buffer has been read (step g - 1)
+        if (g + 1 < steps) {
+          const int n = (g + 1) & 1;
+          ok = mbar_wait(&bar_k[n], (uint32_t)((g + 1) >> 1) & 1, abort_flag, p.status, 43);
+          if (ok && g >= 1) ok = mbar_wait(&bar_sr[n], (uint32_t)(((g + 1) >> 1) - 1) & 1, abort_flag, p.status, 44);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(g + 1);
+        }
+        // 2. the key tile of step g + 2 into this step's buffer, once this step's product has read it
+        if (g + 2 < steps) {
+          ok = mbar_wait(&bar_s[i], (uint32_t)(g >> 1) & 1, abort_flag, p.status, 45);
+          if (!ok) break;
+          load_k(g + 2);
+        }
+        // 3. second pass: O += P V
+        if (g >= nk) {
+          const int t = g - nk;
+          if (t >= 1) ok = mbar_wait(bar_pv, (uint32_t)(t - 1) & 1, abort_flag, p.status, 46);   // V and P buffers free
+          if (!ok) break;
+          mbar_expect_tx(bar_v, DB * ATT_BLOCK_BYTES);
+          for (int kb = 0; kb < DB; kb++) tma_load_4d(v_s + kb * ATT_BLOCK_BYTES, &map_v, 32 * kb, t * ATT_TILE, hi, bi, bar_v);
+          ok = mbar_wait(bar_v, (uint32_t)t & 1, abort_flag, p.status, 47);
+          if (ok) ok = mbar_wait(bar_p, (uint32_t)t & 1, abort_flag, p.status, 48);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < ATT_TILE / 8; ks++) {
+            const uint64_t adesc = make_desc(pa + (ks / 4) * ATT_BLOCK_BYTES + (ks % 4) * 32, 16, 1024, 2);
+            const uint64_t bdesc = make_desc(va + ks * 1024, ATT_BLOCK_BYTES, 512, 1);
+            umma_tf32(tmem_base + COL_O, adesc, bdesc, idesc_o, (t > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_pv);
+        }
+      }
+    }
+  } else {
+    // ---- half a score row per thread: row = 32 * (warp % 4) + lane, columns 64 * (warp / 4) .. + 63 of each tile ----
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane, qrow = q0 + row;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const float LOG2E = 1.4426950408889634f;
+    const float* mrow = nullptr;
+    if (p.mask && qrow < p.lq) mrow = p.mask + (long long)bi * p.mask_batch_stride + (long long)qrow * p.lk;
+    float run_max = -INFINITY, run_sum = 0.f, inv_sum = 0.f, max_l2 = 0.f;
+    bool ok = true;
+    float v[64];
+    for (int g = 0; g < steps && ok; g++) {
+      const int i = g & 1, j = g % nk, col0 = j * ATT_TILE + half * 64;
+      ok = mbar_wait(&bar_s[i], (uint32_t)(g >> 1) & 1, abort_flag, p.status, 49);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_base + (uint32_t)(i * ATT_TILE + half * 64 + c * 32), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 32; jj++) v[c * 32 + jj] = __uint_as_float(r[jj]);
+      }
+      tc_fence_before();
+      mbar_arrive(&bar_sr[i]);                      // the next product may overwrite this S buffer
+      const bool full = mrow == nullptr && col0 + 64 <= p.lk;
+      if (full) {
+#pragma unroll
+        for (int jj = 0; jj < 64; jj++) v[jj] = v[jj] * p.scale;
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < 64; jj++) {
+          float sv = -INFINITY;
+          if (col0 + jj < p.lk) sv = (v[jj] * p.scale) + (mrow ? mrow[col0 + jj] : 0.f);
+          v[jj] = sv;
+        }
+      }
+      if (g < nk) {
+        // pass 1: running maximum and sum of exponentials of this thread's columns
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int jj = 0; jj < 64; jj++) m4[jj & 3] = fmaxf(m4[jj & 3], v[jj]);
+        const float tile_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        const float new_max = fmaxf(run_max, tile_max);
+        if (new_max > -INFINITY) {
+          const float nl = new_max * LOG2E;
+          float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int jj = 0; jj < 64; jj++) s4[jj & 3] += exp2f(fmaf(v[jj], LOG2E, -nl));
+          const float carry = run_max > -INFINITY ? run_sum * exp2f(fmaf(run_max, LOG2E, -nl)) : 0.f;
+          run_sum = carry + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+          run_max = new_max;
+        }
+        if (g == nk - 1) {
+          // the two halves of a row exchange their statistics once
+          stats[(half * ATT_TILE + row) * 2] = run_max;
+          stats[(half * ATT_TILE + row) * 2 + 1] = run_sum;
+          mbar_arrive(bar_x);                       // a bounded wait, not a named barrier: a thread that gave up never arrives
+          ok = mbar_wait(bar_x, 0, abort_flag, p.status, 52);
+          if (!ok) break;
+          const float om = stats[((half ^ 1) * ATT_TILE + row) * 2], os = stats[((half ^ 1) * ATT_TILE + row) * 2 + 1];
+          // combined in the order (columns 0-63, columns 64-127) by both threads, so that they hold the same bits
+          const float m0 = half ? om : run_max, s0 = half ? os : run_sum, m1 = half ? run_max : om, s1 = half ? run_sum : os;
+          const float mx = fmaxf(m0, m1);
+          const float ml = mx * LOG2E;
+          const float t0 = m0 > -INFINITY ? s0 * exp2f(fmaf(m0, LOG2E, -ml)) : 0.f;
+          const float t1 = m1 > -INFINITY ? s1 * exp2f(fmaf(m1, LOG2E, -ml)) : 0.f;
+          const float total = t0 + t1;
+          inv_sum = 1.0f / total;
+          max_l2 = ml;
+          if (half == 0 && p.lse && qrow < p.lq) p.lse[(long long)bh * p.lq + qrow] = mx + logf(total);
+        }
+      } else {
+        // pass 2: the final probabilities of this thread's columns, staged as the K-major operand of P V
+        const int t = g - nk;
+#pragma unroll
+        for (int jj = 0; jj < 64; jj++) v[jj] = to_tf32(exp2f(fmaf(v[jj], LOG2E, -max_l2)) * inv_sum);
+        if (t >= 1) ok = mbar_wait(bar_pv, (uint32_t)(t - 1) & 1, abort_flag, p.status, 50);   // the previous P has been consumed
+        if (ok) {
+#pragma unroll
+          for (int c = 0; c < 2; c++) store_seg_kmajor(p_s + (half * 2 + c) * ATT_BLOCK_BYTES, row, v + c * 32);
+          fence_async_smem();
+        }
+        mbar_arrive(bar_p);
+      }
+    }
+    // ---- output: warps 0-3 write columns 0-31, warps 4-7 columns 32-63 (D = 64) ----
+    if (ok) ok = mbar_wait(bar_pv, (uint32_t)(nk - 1) & 1, abort_flag, p.status, 51);
+    tc_fence_after();
+    if (ok && half < DB) {
+      float* stg = reinterpret_cast<float*>(p_s) + warp * 32 * 36;          // the last P V product has consumed P
+      float* outp = p.out + (long long)bi * p.o_batch + (long long)hi * p.o_head + half * 32;
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(lane_base + COL_O + half * 32, r);
+      tmem_ld_wait();
+      store_rows_32(stg, lane, r, outp, p.o_row, q0 + quad * 32, p.lq);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // Rank-4 map over an activation seen as [B, H, L, D] through element strides; box = [32 floats, 128 rows, 1, 1].
 static bool att_map(CUtensorMap* map, const float* base, int d, int l, int heads, int batch, long long s_row, long long s_head,
                     long long s_batch, bool mn_major) {
@@ -512,7 +754,8 @@ bool attention_tc_fwd_supported(om_ctx* ctx, const float* q, const om_head_strid
                                 const float* v, const om_head_strides* vs, const float* out, const om_head_strides* os, int b, int h,
                                 int lq, int lk, int d) {
   if (!(ctx->flags & OM_TF32) || !encode_fn()) return false;
-  if (lq < 1 || lk < 1 || lq > ATT_TILE || lk > ATT_TILE || (d != 32 && d != 64) || b < 1 || h < 1) return false;
+  if (lq < 1 || lk < 1 || (d != 32 && d != 64) || b < 1 || h < 1) return false;
+  if ((lq > ATT_TILE || lk > ATT_TILE) && (long long)b * h > 65535) return false;   // the several-tile kernel puts (batch, head) on grid.y
   if (!att_operand_ok(q, qs, h, b) || !att_operand_ok(k, ks, h, b) || !att_operand_ok(v, vs, h, b)) return false;
   if ((reinterpret_cast<uintptr_t>(out) & 15) || (os->row & 3) || (os->head & 3) || (os->batch & 3)) return false;
   return true;
@@ -528,6 +771,28 @@ int32_t attention_tc_fwd(om_ctx* ctx, const float* q, const om_head_strides* qs,
   AttFwdParams p;
   p.lq = lq; p.lk = lk; p.d = d; p.heads = h; p.scale = scale; p.mask = mask; p.mask_batch_stride = mask_batch_stride;
   p.out = out; p.o_batch = os->batch; p.o_head = os->head; p.o_row = os->row; p.lse = lse; p.status = ctx->status_dev;
+  if (lq > ATT_TILE || lk > ATT_TILE) {
+    // Several tiles: one CTA per 128 queries walks the key tiles (two passes, see attention_fwd_mt_kernel).
+    const size_t smem_mt = (size_t)(4 * (d / 32) + 4) * ATT_BLOCK_BYTES + 1024 + 4 * ATT_TILE * sizeof(float) + 256;
+    const dim3 grid_mt((unsigned)((lq + ATT_TILE - 1) / ATT_TILE), (unsigned)(b * h));
+    if (d == 32) {
+      static bool set = false;
+      if (!set) {
+        OM_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_mt_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mt));
+        set = true;
+      }
+      launch_chained(ctx, attention_fwd_mt_kernel<32>, grid_mt, ATT_MT_THREADS, smem_mt, mq, mk, mv, p);
+    } else {
+      static bool set = false;
+      if (!set) {
+        OM_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_mt_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mt));
+        set = true;
+      }
+      launch_chained(ctx, attention_fwd_mt_kernel<64>, grid_mt, ATT_MT_THREADS, smem_mt, mq, mk, mv, p);
+    }
+    OM_LAUNCH_CHECK(ctx, "attention_fwd_mt");
+    return OM_OK;
+  }
   const size_t smem = (size_t)((d / 32) + 4) * ATT_BLOCK_BYTES + 1024 + 256;
   const unsigned grid = (unsigned)(b * h);
   if (d == 32) {

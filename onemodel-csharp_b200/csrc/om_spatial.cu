@@ -61,12 +61,26 @@ im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __restrict__ cols,
     const int p = (int)(q - (int64_t)n * plane);
     const float* xc = x + ((int64_t)n * g.cin + c) * g.h * g.w;
     float v[VEC];
+    if (VEC == 4 && (g.ow & 3) == 0) {
+      // The four pixels lie in one output row: one division, one input row, four input columns sw apart.
+      const int oy = p / g.ow, ox = p - oy * g.ow;
+      const int iy = oy * g.sh - g.pt + ky * g.dh;
+      const bool row_ok = (unsigned)iy < (unsigned)g.h;
+      const float* xr = xc + iy * g.w;
+      const int ix0 = ox * g.sw - g.pl + kx * g.dw;
 #pragma unroll
-    for (int j = 0; j < VEC; j++) {
-      const int pj = p + j;
-      const int oy = pj / g.ow, ox = pj - oy * g.ow;
-      const int iy = oy * g.sh - g.pt + ky * g.dh, ix = ox * g.sw - g.pl + kx * g.dw;
-      v[j] = ((unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w) ? __ldg(xc + iy * g.w + ix) : 0.f;
+      for (int j = 0; j < VEC; j++) {
+        const int ix = ix0 + j * g.sw;
+        v[j] = (row_ok && (unsigned)ix < (unsigned)g.w) ? __ldg(xr + ix) : 0.f;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; j++) {
+        const int pj = p + j;
+        const int oy = pj / g.ow, ox = pj - oy * g.ow;
+        const int iy = oy * g.sh - g.pt + ky * g.dh, ix = ox * g.sw - g.pl + kx * g.dw;
+        v[j] = ((unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w) ? __ldg(xc + iy * g.w + ix) : 0.f;
+      }
     }
     float* dst = cols + (int64_t)kidx * k_stride + (int64_t)n * n_stride + p;
     if (VEC == 4) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
@@ -76,9 +90,12 @@ im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __restrict__ cols,
 
 // dx[n][c][iy][ix] = sum over (ky, kx) in increasing order of dcols[(c,ky,kx)][n][oy*OW+ox] where the tap lands on (iy, ix).
 // blockIdx.y = channel, blockIdx.z = image, threads over the input plane.
+// S is the stride when both strides equal it (1 or 2: the divisions become shifts), 0 for the general case.
+template <int S>
 __global__ void __launch_bounds__(256)
 col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restrict__ dx, int64_t k_stride, int64_t n_stride) {
   const int c = blockIdx.y, n = blockIdx.z;
+  const int sh = S ? S : g.sh, sw = S ? S : g.sw;
   const int hw = g.h * g.w;
   const float* base = dcols + (int64_t)n * n_stride + (int64_t)c * g.kh * g.kw * k_stride;
   float* out = dx + ((int64_t)n * g.cin + c) * hw;
@@ -87,19 +104,25 @@ col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restr
     float acc = 0.f;
     for (int ky = 0; ky < g.kh; ky++) {
       int ty = iy + g.pt - ky * g.dh;
-      if (ty < 0 || ty % g.sh) continue;
-      int oy = ty / g.sh;
+      if (ty < 0 || ty % sh) continue;
+      int oy = ty / sh;
       if (oy >= g.oh) continue;
       for (int kx = 0; kx < g.kw; kx++) {
         int tx = ix + g.pl - kx * g.dw;
-        if (tx < 0 || tx % g.sw) continue;
-        int ox = tx / g.sw;
+        if (tx < 0 || tx % sw) continue;
+        int ox = tx / sw;
         if (ox >= g.ow) continue;
         acc += base[(int64_t)(ky * g.kw + kx) * k_stride + oy * g.ow + ox];
       }
     }
     out[e] = acc;
   }
+}
+
+static void launch_col2im(om_ctx* ctx, dim3 grid, const ConvGeom& g, const float* dcols, float* dx, int64_t k_stride, int64_t n_stride) {
+  if (g.sh == 1 && g.sw == 1) col2im_gather_kernel<1><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride);
+  else if (g.sh == 2 && g.sw == 2) col2im_gather_kernel<2><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride);
+  else col2im_gather_kernel<0><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride);
 }
 
 __global__ void add_plane_bias_kernel(float* __restrict__ y, const float* __restrict__ bias, int cout, int plane, int64_t total) {
@@ -532,7 +555,7 @@ int32_t om_conv2d_dgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, co
     if (st == OM_OK) st = gemm_tc(ctx, 1, 0, kk, np, g.cout, w, kk, gt, np, dcols, np, 0, nullptr);
     if (st == OM_OK) {
       dim3 cgrid((unsigned)std::min<int64_t>(ceil_div((int64_t)g.h * g.w, 256), 64), (unsigned)g.cin, (unsigned)g.n);
-      col2im_gather_kernel<<<cgrid, 256, 0, ctx->stream>>>(g, dcols, dx, np, plane);
+      launch_col2im(ctx, cgrid, g, dcols, dx, np, plane);
     }
     if (gt) pool_free(ctx, gt);
     pool_free(ctx, dcols);
@@ -548,7 +571,7 @@ int32_t om_conv2d_dgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, co
   }
   if (st == OM_OK) {
     dim3 cgrid((unsigned)std::min<int64_t>(ceil_div((int64_t)g.h * g.w, 256), 64), (unsigned)g.cin, (unsigned)g.n);
-    col2im_gather_kernel<<<cgrid, 256, 0, ctx->stream>>>(g, dcols, dx, plane, (int64_t)g.cin * g.kh * g.kw * plane);
+    launch_col2im(ctx, cgrid, g, dcols, dx, plane, (int64_t)g.cin * g.kh * g.kw * plane);
   }
   pool_free(ctx, dcols);
   OM_TRY(st);

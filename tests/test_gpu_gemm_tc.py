@@ -124,7 +124,10 @@ def test_tf32_strided_batch(ctx, oracle_built, ta, tb, m, n, k, batch):
 
 
 @pytest.mark.parametrize("b,h,lq,lk,d,masked", [(3, 4, 128, 128, 32, 0), (2, 2, 64, 192, 64, 1), (2, 3, 100, 100, 32, 0), (2, 2, 128, 128, 32, 1),
-                                                (1, 3, 60, 128, 64, 0), (2, 1, 128, 37, 64, 1), (1, 1, 5, 7, 32, 0)])
+                                                (1, 3, 60, 128, 64, 0), (2, 1, 128, 37, 64, 1), (1, 1, 5, 7, 32, 0),
+                                                # several tiles: the two-pass forward kernel (the backward takes the general path)
+                                                (2, 3, 256, 256, 64, 0), (1, 2, 512, 512, 64, 1), (2, 2, 300, 200, 32, 1),
+                                                (1, 2, 129, 128, 64, 0), (1, 1, 128, 130, 32, 0), (1, 2, 64, 640, 32, 0)])
 def test_tf32_attention(ctx, oracle_built, b, h, lq, lk, d, masked):
     """Attention forward and backward with the head products on the tensor pipe, at the TF32 tier of the contract."""
     K = oracle_built
