@@ -349,6 +349,16 @@ int32_t om_attention_bwd_strided(om_ctx* ctx, const float* g, const om_head_stri
                                  int64_t mask_batch_stride, const float* lse, int32_t b, int32_t h, int32_t lq,
                                  int32_t lk, int32_t d, float scale, float* dq, const om_head_strides* dqs,
                                  float* dk, const om_head_strides* dks, float* dv, const om_head_strides* dvs);
+/* om_attention_bwd_strided with the forward's output `out` (strides os) at hand. The reference recomputes the row dots
+ * rowsum(P dP) from the probabilities (BackwardNn.cs:660-676); with O = P V they equal rowsum(dO O), which lets the
+ * several-tile kernel walk the key tiles once instead of twice. out == NULL is om_attention_bwd_strided. */
+int32_t om_attention_bwd_strided_out(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q,
+                                     const om_head_strides* qs, const float* k, const om_head_strides* ks,
+                                     const float* v, const om_head_strides* vs, const float* out,
+                                     const om_head_strides* os, const float* mask, int64_t mask_batch_stride,
+                                     const float* lse, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d,
+                                     float scale, float* dq, const om_head_strides* dqs, float* dk,
+                                     const om_head_strides* dks, float* dv, const om_head_strides* dvs);
 
 /* ---- pooling and convolution ---------------------------------------------------------------------------- */
 

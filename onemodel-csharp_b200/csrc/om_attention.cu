@@ -21,6 +21,13 @@ int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const fl
 bool attention_tc_fwd_supported(om_ctx* ctx, const float* q, const om_head_strides* qs, const float* k, const om_head_strides* ks,
                                 const float* v, const om_head_strides* vs, const float* out, const om_head_strides* os, int b, int h,
                                 int lq, int lk, int d);
+bool attention_bwd_front_supported(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs,
+                                   const float* k, const om_head_strides* ks, const float* v, const om_head_strides* vs, const float* lse,
+                                   int b, int h, int lq, int lk, int d);
+int32_t attention_bwd_front(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs, const float* k,
+                            const om_head_strides* ks, const float* v, const om_head_strides* vs, const float* o, const om_head_strides* os,
+                            const float* mask, long long mask_batch_stride, const float* lse, int b, int h, int lq, int lk, int d, float scale,
+                            float* p_out, float* ds_out);
 int32_t attention_tc_fwd(om_ctx* ctx, const float* q, const om_head_strides* qs, const float* k, const om_head_strides* ks, const float* v,
                          const om_head_strides* vs, const float* mask, long long mask_batch_stride, int b, int h, int lq, int lk, int d,
                          float scale, float* out, const om_head_strides* os, float* lse);
@@ -238,12 +245,14 @@ int32_t om_attention_fwd(om_ctx* ctx, const float* q, const float* k, const floa
   return om_attention_fwd_strided(ctx, q, &sq, k, &sk, v, &sk, mask, mask_batch_stride, b, h, lq, lk, d, scale, out, &sq, lse);
 }
 
-int32_t om_attention_bwd_strided(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs,
-                                 const float* k, const om_head_strides* ks, const float* v, const om_head_strides* vs,
-                                 const float* mask, int64_t mask_batch_stride, const float* lse, int32_t b, int32_t h, int32_t lq,
-                                 int32_t lk, int32_t d, float scale, float* dq, const om_head_strides* dqs, float* dk,
-                                 const om_head_strides* dks, float* dv, const om_head_strides* dvs) {
+int32_t om_attention_bwd_strided_out(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs,
+                                     const float* k, const om_head_strides* ks, const float* v, const om_head_strides* vs,
+                                     const float* out, const om_head_strides* os, const float* mask, int64_t mask_batch_stride,
+                                     const float* lse, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d, float scale, float* dq,
+                                     const om_head_strides* dqs, float* dk, const om_head_strides* dks, float* dv,
+                                     const om_head_strides* dvs) {
   OM_CHECK_CTX(ctx);
+  if (out) OM_TRY(check_strides(ctx, "Attention backward", os, d));
   OM_TRY(check_att(ctx, "Attention backward", b, h, lq, lk, d));
   OM_TRY(check_strides(ctx, "Attention backward", gs, d));
   OM_TRY(check_strides(ctx, "Attention backward", qs, d));
@@ -269,6 +278,19 @@ int32_t om_attention_bwd_strided(om_ctx* ctx, const float* g, const om_head_stri
   const HeadView G = view_of(g, gs), Q = view_of(q, qs), K = view_of(k, ks), V = view_of(v, vs);
   const HeadView P = scores_view(p, h, lq, lk), DP = scores_view(dp, h, lq, lk);
   int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 16);
+  if (attention_bwd_front_supported(ctx, g, gs, q, qs, k, ks, v, vs, lse, b, h, lq, lk, d)) {
+    // P and dS from one tensor-pipe kernel per 128 queries (the forward's log-sum-exp makes P a single pass), then the three
+    // output products.
+    st = attention_bwd_front(ctx, g, gs, q, qs, k, ks, v, vs, out, os, mask, mask_batch_stride, lse, b, h, lq, lk, d, scale, p, dp);
+    if (st == OM_OK && dv) st = head_gemm(ctx, 1, 0, lk, d, lq, P, G, dv, view_of(dv, dvs), bh, h);
+    if (st == OM_OK && dq) st = head_gemm(ctx, 0, 0, lq, d, lk, DP, K, dq, view_of(dq, dqs), bh, h);
+    if (st == OM_OK && dk) st = head_gemm(ctx, 1, 0, lk, d, lq, DP, Q, dk, view_of(dk, dks), bh, h);
+    pool_free(ctx, p);
+    pool_free(ctx, dp);
+    OM_TRY(st);
+    OM_LAUNCH_CHECK(ctx, "om_attention_bwd");
+    return OM_OK;
+  }
   st = head_gemm(ctx, 0, 1, lq, lk, d, Q, K, p, P, bh, h);
   if (st == OM_OK) {
     launch_att_softmax(ctx, grid, p, mask, mask_batch_stride, h, lq, lk, rows, scale, nullptr);
@@ -289,6 +311,15 @@ int32_t om_attention_bwd_strided(om_ctx* ctx, const float* g, const om_head_stri
   OM_TRY(st);
   OM_LAUNCH_CHECK(ctx, "om_attention_bwd");
   return OM_OK;
+}
+
+int32_t om_attention_bwd_strided(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs,
+                                 const float* k, const om_head_strides* ks, const float* v, const om_head_strides* vs,
+                                 const float* mask, int64_t mask_batch_stride, const float* lse, int32_t b, int32_t h, int32_t lq,
+                                 int32_t lk, int32_t d, float scale, float* dq, const om_head_strides* dqs, float* dk,
+                                 const om_head_strides* dks, float* dv, const om_head_strides* dvs) {
+  return om_attention_bwd_strided_out(ctx, g, gs, q, qs, k, ks, v, vs, nullptr, nullptr, mask, mask_batch_stride, lse, b, h, lq, lk, d, scale,
+                                      dq, dqs, dk, dks, dv, dvs);
 }
 
 int32_t om_attention_bwd(om_ctx* ctx, const float* g, const float* q, const float* k, const float* v, const float* mask,

@@ -40,6 +40,13 @@ __device__ __forceinline__ float to_tf32(float x) {
   return __uint_as_float(r);
 }
 
+// 2^x on the special-function unit, one instruction (inputs here are at most 0, or -inf for masked columns: 2^-inf = 0).
+__device__ __forceinline__ float fast_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Instruction descriptor for kind::tf32 with an fp32 accumulator: M = 128, N = n, operand major bits.
 __device__ __forceinline__ uint32_t att_idesc(int n, bool a_mn, bool b_mn) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
@@ -629,6 +636,7 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int row = quad * 32 + lane, qrow = q0 + row;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
     const float LOG2E = 1.4426950408889634f;
+    const float sl2 = p.scale * LOG2E;
     const float* mrow = nullptr;
     if (p.mask && qrow < p.lq) mrow = p.mask + (long long)bi * p.mask_batch_stride + (long long)qrow * p.lk;
     float run_max = -INFINITY, run_sum = 0.f, inv_sum = 0.f, max_l2 = 0.f;
@@ -649,15 +657,16 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       tc_fence_before();
       mbar_arrive(&bar_sr[i]);                      // the next product may overwrite this S buffer
+      // Scores in the base-2 domain from here on: t = (scale s + mask) log2 e, so that an exponential is one ex2.
       const bool full = mrow == nullptr && col0 + 64 <= p.lk;
       if (full) {
 #pragma unroll
-        for (int jj = 0; jj < 64; jj++) v[jj] = v[jj] * p.scale;
+        for (int jj = 0; jj < 64; jj++) v[jj] = v[jj] * sl2;
       } else {
 #pragma unroll
         for (int jj = 0; jj < 64; jj++) {
           float sv = -INFINITY;
-          if (col0 + jj < p.lk) sv = (v[jj] * p.scale) + (mrow ? mrow[col0 + jj] : 0.f);
+          if (col0 + jj < p.lk) sv = fmaf(v[jj], sl2, mrow ? mrow[col0 + jj] * LOG2E : 0.f);
           v[jj] = sv;
         }
       }
@@ -669,11 +678,10 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const float tile_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         const float new_max = fmaxf(run_max, tile_max);
         if (new_max > -INFINITY) {
-          const float nl = new_max * LOG2E;
           float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int jj = 0; jj < 64; jj++) s4[jj & 3] += exp2f(fmaf(v[jj], LOG2E, -nl));
-          const float carry = run_max > -INFINITY ? run_sum * exp2f(fmaf(run_max, LOG2E, -nl)) : 0.f;
+          for (int jj = 0; jj < 64; jj++) s4[jj & 3] += fast_ex2(v[jj] - new_max);
+          const float carry = run_max > -INFINITY ? run_sum * fast_ex2(run_max - new_max) : 0.f;
           run_sum = carry + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
           run_max = new_max;
         }
@@ -688,19 +696,18 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           // combined in the order (columns 0-63, columns 64-127) by both threads, so that they hold the same bits
           const float m0 = half ? om : run_max, s0 = half ? os : run_sum, m1 = half ? run_max : om, s1 = half ? run_sum : os;
           const float mx = fmaxf(m0, m1);
-          const float ml = mx * LOG2E;
-          const float t0 = m0 > -INFINITY ? s0 * exp2f(fmaf(m0, LOG2E, -ml)) : 0.f;
-          const float t1 = m1 > -INFINITY ? s1 * exp2f(fmaf(m1, LOG2E, -ml)) : 0.f;
+          const float t0 = m0 > -INFINITY ? s0 * fast_ex2(m0 - mx) : 0.f;
+          const float t1 = m1 > -INFINITY ? s1 * fast_ex2(m1 - mx) : 0.f;
           const float total = t0 + t1;
           inv_sum = 1.0f / total;
-          max_l2 = ml;
-          if (half == 0 && p.lse && qrow < p.lq) p.lse[(long long)bh * p.lq + qrow] = mx + logf(total);
+          max_l2 = mx;
+          if (half == 0 && p.lse && qrow < p.lq) p.lse[(long long)bh * p.lq + qrow] = mx * 0.6931471805599453f + logf(total);
         }
       } else {
         // pass 2: the final probabilities of this thread's columns, staged as the K-major operand of P V
         const int t = g - nk;
 #pragma unroll
-        for (int jj = 0; jj < 64; jj++) v[jj] = to_tf32(exp2f(fmaf(v[jj], LOG2E, -max_l2)) * inv_sum);
+        for (int jj = 0; jj < 64; jj++) v[jj] = to_tf32(fast_ex2(v[jj] - max_l2) * inv_sum);
         if (t >= 1) ok = mbar_wait(bar_pv, (uint32_t)(t - 1) & 1, abort_flag, p.status, 50);   // the previous P has been consumed
         if (ok) {
 #pragma unroll
@@ -720,6 +727,250 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tmem_ld_32x32b_x32(lane_base + COL_O + half * 32, r);
       tmem_ld_wait();
       store_rows_32(stg, lane, r, outp, p.o_row, q0 + quad * 32, p.lq);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- backward, sequences of several tiles: the probabilities and the score gradients --------------------------------------
+// The first half of AttentionBackward (BackwardNn.cs:636-701) as one kernel per 128 queries: S = Q K_j^T and dP = dO V_j^T in
+// tensor memory for every key tile j, P = exp(scale S + mask - lse) with the forward's log-sum-exp, dS = P (dP - dot) scale,
+// both written to the [B*H, Lq, Lk] matrices that the three output products (dV = P^T dO, dQ = dS K, dK = dS^T Q) read. It
+// replaces two products and two passes over those matrices. dot = rowsum(P dP) needs the whole row: when the forward's
+// output O is at hand it is rowsum(dO O) (the same number, O = P V), taken from the two rows before the first tile and the
+// key tiles are walked once (ONE_PASS); without O a first pass over the key tiles accumulates it and a second pass forms
+// the products again. S and dP are double-buffered in tensor memory (the products of the next tile run under this tile's row
+// pass); each thread owns half a score row of the tile, and a warp turns its 32 x 64 block through shared memory so that the
+// stores to P and dS are whole 256-byte row segments.
+struct AttFrontParams {
+  int lq, lk, heads, d;
+  float scale;
+  const float* mask;
+  long long mask_batch_stride;
+  const float* lse;      // [B*H, lq]
+  const float* g;        // dO and O as strided [B, H, L, D] views (ONE_PASS)
+  const float* o;
+  long long g_batch, g_head, g_row, o_batch, o_head, o_row;
+  float* p_out;          // [B*H, lq, lk]
+  float* ds_out;         // [B*H, lq, lk]
+  int32_t* status;
+};
+
+constexpr int ATT_STG_LD = 68;          // floats per staged row of 64: 16-byte aligned, rows spread over the banks
+
+// Writes a warp's 32 x 64 block (lane l holds row l in v[0..63]) to dst rows row0 + l, columns col0 .. col0 + 63.
+__device__ __forceinline__ void store_block_64(float* stg, int lane, const float* v, float* dst, long long ld, int row0, int rows_valid, int col0,
+                                               int cols_valid, bool vec_ok) {
+#pragma unroll
+  for (int j = 0; j < 64; j += 4) *reinterpret_cast<float4*>(stg + lane * ATT_STG_LD + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  __syncwarp();
+  if (vec_ok && col0 + 64 <= cols_valid) {
+    const int c4 = (lane & 15) * 4;
+#pragma unroll
+    for (int it = 0; it < 16; it++) {
+      const int r = it * 2 + (lane >> 4);
+      if (row0 + r < rows_valid)
+        *reinterpret_cast<float4*>(dst + (long long)(row0 + r) * ld + col0 + c4) = *reinterpret_cast<const float4*>(stg + r * ATT_STG_LD + c4);
+    }
+  } else {
+    for (int r = 0; r < 32; r++) {
+      if (row0 + r >= rows_valid) break;
+      for (int c = lane; c < 64; c += 32)
+        if (col0 + c < cols_valid) dst[(long long)(row0 + r) * ld + col0 + c] = stg[r * ATT_STG_LD + c];
+    }
+  }
+  __syncwarp();
+}
+
+template <int D, bool ONE_PASS>
+__global__ void __launch_bounds__(ATT_MT_THREADS, 1)
+attention_bwd_front_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_g,
+                           const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttFrontParams p) {
+  constexpr int DB = D / 32;
+  constexpr uint32_t TMEM_COLS = 512;                   // S0: 0, S1: 128, dP0: 256, dP1: 384
+  constexpr uint32_t COL_DP = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;
+  uint8_t* g_s = q_s + DB * ATT_BLOCK_BYTES;
+  uint8_t* k_s = q_s + 2 * DB * ATT_BLOCK_BYTES;
+  uint8_t* v_s = q_s + 3 * DB * ATT_BLOCK_BYTES;
+  float* stage = reinterpret_cast<float*>(q_s + 4 * DB * ATT_BLOCK_BYTES);       // [8 warps][32][ATT_STG_LD]
+  float* stats = stage + 8 * 32 * ATT_STG_LD;                                     // [2 halves][128 rows] partial dots
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 2 * ATT_TILE);
+  uint64_t* bar_qg = bars;          // Q and dO landed
+  uint64_t* bar_kv = bars + 1;      // K and V tile landed
+  uint64_t* bar_s = bars + 2;       // [2] both products complete (and the K, V buffer free)
+  uint64_t* bar_sr = bars + 4;      // [2] S and dP buffers read by all rows
+  uint64_t* bar_x = bars + 6;       // both halves of every row have published their partial dot
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * ATT_TILE;
+  const int bh = blockIdx.y, bi = bh / p.heads, hi = bh % p.heads;
+  const int nk = (p.lk + ATT_TILE - 1) / ATT_TILE, steps = ONE_PASS ? nk : 2 * nk;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_qg, 1);
+    mbar_init(bar_kv, 1);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&bar_s[i], 1);
+      mbar_init(&bar_sr[i], 2 * ATT_TILE);
+    }
+    mbar_init(bar_x, 2 * ATT_TILE);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
+  pdl_wait();
+
+  if (warp == 8) {
+    if (lane == 0) {
+      const uint32_t idesc = att_idesc(ATT_TILE, false, false);
+      const uint32_t qa = smem_u32(q_s), ga = smem_u32(g_s), ka = smem_u32(k_s), va = smem_u32(v_s);
+      auto load_kv = [&](int g) {
+        const int j = g % nk;
+        mbar_expect_tx(bar_kv, 2 * DB * ATT_BLOCK_BYTES);
+        for (int kb = 0; kb < DB; kb++) {
+          tma_load_4d(k_s + kb * ATT_BLOCK_BYTES, &map_k, 32 * kb, j * ATT_TILE, hi, bi, bar_kv);
+          tma_load_4d(v_s + kb * ATT_BLOCK_BYTES, &map_v, 32 * kb, j * ATT_TILE, hi, bi, bar_kv);
+        }
+      };
+      auto issue = [&](int g) {           // S[g & 1] = Q K^T, dP[g & 1] = dO V^T
+        const int i = g & 1;
+#pragma unroll
+        for (int ks = 0; ks < D / 8; ks++) {
+          const uint32_t off = (ks / 4) * ATT_BLOCK_BYTES + (ks % 4) * 32;
+          umma_tf32(tmem_base + (uint32_t)(i * ATT_TILE), make_desc(qa + off, 16, 1024, 2), make_desc(ka + off, 16, 1024, 2), idesc, ks > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 8; ks++) {
+          const uint32_t off = (ks / 4) * ATT_BLOCK_BYTES + (ks % 4) * 32;
+          umma_tf32(tmem_base + COL_DP + (uint32_t)(i * ATT_TILE), make_desc(ga + off, 16, 1024, 2), make_desc(va + off, 16, 1024, 2), idesc,
+                    ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&bar_s[i]);
+      };
+      mbar_expect_tx(bar_qg, 2 * DB * ATT_BLOCK_BYTES);
+      for (int kb = 0; kb < DB; kb++) {
+        tma_load_4d(q_s + kb * ATT_BLOCK_BYTES, &map_q, 32 * kb, q0, hi, bi, bar_qg);
+        tma_load_4d(g_s + kb * ATT_BLOCK_BYTES, &map_g, 32 * kb, q0, hi, bi, bar_qg);
+      }
+      load_kv(0);
+      bool ok = mbar_wait(bar_qg, 0, abort_flag, p.status, 61);
+      if (ok) ok = mbar_wait(bar_kv, 0, abort_flag, p.status, 62);
+      if (ok) {
+        tc_fence_after();
+        issue(0);
+      }
+      for (int g = 0; g + 1 < steps && ok; g++) {
+        // The single K, V buffer is free once this step's products have read it; the next tile's load and products then run
+        // under this step's row pass.
+        ok = mbar_wait(&bar_s[g & 1], (uint32_t)(g >> 1) & 1, abort_flag, p.status, 63);
+        if (!ok) break;
+        load_kv(g + 1);
+        ok = mbar_wait(bar_kv, (uint32_t)(g + 1) & 1, abort_flag, p.status, 64);
+        if (ok && g >= 1) ok = mbar_wait(&bar_sr[(g + 1) & 1], (uint32_t)(((g + 1) >> 1) - 1) & 1, abort_flag, p.status, 65);
+        if (!ok) break;
+        tc_fence_after();
+        issue(g + 1);
+      }
+    }
+  } else {
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane, qrow = q0 + row;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const float LOG2E = 1.4426950408889634f;
+    const float sl2 = p.scale * LOG2E;
+    const float* mrow = nullptr;
+    if (p.mask && qrow < p.lq) mrow = p.mask + (long long)bi * p.mask_batch_stride + (long long)qrow * p.lk;
+    const float lse_l = (qrow < p.lq ? p.lse[(long long)bh * p.lq + qrow] : 0.f) * LOG2E;
+    const bool vec_ok = (p.lk & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.p_out) | reinterpret_cast<uintptr_t>(p.ds_out)) & 15) == 0;
+    float* stg = stage + warp * 32 * ATT_STG_LD;
+    float* p_mat = p.p_out + (long long)bh * p.lq * p.lk;
+    float* ds_mat = p.ds_out + (long long)bh * p.lq * p.lk;
+    float dot = 0.f;
+    float d4[4] = {0.f, 0.f, 0.f, 0.f};
+    bool ok = true;
+    if (ONE_PASS) {
+      // dot = rowsum(dO O): this thread's half of the head dimension, the halves added in a fixed order
+      float part = 0.f;
+      if (qrow < p.lq) {
+        const float* gr = p.g + (long long)bi * p.g_batch + (long long)hi * p.g_head + (long long)qrow * p.g_row + half * (D / 2);
+        const float* orow = p.o + (long long)bi * p.o_batch + (long long)hi * p.o_head + (long long)qrow * p.o_row + half * (D / 2);
+#pragma unroll
+        for (int j = 0; j < D / 2; j += 4) {
+          const float4 a = *reinterpret_cast<const float4*>(gr + j), b = *reinterpret_cast<const float4*>(orow + j);
+          d4[0] = fmaf(a.x, b.x, d4[0]); d4[1] = fmaf(a.y, b.y, d4[1]); d4[2] = fmaf(a.z, b.z, d4[2]); d4[3] = fmaf(a.w, b.w, d4[3]);
+        }
+        part = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      }
+      stats[half * ATT_TILE + row] = part;
+      mbar_arrive(bar_x);
+      ok = mbar_wait(bar_x, 0, abort_flag, p.status, 67);
+      if (ok) dot = stats[row] + stats[ATT_TILE + row];
+    }
+    float pv[64], dp[64];
+    for (int g = 0; g < steps && ok; g++) {
+      const int i = g & 1, j = g % nk, col0 = j * ATT_TILE + half * 64;
+      ok = mbar_wait(&bar_s[i], (uint32_t)(g >> 1) & 1, abort_flag, p.status, 66);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32b_x32(lane_base + (uint32_t)(i * ATT_TILE + half * 64 + c * 32), rs);
+        tmem_ld_32x32b_x32(lane_base + COL_DP + (uint32_t)(i * ATT_TILE + half * 64 + c * 32), rd);
+        tmem_ld_wait();
+        if (mrow == nullptr && col0 + 64 <= p.lk) {
+#pragma unroll
+          for (int jj = 0; jj < 32; jj++) {
+            pv[c * 32 + jj] = fast_ex2(fmaf(__uint_as_float(rs[jj]), sl2, -lse_l));
+            dp[c * 32 + jj] = __uint_as_float(rd[jj]);
+          }
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 32; jj++) {
+            const int col = col0 + c * 32 + jj;
+            float e = 0.f;
+            if (col < p.lk) e = fast_ex2(fmaf(__uint_as_float(rs[jj]), sl2, (mrow ? mrow[col] * LOG2E : 0.f) - lse_l));
+            pv[c * 32 + jj] = e;
+            dp[c * 32 + jj] = __uint_as_float(rd[jj]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bar_sr[i]);
+      if (!ONE_PASS && g < nk) {
+#pragma unroll
+        for (int jj = 0; jj < 64; jj++) d4[jj & 3] = fmaf(pv[jj], dp[jj], d4[jj & 3]);
+        if (g == nk - 1) {
+          stats[half * ATT_TILE + row] = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+          mbar_arrive(bar_x);
+          ok = mbar_wait(bar_x, 0, abort_flag, p.status, 67);
+          if (!ok) break;
+          dot = stats[row] + stats[ATT_TILE + row];
+        }
+      } else {
+        store_block_64(stg, lane, pv, p_mat, p.lk, q0 + quad * 32, p.lq, col0, p.lk, vec_ok);
+#pragma unroll
+        for (int jj = 0; jj < 64; jj++) dp[jj] = (pv[jj] * (dp[jj] - dot)) * p.scale;      // dS
+        store_block_64(stg, lane, dp, ds_mat, p.lk, q0 + quad * 32, p.lq, col0, p.lk, vec_ok);
+      }
     }
   }
   tc_fence_before();
@@ -853,6 +1104,53 @@ int32_t attention_tc_bwd(om_ctx* ctx, const float* g, const om_head_strides* gs,
   }
   launch_chained(ctx, attention_bwd_tc_kernel, (unsigned)(b * h), ATT_BWD_THREADS, smem, qk, kk, vk, gk, qm, km, gm, p);
   OM_LAUNCH_CHECK(ctx, "attention_bwd_tc");
+  return OM_OK;
+}
+
+// The several-tile backward front: P and dS for the whole [B*H, Lq, Lk] score space from one kernel.
+bool attention_bwd_front_supported(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs,
+                                   const float* k, const om_head_strides* ks, const float* v, const om_head_strides* vs, const float* lse,
+                                   int b, int h, int lq, int lk, int d) {
+  if (!(ctx->flags & OM_TF32) || !encode_fn() || lse == nullptr) return false;
+  if (lq < 1 || lk < 1 || (d != 32 && d != 64) || b < 1 || h < 1 || (long long)b * h > 65535) return false;
+  return att_operand_ok(g, gs, h, b) && att_operand_ok(q, qs, h, b) && att_operand_ok(k, ks, h, b) && att_operand_ok(v, vs, h, b);
+}
+
+template <int D, bool ONE_PASS>
+static int32_t launch_front(om_ctx* ctx, dim3 grid, size_t smem, const CUtensorMap& mq, const CUtensorMap& mg, const CUtensorMap& mk,
+                            const CUtensorMap& mv, const AttFrontParams& p) {
+  static bool set = false;
+  if (!set) {
+    OM_CUDA(ctx, cudaFuncSetAttribute(attention_bwd_front_kernel<D, ONE_PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    set = true;
+  }
+  launch_chained(ctx, attention_bwd_front_kernel<D, ONE_PASS>, grid, ATT_MT_THREADS, smem, mq, mg, mk, mv, p);
+  return OM_OK;
+}
+
+// o (the forward's output, with its strides) may be null: the kernel then takes a first pass over the key tiles for the row dots.
+int32_t attention_bwd_front(om_ctx* ctx, const float* g, const om_head_strides* gs, const float* q, const om_head_strides* qs, const float* k,
+                            const om_head_strides* ks, const float* v, const om_head_strides* vs, const float* o, const om_head_strides* os,
+                            const float* mask, long long mask_batch_stride, const float* lse, int b, int h, int lq, int lk, int d, float scale,
+                            float* p_out, float* ds_out) {
+  CUtensorMap mq, mg, mk, mv;
+  if (!att_map(&mq, q, d, lq, h, b, qs->row, qs->head, qs->batch, false) || !att_map(&mg, g, d, lq, h, b, gs->row, gs->head, gs->batch, false) ||
+      !att_map(&mk, k, d, lk, h, b, ks->row, ks->head, ks->batch, false) || !att_map(&mv, v, d, lk, h, b, vs->row, vs->head, vs->batch, false))
+    return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed for the attention backward operands");
+  const bool one_pass = o != nullptr && os != nullptr && (reinterpret_cast<uintptr_t>(o) & 15) == 0 && (os->row & 3) == 0 &&
+                        (os->head & 3) == 0 && (os->batch & 3) == 0;
+  AttFrontParams p;
+  p.lq = lq; p.lk = lk; p.heads = h; p.d = d; p.scale = scale; p.mask = mask; p.mask_batch_stride = mask_batch_stride; p.lse = lse;
+  p.g = g; p.g_batch = gs->batch; p.g_head = gs->head; p.g_row = gs->row;
+  p.o = one_pass ? o : nullptr; p.o_batch = one_pass ? os->batch : 0; p.o_head = one_pass ? os->head : 0; p.o_row = one_pass ? os->row : 0;
+  p.p_out = p_out; p.ds_out = ds_out; p.status = ctx->status_dev;
+  const size_t smem = (size_t)(4 * (d / 32)) * ATT_BLOCK_BYTES + 1024 + (8 * 32 * ATT_STG_LD + 2 * ATT_TILE) * sizeof(float) + 256;
+  const dim3 grid((unsigned)((lq + ATT_TILE - 1) / ATT_TILE), (unsigned)(b * h));
+  int32_t st;
+  if (d == 32) st = one_pass ? launch_front<32, true>(ctx, grid, smem, mq, mg, mk, mv, p) : launch_front<32, false>(ctx, grid, smem, mq, mg, mk, mv, p);
+  else st = one_pass ? launch_front<64, true>(ctx, grid, smem, mq, mg, mk, mv, p) : launch_front<64, false>(ctx, grid, smem, mq, mg, mk, mv, p);
+  OM_TRY(st);
+  OM_LAUNCH_CHECK(ctx, "attention_bwd_front");
   return OM_OK;
 }
 

@@ -347,9 +347,13 @@ static void AttentionHeadsBackward(BackwardRecord& r, const Tensor& g) {
   if (!dq.IsEmpty()) dqs = strides(dq);
   if (!dk.IsEmpty()) dks = strides(dk);
   if (!dv.IsEmpty()) dvs = strides(dv);
-  Check(om_attention_bwd_strided(C(), gc.Data(), &gs, q.Data(), &qs, k.Data(), &ks, v.Data(), &vs, mask.IsEmpty() ? nullptr : mask.Data(),
-                                 r.Ints[0], r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, heads, lq, lk, d, (float)r.Floats[0], dq.IsEmpty() ? nullptr : dq.Data(), &dqs,
-                                 dk.IsEmpty() ? nullptr : dk.Data(), &dks, dv.IsEmpty() ? nullptr : dv.Data(), &dvs));
+  const Tensor& out = r.Saved(5);
+  om_head_strides os{};
+  if (!out.IsEmpty()) os = strides(out);
+  Check(om_attention_bwd_strided_out(C(), gc.Data(), &gs, q.Data(), &qs, k.Data(), &ks, v.Data(), &vs, out.IsEmpty() ? nullptr : out.Data(), &os,
+                                     mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0], r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, heads,
+                                     lq, lk, d, (float)r.Floats[0], dq.IsEmpty() ? nullptr : dq.Data(), &dqs, dk.IsEmpty() ? nullptr : dk.Data(), &dks,
+                                     dv.IsEmpty() ? nullptr : dv.Data(), &dvs));
   if (!dq.IsEmpty()) Engine::Emit(r, 0, dq, true);
   if (!dk.IsEmpty()) Engine::Emit(r, 1, dk, true);
   if (!dv.IsEmpty()) Engine::Emit(r, 2, dv, true);
@@ -364,10 +368,11 @@ static void AttentionPackedBackward(BackwardRecord& r, const Tensor& g) {
   Tensor gc = g.Contiguous();
   Tensor dqkv = Tensor::Create(DType::F32, qkv.GetShape());
   om_head_strides ps{(int64_t)l * 3 * width, (int64_t)d, (int64_t)3 * width}, gs{(int64_t)l * width, (int64_t)d, (int64_t)width};
-  Check(om_attention_bwd_strided(C(), gc.Data(), &gs, qkv.Data(), &ps, qkv.Data() + width, &ps, qkv.Data() + 2 * width, &ps,
-                                 mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0], r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, heads, l, l, d,
-                                 (float)r.Floats[0],
-                                 dqkv.Data(), &ps, dqkv.Data() + width, &ps, dqkv.Data() + 2 * width, &ps));
+  const Tensor& out = r.Saved(5);
+  Check(om_attention_bwd_strided_out(C(), gc.Data(), &gs, qkv.Data(), &ps, qkv.Data() + width, &ps, qkv.Data() + 2 * width, &ps,
+                                     out.IsEmpty() ? nullptr : out.Data(), &gs, mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0],
+                                     r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, heads, l, l, d, (float)r.Floats[0], dqkv.Data(), &ps,
+                                     dqkv.Data() + width, &ps, dqkv.Data() + 2 * width, &ps));
   Engine::Emit(r, 0, dqkv, true);
 }
 
@@ -381,9 +386,12 @@ static void AttentionBackward(BackwardRecord& r, const Tensor& g) {
   if (r.NeedsInputGrad(0)) dq = Tensor::Create(DType::F32, q.GetShape());
   if (r.NeedsInputGrad(1)) dk = Tensor::Create(DType::F32, k.GetShape());
   if (r.NeedsInputGrad(2)) dv = Tensor::Create(DType::F32, v.GetShape());
-  Check(om_attention_bwd(C(), gc.Data(), q.Data(), k.Data(), v.Data(), mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0],
-                         r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, h, lq, lk, d, (float)r.Floats[0], dq.IsEmpty() ? nullptr : dq.Data(),
-                         dk.IsEmpty() ? nullptr : dk.Data(), dv.IsEmpty() ? nullptr : dv.Data()));
+  const om_head_strides sq{(int64_t)h * lq * d, (int64_t)lq * d, (int64_t)d}, sk{(int64_t)h * lk * d, (int64_t)lk * d, (int64_t)d};
+  const Tensor& out = r.Saved(5);
+  Check(om_attention_bwd_strided_out(C(), gc.Data(), &sq, q.Data(), &sq, k.Data(), &sk, v.Data(), &sk, out.IsEmpty() ? nullptr : out.Data(), &sq,
+                                     mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0], r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, h, lq,
+                                     lk, d, (float)r.Floats[0], dq.IsEmpty() ? nullptr : dq.Data(), &sq, dk.IsEmpty() ? nullptr : dk.Data(), &sk,
+                                     dv.IsEmpty() ? nullptr : dv.Data(), &sk));
   if (!dq.IsEmpty()) Engine::Emit(r, 0, dq, true);
   if (!dk.IsEmpty()) Engine::Emit(r, 1, dk, true);
   if (!dv.IsEmpty()) Engine::Emit(r, 2, dv, true);

@@ -348,8 +348,9 @@ Tensor Ops::Attention(const Tensor& q, const Tensor& k, const Tensor& v, const T
   Check(om_attention_fwd(C(), qc.Data(), kc.Data(), vc.Data(), mc.IsEmpty() ? nullptr : mc.Data(), maskStride, b, h, lq, lk,
                          d, scale, r.Data(), lse.IsEmpty() ? nullptr : lse.Data()));
   if (!recording) return r;
-  auto rec = BackwardRecord::Create(OpKind::Attention, 5, {&q, &k, &v});
+  auto rec = BackwardRecord::Create(OpKind::Attention, 6, {&q, &k, &v});
   rec->Save(4, lse);
+  rec->Save(5, r.Detach());   // the output: the backward takes the row dots from rowsum(dO O)
   rec->Save(0, qc.Detach());
   rec->Save(1, kc.Detach());
   rec->Save(2, vc.Detach());
@@ -400,8 +401,9 @@ Tensor Ops::AttentionHeads(const Tensor& q, const Tensor& k, const Tensor& v, in
   Check(om_attention_fwd_strided(C(), qc.Data(), &qs, kc.Data(), &ks, vc.Data(), &vs, mc.IsEmpty() ? nullptr : mc.Data(), maskStride,
                                  b, heads, lq, lk, d, scale, r.Data(), &os, lse.IsEmpty() ? nullptr : lse.Data()));
   if (!recording) return r;
-  auto rec = BackwardRecord::Create(OpKind::Attention, 5, {&q, &k, &v});
+  auto rec = BackwardRecord::Create(OpKind::Attention, 6, {&q, &k, &v});
   rec->Save(4, lse);
+  rec->Save(5, r.Detach());   // the output: the backward takes the row dots from rowsum(dO O)
   rec->Save(0, qc.Detach());
   rec->Save(1, kc.Detach());
   rec->Save(2, vc.Detach());
@@ -476,8 +478,9 @@ Tensor Ops::AttentionPacked(const Tensor& qkv, int heads, const Tensor& mask, fl
   Check(om_attention_fwd_strided(C(), pc.Data(), &ps, pc.Data() + width, &ps, pc.Data() + 2 * width, &ps, mc.IsEmpty() ? nullptr : mc.Data(),
                                  maskStride, b, heads, l, l, d, scale, r.Data(), &os, lse.IsEmpty() ? nullptr : lse.Data()));
   if (!recording) return r;
-  auto rec = BackwardRecord::Create(OpKind::Attention, 5, {&qkv});
+  auto rec = BackwardRecord::Create(OpKind::Attention, 6, {&qkv});
   rec->Save(4, lse);
+  rec->Save(5, r.Detach());
   rec->Save(0, pc.Detach());
   if (!mc.IsEmpty()) rec->Save(3, mc);
   rec->Floats = {scale};

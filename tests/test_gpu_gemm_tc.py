@@ -127,7 +127,9 @@ def test_tf32_strided_batch(ctx, oracle_built, ta, tb, m, n, k, batch):
                                                 (1, 3, 60, 128, 64, 0), (2, 1, 128, 37, 64, 1), (1, 1, 5, 7, 32, 0),
                                                 # several tiles: the two-pass forward kernel (the backward takes the general path)
                                                 (2, 3, 256, 256, 64, 0), (1, 2, 512, 512, 64, 1), (2, 2, 300, 200, 32, 1),
-                                                (1, 2, 129, 128, 64, 0), (1, 1, 128, 130, 32, 0), (1, 2, 64, 640, 32, 0)])
+                                                (1, 2, 129, 128, 64, 0), (1, 1, 128, 130, 32, 0), (1, 2, 64, 640, 32, 0),
+                                                # a quarter of one BERT-base-shape layer: 384 CTAs, the case the ncu summary of these kernels uses
+                                                (8, 12, 512, 512, 64, 0)])
 def test_tf32_attention(ctx, oracle_built, b, h, lq, lk, d, masked):
     """Attention forward and backward with the head products on the tensor pipe, at the TF32 tier of the contract."""
     K = oracle_built

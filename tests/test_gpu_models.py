@@ -103,7 +103,8 @@ def test_engine_semantics(B):
 
 
 @pytest.mark.parametrize("tf32", [False, True])
-@pytest.mark.parametrize("b,l,heads,dh,packed", [(3, 128, 4, 32, False), (2, 50, 3, 16, False), (2, 128, 12, 32, True)])
+@pytest.mark.parametrize("b,l,heads,dh,packed", [(3, 128, 4, 32, False), (2, 50, 3, 16, False), (2, 128, 12, 32, True),
+                                                 (2, 300, 4, 64, False), (2, 256, 3, 32, True), (1, 128, 2, 64, False)])
 def test_attention_over_heads_equals_the_permuted_form(ctx, B, tf32, b, l, heads, dh, packed):
     """Ops.AttentionHeads on [batch, length, heads*d] activations against the reference's form (Reshape + Permute around
     Ops.Attention, Layers.cs:503-520): values and all three input gradients. With the fp32 products the two run the same
@@ -140,8 +141,12 @@ def test_attention_over_heads_equals_the_permuted_form(ctx, B, tf32, b, l, heads
         ya, ga = run(True)
         yb, gb = run(False)
         if tf32:
+            # Several tiles (or one tile with d = 64): the head form hands the forward's output to the backward, whose row dots
+            # are then rowsum(dO O); the permuted form recomputes them as rowsum(P dP). Equal in exact arithmetic, a TF32
+            # product apart on the tensor pipe.
+            tol = 2e-5 if (l <= 128 and dh == 32) or dh == 16 else 2e-3
             assert scaled_diff(ya, yb) <= 2e-5
-            assert all(scaled_diff(x, y) <= 2e-5 for x, y in zip(ga, gb))
+            assert all(scaled_diff(x, y) <= tol for x, y in zip(ga, gb))
         else:
             assert np.array_equal(ya, yb)
             assert all(np.array_equal(x, y) for x, y in zip(ga, gb))
