@@ -539,6 +539,9 @@ int32_t om_dp_register_bucket(om_ctx* ctx, int32_t bucket_id, float* base, int64
 int32_t om_dp_allreduce_bucket(om_ctx* ctx, int32_t bucket_id);
 int32_t om_dp_allreduce(om_ctx* ctx, void* buf, int64_t count, int32_t dtype); /* small in-stream sums */
 int32_t om_dp_wait(om_ctx* ctx, int32_t timeout_ms);
+/* Makes the context stream wait for ONE launched bucket: the optimizer can update the parameters of a bucket while
+ * later buckets are still being reduced. om_dp_wait afterwards collects the rest and checks the communicator. */
+int32_t om_dp_wait_bucket(om_ctx* ctx, int32_t bucket_id);
 int32_t om_dp_finalize(om_ctx* ctx);
 
 #if defined(__GNUC__)

@@ -502,10 +502,13 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid
 // K-major operand and accumulates O += P_j V_j in tensor memory: nothing is ever rescaled. The second Q K^T costs tensor
 // pipe time that the kernel does not lack (its pace is set by the exponentials). S is double-buffered in tensor memory
 // and K in shared memory, so the product of the next tile and its load run under the current tile's row pass.
-// Steps g = 0 .. 2 nk - 1 number the (pass, tile) pairs; S buffer and K buffer of step g are g & 1. A score row is
-// shared by two threads (columns 0-63 and 64-127 of the tile): each keeps its own running maximum and sum through pass
-// 1 and the two are combined once, before pass 2.
-constexpr int ATT_MT_THREADS = 288;          // warps 0-7: half a score row per thread; warp 8: TMA + MMA issue
+// The row warps' waits are made warp-uniform (__all_sync): a warp leaves its loop together, so its __syncwarp points hold even
+// when a wait ran out. Steps g = 0 .. 2 nk - 1 number the (pass, tile) pairs; S buffer and K buffer of step g are g & 1. A score row is
+// shared by four threads (32 columns of the tile each): each keeps its own running maximum and sum through pass 1 and the
+// four are combined once, in a fixed order, before pass 2.
+constexpr int ATT_MT_PARTS = 4;              // threads per score row: each owns 32 of the tile's 128 columns
+constexpr int ATT_MT_ISSUE_WARP = 4 * ATT_MT_PARTS;
+constexpr int ATT_MT_THREADS = 32 * (ATT_MT_ISSUE_WARP + 1);   // 16 row warps (enough of them to hide each other's latencies) + TMA / MMA issue
 
 template <int D>
 __global__ void __launch_bounds__(ATT_MT_THREADS, 1)
@@ -518,19 +521,20 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* q_s = smem;                                   // DB blocks
   uint8_t* k_s[2] = {q_s + DB * ATT_BLOCK_BYTES, q_s + 2 * DB * ATT_BLOCK_BYTES};
-  uint8_t* v_s = q_s + 3 * DB * ATT_BLOCK_BYTES;         // DB blocks (MN-major)
-  uint8_t* p_s = q_s + 4 * DB * ATT_BLOCK_BYTES;         // 4 blocks; the output staging at the end
-  float* stats = reinterpret_cast<float*>(p_s + 4 * ATT_BLOCK_BYTES);      // [2 halves][128 rows][max, sum]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 4 * ATT_TILE);
+  uint8_t* v_s[2] = {q_s + 3 * DB * ATT_BLOCK_BYTES, q_s + 4 * DB * ATT_BLOCK_BYTES};   // DB blocks each (MN-major)
+  uint8_t* p_s = q_s + 5 * DB * ATT_BLOCK_BYTES;         // 4 blocks; the output staging at the end
+  float* stats = reinterpret_cast<float*>(p_s);          // [parts][128 rows][max, sum]: used once, before the first P is staged
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 4 * ATT_BLOCK_BYTES);
   uint64_t* bar_q = bars;
   uint64_t* bar_k = bars + 1;       // [2] K tile landed
-  uint64_t* bar_v = bars + 3;       // V tile landed
-  uint64_t* bar_s = bars + 4;       // [2] S product complete (and its K buffer free)
-  uint64_t* bar_sr = bars + 6;      // [2] S buffer read by all rows
-  uint64_t* bar_p = bars + 8;       // P staged by all rows
-  uint64_t* bar_pv = bars + 9;      // P V product complete (P and V buffers free)
-  uint64_t* bar_x = bars + 10;      // both halves of every row have published their pass-1 statistics
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* bar_v = bars + 3;       // [2] V tile landed
+  uint64_t* bar_s = bars + 5;       // [2] S product complete (and its K buffer free)
+  uint64_t* bar_sr = bars + 7;      // [2] S buffer read by all rows
+  uint64_t* bar_p = bars + 9;       // P staged by all rows
+  uint64_t* bar_pv = bars + 10;     // P V product complete (P buffer and that tile's V buffer free)
+  uint64_t* bar_x = bars + 11;      // all parts of every row have published their pass-1 statistics
+  uint64_t* bar_x2 = bars + 12;     // ... and have read them: the statistics share their memory with the first P
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -543,16 +547,18 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     for (int i = 0; i < 2; i++) {
       mbar_init(&bar_k[i], 1);
       mbar_init(&bar_s[i], 1);
-      mbar_init(&bar_sr[i], 2 * ATT_TILE);
+      mbar_init(&bar_sr[i], ATT_MT_ISSUE_WARP);   // one arrival per row warp
     }
-    mbar_init(bar_v, 1);
-    mbar_init(bar_p, 2 * ATT_TILE);
+    mbar_init(&bar_v[0], 1);
+    mbar_init(&bar_v[1], 1);
+    mbar_init(bar_p, ATT_MT_ISSUE_WARP);
     mbar_init(bar_pv, 1);
-    mbar_init(bar_x, 2 * ATT_TILE);
+    mbar_init(bar_x, ATT_MT_PARTS * ATT_TILE);
+    mbar_init(bar_x2, ATT_MT_PARTS * ATT_TILE);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 8) {
+  if (warp == ATT_MT_ISSUE_WARP) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -563,10 +569,14 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   pdl_trigger();
   pdl_wait();
 
-  if (warp == 8) {
+  if (warp == ATT_MT_ISSUE_WARP) {
     if (lane == 0) {
       const uint32_t idesc_s = att_idesc(ATT_TILE, false, false), idesc_o = att_idesc(D, false, true);
-      const uint32_t qa = smem_u32(q_s), va = smem_u32(v_s), pa = smem_u32(p_s);
+      const uint32_t qa = smem_u32(q_s), pa = smem_u32(p_s);
+      auto load_v = [&](int t) {          // value tile t into buffer t & 1
+        mbar_expect_tx(&bar_v[t & 1], DB * ATT_BLOCK_BYTES);
+        for (int kb = 0; kb < DB; kb++) tma_load_4d(v_s[t & 1] + kb * ATT_BLOCK_BYTES, &map_v, 32 * kb, t * ATT_TILE, hi, bi, &bar_v[t & 1]);
+      };
       auto load_k = [&](int g) {          // key tile of step g into its buffer
         const int i = g & 1, j = g % nk;
         mbar_expect_tx(&bar_k[i], DB * ATT_BLOCK_BYTES);
@@ -586,6 +596,8 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       for (int kb = 0; kb < DB; kb++) tma_load_4d(q_s + kb * ATT_BLOCK_BYTES, &map_q, 32 * kb, q0, hi, bi, bar_q);
       load_k(0);
       if (steps > 1) load_k(1);
+      load_v(0);                          // both value buffers are free: the first two tiles come in during pass 1
+      if (nk > 1) load_v(1);
       bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, 41);
       if (ok) ok = mbar_wait(&bar_k[0], 0, abort_flag, p.status, 42);
       if (ok) {
@@ -612,14 +624,17 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         // 3. second pass: O += P V
         if (g >= nk) {
           const int t = g - nk;
-          if (t >= 1) ok = mbar_wait(bar_pv, (uint32_t)(t - 1) & 1, abort_flag, p.status, 46);   // V and P buffers free
-          if (!ok) break;
-          mbar_expect_tx(bar_v, DB * ATT_BLOCK_BYTES);
-          for (int kb = 0; kb < DB; kb++) tma_load_4d(v_s + kb * ATT_BLOCK_BYTES, &map_v, 32 * kb, t * ATT_TILE, hi, bi, bar_v);
-          ok = mbar_wait(bar_v, (uint32_t)t & 1, abort_flag, p.status, 47);
+          if (t >= 1) {
+            // P V of tile t - 1 is complete: its value buffer takes tile t + 1 while this tile's row pass runs
+            ok = mbar_wait(bar_pv, (uint32_t)(t - 1) & 1, abort_flag, p.status, 46);
+            if (!ok) break;
+            if (t + 1 < nk) load_v(t + 1);
+          }
+          ok = mbar_wait(&bar_v[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, p.status, 47);
           if (ok) ok = mbar_wait(bar_p, (uint32_t)t & 1, abort_flag, p.status, 48);
           if (!ok) break;
           tc_fence_after();
+          const uint32_t va = smem_u32(v_s[t & 1]);
 #pragma unroll
           for (int ks = 0; ks < ATT_TILE / 8; ks++) {
             const uint64_t adesc = make_desc(pa + (ks / 4) * ATT_BLOCK_BYTES + (ks % 4) * 32, 16, 1024, 2);
@@ -631,8 +646,8 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
     }
   } else {
-    // ---- half a score row per thread: row = 32 * (warp % 4) + lane, columns 64 * (warp / 4) .. + 63 of each tile ----
-    const int quad = warp & 3, half = warp >> 2;
+    // ---- a quarter of a score row per thread: row = 32 * (warp % 4) + lane, columns 32 * (warp / 4) .. + 31 of each tile ----
+    const int quad = warp & 3, part = warp >> 2;
     const int row = quad * 32 + lane, qrow = q0 + row;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
     const float LOG2E = 1.4426950408889634f;
@@ -641,30 +656,31 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (p.mask && qrow < p.lq) mrow = p.mask + (long long)bi * p.mask_batch_stride + (long long)qrow * p.lk;
     float run_max = -INFINITY, run_sum = 0.f, inv_sum = 0.f, max_l2 = 0.f;
     bool ok = true;
-    float v[64];
+    float v[32];
     for (int g = 0; g < steps && ok; g++) {
-      const int i = g & 1, j = g % nk, col0 = j * ATT_TILE + half * 64;
-      ok = mbar_wait(&bar_s[i], (uint32_t)(g >> 1) & 1, abort_flag, p.status, 49);
+      const int i = g & 1, j = g % nk, col0 = j * ATT_TILE + part * 32;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar_s[i], (uint32_t)(g >> 1) & 1, abort_flag, p.status, 49));
       if (!ok) break;
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; c++) {
+      {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(lane_base + (uint32_t)(i * ATT_TILE + half * 64 + c * 32), r);
+        tmem_ld_32x32b_x32(lane_base + (uint32_t)(i * ATT_TILE + part * 32), r);
         tmem_ld_wait();
 #pragma unroll
-        for (int jj = 0; jj < 32; jj++) v[c * 32 + jj] = __uint_as_float(r[jj]);
+        for (int jj = 0; jj < 32; jj++) v[jj] = __uint_as_float(r[jj]);
       }
       tc_fence_before();
-      mbar_arrive(&bar_sr[i]);                      // the next product may overwrite this S buffer
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_sr[i]);       // the next product may overwrite this S buffer (one arrival per warp:
+                                                    // hundreds of arrivals on one barrier word would serialise)
       // Scores in the base-2 domain from here on: t = (scale s + mask) log2 e, so that an exponential is one ex2.
-      const bool full = mrow == nullptr && col0 + 64 <= p.lk;
+      const bool full = mrow == nullptr && col0 + 32 <= p.lk;
       if (full) {
 #pragma unroll
-        for (int jj = 0; jj < 64; jj++) v[jj] = v[jj] * sl2;
+        for (int jj = 0; jj < 32; jj++) v[jj] = v[jj] * sl2;
       } else {
 #pragma unroll
-        for (int jj = 0; jj < 64; jj++) {
+        for (int jj = 0; jj < 32; jj++) {
           float sv = -INFINITY;
           if (col0 + jj < p.lk) sv = fmaf(v[jj], sl2, mrow ? mrow[col0 + jj] * LOG2E : 0.f);
           v[jj] = sv;
@@ -674,64 +690,69 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         // pass 1: running maximum and sum of exponentials of this thread's columns
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int jj = 0; jj < 64; jj++) m4[jj & 3] = fmaxf(m4[jj & 3], v[jj]);
+        for (int jj = 0; jj < 32; jj++) m4[jj & 3] = fmaxf(m4[jj & 3], v[jj]);
         const float tile_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         const float new_max = fmaxf(run_max, tile_max);
         if (new_max > -INFINITY) {
           float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int jj = 0; jj < 64; jj++) s4[jj & 3] += fast_ex2(v[jj] - new_max);
+          for (int jj = 0; jj < 32; jj++) s4[jj & 3] += fast_ex2(v[jj] - new_max);
           const float carry = run_max > -INFINITY ? run_sum * fast_ex2(run_max - new_max) : 0.f;
           run_sum = carry + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
           run_max = new_max;
         }
         if (g == nk - 1) {
-          // the two halves of a row exchange their statistics once
-          stats[(half * ATT_TILE + row) * 2] = run_max;
-          stats[(half * ATT_TILE + row) * 2 + 1] = run_sum;
+          // the threads of a row exchange their statistics once and combine them in the order of the column ranges, so that
+          // all of them hold the same bits
+          stats[(part * ATT_TILE + row) * 2] = run_max;
+          stats[(part * ATT_TILE + row) * 2 + 1] = run_sum;
           mbar_arrive(bar_x);                       // a bounded wait, not a named barrier: a thread that gave up never arrives
-          ok = mbar_wait(bar_x, 0, abort_flag, p.status, 52);
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_x, 0, abort_flag, p.status, 52));
           if (!ok) break;
-          const float om = stats[((half ^ 1) * ATT_TILE + row) * 2], os = stats[((half ^ 1) * ATT_TILE + row) * 2 + 1];
-          // combined in the order (columns 0-63, columns 64-127) by both threads, so that they hold the same bits
-          const float m0 = half ? om : run_max, s0 = half ? os : run_sum, m1 = half ? run_max : om, s1 = half ? run_sum : os;
-          const float mx = fmaxf(m0, m1);
-          const float t0 = m0 > -INFINITY ? s0 * fast_ex2(m0 - mx) : 0.f;
-          const float t1 = m1 > -INFINITY ? s1 * fast_ex2(m1 - mx) : 0.f;
-          const float total = t0 + t1;
+          float mx = -INFINITY;
+#pragma unroll
+          for (int q = 0; q < ATT_MT_PARTS; q++) mx = fmaxf(mx, stats[(q * ATT_TILE + row) * 2]);
+          float total = 0.f;
+#pragma unroll
+          for (int q = 0; q < ATT_MT_PARTS; q++) {
+            const float mq = stats[(q * ATT_TILE + row) * 2], sq = stats[(q * ATT_TILE + row) * 2 + 1];
+            total += mq > -INFINITY ? sq * fast_ex2(mq - mx) : 0.f;
+          }
+          mbar_arrive(bar_x2);
           inv_sum = 1.0f / total;
           max_l2 = mx;
-          if (half == 0 && p.lse && qrow < p.lq) p.lse[(long long)bh * p.lq + qrow] = mx * 0.6931471805599453f + logf(total);
+          if (part == 0 && p.lse && qrow < p.lq) p.lse[(long long)bh * p.lq + qrow] = mx * 0.6931471805599453f + logf(total);
         }
       } else {
         // pass 2: the final probabilities of this thread's columns, staged as the K-major operand of P V
         const int t = g - nk;
 #pragma unroll
-        for (int jj = 0; jj < 64; jj++) v[jj] = to_tf32(fast_ex2(v[jj] - max_l2) * inv_sum);
-        if (t >= 1) ok = mbar_wait(bar_pv, (uint32_t)(t - 1) & 1, abort_flag, p.status, 50);   // the previous P has been consumed
+        for (int jj = 0; jj < 32; jj++) v[jj] = to_tf32(fast_ex2(v[jj] - max_l2) * inv_sum);
+        if (t >= 1) ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (uint32_t)(t - 1) & 1, abort_flag, p.status, 50));   // the previous P has been consumed
+        else ok = __all_sync(0xffffffffu, mbar_wait(bar_x2, 0, abort_flag, p.status, 53));                               // everyone has read the statistics
         if (ok) {
-#pragma unroll
-          for (int c = 0; c < 2; c++) store_seg_kmajor(p_s + (half * 2 + c) * ATT_BLOCK_BYTES, row, v + c * 32);
+          store_seg_kmajor(p_s + part * ATT_BLOCK_BYTES, row, v);
           fence_async_smem();
         }
-        mbar_arrive(bar_p);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p);
       }
     }
     // ---- output: warps 0-3 write columns 0-31, warps 4-7 columns 32-63 (D = 64) ----
     if (ok) ok = mbar_wait(bar_pv, (uint32_t)(nk - 1) & 1, abort_flag, p.status, 51);
     tc_fence_after();
-    if (ok && half < DB) {
+    if (ok && part < DB) {
       float* stg = reinterpret_cast<float*>(p_s) + warp * 32 * 36;          // the last P V product has consumed P
-      float* outp = p.out + (long long)bi * p.o_batch + (long long)hi * p.o_head + half * 32;
+      float* outp = p.out + (long long)bi * p.o_batch + (long long)hi * p.o_head + part * 32;
       uint32_t r[32];
-      tmem_ld_32x32b_x32(lane_base + COL_O + half * 32, r);
+      tmem_ld_32x32b_x32(lane_base + COL_O + part * 32, r);
       tmem_ld_wait();
       store_rows_32(stg, lane, r, outp, p.o_row, q0 + quad * 32, p.lq);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == ATT_MT_ISSUE_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -745,8 +766,8 @@ attention_fwd_mt_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 // output O is at hand it is rowsum(dO O) (the same number, O = P V), taken from the two rows before the first tile and the
 // key tiles are walked once (ONE_PASS); without O a first pass over the key tiles accumulates it and a second pass forms
 // the products again. S and dP are double-buffered in tensor memory (the products of the next tile run under this tile's row
-// pass); each thread owns half a score row of the tile, and a warp turns its 32 x 64 block through shared memory so that the
-// stores to P and dS are whole 256-byte row segments.
+// pass); each thread owns a quarter of a score row of the tile, and a warp turns its 32 x 32 block through shared memory so
+// that the stores to P and dS are whole 128-byte row segments.
 struct AttFrontParams {
   int lq, lk, heads, d;
   float scale;
@@ -761,27 +782,26 @@ struct AttFrontParams {
   int32_t* status;
 };
 
-constexpr int ATT_STG_LD = 68;          // floats per staged row of 64: 16-byte aligned, rows spread over the banks
+constexpr int ATT_STG_LD = 36;          // floats per staged row of 32: 16-byte aligned, rows spread over the banks
 
-// Writes a warp's 32 x 64 block (lane l holds row l in v[0..63]) to dst rows row0 + l, columns col0 .. col0 + 63.
-__device__ __forceinline__ void store_block_64(float* stg, int lane, const float* v, float* dst, long long ld, int row0, int rows_valid, int col0,
+// Writes a warp's 32 x 32 block (lane l holds row l in v[0..31]) to dst rows row0 + l, columns col0 .. col0 + 31.
+__device__ __forceinline__ void store_block_32(float* stg, int lane, const float* v, float* dst, long long ld, int row0, int rows_valid, int col0,
                                                int cols_valid, bool vec_ok) {
 #pragma unroll
-  for (int j = 0; j < 64; j += 4) *reinterpret_cast<float4*>(stg + lane * ATT_STG_LD + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(stg + lane * ATT_STG_LD + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
   __syncwarp();
-  if (vec_ok && col0 + 64 <= cols_valid) {
-    const int c4 = (lane & 15) * 4;
+  if (vec_ok && col0 + 32 <= cols_valid) {
+    const int c4 = (lane & 7) * 4;
 #pragma unroll
-    for (int it = 0; it < 16; it++) {
-      const int r = it * 2 + (lane >> 4);
+    for (int it = 0; it < 8; it++) {
+      const int r = it * 4 + (lane >> 3);
       if (row0 + r < rows_valid)
         *reinterpret_cast<float4*>(dst + (long long)(row0 + r) * ld + col0 + c4) = *reinterpret_cast<const float4*>(stg + r * ATT_STG_LD + c4);
     }
   } else {
     for (int r = 0; r < 32; r++) {
       if (row0 + r >= rows_valid) break;
-      for (int c = lane; c < 64; c += 32)
-        if (col0 + c < cols_valid) dst[(long long)(row0 + r) * ld + col0 + c] = stg[r * ATT_STG_LD + c];
+      if (col0 + lane < cols_valid) dst[(long long)(row0 + r) * ld + col0 + lane] = stg[r * ATT_STG_LD + lane];
     }
   }
   __syncwarp();
@@ -800,9 +820,9 @@ attention_bwd_front_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   uint8_t* g_s = q_s + DB * ATT_BLOCK_BYTES;
   uint8_t* k_s = q_s + 2 * DB * ATT_BLOCK_BYTES;
   uint8_t* v_s = q_s + 3 * DB * ATT_BLOCK_BYTES;
-  float* stage = reinterpret_cast<float*>(q_s + 4 * DB * ATT_BLOCK_BYTES);       // [8 warps][32][ATT_STG_LD]
-  float* stats = stage + 8 * 32 * ATT_STG_LD;                                     // [2 halves][128 rows] partial dots
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 2 * ATT_TILE);
+  float* stage = reinterpret_cast<float*>(q_s + 4 * DB * ATT_BLOCK_BYTES);       // [row warps][32][ATT_STG_LD]
+  float* stats = stage + ATT_MT_ISSUE_WARP * 32 * ATT_STG_LD;                     // [parts][128 rows] partial dots
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + ATT_MT_PARTS * ATT_TILE);
   uint64_t* bar_qg = bars;          // Q and dO landed
   uint64_t* bar_kv = bars + 1;      // K and V tile landed
   uint64_t* bar_s = bars + 2;       // [2] both products complete (and the K, V buffer free)
@@ -821,13 +841,13 @@ attention_bwd_front_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     mbar_init(bar_kv, 1);
     for (int i = 0; i < 2; i++) {
       mbar_init(&bar_s[i], 1);
-      mbar_init(&bar_sr[i], 2 * ATT_TILE);
+      mbar_init(&bar_sr[i], ATT_MT_ISSUE_WARP);   // one arrival per row warp
     }
-    mbar_init(bar_x, 2 * ATT_TILE);
+    mbar_init(bar_x, ATT_MT_PARTS * ATT_TILE);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 8) {
+  if (warp == ATT_MT_ISSUE_WARP) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -838,7 +858,7 @@ attention_bwd_front_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   pdl_trigger();
   pdl_wait();
 
-  if (warp == 8) {
+  if (warp == ATT_MT_ISSUE_WARP) {
     if (lane == 0) {
       const uint32_t idesc = att_idesc(ATT_TILE, false, false);
       const uint32_t qa = smem_u32(q_s), ga = smem_u32(g_s), ka = smem_u32(k_s), va = smem_u32(v_s);
@@ -891,7 +911,7 @@ attention_bwd_front_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       }
     }
   } else {
-    const int quad = warp & 3, half = warp >> 2;
+    const int quad = warp & 3, part = warp >> 2;
     const int row = quad * 32 + lane, qrow = q0 + row;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
     const float LOG2E = 1.4426950408889634f;
@@ -906,76 +926,81 @@ attention_bwd_front_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     float dot = 0.f;
     float d4[4] = {0.f, 0.f, 0.f, 0.f};
     bool ok = true;
-    if (ONE_PASS) {
-      // dot = rowsum(dO O): this thread's half of the head dimension, the halves added in a fixed order
-      float part = 0.f;
-      if (qrow < p.lq) {
-        const float* gr = p.g + (long long)bi * p.g_batch + (long long)hi * p.g_head + (long long)qrow * p.g_row + half * (D / 2);
-        const float* orow = p.o + (long long)bi * p.o_batch + (long long)hi * p.o_head + (long long)qrow * p.o_row + half * (D / 2);
+    auto combine = [&](float mine) -> bool {      // the row's parts added in the order of their column (or head-dimension) ranges
+      stats[part * ATT_TILE + row] = mine;
+      mbar_arrive(bar_x);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_x, 0, abort_flag, p.status, 67))) return false;
+      float t = stats[row];
 #pragma unroll
-        for (int j = 0; j < D / 2; j += 4) {
+      for (int q = 1; q < ATT_MT_PARTS; q++) t += stats[q * ATT_TILE + row];
+      dot = t;
+      return true;
+    };
+    if (ONE_PASS) {
+      // dot = rowsum(dO O): this thread's quarter of the head dimension
+      constexpr int DW = D / ATT_MT_PARTS;
+      float mine = 0.f;
+      if (qrow < p.lq) {
+        const float* gr = p.g + (long long)bi * p.g_batch + (long long)hi * p.g_head + (long long)qrow * p.g_row + part * DW;
+        const float* orow = p.o + (long long)bi * p.o_batch + (long long)hi * p.o_head + (long long)qrow * p.o_row + part * DW;
+#pragma unroll
+        for (int j = 0; j < DW; j += 4) {
           const float4 a = *reinterpret_cast<const float4*>(gr + j), b = *reinterpret_cast<const float4*>(orow + j);
           d4[0] = fmaf(a.x, b.x, d4[0]); d4[1] = fmaf(a.y, b.y, d4[1]); d4[2] = fmaf(a.z, b.z, d4[2]); d4[3] = fmaf(a.w, b.w, d4[3]);
         }
-        part = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+        mine = (d4[0] + d4[1]) + (d4[2] + d4[3]);
       }
-      stats[half * ATT_TILE + row] = part;
-      mbar_arrive(bar_x);
-      ok = mbar_wait(bar_x, 0, abort_flag, p.status, 67);
-      if (ok) dot = stats[row] + stats[ATT_TILE + row];
+      ok = combine(mine);
     }
-    float pv[64], dp[64];
+    float pv[32], dp[32];
     for (int g = 0; g < steps && ok; g++) {
-      const int i = g & 1, j = g % nk, col0 = j * ATT_TILE + half * 64;
-      ok = mbar_wait(&bar_s[i], (uint32_t)(g >> 1) & 1, abort_flag, p.status, 66);
+      const int i = g & 1, j = g % nk, col0 = j * ATT_TILE + part * 32;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar_s[i], (uint32_t)(g >> 1) & 1, abort_flag, p.status, 66));
       if (!ok) break;
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; c++) {
+      {
         uint32_t rs[32], rd[32];
-        tmem_ld_32x32b_x32(lane_base + (uint32_t)(i * ATT_TILE + half * 64 + c * 32), rs);
-        tmem_ld_32x32b_x32(lane_base + COL_DP + (uint32_t)(i * ATT_TILE + half * 64 + c * 32), rd);
+        tmem_ld_32x32b_x32(lane_base + (uint32_t)(i * ATT_TILE + part * 32), rs);
+        tmem_ld_32x32b_x32(lane_base + COL_DP + (uint32_t)(i * ATT_TILE + part * 32), rd);
         tmem_ld_wait();
-        if (mrow == nullptr && col0 + 64 <= p.lk) {
+        if (mrow == nullptr && col0 + 32 <= p.lk) {
 #pragma unroll
           for (int jj = 0; jj < 32; jj++) {
-            pv[c * 32 + jj] = fast_ex2(fmaf(__uint_as_float(rs[jj]), sl2, -lse_l));
-            dp[c * 32 + jj] = __uint_as_float(rd[jj]);
+            pv[jj] = fast_ex2(fmaf(__uint_as_float(rs[jj]), sl2, -lse_l));
+            dp[jj] = __uint_as_float(rd[jj]);
           }
         } else {
 #pragma unroll
           for (int jj = 0; jj < 32; jj++) {
-            const int col = col0 + c * 32 + jj;
+            const int col = col0 + jj;
             float e = 0.f;
             if (col < p.lk) e = fast_ex2(fmaf(__uint_as_float(rs[jj]), sl2, (mrow ? mrow[col] * LOG2E : 0.f) - lse_l));
-            pv[c * 32 + jj] = e;
-            dp[c * 32 + jj] = __uint_as_float(rd[jj]);
+            pv[jj] = e;
+            dp[jj] = __uint_as_float(rd[jj]);
           }
         }
       }
       tc_fence_before();
-      mbar_arrive(&bar_sr[i]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_sr[i]);
       if (!ONE_PASS && g < nk) {
 #pragma unroll
-        for (int jj = 0; jj < 64; jj++) d4[jj & 3] = fmaf(pv[jj], dp[jj], d4[jj & 3]);
+        for (int jj = 0; jj < 32; jj++) d4[jj & 3] = fmaf(pv[jj], dp[jj], d4[jj & 3]);
         if (g == nk - 1) {
-          stats[half * ATT_TILE + row] = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-          mbar_arrive(bar_x);
-          ok = mbar_wait(bar_x, 0, abort_flag, p.status, 67);
+          ok = combine((d4[0] + d4[1]) + (d4[2] + d4[3]));
           if (!ok) break;
-          dot = stats[row] + stats[ATT_TILE + row];
         }
       } else {
-        store_block_64(stg, lane, pv, p_mat, p.lk, q0 + quad * 32, p.lq, col0, p.lk, vec_ok);
+        store_block_32(stg, lane, pv, p_mat, p.lk, q0 + quad * 32, p.lq, col0, p.lk, vec_ok);
 #pragma unroll
-        for (int jj = 0; jj < 64; jj++) dp[jj] = (pv[jj] * (dp[jj] - dot)) * p.scale;      // dS
-        store_block_64(stg, lane, dp, ds_mat, p.lk, q0 + quad * 32, p.lq, col0, p.lk, vec_ok);
+        for (int jj = 0; jj < 32; jj++) dp[jj] = (pv[jj] * (dp[jj] - dot)) * p.scale;      // dS
+        store_block_32(stg, lane, dp, ds_mat, p.lk, q0 + quad * 32, p.lq, col0, p.lk, vec_ok);
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == ATT_MT_ISSUE_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -1024,7 +1049,7 @@ int32_t attention_tc_fwd(om_ctx* ctx, const float* q, const om_head_strides* qs,
   p.out = out; p.o_batch = os->batch; p.o_head = os->head; p.o_row = os->row; p.lse = lse; p.status = ctx->status_dev;
   if (lq > ATT_TILE || lk > ATT_TILE) {
     // Several tiles: one CTA per 128 queries walks the key tiles (two passes, see attention_fwd_mt_kernel).
-    const size_t smem_mt = (size_t)(4 * (d / 32) + 4) * ATT_BLOCK_BYTES + 1024 + 4 * ATT_TILE * sizeof(float) + 256;
+    const size_t smem_mt = (size_t)(5 * (d / 32) + 4) * ATT_BLOCK_BYTES + 1024 + 256;
     const dim3 grid_mt((unsigned)((lq + ATT_TILE - 1) / ATT_TILE), (unsigned)(b * h));
     if (d == 32) {
       static bool set = false;
@@ -1144,7 +1169,7 @@ int32_t attention_bwd_front(om_ctx* ctx, const float* g, const om_head_strides* 
   p.g = g; p.g_batch = gs->batch; p.g_head = gs->head; p.g_row = gs->row;
   p.o = one_pass ? o : nullptr; p.o_batch = one_pass ? os->batch : 0; p.o_head = one_pass ? os->head : 0; p.o_row = one_pass ? os->row : 0;
   p.p_out = p_out; p.ds_out = ds_out; p.status = ctx->status_dev;
-  const size_t smem = (size_t)(4 * (d / 32)) * ATT_BLOCK_BYTES + 1024 + (8 * 32 * ATT_STG_LD + 2 * ATT_TILE) * sizeof(float) + 256;
+  const size_t smem = (size_t)(4 * (d / 32)) * ATT_BLOCK_BYTES + 1024 + (ATT_MT_ISSUE_WARP * 32 * ATT_STG_LD + ATT_MT_PARTS * ATT_TILE) * sizeof(float) + 256;
   const dim3 grid((unsigned)((lq + ATT_TILE - 1) / ATT_TILE), (unsigned)(b * h));
   int32_t st;
   if (d == 32) st = one_pass ? launch_front<32, true>(ctx, grid, smem, mq, mg, mk, mv, p) : launch_front<32, false>(ctx, grid, smem, mq, mg, mk, mv, p);

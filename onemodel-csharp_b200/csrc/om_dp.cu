@@ -152,6 +152,18 @@ int32_t om_dp_allreduce(om_ctx* ctx, void* buf, int64_t count, int32_t dtype) {
   return OM_OK;
 }
 
+int32_t om_dp_wait_bucket(om_ctx* ctx, int32_t bucket_id) {
+  OM_CHECK_CTX(ctx);
+  DpState* dp = ctx->dp;
+  if (!dp) return OM_OK;
+  if (bucket_id < 0 || (size_t)bucket_id >= dp->buckets.size()) return fail(ctx, OM_ERR_ARG, "om_dp_wait_bucket: unknown bucket %d", bucket_id);
+  Bucket& b = dp->buckets[bucket_id];
+  if (!b.in_flight) return OM_OK;
+  OM_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, b.done, 0));
+  b.in_flight = false;
+  return OM_OK;
+}
+
 int32_t om_dp_wait(om_ctx* ctx, int32_t timeout_ms) {
   OM_CHECK_CTX(ctx);
   DpState* dp = ctx->dp;

@@ -424,6 +424,10 @@ class Optimizer {
   virtual size_t HyperBytes() const = 0;
   virtual void FillHyper(void* host, int64_t step) const = 0;  // scalars for the given 1-based step
   virtual std::vector<Tensor> StateTensors() const = 0;
+  // Step() in groups of parameters (positions in Parameters()): `before(g)` runs before group g is launched. The data-parallel
+  // trainer waits there for the group's gradient bucket, so that the update of early buckets overlaps the reduction of the
+  // late ones. Every parameter gets the same update as from Step().
+  void StepGroups(const std::vector<std::vector<int>>& groups, const std::function<void(int)>& before);
   // What a checkpoint stores (Checkpoint.cs, docs/training.md section 6 of the reference): the kind string, the
   // hyper-parameters in the reference's order, and the state tensors named slot.index in the reference's order. An entry
   // with a null tensor is the Int32 flag vector `flags` (Sgd's "initialized").

@@ -41,6 +41,29 @@ void Optimizer::Step() {
   StepCount++;
 }
 
+void Optimizer::StepGroups(const std::vector<std::vector<int>>& groups, const std::function<void(int)>& before) {
+  BeginStep();
+  for (size_t gi = 0; gi < groups.size(); gi++) {
+    std::vector<float*> p;
+    std::vector<const float*> g;
+    std::vector<int64_t> len;
+    index_.clear();
+    for (int i : groups[gi]) {
+      const Tensor& t = params_[(size_t)i];
+      if (!t.RequiresGrad()) continue;
+      Tensor grad = t.Grad();
+      if (grad.IsEmpty()) continue;
+      p.push_back(t.Data());
+      g.push_back(grad.Data());
+      len.push_back(t.Length());
+      index_.push_back(i);
+    }
+    if (before) before((int)gi);
+    if (!p.empty()) Launch(p, g, len);
+  }
+  StepCount++;
+}
+
 // ---- SGD ------------------------------------------------------------------------------------------------------------
 Sgd::Sgd(std::vector<Tensor> parameters, float lr, float momentum, float dampening, float weightDecay, bool nesterov)
     : Optimizer(std::move(parameters)), momentum_(momentum), dampening_(dampening), nesterov_(nesterov) {

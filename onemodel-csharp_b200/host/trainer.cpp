@@ -179,6 +179,8 @@ struct omh_trainer {
   struct BucketInfo { int64_t begin, end; int pending; int total; };
   std::vector<BucketInfo> buckets;
   std::map<AutogradMeta*, int> bucket_of;
+  std::vector<std::vector<int>> bucket_params;   // positions in the optimizer's parameter list, per bucket
+  int loss_bucket = -1;                          // the loss scalar rides on the communication stream as a bucket of one
 };
 
 static void BuildFlatGrads(omh_trainer* t) {
@@ -260,6 +262,7 @@ static void StepBody(omh_trainer* t) {
   ActivationScope scope;
   Tensor loss = Forward(t);
   Check(om_memcpy_d2d(ctx, t->loss_out.RawData(), loss.RawData(), 4));
+  if (t->world > 1) Check(om_dp_allreduce_bucket(ctx, t->loss_bucket));   // summed beside the backward pass
   t->opt->ZeroGrad();
   if (t->world > 1) {
     for (auto& b : t->buckets) b.pending = b.total;
@@ -276,7 +279,13 @@ static void StepBody(omh_trainer* t) {
     // Buckets whose parameters got no gradient this step are still exchanged so that all ranks agree.
     for (size_t i = 0; i < t->buckets.size(); i++)
       if (t->buckets[i].pending > 0) Check(om_dp_allreduce_bucket(ctx, (int32_t)i));
-    Check(om_dp_allreduce(ctx, t->loss_out.RawData(), 1, OM_F32));
+    if (t->clip_norm <= 0.f) {
+      // No global norm to wait for: each bucket's parameters are updated as soon as that bucket's sum has arrived, while
+      // the later buckets (the embedding table comes last) are still on the wire.
+      t->opt->StepGroups(t->bucket_params, [&](int b) { Check(om_dp_wait_bucket(ctx, b)); });
+      Check(om_dp_wait(ctx, 0));
+      return;
+    }
     Check(om_dp_wait(ctx, 0));
   }
   if (t->clip_norm > 0.f) GradClip::ClipNormAsync(t->opt->Parameters(), t->clip_norm, false, nullptr);
@@ -403,6 +412,13 @@ OMH_API int32_t omh_trainer_dp_init(omh_trainer* t, const uint8_t* id128, int32_
     t->ce_denominator = (float)global_rows;
     for (size_t i = 0; i < t->buckets.size(); i++)
       Check(om_dp_register_bucket(ctx, (int32_t)i, t->flat_grads.Data() + t->buckets[i].begin, t->buckets[i].end - t->buckets[i].begin));
+    t->loss_bucket = (int)t->buckets.size();
+    Check(om_dp_register_bucket(ctx, t->loss_bucket, t->loss_out.Data(), 1));
+    t->bucket_params.assign(t->buckets.size(), {});
+    for (size_t i = 0; i < t->params.size(); i++) {
+      auto it = t->bucket_of.find(t->params[i].second.Autograd().get());
+      if (it != t->bucket_of.end()) t->bucket_params[(size_t)it->second].push_back((int)i);
+    }
   });
 }
 
