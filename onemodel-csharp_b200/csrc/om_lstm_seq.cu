@@ -222,6 +222,7 @@ __global__ void __launch_bounds__(kSeqThreads) lstm_seq_bwd_kernel(const LstmSeq
   const int kspan4 = H4 / 4 / 8;
   const size_t bh = (size_t)B * H;
   unsigned* counter = D.counter + blockIdx.y;
+  float pre[7] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int s = 0; s < T; s++) {
     const int tt = D.reverse ? s : T - 1 - s;
     const int pt = D.reverse ? tt + 1 : tt - 1;
@@ -229,20 +230,27 @@ __global__ void __launch_bounds__(kSeqThreads) lstm_seq_bwd_kernel(const LstmSeq
     const float* cp = first ? D.c0 : D.c + (size_t)pt * bh;
     const float* gates_t = D.gates + (size_t)tt * B * H4;
     float* dg_t = D.dG + (size_t)tt * B * H4;
-    // Gate gradients of this CTA's units (BackwardRecurrent.cs:37-57 of the reference, the same operation order).
+    // Gate gradients of this CTA's units (BackwardRecurrent.cs:37-57 of the reference, the same operation order). With one
+    // pass per CTA the step's saved values were fetched ahead (they do not depend on dh), under the previous step's product.
     for (int pass = 0; pass < p.passes; pass++) {
       const int b = row_base + pass * kSeqRows + cr;
       if (b >= B) continue;
       const int e = (pass * kSeqRows + cr) * kSeqUnits + cj, jg = j0 + cj;
       const size_t idx = (size_t)b * H + jg;
-      const float* g = gates_t + (size_t)b * H4;
       float* d = dg_t + (size_t)b * H4;
-      const float gi = g[jg], gf = g[H + jg], gg = g[2 * H + jg], go = g[3 * H + jg];
-      const float tc = D.tanh_c[(size_t)tt * bh + idx];
-      const float dH = D.gy[(size_t)tt * bh + idx] + dh_s[e];
+      float gi, gf, gg, go, tc, gyv, cpv;
+      if (p.passes == 1 && s > 0) {
+        gi = pre[0]; gf = pre[1]; gg = pre[2]; go = pre[3]; tc = pre[4]; gyv = pre[5]; cpv = pre[6];
+      } else {
+        const float* g = gates_t + (size_t)b * H4;
+        gi = g[jg]; gf = g[H + jg]; gg = g[2 * H + jg]; go = g[3 * H + jg];
+        tc = D.tanh_c[(size_t)tt * bh + idx];
+        gyv = D.gy[(size_t)tt * bh + idx];
+        cpv = cp ? cp[idx] : 0.f;
+      }
+      const float dH = gyv + dh_s[e];
       const float dO = dH * tc;
       const float dC = dc_s[e] + ((dH * go) * (1.f - (tc * tc)));
-      const float cpv = cp ? cp[idx] : 0.f;
       const float dI = dC * gg, dF = dC * cpv, dGg = dC * gi;
       dc_s[e] = dC * gf;
       d[jg] = (dI * gi) * (1.f - gi);
@@ -252,6 +260,22 @@ __global__ void __launch_bounds__(kSeqThreads) lstm_seq_bwd_kernel(const LstmSeq
     }
     if (s == T - 1 && D.dh0 == nullptr) break;
     if (!seq_barrier(counter, (unsigned)(s + 1) * gridDim.x, p.status, &failed, 9200 + (int)blockIdx.z)) return;
+    if (p.passes == 1 && s + 1 < T) {
+      // the next step's saved values: issued now, used after the product below
+      const int b = row_base + cr;
+      if (b < B) {
+        const int tn = D.reverse ? s + 1 : T - 2 - s;
+        const int pn = D.reverse ? tn + 1 : tn - 1;
+        const bool first_n = D.reverse ? tn == T - 1 : tn == 0;
+        const size_t idx = (size_t)b * H + j0 + cj;
+        const float* g = D.gates + ((size_t)tn * B + b) * H4;
+        pre[0] = g[j0 + cj]; pre[1] = g[H + j0 + cj]; pre[2] = g[2 * H + j0 + cj]; pre[3] = g[3 * H + j0 + cj];
+        pre[4] = D.tanh_c[(size_t)tn * bh + idx];
+        pre[5] = D.gy[(size_t)tn * bh + idx];
+        const float* cpn = first_n ? D.c0 : D.c + (size_t)pn * bh;
+        pre[6] = cpn ? cpn[idx] : 0.f;
+      }
+    }
     // dh of the next processed step, this CTA's units: dG_t[b, :] . W_hh[:, j]
     for (int pass = 0; pass < p.passes; pass++) {
       const int r0 = row_base + pass * kSeqRows;

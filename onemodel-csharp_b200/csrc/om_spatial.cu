@@ -48,17 +48,19 @@ static bool conv_geom(const om_conv_shape* s, ConvGeom* g) {
 // The element of tap row k, image n, pixel p sits at k * k_stride + n * n_stride + p: (P, K*P) is the per-image layout
 // [N][K][P], (N*P, P) the all-images layout [K][N*P]. blockIdx.y is the tap row; a thread owns VEC consecutive pixels
 // of one image (VEC == 4 needs P, the strides and the base to be multiples of four: one 16-byte store).
-template <int VEC>
+// IDX is the type of the pixel counter: int when N * P fits 31 bits (the 64-bit divisions are most of the kernel otherwise).
+template <int VEC, typename IDX>
 __global__ void __launch_bounds__(256)
 im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __restrict__ cols, int64_t pixels_all, int64_t k_stride, int64_t n_stride) {
   const int plane = g.oh * g.ow;
   const int kidx = blockIdx.y;
   const int kx = kidx % g.kw, ky = (kidx / g.kw) % g.kh, c = kidx / (g.kw * g.kh);
-  int64_t q0 = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * VEC;
-  int64_t qstride = (int64_t)gridDim.x * blockDim.x * VEC;
-  for (int64_t q = q0; q < pixels_all; q += qstride) {
-    const int n = (int)(q / plane);
-    const int p = (int)(q - (int64_t)n * plane);
+  IDX q0 = (IDX)((blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * VEC);
+  const int64_t qstride = (int64_t)gridDim.x * blockDim.x * VEC;
+  for (int64_t q64 = q0; q64 < pixels_all; q64 += qstride) {
+    const IDX q = (IDX)q64;
+    const int n = (int)(q / (IDX)plane);
+    const int p = (int)(q - (IDX)n * (IDX)plane);
     const float* xc = x + ((int64_t)n * g.cin + c) * g.h * g.w;
     float v[VEC];
     if (VEC == 4 && (g.ow & 3) == 0) {
@@ -89,17 +91,20 @@ im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __restrict__ cols,
 }
 
 // dx[n][c][iy][ix] = sum over (ky, kx) in increasing order of dcols[(c,ky,kx)][n][oy*OW+ox] where the tap lands on (iy, ix).
-// blockIdx.y = channel, blockIdx.z = image, threads over the input plane.
 // S is the stride when both strides equal it (1 or 2: the divisions become shifts), 0 for the general case.
-template <int S>
+template <int S, typename IDX>
 __global__ void __launch_bounds__(256)
-col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restrict__ dx, int64_t k_stride, int64_t n_stride) {
-  const int c = blockIdx.y, n = blockIdx.z;
+col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restrict__ dx, int64_t k_stride, int64_t n_stride, int64_t total) {
   const int sh = S ? S : g.sh, sw = S ? S : g.sw;
   const int hw = g.h * g.w;
-  const float* base = dcols + (int64_t)n * n_stride + (int64_t)c * g.kh * g.kw * k_stride;
-  float* out = dx + ((int64_t)n * g.cin + c) * hw;
-  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < hw; e += gridDim.x * blockDim.x) {
+  // One thread per input element over all images and channels (planes of a deep layer are a few dozen elements: a CTA per
+  // plane would idle most of its threads).
+  for (int64_t t64 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t64 < total; t64 += (int64_t)gridDim.x * blockDim.x) {
+    const IDX t = (IDX)t64;
+    const IDX pl = t / (IDX)hw;
+    const int e = (int)(t - pl * (IDX)hw);
+    const int n = (int)(pl / (IDX)g.cin), c = (int)(pl - (IDX)n * (IDX)g.cin);
+    const float* base = dcols + (int64_t)n * n_stride + (int64_t)c * g.kh * g.kw * k_stride;
     const int iy = e / g.w, ix = e - iy * g.w;
     float acc = 0.f;
     for (int ky = 0; ky < g.kh; ky++) {
@@ -115,14 +120,18 @@ col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restr
         acc += base[(int64_t)(ky * g.kw + kx) * k_stride + oy * g.ow + ox];
       }
     }
-    out[e] = acc;
+    dx[t64] = acc;
   }
 }
 
-static void launch_col2im(om_ctx* ctx, dim3 grid, const ConvGeom& g, const float* dcols, float* dx, int64_t k_stride, int64_t n_stride) {
-  if (g.sh == 1 && g.sw == 1) col2im_gather_kernel<1><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride);
-  else if (g.sh == 2 && g.sw == 2) col2im_gather_kernel<2><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride);
-  else col2im_gather_kernel<0><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride);
+static void launch_col2im(om_ctx* ctx, const ConvGeom& g, const float* dcols, float* dx, int64_t k_stride, int64_t n_stride) {
+  const int64_t total = (int64_t)g.n * g.cin * g.h * g.w;
+  const int grid = grid_for(ctx, total, 256);
+  const bool small = total < (int64_t)INT32_MAX;
+  if (g.sh == 1 && g.sw == 1 && small) col2im_gather_kernel<1, int><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
+  else if (g.sh == 2 && g.sw == 2 && small) col2im_gather_kernel<2, int><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
+  else if (small) col2im_gather_kernel<0, int><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
+  else col2im_gather_kernel<0, int64_t><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
 }
 
 __global__ void add_plane_bias_kernel(float* __restrict__ y, const float* __restrict__ bias, int cout, int plane, int64_t total) {
@@ -226,13 +235,18 @@ static bool pool_out(int size, int kernel, int stride, int pad, int* out) {
 }
 
 // First maximum wins ties, NaN wins over numbers (ReferenceKernels.MaxPool2d, TensorKernels.cs:242-295).
+// IDX: int when the input has fewer than 2^31 elements (32-bit divisions).
+template <typename IDX>
 __global__ void maxpool_fwd_kernel(PoolGeom g, const float* __restrict__ x, int64_t total, float* __restrict__ y, int32_t* __restrict__ idx) {
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t e = i; e < total; e += stride) {
-    int ox = (int)(e % g.ow), oy = (int)((e / g.ow) % g.oh);
-    int64_t pl = e / ((int64_t)g.ow * g.oh);
-    const float* xp = x + pl * g.h * g.w;
+    const IDX e32 = (IDX)e;
+    const IDX row = e32 / (IDX)g.ow;
+    int ox = (int)(e32 - row * (IDX)g.ow);
+    const IDX pl = row / (IDX)g.oh;
+    int oy = (int)(row - pl * (IDX)g.oh);
+    const float* xp = x + (int64_t)pl * g.h * g.w;
     float best = -INFINITY;
     int bestIdx = -1;
     for (int ky = 0; ky < g.kh; ky++) {
@@ -462,8 +476,11 @@ static int32_t unfold(om_ctx* ctx, const ConvGeom& g, const float* x, float** co
     const bool vec = (plane & 3) == 0;
     dim3 grid((unsigned)std::min<int64_t>(ceil_div(pixels_all, vec ? 1024 : 256), 65535), (unsigned)kk_all);
     const int64_t ks = all_images ? pixels_all : plane, ns = all_images ? plane : kk_all * plane;
-    if (vec) im2col_kernel<4><<<grid, 256, 0, ctx->stream>>>(g, x, *cols, pixels_all, ks, ns);
-    else im2col_kernel<1><<<grid, 256, 0, ctx->stream>>>(g, x, *cols, pixels_all, ks, ns);
+    const bool small = pixels_all + 4 < (int64_t)INT32_MAX;
+    if (vec && small) im2col_kernel<4, int><<<grid, 256, 0, ctx->stream>>>(g, x, *cols, pixels_all, ks, ns);
+    else if (vec) im2col_kernel<4, int64_t><<<grid, 256, 0, ctx->stream>>>(g, x, *cols, pixels_all, ks, ns);
+    else if (small) im2col_kernel<1, int><<<grid, 256, 0, ctx->stream>>>(g, x, *cols, pixels_all, ks, ns);
+    else im2col_kernel<1, int64_t><<<grid, 256, 0, ctx->stream>>>(g, x, *cols, pixels_all, ks, ns);
   }
   return OM_OK;
 }
@@ -554,8 +571,7 @@ int32_t om_conv2d_dgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, co
     // dcols [K, N*P] = W^T [K, Cout] * g_t [Cout, N*P]
     if (st == OM_OK) st = gemm_tc(ctx, 1, 0, kk, np, g.cout, w, kk, gt, np, dcols, np, 0, nullptr);
     if (st == OM_OK) {
-      dim3 cgrid((unsigned)std::min<int64_t>(ceil_div((int64_t)g.h * g.w, 256), 64), (unsigned)g.cin, (unsigned)g.n);
-      launch_col2im(ctx, cgrid, g, dcols, dx, np, plane);
+      launch_col2im(ctx, g, dcols, dx, np, plane);
     }
     if (gt) pool_free(ctx, gt);
     pool_free(ctx, dcols);
@@ -570,8 +586,7 @@ int32_t om_conv2d_dgrad(om_ctx* ctx, const om_conv_shape* s, const float* gr, co
                    (int64_t)g.cout * plane, dcols + (size_t)grp * kk * plane, plane, (int64_t)g.groups * kk * plane, g.n, 0);
   }
   if (st == OM_OK) {
-    dim3 cgrid((unsigned)std::min<int64_t>(ceil_div((int64_t)g.h * g.w, 256), 64), (unsigned)g.cin, (unsigned)g.n);
-    launch_col2im(ctx, cgrid, g, dcols, dx, plane, (int64_t)g.cin * g.kh * g.kw * plane);
+    launch_col2im(ctx, g, dcols, dx, plane, (int64_t)g.cin * g.kh * g.kw * plane);
   }
   pool_free(ctx, dcols);
   OM_TRY(st);
@@ -688,7 +703,8 @@ int32_t om_maxpool_fwd(om_ctx* ctx, const float* x, int32_t planes, int32_t h, i
   int64_t total = (int64_t)planes * g.oh * g.ow;
   if (total <= 0) return OM_OK;
   ProfileScope prof(ctx, "om_maxpool_fwd", 0, 4.0 * planes * ((double)h * w + 2.0 * g.oh * g.ow));
-  maxpool_fwd_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, x, total, y, idx);
+  if ((int64_t)planes * h * w < (int64_t)INT32_MAX) maxpool_fwd_kernel<int><<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, x, total, y, idx);
+  else maxpool_fwd_kernel<int64_t><<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(g, x, total, y, idx);
   OM_LAUNCH_CHECK(ctx, "om_maxpool_fwd");
   return OM_OK;
 }
