@@ -92,18 +92,25 @@ im2col_kernel(ConvGeom g, const float* __restrict__ x, float* __restrict__ cols,
 
 // dx[n][c][iy][ix] = sum over (ky, kx) in increasing order of dcols[(c,ky,kx)][n][oy*OW+ox] where the tap lands on (iy, ix).
 // S is the stride when both strides equal it (1 or 2: the divisions become shifts), 0 for the general case.
-template <int S, typename IDX>
+// PLANES: blockIdx.y = channel, blockIdx.z = image, threads over the input plane (no per-element plane arithmetic: the
+// layout for planes of hundreds of elements and more). Otherwise one thread per input element over all images and
+// channels: the planes of a deep layer are a few dozen elements, and a CTA per plane would idle most of its threads.
+template <int S, bool PLANES>
 __global__ void __launch_bounds__(256)
-col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restrict__ dx, int64_t k_stride, int64_t n_stride, int64_t total) {
+col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restrict__ dx, int64_t k_stride, int64_t n_stride, int total) {
   const int sh = S ? S : g.sh, sw = S ? S : g.sw;
   const int hw = g.h * g.w;
-  // One thread per input element over all images and channels (planes of a deep layer are a few dozen elements: a CTA per
-  // plane would idle most of its threads).
-  for (int64_t t64 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t64 < total; t64 += (int64_t)gridDim.x * blockDim.x) {
-    const IDX t = (IDX)t64;
-    const IDX pl = t / (IDX)hw;
-    const int e = (int)(t - pl * (IDX)hw);
-    const int n = (int)(pl / (IDX)g.cin), c = (int)(pl - (IDX)n * (IDX)g.cin);
+  const int limit = PLANES ? hw : total;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < limit; t += gridDim.x * blockDim.x) {
+    int e, n, c;
+    if (PLANES) {
+      e = t; c = blockIdx.y; n = blockIdx.z;
+    } else {
+      const int pl = t / hw;
+      e = t - pl * hw;
+      n = pl / g.cin;
+      c = pl - n * g.cin;
+    }
     const float* base = dcols + (int64_t)n * n_stride + (int64_t)c * g.kh * g.kw * k_stride;
     const int iy = e / g.w, ix = e - iy * g.w;
     float acc = 0.f;
@@ -120,18 +127,26 @@ col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restr
         acc += base[(int64_t)(ky * g.kw + kx) * k_stride + oy * g.ow + ox];
       }
     }
-    dx[t64] = acc;
+    dx[((int64_t)n * g.cin + c) * hw + e] = acc;
   }
 }
 
+template <bool PLANES>
+static void launch_col2im_as(om_ctx* ctx, dim3 grid, const ConvGeom& g, const float* dcols, float* dx, int64_t k_stride, int64_t n_stride, int total) {
+  if (g.sh == 1 && g.sw == 1) col2im_gather_kernel<1, PLANES><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
+  else if (g.sh == 2 && g.sw == 2) col2im_gather_kernel<2, PLANES><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
+  else col2im_gather_kernel<0, PLANES><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
+}
+
 static void launch_col2im(om_ctx* ctx, const ConvGeom& g, const float* dcols, float* dx, int64_t k_stride, int64_t n_stride) {
-  const int64_t total = (int64_t)g.n * g.cin * g.h * g.w;
-  const int grid = grid_for(ctx, total, 256);
-  const bool small = total < (int64_t)INT32_MAX;
-  if (g.sh == 1 && g.sw == 1 && small) col2im_gather_kernel<1, int><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
-  else if (g.sh == 2 && g.sw == 2 && small) col2im_gather_kernel<2, int><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
-  else if (small) col2im_gather_kernel<0, int><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
-  else col2im_gather_kernel<0, int64_t><<<grid, 256, 0, ctx->stream>>>(g, dcols, dx, k_stride, n_stride, total);
+  const int hw = g.h * g.w;
+  const int64_t total = (int64_t)g.n * g.cin * hw;
+  if (hw < 256 && total < (int64_t)INT32_MAX) {
+    launch_col2im_as<false>(ctx, dim3((unsigned)grid_for(ctx, total, 256)), g, dcols, dx, k_stride, n_stride, (int)total);
+  } else {
+    dim3 grid((unsigned)std::min<int64_t>(ceil_div(hw, 256), 64), (unsigned)g.cin, (unsigned)g.n);
+    launch_col2im_as<true>(ctx, grid, g, dcols, dx, k_stride, n_stride, 0);
+  }
 }
 
 __global__ void add_plane_bias_kernel(float* __restrict__ y, const float* __restrict__ bias, int cout, int plane, int64_t total) {
