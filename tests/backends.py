@@ -180,6 +180,12 @@ def load_fixture(group, name):
     return out
 
 
+def load_fixture_manifest(group, name):
+    """The JSON beside a reference fixture (generator version, seed, per-case settings)."""
+    import json
+    return json.load(open(os.path.join(ROOT, "tests", "golden", "reference_testdata", group, name + ".json")))
+
+
 def scaled_diff(a, ref):
     """max|a - ref| / max|ref| : the reference tests' metric (tests/OneModel.Tests/Tensors/AutogradModelTests.cs:61-81)."""
     a, ref = np.asarray(a, np.float64), np.asarray(ref, np.float64)

@@ -53,12 +53,15 @@ def train_mlp(B, fx, steps=None):
     return np.array(losses, np.float32), {k: B.numpy(v) for k, v in p.items()}
 
 
-def train_encoder(B, fx, steps=None):
+def train_encoder(B, fx, steps=None, frozen=()):
     """testdata/training/encoder: embedding + 2 encoder layers + mean pool + classifier, Adam lr 2e-3 with a linear
-    warm-up from 0.1 over 10 steps, batch 16, 80 steps."""
-    w = {k[3:]: B.tensor(v, True) for k, v in fx.items() if k.startswith("in.") and k[3:] not in ("ids", "y", "order")}
+    warm-up from 0.1 over 10 steps, batch 16, 80 steps. Parameters whose name is in `frozen` or starts with one of its
+    entries plus a dot do not require gradients and are not given to the optimizer (NnModule.Freeze of the reference,
+    tests/OneModel.Tests/Training/SparseAndFrozenTests.cs:48-56)."""
     names = [k[3:] for k in fx if k.startswith("in.") and k[3:] not in ("ids", "y", "order")]
-    opt = B.optimizer("adam", [w[k] for k in names], 2e-3)
+    is_frozen = lambda n: any(n == f or n.startswith(f + ".") for f in frozen)
+    w = {k: B.tensor(fx["in." + k], not is_frozen(k)) for k in names}
+    opt = B.optimizer("adam", [w[k] for k in names if not is_frozen(k)], 2e-3)
     ids, y, order = fx["in.ids"].astype(np.int64), fx["in.y"].astype(np.int64), fx["in.order"].astype(np.int64)
     peak, warm = 2e-3, 10
     losses = []
@@ -205,6 +208,55 @@ def conv1d_case(B, case, seed=0):
     if has_bias:
         leaves["b"] = b
     return loss, y, leaves
+
+
+def conv1d_grid_params(case, k):
+    """(stride, pad_left, pad_right, dilation, groups) of one case of testdata/conv1d/grid.json: a number pads both sides,
+    "same" splits dilation*(k-1) with the odd zero on the right, "valid" pads nothing (Conv1dParams.Symmetric / Same,
+    Ops.Nn.cs:12-26; tests/OneModel.Tests/Training/Conv1dTests.cs:22-41 of the reference)."""
+    stride, dil, groups, pad = case["stride"], case["dilation"], case["groups"], case["padding"]
+    if isinstance(pad, int):
+        return stride, pad, pad, dil, groups
+    if pad == "same":
+        total = max(dil, 1) * (k - 1)
+        return 1, total // 2, total - total // 2, dil, groups
+    return 1, 0, 0, dil, groups
+
+
+def conv1d_grid_case(B, fx, i, case):
+    """Case i of testdata/conv1d/grid: y = Conv1d(x, w, b), loss = sum(y * r); returns y and the leaves
+    (Conv1dTests.cs:76-88 of the reference)."""
+    pre = f"c{i}."
+    x, w = B.tensor(fx[pre + "in.x"], True), B.tensor(fx[pre + "in.w"], True)
+    b = B.tensor(fx[pre + "in.b"], True) if case["bias"] else None
+    y = B.conv1d(x, w, b, *conv1d_grid_params(case, fx[pre + "in.w"].shape[2]))
+    loss = B.sum(B.mul(y, B.tensor(fx[pre + "in.r"])))
+    leaves = {"x": x, "w": w}
+    if b is not None:
+        leaves["b"] = b
+    return loss, y, leaves
+
+
+def train_conv1d(B, fx):
+    """testdata/conv1d/train: Conv1d(4,6,3,"same",dilation 2) - ReLU - Conv1d(6,6,3,stride 2,padding 1,groups 2) - ReLU -
+    mean over length - Linear(6,3); cross entropy; SGD lr 0.05 momentum 0.9; 20 steps of 8 samples in the recorded order
+    (Conv1dTests.cs:258-307 of the reference). Returns the losses and the final parameters."""
+    names = ("c1w", "c1b", "c2w", "c2b", "fcw", "fcb")
+    p = {k: B.tensor(fx["in." + k], True) for k in names}
+    opt = B.optimizer("sgd", [p[k] for k in names], 0.05, momentum=0.9)
+    order = fx["in.order"].astype(np.int64)
+    losses = []
+    for s in range(order.shape[0]):
+        x = B.tensor(fx["in.x"][order[s]])
+        t = B.ids(fx["in.y"][order[s]].astype(np.int64))
+        h = B.relu(B.conv1d(x, p["c1w"], p["c1b"], 1, 2, 2, 2, 1))
+        h = B.relu(B.conv1d(h, p["c2w"], p["c2b"], 2, 1, 1, 1, 2))
+        loss = B.cross_entropy(B.linear(B.mean(h, 2), p["fcw"], p["fcb"]), t)
+        opt.zero_grad()
+        B.backward(loss)
+        losses.append(float(B.numpy(loss).reshape(-1)[0]))
+        opt.step()
+    return np.array(losses), {k: B.numpy(p[k]) for k in names}
 
 
 def autograd_decoder(B, fx):

@@ -5,7 +5,8 @@ import pytest
 
 import models
 from backends import GpuBackend, OracleBackend, load_fixture, scaled_diff
-from test_oracle_golden import OPTIM, check_conv1d, check_graph_ops, run_optim_case
+from test_oracle_golden import (OPTIM, check_conv1d, check_conv1d_reference_grid, check_conv1d_training,
+                                check_frozen_encoder, check_graph_ops, run_optim_case)
 
 pytestmark = pytest.mark.gpu
 
@@ -165,6 +166,19 @@ def test_conv1d_on_the_height_one_view(B):
     the GPU through the 2-D convolution entry points on a height-1 view, against the PyTorch golden file the CPU oracle is
     pinned on."""
     check_conv1d(B, 1e-5)
+
+
+def test_frozen_encoder_curve(B):
+    """The reference's frozen-parameter fixture on the GPU (fp32 products): frozen tensors keep their bits, the others
+    follow the recorded curve."""
+    check_frozen_encoder(B, 1e-5, 1e-3, 1e-3)
+
+
+def test_conv1d_reference_grid_and_training(B):
+    """The reference's own Conv1d fixtures on the GPU: every grid case (y, dx, dW, dbias) and the 20-step training curve
+    (tests/OneModel.Tests/Training/Conv1dTests.cs:76-118, 258-307 of the reference), fp32 products."""
+    check_conv1d_reference_grid(B, 1e-5)
+    check_conv1d_training(B, 1e-5, 1e-4)
 
 
 @pytest.mark.parametrize("name,lr,b1,b2,eps", [("sparseadam", 0.05, 0.9, 0.999, 1e-3), ("sparseadam2", 0.02, 0.8, 0.95, 1e-8), ("sgd", 0.5, 0, 0, 0)])

@@ -224,6 +224,66 @@ def check_conv1d(B, tol):
             assert scaled_diff(B.grad(t), gold[f"{i}.grad_{k}"]) <= tol, (i, k)
 
 
+def check_frozen_encoder(B, early_tol, loss_tol, param_tol):
+    """testdata/training/frozen: the encoder curve with the embedding and layer 0 frozen (requires_grad False, left out of
+    the optimizer). Frozen parameters receive no gradient and keep their bits; the rest follows PyTorch's curve
+    (SparseAndFrozenTests.cs:48-118 of the reference: losses 1e-6 over the first 20 steps, 1e-5 overall, parameters 2e-6,
+    the key bias excluded since its true gradient is zero)."""
+    import models
+    fx, want = load_fixture("training", "encoder"), load_fixture("training", "frozen")
+    losses, params = models.train_encoder(B, fx, frozen=("emb", "l0"))
+    rel = np.abs(losses - want["out.loss"]) / np.abs(want["out.loss"])
+    assert rel[:20].max() <= early_tol and rel.max() <= loss_tol
+    frozen = 0
+    for k, v in params.items():
+        if k == "emb" or k.startswith("l0."):
+            frozen += 1
+            assert np.array_equal(v, fx["in." + k]) and np.array_equal(v, want["out." + k]), k
+        elif not k.endswith("bk"):
+            assert scaled_diff(v, want["out." + k]) <= param_tol, k
+    assert frozen > 10
+
+
+def check_conv1d_reference_grid(B, tol):
+    """Every case of the reference's testdata/conv1d/grid (strides, paddings incl. "same"/"valid", dilations, groups, with
+    and without bias): y and the gradients of x, w, b (Conv1dTests.cs:76-118 of the reference, gate 1e-6)."""
+    import models
+    from backends import load_fixture_manifest
+    fx, cases = load_fixture("conv1d", "grid"), load_fixture_manifest("conv1d", "grid")["cases"]
+    assert len(cases) >= 10
+    for i, case in enumerate(cases):
+        loss, y, leaves = models.conv1d_grid_case(B, fx, i, case)
+        assert tuple(B.numpy(y).shape) == fx[f"c{i}.out.y"].shape, i
+        B.backward(loss)
+        assert scaled_diff(B.numpy(y), fx[f"c{i}.out.y"]) <= tol, (i, "y")
+        for k, t in leaves.items():
+            assert scaled_diff(B.grad(t), fx[f"c{i}.grad.{k}"]) <= tol, (i, k)
+
+
+def check_conv1d_training(B, loss_tol, param_tol):
+    """testdata/conv1d/train: 20 SGD-momentum steps of a two-layer Conv1d net; the reference gates the losses at 1e-5
+    relative (Conv1dTests.cs:258-307)."""
+    import models
+    fx = load_fixture("conv1d", "train")
+    losses, params = models.train_conv1d(B, fx)
+    assert np.max(np.abs(losses - fx["out.loss"]) / np.abs(fx["out.loss"])) <= loss_tol
+    assert losses[-1] < losses[0]
+    for k, v in params.items():
+        assert scaled_diff(v, fx["out." + k]) <= param_tol, k
+
+
+def test_frozen_encoder_against_the_reference_curve(B):
+    check_frozen_encoder(B, 1e-6, 1e-5, 2e-6)
+
+
+def test_conv1d_against_the_reference_grid(B):
+    check_conv1d_reference_grid(B, 1e-6)
+
+
+def test_conv1d_training_against_the_reference_curve(B):
+    check_conv1d_training(B, 1e-5, 1e-5)
+
+
 def test_conv1d_against_pytorch_golden(B):
     check_conv1d(B, 2e-6)
 
