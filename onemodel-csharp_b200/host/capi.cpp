@@ -277,5 +277,25 @@ OMH_API int32_t omh_clip_value(int32_t n, omh_tensor* const* params, float clip)
     GradClip::ClipValue(ps, clip);
   });
 }
-OMH_API float omh_lr_cosine(float base, int64_t step, int64_t total, float eta_min) { return LrSchedule::Cosine(base, step, total, eta_min); }
-OMH_API float omh_lr_linear_warmup(float base, int64_t step, int64_t warmup, float start) { return LrSchedule::LinearWarmup(base, step, warmup, start); }
+// Learning-rate schedules. kind: 0 constant {lr}; 1 step {base, gamma} [step size]; 2 cosine {base, min} [total];
+// 3 warm-up {start factor} [warm-up steps] in front of `after`; 4 warm-up + cosine {base, floor fraction} [warm-up, total];
+// 5 one cycle {max, pct start, div factor, final div factor} [total].
+struct omh_schedule { std::shared_ptr<LrSchedule> s; };
+OMH_API int32_t omh_schedule_create(int32_t kind, const float* f, const int64_t* n, const omh_schedule* after, omh_schedule** out) {
+  return Guard([&] {
+    std::shared_ptr<LrSchedule> s;
+    switch (kind) {
+      case 0: s = LrSchedule::Constant(f[0]); break;
+      case 1: s = LrSchedule::Step(f[0], n[0], f[1]); break;
+      case 2: s = LrSchedule::Cosine(f[0], n[0], f[1]); break;
+      case 3: s = LrSchedule::Warmup(after ? after->s : nullptr, n[0], f[0]); break;
+      case 4: s = LrSchedule::WarmupCosine(f[0], n[0], n[1], f[1]); break;
+      case 5: s = LrSchedule::OneCycle(f[0], n[0], f[1], f[2], f[3]); break;
+      default: throw ArgumentOutOfRangeException("Unknown schedule kind.");
+    }
+    *out = new omh_schedule{std::move(s)};
+  });
+}
+OMH_API float omh_schedule_lr_at(const omh_schedule* h, int64_t step) { return h->s->LrAt(step); }
+OMH_API void omh_schedule_free(omh_schedule* h) { delete h; }
+OMH_API double omh_schedule_cos(double t) { return LrSchedule::Cos(t); }

@@ -500,11 +500,30 @@ struct GradClip {
   static void ClipValue(const std::vector<Tensor>& parameters, float clipValue);
 };
 
-// Learning-rate schedules are pure host functions of the step (Schedules.cs:151-422).
-struct LrSchedule {
-  static float Cosine(float base, int64_t step, int64_t total, float etaMin = 0.f);
-  static float LinearWarmup(float base, int64_t step, int64_t warmup, float startFactor);
-  static float StepDecay(float base, int64_t step, int64_t stepSize, float gamma);
+// Learning-rate schedules: pure host functions of the step index, 0 for the first step; a negative step counts as 0
+// (Schedules.cs:151-422 of the reference). All arithmetic is in double and rounded to float once.
+class LrSchedule {
+ public:
+  virtual ~LrSchedule() = default;
+  virtual float LrAt(int64_t stepNumber) const = 0;
+  // Sets the optimizer's learning rate to the rate for its current step count.
+  void Apply(Optimizer& optimizer) const;
+  // cos(pi t) for t in [0, 1] (clamped) from IEEE double operations only: reflected about 1/2 onto [0, pi/2] and summed as
+  // the Maclaurin series up to degree 26 by Horner's rule, so that every platform gets the same rates (Schedules.cs:165-203).
+  static double Cos(double t);
+
+  static std::shared_ptr<LrSchedule> Constant(float lr);
+  // base * gamma^(step / stepSize), the power by repeated squaring.
+  static std::shared_ptr<LrSchedule> Step(float baseLr, int64_t stepSize, float gamma = 0.1f);
+  // min + (base - min) (1 + cos(pi step / total)) / 2, held at min from `total` on.
+  static std::shared_ptr<LrSchedule> Cosine(float baseLr, int64_t totalSteps, float minLr = 0.f);
+  // after(0) * (start + (1 - start) step / warmup) for step < warmup, then after(step - warmup).
+  static std::shared_ptr<LrSchedule> Warmup(std::shared_ptr<LrSchedule> after, int64_t warmupSteps, float startFactor = 0.f);
+  // base (step + 1) / warmup, then base (floor + (1 - floor) (1 + cos(pi p)) / 2), p = (step - warmup) / (total - warmup).
+  static std::shared_ptr<LrSchedule> WarmupCosine(float baseLr, int64_t warmupSteps, int64_t totalSteps, float floorFraction = 0.f);
+  // Two cosine phases: max/div -> max over pctStart*total - 1 steps, then max -> max/div/finalDiv up to step total - 1.
+  static std::shared_ptr<LrSchedule> OneCycle(float maxLr, int64_t totalSteps, float pctStart = 0.3f, float divFactor = 25.f,
+                                              float finalDivFactor = 1e4f);
 };
 
 }  // namespace omh

@@ -224,20 +224,126 @@ void GradClip::ClipValue(const std::vector<Tensor>& parameters, float clipValue)
   Check(om_grad_clip_value(C(), (int32_t)g.size(), g.data(), len.data(), clipValue));
 }
 
-// ---- schedules (closed forms of the PyTorch schedulers the reference matches, Schedules.cs:171-422) -------------------
-float LrSchedule::Cosine(float base, int64_t step, int64_t total, float etaMin) {
-  double t = (double)(step < total ? step : total) / (double)total;
-  return (float)((double)etaMin + ((double)base - (double)etaMin) * (1.0 + cos(M_PI * t)) / 2.0);
+// ---- schedules (Schedules.cs:151-422) ------------------------------------------------------------------------------
+void LrSchedule::Apply(Optimizer& optimizer) const { optimizer.LearningRate = LrAt(optimizer.StepCount); }
+
+double LrSchedule::Cos(double t) {
+  if (!(t > 0.0)) return 1.0;
+  if (t >= 1.0) return -1.0;
+  const bool mirrored = t > 0.5;
+  const double angle = 3.14159265358979323846 * (mirrored ? 1.0 - t : t);
+  const double sq = angle * angle;
+  double series = 1.0;
+  for (int term = 13; term >= 1; term--) series = 1.0 - sq / ((2.0 * term - 1.0) * (2.0 * term)) * series;
+  return mirrored ? -series : series;
 }
 
-float LrSchedule::LinearWarmup(float base, int64_t step, int64_t warmup, float startFactor) {
-  if (step >= warmup) return base;
-  double f = (double)startFactor + (1.0 - (double)startFactor) * (double)step / (double)warmup;
-  return (float)((double)base * f);
+namespace {
+
+int64_t NotNegative(int64_t step) { return step < 0 ? 0 : step; }
+
+struct ConstantRate final : LrSchedule {
+  float lr;
+  explicit ConstantRate(float v) : lr(v) {}
+  float LrAt(int64_t) const override { return lr; }
+};
+
+struct StepRate final : LrSchedule {
+  double base, gamma;
+  int64_t every;
+  StepRate(float b, int64_t e, float g) : base(b), gamma(g), every(e) {}
+  float LrAt(int64_t step) const override {
+    double rate = base, factor = gamma;
+    for (int64_t drops = NotNegative(step) / every; drops > 0; drops >>= 1) {
+      if (drops & 1) rate *= factor;
+      factor *= factor;
+    }
+    return (float)rate;
+  }
+};
+
+struct CosineRate final : LrSchedule {
+  double base, floor;
+  int64_t total;
+  CosineRate(float b, int64_t t, float m) : base(b), floor(m), total(t) {}
+  float LrAt(int64_t step) const override {
+    const int64_t s = NotNegative(step);
+    const double t = s >= total ? 1.0 : (double)s / (double)total;
+    return (float)(floor + (base - floor) * (1.0 + Cos(t)) / 2.0);
+  }
+};
+
+struct WarmupRate final : LrSchedule {
+  std::shared_ptr<LrSchedule> after;
+  int64_t warmup;
+  double start;
+  WarmupRate(std::shared_ptr<LrSchedule> a, int64_t w, float s) : after(std::move(a)), warmup(w), start(s) {}
+  float LrAt(int64_t step) const override {
+    const int64_t s = NotNegative(step);
+    if (s >= warmup) return after->LrAt(s - warmup);
+    const double first = after->LrAt(0);
+    return (float)(first * (start + (1.0 - start) * ((double)s / (double)warmup)));
+  }
+};
+
+struct WarmupCosineRate final : LrSchedule {
+  double base, floor;
+  int64_t warmup, total;
+  WarmupCosineRate(float b, int64_t w, int64_t t, float f) : base(b), floor(f), warmup(w), total(t) {}
+  float LrAt(int64_t step) const override {
+    const int64_t s = NotNegative(step);
+    if (s < warmup) return (float)(base * (double)(s + 1) / (double)warmup);
+    const int64_t span = total - warmup > 1 ? total - warmup : 1;
+    double p = (double)(s - warmup) / (double)span;
+    if (p > 1.0) p = 1.0;
+    return (float)(base * (floor + ((1.0 - floor) * 0.5 * (1.0 + Cos(p)))));
+  }
+};
+
+struct OneCycleRate final : LrSchedule {
+  double peak, first, last, up_end, down_end;
+  OneCycleRate(float maxLr, int64_t total, float pct, float div, float finalDiv)
+      : peak(maxLr), first((double)maxLr / div), last(first / finalDiv), up_end((double)pct * (double)total - 1.0),
+        down_end((double)total - 1.0) {}
+  static double Anneal(double from, double to, double pct) { return to + (from - to) / 2.0 * (Cos(pct) + 1.0); }
+  float LrAt(int64_t step) const override {
+    double s = (double)NotNegative(step);
+    if (s > down_end) s = down_end;
+    return s <= up_end ? (float)Anneal(first, peak, s / up_end) : (float)Anneal(peak, last, (s - up_end) / (down_end - up_end));
+  }
+};
+
+}  // namespace
+
+std::shared_ptr<LrSchedule> LrSchedule::Constant(float lr) { return std::make_shared<ConstantRate>(lr); }
+
+std::shared_ptr<LrSchedule> LrSchedule::Step(float baseLr, int64_t stepSize, float gamma) {
+  if (stepSize < 1) throw ArgumentOutOfRangeException("The step size must be at least 1.");
+  return std::make_shared<StepRate>(baseLr, stepSize, gamma);
 }
 
-float LrSchedule::StepDecay(float base, int64_t step, int64_t stepSize, float gamma) {
-  return (float)((double)base * pow((double)gamma, (double)(step / stepSize)));
+std::shared_ptr<LrSchedule> LrSchedule::Cosine(float baseLr, int64_t totalSteps, float minLr) {
+  if (totalSteps < 1) throw ArgumentOutOfRangeException("The number of steps must be at least 1.");
+  return std::make_shared<CosineRate>(baseLr, totalSteps, minLr);
+}
+
+std::shared_ptr<LrSchedule> LrSchedule::Warmup(std::shared_ptr<LrSchedule> after, int64_t warmupSteps, float startFactor) {
+  if (!after) throw std::invalid_argument("A warm-up needs the schedule that follows it.");
+  if (warmupSteps < 1) throw ArgumentOutOfRangeException("The warm-up must last at least 1 step.");
+  return std::make_shared<WarmupRate>(std::move(after), warmupSteps, startFactor);
+}
+
+std::shared_ptr<LrSchedule> LrSchedule::WarmupCosine(float baseLr, int64_t warmupSteps, int64_t totalSteps, float floorFraction) {
+  if (warmupSteps < 1) throw ArgumentOutOfRangeException("The warm-up must last at least 1 step.");
+  if (totalSteps <= warmupSteps) throw ArgumentOutOfRangeException("The total must exceed the warm-up.");
+  if (!(floorFraction >= 0.f && floorFraction <= 1.f)) throw ArgumentOutOfRangeException("The floor fraction must be in [0, 1].");
+  return std::make_shared<WarmupCosineRate>(baseLr, warmupSteps, totalSteps, floorFraction);
+}
+
+std::shared_ptr<LrSchedule> LrSchedule::OneCycle(float maxLr, int64_t totalSteps, float pctStart, float divFactor, float finalDivFactor) {
+  if (totalSteps < 2) throw ArgumentOutOfRangeException("One cycle needs at least 2 steps.");
+  if (!(pctStart > 0.f && pctStart < 1.f)) throw ArgumentOutOfRangeException("pctStart must be in (0, 1).");
+  return std::make_shared<OneCycleRate>(maxLr, totalSteps, pctStart, divFactor, finalDivFactor);
 }
 
 }  // namespace omh

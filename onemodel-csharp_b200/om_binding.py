@@ -58,10 +58,11 @@ def host_lib():
             raise RuntimeError(f"{HOST_LIB} is missing: run __graft_entry__.build()")
         _host = C.CDLL(HOST_LIB, mode=C.RTLD_GLOBAL)
         _host.omh_tensor_data.restype = C.c_void_p
-        _host.omh_lr_cosine.restype = C.c_float
-        _host.omh_lr_cosine.argtypes = [C.c_float, C.c_int64, C.c_int64, C.c_float]
-        _host.omh_lr_linear_warmup.restype = C.c_float
-        _host.omh_lr_linear_warmup.argtypes = [C.c_float, C.c_int64, C.c_int64, C.c_float]
+        _host.omh_schedule_lr_at.restype = C.c_float
+        _host.omh_schedule_lr_at.argtypes = [C.c_void_p, C.c_int64]
+        _host.omh_schedule_free.argtypes = [C.c_void_p]
+        _host.omh_schedule_cos.restype = C.c_double
+        _host.omh_schedule_cos.argtypes = [C.c_double]
     return _host
 
 
@@ -367,6 +368,51 @@ class Optimizer:
         try:
             if self.h:
                 host_lib().omh_optim_free(self.h)
+        except Exception:
+            pass
+
+
+class LrSchedule:
+    """ConstantLr / StepLr / CosineLr / WarmupLr / WarmupCosineLr / OneCycleLr of RecursiveAI.OneModel.Training
+    (Schedules.cs:151-422): lr_at(step) is the rate of the optimizer step with that index, 0 for the first."""
+
+    def __init__(self, kind, floats, ints, after=None):
+        fa = (C.c_float * max(len(floats), 1))(*floats)
+        ia = (C.c_int64 * max(len(ints), 1))(*[int(v) for v in ints])
+        self.h = C.c_void_p()
+        self._after = after                      # keeps the wrapped schedule's handle alive on this side too
+        _hcheck(host_lib().omh_schedule_create(i32(kind), fa, ia, after.h if after is not None else None, C.byref(self.h)))
+
+    @staticmethod
+    def constant(lr): return LrSchedule(0, [lr], [])
+    @staticmethod
+    def step(base_lr, step_size, gamma=0.1): return LrSchedule(1, [base_lr, gamma], [step_size])
+    @staticmethod
+    def cosine(base_lr, total_steps, min_lr=0.0): return LrSchedule(2, [base_lr, min_lr], [total_steps])
+    @staticmethod
+    def warmup(after, warmup_steps, start_factor=0.0): return LrSchedule(3, [start_factor], [warmup_steps], after)
+    @staticmethod
+    def warmup_cosine(base_lr, warmup_steps, total_steps, floor_fraction=0.0):
+        return LrSchedule(4, [base_lr, floor_fraction], [warmup_steps, total_steps])
+    @staticmethod
+    def one_cycle(max_lr, total_steps, pct_start=0.3, div_factor=25.0, final_div_factor=1e4):
+        return LrSchedule(5, [max_lr, pct_start, div_factor, final_div_factor], [total_steps])
+
+    @staticmethod
+    def cos(t):
+        """cos(pi t) on [0, 1] by the platform-independent series (LrSchedule.Cos, Schedules.cs:165-203)."""
+        return host_lib().omh_schedule_cos(float(t))
+
+    def lr_at(self, step):
+        return float(host_lib().omh_schedule_lr_at(self.h, int(step)))
+
+    def apply(self, optimizer, step):
+        optimizer.set_lr(self.lr_at(step))
+
+    def __del__(self):
+        try:
+            if self.h:
+                host_lib().omh_schedule_free(self.h)
         except Exception:
             pass
 
