@@ -512,6 +512,23 @@ int32_t om_grad_norm_clip(om_ctx* ctx, int32_t n_tensors, float* const* g_host, 
 int32_t om_grad_clip_value(om_ctx* ctx, int32_t n_tensors, float* const* g_host, const int64_t* len_host,
                            float clip);
 
+/* Dropout (the mask of the reference's Dropout module, src/OneModel.Training/Layers.cs:308-371; row a29 of the forward
+ * ops). Element i of call number `draw` is kept, scaled by 1/(1-p), when u >= p with
+ * u = (Mix(Mix(seed + draw*G) + (i+1)*G) >> 40) * 2^-24, Mix the SplitMix64 finaliser and G = 0x9E3779B97F4A7C15
+ * (Generator.cs:10-48): the same bits as the reference. `draws` is the module's call counter in DEVICE memory (int64[1],
+ * the "draws" buffer of the state dict): om_dropout_fwd reads it, writes y = x * mask (and the mask when `mask` is not
+ * NULL), notes the value it used in draw_used (device int64[1], may be NULL) and then advances the counter by one in
+ * stream order, so a captured step draws a new mask on every replay. om_dropout_bwd forms the mask again from draw_used:
+ * dx = g * mask (MulBackward of the reference's Ops.Mul(input, mask), BackwardOps.cs:23-40). om_dropout_mask writes the
+ * mask of the call number in `draw` without touching a counter. p in [0, 1). x and y (g and dx) may alias. */
+int32_t om_dropout_mask(om_ctx* ctx, uint64_t seed, const int64_t* draw, float p, int64_t n, float* mask);
+int32_t om_dropout_fwd(om_ctx* ctx, const float* x, int64_t n, float p, uint64_t seed, int64_t* draws, int64_t* draw_used,
+                       float* y, float* mask);
+int32_t om_dropout_bwd(om_ctx* ctx, const float* g, int64_t n, float p, uint64_t seed, const int64_t* draw_used, float* dx);
+/* mask[i] = 1 where targets[i] != ignore_index, else 0 (the counted rows of Losses.CrossEntropy's label-smoothing term,
+ * Losses.cs:33-46). */
+int32_t om_target_mask(om_ctx* ctx, const void* targets, int32_t target_dtype, int32_t rows, int64_t ignore_index, float* mask);
+
 /* Row-sparse updates for embedding tables (SparseAdam and the sparse path of Sgd, Optimizers.cs:377-397,625-722). The
  * reference carries a RowSparseGradient (sorted unique rows + coalesced values); here the same information is the
  * dense-format table gradient of om_embedding_bwd plus touched[rows] from om_rows_touched (how many positions of the

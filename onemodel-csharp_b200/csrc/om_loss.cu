@@ -172,6 +172,12 @@ __global__ void count_targets_kernel(const void* __restrict__ targets, int dtype
   if (threadIdx.x == 0) count_out[0] = scount[0];
 }
 
+__global__ void target_mask_kernel(const void* __restrict__ targets, int dtype, int32_t rows, int64_t ignore, float* __restrict__ mask) {
+  pdl_enter();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += gridDim.x * blockDim.x)
+    mask[i] = target_at(targets, dtype, i) != ignore ? 1.f : 0.f;
+}
+
 __device__ __forceinline__ float nll_scale(const float* g, int mean, const int32_t* count, float denominator) {
   float gv = g[0];
   if (!mean) return gv;
@@ -241,6 +247,16 @@ int32_t om_logsoftmax_bwd(om_ctx* ctx, const float* g, const float* y, int32_t r
 static int32_t check_targets(om_ctx* ctx, const char* who, int32_t dtype, int32_t rows, int32_t cols) {
   if (dtype != OM_I32 && dtype != OM_I64) return fail(ctx, OM_ERR_SHAPE, "%s: targets must be Int32 or Int64", who);
   if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "%s: [%d,%d]", who, rows, cols);
+  return OM_OK;
+}
+
+int32_t om_target_mask(om_ctx* ctx, const void* targets, int32_t target_dtype, int32_t rows, int64_t ignore_index, float* mask) {
+  OM_CHECK_CTX(ctx);
+  OM_TRY(check_targets(ctx, "om_target_mask", target_dtype, rows, 0));
+  if (rows == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_target_mask", 0, 12.0 * rows);
+  launch_chained(ctx, target_mask_kernel, grid_for(ctx, rows, 256), 256, 0, targets, (int)target_dtype, rows, ignore_index, mask);
+  OM_LAUNCH_CHECK(ctx, "om_target_mask");
   return OM_OK;
 }
 

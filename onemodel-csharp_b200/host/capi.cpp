@@ -173,6 +173,11 @@ OMH_API int32_t omh_call(const char* op, int32_t n_in, omh_tensor* const* in, in
     else if (name == "embedding") r = Ops::Embedding(T(0), T(1), (int)I(0, -1));
     else if (name == "nll_loss") r = Ops::NllLoss(T(0), T(1), I(0, 1) != 0, (int)I(1, -100));
     else if (name == "cross_entropy") r = Ops::CrossEntropy(T(0), T(1), I(0, 1) != 0, (int)I(1, -100), (float)F(0, 0));
+    else if (name == "cross_entropy_smoothed") r = Losses::CrossEntropy(T(0), T(1), (float)F(0, 0), (int)I(1, -100), I(0, 1) != 0);
+    else if (name == "mse_loss") r = Losses::Mse(T(0), T(1), I(0, 1) != 0);
+    else if (name == "l1_loss") r = Losses::L1(T(0), T(1), I(0, 1) != 0);
+    else if (name == "bce_with_logits") r = Losses::BceWithLogits(T(0), T(1), I(0, 1) != 0);
+    else if (name == "dropout") r = Ops::Dropout(T(0), (float)F(0, 0.5), (uint64_t)I(0), T(1));
     else if (name == "linear") r = Ops::Linear(T(0), T(1), T(2));
     else if (name == "attention") r = Ops::Attention(T(0), T(1), T(2), T(3), (float)F(0, 0));
     else if (name == "attention_heads") r = Ops::AttentionHeads(T(0), T(1), T(2), (int)I(0, 1), T(3), (float)F(0, 0));

@@ -155,9 +155,66 @@ Tensor TransformerEncoderLayer::Forward(const Tensor& input, const Tensor& mask)
   return Norm2->Forward(Ops::Add(x1, f));
 }
 
-Tensor Losses::Mse(const Tensor& x, const Tensor& target) {
-  Tensor d = Ops::Sub(x, target);
-  return Ops::Mean(Ops::Mul(d, d));
+Dropout::Dropout(float p, uint64_t seed) : P(p), Seed(seed) {
+  if (!(p >= 0.f && p < 1.f)) throw ArgumentOutOfRangeException("Dropout probability must be in [0, 1).");
+  Counter = RegisterBuffer("draws", Tensor::Zeros(DType::I64, Shape{1}));
+}
+
+int64_t Dropout::Draws() const {
+  int64_t v = 0;
+  Counter.CopyToHost(&v);
+  return v;
+}
+
+// ---- losses (Losses.cs:14-129) ------------------------------------------------------------------------------------------
+Tensor Losses::CrossEntropy(const Tensor& logits, const Tensor& targets, float labelSmoothing, int ignoreIndex, bool mean) {
+  if (!(labelSmoothing >= 0.f && labelSmoothing <= 1.f)) throw ArgumentOutOfRangeException("Label smoothing must be in [0, 1].");
+  if (labelSmoothing == 0.f) return Ops::CrossEntropy(logits, targets, mean, ignoreIndex);
+  if (logits.Rank() != 2) throw TensorShapeException("CrossEntropy needs [rows, classes] logits, not " + logits.GetShape().ToString() + ".");
+  Tensor logp = Ops::LogSoftmax(logits);
+  Tensor nll = Ops::NllLoss(logp, targets, mean, ignoreIndex);
+  // The smoothing term, per row -mean_c(logp), over the counted rows. The mask of counted rows is formed on the device.
+  int rows = logits.GetShape()[0];
+  Tensor tc = targets.Contiguous();
+  Tensor mask = Tensor::Create(DType::F32, Shape{rows});
+  Check(om_target_mask(Device::Current(), tc.RawData(), (int32_t)tc.GetDType(), rows, ignoreIndex, mask.Data()));
+  Tensor perRow = Ops::Neg(Ops::Mean(logp, 1));
+  Tensor smooth = Ops::Sum(Ops::Mul(perRow, mask));
+  if (mean) {
+    // 1 / counted as a float (0 rows: 1/0 = inf, and 0 * inf = NaN like the reference's NaN factor), then one product.
+    Tensor one = Tensor::Create(DType::F32, Shape{});
+    one.Fill(1.f);
+    smooth = Ops::Mul(smooth, Ops::Div(one, Ops::Sum(mask)));
+  }
+  Tensor keep = Tensor::Create(DType::F32, Shape{}), share = Tensor::Create(DType::F32, Shape{});
+  keep.Fill(1.f - labelSmoothing);
+  share.Fill(labelSmoothing);
+  return Ops::Add(Ops::Mul(nll, keep), Ops::Mul(smooth, share));
+}
+
+Tensor Losses::Mse(const Tensor& prediction, const Tensor& target, bool mean) {
+  Tensor d = Ops::Sub(prediction, target);
+  Tensor sq = Ops::Mul(d, d);
+  return mean ? Ops::Mean(sq) : Ops::Sum(sq);
+}
+
+Tensor Losses::L1(const Tensor& prediction, const Tensor& target, bool mean) {
+  Tensor d = Ops::Sub(prediction, target);
+  Tensor magnitude = Ops::Add(Ops::Relu(d), Ops::Relu(Ops::Neg(d)));
+  return mean ? Ops::Mean(magnitude) : Ops::Sum(magnitude);
+}
+
+Tensor Losses::BceWithLogits(const Tensor& logits, const Tensor& targets, bool mean) {
+  if (!(logits.GetShape() == targets.GetShape()))
+    throw TensorShapeException("BceWithLogits needs equal shapes, not " + logits.GetShape().ToString() + " and " + targets.GetShape().ToString() + ".");
+  int count = (int)logits.Length();
+  Tensor x = logits.Reshape(Shape{count, 1});
+  Tensor zeros = Tensor::Zeros(DType::F32, Shape{count, 1});
+  Tensor logSoftmax = Ops::LogSoftmax(Ops::Concat({x, zeros}, 1));
+  Tensor softplus = Ops::Neg(logSoftmax.Select(1, 1));
+  Tensor xt = Ops::Mul(logits.Reshape(Shape{count}), targets.Reshape(Shape{count}));
+  Tensor perElement = Ops::Sub(softplus, xt);
+  return mean ? Ops::Mean(perElement) : Ops::Sum(perElement);
 }
 
 }  // namespace omh

@@ -145,7 +145,7 @@ enum class OpKind {
   None = 0, Add, Sub, Mul, Div, Neg, Relu, MatMul, MaxPool2d, Cast, Slice, Permute, Reshape, Expand, Flip, Select, Gelu,
   Sigmoid, Tanh, Sum, Mean, Softmax, LogSoftmax, LayerNorm, BatchNorm, Conv2d, AvgPool2d, Concat, Embedding, NllLoss,
   Attention, Lstm, Gru, CtcLoss, ConvTranspose2d, Resize2d, Conv1d, BatchMatMul, Erf, Exp, Sqrt, Pow, Where, Gather,
-  Linear, CrossEntropy
+  Linear, CrossEntropy, Dropout
 };
 
 struct AutogradMeta {
@@ -293,6 +293,9 @@ struct Ops {
   static Tensor Exp(const Tensor& x);
   static Tensor Sqrt(const Tensor& x);
   static Tensor Pow(const Tensor& x, float exponent);
+  // y = x * mask, the mask of call number draws[0] of the stream `seed` (kept elements scaled by 1/(1-p)); advances the
+  // device counter `draws` (Int64 [1]) by one. The product of the reference's Dropout.Forward (Layers.cs:339-370).
+  static Tensor Dropout(const Tensor& x, float p, uint64_t seed, const Tensor& draws);
   static Tensor Where(const Tensor& condition, const Tensor& x, const Tensor& y);
   static Tensor Gather(const Tensor& data, const Tensor& indices, int axis);
   // 1-D cross-correlation of an NCL input with OIK weights on the 2-D kernels with a height of 1 (Ops.Layers.cs:338-402;
@@ -355,6 +358,16 @@ struct LayerNorm : NnModule {
   explicit LayerNorm(int width, float eps = 1e-5f);
   Tensor Forward(const Tensor& x) override { return Ops::LayerNorm(x, Gamma, Beta, Epsilon); }
 };
+// Inverted dropout with a seeded counter-based mask (Layers.cs:308-371). The call counter is the module's only buffer
+// ("draws", Int64 [1], in device memory): restoring it from a checkpoint restores the stream of masks.
+struct Dropout : NnModule {
+  float P;
+  uint64_t Seed;
+  Tensor Counter;
+  Dropout(float p, uint64_t seed);
+  int64_t Draws() const;   // reads the counter back (synchronises)
+  Tensor Forward(const Tensor& x) override { return (!Training || P == 0.f) ? x : Ops::Dropout(x, P, Seed, Counter); }
+};
 struct Embedding : NnModule {
   Tensor Weight;
   int PaddingIndex;
@@ -399,14 +412,25 @@ struct Recurrent : NnModule {
   Tensor Forward(const Tensor& x) override;
 };
 
+// Losses.cs:14-129 of the reference: thin compositions of Ops, so their gradients come from the records of those ops.
 struct Losses {
   static Tensor CrossEntropy(const Tensor& logits, const Tensor& targets, bool mean = true, int ignoreIndex = -100) {
     return Ops::CrossEntropy(logits, targets, mean, ignoreIndex);
   }
+  // With label smoothing: (1 - s) * NLL + s * (sum over counted rows of -mean_c(logp)), the second term divided by the
+  // number of counted rows when `mean` (NaN when no row counts, as in the reference).
+  static Tensor CrossEntropy(const Tensor& logits, const Tensor& targets, float labelSmoothing, int ignoreIndex, bool mean);
   static Tensor NllLoss(const Tensor& logp, const Tensor& targets, bool mean = true, int ignoreIndex = -100) {
     return Ops::NllLoss(logp, targets, mean, ignoreIndex);
   }
-  static Tensor Mse(const Tensor& x, const Tensor& target);
+  static Tensor Ctc(const Tensor& logProbs, const Tensor& targets, const Tensor& inputLengths, const Tensor& targetLengths, int blank = 0,
+                    int reduction = 1, bool zeroInfinity = false) {
+    return Ops::CtcLoss(logProbs, targets, inputLengths, targetLengths, blank, reduction, zeroInfinity);
+  }
+  static Tensor Mse(const Tensor& prediction, const Tensor& target, bool mean = true);
+  static Tensor L1(const Tensor& prediction, const Tensor& target, bool mean = true);
+  // Mean or sum of softplus(x) - x*t, the softplus taken as -LogSoftmax([x, 0])[1] as the reference does.
+  static Tensor BceWithLogits(const Tensor& logits, const Tensor& targets, bool mean = true);
 };
 
 class Optimizer {

@@ -40,6 +40,26 @@ Tensor Ops::Pow(const Tensor& x, float exponent) {
   return rec->Attach(r);
 }
 
+// Dropout: the record keeps the call number the forward used (a device Int64 [1] written by the kernel), not the mask;
+// the backward forms the mask bits again from it.
+Tensor Ops::Dropout(const Tensor& x, float p, uint64_t seed, const Tensor& draws) {
+  RequireF32(x);
+  if (!(p >= 0.f && p < 1.f)) throw ArgumentOutOfRangeException("Dropout probability must be in [0, 1).");
+  if (draws.GetDType() != DType::I64 || draws.Length() != 1) throw TensorShapeException("The draw counter must be Int64 [1].");
+  Tensor xc = x.Contiguous();
+  Tensor r = Tensor::Create(DType::F32, x.GetShape());
+  bool record = Recording({&x});
+  Tensor used = record ? Tensor::Create(DType::I64, Shape{1}) : Tensor();
+  Check(om_dropout_fwd(Ctx(), xc.Data(), r.Length(), p, seed, (int64_t*)draws.RawData(), record ? (int64_t*)used.RawData() : nullptr,
+                       r.Data(), nullptr));
+  if (!record) return r;
+  auto rec = BackwardRecord::Create(OpKind::Dropout, 1, {&x});
+  rec->Save(0, used);
+  rec->Floats = {p};
+  rec->Ints = {(int64_t)seed};
+  return rec->Attach(r);
+}
+
 static Shape BroadcastShapes(const Shape& a, const Shape& b) {
   Shape s;
   s.rank = std::max(a.rank, b.rank);
@@ -325,6 +345,13 @@ void RunGraphBackward(BackwardRecord& r, const Tensor& g) {
       const Tensor& x = r.Saved(0);
       Tensor dx = Tensor::Create(DType::F32, x.GetShape());
       Check(om_pow_bwd(Ctx(), gc.Data(), x.Data(), (float)r.Floats[0], dx.Data(), dx.Length()));
+      Engine::Emit(r, 0, dx, true);
+      break;
+    }
+    case OpKind::Dropout: {
+      Tensor dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+      Check(om_dropout_bwd(Ctx(), gc.Data(), dx.Length(), (float)r.Floats[0], (uint64_t)r.Ints[0], (const int64_t*)r.Saved(0).RawData(),
+                           dx.Data()));
       Engine::Emit(r, 0, dx, true);
       break;
     }

@@ -631,3 +631,79 @@ def resize2d(x, out_h, out_w, mode=0, align_corners=False):
         return [(0, dx, "own")]
 
     return _attach(y, Record("resize2d", [x], backward=bw), [x])
+
+
+# ---- Dropout and the loss family (Layers.cs:308-371, Generator.cs:10-48, Losses.cs:14-129 of the reference) -----------
+_GAMMA = 0x9E3779B97F4A7C15
+_M64 = (1 << 64) - 1
+
+
+def splitmix_finish(z):
+    """Generator.Mix: the SplitMix64 finaliser on Python integers (mod 2^64)."""
+    z &= _M64
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+    return z ^ (z >> 31)
+
+
+def dropout_mask(seed, draw, p, n):
+    """The mask of call number `draw` (Layers.cs:354-366): u_i = (Mix(stream + (i+1) G) >> 40) / 2^24 with
+    stream = Mix(seed + draw G); kept (u >= p) elements carry float32(1 / (1 - p))."""
+    stream = splitmix_finish(seed + draw * _GAMMA)
+    with np.errstate(over="ignore"):
+        z = np.uint64(stream) + (np.arange(1, n + 1, dtype=np.uint64) * np.uint64(_GAMMA))
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+    u = (z >> np.uint64(40)).astype(np.float32) * np.float32(1.0 / 16777216.0)
+    scale = np.float32(1.0) / (np.float32(1.0) - np.float32(p))
+    return np.where(u >= np.float32(p), scale, np.float32(0)).astype(np.float32)
+
+
+def neg(x):
+    return _attach((-x.v).astype(np.float32), Record("neg", [x], backward=lambda r, g: [(0, (-g).astype(np.float32), "own")]), [x])
+
+
+def dropout(x, p, seed, draw):
+    """Dropout.Forward in training mode: Ops.Mul(input, mask)."""
+    return mul(x, T(dropout_mask(seed, draw, p, x.v.size).reshape(x.shape)))
+
+
+def _scalar(v):
+    return T(np.array(v, np.float32).reshape(()))
+
+
+def cross_entropy_smoothed(logits, targets, label_smoothing, ignore=-100, reduce_mean=True):
+    """Losses.CrossEntropy with label smoothing (Losses.cs:21-62)."""
+    logp = log_softmax(logits)
+    nll = nll_loss(logp, targets, reduce_mean, ignore)
+    if label_smoothing == 0:
+        return nll
+    keep = (np.asarray(targets, np.int64) != ignore).astype(np.float32)
+    smooth = sum_(mul(neg(mean(logp, 1)), T(keep)))
+    if reduce_mean:
+        counted = int(keep.sum())
+        smooth = mul(smooth, _scalar(np.float32(np.nan) if counted == 0 else np.float32(1.0) / np.float32(counted)))
+    return add(mul(nll, _scalar(np.float32(1.0) - np.float32(label_smoothing))), mul(smooth, _scalar(np.float32(label_smoothing))))
+
+
+def mse_loss(prediction, target, reduce_mean=True):
+    d = sub(prediction, target)
+    sq = mul(d, d)
+    return mean(sq) if reduce_mean else sum_(sq)
+
+
+def l1_loss(prediction, target, reduce_mean=True):
+    d = sub(prediction, target)
+    a = add(relu(d), relu(neg(d)))
+    return mean(a) if reduce_mean else sum_(a)
+
+
+def bce_with_logits(logits, targets, reduce_mean=True):
+    """softplus(x) - x t with softplus(x) = -LogSoftmax([x, 0])[:, 1] (Losses.cs:113-129)."""
+    n = logits.v.size
+    x = logits.reshape(n, 1)
+    ls = log_softmax(concat([x, T(np.zeros((n, 1), np.float32))], 1))
+    softplus = neg(ls.slice(1, 1, 2).reshape(n))
+    per = sub(softplus, mul(logits.reshape(n), targets.reshape(n)))
+    return mean(per) if reduce_mean else sum_(per)

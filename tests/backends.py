@@ -73,6 +73,12 @@ class OracleBackend:
     def pow(self, x, p): return self.tape.pow_(x, p)
     def where(self, c, a, b): return self.tape.where(c, a, b)
     def gather(self, data, idx, axis): return self.tape.gather(data, idx, axis)
+    def cross_entropy_smoothed(self, x, t, smoothing, ignore=-100, mean=True):
+        return self.tape.cross_entropy_smoothed(x, t, smoothing, ignore, mean)
+    def mse_loss(self, x, t, mean=True): return self.tape.mse_loss(x, t, mean)
+    def l1_loss(self, x, t, mean=True): return self.tape.l1_loss(x, t, mean)
+    def bce_with_logits(self, x, t, mean=True): return self.tape.bce_with_logits(x, t, mean)
+    def dropout(self, x, p, seed, draw): return self.tape.dropout(x, p, seed, draw)
     def select(self, t, axis, index):
         shape = list(t.shape)
         del shape[axis]
@@ -141,6 +147,14 @@ class GpuBackend:
     def concat(self, xs, axis): return self.omb.call("concat", list(xs), ints=[axis])
     def gru_layer(self, x, wih, whh, bih, bhh, h0=None, reverse=False):
         return self.omb.call("gru_layer", [x, wih, whh, bih, bhh, h0], ints=[1 if reverse else 0])
+    def cross_entropy_smoothed(self, x, t, smoothing, ignore=-100, mean=True):
+        return self.omb.call("cross_entropy_smoothed", [x, t], ints=[1 if mean else 0, ignore], floats=[smoothing])
+    def mse_loss(self, x, t, mean=True): return self.omb.call("mse_loss", [x, t], ints=[1 if mean else 0])
+    def l1_loss(self, x, t, mean=True): return self.omb.call("l1_loss", [x, t], ints=[1 if mean else 0])
+    def bce_with_logits(self, x, t, mean=True): return self.omb.call("bce_with_logits", [x, t], ints=[1 if mean else 0])
+    def dropout(self, x, p, seed, draw):
+        counter = self.omb.Tensor.from_numpy(np.array([draw], np.int64))
+        return self.omb.call("dropout", [x, counter], ints=[seed], floats=[p])
     def select(self, t, axis, index): return t.select(axis, index)
     def matmul_batched(self, a, b): return self.omb.call("matmul_batched", [a, b])
     def conv_transpose2d(self, x, w, b, stride=1, padding=0, output_padding=0, groups=1):

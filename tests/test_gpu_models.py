@@ -6,7 +6,7 @@ import pytest
 import models
 from backends import GpuBackend, OracleBackend, load_fixture, scaled_diff
 from test_oracle_golden import (OPTIM, check_conv1d, check_conv1d_reference_grid, check_conv1d_training,
-                                check_frozen_encoder, check_graph_ops, run_optim_case)
+                                check_frozen_encoder, check_graph_ops, check_losses, run_optim_case)
 
 pytestmark = pytest.mark.gpu
 
@@ -166,6 +166,48 @@ def test_conv1d_on_the_height_one_view(B):
     the GPU through the 2-D convolution entry points on a height-1 view, against the PyTorch golden file the CPU oracle is
     pinned on."""
     check_conv1d(B, 1e-5)
+
+
+def test_loss_family(B):
+    """Losses.{CrossEntropy with label smoothing, Mse, L1, BceWithLogits} on the GPU against the PyTorch golden file."""
+    check_losses(B, 1e-5)
+
+
+@pytest.mark.parametrize("n,p,seed,draw", [(1000, 0.3, 42, 0), (1003, 0.5, 7, 3), (1 << 20, 0.1, 2**63 + 5, 2**40), (4, 0.0, 1, 0)])
+def test_dropout_mask_bits(ctx, n, p, seed, draw):
+    """om_dropout_mask is the reference's counter-based mask bit for bit (Layers.cs:354-366), vector and scalar paths."""
+    import ctypes as C
+    import om_binding as omb
+    from om_binding import f32, i64
+    from oracle import tape
+    counter = ctx.to_device(np.array([draw], np.int64))
+    mask = ctx.empty((n,))
+    ctx.call("om_dropout_mask", ctx.handle, C.c_uint64(seed), counter.ptr, f32(p), i64(n), mask.ptr)
+    assert np.array_equal(mask.numpy(), tape.dropout_mask(seed, draw, p, n))
+    assert counter.numpy()[0] == draw                          # the mask entry point leaves the counter alone
+    with pytest.raises(omb.OmError):
+        ctx.call("om_dropout_mask", ctx.handle, C.c_uint64(seed), counter.ptr, f32(1.0), i64(n), mask.ptr)
+
+
+def test_dropout_forward_backward_and_counter(ctx, B):
+    """Ops.Dropout: y = x * mask of the counter's call number, the counter advances by one per call in device memory,
+    and the backward forms the same mask again (ModuleAndLossTests.cs:62-102 of the reference)."""
+    import om_binding as omb
+    from oracle import tape
+    x_np = np.random.default_rng(3).standard_normal((37, 29)).astype(np.float32)
+    w_np = np.random.default_rng(4).standard_normal((37, 29)).astype(np.float32)
+    counter = omb.Tensor.from_numpy(np.array([5], np.int64))
+    for call in range(3):
+        x = B.tensor(x_np, True)
+        y = omb.call("dropout", [x, counter], ints=[99], floats=[0.4])
+        m = tape.dropout_mask(99, 5 + call, 0.4, x_np.size).reshape(x_np.shape)
+        assert np.array_equal(y.numpy(), x_np * m)
+        assert int(counter.numpy()[0]) == 6 + call
+        B.backward(B.sum(B.mul(y, B.tensor(w_np))))
+        assert np.array_equal(B.grad(x), w_np * m)
+    with omb.no_grad():
+        y = omb.call("dropout", [B.tensor(x_np), counter], ints=[99], floats=[0.4])
+    assert np.array_equal(y.numpy(), x_np * tape.dropout_mask(99, 8, 0.4, x_np.size).reshape(x_np.shape))
 
 
 def test_frozen_encoder_curve(B):

@@ -224,6 +224,58 @@ def check_conv1d(B, tol):
             assert scaled_diff(B.grad(t), gold[f"{i}.grad_{k}"]) <= tol, (i, k)
 
 
+def check_losses(B, tol):
+    """Cross entropy with label smoothing and ignored rows, MSE, L1 and BCE-with-logits (Losses.cs:14-129 of the reference)
+    against tests/golden/losses.npz (PyTorch CPU, tests/golden/make_losses_golden.py): values and input gradients."""
+    import os
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "losses.npz"))
+    CE_CASES = [(0.1, True), (0.3, True), (0.2, False), (1.0, True)]     # as in tests/golden/make_losses_golden.py
+
+    def run(build, leaves_np, want_loss, want_grads):
+        leaves = [B.tensor(a, True) for a in leaves_np]
+        loss = build(*leaves)
+        B.backward(loss)
+        got = float(B.numpy(loss).reshape(-1)[0])
+        assert abs(got - float(want_loss)) <= 10 * tol * max(1.0, abs(float(want_loss))), (got, float(want_loss))
+        for t, w in zip(leaves, want_grads):
+            assert scaled_diff(B.grad(t), w) <= tol
+
+    tg = gold["targets"]
+    for i, (eps, mean) in enumerate(CE_CASES):
+        run(lambda x: B.cross_entropy_smoothed(x, B.ids(tg), eps, -100, mean), [gold["logits"]], gold[f"ce{i}.loss"], [gold[f"ce{i}.grad"]])
+    for mean in (True, False):
+        goal = gold["goal"]
+        run(lambda x: B.mse_loss(x, B.tensor(goal), mean), [gold["pred"]], gold[f"mse.{int(mean)}.loss"], [gold[f"mse.{int(mean)}.grad"]])
+        run(lambda x: B.l1_loss(x, B.tensor(goal), mean), [gold["pred"]], gold[f"l1.{int(mean)}.loss"], [gold[f"l1.{int(mean)}.grad"]])
+        run(lambda x, t: B.bce_with_logits(x, t, mean), [gold["pred"] * 3, gold["probs"]], gold[f"bce.{int(mean)}.loss"],
+            [gold[f"bce.{int(mean)}.grad"], gold[f"bce.{int(mean)}.grad_t"]])
+    # No counted row: the smoothed mean is NaN, as the reference's 1/0 factor makes it (Losses.cs:55-58).
+    x = B.tensor(gold["logits"][:2], True)
+    assert np.isnan(B.numpy(B.cross_entropy_smoothed(x, B.ids(np.array([-100, -100])), 0.1, -100, True))).all()
+
+
+def test_loss_family_against_pytorch_golden(B):
+    check_losses(B, 2e-6)
+
+
+def test_splitmix_and_dropout_mask_known_answers():
+    """The SplitMix64 finaliser against the published first outputs of the generator seeded with 0, and the properties
+    the reference's own Dropout test checks (ModuleAndLossTests.cs:62-85): seeded, a new mask per call, about p zeros,
+    kept elements exactly float32(1/(1-p))."""
+    from oracle import tape
+    g = 0x9E3779B97F4A7C15
+    assert [tape.splitmix_finish((i + 1) * g) for i in range(3)] == [0xE220A8397B1DCDAF, 0x6E789E6AA1B965F4, 0x06C45D188009454F]
+    a, b, c = tape.dropout_mask(42, 0, 0.3, 1000), tape.dropout_mask(42, 0, 0.3, 1000), tape.dropout_mask(42, 1, 0.3, 1000)
+    assert np.array_equal(a, b) and not np.array_equal(a, c)
+    assert 240 <= int((a == 0).sum()) <= 360
+    assert np.all(a[a != 0] == np.float32(1.0) / np.float32(0.7))
+    # element i agrees with the scalar recurrence written out on Python integers
+    stream = tape.splitmix_finish(42 + 1 * g)
+    for i in (0, 1, 999):
+        u = np.float32(tape.splitmix_finish(stream + (i + 1) * g) >> 40) * np.float32(1.0 / 16777216.0)
+        assert c[i] == (np.float32(1.0) / np.float32(0.7) if u >= np.float32(0.3) else 0.0)
+
+
 def check_frozen_encoder(B, early_tol, loss_tol, param_tol):
     """testdata/training/frozen: the encoder curve with the embedding and layer 0 frozen (requires_grad False, left out of
     the optimizer). Frozen parameters receive no gradient and keep their bits; the rest follows PyTorch's curve
