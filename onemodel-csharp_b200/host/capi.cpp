@@ -1,6 +1,7 @@
 // Plain-C surface of the host mirror (libonemodel_b200_host.so), used by the Python tests and the bench through
 // ctypes: tensors are opaque handles, operations are dispatched by name, and every C++ exception becomes a status
 // code (1 shape, 2 index, 9 invalid operation, 10 other) with the message kept for omh_last_error.
+#include <stdio.h>
 #include <string.h>
 
 #include <map>
@@ -282,6 +283,111 @@ OMH_API int32_t omh_clip_value(int32_t n, omh_tensor* const* params, float clip)
     GradClip::ClipValue(ps, clip);
   });
 }
+// ---- modules (NnModule, Layers.cs, Recurrent.cs) -----------------------------------------------------------------------
+// A module handle owns its module; a Sequential takes over the modules handed to it (their handles become empty and only
+// need omh_module_free). `ints` / `floats` per kind:
+//   linear [in, out, bias]; conv1d [in, out, kernel, stride, padding, dilation, groups, bias]; conv1d_same / conv1d_valid
+//   [in, out, kernel, dilation, groups, bias]; conv2d [in, out, kernel, stride, padding, bias]; conv_transpose2d [in, out,
+//   kernel, stride, padding, output padding, dilation, groups, bias]; batch_norm2d [channels] {momentum, eps}; layer_norm
+//   [width] {eps}; embedding [count, width, padding index]; dropout [seed] {p}; relu, sigmoid, tanh, flatten,
+//   global_avg_pool2d []; gelu [tanh form]; max_pool2d / avg_pool2d [kernel, stride, padding]; mean [axis].
+// The generator state (SplitMix64, Generator.cs:10-48) is passed in and out so that several modules draw their initial
+// weights from one stream as the reference's constructors do.
+struct omh_module { std::unique_ptr<NnModule> m; };
+OMH_API int32_t omh_module_create(const char* kind, uint64_t* generator_state, int32_t n_ints, const int64_t* ints, int32_t n_floats,
+                                  const double* fl, omh_module** out) {
+  return Guard([&] {
+    std::string k = kind;
+    auto I = [&](int i, int64_t dflt = 0) { return i < n_ints ? ints[i] : dflt; };
+    auto F = [&](int i, double dflt = 0) { return i < n_floats ? fl[i] : dflt; };
+    Generator g(generator_state ? *generator_state : 0);
+    NnModule* m = nullptr;
+    if (k == "linear") m = new Linear((int)I(0), (int)I(1), g, I(2, 1) != 0);
+    else if (k == "conv1d") m = new Conv1d((int)I(0), (int)I(1), (int)I(2), g, (int)I(3, 1), (int)I(4, 0), (int)I(5, 1), (int)I(6, 1), I(7, 1) != 0);
+    else if (k == "conv1d_same" || k == "conv1d_valid")
+      m = new Conv1d((int)I(0), (int)I(1), (int)I(2), g, std::string(k == "conv1d_same" ? "same" : "valid"), (int)I(3, 1), (int)I(4, 1), I(5, 1) != 0);
+    else if (k == "conv2d") m = new Conv2d((int)I(0), (int)I(1), (int)I(2), g, (int)I(3, 1), (int)I(4, 0), I(5, 1) != 0);
+    else if (k == "conv_transpose2d")
+      m = new ConvTranspose2d((int)I(0), (int)I(1), (int)I(2), g, (int)I(3, 1), (int)I(4, 0), (int)I(5, 0), (int)I(6, 1), (int)I(7, 1), I(8, 1) != 0);
+    else if (k == "batch_norm2d") m = new BatchNorm2d((int)I(0), (float)F(0, 0.1), (float)F(1, 1e-5));
+    else if (k == "layer_norm") m = new LayerNorm((int)I(0), (float)F(0, 1e-5));
+    else if (k == "embedding") m = new Embedding((int)I(0), (int)I(1), g, (int)I(2, -1));
+    else if (k == "dropout") m = new Dropout((float)F(0, 0.5), (uint64_t)I(0));
+    else if (k == "relu") m = Lambda::Relu();
+    else if (k == "gelu") m = Lambda::Gelu(I(0) != 0);
+    else if (k == "sigmoid") m = Lambda::Sigmoid();
+    else if (k == "tanh") m = Lambda::Tanh();
+    else if (k == "max_pool2d") m = Lambda::MaxPool2d((int)I(0), (int)I(1, 0), (int)I(2, 0));
+    else if (k == "avg_pool2d") m = Lambda::AvgPool2d((int)I(0), (int)I(1, 0), (int)I(2, 0));
+    else if (k == "global_avg_pool2d") m = Lambda::GlobalAvgPool2d();
+    else if (k == "flatten") m = Lambda::Flatten();
+    else if (k == "mean") m = Lambda::Mean((int)I(0));
+    else throw InvalidOperationException("Unknown module kind '" + k + "'.");
+    if (generator_state) *generator_state = g.State();
+    *out = new omh_module{std::unique_ptr<NnModule>(m)};
+  });
+}
+OMH_API int32_t omh_sequential_create(int32_t n, omh_module* const* layers, omh_module** out) {
+  return Guard([&] {
+    std::vector<NnModule*> ls;
+    for (int i = 0; i < n; i++) {
+      if (!layers[i] || !layers[i]->m) throw InvalidOperationException("A layer handle is empty.");
+      ls.push_back(layers[i]->m.get());
+    }
+    for (int i = 0; i < n; i++) layers[i]->m.release();
+    *out = new omh_module{std::unique_ptr<NnModule>(new Sequential(ls))};
+  });
+}
+OMH_API void omh_module_free(omh_module* m) { delete m; }
+OMH_API int32_t omh_module_forward(omh_module* m, omh_tensor* x, omh_tensor** out) {
+  return Guard([&] { *out = Box(m->m->Forward(Unbox(x))); });
+}
+OMH_API int32_t omh_module_train(omh_module* m, int32_t on) {
+  return Guard([&] { m->m->Train(on != 0); });
+}
+OMH_API int32_t omh_module_zero_grad(omh_module* m) {
+  return Guard([&] { m->m->ZeroGrad(); });
+}
+// which: 0 the state dict (parameters, buffers, children), 1 parameters, 2 trainable parameters, 3 buffers.
+static std::vector<std::pair<std::string, Tensor>> ModuleList(omh_module* m, int32_t which) {
+  switch (which) {
+    case 0: return m->m->StateDict();
+    case 1: return m->m->NamedParameters();
+    case 2: return m->m->NamedTrainableParameters();
+    case 3: return m->m->NamedBuffers();
+    default: throw ArgumentOutOfRangeException("Unknown list.");
+  }
+}
+OMH_API int32_t omh_module_count(omh_module* m, int32_t which, int32_t* count) {
+  return Guard([&] { *count = (int32_t)ModuleList(m, which).size(); });
+}
+OMH_API int32_t omh_module_entry(omh_module* m, int32_t which, int32_t index, char* name, int32_t name_capacity, omh_tensor** tensor) {
+  return Guard([&] {
+    auto list = ModuleList(m, which);
+    if (index < 0 || index >= (int32_t)list.size()) throw ArgumentOutOfRangeException("No such entry.");
+    snprintf(name, (size_t)name_capacity, "%s", list[(size_t)index].first.c_str());
+    *tensor = Box(list[(size_t)index].second);
+  });
+}
+// name null or empty: every parameter. The count of parameters that changed is returned in `changed`.
+OMH_API int32_t omh_module_set_frozen(omh_module* m, const char* name_or_prefix, int32_t frozen, int32_t* changed) {
+  return Guard([&] {
+    bool all = !name_or_prefix || !*name_or_prefix;
+    *changed = frozen ? (all ? m->m->Freeze() : m->m->Freeze(std::string(name_or_prefix)))
+                      : (all ? m->m->Unfreeze() : m->m->Unfreeze(std::string(name_or_prefix)));
+  });
+}
+OMH_API int32_t omh_module_is_frozen(omh_module* m, const char* name, int32_t* frozen) {
+  return Guard([&] { *frozen = m->m->IsFrozen(name) ? 1 : 0; });
+}
+OMH_API int32_t omh_module_load_state(omh_module* m, int32_t n, const char* const* names, omh_tensor* const* tensors) {
+  return Guard([&] {
+    std::vector<std::pair<std::string, Tensor>> state;
+    for (int i = 0; i < n; i++) state.emplace_back(names[i], Unbox(tensors[i]));
+    m->m->LoadStateDict(state);
+  });
+}
+
 // Learning-rate schedules. kind: 0 constant {lr}; 1 step {base, gamma} [step size]; 2 cosine {base, min} [total];
 // 3 warm-up {start factor} [warm-up steps] in front of `after`; 4 warm-up + cosine {base, floor fraction} [warm-up, total];
 // 5 one cycle {max, pct start, div factor, final div factor} [total].

@@ -64,6 +64,100 @@ std::vector<Tensor> NnModule::Parameters() const {
   return out;
 }
 
+std::vector<std::pair<std::string, Tensor>> NnModule::NamedBuffers(const std::string& prefix) const {
+  std::vector<std::pair<std::string, Tensor>> out;
+  for (auto& b : buffers_) out.emplace_back(prefix + b.first, b.second);
+  for (auto& c : children_) {
+    auto sub = c.second->NamedBuffers(prefix + c.first + ".");
+    out.insert(out.end(), sub.begin(), sub.end());
+  }
+  return out;
+}
+
+std::vector<std::pair<std::string, Tensor>> NnModule::NamedTrainableParameters() const {
+  std::vector<std::pair<std::string, Tensor>> out;
+  for (auto& p : NamedParameters())
+    if (p.second.RequiresGrad()) out.push_back(p);
+  return out;
+}
+
+std::vector<Tensor> NnModule::TrainableParameters() const {
+  std::vector<Tensor> out;
+  for (auto& p : NamedTrainableParameters()) out.push_back(p.second);
+  return out;
+}
+
+int NnModule::SetTrainable(const std::function<bool(const std::string&, const Tensor&)>& predicate, bool trainable) {
+  if (!predicate) throw std::invalid_argument("A predicate is required.");
+  int changed = 0;
+  for (auto& p : NamedParameters()) {
+    if (predicate(p.first, p.second) && p.second.RequiresGrad() != trainable) {
+      p.second.SetRequiresGrad(trainable);   // the handle shares the parameter's autograd state
+      changed++;
+    }
+  }
+  return changed;
+}
+
+int NnModule::SetTrainable(const std::string& nameOrPrefix, bool trainable) {
+  if (nameOrPrefix.empty()) throw std::invalid_argument("A parameter name or module path is required.");
+  const std::string prefix = nameOrPrefix + ".";
+  bool found = false;
+  int changed = SetTrainable([&](const std::string& n, const Tensor&) {
+    bool hit = n == nameOrPrefix || n.compare(0, prefix.size(), prefix) == 0;
+    found |= hit;
+    return hit;
+  }, trainable);
+  if (!found) throw std::invalid_argument("No parameter is named '" + nameOrPrefix + "' or lies under a module of that path.");
+  return changed;
+}
+
+int NnModule::Freeze() { return SetTrainable([](const std::string&, const Tensor&) { return true; }, false); }
+int NnModule::Freeze(const std::string& nameOrPrefix) { return SetTrainable(nameOrPrefix, false); }
+int NnModule::Freeze(const std::function<bool(const std::string&, const Tensor&)>& predicate) { return SetTrainable(predicate, false); }
+int NnModule::Unfreeze() { return SetTrainable([](const std::string&, const Tensor&) { return true; }, true); }
+int NnModule::Unfreeze(const std::string& nameOrPrefix) { return SetTrainable(nameOrPrefix, true); }
+int NnModule::Unfreeze(const std::function<bool(const std::string&, const Tensor&)>& predicate) { return SetTrainable(predicate, true); }
+
+bool NnModule::IsFrozen(const std::string& name) const {
+  for (auto& p : NamedParameters())
+    if (p.first == name) return !p.second.RequiresGrad();
+  throw std::invalid_argument("No parameter named '" + name + "'.");
+}
+
+void NnModule::LoadStateDict(const std::vector<std::pair<std::string, Tensor>>& state) {
+  std::vector<std::pair<std::string, Tensor>> mine = StateDict();
+  auto find = [&](const std::string& n) -> const Tensor* {
+    const Tensor* hit = nullptr;
+    for (auto& e : state) {
+      if (e.first != n) continue;
+      if (hit) throw std::invalid_argument("State name '" + n + "' appears twice.");
+      hit = &e.second;
+    }
+    return hit;
+  };
+  for (auto& e : state) find(e.first);   // duplicates anywhere in the given state are an error
+  for (auto& m : mine) {
+    const Tensor* src = find(m.first);
+    if (!src) throw std::invalid_argument("State has no entry '" + m.first + "'.");
+    if (src->GetDType() != m.second.GetDType() || !(src->GetShape() == m.second.GetShape()))
+      throw std::invalid_argument("State entry '" + m.first + "' is " + src->GetShape().ToString() + ", the module has " +
+                                  m.second.GetShape().ToString() + ".");
+  }
+  if (state.size() != mine.size())
+    throw std::invalid_argument("State has " + std::to_string(state.size()) + " entries, the module has " + std::to_string(mine.size()) + ".");
+  for (auto& m : mine) {
+    Tensor src = find(m.first)->Contiguous();
+    if (!m.second.IsContiguous()) throw TensorShapeException("Module state must be contiguous.");
+    if (m.second.Length())
+      Check(om_memcpy_d2d(Device::Current(), m.second.RawData(), src.RawData(), (size_t)m.second.Length() * SizeOf(m.second.GetDType())));
+  }
+}
+
+void NnModule::ZeroGrad() {
+  for (auto& p : NamedParameters()) Backprop::ZeroGrad(p.second);
+}
+
 void NnModule::Train(bool on) {
   Training = on;
   for (auto& c : children_) c.second->Train(on);
@@ -153,6 +247,54 @@ Tensor TransformerEncoderLayer::Forward(const Tensor& input, const Tensor& mask)
   Tensor x1 = Norm1->Forward(Ops::Add(input, a));
   Tensor f = Ff2->Forward(Ops::Gelu(Ff1->Forward(x1)));
   return Norm2->Forward(Ops::Add(x1, f));
+}
+
+void Conv1d::Init(int inCh, int outCh, int kernel, Generator& g, bool bias) {
+  if (kernel < 1 || P.groups < 1) throw ArgumentOutOfRangeException("Conv1d needs a positive kernel size and group count.");
+  if (inCh < 1 || outCh < 1 || inCh % P.groups != 0 || outCh % P.groups != 0)
+    throw std::invalid_argument("Channels must be positive and divisible by the groups.");
+  float bound = 1.0f / sqrtf((float)(inCh / P.groups * kernel));
+  Weight = RegisterParameter("weight", InitUniform(g, bound, Shape{outCh, inCh / P.groups, kernel}));
+  if (bias) Bias = RegisterParameter("bias", InitUniform(g, bound, Shape{outCh}));
+}
+
+Conv1d::Conv1d(int inCh, int outCh, int kernel, Generator& g, int stride, int padding, int dilation, int groups, bool bias) {
+  P.stride = stride;
+  P.padLeft = P.padRight = padding;
+  P.dilation = dilation;
+  P.groups = groups;
+  Init(inCh, outCh, kernel, g, bias);
+}
+
+// "same": the total dilation*(kernel-1) is split with the odd zero on the right; "valid": no padding (Ops.Nn.cs:12-26).
+Conv1d::Conv1d(int inCh, int outCh, int kernel, Generator& g, const std::string& padding, int dilation, int groups, bool bias) {
+  if (kernel < 1) throw ArgumentOutOfRangeException("Conv1d needs a positive kernel size.");
+  P.stride = 1;
+  P.dilation = dilation;
+  P.groups = groups;
+  if (padding == "same") {
+    int total = (dilation > 1 ? dilation : 1) * (kernel - 1);
+    P.padLeft = total / 2;
+    P.padRight = total - total / 2;
+  } else if (padding != "valid") {
+    throw std::invalid_argument("Padding must be \"same\" or \"valid\", not \"" + padding + "\".");
+  }
+  Init(inCh, outCh, kernel, g, bias);
+}
+
+ConvTranspose2d::ConvTranspose2d(int inCh, int outCh, int kernel, Generator& g, int stride, int padding, int outputPadding, int dilation,
+                                 int groups, bool bias) {
+  if (kernel < 1 || groups < 1) throw ArgumentOutOfRangeException("ConvTranspose2d needs a positive kernel size and group count.");
+  if (inCh < 1 || outCh < 1 || inCh % groups != 0 || outCh % groups != 0)
+    throw std::invalid_argument("Channels must be positive and divisible by the groups.");
+  P.strideH = P.strideW = stride;
+  P.padH = P.padW = padding;
+  P.outPadH = P.outPadW = outputPadding;
+  P.dilH = P.dilW = dilation;
+  P.groups = groups;
+  float bound = 1.0f / sqrtf((float)(outCh / groups * kernel * kernel));
+  Weight = RegisterParameter("weight", InitUniform(g, bound, Shape{inCh, outCh / groups, kernel, kernel}));
+  if (bias) Bias = RegisterParameter("bias", InitUniform(g, bound, Shape{outCh}));
 }
 
 Dropout::Dropout(float p, uint64_t seed) : P(p), Seed(seed) {

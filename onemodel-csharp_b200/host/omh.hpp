@@ -317,6 +317,8 @@ class Generator {  // SplitMix64, src/OneModel.Training/Generator.cs:10-48
   uint64_t NextUInt64();
   float NextSingle() { return (float)(NextUInt64() >> 40) * (1.0f / 16777216.0f); }
   float Uniform(float low, float high) { return low + (high - low) * NextSingle(); }
+  uint64_t State() const { return state_; }
+  void Restore(uint64_t state) { state_ = state; }
  private:
   uint64_t state_;
 };
@@ -331,9 +333,31 @@ class NnModule {
   // The state order of the reference (docs/training.md section 1): a module's parameters, then its buffers, then each
   // child with a dotted path. Checkpoints store the model in this order.
   std::vector<std::pair<std::string, Tensor>> StateDict(const std::string& prefix = "") const;
+  std::vector<std::pair<std::string, Tensor>> NamedBuffers(const std::string& prefix = "") const;
+  // Parameters that still require gradients: the list an optimizer gets after Freeze (NnModule.cs:160-200).
+  std::vector<std::pair<std::string, Tensor>> NamedTrainableParameters() const;
+  std::vector<Tensor> TrainableParameters() const;
+  // Freeze / Unfreeze switch RequiresGrad of the named parameter, of every parameter under a module path (a prefix ends
+  // at a dot), of those a predicate picks, or of all; they return how many changed and throw when a name matches
+  // nothing. A frozen parameter receives no gradient (its stored gradient is dropped) and costs no optimizer state.
+  int Freeze();
+  int Freeze(const std::string& nameOrPrefix);
+  int Freeze(const std::function<bool(const std::string&, const Tensor&)>& predicate);
+  int Unfreeze();
+  int Unfreeze(const std::string& nameOrPrefix);
+  int Unfreeze(const std::function<bool(const std::string&, const Tensor&)>& predicate);
+  bool IsFrozen(const std::string& name) const;
+  // Copies every entry of `state` into the module's own tensors (device to device) after checking that names, dtypes and
+  // shapes match one to one (NnModule.cs:316-352).
+  void LoadStateDict(const std::vector<std::pair<std::string, Tensor>>& state);
+  void ZeroGrad();
   void Train(bool on = true);
+  void Eval() { Train(false); }
   bool Training = true;
+  const std::vector<std::pair<std::string, std::unique_ptr<NnModule>>>& Children() const { return children_; }
  protected:
+  int SetTrainable(const std::function<bool(const std::string&, const Tensor&)>& predicate, bool trainable);
+  int SetTrainable(const std::string& nameOrPrefix, bool trainable);
   Tensor RegisterParameter(const std::string& name, Tensor t);
   Tensor RegisterBuffer(const std::string& name, Tensor t);
   template <class M> M* RegisterModule(const std::string& name, M* m) {
@@ -379,6 +403,61 @@ struct Conv2d : NnModule {
   Conv2dParams P;
   Conv2d(int inCh, int outCh, int kernel, Generator& g, int stride = 1, int padding = 0, bool bias = true);
   Tensor Forward(const Tensor& x) override { return Ops::Conv2d(x, Weight, Bias, P); }
+};
+// Conv1d over [N, C, L] (Layers.cs:119-186): symmetric padding, or "same" / "valid" by name (stride 1).
+struct Conv1d : NnModule {
+  Tensor Weight, Bias;
+  Conv1dParams P;
+  Conv1d(int inCh, int outCh, int kernel, Generator& g, int stride = 1, int padding = 0, int dilation = 1, int groups = 1, bool bias = true);
+  Conv1d(int inCh, int outCh, int kernel, Generator& g, const std::string& padding, int dilation = 1, int groups = 1, bool bias = true);
+  Tensor Forward(const Tensor& x) override { return Ops::Conv1d(x, Weight, Bias, P); }
+ private:
+  void Init(int inCh, int outCh, int kernel, Generator& g, bool bias);
+};
+// Transposed convolution, weights [in, out/groups, k, k] (Recurrent.cs:71-115).
+struct ConvTranspose2d : NnModule {
+  Tensor Weight, Bias;
+  ConvTranspose2dParams P;
+  ConvTranspose2d(int inCh, int outCh, int kernel, Generator& g, int stride = 1, int padding = 0, int outputPadding = 0, int dilation = 1,
+                  int groups = 1, bool bias = true);
+  Tensor Forward(const Tensor& x) override { return Ops::ConvTranspose2d(x, Weight, Bias, P); }
+};
+// A parameter-free step of a Sequential (Layers.cs:373-426).
+struct Lambda : NnModule {
+  std::function<Tensor(const Tensor&)> Fn;
+  explicit Lambda(std::function<Tensor(const Tensor&)> fn) : Fn(std::move(fn)) {}
+  static Lambda* Relu() { return new Lambda([](const Tensor& x) { return Ops::Relu(x); }); }
+  static Lambda* Gelu(bool approximateTanh = false) { return new Lambda([=](const Tensor& x) { return Ops::Gelu(x, approximateTanh); }); }
+  static Lambda* Sigmoid() { return new Lambda([](const Tensor& x) { return Ops::Sigmoid(x); }); }
+  static Lambda* Tanh() { return new Lambda([](const Tensor& x) { return Ops::Tanh(x); }); }
+  static Lambda* MaxPool2d(int kernel, int stride = 0, int padding = 0) {
+    int s = stride == 0 ? kernel : stride;
+    return new Lambda([=](const Tensor& x) { return Ops::MaxPool2d(x, kernel, kernel, s, s, padding, padding); });
+  }
+  static Lambda* AvgPool2d(int kernel, int stride = 0, int padding = 0) {
+    int s = stride == 0 ? kernel : stride;
+    return new Lambda([=](const Tensor& x) { return Ops::AvgPool2d(x, kernel, kernel, s, s, padding, padding); });
+  }
+  static Lambda* GlobalAvgPool2d() { return new Lambda([](const Tensor& x) { return Ops::GlobalAvgPool2d(x); }); }
+  static Lambda* Flatten() {
+    return new Lambda([](const Tensor& x) {
+      int rows = x.GetShape()[0];
+      return x.Reshape(Shape{rows, (int)(x.Length() / (rows > 0 ? rows : 1))});
+    });
+  }
+  static Lambda* Mean(int axis) { return new Lambda([=](const Tensor& x) { return Ops::Mean(x, axis); }); }
+  Tensor Forward(const Tensor& x) override { return Fn(x); }
+};
+// Children named "0", "1", ... applied in order; takes ownership of the layers (Layers.cs:428-453).
+struct Sequential : NnModule {
+  explicit Sequential(std::vector<NnModule*> layers) {
+    for (size_t i = 0; i < layers.size(); i++) RegisterModule(std::to_string(i), layers[i]);
+  }
+  Tensor Forward(const Tensor& x) override {
+    Tensor h = x;
+    for (auto& c : children_) h = c.second->Forward(h);
+    return h;
+  }
 };
 struct BatchNorm2d : NnModule {
   Tensor Gamma, Beta, RunningMean, RunningVar;

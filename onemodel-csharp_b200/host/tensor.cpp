@@ -302,7 +302,12 @@ bool Tensor::RequiresGrad() const { return meta_ && meta_->RequiresGrad; }
 Tensor& Tensor::SetRequiresGrad(bool on) {
   if (meta_ && meta_->GradFn) throw InvalidOperationException("Only a leaf's RequiresGrad flag can be changed.");
   if (!meta_) meta_ = std::make_shared<AutogradMeta>();
+  if (meta_->RequiresGrad == on) return *this;
   meta_->RequiresGrad = on;
+  if (!on) {  // a frozen leaf drops its stored gradient (Tensor.cs:418-452)
+    meta_->Grad = Tensor();
+    meta_->GradIsZero = false;
+  }
   return *this;
 }
 

@@ -58,6 +58,7 @@ def host_lib():
             raise RuntimeError(f"{HOST_LIB} is missing: run __graft_entry__.build()")
         _host = C.CDLL(HOST_LIB, mode=C.RTLD_GLOBAL)
         _host.omh_tensor_data.restype = C.c_void_p
+        _host.omh_module_free.argtypes = [C.c_void_p]
         _host.omh_schedule_lr_at.restype = C.c_float
         _host.omh_schedule_lr_at.argtypes = [C.c_void_p, C.c_int64]
         _host.omh_schedule_free.argtypes = [C.c_void_p]
@@ -368,6 +369,94 @@ class Optimizer:
         try:
             if self.h:
                 host_lib().omh_optim_free(self.h)
+        except Exception:
+            pass
+
+
+class Generator:
+    """The SplitMix64 state the reference's module constructors draw initial weights from (Generator.cs:10-48)."""
+
+    def __init__(self, seed):
+        self.state = C.c_uint64(seed)
+
+
+class Module:
+    """NnModule of RecursiveAI.OneModel.Training over host/nn.cpp: layers by kind, Sequential, Train/Eval, Freeze/Unfreeze,
+    StateDict / LoadStateDict, ZeroGrad (NnModule.cs, Layers.cs, Recurrent.cs)."""
+
+    STATE, PARAMETERS, TRAINABLE, BUFFERS = 0, 1, 2, 3
+
+    def __init__(self, kind, generator=None, ints=(), floats=()):
+        ia = (C.c_int64 * max(len(ints), 1))(*[int(v) for v in ints])
+        fa = (C.c_double * max(len(floats), 1))(*[float(v) for v in floats])
+        self.h = C.c_void_p()
+        state = C.byref(generator.state) if generator is not None else None
+        _hcheck(host_lib().omh_module_create(kind.encode(), state, i32(len(ints)), ia, i32(len(floats)), fa, C.byref(self.h)))
+
+    @staticmethod
+    def sequential(*layers):
+        arr = (C.c_void_p * max(len(layers), 1))(*[m.h for m in layers])
+        seq = Module.__new__(Module)
+        seq.h = C.c_void_p()
+        _hcheck(host_lib().omh_sequential_create(i32(len(layers)), arr, C.byref(seq.h)))
+        seq._layers = layers                     # their (now empty) handles are freed with them
+        return seq
+
+    def __call__(self, x):
+        out = C.c_void_p()
+        _hcheck(host_lib().omh_module_forward(self.h, x.h, C.byref(out)))
+        return Tensor(out)
+
+    def train(self, on=True):
+        _hcheck(host_lib().omh_module_train(self.h, i32(1 if on else 0)))
+        return self
+
+    def eval(self):
+        return self.train(False)
+
+    def zero_grad(self):
+        _hcheck(host_lib().omh_module_zero_grad(self.h))
+
+    def entries(self, which=0):
+        """[(name, Tensor)] of the state dict (0), the parameters (1), the trainable parameters (2) or the buffers (3)."""
+        n = C.c_int32()
+        _hcheck(host_lib().omh_module_count(self.h, i32(which), C.byref(n)))
+        out = []
+        for i in range(n.value):
+            name, t = C.create_string_buffer(256), C.c_void_p()
+            _hcheck(host_lib().omh_module_entry(self.h, i32(which), i32(i), name, i32(256), C.byref(t)))
+            out.append((name.value.decode(), Tensor(t)))
+        return out
+
+    def state_dict(self): return self.entries(self.STATE)
+    def named_parameters(self): return self.entries(self.PARAMETERS)
+    def parameters(self): return [t for _, t in self.entries(self.PARAMETERS)]
+    def trainable_parameters(self): return [t for _, t in self.entries(self.TRAINABLE)]
+    def named_trainable_parameters(self): return self.entries(self.TRAINABLE)
+
+    def _set_frozen(self, name, frozen):
+        changed = C.c_int32()
+        _hcheck(host_lib().omh_module_set_frozen(self.h, name.encode() if name else None, i32(1 if frozen else 0), C.byref(changed)))
+        return changed.value
+
+    def freeze(self, name_or_prefix=None): return self._set_frozen(name_or_prefix, True)
+    def unfreeze(self, name_or_prefix=None): return self._set_frozen(name_or_prefix, False)
+
+    def is_frozen(self, name):
+        out = C.c_int32()
+        _hcheck(host_lib().omh_module_is_frozen(self.h, name.encode(), C.byref(out)))
+        return bool(out.value)
+
+    def load_state_dict(self, state):
+        state = list(state)
+        names = (C.c_char_p * max(len(state), 1))(*[n.encode() for n, _ in state])
+        arr = (C.c_void_p * max(len(state), 1))(*[t.h for _, t in state])
+        _hcheck(host_lib().omh_module_load_state(self.h, i32(len(state)), names, arr))
+
+    def __del__(self):
+        try:
+            if self.h:
+                host_lib().omh_module_free(self.h)
         except Exception:
             pass
 

@@ -94,7 +94,7 @@ def cases():
     case("layer_norm", lambda B, t: B.layer_norm(t[0], t[1], t[2]), [_u(r, (3, 2, 8), -2, 2), _u(r, (8,), 0.5, 1.5), _u(r, (8,))])
     ids = np.array([[1, 4, 4], [0, 2, 1]], np.int64)
     case("embedding", lambda B, t: B.embedding(t[0], B.ids(ids)), [_u(r, (5, 6))])
-    mask = np.where(r.uniform(size=(1, 1, 5, 6)) < 0.2, np.float32(-1e9), np.float32(0)).astype(np.float32)
+    mask = np.where(r.uniform(size=(5, 6)) < 0.2, np.float32(-1e9), np.float32(0)).astype(np.float32)
     mask[..., 0] = 0
     case("attention", lambda B, t: B.attention(t[0], t[1], t[2]), [_u(r, (1, 2, 5, 4)), _u(r, (1, 2, 6, 4)), _u(r, (1, 2, 6, 4))])
     case("attention_mask", lambda B, t: B.attention(t[0], t[1], t[2], mask), [_u(r, (1, 2, 5, 4)), _u(r, (1, 2, 6, 4)), _u(r, (1, 2, 6, 4))])
