@@ -289,7 +289,8 @@ OMH_API int32_t omh_clip_value(int32_t n, omh_tensor* const* params, float clip)
 //   linear [in, out, bias]; conv1d [in, out, kernel, stride, padding, dilation, groups, bias]; conv1d_same / conv1d_valid
 //   [in, out, kernel, dilation, groups, bias]; conv2d [in, out, kernel, stride, padding, bias]; conv_transpose2d [in, out,
 //   kernel, stride, padding, output padding, dilation, groups, bias]; batch_norm2d [channels] {momentum, eps}; layer_norm
-//   [width] {eps}; embedding [count, width, padding index]; dropout [seed] {p}; relu, sigmoid, tanh, flatten,
+//   [width] {eps}; embedding [count, width, padding index]; dropout [seed] {p}; recurrent [gru, input, hidden, layers,
+//   bidirectional, batch first]; relu, sigmoid, tanh, flatten,
 //   global_avg_pool2d []; gelu [tanh form]; max_pool2d / avg_pool2d [kernel, stride, padding]; mean [axis].
 // The generator state (SplitMix64, Generator.cs:10-48) is passed in and out so that several modules draw their initial
 // weights from one stream as the reference's constructors do.
@@ -313,6 +314,7 @@ OMH_API int32_t omh_module_create(const char* kind, uint64_t* generator_state, i
     else if (k == "layer_norm") m = new LayerNorm((int)I(0), (float)F(0, 1e-5));
     else if (k == "embedding") m = new Embedding((int)I(0), (int)I(1), g, (int)I(2, -1));
     else if (k == "dropout") m = new Dropout((float)F(0, 0.5), (uint64_t)I(0));
+    else if (k == "recurrent") m = new Recurrent(I(0) != 0, (int)I(1), (int)I(2), g, (int)I(3, 1), I(4) != 0, I(5) != 0);
     else if (k == "relu") m = Lambda::Relu();
     else if (k == "gelu") m = Lambda::Gelu(I(0) != 0);
     else if (k == "sigmoid") m = Lambda::Sigmoid();
@@ -341,6 +343,14 @@ OMH_API int32_t omh_sequential_create(int32_t n, omh_module* const* layers, omh_
 OMH_API void omh_module_free(omh_module* m) { delete m; }
 OMH_API int32_t omh_module_forward(omh_module* m, omh_tensor* x, omh_tensor** out) {
   return Guard([&] { *out = Box(m->m->Forward(Unbox(x))); });
+}
+// A Recurrent stack over rows of different lengths padded to a common T (packed-sequence semantics).
+OMH_API int32_t omh_module_forward_lengths(omh_module* m, omh_tensor* x, int32_t n, const int32_t* lengths, omh_tensor** out) {
+  return Guard([&] {
+    auto* r = dynamic_cast<Recurrent*>(m->m.get());
+    if (!r) throw InvalidOperationException("Only a recurrent stack takes lengths.");
+    *out = Box(r->Forward(Unbox(x), std::vector<int>(lengths, lengths + n)));
+  });
 }
 OMH_API int32_t omh_module_train(omh_module* m, int32_t on) {
   return Guard([&] { m->m->Train(on != 0); });

@@ -482,13 +482,21 @@ struct TransformerEncoderLayer : NnModule {
   Tensor Forward(const Tensor& x) override { return Forward(x, Tensor()); }
   Tensor Forward(const Tensor& x, const Tensor& mask);
 };
-// Stacked (bi)directional LSTM over [T,B,I] (src/OneModel.Training/Recurrent.cs:13-67).
+// Stacked (bi)directional LSTM or GRU over [T,B,I] ([B,T,I] when batchFirst) (src/OneModel.Training/Recurrent.cs:13-67).
+// With `lengths` (one per batch row, each in [1, T]) the rows are sequences of different lengths padded to T, with the
+// semantics of a packed sequence (Ops.Recurrent.cs:280-372): a row's reverse direction starts at its own last step from
+// the zero state, and outputs at padded steps are exactly zero with zero gradient.
 struct Recurrent : NnModule {
   int Hidden, Layers;
-  bool Bidirectional;
+  bool Bidirectional, Gru = false, BatchFirst = false;
   std::vector<Tensor> WIh, WHh, BIh, BHh;  // per layer and direction
   Recurrent(int input, int hidden, int layers, bool bidirectional, Generator& g);
-  Tensor Forward(const Tensor& x) override;
+  Recurrent(bool gru, int input, int hidden, Generator& g, int layers = 1, bool bidirectional = false, bool batchFirst = false);
+  Tensor Forward(const Tensor& x) override { return Forward(x, {}); }
+  Tensor Forward(const Tensor& x, const std::vector<int>& lengths);
+ private:
+  void Init(int input, Generator& g);
+  Tensor RunLayer(const Tensor& x, int k, bool reverse) const;
 };
 
 // Losses.cs:14-129 of the reference: thin compositions of Ops, so their gradients come from the records of those ops.

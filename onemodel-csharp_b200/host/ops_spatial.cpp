@@ -259,10 +259,20 @@ Tensor Ops::CtcLoss(const Tensor& logProbs, const Tensor& targets, const Tensor&
 // directions run over the same input and are concatenated on the feature axis.
 Recurrent::Recurrent(int input, int hidden, int layers, bool bidirectional, Generator& g)
     : Hidden(hidden), Layers(layers), Bidirectional(bidirectional) {
-  float bound = 1.0f / sqrtf((float)hidden);
-  int dirs = bidirectional ? 2 : 1;
-  for (int l = 0; l < layers; l++) {
-    int in = l == 0 ? input : hidden * dirs;
+  Init(input, g);
+}
+
+Recurrent::Recurrent(bool gru, int input, int hidden, Generator& g, int layers, bool bidirectional, bool batchFirst)
+    : Hidden(hidden), Layers(layers), Bidirectional(bidirectional), Gru(gru), BatchFirst(batchFirst) {
+  Init(input, g);
+}
+
+void Recurrent::Init(int input, Generator& g) {
+  if (input < 1 || Hidden < 1 || Layers < 1) throw ArgumentOutOfRangeException("A recurrent stack needs positive sizes and at least one layer.");
+  float bound = 1.0f / sqrtf((float)Hidden);
+  int dirs = Bidirectional ? 2 : 1, gates = Gru ? 3 : 4;
+  for (int l = 0; l < Layers; l++) {
+    int in = l == 0 ? input : Hidden * dirs;
     for (int d = 0; d < dirs; d++) {
       std::string suffix = "_l" + std::to_string(l) + (d ? "_reverse" : "");
       auto init = [&](const Shape& s) {
@@ -270,27 +280,67 @@ Recurrent::Recurrent(int input, int hidden, int layers, bool bidirectional, Gene
         for (float& v : hbuf) v = g.Uniform(-bound, bound);
         return Tensor::FromHost(hbuf.data(), s);
       };
-      WIh.push_back(RegisterParameter("weight_ih" + suffix, init(Shape{4 * hidden, in})));
-      WHh.push_back(RegisterParameter("weight_hh" + suffix, init(Shape{4 * hidden, hidden})));
-      BIh.push_back(RegisterParameter("bias_ih" + suffix, init(Shape{4 * hidden})));
-      BHh.push_back(RegisterParameter("bias_hh" + suffix, init(Shape{4 * hidden})));
+      WIh.push_back(RegisterParameter("weight_ih" + suffix, init(Shape{gates * Hidden, in})));
+      WHh.push_back(RegisterParameter("weight_hh" + suffix, init(Shape{gates * Hidden, Hidden})));
+      BIh.push_back(RegisterParameter("bias_ih" + suffix, init(Shape{gates * Hidden})));
+      BHh.push_back(RegisterParameter("bias_hh" + suffix, init(Shape{gates * Hidden})));
     }
   }
 }
 
-Tensor Recurrent::Forward(const Tensor& x) {
-  Tensor h = x;
-  int dirs = Bidirectional ? 2 : 1;
+Tensor Recurrent::RunLayer(const Tensor& x, int k, bool reverse) const {
+  return Gru ? Ops::GruLayer(x, WIh[k], WHh[k], BIh[k], BHh[k], Tensor(), reverse) : Ops::LstmLayer(x, WIh[k], WHh[k], BIh[k], BHh[k], reverse);
+}
+
+Tensor Recurrent::Forward(const Tensor& x, const std::vector<int>& lengths) {
+  if (x.Rank() != 3) throw TensorShapeException("A recurrent network needs a rank-3 input, not " + x.GetShape().ToString() + ".");
+  Tensor cur = BatchFirst ? x.Transpose(0, 1) : x;
+  const int steps = cur.GetShape()[0], batch = cur.GetShape()[1], dirs = Bidirectional ? 2 : 1;
+  const bool packed = !lengths.empty();
+  Tensor map, mask;
+  if (packed) {
+    if ((int)lengths.size() != batch) throw std::invalid_argument("Expected " + std::to_string(batch) + " lengths, got " + std::to_string(lengths.size()) + ".");
+    // map[t*B+b]: the row of the flattened [T*B] sequence that step t of row b's reversed sequence reads (its own
+    // inverse); steps past the row's length stay where they are.
+    std::vector<int32_t> idx((size_t)steps * batch);
+    std::vector<float> keep((size_t)steps * batch);
+    for (int b = 0; b < batch; b++) {
+      int len = lengths[(size_t)b];
+      if (len < 1 || len > steps)
+        throw std::invalid_argument("Length " + std::to_string(len) + " of row " + std::to_string(b) + " is outside [1, " + std::to_string(steps) + "].");
+      for (int t = 0; t < steps; t++) {
+        idx[(size_t)t * batch + b] = (t < len ? len - 1 - t : t) * batch + b;
+        keep[(size_t)t * batch + b] = t < len ? 1.f : 0.f;
+      }
+    }
+    map = Tensor::FromHostInt32(idx.data(), Shape{steps * batch});
+    mask = Tensor::FromHost(keep.data(), Shape{steps, batch, 1});
+  }
   for (int l = 0; l < Layers; l++) {
-    if (dirs == 2) {
+    Tensor next;
+    if (dirs == 2 && !packed && !Gru) {
       // Both directions in one record: they run concurrently on two streams, forward and backward.
       int k = l * 2;
-      h = Ops::LstmBidirectional(h, {WIh[k], WHh[k], BIh[k], BHh[k], WIh[k + 1], WHh[k + 1], BIh[k + 1], BHh[k + 1]});
-      continue;
+      next = Ops::LstmBidirectional(cur, {WIh[k], WHh[k], BIh[k], BHh[k], WIh[k + 1], WHh[k + 1], BIh[k + 1], BHh[k + 1]});
+    } else {
+      next = RunLayer(cur, l * dirs, false);
+      if (dirs == 2) {
+        Tensor back;
+        if (packed) {
+          int width = cur.GetShape()[2];
+          Tensor rev = Ops::Embedding(cur.Reshape(Shape{steps * batch, width}), map, -1).Reshape(Shape{steps, batch, width});
+          Tensor run = RunLayer(rev, l * dirs + 1, false);
+          back = Ops::Embedding(run.Reshape(Shape{steps * batch, Hidden}), map, -1).Reshape(Shape{steps, batch, Hidden});
+        } else {
+          back = RunLayer(cur, l * dirs + 1, true);
+        }
+        next = Ops::Concat({next, back}, 2);
+      }
     }
-    h = Ops::LstmLayer(h, WIh[l], WHh[l], BIh[l], BHh[l], false);
+    if (packed) next = Ops::Mul(next, mask);
+    cur = next;
   }
-  return h;
+  return BatchFirst ? cur.Transpose(0, 1) : cur;
 }
 
 }  // namespace omh

@@ -407,6 +407,13 @@ class Module:
         _hcheck(host_lib().omh_module_forward(self.h, x.h, C.byref(out)))
         return Tensor(out)
 
+    def forward_lengths(self, x, lengths):
+        """A recurrent stack over rows padded to a common length (Recurrent.Forward(input, lengths) of the reference)."""
+        arr = (C.c_int32 * max(len(lengths), 1))(*[int(v) for v in lengths])
+        out = C.c_void_p()
+        _hcheck(host_lib().omh_module_forward_lengths(self.h, x.h, i32(len(lengths)), arr, C.byref(out)))
+        return Tensor(out)
+
     def train(self, on=True):
         _hcheck(host_lib().omh_module_train(self.h, i32(1 if on else 0)))
         return self

@@ -143,3 +143,47 @@ def test_initialisation_is_seeded_and_bounded(ctx, omb):
     assert np.all(np.abs(w) <= bound)
     again = M("linear", omb.Generator(5), [7, 3, 1])
     assert np.array_equal(again.state_dict()[0][1].numpy(), w)
+
+
+@pytest.mark.parametrize("bidirectional,gru,batch_first", [(False, False, False), (True, False, False), (True, True, False), (True, False, True)])
+def test_padded_rows_equal_rows_run_alone(ctx, omb, bidirectional, gru, batch_first):
+    """A padded batch with lengths gives, for every row, what that row gives alone at its own length, zeros after it, zero
+    input gradient at the padded steps, and weight gradients equal to the sum over the rows run alone
+    (tests/OneModel.Tests/Tensors/PackedRecurrentTests.cs:34-66 of the reference)."""
+    steps, batch, in_size, h, dirs = 6, 4, 3, 5, 2 if bidirectional else 1
+    lengths = [6, 3, 1, 4]
+    r = np.random.default_rng(7)
+    model = omb.Module("recurrent", omb.Generator(9), [int(gru), in_size, h, 2, int(bidirectional), int(batch_first)])
+    x_np = r.uniform(-0.6, 0.6, (steps, batch, in_size)).astype(np.float32)
+    w_np = r.uniform(-1, 1, (steps, batch, h * dirs)).astype(np.float32)
+    lay = (lambda a: np.ascontiguousarray(a.transpose(1, 0, 2))) if batch_first else (lambda a: a)
+
+    x = omb.Tensor.from_numpy(lay(x_np), True)
+    out = model.forward_lengths(x, lengths)
+    model.zero_grad()
+    omb.call("sum", [omb.call("mul", [out, omb.Tensor.from_numpy(lay(w_np))])]).backward()
+    got = lay(out.numpy()) if batch_first else out.numpy()
+    gx = lay(x.grad.numpy()) if batch_first else x.grad.numpy()
+    gw = {n: t.grad.numpy().copy() for n, t in model.named_parameters()}
+
+    want_gw = {n: np.zeros_like(v, dtype=np.float64) for n, v in gw.items()}
+    for b, n in enumerate(lengths):
+        xr = omb.Tensor.from_numpy(lay(x_np[:n, b:b + 1]), True)
+        alone = model(xr)
+        model.zero_grad()
+        omb.call("sum", [omb.call("mul", [alone, omb.Tensor.from_numpy(lay(w_np[:n, b:b + 1]))])]).backward()
+        alone_np = lay(alone.numpy()) if batch_first else alone.numpy()
+        assert np.max(np.abs(got[:n, b] - alone_np[:, 0])) < 1e-5, b
+        assert not got[n:, b].any(), b                                 # exactly zero after the row's length
+        gxr = lay(xr.grad.numpy()) if batch_first else xr.grad.numpy()
+        assert np.max(np.abs(gx[:n, b] - gxr[:, 0])) < 1e-5 and not gx[n:, b].any(), b
+        for name, t in model.named_parameters():
+            want_gw[name] += t.grad.numpy()
+    for name in gw:
+        assert scaled_diff(gw[name], want_gw[name]) <= 1e-5, name
+
+    for bad in ([6, 3, 1], [6, 3, 1, 7], [6, 0, 1, 4]):
+        with pytest.raises(omb.OmError):
+            model.forward_lengths(x, bad)
+    with pytest.raises(omb.OmError):
+        omb.Module("linear", omb.Generator(1), [3, 2, 1]).forward_lengths(x, lengths)
