@@ -1,4 +1,4 @@
-"""The data-parallel arithmetic on CPU ranks (gloo, world size 2): shards of the global batch, loss summed per shard and
+"""The data-parallel arithmetic on CPU ranks (gloo, world sizes 2 and 4): shards of the global batch, loss summed per shard and
 divided by the GLOBAL counted rows, flat gradients summed across ranks in bucket order - against one process that sees
 the whole batch. This is the exchange host/trainer.cpp performs with NCCL on the GPUs (om_dp_allreduce_bucket), restated
 on the CPU oracle; the reference is single-process (Engine.cs:164-191), so the single-process result is the contract."""
@@ -59,13 +59,14 @@ dist.destroy_process_group()
 '''
 
 
-def test_two_shards_sum_to_the_single_process_step(tmp_path, oracle_built):
+@pytest.mark.parametrize("world", [2, 4])
+def test_shards_sum_to_the_single_process_step(tmp_path, oracle_built, world):
     script = tmp_path / "dp_worker.py"
     script.write_text(WORKER % {"root": ROOT})
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29611", OMP_NUM_THREADS="2")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29609 + world), OMP_NUM_THREADS="2")
     procs = []
-    for r in range(2):
-        e = dict(env, RANK=str(r), WORLD_SIZE="2")
+    for r in range(world):
+        e = dict(env, RANK=str(r), WORLD_SIZE=str(world))
         procs.append(subprocess.Popen([sys.executable, str(script)], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
     outs = [p.communicate(timeout=240) for p in procs]
     for p, (o, e) in zip(procs, outs):
