@@ -128,6 +128,15 @@ def cases():
     gidx = np.array([[2, 0], [1, 1]], np.int64)
     case("gather", lambda B, t: B.gather(t[0], gidx, 1), [_u(r, (2, 3, 4))])
 
+    # Dropout (a fixed call number, so the mask is the same for every evaluation) and the loss family (Losses.cs:14-129).
+    case("dropout", lambda B, t: B.dropout(t[0], 0.4, 77, 3), [_u(r, (5, 7))])
+    smooth_t = np.array([2, -100, 0, 5], np.int64)
+    case("cross_entropy_smoothed", lambda B, t: B.cross_entropy_smoothed(t[0], B.ids(smooth_t), 0.2, -100, True), [_u(r, (4, 6), -2, 2)])
+    goal = _u(r, (3, 4))
+    case("mse_loss", lambda B, t: B.mse_loss(t[0], B.tensor(goal), True), [_u(r, (3, 4))])
+    case("l1_loss", lambda B, t: B.l1_loss(t[0], B.tensor(goal), False), [goal + _away_from_zero(r, (3, 4))])
+    case("bce_with_logits", lambda B, t: B.bce_with_logits(t[0], t[1], True), [_u(r, (3, 4), -3, 3), _u(r, (3, 4), 0, 1)])
+
     # CTC through LogSoftmax: ordinary, repeated labels that need a blank between, a shorter input (CtcLossTests.cs:41-64).
     targets, in_len, tgt_len = [1, 2, 2, 3, 1, 1], [7, 6, 4], [2, 3, 1]
     for red, name in ((0, "none"), (1, "mean"), (2, "sum")):
