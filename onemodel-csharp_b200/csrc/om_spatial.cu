@@ -106,10 +106,12 @@ col2im_gather_kernel(ConvGeom g, const float* __restrict__ dcols, float* __restr
     if (PLANES) {
       e = t; c = blockIdx.y; n = blockIdx.z;
     } else {
+      // Planes in (channel, image) order: for one channel and tap the unfolded matrix holds all images' output pixels
+      // next to one another, so the planes a CTA covers read neighbouring segments of the same rows.
       const int pl = t / hw;
       e = t - pl * hw;
-      n = pl / g.cin;
-      c = pl - n * g.cin;
+      c = pl / g.n;
+      n = pl - c * g.n;
     }
     const float* base = dcols + (int64_t)n * n_stride + (int64_t)c * g.kh * g.kw * k_stride;
     const int iy = e / g.w, ix = e - iy * g.w;
