@@ -319,12 +319,13 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, e2e_s = float(t[0]), float(t[1])
 
-    # ---- roofline of the matrix products: one uncaptured, profiled step on rank 0 at N = 1 ----
+    # ---- roofline of the matrix products: one uncaptured, profiled step on rank 0 (the CPU baseline at N = 1 only) ----
     roofline, cpu = None, None
     if rank == 0:
-        prof_tr = tr
-        if world == 1:
-            # A fresh trainer without a graph so that every entry point is timed individually.
+        def profile_on_this_gpu():
+            # A fresh single-GPU trainer without a graph so that every entry point is timed individually. Under a multi-rank
+            # launch it runs on rank 0's GPU alone, after the timed region, while the other ranks wait at the barrier below.
+            cpu = None
             prof_tr = omb.Trainer(kind, cfg, lr=lr, weight_decay=WEIGHT_DECAY[kind], seed=0)
             prof_tr.step(batches[0])
             prof_tr.step(batches[1])
@@ -367,9 +368,19 @@ def main():
                         "share_of_step_device_time": g_ms / total_ms if total_ms else None, "peak_source": peak_src,
                         "by_entry_point_ms_per_step": {r[0]: round(r[2] / psteps, 4) for r in sorted(table, key=lambda r: -r[2])[:12]}}
             prof_tr.close()
-            if not args.skip_cpu:
+            if not args.skip_cpu and world == 1:
                 _, cpu = cpu_baseline(args.workload, steps=1 if args.workload != "c1" else 20, warmup=0 if args.workload != "c1" else 3,
                                       batch_override=args.cpu_batch)
+            return roofline, cpu
+
+        try:
+            roofline, cpu = profile_on_this_gpu()
+        except Exception as exc:      # the throughput line must not be lost to the profiled extra step of a multi-rank run
+            if world == 1:
+                raise
+            print(f"roofline step skipped: {exc}", file=sys.stderr, flush=True)
+    if dist is not None:
+        dist.barrier()
 
     if rank == 0:
         samples = batch * world * K
