@@ -88,22 +88,35 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": float(np.median([s for s, _ in self.samples])), "sm_max_mhz": self.max_mhz, "reasons": reasons}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per gemm_tc_kernel launch, averaged over the matrix-product launches of one
-# ncu capture of this workload (profiles/tensor_pipe_kernels_c3.md gives the command and the per-shape table).
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel family, averaged over the matrix-product
+# launches of one ncu capture of the workload (the summaries under profiles/ give the command and the per-shape table);
+# None where no capture of that workload exists.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c3": 50.1e6}
 WEIGHT_DECAY = {"mlp": 0.01, "mlm": 0.01, "cnn": 0.0, "crnn": 0.0}
 # Batch of the CPU sample: the full step where that takes seconds, a slice of the batch where it would take minutes
 # (samples/s does not depend on the batch for these models; the sample string says what was run).
+WORKLOAD_DTYPE = {"c1": "tf32", "c2": "tf32", "c3": "tf32", "c4": "tf32", "c5": "bf16"}
 CPU_SAMPLE_BATCH = {"c1": 128, "c2": 256, "c3": 64, "c4": 64, "c5": 2}
+CPU_ONE_THREAD_BATCH = {"c1": 128, "c2": 16, "c3": 4, "c4": 8, "c5": 1}
 
 
-def cpu_baseline(workload, steps=1, warmup=0, batch_override=0):
-    """Times the CPU restatement of the reference's training step on this box's cores. Returns (samples/s, dict)."""
+def host_threads():
+    """Cores this process may run on (the affinity mask, not the machine's core count)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def cpu_baseline(workload, steps=1, warmup=0, batch_override=0, threads=0):
+    """Times the CPU restatement of the reference's training step on this box's cores with `threads` OpenMP threads
+    (0 = every core this process may use). The count is set through the library, so a launcher's OMP_NUM_THREADS does not
+    change it, and the count OpenMP reports back is the one printed. Returns (samples/s, dict)."""
     from oracle import configs, oracle as K
     import synth
     K.build()
     kind, cfg, lr, desc, _ = WORKLOADS[workload]
-    cores = os.cpu_count() or 1
+    cores = K.set_threads(threads or host_threads())
     batch = batch_override or CPU_SAMPLE_BATCH[workload]
     times = []
     if kind == "mlp":
@@ -154,19 +167,142 @@ def cpu_baseline(workload, steps=1, warmup=0, batch_override=0):
     sec = float(np.median(times))
     what = "full" if batch == cfg[0] else f"batch-{batch} slice of the batch-{cfg[0]}"
     return batch / sec, {"value": batch / sec, "unit": "samples/s", "cores": cores, "kind": "port",
-                         "sample": f"{steps} {what} step(s) of {workload}, median; OpenMP over {cores} host threads in the products, "
-                                   "convolutions, attention heads and softmax rows, the rest single-threaded as the reference is",
-                         "ms_per_step": sec * 1e3}
+                         "sample": f"{len(times)} {what} step(s) of {workload}, median; {cores} OpenMP thread(s) (count reported by OpenMP) in the "
+                                   "products, convolutions, attention heads and softmax rows, the rest single-threaded as the reference is",
+                         "ms_per_step": sec * 1e3, "steps_timed": len(times)}
+
+
+def torch_cpu_step_rate(workload, steps=3, warmup=1):
+    """Cross-check of the CPU column: the same model and synthetic batch as a PyTorch CPU fp32 training step (forward,
+    backward, optimizer) on every core of this box. The reference measured itself at about twice PyTorch's CPU step time
+    on its recurrent model; a restatement far off that ratio would be suspect. Returns a dict or None."""
+    try:
+        import torch
+        import torch.nn as nn
+        import torch.nn.functional as F
+        import synth
+    except Exception:
+        return None
+    kind, cfg, lr, _, _ = WORKLOADS[workload]
+    batch = CPU_SAMPLE_BATCH[workload]
+    threads = host_threads()
+    torch.set_num_threads(threads)
+    torch.manual_seed(0)
+    if kind == "mlp":
+        widths = cfg[1:]
+        layers = []
+        for i in range(len(widths) - 1):
+            layers.append(nn.Linear(widths[i], widths[i + 1]))
+            if i + 2 < len(widths):
+                layers.append(nn.ReLU())
+        model = nn.Sequential(*layers)
+        opt = torch.optim.AdamW(model.parameters(), lr=lr, weight_decay=0.01)
+
+        def step(s):
+            x, y = synth.mlp_batch(batch, cfg[1], cfg[-1], s)
+            return F.cross_entropy(model(torch.from_numpy(x)), torch.from_numpy(y))
+    elif kind == "cnn":
+        n = cfg[5]
+        channels, strides = cfg[6:6 + n], cfg[6 + n:6 + 2 * n]
+        mods, c = [], cfg[1]
+        for o, st in zip(channels, strides):
+            mods += [nn.Conv2d(c, o, 3, st, 1), nn.BatchNorm2d(o), nn.ReLU()]
+            c = o
+        model = nn.Sequential(*mods, nn.AdaptiveAvgPool2d(1), nn.Flatten(), nn.Linear(c, cfg[4]))
+        opt = torch.optim.SGD(model.parameters(), lr=lr, momentum=0.9)
+
+        def step(s):
+            x, y = synth.cnn_batch(batch, cfg[1], cfg[2], cfg[3], cfg[4], s)
+            return F.cross_entropy(model(torch.from_numpy(x)), torch.from_numpy(y))
+    elif kind == "crnn":
+        class Crnn(nn.Module):
+            def __init__(self):
+                super().__init__()
+                ch, c = cfg[6:10], 1
+                pools = [(2, 2), (2, 2), (2, 1), (4, 1)]
+                mods = []
+                for o, pk in zip(ch, pools):
+                    mods += [nn.Conv2d(c, o, 3, 1, 1), nn.ReLU(), nn.MaxPool2d(pk)]
+                    c = o
+                self.conv = nn.Sequential(*mods)
+                self.rnn = nn.LSTM(c, cfg[4], 2, bidirectional=True)
+                self.fc = nn.Linear(2 * cfg[4], cfg[3])
+
+            def forward(self, x):
+                h = self.conv(x).squeeze(2).permute(2, 0, 1)
+                return F.log_softmax(self.fc(self.rnn(h)[0]), -1)
+
+        model = Crnn()
+        opt = torch.optim.Adam(model.parameters(), lr=lr)
+
+        def step(s):
+            x, targets, lengths = synth.crnn_batch(batch, cfg[1], cfg[2], cfg[3], cfg[5], 5, s)
+            lp = model(torch.from_numpy(x))
+            il = torch.full((batch,), lp.shape[0], dtype=torch.long)
+            tl = torch.from_numpy(lengths.astype(np.int64))
+            return F.ctc_loss(lp, torch.from_numpy(targets[: int(lengths.sum())].astype(np.int64)), il, tl, blank=0, zero_infinity=True)
+    else:
+        _, seq, layers, width, heads, ff, vocab, rows = cfg
+        rows = max(1, int(round(rows * batch / cfg[0])))
+
+        class Layer(nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.qkv, self.o = nn.Linear(width, 3 * width), nn.Linear(width, width)
+                self.n1, self.n2 = nn.LayerNorm(width), nn.LayerNorm(width)
+                self.f1, self.f2 = nn.Linear(width, ff), nn.Linear(ff, width)
+
+            def forward(self, x):
+                b, l, _ = x.shape
+                q, k, v = (t.reshape(b, l, heads, width // heads).transpose(1, 2) for t in self.qkv(x).chunk(3, -1))
+                a = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, l, width)
+                x = self.n1(x + self.o(a))
+                return self.n2(x + self.f2(F.gelu(self.f1(x))))
+
+        class Mlm(nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.tok, self.pos = nn.Embedding(vocab, width), nn.Embedding(seq, width)
+                self.layers = nn.ModuleList([Layer() for _ in range(layers)])
+                self.head = nn.Linear(width, vocab)
+
+            def forward(self, ids, picked):
+                x = self.tok(ids) + self.pos(torch.arange(seq))
+                for layer in self.layers:
+                    x = layer(x)
+                return self.head(x.reshape(-1, width)[picked])
+
+        model = Mlm()
+        opt = torch.optim.AdamW(model.parameters(), lr=lr, weight_decay=0.01)
+
+        def step(s):
+            ids, pos, labels = synth.mlm_batch(batch, seq, vocab, rows, s)
+            return F.cross_entropy(model(torch.from_numpy(ids.astype(np.int64)), torch.from_numpy(pos.astype(np.int64))), torch.from_numpy(labels))
+    times = []
+    for s in range(warmup + steps):
+        t0 = time.perf_counter()
+        opt.zero_grad(set_to_none=True)
+        loss = step(s)
+        loss.backward()
+        opt.step()
+        if s >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = float(np.median(times))
+    return {"value": batch / sec, "unit": "samples/s", "threads": threads, "ms_per_step": sec * 1e3,
+            "sample": f"PyTorch {torch.__version__} CPU fp32, {len(times)} step(s) of batch {batch}, median"}
 
 
 def run_reference(args, rank):
+    """The reference arm: the CPU restatement of the reference's step (the reference is C# and cannot run on this box) on
+    every host core, a bounded number of steps of a bounded sample. Under a multi-rank launch rank 0 alone runs it."""
     if rank != 0:
         return
-    value, cb = cpu_baseline(args.workload, steps=max(1, min(args.steps, 3)), warmup=1 if args.workload == "c1" else 0,
-                             batch_override=args.cpu_batch)
+    timed = max(1, min(args.steps, 50 if args.workload == "c1" else 3))
+    value, cb = cpu_baseline(args.workload, steps=timed, warmup=1 if args.workload == "c1" else 0, batch_override=args.cpu_batch)
     kind, cfg, lr, desc, _ = WORKLOADS[args.workload]
     line = {"impl": "reference", "metric": "train samples/s (fwd+bwd+AdamW)", "value": value, "unit": "samples/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"],
+            "n_gpus": args.gpus, "steps": cb["steps_timed"], "steps_requested": args.steps, "warmup": 1 if args.workload == "c1" else 0,
+            "ms_per_step": cb["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {desc}", "note": "CPU restatement of the reference's C# training path (the .NET reference cannot run on this box)"},
             "cpu_baseline": cb, "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -206,6 +342,8 @@ def main():
     ap.add_argument("--cpu-batch", type=int, default=0, help="batch of the CPU baseline sample (0 = the workload default)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--fp32", action="store_true", help="products on the fp32 FMA kernel instead of the tensor pipe")
+    ap.add_argument("--tf32", action="store_true", help="TF32 operands also where the workload states bf16 operands")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median region is reported")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--ctx-flags", type=int, default=0, help="extra context flags (8 = CTA-pair tiles, 16 = two-stream backward)")
     args = ap.parse_args()
@@ -226,7 +364,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     kind, cfg, lr, desc, gflop = WORKLOADS[args.workload]
     W, K = max(3, args.warmup), max(1, args.steps)
-    flags = 0 if args.fp32 else omb.OM_TF32
+    # Products on the tensor pipe: TF32 operands everywhere, bf16 operands (fp32 accumulation, fp32 master weights) for the
+    # BERT-base shape as its configuration states.
+    bf16 = WORKLOAD_DTYPE[args.workload] == "bf16" and not args.fp32 and not args.tf32
+    flags = 0 if args.fp32 else omb.OM_TF32 | (omb.OM_BF16_OPERANDS if bf16 else 0)
     flags |= args.ctx_flags
     if kind == "crnn" and not args.fp32:
         flags |= omb.OM_SEQ_KERNELS   # the LSTM layers' time steps in one cooperative launch each
@@ -274,50 +415,68 @@ def main():
 
     sampler = ClockSampler(local_rank)
     sampler.start()
-    # ---- value: resident inputs, device-timed ----
+    # ---- value: resident inputs, device-timed; R regions of exactly K steps, each between barriers ----
     tr.load_inputs([t.numpy() for t in pinned[0]])
-    barrier()
+    R = max(1, args.repeats)
     # A workload whose parameters, optimizer state and activations fit the 126 MB L2 is timed step by step with a 256 MB
     # write in between (outside the timed pairs), so that no step finds its operands in cache.
     flush_l2 = kind == "mlp"
-    if flush_l2:
-        scrub = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device=torch.device("cuda", local_rank))
-        pairs = []
-        for i in range(K):
-            with torch.cuda.stream(ext):
-                scrub.fill_(float(i))
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(ext)
-            tr.step_resident()
-            b.record(ext)
-            pairs.append((a, b))
+    scrub = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device=torch.device("cuda", local_rank)) if flush_l2 else None
+    dev_regions, e2e_regions = [], []
+    for rep in range(R):
         barrier()
-        dev_ms = sum(a.elapsed_time(b) for a, b in pairs)
-        del scrub
-    else:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(ext)
-        for i in range(K):
-            tr.step_resident()
-        e1.record(ext)
-        barrier()
-        dev_ms = e0.elapsed_time(e1)
+        if flush_l2:
+            pairs = []
+            for i in range(K):
+                with torch.cuda.stream(ext):
+                    scrub.fill_(float(i))
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(ext)
+                tr.step_resident()
+                b.record(ext)
+                pairs.append((a, b))
+            barrier()
+            dev_regions.append(sum(a.elapsed_time(b) for a, b in pairs))
+        else:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(ext)
+            for i in range(K):
+                tr.step_resident()
+            e1.record(ext)
+            barrier()
+            dev_regions.append(e0.elapsed_time(e1))
+    del scrub
     # ---- e2e: host batch in, loss out, every step ----
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(K):
-        tr.step_ptrs(tables[i % nb], C.byref(loss_c))
-    tr.sync()
-    e2e_s = time.perf_counter() - t0
+    for rep in range(R):
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(K):
+            tr.step_ptrs(tables[i % nb], C.byref(loss_c))
+        tr.sync()
+        e2e_regions.append(time.perf_counter() - t0)
     barrier()
     sampler.stop_flag = True
     sampler.join(timeout=2)
     final_loss = loss_c.value
 
+    # Every region is the max over ranks; the reported one is the median region.
+    replicas_equal = None
     if dist is not None:
-        t = torch.tensor([dev_ms, e2e_s], device="cuda", dtype=torch.float64)
+        t = torch.tensor(dev_regions + e2e_regions, device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_s = float(t[0]), float(t[1])
+        dev_regions, e2e_regions = [float(v) for v in t[:R]], [float(v) for v in t[R:]]
+        # Replicas must hold the same bits after the same number of identical updates: a checksum of every parameter's
+        # bit pattern, compared across ranks.
+        import zlib
+        h = 0
+        for i, (_, shape) in enumerate(tr.named_parameters()):
+            h = zlib.crc32(tr.get_param(i, shape).tobytes(), h)
+        hv = torch.tensor([int(h)], device="cuda", dtype=torch.int64)
+        lo, hi = hv.clone(), hv.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        replicas_equal = bool(int(lo) == int(hi))
+    dev_ms, e2e_s = float(np.median(dev_regions)), float(np.median(e2e_regions))
 
     # ---- roofline of the matrix products: one uncaptured, profiled step on rank 0 (the CPU baseline at N = 1 only) ----
     roofline, cpu = None, None
@@ -353,6 +512,12 @@ def main():
                 pass
             if args.fp32:
                 peak, peak_src = 80.0, "nominal fp32 FMA peak (no tensor pipe on this path)"
+            elif bf16:
+                # The products are timed inside a long step under the power cap: the sustained figure is the denominator.
+                if "bf16_tflops_sustained" in peaks:
+                    peak, peak_src = peaks["bf16_tflops_sustained"], "MEASURED_PEAKS.json bf16_tflops_sustained (cuBLAS bf16 8192^3 back to back for 4 s), of measured"
+                else:
+                    peak, peak_src = 1400.0, "fallback: 1.4 PFLOP/s sustained bf16 (an earlier measurement on this pool), of fallback"
             else:
                 live = tf32_peak_tflops(torch.device("cuda", local_rank))
                 if live:
@@ -369,8 +534,13 @@ def main():
                         "by_entry_point_ms_per_step": {r[0]: round(r[2] / psteps, 4) for r in sorted(table, key=lambda r: -r[2])[:12]}}
             prof_tr.close()
             if not args.skip_cpu and world == 1:
-                _, cpu = cpu_baseline(args.workload, steps=1 if args.workload != "c1" else 20, warmup=0 if args.workload != "c1" else 3,
+                # All cores (three steps, median), one thread on a smaller slice, and the PyTorch CPU cross-check.
+                _, cpu = cpu_baseline(args.workload, steps=3 if args.workload != "c1" else 20, warmup=0 if args.workload != "c1" else 3,
                                       batch_override=args.cpu_batch)
+                _, one = cpu_baseline(args.workload, steps=1 if args.workload != "c1" else 10, warmup=0 if args.workload != "c1" else 2,
+                                      batch_override=CPU_ONE_THREAD_BATCH[args.workload], threads=1)
+                cpu["one_thread"] = {k: one[k] for k in ("value", "unit", "cores", "sample", "ms_per_step")}
+                cpu["torch_cpu"] = torch_cpu_step_rate(args.workload)
             return roofline, cpu
 
         try:
@@ -387,16 +557,21 @@ def main():
         line = {
             "metric": "train samples/s (fwd+bwd+AdamW)", "value": samples / (dev_ms * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32" if args.fp32 else "tf32", "data": "synthetic",
+            "vs_baseline": None, "dtype": "f32" if args.fp32 else ("bf16" if bf16 else "tf32"), "data": "synthetic",
             "config": {"workload": f"{args.workload}: {desc}", "global_batch": batch * world, "parallelism": f"dp{world}",
                        "l2": ("256 MB written between timed steps (the working set fits L2); e2e steps are not flushed" if flush_l2 else
                               "per-step working set (weights, optimizer state, activations) exceeds the 126 MB L2; no flush needed"),
-                       "graph": not args.no_graph, "final_loss": final_loss},
+                       "graph": not args.no_graph, "final_loss": final_loss,
+                       "timed_regions": {"count": R, "steps_each": K, "reported": "median region, each region the max over ranks",
+                                         "ms_per_step_min": min(dev_regions) / K, "ms_per_step_max": max(dev_regions) / K,
+                                         "e2e_ms_per_step_min": min(e2e_regions) * 1e3 / K, "e2e_ms_per_step_max": max(e2e_regions) * 1e3 / K}},
             "e2e": {"value": samples / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": int(kernels_per_step.value) * K if kernels_per_step.value else None,
             "clocks": sampler.summary(),
             "tflops_per_gpu": gflop * K / (dev_ms * 1e-3) / 1e3,
         }
+        if replicas_equal is not None:
+            line["replicas_equal"] = replicas_equal
         if roofline:
             line["roofline"] = roofline
         if cpu:

@@ -229,7 +229,8 @@ int32_t om_colsum(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, float
  * allocation's device-wide synchronisation and late out-of-memory failure are not acceptable in the middle of a run).
  * The per-chunk partial sums go to a fixed 1 MiB array inside the loaded module instead of the context's pool, so the
  * call takes nothing from the pool or the driver. Same arithmetic and same bits as om_colsum.
- * Limit: ceil(rows / 512) * cols <= 131072; beyond it the call returns OM_ERR_UNSUPPORTED and om_colsum is the one to use.
+ * Limit: ceil(rows / 512) * cols <= 131072 and ceil(rows / 512) <= 65535; beyond it the call returns OM_ERR_UNSUPPORTED and
+ * om_colsum is the one to use.
  * The first call on a device looks the array's address up (set-up work: make it before any stream capture). The array
  * is shared by every call on the device and keeps its last contents; calls that overlap on one device race on it, so
  * the caller serialises them. */

@@ -94,6 +94,11 @@ extern "C" int32_t om_colsum_static(om_ctx* ctx, const float* g, int32_t rows, i
                 "om_colsum_static: [%d,%d] needs %lld scratch slots (ceil(rows/512) * cols), the fixed array holds %lld; "
                 "use om_colsum",
                 rows, cols, chunks * (long long)cols, kStaticSlots);
+  // The chunks ride on the grid's y dimension, which ends at 65535: a very tall, very narrow table (more than 33.5 million
+  // rows of one or two columns) fits the array but not the launch, and is refused the same way.
+  if (chunks > 65535)
+    return fail(ctx, OM_ERR_UNSUPPORTED, "om_colsum_static: [%d,%d] needs %lld row chunks of 512, the launch holds 65535; use om_colsum", rows,
+                cols, chunks);
   double* partial = nullptr;
   OM_TRY(scratch_for(ctx, &partial));
   dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)chunks);

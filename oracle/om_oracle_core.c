@@ -10,6 +10,9 @@
  * Build: see oracle/Makefile (-ffp-contract=off, so a*b+c rounds twice unless written as fmaf).
  */
 #include <math.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -72,6 +75,18 @@ static float bf16_round(float x) {
 API void orc_round_bf16(const float* x, float* y, int64_t n) {
   for (int64_t i = 0; i < n; i++) y[i] = bf16_round(x[i]);
 }
+/* Thread count of the OpenMP regions below (the products, attention heads and softmax rows): set explicitly by the timed
+ * CPU baseline so that it does not depend on what a launcher put into OMP_NUM_THREADS. Returns the count in effect. */
+API int orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
+
 /* TF32 operand rounding (10 explicit mantissa bits): mode 0 drops the low 13 bits (what the tensor pipe does to raw
  * fp32 operands), mode 1 rounds to nearest, ties to even (what the product's TMA loads do; measured on B200). */
 API void orc_round_tf32(const float* x, float* y, int64_t n, int nearest) {

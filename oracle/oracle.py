@@ -36,6 +36,11 @@ def lib():
     return _LIB
 
 
+def set_threads(n=0):
+    """Sets the OpenMP thread count of the checker's parallel loops (0 = leave as is); returns the count in effect."""
+    return int(lib().orc_set_threads(int(n)))
+
+
 def _f(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 

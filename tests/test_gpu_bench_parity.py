@@ -1,0 +1,222 @@
+"""The path bench.py times, at the sizes it times it, against the CPU oracle.
+
+bench.py runs every workload with the products on the tensor pipe (OM_TF32; OM_BF16_OPERANDS for the BERT-base shape),
+the LSTM layers of the CRNN in whole-sequence kernels (OM_SEQ_KERNELS) and the step replayed from a captured CUDA
+graph. The tests here build the trainer with exactly those flags at the full configured sizes, give the oracle the
+trainer's own initial weights and the same seeded batches, and compare the loss and every parameter gradient of a
+step taken eagerly and of a step replayed from the graph.
+
+Tolerances. The contract for the tensor-pipe tier is 1e-3 relative / 1e-5 absolute per element against the
+reference's fp32 CPU path. The gate asserted here is the reference's own metric for gradients (scaled maximum error
+max|a - b| / max|b| per tensor, AutogradModelTests.cs:61-81 of the reference) at 1e-3 for TF32, and each test also
+prints, per tensor, the share of elements inside np.isclose(rtol=1e-3, atol=1e-5) so that the distance between the
+two readings is on record. A parameter whose gradient is zero in exact arithmetic (a key bias under softmax's shift
+invariance, a convolution bias in front of a batch norm) holds rounding noise on both sides and is compared against
+the largest gradient of the model instead (TrainingCurveTests.cs:49-60 of the reference does the same)."""
+import numpy as np
+import pytest
+
+import om_binding as omb
+import synth
+from backends import scaled_diff
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def configs(oracle_built):
+    from oracle import configs, tape
+    tape.GEMM_MODE = "fp32"
+    yield configs
+    tape.GEMM_MODE = "fp32"
+
+
+def compare_gradients(tr, named, grads, gate, what, report):
+    """Every parameter gradient of the trainer's last step against the oracle's; returns the worst scaled error."""
+    largest = max(float(np.max(np.abs(g))) for g in grads.values())
+    worst, worst_name, inside, total = 0.0, "", 0, 0
+    for i, (n, s) in enumerate(named):
+        got, want = tr.get_grad(i, s), grads[n]
+        if float(np.max(np.abs(want))) < 1e-5 * largest:
+            assert float(np.max(np.abs(got))) < 1e-4 * largest, (what, n, "zero in theory")
+            continue
+        err = scaled_diff(got, want)
+        close = np.isclose(got, want, rtol=1e-3, atol=1e-5)
+        inside += int(close.sum())
+        total += close.size
+        if err > worst:
+            worst, worst_name = err, n
+        assert err <= gate, (what, n, err)
+    report.append(f"{what}: worst scaled gradient error {worst:.2e} ({worst_name}); "
+                  f"{100.0 * inside / max(total, 1):.3f}% of {total} gradient elements inside rtol 1e-3 / atol 1e-5")
+    return worst
+
+
+def sync_parameters(tr, named, weights):
+    for i, (n, _) in enumerate(named):
+        tr.set_param(i, weights[n])
+
+
+def run_mlm(ctx, configs, cfg, flags, gemm_mode, gate, loss_gate, what, capsys):
+    from oracle import tape
+    batch, seq, layers, width, heads, ff, vocab, rows = cfg
+    ctx.set_flags(flags)
+    ctx.make_current()
+    report = []
+    tr = omb.Trainer("mlm", cfg, lr=1e-4, weight_decay=0.01, seed=0)
+    try:
+        named = tr.named_parameters()
+        weights = {n: tr.get_param(i, s) for i, (n, s) in enumerate(named)}
+        state = {}
+        tape.GEMM_MODE = gemm_mode
+        for step in range(3):
+            ids, pos, labels = synth.mlm_batch(batch, seq, vocab, rows, step)
+            if step == 2:
+                tr.enable_graph()
+            if step > 0:
+                sync_parameters(tr, named, weights)     # both sides differentiate at the same point
+            lg = tr.step([ids, pos, labels])
+            lo, grads = configs.mlm_step(weights, ids.astype(np.int64), pos.astype(np.int64), labels, layers, heads, step + 1, state, lr=1e-4)
+            assert abs(lg - lo) <= loss_gate * abs(lo), (what, step, lg, lo)
+            report.append(f"{what} step {step} ({'graph replay' if step == 2 else 'eager'}): loss {lg:.6f} oracle {lo:.6f} rel {abs(lg - lo) / abs(lo):.2e}")
+            if step != 1:
+                compare_gradients(tr, named, grads, gate, f"{what} step {step}", report)
+    finally:
+        tape.GEMM_MODE = "fp32"
+        tr.close()
+        ctx.set_flags(0)
+    with capsys.disabled():
+        print("\n" + "\n".join(report))
+
+
+def test_c3_full_size_step_with_the_bench_flags(ctx, configs, capsys):
+    """MiniLM shape at full size (6 x d384 h12 ff1536, seq 128, batch 64, vocab 30522, 1229 masked rows), TF32 products,
+    fused attention kernels, pitched logits, split-k weight gradients, graph replay: losses within 1e-3, every gradient
+    within 1e-3 scaled of the fp32 oracle."""
+    run_mlm(ctx, configs, [64, 128, 6, 384, 12, 1536, 30522, 1229], omb.OM_TF32, "fp32", 1e-3, 1e-3, "c3", capsys)
+
+
+def test_c5_slice_with_bf16_operands(ctx, configs, capsys):
+    """BERT-base shape (12 x d768 h12 ff3072, seq 512, vocab 30522) on a batch-2 slice, the products of the Linear layers
+    with bf16 operands (round to nearest even) and fp32 accumulation, fp32 master weights. Against the oracle that rounds
+    the operands of the same products the same way: what is left is the summation order and the attention kernels' TF32
+    products, held to the TF32 gate. Against the fp32 oracle the bf16 rounding itself shows: 8 mantissa bits per operand,
+    held to 2e-2 scaled over the 12-layer chain."""
+    cfg = [2, 512, 12, 768, 12, 3072, 30522, 154]
+    run_mlm(ctx, configs, cfg, omb.OM_TF32 | omb.OM_BF16_OPERANDS, "bf16", 2e-3, 1e-3, "c5 slice vs bf16-rounding oracle", capsys)
+    run_mlm(ctx, configs, cfg, omb.OM_TF32 | omb.OM_BF16_OPERANDS, "fp32", 2e-2, 2e-3, "c5 slice vs fp32 oracle", capsys)
+
+
+def test_c2_full_size_step_with_the_bench_flags(ctx, configs, capsys):
+    """The CNN at full size (256 x 3 x 32 x 32, eight 3x3 convolutions 64..512 + batch norm + ReLU, SGD momentum), the
+    convolution products on the tensor pipe: the weight gradients here contract over up to 262144 terms."""
+    cfg = [256, 3, 32, 32, 10, 8, 64, 64, 128, 128, 256, 256, 512, 512, 1, 1, 2, 1, 2, 1, 2, 1]
+    ch, strides = cfg[6:14], cfg[14:22]
+    ctx.set_flags(omb.OM_TF32)
+    ctx.make_current()
+    report = []
+    tr = omb.Trainer("cnn", cfg, lr=0.1, weight_decay=0.0, seed=0)
+    try:
+        named = tr.named_parameters()
+        weights = {n: tr.get_param(i, s) for i, (n, s) in enumerate(named)}
+        running = {f"bn{i}": (np.zeros(c, np.float32), np.ones(c, np.float32)) for i, c in enumerate(ch)}
+        state = {}
+        for step in range(3):
+            x, y = synth.cnn_batch(256, 3, 32, 32, 10, step)
+            if step == 2:
+                tr.enable_graph()
+            if step > 0:
+                sync_parameters(tr, named, weights)
+            lg = tr.step([x, y])
+            lo, grads = configs.cnn_step(weights, running, x, y, strides, state, lr=0.1)
+            report.append(f"c2 step {step}: loss {lg:.6f} oracle {lo:.6f} rel {abs(lg - lo) / abs(lo):.2e}")
+            assert abs(lg - lo) <= 2e-3 * abs(lo), (step, lg, lo)
+            if step == 0:
+                compare_gradients(tr, named, grads, 2e-3, "c2 step 0", report)
+    finally:
+        tr.close()
+        ctx.set_flags(0)
+    with capsys.disabled():
+        print("\n" + "\n".join(report))
+
+
+def test_c4_full_size_step_with_the_bench_flags(ctx, configs, capsys):
+    """The CRNN at full size (64 x 1 x 32 x 256, conv 64-128-256-256, two BiLSTM-256 layers, 97 classes, CTC, Adam) with
+    the whole-sequence LSTM kernels and TF32 products, against the fp32 oracle (not against the step-by-step GPU path)."""
+    cfg = [64, 32, 256, 97, 256, 20, 64, 128, 256, 256]
+    ctx.set_flags(omb.OM_TF32 | omb.OM_SEQ_KERNELS)
+    ctx.make_current()
+    report = []
+    tr = omb.Trainer("crnn", cfg, lr=1e-3, weight_decay=0.0, seed=0)
+    try:
+        named = tr.named_parameters()
+        weights = {n: tr.get_param(i, s) for i, (n, s) in enumerate(named)}
+        state = {}
+        for step in range(3):
+            x, targets, lengths = synth.crnn_batch(64, 32, 256, 97, 20, 5, step)
+            if step == 2:
+                tr.enable_graph()
+            if step > 0:
+                sync_parameters(tr, named, weights)
+            lg = tr.step([x, targets, lengths])
+            lo, grads = configs.crnn_step(weights, x, targets[: int(lengths.sum())], lengths, step + 1, state)
+            report.append(f"c4 step {step}: loss {lg:.6f} oracle {lo:.6f} rel {abs(lg - lo) / abs(lo):.2e}")
+            assert abs(lg - lo) <= 1e-3 * abs(lo), (step, lg, lo)
+            if step != 1:
+                compare_gradients(tr, named, grads, 2e-3, f"c4 step {step}", report)
+    finally:
+        tr.close()
+        ctx.set_flags(0)
+    with capsys.disabled():
+        print("\n" + "\n".join(report))
+
+
+def test_c1_100_steps_on_the_tensor_pipe(ctx, configs):
+    """The MLP at full size with TF32 products, replayed from a graph from step 3 on: every loss within 1e-3 of the fp32
+    oracle's curve and the loss after 100 steps within 1 %."""
+    ctx.set_flags(omb.OM_TF32)
+    ctx.make_current()
+    tr = omb.Trainer("mlp", [128, 784, 512, 512, 10], lr=1e-3, weight_decay=0.01, seed=0)
+    try:
+        named = tr.named_parameters()
+        params = [tr.get_param(i, s) for i, (_, s) in enumerate(named)]
+        state = {}
+        for step in range(100):
+            x, y = synth.mlp_batch(128, 784, 10, step)
+            if step == 2:
+                tr.enable_graph()
+            lg = tr.step([x, y])
+            lo, _ = configs.mlp_step(params, x, y, step + 1, state=state)
+            assert abs(lg - lo) <= 2e-3 * abs(lo), (step, lg, lo)
+        assert abs(lg - lo) <= 0.01 * abs(lo)
+    finally:
+        tr.close()
+        ctx.set_flags(0)
+
+
+def test_c3_width_loss_curve_stays_within_1_percent(ctx, configs, capsys):
+    """The loss-after-N-steps tier on the encoder: the full MiniLM widths, depth, sequence length and vocabulary at batch 4
+    (the oracle takes a fraction of a second per step), 60 AdamW steps with TF32 products replayed from a graph, each
+    side training on its own weights: every loss within 1 % of the oracle's."""
+    cfg = [4, 128, 6, 384, 12, 1536, 30522, 77]
+    ctx.set_flags(omb.OM_TF32)
+    ctx.make_current()
+    tr = omb.Trainer("mlm", cfg, lr=1e-4, weight_decay=0.01, seed=0)
+    try:
+        named = tr.named_parameters()
+        weights = {n: tr.get_param(i, s) for i, (n, s) in enumerate(named)}
+        state = {}
+        worst = 0.0
+        for step in range(60):
+            ids, pos, labels = synth.mlm_batch(4, 128, 30522, 77, step)
+            if step == 2:
+                tr.enable_graph()
+            lg = tr.step([ids, pos, labels])
+            lo, _ = configs.mlm_step(weights, ids.astype(np.int64), pos.astype(np.int64), labels, 6, 12, step + 1, state, lr=1e-4)
+            worst = max(worst, abs(lg - lo) / abs(lo))
+            assert abs(lg - lo) <= 0.01 * abs(lo), (step, lg, lo)
+    finally:
+        tr.close()
+        ctx.set_flags(0)
+    with capsys.disabled():
+        print(f"\nencoder curve over 60 steps: worst relative loss difference {worst:.2e}, last loss {lg:.5f} / {lo:.5f}")

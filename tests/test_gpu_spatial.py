@@ -56,7 +56,10 @@ def test_conv2d_fwd_bwd(ctx, K, n, cin, h, w, cout, k, stride, pad, groups):
 
 @pytest.mark.parametrize("n,cin,h,w,cout,k,stride,pad", [
     (8, 64, 16, 16, 128, 3, 2, 1), (16, 32, 16, 16, 64, 3, 1, 1), (4, 3, 32, 32, 64, 3, 1, 1), (6, 16, 10, 10, 24, 3, 1, 1),
-    (4, 128, 4, 4, 256, 3, 1, 1)])
+    (4, 128, 4, 4, 256, 3, 1, 1),
+    # whole layers of the CNN and CRNN configurations: the weight gradient contracts over 256 * 1024 = 262144 and
+    # 64 * 2048 = 131072 terms as one product with a fixed split of k
+    (256, 64, 32, 32, 64, 3, 1, 1), (256, 64, 32, 32, 128, 3, 2, 1), (64, 64, 16, 128, 128, 3, 1, 1)])
 def test_conv2d_on_the_tensor_pipe(ctx, K, n, cin, h, w, cout, k, stride, pad):
     """With OM_TF32 the three convolution products run as one tensor-pipe product over all images (TF32 operands, fp32
     accumulation): forward, input gradient and weight gradient within the TF32 tier of the contract (1e-3 scaled).
@@ -309,8 +312,8 @@ def test_bidirectional_lstm_on_two_streams_equals_two_layers(ctx, B, tf32):
 @pytest.mark.parametrize("fused", [False, True])
 def test_whole_sequence_lstm_kernels(ctx, B, t, b, i, h, fused):
     """OM_SEQ_KERNELS: all time steps of a layer (or of both directions) in one cooperative launch, forward and backward,
-    against the step-by-step paths (fp32 and TF32). A batch above 256 rows runs the sequence kernel forward and the
-    step-by-step path backward."""
+    against the CPU oracle with fp32 and with TF32 input products. A batch above 256 rows runs the sequence kernel forward
+    and the step-by-step path backward."""
     import om_binding as omb
     r = np.random.default_rng(t * 100 + b)
     xs = r.standard_normal((t, b, i)).astype(np.float32)
@@ -331,16 +334,27 @@ def test_whole_sequence_lstm_kernels(ctx, B, t, b, i, h, fused):
         B.backward(B.sum(B.mul(y, B.tensor(proj))))
         return [y.numpy(), B.grad(x)] + [B.grad(p) for p in w]
 
+    def run_oracle():
+        from backends import OracleBackend
+        O = OracleBackend()
+        x = O.tensor(xs, True)
+        w = [O.tensor(a, True) for a in ws]
+        y = O.concat([O.lstm_layer(x, w[0], w[1], w[2], w[3], False), O.lstm_layer(x, w[4], w[5], w[6], w[7], True)], 2)
+        O.backward(O.sum(O.mul(y, O.tensor(proj))))
+        return [O.numpy(y), O.grad(x)] + [O.grad(p) for p in w]
+
     try:
-        want = run(0)
-        step = run(omb.OM_TF32)
+        want = run_oracle()
+        exact = run(omb.OM_SEQ_KERNELS)
         got = run(omb.OM_TF32 | omb.OM_SEQ_KERNELS)
         again = run(omb.OM_TF32 | omb.OM_SEQ_KERNELS)
-        for k, (p, q0, q, q2) in enumerate(zip(want, step, got, again)):
-            # Under OM_TF32 the input products (and the x / W_ih gradients) run on the tensor pipe on both fast paths, and the
-            # rounding compounds over the time steps; the sequence kernels keep the recurrent products in fp32, so they must
-            # be at least as close to the fp32 path as the step-by-step fast path is (with a floor for the short cases).
-            assert scaled_diff(q, p) <= max(2e-3, 1.25 * scaled_diff(q0, p)), k
+        for k, (p, e, q, q2) in enumerate(zip(want, exact, got, again)):
+            # Against the CPU oracle. With fp32 products the sequence kernels differ from it only in the order of the
+            # recurrent dot products (fixed k ranges): 1e-4, the gate of the exact tier. Under OM_TF32 the input products and
+            # the x / W_ih gradients run on the tensor pipe (the recurrent products stay fp32) and the rounding of one
+            # step's gates feeds the next step, so the chain is held to 2e-3 where a single product is held to 1e-3.
+            assert scaled_diff(e, p) <= 1e-4, k
+            assert scaled_diff(q, p) <= 2e-3, k
             assert np.array_equal(q, q2), k   # run to run the same bits
     finally:
         ctx.set_flags(0)

@@ -47,6 +47,11 @@ def test_sizes_beyond_the_array_are_refused(ctx):
     with pytest.raises(omb.OmError) as e:
         ctx.call("om_colsum_static", ctx.handle, G.ptr, i32(rows), i32(cols), O.ptr, i32(0))
     assert "131072" in str(e.value) and "om_colsum" in str(e.value)
+    # Tall and narrow: 65537 chunks x 1 column fits the array but not the launch grid. Refused before any kernel runs (the
+    # pointers are never read, so a small buffer stands in for the 134 MB table).
+    with pytest.raises(omb.OmError) as e:
+        ctx.call("om_colsum_static", ctx.handle, G.ptr, i32(65537 * 512), i32(1), O.ptr, i32(0))
+    assert "65535" in str(e.value) and "om_colsum" in str(e.value)
     # The context stays usable and the largest admitted size works.
     rows, cols = 512, 131072
     g = np.ones((rows, cols), np.float32)
