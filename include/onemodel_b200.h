@@ -49,8 +49,9 @@ typedef enum om_status {
 /* Context flags. OM_TF32: matrix products run on the tcgen05 tensor pipe with TF32 operands and fp32
  * accumulation (TensorCompute.Mode = Fast); without it they run on an fp32 FMA kernel that keeps the
  * reference's one-accumulator, increasing-k order (TensorCompute.Mode = Exact tier of tolerance,
- * src/OneModel/Tensors/Autograd/TensorCompute.cs:22-78). OM_BF16_OPERANDS: operands of matrix products are
- * rounded to bfloat16 (round to nearest even) and multiplied on the tensor pipe with fp32 accumulation.
+ * src/OneModel/Tensors/Autograd/TensorCompute.cs:22-78). OM_BF16_OPERANDS (with OM_TF32): the host layer above this
+ * library keeps bfloat16 copies of the tensors that feed the Linear products and calls the om_*_bf16 entry points below
+ * (bfloat16 operands rounded to nearest even, fp32 accumulation); the fp32-operand entry points are unchanged by it.
  * OM_CHECKED: index operands are range-checked on the device and buffers carry canary words
  * (the reference's Checked build, docs/tensors.md:108-110). OM_PAIR_TILES (with OM_TF32): every plain product the
  * CTA-pair kernel can take runs on it (tcgen05 cta_group::2, 256-row tiles: fewer operand bytes per SM); without the
@@ -61,7 +62,9 @@ typedef enum om_status {
  * OM_SEQ_KERNELS (with OM_TF32): an LSTM layer whose shape fits (hidden a multiple of 16, batch <= 256 for the backward)
  * runs all its time steps in one cooperative launch with fp32 recurrent products, instead of a product and a gate
  * kernel per step. OM_OVERLAP_LAUNCHES: the frequent kernels are launched as programmatic dependents of their
- * predecessor in the stream, so that launch latency and prologue overlap the predecessor's tail (same results). */
+ * predecessor in the stream, so that launch latency and prologue overlap the predecessor's tail (same results).
+ * OM_PERSISTENT_TILES (with OM_TF32): plain products run on the persistent CTA-pair kernel that the bfloat16 products
+ * always use (two accumulator buffers in tensor memory: a tile's read-back and stores run under the next tile's MMAs). */
 #define OM_TF32 1u
 #define OM_BF16_OPERANDS 2u
 #define OM_CHECKED 4u
@@ -69,6 +72,7 @@ typedef enum om_status {
 #define OM_TWO_STREAMS 16u
 #define OM_SEQ_KERNELS 32u
 #define OM_OVERLAP_LAUNCHES 64u
+#define OM_PERSISTENT_TILES 128u
 
 typedef enum om_dtype { OM_F32 = 0, OM_I32 = 1, OM_I64 = 2 } om_dtype;
 
@@ -159,6 +163,26 @@ int32_t om_linear_bwd_ld(om_ctx* ctx, const float* g, int32_t ldg, const float* 
 int32_t om_linear_bwd(om_ctx* ctx, const float* g, const float* x, const float* W, int32_t rows,
                       int32_t in_features, int32_t out_features, float* dx, float* dW, float* dbias,
                       int32_t accumulate_w);
+
+/* ---- products with bfloat16 operands (OM_BF16_OPERANDS) ------------------------------------------------------------
+ * The tier BERT-base-shape training is configured for: product operands rounded to bfloat16 (round to nearest even,
+ * the rule of docs/tensors.md section 10 / BFloat16.FromSingleBits, src/OneModel/Tensors/Float16.cs:121-160),
+ * fp32 accumulation, fp32 results, fp32 master weights. The reference has no such path on the CPU (its Dense.Gemm,
+ * Dense.cs:12-48, multiplies fp32); these entry points stand where om_matmul / om_linear_fwd / om_linear_bwd stand, with
+ * the operands given as bfloat16 copies that the caller keeps beside the fp32 tensors (one om_cast_bf16 per tensor and
+ * version, reused by every product that reads it: forward and weight gradient share x, forward and input gradient share
+ * W, the two gradients share g). Operand pitches must be multiples of 8 elements, the pitch of C a multiple of 4, base
+ * addresses 16-byte aligned (OM_ERR_UNSUPPORTED otherwise: use the fp32-operand entry point). */
+/* dst[i] = bfloat16(src[i]), round to nearest even. */
+int32_t om_cast_bf16(om_ctx* ctx, const float* src, uint16_t* dst, int64_t n);
+int32_t om_matmul_bf16(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m, int32_t n, int32_t k, const uint16_t* A,
+                       int32_t lda, const uint16_t* B, int32_t ldb, float* C, int32_t ldc, int32_t accumulate);
+int32_t om_linear_fwd_bf16(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows,
+                           int32_t in_features, int32_t out_features, float* y, int32_t ldy);
+/* g16 is the bfloat16 copy of g (same pitch ldg); the bias gradient sums the fp32 g. */
+int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x,
+                           const uint16_t* W, int32_t rows, int32_t in_features, int32_t out_features, float* dx,
+                           float* dW, float* dbias, int32_t accumulate_w);
 
 /* ---- elementwise ------------------------------------------------------------------------------------ */
 

@@ -49,7 +49,7 @@ static int32_t check_gemm_args(om_ctx* ctx, const char* who, int ta, int tb, int
 int32_t gemm_dispatch(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B,
                       int ldb, float* C, int ldc, int acc, const float* bias) {
   if (m == 0 || n == 0) return OM_OK;
-  if ((ctx->flags & (OM_TF32 | OM_BF16_OPERANDS)) && gemm_tc_supported(ctx, ta, tb, m, n, k, A, lda, B, ldb, C, ldc))
+  if ((ctx->flags & OM_TF32) && gemm_tc_supported(ctx, ta, tb, m, n, k, A, lda, B, ldb, C, ldc))
     return gemm_tc(ctx, ta, tb, m, n, k, A, lda, B, ldb, C, ldc, acc, bias);
   // A deep product with a small result that the tensor-pipe kernel cannot take (a pitch that is not a multiple of 16
   // bytes, e.g. the weight gradient of a 97-class output layer) would run as a handful of CTAs each walking all of k.

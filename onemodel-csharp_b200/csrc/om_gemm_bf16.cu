@@ -1,0 +1,117 @@
+// Products with bfloat16 operands and fp32 accumulation (the OM_BF16_OPERANDS tier): the caller keeps, beside each fp32
+// tensor that feeds a product, a bfloat16 copy rounded to nearest even (om_cast_bf16, or the fused producers that write it
+// on their way out), and the entry points here multiply those copies on the tensor pipe (om_gemm_ws.cu, kind::f16) into
+// fp32 results. Master weights, gradients, bias sums and everything that is not a product operand stay fp32.
+#include <cuda_bf16.h>
+
+#include "om_common.cuh"
+
+namespace om {
+
+bool gemm_ws_supported(om_ctx* ctx, int elem, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, const float* C,
+                       long long ldc);
+int32_t gemm_ws(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, float* C,
+                long long ldc, int acc, const float* bias);
+int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64_t ld, float* out, int32_t accumulate);
+
+// Eight elements per thread: two 16-byte loads, one 16-byte store.
+__global__ void cast_bf16_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, int64_t n) {
+  pdl_enter();
+  const int64_t n8 = n >> 3;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(src) + 2 * i);
+    const float4 b = __ldg(reinterpret_cast<const float4*>(src) + 2 * i + 1);
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+    uint4 o;
+    o.x = *reinterpret_cast<uint32_t*>(&p0);
+    o.y = *reinterpret_cast<uint32_t*>(&p1);
+    o.z = *reinterpret_cast<uint32_t*>(&p2);
+    o.w = *reinterpret_cast<uint32_t*>(&p3);
+    reinterpret_cast<uint4*>(dst)[i] = o;
+  }
+  // Tail (fewer than eight elements), by the first threads of the grid.
+  const int64_t t = (n8 << 3) + blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (t < n) {
+    __nv_bfloat16 v = __float2bfloat16_rn(src[t]);
+    dst[t] = *reinterpret_cast<uint16_t*>(&v);
+  }
+}
+
+static int32_t check_args(om_ctx* ctx, const char* who, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, const float* C,
+                          long long ldc) {
+  if (m < 0 || n < 0 || k < 1) return fail(ctx, OM_ERR_SHAPE, "%s: m %d n %d k %d", who, m, n, k);
+  if (m == 0 || n == 0) return OM_OK;
+  if (!gemm_ws_supported(ctx, 1, m, n, k, A, lda, B, ldb, C, ldc))
+    return fail(ctx, OM_ERR_UNSUPPORTED,
+                "%s: bfloat16 operands need pitches that are multiples of 8 elements (A %lld, B %lld), a C pitch that is a multiple of 4 (%lld) "
+                "and 16-byte aligned base addresses; use the fp32-operand entry point for this shape",
+                who, lda, ldb, ldc);
+  return OM_OK;
+}
+
+}  // namespace om
+
+using namespace om;
+
+extern "C" {
+
+int32_t om_cast_bf16(om_ctx* ctx, const float* src, uint16_t* dst, int64_t n) {
+  OM_CHECK_CTX(ctx);
+  if (n < 0) return fail(ctx, OM_ERR_SHAPE, "om_cast_bf16: n %lld", (long long)n);
+  if (n == 0) return OM_OK;
+  if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
+    return fail(ctx, OM_ERR_ARG, "om_cast_bf16: source and destination must be 16-byte aligned");
+  ProfileScope prof(ctx, "om_cast_bf16", 0.0, 6.0 * (double)n);
+  launch_chained(ctx, cast_bf16_kernel, grid_for(ctx, (n + 7) / 8, 256), 256, 0, src, dst, n);
+  OM_LAUNCH_CHECK(ctx, "om_cast_bf16");
+  return OM_OK;
+}
+
+int32_t om_matmul_bf16(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m, int32_t n, int32_t k, const uint16_t* A, int32_t lda,
+                       const uint16_t* B, int32_t ldb, float* C, int32_t ldc, int32_t accumulate) {
+  OM_CHECK_CTX(ctx);
+  OM_TRY(check_args(ctx, "om_matmul_bf16", m, n, k, A, lda, B, ldb, C, ldc));
+  if (m == 0 || n == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_matmul", 2.0 * m * n * k, 2.0 * ((double)m * k + (double)k * n) + 4.0 * (double)m * n);
+  return gemm_ws(ctx, 1, transA, transB, m, n, k, A, lda, B, ldb, C, ldc, accumulate, nullptr);
+}
+
+int32_t om_linear_fwd_bf16(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows, int32_t in_features,
+                           int32_t out_features, float* y, int32_t ldy) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 0 || in_features < 1 || out_features < 1 || ldy < out_features)
+    return fail(ctx, OM_ERR_SHAPE, "om_linear_fwd_bf16: rows %d in %d out %d ldy %d", rows, in_features, out_features, ldy);
+  OM_TRY(check_args(ctx, "om_linear_fwd_bf16", rows, out_features, in_features, x, in_features, W, in_features, y, ldy));
+  if (rows == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_linear_fwd", 2.0 * rows * in_features * out_features,
+                    2.0 * ((double)rows * in_features + (double)in_features * out_features) + 4.0 * (double)rows * out_features);
+  return gemm_ws(ctx, 1, 0, 1, rows, out_features, in_features, x, in_features, W, in_features, y, ldy, 0, bias);
+}
+
+int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x, const uint16_t* W, int32_t rows,
+                           int32_t in_features, int32_t out_features, float* dx, float* dW, float* dbias, int32_t accumulate_w) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 0 || in_features < 1 || out_features < 1 || ldg < out_features)
+    return fail(ctx, OM_ERR_SHAPE, "om_linear_bwd_bf16: rows %d in %d out %d ldg %d", rows, in_features, out_features, ldg);
+  if (rows == 0) return OM_OK;
+  const double flops = 2.0 * rows * in_features * out_features;
+  if (dx) {
+    // dx[rows, in] = g[rows, out] * W[out, in]
+    OM_TRY(check_args(ctx, "om_linear_bwd_bf16 (input gradient)", rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features));
+    ProfileScope prof(ctx, "om_linear_bwd.dgrad", flops, 2.0 * ((double)rows * out_features + (double)in_features * out_features) + 4.0 * (double)rows * in_features);
+    OM_TRY(gemm_ws(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, 0, nullptr));
+  }
+  if (dW) {
+    // dW[out, in] = g[rows, out]^T * x[rows, in]
+    OM_TRY(check_args(ctx, "om_linear_bwd_bf16 (weight gradient)", out_features, in_features, rows, g16, ldg, x, in_features, dW, in_features));
+    ProfileScope prof(ctx, "om_linear_bwd.wgrad", flops, 2.0 * ((double)rows * out_features + (double)rows * in_features) + 4.0 * (double)in_features * out_features);
+    OM_TRY(gemm_ws(ctx, 1, 1, 0, out_features, in_features, rows, g16, ldg, x, in_features, dW, in_features, accumulate_w, nullptr));
+  }
+  // The bias gradient is a sum of fp32 values, not a product: it reads the fp32 gradient.
+  if (dbias) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w));
+  return OM_OK;
+}
+
+}  // extern "C"

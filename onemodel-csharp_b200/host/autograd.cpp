@@ -28,6 +28,7 @@ std::shared_ptr<BackwardRecord> BackwardRecord::Create(OpKind op, int savedSlots
   auto rec = std::make_shared<BackwardRecord>();
   rec->Op = op;
   rec->SavedSlots.resize(savedSlots);
+  rec->SavedVersions.assign(savedSlots, 0);
   for (const Tensor& t : inputs) {
     rec->Inputs.push_back(t.RequiresGrad() ? t.Autograd() : nullptr);
     rec->InputShapes.push_back(t.GetShape());
@@ -48,6 +49,14 @@ Tensor BackwardRecord::Attach(const Tensor& output, int outputIndex) {
   meta->GradFn = shared_from_this();
   meta->OutputIndex = outputIndex;
   return output.WithAutograd(meta);
+}
+
+const Tensor& BackwardRecord::Saved(int slot) const {
+  const Tensor& t = SavedSlots[slot];
+  if (!t.IsEmpty() && t.Version() != SavedVersions[slot])
+    throw TensorVersionException("A tensor saved for the backward pass was modified in place (saved at version " +
+                                 std::to_string(SavedVersions[slot]) + ", now " + std::to_string(t.Version()) + ").");
+  return t;
 }
 
 void BackwardRecord::Release() {
@@ -192,6 +201,7 @@ void Engine::AccumulateLeaf(AutogradMeta& leaf, const Tensor& grad, bool owned) 
     // Logically 0 + grad: overwrite instead of zero-fill then add.
     Tensor src = grad.Contiguous();
     Check(om_memcpy_d2d(Device::Current(), leaf.Grad.RawData(), src.RawData(), (size_t)src.Length() * 4));
+    leaf.Grad.MarkModified();
     leaf.GradIsZero = false;
   } else {
     AddInto(leaf.Grad, grad);
@@ -214,6 +224,7 @@ bool Engine::LeafTarget(BackwardRecord& rec, int i, float** ptr, bool* accumulat
 void Engine::LeafWritten(BackwardRecord& rec, int i) {
   AutogradMeta* meta = rec.Inputs[i].get();
   meta->GradIsZero = false;
+  meta->Grad.MarkModified();
   leaf_arrived(meta);
 }
 
@@ -222,6 +233,7 @@ void Engine::AddInto(const Tensor& dst, const Tensor& src) {
     throw TensorShapeException("Gradient shape " + src.GetShape().ToString() + " does not match " + dst.GetShape().ToString() + ".");
   Tensor s = src.Contiguous();
   Check(om_add_into(Device::Current(), dst.Data(), s.Data(), dst.Length()));
+  dst.MarkModified();
 }
 
 }  // namespace omh

@@ -66,6 +66,20 @@ static void EmitSummed(Engine& e, BackwardRecord& r, const Tensor& g, bool negat
   }
 }
 
+// One call of the Linear backward on fp32 operands, or on their bfloat16 copies when the context asks for bfloat16 products
+// and the three operands fit (g: the gradient with pitch ldg, possibly a column slice `col` of a wider gradient; x: the
+// saved input; w: the saved weights, `col` rows in). The bias gradient always sums the fp32 gradient.
+static void LinearBwdCall(const Tensor& g, int col, int ldg, const Tensor& x, const Tensor& w, int rows, int inF, int outF, float* dx, float* dw,
+                          float* db, bool acc) {
+  if (!dx && !dw && !db) return;
+  const float* gp = g.Data() + col;
+  if (Bf16Products() && rows > 0 && (dx || dw) && Bf16Operand(g, ldg) && col % 8 == 0 && Bf16Operand(x, inF) && Bf16Operand(w, inF) && (inF & 3) == 0) {
+    Check(om_linear_bwd_bf16(C(), g.Bf16() + col, gp, ldg, x.Bf16(), w.Bf16() + (size_t)col * inF, rows, inF, outF, dx, dw, db, acc ? 1 : 0));
+    return;
+  }
+  Check(om_linear_bwd_ld(C(), gp, ldg, x.Data(), w.Data() + (size_t)col * inF, rows, inF, outF, dx, dw, db, acc ? 1 : 0));
+}
+
 // The record of Ops::LinearPacked (Ints = {rows, inF, outF, parts, hasBias}; inputs x, weights..., biases...): the input
 // gradient is one product over the packed weights; the weight and bias gradients are one product and one column sum
 // when the leaves' gradient buffers are adjacent like the parameters, else one per part on column slices of g.
@@ -74,7 +88,7 @@ static void LinearPackedBackward(BackwardRecord& r, const Tensor& g) {
   const int rows = (int)r.Ints[0], inF = (int)r.Ints[1], outF = (int)r.Ints[2], parts = (int)r.Ints[3];
   const bool hasBias = r.Ints[4] != 0;
   Tensor gc = g.Contiguous();
-  const float* wpacked = r.Saved(1).Data();
+  const Tensor& wpacked = r.Saved(1);
   Tensor dx;
   if (r.NeedsInputGrad(0)) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
   std::vector<float*> wp(parts, nullptr), bp(parts, nullptr);
@@ -113,19 +127,17 @@ static void LinearPackedBackward(BackwardRecord& r, const Tensor& g) {
   // Input gradient (+ the packed weight / bias gradients when they can ride along).
   if (!dx.IsEmpty() || wp_one || bp_one) {
     if (wp_one && bp_one && wacc[0] != bacc[0]) {
-      Check(om_linear_bwd_ld(C(), gc.Data(), outF, x.Data(), wpacked, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), wp[0], nullptr, wacc[0]));
-      Check(om_linear_bwd_ld(C(), gc.Data(), outF, x.Data(), wpacked, rows, inF, outF, nullptr, nullptr, bp[0], bacc[0]));
+      LinearBwdCall(gc, 0, outF, x, wpacked, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), wp[0], nullptr, wacc[0]);
+      LinearBwdCall(gc, 0, outF, x, wpacked, rows, inF, outF, nullptr, nullptr, bp[0], bacc[0]);
     } else {
-      Check(om_linear_bwd_ld(C(), gc.Data(), outF, x.Data(), wpacked, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(),
-                             wp_one ? wp[0] : nullptr, bp_one ? bp[0] : nullptr, (wp_one ? wacc[0] : (bp_one && bacc[0])) ? 1 : 0));
+      LinearBwdCall(gc, 0, outF, x, wpacked, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), wp_one ? wp[0] : nullptr,
+                    bp_one ? bp[0] : nullptr, wp_one ? wacc[0] : (bp_one && bacc[0]));
     }
   }
   int col = 0;
   for (int i = 0; i < parts; i++) {
-    const float* gi = gc.Data() + col;
-    const float* wi = wpacked + (size_t)col * inF;
-    if (!wp_one && wp[i]) Check(om_linear_bwd_ld(C(), gi, outF, x.Data(), wi, rows, inF, outs[i], nullptr, wp[i], nullptr, wacc[i]));
-    if (hasBias && !bp_one && bp[i]) Check(om_linear_bwd_ld(C(), gi, outF, x.Data(), wi, rows, inF, outs[i], nullptr, nullptr, bp[i], bacc[i]));
+    if (!wp_one && wp[i]) LinearBwdCall(gc, col, outF, x, wpacked, rows, inF, outs[i], nullptr, wp[i], nullptr, wacc[i]);
+    if (hasBias && !bp_one && bp[i]) LinearBwdCall(gc, col, outF, x, wpacked, rows, inF, outs[i], nullptr, nullptr, bp[i], bacc[i]);
     col += outs[i];
   }
   // Emission order as for the single layer, part by part: bias, (input once), weight.
@@ -176,11 +188,10 @@ static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
     }
   }
   if (accw == accb || !dwp || !dbp) {
-    Check(om_linear_bwd_ld(C(), gc.Data(), ldg, x.Data(), w.Data(), rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, dbp,
-                           (dwp ? accw : accb) ? 1 : 0));
+    LinearBwdCall(gc, 0, ldg, x, w, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, dbp, dwp ? accw : accb);
   } else {
-    Check(om_linear_bwd_ld(C(), gc.Data(), ldg, x.Data(), w.Data(), rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, nullptr, accw));
-    Check(om_linear_bwd_ld(C(), gc.Data(), ldg, x.Data(), w.Data(), rows, inF, outF, nullptr, nullptr, dbp, accb));
+    LinearBwdCall(gc, 0, ldg, x, w, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, nullptr, accw);
+    LinearBwdCall(gc, 0, ldg, x, w, rows, inF, outF, nullptr, nullptr, dbp, accb);
   }
   // Emission order of the reference's record chain: bias (Add record), then input and weight (MatMul record).
   if (hasBias && r.NeedsInputGrad(2)) {

@@ -1,6 +1,6 @@
 // Plain-C surface of the host mirror (libonemodel_b200_host.so), used by the Python tests and the bench through
 // ctypes: tensors are opaque handles, operations are dispatched by name, and every C++ exception becomes a status
-// code (1 shape, 2 index, 9 invalid operation, 10 other) with the message kept for omh_last_error.
+// code (1 shape, 2 index, 9 invalid operation, 11 a saved tensor changed in place, 10 other) with the message kept for omh_last_error.
 #include <stdio.h>
 #include <string.h>
 
@@ -25,6 +25,9 @@ static int32_t Guard(F&& f) {
   } catch (const ArgumentOutOfRangeException& e) {
     t_error = e.what();
     return 2;
+  } catch (const TensorVersionException& e) {
+    t_error = e.what();
+    return 11;
   } catch (const InvalidOperationException& e) {
     t_error = e.what();
     return 9;

@@ -26,6 +26,8 @@ namespace omh {
 struct TensorShapeException : std::runtime_error { using std::runtime_error::runtime_error; };
 struct ArgumentOutOfRangeException : std::runtime_error { using std::runtime_error::runtime_error; };
 struct InvalidOperationException : std::runtime_error { using std::runtime_error::runtime_error; };
+// A tensor saved for the backward pass was modified in place before the pass read it (Autograd.cs:188-192).
+struct TensorVersionException : InvalidOperationException { using InvalidOperationException::InvalidOperationException; };
 struct BackendException : std::runtime_error {
   int32_t status;
   BackendException(int32_t s, const std::string& m) : std::runtime_error(m), status(s) {}
@@ -63,6 +65,13 @@ struct Buffer {
   void* ptr = nullptr;
   size_t bytes = 0;
   bool owned = true;
+  // Counts the in-place writes to the storage (TensorBuffer.Version in the reference): a tensor saved for the backward
+  // pass remembers the count it saw, and the bfloat16 copy below remembers the count it was made at.
+  int64_t version = 0;
+  // The bfloat16 copy of the whole storage, element i of the copy being element i of the fp32 storage rounded to nearest
+  // even: the operand the products read under OM_BF16_OPERANDS. Made on first use, refreshed when the storage changed.
+  std::shared_ptr<Buffer> shadow;
+  int64_t shadow_version = -1;
   Buffer(om_ctx* c, size_t n, bool zero);
   Buffer(om_ctx* c, void* external, size_t n) : ctx(c), ptr(external), bytes(n), owned(false) {}
   ~Buffer();
@@ -95,6 +104,23 @@ class Tensor {
   bool IsContiguous() const;
   float* Data() const;  // device pointer to the first element
   void* RawData() const;
+  // The storage's version counter; 0 for an empty tensor (Tensor.cs:190-191).
+  int64_t Version() const { return buf_ ? buf_->version : 0; }
+  // Tells the tensor that a kernel wrote into its storage in place (what MutableData does in the reference, Tensor.cs:292).
+  void MarkModified() const {
+    if (buf_) buf_->version++;
+  }
+  // Device pointer to this view's first element in the storage's bfloat16 copy (fp32 tensors only; the view's offset must
+  // be a multiple of 8 elements for the copy to be usable as a product operand). Casts the storage when the copy is older
+  // than the storage.
+  const uint16_t* Bf16() const;
+  // True when the storage already has an up-to-date bfloat16 copy.
+  bool HasBf16() const { return buf_ && buf_->shadow && buf_->shadow_version == buf_->version; }
+  // Storage for the bfloat16 copy, for a kernel that writes it together with the fp32 values; the caller then marks it current.
+  uint16_t* Bf16ForWrite() const;
+  void Bf16Written() const {
+    if (buf_) buf_->shadow_version = buf_->version;
+  }
 
   // views (each records a view record when the source requires grad; Tensor.Views.cs:11-21)
   Tensor Reshape(const Shape& s) const;
@@ -165,6 +191,7 @@ struct BackwardRecord : std::enable_shared_from_this<BackwardRecord> {
   std::vector<Shape> InputShapes;
   std::vector<DType> InputTypes;
   std::vector<Tensor> SavedSlots;
+  std::vector<int64_t> SavedVersions;   // the storage version of each saved tensor when it was saved
   std::vector<int64_t> Ints;
   std::vector<double> Floats;
   Tensor PendingGrad;
@@ -175,8 +202,13 @@ struct BackwardRecord : std::enable_shared_from_this<BackwardRecord> {
   static std::shared_ptr<BackwardRecord> Create(OpKind op, int savedSlots, const std::vector<Tensor>& inputs);
   int InputCount() const { return (int)Inputs.size(); }
   bool NeedsInputGrad(int i) const { return Inputs[i] != nullptr; }
-  const Tensor& Saved(int slot) const { return SavedSlots[slot]; }
-  void Save(int slot, const Tensor& t) { SavedSlots[slot] = t; }
+  // The saved tensor after checking that its storage was not written in place since it was saved
+  // (SavedTensor.Unpack, Autograd.cs:198-238); an empty slot comes back empty.
+  const Tensor& Saved(int slot) const;
+  void Save(int slot, const Tensor& t) {
+    SavedSlots[slot] = t;
+    SavedVersions[slot] = t.Version();
+  }
   Tensor Attach(const Tensor& output, int outputIndex = 0);
   void Release();
 };
@@ -222,6 +254,11 @@ class Engine {
   static void LeafWritten(BackwardRecord& rec, int i);
   static void AddInto(const Tensor& dst, const Tensor& src);
 };
+
+// True when the current context multiplies bfloat16 copies of the operands (OM_BF16_OPERANDS with OM_TF32), and whether a
+// tensor with the given row pitch can be such an operand.
+bool Bf16Products();
+bool Bf16Operand(const Tensor& t, int64_t pitch);
 
 void RunBackwardOp(Engine& e, BackwardRecord& r, const Tensor& g);
 void RunGraphBackward(BackwardRecord& r, const Tensor& g);

@@ -16,6 +16,16 @@ bool Ops::Recording(std::initializer_list<const Tensor*> inputs) {
   return false;
 }
 
+// Products with bfloat16 operands (the context's OM_BF16_OPERANDS tier): every operand is read from the bfloat16 copy of
+// its storage. The product kernels address operands through TMA, which wants pitches of 16-byte multiples (8 elements)
+// and views that start on such a boundary; a Linear that does not fit keeps its fp32 operands.
+bool Bf16Products() {
+  uint32_t flags = 0;
+  Check(om_ctx_get_flags(C(), &flags));
+  return (flags & OM_BF16_OPERANDS) != 0 && (flags & OM_TF32) != 0;
+}
+bool Bf16Operand(const Tensor& t, int64_t pitch) { return t.GetDType() == DType::F32 && pitch % 8 == 0 && t.Offset() % 8 == 0; }
+
 static void RequireFloat32(const Tensor& t) {
   if (t.GetDType() != DType::F32) throw TensorShapeException("A float32 tensor is required.");
 }
@@ -309,10 +319,14 @@ Tensor Ops::Linear(const Tensor& x, const Tensor& weight, const Tensor& bias) {
   os.d[os.rank - 1] = outF;
   // A wide rank-2 output whose width is not a multiple of four (the vocabulary logits) gets a row pitch that is, so
   // that the backward products can read it with TMA; consumers see an ordinary strided view.
-  const bool pitched = os.rank == 2 && (outF & 3) != 0 && (int64_t)rows * outF >= (1 << 20);
-  const int ld = pitched ? ((outF + 3) & ~3) : outF;
+  // (a multiple of eight, so that the bfloat16 copy of the gradient has a 16-byte pitch as well)
+  const bool pitched = os.rank == 2 && (outF & 7) != 0 && (int64_t)rows * outF >= (1 << 20);
+  const int ld = pitched ? ((outF + 7) & ~7) : outF;
   Tensor r = pitched ? Tensor::Create(DType::F32, Shape{rows, ld}).View(os, {(int64_t)ld, 1}, 0) : NewOut(os);
-  Check(om_linear_fwd_ld(C(), xc.Data(), wc.Data(), bc.IsEmpty() ? nullptr : bc.Data(), rows, inF, outF, r.Data(), ld));
+  if (Bf16Products() && rows > 0 && Bf16Operand(xc, inF) && Bf16Operand(wc, inF) && (ld & 3) == 0)
+    Check(om_linear_fwd_bf16(C(), xc.Bf16(), wc.Bf16(), bc.IsEmpty() ? nullptr : bc.Data(), rows, inF, outF, r.Data(), ld));
+  else
+    Check(om_linear_fwd_ld(C(), xc.Data(), wc.Data(), bc.IsEmpty() ? nullptr : bc.Data(), rows, inF, outF, r.Data(), ld));
   if (!Recording({&x, &weight, &bias})) return r;
   Tensor none;
   auto rec = bias.IsEmpty() ? BackwardRecord::Create(OpKind::Linear, 2, {&x, &weight})
@@ -439,7 +453,10 @@ Tensor Ops::LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, co
   Shape os = x.GetShape();
   os.d[os.rank - 1] = outF;
   Tensor r = NewOut(os);
-  Check(om_linear_fwd_ld(C(), xc.Data(), weights[0].Data(), biases.empty() ? nullptr : biases[0].Data(), rows, inF, outF, r.Data(), outF));
+  if (Bf16Products() && rows > 0 && Bf16Operand(xc, inF) && Bf16Operand(weights[0], inF) && (outF & 3) == 0)
+    Check(om_linear_fwd_bf16(C(), xc.Bf16(), weights[0].Bf16(), biases.empty() ? nullptr : biases[0].Data(), rows, inF, outF, r.Data(), outF));
+  else
+    Check(om_linear_fwd_ld(C(), xc.Data(), weights[0].Data(), biases.empty() ? nullptr : biases[0].Data(), rows, inF, outF, r.Data(), outF));
   std::vector<Tensor> ins = {x};
   for (auto& w : weights) ins.push_back(w);
   for (auto& b : biases) ins.push_back(b);

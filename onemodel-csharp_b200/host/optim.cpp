@@ -38,6 +38,7 @@ void Optimizer::Step() {
     index_.push_back((int)i);
   }
   Launch(p, g, len);
+  for (int i : index_) params_[(size_t)i].MarkModified();   // written in place: saved copies and bfloat16 copies are stale
   StepCount++;
 }
 
@@ -60,6 +61,7 @@ void Optimizer::StepGroups(const std::vector<std::vector<int>>& groups, const st
     }
     if (before) before((int)gi);
     if (!p.empty()) Launch(p, g, len);
+    for (int i : index_) params_[(size_t)i].MarkModified();
   }
   StepCount++;
 }

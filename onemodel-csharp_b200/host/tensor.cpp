@@ -266,15 +266,41 @@ Tensor Tensor::Detach() const {
   return r;
 }
 
+// After an in-place write from the host side: the storage has a new version, and a bfloat16 copy that exists is brought up
+// to date at once, because a captured step reads the copy without looking at versions.
+static void StorageWritten(const Tensor& t) {
+  t.MarkModified();
+  if (t.GetDType() == DType::F32 && t.Storage()->shadow) t.Bf16();
+}
+
 void Tensor::Fill(float v) const {
   if (!IsContiguous()) throw TensorShapeException("Fill needs a contiguous tensor.");
   if (v == 0.f) Check(om_memset(Device::Current(), RawData(), 0, (size_t)Length() * SizeOf(dtype_)));
   else Check(om_fill(Device::Current(), Data(), v, Length()));
+  StorageWritten(*this);
+}
+
+uint16_t* Tensor::Bf16ForWrite() const {
+  if (IsEmpty() || dtype_ != DType::F32) throw InvalidOperationException("A bfloat16 copy exists for float32 tensors only.");
+  Buffer& b = *buf_;
+  if (!b.shadow) b.shadow = std::make_shared<Buffer>(b.ctx, ((b.bytes / 4) * 2 + 15) & ~(size_t)15, false);
+  return (uint16_t*)b.shadow->ptr + offset_;
+}
+
+const uint16_t* Tensor::Bf16() const {
+  uint16_t* p = Bf16ForWrite();
+  Buffer& b = *buf_;
+  if (b.shadow_version != b.version) {
+    Check(om_cast_bf16(b.ctx, (const float*)b.ptr, (uint16_t*)b.shadow->ptr, (int64_t)(b.bytes / 4)));
+    b.shadow_version = b.version;
+  }
+  return p;
 }
 
 void Tensor::CopyFromHost(const void* src) const {
   if (!IsContiguous()) throw TensorShapeException("CopyFromHost needs a contiguous tensor.");
   Check(om_memcpy_h2d(Device::Current(), RawData(), src, (size_t)Length() * SizeOf(dtype_)));
+  StorageWritten(*this);
   // The source is pageable caller memory: finish the copy before returning so the caller may reuse it.
   Check(om_sync(Device::Current()));
 }

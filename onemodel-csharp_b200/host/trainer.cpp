@@ -168,6 +168,7 @@ struct omh_trainer {
   Tensor loss_out;     // device scalar that survives the step
   Tensor flat_grads;   // all gradients, contiguous, in reverse registration order
   float ce_denominator = 0.f;
+  Tensor dp_loss_scale;   // scalar 1 / world for losses that are means over the local batch (CTC)
   float clip_norm = 0.f;
   // graph replay
   void* graph = nullptr;
@@ -249,7 +250,12 @@ static Tensor Forward(omh_trainer* t) {
   }
   if (t->kind == 4) {
     Tensor lp = t->model->Forward(t->inputs[0]);
-    return Ops::CtcLoss(lp, t->inputs[1], t->input_lengths, t->inputs[2], 0, 1, true);
+    Tensor loss = Ops::CtcLoss(lp, t->inputs[1], t->input_lengths, t->inputs[2], 0, 1, true);
+    // The CTC mean is a mean over sequences of (loss / target length): with equal shards the global mean is the mean of
+    // the shard means, so each shard contributes its mean divided by the world size and the sum over ranks (of the loss
+    // and of every gradient) is the single-process value.
+    if (t->world > 1) loss = Ops::Mul(loss, t->dp_loss_scale);
+    return loss;
   }
   auto* m = static_cast<MlmEncoder*>(t->model.get());
   Tensor logits = m->Logits(t->inputs[0], t->positions, t->inputs[1]);
@@ -410,6 +416,8 @@ OMH_API int32_t omh_trainer_dp_init(omh_trainer* t, const uint8_t* id128, int32_
     t->world = world;
     t->rank = rank;
     t->ce_denominator = (float)global_rows;
+    const float inv_world = 1.0f / (float)world;
+    t->dp_loss_scale = Tensor::FromHost(&inv_world, Shape{});
     for (size_t i = 0; i < t->buckets.size(); i++)
       Check(om_dp_register_bucket(ctx, (int32_t)i, t->flat_grads.Data() + t->buckets[i].begin, t->buckets[i].end - t->buckets[i].begin));
     t->loss_bucket = (int)t->buckets.size();
@@ -424,8 +432,10 @@ OMH_API int32_t omh_trainer_dp_init(omh_trainer* t, const uint8_t* id128, int32_
 
 static void CopyInputs(omh_trainer* t, const void* const* inputs_host) {
   om_ctx* ctx = Device::Current();
-  for (size_t i = 0; i < t->inputs.size(); i++)
+  for (size_t i = 0; i < t->inputs.size(); i++) {
     Check(om_memcpy_h2d(ctx, t->inputs[i].RawData(), inputs_host[i], (size_t)omh_trainer_input_bytes(t, (int32_t)i)));
+    t->inputs[i].MarkModified();   // a new batch: a bfloat16 copy of the old one is stale
+  }
 }
 
 static void RunStep(omh_trainer* t) {
@@ -478,6 +488,9 @@ OMH_API int32_t omh_trainer_enable_graph(omh_trainer* t) {
     t->opt->HyperDevice = t->hyper_dev.RawData();
     Check(om_sync(ctx));
     int64_t saved_count = t->opt->StepCount;
+    // The batch changes between replays without the host code of the step running again: whatever the step derives from
+    // the inputs (a bfloat16 copy) must be derived inside the captured step, so it is made stale before the capture.
+    for (auto& in : t->inputs) in.MarkModified();
     Check(om_graph_begin(ctx));
     int32_t st = 0;
     try {

@@ -14,7 +14,7 @@ KERNEL_LIB = os.path.join(_HERE, "libonemodel_b200.so")
 HOST_LIB = os.path.join(_HERE, "libonemodel_b200_host.so")
 
 OM_F32, OM_I32, OM_I64 = 0, 1, 2
-OM_TF32, OM_BF16_OPERANDS, OM_CHECKED, OM_PAIR_TILES, OM_TWO_STREAMS, OM_SEQ_KERNELS, OM_OVERLAP_LAUNCHES = 1, 2, 4, 8, 16, 32, 64
+OM_TF32, OM_BF16_OPERANDS, OM_CHECKED, OM_PAIR_TILES, OM_TWO_STREAMS, OM_SEQ_KERNELS, OM_OVERLAP_LAUNCHES, OM_PERSISTENT_TILES = 1, 2, 4, 8, 16, 32, 64, 128
 _NP2OM = {np.dtype("float32"): OM_F32, np.dtype("int32"): OM_I32, np.dtype("int64"): OM_I64}
 _OM2NP = {OM_F32: np.float32, OM_I32: np.int32, OM_I64: np.int64}
 
@@ -34,6 +34,10 @@ class ShapeError(OmError):
 
 class IndexOutOfRange(OmError):
     pass
+
+
+class TensorVersionError(OmError):
+    """A tensor saved for the backward pass was written in place before the pass read it (TensorVersionException)."""
 
 
 _kernel = None
@@ -73,6 +77,8 @@ def _raise(status, message):
         raise ShapeError(code, message)
     if code == 2:
         raise IndexOutOfRange(code, message)
+    if code == 11:
+        raise TensorVersionError(code, message)
     raise OmError(code, message)
 
 

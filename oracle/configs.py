@@ -124,7 +124,7 @@ def cnn_step(named, running, x, y, strides, state, lr=0.1, momentum=0.9, wd=0.0)
     return loss, grads
 
 
-def crnn_forward_backward(named, x, targets, target_lengths):
+def crnn_forward_backward(named, x, targets, target_lengths, loss_scale=None):
     """Config 4: four conv 3x3 + ReLU + max-pool stages ((2,2),(2,2),(2,1),(4,1)), a 2-layer bidirectional LSTM over the
     width axis, linear, log-softmax, CTC (blank 0, mean, zero-infinity). named: conv{i}.*, lstm.*, fc.*."""
     w = {k: A.T(v, True) for k, v in named.items()}
@@ -142,6 +142,8 @@ def crnn_forward_backward(named, x, targets, target_lengths):
     lp = A.log_softmax(A.linear(seq, w["fc.weight"], w["fc.bias"]))
     ilen = np.full(b, t, np.int32)
     loss = A.ctc_loss(lp, np.asarray(targets, np.int32), ilen, np.asarray(target_lengths, np.int32), 0, 1, True)
+    if loss_scale is not None:   # a data-parallel shard: its mean times 1 / world
+        loss = A.mul(loss, A.T(np.float32(loss_scale)))
     loss.backward()
     return float(loss.v), {k: v.grad for k, v in w.items()}
 

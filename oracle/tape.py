@@ -344,18 +344,34 @@ def concat(xs, axis):
     return _attach(np.concatenate([t.v for t in xs], axis=axis), Record("concat", list(xs), backward=bw), list(xs))
 
 
+def _round_operand(a):
+    """The operand as a tensor-pipe product sees it under GEMM_MODE (rounded to TF32 or bfloat16, to nearest even)."""
+    if GEMM_MODE == "tf32":
+        return K.round_tf32(a)
+    if GEMM_MODE == "bf16":
+        return K.round_bf16(a)
+    return a
+
+
 def conv2d(x, w, b=None, stride=1, padding=0):
+    """Ops.Conv2d / ConvBackward (BackwardNn.cs:317-462). Under GEMM_MODE 'tf32' / 'bf16' the operands of the three
+    convolution products (x and w forward, g and w for the input gradient, g and x for the weight gradient) are rounded
+    first, as for matmul; the products of rounded operands and all sums stay fp32, the bias gradient sums the unrounded g."""
     xc, wc = np.ascontiguousarray(x.v), np.ascontiguousarray(w.v)
 
     def bw(r, g):
-        dx, dw, db = K.conv2d_bwd(g, r.saved[0], r.saved[1], stride, padding, need_dx=r.inputs[0] is not None)
+        dx, dw, db = K.conv2d_bwd(_round_operand(g), _round_operand(r.saved[0]), _round_operand(r.saved[1]), stride, padding,
+                                  need_dx=r.inputs[0] is not None)
+        if GEMM_MODE != "fp32":
+            db = np.asarray(g, np.float64).sum(axis=(0, 2, 3)).astype(np.float32)
         out = [(2, db, "own"), (1, dw, "own")] if b is not None else [(1, dw, "own")]
         if dx is not None:
             out.append((0, dx, "own"))
         return out
 
     ins = [x, w] + ([b] if b is not None else [])
-    return _attach(K.conv2d_fwd(xc, wc, b.v if b is not None else None, stride, padding), Record("conv2d", ins, saved=(xc, wc), backward=bw), ins)
+    y = K.conv2d_fwd(_round_operand(xc), _round_operand(wc), b.v if b is not None else None, stride, padding)
+    return _attach(y, Record("conv2d", ins, saved=(xc, wc), backward=bw), ins)
 
 
 def max_pool2d(x, k, stride=None):

@@ -59,6 +59,66 @@ dist.destroy_process_group()
 '''
 
 
+CTC_WORKER = r'''
+import os, sys, json
+import numpy as np
+import torch
+import torch.distributed as dist
+sys.path.insert(0, os.path.join(%(root)r, "onemodel-csharp_b200"))
+sys.path.insert(0, %(root)r)
+import synth
+from oracle import configs, tape as A
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world)
+batch, height, width, classes, hidden, max_label = 2, 32, 32, 7, 4, 3
+weights = configs.crnn_init([2, 3, 4, 4], hidden, classes, seed=0)
+x, targets, lengths = synth.crnn_batch(batch, height, width, classes, max_label, 1, 0, rank)
+# The shard's CTC mean divided by the world size (what the trainer multiplies in), gradients summed over ranks.
+loss, grads = configs.crnn_forward_backward(weights, x, targets[: int(lengths.sum())], lengths, loss_scale=1.0 / world)
+names = list(weights)[::-1]
+flat = torch.from_numpy(np.concatenate([grads[n].reshape(-1) for n in names]).astype(np.float32))
+dist.all_reduce(flat, op=dist.ReduceOp.SUM)
+lt = torch.tensor([loss], dtype=torch.float32)
+dist.all_reduce(lt, op=dist.ReduceOp.SUM)
+if rank == 0:
+    xs, ts, ls = [], [], []
+    for r in range(world):
+        xi, ti, li = synth.crnn_batch(batch, height, width, classes, max_label, 1, 0, r)
+        xs.append(xi); ts.append(ti[: int(li.sum())]); ls.append(li)
+    gl, gg = configs.crnn_forward_backward(weights, np.concatenate(xs), np.concatenate(ts), np.concatenate(ls))
+    ref = np.concatenate([gg[n].reshape(-1) for n in names])
+    print(json.dumps({"loss_dp": float(lt[0]), "loss_single": gl,
+                      "grad_err": float(np.max(np.abs(flat.numpy() - ref)) / float(np.max(np.abs(ref))))}))
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def _run_ranks(tmp_path, source, world, port):
+    script = tmp_path / "dp_worker.py"
+    script.write_text(source % {"root": ROOT})
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="2")
+    procs = []
+    for r in range(world):
+        e = dict(env, RANK=str(r), WORLD_SIZE=str(world))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=240) for p in procs]
+    for p, (o, e) in zip(procs, outs):
+        assert p.returncode == 0, e[-2000:]
+    return json.loads(outs[0][0].strip().splitlines()[-1])
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ctc_shards_sum_to_the_single_process_step(tmp_path, oracle_built, world):
+    """The CRNN trainer under data parallelism: the CTC loss is a mean over the local sequences, so each shard's loss is
+    multiplied by 1 / world before the backward pass (host/trainer.cpp); the sum over ranks of loss and gradients is then
+    the single-process mean over the global batch."""
+    res = _run_ranks(tmp_path, CTC_WORKER, world, 29620 + world)
+    assert abs(res["loss_dp"] - res["loss_single"]) <= 1e-5 * abs(res["loss_single"])
+    assert res["grad_err"] <= 1e-5
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_shards_sum_to_the_single_process_step(tmp_path, oracle_built, world):
     script = tmp_path / "dp_worker.py"

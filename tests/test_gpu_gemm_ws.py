@@ -1,0 +1,135 @@
+"""The persistent CTA-pair product kernel (two accumulator buffers in tensor memory) against the CPU oracle: with
+bfloat16 operands (the om_*_bf16 entry points) and, under OM_PERSISTENT_TILES, with TF32 operands.
+
+The oracle rounds the operands the same way (bfloat16 or TF32, to nearest even) and sums in fp32 in increasing k, so
+what is left is the order of the fp32 accumulation: 2e-5 scaled. Against the fp32 oracle the operand rounding itself
+shows: bfloat16 keeps 8 significant bits, so every product is within 2^-7 relative and every element within
+2^-7 * (|A||B|) of the fp32 result."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import om_binding as omb
+from backends import scaled_diff
+from om_binding import i32, i64
+
+pytestmark = pytest.mark.gpu
+
+# m, n, k: one tile, several tiles per cluster, ragged edges in every dimension, a split k, the encoder's own shapes
+SHAPES = [(256, 256, 64), (256, 128, 128), (512, 768, 768), (2048, 2304, 768), (1000, 520, 200), (300, 264, 136),
+          (768, 768, 16384), (2304, 768, 4096), (154, 30528, 768), (4096, 768, 3072), (64, 72, 40)]
+
+
+def to_bf16(ctx, a):
+    """The bfloat16 copy of a float32 array on the device (om_cast_bf16), as a DeviceArray of uint16."""
+    src = ctx.to_device(np.ascontiguousarray(a, np.float32))
+    dst = ctx.empty(a.shape, np.uint16)
+    ctx.call("om_cast_bf16", ctx.handle, src.ptr, dst.ptr, i64(a.size))
+    return dst
+
+
+def test_cast_rounds_to_nearest_even(ctx, oracle_built):
+    K = oracle_built
+    r = np.random.default_rng(5)
+    x = np.concatenate([r.standard_normal(100003).astype(np.float32) * 10.0 ** r.integers(-20, 20, 100003).astype(np.float32),
+                        # ties: exactly half way between two bfloat16 values, both parities
+                        np.array([1.00390625, 1.01171875, -1.00390625, 3.0e38, 0.0, -0.0, 1e-40], np.float32)])
+    got = to_bf16(ctx, x).numpy()
+    ctx.sync()
+    want = (K.round_bf16(x).view(np.uint32) >> 16).astype(np.uint16)
+    assert np.array_equal(got, want)
+
+
+def run_bf16(ctx, ta, tb, m, n, k, a, b, acc=0, c0=None, ldc=None):
+    da, db = to_bf16(ctx, a), to_bf16(ctx, b)
+    ldc = ldc or n
+    dc = ctx.to_device(c0) if c0 is not None else ctx.empty((m, ldc))
+    ctx.call("om_matmul_bf16", ctx.handle, i32(ta), i32(tb), i32(m), i32(n), i32(k), da.ptr, i32(a.shape[1]), db.ptr, i32(b.shape[1]),
+             dc.ptr, i32(ldc), i32(acc))
+    ctx.sync()
+    return dc.numpy()
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_bf16_matmul(ctx, oracle_built, ta, tb, m, n, k):
+    K = oracle_built
+    r = np.random.default_rng(m + 3 * n + 7 * k + ta * 2 + tb)
+    a = r.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
+    b = r.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+    if a.shape[1] % 8 or b.shape[1] % 8:
+        pytest.skip("an operand pitch that is not a multiple of 16 bytes: refused (see the last test of this group)")
+    got = run_bf16(ctx, ta, tb, m, n, k, a, b)
+    ref16 = K.gemm(a, b, bool(ta), bool(tb), mode="bf16")
+    assert scaled_diff(got, ref16) <= 2e-5
+    ref = K.gemm(a, b, bool(ta), bool(tb))
+    aa = np.abs(a.T if ta else a).astype(np.float64)
+    bb = np.abs(b.T if tb else b).astype(np.float64)
+    assert np.all(np.abs(got.astype(np.float64) - ref) <= 2.0 ** -7 * (aa @ bb) + 1e-5)
+    assert scaled_diff(got, ref) <= 8e-3
+    c0 = r.standard_normal((m, n)).astype(np.float32)
+    got2 = run_bf16(ctx, ta, tb, m, n, k, a, b, acc=1, c0=c0)
+    assert scaled_diff(got2, ref16 + c0) <= 2e-5
+    assert np.array_equal(got, run_bf16(ctx, ta, tb, m, n, k, a, b))      # fixed split of k, ordered combine: same bits
+
+
+def test_bf16_linear_forward_and_backward(ctx, oracle_built):
+    """om_linear_fwd_bf16 / om_linear_bwd_bf16 at one feed-forward layer of the BERT-base shape (a quarter of its rows),
+    with a row-pitched output, the bias in the epilogue and the bias gradient from the fp32 gradient."""
+    K = oracle_built
+    r = np.random.default_rng(9)
+    rows, inf, outf, ld = 4096, 768, 3070, 3072
+    x, w = r.standard_normal((rows, inf)).astype(np.float32), (r.standard_normal((outf, inf)) * 0.05).astype(np.float32)
+    bias = r.standard_normal(outf).astype(np.float32)
+    g = np.zeros((rows, ld), np.float32)
+    g[:, :outf] = r.standard_normal((rows, outf))
+    X16, W16, G16 = to_bf16(ctx, x), to_bf16(ctx, w), to_bf16(ctx, g)
+    Bv, G = ctx.to_device(bias), ctx.to_device(g)
+    Y, DX, DW, DB = ctx.zeros((rows, ld)), ctx.empty((rows, inf)), ctx.empty((outf, inf)), ctx.empty((outf,))
+    ctx.call("om_linear_fwd_bf16", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), Y.ptr, i32(ld))
+    ctx.call("om_linear_bwd_bf16", ctx.handle, G16.ptr, G.ptr, i32(ld), X16.ptr, W16.ptr, i32(rows), i32(inf), i32(outf), DX.ptr, DW.ptr, DB.ptr, i32(0))
+    ctx.sync()
+    y = Y.numpy()
+    assert scaled_diff(y[:, :outf], K.gemm(x, w, tb=True, mode="bf16") + bias) <= 2e-5
+    assert np.all(y[:, outf:] == 0)                                          # the pitch columns are not written
+    gv = g[:, :outf]
+    assert scaled_diff(DX.numpy(), K.gemm(gv, w, mode="bf16")) <= 2e-5
+    assert scaled_diff(DW.numpy(), K.gemm(gv, x, ta=True, mode="bf16")) <= 2e-5
+    assert np.allclose(DB.numpy(), gv.astype(np.float64).sum(0), rtol=1e-5, atol=1e-4)
+
+
+def test_bf16_operands_that_tma_cannot_describe_are_refused(ctx):
+    a, b = ctx.empty((64, 100), np.uint16), ctx.empty((100, 72), np.uint16)
+    c = ctx.empty((64, 72))
+    with pytest.raises(omb.OmError) as e:      # an A pitch of 100 elements is 200 bytes
+        ctx.call("om_matmul_bf16", ctx.handle, i32(0), i32(0), i32(64), i32(72), i32(100), a.ptr, i32(100), b.ptr, i32(72), c.ptr, i32(72), i32(0))
+    assert "multiples of 8" in str(e.value)
+    ctx.sync()
+
+
+def run_tf32(ctx, ta, tb, m, n, k, a, b, acc=0, c0=None):
+    da, db = ctx.to_device(a), ctx.to_device(b)
+    dc = ctx.to_device(c0) if c0 is not None else ctx.empty((m, n))
+    ctx.call("om_matmul", ctx.handle, i32(ta), i32(tb), i32(m), i32(n), i32(k), da.ptr, i32(a.shape[1]), db.ptr, i32(b.shape[1]), dc.ptr, i32(n), i32(acc))
+    ctx.sync()
+    return dc.numpy()
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (8192, 384, 384), (8192, 1536, 384), (384, 1536, 8192), (1229, 30524, 384), (1000, 520, 200), (300, 264, 136)])
+def test_tf32_matmul_on_the_persistent_kernel(ctx, oracle_built, ta, tb, m, n, k):
+    K = oracle_built
+    r = np.random.default_rng(m * 3 + n + k)
+    a = r.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
+    b = r.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+    try:
+        ctx.set_flags(omb.OM_TF32 | omb.OM_PERSISTENT_TILES)
+        got = run_tf32(ctx, ta, tb, m, n, k, a, b)
+        ref = K.gemm(a, b, bool(ta), bool(tb), mode="tf32")
+        assert scaled_diff(got, ref) <= 2e-5
+        c0 = r.standard_normal((m, n)).astype(np.float32)
+        assert scaled_diff(run_tf32(ctx, ta, tb, m, n, k, a, b, acc=1, c0=c0), ref + c0) <= 2e-5
+        assert np.array_equal(got, run_tf32(ctx, ta, tb, m, n, k, a, b))
+    finally:
+        ctx.set_flags(0)

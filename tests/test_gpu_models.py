@@ -103,6 +103,33 @@ def test_engine_semantics(B):
     assert not B.grad(x).any()
 
 
+def test_in_place_change_of_a_saved_tensor_is_caught(B):
+    """BackwardEngineTests.InPlaceChangeOfASavedTensorIsCaught (BackwardEngineTests.cs:66-75): a tensor saved by the forward
+    pass remembers its storage version (SavedTensor, Autograd.cs:198-238); a write into that storage before the backward
+    pass reads it raises the version exception instead of producing a gradient from the changed values. A write after the
+    pass has released its records (what an optimizer does) is fine."""
+    import om_binding as omb
+    x = B.tensor(np.array([1.0, 2.0]), True)
+    w = B.tensor(np.array([3.0, 4.0]))
+    y = B.sum(B.mul(x, w))
+    w.copy_from(np.array([9.0, 4.0], np.float32))
+    with pytest.raises(omb.TensorVersionError) as e:
+        B.backward(y)
+    assert "modified in place" in str(e.value)
+    # The same graph without the write, then a write after the backward pass.
+    x2 = B.tensor(np.array([1.0, 2.0]), True)
+    y2 = B.sum(B.mul(x2, w))
+    B.backward(y2)
+    w.copy_from(np.array([0.0, 0.0], np.float32))
+    assert np.array_equal(B.grad(x2), np.array([9.0, 4.0], np.float32))
+    # Writing into a parameter between forward and backward is caught for the fused records too (Linear saves its weights).
+    lin_w = B.tensor(np.ones((4, 8), np.float32), True)
+    out = B.sum(B.linear(B.tensor(np.ones((2, 8), np.float32), True), lin_w, None))
+    lin_w.copy_from(np.zeros((4, 8), np.float32))
+    with pytest.raises(omb.TensorVersionError):
+        B.backward(out)
+
+
 @pytest.mark.parametrize("tf32", [False, True])
 @pytest.mark.parametrize("b,l,heads,dh,packed", [(3, 128, 4, 32, False), (2, 50, 3, 16, False), (2, 128, 12, 32, True),
                                                  (2, 300, 4, 64, False), (2, 256, 3, 32, True), (1, 128, 2, 64, False)])
