@@ -338,7 +338,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-batch", type=int, default=0, help="batch of the CPU baseline sample (0 = the workload default)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--fp32", action="store_true", help="products on the fp32 FMA kernel instead of the tensor pipe")

@@ -43,7 +43,8 @@ typedef enum om_status {
   OM_ERR_NCCL = 5,
   OM_ERR_TIMEOUT = 6,     /* a bounded device-side or host-side wait ran out */
   OM_ERR_UNSUPPORTED = 7,
-  OM_ERR_ARG = 8
+  OM_ERR_ARG = 8,
+  OM_ERR_CANARY = 9       /* OM_CHECKED: the guard bytes behind a released buffer were overwritten */
 } om_status;
 
 /* Context flags. OM_TF32: matrix products run on the tcgen05 tensor pipe with TF32 operands and fp32
@@ -52,8 +53,11 @@ typedef enum om_status {
  * src/OneModel/Tensors/Autograd/TensorCompute.cs:22-78). OM_BF16_OPERANDS (with OM_TF32): the host layer above this
  * library keeps bfloat16 copies of the tensors that feed the Linear products and calls the om_*_bf16 entry points below
  * (bfloat16 operands rounded to nearest even, fp32 accumulation); the fp32-operand entry points are unchanged by it.
- * OM_CHECKED: index operands are range-checked on the device and buffers carry canary words
- * (the reference's Checked build, docs/tensors.md:108-110). OM_PAIR_TILES (with OM_TF32): every plain product the
+ * OM_CHECKED (the reference's CHECKED build, docs/tensors.md:108-110): memory from om_alloc (and every pooled scratch
+ * block) is filled with 0xFF when handed out and again when returned (NaN for floats, -1 for integers: reads of unwritten
+ * or released memory stand out), and 64 guard bytes (0xA5) follow its length; om_free verifies them on the device and a
+ * kernel that wrote past the end shows as OM_ERR_CANARY at the next om_sync. Index operands are range-checked on the
+ * device with or without the flag. A debugging mode: two extra small launches per allocation. OM_PAIR_TILES (with OM_TF32): every plain product the
  * CTA-pair kernel can take runs on it (tcgen05 cta_group::2, 256-row tiles: fewer operand bytes per SM); without the
  * flag only products with several rounds of tiles over the device do.
  * OM_TWO_STREAMS: a backward entry point whose gradients are independent of one another (om_linear_bwd: the input
@@ -83,6 +87,16 @@ int32_t om_ctx_create(int32_t device, uint32_t flags, om_ctx** out);
 int32_t om_ctx_destroy(om_ctx* ctx);
 int32_t om_ctx_set_flags(om_ctx* ctx, uint32_t flags);
 int32_t om_ctx_get_flags(om_ctx* ctx, uint32_t* flags);
+/* Every device-side wait of the tensor-pipe kernels (on an mbarrier: operands landed, stage free, accumulator ready)
+ * is bounded; when the bound runs out the kernel stores OM_ERR_TIMEOUT in the context's status word, every role leaves
+ * its loop, tensor memory is released and the kernel returns, so the next om_sync reports the timeout and the context
+ * stays usable. The bound is about one second of SM clock; this sets another one for the context (0 = the default
+ * again; budgets under a quarter of a millisecond act as a quarter of a millisecond). Synchronises the stream. No
+ * counterpart in the reference (its kernels are host loops). */
+int32_t om_ctx_set_wait_budget_us(om_ctx* ctx, int64_t microseconds);
+/* Launches one warp that waits, under the context's wait budget, on a barrier nothing ever arrives at: the timeout
+ * path above in isolation. The next om_sync returns OM_ERR_TIMEOUT (detail 99). For tests of error handling. */
+int32_t om_selftest_bounded_wait(om_ctx* ctx);
 /* Copies the last error message (NUL terminated, truncated to n) of this context; ctx may be NULL for
  * errors of om_ctx_create. */
 int32_t om_last_error(om_ctx* ctx, char* buf, size_t n);

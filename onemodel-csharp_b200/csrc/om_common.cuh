@@ -23,6 +23,12 @@ struct Pool {
   std::unordered_map<void*, size_t> live;              // ptr -> class bytes
   std::map<size_t, std::vector<void*>> cache;          // class bytes -> free blocks
   uint64_t bytes_in_use = 0, bytes_cached = 0, driver_allocs = 0;
+  // Blocks handed out while a step was being captured belong to that graph: a replay writes to their addresses, so they
+  // must never back an unrelated allocation while the graph exists. Freed, they wait in the graph's own cache (where later
+  // allocations of the same capture find them again) and return to the general cache when the graph is destroyed.
+  std::unordered_map<void*, int> reserved;                          // ptr -> owning graph
+  std::map<int, std::map<size_t, std::vector<void*>>> graph_cache;  // graph -> class bytes -> free blocks
+  std::unordered_map<void*, size_t> guarded;                        // OM_CHECKED: ptr -> offset of its 64 guard bytes
   static size_t size_class(size_t bytes);
 };
 
@@ -57,6 +63,9 @@ struct om_ctx {
   bool aux_active = false;
   bool profiling = false;
   bool capturing = false;
+  int capture_id = 0;                       // the graph being captured (0 when none)
+  int next_graph_id = 1;
+  std::map<void*, int> graph_ids;           // instantiated graph -> its id in the pools
   int32_t last_graph_kernel_nodes = 0;
   std::map<std::string, om::ProfileEntry> profile;
   std::vector<cudaEvent_t> event_pool;

@@ -37,11 +37,51 @@ size_t Pool::size_class(size_t bytes) {
   return b << 1;
 }
 
+constexpr size_t kGuardBytes = 64;
+
+// One thread per guard byte; the first mismatch is reported through the context's status word.
+__global__ void guard_check_kernel(const uint8_t* guard, int32_t* status) {
+  if (guard[threadIdx.x] != 0xA5 && atomicCAS(status, 0, (int32_t)OM_ERR_CANARY) == 0) status[1] = (int32_t)threadIdx.x;
+}
+
+static int32_t pool_alloc_block(om_ctx* ctx, size_t bytes, bool zero, void** out);
+
 int32_t pool_alloc(om_ctx* ctx, size_t bytes, bool zero, void** out) {
+  if (!(ctx->flags & OM_CHECKED)) return pool_alloc_block(ctx, bytes, zero, out);
+  // CHECKED: poison (or zero) the caller's bytes and lay 64 guard bytes behind them.
+  const size_t len = ((bytes == 0 ? 1 : bytes) + 15) & ~(size_t)15;
+  OM_TRY(pool_alloc_block(ctx, len + kGuardBytes, false, out));
+  uint8_t* base = (uint8_t*)*out;
+  OM_CUDA(ctx, cudaMemsetAsync(base, zero ? 0 : 0xFF, len, ctx->stream));
+  OM_CUDA(ctx, cudaMemsetAsync(base + len, 0xA5, kGuardBytes, ctx->stream));
+  (ctx->aux_active ? ctx->pool_aux : ctx->pool).guarded[*out] = len;
+  return OM_OK;
+}
+
+static int32_t pool_alloc_block(om_ctx* ctx, size_t bytes, bool zero, void** out) {
   *out = nullptr;
   size_t cls = Pool::size_class(bytes == 0 ? 1 : bytes);
   Pool& p = ctx->aux_active ? ctx->pool_aux : ctx->pool;
   void* ptr = nullptr;
+  if (ctx->capturing) {
+    // First choice while capturing: a block this capture has already used and freed.
+    auto gc = p.graph_cache.find(ctx->capture_id);
+    if (gc != p.graph_cache.end()) {
+      auto git = gc->second.find(cls);
+      if (git != gc->second.end() && !git->second.empty()) {
+        ptr = git->second.back();
+        git->second.pop_back();
+        p.live[ptr] = cls;
+        p.bytes_in_use += cls;
+        *out = ptr;
+        if (zero) {
+          cudaError_t e = cudaMemsetAsync(ptr, 0, bytes, ctx->stream);
+          if (e != cudaSuccess) return check_cuda(ctx, e, "cudaMemsetAsync");
+        }
+        return OM_OK;
+      }
+    }
+  }
   auto it = p.cache.find(cls);
   if (it != p.cache.end() && !it->second.empty()) {
     ptr = it->second.back();
@@ -68,6 +108,7 @@ int32_t pool_alloc(om_ctx* ctx, size_t bytes, bool zero, void** out) {
   }
   p.live[ptr] = cls;
   p.bytes_in_use += cls;
+  if (ctx->capturing) p.reserved[ptr] = ctx->capture_id;
   if (zero) {
     cudaError_t e = cudaMemsetAsync(ptr, 0, bytes, ctx->stream);
     if (e != cudaSuccess) return check_cuda(ctx, e, "cudaMemsetAsync");
@@ -88,11 +129,38 @@ int32_t pool_free(om_ctx* ctx, void* ptr) {
   }
   Pool& p = *pp;
   size_t cls = it->second;
+  auto gd = p.guarded.find(ptr);
+  if (gd != p.guarded.end()) {
+    // CHECKED: verify the guard bytes, then poison what is returned (in stream order, behind every kernel that used it).
+    guard_check_kernel<<<1, (unsigned)kGuardBytes, 0, ctx->stream>>>((const uint8_t*)ptr + gd->second, ctx->status_dev);
+    cudaMemsetAsync(ptr, 0xFF, gd->second, ctx->stream);
+    p.guarded.erase(gd);
+  }
   p.live.erase(it);
   p.bytes_in_use -= cls;
+  auto rv = p.reserved.find(ptr);
+  if (rv != p.reserved.end()) {
+    p.graph_cache[rv->second][cls].push_back(ptr);   // stays with its graph
+    return OM_OK;
+  }
   p.cache[cls].push_back(ptr);
   p.bytes_cached += cls;
   return OM_OK;
+}
+
+// The graph is gone: its blocks are ordinary blocks again.
+static void release_graph_blocks(Pool& p, int id) {
+  auto gc = p.graph_cache.find(id);
+  if (gc != p.graph_cache.end()) {
+    for (auto& kv : gc->second)
+      for (void* q : kv.second) {
+        p.cache[kv.first].push_back(q);
+        p.bytes_cached += kv.first;
+      }
+    p.graph_cache.erase(gc);
+  }
+  for (auto it = p.reserved.begin(); it != p.reserved.end();)
+    it = it->second == id ? p.reserved.erase(it) : std::next(it);
 }
 
 int32_t run_forked(om_ctx* ctx, const std::function<int32_t()>& first, const std::function<int32_t()>& second) {
@@ -225,6 +293,10 @@ int32_t om_ctx_destroy(om_ctx* ctx) {
   for (auto& kv : ctx->pool_aux.cache)
     for (void* p : kv.second) cudaFree(p);
   for (auto& kv : ctx->pool_aux.live) cudaFree(kv.first);
+  for (Pool* pp : {&ctx->pool, &ctx->pool_aux})
+    for (auto& g : pp->graph_cache)
+      for (auto& kv : g.second)
+        for (void* p : kv.second) cudaFree(p);
   if (ctx->aux_stream) {
     cudaStreamSynchronize(ctx->aux_stream);
     cudaStreamDestroy(ctx->aux_stream);
@@ -248,6 +320,20 @@ int32_t om_ctx_destroy(om_ctx* ctx) {
 int32_t om_ctx_set_flags(om_ctx* ctx, uint32_t flags) {
   if (!ctx) return OM_ERR_ARG;
   ctx->flags = flags;
+  return OM_OK;
+}
+
+int32_t om_ctx_set_wait_budget_us(om_ctx* ctx, int64_t microseconds) {
+  OM_CHECK_CTX(ctx);
+  if (microseconds < 0) return fail(ctx, OM_ERR_ARG, "om_ctx_set_wait_budget_us: %lld", (long long)microseconds);
+  int khz = 0;
+  OM_CUDA(ctx, cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device));
+  // Kernels already queued keep reading the word: finish them first so that one kernel sees one budget.
+  OM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  long long units = microseconds == 0 ? 0 : ((long long)microseconds * khz / 1000) >> 10;
+  if (microseconds > 0 && units < 1) units = 1;
+  if (units > INT32_MAX) units = INT32_MAX;
+  ((volatile int32_t*)ctx->status_host)[2] = (int32_t)units;
   return OM_OK;
 }
 
@@ -352,6 +438,7 @@ int32_t om_sync(om_ctx* ctx) {
     *(volatile int32_t*)ctx->status_host = 0;
     ((volatile int32_t*)ctx->status_host)[1] = 0;
     const char* what = s == OM_ERR_INDEX ? "an index operand was out of range"
+                       : s == OM_ERR_CANARY ? "the guard bytes behind a released buffer were overwritten (a kernel wrote past its end)"
                        : s == OM_ERR_TIMEOUT ? "a bounded device-side wait expired"
                                              : "a kernel reported an error";
     return fail(ctx, s, "device status %d: %s (detail %d)", s, what, detail);
@@ -364,6 +451,7 @@ int32_t om_graph_begin(om_ctx* ctx) {
   if (ctx->capturing) return fail(ctx, OM_ERR_ARG, "om_graph_begin: already capturing");
   OM_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
   ctx->capturing = true;
+  ctx->capture_id = ctx->next_graph_id++;
   return OM_OK;
 }
 
@@ -371,8 +459,15 @@ int32_t om_graph_end(om_ctx* ctx, void** graph_exec) {
   OM_CHECK_CTX(ctx);
   if (!ctx->capturing) return fail(ctx, OM_ERR_ARG, "om_graph_end: not capturing");
   ctx->capturing = false;
+  const int id = ctx->capture_id;
+  ctx->capture_id = 0;
   cudaGraph_t graph = nullptr;
-  OM_CUDA(ctx, cudaStreamEndCapture(ctx->stream, &graph));
+  cudaError_t ce = cudaStreamEndCapture(ctx->stream, &graph);
+  if (ce != cudaSuccess) {
+    release_graph_blocks(ctx->pool, id);
+    release_graph_blocks(ctx->pool_aux, id);
+    return check_cuda(ctx, ce, "cudaStreamEndCapture");
+  }
   {
     size_t n = 0;
     ctx->last_graph_kernel_nodes = 0;
@@ -390,7 +485,12 @@ int32_t om_graph_end(om_ctx* ctx, void** graph_exec) {
   cudaGraphExec_t exec = nullptr;
   cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
   cudaGraphDestroy(graph);
-  if (e != cudaSuccess) return check_cuda(ctx, e, "cudaGraphInstantiate");
+  if (e != cudaSuccess) {
+    release_graph_blocks(ctx->pool, id);
+    release_graph_blocks(ctx->pool_aux, id);
+    return check_cuda(ctx, e, "cudaGraphInstantiate");
+  }
+  ctx->graph_ids[(void*)exec] = id;
   *graph_exec = (void*)exec;
   return OM_OK;
 }
@@ -409,7 +509,16 @@ int32_t om_graph_launch(om_ctx* ctx, void* graph_exec) {
 
 int32_t om_graph_destroy(om_ctx* ctx, void* graph_exec) {
   OM_CHECK_CTX(ctx);
-  if (graph_exec) OM_CUDA(ctx, cudaGraphExecDestroy((cudaGraphExec_t)graph_exec));
+  if (!graph_exec) return OM_OK;
+  // Replays in flight still write to the graph's blocks: let them finish before the blocks become ordinary again.
+  OM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  OM_CUDA(ctx, cudaGraphExecDestroy((cudaGraphExec_t)graph_exec));
+  auto it = ctx->graph_ids.find(graph_exec);
+  if (it != ctx->graph_ids.end()) {
+    release_graph_blocks(ctx->pool, it->second);
+    release_graph_blocks(ctx->pool_aux, it->second);
+    ctx->graph_ids.erase(it);
+  }
   return OM_OK;
 }
 

@@ -7,6 +7,7 @@
 // backward pass overlaps it; om_dp_wait joins the communication stream back and checks the communicator for
 // asynchronous errors under a host deadline instead of blocking without bound.
 #include <dlfcn.h>
+#include <stdlib.h>
 #include <nccl.h>
 
 #include <chrono>
@@ -31,9 +32,18 @@ static NcclApi g_nccl;
 
 static int32_t load_nccl(om_ctx* ctx) {
   if (g_nccl.handle) return OM_OK;
-  void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-  if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
-  if (!h) return fail(ctx, OM_ERR_NCCL, "cannot load libnccl.so.2: %s", dlerror());
+  // OM_NCCL_LIBRARY names another library with the same seven entry points (a host whose NCCL lives elsewhere; the tests'
+  // stand-in communicator that reports errors and delays on demand).
+  const char* named = getenv("OM_NCCL_LIBRARY");
+  void* h = nullptr;
+  if (named && *named) {
+    h = dlopen(named, RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return fail(ctx, OM_ERR_NCCL, "cannot load %s (OM_NCCL_LIBRARY): %s", named, dlerror());
+  } else {
+    h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return fail(ctx, OM_ERR_NCCL, "cannot load libnccl.so.2: %s", dlerror());
+  }
 #define OM_SYM(field, name)                                                        \
   g_nccl.field = (decltype(g_nccl.field))dlsym(h, name);                           \
   if (!g_nccl.field) return fail(ctx, OM_ERR_NCCL, "libnccl has no symbol %s", name);
@@ -132,6 +142,7 @@ int32_t om_dp_allreduce_bucket(om_ctx* ctx, int32_t bucket_id) {
     return fail(ctx, OM_ERR_ARG, "om_dp_allreduce_bucket: unknown bucket %d", bucket_id);
   Bucket& b = dp->buckets[bucket_id];
   if (b.count == 0) return OM_OK;
+  if (!dp->comm) return fail(ctx, OM_ERR_NCCL, "om_dp_allreduce_bucket: the communicator was aborted after an error; create a new group");
   ProfileScope prof(ctx, "om_dp_allreduce_bucket", 0, 4.0 * b.count);
   OM_CUDA(ctx, cudaEventRecord(dp->ready, ctx->stream));
   OM_CUDA(ctx, cudaStreamWaitEvent(dp->comm_stream, dp->ready, 0));
@@ -146,6 +157,7 @@ int32_t om_dp_allreduce(om_ctx* ctx, void* buf, int64_t count, int32_t dtype) {
   OM_CHECK_CTX(ctx);
   DpState* dp = ctx->dp;
   if (!dp) return fail(ctx, OM_ERR_ARG, "om_dp_allreduce: om_dp_init has not run");
+  if (!dp->comm) return fail(ctx, OM_ERR_NCCL, "om_dp_allreduce: the communicator was aborted after an error; create a new group");
   ncclDataType_t t = dtype == OM_F32 ? ncclFloat32 : dtype == OM_I32 ? ncclInt32 : ncclInt64;
   ncclResult_t r = g_nccl.AllReduce(buf, buf, (size_t)count, t, ncclSum, dp->comm, ctx->stream);
   if (r != ncclSuccess) return nccl_fail(ctx, r, "ncclAllReduce");
@@ -173,6 +185,7 @@ int32_t om_dp_wait(om_ctx* ctx, int32_t timeout_ms) {
     OM_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, b.done, 0));
     b.in_flight = false;
   }
+  if (!dp->comm) return fail(ctx, OM_ERR_NCCL, "om_dp_wait: the communicator was aborted after an error; create a new group");
   ncclResult_t async = ncclSuccess;
   ncclResult_t r = g_nccl.CommGetAsyncError(dp->comm, &async);
   if (r != ncclSuccess) return nccl_fail(ctx, r, "ncclCommGetAsyncError");

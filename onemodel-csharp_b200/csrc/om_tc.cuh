@@ -30,14 +30,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait. Returns false (and raises the abort flag) when the bound is hit or another role aborted.
+// Bounded wait. Returns false (and raises the abort flag) when the bound is hit or another role aborted. The bound is
+// WAIT_CYCLES unless the context set its own (om_ctx_set_wait_budget_us): word 2 of the status block holds it in units
+// of 1024 cycles. The block is host memory, so it is looked at only once a wait has already lasted a quarter of a
+// millisecond; shorter budgets act as that.
+constexpr long long WAIT_LOOK_CYCLES = 1LL << 19;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int where) {
   const long long t0 = clock64();
   for (uint32_t i = 0;; i++) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 63u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > WAIT_CYCLES) break;
+      const long long waited = clock64() - t0;
+      if (waited > WAIT_LOOK_CYCLES) {
+        const int32_t own = reinterpret_cast<volatile int32_t*>(status)[2];
+        if (waited > (own > 0 ? ((long long)own << 10) : WAIT_CYCLES)) break;
+      }
     }
   }
   *abort_flag = 1;

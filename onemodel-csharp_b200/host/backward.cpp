@@ -73,7 +73,9 @@ static void LinearBwdCall(const Tensor& g, int col, int ldg, const Tensor& x, co
                           float* db, bool acc) {
   if (!dx && !dw && !db) return;
   const float* gp = g.Data() + col;
-  if (Bf16Products() && rows > 0 && (dx || dw) && Bf16Operand(g, ldg) && col % 8 == 0 && Bf16Operand(x, inF) && Bf16Operand(w, inF) && (inF & 3) == 0) {
+  auto aligned16 = [](const float* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (Bf16Products() && rows > 0 && (dx || dw) && Bf16Operand(g, ldg) && col % 8 == 0 && Bf16Operand(x, inF) && Bf16Operand(w, inF) && (inF & 3) == 0 &&
+      aligned16(dx) && aligned16(dw)) {
     Check(om_linear_bwd_bf16(C(), g.Bf16() + col, gp, ldg, x.Bf16(), w.Bf16() + (size_t)col * inF, rows, inF, outF, dx, dw, db, acc ? 1 : 0));
     return;
   }

@@ -177,6 +177,7 @@ struct omh_trainer {
   int64_t steps_done = 0;
   // data parallel
   int world = 1, rank = 0;
+  int dp_timeout_ms = 0;   // host deadline for the gradient exchange of a step (0: the step is not waited for)
   struct BucketInfo { int64_t begin, end; int pending; int total; };
   std::vector<BucketInfo> buckets;
   std::map<AutogradMeta*, int> bucket_of;
@@ -186,7 +187,7 @@ struct omh_trainer {
 
 static void BuildFlatGrads(omh_trainer* t) {
   int64_t total = 0;
-  for (auto& p : t->params) total += p.second.Length();
+  for (auto& p : t->params) total += p.second.Length() + 63;   // room for the alignment of each gradient
   t->flat_grads = Tensor::Zeros(DType::F32, Shape{(int)std::min<int64_t>(total, INT32_MAX)});
   if (total > INT32_MAX) throw TensorShapeException("more than 2^31-1 parameters");
   // Reverse registration order: the gradients that become final first (last layers) sit at the front, so the first
@@ -198,8 +199,11 @@ static void BuildFlatGrads(omh_trainer* t) {
   // order, so that their weight gradient can be written by one product.
   const int np = (int)t->params.size();
   std::vector<bool> placed(np, false);
-  auto place = [&](int i) {
+  auto place = [&](int i, bool group_start) {
     Tensor& p = t->params[i].second;
+    // Every gradient (every group of adjacent ones) starts on a 256-byte boundary: the product kernels write weight
+    // gradients through TMA, which wants 16-byte aligned rows. The padding words stay zero and ride along in the buckets.
+    if (group_start) off = (off + 63) & ~(int64_t)63;
     auto meta = p.Autograd();
     Tensor view = t->flat_grads.View(p.GetShape(), ContiguousStrides(p.GetShape()), off);
     meta->Grad = view;
@@ -231,7 +235,7 @@ static void BuildFlatGrads(omh_trainer* t) {
     for (int guard = 0, j; guard < np && (j = before(first)) >= 0; guard++) first = j;
     for (int cur = first; cur >= 0;) {
       int nxt = after(cur);
-      place(cur);
+      place(cur, cur == first);
       cur = nxt;
     }
   }
@@ -289,10 +293,10 @@ static void StepBody(omh_trainer* t) {
       // No global norm to wait for: each bucket's parameters are updated as soon as that bucket's sum has arrived, while
       // the later buckets (the embedding table comes last) are still on the wire.
       t->opt->StepGroups(t->bucket_params, [&](int b) { Check(om_dp_wait_bucket(ctx, b)); });
-      Check(om_dp_wait(ctx, 0));
+      Check(om_dp_wait(ctx, t->dp_timeout_ms));
       return;
     }
-    Check(om_dp_wait(ctx, 0));
+    Check(om_dp_wait(ctx, t->dp_timeout_ms));
   }
   if (t->clip_norm > 0.f) GradClip::ClipNormAsync(t->opt->Parameters(), t->clip_norm, false, nullptr);
   t->opt->Step();
@@ -430,6 +434,15 @@ OMH_API int32_t omh_trainer_dp_init(omh_trainer* t, const uint8_t* id128, int32_
   });
 }
 
+// Sets the host deadline under which every later step waits for its gradient exchange (0 switches the wait off: the
+// step is then only enqueued, and a peer that stopped shows at the next synchronisation).
+OMH_API int32_t omh_trainer_set_dp_timeout_ms(omh_trainer* t, int32_t ms) {
+  return Guard([&] {
+    if (ms < 0) throw ArgumentOutOfRangeException("The deadline must not be negative.");
+    t->dp_timeout_ms = ms;
+  });
+}
+
 static void CopyInputs(omh_trainer* t, const void* const* inputs_host) {
   om_ctx* ctx = Device::Current();
   for (size_t i = 0; i < t->inputs.size(); i++) {
@@ -445,6 +458,9 @@ static void RunStep(omh_trainer* t) {
     t->opt->FillHyper(t->hyper_host.data(), t->steps_done + 1);
     Check(om_memcpy_h2d(ctx, t->hyper_dev.RawData(), t->hyper_host.data(), t->hyper_host.size()));
     Check(om_graph_launch(ctx, t->graph));
+    // A replayed step contains its collectives; with a deadline set, the host waits for the step under that deadline and
+    // looks at the communicator, so that a peer that stopped shows as an error here and not as an endless wait later.
+    if (t->world > 1 && t->dp_timeout_ms > 0) Check(om_dp_wait(ctx, t->dp_timeout_ms));
     t->opt->StepCount = t->steps_done + 1;
   } else {
     StepBody(t);

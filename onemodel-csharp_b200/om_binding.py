@@ -685,6 +685,9 @@ class Trainer:
         buf = (C.c_uint8 * 128).from_buffer_copy(bytes(id128))
         self._check(host_lib().omh_trainer_dp_init(self.h, buf, i32(rank), i32(world), C.c_int64(global_rows)))
 
+    def set_dp_timeout_ms(self, ms):
+        self._check(host_lib().omh_trainer_set_dp_timeout_ms(self.h, i32(ms)))
+
     def close(self):
         if self.h:
             host_lib().omh_trainer_free(self.h)

@@ -101,11 +101,12 @@ def test_c3_full_size_step_with_the_bench_flags(ctx, configs, capsys):
 def test_c5_slice_with_bf16_operands(ctx, configs, capsys):
     """BERT-base shape (12 x d768 h12 ff3072, seq 512, vocab 30522) on a batch-2 slice, the products of the Linear layers
     with bf16 operands (round to nearest even) and fp32 accumulation, fp32 master weights. Against the oracle that rounds
-    the operands of the same products the same way: what is left is the summation order and the attention kernels' TF32
-    products, held to the TF32 gate. Against the fp32 oracle the bf16 rounding itself shows: 8 mantissa bits per operand,
-    held to 2e-2 scaled over the 12-layer chain."""
+    the operands of the same products the same way: what is left is the summation order, the attention kernels' TF32
+    products, and operands that sit within an fp32 rounding error of a bfloat16 rounding boundary and round the other way
+    on one side (a step of 2^-9 relative in that operand); held to 5e-3 scaled over the 12-layer chain (measured about
+    3e-3). Against the fp32 oracle the bfloat16 rounding itself shows: 8 significant bits per operand, held to 2e-2."""
     cfg = [2, 512, 12, 768, 12, 3072, 30522, 154]
-    run_mlm(ctx, configs, cfg, omb.OM_TF32 | omb.OM_BF16_OPERANDS, "bf16", 2e-3, 1e-3, "c5 slice vs bf16-rounding oracle", capsys)
+    run_mlm(ctx, configs, cfg, omb.OM_TF32 | omb.OM_BF16_OPERANDS, "bf16", 5e-3, 1e-3, "c5 slice vs bf16-rounding oracle", capsys)
     run_mlm(ctx, configs, cfg, omb.OM_TF32 | omb.OM_BF16_OPERANDS, "fp32", 2e-2, 2e-3, "c5 slice vs fp32 oracle", capsys)
 
 

@@ -123,6 +123,8 @@ def test_tf32_matmul_on_the_persistent_kernel(ctx, oracle_built, ta, tb, m, n, k
     r = np.random.default_rng(m * 3 + n + k)
     a = r.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
     b = r.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+    if a.shape[1] % 4 or b.shape[1] % 4:
+        pytest.skip("operand pitch not a multiple of 16 bytes: this shape runs on the fp32 kernel")
     try:
         ctx.set_flags(omb.OM_TF32 | omb.OM_PERSISTENT_TILES)
         got = run_tf32(ctx, ta, tb, m, n, k, a, b)

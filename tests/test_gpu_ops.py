@@ -332,3 +332,64 @@ def test_zero_and_pool(ctx):
     used, cached, allocs = C.c_uint64(), C.c_uint64(), C.c_uint64()
     ctx.call("om_pool_stats", ctx.handle, C.byref(used), C.byref(cached), C.byref(allocs))
     assert used.value > 0
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_context_stays_usable(ctx):
+    """The tensor-pipe kernels' waits are bounded. With a budget of one millisecond, a wait that nothing will ever satisfy
+    (om_selftest_bounded_wait: one warp on a barrier without arrivals) runs out, the kernel returns, om_sync reports
+    OM_ERR_TIMEOUT with the place of the wait, the status is cleared by the report, and the next product on the same
+    context is correct. Nothing hangs or faults: the wait is one millisecond long."""
+    import time
+    ctx.set_flags(omb.OM_TF32)
+    try:
+        ctx.call("om_ctx_set_wait_budget_us", ctx.handle, C.c_int64(1000))
+        t0 = time.perf_counter()
+        ctx.call("om_selftest_bounded_wait", ctx.handle)
+        with pytest.raises(omb.OmError) as e:
+            ctx.sync()
+        assert e.value.status == 6 and "wait expired" in str(e.value) and "detail 99" in str(e.value)
+        assert time.perf_counter() - t0 < 0.5
+        ctx.sync()                                    # reported once, then clear
+        r = np.random.default_rng(3)
+        a, b = r.standard_normal((256, 128)).astype(np.float32), r.standard_normal((128, 256)).astype(np.float32)
+        A, Bm, Cm = ctx.to_device(a), ctx.to_device(b), ctx.empty((256, 256))
+        ctx.call("om_matmul", ctx.handle, i32(0), i32(0), i32(256), i32(256), i32(128), A.ptr, i32(128), Bm.ptr, i32(256), Cm.ptr, i32(256), i32(0))
+        ctx.sync()
+        assert scaled_diff(Cm.numpy(), a @ b) <= 1e-3
+    finally:
+        ctx.call("om_ctx_set_wait_budget_us", ctx.handle, C.c_int64(0))
+        ctx.set_flags(0)
+
+
+def test_checked_mode_poisons_memory_and_catches_a_write_past_the_end(ctx):
+    """OM_CHECKED (the reference's CHECKED build, docs/tensors.md:108-110): fresh memory reads as 0xFF bytes (NaN), 64 guard
+    bytes follow every buffer, and a write that runs past a buffer's end is reported when the buffer is released. The
+    overrun here stays inside the guard area of the block itself, so no foreign memory is touched."""
+    ctx.set_flags(omb.OM_CHECKED)
+    try:
+        n = 100
+        ptr = C.c_void_p()
+        ctx.call("om_alloc", ctx.handle, C.c_size_t(4 * n), i32(0), C.byref(ptr))
+        host = np.empty(n, np.float32)
+        ctx.call("om_memcpy_d2h", ctx.handle, host.ctypes.data_as(C.c_void_p), ptr, C.c_size_t(4 * n))
+        assert np.all(np.isnan(host)) and np.all(host.view(np.uint32) == 0xFFFFFFFF)
+        ctx.call("om_fill", ctx.handle, ptr, f32(1.0), i64(n))            # inside the buffer: fine
+        ctx.call("om_free", ctx.handle, ptr)
+        ctx.sync()
+        ctx.call("om_alloc", ctx.handle, C.c_size_t(4 * n), i32(1), C.byref(ptr))   # zeroed on request, still guarded
+        ctx.call("om_memcpy_d2h", ctx.handle, host.ctypes.data_as(C.c_void_p), ptr, C.c_size_t(4 * n))
+        assert not host.any()
+        ctx.call("om_fill", ctx.handle, ptr, f32(2.0), i64(n + 3))        # three floats past the end: into the guard bytes
+        ctx.call("om_free", ctx.handle, ptr)
+        with pytest.raises(omb.OmError) as e:
+            ctx.sync()
+        assert e.value.status == 9 and "guard bytes" in str(e.value)
+        ctx.sync()
+        # A whole op under the flag (its scratch blocks are guarded too) still gives the right answer.
+        g = np.random.default_rng(4).standard_normal((700, 96)).astype(np.float32)
+        G, O = ctx.to_device(g), ctx.empty((96,))
+        ctx.call("om_colsum", ctx.handle, G.ptr, i32(700), i32(96), O.ptr, i32(0))
+        ctx.sync()
+        assert np.allclose(O.numpy(), g.astype(np.float64).sum(0), rtol=1e-5, atol=1e-5)
+    finally:
+        ctx.set_flags(0)

@@ -179,3 +179,29 @@ def test_crnn_config_small(ctx, configs, graph):
             for i, (n, s) in enumerate(named):
                 assert scaled_diff(tr.get_grad(i, s), grads[n]) <= 1e-4, n
     tr.close()
+
+
+def test_blocks_of_a_captured_step_are_not_handed_to_other_tensors(ctx):
+    """A captured step writes to the pool blocks it was recorded with on every replay. Those blocks therefore stay with
+    the graph: tensors allocated on the same context after the capture (an evaluation batch a user keeps, a second
+    model) must never receive one of them. Tensors of every size class the step uses are created after the capture, the
+    step is replayed, and their contents must be untouched."""
+    ctx.set_flags(0)
+    ctx.make_current()
+    cfg = [4, 16, 2, 32, 4, 64, 101, 10]
+    tr = omb.Trainer("mlm", cfg, lr=1e-3, weight_decay=0.01, seed=0)
+    try:
+        batches = [synth.mlm_batch(4, 16, 101, 10, s) for s in range(6)]
+        for s in range(2):
+            tr.step(list(batches[s]))
+        tr.enable_graph()
+        kept = []
+        for n in (16, 64, 160, 256, 640, 1010, 1024, 2048, 3232, 4096, 6144, 8192, 16384):
+            for copy in range(6):
+                kept.append((omb.Tensor.from_numpy(np.full((n,), float(n + copy), np.float32)), float(n + copy)))
+        losses = [tr.step(list(batches[s])) for s in range(2, 6)]
+        assert np.all(np.isfinite(losses))
+        for t, v in kept:
+            assert np.all(t.numpy() == v), (t.shape, v)
+    finally:
+        tr.close()
