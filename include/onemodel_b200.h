@@ -172,7 +172,8 @@ int32_t om_linear_bwd_ld(om_ctx* ctx, const float* g, int32_t ldg, const float* 
                          int32_t in_features, int32_t out_features, float* dx, float* dW, float* dbias,
                          int32_t accumulate_w);
 /* Backward of om_linear_fwd: dx = g*W (NULL to skip), dW = g^T*x (NULL to skip), dbias = column sums of g
- * (NULL to skip). accumulate_w != 0 adds into dW/dbias (Engine.AddInto, Engine.cs:330-344).
+ * (NULL to skip). accumulate_w bit 0 adds into dW/dbias, bit 1 adds into dx (Engine.AddInto, Engine.cs:330-344: the
+ * product's epilogue adds to a gradient that already holds another branch's contribution instead of a separate pass).
  * Replaces the Reshape/Add/MatMul/Permute records of one Linear (call stack: BackwardOps.cs:69-82,107-122,156-194). */
 int32_t om_linear_bwd(om_ctx* ctx, const float* g, const float* x, const float* W, int32_t rows,
                       int32_t in_features, int32_t out_features, float* dx, float* dW, float* dbias,
@@ -193,6 +194,24 @@ int32_t om_matmul_bf16(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m, i
                        int32_t lda, const uint16_t* B, int32_t ldb, float* C, int32_t ldc, int32_t accumulate);
 int32_t om_linear_fwd_bf16(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows,
                            int32_t in_features, int32_t out_features, float* y, int32_t ldy);
+/* The forward product and the input gradient with the bfloat16 copy of their result (y16 / dx16, same pitch in elements as
+ * the fp32 result, may be NULL) written by the product's epilogue: the packed q | k | v projections and the gradient of the
+ * attention output are read as bfloat16 by the attention kernels. */
+int32_t om_linear_fwd_bf16_b16(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows,
+                               int32_t in_features, int32_t out_features, float* y, uint16_t* y16, int32_t ldy);
+int32_t om_linear_bwd_bf16_b16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x,
+                               const uint16_t* W, int32_t rows, int32_t in_features, int32_t out_features, float* dx,
+                               uint16_t* dx16, float* dW, float* dbias, int32_t accumulate_w);
+/* Producers that write the bfloat16 copy of their result in the same pass (the copy pointer may be NULL: then they are
+ * om_unary, om_unary_bwd, om_layernorm_fwd, om_layernorm_bwd): the activation, its gradient and the two sides of a
+ * layer norm are what feeds the Linear products of an encoder layer, so no separate cast pass is left for them. */
+int32_t om_unary_b16(om_ctx* ctx, int32_t op, const float* x, float* y, uint16_t* y16, int64_t n);
+int32_t om_unary_bwd_b16(om_ctx* ctx, int32_t op, const float* g, const float* saved, float* dx, uint16_t* dx16, int64_t n);
+int32_t om_layernorm_fwd_b16(om_ctx* ctx, const float* x, const float* gamma, const float* beta, int32_t rows,
+                             int32_t cols, float eps, float* y, uint16_t* y16, float* mean, float* inv);
+int32_t om_layernorm_bwd_b16(om_ctx* ctx, const float* g, const float* x, const float* gamma, const float* mean,
+                             const float* inv, int32_t rows, int32_t cols, float* dx, uint16_t* dx16, float* dgamma,
+                             float* dbeta, int32_t accumulate_params);
 /* g16 is the bfloat16 copy of g (same pitch ldg); the bias gradient sums the fp32 g. */
 int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x,
                            const uint16_t* W, int32_t rows, int32_t in_features, int32_t out_features, float* dx,
@@ -398,6 +417,22 @@ int32_t om_attention_bwd_strided_out(om_ctx* ctx, const float* g, const om_head_
                                      const float* lse, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d,
                                      float scale, float* dq, const om_head_strides* dqs, float* dk,
                                      const om_head_strides* dks, float* dv, const om_head_strides* dvs);
+/* AttentionBackward (src/OneModel/Tensors/Autograd/BackwardNn.cs:636-701) for sequences of several 128-key tiles with
+ * bfloat16 product operands, in one kernel per call: a CTA per (batch, head) forms S = Q K^T and dP = dO V^T tile by tile
+ * in tensor memory, P = exp(scale S + mask - lse) and dS = P (dP - rowsum(dO o O)) scale in registers (rounded to
+ * bfloat16 as the operands of the three output products), and accumulates dV, dK (per key tile) and dQ (all query tiles)
+ * in tensor memory: nothing of size Lq x Lk is written to memory. q16 / k16 / v16 / g16 are the bfloat16 copies of q, k, v
+ * and of the output gradient g; g and out (the forward's output) are read in fp32 for the row dots; lse is the forward's
+ * row log-sum-exp. Results are fp32 with optional bfloat16 copies (dq16 / dk16 / dv16, same strides). Built for head
+ * dimension 64 and Lq <= 512 (om_attention_bwd_bf16_supported tells); strides of the bfloat16 operands multiples of 8. */
+int32_t om_attention_bwd_bf16_supported(om_ctx* ctx, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d);
+int32_t om_attention_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, const om_head_strides* gs,
+                              const uint16_t* q16, const om_head_strides* qs, const uint16_t* k16, const om_head_strides* ks,
+                              const uint16_t* v16, const om_head_strides* vs, const float* out, const om_head_strides* os,
+                              const float* mask, int64_t mask_batch_stride, const float* lse, int32_t b, int32_t h,
+                              int32_t lq, int32_t lk, int32_t d, float scale, float* dq, uint16_t* dq16,
+                              const om_head_strides* dqs, float* dk, uint16_t* dk16, const om_head_strides* dks, float* dv,
+                              uint16_t* dv16, const om_head_strides* dvs);
 
 /* ---- pooling and convolution ---------------------------------------------------------------------------- */
 

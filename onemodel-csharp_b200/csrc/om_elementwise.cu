@@ -1,6 +1,8 @@
 // Bandwidth-bound elementwise, copy and broadcast-sum kernels. All are grid-stride, 128-bit vectorised where the
 // layout allows, and free of floating-point atomics. The library is compiled with --fmad=false so that a*b+c
 // written here rounds twice exactly as the reference's managed code does; fused multiply-adds are explicit fmaf.
+#include <cuda_bf16.h>
+
 #include "om_common.cuh"
 
 namespace om {
@@ -134,8 +136,19 @@ __device__ __forceinline__ float unary_grad(float g, float s) {
   return g;
 }
 
+// Four bfloat16 values (round to nearest even) as one 8-byte word.
+__device__ __forceinline__ uint2 pack_bf16x4(float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  return make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+__device__ __forceinline__ uint16_t bf16_of(float v) {
+  __nv_bfloat16 h = __float2bfloat16_rn(v);
+  return *reinterpret_cast<uint16_t*>(&h);
+}
+
+// y16 (may be null): the bfloat16 copy of y, written in the same pass for the product that reads y next.
 template <int OP>
-__global__ void unary_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n4, int64_t n) {
+__global__ void unary_kernel(const float* __restrict__ x, float* __restrict__ y, uint16_t* __restrict__ y16, int64_t n4, int64_t n) {
   pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -148,13 +161,18 @@ __global__ void unary_kernel(const float* __restrict__ x, float* __restrict__ y,
     r.z = unary_apply<OP>(v.z);
     r.w = unary_apply<OP>(v.w);
     y4[j] = r;
+    if (y16) reinterpret_cast<uint2*>(y16)[j] = pack_bf16x4(r);
   }
-  for (int64_t j = n4 * 4 + i; j < n; j += stride) y[j] = unary_apply<OP>(x[j]);
+  for (int64_t j = n4 * 4 + i; j < n; j += stride) {
+    const float r = unary_apply<OP>(x[j]);
+    y[j] = r;
+    if (y16) y16[j] = bf16_of(r);
+  }
 }
 
 template <int OP>
 __global__ void unary_bwd_kernel(const float* __restrict__ g, const float* __restrict__ s, float* __restrict__ dx,
-                                 int64_t n4, int64_t n) {
+                                 uint16_t* __restrict__ dx16, int64_t n4, int64_t n) {
   pdl_enter();
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -168,8 +186,13 @@ __global__ void unary_bwd_kernel(const float* __restrict__ g, const float* __res
     r.z = unary_grad<OP>(a.z, b.z);
     r.w = unary_grad<OP>(a.w, b.w);
     d4[j] = r;
+    if (dx16) reinterpret_cast<uint2*>(dx16)[j] = pack_bf16x4(r);
   }
-  for (int64_t j = n4 * 4 + i; j < n; j += stride) dx[j] = unary_grad<OP>(g[j], s[j]);
+  for (int64_t j = n4 * 4 + i; j < n; j += stride) {
+    const float r = unary_grad<OP>(g[j], s[j]);
+    dx[j] = r;
+    if (dx16) dx16[j] = bf16_of(r);
+  }
 }
 
 __global__ void add_into_kernel(float* dst, const float* __restrict__ src, int64_t n4, int64_t n) {
@@ -604,32 +627,38 @@ int32_t om_binary(om_ctx* ctx, int32_t op, int32_t rank, const int32_t* shape, c
     default: return fail(ctx, OM_ERR_ARG, "unknown unary op %d", op);                              \
   }
 
-int32_t om_unary(om_ctx* ctx, int32_t op, const float* x, float* y, int64_t n) {
+int32_t om_unary_b16(om_ctx* ctx, int32_t op, const float* x, float* y, uint16_t* y16, int64_t n) {
   OM_CHECK_CTX(ctx);
   if (n < 0) return fail(ctx, OM_ERR_SHAPE, "om_unary: n %lld", (long long)n);
   if (n == 0) return OM_OK;
-  ProfileScope prof(ctx, "om_unary", 0, 8.0 * n);
-  bool vec = aligned16(x) && aligned16(y);
+  ProfileScope prof(ctx, "om_unary", 0, (y16 ? 10.0 : 8.0) * n);
+  bool vec = aligned16(x) && aligned16(y) && (!y16 || (reinterpret_cast<uintptr_t>(y16) & 7) == 0);
   int64_t n4 = vec ? n / 4 : 0;
   const int threads = 256;
   int grid = grid_for(ctx, vec ? (n + 3) / 4 : n, threads);
-  OM_UNARY_DISPATCH(unary_kernel, x, y, n4, n)
+  OM_UNARY_DISPATCH(unary_kernel, x, y, y16, n4, n)
   OM_LAUNCH_CHECK(ctx, "om_unary");
   return OM_OK;
 }
 
-int32_t om_unary_bwd(om_ctx* ctx, int32_t op, const float* g, const float* saved, float* dx, int64_t n) {
+int32_t om_unary(om_ctx* ctx, int32_t op, const float* x, float* y, int64_t n) { return om_unary_b16(ctx, op, x, y, nullptr, n); }
+
+int32_t om_unary_bwd_b16(om_ctx* ctx, int32_t op, const float* g, const float* saved, float* dx, uint16_t* dx16, int64_t n) {
   OM_CHECK_CTX(ctx);
   if (n < 0) return fail(ctx, OM_ERR_SHAPE, "om_unary_bwd: n %lld", (long long)n);
   if (n == 0) return OM_OK;
-  ProfileScope prof(ctx, "om_unary_bwd", 0, 12.0 * n);
-  bool vec = aligned16(g) && aligned16(saved) && aligned16(dx);
+  ProfileScope prof(ctx, "om_unary_bwd", 0, (dx16 ? 14.0 : 12.0) * n);
+  bool vec = aligned16(g) && aligned16(saved) && aligned16(dx) && (!dx16 || (reinterpret_cast<uintptr_t>(dx16) & 7) == 0);
   int64_t n4 = vec ? n / 4 : 0;
   const int threads = 256;
   int grid = grid_for(ctx, vec ? (n + 3) / 4 : n, threads);
-  OM_UNARY_DISPATCH(unary_bwd_kernel, g, saved, dx, n4, n)
+  OM_UNARY_DISPATCH(unary_bwd_kernel, g, saved, dx, dx16, n4, n)
   OM_LAUNCH_CHECK(ctx, "om_unary_bwd");
   return OM_OK;
+}
+
+int32_t om_unary_bwd(om_ctx* ctx, int32_t op, const float* g, const float* saved, float* dx, int64_t n) {
+  return om_unary_bwd_b16(ctx, op, g, saved, dx, nullptr, n);
 }
 
 int32_t om_add_into(om_ctx* ctx, float* dst, const float* src, int64_t n) {

@@ -142,15 +142,15 @@ int32_t om_linear_bwd_ld(om_ctx* ctx, const float* g, int32_t ldg, const float* 
     if (!dx) return OM_OK;
     ProfileScope prof(ctx, "om_linear_bwd.dgrad", flops, bytes);
     // dx[rows, in] = g[rows, out] * W[out, in]
-    return gemm_dispatch(ctx, 0, 0, rows, in_features, out_features, g, ldg, W, in_features, dx, in_features, 0, nullptr);
+    return gemm_dispatch(ctx, 0, 0, rows, in_features, out_features, g, ldg, W, in_features, dx, in_features, (accumulate_w >> 1) & 1, nullptr);
   };
   auto parameter_side = [&]() -> int32_t {
     if (dW) {
       ProfileScope prof(ctx, "om_linear_bwd.wgrad", flops, bytes);
       // dW[out, in] = g[rows, out]^T * x[rows, in]
-      OM_TRY(gemm_dispatch(ctx, 1, 0, out_features, in_features, rows, g, ldg, x, in_features, dW, in_features, accumulate_w, nullptr));
+      OM_TRY(gemm_dispatch(ctx, 1, 0, out_features, in_features, rows, g, ldg, x, in_features, dW, in_features, accumulate_w & 1, nullptr));
     }
-    if (dbias) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w));
+    if (dbias) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w & 1));
     return OM_OK;
   };
   // The two sides share only inputs. With OM_TWO_STREAMS they overlap (not while per-entry times are being taken,

@@ -11,7 +11,7 @@ namespace om {
 bool gemm_ws_supported(om_ctx* ctx, int elem, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, const float* C,
                        long long ldc);
 int32_t gemm_ws(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, float* C,
-                long long ldc, int acc, const float* bias);
+                long long ldc, int acc, const float* bias, uint16_t* C16);
 int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64_t ld, float* out, int32_t accumulate);
 
 // Eight elements per thread: two 16-byte loads, one 16-byte store.
@@ -37,6 +37,15 @@ __global__ void cast_bf16_kernel(const float* __restrict__ src, uint16_t* __rest
     __nv_bfloat16 v = __float2bfloat16_rn(src[t]);
     dst[t] = *reinterpret_cast<uint16_t*>(&v);
   }
+}
+
+// The bfloat16 copy of a row-pitched matrix, element for element (the pitch columns are converted along: harmless).
+int32_t cast_bf16_rows(om_ctx* ctx, const float* src, uint16_t* dst, int rows, int cols, long long ld) {
+  if (rows < 1 || cols < 1) return OM_OK;
+  const int64_t n = (int64_t)(rows - 1) * ld + cols;
+  launch_chained(ctx, cast_bf16_kernel, grid_for(ctx, (n + 7) / 8, 256), 256, 0, src, dst, n);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? OM_OK : check_cuda(ctx, e, "cast_bf16_rows");
 }
 
 static int32_t check_args(om_ctx* ctx, const char* who, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, const float* C,
@@ -75,24 +84,33 @@ int32_t om_matmul_bf16(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m, i
   OM_TRY(check_args(ctx, "om_matmul_bf16", m, n, k, A, lda, B, ldb, C, ldc));
   if (m == 0 || n == 0) return OM_OK;
   ProfileScope prof(ctx, "om_matmul", 2.0 * m * n * k, 2.0 * ((double)m * k + (double)k * n) + 4.0 * (double)m * n);
-  return gemm_ws(ctx, 1, transA, transB, m, n, k, A, lda, B, ldb, C, ldc, accumulate, nullptr);
+  return gemm_ws(ctx, 1, transA, transB, m, n, k, A, lda, B, ldb, C, ldc, accumulate, nullptr, nullptr);
 }
 
-int32_t om_linear_fwd_bf16(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows, int32_t in_features,
-                           int32_t out_features, float* y, int32_t ldy) {
+int32_t om_linear_fwd_bf16_b16(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows, int32_t in_features,
+                               int32_t out_features, float* y, uint16_t* y16, int32_t ldy) {
   OM_CHECK_CTX(ctx);
+  if (y16 && (reinterpret_cast<uintptr_t>(y16) & 15)) return fail(ctx, OM_ERR_ARG, "om_linear_fwd_bf16_b16: the bfloat16 copy must be 16-byte aligned");
   if (rows < 0 || in_features < 1 || out_features < 1 || ldy < out_features)
     return fail(ctx, OM_ERR_SHAPE, "om_linear_fwd_bf16: rows %d in %d out %d ldy %d", rows, in_features, out_features, ldy);
   OM_TRY(check_args(ctx, "om_linear_fwd_bf16", rows, out_features, in_features, x, in_features, W, in_features, y, ldy));
   if (rows == 0) return OM_OK;
   ProfileScope prof(ctx, "om_linear_fwd", 2.0 * rows * in_features * out_features,
                     2.0 * ((double)rows * in_features + (double)in_features * out_features) + 4.0 * (double)rows * out_features);
-  return gemm_ws(ctx, 1, 0, 1, rows, out_features, in_features, x, in_features, W, in_features, y, ldy, 0, bias);
+  return gemm_ws(ctx, 1, 0, 1, rows, out_features, in_features, x, in_features, W, in_features, y, ldy, 0, bias, y16);
 }
 
-int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x, const uint16_t* W, int32_t rows,
-                           int32_t in_features, int32_t out_features, float* dx, float* dW, float* dbias, int32_t accumulate_w) {
+int32_t om_linear_fwd_bf16(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows, int32_t in_features,
+                           int32_t out_features, float* y, int32_t ldy) {
+  return om_linear_fwd_bf16_b16(ctx, x, W, bias, rows, in_features, out_features, y, nullptr, ldy);
+}
+
+int32_t om_linear_bwd_bf16_b16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x, const uint16_t* W, int32_t rows,
+                               int32_t in_features, int32_t out_features, float* dx, uint16_t* dx16, float* dW, float* dbias,
+                               int32_t accumulate_w) {
   OM_CHECK_CTX(ctx);
+  if (dx16 && (!dx || (reinterpret_cast<uintptr_t>(dx16) & 15)))
+    return fail(ctx, OM_ERR_ARG, "om_linear_bwd_bf16_b16: the bfloat16 copy needs dx and 16-byte alignment");
   if (rows < 0 || in_features < 1 || out_features < 1 || ldg < out_features)
     return fail(ctx, OM_ERR_SHAPE, "om_linear_bwd_bf16: rows %d in %d out %d ldg %d", rows, in_features, out_features, ldg);
   if (rows == 0) return OM_OK;
@@ -101,17 +119,22 @@ int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int
     // dx[rows, in] = g[rows, out] * W[out, in]
     OM_TRY(check_args(ctx, "om_linear_bwd_bf16 (input gradient)", rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features));
     ProfileScope prof(ctx, "om_linear_bwd.dgrad", flops, 2.0 * ((double)rows * out_features + (double)in_features * out_features) + 4.0 * (double)rows * in_features);
-    OM_TRY(gemm_ws(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, 0, nullptr));
+    OM_TRY(gemm_ws(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, (accumulate_w >> 1) & 1, nullptr, dx16));
   }
   if (dW) {
     // dW[out, in] = g[rows, out]^T * x[rows, in]
     OM_TRY(check_args(ctx, "om_linear_bwd_bf16 (weight gradient)", out_features, in_features, rows, g16, ldg, x, in_features, dW, in_features));
     ProfileScope prof(ctx, "om_linear_bwd.wgrad", flops, 2.0 * ((double)rows * out_features + (double)rows * in_features) + 4.0 * (double)in_features * out_features);
-    OM_TRY(gemm_ws(ctx, 1, 1, 0, out_features, in_features, rows, g16, ldg, x, in_features, dW, in_features, accumulate_w, nullptr));
+    OM_TRY(gemm_ws(ctx, 1, 1, 0, out_features, in_features, rows, g16, ldg, x, in_features, dW, in_features, accumulate_w & 1, nullptr, nullptr));
   }
   // The bias gradient is a sum of fp32 values, not a product: it reads the fp32 gradient.
-  if (dbias) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w));
+  if (dbias) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w & 1));
   return OM_OK;
+}
+
+int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x, const uint16_t* W, int32_t rows,
+                           int32_t in_features, int32_t out_features, float* dx, float* dW, float* dbias, int32_t accumulate_w) {
+  return om_linear_bwd_bf16_b16(ctx, g16, g, ldg, x, W, rows, in_features, out_features, dx, nullptr, dW, dbias, accumulate_w);
 }
 
 }  // extern "C"

@@ -382,7 +382,7 @@ bool gemm_pair_supported(om_ctx* ctx, int m, int n, int k);
 bool gemm_ws_supported(om_ctx* ctx, int elem, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, const float* C,
                        long long ldc);
 int32_t gemm_ws(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, float* C,
-                long long ldc, int acc, const float* bias);
+                long long ldc, int acc, const float* bias, uint16_t* C16);
 int32_t gemm_pair(om_ctx* ctx, int ta, int tb, int m, int n, int k, const float* A, int lda, const float* B, int ldb, float* C, int ldc,
                   int acc, const float* bias);
 
@@ -394,7 +394,7 @@ int32_t gemm_tc_heads(om_ctx* ctx, int ta, int tb, int m, int n, int k, const fl
                       const float* B, int ldb, long long sB, long long iB, float* C, int ldc, long long sC, long long iC, int batch,
                       int inner, int acc, const float* bias) {
   if (batch == 1 && (ctx->flags & OM_PERSISTENT_TILES) && m >= 256 && n >= 64 && gemm_ws_supported(ctx, 0, m, n, k, A, lda, B, ldb, C, ldc))
-    return gemm_ws(ctx, 0, ta, tb, m, n, k, A, lda, B, ldb, C, ldc, acc, bias);
+    return gemm_ws(ctx, 0, ta, tb, m, n, k, A, lda, B, ldb, C, ldc, acc, bias, nullptr);
   if (batch == 1 && gemm_pair_supported(ctx, m, n, k)) return gemm_pair(ctx, ta, tb, m, n, k, A, lda, B, ldb, C, ldc, acc, bias);
   // op(A) is [m, k]. ta == 0: stored [m, k] (K-major tile, map inner = k). ta != 0: stored [k, m] (MN-major, inner = m).
   // op(B) is [k, n]. tb != 0: stored [n, k] (K-major, inner = k). tb == 0: stored [k, n] (MN-major, inner = n).

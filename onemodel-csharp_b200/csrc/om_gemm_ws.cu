@@ -2,11 +2,12 @@
 //
 // One cluster of two CTAs (tcgen05.mma.cta_group::2) stays on its pair of SMs and walks a fixed list of 256 x BN tiles
 // of C (cluster c takes tiles c, c + clusters, ...). Per CTA: warp 0 issues TMA loads into a ring of operand stages,
-// warp 1 of the pair's leader issues the MMAs into one of TWO accumulator buffers in tensor memory, and eight epilogue
+// warp 1 of the pair's leader issues the MMAs into one of TWO accumulator buffers in tensor memory, and four epilogue
 // warps read the other buffer back (tcgen05.ld), add the bias and hand 32 x 32 blocks to the TMA unit
-// (cp.async.bulk.tensor store, or cp.reduce .add when the product accumulates into C). A tile's read-back and its
-// stores therefore run under the next tile's MMAs; with one tile per CTA they were as long as the main loop of a
-// k = 384 ... 768 product.
+// (cp.async.bulk.tensor store, or cp.reduce .add when the product accumulates into C), optionally together with the same
+// block rounded to bfloat16 for a second tensor (the copy that a following bfloat16 product or attention kernel reads).
+// A tile's read-back and its stores therefore run under the next tile's MMAs; with one tile per CTA they were as long as
+// the main loop of a k = 384 ... 768 product.
 //
 // Operand element types: TF32 (fp32 in memory, rounded to nearest even by the TMA load) or BF16 (bfloat16 in memory:
 // half the bytes through L2 and shared memory per MMA, which is what bounds the fp32-operand tile). Accumulation is fp32
@@ -15,15 +16,28 @@
 // No multicast loads: each CTA fetches its own 128 rows of A and its own half of the B tile. Every wait is bounded
 // (om_tc.cuh): on a timeout the kernel raises OM_ERR_TIMEOUT in the context's status word, all roles leave their loops,
 // tensor memory is released and the kernel returns.
+#include <cuda_bf16.h>
+
 #include "om_tc.cuh"
 
 namespace om {
 
 constexpr int W_BM = 128;                 // rows of C per CTA; a pair computes 256
-constexpr int W_STAGES = 5;
-constexpr int W_EPI_WARPS = 8;            // two per TMEM lane quadrant, each taking half of the tile's columns
+#ifndef OM_WS_STAGES
+#define OM_WS_STAGES 6
+#endif
+#ifndef OM_WS_EPI_WARPS
+#define OM_WS_EPI_WARPS 4
+#endif
+#ifndef OM_WS_RING
+#define OM_WS_RING 1
+#endif
+constexpr int W_STAGES = OM_WS_STAGES;
+constexpr int W_EPI_WARPS = OM_WS_EPI_WARPS;   // a multiple of four: the warps of a TMEM lane quadrant share the tile's columns
+constexpr int W_EPI_PARTS = W_EPI_WARPS / 4;
 constexpr int W_THREADS = 32 * (2 + W_EPI_WARPS);
-constexpr int W_RING = 2;                 // 4 KB staging blocks per epilogue warp
+constexpr int W_RING = OM_WS_RING;        // staging slots per epilogue warp
+constexpr int W_SLOT = 4096 + 2048;       // a 32 x 32 fp32 block and its bfloat16 copy
 constexpr int kWsClusters = 74;           // pairs of one round on a 148-SM device: the k-split target (a constant of the shape rule)
 
 template <int ELEM> struct WsElem;
@@ -44,6 +58,7 @@ struct WsParams {
   int kb_per_split;               // k blocks per slice
   const float* bias;
   int accumulate;
+  int c16;                        // also store the bfloat16 copy of every block through map_c16 (never with accumulate)
   int32_t* status;
 };
 
@@ -103,7 +118,7 @@ __host__ __device__ constexpr uint32_t ws_idesc(int bn, bool a_mn, bool b_mn) {
 
 template <int BN>
 constexpr size_t ws_smem_bytes() {
-  return (size_t)W_STAGES * (W_BM * 128 + (BN / 2) * 128) + (size_t)W_EPI_WARPS * W_RING * 4096 + 1024 + 256;
+  return (size_t)W_STAGES * (W_BM * 128 + (BN / 2) * 128) + (size_t)W_EPI_WARPS * W_RING * W_SLOT + 1024 + 256;
 }
 
 // Shared-memory tiles. K-major: rows (m or n) of 128 bytes of k, 8-row swizzle atoms 1024 bytes apart. MN-major: chunks of
@@ -111,7 +126,7 @@ constexpr size_t ws_smem_bytes() {
 template <int ELEM, int BN, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W_THREADS, 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_c, WsParams p) {
+               const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_c16, WsParams p) {
   using E = WsElem<ELEM>;
   constexpr int BK = E::BK;
   constexpr int HB = BN / 2;                                   // rows of the B tile this CTA loads
@@ -125,7 +140,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* staging = smem + (size_t)W_STAGES * STAGE;
-  uint64_t* full = reinterpret_cast<uint64_t*>(staging + (size_t)W_EPI_WARPS * W_RING * 4096);
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + (size_t)W_EPI_WARPS * W_RING * W_SLOT);
   uint64_t* empty = full + W_STAGES;
   uint64_t* acc_full = empty + W_STAGES;     // [2]
   uint64_t* acc_empty = acc_full + 2;        // [2], used in the leader
@@ -241,8 +256,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     //      the tile's 32-column blocks between them ----
     const int e = warp - 2;
     const int quad = warp & 3;
-    const int half = e >> 2;
-    uint8_t* ring = staging + (size_t)e * W_RING * 4096;
+    const int part = e >> 2;
+    uint8_t* ring = staging + (size_t)e * W_RING * W_SLOT;
     uint32_t tile_i = 0, stored = 0;
     bool ok = true;
     for (int u = cluster_id; u < units && ok; u += clusters, tile_i++) {
@@ -256,7 +271,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int row_base = m0 + quad * 32;
       const uint32_t tmem_acc = tmem_base + a * BN + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
-      for (int cb = half * (NB / 2); cb < (half + 1) * (NB / 2); cb++) {
+      for (int cb = part * (NB / W_EPI_PARTS); cb < (part + 1) * (NB / W_EPI_PARTS); cb++) {
         const int col0 = n0 + cb * 32;
         const bool live = row_base < p.m && col0 < p.n;
         uint32_t r[32];
@@ -264,7 +279,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tmem_ld_32x32b_x32(tmem_acc + (uint32_t)(cb * 32), r);
           tmem_ld_wait();
         }
-        if (cb == (half + 1) * (NB / 2) - 1) {
+        if (cb == (part + 1) * (NB / W_EPI_PARTS) - 1) {
           // This warp has everything it needs out of the buffer: the next tile but one may overwrite it.
           tc_fence_before();
           __syncwarp();
@@ -274,19 +289,40 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (p.bias) add_bias32(r, p.bias, col0, p.n);
         if (stored >= W_RING) {
           // The block about to be overwritten was handed to the TMA unit W_RING stores ago.
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(W_RING - 1) : "memory");
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(W_RING - 1) : "memory");   // all but the newest W_RING - 1
           __syncwarp();
         }
-        uint8_t* blk = ring + (size_t)(stored % W_RING) * 4096;
+        uint8_t* blk = ring + (size_t)(stored % W_RING) * W_SLOT;
         const uint32_t row_addr = smem_u32(blk) + (uint32_t)lane * 128u;
 #pragma unroll
         for (int c4 = 0; c4 < 8; c4++)
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)((c4 ^ (lane & 7)) << 4)), "r"(r[4 * c4]),
                        "r"(r[4 * c4 + 1]), "r"(r[4 * c4 + 2]), "r"(r[4 * c4 + 3])
                        : "memory");
+        if (p.c16) {
+          // The block as bfloat16: 64 bytes per row in the 64-byte swizzle of map_c16 (16-byte chunk c of row r at
+          // c ^ ((r >> 1) & 3)).
+          const uint32_t row16 = smem_u32(blk + 4096) + (uint32_t)lane * 64u;
+#pragma unroll
+          for (int c8 = 0; c8 < 4; c8++) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * c8 + 2 * q]), __uint_as_float(r[8 * c8 + 2 * q + 1]));
+              w[q] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row16 + (uint32_t)((c8 ^ ((lane >> 1) & 3)) << 4)), "r"(w[0]), "r"(w[1]),
+                         "r"(w[2]), "r"(w[3])
+                         : "memory");
+          }
+        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
+          if (p.c16)
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_c16), "r"(col0),
+                         "r"(row_base), "r"(smem_u32(blk + 4096))
+                         : "memory");
           if (p.accumulate)
             asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&map_c),
                          "r"(col0), "r"(row_base), "r"(split), "r"(smem_u32(blk))
@@ -339,6 +375,16 @@ static bool ws_store_map(CUtensorMap* map, float* base, int n, int m, long long 
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The map of the bfloat16 copy of C: [m, n] with the same pitch in elements, box [32 rows, 32 columns], 64-byte swizzle.
+static bool ws_store_map16(CUtensorMap* map, uint16_t* base, int n, int m, long long ld) {
+  cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // What the kernel can take: operand and C pitches and base addresses that TMA can describe (16-byte multiples), any m, n, k.
 bool gemm_ws_supported(om_ctx* ctx, int elem, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, const float* C,
                        long long ldc) {
@@ -352,8 +398,8 @@ bool gemm_ws_supported(om_ctx* ctx, int elem, int m, int n, int k, const void* A
 }
 
 template <int ELEM, int BN>
-static int32_t ws_launch(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const WsParams& p,
-                         int units) {
+static int32_t ws_launch(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                         const CUtensorMap& mc16, const WsParams& p, int units) {
   constexpr size_t smem = ws_smem_bytes<BN>();
 #define OM_WS(AMN, BMN)                                                                                                          \
   do {                                                                                                                           \
@@ -372,7 +418,7 @@ static int32_t ws_launch(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& m
       max_clusters = nc;                                                                                                         \
     }                                                                                                                            \
     const int clusters = units < max_clusters ? units : max_clusters;                                                            \
-    launch_chained(ctx, gemm_ws_kernel<ELEM, BN, AMN, BMN>, dim3(2 * (unsigned)clusters), W_THREADS, smem, ma, mb, mc, p);        \
+    launch_chained(ctx, gemm_ws_kernel<ELEM, BN, AMN, BMN>, dim3(2 * (unsigned)clusters), W_THREADS, smem, ma, mb, mc, mc16, p);  \
   } while (0)
   if (!a_mn && !b_mn) OM_WS(false, false);
   else if (!a_mn && b_mn) OM_WS(false, true);
@@ -385,14 +431,22 @@ static int32_t ws_launch(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& m
 
 // C[m, n] (+)= op(A)[m, k] op(B)[k, n] + bias. elem 0: A and B are fp32 (TF32 products); elem 1: A and B are bfloat16.
 // ta != 0: A is stored [k, m]; tb != 0: B is stored [n, k]. Leading dimensions in elements of the operand's own type.
+// C16 (may be null): also receives C rounded to bfloat16, element i of C16 being element i of C (same pitch). Needs a
+// pitch that is a multiple of 8, a 16-byte aligned C16 and no accumulation; gemm_ws_c16_ok tells.
+bool gemm_ws_c16_ok(const uint16_t* C16, long long ldc, int acc) {
+  return C16 && !acc && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C16) & 15) == 0;
+}
+
+int32_t cast_bf16_rows(om_ctx* ctx, const float* src, uint16_t* dst, int rows, int cols, long long ld);
+
 int32_t gemm_ws(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, float* C,
-                long long ldc, int acc, const float* bias) {
+                long long ldc, int acc, const float* bias, uint16_t* C16) {
   const bool a_mn = ta != 0, b_mn = tb == 0;
   const int bk = elem == 0 ? 32 : 64, mn_chunk = elem == 0 ? 32 : 64;
   // Tile width: 256 unless the last 256-wide tile would be less than half used.
   const int rem = n % 256;
   const int bn = (n <= 128 || (rem > 0 && rem <= 128 && n < 1024)) ? 128 : 256;
-  CUtensorMap map_a, map_b, map_c;
+  CUtensorMap map_a, map_b, map_c, map_c16;
   bool ok = a_mn ? ws_operand_map(&map_a, elem, A, m, k, lda, bk, true) : ws_operand_map(&map_a, elem, A, k, m, lda, W_BM, false);
   ok = ok && (b_mn ? ws_operand_map(&map_b, elem, B, n, k, ldb, bk, true) : ws_operand_map(&map_b, elem, B, k, n, ldb, bn / 2, false));
   (void)mn_chunk;
@@ -422,16 +476,21 @@ int32_t gemm_ws(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, cons
     p.bias = bias; p.accumulate = acc;
     ok = ws_store_map(&map_c, C, n, m, ldc, 1, 0);
   }
+  // The bfloat16 copy rides in the epilogue of an unsplit product; after a split of k it is cast from the finished C.
+  p.c16 = (C16 && splits == 1 && gemm_ws_c16_ok(C16, ldc, acc)) ? 1 : 0;
+  if (p.c16) ok = ok && ws_store_map16(&map_c16, C16, n, m, ldc);
+  else map_c16 = map_c;   // never used, but the parameter must hold a valid map
   if (!ok) {
     if (workspace) pool_free(ctx, workspace);
     return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed for C (persistent product, m %d n %d ldc %lld)", m, n, ldc);
   }
   const int units = tiles * splits;
   int32_t st;
-  if (elem == 0) st = bn == 256 ? ws_launch<0, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, p, units) : ws_launch<0, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, p, units);
-  else st = bn == 256 ? ws_launch<1, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, p, units) : ws_launch<1, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, p, units);
+  if (elem == 0) st = bn == 256 ? ws_launch<0, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<0, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
+  else st = bn == 256 ? ws_launch<1, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<1, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
   if (st == OM_OK && splits > 1) splitk_reduce_launch(ctx, workspace, splits, (int64_t)m * n, n, ldc, bias, C, acc);
   if (workspace) pool_free(ctx, workspace);
+  if (st == OM_OK && C16 && !p.c16) st = cast_bf16_rows(ctx, C, C16, m, n, ldc);
   return st;
 }
 

@@ -2,6 +2,8 @@
 // every kernel streams its operands once with coalesced 128-byte warp accesses. Statistics that the reference
 // accumulates in double (BackwardNn.cs:170-307, Ops.Layers.cs:185-219) are accumulated in double here too, over a
 // partition that depends only on the shape and is combined in a fixed order.
+#include <cuda_bf16.h>
+
 #include "om_common.cuh"
 
 namespace om {
@@ -47,134 +49,6 @@ layernorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamm
   }
 }
 
-// ---- layer norm backward -------------------------------------------------------------------------------------------
-// dx: a warp per row, the row in registers (NC columns per lane), the two row sums in double
-// (LayerNormBackward, BackwardNn.cs:170-242 of the reference). CTA = 8 warps owns kLnRowsPerCta consecutive rows.
-constexpr int kLnRowsPerCta = 16;   // two rows per warp: 512 CTAs for 8192 rows keep enough loads in flight
-
-template <int NC>
-__global__ void __launch_bounds__(256)
-layernorm_bwd_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
-                     const float* __restrict__ mean, const float* __restrict__ inv, int32_t rows, int32_t cols,
-                     float* __restrict__ dx) {
-  pdl_enter();
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int r0 = blockIdx.x * kLnRowsPerCta;
-  const int r1 = min(rows, r0 + kLnRowsPerCta);
-  float gam[NC];
-#pragma unroll
-  for (int i = 0; i < NC; i++) {
-    int j = lane + 32 * i;
-    gam[i] = j < cols ? gamma[j] : 0.f;
-  }
-  for (int r = r0 + w; r < r1; r += 8) {
-    const float* xr = x + (int64_t)r * cols;
-    const float* gr = g + (int64_t)r * cols;
-    const float m = mean[r], s = inv[r];
-    float xh[NC], dh[NC];
-#pragma unroll
-    for (int i = 0; i < NC; i++) {
-      int j = lane + 32 * i;
-      const bool in = j < cols;
-      const float gv = in ? gr[j] : 0.f;
-      const float xv = in ? xr[j] : m;
-      xh[i] = (xv - m) * s;
-      dh[i] = gv * gam[i];
-    }
-    double sum1 = 0.0, sum2 = 0.0;
-#pragma unroll
-    for (int i = 0; i < NC; i++) {
-      if (lane + 32 * i < cols) {
-        sum1 += (double)dh[i];
-        sum2 += (double)(dh[i] * xh[i]);
-      }
-    }
-    sum1 = wsum_d(sum1);
-    sum2 = wsum_d(sum2);
-    const float m1 = (float)(sum1 / cols), m2 = (float)(sum2 / cols);
-    float* dr = dx + (int64_t)r * cols;
-#pragma unroll
-    for (int i = 0; i < NC; i++) {
-      int j = lane + 32 * i;
-      if (j < cols) dr[j] = s * ((dh[i] - m1) - (xh[i] * m2));
-    }
-  }
-}
-
-// Column partials of the layer-norm parameter gradients: dgamma[j] = sum_r g[r,j] * xhat[r,j], dbeta[j] = sum_r g[r,j].
-// CTA (bx, by) owns 32 columns and one chunk of 512 rows: 8 column groups x 32 row lanes, a thread holds four adjacent
-// columns (16-byte loads) and 16 rows, all loads of a row pair in flight together; lanes are combined in lane order.
-constexpr int kLnParamRows = 512;
-__global__ void __launch_bounds__(256)
-layernorm_param_partials_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ mean,
-                                const float* __restrict__ inv, int32_t rows, int32_t cols, double* __restrict__ part_gamma,
-                                double* __restrict__ part_beta) {
-  pdl_enter();
-  __shared__ double sg[32][33], sb[32][33];
-  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
-  const int col = blockIdx.x * 32 + tx * 4;
-  const int r0 = blockIdx.y * kLnParamRows, r1 = min(rows, r0 + kLnParamRows);
-  double ag[4] = {0.0, 0.0, 0.0, 0.0}, ab[4] = {0.0, 0.0, 0.0, 0.0};
-  const bool vec = (cols & 3) == 0 && col + 3 < cols;
-  for (int r = r0 + ty; r < r1; r += 64) {
-    const int r2 = r + 32;
-    float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), xa = ga, gb = ga, xb = ga;
-    float ma = 0.f, sa = 0.f, mb = 0.f, sbv = 0.f;
-    if (vec) {
-      ga = __ldg(reinterpret_cast<const float4*>(g + (int64_t)r * cols + col));
-      xa = __ldg(reinterpret_cast<const float4*>(x + (int64_t)r * cols + col));
-      ma = mean[r]; sa = inv[r];
-      if (r2 < r1) {
-        gb = __ldg(reinterpret_cast<const float4*>(g + (int64_t)r2 * cols + col));
-        xb = __ldg(reinterpret_cast<const float4*>(x + (int64_t)r2 * cols + col));
-        mb = mean[r2]; sbv = inv[r2];
-      }
-    } else {
-      float* gp[2] = {&ga.x, &gb.x};
-      float* xp[2] = {&xa.x, &xb.x};
-      for (int q = 0; q < 2; q++) {
-        const int rr = q ? r2 : r;
-        if (rr >= r1) continue;
-        for (int c = 0; c < 4; c++)
-          if (col + c < cols) {
-            gp[q][c] = g[(int64_t)rr * cols + col + c];
-            xp[q][c] = x[(int64_t)rr * cols + col + c];
-          }
-        if (q) { mb = mean[rr]; sbv = inv[rr]; } else { ma = mean[rr]; sa = inv[rr]; }
-      }
-    }
-    ag[0] += (double)(ga.x * ((xa.x - ma) * sa)); ab[0] += (double)ga.x;
-    ag[1] += (double)(ga.y * ((xa.y - ma) * sa)); ab[1] += (double)ga.y;
-    ag[2] += (double)(ga.z * ((xa.z - ma) * sa)); ab[2] += (double)ga.z;
-    ag[3] += (double)(ga.w * ((xa.w - ma) * sa)); ab[3] += (double)ga.w;
-    if (r2 < r1) {
-      ag[0] += (double)(gb.x * ((xb.x - mb) * sbv)); ab[0] += (double)gb.x;
-      ag[1] += (double)(gb.y * ((xb.y - mb) * sbv)); ab[1] += (double)gb.y;
-      ag[2] += (double)(gb.z * ((xb.z - mb) * sbv)); ab[2] += (double)gb.z;
-      ag[3] += (double)(gb.w * ((xb.w - mb) * sbv)); ab[3] += (double)gb.w;
-    }
-  }
-#pragma unroll
-  for (int c = 0; c < 4; c++) {
-    sg[ty][tx * 4 + c] = ag[c];
-    sb[ty][tx * 4 + c] = ab[c];
-  }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    const int c = blockIdx.x * 32 + threadIdx.x;
-    if (c < cols) {
-      double tg = 0.0, tb = 0.0;
-#pragma unroll
-      for (int l = 0; l < 32; l++) {
-        tg += sg[l][threadIdx.x];
-        tb += sb[l][threadIdx.x];
-      }
-      if (part_gamma) part_gamma[(int64_t)blockIdx.y * cols + c] = tg;
-      if (part_beta) part_beta[(int64_t)blockIdx.y * cols + c] = tb;
-    }
-  }
-}
-
 // out[j] = sum over chunks of partial[chunk, j] for one or two tables of double partials. A CTA owns 32 columns; 16
 // chunk lanes each add chunks lane, lane + 16, ... in increasing order, then the lane sums are added in lane order: a
 // fixed order, so the result does not depend on the launch.
@@ -212,6 +86,152 @@ column_partials_finish_kernel(const double* __restrict__ pa, const double* __res
 #pragma unroll
       for (int l = 0; l < 16; l++) t += sb[l][tx];
       ob[j] = accumulate ? ob[j] + (float)t : (float)t;
+    }
+  }
+}
+
+// ---- layer norm with the row in registers ---------------------------------------------------------------------------
+// Forward: one read of x per row (the kernel above reads it three times through L1), the same sums in the same order
+// (lane l owns columns l, l + 32, ...), and optionally the bfloat16 copy of y that the next product reads.
+__device__ __forceinline__ uint16_t bf16_bits(float v) {
+  __nv_bfloat16 h = __float2bfloat16_rn(v);
+  return *reinterpret_cast<uint16_t*>(&h);
+}
+
+template <int NC>
+__global__ void __launch_bounds__(256)
+layernorm_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta, int32_t rows,
+                         int32_t cols, float eps, float* __restrict__ y, uint16_t* __restrict__ y16, float* __restrict__ mean_out,
+                         float* __restrict__ inv_out) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), warps = (int64_t)gridDim.x * 8;
+  const float n = (float)cols;
+  float gam[NC], bet[NC];
+#pragma unroll
+  for (int i = 0; i < NC; i++) {
+    const int j = lane + 32 * i;
+    gam[i] = j < cols ? gamma[j] : 0.f;
+    bet[i] = j < cols ? beta[j] : 0.f;
+  }
+  for (int64_t r = warp; r < rows; r += warps) {
+    const float* xr = x + r * cols;
+    float v[NC];
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+      const int j = lane + 32 * i;
+      v[i] = j < cols ? xr[j] : 0.f;
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NC; i++)
+      if (lane + 32 * i < cols) s += v[i];
+    const float mean = wsum_f(s) / n;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NC; i++)
+      if (lane + 32 * i < cols) {
+        const float d = v[i] - mean;
+        q += d * d;
+      }
+    const float inv = 1.0f / sqrtf((wsum_f(q) / n) + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[r] = mean;
+      if (inv_out) inv_out[r] = inv;
+    }
+    float* yr = y + r * cols;
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+      const int j = lane + 32 * i;
+      if (j < cols) {
+        const float o = (((v[i] - mean) * inv) * gam[i]) + bet[i];
+        yr[j] = o;
+        if (y16) y16[r * cols + j] = bf16_bits(o);
+      }
+    }
+  }
+}
+
+// Backward in one pass over (g, x): a CTA owns kLnFusedRows consecutive rows, a warp takes every eighth of them with the
+// row in registers, writes dx (and optionally its bfloat16 copy) and keeps, per lane and column, the sums of g * xhat and
+// of g over its eight rows (fp32: eight terms). The eight warps' sums are added in warp order in double through shared
+// memory and written as the CTA's row of two double partial tables; column_partials_finish_kernel adds the CTAs' rows in
+// CTA order. The partition depends on the shape only, so the sums are the same from run to run.
+constexpr int kLnFusedRows = 64;
+template <int NC>
+__global__ void __launch_bounds__(256, 2)
+layernorm_bwd_fused_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
+                           const float* __restrict__ mean, const float* __restrict__ inv, int32_t rows, int32_t cols,
+                           float* __restrict__ dx, uint16_t* __restrict__ dx16, double* __restrict__ part_gamma,
+                           double* __restrict__ part_beta) {
+  pdl_enter();
+  extern __shared__ double ln_smem[];            // [8][cols]
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int r0 = blockIdx.x * kLnFusedRows;
+  const int r1 = min(rows, r0 + kLnFusedRows);
+  float ag[NC], ab[NC];
+#pragma unroll
+  for (int i = 0; i < NC; i++) {
+    ag[i] = 0.f;
+    ab[i] = 0.f;
+  }
+  for (int r = r0 + w; r < r1; r += 8) {
+    const float* xr = x + (int64_t)r * cols;
+    const float* gr = g + (int64_t)r * cols;
+    const float m = mean[r], s = inv[r];
+    float xh[NC], dh[NC];
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+      const int j = lane + 32 * i;
+      const bool in = j < cols;
+      const float gv = in ? gr[j] : 0.f;
+      const float xv = in ? xr[j] : m;
+      xh[i] = (xv - m) * s;
+      dh[i] = gv * (in ? __ldg(gamma + j) : 0.f);   // gamma stays in L1: keeping it in registers would not fit two CTAs per SM
+      ag[i] += gv * xh[i];
+      ab[i] += gv;
+    }
+    double sum1 = 0.0, sum2 = 0.0;
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+      if (lane + 32 * i < cols) {
+        sum1 += (double)dh[i];
+        sum2 += (double)(dh[i] * xh[i]);
+      }
+    }
+    sum1 = wsum_d(sum1);
+    sum2 = wsum_d(sum2);
+    const float m1 = (float)(sum1 / cols), m2 = (float)(sum2 / cols);
+    if (dx) {
+      float* dr = dx + (int64_t)r * cols;
+#pragma unroll
+      for (int i = 0; i < NC; i++) {
+        const int j = lane + 32 * i;
+        if (j < cols) {
+          const float o = s * ((dh[i] - m1) - (xh[i] * m2));
+          dr[j] = o;
+          if (dx16) dx16[(int64_t)r * cols + j] = bf16_bits(o);
+        }
+      }
+    }
+  }
+  // The CTA's column sums: warps in order, one table after the other through the same shared memory.
+#pragma unroll 1
+  for (int table = 0; table < 2; table++) {
+    double* out = table == 0 ? part_gamma : part_beta;
+    if (!out) continue;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+      const int j = lane + 32 * i;
+      if (j < cols) ln_smem[w * cols + j] = (double)(table == 0 ? ag[i] : ab[i]);
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < cols; j += 256) {
+      double t = 0.0;
+#pragma unroll
+      for (int k = 0; k < 8; k++) t += ln_smem[k * cols + j];
+      out[(int64_t)blockIdx.x * cols + j] = t;
     }
   }
 }
@@ -385,52 +405,80 @@ using namespace om;
 
 extern "C" {
 
-int32_t om_layernorm_fwd(om_ctx* ctx, const float* x, const float* gamma, const float* beta, int32_t rows, int32_t cols,
-                         float eps, float* y, float* mean, float* inv) {
+int32_t om_layernorm_fwd_b16(om_ctx* ctx, const float* x, const float* gamma, const float* beta, int32_t rows, int32_t cols,
+                             float eps, float* y, uint16_t* y16, float* mean, float* inv) {
   OM_CHECK_CTX(ctx);
   if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "om_layernorm_fwd: [%d,%d]", rows, cols);
   if (rows == 0 || cols == 0) return OM_OK;
-  ProfileScope prof(ctx, "om_layernorm_fwd", 0, 8.0 * rows * (double)cols);
+  ProfileScope prof(ctx, "om_layernorm_fwd", 0, (y16 ? 10.0 : 8.0) * rows * (double)cols);
   int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 8);
-  launch_chained(ctx, layernorm_fwd_kernel, grid, 256, 0, x, gamma, beta, rows, cols, eps, y, mean, inv);
+  const int nc = (int)ceil_div(cols, 32);
+  if (nc <= 32) {
+#define OM_LN_FWD(NC) launch_chained(ctx, layernorm_fwd_reg_kernel<NC>, grid, 256, 0, x, gamma, beta, rows, cols, eps, y, y16, mean, inv)
+    if (nc <= 4) OM_LN_FWD(4);
+    else if (nc <= 8) OM_LN_FWD(8);
+    else if (nc <= 12) OM_LN_FWD(12);
+    else if (nc <= 16) OM_LN_FWD(16);
+    else if (nc <= 24) OM_LN_FWD(24);
+    else OM_LN_FWD(32);
+#undef OM_LN_FWD
+  } else {
+    if (y16) return fail(ctx, OM_ERR_UNSUPPORTED, "om_layernorm_fwd_b16: rows wider than 1024 (%d) have no fused bfloat16 copy", cols);
+    launch_chained(ctx, layernorm_fwd_kernel, grid, 256, 0, x, gamma, beta, rows, cols, eps, y, mean, inv);
+  }
   OM_LAUNCH_CHECK(ctx, "om_layernorm_fwd");
+  return OM_OK;
+}
+
+int32_t om_layernorm_fwd(om_ctx* ctx, const float* x, const float* gamma, const float* beta, int32_t rows, int32_t cols,
+                         float eps, float* y, float* mean, float* inv) {
+  return om_layernorm_fwd_b16(ctx, x, gamma, beta, rows, cols, eps, y, nullptr, mean, inv);
+}
+
+int32_t om_layernorm_bwd_b16(om_ctx* ctx, const float* g, const float* x, const float* gamma, const float* mean,
+                             const float* inv, int32_t rows, int32_t cols, float* dx, uint16_t* dx16, float* dgamma, float* dbeta,
+                             int32_t accumulate_params) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "om_layernorm_bwd: [%d,%d]", rows, cols);
+  if (cols == 0) return OM_OK;
+  if (cols > 1024) return fail(ctx, OM_ERR_UNSUPPORTED, "om_layernorm_bwd: rows wider than 1024 (%d) are not implemented", cols);
+  if (dx16 && !dx) return fail(ctx, OM_ERR_ARG, "om_layernorm_bwd_b16: the bfloat16 copy needs dx");
+  ProfileScope prof(ctx, "om_layernorm_bwd", 0, (dx16 ? 14.0 : 12.0) * rows * (double)cols);
+  const int nc = (int)ceil_div(cols, 32);
+  // One pass: dx and the CTAs' column partials together; the partials are then added in CTA order.
+  const int used = (int)ceil_div(rows > 0 ? rows : 1, kLnFusedRows);
+  double *pg = nullptr, *pb = nullptr;
+  if (dgamma) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)used * cols, false, (void**)&pg));
+  if (dbeta) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)used * cols, false, (void**)&pb));
+  const size_t smem = sizeof(double) * 8 * (size_t)cols;
+#define OM_LN_BWD(NC)                                                                                                            \
+  do {                                                                                                                           \
+    static bool attr_set = false;                                                                                                \
+    if (!attr_set) {                                                                                                             \
+      OM_CUDA(ctx, cudaFuncSetAttribute(layernorm_bwd_fused_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 1024 * 8)); \
+      attr_set = true;                                                                                                           \
+    }                                                                                                                            \
+    launch_chained(ctx, layernorm_bwd_fused_kernel<NC>, used, 256, smem, g, x, gamma, mean, inv, rows, cols, dx, dx16, pg, pb); \
+  } while (0)
+  if (nc <= 4) OM_LN_BWD(4);
+  else if (nc <= 8) OM_LN_BWD(8);
+  else if (nc <= 12) OM_LN_BWD(12);
+  else if (nc <= 16) OM_LN_BWD(16);
+  else if (nc <= 24) OM_LN_BWD(24);
+  else OM_LN_BWD(32);
+#undef OM_LN_BWD
+  if (dgamma || dbeta)
+    launch_chained(ctx, column_partials_finish_kernel, (unsigned)ceil_div(cols, 32), 512, 0, pg, pb, used, cols, dgamma, dbeta, accumulate_params);
+  if (pg) pool_free(ctx, pg);
+  if (pb) pool_free(ctx, pb);
+  OM_LAUNCH_CHECK(ctx, "om_layernorm_bwd");
   return OM_OK;
 }
 
 int32_t om_layernorm_bwd(om_ctx* ctx, const float* g, const float* x, const float* gamma, const float* mean,
                          const float* inv, int32_t rows, int32_t cols, float* dx, float* dgamma, float* dbeta,
                          int32_t accumulate_params) {
-  OM_CHECK_CTX(ctx);
-  if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "om_layernorm_bwd: [%d,%d]", rows, cols);
-  if (cols == 0) return OM_OK;
-  if (cols > 1024) return fail(ctx, OM_ERR_UNSUPPORTED, "om_layernorm_bwd: rows wider than 1024 (%d) are not implemented", cols);
-  ProfileScope prof(ctx, "om_layernorm_bwd", 0, 12.0 * rows * (double)cols);
-  // dx: a warp per row, the row in registers. The parameter gradients are column sums and run as their own pass over
-  // (g, x) with the column-sum blocking: for wide rows that beats carrying per-lane column partials through the row loop.
-  const int row_ctas = (int)ceil_div(rows > 0 ? rows : 1, kLnRowsPerCta);
-  int nc = (int)ceil_div(cols, 32);
-  if (dx && rows > 0) {
-#define OM_LN_BWD(NC) launch_chained(ctx, layernorm_bwd_kernel<NC>, row_ctas, 256, 0, g, x, gamma, mean, inv, rows, cols, dx)
-    if (nc <= 4) OM_LN_BWD(4);
-    else if (nc <= 8) OM_LN_BWD(8);
-    else if (nc <= 12) OM_LN_BWD(12);
-    else if (nc <= 16) OM_LN_BWD(16);
-    else if (nc <= 24) OM_LN_BWD(24);
-    else OM_LN_BWD(32);
-#undef OM_LN_BWD
-  }
-  double *pg = nullptr, *pb = nullptr;
-  if (dgamma || dbeta) {
-    const int chunks = (int)ceil_div(rows > 0 ? rows : 1, kLnParamRows);
-    if (dgamma) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&pg));
-    if (dbeta) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&pb));
-    launch_chained(ctx, layernorm_param_partials_kernel, dim3((unsigned)ceil_div(cols, 32), (unsigned)chunks), 256, 0, g, x, mean, inv, rows, cols, pg, pb);
-    launch_chained(ctx, column_partials_finish_kernel, (unsigned)ceil_div(cols, 32), 512, 0, pg, pb, chunks, cols, dgamma, dbeta, accumulate_params);
-  }
-  if (pg) pool_free(ctx, pg);
-  if (pb) pool_free(ctx, pb);
-  OM_LAUNCH_CHECK(ctx, "om_layernorm_bwd");
-  return OM_OK;
+  return om_layernorm_bwd_b16(ctx, g, x, gamma, mean, inv, rows, cols, dx, nullptr, dgamma, dbeta, accumulate_params);
 }
 
 static int bn_slices(int n) { return n < 16 ? (n > 0 ? n : 1) : 16; }

@@ -228,6 +228,17 @@ void Engine::LeafWritten(BackwardRecord& rec, int i) {
   leaf_arrived(meta);
 }
 
+bool Engine::PendingTarget(BackwardRecord& rec, int i, Tensor* pending) {
+  AutogradMeta* meta = rec.Inputs[i].get();
+  if (!meta || !meta->GradFn) return false;
+  const Tensor& p = meta->GradFn->PendingGrad;
+  if (p.IsEmpty() || !p.IsContiguous() || p.GetDType() != DType::F32 || p.GetShape() != rec.InputShapes[i]) return false;
+  *pending = p;
+  return true;
+}
+
+void Engine::PendingWritten(BackwardRecord& rec, int i) { rec.Inputs[i]->GradFn->PendingGrad.MarkModified(); }
+
 void Engine::AddInto(const Tensor& dst, const Tensor& src) {
   if (dst.GetShape() != src.GetShape())
     throw TensorShapeException("Gradient shape " + src.GetShape().ToString() + " does not match " + dst.GetShape().ToString() + ".");

@@ -36,7 +36,13 @@ static Tensor SumTo(const Tensor& g, const Shape& target, bool* same) {
 static Tensor UnaryGrad(om_unary_op op, const Tensor& g, const Tensor& saved) {
   Tensor gc = g.Contiguous();
   Tensor dx = Tensor::Create(DType::F32, saved.GetShape());
-  Check(om_unary_bwd(C(), op, gc.Data(), saved.Data(), dx.Data(), dx.Length()));
+  // The gradient of the activation between two Linear layers is the first layer's output gradient: a product operand.
+  if ((op == OM_GELU_ERF || op == OM_GELU_TANH) && Bf16Products()) {
+    Check(om_unary_bwd_b16(C(), op, gc.Data(), saved.Data(), dx.Data(), dx.Bf16ForWrite(), dx.Length()));
+    dx.Bf16Written();
+  } else {
+    Check(om_unary_bwd(C(), op, gc.Data(), saved.Data(), dx.Data(), dx.Length()));
+  }
   return dx;
 }
 
@@ -70,16 +76,20 @@ static void EmitSummed(Engine& e, BackwardRecord& r, const Tensor& g, bool negat
 // and the three operands fit (g: the gradient with pitch ldg, possibly a column slice `col` of a wider gradient; x: the
 // saved input; w: the saved weights, `col` rows in). The bias gradient always sums the fp32 gradient.
 static void LinearBwdCall(const Tensor& g, int col, int ldg, const Tensor& x, const Tensor& w, int rows, int inF, int outF, float* dx, float* dw,
-                          float* db, bool acc) {
+                          float* db, int acc, const Tensor* dx_tensor = nullptr) {
   if (!dx && !dw && !db) return;
   const float* gp = g.Data() + col;
   auto aligned16 = [](const float* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (Bf16Products() && rows > 0 && (dx || dw) && Bf16Operand(g, ldg) && col % 8 == 0 && Bf16Operand(x, inF) && Bf16Operand(w, inF) && (inF & 3) == 0 &&
       aligned16(dx) && aligned16(dw)) {
-    Check(om_linear_bwd_bf16(C(), g.Bf16() + col, gp, ldg, x.Bf16(), w.Bf16() + (size_t)col * inF, rows, inF, outF, dx, dw, db, acc ? 1 : 0));
+    // dx_tensor: the caller wants the bfloat16 copy of the input gradient from the product's epilogue (its consumer reads
+    // bfloat16: the attention backward).
+    uint16_t* dx16 = (dx && dx_tensor && inF % 8 == 0 && !(acc & 2)) ? dx_tensor->Bf16ForWrite() : nullptr;
+    Check(om_linear_bwd_bf16_b16(C(), g.Bf16() + col, gp, ldg, x.Bf16(), w.Bf16() + (size_t)col * inF, rows, inF, outF, dx, dx16, dw, db, acc));
+    if (dx16) dx_tensor->Bf16Written();
     return;
   }
-  Check(om_linear_bwd_ld(C(), gp, ldg, x.Data(), w.Data() + (size_t)col * inF, rows, inF, outF, dx, dw, db, acc ? 1 : 0));
+  Check(om_linear_bwd_ld(C(), gp, ldg, x.Data(), w.Data() + (size_t)col * inF, rows, inF, outF, dx, dw, db, acc));
 }
 
 // The record of Ops::LinearPacked (Ints = {rows, inF, outF, parts, hasBias}; inputs x, weights..., biases...): the input
@@ -92,7 +102,12 @@ static void LinearPackedBackward(BackwardRecord& r, const Tensor& g) {
   Tensor gc = g.Contiguous();
   const Tensor& wpacked = r.Saved(1);
   Tensor dx;
-  if (r.NeedsInputGrad(0)) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+  bool dx_into_pending = false;   // the input already has the residual branch's gradient: the product adds into it
+  if (r.NeedsInputGrad(0)) {
+    dx_into_pending = Engine::PendingTarget(r, 0, &dx);
+    if (!dx_into_pending) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+  }
+  const int accx = dx_into_pending ? 2 : 0;
   std::vector<float*> wp(parts, nullptr), bp(parts, nullptr);
   std::vector<bool> wacc(parts, false), bacc(parts, false), wleaf(parts, false), bleaf(parts, false);
   std::vector<Tensor> wtmp(parts), btmp(parts);
@@ -129,17 +144,17 @@ static void LinearPackedBackward(BackwardRecord& r, const Tensor& g) {
   // Input gradient (+ the packed weight / bias gradients when they can ride along).
   if (!dx.IsEmpty() || wp_one || bp_one) {
     if (wp_one && bp_one && wacc[0] != bacc[0]) {
-      LinearBwdCall(gc, 0, outF, x, wpacked, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), wp[0], nullptr, wacc[0]);
-      LinearBwdCall(gc, 0, outF, x, wpacked, rows, inF, outF, nullptr, nullptr, bp[0], bacc[0]);
+      LinearBwdCall(gc, 0, outF, x, wpacked, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), wp[0], nullptr, (wacc[0] ? 1 : 0) | accx);
+      LinearBwdCall(gc, 0, outF, x, wpacked, rows, inF, outF, nullptr, nullptr, bp[0], bacc[0] ? 1 : 0);
     } else {
       LinearBwdCall(gc, 0, outF, x, wpacked, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), wp_one ? wp[0] : nullptr,
-                    bp_one ? bp[0] : nullptr, wp_one ? wacc[0] : (bp_one && bacc[0]));
+                    bp_one ? bp[0] : nullptr, ((wp_one ? wacc[0] : (bp_one && bacc[0])) ? 1 : 0) | accx);
     }
   }
   int col = 0;
   for (int i = 0; i < parts; i++) {
-    if (!wp_one && wp[i]) LinearBwdCall(gc, col, outF, x, wpacked, rows, inF, outs[i], nullptr, wp[i], nullptr, wacc[i]);
-    if (hasBias && !bp_one && bp[i]) LinearBwdCall(gc, col, outF, x, wpacked, rows, inF, outs[i], nullptr, nullptr, bp[i], bacc[i]);
+    if (!wp_one && wp[i]) LinearBwdCall(gc, col, outF, x, wpacked, rows, inF, outs[i], nullptr, wp[i], nullptr, wacc[i] ? 1 : 0);
+    if (hasBias && !bp_one && bp[i]) LinearBwdCall(gc, col, outF, x, wpacked, rows, inF, outs[i], nullptr, nullptr, bp[i], bacc[i] ? 1 : 0);
     col += outs[i];
   }
   // Emission order as for the single layer, part by part: bias, (input once), weight.
@@ -147,7 +162,8 @@ static void LinearPackedBackward(BackwardRecord& r, const Tensor& g) {
     if (hasBias && r.NeedsInputGrad(1 + parts + i)) {
       if (bleaf[i]) Engine::LeafWritten(r, 1 + parts + i); else Engine::Emit(r, 1 + parts + i, btmp[i], true);
     }
-  if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
+  if (dx_into_pending) Engine::PendingWritten(r, 0);
+  else if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
   for (int i = 0; i < parts; i++)
     if (r.NeedsInputGrad(1 + i)) {
       if (wleaf[i]) Engine::LeafWritten(r, 1 + i); else Engine::Emit(r, 1 + i, wtmp[i], true);
@@ -170,7 +186,13 @@ static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
   }
   bool hasBias = r.InputCount() == 3;
   Tensor dx;
-  if (r.NeedsInputGrad(0)) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+  // When the input already has a gradient from another branch (the residual connection), the product adds into it.
+  bool dx_into_pending = false;
+  if (r.NeedsInputGrad(0)) {
+    dx_into_pending = Engine::PendingTarget(r, 0, &dx);
+    if (!dx_into_pending) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+  }
+  const int accx = dx_into_pending ? 2 : 0;
   // Weight and bias gradients go straight into the leaf's gradient buffer when there is one.
   float *dwp = nullptr, *dbp = nullptr;
   bool accw = false, accb = false, wleaf = false, bleaf = false;
@@ -189,17 +211,21 @@ static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
       dbp = db.Data();
     }
   }
+  // The gradient of an attention output is read as bfloat16 by the attention backward: ask the product for the copy.
+  const bool to_attention = !dx.IsEmpty() && r.Inputs[0] && r.Inputs[0]->GradFn && r.Inputs[0]->GradFn->Op == OpKind::Attention;
+  const Tensor* dxt = to_attention ? &dx : nullptr;
   if (accw == accb || !dwp || !dbp) {
-    LinearBwdCall(gc, 0, ldg, x, w, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, dbp, dwp ? accw : accb);
+    LinearBwdCall(gc, 0, ldg, x, w, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, dbp, ((dwp ? accw : accb) ? 1 : 0) | accx, dxt);
   } else {
-    LinearBwdCall(gc, 0, ldg, x, w, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, nullptr, accw);
-    LinearBwdCall(gc, 0, ldg, x, w, rows, inF, outF, nullptr, nullptr, dbp, accb);
+    LinearBwdCall(gc, 0, ldg, x, w, rows, inF, outF, dx.IsEmpty() ? nullptr : dx.Data(), dwp, nullptr, (accw ? 1 : 0) | accx, dxt);
+    LinearBwdCall(gc, 0, ldg, x, w, rows, inF, outF, nullptr, nullptr, dbp, accb ? 1 : 0);
   }
   // Emission order of the reference's record chain: bias (Add record), then input and weight (MatMul record).
   if (hasBias && r.NeedsInputGrad(2)) {
     if (bleaf) Engine::LeafWritten(r, 2); else Engine::Emit(r, 2, db, true);
   }
-  if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
+  if (dx_into_pending) Engine::PendingWritten(r, 0);
+  else if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
   if (r.NeedsInputGrad(1)) {
     if (wleaf) Engine::LeafWritten(r, 1); else Engine::Emit(r, 1, dw, true);
   }
@@ -307,8 +333,13 @@ static void LayerNormBackward(BackwardRecord& r, const Tensor& g) {
   bool acc, gleaf, bleaf;
   Tensor tg, tb;
   NormParamGrads(r, &dg, &db, &acc, &tg, &tb, &gleaf, &bleaf);
-  Check(om_layernorm_bwd(C(), gc.Data(), x.Data(), gamma.Data(), mean.Data(), inv.Data(), rows, cols,
-                         dx.IsEmpty() ? nullptr : dx.Data(), dg, db, acc));
+  if (Bf16Products() && !dx.IsEmpty()) {
+    Check(om_layernorm_bwd_b16(C(), gc.Data(), x.Data(), gamma.Data(), mean.Data(), inv.Data(), rows, cols, dx.Data(), dx.Bf16ForWrite(), dg, db, acc));
+    dx.Bf16Written();
+  } else {
+    Check(om_layernorm_bwd(C(), gc.Data(), x.Data(), gamma.Data(), mean.Data(), inv.Data(), rows, cols,
+                           dx.IsEmpty() ? nullptr : dx.Data(), dg, db, acc));
+  }
   if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
   EmitNormParams(r, tg, tb, gleaf, bleaf);
 }
@@ -382,6 +413,20 @@ static void AttentionPackedBackward(BackwardRecord& r, const Tensor& g) {
   Tensor dqkv = Tensor::Create(DType::F32, qkv.GetShape());
   om_head_strides ps{(int64_t)l * 3 * width, (int64_t)d, (int64_t)3 * width}, gs{(int64_t)l * width, (int64_t)d, (int64_t)width};
   const Tensor& out = r.Saved(5);
+  if (Bf16Products() && !out.IsEmpty() && !r.Saved(4).IsEmpty() && l > 128 && om_attention_bwd_bf16_supported(C(), b, heads, l, l, d) &&
+      Bf16Operand(qkv, 3 * width) && Bf16Operand(gc, width) && width % 8 == 0) {
+    // Several tiles under bfloat16 products: the fully fused kernel on the bfloat16 copies of the packed projections and of
+    // the gradient; it also writes the bfloat16 copy of dqkv, the next product's operand.
+    const uint16_t* p16 = qkv.Bf16();
+    const uint16_t* g16 = gc.Bf16();
+    uint16_t* d16 = dqkv.Bf16ForWrite();
+    Check(om_attention_bwd_bf16(C(), g16, gc.Data(), &gs, p16, &ps, p16 + width, &ps, p16 + 2 * width, &ps, out.Data(), &gs,
+                                mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0], r.Saved(4).Data(), b, heads, l, l, d, (float)r.Floats[0], dqkv.Data(), d16,
+                                &ps, dqkv.Data() + width, d16 + width, &ps, dqkv.Data() + 2 * width, d16 + 2 * width, &ps));
+    dqkv.Bf16Written();
+    Engine::Emit(r, 0, dqkv, true);
+    return;
+  }
   Check(om_attention_bwd_strided_out(C(), gc.Data(), &gs, qkv.Data(), &ps, qkv.Data() + width, &ps, qkv.Data() + 2 * width, &ps,
                                      out.IsEmpty() ? nullptr : out.Data(), &gs, mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0],
                                      r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, heads, l, l, d, (float)r.Floats[0], dqkv.Data(), &ps,

@@ -252,6 +252,10 @@ class Engine {
   // (accumulate) or overwrite it; the caller then calls LeafWritten instead of Emit.
   static bool LeafTarget(BackwardRecord& rec, int i, float** ptr, bool* accumulate);
   static void LeafWritten(BackwardRecord& rec, int i);
+  // If input i's producer already holds a gradient from another branch (contiguous, of the input's shape), returns it: the
+  // backward kernel then adds into it (what Emit would do with AddInto in a pass of its own) and calls PendingWritten.
+  static bool PendingTarget(BackwardRecord& rec, int i, Tensor* pending);
+  static void PendingWritten(BackwardRecord& rec, int i);
   static void AddInto(const Tensor& dst, const Tensor& src);
 };
 

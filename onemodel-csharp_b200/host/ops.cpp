@@ -79,7 +79,14 @@ static Tensor Unary(OpKind kind, om_unary_op op, const Tensor& x, int saved, std
   RequireFloat32(x);
   Tensor xc = x.Contiguous();
   Tensor r = NewOut(x.GetShape());
-  Check(om_unary(C(), op, xc.Data(), r.Data(), r.Length()));
+  // The activation between two Linear layers: its result is a product operand, so under bfloat16 products the copy is
+  // written here instead of by a cast pass.
+  if (kind == OpKind::Gelu && Bf16Products()) {
+    Check(om_unary_b16(C(), op, xc.Data(), r.Data(), r.Bf16ForWrite(), r.Length()));
+    r.Bf16Written();
+  } else {
+    Check(om_unary(C(), op, xc.Data(), r.Data(), r.Length()));
+  }
   if (!Ops::Recording({&x})) return r;
   auto rec = BackwardRecord::Create(kind, saved ? 1 : 0, {&x});
   if (saved == 1) rec->Save(0, r.Detach());
@@ -204,8 +211,14 @@ Tensor Ops::LayerNorm(const Tensor& x, const Tensor& gamma, const Tensor& beta, 
     mean = Tensor::Create(DType::F32, Shape{rows});
     inv = Tensor::Create(DType::F32, Shape{rows});
   }
-  Check(om_layernorm_fwd(C(), xc.Data(), gc.Data(), bc.Data(), rows, cols, eps, r.Data(), rec ? mean.Data() : nullptr,
-                         rec ? inv.Data() : nullptr));
+  if (Bf16Products() && cols <= 1024) {
+    Check(om_layernorm_fwd_b16(C(), xc.Data(), gc.Data(), bc.Data(), rows, cols, eps, r.Data(), r.Bf16ForWrite(), rec ? mean.Data() : nullptr,
+                               rec ? inv.Data() : nullptr));
+    r.Bf16Written();
+  } else {
+    Check(om_layernorm_fwd(C(), xc.Data(), gc.Data(), bc.Data(), rows, cols, eps, r.Data(), rec ? mean.Data() : nullptr,
+                           rec ? inv.Data() : nullptr));
+  }
   if (!rec) return r;
   auto br = BackwardRecord::Create(OpKind::LayerNorm, 4, {&x, &gamma, &beta});
   br->Save(0, xc.Detach());
@@ -453,9 +466,13 @@ Tensor Ops::LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, co
   Shape os = x.GetShape();
   os.d[os.rank - 1] = outF;
   Tensor r = NewOut(os);
-  if (Bf16Products() && rows > 0 && Bf16Operand(xc, inF) && Bf16Operand(weights[0], inF) && (outF & 3) == 0)
-    Check(om_linear_fwd_bf16(C(), xc.Bf16(), weights[0].Bf16(), biases.empty() ? nullptr : biases[0].Data(), rows, inF, outF, r.Data(), outF));
-  else
+  if (Bf16Products() && rows > 0 && Bf16Operand(xc, inF) && Bf16Operand(weights[0], inF) && (outF & 3) == 0) {
+    // The packed q | k | v projections feed the attention kernels, which read them as bfloat16 under this tier: the
+    // product's epilogue writes that copy along.
+    uint16_t* y16 = outF % 8 == 0 ? r.Bf16ForWrite() : nullptr;
+    Check(om_linear_fwd_bf16_b16(C(), xc.Bf16(), weights[0].Bf16(), biases.empty() ? nullptr : biases[0].Data(), rows, inF, outF, r.Data(), y16, outF));
+    if (y16) r.Bf16Written();
+  } else
     Check(om_linear_fwd_ld(C(), xc.Data(), weights[0].Data(), biases.empty() ? nullptr : biases[0].Data(), rows, inF, outF, r.Data(), outF));
   std::vector<Tensor> ins = {x};
   for (auto& w : weights) ins.push_back(w);

@@ -278,6 +278,38 @@ def attention_bwd(g, q, k, v, mask=None, scale=None):
     return dq, dk, dv
 
 
+def attention_bwd_bf16(g, q, k, v, mask=None, scale=None):
+    """AttentionBackward (BackwardNn.cs:636-701) with the operands of its five products rounded to bfloat16 (nearest even) and
+    everything else in fp32: S = Q K^T and dP = dO V^T from rounded q, k, v, dO; P = softmax(scale S + mask) and the row dots
+    rowsum(dO o O) in fp32 (O from the fp32 forward); dS = P (dP - dot) scale; dV = P^T dO, dK = dS^T Q, dQ = dS K with P and
+    dS rounded. The model of the product's bfloat16 tier; plain numpy, for small cases."""
+    g, q, k, v = _f(g), _f(q), _f(k), _f(v)
+    b, h, lq, d = q.shape
+    lk = k.shape[2]
+    scale = np.float32(1.0) / np.sqrt(np.float32(d)) if scale is None else np.float32(scale)
+    out = attention_fwd(q, k, v, mask, scale)
+    gr, qr, kr, vr = round_bf16(g), round_bf16(q), round_bf16(k), round_bf16(v)
+    dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    for bi in range(b):
+        mb = None if mask is None else (mask if np.ndim(mask) == 2 else mask[bi])
+        for hi in range(h):
+            s = (qr[bi, hi] @ kr[bi, hi].T) * scale
+            if mb is not None:
+                s = s + _f(mb)
+            s64 = s.astype(np.float64)
+            mx = s64.max(axis=1, keepdims=True)
+            e = np.exp(s64 - mx)
+            p = (e / e.sum(axis=1, keepdims=True)).astype(np.float32)
+            dot = (g[bi, hi].astype(np.float64) * out[bi, hi]).sum(axis=1, keepdims=True).astype(np.float32)
+            dp = gr[bi, hi] @ vr[bi, hi].T
+            ds = (p * (dp - dot)) * scale
+            pr, dsr = round_bf16(p), round_bf16(ds)
+            dv[bi, hi] = pr.T @ gr[bi, hi]
+            dk[bi, hi] = dsr.T @ qr[bi, hi]
+            dq[bi, hi] = dsr @ kr[bi, hi]
+    return dq, dk, dv
+
+
 def adam_step(p, g, m, v, vmax, t, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, decoupled=False, amsgrad=False):
     """In place on p, m, v (and vmax). t is the 1-based step."""
     lib().orc_adam_step(_p(p), _p(_f(g)), _p(m), _p(v), _p(vmax), C.c_int64(p.size), C.c_float(lr), C.c_float(beta1),

@@ -324,7 +324,12 @@ def attention(q, k, v, mask=None, scale=None):
     qc, kc, vc = (np.ascontiguousarray(t.v) for t in (q, k, v))
 
     def bw(r, g):
-        dq, dk, dv = K.attention_bwd(g, *r.saved, mask=mask, scale=scale)
+        # Under 'bf16' the backward of sequences of several tiles runs with bfloat16 product operands (the forward and the
+        # one-tile backward keep the TF32 kernels, which the fp32 restatement stands for).
+        if GEMM_MODE == "bf16" and qc.shape[2] > 128 and qc.shape[3] == 64:
+            dq, dk, dv = K.attention_bwd_bf16(g, *r.saved, mask=mask, scale=scale)
+        else:
+            dq, dk, dv = K.attention_bwd(g, *r.saved, mask=mask, scale=scale)
         return [(0, dq, "own"), (1, dk, "own"), (2, dv, "own")]
 
     return _attach(K.attention_fwd(qc, kc, vc, mask, scale), Record("attention", [q, k, v], saved=(qc, kc, vc), backward=bw), [q, k, v])

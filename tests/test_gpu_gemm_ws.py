@@ -135,3 +135,26 @@ def test_tf32_matmul_on_the_persistent_kernel(ctx, oracle_built, ta, tb, m, n, k
         assert np.array_equal(got, run_tf32(ctx, ta, tb, m, n, k, a, b))
     finally:
         ctx.set_flags(0)
+
+
+@pytest.mark.parametrize("rows,inf,outf", [(2048, 768, 2304), (300, 136, 264), (4096, 768, 768), (512, 16384, 768)])
+def test_bf16_copy_of_the_result_from_the_product_epilogue(ctx, oracle_built, rows, inf, outf):
+    """om_linear_fwd_bf16_b16 / om_linear_bwd_bf16_b16: the bfloat16 copy of y and of dx written by the product's epilogue
+    equals the fp32 result rounded to nearest even, bit for bit (including the case where k is split and the copy is made
+    from the finished result)."""
+    K = oracle_built
+    r = np.random.default_rng(rows + outf)
+    x, w = r.standard_normal((rows, inf)).astype(np.float32), (r.standard_normal((outf, inf)) * 0.05).astype(np.float32)
+    bias, g = r.standard_normal(outf).astype(np.float32), r.standard_normal((rows, outf)).astype(np.float32)
+    X16, W16, G16, Bv, G = to_bf16(ctx, x), to_bf16(ctx, w), to_bf16(ctx, g), ctx.to_device(bias), ctx.to_device(g)
+    Y, Y16 = ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16)
+    DX, DX16 = ctx.empty((rows, inf)), ctx.empty((rows, inf), np.uint16)
+    ctx.call("om_linear_fwd_bf16_b16", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), Y.ptr, Y16.ptr, i32(outf))
+    ctx.call("om_linear_bwd_bf16_b16", ctx.handle, G16.ptr, G.ptr, i32(outf), X16.ptr, W16.ptr, i32(rows), i32(inf), i32(outf), DX.ptr, DX16.ptr,
+             None, None, i32(0))
+    ctx.sync()
+    y, dx = Y.numpy(), DX.numpy()
+    assert scaled_diff(y, K.gemm(x, w, tb=True, mode="bf16") + bias) <= 2e-5
+    assert scaled_diff(dx, K.gemm(g, w, mode="bf16")) <= 2e-5
+    assert np.array_equal(Y16.numpy(), (K.round_bf16(y).view(np.uint32) >> 16).astype(np.uint16))
+    assert np.array_equal(DX16.numpy(), (K.round_bf16(dx).view(np.uint32) >> 16).astype(np.uint16))
