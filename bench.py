@@ -446,12 +446,17 @@ def main():
             barrier()
             dev_regions.append(e0.elapsed_time(e1))
     del scrub
-    # ---- e2e: host batch in, loss out, every step ----
+    # ---- e2e: host batch in, loss out, every step. The loader stages one batch ahead: the transfer of batch i + 1 runs
+    # on the copy stream under step i (every transfer is still inside the timed region, K of them per region). ----
+    tr.prefetch_depth(2)
     for rep in range(R):
         barrier()
         t0 = time.perf_counter()
+        tr.prefetch_ptrs(tables[0])
         for i in range(K):
-            tr.step_ptrs(tables[i % nb], C.byref(loss_c))
+            if i + 1 < K:
+                tr.prefetch_ptrs(tables[(i + 1) % nb])
+            tr.step_prefetched(C.byref(loss_c))
         tr.sync()
         e2e_regions.append(time.perf_counter() - t0)
     barrier()

@@ -114,6 +114,23 @@ int32_t om_memcpy_h2d(om_ctx* ctx, void* dst, const void* src_host, size_t bytes
 int32_t om_memcpy_d2h(om_ctx* ctx, void* dst_host, const void* src, size_t bytes); /* synchronises */
 int32_t om_memcpy_d2d(om_ctx* ctx, void* dst, const void* src, size_t bytes);
 int32_t om_memset(om_ctx* ctx, void* dst, int32_t byte, size_t bytes);
+/* Staging of input batches one or more steps ahead (the device side of DataLoader's prefetch ring,
+ * src/OneModel.Training/Data/DataLoader.cs:35, docs/data-loading.md section 1: a batch waits in slot `step mod Prefetch`
+ * until its step takes it). The copies run on a copy stream of the context, beside the compute stream:
+ *   om_stage_h2d(slot, dst, src)  copy pinned host memory to device memory on the copy stream, after the step that
+ *                                 used the slot's previous batch has taken it;
+ *   om_stage_commit(slot)         the slot's batch is complete (an event on the copy stream);
+ *   om_stage_acquire(slot)        the compute stream waits for that event (no host wait);
+ *   om_stage_release(slot)        the work queued so far on the compute stream has taken the batch: the slot may be refilled;
+ *   om_stage_wait_taken(slot)     host wait for that point.
+ * Slots 0..15. The host memory must stay unchanged until the copy has run (keep it in the loader's ring). */
+int32_t om_stage_h2d(om_ctx* ctx, int32_t slot, void* dst, const void* src_pinned, size_t bytes);
+int32_t om_stage_commit(om_ctx* ctx, int32_t slot);
+int32_t om_stage_acquire(om_ctx* ctx, int32_t slot);
+int32_t om_stage_release(om_ctx* ctx, int32_t slot);
+/* Host wait until the slot's last om_stage_release has been reached by the compute stream (the loader's back-pressure:
+ * the pinned buffer behind the slot may be rewritten after it). Returns at once when the slot was never released. */
+int32_t om_stage_wait_taken(om_ctx* ctx, int32_t slot);
 int32_t om_host_alloc_pinned(om_ctx* ctx, size_t bytes, void** hptr);
 int32_t om_host_free_pinned(om_ctx* ctx, void* hptr);
 /* Waits for the stream and returns the device status word: OM_ERR_INDEX if a checked kernel saw an index

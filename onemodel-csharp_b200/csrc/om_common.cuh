@@ -70,6 +70,12 @@ struct om_ctx {
   std::map<std::string, om::ProfileEntry> profile;
   std::vector<cudaEvent_t> event_pool;
   om::DpState* dp = nullptr;
+  // Staging of input batches ahead of the step that uses them: a copy stream of its own and, per ring slot, an event the
+  // copy stream records when the slot's batch has landed and one the compute stream records when the step has taken it.
+  cudaStream_t copy_stream = nullptr;
+  static constexpr int kStageSlots = 16;
+  cudaEvent_t stage_ready[kStageSlots] = {}, stage_taken[kStageSlots] = {};
+  bool stage_has_taken[kStageSlots] = {};
 };
 
 namespace om {

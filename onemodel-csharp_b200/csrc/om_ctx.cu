@@ -297,6 +297,14 @@ int32_t om_ctx_destroy(om_ctx* ctx) {
     for (auto& g : pp->graph_cache)
       for (auto& kv : g.second)
         for (void* p : kv.second) cudaFree(p);
+  if (ctx->copy_stream) {
+    cudaStreamSynchronize(ctx->copy_stream);
+    cudaStreamDestroy(ctx->copy_stream);
+    for (int i = 0; i < om_ctx::kStageSlots; i++) {
+      if (ctx->stage_ready[i]) cudaEventDestroy(ctx->stage_ready[i]);
+      if (ctx->stage_taken[i]) cudaEventDestroy(ctx->stage_taken[i]);
+    }
+  }
   if (ctx->aux_stream) {
     cudaStreamSynchronize(ctx->aux_stream);
     cudaStreamDestroy(ctx->aux_stream);
@@ -392,6 +400,54 @@ int32_t om_memcpy_h2d(om_ctx* ctx, void* dst, const void* src, size_t bytes) {
   OM_CHECK_CTX(ctx);
   if (bytes == 0) return OM_OK;
   OM_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return OM_OK;
+}
+
+static int32_t stage_setup(om_ctx* ctx, int32_t slot) {
+  if (slot < 0 || slot >= om_ctx::kStageSlots) return fail(ctx, OM_ERR_ARG, "staging slot %d outside [0, %d)", slot, om_ctx::kStageSlots);
+  if (!ctx->copy_stream) OM_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+  if (!ctx->stage_ready[slot]) {
+    OM_CUDA(ctx, cudaEventCreateWithFlags(&ctx->stage_ready[slot], cudaEventDisableTiming));
+    OM_CUDA(ctx, cudaEventCreateWithFlags(&ctx->stage_taken[slot], cudaEventDisableTiming));
+  }
+  return OM_OK;
+}
+
+int32_t om_stage_h2d(om_ctx* ctx, int32_t slot, void* dst, const void* src_pinned, size_t bytes) {
+  OM_CHECK_CTX(ctx);
+  OM_TRY(stage_setup(ctx, slot));
+  // The slot's previous batch must have been taken by its step before the copy overwrites it.
+  if (ctx->stage_has_taken[slot]) OM_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->stage_taken[slot], 0));
+  if (bytes != 0) OM_CUDA(ctx, cudaMemcpyAsync(dst, src_pinned, bytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+  return OM_OK;
+}
+
+int32_t om_stage_commit(om_ctx* ctx, int32_t slot) {
+  OM_CHECK_CTX(ctx);
+  OM_TRY(stage_setup(ctx, slot));
+  OM_CUDA(ctx, cudaEventRecord(ctx->stage_ready[slot], ctx->copy_stream));
+  return OM_OK;
+}
+
+int32_t om_stage_acquire(om_ctx* ctx, int32_t slot) {
+  OM_CHECK_CTX(ctx);
+  OM_TRY(stage_setup(ctx, slot));
+  OM_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->stage_ready[slot], 0));
+  return OM_OK;
+}
+
+int32_t om_stage_wait_taken(om_ctx* ctx, int32_t slot) {
+  OM_CHECK_CTX(ctx);
+  OM_TRY(stage_setup(ctx, slot));
+  if (ctx->stage_has_taken[slot]) OM_CUDA(ctx, cudaEventSynchronize(ctx->stage_taken[slot]));
+  return OM_OK;
+}
+
+int32_t om_stage_release(om_ctx* ctx, int32_t slot) {
+  OM_CHECK_CTX(ctx);
+  OM_TRY(stage_setup(ctx, slot));
+  OM_CUDA(ctx, cudaEventRecord(ctx->stage_taken[slot], ctx->stream));
+  ctx->stage_has_taken[slot] = true;
   return OM_OK;
 }
 

@@ -37,7 +37,10 @@ constexpr int W_EPI_WARPS = OM_WS_EPI_WARPS;   // a multiple of four: the warps 
 constexpr int W_EPI_PARTS = W_EPI_WARPS / 4;
 constexpr int W_THREADS = 32 * (2 + W_EPI_WARPS);
 constexpr int W_RING = OM_WS_RING;        // staging slots per epilogue warp
-constexpr int W_SLOT = 4096 + 2048;       // a 32 x 32 fp32 block and its bfloat16 copy
+#ifndef OM_WS_SLOT
+#define OM_WS_SLOT 4096
+#endif
+constexpr int W_SLOT = OM_WS_SLOT;        // 4096: a 32 x 32 fp32 block (its bfloat16 copy follows through the same slot); 6144: both side by side
 constexpr int kWsClusters = 74;           // pairs of one round on a 148-SM device: the k-split target (a constant of the shape rule)
 
 template <int ELEM> struct WsElem;
@@ -299,10 +302,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)((c4 ^ (lane & 7)) << 4)), "r"(r[4 * c4]),
                        "r"(r[4 * c4 + 1]), "r"(r[4 * c4 + 2]), "r"(r[4 * c4 + 3])
                        : "memory");
-        if (p.c16) {
-          // The block as bfloat16: 64 bytes per row in the 64-byte swizzle of map_c16 (16-byte chunk c of row r at
-          // c ^ ((r >> 1) & 3)).
-          const uint32_t row16 = smem_u32(blk + 4096) + (uint32_t)lane * 64u;
+        // The block as bfloat16: 64 bytes per row in the 64-byte swizzle of map_c16 (16-byte chunk c of row r at
+        // c ^ ((r >> 1) & 3)). With a slot of 6144 bytes it lies behind the fp32 block and both stores go out together;
+        // with a slot of 4096 it takes the slot's place once the fp32 store has read it.
+        auto stage_bf16 = [&](uint8_t* dst16) {
+          const uint32_t row16 = smem_u32(dst16) + (uint32_t)lane * 64u;
 #pragma unroll
           for (int c8 = 0; c8 < 4; c8++) {
             uint32_t w[4];
@@ -315,11 +319,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                          "r"(w[2]), "r"(w[3])
                          : "memory");
           }
-        }
+        };
+        if (p.c16 && W_SLOT >= 6144) stage_bf16(blk + 4096);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
-          if (p.c16)
+          if (p.c16 && W_SLOT >= 6144)
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_c16), "r"(col0),
                          "r"(row_base), "r"(smem_u32(blk + 4096))
                          : "memory");
@@ -332,6 +337,19 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                          "r"(row_base), "r"(split), "r"(smem_u32(blk))
                          : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        if (p.c16 && W_SLOT < 6144) {
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+          stage_bf16(blk);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_c16), "r"(col0),
+                         "r"(row_base), "r"(smem_u32(blk))
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
         }
         stored++;
       }

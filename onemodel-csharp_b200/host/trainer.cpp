@@ -183,6 +183,12 @@ struct omh_trainer {
   std::map<AutogradMeta*, int> bucket_of;
   std::vector<std::vector<int>> bucket_params;   // positions in the optimizer's parameter list, per bucket
   int loss_bucket = -1;                          // the loss scalar rides on the communication stream as a bucket of one
+  // Batches staged ahead of their step (DataLoader's prefetch ring on the device): per slot the inputs on the device and a
+  // pinned host copy the asynchronous transfer reads from, so the caller's memory is free again when prefetch returns.
+  int stage_depth = 0;
+  std::vector<std::vector<Tensor>> stage_dev;
+  std::vector<std::vector<void*>> stage_host;
+  int64_t staged = 0, taken = 0;                 // batches put into / taken out of the ring
 };
 
 static void BuildFlatGrads(omh_trainer* t) {
@@ -377,6 +383,12 @@ OMH_API int32_t omh_trainer_create(int32_t kind, const int64_t* cfg, int32_t ncf
 
 OMH_API int32_t omh_trainer_free(omh_trainer* t) {
   if (t && t->graph) om_graph_destroy(Device::Current(), t->graph);
+  if (t) {
+    om_ctx* ctx = Device::Current();
+    om_sync(ctx);
+    for (auto& slot : t->stage_host)
+      for (void* h : slot) om_host_free_pinned(ctx, h);
+  }
   delete t;
   return 0;
 }
@@ -474,6 +486,68 @@ OMH_API int32_t omh_trainer_step(omh_trainer* t, const void* const* inputs_host,
     CopyInputs(t, inputs_host);
     RunStep(t);
     if (loss) Check(om_memcpy_d2h(Device::Current(), loss, t->loss_out.RawData(), 4));
+  });
+}
+
+// ---- batches staged ahead of their step ----------------------------------------------------------------------------------
+// omh_trainer_prefetch(batch) puts the next batch into the ring: a copy into the slot's pinned buffer (the caller's memory
+// is free when the call returns) and an asynchronous transfer on the copy stream, which runs under the steps already
+// queued. omh_trainer_step_prefetched() runs a step on the oldest staged batch: the compute stream waits for that slot's
+// transfer (the host does not), takes the batch with device-to-device copies into the inputs the step (and its captured
+// graph) reads, and frees the slot. Batches are consumed in the order they were staged (docs/data-loading.md section 1 of
+// the reference: a batch waits in slot `step mod Prefetch` until the consumer reaches it).
+OMH_API int32_t omh_trainer_prefetch_depth(omh_trainer* t, int32_t depth) {
+  return Guard([&] {
+    if (depth < 1 || depth > 16) throw ArgumentOutOfRangeException("The prefetch depth must be between 1 and 16.");
+    if (t->stage_depth != 0) throw InvalidOperationException("The prefetch depth is already set.");
+    om_ctx* ctx = Device::Current();
+    t->stage_depth = depth;
+    t->stage_dev.resize(depth);
+    t->stage_host.resize(depth);
+    for (int s = 0; s < depth; s++)
+      for (size_t i = 0; i < t->inputs.size(); i++) {
+        t->stage_dev[s].push_back(Tensor::Zeros(t->inputs[i].GetDType(), t->inputs[i].GetShape()));
+        void* h = nullptr;
+        Check(om_host_alloc_pinned(ctx, (size_t)omh_trainer_input_bytes(t, (int32_t)i), &h));
+        t->stage_host[s].push_back(h);
+      }
+  });
+}
+
+OMH_API int32_t omh_trainer_prefetch(omh_trainer* t, const void* const* inputs_host) {
+  return Guard([&] {
+    if (t->stage_depth == 0) throw InvalidOperationException("Set the prefetch depth first.");
+    if (t->staged - t->taken >= t->stage_depth) throw InvalidOperationException("The prefetch ring is full: take a step first.");
+    om_ctx* ctx = Device::Current();
+    const int slot = (int)(t->staged % t->stage_depth);
+    // The pinned buffer of this slot was last read by the transfer of the batch staged stage_depth batches ago, whose step
+    // has been queued since; the transfer itself has long run by the time its step was taken, except when the caller
+    // stages faster than the device steps: then wait for that step's take (a host wait on purpose: back-pressure).
+    if (t->staged >= t->stage_depth) Check(om_stage_wait_taken(ctx, slot));
+    for (size_t i = 0; i < t->inputs.size(); i++) {
+      const size_t bytes = (size_t)omh_trainer_input_bytes(t, (int32_t)i);
+      memcpy(t->stage_host[slot][i], inputs_host[i], bytes);
+      Check(om_stage_h2d(ctx, slot, t->stage_dev[slot][i].RawData(), t->stage_host[slot][i], bytes));
+    }
+    Check(om_stage_commit(ctx, slot));
+    t->staged++;
+  });
+}
+
+OMH_API int32_t omh_trainer_step_prefetched(omh_trainer* t, float* loss) {
+  return Guard([&] {
+    if (t->taken >= t->staged) throw InvalidOperationException("No batch is staged.");
+    om_ctx* ctx = Device::Current();
+    const int slot = (int)(t->taken % t->stage_depth);
+    Check(om_stage_acquire(ctx, slot));
+    for (size_t i = 0; i < t->inputs.size(); i++) {
+      Check(om_memcpy_d2d(ctx, t->inputs[i].RawData(), t->stage_dev[slot][i].RawData(), (size_t)omh_trainer_input_bytes(t, (int32_t)i)));
+      t->inputs[i].MarkModified();
+    }
+    Check(om_stage_release(ctx, slot));
+    t->taken++;
+    RunStep(t);
+    if (loss) Check(om_memcpy_d2h(ctx, loss, t->loss_out.RawData(), 4));
   });
 }
 

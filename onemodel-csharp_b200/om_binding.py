@@ -685,6 +685,27 @@ class Trainer:
         buf = (C.c_uint8 * 128).from_buffer_copy(bytes(id128))
         self._check(host_lib().omh_trainer_dp_init(self.h, buf, i32(rank), i32(world), C.c_int64(global_rows)))
 
+    def prefetch_depth(self, depth):
+        """Sizes the ring of batches staged ahead of their step (DataLoaderOptions.Prefetch of the reference)."""
+        self._check(host_lib().omh_trainer_prefetch_depth(self.h, i32(depth)))
+
+    def prefetch(self, inputs):
+        """Stages the next batch: copied to a pinned ring slot and sent to the device on the copy stream, under the steps
+        already queued. The arrays may be reused when this returns."""
+        self._check(host_lib().omh_trainer_prefetch(self.h, self._ptrs(inputs)))
+
+    def prefetch_ptrs(self, ptr_table):
+        self._check(host_lib().omh_trainer_prefetch(self.h, ptr_table))
+
+    def step_prefetched(self, loss_ref=None):
+        """One step on the oldest staged batch; returns the loss (or writes it through loss_ref)."""
+        if loss_ref is not None:
+            self._check(host_lib().omh_trainer_step_prefetched(self.h, loss_ref))
+            return None
+        loss = C.c_float()
+        self._check(host_lib().omh_trainer_step_prefetched(self.h, C.byref(loss)))
+        return loss.value
+
     def set_dp_timeout_ms(self, ms):
         self._check(host_lib().omh_trainer_set_dp_timeout_ms(self.h, i32(ms)))
 
