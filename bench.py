@@ -344,6 +344,8 @@ def main():
     ap.add_argument("--fp32", action="store_true", help="products on the fp32 FMA kernel instead of the tensor pipe")
     ap.add_argument("--tf32", action="store_true", help="TF32 operands also where the workload states bf16 operands")
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median region is reported")
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch override: a SMALL case of the same kernels for profiler captures "
+                    "(the line then says so in config.workload and is not the benchmark's number)")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--ctx-flags", type=int, default=0, help="extra context flags (8 = CTA-pair tiles, 16 = two-stream backward)")
     args = ap.parse_args()
@@ -363,6 +365,13 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     kind, cfg, lr, desc, gflop = WORKLOADS[args.workload]
+    if args.batch > 0:
+        cfg = list(cfg)
+        if kind == "mlm":
+            cfg[7] = max(1, int(round(cfg[7] * args.batch / cfg[0])))
+        gflop = gflop * args.batch / cfg[0]
+        cfg[0] = args.batch
+        desc = f"{desc} [REDUCED to batch {args.batch} per GPU for a profiler capture]"
     W, K = max(3, args.warmup), max(1, args.steps)
     # Products on the tensor pipe: TF32 operands everywhere, bf16 operands (fp32 accumulation, fp32 master weights) for the
     # BERT-base shape as its configuration states.

@@ -221,7 +221,10 @@ int32_t om_linear_bwd_bf16_b16(om_ctx* ctx, const uint16_t* g16, const float* g,
                                uint16_t* dx16, float* dW, float* dbias, int32_t accumulate_w);
 /* Producers that write the bfloat16 copy of their result in the same pass (the copy pointer may be NULL: then they are
  * om_unary, om_unary_bwd, om_layernorm_fwd, om_layernorm_bwd): the activation, its gradient and the two sides of a
- * layer norm are what feeds the Linear products of an encoder layer, so no separate cast pass is left for them. */
+ * layer norm are what feeds the Linear products of an encoder layer, so no separate cast pass is left for them.
+ * With a copy requested, OM_GELU_ERF and its derivative evaluate erf in a short branch-free form (within 4e-7 absolute of
+ * erf; the copy then rounds to 8 significant bits), the same form that om_linear_fwd_bf16_act and
+ * om_linear_dgrad_bf16_act apply in their epilogues, so that the fused and the separate calls give the same bits. */
 int32_t om_unary_b16(om_ctx* ctx, int32_t op, const float* x, float* y, uint16_t* y16, int64_t n);
 int32_t om_unary_bwd_b16(om_ctx* ctx, int32_t op, const float* g, const float* saved, float* dx, uint16_t* dx16, int64_t n);
 int32_t om_layernorm_fwd_b16(om_ctx* ctx, const float* x, const float* gamma, const float* beta, int32_t rows,
@@ -233,6 +236,23 @@ int32_t om_layernorm_bwd_b16(om_ctx* ctx, const float* g, const float* x, const 
 int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x,
                            const uint16_t* W, int32_t rows, int32_t in_features, int32_t out_features, float* dx,
                            float* dW, float* dbias, int32_t accumulate_w);
+/* A Linear layer together with the activation that follows it (op: OM_GELU_ERF or OM_GELU_TANH), for the pair
+ * Linear -> activation -> Linear of a feed-forward block (the reference composes Ops.Linear, Ops.Gelu, Ops.Linear,
+ * Ops.Layers.cs:715-733 and Ops.cs Gelu; the values are those of the composition, bit for bit):
+ *   om_linear_fwd_bf16_act: y = x W^T + bias (fp32, what the activation's backward needs) and a16 = bfloat16(op(y)), the
+ *     next layer's operand, from the product's epilogue; op(y) is not stored as fp32.
+ *   om_linear_dgrad_bf16_act: dx = op'(pre) * (g W), the input gradient of the layer AFTER the activation already
+ *     multiplied by the activation's derivative at its saved input `pre` ([rows, in_features] with pitch ldpre), as
+ *     fp32 and (dx16 may be NULL) as bfloat16.
+ * om_linear_act_bf16_supported tells (1 / 0) whether the shape can take the fused form (widths that are multiples of 8, at
+ * least 256 result columns, no split of k); otherwise the caller composes the unfused calls. */
+int32_t om_linear_act_bf16_supported(om_ctx* ctx, int32_t rows, int32_t in_features, int32_t out_features, int32_t op,
+                                     int32_t backward);
+int32_t om_linear_fwd_bf16_act(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows,
+                               int32_t in_features, int32_t out_features, int32_t op, float* y, uint16_t* a16, int32_t ldy);
+int32_t om_linear_dgrad_bf16_act(om_ctx* ctx, const uint16_t* g16, int32_t ldg, const uint16_t* W, int32_t rows,
+                                 int32_t in_features, int32_t out_features, int32_t op, const float* pre, int32_t ldpre,
+                                 float* dx, uint16_t* dx16);
 
 /* ---- elementwise ------------------------------------------------------------------------------------ */
 

@@ -3,6 +3,7 @@
 // written here rounds twice exactly as the reference's managed code does; fused multiply-adds are explicit fmaf.
 #include <cuda_bf16.h>
 
+#include "om_act.cuh"
 #include "om_common.cuh"
 
 namespace om {
@@ -89,52 +90,6 @@ __global__ void binary_strided_kernel(int op, Strided2 s, const float* __restric
 }
 
 // ---- unary forward / backward ---------------------------------------------------------------------------------
-
-__device__ __forceinline__ float gelu_erf(float x) { return (0.5f * x) * (1.0f + erff(x * 0.70710677f)); }
-__device__ __forceinline__ float gelu_tanh(float x) {
-  float u = 0.79788456f * (x + ((0.044715f * x) * x) * x);
-  return (0.5f * x) * (1.0f + tanhf(u));
-}
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
-
-template <int OP>
-__device__ __forceinline__ float unary_apply(float x) {
-  if (OP == OM_RELU) return x > 0.0f ? x : (x == x ? 0.0f : x);
-  if (OP == OM_GELU_ERF) return gelu_erf(x);
-  if (OP == OM_GELU_TANH) return gelu_tanh(x);
-  if (OP == OM_SIGMOID) return sigmoidf_(x);
-  if (OP == OM_TANH) return tanhf(x);
-  if (OP == OM_NEG) return x * -1.0f;
-  if (OP == OM_EXP) return expf(x);
-  if (OP == OM_SQRT) return sqrtf(x);
-  if (OP == OM_ERF) return erff(x);
-  return x;
-}
-
-// g = incoming gradient, s = saved tensor (output or input, see the header).
-template <int OP>
-__device__ __forceinline__ float unary_grad(float g, float s) {
-  if (OP == OM_RELU) return s > 0.0f ? g : 0.0f;
-  if (OP == OM_SIGMOID) return (g * s) * (1.0f - s);
-  if (OP == OM_TANH) return g * (1.0f - s * s);
-  if (OP == OM_GELU_ERF) {
-    float cdf = 0.5f * (1.0f + erff(s * 0.70710677f));
-    float pdf = expf((-0.5f * s) * s) * 0.3989423f;
-    return g * (cdf + s * pdf);
-  }
-  if (OP == OM_GELU_TANH) {
-    float u = 0.79788456f * (s + ((0.044715f * s) * s) * s);
-    float t = tanhf(u);
-    float left = 0.5f * (1.0f + t);
-    float right = (((0.5f * s) * (1.0f - t * t)) * 0.79788456f) * (1.0f + ((3.0f * 0.044715f) * s) * s);
-    return g * (left + right);
-  }
-  if (OP == OM_NEG) return g * -1.0f;
-  if (OP == OM_EXP) return g * s;                       // s = exp(x)
-  if (OP == OM_SQRT) return g / (2.0f * s);             // s = sqrt(x)
-  if (OP == OM_ERF) return g * (1.1283791671f * expf(-(s * s)));  // s = x
-  return g;
-}
 
 // Four bfloat16 values (round to nearest even) as one 8-byte word.
 __device__ __forceinline__ uint2 pack_bf16x4(float4 v) {
@@ -636,7 +591,10 @@ int32_t om_unary_b16(om_ctx* ctx, int32_t op, const float* x, float* y, uint16_t
   int64_t n4 = vec ? n / 4 : 0;
   const int threads = 256;
   int grid = grid_for(ctx, vec ? (n + 3) / 4 : n, threads);
-  OM_UNARY_DISPATCH(unary_kernel, x, y, y16, n4, n)
+  // With a bfloat16 copy to write (the bfloat16-operand tier) the erf GELU takes its short form (om_act.cuh), the same that
+  // the product epilogues apply.
+  if (op == OM_GELU_ERF && y16) launch_chained(ctx, unary_kernel<OM_GELU_ERF_FAST>, grid, threads, 0, x, y, y16, n4, n);
+  else OM_UNARY_DISPATCH(unary_kernel, x, y, y16, n4, n)
   OM_LAUNCH_CHECK(ctx, "om_unary");
   return OM_OK;
 }
@@ -652,7 +610,8 @@ int32_t om_unary_bwd_b16(om_ctx* ctx, int32_t op, const float* g, const float* s
   int64_t n4 = vec ? n / 4 : 0;
   const int threads = 256;
   int grid = grid_for(ctx, vec ? (n + 3) / 4 : n, threads);
-  OM_UNARY_DISPATCH(unary_bwd_kernel, g, saved, dx, dx16, n4, n)
+  if (op == OM_GELU_ERF && dx16) launch_chained(ctx, unary_bwd_kernel<OM_GELU_ERF_FAST>, grid, threads, 0, g, saved, dx, dx16, n4, n);
+  else OM_UNARY_DISPATCH(unary_bwd_kernel, g, saved, dx, dx16, n4, n)
   OM_LAUNCH_CHECK(ctx, "om_unary_bwd");
   return OM_OK;
 }

@@ -12,6 +12,9 @@ bool gemm_ws_supported(om_ctx* ctx, int elem, int m, int n, int k, const void* A
                        long long ldc);
 int32_t gemm_ws(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, float* C,
                 long long ldc, int acc, const float* bias, uint16_t* C16);
+int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, float* C,
+                    long long ldc, int acc, const float* bias, uint16_t* C16, int act, int op, const float* aux, long long ld_aux);
+bool gemm_ws_act_ok(int act, int op, int m, int n, int k, const float* C, long long ldc, const uint16_t* C16, const float* aux, long long ld_aux);
 int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64_t ld, float* out, int32_t accumulate);
 
 // Eight elements per thread: two 16-byte loads, one 16-byte store.
@@ -135,6 +138,45 @@ int32_t om_linear_bwd_bf16_b16(om_ctx* ctx, const uint16_t* g16, const float* g,
 int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x, const uint16_t* W, int32_t rows,
                            int32_t in_features, int32_t out_features, float* dx, float* dW, float* dbias, int32_t accumulate_w) {
   return om_linear_bwd_bf16_b16(ctx, g16, g, ldg, x, W, rows, in_features, out_features, dx, nullptr, dW, dbias, accumulate_w);
+}
+
+// ---- a Linear layer with the activation that follows it, and the input gradient of the layer after that activation ----
+
+int32_t om_linear_act_bf16_supported(om_ctx* ctx, int32_t rows, int32_t in_features, int32_t out_features, int32_t op, int32_t backward) {
+  if (!ctx) return 0;
+  // Aligned stand-ins for the pointers: the query is about the shape (the calls check their own pointers).
+  const float* aligned = reinterpret_cast<const float*>(uintptr_t(256));
+  const uint16_t* aligned16 = reinterpret_cast<const uint16_t*>(uintptr_t(256));
+  if (backward) {
+    if (out_features % 8 || in_features % 8) return 0;
+    return gemm_ws_act_ok(2, op, rows, in_features, out_features, aligned, in_features, aligned16, aligned, in_features) ? 1 : 0;
+  }
+  if (in_features % 8 || out_features % 8) return 0;
+  return gemm_ws_act_ok(1, op, rows, out_features, in_features, aligned, out_features, aligned16, nullptr, 0) ? 1 : 0;
+}
+
+int32_t om_linear_fwd_bf16_act(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows, int32_t in_features,
+                               int32_t out_features, int32_t op, float* y, uint16_t* a16, int32_t ldy) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 1 || in_features < 1 || out_features < 1 || ldy < out_features)
+    return fail(ctx, OM_ERR_SHAPE, "om_linear_fwd_bf16_act: rows %d in %d out %d ldy %d", rows, in_features, out_features, ldy);
+  if (!y || !a16) return fail(ctx, OM_ERR_ARG, "om_linear_fwd_bf16_act: y and a16 are both written");
+  OM_TRY(check_args(ctx, "om_linear_fwd_bf16_act", rows, out_features, in_features, x, in_features, W, in_features, y, ldy));
+  ProfileScope prof(ctx, "om_linear_fwd", 2.0 * rows * in_features * out_features,
+                    2.0 * ((double)rows * in_features + (double)in_features * out_features) + 6.0 * (double)rows * out_features);
+  return gemm_ws_act(ctx, 1, 0, 1, rows, out_features, in_features, x, in_features, W, in_features, y, ldy, 0, bias, a16, 1, op, nullptr, 0);
+}
+
+int32_t om_linear_dgrad_bf16_act(om_ctx* ctx, const uint16_t* g16, int32_t ldg, const uint16_t* W, int32_t rows, int32_t in_features,
+                                 int32_t out_features, int32_t op, const float* pre, int32_t ldpre, float* dx, uint16_t* dx16) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 1 || in_features < 1 || out_features < 1 || ldg < out_features || ldpre < in_features)
+    return fail(ctx, OM_ERR_SHAPE, "om_linear_dgrad_bf16_act: rows %d in %d out %d ldg %d ldpre %d", rows, in_features, out_features, ldg, ldpre);
+  if (!dx || !pre) return fail(ctx, OM_ERR_ARG, "om_linear_dgrad_bf16_act: dx and the activation's saved input are needed");
+  OM_TRY(check_args(ctx, "om_linear_dgrad_bf16_act", rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features));
+  ProfileScope prof(ctx, "om_linear_bwd.dgrad", 2.0 * rows * in_features * out_features,
+                    2.0 * ((double)rows * out_features + (double)in_features * out_features) + (dx16 ? 10.0 : 8.0) * (double)rows * in_features);
+  return gemm_ws_act(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, 0, nullptr, dx16, 2, op, pre, ldpre);
 }
 
 }  // extern "C"

@@ -18,6 +18,7 @@
 // tensor memory is released and the kernel returns.
 #include <cuda_bf16.h>
 
+#include "om_act.cuh"
 #include "om_tc.cuh"
 
 namespace om {
@@ -34,8 +35,7 @@ constexpr int W_BM = 128;                 // rows of C per CTA; a pair computes 
 #endif
 constexpr int W_STAGES = OM_WS_STAGES;
 constexpr int W_EPI_WARPS = OM_WS_EPI_WARPS;   // a multiple of four: the warps of a TMEM lane quadrant share the tile's columns
-constexpr int W_EPI_PARTS = W_EPI_WARPS / 4;
-constexpr int W_THREADS = 32 * (2 + W_EPI_WARPS);
+constexpr int W_ACT_EPI_WARPS = 8;             // with an activation in the epilogue: twice the warps for the arithmetic
 constexpr int W_RING = OM_WS_RING;        // staging slots per epilogue warp
 #ifndef OM_WS_SLOT
 #define OM_WS_SLOT 4096
@@ -63,6 +63,8 @@ struct WsParams {
   int accumulate;
   int c16;                        // also store the bfloat16 copy of every block through map_c16 (never with accumulate)
   int32_t* status;
+  const float* aux;               // ACT 2: the activation's saved input, [m, n] fp32 with pitch ld_aux
+  long long ld_aux;
 };
 
 __device__ __forceinline__ uint32_t ws_cluster_ctarank() {
@@ -119,15 +121,22 @@ __host__ __device__ constexpr uint32_t ws_idesc(int bn, bool a_mn, bool b_mn) {
          ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
-template <int BN>
+template <int BN, int EW>
 constexpr size_t ws_smem_bytes() {
-  return (size_t)W_STAGES * (W_BM * 128 + (BN / 2) * 128) + (size_t)W_EPI_WARPS * W_RING * W_SLOT + 1024 + 256;
+  return (size_t)W_STAGES * (W_BM * 128 + (BN / 2) * 128) + (size_t)EW * W_RING * W_SLOT + 1024 + 256;
 }
 
 // Shared-memory tiles. K-major: rows (m or n) of 128 bytes of k, 8-row swizzle atoms 1024 bytes apart. MN-major: chunks of
 // [BK k-rows x 128 bytes of m/n], BK * 128 bytes apart (leading offset); groups of k-rows MN_SBO bytes apart.
-template <int ELEM, int BN, bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W_THREADS, 1)
+//
+// ACT (with the unary operator OP) puts an activation between two Linear layers into the epilogue:
+//   1: C receives the product (+ bias) as before, the bfloat16 tensor receives OP(C) rounded: the next layer's operand,
+//      without the activation's own pass over C;
+//   2: C and its bfloat16 copy receive d/dx OP(aux) * product, aux being the activation's saved input: the input
+//      gradient of the layer after the activation, already multiplied by the activation's derivative.
+// EW epilogue warps (four, or eight when the epilogue has this arithmetic to do).
+template <int ELEM, int BN, bool A_MN, bool B_MN, int ACT = 0, int OP = 0, int EW = W_EPI_WARPS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (2 + EW), 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_c16, WsParams p) {
   using E = WsElem<ELEM>;
@@ -143,7 +152,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* staging = smem + (size_t)W_STAGES * STAGE;
-  uint64_t* full = reinterpret_cast<uint64_t*>(staging + (size_t)W_EPI_WARPS * W_RING * W_SLOT);
+  constexpr int PARTS = EW / 4, CB_PER = NB / PARTS;            // the warps of a lane quadrant split the tile's column blocks
+  static_assert(ACT != 1 || W_SLOT < 6144, "the activated bfloat16 block is staged after the fp32 block has left the slot");
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + (size_t)EW * W_RING * W_SLOT);
   uint64_t* empty = full + W_STAGES;
   uint64_t* acc_full = empty + W_STAGES;     // [2]
   uint64_t* acc_empty = acc_full + 2;        // [2], used in the leader
@@ -163,7 +174,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 2 * W_EPI_WARPS);               // every epilogue warp of both CTAs
+      mbar_init(&acc_empty[a], 2 * EW);                        // every epilogue warp of both CTAs
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -268,21 +279,34 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int m0 = (2 * (t / p.tiles_n) + (int)rank) * W_BM;
       const int n0 = (t % p.tiles_n) * BN;
       const uint32_t a = tile_i & 1, use = tile_i >> 1;
+      const int row_base = m0 + quad * 32;
+      // ACT 2: this lane's 32 values of the saved input for a column block (n is a multiple of four, so that a 16-byte
+      // load never straddles the last column). The first block's loads are in flight while the accumulator is awaited,
+      // every later block's while the block before it is worked on.
+      float4 aux[8], nxt[8];
+      auto load_aux = [&](float4 (&dst)[8], int cb) {
+        const int c0 = n0 + cb * 32, row = row_base + lane;
+        const bool in = row < p.m && c0 < p.n;
+        const float4* src = reinterpret_cast<const float4*>(p.aux + (int64_t)(in ? row : 0) * p.ld_aux + (in ? c0 : 0));
+#pragma unroll
+        for (int c4 = 0; c4 < 8; c4++) dst[c4] = (in && c0 + 4 * c4 < p.n) ? __ldg(src + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      };
+      if (ACT == 2) load_aux(aux, part * CB_PER);
       ok = mbar_wait(&acc_full[a], use & 1, abort_flag, p.status, 44);
       if (!ok) break;
       tc_fence_after();
-      const int row_base = m0 + quad * 32;
       const uint32_t tmem_acc = tmem_base + a * BN + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
-      for (int cb = part * (NB / W_EPI_PARTS); cb < (part + 1) * (NB / W_EPI_PARTS); cb++) {
+      for (int cb = part * CB_PER; cb < (part + 1) * CB_PER; cb++) {
         const int col0 = n0 + cb * 32;
         const bool live = row_base < p.m && col0 < p.n;
         uint32_t r[32];
+        if (ACT == 2 && cb + 1 < (part + 1) * CB_PER) load_aux(nxt, cb + 1);
         if (live) {
           tmem_ld_32x32b_x32(tmem_acc + (uint32_t)(cb * 32), r);
           tmem_ld_wait();
         }
-        if (cb == (part + 1) * (NB / W_EPI_PARTS) - 1) {
+        if (cb == (part + 1) * CB_PER - 1) {
           // This warp has everything it needs out of the buffer: the next tile but one may overwrite it.
           tc_fence_before();
           __syncwarp();
@@ -290,6 +314,17 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (!live) continue;
         if (p.bias) add_bias32(r, p.bias, col0, p.n);
+        if (ACT == 2) {
+#pragma unroll
+          for (int c4 = 0; c4 < 8; c4++) {
+            r[4 * c4 + 0] = __float_as_uint(unary_grad<OP>(__uint_as_float(r[4 * c4 + 0]), aux[c4].x));
+            r[4 * c4 + 1] = __float_as_uint(unary_grad<OP>(__uint_as_float(r[4 * c4 + 1]), aux[c4].y));
+            r[4 * c4 + 2] = __float_as_uint(unary_grad<OP>(__uint_as_float(r[4 * c4 + 2]), aux[c4].z));
+            r[4 * c4 + 3] = __float_as_uint(unary_grad<OP>(__uint_as_float(r[4 * c4 + 3]), aux[c4].w));
+          }
+#pragma unroll
+          for (int c4 = 0; c4 < 8; c4++) aux[c4] = nxt[c4];
+        }
         if (stored >= W_RING) {
           // The block about to be overwritten was handed to the TMA unit W_RING stores ago.
           if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(W_RING - 1) : "memory");   // all but the newest W_RING - 1
@@ -339,6 +374,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         if (p.c16 && W_SLOT < 6144) {
+          if (ACT == 1) {
+            // The activation's arithmetic runs while the TMA unit reads the fp32 block out of the slot.
+#pragma unroll
+            for (int i = 0; i < 32; i++) r[i] = __float_as_uint(unary_apply<OP>(__uint_as_float(r[i])));
+          }
           if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           __syncwarp();
           stage_bf16(blk);
@@ -418,7 +458,8 @@ bool gemm_ws_supported(om_ctx* ctx, int elem, int m, int n, int k, const void* A
 template <int ELEM, int BN>
 static int32_t ws_launch(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
                          const CUtensorMap& mc16, const WsParams& p, int units) {
-  constexpr size_t smem = ws_smem_bytes<BN>();
+  constexpr size_t smem = ws_smem_bytes<BN, W_EPI_WARPS>();
+  constexpr int W_THREADS = 32 * (2 + W_EPI_WARPS);
 #define OM_WS(AMN, BMN)                                                                                                          \
   do {                                                                                                                           \
     static int max_clusters = 0;                                                                                                 \
@@ -447,6 +488,34 @@ static int32_t ws_launch(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& m
   return OM_OK;
 }
 
+// The variants with an activation in the epilogue: bfloat16 operands, 256-wide tiles, A row-major [m, k]; B is [n, k]
+// for ACT 1 (a Linear forward) and [k, n] for ACT 2 (a Linear input gradient).
+template <int ACT, int OP>
+static int32_t ws_launch_act(om_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& mc16,
+                             const WsParams& p, int units) {
+  constexpr size_t smem = ws_smem_bytes<256, W_ACT_EPI_WARPS>();
+  constexpr int threads = 32 * (2 + W_ACT_EPI_WARPS);
+  auto kernel = gemm_ws_kernel<1, 256, false, ACT == 2, ACT, OP, W_ACT_EPI_WARPS>;
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    OM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3(2 * (unsigned)ctx->sm_count);
+    q.blockDim = dim3(threads);
+    q.dynamicSmemBytes = smem;
+    int nc = 0;
+    if (cudaOccupancyMaxActiveClusters(&nc, kernel, &q) != cudaSuccess || nc < 1) {
+      cudaGetLastError();
+      nc = ctx->sm_count / 2;
+    }
+    max_clusters = nc;
+  }
+  const int clusters = units < max_clusters ? units : max_clusters;
+  launch_chained(ctx, kernel, dim3(2 * (unsigned)clusters), threads, smem, ma, mb, mc, mc16, p);
+  OM_LAUNCH_CHECK(ctx, "gemm_ws (activation epilogue)");
+  return OM_OK;
+}
+
 // C[m, n] (+)= op(A)[m, k] op(B)[k, n] + bias. elem 0: A and B are fp32 (TF32 products); elem 1: A and B are bfloat16.
 // ta != 0: A is stored [k, m]; tb != 0: B is stored [n, k]. Leading dimensions in elements of the operand's own type.
 // C16 (may be null): also receives C rounded to bfloat16, element i of C16 being element i of C (same pitch). Needs a
@@ -457,13 +526,51 @@ bool gemm_ws_c16_ok(const uint16_t* C16, long long ldc, int acc) {
 
 int32_t cast_bf16_rows(om_ctx* ctx, const float* src, uint16_t* dst, int rows, int cols, long long ld);
 
+// act 0: none. act 1 with op: C16 receives op(C) instead of C. act 2 with op: C and C16 receive op'(aux) * C.
+// gemm_ws_act_ok tells whether a product can take the activation (no split of k, the layouts above).
+static int ws_splits(int tiles, int k_blocks) {
+  // Fixed split of k by shape alone: enough slices for one round of pairs, each at least 8 k-blocks deep.
+  int splits = 1;
+  if (tiles < kWsClusters && k_blocks >= 16) {
+    splits = (int)std::min<int64_t>(kWsClusters / tiles, k_blocks / 8);
+    if (splits < 1) splits = 1;
+    if (splits > 32) splits = 32;
+  }
+  return splits;
+}
+
+bool gemm_ws_act_ok(int act, int op, int m, int n, int k, const float* C, long long ldc, const uint16_t* C16, const float* aux, long long ld_aux) {
+  if (act != 1 && act != 2) return false;
+  if (op != OM_GELU_ERF && op != OM_GELU_TANH) return false;
+  if (m < 1 || n < 256 || (n & 3)) return false;
+  const int tiles = (int)(ceil_div(m, 2 * W_BM) * ceil_div(n, 256));
+  if (ws_splits(tiles, (int)ceil_div(k, 64)) != 1) return false;
+  if (act == 1 && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
+  if (act == 2 && (C16 != nullptr) && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
+  if (act == 2 && (!aux || (ld_aux & 3) || (reinterpret_cast<uintptr_t>(aux) & 15))) return false;
+  (void)C;
+  return true;
+}
+
+int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, float* C,
+                    long long ldc, int acc, const float* bias, uint16_t* C16, int act, int op, const float* aux, long long ld_aux);
+
 int32_t gemm_ws(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, float* C,
                 long long ldc, int acc, const float* bias, uint16_t* C16) {
+  return gemm_ws_act(ctx, elem, ta, tb, m, n, k, A, lda, B, ldb, C, ldc, acc, bias, C16, 0, 0, nullptr, 0);
+}
+
+int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, float* C,
+                    long long ldc, int acc, const float* bias, uint16_t* C16, int act, int op, const float* aux, long long ld_aux) {
   const bool a_mn = ta != 0, b_mn = tb == 0;
+  if (act != 0) {
+    if (elem != 1 || acc || a_mn || b_mn != (act == 2) || !gemm_ws_act_ok(act, op, m, n, k, C, ldc, C16, aux, ld_aux))
+      return fail(ctx, OM_ERR_UNSUPPORTED, "persistent product: this shape or layout cannot take the activation in its epilogue (m %d n %d k %d)", m, n, k);
+  }
   const int bk = elem == 0 ? 32 : 64, mn_chunk = elem == 0 ? 32 : 64;
   // Tile width: 256 unless the last 256-wide tile would be less than half used.
   const int rem = n % 256;
-  const int bn = (n <= 128 || (rem > 0 && rem <= 128 && n < 1024)) ? 128 : 256;
+  const int bn = act != 0 ? 256 : (n <= 128 || (rem > 0 && rem <= 128 && n < 1024)) ? 128 : 256;
   CUtensorMap map_a, map_b, map_c, map_c16;
   bool ok = a_mn ? ws_operand_map(&map_a, elem, A, m, k, lda, bk, true) : ws_operand_map(&map_a, elem, A, k, m, lda, W_BM, false);
   ok = ok && (b_mn ? ws_operand_map(&map_b, elem, B, n, k, ldb, bk, true) : ws_operand_map(&map_b, elem, B, k, n, ldb, bn / 2, false));
@@ -474,17 +581,13 @@ int32_t gemm_ws(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, cons
   p.tiles_m = (int)ceil_div(m, 2 * W_BM);
   p.tiles_n = (int)ceil_div(n, bn);
   const int tiles = p.tiles_m * p.tiles_n, k_blocks = (int)ceil_div(k, bk);
-  // Fixed split of k by shape alone: enough slices for one round of pairs, each at least 8 k-blocks deep.
-  int splits = 1;
-  if (tiles < kWsClusters && k_blocks >= 16) {
-    splits = (int)std::min<int64_t>(kWsClusters / tiles, k_blocks / 8);
-    if (splits < 1) splits = 1;
-    if (splits > 32) splits = 32;
-  }
+  int splits = ws_splits(tiles, k_blocks);
   p.kb_per_split = (int)ceil_div(k_blocks, splits);
   splits = (int)ceil_div(k_blocks, p.kb_per_split);
   p.splits = splits;
   p.status = ctx->status_dev;
+  p.aux = aux;
+  p.ld_aux = ld_aux;
   float* workspace = nullptr;
   if (splits > 1) {
     OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)splits * m * n, false, (void**)&workspace));
@@ -504,7 +607,11 @@ int32_t gemm_ws(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, cons
   }
   const int units = tiles * splits;
   int32_t st;
-  if (elem == 0) st = bn == 256 ? ws_launch<0, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<0, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
+  if (act == 1) st = op == OM_GELU_ERF ? ws_launch_act<1, OM_GELU_ERF_FAST>(ctx, map_a, map_b, map_c, map_c16, p, units)
+                                       : ws_launch_act<1, OM_GELU_TANH>(ctx, map_a, map_b, map_c, map_c16, p, units);
+  else if (act == 2) st = op == OM_GELU_ERF ? ws_launch_act<2, OM_GELU_ERF_FAST>(ctx, map_a, map_b, map_c, map_c16, p, units)
+                                            : ws_launch_act<2, OM_GELU_TANH>(ctx, map_a, map_b, map_c, map_c16, p, units);
+  else if (elem == 0) st = bn == 256 ? ws_launch<0, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<0, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
   else st = bn == 256 ? ws_launch<1, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<1, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
   if (st == OM_OK && splits > 1) splitk_reduce_launch(ctx, workspace, splits, (int64_t)m * n, n, ldc, bias, C, acc);
   if (workspace) pool_free(ctx, workspace);

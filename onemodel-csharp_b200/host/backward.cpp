@@ -231,6 +231,70 @@ static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
   }
 }
 
+// The record of Ops::FeedForward (inputs x, w1, b1, w2, b2; saved x, w1, w2, the first layer's result before the
+// activation, the activation's result as bfloat16; Ints = {rows, in, ff, out, op}). The second layer's input gradient comes
+// out of its product already multiplied by the activation's derivative, as fp32 (the first layer's bias gradient sums it)
+// and as bfloat16 (the operand of the first layer's two gradient products).
+static void FeedForwardBackward(BackwardRecord& r, const Tensor& g) {
+  const Tensor& x = r.Saved(0);
+  const Tensor& w1 = r.Saved(1);
+  const Tensor& w2 = r.Saved(2);
+  const Tensor& pre = r.Saved(3);
+  const Tensor& act16 = r.Saved(4);
+  const int rows = (int)r.Ints[0], inF = (int)r.Ints[1], ff = (int)r.Ints[2], outF = (int)r.Ints[3], op = (int)r.Ints[4];
+  Tensor gc = g.Contiguous();
+  struct Leaf {
+    float* p = nullptr;
+    bool acc = false, leaf = false, need = false;
+    Tensor t;
+  };
+  auto target = [&](int i) {
+    Leaf l;
+    l.need = r.NeedsInputGrad(i);
+    if (!l.need) return l;
+    l.leaf = Engine::LeafTarget(r, i, &l.p, &l.acc);
+    if (!l.leaf) {
+      l.t = Tensor::Create(DType::F32, r.InputShapes[i]);
+      l.p = l.t.Data();
+    }
+    return l;
+  };
+  auto done = [&](int i, Leaf& l) {
+    if (!l.need) return;
+    if (l.leaf) Engine::LeafWritten(r, i); else Engine::Emit(r, i, l.t, true);
+  };
+  Leaf dw1 = target(1), db1 = target(2), dw2 = target(3), db2 = target(4);
+  const uint16_t* g16 = gc.Bf16();
+  // Second layer: weight and bias gradients, then the input gradient through the activation.
+  if (dw2.p) Check(om_linear_bwd_bf16_b16(C(), g16, gc.Data(), outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, dw2.p, nullptr, dw2.acc ? 1 : 0));
+  if (db2.p) Check(om_linear_bwd_bf16_b16(C(), g16, gc.Data(), outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, nullptr, db2.p, db2.acc ? 1 : 0));
+  done(4, db2);
+  done(3, dw2);
+  if (!dw1.p && !db1.p && !r.NeedsInputGrad(0)) return;
+  Shape hs = pre.GetShape();
+  Tensor dpre = Tensor::Create(DType::F32, hs);
+  Check(om_linear_dgrad_bf16_act(C(), g16, outF, w2.Bf16(), rows, ff, outF, op, pre.Data(), ff, dpre.Data(), dpre.Bf16ForWrite()));
+  dpre.Bf16Written();
+  // First layer.
+  Tensor dx;
+  bool dx_into_pending = false;
+  if (r.NeedsInputGrad(0)) {
+    dx_into_pending = Engine::PendingTarget(r, 0, &dx);
+    if (!dx_into_pending) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+  }
+  const int accx = dx_into_pending ? 2 : 0;
+  if (dw1.acc == db1.acc || !dw1.p || !db1.p) {
+    LinearBwdCall(dpre, 0, ff, x, w1, rows, inF, ff, dx.IsEmpty() ? nullptr : dx.Data(), dw1.p, db1.p, ((dw1.p ? dw1.acc : db1.acc) ? 1 : 0) | accx);
+  } else {
+    LinearBwdCall(dpre, 0, ff, x, w1, rows, inF, ff, dx.IsEmpty() ? nullptr : dx.Data(), dw1.p, nullptr, (dw1.acc ? 1 : 0) | accx);
+    LinearBwdCall(dpre, 0, ff, x, w1, rows, inF, ff, nullptr, nullptr, db1.p, db1.acc ? 1 : 0);
+  }
+  done(2, db1);
+  if (dx_into_pending) Engine::PendingWritten(r, 0);
+  else if (!dx.IsEmpty()) Engine::Emit(r, 0, dx, true);
+  done(1, dw1);
+}
+
 static bool GemmLayout(const Tensor& t, int* trans, int* ld) {
   int64_t s0 = t.Strides()[0], s1 = t.Strides()[1];
   int rr = t.GetShape()[0], c = t.GetShape()[1];
@@ -489,6 +553,7 @@ void RunBackwardOp(Engine& e, BackwardRecord& r, const Tensor& g) {
     case OpKind::Tanh: Engine::Emit(r, 0, UnaryGrad(OM_TANH, g, r.Saved(0)), true); break;
     case OpKind::MatMul: MatMulBackward(r, g); break;
     case OpKind::Linear: LinearBackward(e, r, g); break;
+    case OpKind::FeedForward: FeedForwardBackward(r, g); break;
     case OpKind::Slice: {
       Tensor dx = Tensor::Zeros(DType::F32, r.InputShapes[0]);
       Tensor dst = dx.Slice((int)r.Ints[0], (int)r.Ints[1], (int)r.Ints[2], (int)r.Ints[3]);

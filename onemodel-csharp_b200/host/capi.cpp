@@ -183,6 +183,7 @@ OMH_API int32_t omh_call(const char* op, int32_t n_in, omh_tensor* const* in, in
     else if (name == "bce_with_logits") r = Losses::BceWithLogits(T(0), T(1), I(0, 1) != 0);
     else if (name == "dropout") r = Ops::Dropout(T(0), (float)F(0, 0.5), (uint64_t)I(0), T(1));
     else if (name == "linear") r = Ops::Linear(T(0), T(1), T(2));
+    else if (name == "feed_forward") r = Ops::FeedForward(T(0), T(1), T(2), T(3), T(4), I(0) != 0);
     else if (name == "attention") r = Ops::Attention(T(0), T(1), T(2), T(3), (float)F(0, 0));
     else if (name == "attention_heads") r = Ops::AttentionHeads(T(0), T(1), T(2), (int)I(0, 1), T(3), (float)F(0, 0));
     else if (name == "concat") {

@@ -245,7 +245,7 @@ TransformerEncoderLayer::TransformerEncoderLayer(int width, int heads, int ff, G
 Tensor TransformerEncoderLayer::Forward(const Tensor& input, const Tensor& mask) {
   Tensor a = Attn->Forward(input, mask);
   Tensor x1 = Norm1->Forward(Ops::Add(input, a));
-  Tensor f = Ff2->Forward(Ops::Gelu(Ff1->Forward(x1)));
+  Tensor f = Ops::FeedForward(x1, Ff1->Weight, Ff1->Bias, Ff2->Weight, Ff2->Bias);
   return Norm2->Forward(Ops::Add(x1, f));
 }
 

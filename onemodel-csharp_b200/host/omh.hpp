@@ -166,12 +166,13 @@ std::array<int64_t, kMaxRank> ContiguousStrides(const Shape& s);
 
 // ---- autograd types ---------------------------------------------------------------------------------------------------
 // The reference's 43 kinds (Autograd.cs:7-97) plus the fused kinds this backend records in their place: Linear for
-// the Reshape/MatMul/Add chain of Ops.Linear, CrossEntropy for LogSoftmax+NllLoss, GlobalAvgPool for Mean over planes.
+// the Reshape/MatMul/Add chain of Ops.Linear, CrossEntropy for LogSoftmax+NllLoss, GlobalAvgPool for Mean over planes,
+// FeedForward for Linear -> Gelu -> Linear when the activation rides in the products' epilogues.
 enum class OpKind {
   None = 0, Add, Sub, Mul, Div, Neg, Relu, MatMul, MaxPool2d, Cast, Slice, Permute, Reshape, Expand, Flip, Select, Gelu,
   Sigmoid, Tanh, Sum, Mean, Softmax, LogSoftmax, LayerNorm, BatchNorm, Conv2d, AvgPool2d, Concat, Embedding, NllLoss,
   Attention, Lstm, Gru, CtcLoss, ConvTranspose2d, Resize2d, Conv1d, BatchMatMul, Erf, Exp, Sqrt, Pow, Where, Gather,
-  Linear, CrossEntropy, Dropout
+  Linear, CrossEntropy, Dropout, FeedForward
 };
 
 struct AutogradMeta {
@@ -316,6 +317,11 @@ struct Ops {
   // Several Linear layers over the same input whose weights (and biases) are adjacent in memory, as one product:
   // returns [..., sum of out features]. Throws when the parameters are not adjacent.
   static Tensor LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, const std::vector<Tensor>& biases);
+  // Linear(Gelu(Linear(x, w1, b1)), w2, b2), the feed-forward block of an encoder layer. Under bfloat16 products (and
+  // shapes the fused kernels take) the activation and its derivative are applied in the epilogues of the first forward
+  // product and of the second layer's input-gradient product; the values are those of the three separate ops, which is
+  // what runs otherwise.
+  static Tensor FeedForward(const Tensor& x, const Tensor& w1, const Tensor& b1, const Tensor& w2, const Tensor& b2, bool approximateTanh = false);
   static bool Adjacent(const std::vector<Tensor>& parts);
   // Self-attention over the packed projections [B, L, 3 * H * D] (q | k | v along the last axis).
   static Tensor AttentionPacked(const Tensor& qkv, int heads, const Tensor& mask, float scale = 0.f);

@@ -350,6 +350,43 @@ Tensor Ops::Linear(const Tensor& x, const Tensor& weight, const Tensor& bias) {
   return rec->Attach(r);
 }
 
+Tensor Ops::FeedForward(const Tensor& x, const Tensor& w1, const Tensor& b1, const Tensor& w2, const Tensor& b2, bool tanhForm) {
+  const int op = tanhForm ? OM_GELU_TANH : OM_GELU_ERF;
+  bool fused = Bf16Products() && !b1.IsEmpty() && !b2.IsEmpty() && w1.Rank() == 2 && w2.Rank() == 2 && x.Rank() >= 1 &&
+               x.GetDType() == DType::F32 && x.GetShape()[x.Rank() - 1] == w1.GetShape()[1] && w2.GetShape()[1] == w1.GetShape()[0];
+  int inF = 0, ff = 0, outF = 0, rows = 0;
+  Tensor xc, w1c, w2c;
+  if (fused) {
+    inF = w1.GetShape()[1], ff = w1.GetShape()[0], outF = w2.GetShape()[0];
+    rows = (int)(x.Length() / std::max(1, inF));
+    xc = x.Contiguous(), w1c = w1.Contiguous(), w2c = w2.Contiguous();
+    fused = rows > 0 && Bf16Operand(xc, inF) && Bf16Operand(w1c, inF) && Bf16Operand(w2c, ff) && (outF & 7) == 0 &&
+            om_linear_act_bf16_supported(C(), rows, inF, ff, op, 0) == 1 && om_linear_act_bf16_supported(C(), rows, ff, outF, op, 1) == 1;
+  }
+  if (!fused) return Linear(Gelu(Linear(x, w1, b1), tanhForm), w2, b2);
+  Tensor b1c = b1.Contiguous(), b2c = b2.Contiguous();
+  Shape hs = x.GetShape(), os = x.GetShape();
+  hs.d[hs.rank - 1] = ff;
+  os.d[os.rank - 1] = outF;
+  // The first layer's result before the activation (fp32: the activation's backward needs it) and the activation's
+  // result as bfloat16 only (two per 32-bit word of an integer tensor): nothing but the second product reads it.
+  Tensor pre = NewOut(hs);
+  Tensor act16 = Tensor::Create(DType::I32, Shape{rows, ff / 2});
+  ActivationScope::Track(act16);
+  Check(om_linear_fwd_bf16_act(C(), xc.Bf16(), w1c.Bf16(), b1c.Data(), rows, inF, ff, op, pre.Data(), (uint16_t*)act16.RawData(), ff));
+  Tensor r = NewOut(os);
+  Check(om_linear_fwd_bf16(C(), (const uint16_t*)act16.RawData(), w2c.Bf16(), b2c.Data(), rows, ff, outF, r.Data(), outF));
+  if (!Recording({&x, &w1, &b1, &w2, &b2})) return r;
+  auto rec = BackwardRecord::Create(OpKind::FeedForward, 5, {&x, &w1, &b1, &w2, &b2});
+  rec->Save(0, xc.Detach());
+  rec->Save(1, w1c.Detach());
+  rec->Save(2, w2c.Detach());
+  rec->Save(3, pre.Detach());
+  rec->Save(4, act16);
+  rec->Ints = {rows, inF, ff, outF, op};
+  return rec->Attach(r);
+}
+
 Tensor Ops::Attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& mask, float scale) {
   if (q.Rank() != 4 || k.Rank() != 4 || v.Rank() != 4 || k.GetShape() != v.GetShape() || q.GetShape()[0] != k.GetShape()[0] ||
       q.GetShape()[1] != k.GetShape()[1] || q.GetShape()[3] != k.GetShape()[3] || q.GetShape()[3] % 2 != 0)

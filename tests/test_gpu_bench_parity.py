@@ -107,16 +107,70 @@ def test_c3_full_size_step_with_the_bench_flags(ctx, configs, capsys):
 
 def test_c5_slice_with_bf16_operands(ctx, configs, capsys):
     """BERT-base shape (12 x d768 h12 ff3072, seq 512, vocab 30522) on a batch-2 slice, the products of the Linear layers
-    with bf16 operands (round to nearest even) and fp32 accumulation, fp32 master weights. Against the oracle that rounds
-    the operands of the same products the same way: what is left is the summation order, the attention kernels' TF32
-    products, and operands that sit within an fp32 rounding error of a bfloat16 rounding boundary and round the other way
-    on one side (a step of 2^-9 relative in that operand); held to 2e-2 scaled over the 12-layer chain (measured 3e-3 on
-    most tensors and up to 1e-2 on the key projections, whose gradient is a small difference of large terms under the
-    softmax's shift invariance). Against the fp32 oracle the bfloat16 rounding itself shows: 8 significant bits per operand, held
-    to 3e-2."""
+    and of the attention backward with bfloat16 operands (round to nearest even), fp32 accumulation, fp32 master weights.
+
+    Three statements per compared step (an eager one and one replayed from the graph).
+    (1) The loss is within 2e-3 of the fp32 oracle's and within 1e-3 of the oracle that rounds the same operands.
+    (2) Every parameter gradient except the query and key projections' is within 1e-2 scaled of the fp32 oracle.
+    (3) The gradients of the query and key projections cannot be held to a fixed gate by any implementation that rounds
+    operands to 8 significant bits: at these near-uniform attention weights they are a small remainder of large terms
+    (the softmax's shift invariance: the key bias gradient, zero in exact arithmetic, is the limit case), and the
+    remainder shrinks from step to step while the rounding noise stays. The test measures this on the CPU: the oracle
+    with bfloat16-rounded operands differs from the fp32 oracle by 0.7e-2 at the first step and by 2 to 5e-2 two AdamW
+    steps later. The GPU is held to at most 2.5 times that distance from the fp32 oracle, parameter by parameter (never
+    below the 1e-2 of statement 2), and the key biases to 5 per cent of the model's largest gradient on both sides."""
+    from oracle import tape
     cfg = [2, 512, 12, 768, 12, 3072, 30522, 154]
-    run_mlm(ctx, configs, cfg, omb.OM_TF32 | omb.OM_BF16_OPERANDS, "bf16", 2e-2, 1e-3, "c5 slice vs bf16-rounding oracle", capsys, noise_floor=0.05)
-    run_mlm(ctx, configs, cfg, omb.OM_TF32 | omb.OM_BF16_OPERANDS, "fp32", 3e-2, 2e-3, "c5 slice vs fp32 oracle", capsys, noise_floor=0.05)
+    batch, seq, layers, width, heads, ff, vocab, rows = cfg
+    ctx.set_flags(omb.OM_TF32 | omb.OM_BF16_OPERANDS)
+    ctx.make_current()
+    report = []
+    tr = omb.Trainer("mlm", cfg, lr=1e-4, weight_decay=0.01, seed=0)
+    try:
+        named = tr.named_parameters()
+        weights = {n: tr.get_param(i, s) for i, (n, s) in enumerate(named)}
+        state = {}
+        for step in range(3):
+            ids, pos, labels = synth.mlm_batch(batch, seq, vocab, rows, step)
+            ids64, pos64 = ids.astype(np.int64), pos.astype(np.int64)
+            if step == 2:
+                tr.enable_graph()
+            if step > 0:
+                sync_parameters(tr, named, weights)
+            lg = tr.step([ids, pos, labels])
+            if step != 1:
+                tape.GEMM_MODE = "bf16"
+                l16, g16 = configs.mlm_forward_backward(weights, ids64, pos64, labels, layers, heads)
+                tape.GEMM_MODE = "fp32"
+            lo, grads = configs.mlm_step(weights, ids64, pos64, labels, layers, heads, step + 1, state, lr=1e-4)
+            assert abs(lg - lo) <= 2e-3 * abs(lo), (step, lg, lo)
+            if step == 1:
+                continue
+            assert abs(lg - l16) <= 1e-3 * abs(l16), (step, lg, l16)
+            largest = max(float(np.max(np.abs(g))) for g in grads.values())
+            worst = [0.0, "", 0.0]
+            worst_qk = [0.0, "", 0.0]
+            for i, (n, s) in enumerate(named):
+                got, want, model = tr.get_grad(i, s), grads[n], g16[n]
+                if n.endswith("attn.k.bias"):
+                    assert max(float(np.max(np.abs(got))), float(np.max(np.abs(model)))) <= 0.05 * largest, (step, n)
+                    continue
+                d_gpu, d_model = scaled_diff(got, want), scaled_diff(model, want)
+                qk = ".attn.q." in n or ".attn.k." in n
+                w = worst_qk if qk else worst
+                if d_gpu > w[0]:
+                    w[:] = [d_gpu, n, d_model]
+                assert d_gpu <= (max(1e-2, 2.5 * d_model) if qk else 1e-2), (step, n, d_gpu, d_model)
+                assert scaled_diff(got, model) <= max(1e-2, 2.5 * d_model), (step, n, scaled_diff(got, model), d_model)
+            report.append(f"c5 slice step {step} ({'graph replay' if step == 2 else 'eager'}): loss {lg:.6f}, fp32 oracle {lo:.6f}, bf16-operand oracle {l16:.6f}; "
+                          f"worst gradient vs fp32 oracle {worst[0]:.2e} ({worst[1]}; the CPU model of the same rounding is {worst[2]:.2e} away); "
+                          f"query/key projections {worst_qk[0]:.2e} ({worst_qk[1]}; CPU model {worst_qk[2]:.2e})")
+    finally:
+        tape.GEMM_MODE = "fp32"
+        tr.close()
+        ctx.set_flags(0)
+    with capsys.disabled():
+        print("\n" + "\n".join(report))
 
 
 def test_c2_full_size_step_with_the_bench_flags(ctx, configs, capsys):

@@ -158,3 +158,119 @@ def test_bf16_copy_of_the_result_from_the_product_epilogue(ctx, oracle_built, ro
     assert scaled_diff(dx, K.gemm(g, w, mode="bf16")) <= 2e-5
     assert np.array_equal(Y16.numpy(), (K.round_bf16(y).view(np.uint32) >> 16).astype(np.uint16))
     assert np.array_equal(DX16.numpy(), (K.round_bf16(dx).view(np.uint32) >> 16).astype(np.uint16))
+
+
+ACT_SHAPES = [(4096, 768, 3072), (8192, 1024, 512), (300, 136, 264), (1000, 200, 520), (256, 64, 256)]
+
+
+@pytest.mark.parametrize("op", [omb.UNARY["gelu_erf"], omb.UNARY["gelu_tanh"]])
+@pytest.mark.parametrize("rows,inf,outf", ACT_SHAPES)
+def test_activation_in_the_forward_epilogue_equals_the_separate_pass(ctx, rows, inf, outf, op):
+    """om_linear_fwd_bf16_act against om_linear_fwd_bf16 followed by om_unary_b16: the same fp32 result before the
+    activation and the same bfloat16 activation, bit for bit (one definition of the activation, no fused multiply-add)."""
+    r = np.random.default_rng(rows + inf + op)
+    x, w = r.standard_normal((rows, inf)).astype(np.float32), (r.standard_normal((outf, inf)) * 0.1).astype(np.float32)
+    bias = r.standard_normal(outf).astype(np.float32)
+    X16, W16, Bv = to_bf16(ctx, x), to_bf16(ctx, w), ctx.to_device(bias)
+    assert ctx.lib.om_linear_act_bf16_supported(ctx.handle, i32(rows), i32(inf), i32(outf), i32(op), i32(0)) == 1
+    Y, A16 = ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16)
+    ctx.call("om_linear_fwd_bf16_act", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), i32(op), Y.ptr, A16.ptr, i32(outf))
+    Y2, A2, A216 = ctx.empty((rows, outf)), ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16)
+    ctx.call("om_linear_fwd_bf16", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), Y2.ptr, i32(outf))
+    ctx.call("om_unary_b16", ctx.handle, i32(op), Y2.ptr, A2.ptr, A216.ptr, i64(rows * outf))
+    ctx.sync()
+    assert np.array_equal(Y.numpy(), Y2.numpy())
+    assert np.array_equal(A16.numpy(), A216.numpy())
+    assert np.any(A16.numpy() != 0)
+
+
+@pytest.mark.parametrize("op", [omb.UNARY["gelu_erf"], omb.UNARY["gelu_tanh"]])
+@pytest.mark.parametrize("rows,outf,inf", ACT_SHAPES)
+def test_activation_derivative_in_the_input_gradient_epilogue_equals_the_separate_pass(ctx, rows, outf, inf, op):
+    """om_linear_dgrad_bf16_act (dx = op'(pre) * (g W)) against om_linear_bwd_bf16_b16 followed by om_unary_bwd_b16: the same
+    fp32 gradient and the same bfloat16 copy, bit for bit. (The layer has `inf` inputs, the width of the activation, and
+    `outf` outputs.)"""
+    r = np.random.default_rng(rows + inf + 7 * op)
+    g, w = r.standard_normal((rows, outf)).astype(np.float32), (r.standard_normal((outf, inf)) * 0.1).astype(np.float32)
+    pre = (r.standard_normal((rows, inf)) * 1.5).astype(np.float32)
+    G16, W16, G, PRE = to_bf16(ctx, g), to_bf16(ctx, w), ctx.to_device(g), ctx.to_device(pre)
+    X16 = ctx.empty((rows, inf), np.uint16)
+    assert ctx.lib.om_linear_act_bf16_supported(ctx.handle, i32(rows), i32(inf), i32(outf), i32(op), i32(1)) == 1
+    DX, DX16 = ctx.empty((rows, inf)), ctx.empty((rows, inf), np.uint16)
+    ctx.call("om_linear_dgrad_bf16_act", ctx.handle, G16.ptr, i32(outf), W16.ptr, i32(rows), i32(inf), i32(outf), i32(op), PRE.ptr, i32(inf), DX.ptr, DX16.ptr)
+    T, D2, D216 = ctx.empty((rows, inf)), ctx.empty((rows, inf)), ctx.empty((rows, inf), np.uint16)
+    ctx.call("om_linear_bwd_bf16_b16", ctx.handle, G16.ptr, G.ptr, i32(outf), X16.ptr, W16.ptr, i32(rows), i32(inf), i32(outf), T.ptr, None, None, None, i32(0))
+    ctx.call("om_unary_bwd_b16", ctx.handle, i32(op), T.ptr, PRE.ptr, D2.ptr, D216.ptr, i64(rows * inf))
+    ctx.sync()
+    assert np.array_equal(DX.numpy(), D2.numpy())
+    assert np.array_equal(DX16.numpy(), D216.numpy())
+    # without the bfloat16 copy
+    DX3 = ctx.empty((rows, inf))
+    ctx.call("om_linear_dgrad_bf16_act", ctx.handle, G16.ptr, i32(outf), W16.ptr, i32(rows), i32(inf), i32(outf), i32(op), PRE.ptr, i32(inf), DX3.ptr, None)
+    ctx.sync()
+    assert np.array_equal(DX3.numpy(), D2.numpy())
+
+
+def test_shapes_that_cannot_take_the_activation_are_refused(ctx):
+    sup = lambda rows, inf, outf, bwd: ctx.lib.om_linear_act_bf16_supported(ctx.handle, i32(rows), i32(inf), i32(outf), i32(omb.UNARY["gelu_erf"]), i32(bwd))
+    assert sup(4096, 768, 128, 0) == 0          # fewer than 256 result columns
+    assert sup(256, 4096, 256, 0) == 0          # one tile and 64 k-blocks: k is split, the activation would see partial sums
+    assert sup(4096, 770, 3072, 0) == 0         # operand pitch not a multiple of 8
+    assert ctx.lib.om_linear_act_bf16_supported(ctx.handle, i32(4096), i32(768), i32(3072), i32(omb.UNARY["relu"]), i32(0)) == 0
+    x16, w16 = ctx.empty((256, 4096), np.uint16), ctx.empty((256, 4096), np.uint16)
+    y, a16, b = ctx.empty((256, 256)), ctx.empty((256, 256), np.uint16), ctx.zeros((256,))
+    with pytest.raises(omb.OmError):
+        ctx.call("om_linear_fwd_bf16_act", ctx.handle, x16.ptr, w16.ptr, b.ptr, i32(256), i32(4096), i32(256), i32(omb.UNARY["gelu_erf"]), y.ptr, a16.ptr, i32(256))
+    ctx.sync()
+
+
+@pytest.mark.parametrize("flags", [0, omb.OM_TF32 | omb.OM_BF16_OPERANDS])
+def test_feed_forward_op_equals_its_three_parts(ctx, flags):
+    """The host mirror's FeedForward (Linear -> Gelu -> Linear with the activation in the epilogues under bfloat16 products)
+    against the composition of the three ops on the same flags: result and all five gradients bit for bit, with the input
+    also feeding a residual sum so that its gradient arrives from two branches."""
+    ctx.set_flags(flags)
+    ctx.make_current()
+    try:
+        r = np.random.default_rng(3)
+        rows, width, ff = 1024, 256, 1024
+        xv = r.standard_normal((4, rows // 4, width)).astype(np.float32)
+        vals = [(r.standard_normal((ff, width)) * 0.06).astype(np.float32), (r.standard_normal(ff) * 0.1).astype(np.float32),
+                (r.standard_normal((width, ff)) * 0.03).astype(np.float32), (r.standard_normal(width) * 0.1).astype(np.float32)]
+        up = r.standard_normal(xv.shape).astype(np.float32)
+        results = []
+        for fused in (True, False):
+            x = omb.Tensor.from_numpy(xv, True)
+            ps = [omb.Tensor.from_numpy(v, True) for v in vals]
+            if fused:
+                f = omb.call("feed_forward", [x] + ps, ints=[0])
+            else:
+                f = omb.call("linear", [omb.call("gelu", [omb.call("linear", [x, ps[0], ps[1]])], ints=[0]), ps[2], ps[3]])
+            y = omb.call("add", [x, f])
+            y.backward(omb.Tensor.from_numpy(up))
+            results.append([y.numpy(), x.grad.numpy()] + [p.grad.numpy() for p in ps])
+        for a, b in zip(*results):
+            assert np.all(np.isfinite(a)) and np.array_equal(a, b)
+    finally:
+        ctx.set_flags(0)
+
+
+def test_short_erf_of_the_bf16_tier_is_within_1e_6(ctx, oracle_built):
+    """With a bfloat16 copy requested the erf GELU and its derivative use the short branch-free erf (rational form, hardware
+    exp and reciprocal): within 1e-6 absolute of the oracle's libm values over a dense grid, including the far tails, zero,
+    and values around the sign change; the bfloat16 copy is the fp32 value rounded."""
+    K = oracle_built
+    x = np.concatenate([np.linspace(-9, 9, 400001), np.array([0.0, -0.0, 1e-30, -1e-30, 1e-8, 40.0, -40.0])]).astype(np.float32)
+    g = np.ones_like(x)
+    n = x.size
+    X, G = ctx.to_device(x), ctx.to_device(g)
+    Y, Y16, D, D16 = ctx.empty((n,)), ctx.empty((n,), np.uint16), ctx.empty((n,)), ctx.empty((n,), np.uint16)
+    op = omb.UNARY["gelu_erf"]
+    ctx.call("om_unary_b16", ctx.handle, i32(op), X.ptr, Y.ptr, Y16.ptr, i64(n))
+    ctx.call("om_unary_bwd_b16", ctx.handle, i32(op), G.ptr, X.ptr, D.ptr, D16.ptr, i64(n))
+    ctx.sync()
+    y, d = Y.numpy(), D.numpy()
+    assert np.max(np.abs(y - K.unary("gelu_erf", x))) <= 1e-6
+    assert np.max(np.abs(d - K.unary_bwd("gelu_erf", g, x))) <= 1e-6
+    assert np.array_equal(Y16.numpy(), (K.round_bf16(y).view(np.uint32) >> 16).astype(np.uint16))
+    assert np.array_equal(D16.numpy(), (K.round_bf16(d).view(np.uint32) >> 16).astype(np.uint16))

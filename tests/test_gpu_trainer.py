@@ -205,3 +205,52 @@ def test_blocks_of_a_captured_step_are_not_handed_to_other_tensors(ctx):
             assert np.all(t.numpy() == v), (t.shape, v)
     finally:
         tr.close()
+
+
+@pytest.mark.parametrize("depth", [1, 2, 4])
+def test_batches_staged_ahead_give_the_same_run(ctx, depth):
+    """The loader's prefetch ring on the device (docs/data-loading.md section 1 of the reference: batches are delivered in
+    step order whatever the prefetch depth): batches staged up to `depth` steps ahead on the copy stream, eager and replayed
+    from a captured graph, give the losses and parameters of the plain step(batch) loop bit for bit; staging into a full
+    ring and stepping on an empty one are refused."""
+    ctx.set_flags(0)
+    ctx.make_current()
+    cfg = [4, 16, 2, 32, 4, 64, 101, 10]
+    batches = [synth.mlm_batch(4, 16, 101, 10, s) for s in range(8)]
+
+    def plain():
+        tr = omb.Trainer("mlm", cfg, lr=1e-3, weight_decay=0.01, seed=0)
+        losses = []
+        for s, b in enumerate(batches):
+            if s == 2:
+                tr.enable_graph()
+            losses.append(np.float32(tr.step(list(b))))
+        params = [tr.get_param(i, sh) for i, (_, sh) in enumerate(tr.named_parameters())]
+        tr.close()
+        return losses, params
+
+    def staged():
+        tr = omb.Trainer("mlm", cfg, lr=1e-3, weight_decay=0.01, seed=0)
+        tr.prefetch_depth(depth)
+        with pytest.raises(omb.OmError):
+            tr.step_prefetched()                       # nothing staged yet
+        losses, nxt = [], 0
+        for s in range(len(batches)):
+            while nxt < len(batches) and nxt - s < depth:
+                tr.prefetch(list(batches[nxt]))
+                nxt += 1
+            if s == 0 and nxt < len(batches):
+                with pytest.raises(omb.OmError):
+                    tr.prefetch(list(batches[nxt]))    # the ring is full
+            if s == 2:
+                tr.enable_graph()
+            losses.append(np.float32(tr.step_prefetched()))
+        params = [tr.get_param(i, sh) for i, (_, sh) in enumerate(tr.named_parameters())]
+        tr.close()
+        return losses, params
+
+    la, pa = plain()
+    lb, pb = staged()
+    assert np.array_equal(np.array(la), np.array(lb))
+    for a, b in zip(pa, pb):
+        assert np.array_equal(a, b)
