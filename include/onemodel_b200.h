@@ -455,13 +455,15 @@ int32_t om_attention_bwd_strided_out(om_ctx* ctx, const float* g, const om_head_
                                      float scale, float* dq, const om_head_strides* dqs, float* dk,
                                      const om_head_strides* dks, float* dv, const om_head_strides* dvs);
 /* AttentionBackward (src/OneModel/Tensors/Autograd/BackwardNn.cs:636-701) for sequences of several 128-key tiles with
- * bfloat16 product operands, in one kernel per call: a CTA per (batch, head) forms S = Q K^T and dP = dO V^T tile by tile
- * in tensor memory, P = exp(scale S + mask - lse) and dS = P (dP - rowsum(dO o O)) scale in registers (rounded to
- * bfloat16 as the operands of the three output products), and accumulates dV, dK (per key tile) and dQ (all query tiles)
- * in tensor memory: nothing of size Lq x Lk is written to memory. q16 / k16 / v16 / g16 are the bfloat16 copies of q, k, v
- * and of the output gradient g; g and out (the forward's output) are read in fp32 for the row dots; lse is the forward's
- * row log-sum-exp. Results are fp32 with optional bfloat16 copies (dq16 / dk16 / dv16, same strides). Built for head
- * dimension 64 and Lq <= 512 (om_attention_bwd_bf16_supported tells); strides of the bfloat16 operands multiples of 8. */
+ * bfloat16 product operands: a CTA per (batch, head, 128-key tile) forms S = Q K^T and dP = dO V^T half a tile at a time
+ * in two alternating accumulator buffers of tensor memory, P = exp(scale S + mask - lse) and dS = P (dP - rowsum(dO o O))
+ * scale in registers (rounded to bfloat16 as the operands of the three output products), accumulates dV and dK of its key
+ * tile over the query tiles in tensor memory, and writes its part of dQ per query tile to a pooled workspace; a second
+ * launch sums the parts of dQ over the key tiles in increasing order (a first one forms the row dots). Nothing of size
+ * Lq x Lk is written to memory. q16 / k16 / v16 / g16 are the bfloat16 copies of q, k, v and of the output gradient g; g and
+ * out (the forward's output) are read in fp32 for the row dots; lse is the forward's row log-sum-exp. Results are fp32
+ * with optional bfloat16 copies (dq16 / dk16 / dv16, same strides). Built for head dimension 64, any Lq and Lk, at most
+ * 65535 (batch, head) pairs (om_attention_bwd_bf16_supported tells); strides of the bfloat16 operands multiples of 8. */
 int32_t om_attention_bwd_bf16_supported(om_ctx* ctx, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d);
 int32_t om_attention_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, const om_head_strides* gs,
                               const uint16_t* q16, const om_head_strides* qs, const uint16_t* k16, const om_head_strides* ks,

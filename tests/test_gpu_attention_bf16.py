@@ -31,7 +31,7 @@ def bf16_bits(K, a):
 
 
 @pytest.mark.parametrize("b,h,lq,lk,masked", [(1, 2, 512, 512, 0), (2, 3, 256, 256, 1), (1, 2, 300, 200, 0), (1, 1, 129, 640, 1), (1, 2, 512, 128, 0),
-                                              (1, 1, 5, 7, 0), (2, 12, 512, 512, 0)])
+                                              (1, 1, 5, 7, 0), (2, 12, 512, 512, 0), (1, 2, 1100, 384, 1), (3, 1, 128, 128, 0)])
 def test_fused_attention_backward_with_bf16_operands(ctx, oracle_built, b, h, lq, lk, masked):
     K = oracle_built
     d = 64
@@ -76,5 +76,6 @@ def test_fused_attention_backward_with_bf16_operands(ctx, oracle_built, b, h, lq
 
 
 def test_shapes_outside_the_fused_kernel_are_refused(ctx):
-    assert ctx.lib.om_attention_bwd_bf16_supported(ctx.handle, i32(1), i32(1), i32(513), i32(512), i32(64)) == 0
+    assert ctx.lib.om_attention_bwd_bf16_supported(ctx.handle, i32(1), i32(1), i32(4096), i32(4096), i32(64)) == 1
     assert ctx.lib.om_attention_bwd_bf16_supported(ctx.handle, i32(1), i32(1), i32(256), i32(256), i32(32)) == 0
+    assert ctx.lib.om_attention_bwd_bf16_supported(ctx.handle, i32(256), i32(256), i32(256), i32(256), i32(64)) == 0
