@@ -454,6 +454,18 @@ int32_t om_attention_bwd_strided_out(om_ctx* ctx, const float* g, const om_head_
                                      const float* lse, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d,
                                      float scale, float* dq, const om_head_strides* dqs, float* dk,
                                      const om_head_strides* dks, float* dv, const om_head_strides* dvs);
+/* Ops.Attention forward (src/OneModel/Tensors/Ops.Layers.cs, the attention op that AttentionBackward differentiates) with
+ * bfloat16 product operands, for sequences of several tiles: out = softmax(scale q k^T + mask) v per (batch, head), from the
+ * bfloat16 copies of q, k, v. A CTA per (128 queries, batch, head) walks the key tiles twice (row maxima first; then
+ * exponentials, their fp32 row sums and the second product with the exponentials rounded to bfloat16), two CTAs per SM.
+ * out is fp32, out16 (may be NULL) its bfloat16 copy with the same strides, lse (may be NULL) the row log-sum-exp
+ * [b * h, lq] that om_attention_bwd_bf16 takes. Built for head dimension 64, any lq and lk, a positive scale, at most 65535
+ * (batch, head) pairs (om_attention_fwd_bf16_supported tells); operand strides multiples of 8. */
+int32_t om_attention_fwd_bf16_supported(om_ctx* ctx, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d, float scale);
+int32_t om_attention_fwd_bf16(om_ctx* ctx, const uint16_t* q16, const om_head_strides* qs, const uint16_t* k16,
+                              const om_head_strides* ks, const uint16_t* v16, const om_head_strides* vs, const float* mask,
+                              int64_t mask_batch_stride, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d, float scale,
+                              float* out, uint16_t* out16, const om_head_strides* os, float* lse);
 /* AttentionBackward (src/OneModel/Tensors/Autograd/BackwardNn.cs:636-701) for sequences of several 128-key tiles with
  * bfloat16 product operands: a CTA per (batch, head, 128-key tile) forms S = Q K^T and dP = dO V^T half a tile at a time
  * in two alternating accumulator buffers of tensor memory, P = exp(scale S + mask - lse) and dS = P (dP - rowsum(dO o O))

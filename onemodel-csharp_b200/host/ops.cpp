@@ -546,8 +546,17 @@ Tensor Ops::AttentionPacked(const Tensor& qkv, int heads, const Tensor& mask, fl
   om_head_strides ps{(int64_t)l * 3 * width, (int64_t)d, (int64_t)3 * width}, os{(int64_t)l * width, (int64_t)d, (int64_t)width};
   const bool recording = Recording({&qkv});
   Tensor lse = recording ? Tensor::Create(DType::F32, Shape{b, heads, l}) : Tensor();
-  Check(om_attention_fwd_strided(C(), pc.Data(), &ps, pc.Data() + width, &ps, pc.Data() + 2 * width, &ps, mc.IsEmpty() ? nullptr : mc.Data(),
-                                 maskStride, b, heads, l, l, d, scale, r.Data(), &os, lse.IsEmpty() ? nullptr : lse.Data()));
+  // Under bfloat16 products a sequence of several tiles runs on the bfloat16 forward: it reads the copy of q | k | v that the
+  // packed projection wrote and writes the copy of its result that the output projection reads.
+  if (Bf16Products() && l > 128 && Bf16Operand(pc, 3 * width) && width % 8 == 0 && om_attention_fwd_bf16_supported(C(), b, heads, l, l, d, scale) == 1) {
+    const uint16_t* p16 = pc.Bf16();
+    Check(om_attention_fwd_bf16(C(), p16, &ps, p16 + width, &ps, p16 + 2 * width, &ps, mc.IsEmpty() ? nullptr : mc.Data(), maskStride, b, heads, l, l, d,
+                                scale, r.Data(), r.Bf16ForWrite(), &os, lse.IsEmpty() ? nullptr : lse.Data()));
+    r.Bf16Written();
+  } else {
+    Check(om_attention_fwd_strided(C(), pc.Data(), &ps, pc.Data() + width, &ps, pc.Data() + 2 * width, &ps, mc.IsEmpty() ? nullptr : mc.Data(),
+                                   maskStride, b, heads, l, l, d, scale, r.Data(), &os, lse.IsEmpty() ? nullptr : lse.Data()));
+  }
   if (!recording) return r;
   auto rec = BackwardRecord::Create(OpKind::Attention, 6, {&qkv});
   rec->Save(4, lse);

@@ -278,16 +278,38 @@ def attention_bwd(g, q, k, v, mask=None, scale=None):
     return dq, dk, dv
 
 
-def attention_bwd_bf16(g, q, k, v, mask=None, scale=None):
+def attention_fwd_bf16(q, k, v, mask=None, scale=None):
+    """The attention forward with the operands of its two products rounded to bfloat16 (nearest even) and everything else in
+    fp32: S = Q K^T from rounded q, k; E = exp(scale S + mask - rowmax) and its row sums in fp32; O = (E rounded) (V rounded)
+    divided by the row sums. The model of the forward's bfloat16 tier; plain numpy, for small cases."""
+    q, k, v = _f(q), _f(k), _f(v)
+    b, h, lq, d = q.shape
+    scale = np.float32(1.0) / np.sqrt(np.float32(d)) if scale is None else np.float32(scale)
+    qr, kr, vr = round_bf16(q), round_bf16(k), round_bf16(v)
+    out = np.empty_like(q)
+    for bi in range(b):
+        mb = None if mask is None else (mask if np.ndim(mask) == 2 else mask[bi])
+        for hi in range(h):
+            s = (qr[bi, hi] @ kr[bi, hi].T) * scale
+            if mb is not None:
+                s = s + _f(mb)
+            s64 = s.astype(np.float64)
+            e = np.exp(s64 - s64.max(axis=1, keepdims=True)).astype(np.float32)
+            total = e.astype(np.float64).sum(axis=1, keepdims=True)
+            out[bi, hi] = ((round_bf16(e) @ vr[bi, hi]).astype(np.float64) / total).astype(np.float32)
+    return out
+
+
+def attention_bwd_bf16(g, q, k, v, mask=None, scale=None, out=None):
     """AttentionBackward (BackwardNn.cs:636-701) with the operands of its five products rounded to bfloat16 (nearest even) and
     everything else in fp32: S = Q K^T and dP = dO V^T from rounded q, k, v, dO; P = softmax(scale S + mask) and the row dots
-    rowsum(dO o O) in fp32 (O from the fp32 forward); dS = P (dP - dot) scale; dV = P^T dO, dK = dS^T Q, dQ = dS K with P and
+    rowsum(dO o O) in fp32 (O given, or from the fp32 forward); dS = P (dP - dot) scale; dV = P^T dO, dK = dS^T Q, dQ = dS K with P and
     dS rounded. The model of the product's bfloat16 tier; plain numpy, for small cases."""
     g, q, k, v = _f(g), _f(q), _f(k), _f(v)
     b, h, lq, d = q.shape
     lk = k.shape[2]
     scale = np.float32(1.0) / np.sqrt(np.float32(d)) if scale is None else np.float32(scale)
-    out = attention_fwd(q, k, v, mask, scale)
+    out = attention_fwd(q, k, v, mask, scale) if out is None else _f(out)
     gr, qr, kr, vr = round_bf16(g), round_bf16(q), round_bf16(k), round_bf16(v)
     dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
     for bi in range(b):

@@ -322,17 +322,19 @@ def embedding(table, ids, pad=-1):
 
 def attention(q, k, v, mask=None, scale=None):
     qc, kc, vc = (np.ascontiguousarray(t.v) for t in (q, k, v))
+    # Under 'bf16' sequences of several tiles run forward and backward with bfloat16 product operands (the one-tile kernels
+    # keep TF32 operands, which the fp32 restatement stands for).
+    tier16 = GEMM_MODE == "bf16" and qc.shape[2] > 128 and qc.shape[3] == 64
+    y = K.attention_fwd_bf16(qc, kc, vc, mask, scale) if tier16 else K.attention_fwd(qc, kc, vc, mask, scale)
 
     def bw(r, g):
-        # Under 'bf16' the backward of sequences of several tiles runs with bfloat16 product operands (the forward and the
-        # one-tile backward keep the TF32 kernels, which the fp32 restatement stands for).
-        if GEMM_MODE == "bf16" and qc.shape[2] > 128 and qc.shape[3] == 64:
-            dq, dk, dv = K.attention_bwd_bf16(g, *r.saved, mask=mask, scale=scale)
+        if tier16:
+            dq, dk, dv = K.attention_bwd_bf16(g, *r.saved, mask=mask, scale=scale, out=y)
         else:
             dq, dk, dv = K.attention_bwd(g, *r.saved, mask=mask, scale=scale)
         return [(0, dq, "own"), (1, dk, "own"), (2, dv, "own")]
 
-    return _attach(K.attention_fwd(qc, kc, vc, mask, scale), Record("attention", [q, k, v], saved=(qc, kc, vc), backward=bw), [q, k, v])
+    return _attach(y, Record("attention", [q, k, v], saved=(qc, kc, vc), backward=bw), [q, k, v])
 
 
 def concat(xs, axis):

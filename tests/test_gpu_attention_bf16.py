@@ -1,4 +1,4 @@
-"""The fused several-tile attention backward with bfloat16 product operands (om_attention_bwd_bf16) against the CPU
+"""The several-tile attention forward (om_attention_fwd_bf16) and the fused backward (om_attention_bwd_bf16) with bfloat16 product operands against the CPU
 oracle: against the oracle's model of the same tier (the operands of the five products rounded to bfloat16, everything
 else fp32: what is left is the summation order, the TF32 forward that supplies the log-sum-exp, and values that round the
 other way at a bfloat16 boundary) and against the plain fp32 AttentionBackward, where the bfloat16 rounding of the
@@ -79,3 +79,59 @@ def test_shapes_outside_the_fused_kernel_are_refused(ctx):
     assert ctx.lib.om_attention_bwd_bf16_supported(ctx.handle, i32(1), i32(1), i32(4096), i32(4096), i32(64)) == 1
     assert ctx.lib.om_attention_bwd_bf16_supported(ctx.handle, i32(1), i32(1), i32(256), i32(256), i32(32)) == 0
     assert ctx.lib.om_attention_bwd_bf16_supported(ctx.handle, i32(256), i32(256), i32(256), i32(256), i32(64)) == 0
+
+
+@pytest.mark.parametrize("b,h,lq,lk,masked", [(1, 2, 512, 512, 0), (2, 3, 256, 256, 1), (1, 2, 300, 200, 0), (1, 1, 129, 640, 1), (1, 2, 512, 128, 0),
+                                              (1, 1, 5, 7, 0), (2, 12, 512, 512, 0), (1, 2, 1100, 384, 1), (3, 1, 128, 128, 0)])
+def test_attention_forward_with_bf16_operands(ctx, oracle_built, b, h, lq, lk, masked):
+    """om_attention_fwd_bf16 against the oracle's model of the same tier (q, k, v and the exponentials rounded to bfloat16, sums
+    in fp32: what is left is the summation order and exponentials that round the other way at a bfloat16 boundary) and
+    against the fp32 forward, where the bfloat16 rounding shows; the log-sum-exp against the fp32 one; the bfloat16 copy is
+    the fp32 result rounded; the same bits from run to run. Some masked cases hold -inf entries and one row masked out
+    entirely in all but one key."""
+    K = oracle_built
+    d = 64
+    r = np.random.default_rng(b * 11 + lq + 3 * lk)
+    q, k, v = (r.standard_normal(s).astype(np.float32) for s in [(b, h, lq, d), (b, h, lk, d), (b, h, lk, d)])
+    mask = None
+    if masked:
+        mask = np.where(r.random((lq, lk)) < 0.25, -4.0, 0.0).astype(np.float32)
+        mask[r.random((lq, lk)) < 0.05] = -np.inf
+        mask[lq // 2, :] = -np.inf
+        mask[lq // 2, lk // 3] = 0.0
+    scale = np.float32(1.0 / np.sqrt(np.float32(d)))
+    Q16, K16, V16 = to_bf16(ctx, q), to_bf16(ctx, k), to_bf16(ctx, v)
+    M = ctx.to_device(mask) if mask is not None else None
+    O, O16, LSE = ctx.empty(q.shape), ctx.empty(q.shape, np.uint16), ctx.empty((b, h, lq))
+    sq, sk = HeadStrides(h * lq * d, lq * d, d), HeadStrides(h * lk * d, lk * d, d)
+    assert ctx.lib.om_attention_fwd_bf16_supported(ctx.handle, i32(b), i32(h), i32(lq), i32(lk), i32(d), f32(scale)) == 1
+
+    def run(o16, lse):
+        ctx.call("om_attention_fwd_bf16", ctx.handle, Q16.ptr, C.byref(sq), K16.ptr, C.byref(sk), V16.ptr, C.byref(sk), M.ptr if M else None, i64(0),
+                 i32(b), i32(h), i32(lq), i32(lk), i32(d), f32(scale), O.ptr, o16, C.byref(sq), lse)
+        ctx.sync()
+        return O.numpy()
+
+    got = run(O16.ptr, LSE.ptr)
+    assert np.all(np.isfinite(got))
+    model = K.attention_fwd_bf16(q, k, v, mask, scale)
+    exact = K.attention_fwd(q, k, v, mask, scale)
+    assert scaled_diff(got, model) <= 4e-3, scaled_diff(got, model)
+    assert scaled_diff(got, exact) <= 2e-2, scaled_diff(got, exact)
+    assert np.array_equal(O16.numpy(), bf16_bits(K, got))
+    # log-sum-exp of scale q k^T + mask from the rounded operands: against fp64 from the same rounded operands
+    qr, kr = K.round_bf16(q).astype(np.float64), K.round_bf16(k).astype(np.float64)
+    s = np.einsum("bhqd,bhkd->bhqk", qr, kr) * np.float64(scale)
+    if mask is not None:
+        s = s + mask.astype(np.float64)
+    mx = s.max(axis=-1, keepdims=True)
+    lse_ref = (mx + np.log(np.exp(s - mx).sum(axis=-1, keepdims=True)))[..., 0]
+    assert np.max(np.abs(LSE.numpy() - lse_ref)) <= 2e-5 * max(1.0, float(np.max(np.abs(lse_ref))))
+    assert np.array_equal(got, run(None, None))
+
+
+def test_forward_shapes_outside_the_kernel_are_refused(ctx):
+    sup = ctx.lib.om_attention_fwd_bf16_supported
+    assert sup(ctx.handle, i32(1), i32(1), i32(4096), i32(4096), i32(64), f32(0.125)) == 1
+    assert sup(ctx.handle, i32(1), i32(1), i32(256), i32(256), i32(32), f32(0.125)) == 0
+    assert sup(ctx.handle, i32(1), i32(1), i32(256), i32(256), i32(64), f32(-1.0)) == 0
