@@ -545,7 +545,8 @@ def main():
                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload), "kernel": "dense contractions: " + ", ".join(sorted({r[0] for r in gemm})),
                         "launches_per_step": g_calls / psteps, "avg_launch_ms": g_ms / max(g_calls, 1),
                         "share_of_step_device_time": g_ms / total_ms if total_ms else None, "peak_source": peak_src,
-                        "by_entry_point_ms_per_step": {r[0]: round(r[2] / psteps, 4) for r in sorted(table, key=lambda r: -r[2]) if r[2] / psteps >= 0.01}}
+                        "by_entry_point_ms_per_step": {r[0]: round(r[2] / psteps, 4) for r in sorted(table, key=lambda r: -r[2]) if r[2] / psteps >= 0.01},
+                        "by_entry_point_calls_per_step": {r[0]: round(r[1] / psteps, 1) for r in sorted(table, key=lambda r: -r[2]) if r[2] / psteps >= 0.01}}
             prof_tr.close()
             if not args.skip_cpu and world == 1:
                 # All cores (three steps, median), one thread on a smaller slice, and the PyTorch CPU cross-check.

@@ -253,6 +253,16 @@ int32_t om_linear_fwd_bf16_act(om_ctx* ctx, const uint16_t* x, const uint16_t* W
 int32_t om_linear_dgrad_bf16_act(om_ctx* ctx, const uint16_t* g16, int32_t ldg, const uint16_t* W, int32_t rows,
                                  int32_t in_features, int32_t out_features, int32_t op, const float* pre, int32_t ldpre,
                                  float* dx, uint16_t* dx16);
+/* dx = residual + g W, out of place: the input gradient of a Linear layer whose input already holds a gradient from
+ * another branch (a residual connection). The sum is formed in the product's epilogue from a plain read of `residual`
+ * ([rows, in_features] fp32 with pitch ldres), so that tensor is not modified and may stay shared with its other readers
+ * (the engine of the reference adds later gradients into the first one that arrived, Engine.cs:124-344; the values are the
+ * same). dx16 (may be NULL) receives the bfloat16 copy. om_linear_dgrad_bf16_add_supported tells (1 / 0) whether the shape
+ * can take it (widths multiples of 8, at least 256 result columns, no split of k). */
+int32_t om_linear_dgrad_bf16_add_supported(om_ctx* ctx, int32_t rows, int32_t in_features, int32_t out_features);
+int32_t om_linear_dgrad_bf16_add(om_ctx* ctx, const uint16_t* g16, int32_t ldg, const uint16_t* W, int32_t rows,
+                                 int32_t in_features, int32_t out_features, const float* residual, int32_t ldres, float* dx,
+                                 uint16_t* dx16);
 
 /* ---- elementwise ------------------------------------------------------------------------------------ */
 

@@ -179,4 +179,24 @@ int32_t om_linear_dgrad_bf16_act(om_ctx* ctx, const uint16_t* g16, int32_t ldg, 
   return gemm_ws_act(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, 0, nullptr, dx16, 2, op, pre, ldpre);
 }
 
+// ---- an input gradient that joins another branch's gradient: dx = residual + g W, out of place ----
+
+int32_t om_linear_dgrad_bf16_add_supported(om_ctx* ctx, int32_t rows, int32_t in_features, int32_t out_features) {
+  if (!ctx || in_features % 8 || out_features % 8) return 0;
+  const float* aligned = reinterpret_cast<const float*>(uintptr_t(256));
+  return gemm_ws_act_ok(3, 0, rows, in_features, out_features, aligned, in_features, nullptr, aligned, in_features) ? 1 : 0;
+}
+
+int32_t om_linear_dgrad_bf16_add(om_ctx* ctx, const uint16_t* g16, int32_t ldg, const uint16_t* W, int32_t rows, int32_t in_features,
+                                 int32_t out_features, const float* residual, int32_t ldres, float* dx, uint16_t* dx16) {
+  OM_CHECK_CTX(ctx);
+  if (rows < 1 || in_features < 1 || out_features < 1 || ldg < out_features || ldres < in_features)
+    return fail(ctx, OM_ERR_SHAPE, "om_linear_dgrad_bf16_add: rows %d in %d out %d ldg %d ldres %d", rows, in_features, out_features, ldg, ldres);
+  if (!dx || !residual || dx == residual) return fail(ctx, OM_ERR_ARG, "om_linear_dgrad_bf16_add: dx and a distinct residual are needed");
+  OM_TRY(check_args(ctx, "om_linear_dgrad_bf16_add", rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features));
+  ProfileScope prof(ctx, "om_linear_bwd.dgrad", 2.0 * rows * in_features * out_features,
+                    2.0 * ((double)rows * out_features + (double)in_features * out_features) + (dx16 ? 10.0 : 8.0) * (double)rows * in_features);
+  return gemm_ws_act(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, 0, nullptr, dx16, 3, 0, residual, ldres);
+}
+
 }  // extern "C"

@@ -35,7 +35,10 @@ constexpr int W_BM = 128;                 // rows of C per CTA; a pair computes 
 #endif
 constexpr int W_STAGES = OM_WS_STAGES;
 constexpr int W_EPI_WARPS = OM_WS_EPI_WARPS;   // a multiple of four: the warps of a TMEM lane quadrant share the tile's columns
-constexpr int W_ACT_EPI_WARPS = 8;             // with an activation in the epilogue: twice the warps for the arithmetic
+// With arithmetic or an extra operand in the epilogue: four warps per lane quadrant, so that their loads and dependent
+// arithmetic hide one another, and one operand stage less to make room for their staging slots.
+constexpr int W_ACT_EPI_WARPS = 16;
+constexpr int W_ACT_STAGES = 5;
 constexpr int W_RING = OM_WS_RING;        // staging slots per epilogue warp
 #ifndef OM_WS_SLOT
 #define OM_WS_SLOT 4096
@@ -63,7 +66,7 @@ struct WsParams {
   int accumulate;
   int c16;                        // also store the bfloat16 copy of every block through map_c16 (never with accumulate)
   int32_t* status;
-  const float* aux;               // ACT 2: the activation's saved input, [m, n] fp32 with pitch ld_aux
+  const float* aux;               // ACT 2: the activation's saved input; ACT 3: the tensor to add; [m, n] fp32 with pitch ld_aux
   long long ld_aux;
 };
 
@@ -121,9 +124,9 @@ __host__ __device__ constexpr uint32_t ws_idesc(int bn, bool a_mn, bool b_mn) {
          ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
-template <int BN, int EW>
+template <int BN, int EW, int ST>
 constexpr size_t ws_smem_bytes() {
-  return (size_t)W_STAGES * (W_BM * 128 + (BN / 2) * 128) + (size_t)EW * W_RING * W_SLOT + 1024 + 256;
+  return (size_t)ST * (W_BM * 128 + (BN / 2) * 128) + (size_t)EW * W_RING * W_SLOT + 1024 + 256;
 }
 
 // Shared-memory tiles. K-major: rows (m or n) of 128 bytes of k, 8-row swizzle atoms 1024 bytes apart. MN-major: chunks of
@@ -133,9 +136,11 @@ constexpr size_t ws_smem_bytes() {
 //   1: C receives the product (+ bias) as before, the bfloat16 tensor receives OP(C) rounded: the next layer's operand,
 //      without the activation's own pass over C;
 //   2: C and its bfloat16 copy receive d/dx OP(aux) * product, aux being the activation's saved input: the input
-//      gradient of the layer after the activation, already multiplied by the activation's derivative.
+//      gradient of the layer after the activation, already multiplied by the activation's derivative;
+//   3: C (and its copy) receive aux + product: a gradient that joins another branch's (a residual connection) without
+//      a read-modify-write of that branch's tensor, which may then stay shared with its other readers.
 // EW epilogue warps (four, or eight when the epilogue has this arithmetic to do).
-template <int ELEM, int BN, bool A_MN, bool B_MN, int ACT = 0, int OP = 0, int EW = W_EPI_WARPS>
+template <int ELEM, int BN, bool A_MN, bool B_MN, int ACT = 0, int OP = 0, int EW = W_EPI_WARPS, int ST = W_STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (2 + EW), 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_c16, WsParams p) {
@@ -151,12 +156,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* staging = smem + (size_t)W_STAGES * STAGE;
+  uint8_t* staging = smem + (size_t)ST * STAGE;
   constexpr int PARTS = EW / 4, CB_PER = NB / PARTS;            // the warps of a lane quadrant split the tile's column blocks
   static_assert(ACT != 1 || W_SLOT < 6144, "the activated bfloat16 block is staged after the fp32 block has left the slot");
   uint64_t* full = reinterpret_cast<uint64_t*>(staging + (size_t)EW * W_RING * W_SLOT);
-  uint64_t* empty = full + W_STAGES;
-  uint64_t* acc_full = empty + W_STAGES;     // [2]
+  uint64_t* empty = full + ST;
+  uint64_t* acc_full = empty + ST;           // [2]
   uint64_t* acc_empty = acc_full + 2;        // [2], used in the leader
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -168,7 +173,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int k_blocks_total = (p.k + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < W_STAGES; s++) {
+    for (int s = 0; s < ST; s++) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -203,8 +208,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(k_blocks_total, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; kb++, it++) {
-          const int s = (int)(it % W_STAGES);
-          const uint32_t round = it / W_STAGES;
+          const int s = (int)(it % ST);
+          const uint32_t round = it / ST;
           if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, abort_flag, p.status, 41)) {
             ok = false;
             break;
@@ -244,8 +249,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + a * BN;
         for (int kb = kb0; kb < kb1; kb++, it++) {
-          const int s = (int)(it % W_STAGES);
-          const uint32_t round = it / W_STAGES;
+          const int s = (int)(it % ST);
+          const uint32_t round = it / ST;
           ok = mbar_wait(&full[s], round & 1, abort_flag, p.status, 43);
           if (!ok) break;
           tc_fence_after();
@@ -280,10 +285,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int n0 = (t % p.tiles_n) * BN;
       const uint32_t a = tile_i & 1, use = tile_i >> 1;
       const int row_base = m0 + quad * 32;
-      // ACT 2: this lane's 32 values of the saved input for a column block (n is a multiple of four, so that a 16-byte
-      // load never straddles the last column). The first block's loads are in flight while the accumulator is awaited,
-      // every later block's while the block before it is worked on.
-      float4 aux[8], nxt[8];
+      // ACT 2, 3: this lane's 32 values of the extra operand for a column block (n is a multiple of four, so that a 16-byte
+      // load never straddles the last column), asked for before the accumulator block is read back; the other warps of
+      // the quadrant work while they are on their way.
+      float4 aux[8];
       auto load_aux = [&](float4 (&dst)[8], int cb) {
         const int c0 = n0 + cb * 32, row = row_base + lane;
         const bool in = row < p.m && c0 < p.n;
@@ -291,7 +296,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
         for (int c4 = 0; c4 < 8; c4++) dst[c4] = (in && c0 + 4 * c4 < p.n) ? __ldg(src + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
       };
-      if (ACT == 2) load_aux(aux, part * CB_PER);
       ok = mbar_wait(&acc_full[a], use & 1, abort_flag, p.status, 44);
       if (!ok) break;
       tc_fence_after();
@@ -301,7 +305,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int col0 = n0 + cb * 32;
         const bool live = row_base < p.m && col0 < p.n;
         uint32_t r[32];
-        if (ACT == 2 && cb + 1 < (part + 1) * CB_PER) load_aux(nxt, cb + 1);
+        if (ACT >= 2) load_aux(aux, cb);
         if (live) {
           tmem_ld_32x32b_x32(tmem_acc + (uint32_t)(cb * 32), r);
           tmem_ld_wait();
@@ -322,8 +326,15 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             r[4 * c4 + 2] = __float_as_uint(unary_grad<OP>(__uint_as_float(r[4 * c4 + 2]), aux[c4].z));
             r[4 * c4 + 3] = __float_as_uint(unary_grad<OP>(__uint_as_float(r[4 * c4 + 3]), aux[c4].w));
           }
+        }
+        if (ACT == 3) {
 #pragma unroll
-          for (int c4 = 0; c4 < 8; c4++) aux[c4] = nxt[c4];
+          for (int c4 = 0; c4 < 8; c4++) {
+            r[4 * c4 + 0] = __float_as_uint(aux[c4].x + __uint_as_float(r[4 * c4 + 0]));
+            r[4 * c4 + 1] = __float_as_uint(aux[c4].y + __uint_as_float(r[4 * c4 + 1]));
+            r[4 * c4 + 2] = __float_as_uint(aux[c4].z + __uint_as_float(r[4 * c4 + 2]));
+            r[4 * c4 + 3] = __float_as_uint(aux[c4].w + __uint_as_float(r[4 * c4 + 3]));
+          }
         }
         if (stored >= W_RING) {
           // The block about to be overwritten was handed to the TMA unit W_RING stores ago.
@@ -458,7 +469,7 @@ bool gemm_ws_supported(om_ctx* ctx, int elem, int m, int n, int k, const void* A
 template <int ELEM, int BN>
 static int32_t ws_launch(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
                          const CUtensorMap& mc16, const WsParams& p, int units) {
-  constexpr size_t smem = ws_smem_bytes<BN, W_EPI_WARPS>();
+  constexpr size_t smem = ws_smem_bytes<BN, W_EPI_WARPS, W_STAGES>();
   constexpr int W_THREADS = 32 * (2 + W_EPI_WARPS);
 #define OM_WS(AMN, BMN)                                                                                                          \
   do {                                                                                                                           \
@@ -493,9 +504,11 @@ static int32_t ws_launch(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& m
 template <int ACT, int OP>
 static int32_t ws_launch_act(om_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& mc16,
                              const WsParams& p, int units) {
-  constexpr size_t smem = ws_smem_bytes<256, W_ACT_EPI_WARPS>();
-  constexpr int threads = 32 * (2 + W_ACT_EPI_WARPS);
-  auto kernel = gemm_ws_kernel<1, 256, false, ACT == 2, ACT, OP, W_ACT_EPI_WARPS>;
+  // The plain sum (ACT 3) has next to no arithmetic: eight warps and the full operand ring, like the products without an epilogue operand.
+  constexpr int EW = ACT == 3 ? 8 : W_ACT_EPI_WARPS, ST = ACT == 3 ? W_STAGES : W_ACT_STAGES;
+  constexpr size_t smem = ws_smem_bytes<256, EW, ST>();
+  constexpr int threads = 32 * (2 + EW);
+  auto kernel = gemm_ws_kernel<1, 256, false, ACT >= 2, ACT, OP, EW, ST>;
   static int max_clusters = 0;
   if (max_clusters == 0) {
     OM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -526,7 +539,7 @@ bool gemm_ws_c16_ok(const uint16_t* C16, long long ldc, int acc) {
 
 int32_t cast_bf16_rows(om_ctx* ctx, const float* src, uint16_t* dst, int rows, int cols, long long ld);
 
-// act 0: none. act 1 with op: C16 receives op(C) instead of C. act 2 with op: C and C16 receive op'(aux) * C.
+// act 0: none. act 1 with op: C16 receives op(C) instead of C. act 2 with op: C and C16 receive op'(aux) * C. act 3: aux + C.
 // gemm_ws_act_ok tells whether a product can take the activation (no split of k, the layouts above).
 static int ws_splits(int tiles, int k_blocks) {
   // Fixed split of k by shape alone: enough slices for one round of pairs, each at least 8 k-blocks deep.
@@ -540,14 +553,14 @@ static int ws_splits(int tiles, int k_blocks) {
 }
 
 bool gemm_ws_act_ok(int act, int op, int m, int n, int k, const float* C, long long ldc, const uint16_t* C16, const float* aux, long long ld_aux) {
-  if (act != 1 && act != 2) return false;
-  if (op != OM_GELU_ERF && op != OM_GELU_TANH) return false;
+  if (act < 1 || act > 3) return false;
+  if (act != 3 && op != OM_GELU_ERF && op != OM_GELU_TANH) return false;
   if (m < 1 || n < 256 || (n & 3)) return false;
   const int tiles = (int)(ceil_div(m, 2 * W_BM) * ceil_div(n, 256));
   if (ws_splits(tiles, (int)ceil_div(k, 64)) != 1) return false;
   if (act == 1 && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
-  if (act == 2 && (C16 != nullptr) && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
-  if (act == 2 && (!aux || (ld_aux & 3) || (reinterpret_cast<uintptr_t>(aux) & 15))) return false;
+  if (act >= 2 && (C16 != nullptr) && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
+  if (act >= 2 && (!aux || (ld_aux & 3) || (reinterpret_cast<uintptr_t>(aux) & 15))) return false;
   (void)C;
   return true;
 }
@@ -564,7 +577,7 @@ int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, 
                     long long ldc, int acc, const float* bias, uint16_t* C16, int act, int op, const float* aux, long long ld_aux) {
   const bool a_mn = ta != 0, b_mn = tb == 0;
   if (act != 0) {
-    if (elem != 1 || acc || a_mn || b_mn != (act == 2) || !gemm_ws_act_ok(act, op, m, n, k, C, ldc, C16, aux, ld_aux))
+    if (elem != 1 || acc || a_mn || b_mn != (act >= 2) || !gemm_ws_act_ok(act, op, m, n, k, C, ldc, C16, aux, ld_aux))
       return fail(ctx, OM_ERR_UNSUPPORTED, "persistent product: this shape or layout cannot take the activation in its epilogue (m %d n %d k %d)", m, n, k);
   }
   const int bk = elem == 0 ? 32 : 64, mn_chunk = elem == 0 ? 32 : 64;
@@ -611,6 +624,7 @@ int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, 
                                        : ws_launch_act<1, OM_GELU_TANH>(ctx, map_a, map_b, map_c, map_c16, p, units);
   else if (act == 2) st = op == OM_GELU_ERF ? ws_launch_act<2, OM_GELU_ERF_FAST>(ctx, map_a, map_b, map_c, map_c16, p, units)
                                             : ws_launch_act<2, OM_GELU_TANH>(ctx, map_a, map_b, map_c, map_c16, p, units);
+  else if (act == 3) st = ws_launch_act<3, 0>(ctx, map_a, map_b, map_c, map_c16, p, units);
   else if (elem == 0) st = bn == 256 ? ws_launch<0, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<0, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
   else st = bn == 256 ? ws_launch<1, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<1, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
   if (st == OM_OK && splits > 1) splitk_reduce_launch(ctx, workspace, splits, (int64_t)m * n, n, ldc, bias, C, acc);

@@ -156,7 +156,10 @@ void Engine::Execute(const std::shared_ptr<BackwardRecord>& root, Tensor rootGra
   struct Cleanup {
     std::vector<BackwardRecord*>& order;
     ~Cleanup() {
-      for (BackwardRecord* r : order) r->PendingGrad = Tensor();
+      for (BackwardRecord* r : order) {
+        r->PendingGrad = Tensor();
+        r->PendingShared = false;
+      }
       t_leaf_edges = nullptr;
     }
   } cleanup{order};
@@ -164,6 +167,8 @@ void Engine::Execute(const std::shared_ptr<BackwardRecord>& root, Tensor rootGra
     BackwardRecord* rec = order[i];
     Tensor g = rec->PendingGrad;
     rec->PendingGrad = Tensor();
+    current_shared_ = rec->PendingShared;
+    rec->PendingShared = false;
     if (g.IsEmpty()) {
       // No gradient reached this record: its leaf inputs still count as served.
       for (auto& in : rec->Inputs)
@@ -185,8 +190,15 @@ void Engine::Emit(BackwardRecord& rec, int i, const Tensor& grad, bool owned) {
   }
   BackwardRecord& p = *meta->GradFn;
   if (p.PendingGrad.IsEmpty()) {
-    p.PendingGrad = owned ? grad : grad.Clone();
+    // The first gradient to arrive is adopted as it is; one that its sender does not give away stays shared and is copied only
+    // if something has to be added into it.
+    p.PendingGrad = grad;
+    p.PendingShared = !owned;
   } else {
+    if (p.PendingShared) {
+      p.PendingGrad = p.PendingGrad.Clone();
+      p.PendingShared = false;
+    }
     AddInto(p.PendingGrad, grad);
   }
 }
@@ -228,13 +240,29 @@ void Engine::LeafWritten(BackwardRecord& rec, int i) {
   leaf_arrived(meta);
 }
 
-bool Engine::PendingTarget(BackwardRecord& rec, int i, Tensor* pending) {
+bool Engine::PendingTarget(BackwardRecord& rec, int i, Tensor* pending, bool* shared) {
   AutogradMeta* meta = rec.Inputs[i].get();
   if (!meta || !meta->GradFn) return false;
   const Tensor& p = meta->GradFn->PendingGrad;
   if (p.IsEmpty() || !p.IsContiguous() || p.GetDType() != DType::F32 || p.GetShape() != rec.InputShapes[i]) return false;
   *pending = p;
+  *shared = meta->GradFn->PendingShared;
   return true;
+}
+
+void Engine::PendingReplace(BackwardRecord& rec, int i, const Tensor& sum) {
+  BackwardRecord& p = *rec.Inputs[i]->GradFn;
+  p.PendingGrad = sum;
+  p.PendingShared = false;
+}
+
+Tensor Engine::PendingOwn(BackwardRecord& rec, int i) {
+  BackwardRecord& p = *rec.Inputs[i]->GradFn;
+  if (p.PendingShared) {
+    p.PendingGrad = p.PendingGrad.Clone();
+    p.PendingShared = false;
+  }
+  return p.PendingGrad;
 }
 
 void Engine::PendingWritten(BackwardRecord& rec, int i) { rec.Inputs[i]->GradFn->PendingGrad.MarkModified(); }

@@ -61,13 +61,14 @@ static void EmitSummed(Engine& e, BackwardRecord& r, const Tensor& g, bool negat
     Tensor s = SumTo(g, r.InputShapes[0], &same);
     if (!same) Engine::Emit(r, 0, s, true);
     else if (!need1) e.EmitAliased(r, 0, g);
-    else Engine::Emit(r, 0, g, false);
+    else Engine::Emit(r, 0, g, false);       // both inputs take g itself: shared, copied only if something is added into it
   }
   if (need1) {
     bool same;
     Tensor s = SumTo(g, r.InputShapes[1], &same);
     if (negateSecond) Engine::Emit(r, 1, NegOf(s), true);
     else if (!same) Engine::Emit(r, 1, s, true);
+    else if (need0 && r.InputShapes[0] == r.InputShapes[1]) Engine::Emit(r, 1, g, false);
     else e.EmitAliased(r, 1, g);
   }
 }
@@ -92,6 +93,25 @@ static void LinearBwdCall(const Tensor& g, int col, int ldg, const Tensor& x, co
   Check(om_linear_bwd_ld(C(), gp, ldg, x.Data(), w.Data() + (size_t)col * inF, rows, inF, outF, dx, dw, db, acc));
 }
 
+// The input gradient of a Linear layer whose input already holds another branch's gradient. Returns the tensor the product
+// must ADD into (in place), or an empty tensor when nothing is left to do because the sum residual + g W was formed out of
+// place by the product's epilogue and installed as the pending gradient (bfloat16 products on shapes the fused kernel takes:
+// the shared gradient of a residual connection is then never copied). A shared gradient that cannot take that route is
+// copied first, as the engine would have done on arrival.
+static Tensor AddIntoPending(BackwardRecord& r, const Tensor& g, int ldg, const Tensor& w, int rows, int inF, int outF, const Tensor& pending,
+                             bool shared) {
+  if (!shared) return pending;
+  auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (Bf16Products() && rows > 0 && Bf16Operand(g, ldg) && Bf16Operand(w, inF) && (inF & 7) == 0 && aligned16(pending.Data()) &&
+      om_linear_dgrad_bf16_add_supported(C(), rows, inF, outF) == 1) {
+    Tensor sum = Tensor::Create(DType::F32, pending.GetShape());
+    Check(om_linear_dgrad_bf16_add(C(), g.Bf16(), ldg, w.Bf16(), rows, inF, outF, pending.Data(), inF, sum.Data(), nullptr));
+    Engine::PendingReplace(r, 0, sum);
+    return Tensor();
+  }
+  return Engine::PendingOwn(r, 0);
+}
+
 // The record of Ops::LinearPacked (Ints = {rows, inF, outF, parts, hasBias}; inputs x, weights..., biases...): the input
 // gradient is one product over the packed weights; the weight and bias gradients are one product and one column sum
 // when the leaves' gradient buffers are adjacent like the parameters, else one per part on column slices of g.
@@ -104,8 +124,14 @@ static void LinearPackedBackward(BackwardRecord& r, const Tensor& g) {
   Tensor dx;
   bool dx_into_pending = false;   // the input already has the residual branch's gradient: the product adds into it
   if (r.NeedsInputGrad(0)) {
-    dx_into_pending = Engine::PendingTarget(r, 0, &dx);
-    if (!dx_into_pending) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+    bool shared = false;
+    dx_into_pending = Engine::PendingTarget(r, 0, &dx, &shared);
+    if (dx_into_pending) {
+      dx = AddIntoPending(r, gc, outF, wpacked, rows, inF, outF, dx, shared);
+      dx_into_pending = !dx.IsEmpty();      // empty: the sum is already in place
+    } else {
+      dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+    }
   }
   const int accx = dx_into_pending ? 2 : 0;
   std::vector<float*> wp(parts, nullptr), bp(parts, nullptr);
@@ -189,8 +215,14 @@ static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
   // When the input already has a gradient from another branch (the residual connection), the product adds into it.
   bool dx_into_pending = false;
   if (r.NeedsInputGrad(0)) {
-    dx_into_pending = Engine::PendingTarget(r, 0, &dx);
-    if (!dx_into_pending) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+    bool shared = false;
+    dx_into_pending = Engine::PendingTarget(r, 0, &dx, &shared);
+    if (dx_into_pending) {
+      dx = AddIntoPending(r, gc, ldg, w, rows, inF, outF, dx, shared);
+      dx_into_pending = !dx.IsEmpty();
+    } else {
+      dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+    }
   }
   const int accx = dx_into_pending ? 2 : 0;
   // Weight and bias gradients go straight into the leaf's gradient buffer when there is one.
@@ -279,8 +311,14 @@ static void FeedForwardBackward(BackwardRecord& r, const Tensor& g) {
   Tensor dx;
   bool dx_into_pending = false;
   if (r.NeedsInputGrad(0)) {
-    dx_into_pending = Engine::PendingTarget(r, 0, &dx);
-    if (!dx_into_pending) dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+    bool shared = false;
+    dx_into_pending = Engine::PendingTarget(r, 0, &dx, &shared);
+    if (dx_into_pending) {
+      dx = AddIntoPending(r, dpre, ff, w1, rows, inF, ff, dx, shared);
+      dx_into_pending = !dx.IsEmpty();
+    } else {
+      dx = Tensor::Create(DType::F32, r.InputShapes[0]);
+    }
   }
   const int accx = dx_into_pending ? 2 : 0;
   if (dw1.acc == db1.acc || !dw1.p || !db1.p) {

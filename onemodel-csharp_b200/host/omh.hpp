@@ -196,6 +196,9 @@ struct BackwardRecord : std::enable_shared_from_this<BackwardRecord> {
   std::vector<int64_t> Ints;
   std::vector<double> Floats;
   Tensor PendingGrad;
+  // The pending gradient's storage is also held by another record's pending gradient (a gradient that an Add hands to both
+  // of its inputs is not copied): it is read freely but copied before anything is added into it.
+  bool PendingShared = false;
   int VisitMark = 0;
   bool IsReleased = false;
 
@@ -247,7 +250,10 @@ class Engine {
  public:
   void Execute(const std::shared_ptr<BackwardRecord>& root, Tensor rootGrad, bool retain);
   static void Emit(BackwardRecord& rec, int i, const Tensor& grad, bool owned);
-  void EmitAliased(BackwardRecord& rec, int i, const Tensor& view) { Emit(rec, i, view, true); }
+  // A view of the gradient this record received: owned by the receiver unless that gradient is itself shared.
+  void EmitAliased(BackwardRecord& rec, int i, const Tensor& view) { Emit(rec, i, view, !current_shared_); }
+  // The gradient the running record received is shared with another record (see BackwardRecord::PendingShared).
+  bool CurrentShared() const { return current_shared_; }
   static void AccumulateLeaf(AutogradMeta& leaf, const Tensor& grad, bool owned);
   // If input i is a leaf that keeps a gradient buffer, returns that buffer and whether the kernel must add to it
   // (accumulate) or overwrite it; the caller then calls LeafWritten instead of Emit.
@@ -255,9 +261,16 @@ class Engine {
   static void LeafWritten(BackwardRecord& rec, int i);
   // If input i's producer already holds a gradient from another branch (contiguous, of the input's shape), returns it: the
   // backward kernel then adds into it (what Emit would do with AddInto in a pass of its own) and calls PendingWritten.
-  static bool PendingTarget(BackwardRecord& rec, int i, Tensor* pending);
+  // *shared: that gradient's storage is shared and must not be written; the caller either forms the sum out of place and
+  // installs it with PendingReplace, or asks for a private copy with PendingOwn and adds into that.
+  static bool PendingTarget(BackwardRecord& rec, int i, Tensor* pending, bool* shared);
   static void PendingWritten(BackwardRecord& rec, int i);
+  static void PendingReplace(BackwardRecord& rec, int i, const Tensor& sum);
+  static Tensor PendingOwn(BackwardRecord& rec, int i);
   static void AddInto(const Tensor& dst, const Tensor& src);
+
+ private:
+  bool current_shared_ = false;
 };
 
 // True when the current context multiplies bfloat16 copies of the operands (OM_BF16_OPERANDS with OM_TF32), and whether a

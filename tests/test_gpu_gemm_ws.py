@@ -274,3 +274,26 @@ def test_short_erf_of_the_bf16_tier_is_within_1e_6(ctx, oracle_built):
     assert np.max(np.abs(d - K.unary_bwd("gelu_erf", g, x))) <= 1e-6
     assert np.array_equal(Y16.numpy(), (K.round_bf16(y).view(np.uint32) >> 16).astype(np.uint16))
     assert np.array_equal(D16.numpy(), (K.round_bf16(d).view(np.uint32) >> 16).astype(np.uint16))
+
+
+@pytest.mark.parametrize("rows,outf,inf", [(8192, 2304, 768), (8192, 3072, 768), (300, 136, 264), (1000, 200, 520)])
+def test_input_gradient_added_to_a_residual_out_of_place(ctx, rows, outf, inf):
+    """om_linear_dgrad_bf16_add (dx = residual + g W, the sum formed in the epilogue from a plain read of the residual) against
+    om_linear_bwd_bf16_b16 adding into a copy of the residual in place (accumulate bit 2): the same bits, the residual
+    untouched, the bfloat16 copy the sum rounded."""
+    r = np.random.default_rng(rows + inf)
+    g, w = r.standard_normal((rows, outf)).astype(np.float32), (r.standard_normal((outf, inf)) * 0.1).astype(np.float32)
+    res = r.standard_normal((rows, inf)).astype(np.float32)
+    G16, W16, G, RES = to_bf16(ctx, g), to_bf16(ctx, w), ctx.to_device(g), ctx.to_device(res)
+    X16 = ctx.empty((rows, inf), np.uint16)
+    assert ctx.lib.om_linear_dgrad_bf16_add_supported(ctx.handle, i32(rows), i32(inf), i32(outf)) == 1
+    DX, DX16 = ctx.empty((rows, inf)), ctx.empty((rows, inf), np.uint16)
+    ctx.call("om_linear_dgrad_bf16_add", ctx.handle, G16.ptr, i32(outf), W16.ptr, i32(rows), i32(inf), i32(outf), RES.ptr, i32(inf), DX.ptr, DX16.ptr)
+    ACC = ctx.to_device(res)
+    ctx.call("om_linear_bwd_bf16_b16", ctx.handle, G16.ptr, G.ptr, i32(outf), X16.ptr, W16.ptr, i32(rows), i32(inf), i32(outf), ACC.ptr, None, None, None, i32(2))
+    ctx.sync()
+    assert np.array_equal(DX.numpy(), ACC.numpy())
+    assert np.array_equal(RES.numpy(), res)
+    from oracle import oracle as K
+    K.build()
+    assert np.array_equal(DX16.numpy(), (K.round_bf16(DX.numpy()).view(np.uint32) >> 16).astype(np.uint16))
