@@ -232,7 +232,9 @@ int32_t om_layernorm_fwd_b16(om_ctx* ctx, const float* x, const float* gamma, co
 int32_t om_layernorm_bwd_b16(om_ctx* ctx, const float* g, const float* x, const float* gamma, const float* mean,
                              const float* inv, int32_t rows, int32_t cols, float* dx, uint16_t* dx16, float* dgamma,
                              float* dbeta, int32_t accumulate_params);
-/* g16 is the bfloat16 copy of g (same pitch ldg); the bias gradient sums the fp32 g. */
+/* g16 is the bfloat16 copy of g (same pitch ldg). The bias gradient g^T 1 sums the fp32 g when one is given; with g NULL
+ * it sums g16, the operand that the weight gradient g^T x reads (om_colsum_bf16), and the fp32 gradient need not exist.
+ * The same holds for om_linear_bwd_bf16_b16. */
 int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x,
                            const uint16_t* W, int32_t rows, int32_t in_features, int32_t out_features, float* dx,
                            float* dW, float* dbias, int32_t accumulate_w);
@@ -243,7 +245,8 @@ int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int
  *     next layer's operand, from the product's epilogue; op(y) is not stored as fp32.
  *   om_linear_dgrad_bf16_act: dx = op'(pre) * (g W), the input gradient of the layer AFTER the activation already
  *     multiplied by the activation's derivative at its saved input `pre` ([rows, in_features] with pitch ldpre), as
- *     fp32 and (dx16 may be NULL) as bfloat16.
+ *     fp32 and as bfloat16 (either of dx and dx16 may be NULL: with dx NULL only the bfloat16 result is written, which is
+ *     all that the gradient products of the layer in front of the activation read).
  * om_linear_act_bf16_supported tells (1 / 0) whether the shape can take the fused form (widths that are multiples of 8, at
  * least 256 result columns, no split of k); otherwise the caller composes the unfused calls. */
 int32_t om_linear_act_bf16_supported(om_ctx* ctx, int32_t rows, int32_t in_features, int32_t out_features, int32_t op,
@@ -263,6 +266,11 @@ int32_t om_linear_dgrad_bf16_add_supported(om_ctx* ctx, int32_t rows, int32_t in
 int32_t om_linear_dgrad_bf16_add(om_ctx* ctx, const uint16_t* g16, int32_t ldg, const uint16_t* W, int32_t rows,
                                  int32_t in_features, int32_t out_features, const float* residual, int32_t ldres, float* dx,
                                  uint16_t* dx16);
+/* out[c] (+)= sum over rows of the bfloat16 matrix g16[rows, cols] with pitch ld (a multiple of 8, 16-byte aligned base):
+ * om_colsum on the bfloat16 copy of a gradient, with the same partition of the rows (chunks of 512, 32 lanes) and double
+ * accumulators, so the result is the same from run to run. */
+int32_t om_colsum_bf16(om_ctx* ctx, const uint16_t* g16, int32_t rows, int32_t cols, int32_t ld, float* out,
+                       int32_t accumulate);
 
 /* ---- elementwise ------------------------------------------------------------------------------------ */
 

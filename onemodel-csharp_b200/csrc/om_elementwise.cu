@@ -269,6 +269,7 @@ constexpr int kColsumLanes = 32;
 // Stage 2 inside stage 1: the CTA that arrives last for its 32 columns (all chunks' partial sums are then in memory)
 // adds them in increasing chunk order, exactly as colsum_stage2_kernel does, and resets the arrival counter for the next
 // launch. Which CTA arrives last does not matter for the result. `tid` is the thread's linear index in the CTA.
+template <int COLS = 32>
 __device__ __forceinline__ void colsum_finish(const double* __restrict__ partial, unsigned* __restrict__ arrival, float* __restrict__ out,
                                               int accumulate, int32_t cols, int tid, int* is_last) {
   __syncthreads();
@@ -276,8 +277,8 @@ __device__ __forceinline__ void colsum_finish(const double* __restrict__ partial
   __syncthreads();
   if (!*is_last) return;
   __threadfence();
-  if (tid < 32) {
-    const int c = blockIdx.x * 32 + tid;
+  if (tid < COLS) {
+    const int c = blockIdx.x * COLS + tid;
     if (c < cols) {
       double t = 0.0;
       for (unsigned ch = 0; ch < gridDim.y; ch++) t += __ldcg(partial + (int64_t)ch * cols + c);
@@ -365,6 +366,61 @@ colsum_stage1_vec4_kernel(const float* __restrict__ g, int32_t rows, int32_t col
     }
   }
   if (arrival != nullptr) colsum_finish(partial, arrival, out, accumulate, cols, threadIdx.x, &is_last);
+}
+
+// The column sums of a bfloat16 matrix (the copy of an output gradient that the products read): the same partition as above
+// (chunks of 512 rows, 32 row lanes, double accumulators, lanes and chunks combined in increasing order), a thread owning
+// eight adjacent columns (one 16-byte load per row) with its 16 rows in flight at once; a CTA covers 64 columns of a chunk.
+__device__ __forceinline__ void add_bf16x8(double (&a)[8], const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int q = 0; q < 4; q++) {
+    a[2 * q] += (double)__uint_as_float(w[q] << 16);
+    a[2 * q + 1] += (double)__uint_as_float(w[q] & 0xFFFF0000u);
+  }
+}
+__global__ void __launch_bounds__(256)
+colsum16_stage1_kernel(const uint16_t* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial,
+                       unsigned* __restrict__ arrival, float* __restrict__ out, int accumulate) {
+  pdl_enter();
+  __shared__ double sm[kColsumLanes][65];
+  __shared__ int is_last;
+  constexpr int PER_LANE = kColsumRowsPerChunk / kColsumLanes;
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const int col = blockIdx.x * 64 + tx * 8;
+  const int r0 = blockIdx.y * kColsumRowsPerChunk;
+  const int r1 = min(rows, r0 + kColsumRowsPerChunk);
+  double a[8];
+#pragma unroll
+  for (int q = 0; q < 8; q++) a[q] = 0.0;
+  if (col + 7 < cols) {
+    uint4 v[PER_LANE];
+#pragma unroll
+    for (int u = 0; u < PER_LANE; u++) {
+      const int r = r0 + ty + kColsumLanes * u;
+      v[u] = r < r1 ? __ldg(reinterpret_cast<const uint4*>(g + (int64_t)r * ld + col)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < PER_LANE; u++)
+      if (r0 + ty + kColsumLanes * u < r1) add_bf16x8(a, v[u]);
+  } else if (col < cols) {
+    for (int r = r0 + ty; r < r1; r += kColsumLanes)
+      for (int q = 0; q < 8 && col + q < cols; q++) a[q] += (double)__uint_as_float((uint32_t)g[(int64_t)r * ld + col + q] << 16);
+  }
+#pragma unroll
+  for (int q = 0; q < 8; q++) sm[ty][tx * 8 + q] = a[q];
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    const int c = blockIdx.x * 64 + threadIdx.x;
+    if (c < cols) {
+      double t = 0.0;
+#pragma unroll
+      for (int l = 0; l < kColsumLanes; l++) t += sm[l][threadIdx.x];
+      partial[(int64_t)blockIdx.y * cols + c] = t;
+      __threadfence();
+    }
+  }
+  if (arrival != nullptr) colsum_finish<64>(partial, arrival, out, accumulate, cols, threadIdx.x, &is_last);
 }
 
 __global__ void colsum_stage2_kernel(const double* __restrict__ partial, int32_t chunks, int32_t cols,
@@ -503,11 +559,36 @@ int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64
   return OM_OK;
 }
 
+// out[c] (+)= sum over rows of the bfloat16 matrix g16[rows, cols] with pitch ld (a multiple of 8, 16-byte aligned base).
+int32_t colsum16_ld(om_ctx* ctx, const uint16_t* g16, int32_t rows, int32_t cols, int64_t ld, float* out, int32_t accumulate) {
+  if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "om_colsum_bf16: [%d,%d]", rows, cols);
+  if (cols == 0) return OM_OK;
+  if ((ld & 7) || (reinterpret_cast<uintptr_t>(g16) & 15)) return fail(ctx, OM_ERR_UNSUPPORTED, "om_colsum_bf16: the pitch must be a multiple of 8 and the base 16-byte aligned");
+  ProfileScope prof(ctx, "om_colsum", 0, 2.0 * rows * cols + 4.0 * cols);
+  int chunks = (int)ceil_div(rows > 0 ? rows : 1, kColsumRowsPerChunk);
+  double* partial = nullptr;
+  OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)chunks * cols, false, (void**)&partial));
+  dim3 grid((unsigned)ceil_div(cols, 64), (unsigned)chunks);
+  unsigned* arrival = grid.x <= (unsigned)kArrivalSlots ? ctx->arrival[ctx->aux_active ? 1 : 0] : nullptr;
+  launch_chained(ctx, colsum16_stage1_kernel, grid, 256, 0, g16, rows, cols, ld, partial, arrival, out, accumulate);
+  if (arrival == nullptr)
+    launch_chained(ctx, colsum_stage2_kernel, (unsigned)ceil_div(cols, 128), 128, 0, partial, chunks, cols, out, accumulate);
+  pool_free(ctx, partial);
+  OM_LAUNCH_CHECK(ctx, "om_colsum_bf16");
+  return OM_OK;
+}
+
 }  // namespace om
 
 using namespace om;
 
 extern "C" {
+
+int32_t om_colsum_bf16(om_ctx* ctx, const uint16_t* g16, int32_t rows, int32_t cols, int32_t ld, float* out, int32_t accumulate) {
+  OM_CHECK_CTX(ctx);
+  if (ld < cols) return fail(ctx, OM_ERR_SHAPE, "om_colsum_bf16: pitch %d below %d columns", ld, cols);
+  return colsum16_ld(ctx, g16, rows, cols, ld, out, accumulate);
+}
 
 int32_t om_binary(om_ctx* ctx, int32_t op, int32_t rank, const int32_t* shape, const float* a,
                   const int64_t* a_strides, const float* b, const int64_t* b_strides, float* out) {

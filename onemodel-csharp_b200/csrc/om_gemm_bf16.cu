@@ -16,6 +16,7 @@ int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, 
                     long long ldc, int acc, const float* bias, uint16_t* C16, int act, int op, const float* aux, long long ld_aux);
 bool gemm_ws_act_ok(int act, int op, int m, int n, int k, const float* C, long long ldc, const uint16_t* C16, const float* aux, long long ld_aux);
 int32_t colsum_ld(om_ctx* ctx, const float* g, int32_t rows, int32_t cols, int64_t ld, float* out, int32_t accumulate);
+int32_t colsum16_ld(om_ctx* ctx, const uint16_t* g16, int32_t rows, int32_t cols, int64_t ld, float* out, int32_t accumulate);
 
 // Eight elements per thread: two 16-byte loads, one 16-byte store.
 __global__ void cast_bf16_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, int64_t n) {
@@ -130,8 +131,12 @@ int32_t om_linear_bwd_bf16_b16(om_ctx* ctx, const uint16_t* g16, const float* g,
     ProfileScope prof(ctx, "om_linear_bwd.wgrad", flops, 2.0 * ((double)rows * out_features + (double)rows * in_features) + 4.0 * (double)in_features * out_features);
     OM_TRY(gemm_ws(ctx, 1, 1, 0, out_features, in_features, rows, g16, ldg, x, in_features, dW, in_features, accumulate_w & 1, nullptr, nullptr));
   }
-  // The bias gradient is a sum of fp32 values, not a product: it reads the fp32 gradient.
-  if (dbias) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w & 1));
+  // The bias gradient g^T 1: from the fp32 gradient when the caller has one, else from the same bfloat16 copy that the weight
+  // gradient g^T x reads (half the bytes, and the fp32 gradient need not exist at all).
+  if (dbias) {
+    if (g) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w & 1));
+    else OM_TRY(colsum16_ld(ctx, g16, rows, out_features, ldg, dbias, accumulate_w & 1));
+  }
   return OM_OK;
 }
 
@@ -172,10 +177,10 @@ int32_t om_linear_dgrad_bf16_act(om_ctx* ctx, const uint16_t* g16, int32_t ldg, 
   OM_CHECK_CTX(ctx);
   if (rows < 1 || in_features < 1 || out_features < 1 || ldg < out_features || ldpre < in_features)
     return fail(ctx, OM_ERR_SHAPE, "om_linear_dgrad_bf16_act: rows %d in %d out %d ldg %d ldpre %d", rows, in_features, out_features, ldg, ldpre);
-  if (!dx || !pre) return fail(ctx, OM_ERR_ARG, "om_linear_dgrad_bf16_act: dx and the activation's saved input are needed");
+  if ((!dx && !dx16) || !pre) return fail(ctx, OM_ERR_ARG, "om_linear_dgrad_bf16_act: a result (dx or dx16) and the activation's saved input are needed");
   OM_TRY(check_args(ctx, "om_linear_dgrad_bf16_act", rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features));
   ProfileScope prof(ctx, "om_linear_bwd.dgrad", 2.0 * rows * in_features * out_features,
-                    2.0 * ((double)rows * out_features + (double)in_features * out_features) + (dx16 ? 10.0 : 8.0) * (double)rows * in_features);
+                    2.0 * ((double)rows * out_features + (double)in_features * out_features) + (4.0 + (dx ? 4.0 : 0.0) + (dx16 ? 2.0 : 0.0)) * (double)rows * in_features);
   return gemm_ws_act(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, 0, nullptr, dx16, 2, op, pre, ldpre);
 }
 

@@ -65,6 +65,7 @@ struct WsParams {
   const float* bias;
   int accumulate;
   int c16;                        // also store the bfloat16 copy of every block through map_c16 (never with accumulate)
+  int store32;                    // store the fp32 result (0: only the bfloat16 copy leaves the kernel)
   int32_t* status;
   const float* aux;               // ACT 2: the activation's saved input; ACT 3: the tensor to add; [m, n] fp32 with pitch ld_aux
   long long ld_aux;
@@ -158,7 +159,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* staging = smem + (size_t)ST * STAGE;
   constexpr int PARTS = EW / 4, CB_PER = NB / PARTS;            // the warps of a lane quadrant split the tile's column blocks
-  static_assert(ACT != 1 || W_SLOT < 6144, "the activated bfloat16 block is staged after the fp32 block has left the slot");
   uint64_t* full = reinterpret_cast<uint64_t*>(staging + (size_t)EW * W_RING * W_SLOT);
   uint64_t* empty = full + ST;
   uint64_t* acc_full = empty + ST;           // [2]
@@ -342,12 +342,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
         }
         uint8_t* blk = ring + (size_t)(stored % W_RING) * W_SLOT;
-        const uint32_t row_addr = smem_u32(blk) + (uint32_t)lane * 128u;
-#pragma unroll
-        for (int c4 = 0; c4 < 8; c4++)
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)((c4 ^ (lane & 7)) << 4)), "r"(r[4 * c4]),
-                       "r"(r[4 * c4 + 1]), "r"(r[4 * c4 + 2]), "r"(r[4 * c4 + 3])
-                       : "memory");
         // The block as bfloat16: 64 bytes per row in the 64-byte swizzle of map_c16 (16-byte chunk c of row r at
         // c ^ ((r >> 1) & 3)). With a slot of 6144 bytes it lies behind the fp32 block and both stores go out together;
         // with a slot of 4096 it takes the slot's place once the fp32 store has read it.
@@ -366,32 +360,43 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                          : "memory");
           }
         };
-        if (p.c16 && W_SLOT >= 6144) stage_bf16(blk + 4096);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          if (p.c16 && W_SLOT >= 6144)
-            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_c16), "r"(col0),
-                         "r"(row_base), "r"(smem_u32(blk + 4096))
+        const bool both_at_once = W_SLOT >= 6144 && ACT != 1;
+        if (p.store32) {
+          const uint32_t row_addr = smem_u32(blk) + (uint32_t)lane * 128u;
+#pragma unroll
+          for (int c4 = 0; c4 < 8; c4++)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)((c4 ^ (lane & 7)) << 4)), "r"(r[4 * c4]),
+                         "r"(r[4 * c4 + 1]), "r"(r[4 * c4 + 2]), "r"(r[4 * c4 + 3])
                          : "memory");
-          if (p.accumulate)
-            asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&map_c),
-                         "r"(col0), "r"(row_base), "r"(split), "r"(smem_u32(blk))
-                         : "memory");
-          else
-            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&map_c), "r"(col0),
-                         "r"(row_base), "r"(split), "r"(smem_u32(blk))
-                         : "memory");
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          if (p.c16 && both_at_once) stage_bf16(blk + 4096);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            if (p.c16 && both_at_once)
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_c16), "r"(col0),
+                           "r"(row_base), "r"(smem_u32(blk + 4096))
+                           : "memory");
+            if (p.accumulate)
+              asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&map_c),
+                           "r"(col0), "r"(row_base), "r"(split), "r"(smem_u32(blk))
+                           : "memory");
+            else
+              asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&map_c), "r"(col0),
+                           "r"(row_base), "r"(split), "r"(smem_u32(blk))
+                           : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
         }
-        if (p.c16 && W_SLOT < 6144) {
+        if (p.c16 && !(p.store32 && both_at_once)) {
           if (ACT == 1) {
             // The activation's arithmetic runs while the TMA unit reads the fp32 block out of the slot.
 #pragma unroll
             for (int i = 0; i < 32; i++) r[i] = __float_as_uint(unary_apply<OP>(__uint_as_float(r[i])));
           }
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          __syncwarp();
+          if (p.store32) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+          }
           stage_bf16(blk);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
@@ -576,6 +581,9 @@ int32_t gemm_ws(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, cons
 int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, const void* A, long long lda, const void* B, long long ldb, float* C,
                     long long ldc, int acc, const float* bias, uint16_t* C16, int act, int op, const float* aux, long long ld_aux) {
   const bool a_mn = ta != 0, b_mn = tb == 0;
+  const bool store32 = C != nullptr;
+  if (!store32 && (!C16 || acc || elem != 1))
+    return fail(ctx, OM_ERR_ARG, "persistent product: without an fp32 result the bfloat16 one is required (bfloat16 operands, no accumulation)");
   if (act != 0) {
     if (elem != 1 || acc || a_mn || b_mn != (act >= 2) || !gemm_ws_act_ok(act, op, m, n, k, C, ldc, C16, aux, ld_aux))
       return fail(ctx, OM_ERR_UNSUPPORTED, "persistent product: this shape or layout cannot take the activation in its epilogue (m %d n %d k %d)", m, n, k);
@@ -599,6 +607,8 @@ int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, 
   splits = (int)ceil_div(k_blocks, p.kb_per_split);
   p.splits = splits;
   p.status = ctx->status_dev;
+  p.store32 = store32 ? 1 : 0;
+  if (!store32 && splits > 1) return fail(ctx, OM_ERR_UNSUPPORTED, "persistent product: a product whose k is split needs its fp32 result (m %d n %d k %d)", m, n, k);
   p.aux = aux;
   p.ld_aux = ld_aux;
   float* workspace = nullptr;
@@ -608,12 +618,14 @@ int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, 
     ok = ws_store_map(&map_c, workspace, n, m, n, splits, (long long)m * n);
   } else {
     p.bias = bias; p.accumulate = acc;
-    ok = ws_store_map(&map_c, C, n, m, ldc, 1, 0);
+    ok = !store32 || ws_store_map(&map_c, C, n, m, ldc, 1, 0);
   }
   // The bfloat16 copy rides in the epilogue of an unsplit product; after a split of k it is cast from the finished C.
   p.c16 = (C16 && splits == 1 && gemm_ws_c16_ok(C16, ldc, acc)) ? 1 : 0;
+  if (!store32 && !p.c16) return fail(ctx, OM_ERR_UNSUPPORTED, "persistent product: the bfloat16 result needs a pitch that is a multiple of 8 and a 16-byte aligned base");
   if (p.c16) ok = ok && ws_store_map16(&map_c16, C16, n, m, ldc);
   else map_c16 = map_c;   // never used, but the parameter must hold a valid map
+  if (!store32) map_c = map_c16;
   if (!ok) {
     if (workspace) pool_free(ctx, workspace);
     return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed for C (persistent product, m %d n %d ldc %lld)", m, n, ldc);

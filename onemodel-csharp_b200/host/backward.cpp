@@ -86,7 +86,8 @@ static void LinearBwdCall(const Tensor& g, int col, int ldg, const Tensor& x, co
     // dx_tensor: the caller wants the bfloat16 copy of the input gradient from the product's epilogue (its consumer reads
     // bfloat16: the attention backward).
     uint16_t* dx16 = (dx && dx_tensor && inF % 8 == 0 && !(acc & 2)) ? dx_tensor->Bf16ForWrite() : nullptr;
-    Check(om_linear_bwd_bf16_b16(C(), g.Bf16() + col, gp, ldg, x.Bf16(), w.Bf16() + (size_t)col * inF, rows, inF, outF, dx, dx16, dw, db, acc));
+    // The bias gradient g^T 1 reads the same bfloat16 copy of g as the weight gradient g^T x (no fp32 gradient is passed).
+    Check(om_linear_bwd_bf16_b16(C(), g.Bf16() + col, nullptr, ldg, x.Bf16(), w.Bf16() + (size_t)col * inF, rows, inF, outF, dx, dx16, dw, db, acc));
     if (dx16) dx_tensor->Bf16Written();
     return;
   }
@@ -98,14 +99,14 @@ static void LinearBwdCall(const Tensor& g, int col, int ldg, const Tensor& x, co
 // place by the product's epilogue and installed as the pending gradient (bfloat16 products on shapes the fused kernel takes:
 // the shared gradient of a residual connection is then never copied). A shared gradient that cannot take that route is
 // copied first, as the engine would have done on arrival.
-static Tensor AddIntoPending(BackwardRecord& r, const Tensor& g, int ldg, const Tensor& w, int rows, int inF, int outF, const Tensor& pending,
+static Tensor AddIntoPending(BackwardRecord& r, const uint16_t* g16, int ldg, const Tensor& w, int rows, int inF, int outF, const Tensor& pending,
                              bool shared) {
   if (!shared) return pending;
   auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  if (Bf16Products() && rows > 0 && Bf16Operand(g, ldg) && Bf16Operand(w, inF) && (inF & 7) == 0 && aligned16(pending.Data()) &&
+  if (g16 && Bf16Products() && rows > 0 && ldg % 8 == 0 && aligned16(g16) && Bf16Operand(w, inF) && (inF & 7) == 0 && aligned16(pending.Data()) &&
       om_linear_dgrad_bf16_add_supported(C(), rows, inF, outF) == 1) {
     Tensor sum = Tensor::Create(DType::F32, pending.GetShape());
-    Check(om_linear_dgrad_bf16_add(C(), g.Bf16(), ldg, w.Bf16(), rows, inF, outF, pending.Data(), inF, sum.Data(), nullptr));
+    Check(om_linear_dgrad_bf16_add(C(), g16, ldg, w.Bf16(), rows, inF, outF, pending.Data(), inF, sum.Data(), nullptr));
     Engine::PendingReplace(r, 0, sum);
     return Tensor();
   }
@@ -127,7 +128,7 @@ static void LinearPackedBackward(BackwardRecord& r, const Tensor& g) {
     bool shared = false;
     dx_into_pending = Engine::PendingTarget(r, 0, &dx, &shared);
     if (dx_into_pending) {
-      dx = AddIntoPending(r, gc, outF, wpacked, rows, inF, outF, dx, shared);
+      dx = AddIntoPending(r, (shared && Bf16Products() && Bf16Operand(gc, outF)) ? gc.Bf16() : nullptr, outF, wpacked, rows, inF, outF, dx, shared);
       dx_into_pending = !dx.IsEmpty();      // empty: the sum is already in place
     } else {
       dx = Tensor::Create(DType::F32, r.InputShapes[0]);
@@ -218,7 +219,7 @@ static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
     bool shared = false;
     dx_into_pending = Engine::PendingTarget(r, 0, &dx, &shared);
     if (dx_into_pending) {
-      dx = AddIntoPending(r, gc, ldg, w, rows, inF, outF, dx, shared);
+      dx = AddIntoPending(r, (shared && Bf16Products() && Bf16Operand(gc, ldg)) ? gc.Bf16() : nullptr, ldg, w, rows, inF, outF, dx, shared);
       dx_into_pending = !dx.IsEmpty();
     } else {
       dx = Tensor::Create(DType::F32, r.InputShapes[0]);
@@ -298,15 +299,16 @@ static void FeedForwardBackward(BackwardRecord& r, const Tensor& g) {
   Leaf dw1 = target(1), db1 = target(2), dw2 = target(3), db2 = target(4);
   const uint16_t* g16 = gc.Bf16();
   // Second layer: weight and bias gradients, then the input gradient through the activation.
-  if (dw2.p) Check(om_linear_bwd_bf16_b16(C(), g16, gc.Data(), outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, dw2.p, nullptr, dw2.acc ? 1 : 0));
-  if (db2.p) Check(om_linear_bwd_bf16_b16(C(), g16, gc.Data(), outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, nullptr, db2.p, db2.acc ? 1 : 0));
+  if (dw2.p) Check(om_linear_bwd_bf16_b16(C(), g16, nullptr, outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, dw2.p, nullptr, dw2.acc ? 1 : 0));
+  if (db2.p) Check(om_linear_bwd_bf16_b16(C(), g16, nullptr, outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, nullptr, db2.p, db2.acc ? 1 : 0));
   done(4, db2);
   done(3, dw2);
   if (!dw1.p && !db1.p && !r.NeedsInputGrad(0)) return;
-  Shape hs = pre.GetShape();
-  Tensor dpre = Tensor::Create(DType::F32, hs);
-  Check(om_linear_dgrad_bf16_act(C(), g16, outF, w2.Bf16(), rows, ff, outF, op, pre.Data(), ff, dpre.Data(), dpre.Bf16ForWrite()));
-  dpre.Bf16Written();
+  // The gradient in front of the activation exists as bfloat16 only (two per 32-bit word of an integer tensor): the three
+  // gradients of the first layer are products that read it as an operand (the bias gradient is g^T 1).
+  Tensor dpre16 = Tensor::Create(DType::I32, Shape{rows, ff / 2});
+  const uint16_t* d16 = (const uint16_t*)dpre16.RawData();
+  Check(om_linear_dgrad_bf16_act(C(), g16, outF, w2.Bf16(), rows, ff, outF, op, pre.Data(), ff, nullptr, (uint16_t*)dpre16.RawData()));
   // First layer.
   Tensor dx;
   bool dx_into_pending = false;
@@ -314,18 +316,20 @@ static void FeedForwardBackward(BackwardRecord& r, const Tensor& g) {
     bool shared = false;
     dx_into_pending = Engine::PendingTarget(r, 0, &dx, &shared);
     if (dx_into_pending) {
-      dx = AddIntoPending(r, dpre, ff, w1, rows, inF, ff, dx, shared);
+      dx = AddIntoPending(r, d16, ff, w1, rows, inF, ff, dx, shared);
       dx_into_pending = !dx.IsEmpty();
     } else {
       dx = Tensor::Create(DType::F32, r.InputShapes[0]);
     }
   }
   const int accx = dx_into_pending ? 2 : 0;
+  float* dxp = dx.IsEmpty() ? nullptr : dx.Data();
   if (dw1.acc == db1.acc || !dw1.p || !db1.p) {
-    LinearBwdCall(dpre, 0, ff, x, w1, rows, inF, ff, dx.IsEmpty() ? nullptr : dx.Data(), dw1.p, db1.p, ((dw1.p ? dw1.acc : db1.acc) ? 1 : 0) | accx);
+    if (dxp || dw1.p || db1.p)
+      Check(om_linear_bwd_bf16_b16(C(), d16, nullptr, ff, x.Bf16(), w1.Bf16(), rows, inF, ff, dxp, nullptr, dw1.p, db1.p, ((dw1.p ? dw1.acc : db1.acc) ? 1 : 0) | accx));
   } else {
-    LinearBwdCall(dpre, 0, ff, x, w1, rows, inF, ff, dx.IsEmpty() ? nullptr : dx.Data(), dw1.p, nullptr, (dw1.acc ? 1 : 0) | accx);
-    LinearBwdCall(dpre, 0, ff, x, w1, rows, inF, ff, nullptr, nullptr, db1.p, db1.acc ? 1 : 0);
+    Check(om_linear_bwd_bf16_b16(C(), d16, nullptr, ff, x.Bf16(), w1.Bf16(), rows, inF, ff, dxp, nullptr, dw1.p, nullptr, (dw1.acc ? 1 : 0) | accx));
+    Check(om_linear_bwd_bf16_b16(C(), d16, nullptr, ff, x.Bf16(), w1.Bf16(), rows, inF, ff, nullptr, nullptr, nullptr, db1.p, db1.acc ? 1 : 0));
   }
   done(2, db1);
   if (dx_into_pending) Engine::PendingWritten(r, 0);

@@ -246,8 +246,22 @@ def linear(x, w, b=None):
     in_f, out_f = w.shape[1], w.shape[0]
     y = matmul(x.reshape(x.v.size // max(1, in_f), in_f), w.t())
     if b is not None:
-        y = add(y, b)
+        y = _bias_add(y, b) if GEMM_MODE == "bf16" else add(y, b)
     return y.reshape(x.shape[:-1] + (out_f,))
+
+
+def _bias_add(y, b):
+    """The Add(bias) of Ops.Linear under bfloat16 products: the bias gradient is the product g^T 1 and reads the same
+    bfloat16 copy of the output gradient as the weight gradient g^T x (summed in double, as the column sum does)."""
+    def bw(r, g):
+        out = []
+        if r.inputs[0] is not None:
+            out.append((0, g, "shared" if r.inputs[1] is not None else "own"))
+        if r.inputs[1] is not None:
+            out.append((1, K.round_bf16(np.ascontiguousarray(g)).astype(np.float64).sum(axis=0).astype(np.float32), "own"))
+        return out
+
+    return _attach((y.v + b.v).astype(np.float32), Record("add", [y, b], backward=bw), [y, b])
 
 
 def mean(x, axis=None):

@@ -249,8 +249,10 @@ def test_feed_forward_op_equals_its_three_parts(ctx, flags):
             y = omb.call("add", [x, f])
             y.backward(omb.Tensor.from_numpy(up))
             results.append([y.numpy(), x.grad.numpy()] + [p.grad.numpy() for p in ps])
-        for a, b in zip(*results):
-            assert np.all(np.isfinite(a)) and np.array_equal(a, b)
+        names = ["y", "dx", "dw1", "db1", "dw2", "db2"]     # the bias gradients too: both read the bfloat16 gradient
+        for name, a, b in zip(names, *results):
+            assert np.all(np.isfinite(a)), name
+            assert np.array_equal(a, b), (name, float(np.max(np.abs(a - b))), float(np.max(np.abs(b))))
     finally:
         ctx.set_flags(0)
 
@@ -297,3 +299,56 @@ def test_input_gradient_added_to_a_residual_out_of_place(ctx, rows, outf, inf):
     from oracle import oracle as K
     K.build()
     assert np.array_equal(DX16.numpy(), (K.round_bf16(DX.numpy()).view(np.uint32) >> 16).astype(np.uint16))
+
+
+@pytest.mark.parametrize("rows,cols,ld", [(16384, 768, 768), (1000, 520, 528), (513, 70, 72), (1, 8, 8), (4096, 3072, 3072)])
+def test_column_sums_of_a_bf16_matrix(ctx, oracle_built, rows, cols, ld):
+    """om_colsum_bf16 against the double sum of the same bfloat16 values: the rounding of the result to fp32 is all that is left
+    (the partition into chunks of 512 rows and 32 lanes only reorders exact double additions here), with accumulation into the
+    destination, the pitch columns ignored, and the same bits from run to run."""
+    K = oracle_built
+    r = np.random.default_rng(rows + cols)
+    g = np.zeros((rows, ld), np.float32)
+    g[:, :cols] = r.standard_normal((rows, cols))
+    g[:, cols:] = 1e6                                     # pitch columns must not be read into the sums
+    G16 = to_bf16(ctx, g)
+    want = K.round_bf16(g[:, :cols]).astype(np.float64).sum(0)
+    before = r.standard_normal(cols).astype(np.float32)
+    OUT, ACC = ctx.empty((cols,)), ctx.to_device(before)
+    ctx.call("om_colsum_bf16", ctx.handle, G16.ptr, i32(rows), i32(cols), i32(ld), OUT.ptr, i32(0))
+    ctx.call("om_colsum_bf16", ctx.handle, G16.ptr, i32(rows), i32(cols), i32(ld), ACC.ptr, i32(1))
+    ctx.sync()
+    assert np.array_equal(OUT.numpy(), want.astype(np.float32))
+    assert np.array_equal(ACC.numpy(), before + want.astype(np.float32))
+    again = ctx.empty((cols,))
+    ctx.call("om_colsum_bf16", ctx.handle, G16.ptr, i32(rows), i32(cols), i32(ld), again.ptr, i32(0))
+    ctx.sync()
+    assert np.array_equal(again.numpy(), OUT.numpy())
+
+
+def test_linear_gradients_from_the_bf16_gradient_alone(ctx, oracle_built):
+    """om_linear_bwd_bf16_b16 without the fp32 gradient (g NULL): the bias gradient is the column sum of the bfloat16 copy;
+    om_linear_dgrad_bf16_act without the fp32 result (dx NULL): the bfloat16 result alone equals the one written beside an
+    fp32 result."""
+    K = oracle_built
+    r = np.random.default_rng(17)
+    rows, inf, outf = 4096, 768, 3072
+    g = r.standard_normal((rows, outf)).astype(np.float32)
+    x, w = r.standard_normal((rows, inf)).astype(np.float32), (r.standard_normal((outf, inf)) * 0.05).astype(np.float32)
+    G16, X16, W16 = to_bf16(ctx, g), to_bf16(ctx, x), to_bf16(ctx, w)
+    DB = ctx.empty((outf,))
+    ctx.call("om_linear_bwd_bf16_b16", ctx.handle, G16.ptr, None, i32(outf), X16.ptr, W16.ptr, i32(rows), i32(inf), i32(outf), None, None, None, DB.ptr, i32(0))
+    ctx.sync()
+    assert np.array_equal(DB.numpy(), K.round_bf16(g).astype(np.float64).sum(0).astype(np.float32))
+    # the activation's derivative into a bfloat16-only result: the layer has `outf` inputs here (the width of the activation)
+    op = omb.UNARY["gelu_erf"]
+    g2 = r.standard_normal((rows, inf)).astype(np.float32)
+    w2 = (r.standard_normal((inf, outf)) * 0.05).astype(np.float32)
+    pre = (r.standard_normal((rows, outf)) * 1.5).astype(np.float32)
+    G216, W216, PRE = to_bf16(ctx, g2), to_bf16(ctx, w2), ctx.to_device(pre)
+    DX, DX16, ONLY16 = ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16), ctx.empty((rows, outf), np.uint16)
+    ctx.call("om_linear_dgrad_bf16_act", ctx.handle, G216.ptr, i32(inf), W216.ptr, i32(rows), i32(outf), i32(inf), i32(op), PRE.ptr, i32(outf), DX.ptr, DX16.ptr)
+    ctx.call("om_linear_dgrad_bf16_act", ctx.handle, G216.ptr, i32(inf), W216.ptr, i32(rows), i32(outf), i32(inf), i32(op), PRE.ptr, i32(outf), None, ONLY16.ptr)
+    ctx.sync()
+    assert np.array_equal(ONLY16.numpy(), DX16.numpy())
+    assert np.any(ONLY16.numpy() != 0)
