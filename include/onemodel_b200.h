@@ -636,6 +636,13 @@ int32_t om_optim_adam_step(om_ctx* ctx, int32_t n_tensors, float* const* p_host,
                            float* const* m_host, float* const* v_host, float* const* vmax_host,
                            const int64_t* len_host, const om_adam_hyper* hyper_host,
                            const om_adam_hyper* hyper_dev);
+/* The same step that also refreshes the bfloat16 copies of the parameters it updates (p16_host[i] may be NULL: no copy for
+ * that parameter): the weights of the Linear layers are product operands under OM_BF16_OPERANDS, and their copies are then
+ * current without a cast pass after the step. */
+int32_t om_optim_adam_step_b16(om_ctx* ctx, int32_t n_tensors, float* const* p_host, const float* const* g_host,
+                               float* const* m_host, float* const* v_host, float* const* vmax_host,
+                               uint16_t* const* p16_host, const int64_t* len_host, const om_adam_hyper* hyper_host,
+                               const om_adam_hyper* hyper_dev);
 typedef struct om_sgd_hyper {
   float lr, weight_decay, momentum, dampening, grad_scale;
   int32_t nesterov;

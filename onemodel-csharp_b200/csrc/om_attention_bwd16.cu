@@ -125,19 +125,27 @@ attention_dots_kernel(const float* __restrict__ g, const float* __restrict__ out
   pdl_enter();
   const int lane = threadIdx.x & 31;
   const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), warps = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long r0 = warp * 8; r0 < rows; r0 += warps * 8) {
+  // Row indices fit 31 bits (the host checks); 32-bit arithmetic keeps the index computation off the critical path.
+  const unsigned nrows = (unsigned)rows, uh = (unsigned)heads, ulq = (unsigned)lq;
+  for (unsigned r0 = (unsigned)warp * 8u; r0 < nrows; r0 += (unsigned)warps * 8u) {
     float2 a[8], b[8];
-    long long slot[8];
+    int slot[8];
+    unsigned hi = r0 % uh, t = r0 / uh, q = t % ulq, bi = t / ulq;
 #pragma unroll
     for (int u = 0; u < 8; u++) {
-      const long long r = r0 + u;
       a[u] = b[u] = make_float2(0.f, 0.f);
       slot[u] = -1;
-      if (r < rows) {
-        const long long hi = r % heads, q = (r / heads) % lq, bi = r / ((long long)heads * lq);
-        a[u] = *reinterpret_cast<const float2*>(g + bi * g_batch + hi * g_head + q * g_row + 2 * lane);
-        b[u] = *reinterpret_cast<const float2*>(out + bi * o_batch + hi * o_head + q * o_row + 2 * lane);
-        slot[u] = (bi * heads + hi) * lq + q;
+      if (r0 + u < nrows) {
+        a[u] = *reinterpret_cast<const float2*>(g + (long long)bi * g_batch + (long long)hi * g_head + (long long)q * g_row + 2 * lane);
+        b[u] = *reinterpret_cast<const float2*>(out + (long long)bi * o_batch + (long long)hi * o_head + (long long)q * o_row + 2 * lane);
+        slot[u] = (int)((bi * uh + hi) * ulq + q);
+      }
+      if (++hi == uh) {
+        hi = 0;
+        if (++q == ulq) {
+          q = 0;
+          bi++;
+        }
       }
     }
 #pragma unroll
@@ -497,7 +505,7 @@ extern "C" {
 
 int32_t om_attention_bwd_bf16_supported(om_ctx* ctx, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d) {
   if (!ctx || !encode_fn()) return 0;
-  return (d == AB_D && lq >= 1 && lk >= 1 && b >= 1 && h >= 1 && (long long)b * h <= 65535) ? 1 : 0;
+  return (d == AB_D && lq >= 1 && lk >= 1 && b >= 1 && h >= 1 && (long long)b * h <= 65535 && (long long)b * h * lq < (1ll << 31)) ? 1 : 0;
 }
 
 int32_t om_attention_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, const om_head_strides* gs, const uint16_t* q16,

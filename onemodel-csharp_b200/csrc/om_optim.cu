@@ -7,6 +7,8 @@
 // fused multiply-add, in exactly the order of Adam.UpdateRange / Sgd.Update of the reference
 // (src/OneModel.Training/Optimizers.cs:335-373,554-589), so the updated parameters are bit-identical to the
 // reference's given the same gradients.
+#include <cuda_bf16.h>
+
 #include "om_common.cuh"
 
 namespace om {
@@ -20,6 +22,7 @@ struct TensorTable {
   float* a[kMaxTensors];  // m (Adam) or momentum buffer (SGD)
   float* b[kMaxTensors];  // v
   float* c[kMaxTensors];  // vmax
+  uint16_t* p16[kMaxTensors];  // Adam: the bfloat16 copy of the parameter to refresh in the same pass (may be null)
   int64_t len[kMaxTensors];
   int32_t chunk_prefix[kMaxTensors + 1];
   int32_t first[kMaxTensors];
@@ -74,7 +77,8 @@ adam_kernel(TensorTable t, om_adam_hyper hv, const om_adam_hyper* __restrict__ h
     float* m = t.a[ti];
     float* v = t.b[ti];
     float* vm = t.c[ti];
-    bool vec = !h.amsgrad && (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15) == 0;
+    uint16_t* p16 = t.p16[ti];
+    bool vec = !h.amsgrad && (((uintptr_t)p16) & 7) == 0 && (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15) == 0;
     if (vec) {
       int64_t e4 = start + ((end - start) & ~(int64_t)3);
       for (int64_t i = start + threadIdx.x * 4; i < e4; i += 256 * 4) {
@@ -87,11 +91,26 @@ adam_kernel(TensorTable t, om_adam_hyper hv, const om_adam_hyper* __restrict__ h
         *reinterpret_cast<float4*>(p + i) = pp;
         *reinterpret_cast<float4*>(m + i) = mm;
         *reinterpret_cast<float4*>(v + i) = vv;
+        if (p16) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(pp.x, pp.y), hi = __floats2bfloat162_rn(pp.z, pp.w);
+          *reinterpret_cast<uint2*>(p16 + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        }
       }
-      for (int64_t i = e4 + threadIdx.x; i < end; i += 256) adam_element(p[i], g[i], m[i], v[i], nullptr, h, omb1, omb2, decay);
+      for (int64_t i = e4 + threadIdx.x; i < end; i += 256) {
+        adam_element(p[i], g[i], m[i], v[i], nullptr, h, omb1, omb2, decay);
+        if (p16) {
+          __nv_bfloat16 hv16 = __float2bfloat16_rn(p[i]);
+          p16[i] = *reinterpret_cast<uint16_t*>(&hv16);
+        }
+      }
     } else {
-      for (int64_t i = start + threadIdx.x; i < end; i += 256)
+      for (int64_t i = start + threadIdx.x; i < end; i += 256) {
         adam_element(p[i], g[i], m[i], v[i], h.amsgrad ? vm + i : nullptr, h, omb1, omb2, decay);
+        if (p16) {
+          __nv_bfloat16 hv16 = __float2bfloat16_rn(p[i]);
+          p16[i] = *reinterpret_cast<uint16_t*>(&hv16);
+        }
+      }
     }
   }
 }
@@ -231,6 +250,7 @@ static int fill_table(TensorTable& t, int base, int count, float* const* p, cons
     t.a[i] = a ? a[s] : nullptr;
     t.b[i] = b ? b[s] : nullptr;
     t.c[i] = c ? c[s] : nullptr;
+    t.p16[i] = nullptr;
     t.first[i] = first ? first[s] : 0;
     t.len[i] = len[s];
     t.chunk_prefix[i] = chunks;
@@ -306,6 +326,12 @@ extern "C" {
 int32_t om_optim_adam_step(om_ctx* ctx, int32_t n_tensors, float* const* p, const float* const* g, float* const* m,
                            float* const* v, float* const* vmax, const int64_t* len, const om_adam_hyper* hyper_host,
                            const om_adam_hyper* hyper_dev) {
+  return om_optim_adam_step_b16(ctx, n_tensors, p, g, m, v, vmax, nullptr, len, hyper_host, hyper_dev);
+}
+
+int32_t om_optim_adam_step_b16(om_ctx* ctx, int32_t n_tensors, float* const* p, const float* const* g, float* const* m,
+                               float* const* v, float* const* vmax, uint16_t* const* p16, const int64_t* len,
+                               const om_adam_hyper* hyper_host, const om_adam_hyper* hyper_dev) {
   OM_CHECK_CTX(ctx);
   if (n_tensors < 0 || !hyper_host) return fail(ctx, OM_ERR_ARG, "om_optim_adam_step: bad arguments");
   if (hyper_host->amsgrad && !vmax) return fail(ctx, OM_ERR_ARG, "om_optim_adam_step: amsgrad needs vmax");
@@ -317,6 +343,8 @@ int32_t om_optim_adam_step(om_ctx* ctx, int32_t n_tensors, float* const* p, cons
     int count = std::min(kMaxTensors, n_tensors - base);
     int chunks = fill_table(t, base, count, p, g, m, v, vmax, nullptr, len);
     if (chunks == 0) continue;
+    if (p16)
+      for (int i = 0; i < count; i++) t.p16[i] = p16[base + i];
     launch_chained(ctx, adam_kernel, grid_chunks(ctx, chunks), 256, 0, t, *hyper_host, hyper_dev);
     OM_LAUNCH_CHECK(ctx, "om_optim_adam_step");
   }

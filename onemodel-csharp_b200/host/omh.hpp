@@ -114,6 +114,8 @@ class Tensor {
   // be a multiple of 8 elements for the copy to be usable as a product operand). Casts the storage when the copy is older
   // than the storage.
   const uint16_t* Bf16() const;
+  // True when the storage has a bfloat16 copy at all (current or not): the tensor is used as a product operand.
+  bool HasBf16Storage() const { return buf_ && buf_->shadow != nullptr; }
   // True when the storage already has an up-to-date bfloat16 copy.
   bool HasBf16() const { return buf_ && buf_->shadow && buf_->shadow_version == buf_->version; }
   // Storage for the bfloat16 copy, for a kernel that writes it together with the fp32 values; the caller then marks it current.
@@ -615,6 +617,14 @@ class Optimizer {
   virtual void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) = 0;
   std::vector<Tensor> params_;
   std::vector<int> index_;  // positions in params_ of the tensors of the running Step
+  // For the tensors of the running Step, the bfloat16 copy to refresh in the same launch (null: none). A copy is offered
+  // only where the launch updates every element of the copy's storage, so that the copy is current as a whole afterwards.
+  std::vector<uint16_t*> p16_;
+  // True for an optimizer whose Launch writes p16_ (Adam); the others leave the copies to the cast on next use.
+  virtual bool WritesBf16Copies() const { return false; }
+ private:
+  void OfferBf16Copies();
+  void Bf16CopiesWritten();
 };
 
 class Sgd : public Optimizer {
@@ -649,6 +659,8 @@ class Adam : public Optimizer {
   std::vector<StateEntry> NamedState() override;
   float GradScale = 1.f;
  protected:
+  bool WritesBf16Copies() const override { return true; }
+ 
   void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) override;
  private:
   float beta1_, beta2_, eps_;

@@ -3,6 +3,8 @@
 // update runs in one fused multi-tensor launch on the device.
 #include <math.h>
 
+#include <map>
+
 #include "omh.hpp"
 
 namespace omh {
@@ -18,6 +20,27 @@ Optimizer::Optimizer(std::vector<Tensor> parameters) : params_(std::move(paramet
 
 void Optimizer::ZeroGrad() {
   for (const Tensor& p : params_) Backprop::ZeroGrad(p);
+}
+
+// The parameters of the running launch that are product operands under bfloat16 products (their storage has a bfloat16
+// copy) get that copy refreshed by the launch itself, when the launch covers the whole storage.
+void Optimizer::OfferBf16Copies() {
+  p16_.assign(index_.size(), nullptr);
+  if (!WritesBf16Copies()) return;
+  std::map<const Buffer*, int64_t> covered;
+  for (int i : index_) {
+    const Tensor& t = params_[(size_t)i];
+    if (t.HasBf16Storage()) covered[t.Storage().get()] += t.Length();
+  }
+  for (size_t k = 0; k < index_.size(); k++) {
+    const Tensor& t = params_[(size_t)index_[k]];
+    if (t.HasBf16Storage() && covered[t.Storage().get()] == (int64_t)(t.Storage()->bytes / 4)) p16_[k] = t.Bf16ForWrite();
+  }
+}
+
+void Optimizer::Bf16CopiesWritten() {
+  for (size_t k = 0; k < index_.size(); k++)
+    if (p16_[k]) params_[(size_t)index_[k]].Bf16Written();
 }
 
 // Optimizer.Step (Optimizers.cs:184-219): parameters without a gradient are skipped.
@@ -37,8 +60,10 @@ void Optimizer::Step() {
     len.push_back(t.Length());
     index_.push_back((int)i);
   }
+  OfferBf16Copies();
   Launch(p, g, len);
   for (int i : index_) params_[(size_t)i].MarkModified();   // written in place: saved copies and bfloat16 copies are stale
+  Bf16CopiesWritten();                                      // ... except the copies the launch itself refreshed
   StepCount++;
 }
 
@@ -60,8 +85,10 @@ void Optimizer::StepGroups(const std::vector<std::vector<int>>& groups, const st
       index_.push_back(i);
     }
     if (before) before((int)gi);
+    OfferBf16Copies();
     if (!p.empty()) Launch(p, g, len);
     for (int i : index_) params_[(size_t)i].MarkModified();
+    Bf16CopiesWritten();
   }
   StepCount++;
 }
@@ -190,8 +217,8 @@ void Adam::Launch(const std::vector<float*>& p, const std::vector<const float*>&
     v.push_back(v_[i].Data());
     if (amsgrad_) vm.push_back(vmax_[i].Data());
   }
-  Check(om_optim_adam_step(C(), (int32_t)p.size(), p.data(), g.data(), m.data(), v.data(), amsgrad_ ? vm.data() : nullptr,
-                           len.data(), &h, (const om_adam_hyper*)HyperDevice));
+  Check(om_optim_adam_step_b16(C(), (int32_t)p.size(), p.data(), g.data(), m.data(), v.data(), amsgrad_ ? vm.data() : nullptr,
+                               p16_.size() == p.size() ? p16_.data() : nullptr, len.data(), &h, (const om_adam_hyper*)HyperDevice));
 }
 
 // ---- clipping -------------------------------------------------------------------------------------------------------

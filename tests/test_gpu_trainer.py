@@ -254,3 +254,34 @@ def test_batches_staged_ahead_give_the_same_run(ctx, depth):
     assert np.array_equal(np.array(la), np.array(lb))
     for a, b in zip(pa, pb):
         assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_bf16_copies_refreshed_by_the_optimizer_equal_a_fresh_cast(ctx, graph):
+    """Under bfloat16 products AdamW refreshes the bfloat16 copies of the weights it updates in the same launch. A second run
+    rewrites every parameter with its own value before each step, which marks the copies stale and has them cast afresh from
+    the fp32 weights: the two runs give the same losses and the same parameters, bit for bit (eager and replayed)."""
+    cfg = [2, 256, 2, 256, 4, 1024, 1000, 40]
+    ctx.set_flags(omb.OM_TF32 | omb.OM_BF16_OPERANDS)
+    ctx.make_current()
+    try:
+        runs = []
+        for recast in (False, True):
+            tr = omb.Trainer("mlm", cfg, lr=1e-3, weight_decay=0.01, seed=0)
+            named = tr.named_parameters()
+            losses = []
+            for step in range(5):
+                if graph and step == 2:
+                    tr.enable_graph()
+                if recast:
+                    for i, (_, s) in enumerate(named):
+                        tr.set_param(i, tr.get_param(i, s))
+                losses.append(tr.step(list(synth.mlm_batch(cfg[0], cfg[1], cfg[6], cfg[7], step))))
+            runs.append((losses, [tr.get_param(i, s) for i, (_, s) in enumerate(named)]))
+            tr.close()
+        assert runs[0][0] == runs[1][0]
+        for a, b in zip(runs[0][1], runs[1][1]):
+            assert np.array_equal(a, b)
+        assert runs[0][0][0] != runs[0][0][4]
+    finally:
+        ctx.set_flags(0)
