@@ -229,6 +229,13 @@ int32_t om_unary_b16(om_ctx* ctx, int32_t op, const float* x, float* y, uint16_t
 int32_t om_unary_bwd_b16(om_ctx* ctx, int32_t op, const float* g, const float* saved, float* dx, uint16_t* dx16, int64_t n);
 int32_t om_layernorm_fwd_b16(om_ctx* ctx, const float* x, const float* gamma, const float* beta, int32_t rows,
                              int32_t cols, float eps, float* y, uint16_t* y16, float* mean, float* inv);
+/* The residual sum in front of a layer norm formed in the same pass: sum = x + addend (written out, the layer norm's
+ * input for the backward pass), y = LayerNorm(sum). The values are those of om_binary(OM_ADD) followed by om_layernorm_fwd;
+ * one read of the two operands instead of a write and a read of the sum between two launches. addend and sum NULL: plain
+ * om_layernorm_fwd_b16. Rows up to 1024 wide. */
+int32_t om_add_layernorm_fwd_b16(om_ctx* ctx, const float* x, const float* addend, float* sum, const float* gamma,
+                                 const float* beta, int32_t rows, int32_t cols, float eps, float* y, uint16_t* y16,
+                                 float* mean, float* inv);
 int32_t om_layernorm_bwd_b16(om_ctx* ctx, const float* g, const float* x, const float* gamma, const float* mean,
                              const float* inv, int32_t rows, int32_t cols, float* dx, uint16_t* dx16, float* dgamma,
                              float* dbeta, int32_t accumulate_params);

@@ -2,6 +2,8 @@
 #include <stdarg.h>
 
 #include <algorithm>
+#include <mutex>
+#include <set>
 
 #include "om_common.cuh"
 
@@ -235,6 +237,12 @@ extern "C" {
 
 int32_t om_version(void) { return 100; }
 
+// The contexts that exist: om_free on a context that was destroyed (a caller that releases its buffers after the context,
+// as a garbage-collected host may) returns OM_ERR_ARG instead of touching freed memory; the destroyed context has given
+// its blocks back to the driver already.
+static std::mutex g_live_mutex;
+static std::set<om_ctx*> g_live;
+
 int32_t om_ctx_create(int32_t device, uint32_t flags, om_ctx** out) {
   if (!out) return OM_ERR_ARG;
   *out = nullptr;
@@ -276,6 +284,10 @@ int32_t om_ctx_create(int32_t device, uint32_t flags, om_ctx** out) {
       return check_cuda(nullptr, e, "arrival counters");
     }
   }
+  {
+    std::lock_guard<std::mutex> lock(g_live_mutex);
+    g_live.insert(ctx);
+  }
   *out = ctx;
   return OM_OK;
 }
@@ -284,6 +296,10 @@ int32_t om_dp_finalize(om_ctx* ctx);
 
 int32_t om_ctx_destroy(om_ctx* ctx) {
   if (!ctx) return OM_OK;
+  {
+    std::lock_guard<std::mutex> lock(g_live_mutex);
+    if (!g_live.erase(ctx)) return OM_ERR_ARG;   // not a context of this library (or destroyed twice)
+  }
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   if (ctx->dp) om_dp_finalize(ctx);
@@ -374,6 +390,10 @@ int32_t om_alloc(om_ctx* ctx, size_t bytes, int32_t zero, void** dptr) {
 
 int32_t om_free(om_ctx* ctx, void* dptr) {
   if (!ctx) return OM_ERR_ARG;
+  {
+    std::lock_guard<std::mutex> lock(g_live_mutex);
+    if (!g_live.count(ctx)) return OM_ERR_ARG;
+  }
   return pool_free(ctx, dptr);
 }
 

@@ -100,9 +100,9 @@ __device__ __forceinline__ uint16_t bf16_bits(float v) {
 
 template <int NC>
 __global__ void __launch_bounds__(256)
-layernorm_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta, int32_t rows,
-                         int32_t cols, float eps, float* __restrict__ y, uint16_t* __restrict__ y16, float* __restrict__ mean_out,
-                         float* __restrict__ inv_out) {
+layernorm_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ addend, float* __restrict__ sum_out,
+                         const float* __restrict__ gamma, const float* __restrict__ beta, int32_t rows, int32_t cols, float eps,
+                         float* __restrict__ y, uint16_t* __restrict__ y16, float* __restrict__ mean_out, float* __restrict__ inv_out) {
   pdl_enter();
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), warps = (int64_t)gridDim.x * 8;
@@ -121,6 +121,19 @@ layernorm_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ 
     for (int i = 0; i < NC; i++) {
       const int j = lane + 32 * i;
       v[i] = j < cols ? xr[j] : 0.f;
+    }
+    if (addend) {
+      // The residual sum x + addend is formed here (and written out: the backward pass normalises it again).
+      const float* ar = addend + r * cols;
+      float* sr = sum_out + r * cols;
+#pragma unroll
+      for (int i = 0; i < NC; i++) {
+        const int j = lane + 32 * i;
+        if (j < cols) {
+          v[i] = v[i] + ar[j];
+          sr[j] = v[i];
+        }
+      }
     }
     float s = 0.f;
 #pragma unroll
@@ -225,6 +238,180 @@ layernorm_bwd_fused_kernel(const float* __restrict__ g, const float* __restrict_
     for (int i = 0; i < NC; i++) {
       const int j = lane + 32 * i;
       if (j < cols) ln_smem[w * cols + j] = (double)(table == 0 ? ag[i] : ab[i]);
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < cols; j += 256) {
+      double t = 0.0;
+#pragma unroll
+      for (int k = 0; k < 8; k++) t += ln_smem[k * cols + j];
+      out[(int64_t)blockIdx.x * cols + j] = t;
+    }
+  }
+}
+
+// ---- layer norm, rows of 16-byte groups ------------------------------------------------------------------------------
+// The same two kernels for rows whose width is a multiple of four and whose tensors are 16-byte aligned: a lane owns the
+// groups of four columns lane, lane + 32, ... (one 16-byte access each, a warp's access 512 contiguous bytes), so a row of 768
+// columns is six loads per tensor instead of twenty-four. Row sums add a lane's columns in increasing order and combine the
+// lanes in the same butterfly as before; the partition is by shape alone, so results are the same from run to run.
+__device__ __forceinline__ uint2 bf16x4_bits(float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  return make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256)
+layernorm_fwd_vec_kernel(const float* __restrict__ x, const float* __restrict__ addend, float* __restrict__ sum_out,
+                         const float* __restrict__ gamma, const float* __restrict__ beta, int32_t rows, int32_t cols, float eps,
+                         float* __restrict__ y, uint16_t* __restrict__ y16, float* __restrict__ mean_out, float* __restrict__ inv_out) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), warps = (int64_t)gridDim.x * 8;
+  const float n = (float)cols;
+  const int nv = cols >> 2;
+  float4 gam[NV], bet[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const int j = lane + 32 * i;
+    gam[i] = j < nv ? __ldg(reinterpret_cast<const float4*>(gamma) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    bet[i] = j < nv ? __ldg(reinterpret_cast<const float4*>(beta) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int64_t r = warp; r < rows; r += warps) {
+    const float4* xr = reinterpret_cast<const float4*>(x + r * cols);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int j = lane + 32 * i;
+      v[i] = j < nv ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (addend) {
+      // The residual sum x + addend is formed here (and written out: the backward pass normalises it again).
+      const float4* ar = reinterpret_cast<const float4*>(addend + r * cols);
+      float4 a[NV];
+#pragma unroll
+      for (int i = 0; i < NV; i++) {
+        const int j = lane + 32 * i;
+        a[i] = j < nv ? ar[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float4* sr = reinterpret_cast<float4*>(sum_out + r * cols);
+#pragma unroll
+      for (int i = 0; i < NV; i++) {
+        const int j = lane + 32 * i;
+        v[i].x += a[i].x; v[i].y += a[i].y; v[i].z += a[i].z; v[i].w += a[i].w;
+        if (j < nv) sr[j] = v[i];
+      }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++)
+      if (lane + 32 * i < nv) s += ((v[i].x + v[i].y) + v[i].z) + v[i].w;
+    const float mean = wsum_f(s) / n;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++)
+      if (lane + 32 * i < nv) {
+        const float d0 = v[i].x - mean, d1 = v[i].y - mean, d2 = v[i].z - mean, d3 = v[i].w - mean;
+        q += ((d0 * d0 + d1 * d1) + d2 * d2) + d3 * d3;
+      }
+    const float inv = 1.0f / sqrtf((wsum_f(q) / n) + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[r] = mean;
+      if (inv_out) inv_out[r] = inv;
+    }
+    float4* yr = reinterpret_cast<float4*>(y + r * cols);
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int j = lane + 32 * i;
+      if (j < nv) {
+        float4 o;
+        o.x = (((v[i].x - mean) * inv) * gam[i].x) + bet[i].x;
+        o.y = (((v[i].y - mean) * inv) * gam[i].y) + bet[i].y;
+        o.z = (((v[i].z - mean) * inv) * gam[i].z) + bet[i].z;
+        o.w = (((v[i].w - mean) * inv) * gam[i].w) + bet[i].w;
+        yr[j] = o;
+        if (y16) reinterpret_cast<uint2*>(y16 + r * cols)[j] = bf16x4_bits(o);
+      }
+    }
+  }
+}
+
+// Backward: a CTA owns kLnVecRows consecutive rows, a warp takes every eighth of them; otherwise as layernorm_bwd_fused_kernel.
+constexpr int kLnVecRows = 56;
+template <int NV>
+__global__ void __launch_bounds__(256, 2)
+layernorm_bwd_vec_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
+                         const float* __restrict__ mean, const float* __restrict__ inv, int32_t rows, int32_t cols,
+                         float* __restrict__ dx, uint16_t* __restrict__ dx16, double* __restrict__ part_gamma, double* __restrict__ part_beta) {
+  pdl_enter();
+  extern __shared__ double ln_smem[];            // [8][cols]
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int nv = cols >> 2;
+  const int r0 = blockIdx.x * kLnVecRows;
+  const int r1 = min(rows, r0 + kLnVecRows);
+  float4 ag[NV], ab[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) ag[i] = ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = r0 + w; r < r1; r += 8) {
+    const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)r * cols);
+    const float4* gr = reinterpret_cast<const float4*>(g + (int64_t)r * cols);
+    float4 xh[NV], dh[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int j = lane + 32 * i;
+      xh[i] = j < nv ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+      dh[i] = j < nv ? gr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float m = mean[r], s = inv[r];
+    double sum1 = 0.0, sum2 = 0.0;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int j = lane + 32 * i;
+      if (j < nv) {
+        const float4 gm = __ldg(reinterpret_cast<const float4*>(gamma) + j);   // gamma stays in L1: registers would not fit two CTAs per SM
+        const float4 gv = dh[i];
+        xh[i].x = (xh[i].x - m) * s; xh[i].y = (xh[i].y - m) * s; xh[i].z = (xh[i].z - m) * s; xh[i].w = (xh[i].w - m) * s;
+        dh[i].x = gv.x * gm.x; dh[i].y = gv.y * gm.y; dh[i].z = gv.z * gm.z; dh[i].w = gv.w * gm.w;
+        ag[i].x += gv.x * xh[i].x; ag[i].y += gv.y * xh[i].y; ag[i].z += gv.z * xh[i].z; ag[i].w += gv.w * xh[i].w;
+        ab[i].x += gv.x; ab[i].y += gv.y; ab[i].z += gv.z; ab[i].w += gv.w;
+        sum1 += (double)dh[i].x; sum1 += (double)dh[i].y; sum1 += (double)dh[i].z; sum1 += (double)dh[i].w;
+        sum2 += (double)(dh[i].x * xh[i].x); sum2 += (double)(dh[i].y * xh[i].y); sum2 += (double)(dh[i].z * xh[i].z);
+        sum2 += (double)(dh[i].w * xh[i].w);
+      }
+    }
+    sum1 = wsum_d(sum1);
+    sum2 = wsum_d(sum2);
+    const float m1 = (float)(sum1 / cols), m2 = (float)(sum2 / cols);
+    if (dx) {
+      float4* dr = reinterpret_cast<float4*>(dx + (int64_t)r * cols);
+#pragma unroll
+      for (int i = 0; i < NV; i++) {
+        const int j = lane + 32 * i;
+        if (j < nv) {
+          float4 o;
+          o.x = s * ((dh[i].x - m1) - (xh[i].x * m2));
+          o.y = s * ((dh[i].y - m1) - (xh[i].y * m2));
+          o.z = s * ((dh[i].z - m1) - (xh[i].z * m2));
+          o.w = s * ((dh[i].w - m1) - (xh[i].w * m2));
+          dr[j] = o;
+          if (dx16) reinterpret_cast<uint2*>(dx16 + (int64_t)r * cols)[j] = bf16x4_bits(o);
+        }
+      }
+    }
+  }
+  // The CTA's column sums: warps in order, one table after the other through the same shared memory.
+#pragma unroll 1
+  for (int table = 0; table < 2; table++) {
+    double* out = table == 0 ? part_gamma : part_beta;
+    if (!out) continue;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int j = lane + 32 * i;
+      if (j < nv) {
+        const float4 a = table == 0 ? ag[i] : ab[i];
+        double* dst = ln_smem + (size_t)w * cols + 4 * j;
+        dst[0] = (double)a.x; dst[1] = (double)a.y; dst[2] = (double)a.z; dst[3] = (double)a.w;
+      }
     }
     __syncthreads();
     for (int j = threadIdx.x; j < cols; j += 256) {
@@ -407,14 +594,34 @@ extern "C" {
 
 int32_t om_layernorm_fwd_b16(om_ctx* ctx, const float* x, const float* gamma, const float* beta, int32_t rows, int32_t cols,
                              float eps, float* y, uint16_t* y16, float* mean, float* inv) {
+  return om_add_layernorm_fwd_b16(ctx, x, nullptr, nullptr, gamma, beta, rows, cols, eps, y, y16, mean, inv);
+}
+
+int32_t om_add_layernorm_fwd_b16(om_ctx* ctx, const float* x, const float* addend, float* sum, const float* gamma, const float* beta,
+                                 int32_t rows, int32_t cols, float eps, float* y, uint16_t* y16, float* mean, float* inv) {
   OM_CHECK_CTX(ctx);
   if (rows < 0 || cols < 0) return fail(ctx, OM_ERR_SHAPE, "om_layernorm_fwd: [%d,%d]", rows, cols);
   if (rows == 0 || cols == 0) return OM_OK;
-  ProfileScope prof(ctx, "om_layernorm_fwd", 0, (y16 ? 10.0 : 8.0) * rows * (double)cols);
+  if ((addend != nullptr) != (sum != nullptr)) return fail(ctx, OM_ERR_ARG, "om_add_layernorm_fwd_b16: the addend and the sum go together");
+  if (addend && cols > 1024) return fail(ctx, OM_ERR_UNSUPPORTED, "om_add_layernorm_fwd_b16: rows wider than 1024 (%d): add first, then om_layernorm_fwd", cols);
+  ProfileScope prof(ctx, "om_layernorm_fwd", 0, ((y16 ? 10.0 : 8.0) + (addend ? 8.0 : 0.0)) * rows * (double)cols);
   int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 8);
   const int nc = (int)ceil_div(cols, 32);
-  if (nc <= 32) {
-#define OM_LN_FWD(NC) launch_chained(ctx, layernorm_fwd_reg_kernel<NC>, grid, 256, 0, x, gamma, beta, rows, cols, eps, y, y16, mean, inv)
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec = (cols & 3) == 0 && cols <= 1024 && al16(x) && al16(y) && al16(gamma) && al16(beta) && (!addend || (al16(addend) && al16(sum))) &&
+                   (!y16 || (reinterpret_cast<uintptr_t>(y16) & 7) == 0);
+  if (vec) {
+    const int nvec = (int)ceil_div(cols, 128);
+#define OM_LN_FWDV(NV) launch_chained(ctx, layernorm_fwd_vec_kernel<NV>, grid, 256, 0, x, addend, sum, gamma, beta, rows, cols, eps, y, y16, mean, inv)
+    if (nvec <= 1) OM_LN_FWDV(1);
+    else if (nvec <= 2) OM_LN_FWDV(2);
+    else if (nvec <= 3) OM_LN_FWDV(3);
+    else if (nvec <= 4) OM_LN_FWDV(4);
+    else if (nvec <= 6) OM_LN_FWDV(6);
+    else OM_LN_FWDV(8);
+#undef OM_LN_FWDV
+  } else if (nc <= 32) {
+#define OM_LN_FWD(NC) launch_chained(ctx, layernorm_fwd_reg_kernel<NC>, grid, 256, 0, x, addend, sum, gamma, beta, rows, cols, eps, y, y16, mean, inv)
     if (nc <= 4) OM_LN_FWD(4);
     else if (nc <= 8) OM_LN_FWD(8);
     else if (nc <= 12) OM_LN_FWD(12);
@@ -445,8 +652,10 @@ int32_t om_layernorm_bwd_b16(om_ctx* ctx, const float* g, const float* x, const 
   if (dx16 && !dx) return fail(ctx, OM_ERR_ARG, "om_layernorm_bwd_b16: the bfloat16 copy needs dx");
   ProfileScope prof(ctx, "om_layernorm_bwd", 0, (dx16 ? 14.0 : 12.0) * rows * (double)cols);
   const int nc = (int)ceil_div(cols, 32);
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec = (cols & 3) == 0 && al16(g) && al16(x) && al16(gamma) && (!dx || al16(dx)) && (!dx16 || (reinterpret_cast<uintptr_t>(dx16) & 7) == 0);
   // One pass: dx and the CTAs' column partials together; the partials are then added in CTA order.
-  const int used = (int)ceil_div(rows > 0 ? rows : 1, kLnFusedRows);
+  const int used = (int)ceil_div(rows > 0 ? rows : 1, vec ? kLnVecRows : kLnFusedRows);
   double *pg = nullptr, *pb = nullptr;
   if (dgamma) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)used * cols, false, (void**)&pg));
   if (dbeta) OM_TRY(pool_alloc(ctx, sizeof(double) * (size_t)used * cols, false, (void**)&pb));
@@ -460,13 +669,30 @@ int32_t om_layernorm_bwd_b16(om_ctx* ctx, const float* g, const float* x, const 
     }                                                                                                                            \
     launch_chained(ctx, layernorm_bwd_fused_kernel<NC>, used, 256, smem, g, x, gamma, mean, inv, rows, cols, dx, dx16, pg, pb); \
   } while (0)
-  if (nc <= 4) OM_LN_BWD(4);
+#define OM_LN_BWDV(NV)                                                                                                           \
+  do {                                                                                                                           \
+    static bool attr_set = false;                                                                                                \
+    if (!attr_set) {                                                                                                             \
+      OM_CUDA(ctx, cudaFuncSetAttribute(layernorm_bwd_vec_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 1024 * 8)); \
+      attr_set = true;                                                                                                           \
+    }                                                                                                                            \
+    launch_chained(ctx, layernorm_bwd_vec_kernel<NV>, used, 256, smem, g, x, gamma, mean, inv, rows, cols, dx, dx16, pg, pb);   \
+  } while (0)
+  const int nvec = (int)ceil_div(cols, 128);
+  if (vec && nvec <= 1) OM_LN_BWDV(1);
+  else if (vec && nvec <= 2) OM_LN_BWDV(2);
+  else if (vec && nvec <= 3) OM_LN_BWDV(3);
+  else if (vec && nvec <= 4) OM_LN_BWDV(4);
+  else if (vec && nvec <= 6) OM_LN_BWDV(6);
+  else if (vec) OM_LN_BWDV(8);
+  else if (nc <= 4) OM_LN_BWD(4);
   else if (nc <= 8) OM_LN_BWD(8);
   else if (nc <= 12) OM_LN_BWD(12);
   else if (nc <= 16) OM_LN_BWD(16);
   else if (nc <= 24) OM_LN_BWD(24);
   else OM_LN_BWD(32);
 #undef OM_LN_BWD
+#undef OM_LN_BWDV
   if (dgamma || dbeta)
     launch_chained(ctx, column_partials_finish_kernel, (unsigned)ceil_div(cols, 32), 512, 0, pg, pb, used, cols, dgamma, dbeta, accumulate_params);
   if (pg) pool_free(ctx, pg);

@@ -173,6 +173,7 @@ OMH_API int32_t omh_call(const char* op, int32_t n_in, omh_tensor* const* in, in
     else if (name == "softmax") r = Ops::Softmax(T(0), (int)I(0, -1));
     else if (name == "log_softmax") r = Ops::LogSoftmax(T(0), (int)I(0, -1));
     else if (name == "layer_norm") r = Ops::LayerNorm(T(0), T(1), T(2), (float)F(0, 1e-5));
+    else if (name == "add_layer_norm") r = Ops::AddLayerNorm(T(0), T(1), T(2), T(3), (float)F(0, 1e-5));
     else if (name == "batch_norm2d") r = Ops::BatchNorm2d(T(0), T(1), T(2), T(3), T(4), I(0) != 0, (float)F(0, 0.1), (float)F(1, 1e-5));
     else if (name == "embedding") r = Ops::Embedding(T(0), T(1), (int)I(0, -1));
     else if (name == "nll_loss") r = Ops::NllLoss(T(0), T(1), I(0, 1) != 0, (int)I(1, -100));

@@ -244,9 +244,9 @@ TransformerEncoderLayer::TransformerEncoderLayer(int width, int heads, int ff, G
 
 Tensor TransformerEncoderLayer::Forward(const Tensor& input, const Tensor& mask) {
   Tensor a = Attn->Forward(input, mask);
-  Tensor x1 = Norm1->Forward(Ops::Add(input, a));
+  Tensor x1 = Ops::AddLayerNorm(input, a, Norm1->Gamma, Norm1->Beta, Norm1->Epsilon);
   Tensor f = Ops::FeedForward(x1, Ff1->Weight, Ff1->Bias, Ff2->Weight, Ff2->Bias);
-  return Norm2->Forward(Ops::Add(x1, f));
+  return Ops::AddLayerNorm(x1, f, Norm2->Gamma, Norm2->Beta, Norm2->Epsilon);
 }
 
 void Conv1d::Init(int inCh, int outCh, int kernel, Generator& g, bool bias) {

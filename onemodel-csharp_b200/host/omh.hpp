@@ -315,6 +315,8 @@ struct Ops {
   static Tensor Softmax(const Tensor& x, int axis = -1);
   static Tensor LogSoftmax(const Tensor& x, int axis = -1);
   static Tensor LayerNorm(const Tensor& x, const Tensor& gamma, const Tensor& beta, float epsilon = 1e-5f);
+  // LayerNorm(Add(a, b), gamma, beta) in one pass over a and b (the residual connection in front of a layer norm).
+  static Tensor AddLayerNorm(const Tensor& a, const Tensor& b, const Tensor& gamma, const Tensor& beta, float epsilon = 1e-5f);
   static Tensor BatchNorm2d(const Tensor& x, const Tensor& gamma, const Tensor& beta, const Tensor& runningMean,
                             const Tensor& runningVar, bool training, float momentum = 0.1f, float epsilon = 1e-5f);
   static Tensor Conv2d(const Tensor& x, const Tensor& weight, const Tensor& bias, const Conv2dParams& p);

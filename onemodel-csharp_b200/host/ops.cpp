@@ -229,6 +229,38 @@ Tensor Ops::LayerNorm(const Tensor& x, const Tensor& gamma, const Tensor& beta, 
   return br->Attach(r);
 }
 
+// LayerNorm(Add(a, b)) with the sum formed inside the layer norm's kernel. The tape holds the same two records as the two
+// separate ops (an Add whose result is the sum, a LayerNorm over it), so the backward pass is theirs.
+Tensor Ops::AddLayerNorm(const Tensor& a, const Tensor& b, const Tensor& gamma, const Tensor& beta, float eps) {
+  const int cols = a.Rank() > 0 ? a.GetShape()[a.Rank() - 1] : 0;
+  const bool fused = a.GetDType() == DType::F32 && b.GetDType() == DType::F32 && a.GetShape() == b.GetShape() && a.IsContiguous() && b.IsContiguous() &&
+                     cols > 0 && cols <= 1024 && gamma.Rank() == 1 && beta.Rank() == 1 && gamma.GetShape()[0] == cols && beta.GetShape()[0] == cols;
+  if (!fused) return LayerNorm(Add(a, b), gamma, beta, eps);
+  const int rows = (int)(a.Length() / cols);
+  Tensor gc = gamma.Contiguous(), bc = beta.Contiguous();
+  Tensor sum = NewOut(a.GetShape()), r = NewOut(a.GetShape());
+  const bool rec_add = Recording({&a, &b});
+  if (rec_add) sum = BackwardRecord::Create(OpKind::Add, 0, {&a, &b})->Attach(sum);
+  const bool rec = Recording({&sum, &gamma, &beta});
+  Tensor mean, inv;
+  if (rec) {
+    mean = Tensor::Create(DType::F32, Shape{rows});
+    inv = Tensor::Create(DType::F32, Shape{rows});
+  }
+  const bool b16 = Bf16Products();
+  Check(om_add_layernorm_fwd_b16(C(), a.Data(), b.Data(), sum.Data(), gc.Data(), bc.Data(), rows, cols, eps, r.Data(), b16 ? r.Bf16ForWrite() : nullptr,
+                                 rec ? mean.Data() : nullptr, rec ? inv.Data() : nullptr));
+  if (b16) r.Bf16Written();
+  if (!rec) return r;
+  auto br = BackwardRecord::Create(OpKind::LayerNorm, 4, {&sum, &gamma, &beta});
+  br->Save(0, sum.Detach());
+  br->Save(1, gc.Detach());
+  br->Save(2, mean);
+  br->Save(3, inv);
+  br->Floats = {eps};
+  return br->Attach(r);
+}
+
 Tensor Ops::BatchNorm2d(const Tensor& x, const Tensor& gamma, const Tensor& beta, const Tensor& runningMean,
                         const Tensor& runningVar, bool training, float momentum, float eps) {
   RequireFloat32(x);

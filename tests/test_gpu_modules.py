@@ -187,3 +187,30 @@ def test_padded_rows_equal_rows_run_alone(ctx, omb, bidirectional, gru, batch_fi
             model.forward_lengths(x, bad)
     with pytest.raises(omb.OmError):
         omb.Module("linear", omb.Generator(1), [3, 2, 1]).forward_lengths(x, lengths)
+
+
+@pytest.mark.parametrize("flags", [0, 3])       # 3: OM_TF32 | OM_BF16_OPERANDS
+@pytest.mark.parametrize("shape", [(3, 7, 768), (64, 40), (2, 5, 1000), (9, 30)])
+def test_add_layer_norm_equals_add_then_layer_norm(ctx, omb, flags, shape):
+    """Ops.AddLayerNorm (the residual sum formed inside the layer norm's kernel) against Add followed by LayerNorm: the result
+    and the four gradients bit for bit, for widths with and without 16-byte rows."""
+    ctx.set_flags(flags)
+    ctx.make_current()
+    try:
+        r = np.random.default_rng(shape[-1])
+        av, bv = r.standard_normal(shape).astype(np.float32), r.standard_normal(shape).astype(np.float32)
+        gv, ev = (1 + 0.1 * r.standard_normal(shape[-1])).astype(np.float32), (0.1 * r.standard_normal(shape[-1])).astype(np.float32)
+        up = r.standard_normal(shape).astype(np.float32)
+        results = []
+        for fused in (True, False):
+            a, b, g, e = (omb.Tensor.from_numpy(v, True) for v in (av, bv, gv, ev))
+            if fused:
+                y = omb.call("add_layer_norm", [a, b, g, e], floats=[1e-5])
+            else:
+                y = omb.call("layer_norm", [omb.call("add", [a, b]), g, e], floats=[1e-5])
+            y.backward(omb.Tensor.from_numpy(up))
+            results.append([y.numpy()] + [t.grad.numpy() for t in (a, b, g, e)])
+        for x, z in zip(*results):
+            assert np.all(np.isfinite(x)) and np.array_equal(x, z)
+    finally:
+        ctx.set_flags(0)
