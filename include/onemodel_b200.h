@@ -263,6 +263,18 @@ int32_t om_linear_fwd_bf16_act(om_ctx* ctx, const uint16_t* x, const uint16_t* W
 int32_t om_linear_dgrad_bf16_act(om_ctx* ctx, const uint16_t* g16, int32_t ldg, const uint16_t* W, int32_t rows,
                                  int32_t in_features, int32_t out_features, int32_t op, const float* pre, int32_t ldpre,
                                  float* dx, uint16_t* dx16);
+/* The same pair with the activation's derivative left behind by the forward pass, so that the backward epilogue only
+ * multiplies: om_linear_fwd_bf16_actd writes deriv = op'(x W^T + bias) (fp32, pitch ldd) and a16 = bfloat16(op(x W^T + bias));
+ * om_linear_dgrad_bf16_mul writes dx = factor * (g W) with factor = that derivative ([rows, in_features], pitch ldf), as
+ * fp32 and / or bfloat16 (either of dx and dx16 may be NULL). The values are those of om_linear_fwd_bf16_act /
+ * om_linear_dgrad_bf16_act, bit for bit; the derivative is evaluated once, where the activation is. Supported shapes as
+ * for those (om_linear_act_bf16_supported). */
+int32_t om_linear_fwd_bf16_actd(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows,
+                                int32_t in_features, int32_t out_features, int32_t op, float* deriv, uint16_t* a16,
+                                int32_t ldd);
+int32_t om_linear_dgrad_bf16_mul(om_ctx* ctx, const uint16_t* g16, int32_t ldg, const uint16_t* W, int32_t rows,
+                                 int32_t in_features, int32_t out_features, const float* factor, int32_t ldf, float* dx,
+                                 uint16_t* dx16);
 /* dx = residual + g W, out of place: the input gradient of a Linear layer whose input already holds a gradient from
  * another branch (a residual connection). The sum is formed in the product's epilogue from a plain read of `residual`
  * ([rows, in_features] fp32 with pitch ldres), so that tensor is not modified and may stay shared with its other readers

@@ -86,4 +86,20 @@ __device__ __forceinline__ float unary_grad(float g, float s) {
   return g;
 }
 
+// An activation and its derivative at the same point, for a product epilogue that leaves both behind (the derivative is what
+// the backward pass multiplies by, so nothing of the activation has to be evaluated again there). deriv equals
+// unary_grad<OP>(1, x), bit for bit: the erf form shares its erf and its Gaussian between the two.
+template <int OP>
+__device__ __forceinline__ void unary_both(float x, float* act, float* deriv) {
+  if (OP == OM_GELU_ERF_FAST) {
+    float gauss;
+    const float erf = erf_fast(x * 0.70710677f, &gauss);
+    *act = (0.5f * x) * (1.0f + erf);
+    *deriv = 1.0f * ((0.5f * (1.0f + erf)) + x * (gauss * 0.3989423f));
+  } else {
+    *act = unary_apply<OP>(x);
+    *deriv = unary_grad<OP>(1.0f, x);
+  }
+}
+
 }  // namespace om

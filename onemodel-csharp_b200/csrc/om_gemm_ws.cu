@@ -139,7 +139,10 @@ constexpr size_t ws_smem_bytes() {
 //   2: C and its bfloat16 copy receive d/dx OP(aux) * product, aux being the activation's saved input: the input
 //      gradient of the layer after the activation, already multiplied by the activation's derivative;
 //   3: C (and its copy) receive aux + product: a gradient that joins another branch's (a residual connection) without
-//      a read-modify-write of that branch's tensor, which may then stay shared with its other readers.
+//      a read-modify-write of that branch's tensor, which may then stay shared with its other readers;
+//   4: C (and its copy) receive aux * product: the input gradient through an activation whose derivative was left behind by
+//      the forward pass (5), with no transcendental arithmetic in this epilogue;
+//   5: as 1, but C receives OP'(product + bias), the derivative that 4 multiplies by, instead of the product itself.
 // EW epilogue warps (four, or eight when the epilogue has this arithmetic to do).
 template <int ELEM, int BN, bool A_MN, bool B_MN, int ACT = 0, int OP = 0, int EW = W_EPI_WARPS, int ST = W_STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (2 + EW), 1)
@@ -288,7 +291,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // ACT 2, 3: this lane's 32 values of the extra operand for a column block (n is a multiple of four, so that a 16-byte
       // load never straddles the last column), asked for before the accumulator block is read back; the other warps of
       // the quadrant work while they are on their way.
-      float4 aux[8];
+      // With eight epilogue warps (two per lane quadrant) the next block's values are asked for a block ahead, into a second
+      // set of registers; with sixteen the other warps of the quadrant cover the wait.
+      constexpr bool AHEAD = (ACT >= 2 && ACT <= 4) && EW == 8;
+      float4 aux[8], nxt[AHEAD ? 8 : 1];
       auto load_aux = [&](float4 (&dst)[8], int cb) {
         const int c0 = n0 + cb * 32, row = row_base + lane;
         const bool in = row < p.m && c0 < p.n;
@@ -296,6 +302,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
         for (int c4 = 0; c4 < 8; c4++) dst[c4] = (in && c0 + 4 * c4 < p.n) ? __ldg(src + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
       };
+      if (AHEAD) load_aux(aux, part * CB_PER);
       ok = mbar_wait(&acc_full[a], use & 1, abort_flag, p.status, 44);
       if (!ok) break;
       tc_fence_after();
@@ -305,7 +312,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int col0 = n0 + cb * 32;
         const bool live = row_base < p.m && col0 < p.n;
         uint32_t r[32];
-        if (ACT >= 2) load_aux(aux, cb);
+        if (AHEAD) {
+          if (cb + 1 < (part + 1) * CB_PER) load_aux(reinterpret_cast<float4(&)[8]>(nxt), cb + 1);
+        } else if (ACT >= 2 && ACT <= 4) {
+          load_aux(aux, cb);
+        }
         if (live) {
           tmem_ld_32x32b_x32(tmem_acc + (uint32_t)(cb * 32), r);
           tmem_ld_wait();
@@ -327,6 +338,29 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             r[4 * c4 + 3] = __float_as_uint(unary_grad<OP>(__uint_as_float(r[4 * c4 + 3]), aux[c4].w));
           }
         }
+        if (ACT == 4) {
+#pragma unroll
+          for (int c4 = 0; c4 < 8; c4++) {
+            r[4 * c4 + 0] = __float_as_uint(__uint_as_float(r[4 * c4 + 0]) * aux[c4].x);
+            r[4 * c4 + 1] = __float_as_uint(__uint_as_float(r[4 * c4 + 1]) * aux[c4].y);
+            r[4 * c4 + 2] = __float_as_uint(__uint_as_float(r[4 * c4 + 2]) * aux[c4].z);
+            r[4 * c4 + 3] = __float_as_uint(__uint_as_float(r[4 * c4 + 3]) * aux[c4].w);
+          }
+        }
+        uint32_t act16[ACT == 5 ? 16 : 1];
+        if (ACT == 5) {
+          // The activation (kept as packed bfloat16 until the fp32 block has left the slot) and its derivative (the fp32 block).
+#pragma unroll
+          for (int c = 0; c < 16; c++) {
+            float a0, a1, d0, d1;
+            unary_both<OP>(__uint_as_float(r[2 * c]), &a0, &d0);
+            unary_both<OP>(__uint_as_float(r[2 * c + 1]), &a1, &d1);
+            __nv_bfloat162 h = __floats2bfloat162_rn(a0, a1);
+            act16[c] = *reinterpret_cast<uint32_t*>(&h);
+            r[2 * c] = __float_as_uint(d0);
+            r[2 * c + 1] = __float_as_uint(d1);
+          }
+        }
         if (ACT == 3) {
 #pragma unroll
           for (int c4 = 0; c4 < 8; c4++) {
@@ -335,6 +369,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             r[4 * c4 + 2] = __float_as_uint(aux[c4].z + __uint_as_float(r[4 * c4 + 2]));
             r[4 * c4 + 3] = __float_as_uint(aux[c4].w + __uint_as_float(r[4 * c4 + 3]));
           }
+        }
+        if (AHEAD) {
+#pragma unroll
+          for (int c4 = 0; c4 < 8; c4++) aux[c4] = nxt[AHEAD ? c4 : 0];
         }
         if (stored >= W_RING) {
           // The block about to be overwritten was handed to the TMA unit W_RING stores ago.
@@ -360,7 +398,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                          : "memory");
           }
         };
-        const bool both_at_once = W_SLOT >= 6144 && ACT != 1;
+        const bool both_at_once = W_SLOT >= 6144 && ACT != 1 && ACT != 5;
         if (p.store32) {
           const uint32_t row_addr = smem_u32(blk) + (uint32_t)lane * 128u;
 #pragma unroll
@@ -397,7 +435,16 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             __syncwarp();
           }
-          stage_bf16(blk);
+          if (ACT == 5) {
+            const uint32_t row16 = smem_u32(blk) + (uint32_t)lane * 64u;
+#pragma unroll
+            for (int c8 = 0; c8 < 4; c8++)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row16 + (uint32_t)((c8 ^ ((lane >> 1) & 3)) << 4)), "r"(act16[4 * c8]),
+                           "r"(act16[4 * c8 + 1]), "r"(act16[4 * c8 + 2]), "r"(act16[4 * c8 + 3])
+                           : "memory");
+          } else {
+            stage_bf16(blk);
+          }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0) {
@@ -509,11 +556,12 @@ static int32_t ws_launch(om_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& m
 template <int ACT, int OP>
 static int32_t ws_launch_act(om_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& mc16,
                              const WsParams& p, int units) {
-  // The plain sum (ACT 3) has next to no arithmetic: eight warps and the full operand ring, like the products without an epilogue operand.
-  constexpr int EW = ACT == 3 ? 8 : W_ACT_EPI_WARPS, ST = ACT == 3 ? W_STAGES : W_ACT_STAGES;
+  // The plain sum (ACT 3) has next to no arithmetic and joins long products: eight warps and the full operand ring.
+  constexpr bool light = ACT == 3 || ACT == 4;
+  constexpr int EW = light ? 8 : W_ACT_EPI_WARPS, ST = light ? W_STAGES : W_ACT_STAGES;
   constexpr size_t smem = ws_smem_bytes<256, EW, ST>();
   constexpr int threads = 32 * (2 + EW);
-  auto kernel = gemm_ws_kernel<1, 256, false, ACT >= 2, ACT, OP, EW, ST>;
+  auto kernel = gemm_ws_kernel<1, 256, false, (ACT >= 2 && ACT <= 4), ACT, OP, EW, ST>;
   static int max_clusters = 0;
   if (max_clusters == 0) {
     OM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -545,6 +593,7 @@ bool gemm_ws_c16_ok(const uint16_t* C16, long long ldc, int acc) {
 int32_t cast_bf16_rows(om_ctx* ctx, const float* src, uint16_t* dst, int rows, int cols, long long ld);
 
 // act 0: none. act 1 with op: C16 receives op(C) instead of C. act 2 with op: C and C16 receive op'(aux) * C. act 3: aux + C.
+// act 4: aux * C. act 5 with op: C receives op'(C), C16 op(C).
 // gemm_ws_act_ok tells whether a product can take the activation (no split of k, the layouts above).
 static int ws_splits(int tiles, int k_blocks) {
   // Fixed split of k by shape alone: enough slices for one round of pairs, each at least 8 k-blocks deep.
@@ -558,14 +607,15 @@ static int ws_splits(int tiles, int k_blocks) {
 }
 
 bool gemm_ws_act_ok(int act, int op, int m, int n, int k, const float* C, long long ldc, const uint16_t* C16, const float* aux, long long ld_aux) {
-  if (act < 1 || act > 3) return false;
-  if (act != 3 && op != OM_GELU_ERF && op != OM_GELU_TANH) return false;
+  if (act < 1 || act > 5) return false;
+  const bool fwd = act == 1 || act == 5, with_aux = act >= 2 && act <= 4;
+  if (act != 3 && act != 4 && op != OM_GELU_ERF && op != OM_GELU_TANH) return false;
   if (m < 1 || n < 256 || (n & 3)) return false;
   const int tiles = (int)(ceil_div(m, 2 * W_BM) * ceil_div(n, 256));
   if (ws_splits(tiles, (int)ceil_div(k, 64)) != 1) return false;
-  if (act == 1 && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
-  if (act >= 2 && (C16 != nullptr) && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
-  if (act >= 2 && (!aux || (ld_aux & 3) || (reinterpret_cast<uintptr_t>(aux) & 15))) return false;
+  if (fwd && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
+  if (with_aux && (C16 != nullptr) && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
+  if (with_aux && (!aux || (ld_aux & 3) || (reinterpret_cast<uintptr_t>(aux) & 15))) return false;
   (void)C;
   return true;
 }
@@ -585,7 +635,7 @@ int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, 
   if (!store32 && (!C16 || acc || elem != 1))
     return fail(ctx, OM_ERR_ARG, "persistent product: without an fp32 result the bfloat16 one is required (bfloat16 operands, no accumulation)");
   if (act != 0) {
-    if (elem != 1 || acc || a_mn || b_mn != (act >= 2) || !gemm_ws_act_ok(act, op, m, n, k, C, ldc, C16, aux, ld_aux))
+    if (elem != 1 || acc || a_mn || b_mn != (act >= 2 && act <= 4) || !gemm_ws_act_ok(act, op, m, n, k, C, ldc, C16, aux, ld_aux))
       return fail(ctx, OM_ERR_UNSUPPORTED, "persistent product: this shape or layout cannot take the activation in its epilogue (m %d n %d k %d)", m, n, k);
   }
   const int bk = elem == 0 ? 32 : 64, mn_chunk = elem == 0 ? 32 : 64;
@@ -637,6 +687,9 @@ int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, 
   else if (act == 2) st = op == OM_GELU_ERF ? ws_launch_act<2, OM_GELU_ERF_FAST>(ctx, map_a, map_b, map_c, map_c16, p, units)
                                             : ws_launch_act<2, OM_GELU_TANH>(ctx, map_a, map_b, map_c, map_c16, p, units);
   else if (act == 3) st = ws_launch_act<3, 0>(ctx, map_a, map_b, map_c, map_c16, p, units);
+  else if (act == 4) st = ws_launch_act<4, 0>(ctx, map_a, map_b, map_c, map_c16, p, units);
+  else if (act == 5) st = op == OM_GELU_ERF ? ws_launch_act<5, OM_GELU_ERF_FAST>(ctx, map_a, map_b, map_c, map_c16, p, units)
+                                            : ws_launch_act<5, OM_GELU_TANH>(ctx, map_a, map_b, map_c, map_c16, p, units);
   else if (elem == 0) st = bn == 256 ? ws_launch<0, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<0, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
   else st = bn == 256 ? ws_launch<1, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<1, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
   if (st == OM_OK && splits > 1) splitk_reduce_launch(ctx, workspace, splits, (int64_t)m * n, n, ldc, bias, C, acc);

@@ -264,17 +264,17 @@ static void LinearBackward(Engine& e, BackwardRecord& r, const Tensor& g) {
   }
 }
 
-// The record of Ops::FeedForward (inputs x, w1, b1, w2, b2; saved x, w1, w2, the first layer's result before the
-// activation, the activation's result as bfloat16; Ints = {rows, in, ff, out, op}). The second layer's input gradient comes
+// The record of Ops::FeedForward (inputs x, w1, b1, w2, b2; saved x, w1, w2, the activation's derivative at the first layer's
+// result, the activation's result as bfloat16; Ints = {rows, in, ff, out, op}). The second layer's input gradient comes
 // out of its product already multiplied by the activation's derivative, as fp32 (the first layer's bias gradient sums it)
 // and as bfloat16 (the operand of the first layer's two gradient products).
 static void FeedForwardBackward(BackwardRecord& r, const Tensor& g) {
   const Tensor& x = r.Saved(0);
   const Tensor& w1 = r.Saved(1);
   const Tensor& w2 = r.Saved(2);
-  const Tensor& pre = r.Saved(3);
+  const Tensor& pre = r.Saved(3);      // the activation's derivative (see Ops::FeedForward)
   const Tensor& act16 = r.Saved(4);
-  const int rows = (int)r.Ints[0], inF = (int)r.Ints[1], ff = (int)r.Ints[2], outF = (int)r.Ints[3], op = (int)r.Ints[4];
+  const int rows = (int)r.Ints[0], inF = (int)r.Ints[1], ff = (int)r.Ints[2], outF = (int)r.Ints[3];
   Tensor gc = g.Contiguous();
   struct Leaf {
     float* p = nullptr;
@@ -308,7 +308,7 @@ static void FeedForwardBackward(BackwardRecord& r, const Tensor& g) {
   // gradients of the first layer are products that read it as an operand (the bias gradient is g^T 1).
   Tensor dpre16 = Tensor::Create(DType::I32, Shape{rows, ff / 2});
   const uint16_t* d16 = (const uint16_t*)dpre16.RawData();
-  Check(om_linear_dgrad_bf16_act(C(), g16, outF, w2.Bf16(), rows, ff, outF, op, pre.Data(), ff, nullptr, (uint16_t*)dpre16.RawData()));
+  Check(om_linear_dgrad_bf16_mul(C(), g16, outF, w2.Bf16(), rows, ff, outF, pre.Data(), ff, nullptr, (uint16_t*)dpre16.RawData()));
   // First layer.
   Tensor dx;
   bool dx_into_pending = false;

@@ -400,12 +400,13 @@ Tensor Ops::FeedForward(const Tensor& x, const Tensor& w1, const Tensor& b1, con
   Shape hs = x.GetShape(), os = x.GetShape();
   hs.d[hs.rank - 1] = ff;
   os.d[os.rank - 1] = outF;
-  // The first layer's result before the activation (fp32: the activation's backward needs it) and the activation's
-  // result as bfloat16 only (two per 32-bit word of an integer tensor): nothing but the second product reads it.
+  // The activation's derivative at the first layer's result (fp32: what the backward pass multiplies by; when nothing is
+  // recorded it is scratch) and the activation's result as bfloat16 only (two per 32-bit word of an integer tensor):
+  // nothing but the second product reads it.
   Tensor pre = NewOut(hs);
   Tensor act16 = Tensor::Create(DType::I32, Shape{rows, ff / 2});
   ActivationScope::Track(act16);
-  Check(om_linear_fwd_bf16_act(C(), xc.Bf16(), w1c.Bf16(), b1c.Data(), rows, inF, ff, op, pre.Data(), (uint16_t*)act16.RawData(), ff));
+  Check(om_linear_fwd_bf16_actd(C(), xc.Bf16(), w1c.Bf16(), b1c.Data(), rows, inF, ff, op, pre.Data(), (uint16_t*)act16.RawData(), ff));
   Tensor r = NewOut(os);
   Check(om_linear_fwd_bf16(C(), (const uint16_t*)act16.RawData(), w2c.Bf16(), b2c.Data(), rows, ff, outF, r.Data(), outF));
   if (!Recording({&x, &w1, &b1, &w2, &b2})) return r;

@@ -352,3 +352,35 @@ def test_linear_gradients_from_the_bf16_gradient_alone(ctx, oracle_built):
     ctx.sync()
     assert np.array_equal(ONLY16.numpy(), DX16.numpy())
     assert np.any(ONLY16.numpy() != 0)
+
+
+@pytest.mark.parametrize("op", [omb.UNARY["gelu_erf"], omb.UNARY["gelu_tanh"]])
+@pytest.mark.parametrize("rows,inf,outf", [(4096, 768, 3072), (300, 136, 264)])
+def test_derivative_left_behind_by_the_forward_epilogue(ctx, rows, inf, outf, op):
+    """om_linear_fwd_bf16_actd / om_linear_dgrad_bf16_mul against om_linear_fwd_bf16_act / om_linear_dgrad_bf16_act: the same
+    bfloat16 activation; the derivative equals op' applied to the separately computed result; the input gradient multiplied
+    by the stored derivative has the same bits as the one that evaluates the derivative in its own epilogue."""
+    r = np.random.default_rng(rows + inf + 3 * op)
+    x, w = r.standard_normal((rows, inf)).astype(np.float32), (r.standard_normal((outf, inf)) * 0.1).astype(np.float32)
+    bias = r.standard_normal(outf).astype(np.float32)
+    X16, W16, Bv = to_bf16(ctx, x), to_bf16(ctx, w), ctx.to_device(bias)
+    PRE, A16, D, A16D = ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16), ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16)
+    ctx.call("om_linear_fwd_bf16_act", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), i32(op), PRE.ptr, A16.ptr, i32(outf))
+    ctx.call("om_linear_fwd_bf16_actd", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), i32(op), D.ptr, A16D.ptr, i32(outf))
+    ONES, REF, REF16 = ctx.to_device(np.ones((rows, outf), np.float32)), ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16)
+    ctx.call("om_unary_bwd_b16", ctx.handle, i32(op), ONES.ptr, PRE.ptr, REF.ptr, REF16.ptr, i64(rows * outf))
+    ctx.sync()
+    assert np.array_equal(A16D.numpy(), A16.numpy())
+    assert np.array_equal(D.numpy(), REF.numpy())
+    # backward through the activation: the layer after it has `outf` inputs and `inf` outputs
+    g, w2 = r.standard_normal((rows, inf)).astype(np.float32), (r.standard_normal((inf, outf)) * 0.1).astype(np.float32)
+    G16, W216 = to_bf16(ctx, g), to_bf16(ctx, w2)
+    DX, DX16, M, M16 = ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16), ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16)
+    ctx.call("om_linear_dgrad_bf16_act", ctx.handle, G16.ptr, i32(inf), W216.ptr, i32(rows), i32(outf), i32(inf), i32(op), PRE.ptr, i32(outf), DX.ptr, DX16.ptr)
+    ctx.call("om_linear_dgrad_bf16_mul", ctx.handle, G16.ptr, i32(inf), W216.ptr, i32(rows), i32(outf), i32(inf), D.ptr, i32(outf), M.ptr, M16.ptr)
+    ONLY16 = ctx.empty((rows, outf), np.uint16)
+    ctx.call("om_linear_dgrad_bf16_mul", ctx.handle, G16.ptr, i32(inf), W216.ptr, i32(rows), i32(outf), i32(inf), D.ptr, i32(outf), None, ONLY16.ptr)
+    ctx.sync()
+    assert np.array_equal(M.numpy(), DX.numpy())
+    assert np.array_equal(M16.numpy(), DX16.numpy())
+    assert np.array_equal(ONLY16.numpy(), DX16.numpy())
