@@ -212,7 +212,8 @@ int32_t om_matmul_bf16(om_ctx* ctx, int32_t transA, int32_t transB, int32_t m, i
 int32_t om_linear_fwd_bf16(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows,
                            int32_t in_features, int32_t out_features, float* y, int32_t ldy);
 /* The forward product and the input gradient with the bfloat16 copy of their result (y16 / dx16, same pitch in elements as
- * the fp32 result, may be NULL) written by the product's epilogue: the packed q | k | v projections and the gradient of the
+ * the fp32 result, may be NULL) written by the product's epilogue (y may be NULL instead when only the bfloat16 result is
+ * wanted and k is not split, i.e. the shape passes om_linear_act_bf16_supported): the packed q | k | v projections and the gradient of the
  * attention output are read as bfloat16 by the attention kernels. */
 int32_t om_linear_fwd_bf16_b16(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows,
                                int32_t in_features, int32_t out_features, float* y, uint16_t* y16, int32_t ldy);
@@ -510,8 +511,9 @@ int32_t om_attention_fwd_bf16(om_ctx* ctx, const uint16_t* q16, const om_head_st
  * tile over the query tiles in tensor memory, and writes its part of dQ per query tile to a pooled workspace; a second
  * launch sums the parts of dQ over the key tiles in increasing order (a first one forms the row dots). Nothing of size
  * Lq x Lk is written to memory. q16 / k16 / v16 / g16 are the bfloat16 copies of q, k, v and of the output gradient g; g and
- * out (the forward's output) are read in fp32 for the row dots; lse is the forward's row log-sum-exp. Results are fp32
- * with optional bfloat16 copies (dq16 / dk16 / dv16, same strides). Built for head dimension 64, any Lq and Lk, at most
+ * out (the forward's output) are read in fp32 for the row dots; lse is the forward's row log-sum-exp. Each of dq, dk, dv
+ * is written as fp32, as bfloat16 (dq16 / dk16 / dv16, same strides) or both: pass NULL for the form that is not wanted
+ * (bfloat16 alone is all that a following product reads). Built for head dimension 64, any Lq and Lk, at most
  * 65535 (batch, head) pairs (om_attention_bwd_bf16_supported tells); strides of the bfloat16 operands multiples of 8. */
 int32_t om_attention_bwd_bf16_supported(om_ctx* ctx, int32_t b, int32_t h, int32_t lq, int32_t lk, int32_t d);
 int32_t om_attention_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, const om_head_strides* gs,

@@ -181,7 +181,7 @@ attention_dq_reduce_kernel(const float* __restrict__ parts, int nk, long long pa
     const long long row = i >> 4, c = (i & 15) * 4;        // 16 groups of four columns per row of 64
     const long long bh = row / lq, q = row % lq, bi = bh / heads, hi = bh % heads;
     const long long o = bi * dq_batch + hi * dq_head + q * dq_row + c;
-    *reinterpret_cast<float4*>(dq + o) = acc;
+    if (dq) *reinterpret_cast<float4*>(dq + o) = acc;
     if (dq16) *reinterpret_cast<uint2*>(dq16 + o) = make_uint2(ab_pack(acc.x, acc.y), ab_pack(acc.z, acc.w));
   }
 }
@@ -416,8 +416,9 @@ attention_bwd16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_fence_after();
       drain_dq(nq - 1);
       // dV_j (warps 0-3) and dK_j (warps 4-7): 32 key rows per warp, 64 columns as two blocks, fp32 and bfloat16.
-      const bool want = hh == 0 ? p.dv != nullptr : p.dk != nullptr;
+      const bool want32 = hh == 0 ? p.dv != nullptr : p.dk != nullptr;
       const bool want16 = hh == 0 ? p.dv16 != nullptr : p.dk16 != nullptr;
+      const bool want = want32 || want16;
       const CUtensorMap* m32 = hh == 0 ? &map_dv : &map_dk;
       const CUtensorMap* m16 = hh == 0 ? &map_dv16 : &map_dk16;
       if (want && j * AB_TILE + quad * 32 < p.lk) {
@@ -432,12 +433,12 @@ attention_bwd16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           uint8_t* f32_slot = cb == 0 ? slot : big;
           uint8_t* b16_slot = big + 4096 + cb * 2048;
           if (cb == 0) ab_slot_free(lane);
-          ab_stage_f32(f32_slot, lane, r);
+          if (want32) ab_stage_f32(f32_slot, lane, r);
           if (want16) ab_stage_bf16(b16_slot, lane, r);
           ab_fence_async();
           __syncwarp();
           if (lane == 0) {
-            ab_tma_store_4d(m32, f32_slot, cb * 32, j * AB_TILE + quad * 32, hi, bi);
+            if (want32) ab_tma_store_4d(m32, f32_slot, cb * 32, j * AB_TILE + quad * 32, hi, bi);
             if (want16) ab_tma_store_4d(m16, b16_slot, cb * 32, j * AB_TILE + quad * 32, hi, bi);
           }
         }
@@ -527,7 +528,10 @@ int32_t om_attention_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, 
   if (!result_ok(dq, dqs) || !result_ok(dk, dks) || !result_ok(dv, dvs) || (gs->row & 1) || (os->row & 1) || (reinterpret_cast<uintptr_t>(g) & 7) ||
       (reinterpret_cast<uintptr_t>(out) & 7) || (gs->head & 1) || (gs->batch & 1) || (os->head & 1) || (os->batch & 1))
     return fail(ctx, OM_ERR_UNSUPPORTED, "om_attention_bwd_bf16: results need 16-byte aligned bases and strides that are multiples of 4");
-  if ((dq16 && !dq) || (dk16 && !dk) || (dv16 && !dv)) return fail(ctx, OM_ERR_ARG, "om_attention_bwd_bf16: a bfloat16 copy needs its fp32 result");
+  // Each of dq, dk, dv may be asked for as fp32, as bfloat16, or both (bfloat16 alone is all that a following product reads).
+  if ((dq16 && !dq && !result_ok(reinterpret_cast<const float*>(dq16), dqs)) || (dk16 && !dk && !result_ok(reinterpret_cast<const float*>(dk16), dks)) ||
+      (dv16 && !dv && !result_ok(reinterpret_cast<const float*>(dv16), dvs)))
+    return fail(ctx, OM_ERR_UNSUPPORTED, "om_attention_bwd_bf16: results need 16-byte aligned bases and strides that are multiples of 4");
   auto copy_ok = [](const uint16_t* c, const om_head_strides* st) {
     return c == nullptr || (((reinterpret_cast<uintptr_t>(c) & 15) == 0) && (st->row & 7) == 0 && (st->head & 7) == 0 && (st->batch & 7) == 0);
   };
@@ -578,7 +582,7 @@ int32_t om_attention_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, 
     set = true;
   }
   launch_chained(ctx, attention_bwd16_kernel, dim3((unsigned)nk, (unsigned)bh), AB_THREADS, smem, mq, mk, mv, mg, mparts, mdk, mdk16, mdv, mdv16, p);
-  if (dq) {
+  if (dq || dq16) {
     const long long n4 = rows * (AB_D / 4);
     launch_chained(ctx, attention_dq_reduce_kernel, grid_for(ctx, n4, 256), 256, 0, (const float*)parts, nk, rows * AB_D, (int)h, (int)lq, n4, dq, dq16,
                    (long long)dqs->batch, (long long)dqs->head, (long long)dqs->row);

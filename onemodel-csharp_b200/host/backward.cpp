@@ -79,7 +79,6 @@ static void EmitSummed(Engine& e, BackwardRecord& r, const Tensor& g, bool negat
 static void LinearBwdCall(const Tensor& g, int col, int ldg, const Tensor& x, const Tensor& w, int rows, int inF, int outF, float* dx, float* dw,
                           float* db, int acc, const Tensor* dx_tensor = nullptr) {
   if (!dx && !dw && !db) return;
-  const float* gp = g.Data() + col;
   auto aligned16 = [](const float* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (Bf16Products() && rows > 0 && (dx || dw) && Bf16Operand(g, ldg) && col % 8 == 0 && Bf16Operand(x, inF) && Bf16Operand(w, inF) && (inF & 3) == 0 &&
       aligned16(dx) && aligned16(dw)) {
@@ -91,7 +90,8 @@ static void LinearBwdCall(const Tensor& g, int col, int ldg, const Tensor& x, co
     if (dx16) dx_tensor->Bf16Written();
     return;
   }
-  Check(om_linear_bwd_ld(C(), gp, ldg, x.Data(), w.Data() + (size_t)col * inF, rows, inF, outF, dx, dw, db, acc));
+  // (A gradient that exists as bfloat16 only cannot take this route: its Data() throws.)
+  Check(om_linear_bwd_ld(C(), g.Data() + col, ldg, x.Data(), w.Data() + (size_t)col * inF, rows, inF, outF, dx, dw, db, acc));
 }
 
 // The input gradient of a Linear layer whose input already holds another branch's gradient. Returns the tensor the product
@@ -516,7 +516,6 @@ static void AttentionPackedBackward(BackwardRecord& r, const Tensor& g) {
   const int b = qkv.GetShape()[0], l = qkv.GetShape()[1], width = qkv.GetShape()[2] / 3, d = width / heads;
   if (!r.NeedsInputGrad(0)) return;
   Tensor gc = g.Contiguous();
-  Tensor dqkv = Tensor::Create(DType::F32, qkv.GetShape());
   om_head_strides ps{(int64_t)l * 3 * width, (int64_t)d, (int64_t)3 * width}, gs{(int64_t)l * width, (int64_t)d, (int64_t)width};
   const Tensor& out = r.Saved(5);
   if (Bf16Products() && !out.IsEmpty() && !r.Saved(4).IsEmpty() && l > 128 && om_attention_bwd_bf16_supported(C(), b, heads, l, l, d) &&
@@ -525,14 +524,21 @@ static void AttentionPackedBackward(BackwardRecord& r, const Tensor& g) {
     // the gradient; it also writes the bfloat16 copy of dqkv, the next product's operand.
     const uint16_t* p16 = qkv.Bf16();
     const uint16_t* g16 = gc.Bf16();
+    // When the packed projection that made q | k | v reads its gradient as bfloat16 only and nothing else has contributed
+    // to that gradient, dqkv is written as bfloat16 alone (a third of the bytes).
+    BackwardRecord* producer = r.Inputs[0] ? r.Inputs[0]->GradFn.get() : nullptr;
+    const bool only16 = producer && producer->TakesBf16OnlyGrad && producer->PendingGrad.IsEmpty();
+    Tensor dqkv = only16 ? Tensor::CreateBf16Only(qkv.GetShape()) : Tensor::Create(DType::F32, qkv.GetShape());
     uint16_t* d16 = dqkv.Bf16ForWrite();
+    float* d32 = only16 ? nullptr : dqkv.Data();
     Check(om_attention_bwd_bf16(C(), g16, gc.Data(), &gs, p16, &ps, p16 + width, &ps, p16 + 2 * width, &ps, out.Data(), &gs,
-                                mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0], r.Saved(4).Data(), b, heads, l, l, d, (float)r.Floats[0], dqkv.Data(), d16,
-                                &ps, dqkv.Data() + width, d16 + width, &ps, dqkv.Data() + 2 * width, d16 + 2 * width, &ps));
+                                mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0], r.Saved(4).Data(), b, heads, l, l, d, (float)r.Floats[0], d32, d16, &ps,
+                                d32 ? d32 + width : nullptr, d16 + width, &ps, d32 ? d32 + 2 * width : nullptr, d16 + 2 * width, &ps));
     dqkv.Bf16Written();
     Engine::Emit(r, 0, dqkv, true);
     return;
   }
+  Tensor dqkv = Tensor::Create(DType::F32, qkv.GetShape());
   Check(om_attention_bwd_strided_out(C(), gc.Data(), &gs, qkv.Data(), &ps, qkv.Data() + width, &ps, qkv.Data() + 2 * width, &ps,
                                      out.IsEmpty() ? nullptr : out.Data(), &gs, mask.IsEmpty() ? nullptr : mask.Data(), r.Ints[0],
                                      r.Saved(4).IsEmpty() ? nullptr : r.Saved(4).Data(), b, heads, l, l, d, (float)r.Floats[0], dqkv.Data(), &ps,

@@ -228,7 +228,10 @@ Tensor MultiHeadAttention::Forward(const Tensor& input, const Tensor& mask) {
   // attention kernels' addressing: q, k, v stay [batch, length, width] and so does the result.
   Tensor a;
   if (Ops::Adjacent({Q->Weight, K->Weight, V->Weight}) && Ops::Adjacent({Q->Bias, K->Bias, V->Bias}))
-    a = Ops::AttentionPacked(Ops::LinearPacked(input, {Q->Weight, K->Weight, V->Weight}, {Q->Bias, K->Bias, V->Bias}), Heads, mask);
+    // (the attention kernels of the bfloat16 tier read q | k | v as bfloat16 only: the projection then writes nothing else)
+    a = Ops::AttentionPacked(Ops::LinearPacked(input, {Q->Weight, K->Weight, V->Weight}, {Q->Bias, K->Bias, V->Bias},
+                                               Ops::AttentionPackedReadsBf16Only(input, Q->Weight.GetShape()[0], Heads)),
+                             Heads, mask);
   else
     a = Ops::AttentionHeads(Q->Forward(input), K->Forward(input), V->Forward(input), Heads, mask);
   return O->Forward(a);

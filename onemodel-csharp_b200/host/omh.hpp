@@ -72,6 +72,10 @@ struct Buffer {
   // even: the operand the products read under OM_BF16_OPERANDS. Made on first use, refreshed when the storage changed.
   std::shared_ptr<Buffer> shadow;
   int64_t shadow_version = -1;
+  // The tensor exists as its bfloat16 copy only (an intermediate between two kernels that both work on bfloat16: the packed
+  // q | k | v projections in front of the attention kernels, their gradient behind them). The fp32 storage is a stub and
+  // any access to it throws, so a consumer that would need fp32 fails loudly instead of reading memory nobody wrote.
+  bool fp32_absent = false;
   Buffer(om_ctx* c, size_t n, bool zero);
   Buffer(om_ctx* c, void* external, size_t n) : ctx(c), ptr(external), bytes(n), owned(false) {}
   ~Buffer();
@@ -94,6 +98,10 @@ class Tensor {
   static Tensor FromHostInt64(const int64_t* data, const Shape& s);
   // A tensor over caller-owned device memory (not freed by the tensor).
   static Tensor Wrap(void* device_ptr, DType t, const Shape& s);
+  // A float32-typed tensor of this shape that holds its values as bfloat16 only (see Buffer::fp32_absent): Bf16() and
+  // Bf16ForWrite() work, Data() throws.
+  static Tensor CreateBf16Only(const Shape& s);
+  bool Fp32Absent() const { return buf_ && buf_->fp32_absent; }
 
   bool IsEmpty() const { return !buf_; }
   const Shape& GetShape() const { return shape_; }
@@ -201,6 +209,9 @@ struct BackwardRecord : std::enable_shared_from_this<BackwardRecord> {
   // The pending gradient's storage is also held by another record's pending gradient (a gradient that an Add hands to both
   // of its inputs is not copied): it is read freely but copied before anything is added into it.
   bool PendingShared = false;
+  // This record's backward reads its incoming gradient as bfloat16 only (a packed Linear on the bfloat16 route): the
+  // producer of that gradient may hand over a tensor made by Tensor::CreateBf16Only.
+  bool TakesBf16OnlyGrad = false;
   int VisitMark = 0;
   bool IsReleased = false;
 
@@ -333,7 +344,12 @@ struct Ops {
   static Tensor AttentionHeads(const Tensor& q, const Tensor& k, const Tensor& v, int heads, const Tensor& mask, float scale = 0.f);
   // Several Linear layers over the same input whose weights (and biases) are adjacent in memory, as one product:
   // returns [..., sum of out features]. Throws when the parameters are not adjacent.
-  static Tensor LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, const std::vector<Tensor>& biases);
+  // bf16_only_result: the caller consumes the result as bfloat16 only (the attention kernels of the bfloat16 tier); under
+  // bfloat16 products the result is then made by Tensor::CreateBf16Only and no fp32 copy is written.
+  static Tensor LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, const std::vector<Tensor>& biases, bool bf16_only_result = false);
+  // True when AttentionPacked on the packed projections of `input` ([B, L, .]) with this width and head count will take the
+  // bfloat16 kernels, forward and backward, and so never read the projections as fp32.
+  static bool AttentionPackedReadsBf16Only(const Tensor& input, int width, int heads);
   // Linear(Gelu(Linear(x, w1, b1)), w2, b2), the feed-forward block of an encoder layer. Under bfloat16 products (and
   // shapes the fused kernels take) the activation and its derivative are applied in the epilogues of the first forward
   // product and of the second layer's input-gradient product; the values are those of the three separate ops, which is

@@ -518,7 +518,7 @@ bool Ops::Adjacent(const std::vector<Tensor>& parts) {
   return !parts.empty();
 }
 
-Tensor Ops::LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, const std::vector<Tensor>& biases) {
+Tensor Ops::LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, const std::vector<Tensor>& biases, bool bf16_only_result) {
   if (weights.empty() || weights.size() > 3 || (!biases.empty() && biases.size() != weights.size()))
     throw TensorShapeException("LinearPacked needs one to three weight matrices and as many biases (or none).");
   if (!Adjacent(weights) || (!biases.empty() && !Adjacent(biases)))
@@ -535,8 +535,16 @@ Tensor Ops::LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, co
   Tensor xc = x.Contiguous();
   Shape os = x.GetShape();
   os.d[os.rank - 1] = outF;
-  Tensor r = NewOut(os);
-  if (Bf16Products() && rows > 0 && Bf16Operand(xc, inF) && Bf16Operand(weights[0], inF) && (outF & 3) == 0) {
+  const bool route16 = Bf16Products() && rows > 0 && Bf16Operand(xc, inF) && Bf16Operand(weights[0], inF) && (outF & 3) == 0;
+  bool parts8 = (inF % 8) == 0;
+  for (auto& w : weights) parts8 = parts8 && (w.GetShape()[0] % 8) == 0;
+  // Without an fp32 result the product may not split k (the slices are summed in fp32): the same rule the kernel applies.
+  const bool only16 = bf16_only_result && route16 && parts8 && om_linear_act_bf16_supported(C(), rows, inF, outF, OM_GELU_ERF, 0) == 1;
+  Tensor r = only16 ? Tensor::CreateBf16Only(os) : NewOut(os);
+  if (only16) {
+    ActivationScope::Track(r);
+    Check(om_linear_fwd_bf16_b16(C(), xc.Bf16(), weights[0].Bf16(), biases.empty() ? nullptr : biases[0].Data(), rows, inF, outF, nullptr, r.Bf16ForWrite(), outF));
+  } else if (route16) {
     // The packed q | k | v projections feed the attention kernels, which read them as bfloat16 under this tier: the
     // product's epilogue writes that copy along.
     uint16_t* y16 = outF % 8 == 0 ? r.Bf16ForWrite() : nullptr;
@@ -554,7 +562,16 @@ Tensor Ops::LinearPacked(const Tensor& x, const std::vector<Tensor>& weights, co
   rec->Save(0, xc.Detach());
   for (size_t i = 0; i < weights.size(); i++) rec->Save(1 + (int)i, weights[i].Detach());
   rec->Ints = {rows, inF, outF, (int64_t)weights.size(), biases.empty() ? 0 : 1};
+  // On the bfloat16 route every gradient this record computes reads the bfloat16 copy of the incoming gradient.
+  rec->TakesBf16OnlyGrad = route16 && parts8;
   return rec->Attach(r);
+}
+
+bool Ops::AttentionPackedReadsBf16Only(const Tensor& input, int width, int heads) {
+  if (!Bf16Products() || input.Rank() != 3 || heads < 1 || width % heads != 0 || width % 8 != 0) return false;
+  const int b = input.GetShape()[0], l = input.GetShape()[1], d = width / heads;
+  const float scale = 1.0f / sqrtf((float)d);
+  return l > 128 && om_attention_fwd_bf16_supported(C(), b, heads, l, l, d, scale) == 1 && om_attention_bwd_bf16_supported(C(), b, heads, l, l, d) == 1;
 }
 
 Tensor Ops::AttentionPacked(const Tensor& qkv, int heads, const Tensor& mask, float scale) {

@@ -79,6 +79,21 @@ Tensor Tensor::Create(DType t, const Shape& s, bool zero) {
   return r;
 }
 
+Tensor Tensor::CreateBf16Only(const Shape& s) {
+  Tensor r;
+  for (int i = 0; i < s.rank; i++)
+    if (s.d[i] < 0) throw TensorShapeException("Negative extent in " + s.ToString());
+  // A stub of fp32 storage (never read or written) whose bfloat16 copy is the tensor.
+  r.buf_ = std::make_shared<Buffer>(Device::Current(), (size_t)16, false);
+  r.buf_->shadow = std::make_shared<Buffer>(Device::Current(), (((size_t)s.Length() * 2) + 15) & ~(size_t)15, false);
+  r.buf_->fp32_absent = true;
+  r.buf_->shadow_version = r.buf_->version;
+  r.shape_ = s;
+  r.strides_ = ContiguousStrides(s);
+  r.dtype_ = DType::F32;
+  return r;
+}
+
 Tensor Tensor::Wrap(void* device_ptr, DType t, const Shape& s) {
   Tensor r;
   r.buf_ = std::make_shared<Buffer>(Device::Current(), device_ptr, (size_t)s.Length() * SizeOf(t));
@@ -115,6 +130,7 @@ bool Tensor::IsContiguous() const {
 
 void* Tensor::RawData() const {
   if (IsEmpty()) return nullptr;
+  if (buf_->fp32_absent) throw InvalidOperationException("This tensor exists as bfloat16 only; a consumer asked for its float32 values.");
   return (char*)buf_->ptr + offset_ * (int64_t)SizeOf(dtype_);
 }
 float* Tensor::Data() const { return (float*)RawData(); }
@@ -290,6 +306,7 @@ uint16_t* Tensor::Bf16ForWrite() const {
 const uint16_t* Tensor::Bf16() const {
   uint16_t* p = Bf16ForWrite();
   Buffer& b = *buf_;
+  if (b.fp32_absent) return p;     // the copy is the tensor
   if (b.shadow_version != b.version) {
     Check(om_cast_bf16(b.ctx, (const float*)b.ptr, (uint16_t*)b.shadow->ptr, (int64_t)(b.bytes / 4)));
     b.shadow_version = b.version;

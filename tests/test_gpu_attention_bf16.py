@@ -71,6 +71,14 @@ def test_fused_attention_backward_with_bf16_operands(ctx, oracle_built, b, h, lq
         ctx.sync()
         for a, again in zip(got, (DQ, DK, DV)):
             assert np.array_equal(a, again.numpy())
+        # bfloat16 results alone (what a following product reads): the same bits as the copies written beside fp32 results
+        O16 = [ctx.empty(t.shape, np.uint16) for t in (q, k, v)]
+        ctx.call("om_attention_bwd_bf16", ctx.handle, G16.ptr, G.ptr, C.byref(sq), Q16.ptr, C.byref(sq), K16.ptr, C.byref(sk), V16.ptr, C.byref(sk),
+                 O.ptr, C.byref(sq), M.ptr if M else None, i64(0), LSE.ptr, i32(b), i32(h), i32(lq), i32(lk), i32(d), f32(scale), None, O16[0].ptr,
+                 C.byref(sq), None, O16[1].ptr, C.byref(sk), None, O16[2].ptr, C.byref(sk))
+        ctx.sync()
+        for only, both in zip(O16, (DQ16, DK16, DV16)):
+            assert np.array_equal(only.numpy(), both.numpy())
     finally:
         ctx.set_flags(0)
 

@@ -384,3 +384,17 @@ def test_derivative_left_behind_by_the_forward_epilogue(ctx, rows, inf, outf, op
     assert np.array_equal(M.numpy(), DX.numpy())
     assert np.array_equal(M16.numpy(), DX16.numpy())
     assert np.array_equal(ONLY16.numpy(), DX16.numpy())
+
+
+def test_forward_product_with_the_bf16_result_alone(ctx):
+    """om_linear_fwd_bf16_b16 without the fp32 result (y NULL): the bfloat16 result equals the copy written beside an fp32 one."""
+    r = np.random.default_rng(23)
+    rows, inf, outf = 4096, 768, 2304
+    x, w = r.standard_normal((rows, inf)).astype(np.float32), (r.standard_normal((outf, inf)) * 0.05).astype(np.float32)
+    bias = r.standard_normal(outf).astype(np.float32)
+    X16, W16, Bv = to_bf16(ctx, x), to_bf16(ctx, w), ctx.to_device(bias)
+    Y, Y16, ONLY = ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16), ctx.empty((rows, outf), np.uint16)
+    ctx.call("om_linear_fwd_bf16_b16", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), Y.ptr, Y16.ptr, i32(outf))
+    ctx.call("om_linear_fwd_bf16_b16", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), None, ONLY.ptr, i32(outf))
+    ctx.sync()
+    assert np.array_equal(ONLY.numpy(), Y16.numpy()) and np.any(ONLY.numpy() != 0)
