@@ -265,16 +265,19 @@ int32_t om_linear_dgrad_bf16_act(om_ctx* ctx, const uint16_t* g16, int32_t ldg, 
                                  int32_t in_features, int32_t out_features, int32_t op, const float* pre, int32_t ldpre,
                                  float* dx, uint16_t* dx16);
 /* The same pair with the activation's derivative left behind by the forward pass, so that the backward epilogue only
- * multiplies: om_linear_fwd_bf16_actd writes deriv = op'(x W^T + bias) (fp32, pitch ldd) and a16 = bfloat16(op(x W^T + bias));
- * om_linear_dgrad_bf16_mul writes dx = factor * (g W) with factor = that derivative ([rows, in_features], pitch ldf), as
- * fp32 and / or bfloat16 (either of dx and dx16 may be NULL). The values are those of om_linear_fwd_bf16_act /
- * om_linear_dgrad_bf16_act, bit for bit; the derivative is evaluated once, where the activation is. Supported shapes as
- * for those (om_linear_act_bf16_supported). */
+ * multiplies: om_linear_fwd_bf16_actd writes deriv = op'(x W^T + bias) as IEEE half (binary16, round to nearest even: the
+ * derivative of GELU lies in [-0.13, 1.13], where half carries 11 significant bits, eight times finer than the bfloat16
+ * rounding of the gradient it multiplies) and a16 = bfloat16(op(x W^T + bias)), both with pitch ldd (a multiple of 8);
+ * om_linear_dgrad_bf16_mul writes dx = factor * (g W) with factor = that derivative ([rows, in_features] half, pitch ldf, a
+ * multiple of 8), as fp32 and / or bfloat16 (either of dx and dx16 may be NULL). a16 has the bits om_linear_fwd_bf16_act
+ * writes; dx is om_linear_dgrad_bf16_act's up to the half rounding of the factor. The derivative is evaluated once, where the
+ * activation is, and costs 2 bytes per element to keep instead of the 4 of the saved input. Supported shapes as for those
+ * (om_linear_act_bf16_supported). */
 int32_t om_linear_fwd_bf16_actd(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows,
-                                int32_t in_features, int32_t out_features, int32_t op, float* deriv, uint16_t* a16,
+                                int32_t in_features, int32_t out_features, int32_t op, uint16_t* deriv, uint16_t* a16,
                                 int32_t ldd);
 int32_t om_linear_dgrad_bf16_mul(om_ctx* ctx, const uint16_t* g16, int32_t ldg, const uint16_t* W, int32_t rows,
-                                 int32_t in_features, int32_t out_features, const float* factor, int32_t ldf, float* dx,
+                                 int32_t in_features, int32_t out_features, const uint16_t* factor, int32_t ldf, float* dx,
                                  uint16_t* dx16);
 /* dx = residual + g W, out of place: the input gradient of a Linear layer whose input already holds a gradient from
  * another branch (a residual connection). The sum is formed in the product's epilogue from a plain read of `residual`
@@ -287,8 +290,9 @@ int32_t om_linear_dgrad_bf16_add(om_ctx* ctx, const uint16_t* g16, int32_t ldg, 
                                  int32_t in_features, int32_t out_features, const float* residual, int32_t ldres, float* dx,
                                  uint16_t* dx16);
 /* out[c] (+)= sum over rows of the bfloat16 matrix g16[rows, cols] with pitch ld (a multiple of 8, 16-byte aligned base):
- * om_colsum on the bfloat16 copy of a gradient, with the same partition of the rows (chunks of 512, 32 lanes) and double
- * accumulators, so the result is the same from run to run. */
+ * om_colsum on the bfloat16 copy of a gradient, with the same partition of the rows (chunks of 512 rows, 32 lanes of 16 rows).
+ * A lane adds its 16 rows (lane, lane + 32, ...) in fp32 in increasing order; the 32 lane sums of a chunk, then the chunks,
+ * are added in double in increasing order. The order is fixed, so the result is the same from run to run. */
 int32_t om_colsum_bf16(om_ctx* ctx, const uint16_t* g16, int32_t rows, int32_t cols, int32_t ld, float* out,
                        int32_t accumulate);
 

@@ -280,8 +280,17 @@ __device__ __forceinline__ void colsum_finish(const double* __restrict__ partial
   if (tid < COLS) {
     const int c = blockIdx.x * COLS + tid;
     if (c < cols) {
+      // Sixteen loads are on their way before the first add; the adds stay in increasing chunk order.
       double t = 0.0;
-      for (unsigned ch = 0; ch < gridDim.y; ch++) t += __ldcg(partial + (int64_t)ch * cols + c);
+      unsigned ch = 0;
+      for (; ch + 16 <= gridDim.y; ch += 16) {
+        double v[16];
+#pragma unroll
+        for (int u = 0; u < 16; u++) v[u] = __ldcg(partial + (int64_t)(ch + u) * cols + c);
+#pragma unroll
+        for (int u = 0; u < 16; u++) t += v[u];
+      }
+      for (; ch < gridDim.y; ch++) t += __ldcg(partial + (int64_t)ch * cols + c);
       const float r = (float)t;
       out[c] = accumulate ? out[c] + r : r;
     }
@@ -369,30 +378,32 @@ colsum_stage1_vec4_kernel(const float* __restrict__ g, int32_t rows, int32_t col
 }
 
 // The column sums of a bfloat16 matrix (the copy of an output gradient that the products read): the same partition as above
-// (chunks of 512 rows, 32 row lanes, double accumulators, lanes and chunks combined in increasing order), a thread owning
-// eight adjacent columns (one 16-byte load per row) with its 16 rows in flight at once; a CTA covers 64 columns of a chunk.
-__device__ __forceinline__ void add_bf16x8(double (&a)[8], const uint4& v) {
+// (chunks of 512 rows, 32 row lanes), a thread owning eight adjacent columns (one 16-byte load per row) with its 16 rows in
+// flight at once; a CTA covers 64 columns of a chunk. A thread adds its 16 rows in fp32, in increasing row order (the
+// conversion of every element to double made the kernel arithmetic-bound at 3 TB/s); the 32 lane sums of a chunk and then
+// the chunks are combined in double, in increasing order. The order is fixed, so the same input gives the same bits.
+__device__ __forceinline__ void add_bf16x8(float (&a)[8], const uint4& v) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int q = 0; q < 4; q++) {
-    a[2 * q] += (double)__uint_as_float(w[q] << 16);
-    a[2 * q + 1] += (double)__uint_as_float(w[q] & 0xFFFF0000u);
+    a[2 * q] += __uint_as_float(w[q] << 16);
+    a[2 * q + 1] += __uint_as_float(w[q] & 0xFFFF0000u);
   }
 }
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 colsum16_stage1_kernel(const uint16_t* __restrict__ g, int32_t rows, int32_t cols, int64_t ld, double* __restrict__ partial,
                        unsigned* __restrict__ arrival, float* __restrict__ out, int accumulate) {
   pdl_enter();
-  __shared__ double sm[kColsumLanes][65];
+  __shared__ float sm[kColsumLanes][65];
   __shared__ int is_last;
   constexpr int PER_LANE = kColsumRowsPerChunk / kColsumLanes;
   const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
   const int col = blockIdx.x * 64 + tx * 8;
   const int r0 = blockIdx.y * kColsumRowsPerChunk;
   const int r1 = min(rows, r0 + kColsumRowsPerChunk);
-  double a[8];
+  float a[8];
 #pragma unroll
-  for (int q = 0; q < 8; q++) a[q] = 0.0;
+  for (int q = 0; q < 8; q++) a[q] = 0.f;
   if (col + 7 < cols) {
     uint4 v[PER_LANE];
 #pragma unroll
@@ -405,7 +416,7 @@ colsum16_stage1_kernel(const uint16_t* __restrict__ g, int32_t rows, int32_t col
       if (r0 + ty + kColsumLanes * u < r1) add_bf16x8(a, v[u]);
   } else if (col < cols) {
     for (int r = r0 + ty; r < r1; r += kColsumLanes)
-      for (int q = 0; q < 8 && col + q < cols; q++) a[q] += (double)__uint_as_float((uint32_t)g[(int64_t)r * ld + col + q] << 16);
+      for (int q = 0; q < 8 && col + q < cols; q++) a[q] += __uint_as_float((uint32_t)g[(int64_t)r * ld + col + q] << 16);
   }
 #pragma unroll
   for (int q = 0; q < 8; q++) sm[ty][tx * 8 + q] = a[q];
@@ -415,7 +426,7 @@ colsum16_stage1_kernel(const uint16_t* __restrict__ g, int32_t rows, int32_t col
     if (c < cols) {
       double t = 0.0;
 #pragma unroll
-      for (int l = 0; l < kColsumLanes; l++) t += sm[l][threadIdx.x];
+      for (int l = 0; l < kColsumLanes; l++) t += (double)sm[l][threadIdx.x];
       partial[(int64_t)blockIdx.y * cols + c] = t;
       __threadfence();
     }

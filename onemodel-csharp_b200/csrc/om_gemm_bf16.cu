@@ -187,27 +187,29 @@ int32_t om_linear_dgrad_bf16_act(om_ctx* ctx, const uint16_t* g16, int32_t ldg, 
 // ---- the same pair with the activation's derivative left behind by the forward pass ----
 
 int32_t om_linear_fwd_bf16_actd(om_ctx* ctx, const uint16_t* x, const uint16_t* W, const float* bias, int32_t rows, int32_t in_features,
-                                int32_t out_features, int32_t op, float* deriv, uint16_t* a16, int32_t ldd) {
+                                int32_t out_features, int32_t op, uint16_t* deriv, uint16_t* a16, int32_t ldd) {
   OM_CHECK_CTX(ctx);
   if (rows < 1 || in_features < 1 || out_features < 1 || ldd < out_features)
     return fail(ctx, OM_ERR_SHAPE, "om_linear_fwd_bf16_actd: rows %d in %d out %d ldd %d", rows, in_features, out_features, ldd);
   if (!deriv || !a16) return fail(ctx, OM_ERR_ARG, "om_linear_fwd_bf16_actd: deriv and a16 are both written");
-  OM_TRY(check_args(ctx, "om_linear_fwd_bf16_actd", rows, out_features, in_features, x, in_features, W, in_features, deriv, ldd));
+  OM_TRY(check_args(ctx, "om_linear_fwd_bf16_actd", rows, out_features, in_features, x, in_features, W, in_features, reinterpret_cast<const float*>(deriv), ldd));
   ProfileScope prof(ctx, "om_linear_fwd", 2.0 * rows * in_features * out_features,
-                    2.0 * ((double)rows * in_features + (double)in_features * out_features) + 6.0 * (double)rows * out_features);
-  return gemm_ws_act(ctx, 1, 0, 1, rows, out_features, in_features, x, in_features, W, in_features, deriv, ldd, 0, bias, a16, 5, op, nullptr, 0);
+                    2.0 * ((double)rows * in_features + (double)in_features * out_features) + 4.0 * (double)rows * out_features);
+  return gemm_ws_act(ctx, 1, 0, 1, rows, out_features, in_features, x, in_features, W, in_features, reinterpret_cast<float*>(deriv), ldd, 0, bias, a16,
+                     5, op, nullptr, 0);
 }
 
 int32_t om_linear_dgrad_bf16_mul(om_ctx* ctx, const uint16_t* g16, int32_t ldg, const uint16_t* W, int32_t rows, int32_t in_features,
-                                 int32_t out_features, const float* factor, int32_t ldf, float* dx, uint16_t* dx16) {
+                                 int32_t out_features, const uint16_t* factor, int32_t ldf, float* dx, uint16_t* dx16) {
   OM_CHECK_CTX(ctx);
   if (rows < 1 || in_features < 1 || out_features < 1 || ldg < out_features || ldf < in_features)
     return fail(ctx, OM_ERR_SHAPE, "om_linear_dgrad_bf16_mul: rows %d in %d out %d ldg %d ldf %d", rows, in_features, out_features, ldg, ldf);
   if ((!dx && !dx16) || !factor) return fail(ctx, OM_ERR_ARG, "om_linear_dgrad_bf16_mul: a result (dx or dx16) and the factor are needed");
   OM_TRY(check_args(ctx, "om_linear_dgrad_bf16_mul", rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features));
   ProfileScope prof(ctx, "om_linear_bwd.dgrad", 2.0 * rows * in_features * out_features,
-                    2.0 * ((double)rows * out_features + (double)in_features * out_features) + (4.0 + (dx ? 4.0 : 0.0) + (dx16 ? 2.0 : 0.0)) * (double)rows * in_features);
-  return gemm_ws_act(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, 0, nullptr, dx16, 4, 0, factor, ldf);
+                    2.0 * ((double)rows * out_features + (double)in_features * out_features) + (2.0 + (dx ? 4.0 : 0.0) + (dx16 ? 2.0 : 0.0)) * (double)rows * in_features);
+  return gemm_ws_act(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, 0, nullptr, dx16, 4, 0,
+                     reinterpret_cast<const float*>(factor), ldf);
 }
 
 // ---- an input gradient that joins another branch's gradient: dx = residual + g W, out of place ----

@@ -17,6 +17,7 @@
 // (om_tc.cuh): on a timeout the kernel raises OM_ERR_TIMEOUT in the context's status word, all roles leave their loops,
 // tensor memory is released and the kernel returns.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "om_act.cuh"
 #include "om_tc.cuh"
@@ -293,14 +294,17 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // the quadrant work while they are on their way.
       // With eight epilogue warps (two per lane quadrant) the next block's values are asked for a block ahead, into a second
       // set of registers; with sixteen the other warps of the quadrant cover the wait.
+      // The factor of ACT 4 is stored as IEEE half (32 values in four 16-byte loads; n is then a multiple of eight).
       constexpr bool AHEAD = (ACT >= 2 && ACT <= 4) && EW == 8;
-      float4 aux[8], nxt[AHEAD ? 8 : 1];
-      auto load_aux = [&](float4 (&dst)[8], int cb) {
+      constexpr int AUXN = ACT == 4 ? 4 : 8, AUX_PER = 32 / AUXN;
+      float4 aux[AUXN], nxt[AHEAD ? AUXN : 1];
+      auto load_aux = [&](float4 (&dst)[AUXN], int cb) {
         const int c0 = n0 + cb * 32, row = row_base + lane;
         const bool in = row < p.m && c0 < p.n;
-        const float4* src = reinterpret_cast<const float4*>(p.aux + (int64_t)(in ? row : 0) * p.ld_aux + (in ? c0 : 0));
+        const int64_t at = (int64_t)(in ? row : 0) * p.ld_aux + (in ? c0 : 0);
+        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p.aux) + at * (ACT == 4 ? 2 : 4));
 #pragma unroll
-        for (int c4 = 0; c4 < 8; c4++) dst[c4] = (in && c0 + 4 * c4 < p.n) ? __ldg(src + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c4 = 0; c4 < AUXN; c4++) dst[c4] = (in && c0 + AUX_PER * c4 < p.n) ? __ldg(src + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
       };
       if (AHEAD) load_aux(aux, part * CB_PER);
       ok = mbar_wait(&acc_full[a], use & 1, abort_flag, p.status, 44);
@@ -313,7 +317,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const bool live = row_base < p.m && col0 < p.n;
         uint32_t r[32];
         if (AHEAD) {
-          if (cb + 1 < (part + 1) * CB_PER) load_aux(reinterpret_cast<float4(&)[8]>(nxt), cb + 1);
+          if (cb + 1 < (part + 1) * CB_PER) load_aux(reinterpret_cast<float4(&)[AUXN]>(nxt), cb + 1);
         } else if (ACT >= 2 && ACT <= 4) {
           load_aux(aux, cb);
         }
@@ -329,7 +333,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (!live) continue;
         if (p.bias) add_bias32(r, p.bias, col0, p.n);
-        if (ACT == 2) {
+        if constexpr (ACT == 2) {
 #pragma unroll
           for (int c4 = 0; c4 < 8; c4++) {
             r[4 * c4 + 0] = __float_as_uint(unary_grad<OP>(__uint_as_float(r[4 * c4 + 0]), aux[c4].x));
@@ -338,30 +342,59 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             r[4 * c4 + 3] = __float_as_uint(unary_grad<OP>(__uint_as_float(r[4 * c4 + 3]), aux[c4].w));
           }
         }
-        if (ACT == 4) {
+        if constexpr (ACT == 4) {
 #pragma unroll
-          for (int c4 = 0; c4 < 8; c4++) {
-            r[4 * c4 + 0] = __float_as_uint(__uint_as_float(r[4 * c4 + 0]) * aux[c4].x);
-            r[4 * c4 + 1] = __float_as_uint(__uint_as_float(r[4 * c4 + 1]) * aux[c4].y);
-            r[4 * c4 + 2] = __float_as_uint(__uint_as_float(r[4 * c4 + 2]) * aux[c4].z);
-            r[4 * c4 + 3] = __float_as_uint(__uint_as_float(r[4 * c4 + 3]) * aux[c4].w);
+          for (int c4 = 0; c4 < 4; c4++) {
+            const __half2* h = reinterpret_cast<const __half2*>(&aux[c4]);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              const float2 f = __half22float2(h[q]);
+              r[8 * c4 + 2 * q] = __float_as_uint(__uint_as_float(r[8 * c4 + 2 * q]) * f.x);
+              r[8 * c4 + 2 * q + 1] = __float_as_uint(__uint_as_float(r[8 * c4 + 2 * q + 1]) * f.y);
+            }
           }
         }
-        uint32_t act16[ACT == 5 ? 16 : 1];
-        if (ACT == 5) {
-          // The activation (kept as packed bfloat16 until the fp32 block has left the slot) and its derivative (the fp32 block).
-#pragma unroll
-          for (int c = 0; c < 16; c++) {
-            float a0, a1, d0, d1;
-            unary_both<OP>(__uint_as_float(r[2 * c]), &a0, &d0);
-            unary_both<OP>(__uint_as_float(r[2 * c + 1]), &a1, &d1);
-            __nv_bfloat162 h = __floats2bfloat162_rn(a0, a1);
-            act16[c] = *reinterpret_cast<uint32_t*>(&h);
-            r[2 * c] = __float_as_uint(d0);
-            r[2 * c + 1] = __float_as_uint(d1);
+        if constexpr (ACT == 5) {
+          // The activation as packed bfloat16 (map_c16) and its derivative as packed IEEE half (map_c, a second 16-bit map of
+          // the same shape): two 2 KB blocks in the 64-byte swizzle, side by side in the slot, stored together.
+          if (stored >= W_RING) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(W_RING - 1) : "memory");
+            __syncwarp();
           }
+          uint8_t* blk5 = ring + (size_t)(stored % W_RING) * W_SLOT;
+          const uint32_t row16 = smem_u32(blk5) + (uint32_t)lane * 64u;
+#pragma unroll
+          for (int c8 = 0; c8 < 4; c8++) {
+            uint32_t wa[4], wd[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              float a0, a1, d0, d1;
+              unary_both<OP>(__uint_as_float(r[8 * c8 + 2 * q]), &a0, &d0);
+              unary_both<OP>(__uint_as_float(r[8 * c8 + 2 * q + 1]), &a1, &d1);
+              __nv_bfloat162 ha = __floats2bfloat162_rn(a0, a1);
+              __half2 hd = __floats2half2_rn(d0, d1);
+              wa[q] = *reinterpret_cast<uint32_t*>(&ha);
+              wd[q] = *reinterpret_cast<uint32_t*>(&hd);
+            }
+            const uint32_t at = row16 + (uint32_t)((c8 ^ ((lane >> 1) & 3)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(wa[0]), "r"(wa[1]), "r"(wa[2]), "r"(wa[3]) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at + 2048u), "r"(wd[0]), "r"(wd[1]), "r"(wd[2]), "r"(wd[3]) : "memory");
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_c16), "r"(col0),
+                         "r"(row_base), "r"(smem_u32(blk5))
+                         : "memory");
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_c), "r"(col0),
+                         "r"(row_base), "r"(smem_u32(blk5 + 2048))
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          stored++;
+          continue;
         }
-        if (ACT == 3) {
+        if constexpr (ACT == 3) {
 #pragma unroll
           for (int c4 = 0; c4 < 8; c4++) {
             r[4 * c4 + 0] = __float_as_uint(aux[c4].x + __uint_as_float(r[4 * c4 + 0]));
@@ -372,7 +405,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (AHEAD) {
 #pragma unroll
-          for (int c4 = 0; c4 < 8; c4++) aux[c4] = nxt[AHEAD ? c4 : 0];
+          for (int c4 = 0; c4 < AUXN; c4++) aux[c4] = nxt[AHEAD ? c4 : 0];
         }
         if (stored >= W_RING) {
           // The block about to be overwritten was handed to the TMA unit W_RING stores ago.
@@ -398,7 +431,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                          : "memory");
           }
         };
-        const bool both_at_once = W_SLOT >= 6144 && ACT != 1 && ACT != 5;
+        const bool both_at_once = W_SLOT >= 6144 && ACT != 1;
         if (p.store32) {
           const uint32_t row_addr = smem_u32(blk) + (uint32_t)lane * 128u;
 #pragma unroll
@@ -435,16 +468,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             __syncwarp();
           }
-          if (ACT == 5) {
-            const uint32_t row16 = smem_u32(blk) + (uint32_t)lane * 64u;
-#pragma unroll
-            for (int c8 = 0; c8 < 4; c8++)
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row16 + (uint32_t)((c8 ^ ((lane >> 1) & 3)) << 4)), "r"(act16[4 * c8]),
-                           "r"(act16[4 * c8 + 1]), "r"(act16[4 * c8 + 2]), "r"(act16[4 * c8 + 3])
-                           : "memory");
-          } else {
-            stage_bf16(blk);
-          }
+          stage_bf16(blk);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0) {
@@ -593,7 +617,8 @@ bool gemm_ws_c16_ok(const uint16_t* C16, long long ldc, int acc) {
 int32_t cast_bf16_rows(om_ctx* ctx, const float* src, uint16_t* dst, int rows, int cols, long long ld);
 
 // act 0: none. act 1 with op: C16 receives op(C) instead of C. act 2 with op: C and C16 receive op'(aux) * C. act 3: aux + C.
-// act 4: aux * C. act 5 with op: C receives op'(C), C16 op(C).
+// act 4: aux * C, aux holding IEEE half values (pitch ld_aux in those). act 5 with op: C16 receives op(C) and the memory at C
+// receives op'(C) as IEEE half with C16's pitch (the pointer is typed float* for the other variants' sake).
 // gemm_ws_act_ok tells whether a product can take the activation (no split of k, the layouts above).
 static int ws_splits(int tiles, int k_blocks) {
   // Fixed split of k by shape alone: enough slices for one round of pairs, each at least 8 k-blocks deep.
@@ -616,6 +641,8 @@ bool gemm_ws_act_ok(int act, int op, int m, int n, int k, const float* C, long l
   if (fwd && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
   if (with_aux && (C16 != nullptr) && !gemm_ws_c16_ok(C16, ldc, 0)) return false;
   if (with_aux && (!aux || (ld_aux & 3) || (reinterpret_cast<uintptr_t>(aux) & 15))) return false;
+  if (act == 4 && ((ld_aux & 7) || (n & 7))) return false;
+  if (act == 5 && (!C || (reinterpret_cast<uintptr_t>(C) & 15))) return false;
   (void)C;
   return true;
 }
@@ -676,6 +703,7 @@ int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, 
   if (p.c16) ok = ok && ws_store_map16(&map_c16, C16, n, m, ldc);
   else map_c16 = map_c;   // never used, but the parameter must hold a valid map
   if (!store32) map_c = map_c16;
+  if (act == 5) ok = ok && ws_store_map16(&map_c, reinterpret_cast<uint16_t*>(C), n, m, ldc);
   if (!ok) {
     if (workspace) pool_free(ctx, workspace);
     return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed for C (persistent product, m %d n %d ldc %lld)", m, n, ldc);

@@ -308,7 +308,7 @@ static void FeedForwardBackward(BackwardRecord& r, const Tensor& g) {
   // gradients of the first layer are products that read it as an operand (the bias gradient is g^T 1).
   Tensor dpre16 = Tensor::Create(DType::I32, Shape{rows, ff / 2});
   const uint16_t* d16 = (const uint16_t*)dpre16.RawData();
-  Check(om_linear_dgrad_bf16_mul(C(), g16, outF, w2.Bf16(), rows, ff, outF, pre.Data(), ff, nullptr, (uint16_t*)dpre16.RawData()));
+  Check(om_linear_dgrad_bf16_mul(C(), g16, outF, w2.Bf16(), rows, ff, outF, (const uint16_t*)pre.RawData(), ff, nullptr, (uint16_t*)dpre16.RawData()));
   // First layer.
   Tensor dx;
   bool dx_into_pending = false;

@@ -397,16 +397,16 @@ Tensor Ops::FeedForward(const Tensor& x, const Tensor& w1, const Tensor& b1, con
   }
   if (!fused) return Linear(Gelu(Linear(x, w1, b1), tanhForm), w2, b2);
   Tensor b1c = b1.Contiguous(), b2c = b2.Contiguous();
-  Shape hs = x.GetShape(), os = x.GetShape();
-  hs.d[hs.rank - 1] = ff;
+  Shape os = x.GetShape();
   os.d[os.rank - 1] = outF;
-  // The activation's derivative at the first layer's result (fp32: what the backward pass multiplies by; when nothing is
-  // recorded it is scratch) and the activation's result as bfloat16 only (two per 32-bit word of an integer tensor):
-  // nothing but the second product reads it.
-  Tensor pre = NewOut(hs);
+  // The activation's derivative at the first layer's result (IEEE half: what the backward pass multiplies by; when nothing
+  // is recorded it is scratch) and the activation's result as bfloat16 only, each two per 32-bit word of an integer tensor:
+  // nothing but the backward epilogue reads the first, nothing but the second product the other.
+  Tensor pre = Tensor::Create(DType::I32, Shape{rows, ff / 2});
   Tensor act16 = Tensor::Create(DType::I32, Shape{rows, ff / 2});
+  ActivationScope::Track(pre);
   ActivationScope::Track(act16);
-  Check(om_linear_fwd_bf16_actd(C(), xc.Bf16(), w1c.Bf16(), b1c.Data(), rows, inF, ff, op, pre.Data(), (uint16_t*)act16.RawData(), ff));
+  Check(om_linear_fwd_bf16_actd(C(), xc.Bf16(), w1c.Bf16(), b1c.Data(), rows, inF, ff, op, (uint16_t*)pre.RawData(), (uint16_t*)act16.RawData(), ff));
   Tensor r = NewOut(os);
   Check(om_linear_fwd_bf16(C(), (const uint16_t*)act16.RawData(), w2c.Bf16(), b2c.Data(), rows, ff, outF, r.Data(), outF));
   if (!Recording({&x, &w1, &b1, &w2, &b2})) return r;
@@ -414,7 +414,7 @@ Tensor Ops::FeedForward(const Tensor& x, const Tensor& w1, const Tensor& b1, con
   rec->Save(0, xc.Detach());
   rec->Save(1, w1c.Detach());
   rec->Save(2, w2c.Detach());
-  rec->Save(3, pre.Detach());
+  rec->Save(3, pre);
   rec->Save(4, act16);
   rec->Ints = {rows, inF, ff, outF, op};
   return rec->Attach(r);

@@ -76,6 +76,29 @@ def round_bf16(x):
     return y
 
 
+def colsum_bf16(g):
+    """The bias gradient g^T 1 of the bfloat16 tier in the order the device adds it (include/onemodel_b200.h,
+    om_colsum_bf16): g [rows, cols] is rounded to bfloat16; in every chunk of 512 rows, lane l adds rows l, l + 32, ... in
+    fp32 in increasing order; the 32 lane sums, then the chunks, are added in double in increasing order. (The reference
+    sums a bias gradient in one fp32 pass, Ops.cs ReduceToShape; the order here is this library's own.)"""
+    g = round_bf16(np.ascontiguousarray(g, np.float32)).reshape(-1, g.shape[-1])
+    rows, cols = g.shape
+    total = np.zeros(cols, np.float64)
+    for r0 in range(0, rows, 512):
+        chunk = np.zeros((512, cols), np.float32)
+        n = min(512, rows - r0)
+        chunk[:n] = g[r0:r0 + n]
+        chunk = chunk.reshape(16, 32, cols)          # [round, lane, column]: row = lane + 32 * round
+        lanes = np.zeros((32, cols), np.float32)
+        for u in range(16):
+            lanes = lanes + chunk[u]
+        part = np.zeros(cols, np.float64)
+        for lane in range(32):
+            part += lanes[lane].astype(np.float64)
+        total += part
+    return total.astype(np.float32)
+
+
 def round_tf32(x, nearest=True):
     x = _f(x)
     y = np.empty_like(x)

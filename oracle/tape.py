@@ -252,13 +252,13 @@ def linear(x, w, b=None):
 
 def _bias_add(y, b):
     """The Add(bias) of Ops.Linear under bfloat16 products: the bias gradient is the product g^T 1 and reads the same
-    bfloat16 copy of the output gradient as the weight gradient g^T x (summed in double, as the column sum does)."""
+    bfloat16 copy of the output gradient as the weight gradient g^T x (summed in the column sum's order)."""
     def bw(r, g):
         out = []
         if r.inputs[0] is not None:
             out.append((0, g, "shared" if r.inputs[1] is not None else "own"))
         if r.inputs[1] is not None:
-            out.append((1, K.round_bf16(np.ascontiguousarray(g)).astype(np.float64).sum(axis=0).astype(np.float32), "own"))
+            out.append((1, K.colsum_bf16(g.reshape(-1, g.shape[-1])), "own"))
         return out
 
     return _attach((y.v + b.v).astype(np.float32), Record("add", [y, b], backward=bw), [y, b])

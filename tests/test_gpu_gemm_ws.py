@@ -227,8 +227,9 @@ def test_shapes_that_cannot_take_the_activation_are_refused(ctx):
 @pytest.mark.parametrize("flags", [0, omb.OM_TF32 | omb.OM_BF16_OPERANDS])
 def test_feed_forward_op_equals_its_three_parts(ctx, flags):
     """The host mirror's FeedForward (Linear -> Gelu -> Linear with the activation in the epilogues under bfloat16 products)
-    against the composition of the three ops on the same flags: result and all five gradients bit for bit, with the input
-    also feeding a residual sum so that its gradient arrives from two branches."""
+    against the composition of the three ops on the same flags: the result and the second layer's gradients bit for bit, the
+    gradients behind the activation bit for bit under fp32 products and within the half rounding of the stored derivative
+    under bfloat16 ones, with the input also feeding a residual sum so that its gradient arrives from two branches."""
     ctx.set_flags(flags)
     ctx.make_current()
     try:
@@ -252,7 +253,12 @@ def test_feed_forward_op_equals_its_three_parts(ctx, flags):
         names = ["y", "dx", "dw1", "db1", "dw2", "db2"]     # the bias gradients too: both read the bfloat16 gradient
         for name, a, b in zip(names, *results):
             assert np.all(np.isfinite(a)), name
-            assert np.array_equal(a, b), (name, float(np.max(np.abs(a - b))), float(np.max(np.abs(b))))
+            if flags and name in ("dx", "dw1", "db1"):
+                # behind the activation's derivative, which the fused forward pass keeps as IEEE half (relative 2^-12): a
+                # fraction of the bfloat16 roundings of the gradient in front of the activation fall the other way
+                assert np.max(np.abs(a - b)) <= 2e-3 * np.max(np.abs(b)), (name, float(np.max(np.abs(a - b))), float(np.max(np.abs(b))))
+            else:
+                assert np.array_equal(a, b), (name, float(np.max(np.abs(a - b))), float(np.max(np.abs(b))))
     finally:
         ctx.set_flags(0)
 
@@ -303,23 +309,25 @@ def test_input_gradient_added_to_a_residual_out_of_place(ctx, rows, outf, inf):
 
 @pytest.mark.parametrize("rows,cols,ld", [(16384, 768, 768), (1000, 520, 528), (513, 70, 72), (1, 8, 8), (4096, 3072, 3072)])
 def test_column_sums_of_a_bf16_matrix(ctx, oracle_built, rows, cols, ld):
-    """om_colsum_bf16 against the double sum of the same bfloat16 values: the rounding of the result to fp32 is all that is left
-    (the partition into chunks of 512 rows and 32 lanes only reorders exact double additions here), with accumulation into the
-    destination, the pitch columns ignored, and the same bits from run to run."""
+    """om_colsum_bf16 against the oracle's restatement of its order (16 rows per lane in fp32, lanes and chunks of 512 rows in
+    double): the same bits, and within fp32 rounding of the plain double sum; with accumulation into the destination, the pitch
+    columns ignored, and the same bits from run to run."""
     K = oracle_built
     r = np.random.default_rng(rows + cols)
     g = np.zeros((rows, ld), np.float32)
     g[:, :cols] = r.standard_normal((rows, cols))
     g[:, cols:] = 1e6                                     # pitch columns must not be read into the sums
     G16 = to_bf16(ctx, g)
-    want = K.round_bf16(g[:, :cols]).astype(np.float64).sum(0)
+    want = K.colsum_bf16(g[:, :cols])
+    plain = K.round_bf16(g[:, :cols]).astype(np.float64).sum(0)
+    assert np.max(np.abs(want - plain)) <= 4e-6 * np.sqrt(rows) + 1e-6 * np.max(np.abs(plain))
     before = r.standard_normal(cols).astype(np.float32)
     OUT, ACC = ctx.empty((cols,)), ctx.to_device(before)
     ctx.call("om_colsum_bf16", ctx.handle, G16.ptr, i32(rows), i32(cols), i32(ld), OUT.ptr, i32(0))
     ctx.call("om_colsum_bf16", ctx.handle, G16.ptr, i32(rows), i32(cols), i32(ld), ACC.ptr, i32(1))
     ctx.sync()
-    assert np.array_equal(OUT.numpy(), want.astype(np.float32))
-    assert np.array_equal(ACC.numpy(), before + want.astype(np.float32))
+    assert np.array_equal(OUT.numpy(), want)
+    assert np.array_equal(ACC.numpy(), before + want)
     again = ctx.empty((cols,))
     ctx.call("om_colsum_bf16", ctx.handle, G16.ptr, i32(rows), i32(cols), i32(ld), again.ptr, i32(0))
     ctx.sync()
@@ -339,7 +347,7 @@ def test_linear_gradients_from_the_bf16_gradient_alone(ctx, oracle_built):
     DB = ctx.empty((outf,))
     ctx.call("om_linear_bwd_bf16_b16", ctx.handle, G16.ptr, None, i32(outf), X16.ptr, W16.ptr, i32(rows), i32(inf), i32(outf), None, None, None, DB.ptr, i32(0))
     ctx.sync()
-    assert np.array_equal(DB.numpy(), K.round_bf16(g).astype(np.float64).sum(0).astype(np.float32))
+    assert np.array_equal(DB.numpy(), K.colsum_bf16(g))
     # the activation's derivative into a bfloat16-only result: the layer has `outf` inputs here (the width of the activation)
     op = omb.UNARY["gelu_erf"]
     g2 = r.standard_normal((rows, inf)).astype(np.float32)
@@ -356,34 +364,41 @@ def test_linear_gradients_from_the_bf16_gradient_alone(ctx, oracle_built):
 
 @pytest.mark.parametrize("op", [omb.UNARY["gelu_erf"], omb.UNARY["gelu_tanh"]])
 @pytest.mark.parametrize("rows,inf,outf", [(4096, 768, 3072), (300, 136, 264)])
-def test_derivative_left_behind_by_the_forward_epilogue(ctx, rows, inf, outf, op):
+def test_derivative_left_behind_by_the_forward_epilogue(ctx, oracle_built, rows, inf, outf, op):
     """om_linear_fwd_bf16_actd / om_linear_dgrad_bf16_mul against om_linear_fwd_bf16_act / om_linear_dgrad_bf16_act: the same
-    bfloat16 activation; the derivative equals op' applied to the separately computed result; the input gradient multiplied
-    by the stored derivative has the same bits as the one that evaluates the derivative in its own epilogue."""
+    bfloat16 activation; the derivative equals op' applied to the separately computed result, rounded to IEEE half; the input
+    gradient is the plain product (factor one) times that half value in one fp32 multiplication, which stays within the half
+    rounding of the gradient that evaluates the derivative in its own epilogue."""
+    K = oracle_built
     r = np.random.default_rng(rows + inf + 3 * op)
     x, w = r.standard_normal((rows, inf)).astype(np.float32), (r.standard_normal((outf, inf)) * 0.1).astype(np.float32)
     bias = r.standard_normal(outf).astype(np.float32)
     X16, W16, Bv = to_bf16(ctx, x), to_bf16(ctx, w), ctx.to_device(bias)
-    PRE, A16, D, A16D = ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16), ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16)
+    PRE, A16, D, A16D = ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16), ctx.empty((rows, outf), np.uint16), ctx.empty((rows, outf), np.uint16)
     ctx.call("om_linear_fwd_bf16_act", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), i32(op), PRE.ptr, A16.ptr, i32(outf))
     ctx.call("om_linear_fwd_bf16_actd", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), i32(op), D.ptr, A16D.ptr, i32(outf))
     ONES, REF, REF16 = ctx.to_device(np.ones((rows, outf), np.float32)), ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16)
     ctx.call("om_unary_bwd_b16", ctx.handle, i32(op), ONES.ptr, PRE.ptr, REF.ptr, REF16.ptr, i64(rows * outf))
     ctx.sync()
     assert np.array_equal(A16D.numpy(), A16.numpy())
-    assert np.array_equal(D.numpy(), REF.numpy())
+    assert np.array_equal(D.numpy(), REF.numpy().astype(np.float16).view(np.uint16))      # numpy rounds to nearest even too
     # backward through the activation: the layer after it has `outf` inputs and `inf` outputs
     g, w2 = r.standard_normal((rows, inf)).astype(np.float32), (r.standard_normal((inf, outf)) * 0.1).astype(np.float32)
     G16, W216 = to_bf16(ctx, g), to_bf16(ctx, w2)
     DX, DX16, M, M16 = ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16), ctx.empty((rows, outf)), ctx.empty((rows, outf), np.uint16)
     ctx.call("om_linear_dgrad_bf16_act", ctx.handle, G16.ptr, i32(inf), W216.ptr, i32(rows), i32(outf), i32(inf), i32(op), PRE.ptr, i32(outf), DX.ptr, DX16.ptr)
     ctx.call("om_linear_dgrad_bf16_mul", ctx.handle, G16.ptr, i32(inf), W216.ptr, i32(rows), i32(outf), i32(inf), D.ptr, i32(outf), M.ptr, M16.ptr)
-    ONLY16 = ctx.empty((rows, outf), np.uint16)
+    ONLY16, RAW = ctx.empty((rows, outf), np.uint16), ctx.empty((rows, outf))
     ctx.call("om_linear_dgrad_bf16_mul", ctx.handle, G16.ptr, i32(inf), W216.ptr, i32(rows), i32(outf), i32(inf), D.ptr, i32(outf), None, ONLY16.ptr)
+    HALF_ONES = ctx.to_device(np.full((rows, outf), 0x3C00, np.uint16))
+    ctx.call("om_linear_dgrad_bf16_mul", ctx.handle, G16.ptr, i32(inf), W216.ptr, i32(rows), i32(outf), i32(inf), HALF_ONES.ptr, i32(outf), RAW.ptr, None)
     ctx.sync()
-    assert np.array_equal(M.numpy(), DX.numpy())
-    assert np.array_equal(M16.numpy(), DX16.numpy())
-    assert np.array_equal(ONLY16.numpy(), DX16.numpy())
+    want = RAW.numpy() * D.numpy().view(np.float16).astype(np.float32)
+    assert np.array_equal(M.numpy(), want)
+    assert np.array_equal(M16.numpy(), (K.round_bf16(want).view(np.uint32) >> 16).astype(np.uint16))
+    assert np.array_equal(ONLY16.numpy(), M16.numpy())
+    assert np.all(np.abs(M.numpy() - DX.numpy()) <= 5e-4 * np.abs(DX.numpy()) + 1e-7 * np.abs(RAW.numpy()))
+    assert np.any(M.numpy() != 0)
 
 
 def test_forward_product_with_the_bf16_result_alone(ctx):
