@@ -158,31 +158,45 @@ attention_dots_kernel(const float* __restrict__ g, const float* __restrict__ out
   }
 }
 
-// dQ[b, q, h, :] = sum over key tiles of the parts, in increasing order; four columns per thread, eight parts in flight.
+// dQ[b, q, h, :] = sum over key tiles of the parts, in increasing order. CTA (x, bh) takes 512 groups of four columns of
+// one (batch, head); a thread owns two of them and has four parts of each in flight. No division per element: the head
+// is the CTA's y index and a row of 64 columns is 16 groups.
 __global__ void __launch_bounds__(256)
-attention_dq_reduce_kernel(const float* __restrict__ parts, int nk, long long part_stride, int heads, int lq, long long n4, float* __restrict__ dq,
+attention_dq_reduce_kernel(const float* __restrict__ parts, int nk, long long part_stride, int heads, int lq, float* __restrict__ dq,
                            uint16_t* __restrict__ dq16, long long dq_batch, long long dq_head, long long dq_row) {
   pdl_enter();
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j0 = 0; j0 < nk; j0 += 8) {
-      float4 v[8];
+  const int bh = blockIdx.y, bi = bh / heads, hi = bh - bi * heads;
+  const int per_head = lq * (AB_D / 4);
+  const float4* src = reinterpret_cast<const float4*>(parts) + (long long)bh * per_head;
+  const long long part4 = part_stride / 4;
+  const long long obase = bi * dq_batch + hi * dq_head;
+  int t[2];
+  t[0] = blockIdx.x * 512 + threadIdx.x;
+  t[1] = t[0] + 256;
+  float4 acc[2];
+  acc[0] = acc[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j0 = 0; j0 < nk; j0 += 4) {
+    float4 v[2][4];
 #pragma unroll
-      for (int u = 0; u < 8; u++)
-        if (j0 + u < nk) v[u] = __ldcs(reinterpret_cast<const float4*>(parts + (long long)(j0 + u) * part_stride) + i);
+    for (int e = 0; e < 2; e++)
 #pragma unroll
-      for (int u = 0; u < 8; u++)
-        if (j0 + u < nk) {
-          if (j0 + u == 0) acc = v[u];
-          else { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+      for (int u = 0; u < 4; u++)
+        if (t[e] < per_head && j0 + u < nk) v[e][u] = __ldcs(src + (long long)(j0 + u) * part4 + t[e]);
+#pragma unroll
+    for (int e = 0; e < 2; e++)
+#pragma unroll
+      for (int u = 0; u < 4; u++)
+        if (t[e] < per_head && j0 + u < nk) {
+          if (j0 + u == 0) acc[e] = v[e][u];
+          else { acc[e].x += v[e][u].x; acc[e].y += v[e][u].y; acc[e].z += v[e][u].z; acc[e].w += v[e][u].w; }
         }
-    }
-    const long long row = i >> 4, c = (i & 15) * 4;        // 16 groups of four columns per row of 64
-    const long long bh = row / lq, q = row % lq, bi = bh / heads, hi = bh % heads;
-    const long long o = bi * dq_batch + hi * dq_head + q * dq_row + c;
-    if (dq) *reinterpret_cast<float4*>(dq + o) = acc;
-    if (dq16) *reinterpret_cast<uint2*>(dq16 + o) = make_uint2(ab_pack(acc.x, acc.y), ab_pack(acc.z, acc.w));
+  }
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    if (t[e] >= per_head) continue;
+    const long long o = obase + (long long)(t[e] >> 4) * dq_row + (t[e] & 15) * 4;
+    if (dq) *reinterpret_cast<float4*>(dq + o) = acc[e];
+    if (dq16) *reinterpret_cast<uint2*>(dq16 + o) = make_uint2(ab_pack(acc[e].x, acc[e].y), ab_pack(acc[e].z, acc[e].w));
   }
 }
 
@@ -583,8 +597,8 @@ int32_t om_attention_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, 
   }
   launch_chained(ctx, attention_bwd16_kernel, dim3((unsigned)nk, (unsigned)bh), AB_THREADS, smem, mq, mk, mv, mg, mparts, mdk, mdk16, mdv, mdv16, p);
   if (dq || dq16) {
-    const long long n4 = rows * (AB_D / 4);
-    launch_chained(ctx, attention_dq_reduce_kernel, grid_for(ctx, n4, 256), 256, 0, (const float*)parts, nk, rows * AB_D, (int)h, (int)lq, n4, dq, dq16,
+    const dim3 grid((unsigned)ceil_div((long long)lq * (AB_D / 4), 512), (unsigned)bh);
+    launch_chained(ctx, attention_dq_reduce_kernel, grid, 256, 0, (const float*)parts, nk, rows * AB_D, (int)h, (int)lq, dq, dq16,
                    (long long)dqs->batch, (long long)dqs->head, (long long)dqs->row);
   }
   pool_free(ctx, parts);
