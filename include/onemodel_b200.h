@@ -717,6 +717,37 @@ int32_t om_optim_sparse_adam_step(om_ctx* ctx, float* p, const float* g, float* 
 int32_t om_optim_sparse_sgd_step(om_ctx* ctx, float* p, const float* g, const int32_t* touched, int32_t rows,
                                  int32_t width, float lr);
 
+/* The row-sparse table gradient as an object of its own (RowSparseGradient.cs:14-120 of the reference): rows[k], k <
+ * *row_count, are the looked-up row numbers in strictly ascending order, each once (the padding row is absent), and
+ * values[k, 0..dim) is the gradient of row rows[k]: the sum of the output gradients g[pos, :] of the row's lookups in
+ * increasing position order starting from zero (EmbeddingSparseBackward, BackwardNn.cs:548-600), which are the bits of the
+ * dense gradient's row. rows, values and row_count are device memory; the count is not read back by any entry point, so the
+ * calls can be captured in a graph. The arrays have `capacity` entries, at least min(n, v); the entries behind the count
+ * are row -1 with zero values, so values can be scaled or normed as a plain [capacity, dim] tensor (gradient clipping,
+ * Schedules.cs:33). An id outside [0, v) sets OM_ERR_INDEX as in om_embedding_bwd. */
+int32_t om_embedding_bwd_sparse(om_ctx* ctx, const float* g, const void* ids, int32_t id_dtype, int64_t n, int32_t v,
+                                int32_t dim, int64_t padding_index, int32_t* rows, float* values, int32_t capacity,
+                                int32_t* row_count);
+/* dense[rows[k], :] += values[k, :] for k < *row_count (RowSparseGradient.AddTo, :47-63; ToDense is this into zeros).
+ * dense is [v, dim]. */
+int32_t om_rowsparse_add_to(om_ctx* ctx, const int32_t* rows, const float* values, const int32_t* row_count,
+                            int32_t capacity, int32_t dim, float* dense, int32_t v);
+/* a + b (RowSparseGradient.Merge, :66-116): the union of the rows in ascending order; a row in both gets a's values plus
+ * b's (a first), a row in one gets that one's values (b's added to zero). The result needs capacity
+ * min(capacity_a + capacity_b, v). */
+int32_t om_rowsparse_merge(om_ctx* ctx, const int32_t* rows_a, const float* values_a, const int32_t* count_a,
+                           int32_t capacity_a, const int32_t* rows_b, const float* values_b, const int32_t* count_b,
+                           int32_t capacity_b, int32_t v, int32_t dim, int32_t* rows_out, float* values_out,
+                           int32_t capacity_out, int32_t* count_out);
+/* SparseAdam.UpdateSparse / Sgd.UpdateSparse (Optimizers.cs:696-722, 377-397) from such a row list: the arithmetic of the
+ * two entry points above on the listed rows only, so the table has the same bits as when it is updated from the
+ * dense-format gradient with touched counts. p, m, v are [table_rows, width]. */
+int32_t om_optim_sparse_adam_step_rows(om_ctx* ctx, float* p, const int32_t* rows, const float* values,
+                                       const int32_t* row_count, int32_t capacity, float* m, float* v, int32_t table_rows,
+                                       int32_t width, float beta1, float beta2, float eps, float step_size);
+int32_t om_optim_sparse_sgd_step_rows(om_ctx* ctx, float* p, const int32_t* rows, const float* values,
+                                      const int32_t* row_count, int32_t capacity, int32_t table_rows, int32_t width, float lr);
+
 /* ---- data parallel ---------------------------------------------------------------------------------------- */
 
 /* The reference is single-process; these have no counterpart there. One rank per process and GPU.

@@ -317,6 +317,51 @@ __global__ void sparse_sgd_kernel(float* __restrict__ p, const float* __restrict
   }
 }
 
+// The same two updates from a row list (the row-sparse gradient of om_embedding_bwd_sparse: rows[k] ascending, values[k, :],
+// the count on the device): one warp per listed row, the same rounding sequence as above, so a table updated from the row
+// list has the bits of one updated from the dense-format gradient.
+__global__ void sparse_adam_rows_kernel(float* __restrict__ p, const int32_t* __restrict__ rows, const float* __restrict__ g,
+                                        const int32_t* __restrict__ row_count, int32_t capacity, float* __restrict__ m, float* __restrict__ v,
+                                        int32_t table_rows, int32_t width, float b1, float b2, float eps, float step_size, int32_t* status) {
+  const int lane = threadIdx.x & 31;
+  const float omb1 = __fsub_rn(1.f, b1), omb2 = __fsub_rn(1.f, b2);
+  int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int n = min(*row_count, capacity);
+  for (int64_t k = warp; k < n; k += warps) {
+    const int r = rows[k];
+    if (r < 0 || r >= table_rows) {
+      if (lane == 0 && atomicCAS(status, 0, (int32_t)OM_ERR_INDEX) == 0) status[1] = (int32_t)k;
+      continue;
+    }
+    const int64_t o = (int64_t)r * width, s = k * width;
+    for (int j = lane; j < width; j += 32) {
+      float gi = g[s + j];
+      float mi = __fadd_rn(__fmul_rn(b1, m[o + j]), __fmul_rn(omb1, gi));
+      float vi = __fadd_rn(__fmul_rn(b2, v[o + j]), __fmul_rn(__fmul_rn(omb2, gi), gi));
+      m[o + j] = mi;
+      v[o + j] = vi;
+      p[o + j] = __fsub_rn(p[o + j], __fdiv_rn(__fmul_rn(step_size, mi), __fadd_rn(__fsqrt_rn(vi), eps)));
+    }
+  }
+}
+
+__global__ void sparse_sgd_rows_kernel(float* __restrict__ p, const int32_t* __restrict__ rows, const float* __restrict__ g,
+                                       const int32_t* __restrict__ row_count, int32_t capacity, int32_t table_rows, int32_t width, float lr,
+                                       int32_t* status) {
+  const int lane = threadIdx.x & 31;
+  int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int n = min(*row_count, capacity);
+  for (int64_t k = warp; k < n; k += warps) {
+    const int r = rows[k];
+    if (r < 0 || r >= table_rows) {
+      if (lane == 0 && atomicCAS(status, 0, (int32_t)OM_ERR_INDEX) == 0) status[1] = (int32_t)k;
+      continue;
+    }
+    const int64_t o = (int64_t)r * width, s = k * width;
+    for (int j = lane; j < width; j += 32) p[o + j] = __fsub_rn(p[o + j], __fmul_rn(lr, g[s + j]));
+  }
+}
+
 }  // namespace om
 
 using namespace om;
@@ -453,6 +498,33 @@ int32_t om_optim_sparse_sgd_step(om_ctx* ctx, float* p, const float* g, const in
   ProfileScope prof(ctx, "om_optim_sparse_sgd_step", 0, 4.0 * rows);
   sparse_sgd_kernel<<<grid_for(ctx, (int64_t)rows * 32, 256), 256, 0, ctx->stream>>>(p, g, touched, rows, width, lr);
   OM_LAUNCH_CHECK(ctx, "om_optim_sparse_sgd_step");
+  return OM_OK;
+}
+
+int32_t om_optim_sparse_adam_step_rows(om_ctx* ctx, float* p, const int32_t* rows, const float* values, const int32_t* row_count,
+                                       int32_t capacity, float* m, float* v, int32_t table_rows, int32_t width, float beta1, float beta2,
+                                       float eps, float step_size) {
+  OM_CHECK_CTX(ctx);
+  if (table_rows < 0 || width < 0 || capacity < 0) return fail(ctx, OM_ERR_SHAPE, "SparseAdam parameters must be rank 2 ([rows, width]) tables.");
+  if (!rows || !values || !row_count) return fail(ctx, OM_ERR_ARG, "om_optim_sparse_adam_step_rows: the row list is needed");
+  if (table_rows == 0 || width == 0 || capacity == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_optim_sparse_adam_step", 0, 28.0 * capacity * width);
+  sparse_adam_rows_kernel<<<grid_for(ctx, (int64_t)capacity * 32, 256), 256, 0, ctx->stream>>>(p, rows, values, row_count, capacity, m, v, table_rows,
+                                                                                              width, beta1, beta2, eps, step_size, ctx->status_dev);
+  OM_LAUNCH_CHECK(ctx, "om_optim_sparse_adam_step_rows");
+  return OM_OK;
+}
+
+int32_t om_optim_sparse_sgd_step_rows(om_ctx* ctx, float* p, const int32_t* rows, const float* values, const int32_t* row_count, int32_t capacity,
+                                      int32_t table_rows, int32_t width, float lr) {
+  OM_CHECK_CTX(ctx);
+  if (table_rows < 0 || width < 0 || capacity < 0) return fail(ctx, OM_ERR_SHAPE, "Sparse Sgd parameters must be rank 2 ([rows, width]) tables.");
+  if (!rows || !values || !row_count) return fail(ctx, OM_ERR_ARG, "om_optim_sparse_sgd_step_rows: the row list is needed");
+  if (table_rows == 0 || width == 0 || capacity == 0) return OM_OK;
+  ProfileScope prof(ctx, "om_optim_sparse_sgd_step", 0, 12.0 * capacity * width);
+  sparse_sgd_rows_kernel<<<grid_for(ctx, (int64_t)capacity * 32, 256), 256, 0, ctx->stream>>>(p, rows, values, row_count, capacity, table_rows, width, lr,
+                                                                                             ctx->status_dev);
+  OM_LAUNCH_CHECK(ctx, "om_optim_sparse_sgd_step_rows");
   return OM_OK;
 }
 

@@ -86,14 +86,17 @@ void Backprop::Run(const Tensor& root, const Tensor* gradient, bool retainGraph)
   engine.Execute(meta->GradFn, g, retainGraph);
 }
 
+// A row-sparse gradient is freed instead of zeroed: zero is the absence of rows (Engine.cs:75-90).
 void Backprop::ZeroGrad(const Tensor& leaf) {
   auto& m = leaf.Autograd();
+  if (m) m->SparseGrad.reset();
   if (m && !m->Grad.IsEmpty()) m->GradIsZero = true;
 }
 
 void Backprop::ClearGrad(const Tensor& leaf) {
   auto& m = leaf.Autograd();
   if (m) {
+    m->SparseGrad.reset();
     m->Grad = Tensor();
     m->GradIsZero = false;
   }
@@ -203,8 +206,38 @@ void Engine::Emit(BackwardRecord& rec, int i, const Tensor& grad, bool owned) {
   }
 }
 
+void Engine::EmitSparse(BackwardRecord& rec, int i, std::shared_ptr<RowSparseGradient> grad) {
+  AutogradMeta* meta = rec.Inputs[i].get();
+  if (!meta) return;
+  if (meta->GradFn) {
+    // The table is itself computed (not a leaf): later operations want a dense gradient.
+    Emit(rec, i, grad->ToDense(), true);
+    return;
+  }
+  if (!meta->RequiresGrad) return;
+  if (!meta->Grad.IsEmpty()) {
+    if (meta->GradIsZero) {
+      meta->Grad.Fill(0.f);
+      meta->GradIsZero = false;
+    }
+    grad->AddTo(meta->Grad);
+  } else if (!meta->SparseGrad) {
+    meta->SparseGrad = std::move(grad);
+  } else {
+    meta->SparseGrad = RowSparseGradient::Merge(*meta->SparseGrad, *grad);
+  }
+  leaf_arrived(meta);
+}
+
 void Engine::AccumulateLeaf(AutogradMeta& leaf, const Tensor& grad, bool owned) {
   if (!leaf.RequiresGrad) return;
+  if (leaf.SparseGrad) {
+    // A dense gradient arrives for a leaf that already has a sparse one (a table used by a lookup and by something
+    // else): go dense (Engine.cs:305-311).
+    leaf.Grad = leaf.SparseGrad->ToDense();
+    leaf.GradIsZero = false;
+    leaf.SparseGrad.reset();
+  }
   if (leaf.Grad.IsEmpty()) {
     // A view (aliased gradient) must not be adopted: the leaf's gradient outlives the step.
     leaf.Grad = (owned && grad.IsContiguous() && grad.Offset() == 0) ? grad.Detach() : grad.Clone();
@@ -273,6 +306,48 @@ void Engine::AddInto(const Tensor& dst, const Tensor& src) {
   Tensor s = src.Contiguous();
   Check(om_add_into(Device::Current(), dst.Data(), s.Data(), dst.Length()));
   dst.MarkModified();
+}
+
+// ---- RowSparseGradient (RowSparseGradient.cs:14-120) --------------------------------------------------------------------
+int RowSparseGradient::RowCount() const {
+  int32_t n = 0;
+  count_.CopyToHost(&n);
+  return n;
+}
+
+std::vector<int32_t> RowSparseGradient::Rows() const {
+  const int n = RowCount();
+  std::vector<int32_t> all((size_t)Capacity());
+  rows_.CopyToHost(all.data());
+  all.resize((size_t)n);
+  return all;
+}
+
+Tensor RowSparseGradient::Values() const { return values_.Slice(0, 0, RowCount()); }
+
+void RowSparseGradient::AddTo(const Tensor& dense) const {
+  if (dense.GetDType() != DType::F32 || dense.GetShape() != dense_shape_ || !dense.IsContiguous())
+    throw TensorShapeException("A row-sparse gradient of a " + dense_shape_.ToString() + " table cannot be added to " + dense.GetShape().ToString() + ".");
+  Check(om_rowsparse_add_to(Device::Current(), (const int32_t*)rows_.RawData(), values_.Data(), (const int32_t*)count_.RawData(), Capacity(),
+                            dense_shape_[1], dense.Data(), dense_shape_[0]));
+  dense.MarkModified();
+}
+
+Tensor RowSparseGradient::ToDense() const {
+  Tensor dense = Tensor::Zeros(DType::F32, dense_shape_);
+  AddTo(dense);
+  return dense;
+}
+
+std::shared_ptr<RowSparseGradient> RowSparseGradient::Merge(const RowSparseGradient& a, const RowSparseGradient& b) {
+  if (a.dense_shape_ != b.dense_shape_) throw TensorShapeException("Row-sparse gradients of different tables cannot be merged.");
+  const int v = a.dense_shape_[0], width = a.dense_shape_[1];
+  const int cap = (int)std::min<int64_t>((int64_t)a.Capacity() + b.Capacity(), v);
+  Tensor rows = Tensor::Create(DType::I32, Shape{cap}), values = Tensor::Create(DType::F32, Shape{cap, width}), count = Tensor::Create(DType::I32, Shape{1});
+  Check(om_rowsparse_merge(Device::Current(), (const int32_t*)a.rows_.RawData(), a.values_.Data(), (const int32_t*)a.count_.RawData(), a.Capacity(),
+                           (const int32_t*)b.rows_.RawData(), b.values_.Data(), (const int32_t*)b.count_.RawData(), b.Capacity(), v, width,
+                           (int32_t*)rows.RawData(), values.Data(), cap, (int32_t*)count.RawData()));
+  return std::make_shared<RowSparseGradient>(a.dense_shape_, rows, values, count);
 }
 
 }  // namespace omh

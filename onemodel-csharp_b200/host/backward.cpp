@@ -466,9 +466,27 @@ static void BatchNormBackward(BackwardRecord& r, const Tensor& g) {
   EmitNormParams(r, tg, tb, gleaf, bleaf);
 }
 
+// Row-sparse table gradient (EmbeddingSparseBackward, BackwardNn.cs:548-600): the looked-up rows in ascending order and, for
+// each, the sum of its lookups' output gradients in increasing position order from zero - the dense gradient's rows bit for
+// bit. The row count stays on the device; a lookup of nothing but padding leaves a gradient without rows, which
+// Tensor::SparseGrad reports as none.
+static void EmbeddingSparseBackward(BackwardRecord& r, const Tensor& g, const Tensor& ids, const Shape& ts) {
+  if (ids.Length() == 0) return;
+  Tensor gc = g.Contiguous();
+  const int cap = (int)std::min<int64_t>(ids.Length(), ts[0]);
+  Tensor rows = Tensor::Create(DType::I32, Shape{cap}), values = Tensor::Create(DType::F32, Shape{cap, ts[1]}), count = Tensor::Create(DType::I32, Shape{1});
+  Check(om_embedding_bwd_sparse(C(), gc.Data(), ids.RawData(), (int32_t)ids.GetDType(), ids.Length(), ts[0], ts[1], r.Ints[0], (int32_t*)rows.RawData(),
+                                values.Data(), cap, (int32_t*)count.RawData()));
+  Engine::EmitSparse(r, 0, std::make_shared<RowSparseGradient>(ts, rows, values, count));
+}
+
 static void EmbeddingBackward(BackwardRecord& r, const Tensor& g) {
   const Tensor& ids = r.Saved(0);
   const Shape& ts = r.InputShapes[0];
+  if (r.Ints.size() > 1 && r.Ints[1] != 0 && r.Inputs[0] && !r.Inputs[0]->GradFn) {
+    EmbeddingSparseBackward(r, g, ids, ts);
+    return;
+  }
   Tensor gc = g.Contiguous();
   float* dt = nullptr;
   bool acc = false;

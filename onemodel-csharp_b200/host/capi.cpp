@@ -1,6 +1,6 @@
 // Plain-C surface of the host mirror (libonemodel_b200_host.so), used by the Python tests and the bench through
 // ctypes: tensors are opaque handles, operations are dispatched by name, and every C++ exception becomes a status
-// code (1 shape, 2 index, 9 invalid operation, 11 a saved tensor changed in place, 10 other) with the message kept for omh_last_error.
+// code (1 shape, 2 index, 9 invalid operation, 11 a saved tensor changed in place, 12 not supported, 10 other) with the message kept for omh_last_error.
 #include <stdio.h>
 #include <string.h>
 
@@ -31,6 +31,9 @@ static int32_t Guard(F&& f) {
   } catch (const InvalidOperationException& e) {
     t_error = e.what();
     return 9;
+  } catch (const NotSupportedException& e) {
+    t_error = e.what();
+    return 12;
   } catch (const BackendException& e) {
     t_error = e.what();
     return 100 + e.status;
@@ -119,6 +122,34 @@ OMH_API int32_t omh_tensor_grad(const omh_tensor* h, omh_tensor** out) {
   return Guard([&] { *out = Box(h->t.Grad()); });
 }
 
+// The leaf's row-sparse gradient (Tensor.SparseGrad): *row_count = 0 and null handles when there is none; otherwise the row
+// count, the row numbers (Int32 [row_count]) and the values (float32 [row_count, width], a view of the gradient's storage).
+OMH_API int32_t omh_tensor_sparse_grad(const omh_tensor* h, int32_t* row_count, omh_tensor** rows, omh_tensor** values) {
+  return Guard([&] {
+    *row_count = 0;
+    *rows = *values = nullptr;
+    auto sg = h->t.SparseGrad();
+    if (!sg) return;
+    *row_count = sg->RowCount();
+    *rows = Box(sg->RowsStorage().Slice(0, 0, *row_count));
+    *values = Box(sg->Values());
+  });
+}
+// RowSparseGradient.ToDense (add_to null: a new tensor in *out) or AddTo (dense[row] += values[k] into add_to). Merge has no
+// entry of its own: it runs when two sparse lookups of one table meet in a backward pass.
+OMH_API int32_t omh_tensor_sparse_grad_to_dense(const omh_tensor* h, omh_tensor* add_to, omh_tensor** out) {
+  return Guard([&] {
+    auto sg = h->t.SparseGrad();
+    if (!sg) throw InvalidOperationException("The tensor has no row-sparse gradient.");
+    if (add_to) {
+      sg->AddTo(add_to->t);
+      if (out) *out = nullptr;
+    } else {
+      *out = Box(sg->ToDense());
+    }
+  });
+}
+
 OMH_API int32_t omh_tensor_zero_grad(const omh_tensor* h) {
   return Guard([&] { Backprop::ZeroGrad(h->t); });
 }
@@ -175,7 +206,7 @@ OMH_API int32_t omh_call(const char* op, int32_t n_in, omh_tensor* const* in, in
     else if (name == "layer_norm") r = Ops::LayerNorm(T(0), T(1), T(2), (float)F(0, 1e-5));
     else if (name == "add_layer_norm") r = Ops::AddLayerNorm(T(0), T(1), T(2), T(3), (float)F(0, 1e-5));
     else if (name == "batch_norm2d") r = Ops::BatchNorm2d(T(0), T(1), T(2), T(3), T(4), I(0) != 0, (float)F(0, 0.1), (float)F(1, 1e-5));
-    else if (name == "embedding") r = Ops::Embedding(T(0), T(1), (int)I(0, -1));
+    else if (name == "embedding") r = Ops::Embedding(T(0), T(1), (int)I(0, -1), I(1, 0) != 0);
     else if (name == "nll_loss") r = Ops::NllLoss(T(0), T(1), I(0, 1) != 0, (int)I(1, -100));
     else if (name == "cross_entropy") r = Ops::CrossEntropy(T(0), T(1), I(0, 1) != 0, (int)I(1, -100), (float)F(0, 0));
     else if (name == "cross_entropy_smoothed") r = Losses::CrossEntropy(T(0), T(1), (float)F(0, 0), (int)I(1, -100), I(0, 1) != 0);
@@ -246,7 +277,7 @@ OMH_API int32_t omh_call(const char* op, int32_t n_in, omh_tensor* const* in, in
 struct omh_optim { std::unique_ptr<Optimizer> o; };
 
 // kind: 0 SGD (f: lr, momentum, dampening, weight_decay; i: nesterov), 1 Adam, 2 AdamW (f: lr, beta1, beta2, eps,
-// weight_decay; i: amsgrad).
+// weight_decay; i: amsgrad), 3 SparseAdam (f: lr, beta1, beta2, eps).
 OMH_API int32_t omh_optim_create(int32_t kind, int32_t n, omh_tensor* const* params, const double* f, const int64_t* i,
                                  omh_optim** out) {
   return Guard([&] {
@@ -256,6 +287,7 @@ OMH_API int32_t omh_optim_create(int32_t kind, int32_t n, omh_tensor* const* par
     if (kind == 0) o.reset(new Sgd(ps, (float)f[0], (float)f[1], (float)f[2], (float)f[3], i[0] != 0));
     else if (kind == 1) o.reset(new Adam(ps, (float)f[0], (float)f[1], (float)f[2], (float)f[3], (float)f[4], false, i[0] != 0));
     else if (kind == 2) o.reset(new AdamW(ps, (float)f[0], (float)f[1], (float)f[2], (float)f[3], (float)f[4], i[0] != 0));
+    else if (kind == 3) o.reset(new SparseAdam(ps, (float)f[0], (float)f[1], (float)f[2], (float)f[3]));
     else throw InvalidOperationException("Unknown optimizer kind.");
     *out = new omh_optim{std::move(o)};
   });
@@ -294,7 +326,7 @@ OMH_API int32_t omh_clip_value(int32_t n, omh_tensor* const* params, float clip)
 //   linear [in, out, bias]; conv1d [in, out, kernel, stride, padding, dilation, groups, bias]; conv1d_same / conv1d_valid
 //   [in, out, kernel, dilation, groups, bias]; conv2d [in, out, kernel, stride, padding, bias]; conv_transpose2d [in, out,
 //   kernel, stride, padding, output padding, dilation, groups, bias]; batch_norm2d [channels] {momentum, eps}; layer_norm
-//   [width] {eps}; embedding [count, width, padding index]; dropout [seed] {p}; recurrent [gru, input, hidden, layers,
+//   [width] {eps}; embedding [count, width, padding index, sparse]; dropout [seed] {p}; recurrent [gru, input, hidden, layers,
 //   bidirectional, batch first]; relu, sigmoid, tanh, flatten,
 //   global_avg_pool2d []; gelu [tanh form]; max_pool2d / avg_pool2d [kernel, stride, padding]; mean [axis].
 // The generator state (SplitMix64, Generator.cs:10-48) is passed in and out so that several modules draw their initial
@@ -317,7 +349,7 @@ OMH_API int32_t omh_module_create(const char* kind, uint64_t* generator_state, i
       m = new ConvTranspose2d((int)I(0), (int)I(1), (int)I(2), g, (int)I(3, 1), (int)I(4, 0), (int)I(5, 0), (int)I(6, 1), (int)I(7, 1), I(8, 1) != 0);
     else if (k == "batch_norm2d") m = new BatchNorm2d((int)I(0), (float)F(0, 0.1), (float)F(1, 1e-5));
     else if (k == "layer_norm") m = new LayerNorm((int)I(0), (float)F(0, 1e-5));
-    else if (k == "embedding") m = new Embedding((int)I(0), (int)I(1), g, (int)I(2, -1));
+    else if (k == "embedding") m = new Embedding((int)I(0), (int)I(1), g, (int)I(2, -1), I(3, 0) != 0);
     else if (k == "dropout") m = new Dropout((float)F(0, 0.5), (uint64_t)I(0));
     else if (k == "recurrent") m = new Recurrent(I(0) != 0, (int)I(1), (int)I(2), g, (int)I(3, 1), I(4) != 0, I(5) != 0);
     else if (k == "relu") m = Lambda::Relu();

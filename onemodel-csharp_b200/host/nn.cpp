@@ -182,7 +182,7 @@ LayerNorm::LayerNorm(int width, float eps) : Epsilon(eps) {
 }
 
 // Embedding rows are uniform in [-1, 1) (Layers.cs:268-313).
-Embedding::Embedding(int count, int width, Generator& g, int paddingIndex) : PaddingIndex(paddingIndex) {
+Embedding::Embedding(int count, int width, Generator& g, int paddingIndex, bool sparse) : PaddingIndex(paddingIndex), IsSparse(sparse) {
   Weight = RegisterParameter("weight", InitUniform(g, 1.0f, Shape{count, width}));
 }
 

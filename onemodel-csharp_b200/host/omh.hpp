@@ -26,6 +26,7 @@ namespace omh {
 struct TensorShapeException : std::runtime_error { using std::runtime_error::runtime_error; };
 struct ArgumentOutOfRangeException : std::runtime_error { using std::runtime_error::runtime_error; };
 struct InvalidOperationException : std::runtime_error { using std::runtime_error::runtime_error; };
+struct NotSupportedException : std::runtime_error { using std::runtime_error::runtime_error; };
 // A tensor saved for the backward pass was modified in place before the pass read it (Autograd.cs:188-192).
 struct TensorVersionException : InvalidOperationException { using InvalidOperationException::InvalidOperationException; };
 struct BackendException : std::runtime_error {
@@ -86,6 +87,7 @@ struct Buffer {
 struct BackwardRecord;
 struct AutogradMeta;
 class Tensor;
+class RowSparseGradient;
 
 // ---- tensor ------------------------------------------------------------------------------------------------------------
 class Tensor {
@@ -154,6 +156,9 @@ class Tensor {
   bool RequiresGrad() const;
   Tensor& SetRequiresGrad(bool on = true);
   Tensor Grad() const;
+  // The row-sparse gradient a sparse Embedding lookup left on this leaf (Tensor.cs:408), or null: none, or one without rows
+  // (nothing but padding was looked up). Reads the row count from the device.
+  std::shared_ptr<RowSparseGradient> SparseGrad() const;
   void Backward(const Tensor* gradient = nullptr, bool retainGraph = false) const;
   const std::shared_ptr<AutogradMeta>& Autograd() const { return meta_; }
   Tensor WithAutograd(std::shared_ptr<AutogradMeta> m) const;
@@ -193,7 +198,37 @@ struct AutogradMeta {
   // The gradient buffer is kept across steps; after ZeroGrad its contents are logically zero and are overwritten by
   // the first gradient that arrives instead of being zero-filled and then added to.
   bool GradIsZero = false;
+  // Set instead of Grad by a sparse Embedding lookup on a leaf table (Autograd.cs:128).
+  std::shared_ptr<RowSparseGradient> SparseGrad;
   bool IsLeaf() const { return !GradFn; }
+};
+
+// The gradient of a [rows, width] table that touches only some rows (RowSparseGradient.cs:14-120): the touched row numbers in
+// ascending order, each once, and their gradients, row k of the values belonging to Rows()[k]; the values are the dense
+// gradient's rows bit for bit. The arrays live on the device with a fixed capacity and a device-side row count (entries
+// behind the count: row -1, zero values), so backward, clipping and the optimizers never read the count back; RowCount(),
+// Rows() and Values() do.
+class RowSparseGradient {
+ public:
+  RowSparseGradient(const Shape& denseShape, Tensor rows, Tensor values, Tensor count)
+      : dense_shape_(denseShape), rows_(std::move(rows)), values_(std::move(values)), count_(std::move(count)) {}
+  const Shape& DenseShape() const { return dense_shape_; }
+  int Capacity() const { return rows_.GetShape()[0]; }
+  int RowCount() const;                   // synchronises
+  std::vector<int32_t> Rows() const;      // strictly ascending, each in [0, rows); synchronises
+  Tensor Values() const;                  // float32 [RowCount, width], a view: writable (gradient clipping scales it); synchronises
+  const Tensor& RowsStorage() const { return rows_; }      // Int32 [capacity]
+  const Tensor& ValuesStorage() const { return values_; }  // float32 [capacity, width], zero behind the row count
+  const Tensor& CountStorage() const { return count_; }    // Int32 [1]
+  int64_t ByteCount() const { return (int64_t)RowCount() * (dense_shape_[1] * 4 + 4); }
+  Tensor ToDense() const;                 // a new zeroed dense tensor with the rows scattered into it
+  void AddTo(const Tensor& dense) const;  // dense[row] += values[k]
+  // a + b: the union of the rows; a row in both gets a's values plus b's (a first).
+  static std::shared_ptr<RowSparseGradient> Merge(const RowSparseGradient& a, const RowSparseGradient& b);
+
+ private:
+  Shape dense_shape_;
+  Tensor rows_, values_, count_;
 };
 
 struct BackwardRecord : std::enable_shared_from_this<BackwardRecord> {
@@ -268,6 +303,10 @@ class Engine {
   // The gradient the running record received is shared with another record (see BackwardRecord::PendingShared).
   bool CurrentShared() const { return current_shared_; }
   static void AccumulateLeaf(AutogradMeta& leaf, const Tensor& grad, bool owned);
+  // Sends a row-sparse gradient to input i, a table the record gathered rows from (Engine.EmitSparse, Engine.cs:252-290): a
+  // computed table gets it as a dense gradient; a leaf that already holds a dense gradient has it added in; otherwise it
+  // becomes (or is merged into) the leaf's SparseGrad.
+  static void EmitSparse(BackwardRecord& rec, int i, std::shared_ptr<RowSparseGradient> grad);
   // If input i is a leaf that keeps a gradient buffer, returns that buffer and whether the kernel must add to it
   // (accumulate) or overwrite it; the caller then calls LeafWritten instead of Emit.
   static bool LeafTarget(BackwardRecord& rec, int i, float** ptr, bool* accumulate);
@@ -335,7 +374,9 @@ struct Ops {
   static Tensor AvgPool2d(const Tensor& x, int kh, int kw, int sh, int sw, int ph = 0, int pw = 0, bool countIncludePad = false);
   static Tensor GlobalAvgPool2d(const Tensor& x);
   static Tensor Concat(const std::vector<Tensor>& xs, int axis);
-  static Tensor Embedding(const Tensor& table, const Tensor& ids, int paddingIndex = -1);
+  // sparse: when the table is a gradient leaf, backward leaves Tensor::SparseGrad (only the looked-up rows) instead of a
+  // dense gradient (Ops.Layers.cs:554).
+  static Tensor Embedding(const Tensor& table, const Tensor& ids, int paddingIndex = -1, bool sparse = false);
   static Tensor NllLoss(const Tensor& logProbs, const Tensor& targets, bool mean = true, int ignoreIndex = -100);
   static Tensor CrossEntropy(const Tensor& logits, const Tensor& targets, bool mean = true, int ignoreIndex = -100,
                              float denominator = 0.f);
@@ -475,8 +516,10 @@ struct Dropout : NnModule {
 struct Embedding : NnModule {
   Tensor Weight;
   int PaddingIndex;
-  Embedding(int count, int width, Generator& g, int paddingIndex = -1);
-  Tensor Forward(const Tensor& ids) override { return Ops::Embedding(Weight, ids, PaddingIndex); }
+  // sparse: backward produces a row-sparse gradient (use with Sgd without momentum or SparseAdam; Layers.cs:276-294).
+  bool IsSparse;
+  Embedding(int count, int width, Generator& g, int paddingIndex = -1, bool sparse = false);
+  Tensor Forward(const Tensor& ids) override { return Ops::Embedding(Weight, ids, PaddingIndex, IsSparse); }
 };
 struct Conv2d : NnModule {
   Tensor Weight, Bias;
@@ -632,6 +675,9 @@ class Optimizer {
   virtual std::vector<StateEntry> NamedState() = 0;
  protected:
   virtual void BeginStep() {}
+  // The update of parameter `index` from a row-sparse gradient (Optimizer.UpdateSparse, Optimizers.cs:184-219): an
+  // optimizer without sparse semantics throws InvalidOperationException.
+  virtual void UpdateSparse(int index, const Tensor& parameter, const RowSparseGradient& gradient);
   virtual void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) = 0;
   std::vector<Tensor> params_;
   std::vector<int> index_;  // positions in params_ of the tensors of the running Step
@@ -658,6 +704,8 @@ class Sgd : public Optimizer {
   float GradScale = 1.f;
  protected:
   void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) override;
+  // p -= lr * g on the touched rows; NotSupportedException with momentum or weight decay (Optimizers.cs:377-397).
+  void UpdateSparse(int index, const Tensor& parameter, const RowSparseGradient& gradient) override;
  private:
   float momentum_, dampening_;
   bool nesterov_;
@@ -691,6 +739,27 @@ class AdamW : public Adam {
   AdamW(std::vector<Tensor> parameters, float lr = 1e-3f, float beta1 = 0.9f, float beta2 = 0.999f, float eps = 1e-8f,
         float weightDecay = 0.01f, bool amsgrad = false)
       : Adam(std::move(parameters), lr, beta1, beta2, eps, weightDecay, true, amsgrad) {}
+};
+
+// Adam with lazy moments for row-sparse gradients (SparseAdam, Optimizers.cs:625-722): only the rows in a step's gradient have
+// their moments and values updated; moments of untouched rows neither decay nor move; no weight decay, no AMSGrad; the step
+// number is the optimizer's global one. A dense gradient throws InvalidOperationException.
+class SparseAdam : public Optimizer {
+ public:
+  SparseAdam(std::vector<Tensor> parameters, float lr = 1e-3f, float beta1 = 0.9f, float beta2 = 0.999f, float eps = 1e-8f);
+  size_t HyperBytes() const override { return 0; }
+  void FillHyper(void*, int64_t) const override {}
+  std::vector<Tensor> StateTensors() const override;
+  std::string Kind() const override { return "sparseadam"; }
+  std::vector<std::pair<std::string, float>> HyperParameters() const override;
+  std::vector<StateEntry> NamedState() override;
+ protected:
+  void BeginStep() override;
+  void Launch(const std::vector<float*>& p, const std::vector<const float*>& g, const std::vector<int64_t>& len) override;
+  void UpdateSparse(int index, const Tensor& parameter, const RowSparseGradient& gradient) override;
+ private:
+  float beta1_, beta2_, eps_, step_size_ = 0.f;
+  std::vector<Tensor> m_, v_;
 };
 
 struct GradClip {

@@ -285,7 +285,7 @@ Tensor Ops::BatchNorm2d(const Tensor& x, const Tensor& gamma, const Tensor& beta
   return br->Attach(r);
 }
 
-Tensor Ops::Embedding(const Tensor& table, const Tensor& ids, int paddingIndex) {
+Tensor Ops::Embedding(const Tensor& table, const Tensor& ids, int paddingIndex, bool sparse) {
   RequireFloat32(table);
   if (table.Rank() != 2 || (ids.GetDType() != DType::I32 && ids.GetDType() != DType::I64))
     throw TensorShapeException("Embedding needs a [V, D] float32 table and Int32 or Int64 ids.");
@@ -300,7 +300,7 @@ Tensor Ops::Embedding(const Tensor& table, const Tensor& ids, int paddingIndex) 
   if (!Recording({&table})) return r;
   auto rec = BackwardRecord::Create(OpKind::Embedding, 1, {&table});
   rec->Save(0, ic.Detach());
-  rec->Ints = {paddingIndex};
+  rec->Ints = {paddingIndex, sparse ? 1 : 0};
   return rec->Attach(r);
 }
 

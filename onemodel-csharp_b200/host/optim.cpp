@@ -43,7 +43,13 @@ void Optimizer::Bf16CopiesWritten() {
     if (p16_[k]) params_[(size_t)index_[k]].Bf16Written();
 }
 
-// Optimizer.Step (Optimizers.cs:184-219): parameters without a gradient are skipped.
+void Optimizer::UpdateSparse(int index, const Tensor&, const RowSparseGradient&) {
+  throw InvalidOperationException("Parameter " + std::to_string(index) + " has a row-sparse gradient, which this optimizer (" + Kind() +
+                                  ") does not support; use Sgd without momentum or SparseAdam for it.");
+}
+
+// Optimizer.Step (Optimizers.cs:184-219): parameters without a gradient are skipped; one with a row-sparse gradient goes
+// through UpdateSparse.
 void Optimizer::Step() {
   BeginStep();
   std::vector<float*> p;
@@ -53,6 +59,11 @@ void Optimizer::Step() {
   for (size_t i = 0; i < params_.size(); i++) {
     const Tensor& t = params_[i];
     if (!t.RequiresGrad()) continue;
+    if (t.Autograd() && t.Autograd()->SparseGrad) {
+      UpdateSparse((int)i, t, *t.Autograd()->SparseGrad);
+      t.MarkModified();
+      continue;
+    }
     Tensor grad = t.Grad();  // materialises zeros if the step produced no gradient for this parameter
     if (grad.IsEmpty()) continue;
     p.push_back(t.Data());
@@ -77,6 +88,11 @@ void Optimizer::StepGroups(const std::vector<std::vector<int>>& groups, const st
     for (int i : groups[gi]) {
       const Tensor& t = params_[(size_t)i];
       if (!t.RequiresGrad()) continue;
+      if (t.Autograd() && t.Autograd()->SparseGrad) {
+        UpdateSparse(i, t, *t.Autograd()->SparseGrad);
+        t.MarkModified();
+        continue;
+      }
       Tensor grad = t.Grad();
       if (grad.IsEmpty()) continue;
       p.push_back(t.Data());
@@ -146,6 +162,14 @@ void Sgd::Launch(const std::vector<float*>& p, const std::vector<const float*>& 
   }
   Check(om_optim_sgd_step(C(), (int32_t)p.size(), p.data(), g.data(), h.has_momentum ? buf.data() : nullptr,
                           h.has_momentum ? first.data() : nullptr, len.data(), &h, (const om_sgd_hyper*)HyperDevice));
+}
+
+void Sgd::UpdateSparse(int, const Tensor& parameter, const RowSparseGradient& gradient) {
+  if (momentum_ != 0.f || WeightDecay != 0.f)
+    throw NotSupportedException("Sgd supports row-sparse gradients only without momentum and weight decay.");
+  const Shape& ds = gradient.DenseShape();
+  Check(om_optim_sparse_sgd_step_rows(C(), parameter.Data(), (const int32_t*)gradient.RowsStorage().RawData(), gradient.ValuesStorage().Data(),
+                                      (const int32_t*)gradient.CountStorage().RawData(), gradient.Capacity(), ds[0], ds[1], LearningRate));
 }
 
 // ---- Adam -----------------------------------------------------------------------------------------------------------
@@ -221,9 +245,67 @@ void Adam::Launch(const std::vector<float*>& p, const std::vector<const float*>&
                                p16_.size() == p.size() ? p16_.data() : nullptr, len.data(), &h, (const om_adam_hyper*)HyperDevice));
 }
 
+// ---- SparseAdam (Optimizers.cs:625-722) ------------------------------------------------------------------------------
+SparseAdam::SparseAdam(std::vector<Tensor> parameters, float lr, float beta1, float beta2, float eps)
+    : Optimizer(std::move(parameters)), beta1_(beta1), beta2_(beta2), eps_(eps) {
+  LearningRate = lr;
+  if (!(beta1 >= 0.f && beta1 < 1.f) || !(beta2 >= 0.f && beta2 < 1.f)) throw ArgumentOutOfRangeException("Betas must be in [0, 1).");
+  if (!(eps > 0.f) || !std::isfinite(eps)) throw ArgumentOutOfRangeException("Epsilon must be positive and finite.");
+  for (const Tensor& p : params_) {
+    if (p.Rank() != 2) throw std::invalid_argument("SparseAdam parameters must be rank 2 ([rows, width]) tables.");
+    m_.push_back(Tensor::Zeros(DType::F32, p.GetShape()));
+    v_.push_back(Tensor::Zeros(DType::F32, p.GetShape()));
+  }
+}
+
+std::vector<Tensor> SparseAdam::StateTensors() const {
+  std::vector<Tensor> out = m_;
+  out.insert(out.end(), v_.begin(), v_.end());
+  return out;
+}
+std::vector<std::pair<std::string, float>> SparseAdam::HyperParameters() const {
+  return {{"lr", LearningRate}, {"beta1", beta1_}, {"beta2", beta2_}, {"epsilon", eps_}};
+}
+std::vector<Optimizer::StateEntry> SparseAdam::NamedState() {
+  std::vector<StateEntry> out;
+  for (size_t i = 0; i < m_.size(); i++) out.push_back({"exp_avg." + std::to_string(i), m_[i], nullptr});
+  for (size_t i = 0; i < v_.size(); i++) out.push_back({"exp_avg_sq." + std::to_string(i), v_[i], nullptr});
+  return out;
+}
+
+// lr * sqrt(1 - beta2^t) / (1 - beta1^t) in double, rounded once (SparseAdam.BeginStep, Optimizers.cs:684-690).
+void SparseAdam::BeginStep() {
+  const int64_t t = StepCount + 1;
+  const double bc1 = 1.0 - IntPow((double)beta1_, t), bc2 = 1.0 - IntPow((double)beta2_, t);
+  step_size_ = (float)((double)LearningRate * sqrt(bc2) / bc1);
+}
+
+void SparseAdam::Launch(const std::vector<float*>& p, const std::vector<const float*>&, const std::vector<int64_t>&) {
+  if (p.empty()) return;
+  throw InvalidOperationException("SparseAdam got a dense gradient for parameter " + std::to_string(index_.empty() ? 0 : index_[0]) +
+                                  "; it only handles row-sparse gradients (build the Embedding with sparse: true, or use Adam).");
+}
+
+void SparseAdam::UpdateSparse(int index, const Tensor& parameter, const RowSparseGradient& gradient) {
+  const Shape& ds = gradient.DenseShape();
+  Check(om_optim_sparse_adam_step_rows(C(), parameter.Data(), (const int32_t*)gradient.RowsStorage().RawData(), gradient.ValuesStorage().Data(),
+                                       (const int32_t*)gradient.CountStorage().RawData(), gradient.Capacity(), m_[(size_t)index].Data(),
+                                       v_[(size_t)index].Data(), ds[0], ds[1], beta1_, beta2_, eps_, step_size_));
+  m_[(size_t)index].MarkModified();
+  v_[(size_t)index].MarkModified();
+}
+
 // ---- clipping -------------------------------------------------------------------------------------------------------
+// The values of a row-sparse gradient stand in for the gradient, each row counted once (Schedules.cs:33,72,130); the entries
+// behind its row count are zero, so the whole storage is normed and scaled.
 static void CollectGrads(const std::vector<Tensor>& parameters, std::vector<float*>& g, std::vector<int64_t>& len) {
   for (const Tensor& p : parameters) {
+    if (p.Autograd() && p.Autograd()->SparseGrad) {
+      const Tensor& values = p.Autograd()->SparseGrad->ValuesStorage();
+      g.push_back(values.Data());
+      len.push_back(values.Length());
+      continue;
+    }
     Tensor grad = p.Grad();
     if (grad.IsEmpty()) continue;
     g.push_back(grad.Data());

@@ -347,9 +347,10 @@ Tensor& Tensor::SetRequiresGrad(bool on) {
   if (!meta_) meta_ = std::make_shared<AutogradMeta>();
   if (meta_->RequiresGrad == on) return *this;
   meta_->RequiresGrad = on;
-  if (!on) {  // a frozen leaf drops its stored gradient (Tensor.cs:418-452)
+  if (!on) {  // a frozen leaf drops its stored gradient, dense or row-sparse (Tensor.cs:418-452)
     meta_->Grad = Tensor();
     meta_->GradIsZero = false;
+    meta_->SparseGrad.reset();
   }
   return *this;
 }
@@ -361,6 +362,11 @@ Tensor Tensor::Grad() const {
     meta_->GradIsZero = false;
   }
   return meta_->Grad;
+}
+
+std::shared_ptr<RowSparseGradient> Tensor::SparseGrad() const {
+  if (!meta_ || !meta_->SparseGrad || meta_->SparseGrad->RowCount() == 0) return nullptr;
+  return meta_->SparseGrad;
 }
 
 void Tensor::Backward(const Tensor* gradient, bool retainGraph) const { Backprop::Run(*this, gradient, retainGraph); }

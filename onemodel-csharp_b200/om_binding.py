@@ -40,6 +40,14 @@ class TensorVersionError(OmError):
     """A tensor saved for the backward pass was written in place before the pass read it (TensorVersionException)."""
 
 
+class InvalidOperation(OmError):
+    """InvalidOperationException of the reference (an optimizer handed a kind of gradient it does not take, for instance)."""
+
+
+class NotSupported(OmError):
+    """NotSupportedException of the reference (Sgd with momentum or weight decay on a row-sparse gradient)."""
+
+
 _kernel = None
 _host = None
 
@@ -71,8 +79,12 @@ def host_lib():
     return _host
 
 
-def _raise(status, message):
+def _raise(status, message, host=False):
     code = status - 100 if status >= 100 else status
+    if host and status == 9:
+        raise InvalidOperation(code, message)
+    if host and status == 12:
+        raise NotSupported(code, message)
     if code == 1:
         raise ShapeError(code, message)
     if code == 2:
@@ -185,7 +197,7 @@ def _hcheck(st):
     if st != 0:
         buf = C.create_string_buffer(512)
         host_lib().omh_last_error(buf, C.c_size_t(512))
-        _raise(st, buf.value.decode())
+        _raise(st, buf.value.decode(), host=True)
 
 
 class Tensor:
@@ -260,6 +272,13 @@ class Tensor:
         h = C.c_void_p()
         _hcheck(host_lib().omh_tensor_grad(self.h, C.byref(h)))
         return Tensor(h) if h else None
+
+    @property
+    def sparse_grad(self):
+        """The row-sparse gradient a sparse embedding lookup left on this leaf (Tensor.SparseGrad of the reference), or None."""
+        n, rows, values = C.c_int32(), C.c_void_p(), C.c_void_p()
+        _hcheck(host_lib().omh_tensor_sparse_grad(self.h, C.byref(n), C.byref(rows), C.byref(values)))
+        return RowSparseGradient(self, n.value, Tensor(rows), Tensor(values)) if n.value else None
 
     def zero_grad(self):
         _hcheck(host_lib().omh_tensor_zero_grad(self.h))
@@ -339,8 +358,28 @@ class no_grad:
         host_lib().omh_no_grad(i32(0))
 
 
+class RowSparseGradient:
+    """RowSparseGradient of the reference (RowSparseGradient.cs:14-120): `rows` strictly ascending Int32 [row_count], `values`
+    float32 [row_count, width] (a writable view of the gradient's storage), to_dense() and add_to(dense)."""
+
+    def __init__(self, owner, row_count, rows, values):
+        self.owner, self.row_count, self.rows, self.values = owner, row_count, rows, values
+
+    @property
+    def byte_count(self):
+        return self.row_count * (self.values.shape[1] * 4 + 4)
+
+    def to_dense(self):
+        out = C.c_void_p()
+        _hcheck(host_lib().omh_tensor_sparse_grad_to_dense(self.owner.h, None, C.byref(out)))
+        return Tensor(out)
+
+    def add_to(self, dense):
+        _hcheck(host_lib().omh_tensor_sparse_grad_to_dense(self.owner.h, dense.h, None))
+
+
 class Optimizer:
-    """Sgd / Adam / AdamW of RecursiveAI.OneModel.Training (Optimizers.cs)."""
+    """Sgd / Adam / AdamW / SparseAdam of RecursiveAI.OneModel.Training (Optimizers.cs)."""
 
     def __init__(self, kind, params, floats, ints):
         self.params = list(params)
@@ -361,6 +400,10 @@ class Optimizer:
     @staticmethod
     def adamw(params, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, amsgrad=False):
         return Optimizer(2, params, [lr, beta1, beta2, eps, weight_decay], [1 if amsgrad else 0])
+
+    @staticmethod
+    def sparse_adam(params, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8):
+        return Optimizer(3, params, [lr, beta1, beta2, eps], [0])
 
     def step(self):
         _hcheck(host_lib().omh_optim_step(self.h))

@@ -532,6 +532,48 @@ def rows_touched(ids, rows, padding_index=-1):
     return np.bincount(ids, minlength=rows).astype(np.int32)
 
 
+def embedding_bwd_sparse(g, ids, pad=-1):
+    """EmbeddingSparseBackward (BackwardNn.cs:548-600): the (id << 31 | position) keys of the lookups that are not padding,
+    sorted; one entry per distinct id in ascending order, its value the sum of the lookups' gradient rows in increasing
+    position order starting from zero. Returns (rows int32 [U], values float32 [U, dim]); U = 0 when only padding was
+    looked up (the reference then keeps no gradient)."""
+    ids = np.asarray(ids).reshape(-1)
+    g = np.asarray(g, np.float32).reshape(ids.size, -1)
+    keys = sorted((int(t) << 31) | i for i, t in enumerate(ids) if t != pad)
+    rows, values = [], []
+    for key in keys:
+        row, pos = key >> 31, key & 0x7FFFFFFF
+        if not rows or rows[-1] != row:
+            rows.append(row)
+            values.append(np.zeros(g.shape[1], np.float32))
+        values[-1] = values[-1] + g[pos]
+    return np.array(rows, np.int32), (np.stack(values) if values else np.zeros((0, g.shape[1]), np.float32))
+
+
+def rowsparse_to_dense(rows, values, v):
+    """RowSparseGradient.ToDense / AddTo (RowSparseGradient.cs:39-63): dense[rows[k]] += values[k] into zeros."""
+    dense = np.zeros((v, values.shape[1]), np.float32)
+    for k, row in enumerate(rows):
+        dense[row] = dense[row] + values[k]
+    return dense
+
+
+def rowsparse_merge(rows_a, values_a, rows_b, values_b):
+    """RowSparseGradient.Merge (RowSparseGradient.cs:66-116): the union of the rows in ascending order; a row's value is a's
+    (or zero) with b's added to it."""
+    width = values_a.shape[1]
+    at = {int(r): k for k, r in enumerate(rows_a)}
+    bt = {int(r): k for k, r in enumerate(rows_b)}
+    rows = sorted(set(at) | set(bt))
+    values = np.zeros((len(rows), width), np.float32)
+    for k, row in enumerate(rows):
+        if row in at:
+            values[k] = values_a[at[row]]
+        if row in bt:
+            values[k] = values[k] + values_b[bt[row]]
+    return np.array(rows, np.int32), values
+
+
 def int_pow(b, n):
     """Adam.IntPow: binary powering in double (Optimizers.cs:483-499)."""
     r, b = 1.0, float(b)

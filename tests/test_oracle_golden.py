@@ -386,3 +386,41 @@ def test_ctc_greedy_known_answers(oracle_built):
         assert first[0, :k].tolist() == c["greedy"]["first"] and last[0, :k].tolist() == c["greedy"]["last"]
         checked += 1
     assert checked >= 10
+
+
+def test_row_sparse_gradient_restatement_against_the_reference_fixture(oracle_built):
+    """EmbeddingSparseBackward / RowSparseGradient (BackwardNn.cs:548-600, RowSparseGradient.cs:14-120) restated in the oracle,
+    on testdata/training/sparse as SparseAndFrozenTests.cs:251-283 uses it: the rows are strictly ascending without the
+    padding row, the sparse gradient scatters to the dense gradient bit for bit and matches the recorded gradient of step 0
+    within 1e-6; Merge is the union with a's values first."""
+    from oracle import oracle as K, tape as A
+    fx = load_fixture("training", "sparse")
+    emb, hw, hb, ids, y = sparse_case(fx)
+    E, W, Bv = A.T(emb, True), A.T(hw, True), A.T(hb, True)
+    looked = A.embedding(E, ids[0], 0)
+    loss = A.cross_entropy(A.linear(A.mean(looked, 1), W, Bv), y[0])
+    loss.backward()
+    dense = E.grad
+    rows = np.nonzero(K.rows_touched(ids[0], 40, 0))[0].astype(np.int32)
+    # the gradient that reaches the lookup's output: softmax - onehot over the 6 rows, through the head, spread over the
+    # 5 positions of the mean
+    logits = A.linear(A.mean(A.embedding(A.T(emb), ids[0], 0), 1), A.T(hw), A.T(hb)).v
+    p = np.exp(logits - logits.max(1, keepdims=True))
+    p = (p / p.sum(1, keepdims=True)).astype(np.float32)
+    p[np.arange(6), y[0]] -= 1
+    dpooled = (p / np.float32(6)) @ hw
+    up = np.repeat((dpooled / np.float32(5))[:, None, :], 5, axis=1).astype(np.float32)
+    r, v = K.embedding_bwd_sparse(up, ids[0], 0)
+    assert np.array_equal(r, rows) and np.all(np.diff(r) > 0) and 0 not in r and 3 < len(r) < 40
+    assert np.array_equal(K.rowsparse_to_dense(r, v, 40), K.embedding_bwd(up, ids[0], 40, 8, 0))
+    assert scaled_diff(K.rowsparse_to_dense(r, v, 40), fx["out.sgd.grad0"]) <= 1e-6
+    assert scaled_diff(dense, fx["out.sgd.grad0"]) <= 1e-6
+    # Merge: union of two lookups' gradients equals the gradient of the concatenated lookup when the second follows the first
+    r2, v2 = K.embedding_bwd_sparse(up[::-1].copy(), ids[1], 0)
+    mr, mv = K.rowsparse_merge(r, v, r2, v2)
+    assert np.array_equal(mr, np.union1d(r, r2))
+    want = K.rowsparse_to_dense(r, v, 40) + K.rowsparse_to_dense(r2, v2, 40)
+    assert np.array_equal(K.rowsparse_to_dense(mr, mv, 40), want)
+    # nothing but padding: no rows
+    r0, v0 = K.embedding_bwd_sparse(np.ones((3, 8), np.float32), np.zeros(3, np.int64), 0)
+    assert r0.size == 0 and v0.shape == (0, 8)
