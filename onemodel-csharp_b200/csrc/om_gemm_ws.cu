@@ -65,6 +65,7 @@ struct WsParams {
   int kb_per_split;               // k blocks per slice
   const float* bias;
   int accumulate;
+  int shared_c;                   // both k-slices add (cp.reduce .add) into the one zeroed C instead of a workspace slice each
   int c16;                        // also store the bfloat16 copy of every block through map_c16 (never with accumulate)
   int store32;                    // store the fp32 result (0: only the bfloat16 copy leaves the kernel)
   int32_t* status;
@@ -284,7 +285,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t tile_i = 0, stored = 0;
     bool ok = true;
     for (int u = cluster_id; u < units && ok; u += clusters, tile_i++) {
-      const int split = u / tiles, t = u % tiles;
+      const int split = p.shared_c ? 0 : u / tiles, t = u % tiles;
       const int m0 = (2 * (t / p.tiles_n) + (int)rank) * W_BM;
       const int n0 = (t % p.tiles_n) * BN;
       const uint32_t a = tile_i & 1, use = tile_i >> 1;
@@ -685,11 +686,20 @@ int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, 
   p.splits = splits;
   p.status = ctx->status_dev;
   p.store32 = store32 ? 1 : 0;
+  p.shared_c = 0;
   if (!store32 && splits > 1) return fail(ctx, OM_ERR_UNSUPPORTED, "persistent product: a product whose k is split needs its fp32 result (m %d n %d k %d)", m, n, k);
   p.aux = aux;
   p.ld_aux = ld_aux;
   float* workspace = nullptr;
-  if (splits > 1) {
+  // Two slices of k and nothing else to fold in (a weight gradient that overwrites): C is zeroed and both slices add their
+  // tiles into it with the TMA unit's reduction. (0 + a) + b and (0 + b) + a are the same fp32 value, so the result does not
+  // depend on which slice arrives first, and it is the a + b that the slice sum gives; more than two slices would.
+  const bool two_in_place = splits == 2 && !acc && !bias && !C16 && store32 && act == 0;
+  if (two_in_place) {
+    OM_CUDA(ctx, cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)n * 4, (size_t)m, ctx->stream));
+    p.bias = nullptr; p.accumulate = 1; p.shared_c = 1;
+    ok = ws_store_map(&map_c, C, n, m, ldc, 1, 0);
+  } else if (splits > 1) {
     OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)splits * m * n, false, (void**)&workspace));
     p.bias = nullptr; p.accumulate = 0;
     ok = ws_store_map(&map_c, workspace, n, m, n, splits, (long long)m * n);
@@ -720,7 +730,7 @@ int32_t gemm_ws_act(om_ctx* ctx, int elem, int ta, int tb, int m, int n, int k, 
                                             : ws_launch_act<5, OM_GELU_TANH>(ctx, map_a, map_b, map_c, map_c16, p, units);
   else if (elem == 0) st = bn == 256 ? ws_launch<0, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<0, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
   else st = bn == 256 ? ws_launch<1, 256>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units) : ws_launch<1, 128>(ctx, a_mn, b_mn, map_a, map_b, map_c, map_c16, p, units);
-  if (st == OM_OK && splits > 1) splitk_reduce_launch(ctx, workspace, splits, (int64_t)m * n, n, ldc, bias, C, acc);
+  if (st == OM_OK && splits > 1 && !two_in_place) splitk_reduce_launch(ctx, workspace, splits, (int64_t)m * n, n, ldc, bias, C, acc);
   if (workspace) pool_free(ctx, workspace);
   if (st == OM_OK && C16 && !p.c16) st = cast_bf16_rows(ctx, C, C16, m, n, ldc);
   return st;
