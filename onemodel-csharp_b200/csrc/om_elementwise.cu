@@ -46,7 +46,8 @@ __global__ void binary_same_kernel(const float* __restrict__ a, const float* __r
   for (int64_t j = n4 * 4 + i; j < n; j += stride) out[j] = binary_apply(OP, a[j], b[j]);
 }
 
-// out[r, c] = a[r, c] (op) b[c]: the bias-add pattern.
+// out[r, c] = a[r, c] (op) b[c]: the bias-add pattern; also a b that spans several trailing axes (a position table added to
+// every batch element), the trailing axes then counting as one row of `cols` elements.
 template <int OP>
 __global__ void binary_rowb_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
                                    int64_t rows, int32_t cols) {
@@ -60,13 +61,27 @@ __global__ void binary_rowb_kernel(const float* __restrict__ a, const float* __r
     const float4* a4 = reinterpret_cast<const float4*>(a);
     const float4* b4 = reinterpret_cast<const float4*>(b);
     float4* o4 = reinterpret_cast<float4*>(out);
-    for (int64_t j = i; j < n4; j += stride) {
-      float4 x = a4[j], y = b4[j % c4], r;
-      r.x = binary_apply(OP, x.x, y.x);
-      r.y = binary_apply(OP, x.y, y.y);
-      r.z = binary_apply(OP, x.z, y.z);
-      r.w = binary_apply(OP, x.w, y.w);
-      o4[j] = r;
+    if (n4 < (int64_t(1) << 31)) {
+      // 32-bit index arithmetic: the 64-bit remainder costs more than the memory access it addresses.
+      const uint32_t un4 = (uint32_t)n4, uc4 = (uint32_t)c4, ustride = (uint32_t)stride;
+      for (uint32_t j = (uint32_t)i; j < un4; j += ustride) {
+        float4 x = a4[j], y = b4[j % uc4], r;
+        r.x = binary_apply(OP, x.x, y.x);
+        r.y = binary_apply(OP, x.y, y.y);
+        r.z = binary_apply(OP, x.z, y.z);
+        r.w = binary_apply(OP, x.w, y.w);
+        o4[j] = r;
+        if (j + ustride < j) break;   // the next index would wrap
+      }
+    } else {
+      for (int64_t j = i; j < n4; j += stride) {
+        float4 x = a4[j], y = b4[j % c4], r;
+        r.x = binary_apply(OP, x.x, y.x);
+        r.y = binary_apply(OP, x.y, y.y);
+        r.z = binary_apply(OP, x.z, y.z);
+        r.w = binary_apply(OP, x.w, y.w);
+        o4[j] = r;
+      }
     }
   } else {
     for (int64_t j = i; j < total; j += stride) out[j] = binary_apply(OP, a[j], b[j % cols]);
@@ -612,18 +627,24 @@ int32_t om_binary(om_ctx* ctx, int32_t op, int32_t rank, const int32_t* shape, c
   }
   if (n == 0) return OM_OK;
   ProfileScope prof(ctx, "om_binary", 0, 12.0 * n);
-  // Classify: both contiguous at the full shape, or a contiguous and b a broadcast row vector.
+  // Classify: both contiguous at the full shape, or a contiguous and b contiguous over some trailing axes and broadcast
+  // (stride 0) over all the axes in front of them: a row vector, or a table added to every batch element.
   bool a_contig = true, b_contig = true, b_row = rank >= 1;
-  int64_t acc = 1;
+  int64_t acc = 1, b_period = 1;
+  bool in_tail = true;
   for (int ax = rank - 1; ax >= 0; ax--) {
     if (shape[ax] != 1) {
       if (a_strides[ax] != acc) a_contig = false;
       if (b_strides[ax] != acc) b_contig = false;
-      if (ax == rank - 1) { if (b_strides[ax] != 1) b_row = false; }
-      else if (b_strides[ax] != 0) b_row = false;
+      if (in_tail && b_strides[ax] == acc && (ax == rank - 1 || b_strides[ax] != 0)) b_period = acc * shape[ax];
+      else {
+        in_tail = false;
+        if (b_strides[ax] != 0) b_row = false;
+      }
     }
     acc *= shape[ax];
   }
+  if (b_period <= 1 || b_period > INT32_MAX) b_row = false;
   const int threads = 256;
   if (a_contig && b_contig) {
     bool vec = aligned16(a) && aligned16(b) && aligned16(out);
@@ -636,7 +657,7 @@ int32_t om_binary(om_ctx* ctx, int32_t op, int32_t rank, const int32_t* shape, c
       default: launch_chained(ctx, binary_same_kernel<OM_DIV>, grid, threads, 0, a, b, out, n4, n); break;
     }
   } else if (a_contig && b_row && aligned16(a) && aligned16(b) && aligned16(out)) {
-    int32_t cols = shape[rank - 1];
+    int32_t cols = (int32_t)b_period;
     int64_t rows = n / cols;
     int grid = grid_for(ctx, (n + 3) / 4, threads);
     switch (op) {

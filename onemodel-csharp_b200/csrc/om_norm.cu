@@ -49,42 +49,51 @@ layernorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamm
   }
 }
 
-// out[j] = sum over chunks of partial[chunk, j] for one or two tables of double partials. A CTA owns 32 columns; 16
-// chunk lanes each add chunks lane, lane + 16, ... in increasing order, then the lane sums are added in lane order: a
-// fixed order, so the result does not depend on the launch.
-__global__ void __launch_bounds__(512)
+// out[j] = sum over chunks of partial[chunk, j] for one or two tables of double partials. A CTA owns 32 columns; 32
+// chunk lanes each add chunks lane, lane + 32, ... in increasing order (five chunks of each table on their way at a time:
+// the kernel is a chain of memory round trips and nothing else), then the lane sums are added in lane order: a fixed
+// order, so the result does not depend on the launch.
+__global__ void __launch_bounds__(1024)
 column_partials_finish_kernel(const double* __restrict__ pa, const double* __restrict__ pb, int chunks, int32_t cols,
                               float* __restrict__ oa, float* __restrict__ ob, int accumulate) {
   pdl_enter();
-  __shared__ double sa[16][33], sb[16][33];
+  __shared__ double sa[32][33], sb[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int j = blockIdx.x * 32 + tx;
+  const bool wa = pa && oa, wb = pb && ob;
   double ta = 0.0, tb = 0.0;
   if (j < cols) {
-    // Eight loads are issued before the first add: the adds stay in increasing chunk order.
-    if (pa && oa) {
-#pragma unroll 8
-      for (int c = ty; c < chunks; c += 16) ta += pa[(int64_t)c * cols + j];
-    }
-    if (pb && ob) {
-#pragma unroll 8
-      for (int c = ty; c < chunks; c += 16) tb += pb[(int64_t)c * cols + j];
+    for (int c0 = ty; c0 < chunks; c0 += 32 * 5) {
+      double va[5], vb[5];
+#pragma unroll
+      for (int u = 0; u < 5; u++) {
+        const int c = c0 + 32 * u;
+        va[u] = (wa && c < chunks) ? pa[(int64_t)c * cols + j] : 0.0;
+        vb[u] = (wb && c < chunks) ? pb[(int64_t)c * cols + j] : 0.0;
+      }
+#pragma unroll
+      for (int u = 0; u < 5; u++) {
+        if (c0 + 32 * u < chunks) {
+          ta += va[u];
+          tb += vb[u];
+        }
+      }
     }
   }
   sa[ty][tx] = ta;
   sb[ty][tx] = tb;
   __syncthreads();
   if (ty == 0 && j < cols) {
-    if (pa && oa) {
+    if (wa) {
       double t = 0.0;
 #pragma unroll
-      for (int l = 0; l < 16; l++) t += sa[l][tx];
+      for (int l = 0; l < 32; l++) t += sa[l][tx];
       oa[j] = accumulate ? oa[j] + (float)t : (float)t;
     }
-    if (pb && ob) {
+    if (wb) {
       double t = 0.0;
 #pragma unroll
-      for (int l = 0; l < 16; l++) t += sb[l][tx];
+      for (int l = 0; l < 32; l++) t += sb[l][tx];
       ob[j] = accumulate ? ob[j] + (float)t : (float)t;
     }
   }
@@ -694,7 +703,7 @@ int32_t om_layernorm_bwd_b16(om_ctx* ctx, const float* g, const float* x, const 
 #undef OM_LN_BWD
 #undef OM_LN_BWDV
   if (dgamma || dbeta)
-    launch_chained(ctx, column_partials_finish_kernel, (unsigned)ceil_div(cols, 32), 512, 0, pg, pb, used, cols, dgamma, dbeta, accumulate_params);
+    launch_chained(ctx, column_partials_finish_kernel, (unsigned)ceil_div(cols, 32), 1024, 0, pg, pb, used, cols, dgamma, dbeta, accumulate_params);
   if (pg) pool_free(ctx, pg);
   if (pb) pool_free(ctx, pb);
   OM_LAUNCH_CHECK(ctx, "om_layernorm_bwd");
@@ -768,7 +777,7 @@ int32_t om_batchnorm_bwd(om_ctx* ctx, const float* g, const float* x, const floa
     pool_free(ctx, coef);
   }
   if (dgamma || dbeta)
-    launch_chained(ctx, column_partials_finish_kernel, (unsigned)ceil_div(c, 32), 512, 0, pa, pb, slices, c, dgamma, dbeta, accumulate_params);
+    launch_chained(ctx, column_partials_finish_kernel, (unsigned)ceil_div(c, 32), 1024, 0, pa, pb, slices, c, dgamma, dbeta, accumulate_params);
   pool_free(ctx, pa);
   pool_free(ctx, pb);
   OM_LAUNCH_CHECK(ctx, "om_batchnorm_bwd");
