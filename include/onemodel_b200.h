@@ -62,7 +62,8 @@ typedef enum om_status {
  * flag only products with several rounds of tiles over the device do.
  * OM_TWO_STREAMS: a backward entry point whose gradients are independent of one another (om_linear_bwd: the input
  * gradient on one side, the weight and bias gradients on the other) runs them on two streams of the context, forked
- * and joined inside the call, so that products too small to fill the device overlap. Results are the same bits.
+ * and joined inside the call, so that products too small to fill the device overlap; om_linear_bwd_bf16_b16 runs the
+ * bias column sum (bound by memory) beside its products (bound by the tensor pipe). Results are the same bits.
  * OM_SEQ_KERNELS (with OM_TF32): an LSTM layer whose shape fits (hidden a multiple of 16, batch <= 256 for the backward)
  * runs all its time steps in one cooperative launch with fp32 recurrent products, instead of a product and a gate
  * kernel per step. OM_OVERLAP_LAUNCHES: the frequent kernels are launched as programmatic dependents of their

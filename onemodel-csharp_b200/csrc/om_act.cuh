@@ -15,11 +15,13 @@ namespace om {
 // absolute of erf over the whole line, far inside the 2^-9 relative rounding of the bfloat16 copy that follows; exp(-z*z)
 // is handed back for the Gaussian of the derivative. NaN comes back NaN.
 constexpr int OM_GELU_ERF_FAST = 64;
-__device__ __forceinline__ float erf_fast(float z, float* gauss) {
-  const float a = fabsf(z);
+// The argument is x, the value erf(x / sqrt 2): the scaling by 1 / sqrt 2 is folded into the two constants (these run in the
+// epilogues of the feed-forward products, whose time is the number of instructions per element).
+__device__ __forceinline__ float erf_fast(float x, float* gauss) {
+  const float a = fabsf(x);
   float e, u;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"((z * z) * -1.4426950408889634f));
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(u) : "f"(fmaf(a, 0.39f, 1.0f)));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"((x * x) * -0.72134752044448170f));   // exp(-x*x / 2)
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(u) : "f"(fmaf(a, 0.39f * 0.70710678f, 1.0f)));
   float q = -2.275369167e-01f;
   q = fmaf(q, u, 8.866635561e-01f);
   q = fmaf(q, u, -6.353989244e-01f);
@@ -27,11 +29,11 @@ __device__ __forceinline__ float erf_fast(float z, float* gauss) {
   q = fmaf(q, u, 9.138885140e-02f);
   q = fmaf(q, u, 2.353251427e-01f);
   *gauss = e;
-  return copysignf(1.0f - (q * u) * e, z);
+  return copysignf(1.0f - (q * u) * e, x);
 }
 __device__ __forceinline__ float gelu_erf_fast(float x) {
   float e;
-  return (0.5f * x) * (1.0f + erf_fast(x * 0.70710677f, &e));
+  return x * fmaf(0.5f, erf_fast(x, &e), 0.5f);
 }
 __device__ __forceinline__ float gelu_erf(float x) { return (0.5f * x) * (1.0f + erff(x * 0.70710677f)); }
 __device__ __forceinline__ float gelu_tanh(float x) {
@@ -67,10 +69,10 @@ __device__ __forceinline__ float unary_grad(float g, float s) {
     return g * (cdf + s * pdf);
   }
   if (OP == OM_GELU_ERF_FAST) {
-    // exp(-z*z) with z = s / sqrt(2) is the Gaussian exp(-s*s / 2) of the density.
+    // gauss is the Gaussian exp(-s*s / 2) of the density.
     float gauss;
-    float cdf = 0.5f * (1.0f + erf_fast(s * 0.70710677f, &gauss));
-    return g * (cdf + s * (gauss * 0.3989423f));
+    const float cdf = fmaf(0.5f, erf_fast(s, &gauss), 0.5f);
+    return g * fmaf(s * 0.3989423f, gauss, cdf);
   }
   if (OP == OM_GELU_TANH) {
     float u = 0.79788456f * (s + ((0.044715f * s) * s) * s);
@@ -93,9 +95,9 @@ template <int OP>
 __device__ __forceinline__ void unary_both(float x, float* act, float* deriv) {
   if (OP == OM_GELU_ERF_FAST) {
     float gauss;
-    const float erf = erf_fast(x * 0.70710677f, &gauss);
-    *act = (0.5f * x) * (1.0f + erf);
-    *deriv = 1.0f * ((0.5f * (1.0f + erf)) + x * (gauss * 0.3989423f));
+    const float cdf = fmaf(0.5f, erf_fast(x, &gauss), 0.5f);
+    *act = x * cdf;
+    *deriv = fmaf(x * 0.3989423f, gauss, cdf);
   } else {
     *act = unary_apply<OP>(x);
     *deriv = unary_grad<OP>(1.0f, x);

@@ -119,25 +119,35 @@ int32_t om_linear_bwd_bf16_b16(om_ctx* ctx, const uint16_t* g16, const float* g,
     return fail(ctx, OM_ERR_SHAPE, "om_linear_bwd_bf16: rows %d in %d out %d ldg %d", rows, in_features, out_features, ldg);
   if (rows == 0) return OM_OK;
   const double flops = 2.0 * rows * in_features * out_features;
-  if (dx) {
-    // dx[rows, in] = g[rows, out] * W[out, in]
-    OM_TRY(check_args(ctx, "om_linear_bwd_bf16 (input gradient)", rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features));
-    ProfileScope prof(ctx, "om_linear_bwd.dgrad", flops, 2.0 * ((double)rows * out_features + (double)in_features * out_features) + 4.0 * (double)rows * in_features);
-    OM_TRY(gemm_ws(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, (accumulate_w >> 1) & 1, nullptr, dx16));
-  }
-  if (dW) {
-    // dW[out, in] = g[rows, out]^T * x[rows, in]
-    OM_TRY(check_args(ctx, "om_linear_bwd_bf16 (weight gradient)", out_features, in_features, rows, g16, ldg, x, in_features, dW, in_features));
-    ProfileScope prof(ctx, "om_linear_bwd.wgrad", flops, 2.0 * ((double)rows * out_features + (double)rows * in_features) + 4.0 * (double)in_features * out_features);
-    OM_TRY(gemm_ws(ctx, 1, 1, 0, out_features, in_features, rows, g16, ldg, x, in_features, dW, in_features, accumulate_w & 1, nullptr, nullptr));
-  }
+  auto products = [&]() -> int32_t {
+    if (dx) {
+      // dx[rows, in] = g[rows, out] * W[out, in]
+      OM_TRY(check_args(ctx, "om_linear_bwd_bf16 (input gradient)", rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features));
+      ProfileScope prof(ctx, "om_linear_bwd.dgrad", flops, 2.0 * ((double)rows * out_features + (double)in_features * out_features) + 4.0 * (double)rows * in_features);
+      OM_TRY(gemm_ws(ctx, 1, 0, 0, rows, in_features, out_features, g16, ldg, W, in_features, dx, in_features, (accumulate_w >> 1) & 1, nullptr, dx16));
+    }
+    if (dW) {
+      // dW[out, in] = g[rows, out]^T * x[rows, in]
+      OM_TRY(check_args(ctx, "om_linear_bwd_bf16 (weight gradient)", out_features, in_features, rows, g16, ldg, x, in_features, dW, in_features));
+      ProfileScope prof(ctx, "om_linear_bwd.wgrad", flops, 2.0 * ((double)rows * out_features + (double)rows * in_features) + 4.0 * (double)in_features * out_features);
+      OM_TRY(gemm_ws(ctx, 1, 1, 0, out_features, in_features, rows, g16, ldg, x, in_features, dW, in_features, accumulate_w & 1, nullptr, nullptr));
+    }
+    return OM_OK;
+  };
   // The bias gradient g^T 1: from the fp32 gradient when the caller has one, else from the same bfloat16 copy that the weight
   // gradient g^T x reads (half the bytes, and the fp32 gradient need not exist at all).
-  if (dbias) {
-    if (g) OM_TRY(colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w & 1));
-    else OM_TRY(colsum16_ld(ctx, g16, rows, out_features, ldg, dbias, accumulate_w & 1));
-  }
-  return OM_OK;
+  auto bias_sum = [&]() -> int32_t {
+    if (!dbias) return OM_OK;
+    if (g) return colsum_ld(ctx, g, rows, out_features, ldg, dbias, accumulate_w & 1);
+    return colsum16_ld(ctx, g16, rows, out_features, ldg, dbias, accumulate_w & 1);
+  };
+  // With OM_TWO_STREAMS the column sum runs beside the products: they are bound by the tensor pipe and leave most of the
+  // memory bandwidth idle, the sum is bound by memory alone, and a product's CTA leaves room on its SM for one of the sum's.
+  // The products are launched first so that they hold their SMs when the sum's CTAs arrive.
+  const bool fork = (ctx->flags & OM_TWO_STREAMS) && !ctx->profiling && !ctx->aux_active && dbias && (dx || dW) && rows >= 512;
+  if (fork) return run_forked(ctx, products, bias_sum);
+  OM_TRY(products());
+  return bias_sum();
 }
 
 int32_t om_linear_bwd_bf16(om_ctx* ctx, const uint16_t* g16, const float* g, int32_t ldg, const uint16_t* x, const uint16_t* W, int32_t rows,

@@ -299,8 +299,13 @@ static void FeedForwardBackward(BackwardRecord& r, const Tensor& g) {
   Leaf dw1 = target(1), db1 = target(2), dw2 = target(3), db2 = target(4);
   const uint16_t* g16 = gc.Bf16();
   // Second layer: weight and bias gradients, then the input gradient through the activation.
-  if (dw2.p) Check(om_linear_bwd_bf16_b16(C(), g16, nullptr, outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, dw2.p, nullptr, dw2.acc ? 1 : 0));
-  if (db2.p) Check(om_linear_bwd_bf16_b16(C(), g16, nullptr, outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, nullptr, db2.p, db2.acc ? 1 : 0));
+  if (dw2.p && db2.p && dw2.acc == db2.acc) {
+    // one call: with OM_TWO_STREAMS the bias sum then runs beside the weight-gradient product
+    Check(om_linear_bwd_bf16_b16(C(), g16, nullptr, outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, dw2.p, db2.p, dw2.acc ? 1 : 0));
+  } else {
+    if (dw2.p) Check(om_linear_bwd_bf16_b16(C(), g16, nullptr, outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, dw2.p, nullptr, dw2.acc ? 1 : 0));
+    if (db2.p) Check(om_linear_bwd_bf16_b16(C(), g16, nullptr, outF, (const uint16_t*)act16.RawData(), w2.Bf16(), rows, ff, outF, nullptr, nullptr, nullptr, db2.p, db2.acc ? 1 : 0));
+  }
   done(4, db2);
   done(3, dw2);
   if (!dw1.p && !db1.p && !r.NeedsInputGrad(0)) return;

@@ -224,7 +224,17 @@ def test_shapes_that_cannot_take_the_activation_are_refused(ctx):
     ctx.sync()
 
 
-@pytest.mark.parametrize("flags", [0, omb.OM_TF32 | omb.OM_BF16_OPERANDS])
+def one_stream_reference(ctx, xv, vals, up):
+    """The fused feed-forward block with a residual sum, forward and backward, under bfloat16 products on one stream."""
+    ctx.set_flags(omb.OM_TF32 | omb.OM_BF16_OPERANDS)
+    x = omb.Tensor.from_numpy(xv, True)
+    ps = [omb.Tensor.from_numpy(v, True) for v in vals]
+    y = omb.call("add", [x, omb.call("feed_forward", [x] + ps, ints=[0])])
+    y.backward(omb.Tensor.from_numpy(up))
+    return [y.numpy(), x.grad.numpy()] + [p.grad.numpy() for p in ps]
+
+
+@pytest.mark.parametrize("flags", [0, omb.OM_TF32 | omb.OM_BF16_OPERANDS, omb.OM_TF32 | omb.OM_BF16_OPERANDS | omb.OM_TWO_STREAMS])
 def test_feed_forward_op_equals_its_three_parts(ctx, flags):
     """The host mirror's FeedForward (Linear -> Gelu -> Linear with the activation in the epilogues under bfloat16 products)
     against the composition of the three ops on the same flags: the result and the second layer's gradients bit for bit, the
@@ -250,6 +260,11 @@ def test_feed_forward_op_equals_its_three_parts(ctx, flags):
             y = omb.call("add", [x, f])
             y.backward(omb.Tensor.from_numpy(up))
             results.append([y.numpy(), x.grad.numpy()] + [p.grad.numpy() for p in ps])
+        if flags & omb.OM_TWO_STREAMS:
+            # the bias sums ran on the context's second stream beside the products: the same bits as on one stream
+            again = one_stream_reference(ctx, xv, vals, up)
+            for a, b in zip(results[0], again):
+                assert np.array_equal(a, b)
         names = ["y", "dx", "dw1", "db1", "dw2", "db2"]     # the bias gradients too: both read the bfloat16 gradient
         for name, a, b in zip(names, *results):
             assert np.all(np.isfinite(a)), name
