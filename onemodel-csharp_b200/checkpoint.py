@@ -89,7 +89,7 @@ class TrainerState:
     """Adapts a device-resident `om_binding.Trainer` (host/trainer.cpp): every read and write is one device copy."""
 
     _FIXED = {"sgd": ("momentum", "dampening", "nesterov"), "adam": ("beta1", "beta2", "epsilon", "amsgrad"),
-              "adamw": ("beta1", "beta2", "epsilon", "amsgrad")}
+              "adamw": ("beta1", "beta2", "epsilon", "amsgrad"), "sparseadam": ("beta1", "beta2", "epsilon")}
 
     def __init__(self, trainer):
         self.t = trainer
