@@ -428,3 +428,29 @@ def test_forward_product_with_the_bf16_result_alone(ctx):
     ctx.call("om_linear_fwd_bf16_b16", ctx.handle, X16.ptr, W16.ptr, Bv.ptr, i32(rows), i32(inf), i32(outf), None, ONLY.ptr, i32(outf))
     ctx.sync()
     assert np.array_equal(ONLY.numpy(), Y16.numpy()) and np.any(ONLY.numpy() != 0)
+
+
+@pytest.mark.parametrize("rows,inf,outf", [(16384, 768, 3072), (4096, 768, 2304), (16384, 3072, 768), (1000, 264, 520), (700, 768, 768), (16896, 768, 768)])
+def test_bias_and_weight_gradient_in_one_call(ctx, oracle_built, rows, inf, outf):
+    """om_linear_bwd_bf16_b16 asked for dW and dbias at once (no fp32 gradient): the bias gradient has the bits of the oracle's
+    restatement of the column sum's order, with and without accumulation, and the weight gradient the bits of a call that
+    asks for it alone (two-slice and eight-slice shapes, ragged rows, more than 32 chunks of rows)."""
+    K = oracle_built
+    r = np.random.default_rng(rows + outf)
+    g = r.standard_normal((rows, outf)).astype(np.float32)
+    x = r.standard_normal((rows, inf)).astype(np.float32)
+    w = (r.standard_normal((outf, inf)) * 0.05).astype(np.float32)
+    G16, X16, W16 = to_bf16(ctx, g), to_bf16(ctx, x), to_bf16(ctx, w)
+    before = r.standard_normal(outf).astype(np.float32)
+    DW, DB, DW_ALONE, DB_ACC = ctx.empty((outf, inf)), ctx.empty((outf,)), ctx.empty((outf, inf)), ctx.to_device(before)
+    DW_ACC = ctx.zeros((outf, inf))
+    args = (G16.ptr, None, i32(outf), X16.ptr, W16.ptr, i32(rows), i32(inf), i32(outf), None, None)
+    ctx.call("om_linear_bwd_bf16_b16", ctx.handle, *args, DW.ptr, DB.ptr, i32(0))
+    ctx.call("om_linear_bwd_bf16_b16", ctx.handle, *args, DW_ALONE.ptr, None, i32(0))
+    ctx.call("om_linear_bwd_bf16_b16", ctx.handle, *args, DW_ACC.ptr, DB_ACC.ptr, i32(1))
+    ctx.sync()
+    want = K.colsum_bf16(g)
+    assert np.array_equal(DB.numpy(), want)
+    assert np.array_equal(DB_ACC.numpy(), before + want)
+    assert np.array_equal(DW.numpy(), DW_ALONE.numpy()) and np.any(DW.numpy() != 0)
+    assert np.array_equal(DW_ACC.numpy(), DW.numpy())
