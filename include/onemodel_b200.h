@@ -501,6 +501,9 @@ int32_t om_attention_bwd_strided_out(om_ctx* ctx, const float* g, const om_head_
  * bfloat16 product operands, for sequences of several tiles: out = softmax(scale q k^T + mask) v per (batch, head), from the
  * bfloat16 copies of q, k, v. A CTA per (128 queries, batch, head) walks the key tiles twice (row maxima first; then
  * exponentials, their fp32 row sums and the second product with the exponentials rounded to bfloat16), two CTAs per SM.
+ * Without a mask it walks them once where scale |q_i| max_j |k_j| (a bound on row i's scores; the key norms come from a
+ * small kernel in front) is at most 40 for every row of the tile: the exponentials are taken against that bound instead
+ * of the row maximum, which changes neither the normalised result nor the log-sum-exp beyond rounding.
  * out is fp32, out16 (may be NULL) its bfloat16 copy with the same strides, lse (may be NULL) the row log-sum-exp
  * [b * h, lq] that om_attention_bwd_bf16 takes. Built for head dimension 64, any lq and lk, a positive scale, at most 65535
  * (batch, head) pairs (om_attention_fwd_bf16_supported tells); operand strides multiples of 8. */

@@ -8,6 +8,12 @@
 //            and O += P_j V_j accumulates in tensor memory. Nothing is rescaled on the way; the result is O / sum at the
 //            end, with the row log-sum-exp max + log(sum) that the backward needs, and optionally O as bfloat16 (the next
 //            Linear layer's operand).
+// ONE pass where a bound on the scores is at hand: without a mask, scale |q_i| max_j |k_j| bounds every scaled score of row i
+// (Cauchy-Schwarz), so it can stand in for the row maximum: exp(score - bound) <= 1 never overflows, and while the bound is
+// at most 40 it is at least e^-80, far inside fp32 and bfloat16 range; sum, O / sum and the log-sum-exp bound + log(sum) are
+// the same quantities, rounded as before. max_j |k_j|^2 per (batch, head) comes from a small kernel in front
+// (attention_kmax_kernel); a CTA one of whose rows has a larger bound, or that has a mask, walks the key tiles twice as
+// described. The first pass is a third of the two-pass kernel's products and read-backs.
 // The second Q K^T costs tensor-pipe time that the kernel does not lack. A CTA keeps its steps in sequence (product,
 // read-back, exponentials, staging, product) and is sized so that TWO CTAs share an SM (112 KB of shared memory, 256 columns
 // of tensor memory, at most 113 registers per thread): one CTA's products run under the other's exponentials.
@@ -33,6 +39,7 @@ struct AttFwd16Params {
   const float* mask;
   long long mask_batch_stride;
   float* lse;                                    // [B*H, lq] (may be null)
+  const float* kmax2;                            // [B*H] max over the keys of |k|^2, or null: always two passes
   int want16;
   int32_t* status;
 };
@@ -71,6 +78,45 @@ __device__ __forceinline__ void af_tma_store_4d(const CUtensorMap* map, const ui
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
+constexpr float AF_BOUND_LIMIT = 40.f;
+
+// kmax2[b, h] = max over the keys of |k|^2 (fp32 sum of the squares of the bfloat16 values). One CTA per (batch, head).
+__global__ void __launch_bounds__(256)
+attention_kmax_kernel(const uint16_t* __restrict__ k16, long long s_batch, long long s_head, long long s_row, int heads, int lk,
+                      float* __restrict__ kmax2) {
+  pdl_enter();
+  __shared__ float wmax[8];
+  const int bh = blockIdx.x, bi = bh / heads, hi = bh - bi * heads;
+  const uint16_t* base = k16 + bi * s_batch + hi * s_head;
+  float best = 0.f;
+  for (int key = threadIdx.x; key < lk; key += 256) {
+    const uint4* rowp = reinterpret_cast<const uint4*>(base + (long long)key * s_row);
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < AF_D / 8; c++) {
+      const uint4 v = __ldg(rowp + c);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const float lo = __uint_as_float(w[q] << 16), hi2 = __uint_as_float(w[q] & 0xFFFF0000u);
+        ss = fmaf(lo, lo, ss);
+        ss = fmaf(hi2, hi2, ss);
+      }
+    }
+    best = fmaxf(best, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = wmax[0];
+#pragma unroll
+    for (int w = 1; w < 8; w++) t = fmaxf(t, wmax[w]);
+    kmax2[bh] = t;
+  }
+}
+
 __global__ void __launch_bounds__(AF_THREADS, 2)
 attention_fwd16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -85,11 +131,13 @@ attention_fwd16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
            *bar_x = bars + 8;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* two_pass_flag = abort_flag + 1;         // set by a row thread whose bound is too large for the one-pass form
   float* xch = reinterpret_cast<float*>(stage_p);       // [2][128]: the two threads of a row exchange their maximum, later their sum
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int i = blockIdx.x, bh = blockIdx.y, bi = bh / p.heads, hi = bh % p.heads;
-  const int nk = (p.lk + AF_TILE - 1) / AF_TILE, steps = 2 * nk;
+  const int nk = (p.lk + AF_TILE - 1) / AF_TILE;
+  const bool bound_known = p.kmax2 != nullptr && p.mask == nullptr && nk >= 2;   // the same for every thread of the CTA
 
   if ((smem_u32(smem) & 1023u) != 0) {
     // The swizzled tiles need 1024-byte alignment; a base that is not would give wrong products, so refuse.
@@ -107,6 +155,7 @@ attention_fwd16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(bar_done, 1);
     mbar_init(bar_x, 256);
     *abort_flag = 0;
+    *two_pass_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 8) {
@@ -144,8 +193,10 @@ attention_fwd16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       };
       mbar_expect_tx(bar_q, AF_BLOCK);
       tma_load_4d(slot_q, &map_q, 0, i * AF_TILE, hi, bi, bar_q);
+      int steps = 2 * nk;                     // nk when the row threads settle on one pass (known after step 0 is staged)
+      bool one_pass = false;
       load_k(0);
-      if (steps > 1) load_k(1);
+      load_k(1);                              // 2 * nk >= 2 steps, or nk >= 2 of them
       load_v(0);
       if (nk > 1) load_v(1);
       bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, 61) && mbar_wait(&bar_k[0], 0, abort_flag, p.status, 62);
@@ -155,11 +206,15 @@ attention_fwd16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       for (int g = 0; g < steps && ok; g++) {
         const int j = g % nk;
-        const bool second = g >= nk;
         // The row threads have read S of step g out of tensor memory (and, in the second pass, staged P_j).
         ok = mbar_wait(bar_staged, (uint32_t)g & 1, abort_flag, p.status, 63);
         if (!ok) break;
         tc_fence_after();
+        if (g == 0 && bound_known && *two_pass_flag == 0) {
+          one_pass = true;
+          steps = nk;
+        }
+        const bool second = one_pass || g >= nk;
         if (second) {
           ok = mbar_wait(&bar_v[j & 1], (uint32_t)(j >> 1) & 1, abort_flag, p.status, 64);
           if (!ok) break;
@@ -205,9 +260,39 @@ attention_fwd16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       n_meet++;
       return got;
     };
+    // One pass if every row of the tile has a bound on its scores that exponentials can be taken against.
+    bool one_pass = false;
+    if (bound_known) {
+      ok = mbar_wait(bar_q, 0, abort_flag, p.status, 68);
+      if (ok) {
+        // |q|^2 of this row from the swizzled tile (the order of the eight 16-byte chunks does not matter for a sum).
+        const uint8_t* qr = slot_q + (size_t)row * 128;
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+          const uint4 v = *reinterpret_cast<const uint4*>(qr + (((c ^ lane) & 7) << 4));
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            const float lo = __uint_as_float(w[q] << 16), hi2 = __uint_as_float(w[q] & 0xFFFF0000u);
+            ss = fmaf(lo, lo, ss);
+            ss = fmaf(hi2, hi2, ss);
+          }
+        }
+        const float bound = p.scale * sqrtf(ss * p.kmax2[bh]);
+        if (!(bound <= AF_BOUND_LIMIT)) *two_pass_flag = 1;       // also a bound that is not a number
+        ok = meet();
+        if (ok && *two_pass_flag == 0) {
+          one_pass = true;
+          m = bound;
+          m2 = m * LOG2E;
+        }
+      }
+    }
+    const int steps = one_pass ? nk : 2 * nk;
     for (int g = 0; g < steps && ok; g++) {
       const int j = g % nk;
-      const bool second = g >= nk;
+      const bool second = one_pass || g >= nk;
       const bool edge = (j + 1) * AF_TILE > p.lk || p.mask != nullptr;
       ok = mbar_wait(bar_s, (uint32_t)g & 1, abort_flag, p.status, 65);
       if (!ok) break;
@@ -266,7 +351,7 @@ attention_fwd16_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
         }
       }
-      if (g == nk - 1) {
+      if (!one_pass && g == nk - 1) {
         // End of the first pass: the two threads of a row combine their maxima (the staging block is not in use yet).
         xch[hh * AF_TILE + row] = m;
         if (!(ok = meet())) break;
@@ -409,6 +494,14 @@ int32_t om_attention_fwd_bf16(om_ctx* ctx, const uint16_t* q16, const om_head_st
   if (!ok) return fail(ctx, OM_ERR_CUDA, "cuTensorMapEncodeTiled failed for the attention forward");
   AttFwd16Params p;
   p.lq = lq; p.lk = lk; p.heads = h; p.scale = scale; p.mask = mask; p.mask_batch_stride = mask_batch_stride; p.lse = lse;
+  // Without a mask and with several key tiles: the largest key norm per (batch, head), for the one-pass form.
+  float* kmax2 = nullptr;
+  if (!mask && lk > AF_TILE) {
+    OM_TRY(pool_alloc(ctx, sizeof(float) * (size_t)b * h, false, (void**)&kmax2));
+    launch_chained(ctx, attention_kmax_kernel, dim3((unsigned)(b * h)), 256, 0, k16, (long long)ks->batch, (long long)ks->head, (long long)ks->row, (int)h,
+                   (int)lk, kmax2);
+  }
+  p.kmax2 = kmax2;
   p.want16 = out16 ? 1 : 0;
   p.status = ctx->status_dev;
   const size_t smem = (size_t)7 * AF_BLOCK + 128;
@@ -420,6 +513,7 @@ int32_t om_attention_fwd_bf16(om_ctx* ctx, const uint16_t* q16, const om_head_st
   }
   const int nq = (lq + AF_TILE - 1) / AF_TILE;
   launch_chained(ctx, attention_fwd16_kernel, dim3((unsigned)nq, (unsigned)(b * h)), AF_THREADS, smem, mq, mk, mv, mo, mo16, p);
+  if (kmax2) pool_free(ctx, kmax2);
   OM_LAUNCH_CHECK(ctx, "om_attention_fwd_bf16");
   return OM_OK;
 }

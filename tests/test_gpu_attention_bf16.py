@@ -138,6 +138,36 @@ def test_attention_forward_with_bf16_operands(ctx, oracle_built, b, h, lq, lk, m
     assert np.array_equal(got, run(None, None))
 
 
+@pytest.mark.parametrize("gain,lq,lk", [(3.0, 512, 512), (1.9, 300, 384), (0.2, 512, 512)])
+def test_attention_forward_with_large_and_small_scores(ctx, oracle_built, gain, lq, lk):
+    """Without a mask the kernel takes scale |q| max|k| as the bound the exponentials are taken against (one pass over the key
+    tiles) while that bound is at most 40, and walks the key tiles twice for the true row maximum otherwise. q and k scaled
+    so that a tile's bound is around 100 (two passes), around 40 (tiles on either side of the limit in one launch) and
+    around 0.4: the same agreement with the oracle's model and the same log-sum-exp in all three."""
+    K = oracle_built
+    b, h, d = 1, 3, 64
+    r = np.random.default_rng(int(gain * 10) + lq)
+    q, k, v = (r.standard_normal(s).astype(np.float32) for s in [(b, h, lq, d), (b, h, lk, d), (b, h, lk, d)])
+    q, k = q * np.float32(gain), k * np.float32(gain)
+    scale = np.float32(1.0 / np.sqrt(np.float32(d)))
+    Q16, K16, V16 = to_bf16(ctx, q), to_bf16(ctx, k), to_bf16(ctx, v)
+    O, LSE = ctx.empty(q.shape), ctx.empty((b, h, lq))
+    sq, sk = HeadStrides(h * lq * d, lq * d, d), HeadStrides(h * lk * d, lk * d, d)
+    ctx.call("om_attention_fwd_bf16", ctx.handle, Q16.ptr, C.byref(sq), K16.ptr, C.byref(sk), V16.ptr, C.byref(sk), None, i64(0),
+             i32(b), i32(h), i32(lq), i32(lk), i32(d), f32(scale), O.ptr, None, C.byref(sq), LSE.ptr)
+    ctx.sync()
+    got = O.numpy()
+    assert np.all(np.isfinite(got)) and np.all(np.isfinite(LSE.numpy()))
+    assert scaled_diff(got, K.attention_fwd_bf16(q, k, v, None, scale)) <= 4e-3
+    qr, kr = K.round_bf16(q).astype(np.float64), K.round_bf16(k).astype(np.float64)
+    s = np.einsum("bhqd,bhkd->bhqk", qr, kr) * np.float64(scale)
+    mx = s.max(axis=-1, keepdims=True)
+    lse_ref = (mx + np.log(np.exp(s - mx).sum(axis=-1, keepdims=True)))[..., 0]
+    assert np.max(np.abs(LSE.numpy() - lse_ref)) <= 2e-5 * max(1.0, float(np.max(np.abs(lse_ref))))
+    bound = float(scale) * np.linalg.norm(qr, axis=-1).max() * np.linalg.norm(kr, axis=-1).max()
+    assert (bound > 80) if gain == 3.0 else (bound < 2) if gain == 0.2 else (30 < bound < 60)
+
+
 def test_forward_shapes_outside_the_kernel_are_refused(ctx):
     sup = ctx.lib.om_attention_fwd_bf16_supported
     assert sup(ctx.handle, i32(1), i32(1), i32(4096), i32(4096), i32(64), f32(0.125)) == 1
