@@ -107,12 +107,21 @@ __global__ void embedding_bwd_rows_kernel(const float* __restrict__ g, int32_t v
   int lane = threadIdx.x & 31;
   int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  // Rows of 16-byte multiples (every table of the configurations): four columns per lane and access. Each column's sum is
+  // formed in the same order either way.
+  const bool vec = (dim & 3) == 0 && ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(dtable)) & 15) == 0;
   for (int64_t row = warp; row < v; row += warps) {
     int b = count[row];
     float* d = dtable + row * dim;
     if (b == 0) {
-      if (!accumulate)
-        for (int j = lane; j < dim; j += 32) d[j] = 0.f;
+      if (!accumulate) {
+        if (vec) {
+          float4* d4 = reinterpret_cast<float4*>(d);
+          for (int j = lane; j < (dim >> 2); j += 32) d4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+          for (int j = lane; j < dim; j += 32) d[j] = 0.f;
+        }
+      }
       continue;
     }
     const int32_t* bk = bucket + offset[row];
@@ -124,10 +133,22 @@ __global__ void embedding_bwd_rows_kernel(const float* __restrict__ g, int32_t v
       so[rank] = p;
     }
     __syncwarp();
-    for (int j = lane; j < dim; j += 32) {
-      float acc = accumulate ? d[j] : 0.f;
-      for (int e = 0; e < b; e++) acc += g[(int64_t)so[e] * dim + j];
-      d[j] = acc;
+    if (vec) {
+      float4* d4 = reinterpret_cast<float4*>(d);
+      for (int j = lane; j < (dim >> 2); j += 32) {
+        float4 acc = accumulate ? d4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int e = 0; e < b; e++) {
+          const float4 t = reinterpret_cast<const float4*>(g + (int64_t)so[e] * dim)[j];
+          acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+        }
+        d4[j] = acc;
+      }
+    } else {
+      for (int j = lane; j < dim; j += 32) {
+        float acc = accumulate ? d[j] : 0.f;
+        for (int e = 0; e < b; e++) acc += g[(int64_t)so[e] * dim + j];
+        d[j] = acc;
+      }
     }
     __syncwarp();
   }
