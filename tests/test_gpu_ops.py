@@ -230,6 +230,18 @@ def test_embedding_fwd_bwd_bit_exact(ctx, K, dtype):
         ctx.call("om_embedding_bwd", ctx.handle, G.ptr, Id.ptr, i32(dt), i64(n), i32(v), i32(dim), i64(pad), DT.ptr, i32(0))
         assert np.array_equal(DT.numpy(), K.embedding_bwd(g, ids, v, dim, pad))
     ctx.sync()
+    # accumulate: each touched row continues from what the table gradient already holds, in the same position order
+    # (existing + g[p0] + g[p1] + ...); untouched rows keep their values. Also a width that is not a multiple of four.
+    for width in (dim, 7):
+        gw = np.ascontiguousarray(g[:, :width])
+        held = normal(r, v, width)
+        Gw, ACC = ctx.to_device(gw), ctx.to_device(held)
+        ctx.call("om_embedding_bwd", ctx.handle, Gw.ptr, Id.ptr, i32(dt), i64(n), i32(v), i32(width), i64(-1), ACC.ptr, i32(1))
+        ctx.sync()
+        want = held.copy()
+        for p_, t in enumerate(ids):
+            want[t] = want[t] + gw[p_]
+        assert np.array_equal(ACC.numpy(), want)
 
 
 def test_embedding_id_out_of_range(ctx):
