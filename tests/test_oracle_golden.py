@@ -424,3 +424,20 @@ def test_row_sparse_gradient_restatement_against_the_reference_fixture(oracle_bu
     # nothing but padding: no rows
     r0, v0 = K.embedding_bwd_sparse(np.ones((3, 8), np.float32), np.zeros(3, np.int64), 0)
     assert r0.size == 0 and v0.shape == (0, 8)
+
+
+def test_bias_sum_order_of_the_bf16_tier_stays_within_fp32_rounding_of_the_plain_sum(oracle_built):
+    """oracle.colsum_bf16 restates the order in which the device adds a bias gradient from the bfloat16 gradient (16 rows per
+    lane in fp32, lanes and chunks of 512 rows in double). Against the plain double sum of the same rounded values it may
+    differ by the fp32 roundings of the 16-row lane sums only; ragged row counts, one row and exact cases included."""
+    K = oracle_built
+    r = np.random.default_rng(4)
+    for rows, cols in [(16384, 24), (1000, 16), (513, 8), (1, 8), (31, 40)]:
+        g = r.standard_normal((rows, cols)).astype(np.float32)
+        got = K.colsum_bf16(g)
+        plain = K.round_bf16(g).astype(np.float64).sum(0)
+        assert got.dtype == np.float32 and got.shape == (cols,)
+        assert np.max(np.abs(got - plain)) <= 4e-6 * np.sqrt(rows) + 1e-6 * np.max(np.abs(plain))
+    # values whose sums are exact in fp32 (small integers): the order cannot matter, the result is the integer sum
+    ints = r.integers(-8, 9, (2000, 8)).astype(np.float32)
+    assert np.array_equal(K.colsum_bf16(ints), ints.astype(np.float64).sum(0).astype(np.float32))
